@@ -1,0 +1,421 @@
+// Full-attention kernels for the gated GQA layers (fp8 e4m3 paged KV, page = 16 tokens).
+//
+//   owl_qknorm_rope_insert : per-head q/k RMSNorm x(1+w), partial rotate-half RoPE (m-RoPE
+//                            capable: 3 position streams + per-frequency section map), K/V cast to
+//                            e4m3 and scattered into the paged pool, q written as bf16.
+//   owl_paged_attn         : split-KV GQA attention over the paged fp8 pool for decode (T=1),
+//                            verify (T<=8 rows, causal inside the new rows) and prefill chunks
+//                            (issued as groups of <=8 consecutive rows). Tensor-core QK^T and PV
+//                            with fp8 -> f16 conversion in registers; one 16-token page per tile.
+//   owl_attn_reduce        : merges the split partials, applies the sigmoid output gate and
+//                            writes bf16 and/or ActPack for o_proj.
+//
+// Role in the reference: owl_qknorm_rope_kv_insert_* (crates/kernels/cu/fused/qknorm_insert.cu),
+// the XQA / paged-attention-v2 / FlashInfer decode+verify arms (cu/xqa/mha.cu,
+// cu/attn/pagedattention_f16.cu, cu/flashinfer/*) and owl_sigmoid_gate_mul_f16.
+#include "common.cuh"
+#include "actpack.cuh"
+
+namespace owl {
+
+constexpr int PAGE = 16;
+
+// ---------------------------------------------------------------------------------------
+// grid (rows, hq + 2*hkv), block 128. head < hq: q; < hq+hkv: k; else v.
+// qraw row layout: per q head [q_h (hd) | gate_h (hd)]; kraw/vraw: [hkv][hd].
+// ---------------------------------------------------------------------------------------
+struct InsertParams {
+  const __nv_bfloat16* qraw; int ldq;
+  const __nv_bfloat16* kraw; int ldk;
+  const __nv_bfloat16* vraw; int ldv;
+  const __nv_bfloat16* qnorm_w; const __nv_bfloat16* knorm_w;
+  const int* pos3;              // [3][rows] position streams (T,H,W); text rows have all equal
+  const float* inv_freq;        // [rot/2]
+  const unsigned char* section; // [rot/2] stream index per frequency
+  const int* kv_slot;           // [rows] physical token index (page*16 + off); < 0 = skip write
+  __nv_bfloat16* q_out;         // [rows][hq][hd]
+  uint8_t* k_pool; uint8_t* v_pool;  // [pages][16][hkv][hd] e4m3
+  int rows, hq, hkv, hd, rot;
+  float eps, rope_scale;        // rope_scale multiplies cos/sin (YaRN attention factor)
+};
+
+__global__ void __launch_bounds__(128) qknorm_rope_insert_kernel(InsertParams p) {
+  __shared__ float y[256];
+  __shared__ float red[32];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int row = blockIdx.x, head = blockIdx.y, tid = threadIdx.x;
+  const int hd = p.hd;
+  const bool is_q = head < p.hq, is_k = !is_q && head < p.hq + p.hkv;
+  const int kvh = is_q ? 0 : (is_k ? head - p.hq : head - p.hq - p.hkv);
+  const __nv_bfloat16* src = is_q ? p.qraw + (size_t)row * p.ldq + (size_t)head * 2 * hd
+                           : is_k ? p.kraw + (size_t)row * p.ldk + (size_t)kvh * hd
+                                  : p.vraw + (size_t)row * p.ldv + (size_t)kvh * hd;
+  const int e0 = tid * 2;
+  float a = 0.f, b = 0.f;
+  if (e0 < hd) {
+    const uint32_t u = *reinterpret_cast<const uint32_t*>(src + e0);
+    a = bf16_lo(u); b = bf16_hi(u);
+  }
+  if (is_q || is_k) {
+    const float ss = block_sum(a * a + b * b, red);
+    const float rinv = rsqrtf(ss / (float)hd + p.eps);
+    const __nv_bfloat16* w = is_q ? p.qnorm_w : p.knorm_w;
+    if (e0 < hd) {
+      a = a * rinv * (1.f + __bfloat162float(w[e0]));
+      b = b * rinv * (1.f + __bfloat162float(w[e0 + 1]));
+      y[e0] = a; y[e0 + 1] = b;
+    }
+    __syncthreads();
+    const int half = p.rot >> 1;
+    if (e0 < p.rot) {
+      float o[2];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int d = e0 + i;
+        const int j = d < half ? d : d - half;
+        const int pos = p.pos3[(size_t)p.section[j] * p.rows + row];
+        float sn, cs;
+        sincosf((float)pos * p.inv_freq[j], &sn, &cs);
+        sn *= p.rope_scale; cs *= p.rope_scale;
+        o[i] = d < half ? y[d] * cs - y[d + half] * sn : y[d] * cs + y[d - half] * sn;
+      }
+      a = o[0]; b = o[1];
+    }
+  }
+  if (e0 >= hd) return;
+  if (is_q) {
+    *reinterpret_cast<uint32_t*>(p.q_out + ((size_t)row * p.hq + head) * hd + e0) = pack_bf16(a, b);
+  } else {
+    const int slot = p.kv_slot[row];
+    if (slot < 0) return;
+    uint8_t* dst = (is_k ? p.k_pool : p.v_pool) + ((size_t)slot * p.hkv + kvh) * hd + e0;
+    // values are rounded to bf16 first so the pool holds cast(bf16(x)) like a two-step pipeline
+    const float ar = __bfloat162float(__float2bfloat16(a)), br = __bfloat162float(__float2bfloat16(b));
+    *reinterpret_cast<uint16_t*>(dst) = (uint16_t)f_to_fp8e4m3(ar) | ((uint16_t)f_to_fp8e4m3(br) << 8);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Paged attention. grid (splits, hkv, groups); block = 4 warps.
+// A "group" is T consecutive query rows of one sequence; each query row contributes Gq = hq/hkv
+// heads (<= 8) = one MMA row group. Warps = RG row groups x TS token splits (RG*TS = 4).
+// ---------------------------------------------------------------------------------------
+struct AttnParams {
+  const __nv_bfloat16* q;       // [groups*T][hq][hd]
+  const uint8_t* k_pool; const uint8_t* v_pool;
+  const int* block_table;       // [seqs][max_blocks]
+  const int* bt_row;            // [groups] -> block_table row (nullptr: identity)
+  const int* ctx_len;           // [groups] tokens visible to the LAST row of the group
+  float* part_o;                // [groups*T][hq][splits][hd]
+  float* part_ml;               // [groups*T][hq][splits][2]
+  int T, hq, hkv, max_blocks, splits;
+  float scale_log2;             // softmax scale * log2(e)
+};
+
+constexpr int AT_WARPS = 4;
+constexpr int HD = 256;
+
+__device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t two_bytes) {
+  __half2_raw r = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)two_bytes, __NV_E4M3);
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+__device__ __forceinline__ void mma16816(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int RG>
+__global__ void __launch_bounds__(AT_WARPS * 32) paged_attn_kernel(AttnParams p) {
+  constexpr int TS = AT_WARPS / RG;
+  // cross-warp merge buffers (token splits of the same row group)
+  __shared__ float mo[AT_WARPS][8][HD + 1];   // O by [row][dim]
+  __shared__ float mml[AT_WARPS][8][2];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+  const int split = blockIdx.x, kvh = blockIdx.y, grp = blockIdx.z;
+  const int Gq = p.hq / p.hkv;
+  const int rg = warp / TS, ts = warp % TS;  // row group index within the CTA pass, token split
+  pdl_wait();
+  const int ctx_last = p.ctx_len[grp];
+  const int btr = p.bt_row ? p.bt_row[grp] : grp;
+  const int* bt = p.block_table + (size_t)btr * p.max_blocks;
+
+  for (int r0 = 0; r0 < p.T; r0 += RG) {
+    const int r = r0 + rg;                       // query row inside the group
+    const bool row_ok = r < p.T;
+    const int limit = ctx_last - (p.T - 1 - r);  // tokens visible to this row
+    const int npages_all = (ctx_last + PAGE - 1) / PAGE;
+    const int per = (npages_all + p.splits - 1) / p.splits;
+    const int pg0 = split * per, pg1 = min(npages_all, pg0 + per);
+
+    // Q fragments (f16) for k-steps (blk 0..3, j 0..3): dims blk*64 + t*16 + j*4 + {0,1 | 2,3}
+    uint32_t qa0[16], qa2[16];
+    {
+      const size_t qrow = (size_t)grp * p.T + (row_ok ? r : 0);
+      const __nv_bfloat16* qp = p.q + (qrow * p.hq + (size_t)kvh * Gq + g) * HD;
+      const bool head_ok = row_ok && g < Gq;
+#pragma unroll
+      for (int blk = 0; blk < 4; ++blk) {
+        uint4 u0 = make_uint4(0, 0, 0, 0), u1 = u0;
+        if (head_ok) {
+          u0 = *reinterpret_cast<const uint4*>(qp + blk * 64 + t * 16);
+          u1 = *reinterpret_cast<const uint4*>(qp + blk * 64 + t * 16 + 8);
+        }
+        const uint32_t w[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          qa0[blk * 4 + j] = pack_f16(bf16_lo(w[j * 2]), bf16_hi(w[j * 2]));
+          qa2[blk * 4 + j] = pack_f16(bf16_lo(w[j * 2 + 1]), bf16_hi(w[j * 2 + 1]));
+        }
+      }
+    }
+    float m_run = -INFINITY, l_run = 0.f;  // for row g (replicated over t)
+    float o[16][4];                         // O^T m-tiles (blk 0..7, ip 0..1)
+#pragma unroll
+    for (int i = 0; i < 16; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+
+    if (row_ok) {
+      for (int pg = pg0 + ts; pg < pg1; pg += TS) {
+        const int tk0 = pg * PAGE;
+        if (tk0 >= limit) break;
+        const int page = bt[pg];
+        const uint8_t* kp = p.k_pool + (((size_t)page * PAGE) * p.hkv + kvh) * HD;
+        const uint8_t* vp = p.v_pool + (((size_t)page * PAGE) * p.hkv + kvh) * HD;
+        const size_t tstride = (size_t)p.hkv * HD;
+        // ---- S = Q K^T for tokens tk0+g (s0) and tk0+8+g (s1) -----------------------------
+        float s0[4] = {0, 0, 0, 0}, s1[4] = {0, 0, 0, 0};
+        uint4 ka[4], kb[4];
+#pragma unroll
+        for (int blk = 0; blk < 4; ++blk) {
+          ka[blk] = ldg_stream(reinterpret_cast<const uint4*>(kp + (size_t)g * tstride + blk * 64 + t * 16));
+          kb[blk] = ldg_stream(reinterpret_cast<const uint4*>(kp + (size_t)(g + 8) * tstride + blk * 64 + t * 16));
+        }
+        // V words for tokens tk0 + {2t, 2t+1, 2t+8, 2t+9}, dims blk*32 + g*4 .. +3
+        uint32_t va[8], vb[8], vc[8], vd[8];
+#pragma unroll
+        for (int blk = 0; blk < 8; ++blk) {
+          va[blk] = ldg_stream_u32(reinterpret_cast<const uint32_t*>(vp + (size_t)(2 * t) * tstride + blk * 32 + g * 4));
+          vb[blk] = ldg_stream_u32(reinterpret_cast<const uint32_t*>(vp + (size_t)(2 * t + 1) * tstride + blk * 32 + g * 4));
+          vc[blk] = ldg_stream_u32(reinterpret_cast<const uint32_t*>(vp + (size_t)(2 * t + 8) * tstride + blk * 32 + g * 4));
+          vd[blk] = ldg_stream_u32(reinterpret_cast<const uint32_t*>(vp + (size_t)(2 * t + 9) * tstride + blk * 32 + g * 4));
+        }
+#pragma unroll
+        for (int blk = 0; blk < 4; ++blk) {
+          const uint32_t wa[4] = {ka[blk].x, ka[blk].y, ka[blk].z, ka[blk].w};
+          const uint32_t wb[4] = {kb[blk].x, kb[blk].y, kb[blk].z, kb[blk].w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            mma16816(s0, qa0[blk * 4 + j], 0u, qa2[blk * 4 + j], 0u, e4m3x2_to_f16x2(wa[j] & 0xffffu),
+                     e4m3x2_to_f16x2(wa[j] >> 16));
+            mma16816(s1, qa0[blk * 4 + j], 0u, qa2[blk * 4 + j], 0u, e4m3x2_to_f16x2(wb[j] & 0xffffu),
+                     e4m3x2_to_f16x2(wb[j] >> 16));
+          }
+        }
+        // s0[0..1]: (row g, tokens tk0+2t, +1); s1[0..1]: (row g, tokens tk0+8+2t, +1)
+        float sv[4] = {s0[0], s0[1], s1[0], s1[1]};
+        const int tk[4] = {tk0 + 2 * t, tk0 + 2 * t + 1, tk0 + 8 + 2 * t, tk0 + 9 + 2 * t};
+        float mx = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          sv[i] = tk[i] < limit ? sv[i] * p.scale_log2 : -INFINITY;
+          mx = fmaxf(mx, sv[i]);
+        }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run, mx);     // finite: token tk0 < limit is visible
+        const float alpha = exp2f(m_run - m_new);
+        float ps = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { sv[i] = exp2f(sv[i] - m_new); ps += sv[i]; }
+        ps += __shfl_xor_sync(0xffffffffu, ps, 1);
+        ps += __shfl_xor_sync(0xffffffffu, ps, 2);
+        l_run = l_run * alpha + ps;
+        m_run = m_new;
+        // P^T as the B operand: b0 = (tokens 2t,2t+1 ; row g), b1 = (tokens 8+2t, 9+2t ; row g)
+        const uint32_t pb0 = pack_f16(sv[0], sv[1]), pb1 = pack_f16(sv[2], sv[3]);
+        // rescale factors for the O^T columns (rows 2t, 2t+1)
+        const float al0 = __shfl_sync(0xffffffffu, alpha, (2 * t) * 4);
+        const float al1 = __shfl_sync(0xffffffffu, alpha, (2 * t + 1) * 4);
+#pragma unroll
+        for (int blk = 0; blk < 8; ++blk) {
+#pragma unroll
+          for (int ip = 0; ip < 2; ++ip) {
+            float* c = o[blk * 2 + ip];
+            c[0] *= al0; c[1] *= al1; c[2] *= al0; c[3] *= al1;
+            // m-tile rows: g -> dim blk*32 + g*4 + ip*2, g+8 -> that + 1
+            const uint32_t selA = ip ? 0x0062u : 0x0040u;  // bytes (x.b[2ip], y.b[2ip])
+            const uint32_t selB = ip ? 0x0073u : 0x0051u;  // bytes (x.b[2ip+1], y.b[2ip+1])
+            const uint32_t a0 = e4m3x2_to_f16x2(__byte_perm(va[blk], vb[blk], selA) & 0xffffu);
+            const uint32_t a1 = e4m3x2_to_f16x2(__byte_perm(va[blk], vb[blk], selB) & 0xffffu);
+            const uint32_t a2 = e4m3x2_to_f16x2(__byte_perm(vc[blk], vd[blk], selA) & 0xffffu);
+            const uint32_t a3 = e4m3x2_to_f16x2(__byte_perm(vc[blk], vd[blk], selB) & 0xffffu);
+            mma16816(c, a0, a1, a2, a3, pb0, pb1);
+          }
+        }
+      }
+    }
+    // ---- merge the token-split warps of each row group, write the split partial ----------
+    // O^T regs: o[blk*2+ip][0..1] = (dim blk*32+g*4+ip*2, rows 2t, 2t+1); [2..3] = dim + 1.
+    __syncthreads();
+#pragma unroll
+    for (int blk = 0; blk < 8; ++blk)
+#pragma unroll
+      for (int ip = 0; ip < 2; ++ip) {
+        const int d = blk * 32 + g * 4 + ip * 2;
+        mo[warp][2 * t][d] = o[blk * 2 + ip][0];
+        mo[warp][2 * t + 1][d] = o[blk * 2 + ip][1];
+        mo[warp][2 * t][d + 1] = o[blk * 2 + ip][2];
+        mo[warp][2 * t + 1][d + 1] = o[blk * 2 + ip][3];
+      }
+    if (t == 0) { mml[warp][g][0] = m_run; mml[warp][g][1] = l_run; }
+    __syncthreads();
+    // every warp finalises rows of its own row group for a slice of dims
+    {
+      const int rr = r0 + rg;
+      if (rr < p.T) {
+        for (int row = 0; row < Gq; ++row) {
+          float M = -INFINITY;
+          for (int s = 0; s < TS; ++s) M = fmaxf(M, mml[rg * TS + s][row][0]);
+          float L = 0.f, w[TS];
+          for (int s = 0; s < TS; ++s) {
+            const float ms = mml[rg * TS + s][row][0];
+            w[s] = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
+            L += w[s] * mml[rg * TS + s][row][1];
+          }
+          const size_t qrow = (size_t)grp * p.T + rr;
+          const size_t base = ((qrow * p.hq + (size_t)kvh * Gq + row) * p.splits + split);
+          // dims handled by this warp's lanes: ts*(HD/TS) + lane, + 32, ...
+          for (int d = ts * (HD / TS) + lane; d < (ts + 1) * (HD / TS); d += 32) {
+            float acc = 0.f;
+            for (int s = 0; s < TS; ++s) acc += w[s] * mo[rg * TS + s][row][d];
+            p.part_o[base * HD + d] = acc;
+          }
+          if (ts == 0 && lane == 0) { p.part_ml[base * 2] = M; p.part_ml[base * 2 + 1] = L; }
+        }
+      }
+    }
+  }
+  pdl_launch_dependents();
+}
+
+// grid (rows, hq/4), block 128: warp per (row, head); lane handles 8 dims.
+__global__ void __launch_bounds__(128) attn_reduce_kernel(const float* __restrict__ part_o,
+                                                          const float* __restrict__ part_ml, int splits,
+                                                          const __nv_bfloat16* __restrict__ qraw, int ldq,
+                                                          __nv_bfloat16* out, uint4* xpack, float2* xs, int hq, int G) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int row = blockIdx.x, head = blockIdx.y * 4 + warp;
+  if (head >= hq) return;
+  const size_t base = ((size_t)row * hq + head) * splits;
+  float M = -INFINITY;
+  for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
+  float L = 0.f, acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (int s = 0; s < splits; ++s) {
+    const float ms = part_ml[(base + s) * 2];
+    if (ms == -INFINITY) continue;
+    const float w = exp2f(ms - M);
+    L += w * part_ml[(base + s) * 2 + 1];
+    const float4 a = *reinterpret_cast<const float4*>(part_o + (base + s) * HD + lane * 8);
+    const float4 b = *reinterpret_cast<const float4*>(part_o + (base + s) * HD + lane * 8 + 4);
+    acc[0] += w * a.x; acc[1] += w * a.y; acc[2] += w * a.z; acc[3] += w * a.w;
+    acc[4] += w * b.x; acc[5] += w * b.y; acc[6] += w * b.z; acc[7] += w * b.w;
+  }
+  const float inv = L > 0.f ? 1.f / L : 0.f;
+  float v[8];
+  if (qraw) {
+    const uint4 gq = *reinterpret_cast<const uint4*>(qraw + (size_t)row * ldq + (size_t)head * 2 * HD + HD + lane * 8);
+    float gf[8];
+    unpack_bf16x8(gq, gf);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float a = __bfloat162float(__float2bfloat16(acc[i] * inv));
+      v[i] = __bfloat162float(__float2bfloat16(a * sigmoid_f(gf[i])));
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __bfloat162float(__float2bfloat16(acc[i] * inv));
+  }
+  const size_t e = ((size_t)row * hq + head) * HD + lane * 8;
+  if (out) *reinterpret_cast<uint4*>(out + e) = pack_bf16x8(v);
+  if (xpack) {
+    float s_st, s_eff;
+    uint4 pk = actpack_chunk(v, s_st, s_eff);
+    xpack[e / 8] = pk;
+    const int cpg = G >> 3;
+    actpack_group_reduce(s_st, s_eff, cpg);
+    if ((lane % cpg) == 0) xs[e / G] = make_float2(s_eff, 1024.f * s_st);
+  }
+}
+
+}  // namespace owl
+using namespace owl;
+
+OWL_API int owl_qknorm_rope_insert(const void* qraw, int ldq, const void* kraw, int ldk, const void* vraw, int ldv,
+                                   const void* qnorm_w, const void* knorm_w, const void* pos3, const void* inv_freq,
+                                   const void* section, const void* kv_slot, void* q_out, void* k_pool, void* v_pool,
+                                   int rows, int hq, int hkv, int hd, int rot, float eps, float rope_scale, int pdl,
+                                   cudaStream_t st) {
+  if (rows < 1 || hd > 256 || (hd & 1) || rot > hd || (rot & 3)) return OWL_ERR_BAD_ARG;
+  InsertParams p;
+  p.qraw = (const __nv_bfloat16*)qraw; p.ldq = ldq; p.kraw = (const __nv_bfloat16*)kraw; p.ldk = ldk;
+  p.vraw = (const __nv_bfloat16*)vraw; p.ldv = ldv; p.qnorm_w = (const __nv_bfloat16*)qnorm_w;
+  p.knorm_w = (const __nv_bfloat16*)knorm_w; p.pos3 = (const int*)pos3; p.inv_freq = (const float*)inv_freq;
+  p.section = (const unsigned char*)section; p.kv_slot = (const int*)kv_slot; p.q_out = (__nv_bfloat16*)q_out;
+  p.k_pool = (uint8_t*)k_pool; p.v_pool = (uint8_t*)v_pool; p.rows = rows; p.hq = hq; p.hkv = hkv; p.hd = hd;
+  p.rot = rot; p.eps = eps; p.rope_scale = rope_scale;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(rows, hq + 2 * hkv); cfg.blockDim = dim3(128); cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, qknorm_rope_insert_kernel, p);
+  if (e != cudaSuccess) return (int)OWL_ERR_LAUNCH * 1000 - (int)e;
+  return OWL_OK;
+}
+
+// part_o: float[groups*T*hq*splits*256], part_ml: float[groups*T*hq*splits*2].
+OWL_API int owl_paged_attn(const void* q, const void* k_pool, const void* v_pool, const void* block_table,
+                           const void* bt_row, const void* ctx_len, void* part_o, void* part_ml, int groups, int T,
+                           int hq, int hkv, int hd, int max_blocks, int splits, float scale, int pdl,
+                           cudaStream_t st) {
+  if (hd != HD || groups < 1 || T < 1 || T > 8 || hq % hkv || hq / hkv > 8 || splits < 1) return OWL_ERR_BAD_ARG;
+  AttnParams p;
+  p.q = (const __nv_bfloat16*)q; p.k_pool = (const uint8_t*)k_pool; p.v_pool = (const uint8_t*)v_pool;
+  p.block_table = (const int*)block_table; p.bt_row = (const int*)bt_row; p.ctx_len = (const int*)ctx_len;
+  p.part_o = (float*)part_o; p.part_ml = (float*)part_ml; p.T = T; p.hq = hq; p.hkv = hkv;
+  p.max_blocks = max_blocks; p.splits = splits; p.scale_log2 = scale * 1.4426950408889634f;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(splits, hkv, groups); cfg.blockDim = dim3(AT_WARPS * 32); cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
+  cudaError_t e;
+  if (T == 1) e = cudaLaunchKernelEx(&cfg, paged_attn_kernel<1>, p);
+  else if (T == 2) e = cudaLaunchKernelEx(&cfg, paged_attn_kernel<2>, p);
+  else e = cudaLaunchKernelEx(&cfg, paged_attn_kernel<4>, p);
+  if (e != cudaSuccess) return (int)OWL_ERR_LAUNCH * 1000 - (int)e;
+  return OWL_OK;
+}
+
+OWL_API int owl_attn_reduce(const void* part_o, const void* part_ml, int splits, const void* qraw, int ldq, void* out,
+                            void* xpack, void* xs, int rows, int hq, int G, int pdl, cudaStream_t st) {
+  if (rows < 1 || splits < 1 || (G != 32 && G != 128)) return OWL_ERR_BAD_ARG;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(rows, (hq + 3) / 4); cfg.blockDim = dim3(128); cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, attn_reduce_kernel, (const float*)part_o, (const float*)part_ml, splits,
+                                     (const __nv_bfloat16*)qraw, ldq, (__nv_bfloat16*)out, (uint4*)xpack, (float2*)xs,
+                                     hq, G);
+  if (e != cudaSuccess) return (int)OWL_ERR_LAUNCH * 1000 - (int)e;
+  return OWL_OK;
+}

@@ -1,0 +1,166 @@
+"""Thin Python bindings of the sm_100a kernel launchers (``libowl_b200_cuda.so``).
+
+Every function takes torch CUDA tensors, launches on the current torch stream (so torch CUDA
+graph capture records the launch) and raises ``NativeError`` on a rejected shape or a launch
+failure. There is no fallback: CPU numerics live in ``ops/reference.py``.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+
+import torch
+
+from .. import _native
+
+_P = c_void_p
+_I = c_int
+_F = c_float
+
+_SIGS = {
+    "owl_w4a16_skinny": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "owl_bf16_skinny": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    "owl_w8a16_skinny": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    "owl_rmsnorm_pack": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _I, _I, _P],
+    "owl_act_pack": [_P, _I, _P, _P, _I, _I, _I, _I, _P],
+    "owl_silu_mul": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "owl_sigmoid_gate": [_P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _P],
+    "owl_embed": [_P, _P, _P, _I, _I, _I, _I, _P],
+    "owl_argmax": [_P, _I, _I, _I, _P, _P, _I, _P, _I, _I, _P],
+    "owl_gdn_decode": [_P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
+    "owl_gdn_conv_fwd": [_P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _P],
+    "owl_gdn_scan": [_P, _P, _I, _P, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _F, _P],
+    "owl_qknorm_rope_insert": [_P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F,
+                               _F, _I, _P],
+    "owl_paged_attn": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+    "owl_attn_reduce": [_P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P],
+}
+_bound: dict = {}
+
+
+def fn(name: str):
+    f = _bound.get(name)
+    if f is None:
+        lib = _native.cuda()
+        f = getattr(lib, name)
+        sig = _SIGS.get(name)
+        if sig is not None:
+            f.argtypes = sig
+        f.restype = c_int
+        _bound[name] = f
+    return f
+
+
+def register(name: str, sig: list) -> None:
+    _SIGS[name] = sig
+
+
+def ptr(t) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def call(name: str, *args) -> None:
+    rc = fn(name)(*args)
+    if rc != 0:
+        _native.check(rc, name)
+
+
+EPI_STORE, EPI_RESIDUAL, EPI_SILU_MUL, EPI_F32 = 0, 1, 2, 3
+
+
+def w4a16_skinny(w, xpack, xs, out, m: int, *, residual=None, epi: int = EPI_STORE, ldo: int | None = None,
+                 ks: int = 0, pdl: bool = False) -> None:
+    """out[m, :] = dequant(w) @ x for m <= 32 rows. ``w`` is a ``W4Skinny``."""
+    if ldo is None:
+        ldo = out.shape[-1]
+    call("owl_w4a16_skinny", ptr(w.tiles), ptr(w.sz), ptr(xpack), ptr(xs), ptr(out), ptr(residual), m, w.n, w.k, ldo,
+         w.group, epi, ks, int(pdl), stream())
+
+
+def bf16_skinny(w, x, out, m: int, *, residual=None, epi: int = EPI_STORE, ldo: int | None = None, ks: int = 0,
+                pdl: bool = False) -> None:
+    n, k = w.shape
+    if ldo is None:
+        ldo = out.shape[-1]
+    call("owl_bf16_skinny", ptr(w), ptr(x), ptr(out), ptr(residual), m, n, k, ldo, epi, ks, int(pdl), stream())
+
+
+def w8a16_skinny(wq, row_scale, x, out, m: int, *, epi: int = EPI_STORE, ldo: int | None = None, ks: int = 0,
+                 pdl: bool = False) -> None:
+    n, k = wq.shape
+    if ldo is None:
+        ldo = out.shape[-1]
+    call("owl_w8a16_skinny", ptr(wq), ptr(row_scale), ptr(x), ptr(out), m, n, k, ldo, epi, ks, int(pdl), stream())
+
+
+def rmsnorm_pack(h, w, *, delta=None, out_h=None, normed=None, xpack=None, xs=None, m: int, k: int, group: int = 128,
+                 eps: float = 1e-6, one_plus_w: bool = True, pdl: bool = False) -> None:
+    call("owl_rmsnorm_pack", ptr(h), ptr(delta), ptr(w), ptr(out_h), ptr(normed), ptr(xpack), ptr(xs), m, k, group,
+         eps, int(one_plus_w), int(pdl), stream())
+
+
+def act_pack(x, xpack, xs, m: int, k: int, group: int = 128, ldx: int | None = None, pdl: bool = False) -> None:
+    call("owl_act_pack", ptr(x), ldx if ldx is not None else k, ptr(xpack), ptr(xs), m, k, group, int(pdl), stream())
+
+
+def silu_mul(gate_up, m: int, inter: int, *, out=None, xpack=None, xs=None, group: int = 128, pdl: bool = False):
+    call("owl_silu_mul", ptr(gate_up), ptr(out), ptr(xpack), ptr(xs), m, inter, group, int(pdl), stream())
+
+
+def sigmoid_gate(attn, qraw, ldq: int, hd: int, m: int, hdim_total: int, *, out=None, xpack=None, xs=None,
+                 group: int = 128, pdl: bool = False):
+    call("owl_sigmoid_gate", ptr(attn), ptr(qraw), ldq, hd, ptr(out), ptr(xpack), ptr(xs), m, hdim_total, group,
+         int(pdl), stream())
+
+
+def embed(ids, table, out, m: int, pdl: bool = False) -> None:
+    call("owl_embed", ptr(ids), ptr(table), ptr(out), m, table.shape[1], table.shape[0], int(pdl), stream())
+
+
+def argmax(logits, m: int, vocab: int, ld: int, scratch_val, scratch_idx, nparts: int, out_idx, vocab_offset: int = 0,
+           pdl: bool = False) -> None:
+    call("owl_argmax", ptr(logits), m, vocab, ld, ptr(scratch_val), ptr(scratch_idx), nparts, ptr(out_idx),
+         vocab_offset, int(pdl), stream())
+
+
+def gdn_decode(qkvz, ld: int, ab, ldab: int, conv_w, a_log, dt_bias, gamma, conv_state, state, slots, *, out=None,
+               xpack=None, xs=None, batch: int, t: int, nk: int, nv: int, group: int = 128, eps: float = 1e-6,
+               pdl: bool = False) -> None:
+    call("owl_gdn_decode", ptr(qkvz), ld, ptr(ab), ldab, ptr(conv_w), ptr(a_log), ptr(dt_bias), ptr(gamma),
+         ptr(conv_state), ptr(state), ptr(slots), ptr(out), ptr(xpack), ptr(xs), batch, t, nk, nv, group, eps,
+         int(pdl), stream())
+
+
+def gdn_conv_fwd(x, ld: int, conv_w, conv_state, slot: int, out, t: int, nk: int, nv: int, use_state: bool) -> None:
+    call("owl_gdn_conv_fwd", ptr(x), ld, ptr(conv_w), ptr(conv_state), slot, ptr(out), t, nk, nv, int(use_state),
+         stream())
+
+
+def gdn_scan(qkv, z, ldz: int, ab, ldab: int, a_log, dt_bias, gamma, state, slot: int, out, t: int, nk: int, nv: int,
+             use_state: bool, eps: float = 1e-6) -> None:
+    call("owl_gdn_scan", ptr(qkv), ptr(z), ldz, ptr(ab), ldab, ptr(a_log), ptr(dt_bias), ptr(gamma), ptr(state), slot,
+         ptr(out), t, nk, nv, int(use_state), eps, stream())
+
+
+def qknorm_rope_insert(qraw, ldq: int, kraw, ldk: int, vraw, ldv: int, qnorm_w, knorm_w, pos3, inv_freq, section,
+                       kv_slot, q_out, k_pool, v_pool, rows: int, hq: int, hkv: int, hd: int, rot: int,
+                       eps: float = 1e-6, rope_scale: float = 1.0, pdl: bool = False) -> None:
+    call("owl_qknorm_rope_insert", ptr(qraw), ldq, ptr(kraw), ldk, ptr(vraw), ldv, ptr(qnorm_w), ptr(knorm_w),
+         ptr(pos3), ptr(inv_freq), ptr(section), ptr(kv_slot), ptr(q_out), ptr(k_pool), ptr(v_pool), rows, hq, hkv,
+         hd, rot, eps, rope_scale, int(pdl), stream())
+
+
+def paged_attn(q, k_pool, v_pool, block_table, bt_row, ctx_len, part_o, part_ml, groups: int, t: int, hq: int,
+               hkv: int, hd: int, max_blocks: int, splits: int, scale: float, pdl: bool = False) -> None:
+    call("owl_paged_attn", ptr(q), ptr(k_pool), ptr(v_pool), ptr(block_table), ptr(bt_row), ptr(ctx_len), ptr(part_o),
+         ptr(part_ml), groups, t, hq, hkv, hd, max_blocks, splits, scale, int(pdl), stream())
+
+
+def attn_reduce(part_o, part_ml, splits: int, qraw, ldq: int, rows: int, hq: int, *, out=None, xpack=None, xs=None,
+                group: int = 128, pdl: bool = False) -> None:
+    call("owl_attn_reduce", ptr(part_o), ptr(part_ml), splits, ptr(qraw), ldq, ptr(out), ptr(xpack), ptr(xs), rows, hq,
+         group, int(pdl), stream())
