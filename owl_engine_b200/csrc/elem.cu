@@ -247,6 +247,28 @@ __global__ void __launch_bounds__(128) argmax_stage2(const float* pval, const in
   if (threadIdx.x == 0) out[row] = bi + vocab_offset;
 }
 
+// Self-feeding greedy decode: after sampling, make the sampled token the next step's input
+// and advance the per-sequence position, context length and KV write slot on the device so a
+// replayed graph needs no host update between steps. inp layout (int32):
+//   ids[M] | pos3[3*M] | kv_slot[M] | ctx_len[B] | gdn_slot[B] | bt_row[B]   (M = B rows, T = 1)
+__global__ void decode_advance_kernel(int* inp, const int* __restrict__ tok, const int* __restrict__ block_table,
+                                      int max_blocks, int B) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  int* ids = inp; int* pos3 = inp + B; int* kv_slot = inp + 4 * B; int* ctx = inp + 5 * B;
+  const int* gslot = inp + 6 * B; const int* bt_row = inp + 7 * B;
+  if (gslot[b] < 0) return;  // padding row
+  ids[b] = tok[b];
+  const int np = pos3[b] + 1;
+  pos3[b] = np; pos3[B + b] += 1; pos3[2 * B + b] += 1;
+  ctx[b] += 1;
+  const int tpos = ctx[b] - 1;   // cache index of the token that will be written next step
+  const int pg = tpos >> 4;
+  kv_slot[b] = pg < max_blocks ? block_table[(size_t)bt_row[b] * max_blocks + pg] * 16 + (tpos & 15) : -1;
+}
+
 template <typename... Args>
 static int launch_pdl(void (*kernel)(Args...), dim3 grid, dim3 block, int pdl, cudaStream_t st, Args... args) {
   cudaLaunchConfig_t cfg = {};
@@ -308,4 +330,11 @@ OWL_API int owl_argmax(const void* logits, int M, int V, int ld, void* scratch_v
   if (r) return r;
   return launch_pdl(argmax_stage2, dim3(M), dim3(32), pdl, st, (const float*)scratch_val, (const int*)scratch_idx,
                     nparts, (int*)out_idx, vocab_offset);
+}
+
+OWL_API int owl_decode_advance(void* inp, const void* tok, const void* block_table, int max_blocks, int B, int pdl,
+                               cudaStream_t st) {
+  if (B < 1) return OWL_ERR_BAD_ARG;
+  return launch_pdl(decode_advance_kernel, dim3((B + 63) / 64), dim3(64), pdl, st, (int*)inp, (const int*)tok,
+                    (const int*)block_table, max_blocks, B);
 }

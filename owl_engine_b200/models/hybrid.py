@@ -1,0 +1,530 @@
+"""GPU runner of the hybrid model: device weights in kernel layouts, the state pool (paged fp8
+KV + GDN rows), the decode / verify step as a capturable kernel sequence, chunked prefill.
+
+One ``HybridRunner`` lives in each rank's process. With ``spec.tp_world > 1`` the row-parallel
+projections (o_proj / out_proj / down_proj) hand their partial sums to ``comm`` (see
+``owl_engine_b200.parallel``), which reduces them across ranks fused with the residual add.
+
+Reference counterpart: the model backbone (``crates/models/src/model.rs``), decoder layer
+(``layers/decoder.rs:80-100``), executor device halves (``crates/engine/src/exec/phases.rs``) and
+the state pool (``crates/engine/src/mem/state.rs``). The reference's TensorOps interpreter is
+not reproduced: the step is a fixed launch sequence recorded into a CUDA graph.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import torch
+
+from ..ops import kernels as K
+from ..ops import quant as Q
+from ..ops import reference as R
+from .spec import ModelSpec, mrope_section_map
+
+PAGE = 16
+
+
+# ---------------------------------------------------------------------------------------------
+# weights
+# ---------------------------------------------------------------------------------------------
+@dataclass
+class LayerWeights:
+    kind: str
+    ln1: torch.Tensor
+    ln2: torch.Tensor
+    gate_up: object
+    down: object
+    # gdn
+    qkvz: object = None
+    ab: torch.Tensor = None
+    conv_w: torch.Tensor = None
+    a_log: torch.Tensor = None
+    dt_bias: torch.Tensor = None
+    gamma: torch.Tensor = None
+    out_proj: object = None
+    # full
+    qkv: object = None
+    q_norm: torch.Tensor = None
+    k_norm: torch.Tensor = None
+    o_proj: object = None
+
+
+@dataclass
+class HybridWeights:
+    spec: ModelSpec
+    embed: torch.Tensor
+    final_norm: torch.Tensor
+    lm_head: torch.Tensor            # bf16 [V, H] (vocab shard with TP vocab split) or None when lm_head_q is set
+    layers: list
+    group: int
+    lm_head_q: torch.Tensor = None   # int8 rows
+    lm_head_s: torch.Tensor = None
+    vocab_offset: int = 0
+
+    def nbytes(self) -> int:
+        n = self.embed.numel() * 2 + (self.lm_head.numel() * 2 if self.lm_head is not None else 0)
+        if self.lm_head_q is not None:
+            n += self.lm_head_q.numel()
+        for l in self.layers:
+            for w in (l.gate_up, l.down, l.qkvz, l.out_proj, l.qkv, l.o_proj):
+                if w is not None:
+                    n += w.nbytes
+        return n
+
+
+def _pad16_rows(w: torch.Tensor) -> torch.Tensor:
+    n = w.shape[0]
+    if n % 16 == 0:
+        return w
+    return torch.cat([w, torch.zeros(16 - n % 16, w.shape[1], dtype=w.dtype, device=w.device)])
+
+
+def weights_from_dense(spec: ModelSpec, dense: dict, device, group: int = 128, lm_head_int8: bool = False,
+                       quantize=True):
+    """Build device weights from HF-named dense tensors (full, unsharded model; ``spec`` may be
+    a TP shard, in which case rows / columns are cut with ``parallel.plan``). Returns
+    ``(HybridWeights, dense_equiv)`` where ``dense_equiv`` holds the dequantised weights under
+    the same HF names, i.e. exactly what the kernels compute with (for the CPU oracle)."""
+    from ..parallel.plan import shard_dense_for_rank
+
+    dense = shard_dense_for_rank(spec, dense)
+    equiv = dict(dense)
+
+    def w4(name_or_tensor, names=None):
+        w = name_or_tensor.float()
+        c = Q.quantize_w4(w, group)
+        if names:
+            deq = c.dequant()
+            off = 0
+            for nm, rows in names:
+                equiv[nm] = deq[off:off + rows]
+                off += rows
+        return Q.pack_skinny(c).to(device)
+
+    bf = lambda t: t.to(torch.bfloat16).to(device)
+    f32 = lambda t: t.float().to(device)
+    layers = []
+    for i in range(spec.n_layers):
+        p = f"model.layers.{i}."
+        m = p + "mlp."
+        gu = Q.interleave_gate_up(dense[m + "gate_proj.weight"].float(), dense[m + "up_proj.weight"].float())
+        cgu = Q.quantize_w4(gu, group)
+        ge, ue = Q.deinterleave_gate_up(cgu.dequant().t())
+        equiv[m + "gate_proj.weight"], equiv[m + "up_proj.weight"] = ge.t().contiguous(), ue.t().contiguous()
+        lw = LayerWeights(kind="full" if spec.is_full(i) else "gdn", ln1=bf(dense[p + "input_layernorm.weight"]),
+                          ln2=bf(dense[p + "post_attention_layernorm.weight"]), gate_up=Q.pack_skinny(cgu).to(device),
+                          down=w4(dense[m + "down_proj.weight"], [(m + "down_proj.weight", spec.hidden)]))
+        if lw.kind == "gdn":
+            a = p + "linear_attn."
+            qkvz = torch.cat([dense[a + "in_proj_qkv.weight"], dense[a + "in_proj_z.weight"]]).float()
+            lw.qkvz = w4(qkvz, [(a + "in_proj_qkv.weight", spec.conv_dim), (a + "in_proj_z.weight", spec.value_dim)])
+            ab = torch.cat([dense[a + "in_proj_a.weight"], dense[a + "in_proj_b.weight"]]).to(torch.bfloat16)
+            equiv[a + "in_proj_a.weight"], equiv[a + "in_proj_b.weight"] = ab[:spec.nv].float(), ab[spec.nv:].float()
+            lw.ab = _pad16_rows(ab).to(device)
+            lw.conv_w = f32(dense[a + "conv1d.weight"].reshape(spec.conv_dim, spec.conv_k))
+            lw.a_log, lw.dt_bias = f32(dense[a + "A_log"]), f32(dense[a + "dt_bias"])
+            lw.gamma = f32(dense[a + "norm.weight"])
+            lw.out_proj = w4(dense[a + "out_proj.weight"], [(a + "out_proj.weight", spec.hidden)])
+        else:
+            a = p + "self_attn."
+            qkv = torch.cat([dense[a + "q_proj.weight"], dense[a + "k_proj.weight"], dense[a + "v_proj.weight"]]).float()
+            lw.qkv = w4(qkv, [(a + "q_proj.weight", 2 * spec.hq * spec.hd), (a + "k_proj.weight", spec.hkv * spec.hd),
+                              (a + "v_proj.weight", spec.hkv * spec.hd)])
+            lw.q_norm, lw.k_norm = bf(dense[a + "q_norm.weight"]), bf(dense[a + "k_norm.weight"])
+            lw.o_proj = w4(dense[a + "o_proj.weight"], [(a + "o_proj.weight", spec.hidden)])
+        for nm in ("input_layernorm.weight", "post_attention_layernorm.weight"):
+            equiv[p + nm] = dense[p + nm].to(torch.bfloat16).float()
+        layers.append(lw)
+    emb = dense["model.embed_tokens.weight"].to(torch.bfloat16)
+    head = emb if spec.tied else dense["lm_head.weight"].to(torch.bfloat16)
+    equiv["model.embed_tokens.weight"] = emb.float()
+    equiv["model.norm.weight"] = dense["model.norm.weight"].to(torch.bfloat16).float()
+    hw = HybridWeights(spec=spec, embed=emb.to(device), final_norm=bf(dense["model.norm.weight"]), lm_head=None,
+                       layers=layers, group=group)
+    if lm_head_int8:
+        q8, s8 = Q.quantize_w8_rows(head.float())
+        hw.lm_head_q, hw.lm_head_s = q8.to(device), s8.to(device)
+        equiv["lm_head.weight"] = q8.float() * s8[:, None]
+    else:
+        hw.lm_head = head.to(device)
+        equiv["lm_head.weight"] = head.float()
+    return hw, equiv
+
+
+def random_weights(spec: ModelSpec, device, group: int = 128, seed: int = 0, lm_head_int8: bool = False,
+                   std: float = 0.02) -> HybridWeights:
+    """Random-init weights generated directly in the device layouts (benchmarks: no dense copy)."""
+    gen = torch.Generator(device=device).manual_seed(seed)
+    rnd = lambda *s: (torch.randn(*s, device=device, generator=gen) * std)
+    H = spec.hidden
+    layers = []
+    sd = seed * 100003
+    for i in range(spec.n_layers):
+        sd += 17
+        lw = LayerWeights(kind="full" if spec.is_full(i) else "gdn", ln1=rnd(H).to(torch.bfloat16),
+                          ln2=rnd(H).to(torch.bfloat16),
+                          gate_up=Q.random_skinny(2 * spec.inter, H, group, device, std, sd + 1),
+                          down=Q.random_skinny(H, spec.inter, group, device, std, sd + 2))
+        if lw.kind == "gdn":
+            lw.qkvz = Q.random_skinny(spec.conv_dim + spec.value_dim, H, group, device, std, sd + 3)
+            lw.ab = _pad16_rows(rnd(2 * spec.nv, H).to(torch.bfloat16))
+            lw.conv_w = (torch.randn(spec.conv_dim, spec.conv_k, device=device, generator=gen) * 0.2)
+            lw.a_log = torch.log(torch.empty(spec.nv, device=device).uniform_(1.0, 16.0, generator=gen))
+            lw.dt_bias = torch.ones(spec.nv, device=device)
+            lw.gamma = torch.ones(spec.vd, device=device)
+            lw.out_proj = Q.random_skinny(H, spec.value_dim, group, device, std, sd + 4)
+        else:
+            lw.qkv = Q.random_skinny(2 * spec.hq * spec.hd + 2 * spec.hkv * spec.hd, H, group, device, std, sd + 5)
+            lw.q_norm, lw.k_norm = rnd(spec.hd).to(torch.bfloat16), rnd(spec.hd).to(torch.bfloat16)
+            lw.o_proj = Q.random_skinny(H, spec.hq * spec.hd, group, device, std, sd + 6)
+        layers.append(lw)
+    emb = rnd(spec.vocab, H).to(torch.bfloat16)
+    hw = HybridWeights(spec=spec, embed=emb, final_norm=torch.zeros(H, dtype=torch.bfloat16, device=device),
+                       lm_head=None, layers=layers, group=group)
+    if lm_head_int8:
+        hw.lm_head_q = torch.randint(-127, 128, (spec.vocab, H), device=device, dtype=torch.int8, generator=gen)
+        hw.lm_head_s = torch.full((spec.vocab,), std / 40.0, device=device)
+    else:
+        hw.lm_head = emb if spec.tied else rnd(spec.vocab, H).to(torch.bfloat16)
+    return hw
+
+
+# ---------------------------------------------------------------------------------------------
+# state pool
+# ---------------------------------------------------------------------------------------------
+class StatePool:
+    """Device state: paged fp8 KV (``[layer][page][16][hkv][hd]`` e4m3, zero-initialised so that
+    masked slots never hold NaN encodings), GDN convolution history and recurrent state rows."""
+
+    def __init__(self, spec: ModelSpec, device, n_pages: int, n_slots: int, ledger=None):
+        self.spec, self.device, self.n_pages, self.n_slots = spec, device, n_pages, n_slots
+        nf, ng = spec.n_full, spec.n_gdn
+        self.k_pool = torch.zeros(nf, n_pages, PAGE, spec.hkv, spec.hd, dtype=torch.uint8, device=device)
+        self.v_pool = torch.zeros(nf, n_pages, PAGE, spec.hkv, spec.hd, dtype=torch.uint8, device=device)
+        self.conv_state = torch.zeros(ng, n_slots, spec.conv_dim, spec.conv_k - 1, dtype=torch.float32, device=device)
+        self.rec_state = torch.zeros(ng, n_slots, spec.nv, spec.kd, spec.vd, dtype=torch.float32, device=device)
+        if ledger is not None:
+            ledger.record("kv_pool", "pool", self.k_pool.numel() * 2)
+            ledger.record("gdn_state", "pool", self.conv_state.numel() * 4 + self.rec_state.numel() * 4)
+
+    @staticmethod
+    def bytes_per_page(spec: ModelSpec) -> int:
+        return spec.n_full * 2 * PAGE * spec.hkv * spec.hd
+
+    @staticmethod
+    def bytes_per_slot(spec: ModelSpec) -> int:
+        return spec.gdn_state_bytes()
+
+    def reset_slot(self, slot: int) -> None:
+        self.conv_state[:, slot].zero_()
+        self.rec_state[:, slot].zero_()
+
+    def copy_slot(self, src: int, dst: int) -> None:
+        """Snapshot / restore of a GDN row (speculative rollback, prefix-boundary snapshots)."""
+        self.conv_state[:, dst].copy_(self.conv_state[:, src])
+        self.rec_state[:, dst].copy_(self.rec_state[:, src])
+
+
+# ---------------------------------------------------------------------------------------------
+# runner
+# ---------------------------------------------------------------------------------------------
+class StepLayout:
+    """Offsets (int32 elements) of the packed per-step input buffer for B sequences x T rows."""
+
+    def __init__(self, b: int, t: int):
+        m = b * t
+        self.b, self.t, self.m = b, t, m
+        self.ids, self.pos3, self.kv_slot = 0, m, 4 * m
+        self.ctx, self.gslot, self.bt_row = 5 * m, 5 * m + b, 5 * m + 2 * b
+        self.size = 5 * m + 3 * b
+
+
+class HybridRunner:
+    MAX_ROWS = 32
+
+    def __init__(self, spec: ModelSpec, weights: HybridWeights, pool: StatePool, *, max_seqs: int = 32,
+                 max_blocks: int = 1024, prefill_chunk: int = 2048, comm=None, pdl: bool = True,
+                 attn_splits: int = 0, prefill_gemm: str = "tc"):
+        self.spec, self.w, self.pool, self.comm = spec, weights, pool, comm
+        self.device = pool.device
+        self.max_seqs, self.max_blocks, self.prefill_chunk = max_seqs, max_blocks, prefill_chunk
+        self.pdl = pdl
+        self.prefill_gemm = prefill_gemm
+        self.G = weights.group
+        dev, H, M = self.device, spec.hidden, self.MAX_ROWS
+        bf = lambda *s: torch.zeros(*s, dtype=torch.bfloat16, device=dev)
+        f16 = lambda *s: torch.zeros(*s, dtype=torch.float16, device=dev)
+        f32 = lambda *s: torch.zeros(*s, dtype=torch.float32, device=dev)
+        G = self.G
+        self.block_table = torch.zeros(max_seqs, max_blocks, dtype=torch.int32, device=dev)
+        self.inp = torch.zeros(8 * M + 3 * max_seqs, dtype=torch.int32, device=dev)
+        self.h = bf(M, H)
+        self.xn = bf(M, H)
+        self.xp_h, self.xs_h = f16(M, H), f32(M, H // G, 2)
+        self.partial = bf(M, H)
+        qkvz_n = spec.conv_dim + spec.value_dim
+        self.qkvz_out = bf(M, qkvz_n)
+        self.ldab = ((2 * spec.nv + 15) // 16) * 16
+        self.ab_out = bf(M, self.ldab)
+        self.xp_v, self.xs_v = f16(M, spec.value_dim), f32(M, spec.value_dim // G, 2)
+        self.qkv_n = 2 * spec.hq * spec.hd + 2 * spec.hkv * spec.hd
+        self.qkv_out = bf(M, self.qkv_n)
+        self.q_rope = bf(M, spec.hq, spec.hd)
+        self.attn_splits = attn_splits
+        self.max_splits = 64
+        self.part_o = f32(M * spec.hq * self.max_splits * spec.hd)
+        self.part_ml = f32(M * spec.hq * self.max_splits * 2)
+        self.xp_a, self.xs_a = f16(M, spec.hq * spec.hd), f32(M, spec.hq * spec.hd // G, 2)
+        self.act = bf(M, spec.inter)
+        self.xp_i, self.xs_i = f16(M, spec.inter), f32(M, spec.inter // G, 2)
+        self.vocab_local = (weights.lm_head if weights.lm_head is not None else weights.lm_head_q).shape[0]
+        self.logits = bf(M, self.vocab_local)
+        self.am_parts = 64
+        self.am_val, self.am_idx = f32(M * self.am_parts), torch.zeros(M * self.am_parts, dtype=torch.int32, device=dev)
+        self.out_tok = torch.zeros(M, dtype=torch.int32, device=dev)
+        self.inv_freq = R.rope_inv_freq(spec.rotary_dim, spec.rope_theta).to(dev)
+        self.section = torch.tensor(mrope_section_map(spec), dtype=torch.uint8, device=dev)
+        self.rope_scale = 1.0
+        self.scale = 1.0 / math.sqrt(spec.hd)
+        self.graphs: dict = {}
+        self._pf = None   # lazily allocated prefill workspace
+        self.taps: dict | None = None   # layer -> bf16 [M,H] buffers filled during decode/prefill for draft heads
+
+    # -- step inputs -------------------------------------------------------------------------
+    def views(self, lay: StepLayout):
+        i = self.inp
+        return dict(ids=i[lay.ids:lay.ids + lay.m], pos3=i[lay.pos3:lay.pos3 + 3 * lay.m],
+                    kv_slot=i[lay.kv_slot:lay.kv_slot + lay.m], ctx=i[lay.ctx:lay.ctx + lay.b],
+                    gslot=i[lay.gslot:lay.gslot + lay.b], bt_row=i[lay.bt_row:lay.bt_row + lay.b])
+
+    # -- building blocks ---------------------------------------------------------------------
+    def _row_parallel(self, w, xp, xs, m: int) -> None:
+        """h += W x for a row-parallel projection (TP: partial sums are reduced by ``comm``)."""
+        if self.comm is None or self.spec.tp_world == 1:
+            K.w4a16_skinny(w, xp, xs, self.h, m, residual=self.h, epi=K.EPI_RESIDUAL, pdl=self.pdl)
+        else:
+            K.w4a16_skinny(w, xp, xs, self.partial, m, pdl=self.pdl)
+            self.comm.allreduce_add_residual(self.partial, self.h, m)
+
+    def _mlp(self, lw: LayerWeights, m: int) -> None:
+        sp = self.spec
+        K.rmsnorm_pack(self.h, lw.ln2, xpack=self.xp_h, xs=self.xs_h, m=m, k=sp.hidden, group=self.G, eps=sp.eps,
+                       pdl=self.pdl)
+        K.w4a16_skinny(lw.gate_up, self.xp_h, self.xs_h, self.act, m, epi=K.EPI_SILU_MUL, ldo=sp.inter, pdl=self.pdl)
+        K.act_pack(self.act, self.xp_i, self.xs_i, m, sp.inter, self.G, pdl=self.pdl)
+        self._row_parallel(lw.down, self.xp_i, self.xs_i, m)
+
+    def _gdn(self, lw: LayerWeights, li: int, lay: StepLayout, v: dict) -> None:
+        sp, m = self.spec, lay.m
+        K.rmsnorm_pack(self.h, lw.ln1, normed=self.xn, xpack=self.xp_h, xs=self.xs_h, m=m, k=sp.hidden, group=self.G,
+                       eps=sp.eps, pdl=self.pdl)
+        K.w4a16_skinny(lw.qkvz, self.xp_h, self.xs_h, self.qkvz_out, m, pdl=self.pdl)
+        K.bf16_skinny(lw.ab, self.xn, self.ab_out, m, pdl=self.pdl)
+        K.gdn_decode(self.qkvz_out, self.qkvz_out.shape[1], self.ab_out, self.ldab, lw.conv_w, lw.a_log, lw.dt_bias,
+                     lw.gamma, self.pool.conv_state[li], self.pool.rec_state[li], v["gslot"], xpack=self.xp_v,
+                     xs=self.xs_v, batch=lay.b, t=lay.t, nk=sp.nk, nv=sp.nv, group=self.G, eps=sp.eps, pdl=self.pdl)
+        self._row_parallel(lw.out_proj, self.xp_v, self.xs_v, m)
+
+    def _pick_splits(self, b: int, ctx_hint: int) -> int:
+        if self.attn_splits:
+            return self.attn_splits
+        pages = max(1, (ctx_hint + PAGE - 1) // PAGE)
+        want = max(1, (2 * 148) // max(1, b * self.spec.hkv))
+        return max(1, min(self.max_splits, want, (pages + 3) // 4))
+
+    def _full(self, lw: LayerWeights, li: int, lay: StepLayout, v: dict, splits: int) -> None:
+        sp, m = self.spec, lay.m
+        K.rmsnorm_pack(self.h, lw.ln1, xpack=self.xp_h, xs=self.xs_h, m=m, k=sp.hidden, group=self.G, eps=sp.eps,
+                       pdl=self.pdl)
+        K.w4a16_skinny(lw.qkv, self.xp_h, self.xs_h, self.qkv_out, m, pdl=self.pdl)
+        qn = 2 * sp.hq * sp.hd
+        kraw = self.qkv_out[:, qn:]
+        vraw = self.qkv_out[:, qn + sp.hkv * sp.hd:]
+        K.qknorm_rope_insert(self.qkv_out, self.qkv_n, kraw, self.qkv_n, vraw, self.qkv_n, lw.q_norm, lw.k_norm,
+                             v["pos3"], self.inv_freq, self.section, v["kv_slot"], self.q_rope, self.pool.k_pool[li],
+                             self.pool.v_pool[li], m, sp.hq, sp.hkv, sp.hd, sp.rotary_dim, sp.eps, self.rope_scale,
+                             pdl=self.pdl)
+        K.paged_attn(self.q_rope, self.pool.k_pool[li], self.pool.v_pool[li], self.block_table, v["bt_row"], v["ctx"],
+                     self.part_o, self.part_ml, lay.b, lay.t, sp.hq, sp.hkv, sp.hd, self.max_blocks, splits, self.scale,
+                     pdl=self.pdl)
+        K.attn_reduce(self.part_o, self.part_ml, splits, self.qkv_out, self.qkv_n, m, sp.hq, xpack=self.xp_a,
+                      xs=self.xs_a, group=self.G, pdl=self.pdl)
+        self._row_parallel(lw.o_proj, self.xp_a, self.xs_a, m)
+
+    def _head(self, m: int, sample: bool = True) -> None:
+        sp, w = self.spec, self.w
+        K.rmsnorm_pack(self.h, w.final_norm, normed=self.xn, m=m, k=sp.hidden, group=self.G, eps=sp.eps, pdl=self.pdl)
+        if w.lm_head_q is not None:
+            K.w8a16_skinny(w.lm_head_q, w.lm_head_s, self.xn, self.logits, m, pdl=self.pdl)
+        else:
+            K.bf16_skinny(w.lm_head, self.xn, self.logits, m, pdl=self.pdl)
+        if sample:
+            K.argmax(self.logits, m, self.vocab_local, self.vocab_local, self.am_val, self.am_idx, self.am_parts,
+                     self.out_tok, w.vocab_offset, pdl=self.pdl)
+
+    # -- decode / verify step ------------------------------------------------------------------
+    def step_forward(self, lay: StepLayout, *, ctx_hint: int = 2048, advance: bool = False, sample: bool = True) -> None:
+        """One forward over ``lay.m`` rows whose inputs sit in ``self.inp``. Capturable."""
+        v = self.views(lay)
+        m = lay.m
+        splits = self._pick_splits(lay.b, ctx_hint)
+        K.embed(v["ids"], self.w.embed, self.h, m, pdl=False)
+        fi = gi = 0
+        for i, lw in enumerate(self.w.layers):
+            if lw.kind == "gdn":
+                self._gdn(lw, gi, lay, v)
+                gi += 1
+            else:
+                self._full(lw, fi, lay, v, splits)
+                fi += 1
+            self._mlp(lw, m)
+            if self.taps is not None and i in self.taps:
+                self.taps[i][:m].copy_(self.h[:m])
+        self._head(m, sample)
+        if advance:
+            assert lay.t == 1
+            K.decode_advance(self.inp, self.out_tok, self.block_table, self.max_blocks, lay.b, pdl=self.pdl)
+
+    def capture(self, b: int, t: int = 1, *, ctx_hint: int = 2048, advance: bool = False, sample: bool = True):
+        """Capture (once) and return the CUDA graph of a (b, t) step."""
+        key = (b, t, self._pick_splits(b, ctx_hint), advance, sample)
+        g = self.graphs.get(key)
+        if g is not None:
+            return g
+        lay = StepLayout(b, t)
+        stream = torch.cuda.Stream(device=self.device)
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            # warm-up outside capture writes state; callers capture before real traffic or accept
+            # that rows with gdn slot -1 / kv slot -1 are inert. Here inputs are forced inert.
+            saved = self.inp.clone()
+            v = self.views(lay)
+            v["gslot"].fill_(-1)
+            v["kv_slot"].fill_(-1)
+            v["ctx"].fill_(1)
+            v["bt_row"].zero_()
+            self.step_forward(lay, ctx_hint=ctx_hint, advance=False, sample=sample)
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                self.step_forward(lay, ctx_hint=ctx_hint, advance=advance, sample=sample)
+            self.inp.copy_(saved)
+        torch.cuda.current_stream().wait_stream(stream)
+        self.graphs[key] = graph
+        return graph
+
+    # -- prefill ---------------------------------------------------------------------------------
+    def _prefill_ws(self, t: int):
+        if self._pf is not None and self._pf["t"] >= t:
+            return self._pf
+        sp, dev = self.spec, self.device
+        bf = lambda *s: torch.empty(*s, dtype=torch.bfloat16, device=dev)
+        widest = max(2 * sp.inter, sp.conv_dim + sp.value_dim, self.qkv_n)
+        ws = dict(t=t, h=bf(t, sp.hidden), x=bf(t, sp.hidden), wide=bf(t, widest), act=bf(t, sp.inter),
+                  conv=bf(t, sp.conv_dim), mix=bf(t, max(sp.value_dim, sp.hq * sp.hd)), ab=bf(t, self.ldab),
+                  q=bf(t + 8, sp.hq, sp.hd), y=bf(t, sp.hidden),
+                  part_o=torch.empty((t + 8) * sp.hq * sp.hd, dtype=torch.float32, device=dev),
+                  part_ml=torch.empty((t + 8) * sp.hq * 2, dtype=torch.float32, device=dev),
+                  pos3=torch.zeros(3, t, dtype=torch.int32, device=dev),
+                  kv_slot=torch.zeros(t, dtype=torch.int32, device=dev),
+                  ctx=torch.zeros(t // 8 + 2, dtype=torch.int32, device=dev),
+                  bt_row=torch.zeros(t // 8 + 2, dtype=torch.int32, device=dev),
+                  ids=torch.zeros(t, dtype=torch.int32, device=dev))
+        self._pf = ws
+        return ws
+
+    def _gemm(self, w, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """out[T, N] = x[T, K] @ dequant(w)^T for a prefill chunk."""
+        from ..ops import linear
+
+        return linear.w4_gemm(w, x, out, arm=self.prefill_gemm)
+
+    def prefill_chunk_forward(self, ids: torch.Tensor, pos0: int, seq_row: int, gdn_slot: int, *,
+                              pos3: torch.Tensor | None = None, want_logits: bool = True,
+                              embeds: torch.Tensor | None = None):
+        """Run one prefill chunk (eager). ``ids`` int32 [T] on device; KV pages for positions
+        pos0..pos0+T-1 must already be in ``block_table[seq_row]``. Returns the argmax token of
+        the last row when ``want_logits``."""
+        sp, pool = self.spec, self.pool
+        t = ids.shape[0]
+        ws = self._prefill_ws(max(t, 16))
+        h, x = ws["h"][:t], ws["x"][:t]
+        if pos3 is None:
+            p = torch.arange(pos0, pos0 + t, dtype=torch.int32, device=self.device)
+            ws["pos3"][:, :t] = p[None]
+        else:
+            ws["pos3"][:, :t] = pos3
+        pos3_v = ws["pos3"][:, :t].contiguous()
+        tpos = torch.arange(pos0, pos0 + t, device=self.device)
+        pages = self.block_table[seq_row, (tpos // PAGE).long()]
+        kv_slot = (pages * PAGE + (tpos % PAGE).int()).int()
+        # query groups of 8 rows (+ a tail group)
+        ng, tail = t // 8, t % 8
+        if ng:
+            ws["ctx"][:ng] = pos0 + 8 * torch.arange(1, ng + 1, dtype=torch.int32, device=self.device)
+            ws["bt_row"][:ng] = seq_row
+        if tail:
+            ws["ctx"][ng] = pos0 + t
+            ws["bt_row"][ng] = seq_row
+        if embeds is None:
+            K.embed(ids, self.w.embed, h, t)
+        else:
+            h.copy_(embeds)
+        fi = gi = 0
+        use_state = pos0 > 0
+        for i, lw in enumerate(self.w.layers):
+            K.rmsnorm_pack(h, lw.ln1, normed=x, m=t, k=sp.hidden, group=self.G, eps=sp.eps)
+            if lw.kind == "gdn":
+                nq = sp.conv_dim + sp.value_dim
+                wide = ws["wide"].view(-1)[:t * nq].view(t, nq)
+                self._gemm(lw.qkvz, x, wide)
+                ab = ws["ab"][:t]
+                torch.matmul(x, lw.ab.t(), out=ab)
+                conv = ws["conv"][:t]
+                K.gdn_conv_fwd(wide, nq, lw.conv_w, pool.conv_state[gi], gdn_slot, conv, t, sp.nk, sp.nv, use_state)
+                mix = ws["mix"].view(-1)[:t * sp.value_dim].view(t, sp.value_dim)
+                K.gdn_scan(conv, wide[:, sp.conv_dim:], nq, ab, self.ldab, lw.a_log, lw.dt_bias, lw.gamma,
+                           pool.rec_state[gi], gdn_slot, mix, t, sp.nk, sp.nv, use_state, sp.eps)
+                self._gemm(lw.out_proj, mix, ws["y"][:t])
+                gi += 1
+            else:
+                wide = ws["wide"].view(-1)[:t * self.qkv_n].view(t, self.qkv_n)
+                self._gemm(lw.qkv, x, wide)
+                qn = 2 * sp.hq * sp.hd
+                K.qknorm_rope_insert(wide, self.qkv_n, wide[:, qn:], self.qkv_n, wide[:, qn + sp.hkv * sp.hd:],
+                                     self.qkv_n, lw.q_norm, lw.k_norm, pos3_v, self.inv_freq, self.section, kv_slot,
+                                     ws["q"], pool.k_pool[fi], pool.v_pool[fi], t, sp.hq, sp.hkv, sp.hd, sp.rotary_dim,
+                                     sp.eps, self.rope_scale)
+                if ng:
+                    K.paged_attn(ws["q"], pool.k_pool[fi], pool.v_pool[fi], self.block_table, ws["bt_row"], ws["ctx"],
+                                 ws["part_o"], ws["part_ml"], ng, 8, sp.hq, sp.hkv, sp.hd, self.max_blocks, 1, self.scale)
+                if tail:
+                    off = ng * 8
+                    K.paged_attn(ws["q"][off:], pool.k_pool[fi], pool.v_pool[fi], self.block_table, ws["bt_row"][ng:],
+                                 ws["ctx"][ng:], ws["part_o"][off * sp.hq * sp.hd:], ws["part_ml"][off * sp.hq * 2:], 1,
+                                 tail, sp.hq, sp.hkv, sp.hd, self.max_blocks, 1, self.scale)
+                mix = ws["mix"].view(-1)[:t * sp.hq * sp.hd].view(t, sp.hq * sp.hd)
+                K.attn_reduce(ws["part_o"], ws["part_ml"], 1, wide, self.qkv_n, t, sp.hq, out=mix, group=self.G)
+                self._gemm(lw.o_proj, mix, ws["y"][:t])
+                fi += 1
+            if self.comm is not None and sp.tp_world > 1:
+                self.comm.allreduce_prefill(ws["y"][:t])
+            K.rmsnorm_pack(h, lw.ln2, delta=ws["y"][:t], out_h=h, normed=x, m=t, k=sp.hidden, group=self.G, eps=sp.eps)
+            gu = ws["wide"].view(-1)[:t * 2 * sp.inter].view(t, 2 * sp.inter)
+            self._gemm(lw.gate_up, x, gu)
+            K.silu_mul(gu, t, sp.inter, out=ws["act"][:t], group=self.G)
+            self._gemm(lw.down, ws["act"][:t], ws["y"][:t])
+            if self.comm is not None and sp.tp_world > 1:
+                self.comm.allreduce_prefill(ws["y"][:t])
+            h.add_(ws["y"][:t])
+            if self.taps is not None and i in self.taps and "prefill" in self.taps:
+                self.taps["prefill"][i] = h.clone()
+        if not want_logits:
+            return None
+        self.h[:1].copy_(h[t - 1:t])
+        self._head(1, sample=True)
+        return self.out_tok[:1]
+
+    def last_hidden(self) -> torch.Tensor:
+        return self.h

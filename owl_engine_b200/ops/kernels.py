@@ -33,6 +33,8 @@ _SIGS = {
     "owl_qknorm_rope_insert": [_P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F,
                                _F, _I, _P],
     "owl_paged_attn": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+    "owl_decode_advance": [_P, _P, _P, _I, _I, _I, _P],
+    "owl_w4_dequant": [_P, _P, _P, _I, _I, _I, _P],
     "owl_attn_reduce": [_P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P],
 }
 _bound: dict = {}
@@ -164,3 +166,15 @@ def attn_reduce(part_o, part_ml, splits: int, qraw, ldq: int, rows: int, hq: int
                 group: int = 128, pdl: bool = False) -> None:
     call("owl_attn_reduce", ptr(part_o), ptr(part_ml), splits, ptr(qraw), ldq, ptr(out), ptr(xpack), ptr(xs), rows, hq,
          group, int(pdl), stream())
+
+
+def w4_dequant(w, out=None):
+    """Dense bf16 [N, K] copy of a ``W4Skinny`` weight (baseline arm / tests)."""
+    if out is None:
+        out = torch.empty(w.n, w.k, dtype=torch.bfloat16, device=w.tiles.device)
+    call("owl_w4_dequant", ptr(w.tiles), ptr(w.sz), ptr(out), w.n, w.k, w.group, stream())
+    return out
+
+
+def decode_advance(inp, tok, block_table, max_blocks: int, b: int, pdl: bool = False) -> None:
+    call("owl_decode_advance", ptr(inp), ptr(tok), ptr(block_table), max_blocks, b, int(pdl), stream())
