@@ -1,5 +1,5 @@
 // ActPack helpers: the fp16 activation format consumed by the W4A16 weight-streaming kernels.
-// Per run of 8 consecutive k the stored order is [x0, x4, x1/16, x5/16, x2, x6, x3/16, x7/16].
+// Per run of 8 consecutive k the stored halves are [x0, x1, x2/16, x3/16, x4, x5, x6/16, x7/16].
 #pragma once
 #include "common.cuh"
 
@@ -17,10 +17,10 @@ __device__ __forceinline__ float clamp_h(float x) { return fminf(fmaxf(x, -65504
 // v: 8 consecutive activations. Returns the packed chunk; s_stored = sum of the 8 stored
 // halves, s_eff = sum of the effective activations (stored * 16 for the pre-scaled slots).
 __device__ __forceinline__ uint4 actpack_chunk(const float* v, float& s_stored, float& s_eff) {
-  const __half h0 = __float2half_rn(clamp_h(v[0])), h1 = __float2half_rn(clamp_h(v[4]));
-  const __half h2 = __float2half_rn(clamp_h(v[1]) * 0.0625f), h3 = __float2half_rn(clamp_h(v[5]) * 0.0625f);
-  const __half h4 = __float2half_rn(clamp_h(v[2])), h5 = __float2half_rn(clamp_h(v[6]));
-  const __half h6 = __float2half_rn(clamp_h(v[3]) * 0.0625f), h7 = __float2half_rn(clamp_h(v[7]) * 0.0625f);
+  const __half h0 = __float2half_rn(clamp_h(v[0])), h1 = __float2half_rn(clamp_h(v[1]));
+  const __half h2 = __float2half_rn(clamp_h(v[2]) * 0.0625f), h3 = __float2half_rn(clamp_h(v[3]) * 0.0625f);
+  const __half h4 = __float2half_rn(clamp_h(v[4])), h5 = __float2half_rn(clamp_h(v[5]));
+  const __half h6 = __float2half_rn(clamp_h(v[6]) * 0.0625f), h7 = __float2half_rn(clamp_h(v[7]) * 0.0625f);
   const float lo = __half2float(h0) + __half2float(h1) + __half2float(h4) + __half2float(h5);
   const float hi = __half2float(h2) + __half2float(h3) + __half2float(h6) + __half2float(h7);
   s_stored = lo + hi;

@@ -301,29 +301,49 @@ __global__ void __launch_bounds__(AT_WARPS * 32) paged_attn_kernel(AttnParams p)
   pdl_launch_dependents();
 }
 
-// grid (rows, hq/4), block 128: warp per (row, head); lane handles 8 dims.
-__global__ void __launch_bounds__(128) attn_reduce_kernel(const float* __restrict__ part_o,
+// grid (rows, hq), block 256: CTA per (row, head); warp w merges splits w, w+8, ... (loads of
+// different splits are independent), lane handles 8 dims; warp 0 combines and finishes.
+__global__ void __launch_bounds__(256) attn_reduce_kernel(const float* __restrict__ part_o,
                                                           const float* __restrict__ part_ml, int splits,
                                                           const __nv_bfloat16* __restrict__ qraw, int ldq,
                                                           __nv_bfloat16* out, uint4* xpack, float2* xs, int hq, int G) {
+  __shared__ float sm_acc[8][HD];
+  __shared__ float sm_l[8];
+  __shared__ float sm_M;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int row = blockIdx.x, head = blockIdx.y;
+  // gate does not depend on the previous kernel's output only when qraw is older; load after the wait
   pdl_wait();
   pdl_launch_dependents();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int row = blockIdx.x, head = blockIdx.y * 4 + warp;
-  if (head >= hq) return;
   const size_t base = ((size_t)row * hq + head) * splits;
-  float M = -INFINITY;
-  for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
+  // global max over splits (every warp computes it: splits <= 64 -> two loads per lane)
+  float mloc = -INFINITY;
+  for (int s = lane; s < splits; s += 32) mloc = fmaxf(mloc, part_ml[(base + s) * 2]);
+  const float M = warp_max(mloc);
   float L = 0.f, acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  for (int s = 0; s < splits; ++s) {
+  for (int s = warp; s < splits; s += 8) {
     const float ms = part_ml[(base + s) * 2];
-    if (ms == -INFINITY) continue;
-    const float w = exp2f(ms - M);
+    const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
     L += w * part_ml[(base + s) * 2 + 1];
     const float4 a = *reinterpret_cast<const float4*>(part_o + (base + s) * HD + lane * 8);
     const float4 b = *reinterpret_cast<const float4*>(part_o + (base + s) * HD + lane * 8 + 4);
     acc[0] += w * a.x; acc[1] += w * a.y; acc[2] += w * a.z; acc[3] += w * a.w;
     acc[4] += w * b.x; acc[5] += w * b.y; acc[6] += w * b.z; acc[7] += w * b.w;
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) sm_acc[warp][lane * 8 + i] = acc[i];
+  if (lane == 0) sm_l[warp] = L;
+  __syncthreads();
+  if (warp != 0) return;
+  L = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) L += sm_l[w];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float a = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) a += sm_acc[w][lane * 8 + i];
+    acc[i] = a;
   }
   const float inv = L > 0.f ? 1.f / L : 0.f;
   float v[8];
@@ -408,7 +428,7 @@ OWL_API int owl_attn_reduce(const void* part_o, const void* part_ml, int splits,
                             void* xpack, void* xs, int rows, int hq, int G, int pdl, cudaStream_t st) {
   if (rows < 1 || splits < 1 || (G != 32 && G != 128)) return OWL_ERR_BAD_ARG;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(rows, (hq + 3) / 4); cfg.blockDim = dim3(128); cfg.stream = st;
+  cfg.gridDim = dim3(rows, hq); cfg.blockDim = dim3(256); cfg.stream = st;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;

@@ -4,24 +4,32 @@
 // Reference counterpart: owl_gguf_dequant_range_* + cuBLAS arm (crates/kernels/cu/gguf/gguf_smem.cu).
 #include "common.cuh"
 
+#include "records.cuh"
+
 namespace owl {
 // grid (K/128, N/16), block 64: thread L handles uint4 #L of the tile (row, 4 words of 8 nibbles).
-__global__ void __launch_bounds__(64) w4_dequant_kernel(const uint4* __restrict__ tiles, const __half2* __restrict__ sz,
-                                                        __nv_bfloat16* out, int N, int K, int G) {
+__global__ void __launch_bounds__(64) w4_dequant_kernel(const uint8_t* __restrict__ records, __nv_bfloat16* out, int N,
+                                                        int K, int G) {
   const int kt = blockIdx.x, nt = blockIdx.y, L = threadIdx.x;
   const int KT = K >> 7, GPT = 128 / G;
   const int half = L >> 5, g = (L & 31) >> 2, t = L & 3;
   const int row = nt * 16 + half * 8 + g;
-  const uint4 u = tiles[((size_t)nt * KT + kt) * 64 + L];
+  const int REC = 1024 + 64 * GPT;
+  const uint8_t* rec = records + record_offset(N / 16, KT, nt, kt) * (size_t)REC;
+  const uint4 u = reinterpret_cast<const uint4*>(rec)[L];
+  const __half2* sz = reinterpret_cast<const __half2*>(rec + 1024);
   const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
   for (int wi = 0; wi < 4; ++wi) {
-    const int kg = (G == 128) ? kt : kt * 4 + wi;
-    const __half2 s = sz[((size_t)nt * KT * GPT + kg) * 16 + half * 8 + g];
+    const int q = (G == 128) ? 0 : wi;
+    const __half2 s = sz[q * 16 + half * 8 + g];
     const float sc = __low2float(s), z = __high2float(s);
     float v[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = ((float)((w[wi] >> (4 * i)) & 0xF) - z) * sc;
+    for (int i = 0; i < 8; ++i) {
+      const int nib = (i >> 1) + (i & 1) * 4;   // k_local i sits at nibble (i/2) + 4*(i%2)
+      v[i] = ((float)((w[wi] >> (4 * nib)) & 0xF) - z) * sc;
+    }
     uint4 o = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
     *reinterpret_cast<uint4*>(out + (size_t)row * K + kt * 128 + wi * 32 + t * 8) = o;
   }
@@ -29,10 +37,9 @@ __global__ void __launch_bounds__(64) w4_dequant_kernel(const uint4* __restrict_
 }  // namespace owl
 using namespace owl;
 
-OWL_API int owl_w4_dequant(const void* tiles, const void* sz, void* out, int N, int K, int G, cudaStream_t st) {
+OWL_API int owl_w4_dequant(const void* records, void* out, int N, int K, int G, cudaStream_t st) {
   if ((N & 15) || (K & 127) || (G != 32 && G != 128)) return OWL_ERR_BAD_ARG;
-  w4_dequant_kernel<<<dim3(K / 128, N / 16), 64, 0, st>>>((const uint4*)tiles, (const __half2*)sz, (__nv_bfloat16*)out,
-                                                          N, K, G);
+  w4_dequant_kernel<<<dim3(K / 128, N / 16), 64, 0, st>>>((const uint8_t*)records, (__nv_bfloat16*)out, N, K, G);
   OWL_LAUNCH_CHECK();
   return OWL_OK;
 }

@@ -62,7 +62,9 @@ __global__ void __launch_bounds__(256) gdn_decode_kernel(GdnDecodeParams p) {
   const int hk = h / R;
   const unsigned rank = (R > 1) ? cluster.block_rank() : 0;
   const int K = p.nk * GD, V = p.nv * GD, conv_dim = 2 * K + V;
-  pdl_wait();
+  // The recurrent / convolution state and the step inputs (slots) are not written by the
+  // preceding kernels of the same forward pass, so they are fetched before the
+  // programmatic-dependency wait and overlap the predecessor's tail.
   const int slot = p.slots[b];
   // Padding rows still take part in the cluster barriers (slot is uniform per cluster).
   const bool live = slot >= 0;
@@ -99,6 +101,10 @@ __global__ void __launch_bounds__(256) gdn_decode_kernel(GdnDecodeParams p) {
   }
   const float a_log = p.a_log[h], dt_bias = p.dt_bias[h];
   const float scale = rsqrtf((float)GD);
+  const float4 gam4 = *reinterpret_cast<const float4*>(p.gamma + lane * 4);
+  const float gam[4] = {gam4.x, gam4.y, gam4.z, gam4.w};
+  pdl_wait();
+  pdl_launch_dependents();
 
   for (int r = 0; r < p.T; ++r) {
     const size_t row = (size_t)b * p.T + r;
@@ -193,7 +199,7 @@ __global__ void __launch_bounds__(256) gdn_decode_kernel(GdnDecodeParams p) {
       for (int j = 0; j < 4; ++j) {
         const int vi = lane * 4 + j;
         const float z = live ? __bfloat162float(xr[2 * K + V + h * GD + vi]) : 0.f;
-        y[j] = __bfloat162float(__float2bfloat16(o[j] * rinv * p.gamma[vi] * silu_f(z)));
+        y[j] = __bfloat162float(__float2bfloat16(o[j] * rinv * gam[j] * silu_f(z)));
         o_s[vi] = y[j];
       }
       if (live && p.out) {
@@ -220,7 +226,6 @@ __global__ void __launch_bounds__(256) gdn_decode_kernel(GdnDecodeParams p) {
     // qk_s is double buffered, v_s/part/scal are rewritten only after the next barrier pair.
     __syncthreads();
   }
-  pdl_launch_dependents();
   if (live) {
 #pragma unroll
     for (int i = 0; i < 16; ++i)

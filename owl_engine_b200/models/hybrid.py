@@ -37,7 +37,8 @@ class LayerWeights:
     down: object
     # gdn
     qkvz: object = None
-    ab: torch.Tensor = None
+    ab: object = None               # DenseSkinny [pad16(2*nv), H]: in_proj_a rows then in_proj_b rows
+    ab_dense: torch.Tensor = None   # same rows as plain bf16 [pad16(2*nv), H] for the prefill GEMM
     conv_w: torch.Tensor = None
     a_log: torch.Tensor = None
     dt_bias: torch.Tensor = None
@@ -55,22 +56,22 @@ class HybridWeights:
     spec: ModelSpec
     embed: torch.Tensor
     final_norm: torch.Tensor
-    lm_head: torch.Tensor            # bf16 [V, H] (vocab shard with TP vocab split) or None when lm_head_q is set
+    lm_head: object                  # DenseSkinny (bf16 or int8 records), [V or vocab shard, H]
     layers: list
     group: int
-    lm_head_q: torch.Tensor = None   # int8 rows
-    lm_head_s: torch.Tensor = None
     vocab_offset: int = 0
 
     def nbytes(self) -> int:
-        n = self.embed.numel() * 2 + (self.lm_head.numel() * 2 if self.lm_head is not None else 0)
-        if self.lm_head_q is not None:
-            n += self.lm_head_q.numel()
+        n = self.embed.numel() * 2 + self.lm_head.nbytes
         for l in self.layers:
-            for w in (l.gate_up, l.down, l.qkvz, l.out_proj, l.qkv, l.o_proj):
+            for w in (l.gate_up, l.down, l.qkvz, l.out_proj, l.qkv, l.o_proj, l.ab):
                 if w is not None:
                     n += w.nbytes
         return n
+
+    def streamed_bytes(self) -> int:
+        """Bytes one decode step must read from HBM (everything but the embedding table)."""
+        return self.nbytes() - self.embed.numel() * 2
 
 
 def _pad16_rows(w: torch.Tensor) -> torch.Tensor:
@@ -121,7 +122,8 @@ def weights_from_dense(spec: ModelSpec, dense: dict, device, group: int = 128, l
             lw.qkvz = w4(qkvz, [(a + "in_proj_qkv.weight", spec.conv_dim), (a + "in_proj_z.weight", spec.value_dim)])
             ab = torch.cat([dense[a + "in_proj_a.weight"], dense[a + "in_proj_b.weight"]]).to(torch.bfloat16)
             equiv[a + "in_proj_a.weight"], equiv[a + "in_proj_b.weight"] = ab[:spec.nv].float(), ab[spec.nv:].float()
-            lw.ab = _pad16_rows(ab).to(device)
+            lw.ab_dense = _pad16_rows(ab).to(device)
+            lw.ab = Q.dense_skinny(lw.ab_dense, device)
             lw.conv_w = f32(dense[a + "conv1d.weight"].reshape(spec.conv_dim, spec.conv_k))
             lw.a_log, lw.dt_bias = f32(dense[a + "A_log"]), f32(dense[a + "dt_bias"])
             lw.gamma = f32(dense[a + "norm.weight"])
@@ -142,12 +144,11 @@ def weights_from_dense(spec: ModelSpec, dense: dict, device, group: int = 128, l
     equiv["model.norm.weight"] = dense["model.norm.weight"].to(torch.bfloat16).float()
     hw = HybridWeights(spec=spec, embed=emb.to(device), final_norm=bf(dense["model.norm.weight"]), lm_head=None,
                        layers=layers, group=group)
+    hw.lm_head = Q.dense_skinny(head.to(device), device, int8=lm_head_int8)
     if lm_head_int8:
         q8, s8 = Q.quantize_w8_rows(head.float())
-        hw.lm_head_q, hw.lm_head_s = q8.to(device), s8.to(device)
         equiv["lm_head.weight"] = q8.float() * s8[:, None]
     else:
-        hw.lm_head = head.to(device)
         equiv["lm_head.weight"] = head.float()
     return hw, equiv
 
@@ -168,7 +169,8 @@ def random_weights(spec: ModelSpec, device, group: int = 128, seed: int = 0, lm_
                           down=Q.random_skinny(H, spec.inter, group, device, std, sd + 2))
         if lw.kind == "gdn":
             lw.qkvz = Q.random_skinny(spec.conv_dim + spec.value_dim, H, group, device, std, sd + 3)
-            lw.ab = _pad16_rows(rnd(2 * spec.nv, H).to(torch.bfloat16))
+            lw.ab_dense = _pad16_rows(rnd(2 * spec.nv, H).to(torch.bfloat16))
+            lw.ab = Q.dense_skinny(lw.ab_dense, device)
             lw.conv_w = (torch.randn(spec.conv_dim, spec.conv_k, device=device, generator=gen) * 0.2)
             lw.a_log = torch.log(torch.empty(spec.nv, device=device).uniform_(1.0, 16.0, generator=gen))
             lw.dt_bias = torch.ones(spec.nv, device=device)
@@ -183,10 +185,11 @@ def random_weights(spec: ModelSpec, device, group: int = 128, seed: int = 0, lm_
     hw = HybridWeights(spec=spec, embed=emb, final_norm=torch.zeros(H, dtype=torch.bfloat16, device=device),
                        lm_head=None, layers=layers, group=group)
     if lm_head_int8:
-        hw.lm_head_q = torch.randint(-127, 128, (spec.vocab, H), device=device, dtype=torch.int8, generator=gen)
-        hw.lm_head_s = torch.full((spec.vocab,), std / 40.0, device=device)
+        q8 = torch.randint(-127, 128, (spec.vocab, H), device=device, dtype=torch.int8, generator=gen)
+        hw.lm_head = Q.DenseSkinny(Q.pack_dense_int8(q8), spec.vocab, H, "int8",
+                                   torch.full((spec.vocab,), std / 40.0, device=device))
     else:
-        hw.lm_head = emb if spec.tied else rnd(spec.vocab, H).to(torch.bfloat16)
+        hw.lm_head = Q.dense_skinny(emb if spec.tied else rnd(spec.vocab, H).to(torch.bfloat16), device)
     return hw
 
 
@@ -276,9 +279,9 @@ class HybridRunner:
         self.part_o = f32(M * spec.hq * self.max_splits * spec.hd)
         self.part_ml = f32(M * spec.hq * self.max_splits * 2)
         self.xp_a, self.xs_a = f16(M, spec.hq * spec.hd), f32(M, spec.hq * spec.hd // G, 2)
-        self.act = bf(M, spec.inter)
+        self.side = torch.cuda.Stream(device=dev)   # forked branch for the small a/b projection
         self.xp_i, self.xs_i = f16(M, spec.inter), f32(M, spec.inter // G, 2)
-        self.vocab_local = (weights.lm_head if weights.lm_head is not None else weights.lm_head_q).shape[0]
+        self.vocab_local = weights.lm_head.n
         self.logits = bf(M, self.vocab_local)
         self.am_parts = 64
         self.am_val, self.am_idx = f32(M * self.am_parts), torch.zeros(M * self.am_parts, dtype=torch.int32, device=dev)
@@ -311,19 +314,24 @@ class HybridRunner:
         sp = self.spec
         K.rmsnorm_pack(self.h, lw.ln2, xpack=self.xp_h, xs=self.xs_h, m=m, k=sp.hidden, group=self.G, eps=sp.eps,
                        pdl=self.pdl)
-        K.w4a16_skinny(lw.gate_up, self.xp_h, self.xs_h, self.act, m, epi=K.EPI_SILU_MUL, ldo=sp.inter, pdl=self.pdl)
-        K.act_pack(self.act, self.xp_i, self.xs_i, m, sp.inter, self.G, pdl=self.pdl)
+        K.w4a16_skinny(lw.gate_up, self.xp_h, self.xs_h, None, m, epi=K.EPI_SILU_PACK, ldo=sp.inter,
+                       out_pack=self.xp_i, out_xs=self.xs_i, gout=self.G, pdl=self.pdl)
         self._row_parallel(lw.down, self.xp_i, self.xs_i, m)
 
     def _gdn(self, lw: LayerWeights, li: int, lay: StepLayout, v: dict) -> None:
         sp, m = self.spec, lay.m
         K.rmsnorm_pack(self.h, lw.ln1, normed=self.xn, xpack=self.xp_h, xs=self.xs_h, m=m, k=sp.hidden, group=self.G,
                        eps=sp.eps, pdl=self.pdl)
-        K.w4a16_skinny(lw.qkvz, self.xp_h, self.xs_h, self.qkvz_out, m, pdl=self.pdl)
-        K.bf16_skinny(lw.ab, self.xn, self.ab_out, m, pdl=self.pdl)
+        # fork: the tiny dense a/b projection runs beside the big qkvz stream
+        main = torch.cuda.current_stream()
+        self.side.wait_stream(main)
+        with torch.cuda.stream(self.side):
+            K.dense_skinny(lw.ab, self.xn, self.ab_out, m, pdl=False)
+        K.w4a16_skinny(lw.qkvz, self.xp_h, self.xs_h, self.qkvz_out, m, pdl=False)
+        main.wait_stream(self.side)
         K.gdn_decode(self.qkvz_out, self.qkvz_out.shape[1], self.ab_out, self.ldab, lw.conv_w, lw.a_log, lw.dt_bias,
                      lw.gamma, self.pool.conv_state[li], self.pool.rec_state[li], v["gslot"], xpack=self.xp_v,
-                     xs=self.xs_v, batch=lay.b, t=lay.t, nk=sp.nk, nv=sp.nv, group=self.G, eps=sp.eps, pdl=self.pdl)
+                     xs=self.xs_v, batch=lay.b, t=lay.t, nk=sp.nk, nv=sp.nv, group=self.G, eps=sp.eps, pdl=False)
         self._row_parallel(lw.out_proj, self.xp_v, self.xs_v, m)
 
     def _pick_splits(self, b: int, ctx_hint: int) -> int:
@@ -355,10 +363,7 @@ class HybridRunner:
     def _head(self, m: int, sample: bool = True) -> None:
         sp, w = self.spec, self.w
         K.rmsnorm_pack(self.h, w.final_norm, normed=self.xn, m=m, k=sp.hidden, group=self.G, eps=sp.eps, pdl=self.pdl)
-        if w.lm_head_q is not None:
-            K.w8a16_skinny(w.lm_head_q, w.lm_head_s, self.xn, self.logits, m, pdl=self.pdl)
-        else:
-            K.bf16_skinny(w.lm_head, self.xn, self.logits, m, pdl=self.pdl)
+        K.dense_skinny(w.lm_head, self.xn, self.logits, m, pdl=self.pdl)
         if sample:
             K.argmax(self.logits, m, self.vocab_local, self.vocab_local, self.am_val, self.am_idx, self.am_parts,
                      self.out_tok, w.vocab_offset, pdl=self.pdl)
@@ -480,7 +485,7 @@ class HybridRunner:
                 wide = ws["wide"].view(-1)[:t * nq].view(t, nq)
                 self._gemm(lw.qkvz, x, wide)
                 ab = ws["ab"][:t]
-                torch.matmul(x, lw.ab.t(), out=ab)
+                torch.matmul(x, lw.ab_dense.t(), out=ab)
                 conv = ws["conv"][:t]
                 K.gdn_conv_fwd(wide, nq, lw.conv_w, pool.conv_state[gi], gdn_slot, conv, t, sp.nk, sp.nv, use_state)
                 mix = ws["mix"].view(-1)[:t * sp.value_dim].view(t, sp.value_dim)

@@ -1,0 +1,35 @@
+"""Python entry points of the tcgen05 / TMEM GEMM kernels (``csrc/gemm_tc.cu``)."""
+from __future__ import annotations
+
+from ctypes import c_int, c_void_p
+
+import torch
+
+from . import kernels as K
+
+K.register("owl_w4a16_gemm_tc", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+K.register("owl_f16_gemm_tc", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+
+
+def w4a16_gemm(w, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[T, N] (bf16) = x[T, K] (fp16) @ dequant(w)^T on the tcgen05 path."""
+    assert x.dtype == torch.float16 and out.dtype == torch.bfloat16 and x.stride(-1) == 1 and out.stride(-1) == 1
+    t = x.shape[0]
+    K.call("owl_w4a16_gemm_tc", K.ptr(x), x.stride(0), K.ptr(w.records), K.ptr(out), t, w.n, w.k, out.stride(0), w.group,
+           K.stream())
+    return out
+
+
+def f16_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[T, N] (bf16) = x[T, K] @ w[N, K]^T with fp16 or bf16 operands on the tcgen05 path."""
+    assert x.dtype == w.dtype and x.dtype in (torch.float16, torch.bfloat16) and out.dtype == torch.bfloat16
+    t, k = x.shape
+    K.call("owl_f16_gemm_tc", K.ptr(x), x.stride(0), K.ptr(w), w.stride(0), K.ptr(out), t, w.shape[0], k, out.stride(0),
+           1 if x.dtype == torch.bfloat16 else 0, K.stream())
+    return out
+
+
+def gemm_status() -> int:
+    f = K.fn("owl_gemm_status")
+    f.argtypes = []
+    return f()

@@ -18,7 +18,7 @@ _I = c_int
 _F = c_float
 
 _SIGS = {
-    "owl_w4a16_skinny": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "owl_w4a16_skinny": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "owl_bf16_skinny": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "owl_w8a16_skinny": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "owl_rmsnorm_pack": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _I, _I, _P],
@@ -34,7 +34,7 @@ _SIGS = {
                                _F, _I, _P],
     "owl_paged_attn": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "owl_decode_advance": [_P, _P, _P, _I, _I, _I, _P],
-    "owl_w4_dequant": [_P, _P, _P, _I, _I, _I, _P],
+    "owl_w4_dequant": [_P, _P, _I, _I, _I, _P],
     "owl_attn_reduce": [_P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P],
 }
 _bound: dict = {}
@@ -71,32 +71,36 @@ def call(name: str, *args) -> None:
         _native.check(rc, name)
 
 
-EPI_STORE, EPI_RESIDUAL, EPI_SILU_MUL, EPI_F32 = 0, 1, 2, 3
+EPI_STORE, EPI_RESIDUAL, EPI_SILU_MUL, EPI_F32, EPI_SILU_PACK = 0, 1, 2, 3, 4
 
 
 def w4a16_skinny(w, xpack, xs, out, m: int, *, residual=None, epi: int = EPI_STORE, ldo: int | None = None,
-                 ks: int = 0, pdl: bool = False) -> None:
+                 out_pack=None, out_xs=None, gout: int = 128, tiles_per_cta: int = 0, pdl: bool = False) -> None:
     """out[m, :] = dequant(w) @ x for m <= 32 rows. ``w`` is a ``W4Skinny``."""
     if ldo is None:
-        ldo = out.shape[-1]
-    call("owl_w4a16_skinny", ptr(w.tiles), ptr(w.sz), ptr(xpack), ptr(xs), ptr(out), ptr(residual), m, w.n, w.k, ldo,
-         w.group, epi, ks, int(pdl), stream())
+        ldo = out.shape[-1] if out is not None else w.n
+    call("owl_w4a16_skinny", ptr(w.records), ptr(xpack), ptr(xs), ptr(out), ptr(residual), ptr(out_pack), ptr(out_xs),
+         m, w.n, w.k, ldo, w.group, epi, gout, tiles_per_cta, int(pdl), stream())
 
 
-def bf16_skinny(w, x, out, m: int, *, residual=None, epi: int = EPI_STORE, ldo: int | None = None, ks: int = 0,
-                pdl: bool = False) -> None:
-    n, k = w.shape
+def dense_skinny(w, x, out, m: int, *, residual=None, epi: int = EPI_STORE, ldo: int | None = None,
+                 tiles_per_cta: int = 0, pdl: bool = False) -> None:
+    """out[m, :] = W @ x for a ``DenseSkinny`` weight (bf16 records or int8 records + row scale)."""
     if ldo is None:
         ldo = out.shape[-1]
-    call("owl_bf16_skinny", ptr(w), ptr(x), ptr(out), ptr(residual), m, n, k, ldo, epi, ks, int(pdl), stream())
+    if w.kind == "int8":
+        call("owl_w8a16_skinny", ptr(w.records), ptr(w.row_scale), ptr(x), ptr(out), m, w.n, w.k, ldo, epi,
+             tiles_per_cta, int(pdl), stream())
+    else:
+        call("owl_bf16_skinny", ptr(w.records), ptr(x), ptr(out), ptr(residual), m, w.n, w.k, ldo, epi, tiles_per_cta,
+             int(pdl), stream())
 
 
-def w8a16_skinny(wq, row_scale, x, out, m: int, *, epi: int = EPI_STORE, ldo: int | None = None, ks: int = 0,
-                 pdl: bool = False) -> None:
-    n, k = wq.shape
-    if ldo is None:
-        ldo = out.shape[-1]
-    call("owl_w8a16_skinny", ptr(wq), ptr(row_scale), ptr(x), ptr(out), m, n, k, ldo, epi, ks, int(pdl), stream())
+def skinny_status() -> int:
+    """First bounded-wait failure recorded by a weight-streaming kernel (0 = none); clears it."""
+    f = fn("owl_skinny_status")
+    f.argtypes = []
+    return f()
 
 
 def rmsnorm_pack(h, w, *, delta=None, out_h=None, normed=None, xpack=None, xs=None, m: int, k: int, group: int = 128,
@@ -171,8 +175,8 @@ def attn_reduce(part_o, part_ml, splits: int, qraw, ldq: int, rows: int, hq: int
 def w4_dequant(w, out=None):
     """Dense bf16 [N, K] copy of a ``W4Skinny`` weight (baseline arm / tests)."""
     if out is None:
-        out = torch.empty(w.n, w.k, dtype=torch.bfloat16, device=w.tiles.device)
-    call("owl_w4_dequant", ptr(w.tiles), ptr(w.sz), ptr(out), w.n, w.k, w.group, stream())
+        out = torch.empty(w.n, w.k, dtype=torch.bfloat16, device=w.records.device)
+    call("owl_w4_dequant", ptr(w.records), ptr(out), w.n, w.k, w.group, stream())
     return out
 
 

@@ -69,45 +69,97 @@ def deinterleave_gate_up(y: torch.Tensor):
     return v[..., 0, :].reshape(*lead, i2 // 2), v[..., 1, :].reshape(*lead, i2 // 2)
 
 
+K_SLICES = 8   # record streams are stored slice-major: [slice][row tile][record in slice]
+
+
+def _slice_bounds(kt: int):
+    return [(w * kt) // K_SLICES for w in range(K_SLICES + 1)]
+
+
+def to_slice_major(rec: torch.Tensor) -> torch.Tensor:
+    """[NT, KT, REC] -> flat bytes ordered [slice w][nt][kt in slice w] (slice w = record columns
+    [w*KT/8, (w+1)*KT/8)), so that one warp of the streaming kernel reads one contiguous range."""
+    nt, kt, r = rec.shape
+    b = _slice_bounds(kt)
+    return torch.cat([rec[:, b[w]:b[w + 1], :].reshape(-1) for w in range(K_SLICES)])
+
+
+def from_slice_major(flat: torch.Tensor, nt: int, kt: int, r: int) -> torch.Tensor:
+    b = _slice_bounds(kt)
+    out = torch.empty(nt, kt, r, dtype=flat.dtype, device=flat.device)
+    off = 0
+    for w in range(K_SLICES):
+        n = nt * (b[w + 1] - b[w]) * r
+        out[:, b[w]:b[w + 1], :] = flat[off:off + n].view(nt, b[w + 1] - b[w], r)
+        off += n
+    return out
+
+
+def record_offset(nt_total: int, kt_total: int, rec_bytes: int, nt: int, kt: int) -> int:
+    """Byte offset of record (nt, kt) in a slice-major stream (host mirror of the device formula)."""
+    b = _slice_bounds(kt_total)
+    w = max(i for i in range(K_SLICES) if b[i] <= kt and b[i] < b[i + 1] or i == 0)
+    while not (b[w] <= kt < b[w + 1]):
+        w += 1
+    return (nt_total * b[w] + nt * (b[w + 1] - b[w]) + (kt - b[w])) * rec_bytes
+
+
+# Inside a 32-bit word of 8 nibbles, k_local j sits at nibble position _NIB_OF_K[j], so that
+# (q & 0x000F000F) yields the pair (k0, k1), (q & 0x00F000F0) the pair (k2, k3), and the same on
+# q >> 8 the pairs (k4, k5), (k6, k7): dequantised halves come out in k order.
+_NIB_OF_K = [0, 4, 1, 5, 2, 6, 3, 7]
+_K_OF_NIB = [0, 2, 4, 6, 1, 3, 5, 7]
+
+
 @dataclass
 class W4Skinny:
-    """Device-ready W4 weight: tile stream + (scale, zero) table."""
-    tiles: torch.Tensor   # uint8 [N/16, K/128, 1024]
-    sz: torch.Tensor      # fp16 [N/16, K/G, 16, 2]
+    """Device-ready W4 weight: a flat slice-major stream of ``N/16 x K/128`` records of
+    ``1024 + 64*(128/G)`` bytes. Each record is 1024 bytes of nibbles followed by the (scale, zero)
+    half2 pairs of its groups."""
+    records: torch.Tensor
     n: int
     k: int
     group: int
 
     def to(self, device):
-        return W4Skinny(self.tiles.to(device), self.sz.to(device), self.n, self.k, self.group)
+        return W4Skinny(self.records.to(device), self.n, self.k, self.group)
 
     @property
     def nbytes(self) -> int:
-        return self.tiles.numel() + self.sz.numel() * 2
+        return self.records.numel()
+
+    @property
+    def rec_bytes(self) -> int:
+        return 1024 + 64 * (128 // self.group)
 
 
 def pack_skinny(c: W4Canonical) -> W4Skinny:
     n, k = c.q.shape
     assert n % 16 == 0 and k % 128 == 0, (n, k)
     nt, kt = n // 16, k // 128
-    # q[nt*16 + half*8 + g, kt*128 + w*32 + t*8 + i] -> tiles[nt, kt, half, g, t, w, i]
-    v = c.q.view(nt, 2, 8, kt, 4, 4, 8).permute(0, 3, 1, 2, 5, 4, 6).contiguous()
+    # q[nt*16 + half*8 + g, kt*128 + w*32 + t*8 + j] -> tiles[nt, kt, half, g, t, w, nibble NIB[j]]
+    v = c.q.view(nt, 2, 8, kt, 4, 4, 8).permute(0, 3, 1, 2, 5, 4, 6)[..., _K_OF_NIB].contiguous()
     lo, hi = v[..., 0::2], v[..., 1::2]
     tiles = (lo | (hi << 4)).to(torch.uint8).reshape(nt, kt, 1024)
     kg = k // c.group
+    gpt = 128 // c.group
     sz = torch.stack([c.scales.view(nt, 16, kg).permute(0, 2, 1),
                       c.zeros.view(nt, 16, kg).permute(0, 2, 1).to(torch.float16)], dim=-1).contiguous()
-    return W4Skinny(tiles, sz, n, k, c.group)
+    szb = sz.view(torch.uint8).reshape(nt, kt, gpt * 64)
+    return W4Skinny(to_slice_major(torch.cat([tiles, szb], dim=-1)), n, k, c.group)
 
 
 def unpack_skinny(s: W4Skinny) -> W4Canonical:
     nt, kt = s.n // 16, s.k // 128
-    b = s.tiles.view(nt, kt, 2, 8, 4, 4, 4)
-    v = torch.stack([b & 0xF, b >> 4], dim=-1).reshape(nt, kt, 2, 8, 4, 4, 8)
+    gpt = 128 // s.group
+    rec = from_slice_major(s.records, nt, kt, s.rec_bytes)
+    b = rec[..., :1024].reshape(nt, kt, 2, 8, 4, 4, 4)
+    sz = rec[..., 1024:].contiguous().view(torch.float16).reshape(nt, kt * gpt, 16, 2)
+    v = torch.stack([b & 0xF, b >> 4], dim=-1).reshape(nt, kt, 2, 8, 4, 4, 8)[..., _NIB_OF_K]
     q = v.permute(0, 2, 3, 1, 5, 4, 6).reshape(s.n, s.k).contiguous()
     kg = s.k // s.group
-    scales = s.sz[..., 0].permute(0, 2, 1).reshape(s.n, kg).contiguous()
-    zeros = s.sz[..., 1].permute(0, 2, 1).reshape(s.n, kg).to(torch.uint8).contiguous()
+    scales = sz[..., 0].permute(0, 2, 1).reshape(s.n, kg).contiguous()
+    zeros = sz[..., 1].permute(0, 2, 1).reshape(s.n, kg).to(torch.uint8).contiguous()
     return W4Canonical(q, scales, zeros, s.group)
 
 
@@ -122,20 +174,78 @@ def random_skinny(n: int, k: int, group: int, device, std: float = 0.02, seed: i
     vals = (torch.randn(nt, kt, 2048, device=device, generator=gen) * 2.5 + 8.0).round().clamp_(0, 15).to(torch.uint8)
     tiles = (vals[..., 0::2] | (vals[..., 1::2] << 4)).contiguous()
     kg = k // group
+    gpt = 128 // group
     sz = torch.empty(nt, kg, 16, 2, dtype=torch.float16, device=device)
     sz[..., 0] = (std / 2.5) * (1.0 + 0.1 * torch.rand(nt, kg, 16, device=device, generator=gen))
     sz[..., 1] = torch.randint(7, 10, (nt, kg, 16), device=device, generator=gen).to(torch.float16)
-    return W4Skinny(tiles, sz, n, k, group)
+    szb = sz.view(torch.uint8).reshape(nt, kt, gpt * 64)
+    # a random stream is layout-agnostic: any record order is an equally random weight
+    return W4Skinny(torch.cat([tiles, szb], dim=-1).reshape(-1).contiguous(), n, k, group)
+
+
+def pack_dense_bf16(w: torch.Tensor) -> torch.Tensor:
+    """Dense bf16 ``[N, K]`` -> skinny records ``[N/16, K/64, 2048]`` bytes (see csrc/gemv.cu):
+    uint4 #((s*2+half)*32 + g*4+t) holds row half*8+g, k = s*32 + t*8 .. +7."""
+    n, k = w.shape
+    assert n % 16 == 0 and k % 64 == 0, (n, k)
+    v = w.to(torch.bfloat16).view(n // 16, 2, 8, k // 64, 2, 4, 8)      # nt, half, g, kt, s, t, e
+    v = v.permute(0, 3, 4, 1, 2, 5, 6).contiguous()                      # nt, kt, s, half, g, t, e
+    return to_slice_major(v.view(torch.uint8).reshape(n // 16, k // 64, 2048))
+
+
+def unpack_dense_bf16(rec: torch.Tensor, n: int, k: int) -> torch.Tensor:
+    rec = from_slice_major(rec, n // 16, k // 64, 2048)
+    v = rec.contiguous().view(torch.bfloat16).reshape(n // 16, k // 64, 2, 2, 8, 4, 8)
+    return v.permute(0, 3, 4, 1, 2, 5, 6).reshape(n, k)
+
+
+def pack_dense_int8(q: torch.Tensor) -> torch.Tensor:
+    """int8 ``[N, K]`` -> records ``[N/16, K/128, 2048]``: uint4 #((s*2+half)*32 + g*4+t) holds
+    row half*8+g, k = s*64 + t*16 .. +15."""
+    n, k = q.shape
+    assert n % 16 == 0 and k % 128 == 0, (n, k)
+    v = q.view(n // 16, 2, 8, k // 128, 2, 4, 16).permute(0, 3, 4, 1, 2, 5, 6).contiguous()
+    return to_slice_major(v.view(torch.uint8).reshape(n // 16, k // 128, 2048))
+
+
+@dataclass
+class DenseSkinny:
+    """Dense weight in skinny-record layout. ``kind`` is "bf16" or "int8" (``row_scale`` set)."""
+    records: torch.Tensor
+    n: int
+    k: int
+    kind: str = "bf16"
+    row_scale: torch.Tensor = None
+
+    @property
+    def nbytes(self) -> int:
+        return self.records.numel()
+
+    @property
+    def shape(self):
+        return (self.n, self.k)
+
+
+def dense_skinny(w: torch.Tensor, device=None, int8: bool = False) -> DenseSkinny:
+    n, k = w.shape
+    if int8:
+        q, s = quantize_w8_rows(w)
+        d = DenseSkinny(pack_dense_int8(q), n, k, "int8", s)
+    else:
+        d = DenseSkinny(pack_dense_bf16(w), n, k, "bf16")
+    if device is not None:
+        d.records = d.records.to(device)
+        if d.row_scale is not None:
+            d.row_scale = d.row_scale.to(device)
+    return d
 
 
 # ---- ActPack -----------------------------------------------------------------------------
-_PERM = [0, 4, 1, 5, 2, 6, 3, 7]
-
-
 def act_pack_ref(x: torch.Tensor, group: int):
-    """fp32 reference of the ActPack producer: returns (xpack fp16 [M,K], xs fp32 [M,K/G,2])."""
+    """fp32 reference of the ActPack producer: returns (xpack fp16 [M,K], xs fp32 [M,K/G,2]).
+    Per 8 consecutive k the stored halves are [x0, x1, x2/16, x3/16, x4, x5, x6/16, x7/16]."""
     m, k = x.shape
-    v = x.to(torch.float32).clamp(-65504, 65504).view(m, k // 8, 8)[..., _PERM].clone()
+    v = x.to(torch.float32).clamp(-65504, 65504).view(m, k // 8, 8).clone()
     v[..., [2, 3, 6, 7]] *= 0.0625
     h = v.to(torch.float16)
     hf = h.to(torch.float32)

@@ -1,0 +1,43 @@
+"""tcgen05 GEMM numerics against fp32 torch references."""
+import pytest
+import torch
+
+from owl_engine_b200.ops import gemm_tc, quant as Q
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def gen(s):
+    return torch.Generator().manual_seed(s)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(128, 128, 64), (300, 256, 512), (77, 384, 192), (1024, 1024, 1024)])
+def test_dense_gemm(dtype, shape):
+    t, n, k = shape
+    x = (torch.randn(t, k, generator=gen(1))).to(dtype)
+    w = (torch.randn(n, k, generator=gen(2)) * 0.05).to(dtype)
+    out = torch.zeros(t, n, dtype=torch.bfloat16, device=DEV)
+    gemm_tc.f16_gemm(x.to(DEV), w.to(DEV), out)
+    torch.cuda.synchronize()
+    assert gemm_tc.gemm_status() == 0
+    want = x.float() @ w.float().t()
+    err = (out.float().cpu() - want).norm() / want.norm()
+    assert err < 4e-3, err
+
+
+@pytest.mark.parametrize("group", [128, 32])
+@pytest.mark.parametrize("shape", [(128, 128, 128), (200, 256, 512), (37, 3584, 256), (512, 1024, 2176)])
+def test_w4a16_gemm(group, shape):
+    t, n, k = shape
+    c = Q.quantize_w4(torch.randn(n, k, generator=gen(3)) * 0.05, group)
+    w = Q.pack_skinny(c).to(DEV)
+    x = torch.randn(t, k, generator=gen(4)).to(torch.float16)
+    out = torch.zeros(t, n, dtype=torch.bfloat16, device=DEV)
+    gemm_tc.w4a16_gemm(w, x.to(DEV), out)
+    torch.cuda.synchronize()
+    assert gemm_tc.gemm_status() == 0
+    want = x.float() @ c.dequant().t()
+    err = (out.float().cpu() - want).norm() / want.norm()
+    assert err < 4e-3, err

@@ -74,16 +74,36 @@ def test_w4a16_skinny_splitk_and_epilogues(ks):
     want = x.float() @ c.dequant().t()
     res = bf(torch.randn(m, n, generator=gen(7)))
     out = res.to(DEV).clone()
-    K.w4a16_skinny(s, xp, xs, out, m, residual=out, epi=K.EPI_RESIDUAL, ks=ks)
+    K.w4a16_skinny(s, xp, xs, out, m, residual=out, epi=K.EPI_RESIDUAL, tiles_per_cta=ks)
     torch.testing.assert_close(out.float().cpu(), want + res.float(), rtol=2e-2, atol=3e-2)
     out32 = torch.zeros(m, n, dtype=torch.float32, device=DEV)
-    K.w4a16_skinny(s, xp, xs, out32, m, epi=K.EPI_F32, ks=ks)
+    K.w4a16_skinny(s, xp, xs, out32, m, epi=K.EPI_F32, tiles_per_cta=ks)
     torch.testing.assert_close(out32.cpu(), want, rtol=2e-3, atol=2e-3)
     # silu-mul epilogue: rows interleaved (8 gate, 8 up)
     sm = torch.zeros(m, n // 2, dtype=torch.bfloat16, device=DEV)
-    K.w4a16_skinny(s, xp, xs, sm, m, epi=K.EPI_SILU_MUL, ks=ks)
+    K.w4a16_skinny(s, xp, xs, sm, m, epi=K.EPI_SILU_MUL, tiles_per_cta=ks)
     gate, up = Q.deinterleave_gate_up(want)
     torch.testing.assert_close(sm.float().cpu(), R.swiglu(gate, up), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("m,gout", [(1, 128), (5, 32), (20, 128)])
+def test_w4a16_skinny_fused_silu_pack(m, gout):
+    n, k, group = 1024, 512, 128
+    c = Q.quantize_w4(torch.randn(n, k, generator=gen(50)) * 0.05, group)
+    s = Q.pack_skinny(c).to(DEV)
+    x = bf(torch.randn(m, k, generator=gen(51)))
+    xp = torch.empty(m, k, dtype=torch.float16, device=DEV)
+    xs = torch.empty(m, k // group, 2, dtype=torch.float32, device=DEV)
+    K.act_pack(x.to(DEV), xp, xs, m, k, group)
+    inter = n // 2
+    op = torch.zeros(m, inter, dtype=torch.float16, device=DEV)
+    oxs = torch.zeros(m, inter // gout, 2, dtype=torch.float32, device=DEV)
+    K.w4a16_skinny(s, xp, xs, None, m, epi=K.EPI_SILU_PACK, ldo=inter, out_pack=op, out_xs=oxs, gout=gout)
+    sm = torch.zeros(m, inter, dtype=torch.bfloat16, device=DEV)
+    K.w4a16_skinny(s, xp, xs, sm, m, epi=K.EPI_SILU_MUL)
+    wp, ws = Q.act_pack_ref(sm.float().cpu(), gout)
+    assert torch.equal(op.cpu(), wp)
+    torch.testing.assert_close(oxs.cpu(), ws, rtol=1e-5, atol=1e-2)
 
 
 @pytest.mark.parametrize("m", [1, 5, 16])
@@ -92,12 +112,13 @@ def test_bf16_and_w8_skinny(m):
     w = bf(torch.randn(n, k, generator=gen(8)) * 0.05)
     x = bf(torch.randn(m, k, generator=gen(9)))
     out = torch.zeros(m, n, dtype=torch.bfloat16, device=DEV)
-    K.bf16_skinny(w.to(DEV), x.to(DEV), out, m)
+    assert torch.equal(Q.unpack_dense_bf16(Q.pack_dense_bf16(w), n, k), w)
+    K.dense_skinny(Q.dense_skinny(w, DEV), x.to(DEV), out, m)
     want = x.float() @ w.float().t()
     torch.testing.assert_close(out.float().cpu(), want, rtol=2e-2, atol=2e-2)
     q8, s8 = Q.quantize_w8_rows(w.float())
     out8 = torch.zeros(m, n, dtype=torch.bfloat16, device=DEV)
-    K.w8a16_skinny(q8.to(DEV), s8.to(DEV), x.to(DEV), out8, m)
+    K.dense_skinny(Q.dense_skinny(w.float(), DEV, int8=True), x.to(DEV), out8, m)
     want8 = x.float() @ (q8.float() * s8[:, None]).t()
     torch.testing.assert_close(out8.float().cpu(), want8, rtol=2e-2, atol=2e-2)
 
@@ -310,3 +331,8 @@ def test_qknorm_rope_insert():
         torch.testing.assert_close(kp[s], want_k[r], rtol=0.07, atol=0.02)
         torch.testing.assert_close(vp[s], vraw[r].float().view(hkv, hd), rtol=0.07, atol=0.02)
     assert torch.count_nonzero(kp[1]) == 0
+
+
+def test_zz_skinny_status_clean_after_all():
+    torch.cuda.synchronize()
+    assert K.skinny_status() == 0
