@@ -1,0 +1,237 @@
+#!/usr/bin/env python
+"""Headline benchmark: 27B hybrid decode (output tokens/s) at TP = number of GPUs.
+
+Workload (the reference's headline configuration, random-init weights, synthetic prompt):
+27B hybrid (hidden 5120, 64 layers 3 GDN : 1 full attention, SwiGLU 17408, vocab 151936),
+AWQ-style int4 W4A16 weights (group 128, asymmetric, fp16 scales / zero points), fp8 e4m3 paged KV
+(block 16), batch 1, 2048-token random prompt, greedy decode under CUDA-graph replay.
+
+``python bench.py --gpus N --steps K --warmup W`` (N > 1 under torchrun, one rank per GPU):
+prefill the prompt, run W untimed decode steps, then time exactly K decode steps twice:
+
+* ``value`` / ``ms_per_step``: device time of K replays of the self-feeding decode graph (CUDA
+  events on the launching stream, barrier + synchronize on both sides, max over ranks);
+* ``e2e``: the same K steps through ``Engine.decode_step`` -- every step copies its inputs from
+  pinned host memory, replays the graph and reads the sampled token back to the host.
+
+Every decode step streams the full ~14.5 GB of weights, far more than the 126 MB L2, so no L2
+flush is needed between timed iterations. ``--impl reference`` reports that the reference
+(a Rust workspace) cannot be installed in this environment.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+BASELINE_TOK_S = 48.8   # reference: 27B AWQ W4A16 bare decode on 1x3090 Ti (AGENTS.md:152)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        clocks, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                clocks.append(float(f[1]))
+                mx = float(f[2])
+            except ValueError:
+                continue
+            for nm, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        clocks.sort()
+        med = clocks[len(clocks) // 2] if clocks else None
+        return {"sm_mhz": med, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--prompt-len", type=int, default=2048)
+    ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (result marked invalid)")
+    ap.add_argument("--comm", default="nccl", choices=["nccl", "fused"])
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference",
+                          "unavailable": "reference is a Rust/CUDA cargo workspace (no setup.py/pyproject, no cargo "
+                                         "in the image, no sm_100 arch arm): pip install reports 'not installable'"}))
+        return
+
+    import torch
+
+    from owl_engine_b200.engine.core import Engine, EngineConfig
+    from owl_engine_b200.models import hybrid as H
+    from owl_engine_b200.ops import kernels as K
+    from owl_engine_b200.parallel.comm import TpComm
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    comm = TpComm.from_env(args.comm) if world > 1 else None
+    rank = comm.rank if comm else 0
+    if comm is None:
+        torch.cuda.set_device(0)
+    dev = torch.device(f"cuda:{torch.cuda.current_device()}")
+    warmup = max(3, args.warmup)
+    steps = args.steps
+
+    cfg = EngineConfig(model="qwen3.8-27b", group=128, n_pages=1024, n_slots=2, max_seqs=2,
+                       max_seq=args.prompt_len + 2 * (warmup + steps) + 64, n_layers=args.layers)
+    eng = Engine(cfg, comm=comm)
+    g = torch.Generator().manual_seed(1234)
+    prompt = torch.randint(0, eng.spec.vocab, (args.prompt_len,), generator=g).tolist()
+
+    def sync_all():
+        if comm:
+            comm.barrier()
+        torch.cuda.synchronize()
+
+    # ---- prefill (TTFT) -------------------------------------------------------------------
+    sid = eng.add_sequence(prompt)
+    sync_all()
+    t0 = time.perf_counter()
+    eng.prefill(sid)
+    torch.cuda.synchronize()
+    ttft_ms = (time.perf_counter() - t0) * 1e3
+
+    # ---- count our kernel launches per decode step ---------------------------------------
+    launches = {"n": 0}
+    orig_call = K.call
+
+    def counting_call(name, *a):
+        launches["n"] += 1
+        return orig_call(name, *a)
+
+    K.call = counting_call
+    lay = H.StepLayout(1, 1)
+    v = eng.runner.views(lay)
+    saved = eng.runner.inp.clone()
+    v["gslot"].fill_(-1); v["kv_slot"].fill_(-1); v["ctx"].fill_(1); v["bt_row"].zero_()
+    eng.runner.step_forward(lay, ctx_hint=eng._ctx_bucket(args.prompt_len + 1), advance=True)
+    torch.cuda.synchronize()
+    eng.runner.inp.copy_(saved)
+    K.call = orig_call
+    launches_per_step = launches["n"] + 1   # argmax is two kernels behind one call
+
+    # ---- end-to-end arm: host-fed steps through the public API ---------------------------
+    for _ in range(warmup):
+        eng.decode_step([sid])
+    sync_all()
+    itl = []
+    h2d0, d2h0 = eng.h2d_bytes, eng.d2h_bytes
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        ts = time.perf_counter()
+        eng.decode_step([sid])
+        itl.append((time.perf_counter() - ts) * 1e3)
+    sync_all()
+    e2e_s = time.perf_counter() - t0
+    if comm:
+        e2e_s = comm.max_over_ranks(e2e_s)
+    itl.sort()
+
+    # ---- device-timed arm: self-feeding graph, K replays ----------------------------------
+    seq = eng.seqs[sid]
+    eng._ensure_pages(seq, seq.n_cached + warmup + steps + 2)
+    pos = seq.n_cached
+    hi = eng.h_inp_np
+    hi[lay.ids] = seq.tokens[-1]
+    hi[lay.pos3:lay.pos3 + 3] = pos
+    hi[lay.kv_slot] = seq.pages[pos // 16] * 16 + pos % 16
+    hi[lay.ctx] = pos + 1
+    hi[lay.gslot] = seq.slot
+    hi[lay.bt_row] = seq.row
+    eng.runner.inp[:lay.size].copy_(eng.h_inp[:lay.size])
+    graph = eng.runner.capture(1, 1, ctx_hint=eng._ctx_bucket(pos + warmup + steps + 1), advance=True)
+    for _ in range(warmup):
+        graph.replay()
+    sync_all()
+    sampler = ClockSampler(torch.cuda.current_device())
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all()
+    e0.record()
+    for _ in range(steps):
+        graph.replay()
+    e1.record()
+    sync_all()
+    dev_ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else {}
+    if comm:
+        dev_ms = comm.max_over_ranks(dev_ms)
+
+    status = K.skinny_status()
+    if rank == 0:
+        ms_per_step = dev_ms / steps
+        value = 1000.0 / ms_per_step
+        e2e_value = steps / e2e_s
+        out = {
+            "metric": "27B hybrid output tok/s (box, max over ranks) + p50 TTFT/ITL",
+            "value": round(value, 2), "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+            "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": round(value / BASELINE_TOK_S, 3), "dtype": "bf16 activations / int4 W4A16 weights / fp8 KV",
+            "data": "synthetic (random prompt ids, random-init weights)",
+            "impl": "ours",
+            "config": {"model": "qwen3.8-27b hybrid (64 layers, hidden 5120, vocab 151936)", "global_batch": 1,
+                       "seq_len": args.prompt_len, "generated": steps, "parallelism": f"tp{world}",
+                       "weights": "int4 g128 asym (W4A16)", "kv": "fp8 e4m3 paged, block 16",
+                       "l2": "inputs larger than L2: every step streams the full weight set "
+                             f"({eng.weights.streamed_bytes() / 1e9:.1f} GB per rank)",
+                       "comm": args.comm if world > 1 else "none", "cuda_graph": True},
+            "e2e": {"value": round(e2e_value, 2), "unit": "tokens/s",
+                    "h2d_bytes_per_step": (eng.h2d_bytes - h2d0) // steps,
+                    "d2h_bytes_per_step": (eng.d2h_bytes - d2h0) // steps,
+                    "p50_itl_ms": round(itl[len(itl) // 2], 4), "ttft_ms": round(ttft_ms, 2)},
+            "gpu_launches": launches_per_step * steps,
+            "launches_per_step": launches_per_step,
+            "clocks": clocks,
+            "kernel_status": status,
+        }
+        if args.layers is not None:
+            out["invalid"] = "debug run with fewer layers"
+        print(json.dumps(out))
+    if comm:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -12,6 +12,9 @@ __device__ __forceinline__ void unpack_bf16x8(const uint4& a, float* v) {
 __device__ __forceinline__ uint4 pack_bf16x8(const float* v) {
   return make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
 }
+__device__ __forceinline__ uint4 pack_f16x8(const float* v) {
+  return make_uint4(pack_f16(v[0], v[1]), pack_f16(v[2], v[3]), pack_f16(v[4], v[5]), pack_f16(v[6], v[7]));
+}
 __device__ __forceinline__ float clamp_h(float x) { return fminf(fmaxf(x, -65504.f), 65504.f); }
 
 // v: 8 consecutive activations. Returns the packed chunk; s_stored = sum of the 8 stored

@@ -306,7 +306,8 @@ __global__ void __launch_bounds__(AT_WARPS * 32) paged_attn_kernel(AttnParams p)
 __global__ void __launch_bounds__(256) attn_reduce_kernel(const float* __restrict__ part_o,
                                                           const float* __restrict__ part_ml, int splits,
                                                           const __nv_bfloat16* __restrict__ qraw, int ldq,
-                                                          __nv_bfloat16* out, uint4* xpack, float2* xs, int hq, int G) {
+                                                          __nv_bfloat16* out, uint4* xpack, float2* xs, int hq, int G,
+                                                          int out_f16) {
   __shared__ float sm_acc[8][HD];
   __shared__ float sm_l[8];
   __shared__ float sm_M;
@@ -354,14 +355,15 @@ __global__ void __launch_bounds__(256) attn_reduce_kernel(const float* __restric
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const float a = __bfloat162float(__float2bfloat16(acc[i] * inv));
-      v[i] = __bfloat162float(__float2bfloat16(a * sigmoid_f(gf[i])));
+      const float y = a * sigmoid_f(gf[i]);
+      v[i] = out_f16 ? __half2float(__float2half_rn(clamp_h(y))) : __bfloat162float(__float2bfloat16(y));
     }
   } else {
 #pragma unroll
     for (int i = 0; i < 8; ++i) v[i] = __bfloat162float(__float2bfloat16(acc[i] * inv));
   }
   const size_t e = ((size_t)row * hq + head) * HD + lane * 8;
-  if (out) *reinterpret_cast<uint4*>(out + e) = pack_bf16x8(v);
+  if (out) *reinterpret_cast<uint4*>(out + e) = out_f16 ? pack_f16x8(v) : pack_bf16x8(v);
   if (xpack) {
     float s_st, s_eff;
     uint4 pk = actpack_chunk(v, s_st, s_eff);
@@ -425,7 +427,7 @@ OWL_API int owl_paged_attn(const void* q, const void* k_pool, const void* v_pool
 }
 
 OWL_API int owl_attn_reduce(const void* part_o, const void* part_ml, int splits, const void* qraw, int ldq, void* out,
-                            void* xpack, void* xs, int rows, int hq, int G, int pdl, cudaStream_t st) {
+                            void* xpack, void* xs, int rows, int hq, int G, int out_f16, int pdl, cudaStream_t st) {
   if (rows < 1 || splits < 1 || (G != 32 && G != 128)) return OWL_ERR_BAD_ARG;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(rows, hq); cfg.blockDim = dim3(256); cfg.stream = st;
@@ -435,7 +437,7 @@ OWL_API int owl_attn_reduce(const void* part_o, const void* part_ml, int splits,
   cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
   cudaError_t e = cudaLaunchKernelEx(&cfg, attn_reduce_kernel, (const float*)part_o, (const float*)part_ml, splits,
                                      (const __nv_bfloat16*)qraw, ldq, (__nv_bfloat16*)out, (uint4*)xpack, (float2*)xs,
-                                     hq, G);
+                                     hq, G, out_f16);
   if (e != cudaSuccess) return (int)OWL_ERR_LAUNCH * 1000 - (int)e;
   return OWL_OK;
 }

@@ -22,7 +22,8 @@ __global__ void __launch_bounds__(1024) rmsnorm_pack_kernel(const __nv_bfloat16*
                                                             const __nv_bfloat16* __restrict__ delta,
                                                             const __nv_bfloat16* __restrict__ w,
                                                             __nv_bfloat16* out_h, __nv_bfloat16* normed, uint4* xpack,
-                                                            float2* xs, int K, int G, float eps, int one_plus_w) {
+                                                            float2* xs, int K, int G, float eps, int one_plus_w,
+                                                            int normed_f16) {
   __shared__ float red[32];
   pdl_wait();
   const int row = blockIdx.x;
@@ -71,9 +72,10 @@ __global__ void __launch_bounds__(1024) rmsnorm_pack_kernel(const __nv_bfloat16*
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const float g = one_plus_w ? 1.f + wf[i] : wf[i];
-        v[i] = __bfloat162float(__float2bfloat16(v[i] * rinv * g));
+        const float y = v[i] * rinv * g;
+        v[i] = normed_f16 ? __half2float(__float2half_rn(clamp_h(y))) : __bfloat162float(__float2bfloat16(y));
       }
-      if (normed) reinterpret_cast<uint4*>(normed + (size_t)row * K)[c] = pack_bf16x8(v);
+      if (normed) reinterpret_cast<uint4*>(normed + (size_t)row * K)[c] = normed_f16 ? pack_f16x8(v) : pack_bf16x8(v);
     } else {
 #pragma unroll
       for (int i = 0; i < 8; ++i) v[i] = 0.f;
@@ -115,7 +117,7 @@ __global__ void __launch_bounds__(256) act_pack_kernel(const __nv_bfloat16* __re
 // Merged gate_up output in "interleaved-8" order: columns [t*16 .. t*16+7] are gate_j and
 // [t*16+8 .. t*16+15] are up_j for j = t*8 .. t*8+7. Produces silu(gate)*up as bf16 [M][I] and/or ActPack.
 __global__ void __launch_bounds__(256) silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* out,
-                                                       uint4* xpack, float2* xs, int I, int G) {
+                                                       uint4* xpack, float2* xs, int I, int G, int out_f16) {
   pdl_wait();
   pdl_launch_dependents();
   const int row = blockIdx.y;
@@ -130,8 +132,11 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const __nv_bfloat16* __re
     unpack_bf16x8(ga, gf);
     unpack_bf16x8(ua, uf);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = __bfloat162float(__float2bfloat16(silu_f(gf[i]) * uf[i]));
-    if (out) reinterpret_cast<uint4*>(out + (size_t)row * I)[c] = pack_bf16x8(v);
+    for (int i = 0; i < 8; ++i) {
+      const float y = silu_f(gf[i]) * uf[i];
+      v[i] = out_f16 ? __half2float(__float2half_rn(clamp_h(y))) : __bfloat162float(__float2bfloat16(y));
+    }
+    if (out) reinterpret_cast<uint4*>(out + (size_t)row * I)[c] = out_f16 ? pack_f16x8(v) : pack_bf16x8(v);
   } else {
 #pragma unroll
     for (int i = 0; i < 8; ++i) v[i] = 0.f;
@@ -286,13 +291,14 @@ static int launch_pdl(void (*kernel)(Args...), dim3 grid, dim3 block, int pdl, c
 using namespace owl;
 
 OWL_API int owl_rmsnorm_pack(const void* h, const void* delta, const void* w, void* out_h, void* normed, void* xpack,
-                             void* xs, int M, int K, int G, float eps, int one_plus_w, int pdl, cudaStream_t st) {
+                             void* xs, int M, int K, int G, float eps, int one_plus_w, int normed_f16, int pdl,
+                             cudaStream_t st) {
   if (M < 1 || (K & 127) || (G != 32 && G != 128)) return OWL_ERR_BAD_ARG;
   int threads = ((K / 8 + 31) / 32) * 32;
   if (threads > 1024) threads = 1024;
   return launch_pdl(rmsnorm_pack_kernel, dim3(M), dim3(threads), pdl, st, (const __nv_bfloat16*)h,
                     (const __nv_bfloat16*)delta, (const __nv_bfloat16*)w, (__nv_bfloat16*)out_h,
-                    (__nv_bfloat16*)normed, (uint4*)xpack, (float2*)xs, K, G, eps, one_plus_w);
+                    (__nv_bfloat16*)normed, (uint4*)xpack, (float2*)xs, K, G, eps, one_plus_w, normed_f16);
 }
 OWL_API int owl_act_pack(const void* x, int ldx, void* xpack, void* xs, int M, int K, int G, int pdl, cudaStream_t st) {
   if (M < 1 || (K & 127) || (ldx & 7) || (G != 32 && G != 128)) return OWL_ERR_BAD_ARG;
@@ -300,12 +306,12 @@ OWL_API int owl_act_pack(const void* x, int ldx, void* xpack, void* xs, int M, i
   return launch_pdl(act_pack_kernel, dim3((nchunks + 255) / 256, M), dim3(256), pdl, st, (const __nv_bfloat16*)x, ldx,
                     (uint4*)xpack, (float2*)xs, K, G);
 }
-OWL_API int owl_silu_mul(const void* gate_up, void* out, void* xpack, void* xs, int M, int I, int G, int pdl,
-                         cudaStream_t st) {
+OWL_API int owl_silu_mul(const void* gate_up, void* out, void* xpack, void* xs, int M, int I, int G, int out_f16,
+                         int pdl, cudaStream_t st) {
   if (M < 1 || (I & 127) || (G != 32 && G != 128)) return OWL_ERR_BAD_ARG;
   const int nchunks = I / 8;
   return launch_pdl(silu_mul_kernel, dim3((nchunks + 255) / 256, M), dim3(256), pdl, st,
-                    (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, (uint4*)xpack, (float2*)xs, I, G);
+                    (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, (uint4*)xpack, (float2*)xs, I, G, out_f16);
 }
 OWL_API int owl_sigmoid_gate(const void* attn, const void* qraw, int ldq, int D, void* out, void* xpack, void* xs,
                              int M, int HD, int G, int pdl, cudaStream_t st) {

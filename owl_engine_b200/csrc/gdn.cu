@@ -314,7 +314,7 @@ struct GdnScanParams {
   const float* a_log; const float* dt_bias; const float* gamma;
   float* state;                 // [slots][nv][128][128]
   __nv_bfloat16* out;           // [T][V]
-  int ldz, ldab, nk, nv, T, slot, use_state;
+  int ldz, ldab, nk, nv, T, slot, use_state, out_f16;
   float eps;
 };
 __global__ void __launch_bounds__(256) gdn_scan_kernel(GdnScanParams p) {
@@ -397,7 +397,8 @@ __global__ void __launch_bounds__(256) gdn_scan_kernel(GdnScanParams p) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) y[j] = o[j] * rinv * p.gamma[lane * 4 + j] * silu_f(z[j]);
       *reinterpret_cast<uint2*>(p.out + (size_t)r * V + h * GD + lane * 4) =
-          make_uint2(pack_bf16(y[0], y[1]), pack_bf16(y[2], y[3]));
+          p.out_f16 ? make_uint2(pack_f16(y[0], y[1]), pack_f16(y[2], y[3]))
+                    : make_uint2(pack_bf16(y[0], y[1]), pack_bf16(y[2], y[3]));
     }
     __syncthreads();
   }
@@ -459,13 +460,13 @@ OWL_API int owl_gdn_conv_fwd(const void* x, int ld, const void* conv_w, void* co
 
 OWL_API int owl_gdn_scan(const void* qkv, const void* z, int ldz, const void* ab, int ldab, const void* a_log,
                          const void* dt_bias, const void* gamma, void* state, int slot, void* out, int T, int nk, int nv,
-                         int use_state, float eps, cudaStream_t st) {
+                         int use_state, float eps, int out_f16, cudaStream_t st) {
   if (T < 1 || nk < 1 || nv % nk || (ldz & 3)) return OWL_ERR_BAD_ARG;
   GdnScanParams p;
   p.qkv = (const __nv_bfloat16*)qkv; p.z = (const __nv_bfloat16*)z; p.ab = (const __nv_bfloat16*)ab;
   p.a_log = (const float*)a_log; p.dt_bias = (const float*)dt_bias; p.gamma = (const float*)gamma;
   p.state = (float*)state; p.out = (__nv_bfloat16*)out; p.ldz = ldz; p.ldab = ldab; p.nk = nk; p.nv = nv; p.T = T;
-  p.slot = slot; p.use_state = use_state; p.eps = eps;
+  p.slot = slot; p.use_state = use_state; p.eps = eps; p.out_f16 = out_f16;
   gdn_scan_kernel<<<nv, 256, 0, st>>>(p);
   OWL_LAUNCH_CHECK();
   return OWL_OK;

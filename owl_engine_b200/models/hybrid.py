@@ -425,9 +425,12 @@ class HybridRunner:
             return self._pf
         sp, dev = self.spec, self.device
         bf = lambda *s: torch.empty(*s, dtype=torch.bfloat16, device=dev)
+        # GEMM inputs are fp16 on the tcgen05 arm (exact int4 dequant), bf16 on the baseline arm
+        xd = torch.float16 if self.prefill_gemm == "tc" else torch.bfloat16
+        xa = lambda *s: torch.empty(*s, dtype=xd, device=dev)
         widest = max(2 * sp.inter, sp.conv_dim + sp.value_dim, self.qkv_n)
-        ws = dict(t=t, h=bf(t, sp.hidden), x=bf(t, sp.hidden), wide=bf(t, widest), act=bf(t, sp.inter),
-                  conv=bf(t, sp.conv_dim), mix=bf(t, max(sp.value_dim, sp.hq * sp.hd)), ab=bf(t, self.ldab),
+        ws = dict(t=t, h=bf(t, sp.hidden), x=xa(t, sp.hidden), wide=bf(t, widest), act=xa(t, sp.inter),
+                  conv=bf(t, sp.conv_dim), mix=xa(t, max(sp.value_dim, sp.hq * sp.hd)), ab=bf(t, self.ldab),
                   q=bf(t + 8, sp.hq, sp.hd), y=bf(t, sp.hidden),
                   part_o=torch.empty((t + 8) * sp.hq * sp.hd, dtype=torch.float32, device=dev),
                   part_ml=torch.empty((t + 8) * sp.hq * 2, dtype=torch.float32, device=dev),
@@ -451,6 +454,8 @@ class HybridRunner:
         """Run one prefill chunk (eager). ``ids`` int32 [T] on device; KV pages for positions
         pos0..pos0+T-1 must already be in ``block_table[seq_row]``. Returns the argmax token of
         the last row when ``want_logits``."""
+        from ..ops import linear
+
         sp, pool = self.spec, self.pool
         t = ids.shape[0]
         ws = self._prefill_ws(max(t, 16))
@@ -485,7 +490,7 @@ class HybridRunner:
                 wide = ws["wide"].view(-1)[:t * nq].view(t, nq)
                 self._gemm(lw.qkvz, x, wide)
                 ab = ws["ab"][:t]
-                torch.matmul(x, lw.ab_dense.t(), out=ab)
+                linear.dense_gemm(x, lw.ab_dense, ab, arm=self.prefill_gemm)
                 conv = ws["conv"][:t]
                 K.gdn_conv_fwd(wide, nq, lw.conv_w, pool.conv_state[gi], gdn_slot, conv, t, sp.nk, sp.nv, use_state)
                 mix = ws["mix"].view(-1)[:t * sp.value_dim].view(t, sp.value_dim)

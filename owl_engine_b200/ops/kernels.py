@@ -21,21 +21,21 @@ _SIGS = {
     "owl_w4a16_skinny": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "owl_bf16_skinny": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "owl_w8a16_skinny": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
-    "owl_rmsnorm_pack": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _I, _I, _P],
+    "owl_rmsnorm_pack": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _I, _I, _I, _P],
     "owl_act_pack": [_P, _I, _P, _P, _I, _I, _I, _I, _P],
-    "owl_silu_mul": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "owl_silu_mul": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "owl_sigmoid_gate": [_P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _P],
     "owl_embed": [_P, _P, _P, _I, _I, _I, _I, _P],
     "owl_argmax": [_P, _I, _I, _I, _P, _P, _I, _P, _I, _I, _P],
     "owl_gdn_decode": [_P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
     "owl_gdn_conv_fwd": [_P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _P],
-    "owl_gdn_scan": [_P, _P, _I, _P, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _F, _P],
+    "owl_gdn_scan": [_P, _P, _I, _P, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _F, _I, _P],
     "owl_qknorm_rope_insert": [_P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F,
                                _F, _I, _P],
     "owl_paged_attn": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "owl_decode_advance": [_P, _P, _P, _I, _I, _I, _P],
     "owl_w4_dequant": [_P, _P, _I, _I, _I, _P],
-    "owl_attn_reduce": [_P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P],
+    "owl_attn_reduce": [_P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _P],
 }
 _bound: dict = {}
 
@@ -103,10 +103,15 @@ def skinny_status() -> int:
     return f()
 
 
+def _is_f16(t) -> int:
+    return int(t is not None and t.dtype == torch.float16)
+
+
 def rmsnorm_pack(h, w, *, delta=None, out_h=None, normed=None, xpack=None, xs=None, m: int, k: int, group: int = 128,
                  eps: float = 1e-6, one_plus_w: bool = True, pdl: bool = False) -> None:
+    """``normed`` may be bf16 or fp16 (the tcgen05 W4A16 GEMM takes fp16 activations)."""
     call("owl_rmsnorm_pack", ptr(h), ptr(delta), ptr(w), ptr(out_h), ptr(normed), ptr(xpack), ptr(xs), m, k, group,
-         eps, int(one_plus_w), int(pdl), stream())
+         eps, int(one_plus_w), _is_f16(normed), int(pdl), stream())
 
 
 def act_pack(x, xpack, xs, m: int, k: int, group: int = 128, ldx: int | None = None, pdl: bool = False) -> None:
@@ -114,7 +119,8 @@ def act_pack(x, xpack, xs, m: int, k: int, group: int = 128, ldx: int | None = N
 
 
 def silu_mul(gate_up, m: int, inter: int, *, out=None, xpack=None, xs=None, group: int = 128, pdl: bool = False):
-    call("owl_silu_mul", ptr(gate_up), ptr(out), ptr(xpack), ptr(xs), m, inter, group, int(pdl), stream())
+    call("owl_silu_mul", ptr(gate_up), ptr(out), ptr(xpack), ptr(xs), m, inter, group, _is_f16(out), int(pdl),
+         stream())
 
 
 def sigmoid_gate(attn, qraw, ldq: int, hd: int, m: int, hdim_total: int, *, out=None, xpack=None, xs=None,
@@ -149,7 +155,7 @@ def gdn_conv_fwd(x, ld: int, conv_w, conv_state, slot: int, out, t: int, nk: int
 def gdn_scan(qkv, z, ldz: int, ab, ldab: int, a_log, dt_bias, gamma, state, slot: int, out, t: int, nk: int, nv: int,
              use_state: bool, eps: float = 1e-6) -> None:
     call("owl_gdn_scan", ptr(qkv), ptr(z), ldz, ptr(ab), ldab, ptr(a_log), ptr(dt_bias), ptr(gamma), ptr(state), slot,
-         ptr(out), t, nk, nv, int(use_state), eps, stream())
+         ptr(out), t, nk, nv, int(use_state), eps, _is_f16(out), stream())
 
 
 def qknorm_rope_insert(qraw, ldq: int, kraw, ldk: int, vraw, ldv: int, qnorm_w, knorm_w, pos3, inv_freq, section,
@@ -169,7 +175,7 @@ def paged_attn(q, k_pool, v_pool, block_table, bt_row, ctx_len, part_o, part_ml,
 def attn_reduce(part_o, part_ml, splits: int, qraw, ldq: int, rows: int, hq: int, *, out=None, xpack=None, xs=None,
                 group: int = 128, pdl: bool = False) -> None:
     call("owl_attn_reduce", ptr(part_o), ptr(part_ml), splits, ptr(qraw), ldq, ptr(out), ptr(xpack), ptr(xs), rows, hq,
-         group, int(pdl), stream())
+         group, _is_f16(out), int(pdl), stream())
 
 
 def w4_dequant(w, out=None):

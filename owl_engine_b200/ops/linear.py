@@ -37,3 +37,23 @@ def w4_gemm(w, x: torch.Tensor, out: torch.Tensor, arm: str = "tc") -> torch.Ten
 
         return gemm_tc.w4a16_gemm(w, x, out)
     raise ValueError(f"unknown prefill GEMM arm {arm!r}")
+
+
+_w16: dict = {}
+
+
+def dense_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, arm: str = "tc") -> torch.Tensor:
+    """out[T, N] (bf16) = x @ w^T for a small dense bf16 weight (GDN a/b projections, draft heads)."""
+    if arm == "baseline":
+        torch.matmul(x.to(w.dtype), w.t(), out=out)
+        return out
+    from . import gemm_tc
+
+    if x.dtype != w.dtype:
+        key = (w.data_ptr(), x.dtype)
+        wc = _w16.get(key)
+        if wc is None:
+            wc = w.to(x.dtype)
+            _w16[key] = wc
+        w = wc
+    return gemm_tc.f16_gemm(x, w, out)
