@@ -42,8 +42,8 @@ struct InsertParams {
 __global__ void __launch_bounds__(128) qknorm_rope_insert_kernel(InsertParams p) {
   __shared__ float y[256];
   __shared__ float red[32];
-  pdl_wait();
   pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x, head = blockIdx.y, tid = threadIdx.x;
   const int hd = p.hd;
   const bool is_q = head < p.hq, is_k = !is_q && head < p.hq + p.hkv;
@@ -138,6 +138,7 @@ __global__ void __launch_bounds__(AT_WARPS * 32) paged_attn_kernel(AttnParams p)
   const int split = blockIdx.x, kvh = blockIdx.y, grp = blockIdx.z;
   const int Gq = p.hq / p.hkv;
   const int rg = warp / TS, ts = warp % TS;  // row group index within the CTA pass, token split
+  pdl_launch_dependents();
   pdl_wait();
   const int ctx_last = p.ctx_len[grp];
   const int btr = p.bt_row ? p.bt_row[grp] : grp;
@@ -298,7 +299,6 @@ __global__ void __launch_bounds__(AT_WARPS * 32) paged_attn_kernel(AttnParams p)
       }
     }
   }
-  pdl_launch_dependents();
 }
 
 // grid (rows, hq), block 256: CTA per (row, head); warp w merges splits w, w+8, ... (loads of
@@ -314,8 +314,8 @@ __global__ void __launch_bounds__(256) attn_reduce_kernel(const float* __restric
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int row = blockIdx.x, head = blockIdx.y;
   // gate does not depend on the previous kernel's output only when qraw is older; load after the wait
-  pdl_wait();
   pdl_launch_dependents();
+  pdl_wait();
   const size_t base = ((size_t)row * hq + head) * splits;
   // global max over splits (every warp computes it: splits <= 64 -> two loads per lane)
   float mloc = -INFINITY;
@@ -365,12 +365,11 @@ __global__ void __launch_bounds__(256) attn_reduce_kernel(const float* __restric
   const size_t e = ((size_t)row * hq + head) * HD + lane * 8;
   if (out) *reinterpret_cast<uint4*>(out + e) = out_f16 ? pack_f16x8(v) : pack_bf16x8(v);
   if (xpack) {
-    float s_st, s_eff;
-    uint4 pk = actpack_chunk(v, s_st, s_eff);
-    xpack[e / 8] = pk;
     const int cpg = G >> 3;
-    actpack_group_reduce(s_st, s_eff, cpg);
-    if ((lane % cpg) == 0) xs[e / G] = make_float2(s_eff, 1024.f * s_st);
+    float sx, xsum;
+    const uint4 pk = actpack_emit(v, cpg, sx, xsum);
+    xpack[e / 8] = pk;
+    if ((lane % cpg) == 0) xs[e / G] = make_float2(sx, xsum);
   }
 }
 

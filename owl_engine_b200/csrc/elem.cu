@@ -25,6 +25,7 @@ __global__ void __launch_bounds__(1024) rmsnorm_pack_kernel(const __nv_bfloat16*
                                                             float2* xs, int K, int G, float eps, int one_plus_w,
                                                             int normed_f16) {
   __shared__ float red[32];
+  pdl_launch_dependents();
   pdl_wait();
   const int row = blockIdx.x;
   const int nchunks = K >> 3;
@@ -48,7 +49,6 @@ __global__ void __launch_bounds__(1024) rmsnorm_pack_kernel(const __nv_bfloat16*
   }
   ss = block_sum(ss, red);
   const float rinv = rsqrtf(ss / (float)K + eps);
-  pdl_launch_dependents();
   if (!normed && !xpack) return;
   const uint4* src = (dp && out_h) ? reinterpret_cast<const uint4*>(out_h + (size_t)row * K) : hp;
   const int nround = (nchunks + 31) & ~31;
@@ -81,11 +81,10 @@ __global__ void __launch_bounds__(1024) rmsnorm_pack_kernel(const __nv_bfloat16*
       for (int i = 0; i < 8; ++i) v[i] = 0.f;
     }
     if (xpack) {
-      float s_st, s_eff;
-      uint4 pk = actpack_chunk(v, s_st, s_eff);
+      float sx, xsum;
+      const uint4 pk = actpack_emit(v, cpg, sx, xsum);
       if (live) xpack[(size_t)row * nchunks + c] = pk;
-      actpack_group_reduce(s_st, s_eff, cpg);
-      if (live && (c % cpg) == 0) xs[(size_t)row * (K / G) + c / cpg] = make_float2(s_eff, 1024.f * s_st);
+      if (live && (c % cpg) == 0) xs[(size_t)row * (K / G) + c / cpg] = make_float2(sx, xsum);
     }
   }
 }
@@ -93,8 +92,8 @@ __global__ void __launch_bounds__(1024) rmsnorm_pack_kernel(const __nv_bfloat16*
 // bf16 [M][K] -> ActPack.
 __global__ void __launch_bounds__(256) act_pack_kernel(const __nv_bfloat16* __restrict__ x, int ldx, uint4* xpack,
                                                        float2* xs, int K, int G) {
-  pdl_wait();
   pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.y;
   const int nchunks = K >> 3, cpg = G >> 3;
   const int c = blockIdx.x * blockDim.x + threadIdx.x;  // grid.x covers nchunks rounded up to 32
@@ -107,19 +106,18 @@ __global__ void __launch_bounds__(256) act_pack_kernel(const __nv_bfloat16* __re
 #pragma unroll
     for (int i = 0; i < 8; ++i) v[i] = 0.f;
   }
-  float s_st, s_eff;
-  uint4 pk = actpack_chunk(v, s_st, s_eff);
+  float sx, xsum;
+  const uint4 pk = actpack_emit(v, cpg, sx, xsum);
   if (live) xpack[(size_t)row * nchunks + c] = pk;
-  actpack_group_reduce(s_st, s_eff, cpg);
-  if (live && (c % cpg) == 0) xs[(size_t)row * (K / G) + c / cpg] = make_float2(s_eff, 1024.f * s_st);
+  if (live && (c % cpg) == 0) xs[(size_t)row * (K / G) + c / cpg] = make_float2(sx, xsum);
 }
 
 // Merged gate_up output in "interleaved-8" order: columns [t*16 .. t*16+7] are gate_j and
 // [t*16+8 .. t*16+15] are up_j for j = t*8 .. t*8+7. Produces silu(gate)*up as bf16 [M][I] and/or ActPack.
 __global__ void __launch_bounds__(256) silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* out,
                                                        uint4* xpack, float2* xs, int I, int G, int out_f16) {
-  pdl_wait();
   pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.y;
   const int nchunks = I >> 3, cpg = G >> 3;
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -142,11 +140,10 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const __nv_bfloat16* __re
     for (int i = 0; i < 8; ++i) v[i] = 0.f;
   }
   if (xpack) {
-    float s_st, s_eff;
-    uint4 pk = actpack_chunk(v, s_st, s_eff);
+    float sx, xsum;
+    const uint4 pk = actpack_emit(v, cpg, sx, xsum);
     if (live) xpack[(size_t)row * nchunks + c] = pk;
-    actpack_group_reduce(s_st, s_eff, cpg);
-    if (live && (c % cpg) == 0) xs[(size_t)row * (I / G) + c / cpg] = make_float2(s_eff, 1024.f * s_st);
+    if (live && (c % cpg) == 0) xs[(size_t)row * (I / G) + c / cpg] = make_float2(sx, xsum);
   }
 }
 
@@ -156,8 +153,8 @@ __global__ void __launch_bounds__(256) sigmoid_gate_kernel(const __nv_bfloat16* 
                                                            const __nv_bfloat16* __restrict__ qraw, int ldq, int D,
                                                            __nv_bfloat16* out, uint4* xpack, float2* xs, int HD,
                                                            int G) {
-  pdl_wait();
   pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.y;
   const int nchunks = HD >> 3, cpg = G >> 3;
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -178,19 +175,18 @@ __global__ void __launch_bounds__(256) sigmoid_gate_kernel(const __nv_bfloat16* 
     for (int i = 0; i < 8; ++i) v[i] = 0.f;
   }
   if (xpack) {
-    float s_st, s_eff;
-    uint4 pk = actpack_chunk(v, s_st, s_eff);
+    float sx, xsum;
+    const uint4 pk = actpack_emit(v, cpg, sx, xsum);
     if (live) xpack[(size_t)row * nchunks + c] = pk;
-    actpack_group_reduce(s_st, s_eff, cpg);
-    if (live && (c % cpg) == 0) xs[(size_t)row * (HD / G) + c / cpg] = make_float2(s_eff, 1024.f * s_st);
+    if (live && (c % cpg) == 0) xs[(size_t)row * (HD / G) + c / cpg] = make_float2(sx, xsum);
   }
 }
 
 // Embedding gather: out[m][:] = table[ids[m]][:]  (bf16, H multiple of 8).
 __global__ void __launch_bounds__(256) embed_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
                                                     __nv_bfloat16* out, int H, int vocab) {
-  pdl_wait();
   pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x;
   int id = ids[row];
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
@@ -204,8 +200,8 @@ __global__ void __launch_bounds__(256) argmax_stage1(const __nv_bfloat16* __rest
                                                      float* pval, int* pidx, int nparts) {
   __shared__ float sv[8];
   __shared__ int si[8];
-  pdl_wait();
   pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.y, part = blockIdx.x;
   const int per = (((V + nparts - 1) / nparts) + 7) & ~7;
   const int beg = part * per, end = min(V, beg + per);
@@ -233,8 +229,8 @@ __global__ void __launch_bounds__(256) argmax_stage1(const __nv_bfloat16* __rest
 }
 __global__ void __launch_bounds__(128) argmax_stage2(const float* pval, const int* pidx, int nparts, int* out,
                                                      int vocab_offset) {
-  pdl_wait();
   pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x;
   float best = -INFINITY;
   int bi = 0x7fffffff;
@@ -258,8 +254,8 @@ __global__ void __launch_bounds__(128) argmax_stage2(const float* pval, const in
 //   ids[M] | pos3[3*M] | kv_slot[M] | ctx_len[B] | gdn_slot[B] | bt_row[B]   (M = B rows, T = 1)
 __global__ void decode_advance_kernel(int* inp, const int* __restrict__ tok, const int* __restrict__ block_table,
                                       int max_blocks, int B) {
-  pdl_wait();
   pdl_launch_dependents();
+  pdl_wait();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= B) return;
   int* ids = inp; int* pos3 = inp + B; int* kv_slot = inp + 4 * B; int* ctx = inp + 5 * B;

@@ -103,8 +103,8 @@ __global__ void __launch_bounds__(256) gdn_decode_kernel(GdnDecodeParams p) {
   const float scale = rsqrtf((float)GD);
   const float4 gam4 = *reinterpret_cast<const float4*>(p.gamma + lane * 4);
   const float gam[4] = {gam4.x, gam4.y, gam4.z, gam4.w};
-  pdl_wait();
   pdl_launch_dependents();
+  pdl_wait();
 
   for (int r = 0; r < p.T; ++r) {
     const size_t row = (size_t)b * p.T + r;
@@ -212,14 +212,12 @@ __global__ void __launch_bounds__(256) gdn_decode_kernel(GdnDecodeParams p) {
         float v8[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) v8[i] = (lane < 16) ? o_s[lane * 8 + i] : 0.f;
-        float s_st, s_eff;
-        uint4 pk = actpack_chunk(v8, s_st, s_eff);
         const int cpg = p.G >> 3;
-        actpack_group_reduce(s_st, s_eff, cpg);
+        float sx, xsum;
+        const uint4 pk = actpack_emit(v8, cpg, sx, xsum);
         if (live && lane < 16) {
           p.xpack[(row * V + h * GD) / 8 + lane] = pk;
-          if ((lane % cpg) == 0)
-            p.xs[row * (V / p.G) + (h * GD) / p.G + lane / cpg] = make_float2(s_eff, 1024.f * s_st);
+          if ((lane % cpg) == 0) p.xs[row * (V / p.G) + (h * GD) / p.G + lane / cpg] = make_float2(sx, xsum);
         }
       }
     }

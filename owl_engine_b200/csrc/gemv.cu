@@ -29,20 +29,21 @@
 //   uint4 #((s*2 + half)*32 + L): row half*8+g, k = s*KH + t*KV .. +KV-1  (bf16: KH 32, KV 8;
 //   int8: KH 64, KV 16)
 //
-// ---- activation pack ("ActPack") --------------------------------------------------------------
-// The int4 -> fp16 conversion uses the exponent-bias trick: (q & 0x000F000F) | 0x64006400 is
-// the half2 (1024+q_lo, 1024+q_hi), and the same with mask 0x00F000F0 is (1024+16 q, ...).
-// Instead of subtracting the bias and rescaling per weight, the producer of the activations
-// stores them pre-permuted and pre-scaled as fp16:
-//   per 8 consecutive k: [x0, x1, x2/16, x3/16, x4, x5, x6/16, x7/16]
-// plus per (token, group) two fp32 sums: xsum = sum of effective x, xoff = 1024 * sum of the
-// stored halves. Then  sum_k (q_k - z) x_k = acc - xoff - z * xsum  exactly (fp32 accumulate).
+// ---- activation pack ("ActPack", see actpack.cuh) ---------------------------------------------
+// The int4 weights go to the integer tensor-core path (m16n8k32, u8 x s8/u8) as bytes: one AND
+// extracts the four low nibbles of a weight word, one shift + AND the four high nibbles. The
+// producer of the activations stores x as 16-bit fixed point (signed high byte, unsigned low
+// byte, one scale per token and group) plus the group sum of x; then
+//   sum_k (q_k - z) x_k = sx * (256 * acc_h + acc_l) - z * xsum   with exact int32 accumulation.
 #include "common.cuh"
 #include "actpack.cuh"
 
 namespace owl {
 
 __device__ int g_skinny_status = 0;   // first bounded-wait failure of any skinny kernel (0 = none)
+// Lanes whose token column does not exist read their B fragments / group sums from this zero
+// page (pointer step 0) instead of branching around the loads.
+__device__ __align__(16) uint4 g_zero_page[32];
 
 __device__ __forceinline__ void mma_f16_16816(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                               uint32_t b0, uint32_t b1) {
@@ -57,6 +58,31 @@ __device__ __forceinline__ void mma_bf16_16816(float* c, uint32_t a0, uint32_t a
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// m16n8k32 integer MMAs: A = unsigned weight bytes, B = signed (high plane) or unsigned (low plane)
+__device__ __forceinline__ void imma_u8s8(int* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                          uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void imma_u8u8(int* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                          uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {   // unsigned a bytes x signed b bytes
+  int d;
+  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ int dp4a_uu(uint32_t a, uint32_t b, int c) {   // unsigned x unsigned
+  int d;
+  asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
 }
 __device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t mask, uint32_t orv) {
   uint32_t r;
@@ -86,11 +112,12 @@ struct SkinnyParams {
   int n_tiles;           // N / 16
   int tiles_per_cta;     // contiguous row tiles per CTA
   int gout;              // EPI_SILU_PACK: group size of the produced ActPack (32 or 128)
+  int force_mma;         // tests / A-B runs: use the tensor-core arm even for one token
 };
 
 constexpr int SK_WARPS = 8;    // warps per CTA = K slices of the record layout
 constexpr int SK_SLOTS = 2;    // chunks in flight per warp
-constexpr int SK_CHUNK_BYTES = 4352;   // bulk-copy size target (one mbarrier per chunk)
+constexpr int SK_CHUNK_BYTES = 2176;   // bulk-copy size target (one mbarrier per chunk)
 
 template <int KIND> struct RecInfo;
 template <> struct RecInfo<KIND_W4_G128> { static constexpr int BYTES = 1024 + 64, KREC = 128; };
@@ -119,8 +146,12 @@ __device__ __forceinline__ void mma_f16_16816_z(float* c, uint32_t a0, uint32_t 
 // columns [w*KT/8, (w+1)*KT/8)), and inside a slice the order is [row tile][record]. Warp w of a
 // CTA that owns row tiles nt0.. therefore reads ONE contiguous byte stream, cut into fixed-size
 // chunks that ignore row-tile boundaries (one bulk copy + one mbarrier per chunk).
-template <int MT, int KIND>
-__global__ void __launch_bounds__(SK_WARPS * 32, 2) skinny_stream_kernel(SkinnyParams p, int epi) {
+// SIMT = true (single token only): the contraction runs on the CUDA cores with dp4a instead of the
+// warp-level tensor-core path. On sm_100 the legacy mma.sync path issues one m16n8k16/k32 MMA per
+// ~34 cycles per SM sub-core, which caps a W4 stream at ~4 TB/s (8 MMAs per 1088-byte record
+// whatever the token count); for one token 32 dp4a per lane per record are cheaper than that.
+template <int MT, int KIND, bool SIMT>
+__global__ void __launch_bounds__(SK_WARPS * 32, MT == 1 ? 4 : 2) skinny_stream_kernel(SkinnyParams p, int epi) {
   constexpr int REC = RecInfo<KIND>::BYTES, KREC = RecInfo<KIND>::KREC;
   constexpr bool W4 = KIND == KIND_W4_G128 || KIND == KIND_W4_G32;
   constexpr int G = KIND == KIND_W4_G32 ? 32 : 128;
@@ -160,9 +191,6 @@ __global__ void __launch_bounds__(SK_WARPS * 32, 2) skinny_stream_kernel(SkinnyP
     }
   }
   pdl_wait();
-  // Let the next kernel's CTAs come in as SM resources free up: their own weight prefetch
-  // overlaps the tail of this kernel (they still wait for this grid before reading its output).
-  pdl_launch_dependents();
 
   float acc[MT][4];
 #pragma unroll
@@ -172,17 +200,21 @@ __global__ void __launch_bounds__(SK_WARPS * 32, 2) skinny_stream_kernel(SkinnyP
   bool failed = false;
   constexpr int XSTRIDE = (KIND == KIND_BF16) ? 8 : 16;   // uint4 of x per record and token
   const uint4* xbase[MT];
-  const float2* xsA[MT];
-  bool tok_ok[MT], okA[MT], okB[MT];
+  const float2 *xsA[MT], *xsB[MT];
+  int xstep[MT], sstepA[MT], sstepB[MT];
   const int KG = p.K / G;
 #pragma unroll
   for (int m = 0; m < MT; ++m) {
-    const int tok = m * 8 + g;
-    tok_ok[m] = tok < p.M;
-    xbase[m] = p.x + ((size_t)tok * p.K) / 8 + (size_t)kt0 * XSTRIDE + (KIND == KIND_W8 ? t * 2 : t);
-    const int tokA = m * 8 + 2 * t;
-    okA[m] = tokA < p.M; okB[m] = tokA + 1 < p.M;
-    xsA[m] = W4 ? p.xs + (size_t)tokA * KG + (size_t)kt0 * GPT : nullptr;
+    const int tok = SIMT ? 0 : m * 8 + g;
+    const bool ok = tok < p.M;
+    xbase[m] = ok ? p.x + ((size_t)tok * p.K) / 8 + (size_t)kt0 * XSTRIDE + (KIND == KIND_W8 ? t * 2 : t) : g_zero_page;
+    xstep[m] = ok ? XSTRIDE : 0;
+    const int tokA = SIMT ? 0 : m * 8 + 2 * t;
+    const float2* z2 = reinterpret_cast<const float2*>(g_zero_page);
+    xsA[m] = (W4 && tokA < p.M) ? p.xs + (size_t)tokA * KG + (size_t)kt0 * GPT : z2;
+    xsB[m] = (W4 && tokA + 1 < p.M) ? p.xs + (size_t)(tokA + 1) * KG + (size_t)kt0 * GPT : z2;
+    sstepA[m] = (W4 && tokA < p.M) ? GPT : 0;
+    sstepB[m] = (W4 && tokA + 1 < p.M) ? GPT : 0;
   }
 
   int item = 0, kk = 0;       // position of the current record: row tile nt0+item, record kt0+kk
@@ -195,20 +227,15 @@ __global__ void __launch_bounds__(SK_WARPS * 32, 2) skinny_stream_kernel(SkinnyP
       uint4 xb[MT][4];
 #pragma unroll
       for (int m = 0; m < MT; ++m) {
-        const uint4* xp = xbase[m] + (size_t)kk * XSTRIDE;
-        if (tok_ok[m]) {
-          if (W4) {
+        const uint4* xp = xbase[m] + kk * xstep[m];
+        if (W4) {
 #pragma unroll
-            for (int w = 0; w < 4; ++w) xb[m][w] = __ldg(xp + w * 4);
-          } else if (KIND == KIND_BF16) {
-            xb[m][0] = __ldg(xp); xb[m][1] = __ldg(xp + 4);
-          } else {
-            xb[m][0] = __ldg(xp); xb[m][1] = __ldg(xp + 1);       // k-step 0: 16 consecutive x
-            xb[m][2] = __ldg(xp + 8); xb[m][3] = __ldg(xp + 9);   // k-step 1 (+64 k)
-          }
+          for (int w = 0; w < 4; ++w) xb[m][w] = __ldg(xp + w * 4);
+        } else if (KIND == KIND_BF16) {
+          xb[m][0] = __ldg(xp); xb[m][1] = __ldg(xp + 4);
         } else {
-#pragma unroll
-          for (int w = 0; w < 4; ++w) xb[m][w] = make_uint4(0, 0, 0, 0);
+          xb[m][0] = __ldg(xp); xb[m][1] = __ldg(xp + 1);       // k-step 0: 16 consecutive x
+          xb[m][2] = __ldg(xp + 8); xb[m][3] = __ldg(xp + 9);   // k-step 1 (+64 k)
         }
       }
       float2 sa[MT][GPT], sb[MT][GPT];
@@ -217,8 +244,8 @@ __global__ void __launch_bounds__(SK_WARPS * 32, 2) skinny_stream_kernel(SkinnyP
         for (int m = 0; m < MT; ++m)
 #pragma unroll
           for (int q = 0; q < GPT; ++q) {
-            sa[m][q] = okA[m] ? __ldg(xsA[m] + kk * GPT + q) : make_float2(0.f, 0.f);
-            sb[m][q] = okB[m] ? __ldg(xsA[m] + KG + kk * GPT + q) : make_float2(0.f, 0.f);
+            sa[m][q] = __ldg(xsA[m] + kk * sstepA[m] + q);
+            sb[m][q] = __ldg(xsB[m] + kk * sstepB[m] + q);
           }
       }
       if (in_chunk == 0) {
@@ -230,51 +257,65 @@ __global__ void __launch_bounds__(SK_WARPS * 32, 2) skinny_stream_kernel(SkinnyP
       const uint4* rec = reinterpret_cast<const uint4*>(rec_b);
       if (W4) {
         const uint4 lo = rec[lane], hi = rec[32 + lane];
-        const uint32_t ql[4] = {lo.x, lo.y, lo.z, lo.w};
-        const uint32_t qh[4] = {hi.x, hi.y, hi.z, hi.w};
+        const uint32_t ql[4] = {lo.x, lo.y, lo.z, lo.w};   // row g:   word w = bytes of k-run (w, t)
+        const uint32_t qh[4] = {hi.x, hi.y, hi.z, hi.w};   // row g+8
         const uint32_t* szr = reinterpret_cast<const uint32_t*>(rec + 64);
         uint32_t su0[GPT], su1[GPT];
 #pragma unroll
         for (int q = 0; q < GPT; ++q) { su0[q] = szr[q * 16 + g]; su1[q] = szr[q * 16 + 8 + g]; }
-        uint32_t fa[4][8];
+        uint32_t nl[4], nh[4], ul[4], uh[4];                // low / high nibbles as bytes, rows g / g+8
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
-          fa[w][0] = lop3_and_or(ql[w], 0x000F000Fu, 0x64006400u);
-          fa[w][2] = lop3_and_or(ql[w], 0x00F000F0u, 0x64006400u);
-          fa[w][1] = lop3_and_or(qh[w], 0x000F000Fu, 0x64006400u);
-          fa[w][3] = lop3_and_or(qh[w], 0x00F000F0u, 0x64006400u);
-          const uint32_t ql8 = ql[w] >> 8, qh8 = qh[w] >> 8;
-          fa[w][4] = lop3_and_or(ql8, 0x000F000Fu, 0x64006400u);
-          fa[w][6] = lop3_and_or(ql8, 0x00F000F0u, 0x64006400u);
-          fa[w][5] = lop3_and_or(qh8, 0x000F000Fu, 0x64006400u);
-          fa[w][7] = lop3_and_or(qh8, 0x00F000F0u, 0x64006400u);
+          nl[w] = ql[w] & 0x0F0F0F0Fu; nh[w] = qh[w] & 0x0F0F0F0Fu;
+          ul[w] = (ql[w] >> 4) & 0x0F0F0F0Fu; uh[w] = (qh[w] >> 4) & 0x0F0F0F0Fu;
         }
-        if (G == 128) {
-          // two independent chains of four MMAs (words 0,1 and words 2,3)
-          float c0[MT][4], c1[MT][4];
+        // xb[m][w] = chunk of k-run (w, t) for token g: .x/.y = high/low byte plane of the
+        // activations under the low nibbles, .z/.w = the same for the high nibbles.
+        if (SIMT) {
+          // one token: per row (g, g+8) and word, 4 dp4a; the partial sums cover this lane's k-runs
+          // (quarter t of every word), the four t lanes are summed once per row tile
 #pragma unroll
-          for (int m = 0; m < MT; ++m) {
-            mma_f16_16816_z(c0[m], fa[0][0], fa[0][1], fa[0][2], fa[0][3], xb[m][0].x, xb[m][0].y);
-            mma_f16_16816_z(c1[m], fa[2][0], fa[2][1], fa[2][2], fa[2][3], xb[m][2].x, xb[m][2].y);
-            mma_f16_16816(c0[m], fa[0][4], fa[0][5], fa[0][6], fa[0][7], xb[m][0].z, xb[m][0].w);
-            mma_f16_16816(c1[m], fa[2][4], fa[2][5], fa[2][6], fa[2][7], xb[m][2].z, xb[m][2].w);
-            mma_f16_16816(c0[m], fa[1][0], fa[1][1], fa[1][2], fa[1][3], xb[m][1].x, xb[m][1].y);
-            mma_f16_16816(c1[m], fa[3][0], fa[3][1], fa[3][2], fa[3][3], xb[m][3].x, xb[m][3].y);
-            mma_f16_16816(c0[m], fa[1][4], fa[1][5], fa[1][6], fa[1][7], xb[m][1].z, xb[m][1].w);
-            mma_f16_16816(c1[m], fa[3][4], fa[3][5], fa[3][6], fa[3][7], xb[m][3].z, xb[m][3].w);
+          for (int q = 0; q < GPT; ++q) {
+            int h0 = 0, l0 = 0, h1 = 0, l1 = 0;
+#pragma unroll
+            for (int w = (G == 128 ? 0 : q); w < (G == 128 ? 4 : q + 1); ++w) {
+              h0 = dp4a_us(nl[w], xb[0][w].x, h0); l0 = dp4a_uu(nl[w], xb[0][w].y, l0);
+              h0 = dp4a_us(ul[w], xb[0][w].z, h0); l0 = dp4a_uu(ul[w], xb[0][w].w, l0);
+              h1 = dp4a_us(nh[w], xb[0][w].x, h1); l1 = dp4a_uu(nh[w], xb[0][w].y, l1);
+              h1 = dp4a_us(uh[w], xb[0][w].z, h1); l1 = dp4a_uu(uh[w], xb[0][w].w, l1);
+            }
+            const __half2 hh0 = *reinterpret_cast<const __half2*>(&su0[q]);
+            const __half2 hh1 = *reinterpret_cast<const __half2*>(&su1[q]);
+            const float sc0 = __low2float(hh0), z0 = __high2float(hh0);
+            const float sc1 = __low2float(hh1), z1 = __high2float(hh1);
+            const float xq = 0.25f * sa[0][q].y;    // each of the 4 t lanes carries a quarter of z * xsum
+            acc[0][0] = fmaf(sc0, fmaf(sa[0][q].x, (float)(h0 * 256 + l0), -z0 * xq), acc[0][0]);
+            acc[0][2] = fmaf(sc1, fmaf(sa[0][q].x, (float)(h1 * 256 + l1), -z1 * xq), acc[0][2]);
           }
-          const __half2 h0 = *reinterpret_cast<const __half2*>(&su0[0]);
-          const __half2 h1 = *reinterpret_cast<const __half2*>(&su1[0]);
-          const float sc0 = __low2float(h0), z0 = __high2float(h0);
-          const float sc1 = __low2float(h1), z1 = __high2float(h1);
+        } else if (G == 128) {
 #pragma unroll
           for (int m = 0; m < MT; ++m) {
-            acc[m][0] = fmaf(sc0, (c0[m][0] + c1[m][0]) - fmaf(z0, sa[m][0].x, sa[m][0].y), acc[m][0]);
-            acc[m][1] = fmaf(sc0, (c0[m][1] + c1[m][1]) - fmaf(z0, sb[m][0].x, sb[m][0].y), acc[m][1]);
-            acc[m][2] = fmaf(sc1, (c0[m][2] + c1[m][2]) - fmaf(z1, sa[m][0].x, sa[m][0].y), acc[m][2]);
-            acc[m][3] = fmaf(sc1, (c0[m][3] + c1[m][3]) - fmaf(z1, sb[m][0].x, sb[m][0].y), acc[m][3]);
+            int ch[4] = {0, 0, 0, 0}, cl[4] = {0, 0, 0, 0};
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {   // one k32-byte MMA covers words 2i and 2i+1
+              imma_u8s8(ch, nl[2 * i], nh[2 * i], nl[2 * i + 1], nh[2 * i + 1], xb[m][2 * i].x, xb[m][2 * i + 1].x);
+              imma_u8u8(cl, nl[2 * i], nh[2 * i], nl[2 * i + 1], nh[2 * i + 1], xb[m][2 * i].y, xb[m][2 * i + 1].y);
+              imma_u8s8(ch, ul[2 * i], uh[2 * i], ul[2 * i + 1], uh[2 * i + 1], xb[m][2 * i].z, xb[m][2 * i + 1].z);
+              imma_u8u8(cl, ul[2 * i], uh[2 * i], ul[2 * i + 1], uh[2 * i + 1], xb[m][2 * i].w, xb[m][2 * i + 1].w);
+            }
+            const __half2 h0 = *reinterpret_cast<const __half2*>(&su0[0]);
+            const __half2 h1 = *reinterpret_cast<const __half2*>(&su1[0]);
+            const float sc0 = __low2float(h0), z0 = __high2float(h0);
+            const float sc1 = __low2float(h1), z1 = __high2float(h1);
+            const float f0 = (float)(ch[0] * 256 + cl[0]), f1 = (float)(ch[1] * 256 + cl[1]);
+            const float f2 = (float)(ch[2] * 256 + cl[2]), f3 = (float)(ch[3] * 256 + cl[3]);
+            acc[m][0] = fmaf(sc0, fmaf(sa[m][0].x, f0, -z0 * sa[m][0].y), acc[m][0]);
+            acc[m][1] = fmaf(sc0, fmaf(sb[m][0].x, f1, -z0 * sb[m][0].y), acc[m][1]);
+            acc[m][2] = fmaf(sc1, fmaf(sa[m][0].x, f2, -z1 * sa[m][0].y), acc[m][2]);
+            acc[m][3] = fmaf(sc1, fmaf(sb[m][0].x, f3, -z1 * sb[m][0].y), acc[m][3]);
           }
         } else {
+          // group 32 = one word per group: the second half of the k32 MMA is fed zeros
 #pragma unroll
           for (int q = 0; q < GPT; ++q) {
             const __half2 h0 = *reinterpret_cast<const __half2*>(&su0[q]);
@@ -283,13 +324,17 @@ __global__ void __launch_bounds__(SK_WARPS * 32, 2) skinny_stream_kernel(SkinnyP
             const float sc1 = __low2float(h1), z1 = __high2float(h1);
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
-              float c[4];
-              mma_f16_16816_z(c, fa[q][0], fa[q][1], fa[q][2], fa[q][3], xb[m][q].x, xb[m][q].y);
-              mma_f16_16816(c, fa[q][4], fa[q][5], fa[q][6], fa[q][7], xb[m][q].z, xb[m][q].w);
-              acc[m][0] = fmaf(sc0, c[0] - fmaf(z0, sa[m][q].x, sa[m][q].y), acc[m][0]);
-              acc[m][1] = fmaf(sc0, c[1] - fmaf(z0, sb[m][q].x, sb[m][q].y), acc[m][1]);
-              acc[m][2] = fmaf(sc1, c[2] - fmaf(z1, sa[m][q].x, sa[m][q].y), acc[m][2]);
-              acc[m][3] = fmaf(sc1, c[3] - fmaf(z1, sb[m][q].x, sb[m][q].y), acc[m][3]);
+              int ch[4] = {0, 0, 0, 0}, cl[4] = {0, 0, 0, 0};
+              imma_u8s8(ch, nl[q], nh[q], 0u, 0u, xb[m][q].x, 0u);
+              imma_u8u8(cl, nl[q], nh[q], 0u, 0u, xb[m][q].y, 0u);
+              imma_u8s8(ch, ul[q], uh[q], 0u, 0u, xb[m][q].z, 0u);
+              imma_u8u8(cl, ul[q], uh[q], 0u, 0u, xb[m][q].w, 0u);
+              const float f0 = (float)(ch[0] * 256 + cl[0]), f1 = (float)(ch[1] * 256 + cl[1]);
+              const float f2 = (float)(ch[2] * 256 + cl[2]), f3 = (float)(ch[3] * 256 + cl[3]);
+              acc[m][0] = fmaf(sc0, fmaf(sa[m][q].x, f0, -z0 * sa[m][q].y), acc[m][0]);
+              acc[m][1] = fmaf(sc0, fmaf(sb[m][q].x, f1, -z0 * sb[m][q].y), acc[m][1]);
+              acc[m][2] = fmaf(sc1, fmaf(sa[m][q].x, f2, -z1 * sa[m][q].y), acc[m][2]);
+              acc[m][3] = fmaf(sc1, fmaf(sb[m][q].x, f3, -z1 * sb[m][q].y), acc[m][3]);
             }
           }
         }
@@ -364,6 +409,12 @@ __global__ void __launch_bounds__(SK_WARPS * 32, 2) skinny_stream_kernel(SkinnyP
 #pragma unroll
       for (int m = 0; m < MT; ++m) { acc[m][0] *= s0; acc[m][1] *= s0; acc[m][2] *= s1; acc[m][3] *= s1; }
     }
+    if (SIMT) {
+      acc[0][0] += __shfl_xor_sync(0xffffffffu, acc[0][0], 1);
+      acc[0][0] += __shfl_xor_sync(0xffffffffu, acc[0][0], 2);
+      acc[0][2] += __shfl_xor_sync(0xffffffffu, acc[0][2], 1);
+      acc[0][2] += __shfl_xor_sync(0xffffffffu, acc[0][2], 2);
+    }
     // split-K reduction across the 8 warps (double buffered: one barrier per item)
     float* rbuf = red + (size_t)(item & 1) * SK_WARPS * 32 * MT * 4;
     float* mine = rbuf + ((size_t)wi * 32 + lane) * (MT * 4);
@@ -388,6 +439,7 @@ __global__ void __launch_bounds__(SK_WARPS * 32, 2) skinny_stream_kernel(SkinnyP
       }
       const int grp = item >> 4;            // 16 row tiles = 128 silu outputs = one pack group set
       __nv_bfloat16* gb = gbuf + (size_t)(grp & 1) * MT * 8 * 128;
+
 #pragma unroll
       for (int m = 0; m < MT; ++m) {
 #pragma unroll
@@ -415,7 +467,7 @@ __global__ void __launch_bounds__(SK_WARPS * 32, 2) skinny_stream_kernel(SkinnyP
           }
         }
       }
-      if (epi == EPI_SILU_PACK && ((item & 15) == 15 || item == n_items - 1)) {
+      if (epi == EPI_SILU_PACK && (item & 15) == 15) {
         // 128 activations per token are complete (earlier tiles were finished by other warps
         // before they reached this item's barrier): pack them. Host guarantees tiles_per_cta % 16 == 0.
         __syncwarp();
@@ -427,24 +479,25 @@ __global__ void __launch_bounds__(SK_WARPS * 32, 2) skinny_stream_kernel(SkinnyP
           float v8[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) v8[i] = __bfloat162float(gb[(size_t)tok * 128 + ch * 8 + i]);
-          float s_st, s_eff;
-          const uint4 pk = actpack_chunk(v8, s_st, s_eff);
-          actpack_group_reduce(s_st, s_eff, cpg);
+          float sx, xsum;
+          const uint4 pk = actpack_emit(v8, cpg, sx, xsum);
           if (tok < p.M) {
             p.out_pack[((size_t)tok * I + col0) / 8 + ch] = pk;
-            if ((ch % cpg) == 0)
-              p.out_xs[(size_t)tok * (I / p.gout) + col0 / p.gout + ch / cpg] = make_float2(s_eff, 1024.f * s_st);
+            if ((ch % cpg) == 0) p.out_xs[(size_t)tok * (I / p.gout) + col0 / p.gout + ch / cpg] = make_float2(sx, xsum);
           }
         }
       }
     }
     ++item;
   }
+  // Dependents are released when this CTA is done streaming: releasing them earlier only parks
+  // their CTAs on SM resources this kernel still needs (measured slower).
+  pdl_launch_dependents();
 }
 
-template <int MT, int KIND>
+template <int MT, int KIND, bool SIMT = false>
 static int launch_skinny(const SkinnyParams& p, int epi, int pdl, cudaStream_t st) {
-  auto kernel = skinny_stream_kernel<MT, KIND>;
+  auto kernel = skinny_stream_kernel<MT, KIND, SIMT>;
   constexpr int smem = skinny_smem_bytes<MT, KIND>();
   static bool attr_done = false;
   if (!attr_done) {
@@ -470,7 +523,7 @@ static int launch_skinny(const SkinnyParams& p, int epi, int pdl, cudaStream_t s
 // Contiguous row tiles per CTA: enough CTAs to fill every SM twice, multiples of 16 for the
 // fused pack epilogue.
 static int pick_tiles_per_cta(int n_tiles, int epi, int want) {
-  int tpc = want > 0 ? want : (n_tiles + 295) / 296;
+  int tpc = want > 0 ? want : (n_tiles + 591) / 592;   // ~4 CTAs per SM: the dp4a arm needs the warps
   if (tpc < 1) tpc = 1;
   if (epi == EPI_SILU_PACK) tpc = ((tpc + 15) / 16) * 16;
   return tpc;
@@ -479,6 +532,8 @@ static int pick_tiles_per_cta(int n_tiles, int epi, int want) {
 template <int KIND>
 static int dispatch_mt(const SkinnyParams& p, int epi, int pdl, cudaStream_t st) {
   const int mt = (p.M + 7) / 8;
+  constexpr bool W4K = KIND == KIND_W4_G128 || KIND == KIND_W4_G32;
+  if (W4K && p.M == 1 && !p.force_mma) return launch_skinny<1, KIND, W4K>(p, epi, pdl, st);
   if (mt == 1) return launch_skinny<1, KIND>(p, epi, pdl, st);
   if (mt == 2) return launch_skinny<2, KIND>(p, epi, pdl, st);
   return launch_skinny<4, KIND>(p, epi, pdl, st);
@@ -503,7 +558,8 @@ OWL_API int owl_w4a16_skinny(const void* records, const void* xpack, const void*
   p.out = out; p.residual = (const __nv_bfloat16*)residual; p.out_pack = (uint4*)out_pack; p.out_xs = (float2*)out_xs;
   p.M = M; p.N = N; p.K = K; p.ldo = ldo; p.gout = gout;
   p.n_tiles = N / 16;
-  p.tiles_per_cta = pick_tiles_per_cta(p.n_tiles, epi, tiles_per_cta);
+  p.force_mma = (tiles_per_cta < 0);
+  p.tiles_per_cta = pick_tiles_per_cta(p.n_tiles, epi, tiles_per_cta < 0 ? -tiles_per_cta - 1 : tiles_per_cta);
   return group == 128 ? dispatch_mt<KIND_W4_G128>(p, epi, pdl, st) : dispatch_mt<KIND_W4_G32>(p, epi, pdl, st);
 }
 

@@ -257,7 +257,7 @@ class HybridRunner:
         self.G = weights.group
         dev, H, M = self.device, spec.hidden, self.MAX_ROWS
         bf = lambda *s: torch.zeros(*s, dtype=torch.bfloat16, device=dev)
-        f16 = lambda *s: torch.zeros(*s, dtype=torch.float16, device=dev)
+        f16 = lambda m_, k_: torch.zeros(m_, 2 * k_, dtype=torch.uint8, device=dev)   # ActPack: 2 bytes per k
         f32 = lambda *s: torch.zeros(*s, dtype=torch.float32, device=dev)
         G = self.G
         self.block_table = torch.zeros(max_seqs, max_blocks, dtype=torch.int32, device=dev)
@@ -279,6 +279,7 @@ class HybridRunner:
         self.part_o = f32(M * spec.hq * self.max_splits * spec.hd)
         self.part_ml = f32(M * spec.hq * self.max_splits * 2)
         self.xp_a, self.xs_a = f16(M, spec.hq * spec.hd), f32(M, spec.hq * spec.hd // G, 2)
+        self.act = bf(M, spec.inter)
         self.side = torch.cuda.Stream(device=dev)   # forked branch for the small a/b projection
         self.xp_i, self.xs_i = f16(M, spec.inter), f32(M, spec.inter // G, 2)
         self.vocab_local = weights.lm_head.n
@@ -314,8 +315,10 @@ class HybridRunner:
         sp = self.spec
         K.rmsnorm_pack(self.h, lw.ln2, xpack=self.xp_h, xs=self.xs_h, m=m, k=sp.hidden, group=self.G, eps=sp.eps,
                        pdl=self.pdl)
-        K.w4a16_skinny(lw.gate_up, self.xp_h, self.xs_h, None, m, epi=K.EPI_SILU_PACK, ldo=sp.inter,
-                       out_pack=self.xp_i, out_xs=self.xs_i, gout=self.G, pdl=self.pdl)
+        # silu(gate)*up is written as bf16 and packed by a small kernel: the fused pack epilogue
+        # (EPI_SILU_PACK) needs 16 row tiles per CTA, which leaves too few CTAs at this size
+        K.w4a16_skinny(lw.gate_up, self.xp_h, self.xs_h, self.act, m, epi=K.EPI_SILU_MUL, ldo=sp.inter, pdl=self.pdl)
+        K.act_pack(self.act, self.xp_i, self.xs_i, m, sp.inter, self.G, pdl=self.pdl)
         self._row_parallel(lw.down, self.xp_i, self.xs_i, m)
 
     def _gdn(self, lw: LayerWeights, li: int, lay: StepLayout, v: dict) -> None:

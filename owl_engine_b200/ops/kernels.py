@@ -75,10 +75,14 @@ EPI_STORE, EPI_RESIDUAL, EPI_SILU_MUL, EPI_F32, EPI_SILU_PACK = 0, 1, 2, 3, 4
 
 
 def w4a16_skinny(w, xpack, xs, out, m: int, *, residual=None, epi: int = EPI_STORE, ldo: int | None = None,
-                 out_pack=None, out_xs=None, gout: int = 128, tiles_per_cta: int = 0, pdl: bool = False) -> None:
-    """out[m, :] = dequant(w) @ x for m <= 32 rows. ``w`` is a ``W4Skinny``."""
+                 out_pack=None, out_xs=None, gout: int = 128, tiles_per_cta: int = 0, pdl: bool = False,
+                 force_mma: bool = False) -> None:
+    """out[m, :] = dequant(w) @ x for m <= 32 rows. ``w`` is a ``W4Skinny``. One token runs on the
+    dp4a arm unless ``force_mma`` (A/B runs and tests of the tensor-core arm)."""
     if ldo is None:
         ldo = out.shape[-1] if out is not None else w.n
+    if force_mma:
+        tiles_per_cta = -tiles_per_cta - 1
     call("owl_w4a16_skinny", ptr(w.records), ptr(xpack), ptr(xs), ptr(out), ptr(residual), ptr(out_pack), ptr(out_xs),
          m, w.n, w.k, ldo, w.group, epi, gout, tiles_per_cta, int(pdl), stream())
 

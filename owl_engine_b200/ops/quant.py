@@ -242,19 +242,42 @@ def dense_skinny(w: torch.Tensor, device=None, int8: bool = False) -> DenseSkinn
 
 # ---- ActPack -----------------------------------------------------------------------------
 def act_pack_ref(x: torch.Tensor, group: int):
-    """fp32 reference of the ActPack producer: returns (xpack fp16 [M,K], xs fp32 [M,K/G,2]).
-    Per 8 consecutive k the stored halves are [x0, x1, x2/16, x3/16, x4, x5, x6/16, x7/16]."""
+    """fp32 reference of the ActPack producer (see ``csrc/actpack.cuh``).
+
+    Returns ``(xpack uint8 [M, 2K], xs fp32 [M, K/G, 2])``. Activations are 16-bit fixed point,
+    ``x = sx * (256 h + l)`` (h signed, l unsigned byte), one scale per (token, group). Every run of
+    8 consecutive k is one 16-byte chunk ``[h(a) x4 | l(a) x4 | h(c) x4 | l(c) x4]`` where for weight
+    byte b, a = x[{0,4,1,5}[b]] (low nibble) and c = x[{2,6,3,7}[b]] (high nibble);
+    ``xs = (sx, xsum)``."""
     m, k = x.shape
-    v = x.to(torch.float32).clamp(-65504, 65504).view(m, k // 8, 8).clone()
-    v[..., [2, 3, 6, 7]] *= 0.0625
-    h = v.to(torch.float16)
-    hf = h.to(torch.float32)
-    eff = hf.clone()
-    eff[..., [2, 3, 6, 7]] *= 16.0
+    v = x.to(torch.float32).view(m, k // 8, 8)
+    a, c = v[..., [0, 4, 1, 5]], v[..., [2, 6, 3, 7]]
     cpg = group // 8
-    s_st = hf.sum(-1).view(m, k // group, cpg).sum(-1)
-    s_eff = eff.sum(-1).view(m, k // group, cpg).sum(-1)
-    return h.view(m, k), torch.stack([s_eff, 1024.0 * s_st], dim=-1)
+    amax = torch.maximum(a.abs(), c.abs()).amax(-1).view(m, k // group, cpg).amax(-1)
+    sx = amax.clamp_min(1e-30) * torch.tensor(1.0 / 32767.0, dtype=torch.float32)
+    inv = (1.0 / sx).repeat_interleave(cpg, dim=1)[..., None]
+    qa = torch.round(a * inv).to(torch.int32)
+    qc = torch.round(c * inv).to(torch.int32)
+    planes = torch.stack([(qa >> 8) & 0xFF, qa & 0xFF, (qc >> 8) & 0xFF, qc & 0xFF], dim=2)   # [m, chunks, 4, 4]
+    xpack = planes.to(torch.uint8).reshape(m, 2 * k)
+    xsum = (a + c).sum(-1).view(m, k // group, cpg).sum(-1)
+    return xpack, torch.stack([sx, xsum], dim=-1)
+
+
+def act_unpack_ref(xpack: torch.Tensor, xs: torch.Tensor, group: int) -> torch.Tensor:
+    """Inverse of ``act_pack_ref`` up to the fixed-point rounding: fp32 activations [M, K]."""
+    m = xpack.shape[0]
+    p = xpack.view(m, -1, 4, 4).to(torch.int32)
+    def val(h, l):
+        h = torch.where(h >= 128, h - 256, h)
+        return (h * 256 + l).to(torch.float32)
+    cpg = group // 8
+    sx = xs[..., 0].repeat_interleave(cpg, dim=1)[..., None]
+    a, c = val(p[:, :, 0], p[:, :, 1]) * sx, val(p[:, :, 2], p[:, :, 3]) * sx
+    out = torch.empty(m, p.shape[1], 8)
+    out[..., [0, 4, 1, 5]] = a
+    out[..., [2, 6, 3, 7]] = c
+    return out.reshape(m, -1)
 
 
 def quantize_w8_rows(w: torch.Tensor):

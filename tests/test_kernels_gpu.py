@@ -32,12 +32,12 @@ def test_pack_roundtrip_cpu_layout():
 def test_act_pack_matches_reference(group):
     m, k = 3, 512
     x = bf(torch.randn(m, k, generator=gen(2)) * 3)
-    xp = torch.empty(m, k, dtype=torch.float16, device=DEV)
+    xp = torch.empty(m, 2 * k, dtype=torch.uint8, device=DEV)
     xs = torch.empty(m, k // group, 2, dtype=torch.float32, device=DEV)
     K.act_pack(x.to(DEV), xp, xs, m, k, group)
     want_p, want_s = Q.act_pack_ref(x.float(), group)
     assert torch.equal(xp.cpu(), want_p)
-    torch.testing.assert_close(xs.cpu(), want_s, rtol=1e-5, atol=1e-3)
+    torch.testing.assert_close(xs.cpu(), want_s, rtol=1e-5, atol=1e-4)
 
 
 @pytest.mark.parametrize("m", [1, 3, 8, 13, 32])
@@ -49,13 +49,17 @@ def test_w4a16_skinny(m, group, shape):
     c = Q.quantize_w4(w, group)
     s = Q.pack_skinny(c).to(DEV)
     x = bf(torch.randn(m, k, generator=gen(4)))
-    xp = torch.empty(m, k, dtype=torch.float16, device=DEV)
+    xp = torch.empty(m, 2 * k, dtype=torch.uint8, device=DEV)
     xs = torch.empty(m, k // group, 2, dtype=torch.float32, device=DEV)
     K.act_pack(x.to(DEV), xp, xs, m, k, group)
     out = torch.zeros(m, n, dtype=torch.bfloat16, device=DEV)
     K.w4a16_skinny(s, xp, xs, out, m)
     want = x.float() @ c.dequant().t()
     torch.testing.assert_close(out.float().cpu(), want, rtol=2e-2, atol=2e-2 * want.abs().max().item())
+    if m == 1:   # the tensor-core arm must agree with the dp4a arm (both accumulate exactly in int32)
+        out2 = torch.zeros_like(out)
+        K.w4a16_skinny(s, xp, xs, out2, m, force_mma=True)
+        torch.testing.assert_close(out2.float(), out.float(), rtol=1e-2, atol=1e-3)
     # tighter: relative Frobenius error at bf16-output level
     err = (out.float().cpu() - want).norm() / want.norm()
     assert err < 5e-3, err
@@ -68,7 +72,7 @@ def test_w4a16_skinny_splitk_and_epilogues(ks):
     c = Q.quantize_w4(w, group)
     s = Q.pack_skinny(c).to(DEV)
     x = bf(torch.randn(m, k, generator=gen(6)))
-    xp = torch.empty(m, k, dtype=torch.float16, device=DEV)
+    xp = torch.empty(m, 2 * k, dtype=torch.uint8, device=DEV)
     xs = torch.empty(m, k // group, 2, dtype=torch.float32, device=DEV)
     K.act_pack(x.to(DEV), xp, xs, m, k, group)
     want = x.float() @ c.dequant().t()
@@ -92,18 +96,18 @@ def test_w4a16_skinny_fused_silu_pack(m, gout):
     c = Q.quantize_w4(torch.randn(n, k, generator=gen(50)) * 0.05, group)
     s = Q.pack_skinny(c).to(DEV)
     x = bf(torch.randn(m, k, generator=gen(51)))
-    xp = torch.empty(m, k, dtype=torch.float16, device=DEV)
+    xp = torch.empty(m, 2 * k, dtype=torch.uint8, device=DEV)
     xs = torch.empty(m, k // group, 2, dtype=torch.float32, device=DEV)
     K.act_pack(x.to(DEV), xp, xs, m, k, group)
     inter = n // 2
-    op = torch.zeros(m, inter, dtype=torch.float16, device=DEV)
+    op = torch.zeros(m, 2 * inter, dtype=torch.uint8, device=DEV)
     oxs = torch.zeros(m, inter // gout, 2, dtype=torch.float32, device=DEV)
     K.w4a16_skinny(s, xp, xs, None, m, epi=K.EPI_SILU_PACK, ldo=inter, out_pack=op, out_xs=oxs, gout=gout)
     sm = torch.zeros(m, inter, dtype=torch.bfloat16, device=DEV)
     K.w4a16_skinny(s, xp, xs, sm, m, epi=K.EPI_SILU_MUL)
     wp, ws = Q.act_pack_ref(sm.float().cpu(), gout)
     assert torch.equal(op.cpu(), wp)
-    torch.testing.assert_close(oxs.cpu(), ws, rtol=1e-5, atol=1e-2)
+    torch.testing.assert_close(oxs.cpu(), ws, rtol=1e-5, atol=1e-3)
 
 
 @pytest.mark.parametrize("m", [1, 5, 16])
@@ -131,7 +135,7 @@ def test_rmsnorm_pack(with_delta):
     w = bf(torch.randn(k, generator=gen(12)) * 0.1)
     out_h = torch.empty(m, k, dtype=torch.bfloat16, device=DEV)
     normed = torch.empty(m, k, dtype=torch.bfloat16, device=DEV)
-    xp = torch.empty(m, k, dtype=torch.float16, device=DEV)
+    xp = torch.empty(m, 2 * k, dtype=torch.uint8, device=DEV)
     xs = torch.empty(m, k // group, 2, dtype=torch.float32, device=DEV)
     K.rmsnorm_pack(h.to(DEV), w.to(DEV), delta=d.to(DEV) if with_delta else None, out_h=out_h if with_delta else None,
                    normed=normed, xpack=xp, xs=xs, m=m, k=k, group=group)
@@ -142,7 +146,7 @@ def test_rmsnorm_pack(with_delta):
     torch.testing.assert_close(normed.float().cpu(), want, rtol=1e-2, atol=1e-2)
     wp, ws = Q.act_pack_ref(normed.float().cpu(), group)
     assert torch.equal(xp.cpu(), wp)
-    torch.testing.assert_close(xs.cpu(), ws, rtol=1e-5, atol=1e-2)
+    torch.testing.assert_close(xs.cpu(), ws, rtol=1e-5, atol=1e-3)
 
 
 def test_silu_mul_embed_argmax():
@@ -208,7 +212,7 @@ def test_gdn_decode(nk, nv, t):
     d = {k: (v.to(DEV) if torch.is_tensor(v) else v) for k, v in s.items()}
     slots = torch.tensor([2, 0], dtype=torch.int32, device=DEV)
     out = torch.zeros(batch * t, s["vdim"], dtype=torch.bfloat16, device=DEV)
-    xp = torch.zeros(batch * t, s["vdim"], dtype=torch.float16, device=DEV)
+    xp = torch.zeros(batch * t, 2 * s["vdim"], dtype=torch.uint8, device=DEV)
     xs = torch.zeros(batch * t, s["vdim"] // 128, 2, dtype=torch.float32, device=DEV)
     K.gdn_decode(d["qkvz"], d["qkvz"].shape[1], d["ab"], 2 * nv, d["conv_w"], d["a_log"], d["dt_bias"], d["gamma"],
                  d["conv_state"], d["state"], slots, out=out, xpack=xp, xs=xs, batch=batch, t=t, nk=nk, nv=nv)
@@ -223,7 +227,7 @@ def test_gdn_decode(nk, nv, t):
     assert torch.equal(d["state"][1].cpu(), s["state"][1])
     wp, ws = Q.act_pack_ref(out.float().cpu(), 128)
     assert torch.equal(xp.cpu(), wp)
-    torch.testing.assert_close(xs.cpu(), ws, rtol=1e-5, atol=1e-2)
+    torch.testing.assert_close(xs.cpu(), ws, rtol=1e-5, atol=1e-3)
 
 
 @pytest.mark.parametrize("t,use_state", [(70, True), (5, False), (2, True)])
