@@ -340,3 +340,40 @@ OWL_API int owl_decode_advance(void* inp, const void* tok, const void* block_tab
   return launch_pdl(decode_advance_kernel, dim3((B + 63) / 64), dim3(64), pdl, st, (int*)inp, (const int*)tok,
                     (const int*)block_table, max_blocks, B);
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free argmax (declared and documented in owl_noalloc.h).
+// ---------------------------------------------------------------------------------------------
+#include "owl_noalloc.h"
+
+namespace {
+constexpr int NA_PARTS = 64;
+constexpr int NA_MAX_DEV = 64;
+// Partial maxima of stage 1: [rows][parts] values followed by [rows][parts] indices.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[OWL_NOALLOC_MAX_ROWS * NA_PARTS * 8];
+// In host code the symbol above is only a handle; the device address is looked up once per device.
+static void* g_noalloc_ptr[NA_MAX_DEV] = {nullptr};
+}  // namespace
+
+OWL_API int owl_argmax_noalloc(const void* logits, int rows, int V, int ld, void* out_idx, int vocab_offset,
+                               cudaStream_t st) {
+  if (rows < 1 || rows > OWL_NOALLOC_MAX_ROWS || V < 1 || ld < V || !logits || !out_idx) return OWL_ERR_BAD_ARG;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)OWL_ERR_LAUNCH * 1000 - (int)e;
+  if (dev < 0 || dev >= NA_MAX_DEV) return OWL_ERR_BAD_ARG;
+  if (!g_noalloc_ptr[dev]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+    if (e != cudaSuccess || !ptr) return (int)OWL_ERR_LAUNCH * 1000 - (int)e;
+    g_noalloc_ptr[dev] = ptr;
+  }
+  float* pval = reinterpret_cast<float*>(g_noalloc_ptr[dev]);
+  int* pidx = reinterpret_cast<int*>(reinterpret_cast<unsigned char*>(g_noalloc_ptr[dev]) +
+                                     (size_t)OWL_NOALLOC_MAX_ROWS * NA_PARTS * 4);
+  int r = launch_pdl(argmax_stage1, dim3(NA_PARTS, rows), dim3(256), 0, st, (const __nv_bfloat16*)logits, V, ld, pval,
+                     pidx, NA_PARTS);
+  if (r) return r;
+  return launch_pdl(argmax_stage2, dim3(rows), dim3(32), 0, st, (const float*)pval, (const int*)pidx, NA_PARTS,
+                    (int*)out_idx, vocab_offset);
+}
