@@ -86,7 +86,8 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--prompt-len", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (result marked invalid)")
-    ap.add_argument("--comm", default="nccl", choices=["nccl", "fused"])
+    ap.add_argument("--comm", default="fused", choices=["nccl", "fused"],
+                    help="TP collectives: our symmetric-memory kernels (fused) or the NCCL baseline arm")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -103,7 +104,7 @@ def main() -> None:
     from owl_engine_b200.parallel.comm import TpComm
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    comm = TpComm.from_env(args.comm) if world > 1 else None
+    comm = TpComm.from_env(args.comm, hidden=5120, big_elems=2048 * 5120) if world > 1 else None
     rank = comm.rank if comm else 0
     if comm is None:
         torch.cuda.set_device(0)

@@ -1,0 +1,335 @@
+// Tensor-parallel collectives written as kernels over symmetric (peer-mapped) memory.
+//
+//   owl_ar_residual_norm : one-shot all-reduce of a row-parallel projection's partial sums
+//                          fused with the residual add, the following RMSNorm and the ActPack
+//                          producer:  h += sum_r partial_r ;  x = rmsnorm(h) * (1 + w)
+//                          One CTA per token row; every rank reduces the same values in the same
+//                          (rank) order, so all ranks hold bit-identical h. Decode / verify sizes.
+//   owl_ar_inplace       : plain one-shot all-reduce (sum) of a bf16 buffer, grid-strided; used for
+//                          prefill-size payloads when the GEMM-fused path is not taken.
+//   owl_argmax_merge     : vocab-split lm_head: exchange each rank's (max, index) per row and pick
+//                          the global winner on every rank.
+//
+// Protocol: every rank owns, inside its symmetric buffer, a flag table flags[slot][src_rank]
+// (uint32, monotonically increasing sequence numbers kept in a device-side counter so that a
+// replayed CUDA graph needs no host update). A CTA signals by storing its sequence number into
+// slot[cta] of every peer with st.release.sys and then waits (ld.acquire.sys, bounded) until all
+// peers' numbers arrived in its own table. Payload buffers are double-buffered by call site
+// (mixer / MLP alternate), so one barrier per collective is enough. A wait that runs out records
+// OWL_ERR_WAIT_PEER in the status word and the kernel finishes without hanging.
+//
+// Peer data is read with ld.relaxed.sys (plain NVLink P2P loads) or, when the caller passes a
+// multicast address, with multimem.ld_reduce (in-switch reduction over NVLink SHARP).
+// No TMA multicast is used anywhere in this file.
+//
+// Role in the reference: owl_comm_ar_barrier_* / owl_comm_ar_fused_* (crates/kernels/cu/comm/*.cu,
+// 2 ranks over PCIe P2P) followed by a separate owl_fused_add_rmsnorm launch; the fused
+// "AR + add + rmsnorm" hook the reference's charter reserves (charter.md:79-80) is what this is.
+#include "common.cuh"
+#include "actpack.cuh"
+
+namespace owl {
+
+constexpr int MAX_RANKS = 8;
+__device__ int g_comm_status = 0;
+
+struct PeerTable {
+  const void* ptr[MAX_RANKS];
+};
+struct FlagTable {
+  uint32_t* ptr[MAX_RANKS];   // base of each rank's flag table (peer-mapped)
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_relaxed_sys_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+// In-switch reduction of 8 bf16 values over all ranks' copies (fp32 accumulation in the switch).
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+  return v;
+}
+
+// Cross-rank barrier of one CTA slot. `counter` is this rank's private sequence counter for the
+// slot. Returns false when a peer's flag did not arrive within the limit.
+__device__ __forceinline__ bool rank_barrier(const FlagTable& ft, uint32_t* counters, int slot, int rank, int world,
+                                             uint32_t spin_limit) {
+  __shared__ uint32_t s_seq;
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    s_seq = counters[slot] + 1;
+    counters[slot] = s_seq;
+    s_ok = 1;
+  }
+  __syncthreads();
+  const uint32_t seq = s_seq;
+  if (threadIdx.x < world) {
+    const int peer = threadIdx.x;
+    // flags[slot][src = rank] in the peer's table
+    st_release_sys(ft.ptr[peer] + slot * MAX_RANKS + rank, seq);
+    const uint32_t* mine = ft.ptr[rank] + slot * MAX_RANKS + peer;
+    bool got = false;
+    for (uint32_t i = 0; i < spin_limit; ++i) {
+      // sequence numbers only grow; (int) difference handles wrap-around
+      if ((int)(ld_acquire_sys(mine) - seq) >= 0) { got = true; break; }
+      if (i > 64) __nanosleep(64);
+    }
+    if (!got) {
+      s_ok = 0;
+      atomicCAS(&g_comm_status, 0, OWL_ERR_WAIT_PEER);
+    }
+  }
+  __syncthreads();
+  return s_ok != 0;
+}
+
+struct ArNormParams {
+  PeerTable parts;            // each rank's partial [M][H] bf16 (same offset in every symmetric buffer)
+  const void* mc_part;        // multicast address of the partial buffer, or nullptr
+  FlagTable flags;
+  uint32_t* counters;         // [slots] private
+  __nv_bfloat16* h;           // [M][H] residual stream (in/out)
+  const __nv_bfloat16* w;     // norm weight [H] (nullptr: no norm, only h is updated)
+  __nv_bfloat16* normed;      // optional bf16 normalised output
+  uint4* xpack; float2* xs;   // optional ActPack of the normalised output
+  int H, G, rank, world, slot0, one_plus_w;
+  float eps;
+  uint32_t spin_limit;
+};
+
+__global__ void __launch_bounds__(1024) ar_residual_norm_kernel(ArNormParams p) {
+  __shared__ float red[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x;
+  rank_barrier(p.flags, p.counters, p.slot0 + row, p.rank, p.world, p.spin_limit);
+  const int nchunks = p.H >> 3;
+  __nv_bfloat16* hrow = p.h + (size_t)row * p.H;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < nchunks; c += blockDim.x) {
+    float acc[8];
+    if (p.mc_part) {
+      const uint4 u = multimem_ld_reduce_bf16x8(reinterpret_cast<const uint4*>(p.mc_part) + (size_t)row * nchunks + c);
+      unpack_bf16x8(u, acc);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+      for (int r = 0; r < p.world; ++r) {   // fixed rank order -> identical sums on every rank
+        const uint4 u = ld_relaxed_sys_v4(reinterpret_cast<const uint4*>(p.parts.ptr[r]) + (size_t)row * nchunks + c);
+        float v[8];
+        unpack_bf16x8(u, v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += v[i];
+      }
+    }
+    const uint4 hu = reinterpret_cast<const uint4*>(hrow)[c];
+    float hv[8];
+    unpack_bf16x8(hu, hv);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      hv[i] = __bfloat162float(__float2bfloat16(hv[i] + acc[i]));
+      ss += hv[i] * hv[i];
+    }
+    reinterpret_cast<uint4*>(hrow)[c] = pack_bf16x8(hv);
+  }
+  if (!p.w) return;
+  ss = block_sum(ss, red);
+  const float rinv = rsqrtf(ss / (float)p.H + p.eps);
+  const int nround = (nchunks + 31) & ~31;
+  const int cpg = p.G >> 3;
+  for (int c = threadIdx.x; c < nround; c += blockDim.x) {
+    float v[8];
+    const bool live = c < nchunks;
+    if (live) {
+      const uint4 a = reinterpret_cast<const uint4*>(hrow)[c];   // written by this thread above
+      unpack_bf16x8(a, v);
+      const uint4 wv = reinterpret_cast<const uint4*>(p.w)[c];
+      float wf[8];
+      unpack_bf16x8(wv, wf);
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        v[i] = __bfloat162float(__float2bfloat16(v[i] * rinv * (p.one_plus_w ? 1.f + wf[i] : wf[i])));
+      if (p.normed) reinterpret_cast<uint4*>(p.normed + (size_t)row * p.H)[c] = pack_bf16x8(v);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = 0.f;
+    }
+    if (p.xpack) {
+      float sx, xsum;
+      const uint4 pk = actpack_emit(v, cpg, sx, xsum);
+      if (live) p.xpack[(size_t)row * nchunks + c] = pk;
+      if (live && (c % cpg) == 0) p.xs[(size_t)row * (p.H / p.G) + c / cpg] = make_float2(sx, xsum);
+    }
+  }
+}
+
+// In-place sum over ranks of buf (bf16, n8 chunks of 8), every rank ends with the full sum.
+// Each CTA reduces a contiguous share and writes it back to its OWN buffer only; two barriers
+// (before reading, after reading) protect the in-place update.
+struct ArInplaceParams {
+  PeerTable bufs; FlagTable flags; uint32_t* counters;
+  __nv_bfloat16* scratch;      // local [n8*8] staging for the reduced values
+  size_t n8; int rank, world, slot0;
+  uint32_t spin_limit;
+};
+__global__ void __launch_bounds__(512) ar_inplace_kernel(ArInplaceParams p) {
+  const int slot = p.slot0 + blockIdx.x;
+  rank_barrier(p.flags, p.counters, slot, p.rank, p.world, p.spin_limit);
+  const size_t per = (p.n8 + gridDim.x - 1) / gridDim.x;
+  const size_t lo = per * blockIdx.x, hi = min(p.n8, lo + per);
+  for (size_t c = lo + threadIdx.x; c < hi; c += blockDim.x) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int r = 0; r < p.world; ++r) {
+      const uint4 u = ld_relaxed_sys_v4(reinterpret_cast<const uint4*>(p.bufs.ptr[r]) + c);
+      float v[8];
+      unpack_bf16x8(u, v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += v[i];
+    }
+    reinterpret_cast<uint4*>(p.scratch)[c] = pack_bf16x8(acc);
+  }
+  // every rank has finished reading this share before anyone overwrites it
+  rank_barrier(p.flags, p.counters, slot, p.rank, p.world, p.spin_limit);
+  uint4* mine = reinterpret_cast<uint4*>(const_cast<void*>(p.bufs.ptr[p.rank]));
+  for (size_t c = lo + threadIdx.x; c < hi; c += blockDim.x) mine[c] = reinterpret_cast<const uint4*>(p.scratch)[c];
+}
+
+// Vocab-split argmax merge: each rank publishes (value, index) per row, then all pick the max.
+struct ArgmaxMergeParams {
+  PeerTable exch;              // each rank's exchange area: float2-like {value, index} [rows][MAX_RANKS]
+  FlagTable flags; uint32_t* counters;
+  const float* local_val; const int* local_idx;   // this rank's per-row winner (index already global)
+  int* out_idx; int rows, rank, world, slot;
+  uint32_t spin_limit;
+};
+__global__ void __launch_bounds__(64) argmax_merge_kernel(ArgmaxMergeParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  // publish into every peer's exchange area (tiny: rows * 8 bytes per peer)
+  for (int i = threadIdx.x; i < p.rows * p.world; i += blockDim.x) {
+    const int row = i / p.world, peer = i % p.world;
+    uint2 v = make_uint2(__float_as_uint(p.local_val[row]), (uint32_t)p.local_idx[row]);
+    uint2* dst = reinterpret_cast<uint2*>(const_cast<void*>(p.exch.ptr[peer])) + row * MAX_RANKS + p.rank;
+    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1,%2};" ::"l"(dst), "r"(v.x), "r"(v.y) : "memory");
+  }
+  __threadfence_system();
+  __syncthreads();
+  rank_barrier(p.flags, p.counters, p.slot, p.rank, p.world, p.spin_limit);
+  for (int row = threadIdx.x; row < p.rows; row += blockDim.x) {
+    const uint2* src = reinterpret_cast<const uint2*>(p.exch.ptr[p.rank]) + row * MAX_RANKS;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int r = 0; r < p.world; ++r) {
+      uint2 v;
+      asm volatile("ld.relaxed.sys.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(src + r) : "memory");
+      const float val = __uint_as_float(v.x);
+      const int idx = (int)v.y;
+      if (val > best || (val == best && idx < bi)) { best = val; bi = idx; }
+    }
+    p.out_idx[row] = bi;
+  }
+}
+
+}  // namespace owl
+using namespace owl;
+
+static void fill_tables(PeerTable& pt, const void* const* ptrs, FlagTable& ft, void* const* flags, int world) {
+  for (int r = 0; r < MAX_RANKS; ++r) {
+    pt.ptr[r] = r < world ? ptrs[r] : nullptr;
+    ft.ptr[r] = r < world ? (uint32_t*)flags[r] : nullptr;
+  }
+}
+
+// part_ptrs / flag_ptrs: host arrays of `world` device pointers (peer-mapped). slot0: first flag slot
+// (rows M use slots slot0 .. slot0+M-1). mc_part may be null.
+OWL_API int owl_ar_residual_norm(const void* const* part_ptrs, const void* mc_part, void* const* flag_ptrs,
+                                 void* counters, void* h, const void* w, void* normed, void* xpack, void* xs, int M,
+                                 int H, int G, int rank, int world, int slot0, float eps, int one_plus_w,
+                                 unsigned spin_limit, int pdl, cudaStream_t st) {
+  if (M < 1 || (H & 127) || world < 2 || world > MAX_RANKS || rank < 0 || rank >= world || (G != 32 && G != 128))
+    return OWL_ERR_BAD_ARG;
+  ArNormParams p = {};
+  fill_tables(p.parts, part_ptrs, p.flags, flag_ptrs, world);
+  p.mc_part = mc_part; p.counters = (uint32_t*)counters; p.h = (__nv_bfloat16*)h; p.w = (const __nv_bfloat16*)w;
+  p.normed = (__nv_bfloat16*)normed; p.xpack = (uint4*)xpack; p.xs = (float2*)xs; p.H = H; p.G = G; p.rank = rank;
+  p.world = world; p.slot0 = slot0; p.one_plus_w = one_plus_w; p.eps = eps; p.spin_limit = spin_limit;
+  int threads = ((H / 8 + 31) / 32) * 32;
+  if (threads > 1024) threads = 1024;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(M); cfg.blockDim = dim3(threads); cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, ar_residual_norm_kernel, p);
+  if (e != cudaSuccess) return (int)OWL_ERR_LAUNCH * 1000 - (int)e;
+  return OWL_OK;
+}
+
+OWL_API int owl_ar_inplace(const void* const* buf_ptrs, void* const* flag_ptrs, void* counters, void* scratch,
+                           long long n_elems, int rank, int world, int slot0, int ctas, unsigned spin_limit,
+                           cudaStream_t st) {
+  if (n_elems < 8 || (n_elems & 7) || world < 2 || world > MAX_RANKS || ctas < 1 || ctas > 64) return OWL_ERR_BAD_ARG;
+  ArInplaceParams p = {};
+  fill_tables(p.bufs, buf_ptrs, p.flags, flag_ptrs, world);
+  p.counters = (uint32_t*)counters; p.scratch = (__nv_bfloat16*)scratch; p.n8 = (size_t)n_elems / 8; p.rank = rank;
+  p.world = world; p.slot0 = slot0; p.spin_limit = spin_limit;
+  ar_inplace_kernel<<<ctas, 512, 0, st>>>(p);
+  OWL_LAUNCH_CHECK();
+  return OWL_OK;
+}
+
+OWL_API int owl_argmax_merge(const void* const* exch_ptrs, void* const* flag_ptrs, void* counters,
+                             const void* local_val, const void* local_idx, void* out_idx, int rows, int rank, int world,
+                             int slot, unsigned spin_limit, int pdl, cudaStream_t st) {
+  if (rows < 1 || rows > 32 || world < 2 || world > MAX_RANKS) return OWL_ERR_BAD_ARG;
+  ArgmaxMergeParams p = {};
+  fill_tables(p.exch, exch_ptrs, p.flags, flag_ptrs, world);
+  p.counters = (uint32_t*)counters; p.local_val = (const float*)local_val; p.local_idx = (const int*)local_idx;
+  p.out_idx = (int*)out_idx; p.rows = rows; p.rank = rank; p.world = world; p.slot = slot; p.spin_limit = spin_limit;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(1); cfg.blockDim = dim3(64); cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, argmax_merge_kernel, p);
+  if (e != cudaSuccess) return (int)OWL_ERR_LAUNCH * 1000 - (int)e;
+  return OWL_OK;
+}
+
+// A single-rank wait that nothing satisfies: used by tests of the bounded-wait path (a flag that
+// nobody sets). Returns after `spin_limit` polls with OWL_ERR_WAIT_PEER in the status word.
+__global__ void wait_probe_kernel(uint32_t* flag, uint32_t want, uint32_t spin_limit, int* result) {
+  bool got = false;
+  for (uint32_t i = 0; i < spin_limit; ++i) {
+    if ((int)(ld_acquire_sys(flag) - want) >= 0) { got = true; break; }
+    if (i > 64) __nanosleep(64);
+  }
+  if (!got) atomicCAS(&g_comm_status, 0, OWL_ERR_WAIT_PEER);
+  *result = got ? 0 : OWL_ERR_WAIT_PEER;
+}
+OWL_API int owl_comm_wait_probe(void* flag, unsigned want, unsigned spin_limit, void* result, cudaStream_t st) {
+  wait_probe_kernel<<<1, 1, 0, st>>>((uint32_t*)flag, want, spin_limit, (int*)result);
+  OWL_LAUNCH_CHECK();
+  return OWL_OK;
+}
+
+OWL_API int owl_comm_status() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_comm_status, sizeof(int)) != cudaSuccess) return -1;
+  if (v != 0) cudaMemcpyToSymbol(g_comm_status, &zero, sizeof(int));
+  return v;
+}

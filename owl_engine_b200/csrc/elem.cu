@@ -228,7 +228,7 @@ __global__ void __launch_bounds__(256) argmax_stage1(const __nv_bfloat16* __rest
   }
 }
 __global__ void __launch_bounds__(128) argmax_stage2(const float* pval, const int* pidx, int nparts, int* out,
-                                                     int vocab_offset) {
+                                                     int vocab_offset, float* out_val = nullptr) {
   pdl_launch_dependents();
   pdl_wait();
   const int row = blockIdx.x;
@@ -245,7 +245,10 @@ __global__ void __launch_bounds__(128) argmax_stage2(const float* pval, const in
     const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
     if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
   }
-  if (threadIdx.x == 0) out[row] = bi + vocab_offset;
+  if (threadIdx.x == 0) {
+    out[row] = bi + vocab_offset;
+    if (out_val) out_val[row] = best;
+  }
 }
 
 // Self-feeding greedy decode: after sampling, make the sampled token the next step's input
@@ -325,13 +328,13 @@ OWL_API int owl_embed(const void* ids, const void* table, void* out, int M, int 
 }
 // scratch: float[M*nparts] + int[M*nparts]; nparts <= 1024.
 OWL_API int owl_argmax(const void* logits, int M, int V, int ld, void* scratch_val, void* scratch_idx, int nparts,
-                       void* out_idx, int vocab_offset, int pdl, cudaStream_t st) {
+                       void* out_idx, int vocab_offset, void* out_val, int pdl, cudaStream_t st) {
   if (M < 1 || nparts < 1 || nparts > 1024) return OWL_ERR_BAD_ARG;
   int r = launch_pdl(argmax_stage1, dim3(nparts, M), dim3(256), pdl, st, (const __nv_bfloat16*)logits, V, ld,
                      (float*)scratch_val, (int*)scratch_idx, nparts);
   if (r) return r;
   return launch_pdl(argmax_stage2, dim3(M), dim3(32), pdl, st, (const float*)scratch_val, (const int*)scratch_idx,
-                    nparts, (int*)out_idx, vocab_offset);
+                    nparts, (int*)out_idx, vocab_offset, (float*)out_val);
 }
 
 OWL_API int owl_decode_advance(void* inp, const void* tok, const void* block_table, int max_blocks, int B, int pdl,
@@ -375,5 +378,5 @@ OWL_API int owl_argmax_noalloc(const void* logits, int rows, int V, int ld, void
                      pidx, NA_PARTS);
   if (r) return r;
   return launch_pdl(argmax_stage2, dim3(rows), dim3(32), 0, st, (const float*)pval, (const int*)pidx, NA_PARTS,
-                    (int*)out_idx, vocab_offset);
+                    (int*)out_idx, vocab_offset, (float*)nullptr);
 }

@@ -82,7 +82,7 @@ def _pad16_rows(w: torch.Tensor) -> torch.Tensor:
 
 
 def weights_from_dense(spec: ModelSpec, dense: dict, device, group: int = 128, lm_head_int8: bool = False,
-                       quantize=True):
+                       vocab_split: bool = False):
     """Build device weights from HF-named dense tensors (full, unsharded model; ``spec`` may be
     a TP shard, in which case rows / columns are cut with ``parallel.plan``). Returns
     ``(HybridWeights, dense_equiv)`` where ``dense_equiv`` holds the dequantised weights under
@@ -144,7 +144,13 @@ def weights_from_dense(spec: ModelSpec, dense: dict, device, group: int = 128, l
     equiv["model.norm.weight"] = dense["model.norm.weight"].to(torch.bfloat16).float()
     hw = HybridWeights(spec=spec, embed=emb.to(device), final_norm=bf(dense["model.norm.weight"]), lm_head=None,
                        layers=layers, group=group)
-    hw.lm_head = Q.dense_skinny(head.to(device), device, int8=lm_head_int8)
+    if vocab_split and spec.tp_world > 1 and spec.vocab % (16 * spec.tp_world) == 0:
+        vrows = spec.vocab // spec.tp_world
+        hw.vocab_offset = spec.tp_rank * vrows
+        head_dev = head[hw.vocab_offset:hw.vocab_offset + vrows].contiguous()
+    else:
+        head_dev = head
+    hw.lm_head = Q.dense_skinny(head_dev.to(device), device, int8=lm_head_int8)
     if lm_head_int8:
         q8, s8 = Q.quantize_w8_rows(head.float())
         equiv["lm_head.weight"] = q8.float() * s8[:, None]
@@ -154,7 +160,7 @@ def weights_from_dense(spec: ModelSpec, dense: dict, device, group: int = 128, l
 
 
 def random_weights(spec: ModelSpec, device, group: int = 128, seed: int = 0, lm_head_int8: bool = False,
-                   std: float = 0.02) -> HybridWeights:
+                   std: float = 0.02, vocab_split: bool = True) -> HybridWeights:
     """Random-init weights generated directly in the device layouts (benchmarks: no dense copy)."""
     gen = torch.Generator(device=device).manual_seed(seed)
     rnd = lambda *s: (torch.randn(*s, device=device, generator=gen) * std)
@@ -184,12 +190,17 @@ def random_weights(spec: ModelSpec, device, group: int = 128, seed: int = 0, lm_
     emb = rnd(spec.vocab, H).to(torch.bfloat16)
     hw = HybridWeights(spec=spec, embed=emb, final_norm=torch.zeros(H, dtype=torch.bfloat16, device=device),
                        lm_head=None, layers=layers, group=group)
+    # vocab-split head: each TP rank holds V / world rows and the winners are merged across ranks
+    vrows = spec.vocab
+    if vocab_split and spec.tp_world > 1 and spec.vocab % (16 * spec.tp_world) == 0:
+        vrows = spec.vocab // spec.tp_world
+        hw.vocab_offset = spec.tp_rank * vrows
     if lm_head_int8:
-        q8 = torch.randint(-127, 128, (spec.vocab, H), device=device, dtype=torch.int8, generator=gen)
-        hw.lm_head = Q.DenseSkinny(Q.pack_dense_int8(q8), spec.vocab, H, "int8",
-                                   torch.full((spec.vocab,), std / 40.0, device=device))
+        q8 = torch.randint(-127, 128, (vrows, H), device=device, dtype=torch.int8, generator=gen)
+        hw.lm_head = Q.DenseSkinny(Q.pack_dense_int8(q8), vrows, H, "int8", torch.full((vrows,), std / 40.0, device=device))
     else:
-        hw.lm_head = Q.dense_skinny(emb if spec.tied else rnd(spec.vocab, H).to(torch.bfloat16), device)
+        head = emb if spec.tied else rnd(spec.vocab, H).to(torch.bfloat16)
+        hw.lm_head = Q.dense_skinny(head[hw.vocab_offset:hw.vocab_offset + vrows].contiguous(), device)
     return hw
 
 
@@ -287,6 +298,8 @@ class HybridRunner:
         self.am_parts = 64
         self.am_val, self.am_idx = f32(M * self.am_parts), torch.zeros(M * self.am_parts, dtype=torch.int32, device=dev)
         self.out_tok = torch.zeros(M, dtype=torch.int32, device=dev)
+        self.loc_val, self.loc_idx = f32(M), torch.zeros(M, dtype=torch.int32, device=dev)
+        self.vocab_split = self.vocab_local != spec.vocab
         self.inv_freq = R.rope_inv_freq(spec.rotary_dim, spec.rope_theta).to(dev)
         self.section = torch.tensor(mrope_section_map(spec), dtype=torch.uint8, device=dev)
         self.rope_scale = 1.0
@@ -303,28 +316,42 @@ class HybridRunner:
                     gslot=i[lay.gslot:lay.gslot + lay.b], bt_row=i[lay.bt_row:lay.bt_row + lay.b])
 
     # -- building blocks ---------------------------------------------------------------------
-    def _row_parallel(self, w, xp, xs, m: int) -> None:
-        """h += W x for a row-parallel projection (TP: partial sums are reduced by ``comm``)."""
-        if self.comm is None or self.spec.tp_world == 1:
+    def _norm(self, m: int, w, *, want_xn: bool, want_pack: bool = True) -> None:
+        sp = self.spec
+        K.rmsnorm_pack(self.h, w, normed=self.xn if want_xn else None, xpack=self.xp_h if want_pack else None,
+                       xs=self.xs_h if want_pack else None, m=m, k=sp.hidden, group=self.G, eps=sp.eps, pdl=self.pdl)
+
+    def _row_parallel(self, which: int, w, xp, xs, m: int, next_norm, *, want_xn: bool, want_pack: bool = True) -> None:
+        """h += W x for a row-parallel projection, then x_next = rmsnorm(h) * (1 + next_norm).
+
+        TP=1: residual fused into the GEMV epilogue, then the norm kernel. TP>1 (fused arm): the
+        GEMV writes its partial sums into the symmetric buffer `which` (mixer / MLP alternate) and one
+        kernel does all-reduce + residual + norm + pack. TP>1 (nccl arm): library all-reduce."""
+        sp = self.spec
+        symm = getattr(self.comm, "symm", None) if self.comm is not None else None
+        if self.comm is None or sp.tp_world == 1:
             K.w4a16_skinny(w, xp, xs, self.h, m, residual=self.h, epi=K.EPI_RESIDUAL, pdl=self.pdl)
+            self._norm(m, next_norm, want_xn=want_xn, want_pack=want_pack)
+        elif symm is not None:
+            K.w4a16_skinny(w, xp, xs, symm.partial(which), m, pdl=self.pdl)
+            symm.ar_residual_norm(which, self.h, m, next_norm, normed=self.xn if want_xn else None,
+                                  xpack=self.xp_h if want_pack else None, xs=self.xs_h if want_pack else None,
+                                  group=self.G, eps=sp.eps, pdl=self.pdl)
         else:
             K.w4a16_skinny(w, xp, xs, self.partial, m, pdl=self.pdl)
             self.comm.allreduce_add_residual(self.partial, self.h, m)
+            self._norm(m, next_norm, want_xn=want_xn, want_pack=want_pack)
 
-    def _mlp(self, lw: LayerWeights, m: int) -> None:
+    def _mlp(self, lw: LayerWeights, m: int, next_norm, *, want_xn: bool, want_pack: bool = True) -> None:
         sp = self.spec
-        K.rmsnorm_pack(self.h, lw.ln2, xpack=self.xp_h, xs=self.xs_h, m=m, k=sp.hidden, group=self.G, eps=sp.eps,
-                       pdl=self.pdl)
         # silu(gate)*up is written as bf16 and packed by a small kernel: the fused pack epilogue
         # (EPI_SILU_PACK) needs 16 row tiles per CTA, which leaves too few CTAs at this size
         K.w4a16_skinny(lw.gate_up, self.xp_h, self.xs_h, self.act, m, epi=K.EPI_SILU_MUL, ldo=sp.inter, pdl=self.pdl)
         K.act_pack(self.act, self.xp_i, self.xs_i, m, sp.inter, self.G, pdl=self.pdl)
-        self._row_parallel(lw.down, self.xp_i, self.xs_i, m)
+        self._row_parallel(1, lw.down, self.xp_i, self.xs_i, m, next_norm, want_xn=want_xn, want_pack=want_pack)
 
     def _gdn(self, lw: LayerWeights, li: int, lay: StepLayout, v: dict) -> None:
         sp, m = self.spec, lay.m
-        K.rmsnorm_pack(self.h, lw.ln1, normed=self.xn, xpack=self.xp_h, xs=self.xs_h, m=m, k=sp.hidden, group=self.G,
-                       eps=sp.eps, pdl=self.pdl)
         # fork: the tiny dense a/b projection runs beside the big qkvz stream
         main = torch.cuda.current_stream()
         self.side.wait_stream(main)
@@ -335,7 +362,7 @@ class HybridRunner:
         K.gdn_decode(self.qkvz_out, self.qkvz_out.shape[1], self.ab_out, self.ldab, lw.conv_w, lw.a_log, lw.dt_bias,
                      lw.gamma, self.pool.conv_state[li], self.pool.rec_state[li], v["gslot"], xpack=self.xp_v,
                      xs=self.xs_v, batch=lay.b, t=lay.t, nk=sp.nk, nv=sp.nv, group=self.G, eps=sp.eps, pdl=False)
-        self._row_parallel(lw.out_proj, self.xp_v, self.xs_v, m)
+        self._row_parallel(0, lw.out_proj, self.xp_v, self.xs_v, m, lw.ln2, want_xn=False)
 
     def _pick_splits(self, b: int, ctx_hint: int) -> int:
         if self.attn_splits:
@@ -346,8 +373,6 @@ class HybridRunner:
 
     def _full(self, lw: LayerWeights, li: int, lay: StepLayout, v: dict, splits: int) -> None:
         sp, m = self.spec, lay.m
-        K.rmsnorm_pack(self.h, lw.ln1, xpack=self.xp_h, xs=self.xs_h, m=m, k=sp.hidden, group=self.G, eps=sp.eps,
-                       pdl=self.pdl)
         K.w4a16_skinny(lw.qkv, self.xp_h, self.xs_h, self.qkv_out, m, pdl=self.pdl)
         qn = 2 * sp.hq * sp.hd
         kraw = self.qkv_out[:, qn:]
@@ -361,13 +386,21 @@ class HybridRunner:
                      pdl=self.pdl)
         K.attn_reduce(self.part_o, self.part_ml, splits, self.qkv_out, self.qkv_n, m, sp.hq, xpack=self.xp_a,
                       xs=self.xs_a, group=self.G, pdl=self.pdl)
-        self._row_parallel(lw.o_proj, self.xp_a, self.xs_a, m)
+        self._row_parallel(0, lw.o_proj, self.xp_a, self.xs_a, m, lw.ln2, want_xn=False)
 
     def _head(self, m: int, sample: bool = True) -> None:
-        sp, w = self.spec, self.w
-        K.rmsnorm_pack(self.h, w.final_norm, normed=self.xn, m=m, k=sp.hidden, group=self.G, eps=sp.eps, pdl=self.pdl)
+        """lm_head over ``self.xn`` (the final norm is produced by the last row-parallel step) and the
+        greedy sample; with a vocab-split head the per-rank winners are merged across ranks."""
+        w = self.w
         K.dense_skinny(w.lm_head, self.xn, self.logits, m, pdl=self.pdl)
-        if sample:
+        if not sample:
+            return
+        symm = getattr(self.comm, "symm", None) if self.comm is not None else None
+        if self.vocab_split and symm is not None:
+            K.argmax(self.logits, m, self.vocab_local, self.vocab_local, self.am_val, self.am_idx, self.am_parts,
+                     self.loc_idx, w.vocab_offset, pdl=self.pdl, out_val=self.loc_val)
+            symm.argmax_merge(self.loc_val, self.loc_idx, self.out_tok, m, pdl=self.pdl)
+        else:
             K.argmax(self.logits, m, self.vocab_local, self.vocab_local, self.am_val, self.am_idx, self.am_parts,
                      self.out_tok, w.vocab_offset, pdl=self.pdl)
 
@@ -378,15 +411,19 @@ class HybridRunner:
         m = lay.m
         splits = self._pick_splits(lay.b, ctx_hint)
         K.embed(v["ids"], self.w.embed, self.h, m, pdl=False)
+        layers = self.w.layers
+        self._norm(m, layers[0].ln1, want_xn=layers[0].kind == "gdn")
         fi = gi = 0
-        for i, lw in enumerate(self.w.layers):
+        for i, lw in enumerate(layers):
             if lw.kind == "gdn":
                 self._gdn(lw, gi, lay, v)
                 gi += 1
             else:
                 self._full(lw, fi, lay, v, splits)
                 fi += 1
-            self._mlp(lw, m)
+            last = i + 1 == len(layers)
+            nxt_w = self.w.final_norm if last else layers[i + 1].ln1
+            self._mlp(lw, m, nxt_w, want_xn=last or layers[i + 1].kind == "gdn", want_pack=not last)
             if self.taps is not None and i in self.taps:
                 self.taps[i][:m].copy_(self.h[:m])
         self._head(m, sample)
@@ -536,6 +573,7 @@ class HybridRunner:
         if not want_logits:
             return None
         self.h[:1].copy_(h[t - 1:t])
+        self._norm(1, self.w.final_norm, want_xn=True, want_pack=False)
         self._head(1, sample=True)
         return self.out_tok[:1]
 

@@ -26,7 +26,7 @@ _SIGS = {
     "owl_silu_mul": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "owl_sigmoid_gate": [_P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _P],
     "owl_embed": [_P, _P, _P, _I, _I, _I, _I, _P],
-    "owl_argmax": [_P, _I, _I, _I, _P, _P, _I, _P, _I, _I, _P],
+    "owl_argmax": [_P, _I, _I, _I, _P, _P, _I, _P, _I, _P, _I, _P],
     "owl_gdn_decode": [_P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
     "owl_gdn_conv_fwd": [_P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _P],
     "owl_gdn_scan": [_P, _P, _I, _P, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _F, _I, _P],
@@ -138,9 +138,9 @@ def embed(ids, table, out, m: int, pdl: bool = False) -> None:
 
 
 def argmax(logits, m: int, vocab: int, ld: int, scratch_val, scratch_idx, nparts: int, out_idx, vocab_offset: int = 0,
-           pdl: bool = False) -> None:
+           pdl: bool = False, out_val=None) -> None:
     call("owl_argmax", ptr(logits), m, vocab, ld, ptr(scratch_val), ptr(scratch_idx), nparts, ptr(out_idx),
-         vocab_offset, int(pdl), stream())
+         vocab_offset, ptr(out_val), int(pdl), stream())
 
 
 def gdn_decode(qkvz, ld: int, ab, ldab: int, conv_w, a_log, dt_bias, gamma, conv_state, state, slots, *, out=None,

@@ -23,17 +23,19 @@ import torch.distributed as dist
 
 
 class TpComm:
-    def __init__(self, rank: int, world: int, device, mode: str = "nccl", group=None):
+    def __init__(self, rank: int, world: int, device, mode: str = "nccl", group=None, hidden: int = 5120,
+                 big_elems: int = 2048 * 5120, use_multimem: bool = False):
         self.rank, self.world, self.device, self.mode = rank, world, device, mode
         self.group = group
         self.symm = None
         if mode == "fused" and world > 1:
             from .symm import SymmetricWorkspace
 
-            self.symm = SymmetricWorkspace(rank, world, device, group)
+            self.symm = SymmetricWorkspace(rank, world, device, group, hidden=hidden, big_elems=big_elems,
+                                           use_multimem=use_multimem)
 
     @classmethod
-    def from_env(cls, mode: str = "nccl") -> "TpComm | None":
+    def from_env(cls, mode: str = "nccl", **kw) -> "TpComm | None":
         """Build from torchrun's environment (RANK / LOCAL_RANK / WORLD_SIZE / MASTER_*)."""
         world = int(os.environ.get("WORLD_SIZE", "1"))
         if world == 1:
@@ -43,7 +45,7 @@ class TpComm:
         torch.cuda.set_device(local)
         if not dist.is_initialized():
             dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
-        return cls(rank, world, torch.device(f"cuda:{local}"), mode)
+        return cls(rank, world, torch.device(f"cuda:{local}"), mode, **kw)
 
     # row-parallel projection output: h[:m] += sum over ranks of partial[:m]
     def allreduce_add_residual(self, partial: torch.Tensor, h: torch.Tensor, m: int) -> None:

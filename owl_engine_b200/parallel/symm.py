@@ -1,0 +1,110 @@
+"""Symmetric (peer-mapped) workspace of one tensor-parallel rank and the fused collectives on it.
+
+Allocation and the address exchange use ``torch.distributed._symmetric_memory`` (CUDA VMM
+allocation + handle exchange between the rank processes, NVLS multicast binding when the fabric
+offers it) -- that is plumbing. Everything that moves data is our own kernel (``csrc/comm.cu``):
+peers' buffers are read with plain NVLink P2P loads or ``multimem.ld_reduce`` through NVSwitch.
+
+Workspace layout (identical on every rank, so an offset is valid on all peers):
+
+    flags      : uint32[FLAG_SLOTS][8]          sequence numbers written by peers
+    part_a/b   : bf16[MAX_ROWS][hidden]         partial sums of the two row-parallel call sites
+    exch       : uint2[MAX_ROWS][8]             vocab-split argmax exchange
+    big        : bf16[big_elems]                prefill-size all-reduce payload
+
+Reference counterpart: VMM peer grant + staging header (``crates/backends/cuda/src/vmm.rs``,
+``comm/ar.rs:38-175``), generalised from 2 threads in one process to 2/4/8 processes.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from ..ops import kernels as K
+
+_P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+K.register("owl_ar_residual_norm", [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, ctypes.c_uint,
+                                    _I, _P])
+K.register("owl_ar_inplace", [_P, _P, _P, _P, ctypes.c_longlong, _I, _I, _I, _I, ctypes.c_uint, _P])
+K.register("owl_argmax_merge", [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, ctypes.c_uint, _I, _P])
+K.register("owl_comm_wait_probe", [_P, ctypes.c_uint, ctypes.c_uint, _P, _P])
+
+FLAG_SLOTS = 128
+MAX_ROWS = 32
+SPIN_LIMIT = 1 << 22          # polls (each ~100 ns once backing off): a couple of hundred ms
+
+
+def _ptr_array(ptrs):
+    arr = (ctypes.c_void_p * 8)()
+    for i, p in enumerate(ptrs):
+        arr[i] = p
+    return arr
+
+
+class SymmetricWorkspace:
+    def __init__(self, rank: int, world: int, device, group=None, hidden: int = 5120, big_elems: int = 2048 * 5120,
+                 use_multimem: bool = False):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.rank, self.world, self.device, self.hidden = rank, world, device, hidden
+        self.off_flags = 0
+        self.off_a = FLAG_SLOTS * 8 * 4
+        self.off_b = self.off_a + MAX_ROWS * hidden * 2
+        self.off_exch = self.off_b + MAX_ROWS * hidden * 2
+        self.off_big = (self.off_exch + MAX_ROWS * 8 * 8 + 255) // 256 * 256
+        self.big_elems = big_elems
+        nbytes = self.off_big + big_elems * 2
+        self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+        self.buf.zero_()
+        gname = (group or dist.group.WORLD).group_name
+        self.handle = symm_mem.rendezvous(self.buf, gname)
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
+        base = [int(p) for p in self.handle.buffer_ptrs]
+        self.flag_ptrs = _ptr_array([b + self.off_flags for b in base])
+        self.a_ptrs = _ptr_array([b + self.off_a for b in base])
+        self.b_ptrs = _ptr_array([b + self.off_b for b in base])
+        self.exch_ptrs = _ptr_array([b + self.off_exch for b in base])
+        self.big_ptrs = _ptr_array([b + self.off_big for b in base])
+        mc = int(getattr(self.handle, "multicast_ptr", 0) or 0) if use_multimem else 0
+        self.mc_a = mc + self.off_a if mc else None
+        self.mc_b = mc + self.off_b if mc else None
+        self.part_a = self.buf[self.off_a:self.off_b].view(torch.bfloat16).view(MAX_ROWS, hidden)
+        self.part_b = self.buf[self.off_b:self.off_exch].view(torch.bfloat16).view(MAX_ROWS, hidden)
+        self.big = self.buf[self.off_big:self.off_big + big_elems * 2].view(torch.bfloat16)
+        self.counters = torch.zeros(FLAG_SLOTS, dtype=torch.int32, device=device)
+        self.scratch = torch.empty(big_elems, dtype=torch.bfloat16, device=device)
+
+    # slots 0..31: part_a rows, 32..63: part_b rows, 64: argmax merge, 65..: big all-reduce CTAs
+    def ar_residual_norm(self, which: int, h, m: int, norm_w, *, normed=None, xpack=None, xs=None, group: int = 128,
+                         eps: float = 1e-6, pdl: bool = False) -> None:
+        ptrs, mc, slot0 = (self.a_ptrs, self.mc_a, 0) if which == 0 else (self.b_ptrs, self.mc_b, 32)
+        K.call("owl_ar_residual_norm", ptrs, mc, self.flag_ptrs, K.ptr(self.counters), K.ptr(h), K.ptr(norm_w),
+               K.ptr(normed), K.ptr(xpack), K.ptr(xs), m, self.hidden, group, self.rank, self.world, slot0, eps, 1,
+               SPIN_LIMIT, int(pdl), K.stream())
+
+    def partial(self, which: int) -> torch.Tensor:
+        return self.part_a if which == 0 else self.part_b
+
+    def argmax_merge(self, local_val, local_idx, out_idx, rows: int, pdl: bool = False) -> None:
+        K.call("owl_argmax_merge", self.exch_ptrs, self.flag_ptrs, K.ptr(self.counters), K.ptr(local_val),
+               K.ptr(local_idx), K.ptr(out_idx), rows, self.rank, self.world, 64, SPIN_LIMIT, int(pdl), K.stream())
+
+    def can_reduce(self, y: torch.Tensor) -> bool:
+        return y.dtype == torch.bfloat16 and y.is_contiguous() and y.numel() <= self.big_elems and y.numel() % 8 == 0
+
+    def allreduce_(self, y: torch.Tensor) -> None:
+        """In-place sum over ranks of a contiguous bf16 tensor (copied through the symmetric area)."""
+        n = y.numel()
+        self.big[:n].copy_(y.view(-1))
+        K.call("owl_ar_inplace", self.big_ptrs, self.flag_ptrs, K.ptr(self.counters), K.ptr(self.scratch), n, self.rank,
+               self.world, 65, 48, SPIN_LIMIT, K.stream())
+        y.view(-1).copy_(self.big[:n])
+
+    @staticmethod
+    def status() -> int:
+        f = K.fn("owl_comm_status")
+        f.argtypes = []
+        return f()
