@@ -1,0 +1,63 @@
+"""Memory model: what a profile costs in device memory and how much context it can hold.
+
+``estimate`` splits the declared budget ``V_avail = total * vram_budget - vram_reserve`` into
+weights, GDN state rows, graph / workspace reserve and the KV pool, exactly the decomposition
+the store's ``MemoryPlan`` enforces at boot; ``solve_max_context`` answers ``context = "max"``.
+
+Reference counterpart: ``crates/shared/src/config/memory.rs`` and ``crates/store/src/budget.rs``.
+"""
+from __future__ import annotations
+
+from ..models.spec import PRESETS, ModelSpec
+
+B200_HBM_BYTES = 183_359 * (1 << 20)       # nvidia-smi total on a B200
+WORKSPACE_RESERVE = 3 << 30                # graphs, prefill workspace, split-KV partials, allocator slack
+
+
+def weight_bytes(spec: ModelSpec, quant: str, group: int, head_int8: bool) -> int:
+    h = spec.hidden
+    per_w4 = 0.5 + (4.0 / group)            # nibble + (fp16 scale, fp16 zero) per group
+    lin_mlp = 3 * spec.inter * h
+    lin_gdn = (spec.conv_dim + spec.value_dim) * h + spec.value_dim * h
+    lin_full = (2 * spec.hq * spec.hd + 2 * spec.hkv * spec.hd) * h + spec.hq * spec.hd * h
+    params = spec.n_layers * lin_mlp + spec.n_gdn * lin_gdn + spec.n_full * lin_full
+    if quant in ("w4a16", "w4a8", "gguf"):
+        body = params * per_w4
+    elif quant == "nvfp4":
+        body = params * (0.5 + 1.0 / 16)
+    else:
+        body = params * 2
+    small = spec.n_gdn * 2 * spec.nv * h * 2
+    embed = spec.vocab * h * 2
+    head = 0 if spec.tied else spec.vocab * h * (1 if head_int8 else 2)
+    return int(body + small + embed + head)
+
+
+def estimate(cfg) -> dict:
+    v = cfg.values
+    spec = PRESETS[v["model"]["name"]]()
+    world = max(1, len(v["parallel"]["device"])) if v["parallel"]["mode"] == "tp" else 1
+    rspec = spec.sharded(0, world) if world > 1 else spec
+    total = B200_HBM_BYTES
+    avail = int(total * v["store"]["vram_budget"]) - (v["store"]["vram_reserve_mb"] << 20)
+    kv_elem = {"fp8": 1, "int8": 1, "bf16": 2}[v["store.kv"]["kv_dtype"]]
+    w = weight_bytes(rspec, v["model"]["quant"], v["model"]["group"], v["model"]["head_quant"] != "bf16")
+    slots = v["store.gdn"]["gdn_slots"] + v["store.gdn"]["snap_max"]
+    gdn = slots * rspec.gdn_state_bytes()
+    kv_per_tok = rspec.kv_bytes_per_token(kv_elem)
+    pool = avail - w - gdn - WORKSPACE_RESERVE
+    block = v["store"]["block_tokens"]
+    pages = max(0, pool // (kv_per_tok * block))
+    return {"model": spec.name, "tp": world, "total_bytes": total, "avail_bytes": avail, "weights_bytes": w,
+            "gdn_state_bytes": gdn, "workspace_reserve_bytes": WORKSPACE_RESERVE, "kv_pool_bytes": max(0, pool),
+            "kv_bytes_per_token": kv_per_tok, "kv_pages": int(pages), "kv_tokens": int(pages * block),
+            "fits": pool > 0 and pages * block >= v["runtime"]["max_seq"],
+            "max_seq": v["runtime"]["max_seq"]}
+
+
+def solve_max_context(cfg) -> int:
+    """Largest max_seq (multiple of the block size) one sequence per slot can reach in the pool."""
+    e = estimate(cfg)
+    block = cfg.values["store"]["block_tokens"]
+    per = e["kv_tokens"] // max(1, cfg.values["store.gdn"]["gdn_slots"])
+    return max(block, min(per, 1 << 20) // block * block)
