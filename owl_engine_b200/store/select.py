@@ -1,0 +1,63 @@
+"""KV-cache virtualisation (KVMem-style block selection).
+
+For long contexts the per-turn device working set is bounded: a *Mean-K index* keeps, per block,
+layer and kv head, the mean of the block's de-rotated keys; ``score_blocks`` scores every block
+against the current (de-rotated) queries and ``select`` keeps the sink blocks, the most recent
+blocks and the top-k scored ones, up to ``workspace`` tokens. The result is a *view* page table
+that replaces the sequence's block table for that step.
+
+Reference counterpart: ``crates/store/src/select.rs`` (``score_blocks``, ``select``),
+``crates/kernels/cu/elems/{mean_k,page_softmax}.cu`` (GPU index + scoring).
+"""
+from __future__ import annotations
+
+import torch
+
+
+def mean_k_index(k_blocks: torch.Tensor) -> torch.Tensor:
+    """k_blocks: [n_blocks, block, hkv, hd] de-rotated keys -> [n_blocks, hkv, hd] block means."""
+    return k_blocks.float().mean(dim=1)
+
+
+def derope(k: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """Inverse of the partial rotate-half RoPE (k: [T, H, hd]; cos/sin: [T, half])."""
+    half = cos.shape[-1]
+    x1, x2, rest = k[..., :half], k[..., half:2 * half], k[..., 2 * half:]
+    c, s = cos[:, None, :], sin[:, None, :]
+    return torch.cat([x1 * c + x2 * s, x2 * c - x1 * s, rest], dim=-1)
+
+
+def score_blocks(q: torch.Tensor, index: torch.Tensor, mode: str = "cosine-max", gqa: str = "max") -> torch.Tensor:
+    """q: [nq, hq, hd] recent queries (de-rotated); index: [n_blocks, hkv, hd]. Returns [n_blocks]."""
+    nq, hq, hd = q.shape
+    nb, hkv, _ = index.shape
+    rep = hq // hkv
+    qf = q.float().view(nq, hkv, rep, hd)
+    kf = index.float()
+    if mode.startswith("cosine"):
+        qf = torch.nn.functional.normalize(qf, dim=-1)
+        kf = torch.nn.functional.normalize(kf, dim=-1)
+    s = torch.einsum("qgrd,bgd->bqgr", qf, kf)               # [nb, nq, hkv, rep]
+    s = s.amax(-1) if gqa == "max" else s.mean(-1)           # over the q heads of a kv head
+    s = s.amax(1) if mode.endswith("max") else s.mean(1)     # over queries
+    return s.amax(-1)                                         # over kv heads
+
+
+def select(scores: torch.Tensor, n_blocks: int, budget_blocks: int, sink: int = 2, recent: int = 4) -> list[int]:
+    """Block ids kept for this step, ascending (causal order is preserved in the view)."""
+    if n_blocks <= budget_blocks:
+        return list(range(n_blocks))
+    keep = set(range(min(sink, n_blocks))) | set(range(max(0, n_blocks - recent), n_blocks))
+    room = budget_blocks - len(keep)
+    if room > 0:
+        masked = scores[:n_blocks].clone()
+        for b in keep:
+            masked[b] = float("-inf")
+        top = torch.topk(masked, min(room, n_blocks - len(keep))).indices.tolist()
+        keep |= set(top)
+    return sorted(keep)
+
+
+def view_table(block_table_row: torch.Tensor, kept: list[int]) -> torch.Tensor:
+    """Page table of the selected blocks (what the attention kernel walks instead of the full row)."""
+    return block_table_row[torch.tensor(kept, dtype=torch.long, device=block_table_row.device)]
