@@ -1,0 +1,97 @@
+"""Minimal safetensors reader / writer (no dependency on the ``safetensors`` package).
+
+File = u64 header length, JSON header {name: {dtype, shape, data_offsets}}, raw little-endian data.
+Tensors are served as zero-copy views of an ``np.memmap`` (bf16 / fp8 are reinterpreted through
+torch). A model directory may be a single file or shards listed in ``*.safetensors.index.json``.
+
+Reference counterpart: ``crates/models/src/formats/{mmap_index,safetensors}.rs``.
+"""
+from __future__ import annotations
+
+import json
+import struct
+from pathlib import Path
+
+import numpy as np
+import torch
+
+_DT = {"F32": (np.float32, torch.float32), "F16": (np.float16, torch.float16), "BF16": (np.uint16, torch.bfloat16),
+       "I32": (np.int32, torch.int32), "I64": (np.int64, torch.int64), "I8": (np.int8, torch.int8),
+       "U8": (np.uint8, torch.uint8), "I16": (np.int16, torch.int16), "F8_E4M3": (np.uint8, torch.float8_e4m3fn),
+       "BOOL": (np.bool_, torch.bool), "F64": (np.float64, torch.float64)}
+_REV = {v[1]: k for k, v in _DT.items()}
+
+
+class SafeFile:
+    def __init__(self, path: str | Path):
+        self.path = Path(path)
+        with open(self.path, "rb") as f:
+            (n,) = struct.unpack("<Q", f.read(8))
+            self.header = json.loads(f.read(n))
+        self.base = 8 + n
+        self.meta = self.header.pop("__metadata__", {})
+        self.mm = np.memmap(self.path, dtype=np.uint8, mode="r")
+
+    def keys(self):
+        return self.header.keys()
+
+    def get(self, name: str) -> torch.Tensor:
+        info = self.header[name]
+        npdt, tdt = _DT[info["dtype"]]
+        lo, hi = info["data_offsets"]
+        raw = self.mm[self.base + lo:self.base + hi]
+        arr = np.frombuffer(raw, dtype=npdt).reshape(info["shape"])
+        t = torch.from_numpy(arr.copy() if not arr.flags.writeable else arr)
+        return t.view(tdt) if t.dtype != tdt else t
+
+
+class SafeDir:
+    """All tensors of a HF-style checkpoint directory (single file or sharded)."""
+
+    def __init__(self, path: str | Path):
+        p = Path(path)
+        self.files: dict[str, SafeFile] = {}
+        self.where: dict[str, str] = {}
+        idx = list(p.glob("*.safetensors.index.json"))
+        if p.is_file():
+            shards = [p]
+        elif idx:
+            wm = json.loads(idx[0].read_text())["weight_map"]
+            shards = sorted({p / f for f in wm.values()})
+        else:
+            shards = sorted(p.glob("*.safetensors"))
+        if not shards:
+            raise FileNotFoundError(f"no safetensors under {p}")
+        for s in shards:
+            sf = SafeFile(s)
+            self.files[s.name] = sf
+            for k in sf.keys():
+                self.where[k] = s.name
+
+    def keys(self):
+        return self.where.keys()
+
+    def __contains__(self, k):
+        return k in self.where
+
+    def get(self, name: str) -> torch.Tensor:
+        return self.files[self.where[name]].get(name)
+
+
+def save_file(tensors: dict, path: str | Path, metadata: dict | None = None) -> None:
+    header, blobs, off = {}, [], 0
+    for k, t in tensors.items():
+        t = t.detach().cpu().contiguous()
+        raw = t.view(torch.uint8).numpy().tobytes() if t.dtype in (torch.bfloat16, torch.float8_e4m3fn) \
+            else t.numpy().tobytes()
+        header[k] = {"dtype": _REV[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + len(raw)]}
+        blobs.append(raw)
+        off += len(raw)
+    if metadata:
+        header["__metadata__"] = metadata
+    hj = json.dumps(header).encode()
+    hj += b" " * ((8 - len(hj) % 8) % 8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(hj)) + hj)
+        for b in blobs:
+            f.write(b)

@@ -1,0 +1,88 @@
+import numpy as np
+import pytest
+import torch
+
+from owl_engine_b200.formats import awq, gguf, nvfp4, safetensors as st
+from owl_engine_b200.ops import quant as Q
+
+
+def test_safetensors_roundtrip(tmp_path):
+    t = {"a": torch.randn(3, 5), "b": torch.randn(4, 2).to(torch.bfloat16), "c": torch.arange(6, dtype=torch.int32),
+         "d": torch.randn(8).to(torch.float8_e4m3fn)}
+    st.save_file(t, tmp_path / "m.safetensors", {"format": "pt"})
+    d = st.SafeDir(tmp_path)
+    assert set(d.keys()) == set(t)
+    for k in t:
+        assert torch.equal(d.get(k).view(torch.uint8) if t[k].dtype == torch.float8_e4m3fn else d.get(k),
+                           t[k].view(torch.uint8) if t[k].dtype == torch.float8_e4m3fn else t[k])
+
+
+@pytest.mark.parametrize("group", [32, 128])
+def test_awq_compressed_tensors_roundtrip(tmp_path, group):
+    c = Q.quantize_w4(torch.randn(64, 256), group)
+    st.save_file(awq.to_compressed_tensors(c, "l.down_proj"), tmp_path / "q.safetensors")
+    c2 = awq.from_compressed_tensors(st.SafeDir(tmp_path), "l.down_proj")
+    assert torch.equal(c.q, c2.q) and torch.equal(c.zeros, c2.zeros) and c2.group == group
+    torch.testing.assert_close(c2.dequant(), c.dequant())
+
+
+def test_autoawq_layout():
+    c = Q.quantize_w4(torch.randn(16, 256), 128)
+    order = [0, 2, 4, 6, 1, 3, 5, 7]
+    def pack(x):   # x [rows, cols] uint8, pack along cols in AutoAWQ order
+        v = x.view(x.shape[0], -1, 8)[..., order].to(torch.int64)
+        w = (v << (torch.arange(8) * 4)).sum(-1)
+        return torch.where(w >= 2**31, w - 2**32, w).to(torch.int32)
+    c2 = awq.from_autoawq(pack(c.q.t().contiguous()), pack(c.zeros.t().contiguous()), c.scales.t().contiguous())
+    assert torch.equal(c2.q, c.q) and torch.equal(c2.zeros, c.zeros)
+
+
+def test_nvfp4_codec():
+    w = torch.randn(128, 256) * 0.05
+    q = nvfp4.quantize(w)
+    d = nvfp4.dequantize(q)
+    assert ((d - w).norm() / w.norm()) < 0.12
+    vals = torch.tensor([0, 0.5, 1, 1.5, 2, 3, 4, 6, -0.5, -6.0])
+    assert torch.equal(nvfp4.decode_e2m1(nvfp4.encode_e2m1(vals)), vals)
+    codes, sf = nvfp4.pack_for_mma(q)
+    assert sf.shape == (1, 4, 512)
+
+
+def test_gguf_container_and_codecs(tmp_path):
+    rng = np.random.default_rng(0)
+    w = (rng.standard_normal((64, 256)) * 0.05).astype(np.float32)
+    tensors = {"a.f32": ((64, 256), "F32", w.view(np.uint8).reshape(-1)),
+               "a.q8": ((64, 256), "Q8_0", gguf.quantize_q8_0(w)),
+               "a.q4k": ((64, 256), "Q4_K", gguf.quantize_q4_k(w))}
+    meta = {"general.architecture": "qwen35", "general.name": "t", "qwen35.embedding_length": 256,
+            "qwen35.feed_forward_length": 512, "qwen35.block_count": 4, "qwen35.attention.head_count": 6,
+            "qwen35.attention.head_count_kv": 1, "tokenizer.ggml.tokens": ["a", "b", "c"], "tokenizer.ggml.eos_token_id": 2}
+    gguf.write_gguf(tmp_path / "m.gguf", meta, tensors)
+    f = gguf.GgufFile(tmp_path / "m.gguf")
+    assert f.meta["qwen35.block_count"] == 4 and f.tensors["a.q4k"].shape == (64, 256)
+    assert torch.equal(f.dequant("a.f32"), torch.from_numpy(w))
+    assert (f.dequant("a.q8") - torch.from_numpy(w)).abs().max() < 2e-3
+    dq = f.dequant("a.q4k")
+    assert ((dq - torch.from_numpy(w)).norm() / np.linalg.norm(w)) < 0.12
+    c = gguf.q4k_to_w4(f.raw("a.q4k"), 64, 256)
+    torch.testing.assert_close(c.dequant(), dq, rtol=2e-2, atol=2e-3)
+    spec = gguf.spec_from_meta(f.meta)
+    assert spec.hidden == 256 and spec.n_layers == 4 and gguf.tokenizer_from_meta(f.meta)["eos"] == 2
+
+
+def test_gguf_other_codecs_shapes():
+    rng = np.random.default_rng(1)
+    for t in ["Q4_0", "Q5_K", "Q6_K", "IQ4_NL", "IQ4_XS"]:
+        be, bb = gguf.BLOCK[t]
+        raw = rng.integers(0, 255, size=bb * 4, dtype=np.uint8)
+        d16 = np.frombuffer(np.float16(0.01).tobytes(), dtype=np.uint8)
+        if t == "Q6_K":
+            raw.reshape(4, bb)[:, 208:210] = d16
+        else:
+            raw.reshape(4, bb)[:, 0:2] = d16
+            if t == "Q5_K":
+                raw.reshape(4, bb)[:, 2:4] = d16
+        out = gguf.dequantize(raw, t, be * 4)
+        assert out.shape == (be * 4,) and np.isfinite(out).all()
+    with pytest.raises(gguf.UnsupportedGgufType):
+        gguf.dequantize(np.zeros(10, dtype=np.uint8), "IQ3_S", 256)
