@@ -1,0 +1,253 @@
+"""Checkpoint loading: detect the source kind, read every tensor as-is, build device weights.
+
+A *provider* answers two questions for an HF-style tensor name: ``w4(name)`` (the int4 canonical
+form of a linear weight, read without re-quantisation when the checkpoint already is int4) and
+``dense(name)`` (norms, embeddings, small projections). ``build_weights`` merges projections the
+kernels want merged (q|k|v, qkv|z, interleaved gate|up), cuts them for the TP rank and packs the
+skinny record streams.
+
+Sources: HF directory with bf16 safetensors (quantised on load, RTN), compressed-tensors AWQ /
+W4A16 directories (loaded as-is), GGUF files (Q4_K loaded as-is with group 32; other GGUF types are
+dequantised and re-quantised to int4 g32 with a warning; norm weights have the +1 that GGUF bakes in
+removed). Reference counterpart: ``crates/engine/src/loader.rs``, ``crates/models/src/formats/
+{load,kind,sharded}.rs`` and ``formats/gguf/{keys,source,shard}.rs``.
+"""
+from __future__ import annotations
+
+import json
+from pathlib import Path
+
+import torch
+
+from ..models import hybrid as H
+from ..models.spec import ModelSpec
+from ..ops import quant as Q
+from ..parallel.plan import Rule, TpPlan, rule_of
+from ..utils import log
+from . import awq, gguf
+from .safetensors import SafeDir
+
+
+def detect_kind(path: str | Path) -> str:
+    p = Path(path)
+    if p.is_file() and p.suffix == ".gguf":
+        return "gguf"
+    cfg = p / "config.json"
+    if cfg.exists():
+        qc = json.loads(cfg.read_text()).get("quantization_config", {})
+        fmt = (qc.get("format") or qc.get("quant_method") or "").lower()
+        if "pack" in fmt or "awq" in fmt or "compressed" in fmt:
+            return "awq"
+        if "nvfp4" in fmt or "modelopt" in fmt:
+            return "nvfp4"
+    if list(p.glob("*.safetensors")):
+        names = SafeDir(p).keys()
+        if any(k.endswith(".weight_packed") for k in names):
+            return "awq"
+        return "safetensors"
+    raise FileNotFoundError(f"cannot tell what kind of checkpoint {p} is")
+
+
+class DenseProvider:
+    """bf16 / fp32 tensors (dict or SafeDir); linear weights are quantised on load."""
+
+    def __init__(self, src, group: int = 128):
+        self.src, self.group = src, group
+
+    def _get(self, name):
+        return self.src[name] if isinstance(self.src, dict) else self.src.get(name)
+
+    def dense(self, name: str) -> torch.Tensor:
+        return self._get(name)
+
+    def w4(self, name: str) -> Q.W4Canonical:
+        return Q.quantize_w4(self._get(name).float(), self.group)
+
+    def has(self, name: str) -> bool:
+        return name in self.src if isinstance(self.src, dict) else name in self.src
+
+
+class AwqProvider(DenseProvider):
+    def w4(self, name: str) -> Q.W4Canonical:
+        prefix = name[:-len(".weight")]
+        if (prefix + ".weight_packed") in self.src:
+            return awq.from_compressed_tensors(self.src, prefix)
+        return super().w4(name)
+
+
+# HF name fragment -> GGUF name (llama.cpp-style key convention)
+_GGUF_LAYER = {
+    "input_layernorm.weight": "attn_norm.weight", "post_attention_layernorm.weight": "post_attention_norm.weight",
+    "mlp.gate_proj.weight": "ffn_gate.weight", "mlp.up_proj.weight": "ffn_up.weight", "mlp.down_proj.weight": "ffn_down.weight",
+    "self_attn.q_proj.weight": "attn_q.weight", "self_attn.k_proj.weight": "attn_k.weight",
+    "self_attn.v_proj.weight": "attn_v.weight", "self_attn.o_proj.weight": "attn_output.weight",
+    "self_attn.q_norm.weight": "attn_q_norm.weight", "self_attn.k_norm.weight": "attn_k_norm.weight",
+    "linear_attn.in_proj_qkv.weight": "attn_qkv.weight", "linear_attn.in_proj_z.weight": "attn_gate.weight",
+    "linear_attn.in_proj_a.weight": "ssm_alpha.weight", "linear_attn.in_proj_b.weight": "ssm_beta.weight",
+    "linear_attn.conv1d.weight": "ssm_conv1d.weight", "linear_attn.A_log": "ssm_a", "linear_attn.dt_bias": "ssm_dt.bias",
+    "linear_attn.norm.weight": "ssm_norm.weight", "linear_attn.out_proj.weight": "ssm_out.weight",
+}
+_GGUF_TOP = {"model.embed_tokens.weight": "token_embd.weight", "model.norm.weight": "output_norm.weight",
+             "lm_head.weight": "output.weight"}
+_PLUS_ONE_NORMS = ("input_layernorm.weight", "post_attention_layernorm.weight", "q_norm.weight", "k_norm.weight",
+                   "model.norm.weight")
+
+
+def gguf_name(hf: str) -> str:
+    if hf in _GGUF_TOP:
+        return _GGUF_TOP[hf]
+    parts = hf.split(".")
+    assert parts[0] == "model" and parts[1] == "layers", hf
+    return f"blk.{parts[2]}." + _GGUF_LAYER[".".join(parts[3:])]
+
+
+class GgufProvider:
+    def __init__(self, f: gguf.GgufFile):
+        self.f = f
+
+    def has(self, name: str) -> bool:
+        try:
+            return gguf_name(name) in self.f.tensors
+        except (KeyError, AssertionError):
+            return False
+
+    def dense(self, name: str) -> torch.Tensor:
+        t = self.f.dequant(gguf_name(name))
+        if name.endswith(_PLUS_ONE_NORMS):
+            t = t - 1.0                     # GGUF stores gamma with the +1 baked in; kernels apply (1 + w)
+        if name.endswith("A_log"):
+            t = torch.log(-t) if (t < 0).all() else t     # some converters store A = -exp(A_log)
+        return t
+
+    def w4(self, name: str) -> Q.W4Canonical:
+        g = gguf_name(name)
+        t = self.f.tensors[g]
+        if t.type == "Q4_K":
+            return gguf.q4k_to_w4(self.f.raw(g), t.shape[0], t.shape[1])
+        log.warn("load.gguf", f"{g}: {t.type} is dequantised and re-quantised to int4 g32")
+        return Q.quantize_w4(self.f.dequant(g).float(), 32)
+
+
+def open_source(path: str | Path, group: int = 128):
+    kind = detect_kind(path)
+    if kind == "gguf":
+        f = gguf.GgufFile(path)
+        return kind, GgufProvider(f), f
+    d = SafeDir(path)
+    return kind, (AwqProvider(d, group) if kind == "awq" else DenseProvider(d, group)), d
+
+
+# ---- canonical-form surgery --------------------------------------------------------------------
+def cat_rows(parts: list[Q.W4Canonical]) -> Q.W4Canonical:
+    g = parts[0].group
+    assert all(p.group == g and p.q.shape[1] == parts[0].q.shape[1] for p in parts)
+    return Q.W4Canonical(torch.cat([p.q for p in parts]), torch.cat([p.scales for p in parts]),
+                         torch.cat([p.zeros for p in parts]), g)
+
+
+def rows(c: Q.W4Canonical, idx) -> Q.W4Canonical:
+    return Q.W4Canonical(c.q[idx].contiguous(), c.scales[idx].contiguous(), c.zeros[idx].contiguous(), c.group)
+
+
+def cols(c: Q.W4Canonical, lo: int, hi: int) -> Q.W4Canonical:
+    g = c.group
+    assert lo % g == 0 and hi % g == 0, "column cut must fall on a quantisation group boundary"
+    return Q.W4Canonical(c.q[:, lo:hi].contiguous(), c.scales[:, lo // g:hi // g].contiguous(),
+                         c.zeros[:, lo // g:hi // g].contiguous(), g)
+
+
+def shard_w4(name: str, c: Q.W4Canonical, full: ModelSpec, plan: TpPlan) -> Q.W4Canonical:
+    if plan.world == 1:
+        return c
+    r = rule_of(name)
+    n, k = c.q.shape
+    if r is Rule.COL:
+        lo, hi = plan.shard_range(n)
+        return rows(c, slice(lo, hi))
+    if r is Rule.ROW:
+        lo, hi = plan.shard_range(k)
+        return cols(c, lo, hi)
+    if r is Rule.Q_COL:
+        lo, hi = plan.shard_range(full.hq)
+        return rows(c, slice(lo * 2 * full.hd, hi * 2 * full.hd))
+    if r is Rule.KV_COL:
+        if full.hkv % plan.world == 0:
+            lo, hi = plan.shard_range(full.hkv)
+        else:
+            lo = plan.rank // (plan.world // full.hkv)
+            hi = lo + 1
+        return rows(c, slice(lo * full.hd, hi * full.hd))
+    if r is Rule.SEG_COL:
+        idx = torch.cat([torch.arange(lo, hi) for lo, hi in plan.segmented_ranges([full.key_dim, full.key_dim, full.value_dim])])
+        return rows(c, idx)
+    return c
+
+
+def interleave_rows(gate: Q.W4Canonical, up: Q.W4Canonical) -> Q.W4Canonical:
+    def il(a, b):
+        i = a.shape[0]
+        return torch.stack([a.view(i // 8, 8, -1), b.view(i // 8, 8, -1)], dim=1).reshape(2 * i, -1)
+    return Q.W4Canonical(il(gate.q, up.q), il(gate.scales, up.scales), il(gate.zeros, up.zeros), gate.group)
+
+
+def build_weights(full: ModelSpec, provider, device, rank: int = 0, world: int = 1, lm_head_int8: bool = False,
+                  vocab_split: bool = True) -> H.HybridWeights:
+    """Read every tensor through ``provider`` and produce the rank's device weights."""
+    from ..parallel.plan import shard_tensor
+
+    spec = full.sharded(rank, world) if world > 1 else full
+    plan = TpPlan(rank, world)
+    bf = lambda t: t.to(torch.bfloat16).to(device)
+    f32 = lambda t: t.float().to(device)
+    dn = lambda name: shard_tensor(name, provider.dense(name), full, plan)
+    w4 = lambda name: shard_w4(name, provider.w4(name), full, plan)
+    pack = lambda c: Q.pack_skinny(c).to(device)
+    layers, group = [], None
+    for i in range(full.n_layers):
+        p = f"model.layers.{i}."
+        gate, up = w4(p + "mlp.gate_proj.weight"), w4(p + "mlp.up_proj.weight")
+        group = gate.group
+        lw = H.LayerWeights(kind="full" if full.is_full(i) else "gdn", ln1=bf(dn(p + "input_layernorm.weight")),
+                            ln2=bf(dn(p + "post_attention_layernorm.weight")), gate_up=pack(interleave_rows(gate, up)),
+                            down=pack(w4(p + "mlp.down_proj.weight")))
+        if lw.kind == "gdn":
+            a = p + "linear_attn."
+            lw.qkvz = pack(cat_rows([w4(a + "in_proj_qkv.weight"), w4(a + "in_proj_z.weight")]))
+            ab = torch.cat([dn(a + "in_proj_a.weight"), dn(a + "in_proj_b.weight")]).to(torch.bfloat16)
+            lw.ab_dense = H._pad16_rows(ab).to(device)
+            lw.ab = Q.dense_skinny(lw.ab_dense, device)
+            lw.conv_w = f32(dn(a + "conv1d.weight").reshape(spec.conv_dim, spec.conv_k))
+            lw.a_log, lw.dt_bias = f32(dn(a + "A_log")), f32(dn(a + "dt_bias"))
+            lw.gamma = f32(provider.dense(a + "norm.weight"))
+            lw.out_proj = pack(w4(a + "out_proj.weight"))
+        else:
+            a = p + "self_attn."
+            lw.qkv = pack(cat_rows([w4(a + "q_proj.weight"), w4(a + "k_proj.weight"), w4(a + "v_proj.weight")]))
+            lw.q_norm, lw.k_norm = bf(provider.dense(a + "q_norm.weight")), bf(provider.dense(a + "k_norm.weight"))
+            lw.o_proj = pack(w4(a + "o_proj.weight"))
+        layers.append(lw)
+    emb = provider.dense("model.embed_tokens.weight").to(torch.bfloat16)
+    head = emb if (full.tied or not provider.has("lm_head.weight")) else provider.dense("lm_head.weight").to(torch.bfloat16)
+    hw = H.HybridWeights(spec=spec, embed=emb.to(device), final_norm=bf(provider.dense("model.norm.weight")),
+                         lm_head=None, layers=layers, group=group)
+    vrows = full.vocab
+    if vocab_split and world > 1 and full.vocab % (16 * world) == 0:
+        vrows = full.vocab // world
+        hw.vocab_offset = rank * vrows
+    hw.lm_head = Q.dense_skinny(head[hw.vocab_offset:hw.vocab_offset + vrows].contiguous().to(device), device,
+                                int8=lm_head_int8)
+    return hw
+
+
+def load_model(path: str | Path, device, spec: ModelSpec | None = None, rank: int = 0, world: int = 1, group: int = 128,
+               **kw):
+    """Open a checkpoint (any supported kind) and build the rank's weights. Returns (spec, weights)."""
+    kind, provider, handle = open_source(path, group)
+    if spec is None:
+        if kind == "gguf":
+            spec = gguf.spec_from_meta(handle.meta)
+        else:
+            from ..models.config_json import spec_from_hf_config
+
+            spec = spec_from_hf_config(json.loads((Path(path) / "config.json").read_text()))
+    return spec, build_weights(spec, provider, device, rank, world, **kw)

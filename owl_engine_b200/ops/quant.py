@@ -21,7 +21,7 @@ import torch
 class W4Canonical:
     q: torch.Tensor        # uint8 [N, K], 0..15
     scales: torch.Tensor   # fp16 [N, K/G]
-    zeros: torch.Tensor    # uint8 [N, K/G]
+    zeros: torch.Tensor    # uint8 [N, K/G] (fp16 with fractional values for GGUF K-quant sources)
     group: int
 
     @property
@@ -159,7 +159,9 @@ def unpack_skinny(s: W4Skinny) -> W4Canonical:
     q = v.permute(0, 2, 3, 1, 5, 4, 6).reshape(s.n, s.k).contiguous()
     kg = s.k // s.group
     scales = sz[..., 0].permute(0, 2, 1).reshape(s.n, kg).contiguous()
-    zeros = sz[..., 1].permute(0, 2, 1).reshape(s.n, kg).to(torch.uint8).contiguous()
+    zeros = sz[..., 1].permute(0, 2, 1).reshape(s.n, kg).contiguous()
+    if bool((zeros == zeros.round()).all()):      # integer zero points (AWQ); GGUF-derived ones are fractional
+        zeros = zeros.to(torch.uint8)
     return W4Canonical(q, scales, zeros, s.group)
 
 

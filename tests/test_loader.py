@@ -1,0 +1,90 @@
+"""Checkpoints of every supported kind load into identical device weights (CPU tensors here)."""
+import json
+
+import numpy as np
+import torch
+
+from owl_engine_b200.formats import awq, gguf, loader, safetensors as st
+from owl_engine_b200.models.reference import init_weights
+from owl_engine_b200.models.spec import test_hybrid as make_spec
+from owl_engine_b200.ops import quant as Q
+
+
+def _linear_names(spec):
+    for i in range(spec.n_layers):
+        p = f"model.layers.{i}."
+        yield from (p + "mlp." + n + "_proj.weight" for n in ("gate", "up", "down"))
+        if spec.is_full(i):
+            yield from (p + "self_attn." + n + "_proj.weight" for n in "qkvo")
+        else:
+            yield from (p + "linear_attn." + n + ".weight" for n in ("in_proj_qkv", "in_proj_z", "out_proj"))
+
+
+def test_awq_directory_loads_as_is_and_matches_dense_path(tmp_path):
+    spec = make_spec(n_layers=4, vocab=512)
+    dense = init_weights(spec, seed=1, std=0.05)
+    tensors = {}
+    for k, v in dense.items():
+        tensors[k] = v
+    for name in _linear_names(spec):
+        c = Q.quantize_w4(dense[name], 32)
+        tensors.pop(name)
+        tensors.update(awq.to_compressed_tensors(c, name[:-len(".weight")]))
+    st.save_file(tensors, tmp_path / "model.safetensors")
+    (tmp_path / "config.json").write_text(json.dumps({"quantization_config": {"format": "pack-quantized"}}))
+    assert loader.detect_kind(tmp_path) == "awq"
+    kind, prov, _ = loader.open_source(tmp_path)
+    hw = loader.build_weights(spec, prov, "cpu")
+    hw2 = loader.build_weights(spec, loader.DenseProvider(dense, 32), "cpu")
+    for a, b in zip(hw.layers, hw2.layers):
+        assert torch.equal(a.gate_up.records, b.gate_up.records) and torch.equal(a.down.records, b.down.records)
+        if a.kind == "gdn":
+            assert torch.equal(a.qkvz.records, b.qkvz.records)
+        else:
+            assert torch.equal(a.qkv.records, b.qkv.records)
+    assert hw.group == 32
+
+
+def test_tp_shards_tile_the_full_weight():
+    spec = make_spec(n_layers=4, vocab=512)
+    dense = init_weights(spec, seed=2, std=0.05)
+    prov = loader.DenseProvider(dense, 128)
+    full = loader.build_weights(spec, prov, "cpu")
+    parts = [loader.build_weights(spec, prov, "cpu", rank=r, world=2, vocab_split=True) for r in range(2)]
+    assert parts[0].spec.inter * 2 == spec.inter and parts[1].vocab_offset == 256
+    # row-parallel down_proj: the two column shards concatenate to the full canonical weight
+    f = Q.unpack_skinny(full.layers[0].down)
+    ps = [Q.unpack_skinny(p.layers[0].down) for p in parts]
+    assert torch.equal(torch.cat([p.q for p in ps], dim=1), f.q)
+    # column-parallel (interleaved) gate_up: row shards concatenate
+    f = Q.unpack_skinny(full.layers[0].gate_up)
+    ps = [Q.unpack_skinny(p.layers[0].gate_up) for p in parts]
+    assert torch.equal(torch.cat([p.q for p in ps], dim=0), f.q)
+
+
+def test_gguf_q4k_file_loads(tmp_path):
+    spec = make_spec(n_layers=4, vocab=512)
+    dense = init_weights(spec, seed=3, std=0.05)
+    tensors = {}
+    lin = set(_linear_names(spec))
+    for k, v in dense.items():
+        g = loader.gguf_name(k)
+        a = v.float().numpy()
+        if k.endswith(loader._PLUS_ONE_NORMS):
+            a = a + 1.0
+        if k in lin:
+            tensors[g] = (tuple(a.shape), "Q4_K", gguf.quantize_q4_k(a))
+        else:
+            a = np.ascontiguousarray(a.reshape(a.shape[0], -1) if a.ndim == 3 else a)
+            tensors[g] = (tuple(a.shape), "F32", a.view(np.uint8).reshape(-1))
+    meta = {"general.architecture": "qwen35", "qwen35.embedding_length": spec.hidden,
+            "qwen35.feed_forward_length": spec.inter, "qwen35.block_count": spec.n_layers,
+            "qwen35.attention.head_count": spec.hq, "qwen35.attention.head_count_kv": spec.hkv,
+            "qwen35.ssm.group_count": spec.nk, "qwen35.ssm.time_step_rank": spec.nv, "qwen35.vocab_size": spec.vocab}
+    gguf.write_gguf(tmp_path / "m.gguf", meta, tensors)
+    got_spec, hw = loader.load_model(tmp_path / "m.gguf", "cpu")
+    assert got_spec.hidden == spec.hidden and got_spec.nv == spec.nv and hw.group == 32
+    c = Q.unpack_skinny(hw.layers[0].down)
+    w = dense["model.layers.0.mlp.down_proj.weight"]
+    assert ((c.dequant() - w).norm() / w.norm()) < 0.15
+    torch.testing.assert_close(hw.layers[0].ln1.float(), dense["model.layers.0.input_layernorm.weight"], atol=1e-2, rtol=1e-2)
