@@ -31,6 +31,8 @@ class EngineConfig:
     lm_head_int8: bool = False
     n_pages: int = 4096            # KV pool pages (16 tokens each) per rank
     n_slots: int = 8               # GDN state rows (= concurrency ceiling, like gdn_slots)
+    n_snap_rows: int = 2           # extra state rows that hold prefix-boundary snapshots
+    host_cache_mb: int = 0         # pinned-host KV tier (0 = off)
     max_seqs: int = 8
     max_seq: int = 8192
     prefill_chunk: int = 2048
@@ -47,12 +49,19 @@ class Sequence:
     slot: int                      # GDN state row
     tokens: list = field(default_factory=list)    # all tokens so far (prompt + generated)
     n_cached: int = 0              # tokens whose KV / GDN state is materialised
-    pages: list = field(default_factory=list)
+    pages: list = field(default_factory=list)     # device pages, one reference each held by the sequence
+    n_prompt: int = 0
+    reused: int = 0                # prompt tokens served from the prefix cache
+    chain: object = None           # block hashes of the prompt (numpy uint64)
 
 
 class Engine:
     def __init__(self, cfg: EngineConfig, *, spec: ModelSpec | None = None, weights: H.HybridWeights | None = None,
                  comm=None, device=None):
+        from ..store.kv import KvStore
+        from ..store.state import StateStore
+        from ..store.tiers import HostTier, Mover, page_bytes
+
         self.cfg = cfg
         self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
         full = spec or PRESETS[cfg.model]()
@@ -66,14 +75,17 @@ class Engine:
         self.spec = full.sharded(rank, world) if world > 1 and full.tp_world == 1 else full
         self.weights = weights or H.random_weights(self.spec, self.device, group=cfg.group, seed=cfg.seed + rank * 7919,
                                                    lm_head_int8=cfg.lm_head_int8)
-        self.pool = H.StatePool(self.spec, self.device, cfg.n_pages, cfg.n_slots)
+        self.pool = H.StatePool(self.spec, self.device, cfg.n_pages, cfg.n_slots + cfg.n_snap_rows)
         self.max_blocks = (cfg.max_seq + PAGE - 1) // PAGE
         self.runner = H.HybridRunner(self.spec, self.weights, self.pool, max_seqs=cfg.max_seqs,
                                      max_blocks=self.max_blocks, prefill_chunk=cfg.prefill_chunk, comm=comm,
                                      pdl=cfg.pdl, prefill_gemm=cfg.prefill_gemm)
-        self.free_pages = list(range(cfg.n_pages - 1, -1, -1))
+        self.kv = KvStore(cfg.n_pages, PAGE)
+        self.states = StateStore(cfg.n_slots, cfg.n_snap_rows)
+        self.host = HostTier(page_bytes(self.pool), cfg.host_cache_mb << 20) if cfg.host_cache_mb else None
+        self.mover = Mover(self.pool, self.host) if self.host else None
+        self.host_slot_of: dict[int, int] = {}       # chain hash -> host slot (demoted blocks)
         self.free_rows = list(range(cfg.max_seqs - 1, -1, -1))
-        self.free_slots = list(range(cfg.n_slots - 1, -1, -1))
         self.seqs: dict[int, Sequence] = {}
         self._next_sid = 0
         # pinned staging for the host-fed step
@@ -83,58 +95,137 @@ class Engine:
         self.h_tok_np = self.h_tok.numpy()
         self.h2d_bytes = 0
         self.d2h_bytes = 0
-        self.stream = torch.cuda.current_stream(self.device)
+        self.prefix_hits = self.prefix_lookups = 0
 
-    # -- sequences ----------------------------------------------------------------------------
-    def add_sequence(self, prompt: list[int]) -> int:
-        if not self.free_rows or not self.free_slots:
-            raise RuntimeError("no free sequence row / GDN slot (concurrency ceiling reached)")
-        sid = self._next_sid
-        self._next_sid += 1
-        seq = Sequence(sid, self.free_rows.pop(), self.free_slots.pop(), list(prompt))
-        self.pool.reset_slot(seq.slot)
-        self.seqs[sid] = seq
-        return sid
-
-    def free_sequence(self, sid: int) -> None:
-        seq = self.seqs.pop(sid)
-        self.free_pages.extend(seq.pages)
-        self.free_rows.append(seq.row)
-        self.free_slots.append(seq.slot)
+    # -- pages ----------------------------------------------------------------------------------
+    def _alloc_pages(self, n: int) -> list[int]:
+        """Pages from the pool; under pressure the prefix tree gives up leaf-LRU blocks (demoted to the
+        pinned-host tier when one is configured, dropped otherwise)."""
+        got = self.kv.alloc(n)
+        if got is not None:
+            return got
+        demote = self.host is not None and len(self.host.free) >= n
+        pages, hashes = self.kv.evict(need_free=n, demote=demote)
+        if demote:
+            for pg, h in zip(pages, hashes):
+                slot = self.host.alloc()
+                self.mover.copy_out(pg, slot)
+                self.kv.set_carrier(h, 1, slot)
+                self.host_slot_of[h] = slot
+            self.mover.fence()
+        got = self.kv.alloc(n)
+        if got is None:
+            raise RuntimeError("KV pool exhausted")
+        return got
 
     def _ensure_pages(self, seq: Sequence, n_tokens: int) -> None:
         need = (n_tokens + PAGE - 1) // PAGE
         if need > self.max_blocks:
             raise RuntimeError(f"sequence longer than max_seq ({n_tokens} tokens)")
         if need > len(seq.pages):
-            add = need - len(seq.pages)
-            if add > len(self.free_pages):
-                raise RuntimeError("KV pool exhausted")
-            new = [self.free_pages.pop() for _ in range(add)]
+            new = self._alloc_pages(need - len(seq.pages))
             start = len(seq.pages)
             seq.pages.extend(new)
-            self.runner.block_table[seq.row, start:start + add] = torch.tensor(new, dtype=torch.int32,
-                                                                                 device=self.device)
+            self.runner.block_table[seq.row, start:start + len(new)] = torch.tensor(new, dtype=torch.int32,
+                                                                                      device=self.device)
+
+    # -- sequences ------------------------------------------------------------------------------
+    def add_sequence(self, prompt: list[int], reuse: bool = True) -> int:
+        """Start a sequence. With ``reuse`` the longest cached prefix for which a GDN snapshot exists
+        is adopted: its KV pages are shared (pinned) and the snapshot is copied into the new row."""
+        if not self.free_rows:
+            raise RuntimeError("no free sequence row")
+        sid = self._next_sid
+        slot = self.states.borrow(sid)
+        if slot is None:
+            raise RuntimeError("no free GDN state row (concurrency ceiling reached)")
+        self._next_sid += 1
+        seq = Sequence(sid, self.free_rows.pop(), slot, list(prompt), n_prompt=len(prompt))
+        self.pool.reset_slot(slot)
+        usable = (len(prompt) - 1) // PAGE * PAGE             # at least one token is always prefilled
+        seq.chain = self.kv.chain(prompt[:usable]) if reuse and usable else None
+        if seq.chain is not None and len(seq.chain):
+            self.prefix_lookups += 1
+            m, pages, carriers = self.kv.match(seq.chain)
+            snap = self.states.find(seq.chain[:m]) if m else None
+            keep = snap.n_tokens // PAGE if snap else 0
+            for i in range(keep):                              # promote demoted blocks of the kept prefix
+                if carriers[i] != 0:
+                    h = int(seq.chain[i])
+                    pg = self.kv.alloc(1)
+                    if pg is None or h not in self.host_slot_of:
+                        keep = i
+                        break
+                    self.mover.copy_in(self.host_slot_of[h], pg[0])
+                    self.kv.set_carrier(h, 0, pg[0])
+                    self.host.release(self.host_slot_of.pop(h))
+                    pages[i] = pg[0]                           # alloc's reference is the sequence's
+            if self.mover:
+                self.mover.fence()
+            self.kv.unref([p for p, c in zip(pages[keep:m], carriers[keep:m]) if c == 0])
+            if keep:
+                seq.pages = pages[:keep]
+                self.runner.block_table[seq.row, :keep] = torch.tensor(seq.pages, dtype=torch.int32, device=self.device)
+                self.pool.copy_slot(snap.row, slot)
+                seq.n_cached = seq.reused = keep * PAGE
+                self.prefix_hits += 1
+        self.seqs[sid] = seq
+        return sid
+
+    def free_sequence(self, sid: int, publish: bool = True) -> None:
+        """End a sequence: index its full blocks in the prefix tree (the tree takes its own
+        references) and give pages, row and state row back."""
+        seq = self.seqs.pop(sid)
+        if publish and seq.n_cached >= PAGE:
+            nb = min(seq.n_cached // PAGE, len(seq.pages))
+            chain = self.kv.chain(seq.tokens[:nb * PAGE])
+            self.kv.publish(chain, seq.pages[:nb])
+        self.kv.unref(seq.pages)
+        self.free_rows.append(seq.row)
+        self.states.give_back(sid)
 
     # -- prefill ------------------------------------------------------------------------------
+    def prefill_range(self, sid: int, start: int, end: int, want_token: bool):
+        """Feed prompt tokens [start, end) (start == tokens already cached). A GDN snapshot is taken when
+        ``end`` is the last block boundary of the prompt, so later requests can reuse the prefix."""
+        seq = self.seqs[sid]
+        assert start == seq.n_cached and end <= seq.n_prompt
+        self._ensure_pages(seq, end + 1)
+        ids = torch.tensor(seq.tokens[start:end], dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
+        tok = self.runner.prefill_chunk_forward(ids, start, seq.row, seq.slot, want_logits=want_token)
+        seq.n_cached = end
+        boundary = (seq.n_prompt - 1) // PAGE * PAGE
+        if end == boundary and boundary > seq.reused and seq.chain is not None and len(seq.chain):
+            row = self.states.snapshot(int(seq.chain[boundary // PAGE - 1]), boundary)
+            if row is not None:
+                self.pool.copy_slot(seq.slot, row)
+        if want_token:
+            t = int(tok.item())
+            seq.tokens.append(t)
+            return t
+        return None
+
+    def prefill_plan(self, sid: int) -> list[tuple[int, int]]:
+        """Chunk boundaries for the rest of the prompt: multiples of prefill_chunk plus a cut at the
+        last block boundary (where the GDN snapshot is taken)."""
+        seq = self.seqs[sid]
+        n, c = seq.n_prompt, self.cfg.prefill_chunk
+        boundary = (n - 1) // PAGE * PAGE
+        cuts = sorted({min(n, x) for x in range(seq.n_cached + c, n + c, c)} | ({boundary} if boundary > seq.n_cached else set()) | {n})
+        out, lo = [], seq.n_cached
+        for hi in cuts:
+            if hi > lo:
+                out.append((lo, hi))
+                lo = hi
+        return out
+
     def prefill(self, sid: int) -> int:
         """Feed every not-yet-cached prompt token; returns the first generated token."""
-        seq = self.seqs[sid]
-        n = len(seq.tokens)
-        self._ensure_pages(seq, n + 1)
-        ids = torch.tensor(seq.tokens[seq.n_cached:], dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
         tok = None
-        pos = seq.n_cached
-        chunk = self.cfg.prefill_chunk
-        for s in range(0, ids.shape[0], chunk):
-            part = ids[s:s + chunk]
-            last = s + chunk >= ids.shape[0]
-            tok = self.runner.prefill_chunk_forward(part, pos, seq.row, seq.slot, want_logits=last)
-            pos += part.shape[0]
-        seq.n_cached = n
-        t = int(tok.item())
-        seq.tokens.append(t)
-        return t
+        plan = self.prefill_plan(sid)
+        for i, (lo, hi) in enumerate(plan):
+            tok = self.prefill_range(sid, lo, hi, want_token=i + 1 == len(plan))
+        return tok
 
     # -- host-fed decode step -----------------------------------------------------------------
     def decode_step(self, sids: list[int]) -> list[int]:

@@ -1,0 +1,226 @@
+"""RunningEngine: the turn ledger and the single-threaded pump.
+
+``submit`` queues a turn (token ids + options); every ``pump()`` asks the scheduler for one step
+and executes it -- begin (borrow a state row, adopt a cached prefix), one prefill chunk, one batched
+decode step, or one speculative round -- and emits events to the turn's sink:
+
+    Prefill{turn, fed, total} | Token{turn, token} | Completed{turn, reason, usage} | Failed{turn, error}
+
+Cancellation takes effect at the next step boundary and still publishes the written prefix. The
+pump never blocks except on the step's single device-to-host read.
+
+Reference counterpart: ``crates/engine/src/running.rs`` (``submit_session_opts``, ``pump``,
+``cancel_turn``), ``serve/turn.rs`` (events, ``TurnOpts``), ``exec/turn_end.rs``.
+"""
+from __future__ import annotations
+
+import queue
+from dataclasses import dataclass, field
+
+import torch
+
+from ..store import budget as B
+from ..utils import log
+from ..utils.metrics import METRICS
+from ..utils.stepgate import GATE
+from . import sampler as S
+from .core import PAGE, Engine
+from .scheduler import DECODE, DONE, PREFILL, QUEUED, Scheduler, TurnView
+
+
+@dataclass
+class TurnOpts:
+    max_new: int = 256
+    ignore_eos: bool = False
+    sampling: S.SamplingParams = field(default_factory=S.SamplingParams)
+    stop_ids: tuple = ()
+    eos_ids: tuple = ()
+    session: str | None = None
+    images: list = field(default_factory=list)
+
+
+@dataclass
+class Turn:
+    turn: int
+    tokens: list
+    opts: TurnOpts
+    sink: "queue.Queue"
+    state: str = QUEUED
+    sid: int | None = None
+    plan: list = field(default_factory=list)
+    n_out: int = 0
+    cancelled: bool = False
+    arrival: int = 0
+    history: set = field(default_factory=set)
+
+
+class RunningEngine:
+    def __init__(self, engine: Engine, max_batch: int = 8, on_full: str = "reject", spec_runner=None):
+        self.e = engine
+        self.sched = Scheduler(max_batch, engine.cfg.prefill_chunk, on_full)
+        self.turns: dict[int, Turn] = {}
+        self.reservations = B.Reservations()
+        self._next = 0
+        self._tick = 0
+        self.spec_runner = spec_runner
+        self.completed = 0
+        self.trace: list = []        # last turns' structured trace (/debug/agent)
+
+    # -- API ------------------------------------------------------------------------------------
+    def submit(self, tokens: list[int], opts: TurnOpts | None = None, sink=None) -> int:
+        t = Turn(self._next, list(tokens), opts or TurnOpts(), sink or queue.Queue(), arrival=self._tick)
+        self._next += 1
+        self.turns[t.turn] = t
+        METRICS.count("engine.turns_submitted")
+        return t.turn
+
+    def cancel_turn(self, turn: int) -> None:
+        t = self.turns.get(turn)
+        if t:
+            t.cancelled = True
+
+    def idle(self) -> bool:
+        return not any(t.state != DONE for t in self.turns.values())
+
+    def queue_facts(self) -> dict:
+        st = [t.state for t in self.turns.values()]
+        return {"queued": st.count(QUEUED), "prefill": st.count(PREFILL), "decode": st.count(DECODE),
+                "free_rows": len(self.e.states.free_rows), "free_pages": self.e.kv.free_pages,
+                "prefix_hits": self.e.prefix_hits, "prefix_lookups": self.e.prefix_lookups}
+
+    # -- pump -----------------------------------------------------------------------------------
+    def _views(self) -> list[TurnView]:
+        out = []
+        for t in self.turns.values():
+            if t.state == DONE:
+                continue
+            fed = self.e.seqs[t.sid].n_cached if t.sid is not None else 0
+            need = (len(t.tokens) + t.opts.max_new + PAGE - 1) // PAGE
+            out.append(TurnView(t.turn, t.state, len(t.tokens), fed, need, self.spec_runner is not None, t.arrival))
+        return out
+
+    def pump(self) -> bool:
+        """Run one step. Returns False when there was nothing to do."""
+        self._tick += 1
+        GATE.checkpoint("pump")
+        for t in list(self.turns.values()):
+            if t.cancelled and t.state != DONE:
+                self._finish(t, "cancelled")
+        kvs = self.e.kv.stats()
+        evictable = kvs["lru_len"]
+        step, rejected = self.sched.schedule(self._views(), self.e.kv.free_pages, evictable,
+                                             self.reservations.outstanding, self.e.cfg.n_pages,
+                                             min(len(self.e.states.free_rows), len(self.e.free_rows)))
+        for r in rejected:
+            t = self.turns[r]
+            t.state = DONE
+            t.sink.put(("failed", r, "rejected: the request does not fit the KV pool / no free slot"))
+        if step.kind == "idle":
+            return bool(rejected)
+        try:
+            with METRICS.timer("pump." + step.kind):
+                getattr(self, "_do_" + step.kind)(step)
+        except Exception as ex:  # a failed step fails its turns, the engine keeps serving
+            log.error("engine.pump", f"{step.kind} failed: {ex!r}")
+            for tid in step.turns:
+                t = self.turns[tid]
+                if t.state != DONE:
+                    self._finish(t, "failed", error=repr(ex))
+        return True
+
+    def run_until_idle(self, max_steps: int = 1 << 30) -> None:
+        n = 0
+        while not self.idle() and n < max_steps:
+            if not self.pump():
+                break
+            n += 1
+
+    # -- step executors -------------------------------------------------------------------------
+    def _do_begin(self, step) -> None:
+        t = self.turns[step.turns[0]]
+        t.sid = self.e.add_sequence(t.tokens)
+        seq = self.e.seqs[t.sid]
+        t.plan = self.e.prefill_plan(t.sid)
+        t.state = PREFILL
+        self.reservations.reserve(t.turn, (len(t.tokens) + t.opts.max_new + PAGE - 1) // PAGE - len(seq.pages))
+        t.sink.put(("prefill", t.turn, seq.n_cached, len(t.tokens)))
+
+    def _do_prefill(self, step) -> None:
+        t = self.turns[step.turns[0]]
+        lo, hi = t.plan.pop(0)
+        last = not t.plan
+        tok = self.e.prefill_range(t.sid, lo, hi, want_token=last)
+        t.sink.put(("prefill", t.turn, hi, len(t.tokens)))
+        if last:
+            t.state = DECODE
+            self._emit(t, tok)
+
+    def _do_decode(self, step) -> None:
+        ts = [self.turns[i] for i in step.turns]
+        sids = [t.sid for t in ts]
+        toks = self.e.decode_step(sids)
+        for i, t in enumerate(ts):
+            tok = toks[i]
+            if t.opts.sampling.mode != "greedy":
+                tok = self._resample(t, i)
+                self.e.seqs[t.sid].tokens[-1] = tok
+            self._emit(t, tok)
+
+    def _do_spec(self, step) -> None:
+        t = self.turns[step.turns[0]]
+        for tok in self.spec_runner.round(self.e, t.sid):
+            if t.state == DONE:
+                break
+            self._emit(t, tok)
+
+    def _resample(self, t: Turn, row: int) -> int:
+        """Sampling modes: top-32 candidates of the row's logits come back from the device."""
+        k = min(32, self.e.runner.vocab_local)
+        vals, idx = torch.topk(self.e.runner.logits[row].float(), k)
+        cands = list(zip((idx + self.e.weights.vocab_offset).tolist(), vals.tolist()))
+        # an explicit seed makes the stream a function of (seed, step) only, so a request replays exactly
+        return S.sample(cands, t.opts.sampling, 0 if t.opts.sampling.seed else t.turn, t.n_out, t.history)
+
+    def _emit(self, t: Turn, tok: int) -> None:
+        t.n_out += 1
+        t.history.add(tok)
+        o = t.opts
+        is_eos = tok in o.eos_ids and not o.ignore_eos
+        if not is_eos:
+            t.sink.put(("token", t.turn, tok))
+        METRICS.count("engine.tokens_out")
+        if is_eos:
+            self._finish(t, "stop")
+        elif tok in o.stop_ids:
+            self._finish(t, "stop")
+        elif t.n_out >= o.max_new:
+            self._finish(t, "length")
+
+    def _finish(self, t: Turn, reason: str, error: str | None = None) -> None:
+        usage = {"prompt_tokens": len(t.tokens), "completion_tokens": t.n_out, "cached_tokens": 0}
+        if t.sid is not None and t.sid in self.e.seqs:
+            usage["cached_tokens"] = self.e.seqs[t.sid].reused
+            self.e.free_sequence(t.sid, publish=True)     # cancelled turns publish their written prefix too
+        self.reservations.release(t.turn)
+        t.state = DONE
+        self.completed += 1
+        self.trace.append({"turn": t.turn, "reason": reason, **usage})
+        del self.trace[:-64]
+        if reason == "failed":
+            t.sink.put(("failed", t.turn, error or "failed"))
+        else:
+            t.sink.put(("completed", t.turn, reason, usage))
+
+    # -- convenience ----------------------------------------------------------------------------
+    def generate(self, tokens: list[int], opts: TurnOpts | None = None) -> list[int]:
+        tid = self.submit(tokens, opts)
+        t = self.turns[tid]
+        self.run_until_idle()
+        out = []
+        while not t.sink.empty():
+            ev = t.sink.get()
+            if ev[0] == "token":
+                out.append(ev[2])
+            elif ev[0] == "failed":
+                raise RuntimeError(ev[2])
+        return out

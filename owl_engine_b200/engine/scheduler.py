@@ -1,0 +1,96 @@
+"""Scheduler: a pure host decision from the turn ledger to the next step.
+
+Two decoupled state machines: **admission** (Admit / Hold / Reject a queued turn, from its page
+need, the pool state and free GDN rows) and **phase policy** (round-robin between decode and
+prefill: a prefill chunk is granted after every ``PREFILL_EVERY`` decode beats, immediately when
+nothing is decoding). ``schedule`` returns ``Idle`` or one ``Step``: ``Begin`` (start a queued
+turn: borrow a row, plan prefix reuse), ``Prefill`` (one chunk of one turn), ``Decode`` (all
+decoding turns, up to ``max_batch`` rows) or ``SpecRound`` (one speculative round of one turn).
+
+Reference counterpart: ``crates/engine/src/sched/{scheduler,sched_policy}.rs``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+from ..store import budget as B
+
+PREFILL_EVERY = 8
+
+QUEUED, PREFILL, DECODE, DONE = "queued", "prefill", "decode", "done"
+
+
+@dataclass
+class TurnView:
+    """What the scheduler needs to know about a turn."""
+    turn: int
+    state: str
+    n_prompt: int
+    fed: int = 0
+    need_pages: int = 0
+    spec: bool = False
+    arrival: int = 0
+
+
+@dataclass
+class Step:
+    kind: str                          # begin | prefill | decode | spec
+    turns: list = field(default_factory=list)
+    chunk: tuple = (0, 0)              # prefill: (start, end) token positions
+
+
+IDLE = Step("idle")
+
+
+class PhaseSched:
+    def __init__(self):
+        self.decode_beats = 0
+        self.rr = 0
+
+    def pick(self, prefilling: list, decoding: list) -> str:
+        if prefilling and (not decoding or self.decode_beats >= PREFILL_EVERY):
+            self.decode_beats = 0
+            return "prefill"
+        if decoding:
+            self.decode_beats += 1
+            return "decode"
+        return "idle"
+
+
+class Scheduler:
+    def __init__(self, max_batch: int, prefill_chunk: int, on_full: str = "reject"):
+        self.max_batch, self.prefill_chunk, self.on_full = max_batch, prefill_chunk, on_full
+        self.phase = PhaseSched()
+
+    def admission(self, t: TurnView, free_pages: int, evictable: int, outstanding: int, pool_pages: int,
+                  free_rows: int) -> str:
+        return B.check_admission(t.need_pages, free_pages, evictable, outstanding, pool_pages, free_rows, self.on_full)
+
+    def schedule(self, turns: list[TurnView], free_pages: int, evictable: int, outstanding: int, pool_pages: int,
+                 free_rows: int):
+        """Returns (Step, rejected_turn_ids)."""
+        rejected = []
+        queued = sorted((t for t in turns if t.state == QUEUED), key=lambda t: t.arrival)
+        for t in queued:
+            verdict = self.admission(t, free_pages, evictable, outstanding, pool_pages, free_rows)
+            if verdict == B.ADMIT:
+                return Step("begin", [t.turn]), rejected
+            if verdict == B.REJECT:
+                rejected.append(t.turn)
+                continue
+            break                           # Hold: keep FIFO order, try again next pump
+        prefilling = [t for t in turns if t.state == PREFILL]
+        decoding = [t for t in turns if t.state == DECODE]
+        what = self.phase.pick(prefilling, decoding)
+        if what == "prefill":
+            t = prefilling[self.phase.rr % len(prefilling)]
+            self.phase.rr += 1
+            end = min(t.n_prompt, t.fed + self.prefill_chunk)
+            return Step("prefill", [t.turn], (t.fed, end)), rejected
+        if what == "decode":
+            spec = [t for t in decoding if t.spec]
+            if spec and len(decoding) == 1:
+                return Step("spec", [spec[0].turn]), rejected
+            batch = decoding[:self.max_batch]
+            return Step("decode", [t.turn for t in batch]), rejected
+        return IDLE, rejected

@@ -1,0 +1,123 @@
+"""EngineService: the engine runs on its own OS thread; clients talk to it through a bounded inbox.
+
+``boot`` builds the engine on the engine thread (the only thread that touches the CUDA context),
+then loops: drain the inbox (submit / cancel / query / stop), pump until idle, sleep briefly when
+there is nothing to do. ``EngineClient.chat`` returns an iterator of turn events fed by a bounded
+per-turn queue (back-pressure). A fatal error ends the loop with ``ServiceExit(kind, code)``:
+normal 0, fatal 1, panic 70.
+
+Reference counterpart: ``crates/engine/src/service/{mod,pump,boot,diag}.rs``.
+"""
+from __future__ import annotations
+
+import queue
+import threading
+import time
+import traceback
+from dataclasses import dataclass
+
+from ..utils import log
+from .running import RunningEngine, TurnOpts
+
+
+@dataclass
+class ServiceExit:
+    kind: str        # normal | fatal | panic
+    code: int
+    detail: str = ""
+
+
+class EngineService:
+    def __init__(self, build_engine, max_batch: int = 8, on_full: str = "reject", spec_runner=None):
+        """``build_engine()`` is called on the engine thread and returns an ``Engine``."""
+        self.inbox: queue.Queue = queue.Queue(maxsize=64)
+        self.ready = threading.Event()
+        self.exit: ServiceExit | None = None
+        self.re: RunningEngine | None = None
+        self._args = (build_engine, max_batch, on_full, spec_runner)
+        self.thread = threading.Thread(target=self._main, name="owl-engine", daemon=True)
+        self.boot_error: str | None = None
+
+    def boot(self, timeout: float = 600.0) -> "EngineClient":
+        self.thread.start()
+        if not self.ready.wait(timeout):
+            raise TimeoutError("engine did not become ready")
+        if self.boot_error:
+            raise RuntimeError(self.boot_error)
+        return EngineClient(self)
+
+    def _main(self) -> None:
+        build, max_batch, on_full, spec_runner = self._args
+        try:
+            self.re = RunningEngine(build(), max_batch, on_full, spec_runner)
+        except Exception as ex:
+            self.boot_error = f"boot failed: {ex!r}\n{traceback.format_exc()}"
+            self.exit = ServiceExit("fatal", 1, self.boot_error)
+            self.ready.set()
+            return
+        self.ready.set()
+        try:
+            while True:
+                stop = self._drain()
+                if stop:
+                    self.exit = ServiceExit("normal", 0)
+                    return
+                if not self.re.pump():
+                    time.sleep(0.0005)
+        except MemoryError as ex:
+            self.exit = ServiceExit("fatal", 1, repr(ex))
+        except Exception as ex:
+            log.error("engine.service", traceback.format_exc())
+            self.exit = ServiceExit("panic", 70, repr(ex))
+
+    def _drain(self) -> bool:
+        while True:
+            try:
+                msg = self.inbox.get_nowait()
+            except queue.Empty:
+                return False
+            kind = msg[0]
+            if kind == "stop":
+                return True
+            if kind == "submit":
+                _, tokens, opts, sink, reply = msg
+                reply.put(self.re.submit(tokens, opts, sink))
+            elif kind == "cancel":
+                self.re.cancel_turn(msg[1])
+            elif kind == "query":
+                _, fn, reply = msg
+                try:
+                    reply.put(fn(self.re))
+                except Exception as ex:
+                    reply.put(ex)
+
+    def shutdown(self, timeout: float = 30.0) -> ServiceExit:
+        self.inbox.put(("stop",))
+        self.thread.join(timeout)
+        return self.exit or ServiceExit("fatal", 1, "engine thread did not stop")
+
+
+class EngineClient:
+    def __init__(self, svc: EngineService):
+        self.svc = svc
+
+    def chat(self, tokens: list[int], opts: TurnOpts | None = None):
+        """Submit a turn; returns (turn_id, event_queue). Events: see ``RunningEngine``."""
+        sink: queue.Queue = queue.Queue(maxsize=4096)
+        reply: queue.Queue = queue.Queue()
+        self.svc.inbox.put(("submit", tokens, opts, sink, reply))
+        return reply.get(timeout=60), sink
+
+    def cancel(self, turn: int) -> None:
+        self.svc.inbox.put(("cancel", turn))
+
+    def query(self, fn, timeout: float = 30.0):
+        reply: queue.Queue = queue.Queue()
+        self.svc.inbox.put(("query", fn, reply))
+        out = reply.get(timeout=timeout)
+        if isinstance(out, Exception):
+            raise out
+        return out
+
+    def queue_facts(self) -> dict:
+        return self.query(lambda re: re.queue_facts())

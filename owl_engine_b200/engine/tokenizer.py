@@ -1,0 +1,77 @@
+"""Tokenizers: a wrapper over a HF ``tokenizer.json`` directory and a byte-level fallback.
+
+The fallback (``ByteTokenizer``) needs no files: ids 0..255 are bytes, followed by the special
+tokens of the built-in chat template. It lets the server, the CLI and the tests run with
+random-init weights. Reference counterpart: ``crates/models/src/tokenizer.rs``.
+"""
+from __future__ import annotations
+
+
+class ByteTokenizer:
+    SPECIALS = ["<|im_start|>", "<|im_end|>", "<|endoftext|>", "<think>", "</think>", "<tool_call>", "</tool_call>",
+                "<|image_pad|>", "<|vision_start|>", "<|vision_end|>"]
+
+    def __init__(self, vocab_size: int = 512):
+        self.vocab_size = vocab_size
+        self.special_ids = {s: 256 + i for i, s in enumerate(self.SPECIALS)}
+        self.id_special = {v: k for k, v in self.special_ids.items()}
+        self.eos_ids = [self.special_ids["<|im_end|>"], self.special_ids["<|endoftext|>"]]
+        self.image_pad_id = self.special_ids["<|image_pad|>"]
+
+    def encode(self, text: str) -> list[int]:
+        out, i = [], 0
+        while i < len(text):
+            for s, sid in self.special_ids.items():
+                if text.startswith(s, i):
+                    out.append(sid)
+                    i += len(s)
+                    break
+            else:
+                out.extend(text[i].encode("utf-8"))
+                i += 1
+        return out
+
+    def decode(self, ids) -> str:
+        buf, out = bytearray(), []
+        for t in ids:
+            if t < 256:
+                buf.append(t)
+            else:
+                out.append(buf.decode("utf-8", errors="replace"))
+                buf = bytearray()
+                out.append(self.id_special.get(t, ""))
+        out.append(buf.decode("utf-8", errors="replace"))
+        return "".join(out)
+
+
+class HfTokenizer:
+    def __init__(self, path: str):
+        from transformers import AutoTokenizer
+
+        self.tok = AutoTokenizer.from_pretrained(path)
+        self.vocab_size = len(self.tok)
+        eos = self.tok.eos_token_id
+        self.eos_ids = [eos] if isinstance(eos, int) else list(eos or [])
+        self.image_pad_id = self.tok.convert_tokens_to_ids("<|image_pad|>")
+
+    def encode(self, text: str) -> list[int]:
+        return self.tok.encode(text, add_special_tokens=False)
+
+    def decode(self, ids) -> str:
+        return self.tok.decode(list(ids), skip_special_tokens=False)
+
+
+class StreamDecoder:
+    """Incremental detokenisation that never emits half of a multi-byte character."""
+
+    def __init__(self, tok):
+        self.tok, self.ids, self.emitted = tok, [], 0
+
+    def push(self, token: int) -> str:
+        self.ids.append(token)
+        text = self.tok.decode(self.ids)
+        if text.endswith("�"):
+            return ""
+        delta = text[self.emitted:]
+        self.emitted = len(text)
+        return delta
