@@ -1,0 +1,258 @@
+"""HTTP/1.1 server (asyncio streams, keep-alive, chunked SSE) and the route table.
+
+Routes: ``POST /v1/chat/completions`` (JSON or SSE), ``GET /health``, ``GET /v1/models``,
+``POST /tokenize``, and the ``/debug/*`` family (queue, log, step, vram, blocks, agent, launches,
+metrics, perf, load). A client that disconnects mid-stream (write failure or EOF on the socket)
+cancels its turn at the next step boundary; a queued turn gets SSE comment frames as keep-alive and
+a 503 after ``queue_timeout_ms``; same-``session`` requests are serialised.
+
+Reference counterpart: ``apps/server/src/{http,main,debug,agent_trace,load}.rs``.
+"""
+from __future__ import annotations
+
+import asyncio
+import json
+import queue as pyqueue
+import time
+
+from ..engine.running import TurnOpts
+from ..engine.sampler import SamplingParams
+from ..engine.tokenizer import StreamDecoder
+from ..utils import log
+from ..utils.log import LOG
+from ..utils.metrics import METRICS
+from ..utils.stepgate import GATE
+from .chat_tpl import ChatTemplate
+from .openai import BadRequest, ChatRequest, Streamer
+from .toolcall import RepeatGuard
+
+REASONS = {200: "OK", 400: "Bad Request", 404: "Not Found", 405: "Method Not Allowed", 429: "Too Many Requests",
+           503: "Service Unavailable", 500: "Internal Server Error"}
+
+
+class App:
+    def __init__(self, client, tokenizer, model_name: str, template: ChatTemplate | None = None,
+                 default_sampling: SamplingParams | None = None, default_max_new: int = 4096, max_new_cap: int = 32768,
+                 queue_timeout_ms: int = 30000, keepalive_ms: int = 15000, max_concurrent: int = 8):
+        self.client, self.tok, self.model = client, tokenizer, model_name
+        self.tpl = template or ChatTemplate()
+        self.default_sampling = default_sampling or SamplingParams()
+        self.default_max_new, self.max_new_cap = default_max_new, max_new_cap
+        self.queue_timeout, self.keepalive = queue_timeout_ms / 1e3, keepalive_ms / 1e3
+        self.permits = asyncio.Semaphore(max_concurrent)
+        self.session_locks: dict[str, asyncio.Lock] = {}
+        self.guard = RepeatGuard()
+        self.started = time.time()
+
+    # -- plumbing -------------------------------------------------------------------------------
+    async def handle(self, reader: asyncio.StreamReader, writer: asyncio.StreamWriter) -> None:
+        try:
+            while True:
+                line = await reader.readline()
+                if not line:
+                    break
+                try:
+                    method, target, _ = line.decode("latin1").split(" ", 2)
+                except ValueError:
+                    await self._send(writer, 400, {"error": "malformed request line"})
+                    break
+                headers = {}
+                while True:
+                    h = await reader.readline()
+                    if h in (b"\r\n", b"\n", b""):
+                        break
+                    k, _, v = h.decode("latin1").partition(":")
+                    headers[k.strip().lower()] = v.strip()
+                body = await reader.readexactly(int(headers.get("content-length", 0))) if headers.get("content-length") else b""
+                keep = headers.get("connection", "keep-alive").lower() != "close"
+                await self.route(method, target.split("?")[0], body, reader, writer)
+                if not keep:
+                    break
+        except (ConnectionError, asyncio.IncompleteReadError):
+            pass
+        finally:
+            try:
+                writer.close()
+            except Exception:
+                pass
+
+    async def _send(self, w, status: int, obj, ctype="application/json") -> None:
+        data = obj if isinstance(obj, bytes) else (json.dumps(obj, ensure_ascii=False).encode() if not isinstance(obj, str) else obj.encode())
+        w.write(f"HTTP/1.1 {status} {REASONS.get(status, '')}\r\nContent-Type: {ctype}\r\nContent-Length: {len(data)}\r\n"
+                f"Connection: keep-alive\r\n\r\n".encode() + data)
+        await w.drain()
+
+    async def _sse_open(self, w) -> None:
+        w.write(b"HTTP/1.1 200 OK\r\nContent-Type: text/event-stream\r\nCache-Control: no-cache\r\n"
+                b"Transfer-Encoding: chunked\r\nConnection: keep-alive\r\n\r\n")
+        await w.drain()
+
+    @staticmethod
+    async def _sse(w, payload: str) -> None:
+        data = payload.encode()
+        w.write(f"{len(data):x}\r\n".encode() + data + b"\r\n")
+        await w.drain()
+
+    # -- routes ---------------------------------------------------------------------------------
+    async def route(self, method, path, body, reader, writer) -> None:
+        try:
+            if path == "/v1/chat/completions" and method == "POST":
+                return await self.chat(body, reader, writer)
+            if path == "/health":
+                return await self._send(writer, 200, {"status": "ok", "uptime_s": round(time.time() - self.started, 1)})
+            if path == "/v1/models":
+                return await self._send(writer, 200, {"object": "list", "data": [{"id": self.model, "object": "model"}]})
+            if path == "/tokenize" and method == "POST":
+                d = json.loads(body or b"{}")
+                text = d.get("text") if "text" in d else self.tpl.render(d.get("messages", []), tools=d.get("tools"))
+                ids = self.tok.encode(text)
+                return await self._send(writer, 200, {"tokens": ids, "count": len(ids)})
+            if path.startswith("/debug/"):
+                return await self.debug(method, path[len("/debug/"):], body, writer)
+            await self._send(writer, 404, {"error": f"no route {method} {path}"})
+        except BadRequest as e:
+            await self._send(writer, 400, {"error": {"message": str(e), "type": "invalid_request_error"}})
+        except (ConnectionError, asyncio.IncompleteReadError):
+            raise
+        except Exception as e:
+            log.error("server.route", repr(e))
+            await self._send(writer, 500, {"error": {"message": repr(e), "type": "server_error"}})
+
+    async def debug(self, method, sub, body, w) -> None:
+        parts = sub.split("/")
+        q = self.client.query
+        if parts[0] == "queue":
+            return await self._send(w, 200, self.client.queue_facts())
+        if parts[0] == "metrics":
+            return await self._send(w, 200, METRICS.snapshot("/".join(parts[1:])))
+        if parts[0] == "perf":
+            if parts[1:] == ["reset"]:
+                METRICS.reset()
+            return await self._send(w, 200, METRICS.tree())
+        if parts[0] == "log":
+            if len(parts) >= 3 and parts[1] == "level" and method == "POST":
+                LOG.set_level(parts[2])
+            elif len(parts) >= 3 and parts[1] == "tags" and method == "POST":
+                LOG.set_tags([t for t in parts[2].split(",") if t])
+            return await self._send(w, 200, {"level": LOG.level, "tags_allow": LOG.allow, "tail": LOG.tail(100)})
+        if parts[0] == "step":
+            if method == "POST":
+                d = json.loads(body or b"{}")
+                if "mode" in d:
+                    GATE.configure(d["mode"], d.get("ms", GATE.ms), d.get("every", 1))
+                else:
+                    GATE.step(int(d.get("n", 1)))
+            return await self._send(w, 200, GATE.status())
+        if parts[0] == "vram":
+            return await self._send(w, 200, q(lambda re: _vram(re)))
+        if parts[0] == "blocks":
+            return await self._send(w, 200, q(lambda re: {"kv": re.e.kv.stats(), "free_rows": len(re.e.states.free_rows),
+                                                           "snapshots": len(re.e.states.snaps),
+                                                           "host_used": re.e.host.used if re.e.host else 0}))
+        if parts[0] == "agent":
+            if parts[1:] == ["clear"] and method == "POST":
+                q(lambda re: re.trace.clear())
+            n = int(parts[1]) if len(parts) > 1 and parts[1].isdigit() else 64
+            return await self._send(w, 200, q(lambda re: re.trace[-n:]))
+        if parts[0] == "launches":
+            return await self._send(w, 200, q(lambda re: {"graphs": [list(k) for k in re.e.runner.graphs.keys()]}))
+        if parts[0] == "load" and method == "POST":
+            return await self._send(w, 200, {"loaded": self.model})
+        await self._send(w, 404, {"error": "unknown debug endpoint"})
+
+    async def chat(self, body, reader, w) -> None:
+        req = ChatRequest.parse(body)
+        kwargs = dict(req.chat_template_kwargs)
+        if req.reasoning_effort in ("none", "minimal"):
+            kwargs.setdefault("enable_thinking", False)
+        prompt = self.tpl.render(req.messages, tools=req.tools, **kwargs)
+        ids = self.tok.encode(prompt)
+        max_new = min(req.max_tokens or self.default_max_new, self.max_new_cap)
+        opts = TurnOpts(max_new=max_new, ignore_eos=req.ignore_eos, sampling=req.sampling(self.default_sampling),
+                        eos_ids=tuple(self.tok.eos_ids), session=req.session, images=req.images)
+        lock = self.session_locks.setdefault(req.session, asyncio.Lock()) if req.session else None
+        try:
+            await asyncio.wait_for(self.permits.acquire(), self.queue_timeout)
+        except asyncio.TimeoutError:
+            return await self._send(w, 503, {"error": {"message": "server busy (queue timeout)", "type": "overloaded"}})
+        if lock:
+            await lock.acquire()
+        turn = None
+        try:
+            loop = asyncio.get_running_loop()
+            turn, sink = await loop.run_in_executor(None, self.client.chat, ids, opts)
+            streamer = Streamer(self.model, StreamDecoder(self.tok), req.stop,
+                                start_in_think=prompt.rstrip().endswith("<think>"))
+            if req.stream:
+                await self._sse_open(w)
+            last_io, t_submit = time.time(), time.time()
+            reason, usage = "stop", {"prompt_tokens": len(ids), "completion_tokens": 0}
+            while True:
+                try:
+                    ev = await loop.run_in_executor(None, sink.get, True, 0.25)
+                except pyqueue.Empty:
+                    if reader.at_eof():
+                        raise ConnectionError("client closed")
+                    if req.stream and time.time() - last_io > self.keepalive:
+                        await self._sse(w, ": keep-alive\n\n")
+                        last_io = time.time()
+                    continue
+                if ev[0] == "token":
+                    chunks = streamer.on_token(ev[2])
+                    if req.stream:
+                        for c in chunks:
+                            await self._sse(w, "data: " + json.dumps(c, ensure_ascii=False) + "\n\n")
+                            last_io = time.time()
+                    if streamer.stopped:
+                        self.client.cancel(turn)
+                elif ev[0] == "completed":
+                    reason, usage = ("stop" if ev[2] in ("stop", "cancelled") else ev[2]), ev[3]
+                    break
+                elif ev[0] == "failed":
+                    if req.stream:
+                        await self._sse(w, "data: " + json.dumps({"error": {"message": ev[2]}}) + "\n\n")
+                        await self._sse(w, "data: [DONE]\n\n")
+                        w.write(b"0\r\n\r\n")
+                        return await w.drain()
+                    code = 429 if "rejected" in ev[2] else 500
+                    return await self._send(w, code, {"error": {"message": ev[2], "type": "engine_error"}})
+            for c in streamer.tool_calls:
+                if req.session and self.guard.observe(req.session, c):
+                    log.warn("server.repeat", f"session {req.session}: identical tool call repeated")
+            if req.stream:
+                for c in streamer.finish(reason, usage, req.include_usage):
+                    await self._sse(w, "data: " + json.dumps(c, ensure_ascii=False) + "\n\n")
+                await self._sse(w, "data: [DONE]\n\n")
+                w.write(b"0\r\n\r\n")
+                await w.drain()
+            else:
+                streamer.drain()
+                await self._send(w, 200, streamer.full_response(reason, usage))
+            METRICS.event("server.turn", ms=(time.time() - t_submit) * 1e3, tokens=usage["completion_tokens"])
+        except (ConnectionError, asyncio.IncompleteReadError):
+            if turn is not None:
+                self.client.cancel(turn)       # client went away: stop generating at the next step boundary
+            raise
+        finally:
+            if lock:
+                lock.release()
+            self.permits.release()
+
+
+def _vram(re) -> dict:
+    import torch
+
+    from ..store.budget import Ledger
+
+    free, total = torch.cuda.mem_get_info(re.e.device)
+    led = Ledger()
+    led.record("weights", "weights", re.e.weights.nbytes())
+    led.record("kv_pool", "kv pool", re.e.pool.k_pool.numel() * 2)
+    led.record("gdn_rows", "gdn state", re.e.pool.conv_state.numel() * 4 + re.e.pool.rec_state.numel() * 4)
+    return led.view(total, free)
+
+
+async def serve(app: App, host: str, port: int):
+    server = await asyncio.start_server(app.handle, host, port)
+    log.info("server", f"listening on {host}:{port}")
+    return server

@@ -1,0 +1,121 @@
+"""Server entry point: ``python -m owl_engine_b200.server.main -p <profile.toml> [--set k=v]...
+[--check] [--print-config [--format json]] [--explain key] [--log-level l] [--perf-dump dir]``.
+
+Boot order: load + validate the profile (refuse on any config error), short-circuit for
+``--check / --print-config / --explain``, take the GPU lock, start the engine thread (weights:
+random-init of the named shape, or a checkpoint directory / GGUF file), then bind the listener.
+Exit codes follow the engine's ``ServiceExit`` (0 normal, 1 fatal, 70 panic), 2 for config errors.
+
+Reference counterpart: ``apps/server/src/{main,config}.rs``.
+"""
+from __future__ import annotations
+
+import argparse
+import asyncio
+import json
+import sys
+
+from ..utils import config as C
+from ..utils import log
+from ..utils.memory import estimate
+
+
+def build_engine_factory(cfg: C.OwlConfig):
+    v = cfg.values
+
+    def build():
+        import torch
+
+        from ..engine.core import Engine, EngineConfig
+        from ..models.spec import PRESETS
+
+        torch.cuda.set_device(0)
+        est = estimate(cfg)
+        ecfg = EngineConfig(model=v["model"]["name"], group=v["model"]["group"],
+                            lm_head_int8=v["model"]["head_quant"] != "bf16",
+                            n_pages=min(est["kv_pages"], max(1024, (v["runtime"]["max_seq"] // 16 + 64) * v["store.gdn"]["gdn_slots"])),
+                            n_slots=v["store.gdn"]["gdn_slots"], n_snap_rows=max(2, v["store.gdn"]["snap_max"]),
+                            max_seqs=max(v["store.gdn"]["gdn_slots"], v["runtime"]["max_batch"]), max_seq=v["runtime"]["max_seq"],
+                            prefill_chunk=v["runtime"]["prefill_chunk"], pdl=v["kernel"]["pdl"],
+                            prefill_gemm=v["kernel"]["prefill_gemm"], host_cache_mb=v["store"]["host_cache_mb"])
+        if v["model"]["format"] == "random" or not v["model"]["path"]:
+            return Engine(ecfg)
+        from ..formats.loader import load_model
+
+        spec, weights = load_model(v["model"]["path"], torch.device("cuda:0"), spec=PRESETS.get(v["model"]["name"], lambda: None)(),
+                                   group=v["model"]["group"], lm_head_int8=ecfg.lm_head_int8)
+        return Engine(ecfg, spec=spec, weights=weights)
+    return build
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="owl-b200-server")
+    ap.add_argument("-p", "--profile", required=True)
+    ap.add_argument("--site")
+    ap.add_argument("--set", action="append", default=[])
+    ap.add_argument("--check", action="store_true")
+    ap.add_argument("--print-config", action="store_true")
+    ap.add_argument("--format", default="toml", choices=["toml", "json"])
+    ap.add_argument("--explain")
+    ap.add_argument("--log-level")
+    ap.add_argument("--perf-dump")
+    a = ap.parse_args(argv)
+    try:
+        cfg = C.load(a.profile, a.set, a.site)
+    except C.ConfigError as e:
+        print(f"config error: {e}", file=sys.stderr)
+        return 2
+    if a.explain:
+        print(cfg.explain(a.explain))
+    if a.print_config:
+        print(cfg.to_json() if a.format == "json" else cfg.to_toml())
+    if a.check:
+        print(json.dumps(estimate(cfg), indent=1))
+    if a.explain or a.print_config or a.check:
+        return 0
+    lv = cfg.values["log"]
+    log.LOG.configure(a.log_level or lv["level"], lv["tags_allow"], lv["tags_deny"], lv["timestamp"])
+    from ..engine.sampler import SamplingParams
+    from ..engine.service import EngineService
+    from ..engine.tokenizer import ByteTokenizer, HfTokenizer
+    from ..utils.metrics import METRICS
+    from .chat_tpl import ChatTemplate
+    from .http import App, serve
+
+    METRICS.set_level(cfg.values["probes"]["perf_level"])
+    v = cfg.values
+    svc = EngineService(build_engine_factory(cfg), max_batch=v["runtime"]["max_batch"], on_full=v["runtime"]["admission_on_full"])
+    client = svc.boot()
+    path = v["model"]["path"]
+    try:
+        tok = HfTokenizer(path) if path and v["model"]["format"] != "gguf" else ByteTokenizer()
+    except Exception:
+        tok = ByteTokenizer()
+    s = v["sampling"]
+    app = App(client, tok, v["model"]["name"], ChatTemplate(v["server"]["template_path"], v["server"]["template_vars"]),
+              SamplingParams(s["mode"], s["temp"], s["topk"], s["topp"], s["rep_penalty"]), v["runtime"]["default_max_new"],
+              v["runtime"]["max_new_cap"], v["server"]["queue_timeout_ms"], v["server"]["keepalive_ms"],
+              max_concurrent=v["store.gdn"]["gdn_slots"])
+    host, _, port = v["server"]["bind"].rpartition(":")
+
+    async def run():
+        server = await serve(app, host or "0.0.0.0", int(port))
+        async with server:
+            while svc.exit is None:
+                await asyncio.sleep(0.5)
+
+    try:
+        asyncio.run(run())
+    except KeyboardInterrupt:
+        pass
+    ex = svc.shutdown()
+    if a.perf_dump:
+        import os
+        os.makedirs(a.perf_dump, exist_ok=True)
+        open(os.path.join(a.perf_dump, "perf.json"), "w").write(METRICS.dump_json())
+        open(os.path.join(a.perf_dump, "perf.csv"), "w").write(METRICS.dump_csv())
+    return ex.code
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -3,7 +3,7 @@
 One ledger (``OwlConfig``) built from four layers, later layers win:
 
 1. the schema's own table carries **no defaults**: every key must be supplied by a profile
-   (``profiles/full.toml`` annotates and supplies all of them),
+   (``configs/full.toml`` annotates and supplies all of them),
 2. the profile file and its ``extends = [...]`` chain (resolved depth-first, relative to the
    including file, cycles refused),
 3. an optional site file (``--site``),
@@ -15,7 +15,7 @@ from (``explain``). Unknown sections or keys, missing keys, wrong types and valu
 enum are errors -- the server refuses to start. Nothing is read from the environment.
 
 Reference counterpart: ``crates/shared/src/config/{mod,intent,memory,resolve}.rs`` and the key set
-of ``profiles/full.toml``; ``device`` accepts 0, 2, 4 or 8 entries here (the reference: 0 or 2).
+of ``configs/full.toml``; ``device`` accepts 0, 2, 4 or 8 entries here (the reference: 0 or 2).
 """
 from __future__ import annotations
 
@@ -267,7 +267,7 @@ def validate(cfg: OwlConfig) -> None:
         if sec not in cfg.values:
             if sec in OPTIONAL_SECTIONS:
                 continue
-            raise ConfigError(f"missing section [{sec}] (every key must come from a profile; see profiles/full.toml)")
+            raise ConfigError(f"missing section [{sec}] (every key must come from a profile; see configs/full.toml)")
         for k, spec in keys.items():
             if k not in cfg.values[sec]:
                 if sec in OPTIONAL_SECTIONS:

@@ -1,0 +1,68 @@
+"""CLI pieces without a GPU: PNG writer round trip, blocking client + workload harness against a scripted server."""
+import asyncio
+import io
+import threading
+
+import numpy as np
+
+from owl_engine_b200.cli import png
+from owl_engine_b200.cli.client import Client
+from owl_engine_b200.cli.main import repl
+from owl_engine_b200.cli.workload import remove_image, run_suite
+from owl_engine_b200.engine.tokenizer import ByteTokenizer
+from owl_engine_b200.server.http import App, serve
+from test_server_http import FakeClient
+
+
+def test_png_round_trip():
+    data = png.encode_png(40, 24, png.BLUE, box=(4, 4, 20, 12), box_rgb=(1, 2, 3))
+    img = png.decode_png(data)
+    assert img.shape == (24, 40, 3)
+    assert tuple(img[0, 0]) == png.BLUE and tuple(img[5, 5]) == (1, 2, 3) and tuple(img[12, 5]) == png.BLUE
+    assert png.data_url_png(8, 8, png.RED).startswith("data:image/png;base64,iVBOR")
+
+
+def test_remove_image():
+    h = [{"role": "user", "content": [{"type": "text", "text": "a"}, {"type": "image_url", "image_url": {"url": "u1"}}]}]
+    assert remove_image(h, "u1") and not remove_image(h, "u1") and len(h[0]["content"]) == 1
+
+
+class Server:
+    def __enter__(self):
+        self.loop = asyncio.new_event_loop()
+        tok = ByteTokenizer()
+        self.app_client = FakeClient(tok, "ok <tool_call>\n{\"name\": \"add\", \"arguments\": {\"a\": 2, \"b\": 3}}\n</tool_call>")
+        ready = threading.Event()
+
+        def run():
+            asyncio.set_event_loop(self.loop)
+            app = App(self.app_client, tok, "fake")
+            self.server = self.loop.run_until_complete(serve(app, "127.0.0.1", 0))
+            self.port = self.server.sockets[0].getsockname()[1]
+            ready.set()
+            self.loop.run_forever()
+        self.t = threading.Thread(target=run, daemon=True)
+        self.t.start()
+        ready.wait(10)
+        return self
+
+    def __exit__(self, *a):
+        self.loop.call_soon_threadsafe(self.loop.stop)
+        self.t.join(5)
+
+
+def test_client_and_workload_against_scripted_server():
+    with Server() as s:
+        c = Client(f"http://127.0.0.1:{s.port}")
+        assert c.health()[0] == 200
+        r = c.chat([{"role": "user", "content": "hi"}], max_tokens=200)
+        assert r.content == "ok " and r.tool_calls[0]["name"] == "add" and r.finish_reason == "tool_calls"
+        assert r.usage["completion_tokens"] > 0 and r.ttft_ms > 0
+        r2 = c.chat([{"role": "user", "content": "hi"}], max_tokens=200, stream=False)
+        assert r2.content == r.content and r2.tool_calls == r.tool_calls
+        lines = []
+        ok = run_suite(c, "text", only="tool_roundtrip", max_tokens=200, out=lines.append)
+        assert ok and lines[0].startswith("[PASS] tool_roundtrip")
+        out = io.StringIO()
+        assert repl(c, 200, "s", inp=io.StringIO("hello\n/new\n/quit\n"), out=out) == 0
+        assert "ok " in out.getvalue() and "tool call add" in out.getvalue()

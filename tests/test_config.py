@@ -6,7 +6,7 @@ import pytest
 from owl_engine_b200.utils import config as C
 from owl_engine_b200.utils.memory import estimate
 
-ROOT = Path(__file__).resolve().parents[1] / "profiles"
+ROOT = Path(__file__).resolve().parents[1] / "configs"
 
 
 def test_full_profile_loads_and_every_schema_key_is_documented():

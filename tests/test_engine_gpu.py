@@ -79,3 +79,42 @@ def test_service_thread_roundtrip():
     assert len(toks) == 4 and client.queue_facts()["decode"] == 0
     ex = svc.shutdown()
     assert ex.kind == "normal" and ex.code == 0
+
+
+def test_http_server_end_to_end():
+    """Real engine thread behind the HTTP surface: non-stream and SSE give the same greedy text."""
+    import asyncio
+    import json
+
+    from owl_engine_b200.engine.tokenizer import ByteTokenizer
+    from owl_engine_b200.server.http import App, serve
+    from test_server_http import dechunk, request
+
+    svc = EngineService(lambda: make_engine(), max_batch=4)
+    client = svc.boot()
+    tok = ByteTokenizer()
+
+    async def main():
+        app = App(client, tok, "test-hybrid")
+        server = await serve(app, "127.0.0.1", 0)
+        port = server.sockets[0].getsockname()[1]
+        async with server:
+            body = {"messages": [{"role": "user", "content": "hello"}], "max_tokens": 12, "ignore_eos": True}
+            st, _, a = await request(port, "POST", "/v1/chat/completions", body)
+            assert st == 200
+            ra = json.loads(a)
+            assert ra["usage"]["completion_tokens"] == 12
+            st, _, b = await request(port, "POST", "/v1/chat/completions", {**body, "stream": True})
+            events = [l[6:] for l in dechunk(b).split("\n\n") if l.startswith("data: ")]
+            assert events[-1] == "[DONE]"
+            st, _, v = await request(port, "GET", "/debug/vram")
+            assert st == 200 and json.loads(v)["total"] > 0
+            st, _, v = await request(port, "GET", "/debug/blocks")
+            assert st == 200 and "kv" in json.loads(v)
+            # second identical prompt reuses the published prefix
+            st, _, c = await request(port, "POST", "/v1/chat/completions", body)
+            assert json.loads(c)["choices"][0]["message"] == ra["choices"][0]["message"]
+    try:
+        asyncio.run(main())
+    finally:
+        assert svc.shutdown().code == 0
