@@ -86,6 +86,8 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--prompt-len", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (result marked invalid)")
+    ap.add_argument("--gemv", default="dp4a", choices=["dp4a", "tc"],
+                    help="W4 decode arm: legacy streaming kernels or the tcgen05 streaming kernel")
     ap.add_argument("--comm", default="fused", choices=["nccl", "fused"],
                     help="TP collectives: our symmetric-memory kernels (fused) or the NCCL baseline arm")
     args = ap.parse_args()
@@ -113,7 +115,8 @@ def main() -> None:
     steps = args.steps
 
     cfg = EngineConfig(model="qwen3.8-27b", group=128, n_pages=1024, n_slots=2, max_seqs=2,
-                       max_seq=args.prompt_len + 2 * (warmup + steps) + 64, n_layers=args.layers)
+                       max_seq=args.prompt_len + 2 * (warmup + steps) + 64, n_layers=args.layers,
+                       decode_gemv=args.gemv)
     eng = Engine(cfg, comm=comm)
     g = torch.Generator().manual_seed(1234)
     prompt = torch.randint(0, eng.spec.vocab, (args.prompt_len,), generator=g).tolist()
@@ -216,7 +219,7 @@ def main() -> None:
                        "weights": "int4 g128 asym (W4A16)", "kv": "fp8 e4m3 paged, block 16",
                        "l2": "inputs larger than L2: every step streams the full weight set "
                              f"({eng.weights.streamed_bytes() / 1e9:.1f} GB per rank)",
-                       "comm": args.comm if world > 1 else "none", "cuda_graph": True},
+                       "comm": args.comm if world > 1 else "none", "cuda_graph": True, "decode_gemv": args.gemv},
             "e2e": {"value": round(e2e_value, 2), "unit": "tokens/s",
                     "h2d_bytes_per_step": (eng.h2d_bytes - h2d0) // steps,
                     "d2h_bytes_per_step": (eng.d2h_bytes - d2h0) // steps,

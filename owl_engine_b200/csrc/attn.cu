@@ -365,11 +365,10 @@ __global__ void __launch_bounds__(256) attn_reduce_kernel(const float* __restric
   const size_t e = ((size_t)row * hq + head) * HD + lane * 8;
   if (out) *reinterpret_cast<uint4*>(out + e) = out_f16 ? pack_f16x8(v) : pack_bf16x8(v);
   if (xpack) {
-    const int cpg = G >> 3;
+    const int tiles = G & ACT_TILES, g = G & ~ACT_TILES;
     float sx, xsum;
-    const uint4 pk = actpack_emit(v, cpg, sx, xsum);
-    xpack[e / 8] = pk;
-    if ((lane % cpg) == 0) xs[e / G] = make_float2(sx, xsum);
+    const uint4 pk = actpack_emit(v, g >> 3, sx, xsum);
+    actpack_store(xpack, xs, tiles, g, row, head * (HD / 8) + lane, hq * (HD / 8), pk, sx, xsum);
   }
 }
 
@@ -427,7 +426,7 @@ OWL_API int owl_paged_attn(const void* q, const void* k_pool, const void* v_pool
 
 OWL_API int owl_attn_reduce(const void* part_o, const void* part_ml, int splits, const void* qraw, int ldq, void* out,
                             void* xpack, void* xs, int rows, int hq, int G, int out_f16, int pdl, cudaStream_t st) {
-  if (rows < 1 || splits < 1 || (G != 32 && G != 128)) return OWL_ERR_BAD_ARG;
+  if (rows < 1 || splits < 1 || !actpack_group_ok(G, rows)) return OWL_ERR_BAD_ARG;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(rows, hq); cfg.blockDim = dim3(256); cfg.stream = st;
   cudaLaunchAttribute attr[1];

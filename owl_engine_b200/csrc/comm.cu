@@ -148,7 +148,7 @@ __global__ void __launch_bounds__(1024) ar_residual_norm_kernel(ArNormParams p) 
   ss = block_sum(ss, red);
   const float rinv = rsqrtf(ss / (float)p.H + p.eps);
   const int nround = (nchunks + 31) & ~31;
-  const int cpg = p.G >> 3;
+  const int tiles = p.G & ACT_TILES, gq = p.G & ~ACT_TILES, cpg = gq >> 3;
   for (int c = threadIdx.x; c < nround; c += blockDim.x) {
     float v[8];
     const bool live = c < nchunks;
@@ -169,8 +169,7 @@ __global__ void __launch_bounds__(1024) ar_residual_norm_kernel(ArNormParams p) 
     if (p.xpack) {
       float sx, xsum;
       const uint4 pk = actpack_emit(v, cpg, sx, xsum);
-      if (live) p.xpack[(size_t)row * nchunks + c] = pk;
-      if (live && (c % cpg) == 0) p.xs[(size_t)row * (p.H / p.G) + c / cpg] = make_float2(sx, xsum);
+      if (live) actpack_store(p.xpack, p.xs, tiles, gq, row, c, nchunks, pk, sx, xsum);
     }
   }
 }
@@ -258,7 +257,7 @@ OWL_API int owl_ar_residual_norm(const void* const* part_ptrs, const void* mc_pa
                                  void* counters, void* h, const void* w, void* normed, void* xpack, void* xs, int M,
                                  int H, int G, int rank, int world, int slot0, float eps, int one_plus_w,
                                  unsigned spin_limit, int pdl, cudaStream_t st) {
-  if (M < 1 || (H & 127) || world < 2 || world > MAX_RANKS || rank < 0 || rank >= world || (G != 32 && G != 128))
+  if (M < 1 || (H & 127) || world < 2 || world > MAX_RANKS || rank < 0 || rank >= world || !actpack_group_ok(G, M))
     return OWL_ERR_BAD_ARG;
   ArNormParams p = {};
   fill_tables(p.parts, part_ptrs, p.flags, flag_ptrs, world);

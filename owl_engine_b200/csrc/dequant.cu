@@ -9,13 +9,13 @@
 namespace owl {
 // grid (K/128, N/16), block 64: thread L handles uint4 #L of the tile (row, 4 words of 8 nibbles).
 __global__ void __launch_bounds__(64) w4_dequant_kernel(const uint8_t* __restrict__ records, __nv_bfloat16* out, int N,
-                                                        int K, int G) {
+                                                        int K, int G, int layout) {
   const int kt = blockIdx.x, nt = blockIdx.y, L = threadIdx.x;
   const int KT = K >> 7, GPT = 128 / G;
   const int half = L >> 5, g = (L & 31) >> 2, t = L & 3;
   const int row = nt * 16 + half * 8 + g;
   const int REC = 1024 + 64 * GPT;
-  const uint8_t* rec = records + record_offset(N / 16, KT, nt, kt) * (size_t)REC;
+  const uint8_t* rec = records + record_offset_any(layout, N / 16, KT, nt, kt) * (size_t)REC;
   const uint4 u = reinterpret_cast<const uint4*>(rec)[L];
   const __half2* sz = reinterpret_cast<const __half2*>(rec + 1024);
   const uint32_t w[4] = {u.x, u.y, u.z, u.w};
@@ -37,9 +37,9 @@ __global__ void __launch_bounds__(64) w4_dequant_kernel(const uint8_t* __restric
 }  // namespace owl
 using namespace owl;
 
-OWL_API int owl_w4_dequant(const void* records, void* out, int N, int K, int G, cudaStream_t st) {
+OWL_API int owl_w4_dequant(const void* records, void* out, int N, int K, int G, int layout, cudaStream_t st) {
   if ((N & 15) || (K & 127) || (G != 32 && G != 128)) return OWL_ERR_BAD_ARG;
-  w4_dequant_kernel<<<dim3(K / 128, N / 16), 64, 0, st>>>((const uint8_t*)records, (__nv_bfloat16*)out, N, K, G);
+  w4_dequant_kernel<<<dim3(K / 128, N / 16), 64, 0, st>>>((const uint8_t*)records, (__nv_bfloat16*)out, N, K, G, layout);
   OWL_LAUNCH_CHECK();
   return OWL_OK;
 }

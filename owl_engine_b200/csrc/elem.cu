@@ -27,6 +27,8 @@ __global__ void __launch_bounds__(1024) rmsnorm_pack_kernel(const __nv_bfloat16*
   __shared__ float red[32];
   pdl_launch_dependents();
   pdl_wait();
+  const int tiles = G & ACT_TILES;
+  G &= ~ACT_TILES;
   const int row = blockIdx.x;
   const int nchunks = K >> 3;
   const uint4* hp = reinterpret_cast<const uint4*>(h + (size_t)row * K);
@@ -83,8 +85,7 @@ __global__ void __launch_bounds__(1024) rmsnorm_pack_kernel(const __nv_bfloat16*
     if (xpack) {
       float sx, xsum;
       const uint4 pk = actpack_emit(v, cpg, sx, xsum);
-      if (live) xpack[(size_t)row * nchunks + c] = pk;
-      if (live && (c % cpg) == 0) xs[(size_t)row * (K / G) + c / cpg] = make_float2(sx, xsum);
+      if (live) actpack_store(xpack, xs, tiles, G, row, c, nchunks, pk, sx, xsum);
     }
   }
 }
@@ -94,6 +95,8 @@ __global__ void __launch_bounds__(256) act_pack_kernel(const __nv_bfloat16* __re
                                                        float2* xs, int K, int G) {
   pdl_launch_dependents();
   pdl_wait();
+  const int tiles = G & ACT_TILES;
+  G &= ~ACT_TILES;
   const int row = blockIdx.y;
   const int nchunks = K >> 3, cpg = G >> 3;
   const int c = blockIdx.x * blockDim.x + threadIdx.x;  // grid.x covers nchunks rounded up to 32
@@ -108,8 +111,7 @@ __global__ void __launch_bounds__(256) act_pack_kernel(const __nv_bfloat16* __re
   }
   float sx, xsum;
   const uint4 pk = actpack_emit(v, cpg, sx, xsum);
-  if (live) xpack[(size_t)row * nchunks + c] = pk;
-  if (live && (c % cpg) == 0) xs[(size_t)row * (K / G) + c / cpg] = make_float2(sx, xsum);
+  if (live) actpack_store(xpack, xs, tiles, G, row, c, nchunks, pk, sx, xsum);
 }
 
 // Merged gate_up output in "interleaved-8" order: columns [t*16 .. t*16+7] are gate_j and
@@ -118,6 +120,8 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const __nv_bfloat16* __re
                                                        uint4* xpack, float2* xs, int I, int G, int out_f16) {
   pdl_launch_dependents();
   pdl_wait();
+  const int tiles = G & ACT_TILES;
+  G &= ~ACT_TILES;
   const int row = blockIdx.y;
   const int nchunks = I >> 3, cpg = G >> 3;
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -142,8 +146,7 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const __nv_bfloat16* __re
   if (xpack) {
     float sx, xsum;
     const uint4 pk = actpack_emit(v, cpg, sx, xsum);
-    if (live) xpack[(size_t)row * nchunks + c] = pk;
-    if (live && (c % cpg) == 0) xs[(size_t)row * (I / G) + c / cpg] = make_float2(sx, xsum);
+    if (live) actpack_store(xpack, xs, tiles, G, row, c, nchunks, pk, sx, xsum);
   }
 }
 
@@ -155,6 +158,8 @@ __global__ void __launch_bounds__(256) sigmoid_gate_kernel(const __nv_bfloat16* 
                                                            int G) {
   pdl_launch_dependents();
   pdl_wait();
+  const int tiles = G & ACT_TILES;
+  G &= ~ACT_TILES;
   const int row = blockIdx.y;
   const int nchunks = HD >> 3, cpg = G >> 3;
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -177,8 +182,7 @@ __global__ void __launch_bounds__(256) sigmoid_gate_kernel(const __nv_bfloat16* 
   if (xpack) {
     float sx, xsum;
     const uint4 pk = actpack_emit(v, cpg, sx, xsum);
-    if (live) xpack[(size_t)row * nchunks + c] = pk;
-    if (live && (c % cpg) == 0) xs[(size_t)row * (HD / G) + c / cpg] = make_float2(sx, xsum);
+    if (live) actpack_store(xpack, xs, tiles, G, row, c, nchunks, pk, sx, xsum);
   }
 }
 
@@ -292,7 +296,7 @@ using namespace owl;
 OWL_API int owl_rmsnorm_pack(const void* h, const void* delta, const void* w, void* out_h, void* normed, void* xpack,
                              void* xs, int M, int K, int G, float eps, int one_plus_w, int normed_f16, int pdl,
                              cudaStream_t st) {
-  if (M < 1 || (K & 127) || (G != 32 && G != 128)) return OWL_ERR_BAD_ARG;
+  if (M < 1 || (K & 127) || !actpack_group_ok(G, M)) return OWL_ERR_BAD_ARG;
   int threads = ((K / 8 + 31) / 32) * 32;
   if (threads > 1024) threads = 1024;
   return launch_pdl(rmsnorm_pack_kernel, dim3(M), dim3(threads), pdl, st, (const __nv_bfloat16*)h,
@@ -300,21 +304,21 @@ OWL_API int owl_rmsnorm_pack(const void* h, const void* delta, const void* w, vo
                     (__nv_bfloat16*)normed, (uint4*)xpack, (float2*)xs, K, G, eps, one_plus_w, normed_f16);
 }
 OWL_API int owl_act_pack(const void* x, int ldx, void* xpack, void* xs, int M, int K, int G, int pdl, cudaStream_t st) {
-  if (M < 1 || (K & 127) || (ldx & 7) || (G != 32 && G != 128)) return OWL_ERR_BAD_ARG;
+  if (M < 1 || (K & 127) || (ldx & 7) || !actpack_group_ok(G, M)) return OWL_ERR_BAD_ARG;
   const int nchunks = K / 8;
   return launch_pdl(act_pack_kernel, dim3((nchunks + 255) / 256, M), dim3(256), pdl, st, (const __nv_bfloat16*)x, ldx,
                     (uint4*)xpack, (float2*)xs, K, G);
 }
 OWL_API int owl_silu_mul(const void* gate_up, void* out, void* xpack, void* xs, int M, int I, int G, int out_f16,
                          int pdl, cudaStream_t st) {
-  if (M < 1 || (I & 127) || (G != 32 && G != 128)) return OWL_ERR_BAD_ARG;
+  if (M < 1 || (I & 127) || !actpack_group_ok(G, M)) return OWL_ERR_BAD_ARG;
   const int nchunks = I / 8;
   return launch_pdl(silu_mul_kernel, dim3((nchunks + 255) / 256, M), dim3(256), pdl, st,
                     (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, (uint4*)xpack, (float2*)xs, I, G, out_f16);
 }
 OWL_API int owl_sigmoid_gate(const void* attn, const void* qraw, int ldq, int D, void* out, void* xpack, void* xs,
                              int M, int HD, int G, int pdl, cudaStream_t st) {
-  if (M < 1 || (HD & 127) || (D & 7) || (ldq & 7) || (G != 32 && G != 128)) return OWL_ERR_BAD_ARG;
+  if (M < 1 || (HD & 127) || (D & 7) || (ldq & 7) || !actpack_group_ok(G, M)) return OWL_ERR_BAD_ARG;
   const int nchunks = HD / 8;
   return launch_pdl(sigmoid_gate_kernel, dim3((nchunks + 255) / 256, M), dim3(256), pdl, st,
                     (const __nv_bfloat16*)attn, (const __nv_bfloat16*)qraw, ldq, D, (__nv_bfloat16*)out,

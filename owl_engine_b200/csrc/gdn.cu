@@ -212,13 +212,10 @@ __global__ void __launch_bounds__(256) gdn_decode_kernel(GdnDecodeParams p) {
         float v8[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) v8[i] = (lane < 16) ? o_s[lane * 8 + i] : 0.f;
-        const int cpg = p.G >> 3;
+        const int tiles = p.G & ACT_TILES, gq = p.G & ~ACT_TILES;
         float sx, xsum;
-        const uint4 pk = actpack_emit(v8, cpg, sx, xsum);
-        if (live && lane < 16) {
-          p.xpack[(row * V + h * GD) / 8 + lane] = pk;
-          if ((lane % cpg) == 0) p.xs[row * (V / p.G) + (h * GD) / p.G + lane / cpg] = make_float2(sx, xsum);
-        }
+        const uint4 pk = actpack_emit(v8, gq >> 3, sx, xsum);
+        if (live && lane < 16) actpack_store(p.xpack, p.xs, tiles, gq, row, (h * GD) / 8 + lane, V / 8, pk, sx, xsum);
       }
     }
     // qk_s is double buffered, v_s/part/scal are rewritten only after the next barrier pair.
@@ -412,7 +409,7 @@ OWL_API int owl_gdn_decode(const void* qkvz, int ld, const void* ab, int ldab, c
                            const void* dt_bias, const void* gamma, void* conv_state, void* state, const void* slots,
                            void* out, void* xpack, void* xs, int batch, int T, int nk, int nv, int G, float eps,
                            int pdl, cudaStream_t st) {
-  if (batch < 1 || T < 1 || T > GDN_MAX_T || nk < 1 || nv % nk || nv / nk > 8 || (G != 32 && G != 128))
+  if (batch < 1 || T < 1 || T > GDN_MAX_T || nk < 1 || nv % nk || nv / nk > 8 || !actpack_group_ok(G, xpack ? batch * T : 1))
     return OWL_ERR_BAD_ARG;
   GdnDecodeParams p;
   p.qkvz = (const __nv_bfloat16*)qkvz; p.ab = (const __nv_bfloat16*)ab; p.conv_w = (const float*)conv_w;

@@ -33,10 +33,11 @@ constexpr int GT_THREADS = 192;
 constexpr int GT_SMEM = GT_STAGES * 2 * GT_TILE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 
 struct GemmTcParams {
-  const uint8_t* wrec;   // W4 records (slice-major) or nullptr for the dense path
+  const uint8_t* wrec;   // W4 records or nullptr for the dense path
   __nv_bfloat16* out;
   int T, N, K, ldo;
   int group;             // 32 / 128
+  int layout;            // record stream layout: 0 slice-major, 1 block-major
   int fmt;               // dense path: 0 fp16, 1 bf16 operands
 };
 
@@ -159,7 +160,7 @@ __global__ void __launch_bounds__(GT_THREADS, 2) gemm_tc_kernel(const __grid_con
         for (int jt = 0; jt < 2; ++jt) {
           const int nt = n0 / 16 + wq * 2 + jt;
           if (nt < NT && kt < KT) {
-            const uint8_t* rec = p.wrec + record_offset(NT, KT, nt, kt) * (size_t)REC;
+            const uint8_t* rec = p.wrec + record_offset_any(p.layout, NT, KT, nt, kt) * (size_t)REC;
             q[jt * 2 + 0] = ldg_stream(reinterpret_cast<const uint4*>(rec) + lane);
             q[jt * 2 + 1] = ldg_stream(reinterpret_cast<const uint4*>(rec) + 32 + lane);
             const uint32_t* szr = reinterpret_cast<const uint32_t*>(rec + 1024);
@@ -308,7 +309,7 @@ using namespace owl;
 
 // x: fp16 [T][ldx] (ldx multiple of 8, base 16-byte aligned); out: bf16 [T][ldo].
 OWL_API int owl_w4a16_gemm_tc(const void* x, int ldx, const void* records, void* out, int T, int N, int K, int ldo,
-                              int group, cudaStream_t st) {
+                              int group, int layout, cudaStream_t st) {
   if (T < 1 || (N & 15) || (K & 127) || (ldx & 7) || (ldo & 7) || (group != 32 && group != 128) ||
       (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(out) & 15))
     return OWL_ERR_BAD_ARG;
@@ -316,7 +317,7 @@ OWL_API int owl_w4a16_gemm_tc(const void* x, int ldx, const void* records, void*
   int r = make_map(&a, x, T, K, ldx, 0);
   if (r) return r;
   GemmTcParams p = {};
-  p.wrec = (const uint8_t*)records; p.out = (__nv_bfloat16*)out; p.T = T; p.N = N; p.K = K; p.ldo = ldo; p.group = group;
+  p.wrec = (const uint8_t*)records; p.out = (__nv_bfloat16*)out; p.T = T; p.N = N; p.K = K; p.ldo = ldo; p.group = group; p.layout = layout;
   return launch_gemm<true>(a, a, p, st);
 }
 

@@ -32,9 +32,9 @@
 // ---- activation pack ("ActPack", see actpack.cuh) ---------------------------------------------
 // The int4 weights go to the integer tensor-core path (m16n8k32, u8 x s8/u8) as bytes: one AND
 // extracts the four low nibbles of a weight word, one shift + AND the four high nibbles. The
-// producer of the activations stores x as 16-bit fixed point (signed high byte, unsigned low
-// byte, one scale per token and group) plus the group sum of x; then
-//   sum_k (q_k - z) x_k = sx * (256 * acc_h + acc_l) - z * xsum   with exact int32 accumulation.
+// producer of the activations stores x as 15-bit fixed point (signed high byte, 7-bit low
+// part, one scale per token and group) plus the group sum of x; then
+//   sum_k (q_k - z) x_k = sx * (128 * acc_h + acc_l) - z * xsum   with exact int32 accumulation.
 #include "common.cuh"
 #include "actpack.cuh"
 
@@ -289,8 +289,8 @@ __global__ void __launch_bounds__(SK_WARPS * 32, MT == 1 ? 4 : 2) skinny_stream_
             const float sc0 = __low2float(hh0), z0 = __high2float(hh0);
             const float sc1 = __low2float(hh1), z1 = __high2float(hh1);
             const float xq = 0.25f * sa[0][q].y;    // each of the 4 t lanes carries a quarter of z * xsum
-            acc[0][0] = fmaf(sc0, fmaf(sa[0][q].x, (float)(h0 * 256 + l0), -z0 * xq), acc[0][0]);
-            acc[0][2] = fmaf(sc1, fmaf(sa[0][q].x, (float)(h1 * 256 + l1), -z1 * xq), acc[0][2]);
+            acc[0][0] = fmaf(sc0, fmaf(sa[0][q].x, (float)(h0 * 128 + l0), -z0 * xq), acc[0][0]);
+            acc[0][2] = fmaf(sc1, fmaf(sa[0][q].x, (float)(h1 * 128 + l1), -z1 * xq), acc[0][2]);
           }
         } else if (G == 128) {
 #pragma unroll
@@ -307,8 +307,8 @@ __global__ void __launch_bounds__(SK_WARPS * 32, MT == 1 ? 4 : 2) skinny_stream_
             const __half2 h1 = *reinterpret_cast<const __half2*>(&su1[0]);
             const float sc0 = __low2float(h0), z0 = __high2float(h0);
             const float sc1 = __low2float(h1), z1 = __high2float(h1);
-            const float f0 = (float)(ch[0] * 256 + cl[0]), f1 = (float)(ch[1] * 256 + cl[1]);
-            const float f2 = (float)(ch[2] * 256 + cl[2]), f3 = (float)(ch[3] * 256 + cl[3]);
+            const float f0 = (float)(ch[0] * 128 + cl[0]), f1 = (float)(ch[1] * 128 + cl[1]);
+            const float f2 = (float)(ch[2] * 128 + cl[2]), f3 = (float)(ch[3] * 128 + cl[3]);
             acc[m][0] = fmaf(sc0, fmaf(sa[m][0].x, f0, -z0 * sa[m][0].y), acc[m][0]);
             acc[m][1] = fmaf(sc0, fmaf(sb[m][0].x, f1, -z0 * sb[m][0].y), acc[m][1]);
             acc[m][2] = fmaf(sc1, fmaf(sa[m][0].x, f2, -z1 * sa[m][0].y), acc[m][2]);
@@ -329,8 +329,8 @@ __global__ void __launch_bounds__(SK_WARPS * 32, MT == 1 ? 4 : 2) skinny_stream_
               imma_u8u8(cl, nl[q], nh[q], 0u, 0u, xb[m][q].y, 0u);
               imma_u8s8(ch, ul[q], uh[q], 0u, 0u, xb[m][q].z, 0u);
               imma_u8u8(cl, ul[q], uh[q], 0u, 0u, xb[m][q].w, 0u);
-              const float f0 = (float)(ch[0] * 256 + cl[0]), f1 = (float)(ch[1] * 256 + cl[1]);
-              const float f2 = (float)(ch[2] * 256 + cl[2]), f3 = (float)(ch[3] * 256 + cl[3]);
+              const float f0 = (float)(ch[0] * 128 + cl[0]), f1 = (float)(ch[1] * 128 + cl[1]);
+              const float f2 = (float)(ch[2] * 128 + cl[2]), f3 = (float)(ch[3] * 128 + cl[3]);
               acc[m][0] = fmaf(sc0, fmaf(sa[m][q].x, f0, -z0 * sa[m][q].y), acc[m][0]);
               acc[m][1] = fmaf(sc0, fmaf(sb[m][q].x, f1, -z0 * sb[m][q].y), acc[m][1]);
               acc[m][2] = fmaf(sc1, fmaf(sa[m][q].x, f2, -z1 * sa[m][q].y), acc[m][2]);

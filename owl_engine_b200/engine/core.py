@@ -38,6 +38,7 @@ class EngineConfig:
     prefill_chunk: int = 2048
     pdl: bool = True
     prefill_gemm: str = "tc"
+    decode_gemv: str = "dp4a"      # W4 decode arm: "dp4a" (legacy streaming kernels) or "tc" (tcgen05 streaming kernel)
     seed: int = 0
     n_layers: int | None = None    # override (tests / smoke)
 
@@ -74,7 +75,8 @@ class Engine:
         rank = comm.rank if comm is not None else 0
         self.spec = full.sharded(rank, world) if world > 1 and full.tp_world == 1 else full
         self.weights = weights or H.random_weights(self.spec, self.device, group=cfg.group, seed=cfg.seed + rank * 7919,
-                                                   lm_head_int8=cfg.lm_head_int8)
+                                                   lm_head_int8=cfg.lm_head_int8,
+                                                   layout="block" if cfg.decode_gemv == "tc" else "slice")
         self.pool = H.StatePool(self.spec, self.device, cfg.n_pages, cfg.n_slots + cfg.n_snap_rows)
         self.max_blocks = (cfg.max_seq + PAGE - 1) // PAGE
         self.runner = H.HybridRunner(self.spec, self.weights, self.pool, max_seqs=cfg.max_seqs,

@@ -61,6 +61,11 @@ class HybridWeights:
     group: int
     vocab_offset: int = 0
 
+    @property
+    def layout(self) -> str:
+        """Record layout of the W4 weights: "slice" (legacy streaming kernels) or "block" (tcgen05 streaming kernel)."""
+        return self.layers[0].gate_up.layout if self.layers else "slice"
+
     def nbytes(self) -> int:
         n = self.embed.numel() * 2 + self.lm_head.nbytes
         for l in self.layers:
@@ -81,7 +86,7 @@ def _pad16_rows(w: torch.Tensor) -> torch.Tensor:
     return torch.cat([w, torch.zeros(16 - n % 16, w.shape[1], dtype=w.dtype, device=w.device)])
 
 
-def weights_from_dense(spec: ModelSpec, dense: dict, device, group: int = 128, lm_head_int8: bool = False,
+def weights_from_dense(spec: ModelSpec, dense: dict, device, group: int = 128, lm_head_int8: bool = False, layout: str = "slice",
                        vocab_split: bool = False):
     """Build device weights from HF-named dense tensors (full, unsharded model; ``spec`` may be
     a TP shard, in which case rows / columns are cut with ``parallel.plan``). Returns
@@ -101,7 +106,7 @@ def weights_from_dense(spec: ModelSpec, dense: dict, device, group: int = 128, l
             for nm, rows in names:
                 equiv[nm] = deq[off:off + rows]
                 off += rows
-        return Q.pack_skinny(c).to(device)
+        return Q.pack_skinny(c, layout).to(device)
 
     bf = lambda t: t.to(torch.bfloat16).to(device)
     f32 = lambda t: t.float().to(device)
@@ -114,7 +119,7 @@ def weights_from_dense(spec: ModelSpec, dense: dict, device, group: int = 128, l
         ge, ue = Q.deinterleave_gate_up(cgu.dequant().t())
         equiv[m + "gate_proj.weight"], equiv[m + "up_proj.weight"] = ge.t().contiguous(), ue.t().contiguous()
         lw = LayerWeights(kind="full" if spec.is_full(i) else "gdn", ln1=bf(dense[p + "input_layernorm.weight"]),
-                          ln2=bf(dense[p + "post_attention_layernorm.weight"]), gate_up=Q.pack_skinny(cgu).to(device),
+                          ln2=bf(dense[p + "post_attention_layernorm.weight"]), gate_up=Q.pack_skinny(cgu, layout).to(device),
                           down=w4(dense[m + "down_proj.weight"], [(m + "down_proj.weight", spec.hidden)]))
         if lw.kind == "gdn":
             a = p + "linear_attn."
@@ -159,7 +164,7 @@ def weights_from_dense(spec: ModelSpec, dense: dict, device, group: int = 128, l
     return hw, equiv
 
 
-def random_weights(spec: ModelSpec, device, group: int = 128, seed: int = 0, lm_head_int8: bool = False,
+def random_weights(spec: ModelSpec, device, group: int = 128, seed: int = 0, lm_head_int8: bool = False, layout: str = "slice",
                    std: float = 0.02, vocab_split: bool = True) -> HybridWeights:
     """Random-init weights generated directly in the device layouts (benchmarks: no dense copy)."""
     gen = torch.Generator(device=device).manual_seed(seed)
@@ -171,21 +176,21 @@ def random_weights(spec: ModelSpec, device, group: int = 128, seed: int = 0, lm_
         sd += 17
         lw = LayerWeights(kind="full" if spec.is_full(i) else "gdn", ln1=rnd(H).to(torch.bfloat16),
                           ln2=rnd(H).to(torch.bfloat16),
-                          gate_up=Q.random_skinny(2 * spec.inter, H, group, device, std, sd + 1),
-                          down=Q.random_skinny(H, spec.inter, group, device, std, sd + 2))
+                          gate_up=Q.random_skinny(2 * spec.inter, H, group, device, std, sd + 1, layout),
+                          down=Q.random_skinny(H, spec.inter, group, device, std, sd + 2, layout))
         if lw.kind == "gdn":
-            lw.qkvz = Q.random_skinny(spec.conv_dim + spec.value_dim, H, group, device, std, sd + 3)
+            lw.qkvz = Q.random_skinny(spec.conv_dim + spec.value_dim, H, group, device, std, sd + 3, layout)
             lw.ab_dense = _pad16_rows(rnd(2 * spec.nv, H).to(torch.bfloat16))
             lw.ab = Q.dense_skinny(lw.ab_dense, device)
             lw.conv_w = (torch.randn(spec.conv_dim, spec.conv_k, device=device, generator=gen) * 0.2)
             lw.a_log = torch.log(torch.empty(spec.nv, device=device).uniform_(1.0, 16.0, generator=gen))
             lw.dt_bias = torch.ones(spec.nv, device=device)
             lw.gamma = torch.ones(spec.vd, device=device)
-            lw.out_proj = Q.random_skinny(H, spec.value_dim, group, device, std, sd + 4)
+            lw.out_proj = Q.random_skinny(H, spec.value_dim, group, device, std, sd + 4, layout)
         else:
-            lw.qkv = Q.random_skinny(2 * spec.hq * spec.hd + 2 * spec.hkv * spec.hd, H, group, device, std, sd + 5)
+            lw.qkv = Q.random_skinny(2 * spec.hq * spec.hd + 2 * spec.hkv * spec.hd, H, group, device, std, sd + 5, layout)
             lw.q_norm, lw.k_norm = rnd(spec.hd).to(torch.bfloat16), rnd(spec.hd).to(torch.bfloat16)
-            lw.o_proj = Q.random_skinny(H, spec.hq * spec.hd, group, device, std, sd + 6)
+            lw.o_proj = Q.random_skinny(H, spec.hq * spec.hd, group, device, std, sd + 6, layout)
         layers.append(lw)
     emb = rnd(spec.vocab, H).to(torch.bfloat16)
     hw = HybridWeights(spec=spec, embed=emb, final_norm=torch.zeros(H, dtype=torch.bfloat16, device=device),
@@ -268,7 +273,11 @@ class HybridRunner:
         self.G = weights.group
         dev, H, M = self.device, spec.hidden, self.MAX_ROWS
         bf = lambda *s: torch.zeros(*s, dtype=torch.bfloat16, device=dev)
-        f16 = lambda m_, k_: torch.zeros(m_, 2 * k_, dtype=torch.uint8, device=dev)   # ActPack: 2 bytes per k
+        self.tiles = weights.layout == "block"      # decode GEMVs on the tcgen05 streaming kernel
+        self.tc_ws = K.StreamTcWorkspace(dev, max_n=max(2 * spec.inter, spec.conv_dim + spec.value_dim, 4096)) if self.tiles else None
+        # ActPack: 2 bytes per k in the row layout; the tile layout needs a little more (scale pairs ride along)
+        f16 = lambda m_, k_: torch.zeros(max(m_ * 2 * k_, ((m_ + 7) // 8) * K.act_tile_bytes(k_, weights.group)),
+                                         dtype=torch.uint8, device=dev)
         f32 = lambda *s: torch.zeros(*s, dtype=torch.float32, device=dev)
         G = self.G
         self.block_table = torch.zeros(max_seqs, max_blocks, dtype=torch.int32, device=dev)
@@ -316,10 +325,26 @@ class HybridRunner:
                     gslot=i[lay.gslot:lay.gslot + lay.b], bt_row=i[lay.bt_row:lay.bt_row + lay.b])
 
     # -- building blocks ---------------------------------------------------------------------
+    def _grp(self) -> int:
+        """``group`` argument for the ActPack producers: the tile layout when the tcgen05 streaming kernel consumes it."""
+        return self.G | K.ACT_TILES if self.tiles else self.G
+
+    def _gemv(self, w, xp, xs, out, m: int, *, residual=None, epi: int = K.EPI_STORE, ldo=None, pdl: bool = False) -> None:
+        """out[m] = W x on the weight-streaming kernel that matches the weight's record layout."""
+        if w.layout != "block":
+            K.w4a16_skinny(w, xp, xs, out, m, residual=residual, epi=epi, ldo=ldo, pdl=pdl)
+            return
+        tb = K.act_tile_bytes(w.k, w.group)
+        for r0 in range(0, m, 8):       # 8 tokens per pass (one activation tile buffer each)
+            rows = min(8, m - r0)
+            K.w4a16_stream_tc(w, xp.view(-1)[(r0 // 8) * tb:], out[r0:], rows, self.tc_ws,
+                              residual=None if residual is None else residual[r0:], epi=epi,
+                              ldo=ldo if ldo is not None else out.shape[-1], pdl=pdl)
+
     def _norm(self, m: int, w, *, want_xn: bool, want_pack: bool = True) -> None:
         sp = self.spec
         K.rmsnorm_pack(self.h, w, normed=self.xn if want_xn else None, xpack=self.xp_h if want_pack else None,
-                       xs=self.xs_h if want_pack else None, m=m, k=sp.hidden, group=self.G, eps=sp.eps, pdl=self.pdl)
+                       xs=self.xs_h if want_pack else None, m=m, k=sp.hidden, group=self._grp(), eps=sp.eps, pdl=self.pdl)
 
     def _row_parallel(self, which: int, w, xp, xs, m: int, next_norm, *, want_xn: bool, want_pack: bool = True) -> None:
         """h += W x for a row-parallel projection, then x_next = rmsnorm(h) * (1 + next_norm).
@@ -330,15 +355,15 @@ class HybridRunner:
         sp = self.spec
         symm = getattr(self.comm, "symm", None) if self.comm is not None else None
         if self.comm is None or sp.tp_world == 1:
-            K.w4a16_skinny(w, xp, xs, self.h, m, residual=self.h, epi=K.EPI_RESIDUAL, pdl=self.pdl)
+            self._gemv(w, xp, xs, self.h, m, residual=self.h, epi=K.EPI_RESIDUAL, pdl=self.pdl)
             self._norm(m, next_norm, want_xn=want_xn, want_pack=want_pack)
         elif symm is not None:
-            K.w4a16_skinny(w, xp, xs, symm.partial(which), m, pdl=self.pdl)
+            self._gemv(w, xp, xs, symm.partial(which), m, pdl=self.pdl)
             symm.ar_residual_norm(which, self.h, m, next_norm, normed=self.xn if want_xn else None,
                                   xpack=self.xp_h if want_pack else None, xs=self.xs_h if want_pack else None,
-                                  group=self.G, eps=sp.eps, pdl=self.pdl)
+                                  group=self._grp(), eps=sp.eps, pdl=self.pdl)
         else:
-            K.w4a16_skinny(w, xp, xs, self.partial, m, pdl=self.pdl)
+            self._gemv(w, xp, xs, self.partial, m, pdl=self.pdl)
             self.comm.allreduce_add_residual(self.partial, self.h, m)
             self._norm(m, next_norm, want_xn=want_xn, want_pack=want_pack)
 
@@ -346,8 +371,8 @@ class HybridRunner:
         sp = self.spec
         # silu(gate)*up is written as bf16 and packed by a small kernel: the fused pack epilogue
         # (EPI_SILU_PACK) needs 16 row tiles per CTA, which leaves too few CTAs at this size
-        K.w4a16_skinny(lw.gate_up, self.xp_h, self.xs_h, self.act, m, epi=K.EPI_SILU_MUL, ldo=sp.inter, pdl=self.pdl)
-        K.act_pack(self.act, self.xp_i, self.xs_i, m, sp.inter, self.G, pdl=self.pdl)
+        self._gemv(lw.gate_up, self.xp_h, self.xs_h, self.act, m, epi=K.EPI_SILU_MUL, ldo=sp.inter, pdl=self.pdl)
+        K.act_pack(self.act, self.xp_i, self.xs_i, m, sp.inter, self._grp(), pdl=self.pdl)
         self._row_parallel(1, lw.down, self.xp_i, self.xs_i, m, next_norm, want_xn=want_xn, want_pack=want_pack)
 
     def _gdn(self, lw: LayerWeights, li: int, lay: StepLayout, v: dict) -> None:
@@ -357,11 +382,11 @@ class HybridRunner:
         self.side.wait_stream(main)
         with torch.cuda.stream(self.side):
             K.dense_skinny(lw.ab, self.xn, self.ab_out, m, pdl=False)
-        K.w4a16_skinny(lw.qkvz, self.xp_h, self.xs_h, self.qkvz_out, m, pdl=False)
+        self._gemv(lw.qkvz, self.xp_h, self.xs_h, self.qkvz_out, m, pdl=False)
         main.wait_stream(self.side)
         K.gdn_decode(self.qkvz_out, self.qkvz_out.shape[1], self.ab_out, self.ldab, lw.conv_w, lw.a_log, lw.dt_bias,
                      lw.gamma, self.pool.conv_state[li], self.pool.rec_state[li], v["gslot"], xpack=self.xp_v,
-                     xs=self.xs_v, batch=lay.b, t=lay.t, nk=sp.nk, nv=sp.nv, group=self.G, eps=sp.eps, pdl=False)
+                     xs=self.xs_v, batch=lay.b, t=lay.t, nk=sp.nk, nv=sp.nv, group=self._grp(), eps=sp.eps, pdl=False)
         self._row_parallel(0, lw.out_proj, self.xp_v, self.xs_v, m, lw.ln2, want_xn=False)
 
     def _pick_splits(self, b: int, ctx_hint: int) -> int:
@@ -373,7 +398,7 @@ class HybridRunner:
 
     def _full(self, lw: LayerWeights, li: int, lay: StepLayout, v: dict, splits: int) -> None:
         sp, m = self.spec, lay.m
-        K.w4a16_skinny(lw.qkv, self.xp_h, self.xs_h, self.qkv_out, m, pdl=self.pdl)
+        self._gemv(lw.qkv, self.xp_h, self.xs_h, self.qkv_out, m, pdl=self.pdl)
         qn = 2 * sp.hq * sp.hd
         kraw = self.qkv_out[:, qn:]
         vraw = self.qkv_out[:, qn + sp.hkv * sp.hd:]
@@ -385,7 +410,7 @@ class HybridRunner:
                      self.part_o, self.part_ml, lay.b, lay.t, sp.hq, sp.hkv, sp.hd, self.max_blocks, splits, self.scale,
                      pdl=self.pdl)
         K.attn_reduce(self.part_o, self.part_ml, splits, self.qkv_out, self.qkv_n, m, sp.hq, xpack=self.xp_a,
-                      xs=self.xs_a, group=self.G, pdl=self.pdl)
+                      xs=self.xs_a, group=self._grp(), pdl=self.pdl)
         self._row_parallel(0, lw.o_proj, self.xp_a, self.xs_a, m, lw.ln2, want_xn=False)
 
     def _head(self, m: int, sample: bool = True) -> None:

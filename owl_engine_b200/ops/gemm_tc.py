@@ -7,7 +7,7 @@ import torch
 
 from . import kernels as K
 
-K.register("owl_w4a16_gemm_tc", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+K.register("owl_w4a16_gemm_tc", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
 K.register("owl_f16_gemm_tc", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
 
 
@@ -16,7 +16,7 @@ def w4a16_gemm(w, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     assert x.dtype == torch.float16 and out.dtype == torch.bfloat16 and x.stride(-1) == 1 and out.stride(-1) == 1
     t = x.shape[0]
     K.call("owl_w4a16_gemm_tc", K.ptr(x), x.stride(0), K.ptr(w.records), K.ptr(out), t, w.n, w.k, out.stride(0), w.group,
-           K.stream())
+           w.layout_id, K.stream())
     return out
 
 

@@ -7,7 +7,7 @@ failure. There is no fallback: CPU numerics live in ``ops/reference.py``.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_float, c_int, c_void_p
+from ctypes import c_longlong, c_float, c_int, c_void_p
 
 import torch
 
@@ -19,6 +19,7 @@ _F = c_float
 
 _SIGS = {
     "owl_w4a16_skinny": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "owl_w4a16_stream_tc": [_P, _P, _P, _P, _P, c_longlong, _P, c_longlong, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "owl_bf16_skinny": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "owl_w8a16_skinny": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "owl_rmsnorm_pack": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _I, _I, _I, _P],
@@ -34,7 +35,7 @@ _SIGS = {
                                _F, _I, _P],
     "owl_paged_attn": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "owl_decode_advance": [_P, _P, _P, _I, _I, _I, _P],
-    "owl_w4_dequant": [_P, _P, _I, _I, _I, _P],
+    "owl_w4_dequant": [_P, _P, _I, _I, _I, _I, _P],
     "owl_attn_reduce": [_P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _P],
 }
 _bound: dict = {}
@@ -81,10 +82,51 @@ def w4a16_skinny(w, xpack, xs, out, m: int, *, residual=None, epi: int = EPI_STO
     dp4a arm unless ``force_mma`` (A/B runs and tests of the tensor-core arm)."""
     if ldo is None:
         ldo = out.shape[-1] if out is not None else w.n
+    assert w.layout == "slice", "w4a16_skinny reads slice-major records"
     if force_mma:
         tiles_per_cta = -tiles_per_cta - 1
     call("owl_w4a16_skinny", ptr(w.records), ptr(xpack), ptr(xs), ptr(out), ptr(residual), ptr(out_pack), ptr(out_xs),
          m, w.n, w.k, ldo, w.group, epi, gout, tiles_per_cta, int(pdl), stream())
+
+
+class StreamTcWorkspace:
+    """Scratch for the split-K partial sums and arrival tickets of ``w4a16_stream_tc``. One per
+    stream of launches (launches on one stream are ordered; concurrent streams need their own).
+    ``ctas`` = 0 lets the launcher use every CTA slot of the device."""
+
+    def __init__(self, device, max_n: int = 65536, ctas: int = 0):
+        props = torch.cuda.get_device_properties(device)
+        self.ctas = ctas
+        nrb = (max_n + 127) // 128
+        slots = (ctas or 2 * props.multi_processor_count) + 2 * nrb     # row blocks x slots never exceeds this
+        self.scratch = torch.empty(slots * 128 * 8, dtype=torch.float32, device=device)
+        self.counters = torch.zeros(nrb * 4, dtype=torch.int32, device=device)
+
+
+ACT_TILES = 0x1000     # OR into a producer's ``group`` argument: write ActPack in the tile layout
+
+
+def act_tile_bytes(k: int, group: int) -> int:
+    """Size of an ActPack tile-layout buffer for a K-wide activation (any number of tokens <= 8)."""
+    return (k // 128) * (2048 + 64 * (128 // (group & ~ACT_TILES)))
+
+
+def w4a16_stream_tc(w, xtiles, out, m: int, ws: StreamTcWorkspace, *, residual=None, epi: int = EPI_STORE,
+                    ldo: int | None = None, pdl: bool = False) -> None:
+    """out[m, :] = dequant(w) @ x for m <= 8 rows on the tcgen05 integer path (``csrc/gemv_tc.cu``).
+    ``xtiles``: the activations as written by a producer called with ``group | ACT_TILES``."""
+    if ldo is None:
+        ldo = out.shape[-1]
+    assert w.layout == "block", "w4a16_stream_tc reads block-major records (quant.pack_skinny(..., layout='block'))"
+    call("owl_w4a16_stream_tc", ptr(w.records), ptr(xtiles), ptr(out), ptr(residual), ptr(ws.scratch),
+         ws.scratch.numel() * 4, ptr(ws.counters), ws.counters.numel() * 4, m, w.n, w.k, ldo, w.group, epi, ws.ctas,
+         int(pdl), stream())
+
+
+def stream_tc_status() -> int:
+    f = fn("owl_stream_tc_status")
+    f.argtypes = []
+    return f()
 
 
 def dense_skinny(w, x, out, m: int, *, residual=None, epi: int = EPI_STORE, ldo: int | None = None,
@@ -186,7 +228,7 @@ def w4_dequant(w, out=None):
     """Dense bf16 [N, K] copy of a ``W4Skinny`` weight (baseline arm / tests)."""
     if out is None:
         out = torch.empty(w.n, w.k, dtype=torch.bfloat16, device=w.records.device)
-    call("owl_w4_dequant", ptr(w.records), ptr(out), w.n, w.k, w.group, stream())
+    call("owl_w4_dequant", ptr(w.records), ptr(out), w.n, w.k, w.group, w.layout_id, stream())
     return out
 
 

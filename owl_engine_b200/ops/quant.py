@@ -113,16 +113,23 @@ _K_OF_NIB = [0, 2, 4, 6, 1, 3, 5, 7]
 
 @dataclass
 class W4Skinny:
-    """Device-ready W4 weight: a flat slice-major stream of ``N/16 x K/128`` records of
-    ``1024 + 64*(128/G)`` bytes. Each record is 1024 bytes of nibbles followed by the (scale, zero)
-    half2 pairs of its groups."""
+    """Device-ready W4 weight: a flat stream of ``N/16 x K/128`` records of ``1024 + 64*(128/G)``
+    bytes. Each record is 1024 bytes of nibbles followed by the (scale, zero) half2 pairs of its
+    groups. ``layout`` is the record order: "slice" (k-slice major, read by the legacy streaming
+    kernels) or "block" ([128-row block][k-record][row tile], row tiles padded to a multiple of 8
+    with zero records; read by the tcgen05 streaming kernel as one contiguous run per CTA)."""
     records: torch.Tensor
     n: int
     k: int
     group: int
+    layout: str = "slice"
 
     def to(self, device):
-        return W4Skinny(self.records.to(device), self.n, self.k, self.group)
+        return W4Skinny(self.records.to(device), self.n, self.k, self.group, self.layout)
+
+    @property
+    def layout_id(self) -> int:
+        return 1 if self.layout == "block" else 0
 
     @property
     def nbytes(self) -> int:
@@ -133,7 +140,22 @@ class W4Skinny:
         return 1024 + 64 * (128 // self.group)
 
 
-def pack_skinny(c: W4Canonical) -> W4Skinny:
+def to_block_major(rec: torch.Tensor) -> torch.Tensor:
+    """[NT, KT, REC] -> flat bytes ordered [row block][kt][row tile in block (8)], zero records appended
+    so that NT becomes a multiple of 8."""
+    nt, kt, r = rec.shape
+    nrb = (nt + 7) // 8
+    if nrb * 8 != nt:
+        rec = torch.cat([rec, torch.zeros(nrb * 8 - nt, kt, r, dtype=rec.dtype, device=rec.device)])
+    return rec.view(nrb, 8, kt, r).permute(0, 2, 1, 3).reshape(-1).contiguous()
+
+
+def from_block_major(flat: torch.Tensor, nt: int, kt: int, r: int) -> torch.Tensor:
+    nrb = (nt + 7) // 8
+    return flat.view(nrb, kt, 8, r).permute(0, 2, 1, 3).reshape(nrb * 8, kt, r)[:nt].contiguous()
+
+
+def pack_skinny(c: W4Canonical, layout: str = "slice") -> W4Skinny:
     n, k = c.q.shape
     assert n % 16 == 0 and k % 128 == 0, (n, k)
     nt, kt = n // 16, k // 128
@@ -146,13 +168,14 @@ def pack_skinny(c: W4Canonical) -> W4Skinny:
     sz = torch.stack([c.scales.view(nt, 16, kg).permute(0, 2, 1),
                       c.zeros.view(nt, 16, kg).permute(0, 2, 1).to(torch.float16)], dim=-1).contiguous()
     szb = sz.view(torch.uint8).reshape(nt, kt, gpt * 64)
-    return W4Skinny(to_slice_major(torch.cat([tiles, szb], dim=-1)), n, k, c.group)
+    rec = torch.cat([tiles, szb], dim=-1)
+    return W4Skinny(to_block_major(rec) if layout == "block" else to_slice_major(rec), n, k, c.group, layout)
 
 
 def unpack_skinny(s: W4Skinny) -> W4Canonical:
     nt, kt = s.n // 16, s.k // 128
     gpt = 128 // s.group
-    rec = from_slice_major(s.records, nt, kt, s.rec_bytes)
+    rec = (from_block_major if s.layout == "block" else from_slice_major)(s.records, nt, kt, s.rec_bytes)
     b = rec[..., :1024].reshape(nt, kt, 2, 8, 4, 4, 4)
     sz = rec[..., 1024:].contiguous().view(torch.float16).reshape(nt, kt * gpt, 16, 2)
     v = torch.stack([b & 0xF, b >> 4], dim=-1).reshape(nt, kt, 2, 8, 4, 4, 8)[..., _NIB_OF_K]
@@ -165,7 +188,7 @@ def unpack_skinny(s: W4Skinny) -> W4Canonical:
     return W4Canonical(q, scales, zeros, s.group)
 
 
-def random_skinny(n: int, k: int, group: int, device, std: float = 0.02, seed: int = 0) -> W4Skinny:
+def random_skinny(n: int, k: int, group: int, device, std: float = 0.02, seed: int = 0, layout: str = "slice") -> W4Skinny:
     """Random W4 weight generated directly in the device layout (benchmark initialisation).
 
     Equivalent to quantising N(0, std) weights: nibbles are drawn from a rounded normal around
@@ -173,6 +196,8 @@ def random_skinny(n: int, k: int, group: int, device, std: float = 0.02, seed: i
     """
     gen = torch.Generator(device=device).manual_seed(seed)
     nt, kt = n // 16, k // 128
+    if layout == "block":
+        nt = (nt + 7) // 8 * 8        # padded row tiles are never stored, so their content is free
     vals = (torch.randn(nt, kt, 2048, device=device, generator=gen) * 2.5 + 8.0).round().clamp_(0, 15).to(torch.uint8)
     tiles = (vals[..., 0::2] | (vals[..., 1::2] << 4)).contiguous()
     kg = k // group
@@ -182,7 +207,7 @@ def random_skinny(n: int, k: int, group: int, device, std: float = 0.02, seed: i
     sz[..., 1] = torch.randint(7, 10, (nt, kg, 16), device=device, generator=gen).to(torch.float16)
     szb = sz.view(torch.uint8).reshape(nt, kt, gpt * 64)
     # a random stream is layout-agnostic: any record order is an equally random weight
-    return W4Skinny(torch.cat([tiles, szb], dim=-1).reshape(-1).contiguous(), n, k, group)
+    return W4Skinny(torch.cat([tiles, szb], dim=-1).reshape(-1).contiguous(), n, k, group, layout)
 
 
 def pack_dense_bf16(w: torch.Tensor) -> torch.Tensor:
@@ -246,8 +271,8 @@ def dense_skinny(w: torch.Tensor, device=None, int8: bool = False) -> DenseSkinn
 def act_pack_ref(x: torch.Tensor, group: int):
     """fp32 reference of the ActPack producer (see ``csrc/actpack.cuh``).
 
-    Returns ``(xpack uint8 [M, 2K], xs fp32 [M, K/G, 2])``. Activations are 16-bit fixed point,
-    ``x = sx * (256 h + l)`` (h signed, l unsigned byte), one scale per (token, group). Every run of
+    Returns ``(xpack uint8 [M, 2K], xs fp32 [M, K/G, 2])``. Activations are 15-bit fixed point,
+    ``x = sx * (128 h + l)`` (h signed byte, l in 0..127), one scale per (token, group). Every run of
     8 consecutive k is one 16-byte chunk ``[h(a) x4 | l(a) x4 | h(c) x4 | l(c) x4]`` where for weight
     byte b, a = x[{0,4,1,5}[b]] (low nibble) and c = x[{2,6,3,7}[b]] (high nibble);
     ``xs = (sx, xsum)``."""
@@ -256,14 +281,37 @@ def act_pack_ref(x: torch.Tensor, group: int):
     a, c = v[..., [0, 4, 1, 5]], v[..., [2, 6, 3, 7]]
     cpg = group // 8
     amax = torch.maximum(a.abs(), c.abs()).amax(-1).view(m, k // group, cpg).amax(-1)
-    sx = amax.clamp_min(1e-30) * torch.tensor(1.0 / 32767.0, dtype=torch.float32)
+    sx = amax.clamp_min(1e-30) * torch.tensor(1.0 / 16383.0, dtype=torch.float32)
     inv = (1.0 / sx).repeat_interleave(cpg, dim=1)[..., None]
     qa = torch.round(a * inv).to(torch.int32)
     qc = torch.round(c * inv).to(torch.int32)
-    planes = torch.stack([(qa >> 8) & 0xFF, qa & 0xFF, (qc >> 8) & 0xFF, qc & 0xFF], dim=2)   # [m, chunks, 4, 4]
+    planes = torch.stack([(qa >> 7) & 0xFF, qa & 0x7F, (qc >> 7) & 0xFF, qc & 0x7F], dim=2)   # [m, chunks, 4, 4]
     xpack = planes.to(torch.uint8).reshape(m, 2 * k)
     xsum = (a + c).sum(-1).view(m, k // group, cpg).sum(-1)
     return xpack, torch.stack([sx, xsum], dim=-1)
+
+
+def act_pack_tiles_ref(x: torch.Tensor, group: int) -> torch.Tensor:
+    """ActPack of ``x`` [M <= 8, K] in the tile layout (see ``csrc/actpack.cuh``): per 128-k record
+    ``[4 steps][2 k halves][16 columns][16 B]`` + ``[128/G groups][8 tokens]`` float2 (sx, xsum); flat uint8.
+    Bytes of token slots >= M are zero here (the kernels leave them untouched)."""
+    m, k = x.shape
+    assert m <= 8
+    xp, xs = act_pack_ref(x, group)
+    gpt = 128 // group
+    kt_n = k // 128
+    chunks = xp.view(m, kt_n, 4, 4, 4, 4)                     # m, kt, w, t, plane(ha,la,hc,lc), 4 bytes
+    tile = torch.zeros(kt_n, 4, 2, 16, 16, dtype=torch.uint8)  # kt, w, k half, column, byte
+    for mm in range(m):
+        for t in range(4):
+            kc, off = t >> 1, (t & 1) * 8
+            tile[:, :, kc, mm, off:off + 4] = chunks[mm, :, :, t, 0]          # h(a)
+            tile[:, :, kc, mm, off + 4:off + 8] = chunks[mm, :, :, t, 2]      # h(c)
+            tile[:, :, kc, 8 + mm, off:off + 4] = chunks[mm, :, :, t, 1]      # l(a)
+            tile[:, :, kc, 8 + mm, off + 4:off + 8] = chunks[mm, :, :, t, 3]  # l(c)
+    sc = torch.zeros(kt_n, gpt, 8, 2, dtype=torch.float32)
+    sc[:, :, :m] = xs.view(m, kt_n, gpt, 2).permute(1, 2, 0, 3)
+    return torch.cat([tile.reshape(kt_n, 2048), sc.view(torch.uint8).reshape(kt_n, gpt * 64)], dim=1).reshape(-1)
 
 
 def act_unpack_ref(xpack: torch.Tensor, xs: torch.Tensor, group: int) -> torch.Tensor:
@@ -272,7 +320,7 @@ def act_unpack_ref(xpack: torch.Tensor, xs: torch.Tensor, group: int) -> torch.T
     p = xpack.view(m, -1, 4, 4).to(torch.int32)
     def val(h, l):
         h = torch.where(h >= 128, h - 256, h)
-        return (h * 256 + l).to(torch.float32)
+        return (h * 128 + l).to(torch.float32)
     cpg = group // 8
     sx = xs[..., 0].repeat_interleave(cpg, dim=1)[..., None]
     a, c = val(p[:, :, 0], p[:, :, 1]) * sx, val(p[:, :, 2], p[:, :, 3]) * sx

@@ -10,10 +10,10 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-def build(arm="baseline", n_layers=4, group=128):
+def build(arm="baseline", n_layers=4, group=128, layout="slice"):
     spec = make_spec(n_layers=n_layers)
     dense = init_weights(spec, seed=3, std=0.05)
-    hw, equiv = H.weights_from_dense(spec, dense, DEV, group=group)
+    hw, equiv = H.weights_from_dense(spec, dense, DEV, group=group, layout=layout)
     pool = H.StatePool(spec, DEV, n_pages=32, n_slots=4)
     run = H.HybridRunner(spec, hw, pool, max_seqs=4, max_blocks=16, prefill_gemm=arm, pdl=True)
     ref = RefModel(spec, equiv, kv_fp8=True)
@@ -24,9 +24,10 @@ def rel_err(a, b):
     return ((a - b).norm() / b.norm().clamp_min(1e-6)).item()
 
 
-@pytest.mark.parametrize("arm", ["baseline", "tc"])
-def test_prefill_then_decode_matches_reference(arm):
-    spec, run, ref = build(arm)
+@pytest.mark.parametrize("arm,layout", [("baseline", "slice"), ("tc", "slice"), ("tc", "block")])
+def test_prefill_then_decode_matches_reference(arm, layout):
+    """layout "block": decode GEMVs run on the tcgen05 streaming kernel, producers write ActPack tiles."""
+    spec, run, ref = build(arm, layout=layout)
     g = torch.Generator().manual_seed(0)
     prompt = torch.randint(0, spec.vocab, (37,), generator=g)
     seq_row, slot = 1, 2
@@ -65,8 +66,9 @@ def test_prefill_then_decode_matches_reference(arm):
         nxt = int(want.argmax(-1))
 
 
-def test_batched_decode_and_self_feeding_graph():
-    spec, run, ref = build()
+@pytest.mark.parametrize("layout", ["slice", "block"])
+def test_batched_decode_and_self_feeding_graph(layout):
+    spec, run, ref = build(layout=layout)
     g = torch.Generator().manual_seed(1)
     prompts = [torch.randint(0, spec.vocab, (n,), generator=g) for n in (9, 20)]
     rows, slots = [0, 2], [1, 3]
