@@ -54,6 +54,9 @@ class Sequence:
     n_prompt: int = 0
     reused: int = 0                # prompt tokens served from the prefix cache
     chain: object = None           # block hashes of the prompt (numpy uint64)
+    images: list = field(default_factory=list)    # [(first token index, merged embeddings [n, H], fingerprint)]
+    pos3: object = None            # multimodal (t, h, w) position ids of the prompt, int32 [3, n_prompt] (None = text only)
+    rope_delta: int = 0            # rope position of a decode token = its cache index + rope_delta
 
 
 class Engine:
@@ -77,7 +80,9 @@ class Engine:
         self.weights = weights or H.random_weights(self.spec, self.device, group=cfg.group, seed=cfg.seed + rank * 7919,
                                                    lm_head_int8=cfg.lm_head_int8,
                                                    layout="block" if cfg.decode_gemv == "tc" else "slice")
-        self.pool = H.StatePool(self.spec, self.device, cfg.n_pages, cfg.n_slots + cfg.n_snap_rows)
+        # GDN rows: one per sequence slot, the prefix-snapshot rows, and one scratch row for speculative rollback
+        self.pool = H.StatePool(self.spec, self.device, cfg.n_pages, cfg.n_slots + cfg.n_snap_rows + 1)
+        self.spec_row = cfg.n_slots + cfg.n_snap_rows
         self.max_blocks = (cfg.max_seq + PAGE - 1) // PAGE
         self.runner = H.HybridRunner(self.spec, self.weights, self.pool, max_seqs=cfg.max_seqs,
                                      max_blocks=self.max_blocks, prefill_chunk=cfg.prefill_chunk, comm=comm,
@@ -132,9 +137,24 @@ class Engine:
                                                                                       device=self.device)
 
     # -- sequences ------------------------------------------------------------------------------
-    def add_sequence(self, prompt: list[int], reuse: bool = True) -> int:
+    def _hash_tokens(self, seq_or_tokens, images=None) -> list[int]:
+        """Tokens as seen by the prefix cache: every image-pad run is replaced by values derived from the
+        image's content fingerprint, so two prompts share a cached block only if they show the same pixels."""
+        toks = list(seq_or_tokens)
+        for first, emb, fp in images or []:
+            for j in range(emb.shape[0]):
+                if first + j < len(toks):
+                    toks[first + j] = ((fp >> (8 * (j % 8))) ^ (j * 0x9E3779B1)) & 0x7FFFFFFF
+        return toks
+
+    def add_sequence(self, prompt: list[int], reuse: bool = True, images: list | None = None,
+                     image_pad_id: int | None = None) -> int:
         """Start a sequence. With ``reuse`` the longest cached prefix for which a GDN snapshot exists
-        is adopted: its KV pages are shared (pinned) and the snapshot is copied into the new row."""
+        is adopted: its KV pages are shared (pinned) and the snapshot is copied into the new row.
+
+        ``images``: ``[(merged embeddings [n_i, hidden], (t, gh, gw), fingerprint)]`` in prompt order
+        (``models.vision``); their rows replace the ``image_pad_id`` tokens and the prompt gets
+        (t, h, w) position ids."""
         if not self.free_rows:
             raise RuntimeError("no free sequence row")
         sid = self._next_sid
@@ -144,8 +164,20 @@ class Engine:
         self._next_sid += 1
         seq = Sequence(sid, self.free_rows.pop(), slot, list(prompt), n_prompt=len(prompt))
         self.pool.reset_slot(slot)
+        if images:
+            from ..models.vision import mrope_positions
+
+            merge = 2
+            seq.pos3, nxt = mrope_positions(list(prompt), image_pad_id, [g for _, g, _ in images], merge)
+            seq.rope_delta = nxt - len(prompt)
+            i = 0
+            for emb, grid, fp in images:
+                while prompt[i] != image_pad_id:
+                    i += 1
+                seq.images.append((i, emb, fp))
+                i += emb.shape[0]
         usable = (len(prompt) - 1) // PAGE * PAGE             # at least one token is always prefilled
-        seq.chain = self.kv.chain(prompt[:usable]) if reuse and usable else None
+        seq.chain = self.kv.chain(self._hash_tokens(prompt, seq.images)[:usable]) if reuse and usable else None
         if seq.chain is not None and len(seq.chain):
             self.prefix_lookups += 1
             m, pages, carriers = self.kv.match(seq.chain)
@@ -180,7 +212,7 @@ class Engine:
         seq = self.seqs.pop(sid)
         if publish and seq.n_cached >= PAGE:
             nb = min(seq.n_cached // PAGE, len(seq.pages))
-            chain = self.kv.chain(seq.tokens[:nb * PAGE])
+            chain = self.kv.chain(self._hash_tokens(seq.tokens, seq.images)[:nb * PAGE])
             self.kv.publish(chain, seq.pages[:nb])
         self.kv.unref(seq.pages)
         self.free_rows.append(seq.row)
@@ -194,7 +226,18 @@ class Engine:
         assert start == seq.n_cached and end <= seq.n_prompt
         self._ensure_pages(seq, end + 1)
         ids = torch.tensor(seq.tokens[start:end], dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
-        tok = self.runner.prefill_chunk_forward(ids, start, seq.row, seq.slot, want_logits=want_token)
+        embeds = pos3 = None
+        if seq.images:
+            # text rows from the embedding table, image rows from the vision tower's merged embeddings
+            embeds = torch.empty(end - start, self.spec.hidden, dtype=torch.bfloat16, device=self.device)
+            K.embed(ids, self.weights.embed, embeds, end - start)
+            for first, emb, _ in seq.images:
+                lo, hi = max(first, start), min(first + emb.shape[0], end)
+                if lo < hi:
+                    embeds[lo - start:hi - start] = emb[lo - first:hi - first].to(self.device, torch.bfloat16)
+            pos3 = seq.pos3[:, start:end].to(self.device)
+        tok = self.runner.prefill_chunk_forward(ids, start, seq.row, seq.slot, want_logits=want_token, embeds=embeds,
+                                                pos3=pos3)
         seq.n_cached = end
         boundary = (seq.n_prompt - 1) // PAGE * PAGE
         if end == boundary and boundary > seq.reused and seq.chain is not None and len(seq.chain):
@@ -241,9 +284,9 @@ class Engine:
             pos = seq.n_cached
             self._ensure_pages(seq, pos + 1)
             hi[lay.ids + i] = seq.tokens[-1]
-            hi[lay.pos3 + i] = pos
-            hi[lay.pos3 + b + i] = pos
-            hi[lay.pos3 + 2 * b + i] = pos
+            hi[lay.pos3 + i] = pos + seq.rope_delta
+            hi[lay.pos3 + b + i] = pos + seq.rope_delta
+            hi[lay.pos3 + 2 * b + i] = pos + seq.rope_delta
             hi[lay.kv_slot + i] = seq.pages[pos // PAGE] * PAGE + pos % PAGE
             hi[lay.ctx + i] = pos + 1
             hi[lay.gslot + i] = seq.slot

@@ -153,6 +153,8 @@ class RunningEngine:
         t.sink.put(("prefill", t.turn, hi, len(t.tokens)))
         if last:
             t.state = DECODE
+            if self.spec_runner is not None:
+                self.spec_runner.after_prefill(self.e, t.sid)
             self._emit(t, tok)
 
     def _do_decode(self, step) -> None:
@@ -174,12 +176,25 @@ class RunningEngine:
             self._emit(t, tok)
 
     def _resample(self, t: Turn, row: int) -> int:
-        """Sampling modes: top-32 candidates of the row's logits come back from the device."""
-        k = min(32, self.e.runner.vocab_local)
-        vals, idx = torch.topk(self.e.runner.logits[row].float(), k)
-        cands = list(zip((idx + self.e.weights.vocab_offset).tolist(), vals.tolist()))
+        """Sampling modes: the device returns the row's top-32 logits with the repetition penalty
+        already applied (``csrc/sample.cu``); temperature / top-k / top-p / the draw run on the host."""
+        from ..ops import kernels as K
+
+        r = self.e.runner
+        if not hasattr(self, "_topk"):
+            self._topk = K.TopK(r.device, max_rows=r.MAX_ROWS, k=min(32, r.vocab_local))
+            self._hist = torch.zeros(r.MAX_ROWS, 4096, dtype=torch.int32, device=r.device)
+            self._hist_len = torch.zeros(r.MAX_ROWS, dtype=torch.int32, device=r.device)
+        pen = t.opts.sampling.rep_penalty
+        hist = sorted(t.history)[-4096:] if pen != 1.0 else []
+        if hist:
+            self._hist[row, :len(hist)].copy_(torch.tensor(hist, dtype=torch.int32), non_blocking=True)
+        self._hist_len[row] = len(hist)
+        vals, idx = self._topk(r.logits[row:row + 1], 1, r.vocab_local, hist=self._hist[row:row + 1],
+                               hist_len=self._hist_len[row:row + 1], penalty=pen, vocab_offset=self.e.weights.vocab_offset)
+        cands = [(i, v) for i, v in zip(idx[0].tolist(), vals[0].tolist()) if i >= 0]
         # an explicit seed makes the stream a function of (seed, step) only, so a request replays exactly
-        return S.sample(cands, t.opts.sampling, 0 if t.opts.sampling.seed else t.turn, t.n_out, t.history)
+        return S.sample(cands, t.opts.sampling, 0 if t.opts.sampling.seed else t.turn, t.n_out, None)
 
     def _emit(self, t: Turn, tok: int) -> None:
         t.n_out += 1

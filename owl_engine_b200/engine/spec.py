@@ -1,0 +1,261 @@
+"""Speculative decoding: propose -> verify -> accept -> fold.
+
+One round for one sequence whose last token (the *anchor*) has not been fed yet:
+
+1. **propose**: ``depth`` draft tokens from the draft source -- the MTP head (device chain), a
+   suffix lookup in the sequence's own history (host), or an oracle that replays a recorded
+   continuation (forced-acceptance harness for throughput studies and tests);
+2. **verify**: the target runs ``T = 1 + depth`` rows (anchor + drafts) in one step, causal inside
+   the rows, with every GDN layer's inputs kept; its GDN state rows were copied to the sequence's
+   scratch state row first;
+3. **accept**: greedy -- the longest prefix where draft i equals the target's argmax of row i-1;
+   sampling -- exact rejection sampling ``min(1, p/q)`` with a residual resample (``accept_rejection``);
+   ``m`` accepted drafts emit ``m + 1`` tokens (the target's token after the last accepted row);
+4. **fold**: if some rows were rejected the GDN state is restored from the scratch row and only the
+   recurrence of the accepted ``m + 1`` rows is replayed (``HybridRunner.fold``), so the state equals
+   plain decoding. KV entries of rejected rows stay in their pages but are beyond the context
+   length and are overwritten by the next rows.
+
+Greedy speculative output is bit-identical to plain greedy decoding (same kernels, same per-row
+arithmetic), which the tests assert. A window of acceptance lengths drives degrade / restore:
+after ``window`` rounds with a mean accepted length below ``degrade_below`` the runner falls back
+to plain decoding for ``cooldown`` steps.
+
+Reference counterpart: ``crates/engine/src/exec/spec.rs:152,1104,1377``, ``exec/draft.rs``,
+``exec/lookup.rs:1-40``, ``exec/proposal_q.rs:417``, constants ``exec/mod.rs:17-90``.
+"""
+from __future__ import annotations
+
+import random
+from dataclasses import dataclass, field
+
+import torch
+
+from ..models import hybrid as H
+from .core import PAGE, Engine
+
+
+# ---- acceptance rules -------------------------------------------------------------------------
+def accept_greedy(drafts: list[int], target: list[int]) -> int:
+    """``target[i]`` = the target's argmax after row i (row 0 = anchor). Number of accepted drafts."""
+    m = 0
+    while m < len(drafts) and drafts[m] == target[m]:
+        m += 1
+    return m
+
+
+def accept_rejection(drafts: list[int], q: list[dict], p: list[dict], rng: random.Random) -> tuple[int, int]:
+    """Exact speculative sampling. ``q[i]`` / ``p[i]``: proposal / target distributions (token -> prob) for
+    draft i; ``p`` has one more entry (the distribution after the last draft). Returns ``(m, next_token)``:
+    ``m`` accepted drafts and the token that follows them, distributed exactly as target sampling."""
+    for i, d in enumerate(drafts):
+        pi, qi = p[i].get(d, 0.0), q[i].get(d, 0.0)
+        if qi > 0.0 and rng.random() < min(1.0, pi / qi):
+            continue
+        # rejected: resample from the residual max(0, p - q), renormalised
+        res = {t: max(0.0, pv - q[i].get(t, 0.0)) for t, pv in p[i].items()}
+        z = sum(res.values())
+        dist = res if z > 0.0 else p[i]
+        return i, _draw(dist, rng)
+    return len(drafts), _draw(p[len(drafts)], rng)
+
+
+def _draw(dist: dict, rng: random.Random) -> int:
+    z = sum(dist.values())
+    u, acc = rng.random() * z, 0.0
+    for t, v in dist.items():
+        acc += v
+        if u <= acc:
+            return t
+    return next(reversed(dist))
+
+
+# ---- draft sources ----------------------------------------------------------------------------
+class LookupDraft:
+    """Suffix lookup: if the last ``n`` tokens occurred earlier in the sequence, propose what followed."""
+
+    def __init__(self, min_match: int = 2, max_match: int = 8):
+        self.min_match, self.max_match = min_match, max_match
+
+    def propose(self, engine: Engine, sid: int, depth: int) -> list[int]:
+        toks = engine.seqs[sid].tokens
+        n = len(toks)
+        for k in range(min(self.max_match, n - 1), self.min_match - 1, -1):
+            suffix = toks[n - k:]
+            for start in range(n - k - 1, -1, -1):
+                if toks[start:start + k] == suffix:
+                    follow = toks[start + k:start + k + depth]
+                    if follow:
+                        return follow
+        return []
+
+    def observe(self, engine, sid, n_rows, emitted):
+        pass
+
+
+class OracleDraft:
+    """Replays a recorded continuation with a fixed number of correct drafts per round, then a wrong
+    one: the forced-acceptance harness (acceptance length is an input, not a model property)."""
+
+    def __init__(self, continuation: list[int], n_prompt: int, accept: int, vocab: int):
+        self.cont, self.n_prompt, self.accept, self.vocab = continuation, n_prompt, accept, vocab
+
+    def propose(self, engine: Engine, sid: int, depth: int) -> list[int]:
+        seq = engine.seqs[sid]
+        i = len(seq.tokens) - self.n_prompt          # index into the continuation of the NEXT token
+        good = self.cont[i:i + min(self.accept, depth)]
+        out = list(good)
+        if len(out) < depth and i + len(out) < len(self.cont):
+            out.append((self.cont[i + len(out)] + 1) % self.vocab)     # a deliberately wrong draft
+        return out
+
+    def observe(self, engine, sid, n_rows, emitted):
+        pass
+
+
+class MtpDraft:
+    """The MTP head as draft source (``models/mtp.py``); optionally overridden by a suffix lookup."""
+
+    def __init__(self, head, lookup: LookupDraft | None = None):
+        self.head, self.lookup = head, lookup
+        self.ready: dict = {}        # sid -> True once the head has absorbed the row before the anchor
+
+    def after_prefill(self, engine: Engine, sid: int) -> None:
+        """Absorb the last prompt row: (first generated token, hidden of the last prompt position)."""
+        seq = engine.seqs[sid]
+        q = seq.n_cached - 1
+        self.head.absorb([seq.tokens[-1]], engine.runner.h[:1], q, seq.row, seq.pages)
+        self.ready[sid] = True
+
+    def propose(self, engine: Engine, sid: int, depth: int) -> list[int]:
+        if self.lookup is not None:
+            hit = self.lookup.propose(engine, sid, depth)
+            if len(hit) >= depth:
+                return hit
+        if not self.ready.get(sid):
+            return []
+        return self.head.chain(depth).tolist()
+
+    def observe(self, engine: Engine, sid: int, n_rows: int, emitted: list[int]) -> None:
+        """After a verify step: rows 0..n_rows-1 were accepted; feed them with the target's hiddens."""
+        seq = engine.seqs[sid]
+        q0 = seq.n_cached - n_rows
+        self.head.absorb(emitted, engine.runner.h[:n_rows], q0, seq.row, seq.pages)
+        self.ready[sid] = True
+
+
+# ---- the round machine ------------------------------------------------------------------------
+@dataclass
+class SpecStats:
+    rounds: int = 0
+    drafted: int = 0
+    accepted: int = 0
+    emitted: int = 0
+    folds: int = 0
+    degraded_steps: int = 0
+    window: list = field(default_factory=list)
+
+    @property
+    def mean_accept(self) -> float:
+        return self.accepted / max(1, self.rounds)
+
+
+class SpecRunner:
+    def __init__(self, draft, depth: int = 3, *, window: int = 16, degrade_below: float = 0.3, cooldown: int = 64):
+        assert 1 <= depth <= 7
+        self.draft, self.depth = draft, depth
+        self.window, self.degrade_below, self.cooldown = window, degrade_below, cooldown
+        self.stats = SpecStats()
+        self._cool = 0
+
+    def after_prefill(self, engine: Engine, sid: int) -> None:
+        if hasattr(self.draft, "after_prefill"):
+            self.draft.after_prefill(engine, sid)
+
+    def round(self, engine: Engine, sid: int) -> list[int]:
+        """Emit one or more tokens for the sequence (appended to ``seq.tokens``)."""
+        st = self.stats
+        if self._cool > 0:                       # degraded: plain decoding until the cooldown ends
+            self._cool -= 1
+            st.degraded_steps += 1
+            out = engine.decode_step([sid])
+            self.draft.observe(engine, sid, 1, out)
+            return out
+        drafts = self.draft.propose(engine, sid, self.depth)[:self.depth]
+        if not drafts:
+            out = engine.decode_step([sid])
+            self.draft.observe(engine, sid, 1, out)
+            return out
+        seq = engine.seqs[sid]
+        rows = [seq.tokens[-1]] + drafts
+        target = verify_step(engine, sid, rows)
+        m = accept_greedy(drafts, target)
+        n_rows = m + 1
+        if n_rows < len(rows):
+            # rejected rows advanced the recurrent state: restore and replay the accepted prefix
+            engine.pool.copy_slot(engine.spec_row, seq.slot)
+            engine.runner.fold_slot.fill_(seq.slot)
+            engine.runner.capture_fold(n_rows).replay()
+            st.folds += 1
+        emitted = target[:n_rows]
+        seq.tokens.extend(emitted)
+        seq.n_cached += n_rows
+        self.draft.observe(engine, sid, n_rows, emitted)
+        st.rounds += 1
+        st.drafted += len(drafts)
+        st.accepted += m
+        st.emitted += n_rows
+        st.window.append(m)
+        if len(st.window) >= self.window:
+            if sum(st.window) / len(st.window) < self.degrade_below:
+                self._cool = self.cooldown
+            st.window.clear()
+        return emitted
+
+
+def generate_spec(engine: Engine, prompt: list[int], max_new_tokens: int, spec: SpecRunner, eos: int | None = None) -> list[int]:
+    """Greedy generation with speculative rounds (the speculative twin of ``Engine.generate``)."""
+    sid = engine.add_sequence(prompt)
+    try:
+        out = [engine.prefill(sid)]
+        spec.after_prefill(engine, sid)
+        while len(out) < max_new_tokens and (eos is None or eos not in out):
+            out.extend(spec.round(engine, sid))
+        if eos is not None and eos in out:
+            out = out[:out.index(eos) + 1]
+        return out[:max_new_tokens]
+    finally:
+        engine.free_sequence(sid, publish=False)
+
+
+def verify_step(engine: Engine, sid: int, rows: list[int]) -> list[int]:
+    """Run the target over ``rows`` (anchor + drafts) as one (1, T) step; returns the argmax after each row.
+    The sequence's GDN state is copied to the engine's scratch row first; every GDN layer's inputs are kept."""
+    seq, r = engine.seqs[sid], engine.runner
+    t, pos = len(rows), seq.n_cached
+    engine._ensure_pages(seq, pos + t + 1)
+    if r.gdn_save is None:
+        r.enable_gdn_save()
+        r.capture_fold(1)          # allocates fold_slot
+    engine.pool.copy_slot(seq.slot, engine.spec_row)
+    lay = H.StepLayout(1, t)
+    hi = engine.h_inp_np
+    for i, tok in enumerate(rows):
+        p = pos + i
+        hi[lay.ids + i] = tok
+        hi[lay.pos3 + i] = p + seq.rope_delta
+        hi[lay.pos3 + t + i] = p + seq.rope_delta
+        hi[lay.pos3 + 2 * t + i] = p + seq.rope_delta
+        hi[lay.kv_slot + i] = seq.pages[p // PAGE] * PAGE + p % PAGE
+    hi[lay.ctx] = pos + t
+    hi[lay.gslot] = seq.slot
+    hi[lay.bt_row] = seq.row
+    graph = r.capture(1, t, ctx_hint=engine._ctx_bucket(pos + t))
+    n = lay.size
+    r.inp[:n].copy_(engine.h_inp[:n], non_blocking=True)
+    graph.replay()
+    engine.h_tok[:t].copy_(r.out_tok[:t], non_blocking=True)
+    torch.cuda.current_stream().synchronize()
+    engine.h2d_bytes += n * 4
+    engine.d2h_bytes += t * 4
+    return [int(x) for x in engine.h_tok_np[:t]]

@@ -316,6 +316,8 @@ class HybridRunner:
         self.graphs: dict = {}
         self._pf = None   # lazily allocated prefill workspace
         self.taps: dict | None = None   # layer -> bf16 [M,H] buffers filled during decode/prefill for draft heads
+        self.pre_hook = None            # callable(m): rewrites self.h after the embedding (draft heads mix in the target's hidden)
+        self.gdn_save = None            # (qkvz [n_gdn, M, nq], ab [n_gdn, M, ldab]): GDN inputs of the last step, kept for fold()
 
     # -- step inputs -------------------------------------------------------------------------
     def views(self, lay: StepLayout):
@@ -379,12 +381,14 @@ class HybridRunner:
         sp, m = self.spec, lay.m
         # fork: the tiny dense a/b projection runs beside the big qkvz stream
         main = torch.cuda.current_stream()
+        # a speculative verify step keeps every layer's GDN inputs so that fold() can replay a prefix
+        qo, ao = (self.qkvz_out, self.ab_out) if self.gdn_save is None else (self.gdn_save[0][li], self.gdn_save[1][li])
         self.side.wait_stream(main)
         with torch.cuda.stream(self.side):
-            K.dense_skinny(lw.ab, self.xn, self.ab_out, m, pdl=False)
-        self._gemv(lw.qkvz, self.xp_h, self.xs_h, self.qkvz_out, m, pdl=False)
+            K.dense_skinny(lw.ab, self.xn, ao, m, pdl=False)
+        self._gemv(lw.qkvz, self.xp_h, self.xs_h, qo, m, pdl=False)
         main.wait_stream(self.side)
-        K.gdn_decode(self.qkvz_out, self.qkvz_out.shape[1], self.ab_out, self.ldab, lw.conv_w, lw.a_log, lw.dt_bias,
+        K.gdn_decode(qo, qo.shape[1], ao, self.ldab, lw.conv_w, lw.a_log, lw.dt_bias,
                      lw.gamma, self.pool.conv_state[li], self.pool.rec_state[li], v["gslot"], xpack=self.xp_v,
                      xs=self.xs_v, batch=lay.b, t=lay.t, nk=sp.nk, nv=sp.nv, group=self._grp(), eps=sp.eps, pdl=False)
         self._row_parallel(0, lw.out_proj, self.xp_v, self.xs_v, m, lw.ln2, want_xn=False)
@@ -436,6 +440,8 @@ class HybridRunner:
         m = lay.m
         splits = self._pick_splits(lay.b, ctx_hint)
         K.embed(v["ids"], self.w.embed, self.h, m, pdl=False)
+        if self.pre_hook is not None:
+            self.pre_hook(m)
         layers = self.w.layers
         self._norm(m, layers[0].ln1, want_xn=layers[0].kind == "gdn")
         fi = gi = 0
@@ -455,6 +461,52 @@ class HybridRunner:
         if advance:
             assert lay.t == 1
             K.decode_advance(self.inp, self.out_tok, self.block_table, self.max_blocks, lay.b, pdl=self.pdl)
+
+    def enable_gdn_save(self) -> None:
+        """Allocate the per-layer GDN input buffers that a verify step fills and fold() replays."""
+        if self.gdn_save is None:
+            sp, ng = self.spec, self.spec.n_layers - self.spec.n_full
+            self.gdn_save = (torch.zeros(ng, self.MAX_ROWS, sp.conv_dim + sp.value_dim, dtype=torch.bfloat16, device=self.device),
+                             torch.zeros(ng, self.MAX_ROWS, self.ldab, dtype=torch.bfloat16, device=self.device))
+            self.graphs.clear()     # captured graphs point at the old buffers
+
+    def fold(self, gslot: torch.Tensor, t: int) -> None:
+        """Advance the GDN state of one sequence over the first ``t`` rows of the last (saved)
+        step: the recurrent state update only, no outputs. After a speculative verify the caller
+        restores the pre-verify state and folds the accepted prefix, so the state equals what
+        plain decoding of those tokens would have produced. Capturable; ``gslot`` int32 [1]."""
+        sp = self.spec
+        qs, as_ = self.gdn_save
+        gi = 0
+        for lw in self.w.layers:
+            if lw.kind != "gdn":
+                continue
+            K.gdn_decode(qs[gi], qs.shape[2], as_[gi], self.ldab, lw.conv_w, lw.a_log, lw.dt_bias, lw.gamma,
+                         self.pool.conv_state[gi], self.pool.rec_state[gi], gslot, batch=1, t=t, nk=sp.nk, nv=sp.nv,
+                         group=self.G, eps=sp.eps, pdl=False)
+            gi += 1
+
+    def capture_fold(self, t: int):
+        """CUDA graph of fold(t) reading the GDN slot from ``self.fold_slot``."""
+        key = ("fold", t)
+        g = self.graphs.get(key)
+        if g is None:
+            if not hasattr(self, "fold_slot"):
+                self.fold_slot = torch.full((1,), -1, dtype=torch.int32, device=self.device)
+            stream = torch.cuda.Stream(device=self.device)
+            stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(stream):
+                saved = self.fold_slot.clone()
+                self.fold_slot.fill_(-1)
+                self.fold(self.fold_slot, t)           # warm-up on an inert slot
+                stream.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    self.fold(self.fold_slot, t)
+                self.fold_slot.copy_(saved)
+            torch.cuda.current_stream().wait_stream(stream)
+            self.graphs[key] = g
+        return g
 
     def capture(self, b: int, t: int = 1, *, ctx_hint: int = 2048, advance: bool = False, sample: bool = True):
         """Capture (once) and return the CUDA graph of a (b, t) step."""

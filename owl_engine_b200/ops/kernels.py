@@ -224,6 +224,36 @@ def attn_reduce(part_o, part_ml, splits: int, qraw, ldq: int, rows: int, hq: int
          group, _is_f16(out), int(pdl), stream())
 
 
+register("owl_topk", [_P, _I, _I, _I, _I, _P, _P, _I, _F, _I, _P, _P, _I, _P, _P, _P])
+register("owl_topk_merge", [_P, _P, _I, _I, _I, _P, _P, _P])
+
+
+class TopK:
+    """Device top-k (k <= 32) of logits rows with an optional repetition penalty (``csrc/sample.cu``)."""
+
+    def __init__(self, device, max_rows: int = 32, k: int = 32, parts: int = 64):
+        self.k, self.parts = k, parts
+        self.sval = torch.empty(max_rows * parts * k, dtype=torch.float32, device=device)
+        self.sidx = torch.empty(max_rows * parts * k, dtype=torch.int32, device=device)
+        self.val = torch.empty(max_rows, k, dtype=torch.float32, device=device)
+        self.idx = torch.empty(max_rows, k, dtype=torch.int32, device=device)
+
+    def __call__(self, logits, m: int, vocab: int, *, hist=None, hist_len=None, penalty: float = 1.0, vocab_offset: int = 0):
+        call("owl_topk", ptr(logits), logits.stride(0), m, vocab, self.k, ptr(hist), ptr(hist_len),
+             hist.stride(0) if hist is not None else 0, float(penalty), vocab_offset, ptr(self.sval), ptr(self.sidx),
+             self.parts, ptr(self.val), ptr(self.idx), stream())
+        return self.val[:m], self.idx[:m]
+
+
+def topk_merge(cand_val, cand_idx, k: int):
+    """Global top-k of concatenated per-rank candidates ``[M, n]`` (vocab-split head)."""
+    m, n = cand_val.shape
+    ov = torch.empty(m, k, dtype=torch.float32, device=cand_val.device)
+    oi = torch.empty(m, k, dtype=torch.int32, device=cand_val.device)
+    call("owl_topk_merge", ptr(cand_val), ptr(cand_idx), m, n, k, ptr(ov), ptr(oi), stream())
+    return ov, oi
+
+
 def w4_dequant(w, out=None):
     """Dense bf16 [N, K] copy of a ``W4Skinny`` weight (baseline arm / tests)."""
     if out is None:

@@ -118,3 +118,41 @@ def test_http_server_end_to_end():
         asyncio.run(main())
     finally:
         assert svc.shutdown().code == 0
+
+
+def test_image_prompt_embeds_positions_and_content_keyed_prefix_cache():
+    """Image rows come from the vision tower, positions are (t, h, w), and the prefix cache keys image
+    blocks by pixel content: the same tokens with other pixels must not hit."""
+    from owl_engine_b200.cli import png
+    from owl_engine_b200.models import vision as V
+
+    eng = make_engine()
+    spec = V.tiny_vision(out_hidden=eng.spec.hidden)
+    tower, cache = V.VisionTower(spec), V.ImageCache()
+    pad = 500
+
+    def build(rgb):
+        emb, grid, fp = cache.get(tower, png.encode_png(96, 64, rgb), png.decode_png)
+        n = tower.n_tokens(grid)
+        g = torch.Generator().manual_seed(5)
+        head = torch.randint(0, 400, (9,), generator=g).tolist()
+        tail = torch.randint(0, 400, (40,), generator=g).tolist()
+        return head + [pad] * n + tail, [(emb * 20, grid, fp)]
+
+    def run(rgb):
+        prompt, images = build(rgb)
+        sid = eng.add_sequence(prompt, images=images, image_pad_id=pad)
+        seq = eng.seqs[sid]
+        reused = seq.reused
+        assert seq.rope_delta == 3 - 6            # a 2 x 3 merged grid spans 3 positions for 6 tokens
+        out = [eng.prefill(sid)]
+        for _ in range(5):
+            out += eng.decode_step([sid])
+        eng.free_sequence(sid, publish=True)
+        return out, reused
+
+    a, r0 = run(png.RED)
+    b, r1 = run(png.RED)
+    c, r2 = run(png.BLUE)
+    assert r0 == 0 and r1 >= 32 and a == b          # same pixels: cached prefix reused, same continuation
+    assert r2 <= 0 + 16 * 0 and c != a              # other pixels: no reuse past the text head, other output

@@ -340,3 +340,27 @@ def test_qknorm_rope_insert():
 def test_zz_skinny_status_clean_after_all():
     torch.cuda.synchronize()
     assert K.skinny_status() == 0
+
+
+# ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("m,v,k", [(1, 151936, 32), (3, 5000, 16), (2, 40, 32)])
+def test_topk_with_repetition_penalty(m, v, k):
+    logits = bf(torch.randn(m, v, generator=gen(21)) * 4)
+    hist = torch.stack([torch.randperm(v, generator=gen(22 + r))[:12] for r in range(m)]).to(torch.int32)
+    hlen = torch.tensor([12, 5, 0][:m], dtype=torch.int32)
+    pen = 1.3
+    tk = K.TopK(DEV, max_rows=4, k=k)
+    val, idx = tk(logits.to(DEV), m, v, hist=hist.to(DEV), hist_len=hlen.to(DEV), penalty=pen)
+    ref = logits.float().clone()
+    for r in range(m):
+        for t in hist[r, :int(hlen[r])].tolist():
+            ref[r, t] = ref[r, t] / pen if ref[r, t] > 0 else ref[r, t] * pen
+    kk = min(k, v)
+    want_v, want_i = torch.topk(ref, kk, dim=-1)
+    torch.testing.assert_close(val.cpu()[:, :kk], want_v, rtol=0, atol=0)
+    # equal values may come in any index order in torch; ours breaks ties by the lowest index
+    assert torch.equal(torch.gather(ref, 1, idx.cpu()[:, :kk].long()), want_v)
+    if kk < k:
+        assert (idx.cpu()[:, kk:] == -1).all()
+    mv, mi = K.topk_merge(torch.cat([val, val - 1], 1).contiguous(), torch.cat([idx, idx], 1).contiguous(), kk)
+    torch.testing.assert_close(mv.cpu(), want_v[:, :kk], rtol=0, atol=0)

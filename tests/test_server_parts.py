@@ -57,3 +57,23 @@ def test_builtin_template_renders_tools_and_roles():
     assert out.rstrip().endswith("</think>")
     plain = t.render([{"role": "user", "content": "hi"}])
     assert plain == "<|im_start|>user\nhi<|im_end|>\n<|im_start|>assistant\n"
+
+
+def test_rejection_sampling_is_exact():
+    """accept_rejection draws from the target distribution whatever the proposal is."""
+    import random
+    from collections import Counter
+
+    from owl_engine_b200.engine.spec import accept_greedy, accept_rejection
+
+    assert accept_greedy([5, 6, 7], [5, 6, 9, 1]) == 2 and accept_greedy([], [3]) == 0
+    p0, p1 = {1: 0.5, 2: 0.3, 3: 0.2}, {4: 0.9, 5: 0.1}
+    q0 = {1: 0.1, 2: 0.8, 3: 0.1}
+    rng = random.Random(0)
+    first, n = Counter(), 20000
+    for _ in range(n):
+        d = rng.choices(list(q0), weights=list(q0.values()))[0]      # the draft is sampled from q
+        m, nxt = accept_rejection([d], [q0], [p0, p1], rng)
+        first[d if m == 1 else nxt] += 1
+    for t, pv in p0.items():
+        assert abs(first[t] / n - pv) < 0.015
