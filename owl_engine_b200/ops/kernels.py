@@ -254,6 +254,49 @@ def topk_merge(cand_val, cand_idx, k: int):
     return ov, oi
 
 
+register("owl_nvfp4_gemv", [_P, _P, _F, _P, _I, _P, _I, _I, _I, _I, _P])
+register("owl_nvfp4_dequant", [_P, _P, _F, _P, c_longlong, _P])
+register("owl_nvfp4_quant_act", [_P, _F, _P, _P, c_longlong, _P])
+register("owl_gguf_dequant", [_P, _I, _I, _P, _I, _P, _P])
+register("owl_gguf_gemv", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P])
+
+
+def nvfp4_gemv(codes, scales, alpha: float, x, out, m: int) -> None:
+    """out[m, N] = alpha * x . dequant(NVFP4 W)^T for m <= 8 (``csrc/lowbit.cu``). codes uint8 [N, K/2], scales e4m3 bytes [N, K/16]."""
+    n, k = codes.shape[0], codes.shape[1] * 2
+    call("owl_nvfp4_gemv", ptr(codes), ptr(scales), float(alpha), ptr(x), x.stride(0), ptr(out), out.stride(0), m, n, k, stream())
+
+
+def nvfp4_dequant(codes, scales, alpha: float, out=None):
+    n, k = codes.shape[0], codes.shape[1] * 2
+    if out is None:
+        out = torch.empty(n, k, dtype=torch.bfloat16, device=codes.device)
+    call("owl_nvfp4_dequant", ptr(codes), ptr(scales), float(alpha), ptr(out), n * k, stream())
+    return out
+
+
+def nvfp4_quant_act(x, global_scale: float):
+    """bf16 [M, K] -> (codes uint8 [M, K/2], e4m3 block scales uint8 [M, K/16]) for the given global scale."""
+    m, k = x.shape
+    codes = torch.empty(m, k // 2, dtype=torch.uint8, device=x.device)
+    sf = torch.empty(m, k // 16, dtype=torch.uint8, device=x.device)
+    call("owl_nvfp4_quant_act", ptr(x), float(global_scale), ptr(codes), ptr(sf), m * k, stream())
+    return codes, sf
+
+
+def gguf_dequant(blocks, type_id: int, k: int, n_rows: int, rows=None, out=None):
+    """GGUF blocks (uint8, ``n_src_rows * K / elems`` blocks) -> bf16 [R, K]; ``rows`` int32 picks source rows (embedding lookup)."""
+    r = n_rows if rows is None else rows.numel()
+    if out is None:
+        out = torch.empty(r, k, dtype=torch.bfloat16, device=blocks.device)
+    call("owl_gguf_dequant", ptr(blocks), type_id, k, ptr(rows), r, ptr(out), stream())
+    return out
+
+
+def gguf_gemv(blocks, type_id: int, n: int, k: int, x, out, m: int) -> None:
+    call("owl_gguf_gemv", ptr(blocks), type_id, ptr(x), x.stride(0), ptr(out), out.stride(0), m, n, k, stream())
+
+
 def w4_dequant(w, out=None):
     """Dense bf16 [N, K] copy of a ``W4Skinny`` weight (baseline arm / tests)."""
     if out is None:

@@ -1,0 +1,119 @@
+"""Kernel registry: one table row per exported launcher of the native CUDA library.
+
+Every row names the entry symbol, its source file, the op family, whether the launch may be recorded
+into a CUDA graph (no host synchronisation, no allocation, fixed launch geometry for fixed shapes),
+whether the result is bit-reproducible run to run, and the instruction generation the kernel is
+written for. ``cross_check`` parses the ``OWL_API`` declarations of the ``.cu`` sources and verifies
+that (a) every exported symbol has a row and every row an exported symbol, (b) the ctypes signature
+registered in ``ops.kernels`` has as many parameters as the C declaration. The unit tests run it, so a
+launcher cannot change its argument list without the binding noticing.
+
+Reference counterpart: ``crates/kernels/src/{spec,registry,cu_sig}.rs`` (KernelSpec table and the
+``.cu`` signature cross-check), ``admit.rs`` (per-architecture admission: here one architecture).
+"""
+from __future__ import annotations
+
+import re
+from dataclasses import dataclass
+from pathlib import Path
+
+CSRC = Path(__file__).resolve().parents[1] / "csrc"
+ARCH = "sm_100a"
+
+
+@dataclass(frozen=True)
+class KernelSpec:
+    entry: str
+    src: str
+    family: str
+    capture: bool = True          # safe inside CUDA graph capture
+    deterministic: bool = True
+    gen: str = "simt"             # simt | mma.sync | dp4a | tcgen05 | tma | p2p
+
+
+_T = [
+    # weight streaming / GEMM
+    KernelSpec("owl_w4a16_skinny", "gemv.cu", "gemv", gen="dp4a+mma.sync+bulk-copy"),
+    KernelSpec("owl_bf16_skinny", "gemv.cu", "gemv", gen="mma.sync+bulk-copy"),
+    KernelSpec("owl_w8a16_skinny", "gemv.cu", "gemv", gen="mma.sync+bulk-copy"),
+    KernelSpec("owl_skinny_status", "gemv.cu", "status", capture=False),
+    KernelSpec("owl_w4a16_stream_tc", "gemv_tc.cu", "gemv", gen="tcgen05+tmem+bulk-copy"),
+    KernelSpec("owl_stream_tc_status", "gemv_tc.cu", "status", capture=False),
+    KernelSpec("owl_w4a16_gemm_tc", "gemm_tc.cu", "gemm", gen="tcgen05+tmem+tma"),
+    KernelSpec("owl_f16_gemm_tc", "gemm_tc.cu", "gemm", gen="tcgen05+tmem+tma"),
+    KernelSpec("owl_gemm_status", "gemm_tc.cu", "status", capture=False),
+    KernelSpec("owl_w4_dequant", "dequant.cu", "load"),
+    KernelSpec("owl_nvfp4_gemv", "lowbit.cu", "gemv"),
+    KernelSpec("owl_nvfp4_dequant", "lowbit.cu", "load"),
+    KernelSpec("owl_nvfp4_quant_act", "lowbit.cu", "quant"),
+    KernelSpec("owl_gguf_dequant", "lowbit.cu", "load"),
+    KernelSpec("owl_gguf_gemv", "lowbit.cu", "gemv"),
+    # elementwise / norms / sampling
+    KernelSpec("owl_rmsnorm_pack", "elem.cu", "norm"),
+    KernelSpec("owl_act_pack", "elem.cu", "quant"),
+    KernelSpec("owl_silu_mul", "elem.cu", "act"),
+    KernelSpec("owl_sigmoid_gate", "elem.cu", "act"),
+    KernelSpec("owl_embed", "elem.cu", "embed"),
+    KernelSpec("owl_argmax", "elem.cu", "sample"),
+    KernelSpec("owl_argmax_noalloc", "elem.cu", "sample"),
+    KernelSpec("owl_decode_advance", "elem.cu", "step"),
+    KernelSpec("owl_topk", "sample.cu", "sample"),
+    KernelSpec("owl_topk_merge", "sample.cu", "sample"),
+    # GDN
+    KernelSpec("owl_gdn_decode", "gdn.cu", "gdn", gen="simt+cluster-dsmem"),
+    KernelSpec("owl_gdn_conv_fwd", "gdn.cu", "gdn"),
+    KernelSpec("owl_gdn_scan", "gdn.cu", "gdn"),
+    # attention / KV
+    KernelSpec("owl_qknorm_rope_insert", "attn.cu", "attn"),
+    KernelSpec("owl_paged_attn", "attn.cu", "attn", gen="mma.sync"),
+    KernelSpec("owl_attn_reduce", "attn.cu", "attn"),
+    # collectives over peer memory
+    KernelSpec("owl_ar_residual_norm", "comm.cu", "comm", gen="p2p+multimem"),
+    KernelSpec("owl_ar_inplace", "comm.cu", "comm", gen="p2p+multimem"),
+    KernelSpec("owl_argmax_merge", "comm.cu", "comm", gen="p2p"),
+    KernelSpec("owl_comm_wait_probe", "comm.cu", "comm", gen="p2p"),
+    KernelSpec("owl_comm_status", "comm.cu", "status", capture=False),
+]
+TABLE = {k.entry: k for k in _T}
+
+_DECL = re.compile(r"OWL_API\s+int\s+(owl_\w+)\s*\(([^)]*)\)", re.S)
+
+
+def declared() -> dict[str, tuple[str, int]]:
+    """entry -> (source file, parameter count) from the OWL_API declarations under csrc/."""
+    out = {}
+    for f in sorted(CSRC.glob("*.cu")):
+        text = re.sub(r"#ifdef OWL_VT_TRACE.*?#endif", "", f.read_text(), flags=re.S)   # tuning-only exports are not built
+        for name, args in _DECL.findall(text):
+            args = args.strip()
+            n = 0 if args in ("", "void") else len([a for a in args.split(",") if a.strip()])
+            out[name] = (f.name, n)
+    return out
+
+
+def cross_check() -> list[str]:
+    """Mismatches between the sources, this table and the ctypes signatures (empty = consistent)."""
+    from . import kernels as K
+    from . import gemm_tc  # noqa: F401  (registers its signatures)
+
+    problems = []
+    decl = declared()
+    for name, (src, n) in decl.items():
+        row = TABLE.get(name)
+        if row is None:
+            problems.append(f"{name} ({src}) is exported but has no registry row")
+            continue
+        if row.src != src:
+            problems.append(f"{name}: registry says {row.src}, declared in {src}")
+        sig = K._SIGS.get(name)
+        if sig is not None and len(sig) != n:
+            problems.append(f"{name}: ctypes signature has {len(sig)} parameters, the C declaration {n}")
+    for name in TABLE:
+        if name not in decl:
+            problems.append(f"{name}: registry row without an exported symbol")
+    return problems
+
+
+def admit(family: str) -> list[KernelSpec]:
+    """Kernels of a family that this build admits (one architecture: everything in the table)."""
+    return [k for k in _T if k.family == family]

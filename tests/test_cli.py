@@ -66,3 +66,14 @@ def test_client_and_workload_against_scripted_server():
         out = io.StringIO()
         assert repl(c, 200, "s", inp=io.StringIO("hello\n/new\n/quit\n"), out=out) == 0
         assert "ok " in out.getvalue() and "tool call add" in out.getvalue()
+
+
+def test_needle_and_ladder_fixtures_against_scripted_server():
+    from owl_engine_b200.fixtures import needle
+
+    with Server() as s:
+        c = Client(f"http://127.0.0.1:{s.port}")
+        rows = needle.run_needle(c, [50], [0.5])
+        assert rows[0]["hit_rate"] == 0.0 and rows[0]["words"] == 50        # the scripted reply never contains the value
+        lad = needle.run_ladder(c, [30], new_tokens=8)
+        assert lad[0]["error"] is None and lad[0]["prompt_tokens"] > 30

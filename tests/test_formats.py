@@ -86,3 +86,39 @@ def test_gguf_other_codecs_shapes():
         assert out.shape == (be * 4,) and np.isfinite(out).all()
     with pytest.raises(gguf.UnsupportedGgufType):
         gguf.dequantize(np.zeros(10, dtype=np.uint8), "IQ3_S", 256)
+
+
+def test_awq_forge_converts_a_dense_checkpoint(tmp_path):
+    import json
+    import torch
+    from owl_engine_b200.forge import awq as forge
+    from owl_engine_b200.formats import awq as A
+    from owl_engine_b200.formats import safetensors as ST
+
+    g = torch.Generator().manual_seed(0)
+    src = tmp_path / "src"; src.mkdir()
+    w = (torch.randn(64, 128, generator=g) * 0.05)
+    dense = {"model.layers.0.mlp.down_proj.weight": w.to(torch.bfloat16),
+             "model.layers.0.input_layernorm.weight": torch.ones(128, dtype=torch.bfloat16),
+             "lm_head.weight": torch.randn(32, 128, generator=g).to(torch.bfloat16)}
+    ST.save_file(dense, src / "model.safetensors")
+    (src / "config.json").write_text(json.dumps({"hidden_size": 128}))
+    rep = forge.convert(src, tmp_path / "rtn", group=32)
+    assert rep["quantized"] == 1 and rep["bytes_after"] < rep["bytes_before"]
+    out = ST.SafeDir(tmp_path / "rtn")
+    assert "lm_head.weight" in out and "model.layers.0.mlp.down_proj.weight_packed" in out
+    c = A.from_compressed_tensors(out, "model.layers.0.mlp.down_proj")
+    err = (c.dequant() - w.to(torch.bfloat16).float()).abs().max() / w.abs().max()
+    assert err < 0.08
+    assert json.loads((tmp_path / "rtn" / "config.json").read_text())["quantization_config"]["config_groups"]["group_0"]["weights"]["group_size"] == 32
+    # activation-aware mode: channels with large activations get finer resolution -> lower output error
+    x = torch.randn(256, 128, generator=g)
+    x[:, :8] *= 30.0
+    forge.convert(src, tmp_path / "awq", group=32, mode="awq", calib={"model.layers.0.mlp.down_proj": x})
+    o2 = ST.SafeDir(tmp_path / "awq")
+    c2 = A.from_compressed_tensors(o2, "model.layers.0.mlp.down_proj")
+    sinv = o2.get("model.layers.0.mlp.down_proj.input_scale_inv").float()
+    ref = x @ w.to(torch.bfloat16).float().t()
+    e_rtn = (x @ c.dequant().t() - ref).pow(2).mean()
+    e_awq = ((x * sinv) @ c2.dequant().t() - ref).pow(2).mean()
+    assert e_awq <= e_rtn * 1.02

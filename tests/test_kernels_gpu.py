@@ -364,3 +364,10 @@ def test_topk_with_repetition_penalty(m, v, k):
         assert (idx.cpu()[:, kk:] == -1).all()
     mv, mi = K.topk_merge(torch.cat([val, val - 1], 1).contiguous(), torch.cat([idx, idx], 1).contiguous(), kk)
     torch.testing.assert_close(mv.cpu(), want_v[:, :kk], rtol=0, atol=0)
+
+
+def test_boot_selfcheck_passes():
+    from owl_engine_b200.ops import selfcheck
+
+    res = selfcheck.run_all(DEV)
+    assert all(ok for _, ok, _ in res), res

@@ -1,0 +1,69 @@
+"""NVFP4 and GGUF device kernels against the host codecs."""
+import numpy as np
+import pytest
+import torch
+
+from owl_engine_b200.formats import gguf as G
+from owl_engine_b200.formats import nvfp4 as NV
+from owl_engine_b200.ops import kernels as K
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def gen(seed=0):
+    return torch.Generator().manual_seed(seed)
+
+
+@pytest.mark.parametrize("m", [1, 3, 8])
+def test_nvfp4_gemv_dequant_and_act_quant(m):
+    n, k = 200, 512
+    w = torch.randn(n, k, generator=gen(1)) * 0.05
+    q = NV.quantize(w)
+    ref = NV.dequantize(q)
+    codes, sf = q.codes.to(DEV), q.scales.to(DEV)
+    deq = K.nvfp4_dequant(codes, sf, q.global_scale)
+    torch.testing.assert_close(deq.float().cpu(), ref, rtol=1e-2, atol=1e-4)
+    x = torch.randn(m, k, generator=gen(2)).to(torch.bfloat16)
+    out = torch.zeros(m, n, dtype=torch.bfloat16, device=DEV)
+    K.nvfp4_gemv(codes, sf, q.global_scale, x.to(DEV), out, m)
+    want = x.float() @ ref.t()
+    torch.testing.assert_close(out.float().cpu(), want, rtol=2e-2, atol=2e-2 * want.abs().max().item())
+    # activation quantisation: same format, the dequantised result matches the host quantiser's
+    a = NV.quantize_act(x.float())
+    ac, asf = K.nvfp4_quant_act(x.to(DEV), a.global_scale)
+    got = NV.dequantize(NV.NvFp4(ac.cpu(), asf.cpu(), a.global_scale, (m, k)))
+    assert (asf.cpu() == a.scales).float().mean() > 0.99
+    torch.testing.assert_close(got, NV.dequantize(a), rtol=0, atol=0.26 * x.float().abs().max().item() / 6 * 1.01)
+    assert (ac.cpu() == a.codes).float().mean() > 0.98
+
+
+@pytest.mark.parametrize("tname", ["Q8_0", "Q4_0", "IQ4_NL", "Q4_K", "Q5_K", "Q6_K", "IQ4_XS"])
+def test_gguf_dequant_and_gemv(tname):
+    n, k = 24, 512
+    be, bb = G.BLOCK[tname]
+    rng = np.random.default_rng(3)
+    raw = rng.integers(0, 256, size=(n * k // be, bb), dtype=np.uint8)
+    # keep the fp16 scale fields finite and moderate
+    def set_f16(col, lo=0.001, hi=0.02):
+        raw[:, col:col + 2] = rng.uniform(lo, hi, size=(raw.shape[0],)).astype(np.float16).view(np.uint8).reshape(-1, 2)
+    if tname in ("Q8_0", "Q4_0", "IQ4_NL", "IQ4_XS"):
+        set_f16(0)
+    elif tname in ("Q4_K", "Q5_K"):
+        set_f16(0); set_f16(2)
+    else:
+        set_f16(208)
+    want = torch.from_numpy(G.dequantize(raw.reshape(-1), tname, n * k)).view(n, k)
+    blocks = torch.from_numpy(raw.reshape(-1)).to(DEV)
+    tid = G.TYPE_ID[tname]
+    got = K.gguf_dequant(blocks, tid, k, n)
+    torch.testing.assert_close(got.float().cpu(), want, rtol=1e-2, atol=1e-3 * want.abs().max().item())
+    rows = torch.tensor([5, 0, 23], dtype=torch.int32, device=DEV)
+    torch.testing.assert_close(K.gguf_dequant(blocks, tid, k, n, rows=rows).float().cpu(), want[[5, 0, 23]], rtol=1e-2,
+                               atol=1e-3 * want.abs().max().item())
+    m = 3
+    x = torch.randn(m, k, generator=gen(4)).to(torch.bfloat16)
+    out = torch.zeros(m, n, dtype=torch.bfloat16, device=DEV)
+    K.gguf_gemv(blocks, tid, n, k, x.to(DEV), out, m)
+    ref = x.float() @ want.t()
+    torch.testing.assert_close(out.float().cpu(), ref, rtol=2e-2, atol=2e-2 * ref.abs().max().item())

@@ -85,3 +85,42 @@ def test_testkit():
     assert r1.next_u64() == r2.next_u64() and 0 <= r1.uniform() < 1
     rep = testkit.allclose(torch.tensor([1.0, 2.0]), torch.tensor([1.0, 2.1]), rtol=1e-3)
     assert not rep.ok and rep.worst_index == (1,) and "MISMATCH" in str(rep)
+
+
+def test_kernel_registry_matches_sources_and_bindings():
+    from owl_engine_b200.ops import registry as R
+
+    assert R.cross_check() == []
+    assert {k.entry for k in R.admit("gemm")} == {"owl_w4a16_gemm_tc", "owl_f16_gemm_tc"}
+    assert all("tcgen05" in k.gen for k in R.admit("gemm"))
+
+
+def test_cpu_face_ledger_limits_and_capture_gate():
+    import pytest
+    import torch
+    from owl_engine_b200.utils.cpuface import (CaptureUnsupported, CaptureViolation, CpuFace, MockLimits, OutOfMemory)
+
+    dev = CpuFace(MockLimits(vram_bytes=4096, poison_uninit=True))
+    a = dev.alloc((256,), owner="engine", klass="kv")          # 1 KiB
+    b = dev.alloc((256,), owner="engine", klass="state")
+    assert torch.isnan(dev.tensor(a)).all() and dev.ledger()[("engine", "kv")] == 1024
+    with pytest.raises(OutOfMemory):
+        dev.alloc((1024,), owner="engine", klass="kv")
+    dev.register("axpy", lambda x, y, alpha=1.0: y.add_(alpha * x))
+    dev.memset(a, 1.0); dev.memset(b, 0.0)
+    dev.graph_begin()
+    dev.launch("axpy", a, b, alpha=2.0)
+    with pytest.raises(CaptureViolation):
+        dev.free(a)
+    g = dev.graph_end()
+    dev.graph_launch(g)
+    assert torch.allclose(dev.tensor(b), torch.full((256,), 4.0))       # once at capture, once at replay
+    dev.free(a)
+    assert dev.used == 1024 and dev.peak == 2048
+    null = CpuFace(MockLimits(null_kernels=True, graph_capture=False))
+    null.register("axpy", lambda x, y, alpha=1.0: y.add_(x))
+    h = null.alloc((4,)); null.memset(h, 3.0)
+    null.launch("axpy", h, h)
+    assert null.launch_log == ["axpy"] and torch.allclose(null.tensor(h), torch.full((4,), 3.0))
+    with pytest.raises(CaptureUnsupported):
+        null.graph_begin()
