@@ -110,6 +110,8 @@ struct AttnParams {
   float* part_o;                // [groups*T][hq][splits][hd]
   float* part_ml;               // [groups*T][hq][splits][2]
   int T, hq, hkv, max_blocks, splits;
+  int per_pages;                // > 0: pages per split fixed by the caller (partitions aligned to positions, the same for
+                                //      every T); 0: the pages of the longest row divided evenly
   float scale_log2;             // softmax scale * log2(e)
 };
 
@@ -149,7 +151,7 @@ __global__ void __launch_bounds__(AT_WARPS * 32) paged_attn_kernel(AttnParams p)
     const bool row_ok = r < p.T;
     const int limit = ctx_last - (p.T - 1 - r);  // tokens visible to this row
     const int npages_all = (ctx_last + PAGE - 1) / PAGE;
-    const int per = (npages_all + p.splits - 1) / p.splits;
+    const int per = p.per_pages > 0 ? p.per_pages : (npages_all + p.splits - 1) / p.splits;
     const int pg0 = split * per, pg1 = min(npages_all, pg0 + per);
 
     // Q fragments (f16) for k-steps (blk 0..3, j 0..3): dims blk*64 + t*16 + j*4 + {0,1 | 2,3}
@@ -402,14 +404,14 @@ OWL_API int owl_qknorm_rope_insert(const void* qraw, int ldq, const void* kraw, 
 // part_o: float[groups*T*hq*splits*256], part_ml: float[groups*T*hq*splits*2].
 OWL_API int owl_paged_attn(const void* q, const void* k_pool, const void* v_pool, const void* block_table,
                            const void* bt_row, const void* ctx_len, void* part_o, void* part_ml, int groups, int T,
-                           int hq, int hkv, int hd, int max_blocks, int splits, float scale, int pdl,
+                           int hq, int hkv, int hd, int max_blocks, int splits, int per_pages, float scale, int pdl,
                            cudaStream_t st) {
   if (hd != HD || groups < 1 || T < 1 || T > 8 || hq % hkv || hq / hkv > 8 || splits < 1) return OWL_ERR_BAD_ARG;
   AttnParams p;
   p.q = (const __nv_bfloat16*)q; p.k_pool = (const uint8_t*)k_pool; p.v_pool = (const uint8_t*)v_pool;
   p.block_table = (const int*)block_table; p.bt_row = (const int*)bt_row; p.ctx_len = (const int*)ctx_len;
   p.part_o = (float*)part_o; p.part_ml = (float*)part_ml; p.T = T; p.hq = hq; p.hkv = hkv;
-  p.max_blocks = max_blocks; p.splits = splits; p.scale_log2 = scale * 1.4426950408889634f;
+  p.max_blocks = max_blocks; p.splits = splits; p.per_pages = per_pages; p.scale_log2 = scale * 1.4426950408889634f;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(splits, hkv, groups); cfg.blockDim = dim3(AT_WARPS * 32); cfg.stream = st;
   cudaLaunchAttribute attr[1];
@@ -417,7 +419,9 @@ OWL_API int owl_paged_attn(const void* q, const void* k_pool, const void* v_pool
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
   cudaError_t e;
-  if (T == 1) e = cudaLaunchKernelEx(&cfg, paged_attn_kernel<1>, p);
+  // per_pages > 0 asks for arithmetic that does not depend on T: one warp per row (no token split inside a CTA)
+  if (per_pages > 0) e = cudaLaunchKernelEx(&cfg, paged_attn_kernel<4>, p);
+  else if (T == 1) e = cudaLaunchKernelEx(&cfg, paged_attn_kernel<1>, p);
   else if (T == 2) e = cudaLaunchKernelEx(&cfg, paged_attn_kernel<2>, p);
   else e = cudaLaunchKernelEx(&cfg, paged_attn_kernel<4>, p);
   if (e != cudaSuccess) return (int)OWL_ERR_LAUNCH * 1000 - (int)e;

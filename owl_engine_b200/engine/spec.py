@@ -169,6 +169,10 @@ class SpecRunner:
         self._cool = 0
 
     def after_prefill(self, engine: Engine, sid: int) -> None:
+        if not engine.runner.uniform_rows:
+            # from here on every step of this engine (plain or verify) uses row-count-independent arithmetic
+            engine.runner.uniform_rows = True
+            engine.runner.graphs.clear()
         if hasattr(self.draft, "after_prefill"):
             self.draft.after_prefill(engine, sid)
 
@@ -236,6 +240,7 @@ def verify_step(engine: Engine, sid: int, rows: list[int]) -> list[int]:
     engine._ensure_pages(seq, pos + t + 1)
     if r.gdn_save is None:
         r.enable_gdn_save()
+        r.uniform_rows = True
         r.capture_fold(1)          # allocates fold_slot
     engine.pool.copy_slot(seq.slot, engine.spec_row)
     lay = H.StepLayout(1, t)

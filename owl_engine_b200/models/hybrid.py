@@ -317,6 +317,9 @@ class HybridRunner:
         self._pf = None   # lazily allocated prefill workspace
         self.taps: dict | None = None   # layer -> bf16 [M,H] buffers filled during decode/prefill for draft heads
         self.pre_hook = None            # callable(m): rewrites self.h after the embedding (draft heads mix in the target's hidden)
+        self.uniform_rows = False       # per-row arithmetic independent of the number of rows in the step (speculative
+                                        # verify must reproduce plain decoding bit for bit): one GEMV arm for 1..8 rows,
+                                        # KV splits aligned to positions instead of to the row's length
         self.gdn_save = None            # (qkvz [n_gdn, M, nq], ab [n_gdn, M, ldab]): GDN inputs of the last step, kept for fold()
 
     # -- step inputs -------------------------------------------------------------------------
@@ -334,7 +337,8 @@ class HybridRunner:
     def _gemv(self, w, xp, xs, out, m: int, *, residual=None, epi: int = K.EPI_STORE, ldo=None, pdl: bool = False) -> None:
         """out[m] = W x on the weight-streaming kernel that matches the weight's record layout."""
         if w.layout != "block":
-            K.w4a16_skinny(w, xp, xs, out, m, residual=residual, epi=epi, ldo=ldo, pdl=pdl)
+            K.w4a16_skinny(w, xp, xs, out, m, residual=residual, epi=epi, ldo=ldo, pdl=pdl,
+                           force_mma=self.uniform_rows and m == 1)
             return
         tb = K.act_tile_bytes(w.k, w.group)
         for r0 in range(0, m, 8):       # 8 tokens per pass (one activation tile buffer each)
@@ -400,7 +404,7 @@ class HybridRunner:
         want = max(1, (2 * 148) // max(1, b * self.spec.hkv))
         return max(1, min(self.max_splits, want, (pages + 3) // 4))
 
-    def _full(self, lw: LayerWeights, li: int, lay: StepLayout, v: dict, splits: int) -> None:
+    def _full(self, lw: LayerWeights, li: int, lay: StepLayout, v: dict, splits: int, ctx_hint: int = 0) -> None:
         sp, m = self.spec, lay.m
         self._gemv(lw.qkv, self.xp_h, self.xs_h, self.qkv_out, m, pdl=self.pdl)
         qn = 2 * sp.hq * sp.hd
@@ -412,7 +416,8 @@ class HybridRunner:
                              pdl=self.pdl)
         K.paged_attn(self.q_rope, self.pool.k_pool[li], self.pool.v_pool[li], self.block_table, v["bt_row"], v["ctx"],
                      self.part_o, self.part_ml, lay.b, lay.t, sp.hq, sp.hkv, sp.hd, self.max_blocks, splits, self.scale,
-                     pdl=self.pdl)
+                     pdl=self.pdl,
+                     per_pages=((ctx_hint + PAGE - 1) // PAGE + splits - 1) // splits if self.uniform_rows and ctx_hint else 0)
         K.attn_reduce(self.part_o, self.part_ml, splits, self.qkv_out, self.qkv_n, m, sp.hq, xpack=self.xp_a,
                       xs=self.xs_a, group=self._grp(), pdl=self.pdl)
         self._row_parallel(0, lw.o_proj, self.xp_a, self.xs_a, m, lw.ln2, want_xn=False)
@@ -450,7 +455,7 @@ class HybridRunner:
                 self._gdn(lw, gi, lay, v)
                 gi += 1
             else:
-                self._full(lw, fi, lay, v, splits)
+                self._full(lw, fi, lay, v, splits, ctx_hint)
                 fi += 1
             last = i + 1 == len(layers)
             nxt_w = self.w.final_norm if last else layers[i + 1].ln1
@@ -510,7 +515,7 @@ class HybridRunner:
 
     def capture(self, b: int, t: int = 1, *, ctx_hint: int = 2048, advance: bool = False, sample: bool = True):
         """Capture (once) and return the CUDA graph of a (b, t) step."""
-        key = (b, t, self._pick_splits(b, ctx_hint), advance, sample)
+        key = (b, t, self._pick_splits(b, ctx_hint), advance, sample, ctx_hint if self.uniform_rows else 0)
         g = self.graphs.get(key)
         if g is not None:
             return g

@@ -33,7 +33,7 @@ _SIGS = {
     "owl_gdn_scan": [_P, _P, _I, _P, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _F, _I, _P],
     "owl_qknorm_rope_insert": [_P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F,
                                _F, _I, _P],
-    "owl_paged_attn": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+    "owl_paged_attn": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "owl_decode_advance": [_P, _P, _P, _I, _I, _I, _P],
     "owl_w4_dequant": [_P, _P, _I, _I, _I, _I, _P],
     "owl_attn_reduce": [_P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _P],
@@ -213,9 +213,10 @@ def qknorm_rope_insert(qraw, ldq: int, kraw, ldk: int, vraw, ldv: int, qnorm_w, 
 
 
 def paged_attn(q, k_pool, v_pool, block_table, bt_row, ctx_len, part_o, part_ml, groups: int, t: int, hq: int,
-               hkv: int, hd: int, max_blocks: int, splits: int, scale: float, pdl: bool = False) -> None:
+               hkv: int, hd: int, max_blocks: int, splits: int, scale: float, pdl: bool = False, per_pages: int = 0) -> None:
+    """``per_pages`` > 0 fixes the pages per KV split (must satisfy splits * per_pages >= pages of the longest row)."""
     call("owl_paged_attn", ptr(q), ptr(k_pool), ptr(v_pool), ptr(block_table), ptr(bt_row), ptr(ctx_len), ptr(part_o),
-         ptr(part_ml), groups, t, hq, hkv, hd, max_blocks, splits, scale, int(pdl), stream())
+         ptr(part_ml), groups, t, hq, hkv, hd, max_blocks, splits, per_pages, scale, int(pdl), stream())
 
 
 def attn_reduce(part_o, part_ml, splits: int, qraw, ldq: int, rows: int, hq: int, *, out=None, xpack=None, xs=None,

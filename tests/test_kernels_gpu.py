@@ -362,7 +362,7 @@ def test_topk_with_repetition_penalty(m, v, k):
     assert torch.equal(torch.gather(ref, 1, idx.cpu()[:, :kk].long()), want_v)
     if kk < k:
         assert (idx.cpu()[:, kk:] == -1).all()
-    mv, mi = K.topk_merge(torch.cat([val, val - 1], 1).contiguous(), torch.cat([idx, idx], 1).contiguous(), kk)
+    mv, mi = K.topk_merge(torch.cat([val - 1000, val], 1).contiguous(), torch.cat([idx, idx], 1).contiguous(), kk)
     torch.testing.assert_close(mv.cpu(), want_v[:, :kk], rtol=0, atol=0)
 
 
