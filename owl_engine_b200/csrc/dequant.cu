@@ -9,7 +9,7 @@
 namespace owl {
 // grid (K/128, N/16), block 64: thread L handles uint4 #L of the tile (row, 4 words of 8 nibbles).
 __global__ void __launch_bounds__(64) w4_dequant_kernel(const uint8_t* __restrict__ records, __nv_bfloat16* out, int N,
-                                                        int K, int G, int layout) {
+                                                        int K, int G, int layout, int f16) {
   const int kt = blockIdx.x, nt = blockIdx.y, L = threadIdx.x;
   const int KT = K >> 7, GPT = 128 / G;
   const int half = L >> 5, g = (L & 31) >> 2, t = L & 3;
@@ -30,16 +30,18 @@ __global__ void __launch_bounds__(64) w4_dequant_kernel(const uint8_t* __restric
       const int nib = (i >> 1) + (i & 1) * 4;   // k_local i sits at nibble (i/2) + 4*(i%2)
       v[i] = ((float)((w[wi] >> (4 * nib)) & 0xF) - z) * sc;
     }
-    uint4 o = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+    uint4 o = f16 ? make_uint4(pack_f16(v[0], v[1]), pack_f16(v[2], v[3]), pack_f16(v[4], v[5]), pack_f16(v[6], v[7]))
+                  : make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
     *reinterpret_cast<uint4*>(out + (size_t)row * K + kt * 128 + wi * 32 + t * 8) = o;
   }
 }
 }  // namespace owl
 using namespace owl;
 
-OWL_API int owl_w4_dequant(const void* records, void* out, int N, int K, int G, int layout, cudaStream_t st) {
+// out: bf16 (f16 = 0) or fp16 (f16 = 1) [N][K].
+OWL_API int owl_w4_dequant(const void* records, void* out, int N, int K, int G, int layout, int f16, cudaStream_t st) {
   if ((N & 15) || (K & 127) || (G != 32 && G != 128)) return OWL_ERR_BAD_ARG;
-  w4_dequant_kernel<<<dim3(K / 128, N / 16), 64, 0, st>>>((const uint8_t*)records, (__nv_bfloat16*)out, N, K, G, layout);
+  w4_dequant_kernel<<<dim3(K / 128, N / 16), 64, 0, st>>>((const uint8_t*)records, (__nv_bfloat16*)out, N, K, G, layout, f16);
   OWL_LAUNCH_CHECK();
   return OWL_OK;
 }

@@ -402,6 +402,133 @@ __global__ void __launch_bounds__(256) gdn_scan_kernel(GdnScanParams p) {
     *reinterpret_cast<float4*>(sp + (size_t)i * GD) = make_float4(S[i][0], S[i][1], S[i][2], S[i][3]);
 }
 
+// ---------------------------------------------------------------------------------------
+// Column-split scan: the delta rule never mixes the columns (v dimension) of the state, so a head is
+// cut into GS2_CS column slices with one CTA each (nv * GS2_CS CTAs instead of nv). Warp w owns 16 state
+// rows, lane one column: 16 state registers per thread. Token inputs arrive in chunks of GS2_CH tokens
+// through a three-deep cp.async ring, q.k is precomputed per chunk, and one __syncthreads per token
+// separates the partial row sums from their use. Raw outputs go to a fp32 scratch; the gated RMSNorm
+// over the head's 128 columns is a second, elementwise kernel.
+// ---------------------------------------------------------------------------------------
+constexpr int GS2_CS = 4, GS2_COLS = GD / GS2_CS, GS2_CH = 16, GS2_RING = 3;
+struct GdnScan2Smem {
+  __nv_bfloat16 q[GS2_RING][GS2_CH][GD];
+  __nv_bfloat16 k[GS2_RING][GS2_CH][GD];
+  __nv_bfloat16 v[GS2_RING][GS2_CH][GS2_COLS];
+  float scal[GS2_RING][GS2_CH][4];      // e^g, beta, q.k
+  float part[2][2][8][GS2_COLS];
+};
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(src) : "memory");
+}
+__global__ void __launch_bounds__(256) gdn_scan2_kernel(GdnScanParams p, float* raw) {
+  __shared__ __align__(16) GdnScan2Smem sm;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int h = blockIdx.x, cs = blockIdx.y, R = p.nv / p.nk, hk = h / R;
+  const int K = p.nk * GD, V = p.nv * GD, conv_dim = 2 * K + V;
+  const int col = cs * GS2_COLS + lane;
+  float S[16];
+  float* sp = p.state + (((size_t)p.slot * p.nv + h) * GD + warp * 16) * GD + col;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) S[i] = p.use_state ? sp[(size_t)i * GD] : 0.f;
+  const float a_log = p.a_log[h], dt_bias = p.dt_bias[h];
+  const float scale = rsqrtf((float)GD);
+  const int nchunks = (p.T + GS2_CH - 1) / GS2_CH;
+  // one chunk = 16 tokens x (16 + 16 + 4) 16-byte pieces
+  auto issue = [&](int c) {
+    if (c < nchunks) {
+      const int buf = c % GS2_RING, r0 = c * GS2_CH;
+      for (int i = tid; i < GS2_CH * 36; i += 256) {
+        const int t = i / 36, piece = i % 36, r = r0 + t;
+        if (r < p.T) {
+          const __nv_bfloat16* xr = p.qkv + (size_t)r * conv_dim;
+          if (piece < 16) cp_async16(&sm.q[buf][t][piece * 8], xr + hk * GD + piece * 8);
+          else if (piece < 32) cp_async16(&sm.k[buf][t][(piece - 16) * 8], xr + K + hk * GD + (piece - 16) * 8);
+          else cp_async16(&sm.v[buf][t][(piece - 32) * 8], xr + 2 * K + h * GD + cs * GS2_COLS + (piece - 32) * 8);
+        }
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  issue(0);
+  issue(1);
+  for (int c = 0; c < nchunks; ++c) {
+    const int buf = c % GS2_RING, r0 = c * GS2_CH, nt = min(GS2_CH, p.T - r0);
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
+    __syncthreads();                    // chunk c landed for every thread; chunk c-1 fully consumed
+    issue(c + 2);
+    // per-token scalars of the chunk: warp w handles tokens 2w, 2w+1
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int t = warp * 2 + u;
+      if (t < nt) {
+        float pq = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) pq += __bfloat162float(sm.q[buf][t][lane * 4 + i]) * __bfloat162float(sm.k[buf][t][lane * 4 + i]);
+        const float qk = warp_sum(pq);
+        if (lane == 0) {
+          const float a = __bfloat162float(p.ab[(size_t)(r0 + t) * p.ldab + h]);
+          const float bb = __bfloat162float(p.ab[(size_t)(r0 + t) * p.ldab + p.nv + h]);
+          sm.scal[buf][t][0] = __expf(-__expf(a_log) * softplus_f(a + dt_bias));
+          sm.scal[buf][t][1] = sigmoid_f(bb);
+          sm.scal[buf][t][2] = qk;
+        }
+      }
+    }
+    __syncthreads();
+    for (int t = 0; t < nt; ++t) {
+      const int pb = t & 1;
+      float kk[16], kS = 0.f, qS = 0.f;
+      const uint4* kp = reinterpret_cast<const uint4*>(&sm.k[buf][t][warp * 16]);
+      const uint4* qp = reinterpret_cast<const uint4*>(&sm.q[buf][t][warp * 16]);
+      const uint4 k0 = kp[0], k1 = kp[1], q0 = qp[0], q1 = qp[1];
+      const uint32_t kw[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
+      const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        kk[2 * i] = bf16_lo(kw[i]); kk[2 * i + 1] = bf16_hi(kw[i]);
+        kS += kk[2 * i] * S[2 * i] + kk[2 * i + 1] * S[2 * i + 1];
+        qS += bf16_lo(qw[i]) * S[2 * i] + bf16_hi(qw[i]) * S[2 * i + 1];
+      }
+      sm.part[pb][0][warp][lane] = kS;
+      sm.part[pb][1][warp][lane] = qS;
+      __syncthreads();
+      float ksum = 0.f, qsum = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) { ksum += sm.part[pb][0][w][lane]; qsum += sm.part[pb][1][w][lane]; }
+      const float eg = sm.scal[buf][t][0], beta = sm.scal[buf][t][1], qk = sm.scal[buf][t][2];
+      const float delta = beta * (__bfloat162float(sm.v[buf][t][lane]) - eg * ksum);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) S[i] = eg * S[i] + kk[i] * delta;
+      if (warp == (t & 7)) raw[(size_t)(r0 + t) * V + h * GD + col] = scale * (eg * qsum + qk * delta);
+    }
+  }
+  asm volatile("cp.async.wait_all;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) sp[(size_t)i * GD] = S[i];
+}
+
+// out[r][h] = rmsnorm(raw[r][h]) * gamma * silu(z): one warp per (token, head)
+__global__ void __launch_bounds__(256) gdn_norm_gate_kernel(const float* __restrict__ raw, const __nv_bfloat16* __restrict__ z,
+                                                            int ldz, const float* __restrict__ gamma, __nv_bfloat16* out,
+                                                            int T, int nv, float eps, int out_f16) {
+  const int lane = threadIdx.x & 31;
+  const long long wid = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (wid >= (long long)T * nv) return;
+  const int r = (int)(wid / nv), h = (int)(wid % nv), V = nv * GD;
+  const float4 o = *reinterpret_cast<const float4*>(raw + (size_t)r * V + h * GD + lane * 4);
+  const float ss = warp_sum(o.x * o.x + o.y * o.y + o.z * o.z + o.w * o.w);
+  const float rinv = rsqrtf(ss / (float)GD + eps);
+  const uint2 zu = *reinterpret_cast<const uint2*>(z + (size_t)r * ldz + h * GD + lane * 4);
+  const float zz[4] = {bf16_lo(zu.x), bf16_hi(zu.x), bf16_lo(zu.y), bf16_hi(zu.y)};
+  const float ov[4] = {o.x, o.y, o.z, o.w};
+  float y[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) y[j] = ov[j] * rinv * gamma[lane * 4 + j] * silu_f(zz[j]);
+  *reinterpret_cast<uint2*>(out + (size_t)r * V + h * GD + lane * 4) =
+      out_f16 ? make_uint2(pack_f16(y[0], y[1]), pack_f16(y[2], y[3])) : make_uint2(pack_bf16(y[0], y[1]), pack_bf16(y[2], y[3]));
+}
+
 }  // namespace owl
 using namespace owl;
 
@@ -463,6 +590,26 @@ OWL_API int owl_gdn_scan(const void* qkv, const void* z, int ldz, const void* ab
   p.state = (float*)state; p.out = (__nv_bfloat16*)out; p.ldz = ldz; p.ldab = ldab; p.nk = nk; p.nv = nv; p.T = T;
   p.slot = slot; p.use_state = use_state; p.eps = eps; p.out_f16 = out_f16;
   gdn_scan_kernel<<<nv, 256, 0, st>>>(p);
+  OWL_LAUNCH_CHECK();
+  return OWL_OK;
+}
+
+// Same contract as owl_gdn_scan with a caller-provided fp32 scratch of T * nv * 128 floats: the column-split
+// scan (4 CTAs per head) followed by the gated RMSNorm kernel. conv_dim must be a multiple of 8 elements.
+OWL_API int owl_gdn_scan_split(const void* qkv, const void* z, int ldz, const void* ab, int ldab, const void* a_log,
+                               const void* dt_bias, const void* gamma, void* state, int slot, void* out, void* scratch,
+                               int T, int nk, int nv, int use_state, float eps, int out_f16, cudaStream_t st) {
+  if (T < 1 || nk < 1 || nv % nk || (ldz & 3) || !scratch) return OWL_ERR_BAD_ARG;
+  GdnScanParams p;
+  p.qkv = (const __nv_bfloat16*)qkv; p.z = (const __nv_bfloat16*)z; p.ab = (const __nv_bfloat16*)ab;
+  p.a_log = (const float*)a_log; p.dt_bias = (const float*)dt_bias; p.gamma = (const float*)gamma;
+  p.state = (float*)state; p.out = (__nv_bfloat16*)out; p.ldz = ldz; p.ldab = ldab; p.nk = nk; p.nv = nv; p.T = T;
+  p.slot = slot; p.use_state = use_state; p.eps = eps; p.out_f16 = out_f16;
+  gdn_scan2_kernel<<<dim3(nv, GS2_CS), 256, 0, st>>>(p, (float*)scratch);
+  OWL_LAUNCH_CHECK();
+  const long long warps = (long long)T * nv;
+  gdn_norm_gate_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, st>>>((const float*)scratch, (const __nv_bfloat16*)z, ldz,
+                                                                   (const float*)gamma, (__nv_bfloat16*)out, T, nv, eps, out_f16);
   OWL_LAUNCH_CHECK();
   return OWL_OK;
 }

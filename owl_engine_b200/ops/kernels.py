@@ -35,7 +35,7 @@ _SIGS = {
                                _F, _I, _P],
     "owl_paged_attn": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "owl_decode_advance": [_P, _P, _P, _I, _I, _I, _P],
-    "owl_w4_dequant": [_P, _P, _I, _I, _I, _I, _P],
+    "owl_w4_dequant": [_P, _P, _I, _I, _I, _I, _I, _P],
     "owl_attn_reduce": [_P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _P],
 }
 _bound: dict = {}
@@ -198,10 +198,28 @@ def gdn_conv_fwd(x, ld: int, conv_w, conv_state, slot: int, out, t: int, nk: int
          stream())
 
 
+register("owl_gdn_scan_split", [_P, _P, _I, _P, _I, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _F, _I, _P])
+_scan_scratch: dict = {}
+GDN_SPLIT_FROM = 32      # tokens from which the column-split scan (4 CTAs per head + norm kernel) is used
+
+
 def gdn_scan(qkv, z, ldz: int, ab, ldab: int, a_log, dt_bias, gamma, state, slot: int, out, t: int, nk: int, nv: int,
-             use_state: bool, eps: float = 1e-6) -> None:
-    call("owl_gdn_scan", ptr(qkv), ptr(z), ldz, ptr(ab), ldab, ptr(a_log), ptr(dt_bias), ptr(gamma), ptr(state), slot,
-         ptr(out), t, nk, nv, int(use_state), eps, _is_f16(out), stream())
+             use_state: bool, eps: float = 1e-6, split: bool | None = None) -> None:
+    """Gated delta rule over ``t`` tokens of one sequence (prefill). Long chunks run the column-split kernel,
+    which needs a fp32 scratch of t * nv * 128 floats (cached per device)."""
+    if split is None:
+        split = t >= GDN_SPLIT_FROM
+    if not split:
+        call("owl_gdn_scan", ptr(qkv), ptr(z), ldz, ptr(ab), ldab, ptr(a_log), ptr(dt_bias), ptr(gamma), ptr(state), slot,
+             ptr(out), t, nk, nv, int(use_state), eps, _is_f16(out), stream())
+        return
+    key = str(qkv.device)
+    buf = _scan_scratch.get(key)
+    if buf is None or buf.numel() < t * nv * 128:
+        buf = torch.empty(t * nv * 128, dtype=torch.float32, device=qkv.device)
+        _scan_scratch[key] = buf
+    call("owl_gdn_scan_split", ptr(qkv), ptr(z), ldz, ptr(ab), ldab, ptr(a_log), ptr(dt_bias), ptr(gamma), ptr(state), slot,
+         ptr(out), ptr(buf), t, nk, nv, int(use_state), eps, _is_f16(out), stream())
 
 
 def qknorm_rope_insert(qraw, ldq: int, kraw, ldk: int, vraw, ldv: int, qnorm_w, knorm_w, pos3, inv_freq, section,
@@ -299,10 +317,10 @@ def gguf_gemv(blocks, type_id: int, n: int, k: int, x, out, m: int) -> None:
 
 
 def w4_dequant(w, out=None):
-    """Dense bf16 [N, K] copy of a ``W4Skinny`` weight (baseline arm / tests)."""
+    """Dense bf16 (or fp16, by ``out.dtype``) [N, K] copy of a ``W4Skinny`` weight."""
     if out is None:
         out = torch.empty(w.n, w.k, dtype=torch.bfloat16, device=w.records.device)
-    call("owl_w4_dequant", ptr(w.records), ptr(out), w.n, w.k, w.group, w.layout_id, stream())
+    call("owl_w4_dequant", ptr(w.records), ptr(out), w.n, w.k, w.group, w.layout_id, _is_f16(out), stream())
     return out
 
 

@@ -3,8 +3,12 @@
 ``w4_gemm`` computes ``out[T, N] = x[T, K] @ dequant(w)^T`` for a ``W4Skinny`` weight with one of
 two arms:
 
-* ``"tc"``        the product path: the tcgen05 / TMEM W4A16 GEMM (``csrc/gemm_tc.cu``), weights
-                  dequantised inside the kernel;
+* ``"tc"``        the product path, both steps our own sm_100a kernels: for short chunks (fewer than
+                  ``DEQUANT_FROM`` tokens) the tcgen05 / TMEM W4A16 GEMM that dequantises inside the kernel
+                  (``csrc/gemm_tc.cu``); for long chunks the weight is dequantised ONCE into a dense
+                  scratch matrix (``csrc/dequant.cu``, runs at copy bandwidth) and the dense tcgen05 GEMM
+                  multiplies it -- the in-kernel dequantisation repeats per 128-token tile and caps
+                  the fused kernel near 300 TFLOP/s, the dense kernel runs at 750-1000;
 * ``"baseline"``  dequantise to a dense bf16 scratch matrix, then the library GEMM
                   (``torch.matmul`` = cuBLAS). This is the comparison arm, like the reference's
                   range-dequant -> cuBLAS arm (``crates/kernels/cu/gguf/gguf_smem.cu:415-552``).
@@ -16,13 +20,15 @@ import torch
 from . import kernels as K
 
 _scratch: dict = {}
+DEQUANT_FROM = 128      # tokens per chunk from which dequantise-once + dense GEMM wins
+SKINNY_UPTO = 32        # rows up to which the decode-shape weight-streaming kernel is used instead of a GEMM
 
 
-def _dense_scratch(n: int, k: int, device) -> torch.Tensor:
-    key = (str(device),)
+def _dense_scratch(n: int, k: int, device, dtype=torch.bfloat16) -> torch.Tensor:
+    key = (str(device), dtype)
     buf = _scratch.get(key)
     if buf is None or buf.numel() < n * k:
-        buf = torch.empty(n * k, dtype=torch.bfloat16, device=device)
+        buf = torch.empty(n * k, dtype=dtype, device=device)
         _scratch[key] = buf
     return buf[:n * k].view(n, k)
 
@@ -35,6 +41,18 @@ def w4_gemm(w, x: torch.Tensor, out: torch.Tensor, arm: str = "tc") -> torch.Ten
     if arm == "tc":
         from . import gemm_tc
 
+        if x.shape[0] <= SKINNY_UPTO and w.layout == "slice":
+            # a handful of rows (the tail chunk after the last block boundary): the weight-streaming kernel
+            t, k = x.shape
+            xb = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
+            xp = torch.empty(t, 2 * k, dtype=torch.uint8, device=x.device)
+            xs = torch.empty(t, k // w.group, 2, dtype=torch.float32, device=x.device)
+            K.act_pack(xb, xp, xs, t, k, w.group)
+            K.w4a16_skinny(w, xp, xs, out, t, ldo=out.stride(0))
+            return out
+        if x.shape[0] >= DEQUANT_FROM:
+            dense = K.w4_dequant(w, _dense_scratch(w.n, w.k, x.device, x.dtype))
+            return gemm_tc.f16_gemm(x, dense, out)
         return gemm_tc.w4a16_gemm(w, x, out)
     raise ValueError(f"unknown prefill GEMM arm {arm!r}")
 

@@ -63,6 +63,7 @@ _T = [
     KernelSpec("owl_gdn_decode", "gdn.cu", "gdn", gen="simt+cluster-dsmem"),
     KernelSpec("owl_gdn_conv_fwd", "gdn.cu", "gdn"),
     KernelSpec("owl_gdn_scan", "gdn.cu", "gdn"),
+    KernelSpec("owl_gdn_scan_split", "gdn.cu", "gdn", gen="simt+cp.async"),
     # attention / KV
     KernelSpec("owl_qknorm_rope_insert", "attn.cu", "attn"),
     KernelSpec("owl_paged_attn", "attn.cu", "attn", gen="mma.sync"),

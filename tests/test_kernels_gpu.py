@@ -230,7 +230,7 @@ def test_gdn_decode(nk, nv, t):
     torch.testing.assert_close(xs.cpu(), ws, rtol=1e-5, atol=1e-3)
 
 
-@pytest.mark.parametrize("t,use_state", [(70, True), (5, False), (2, True)])
+@pytest.mark.parametrize("t,use_state", [(70, True), (33, False), (5, False), (2, True)])
 def test_gdn_prefill_conv_and_scan(t, use_state):
     nk, nv = 2, 6
     s = _gdn_setup(nk, nv, t, 1, 21)
