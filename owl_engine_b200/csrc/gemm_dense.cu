@@ -1,0 +1,235 @@
+// Dense 16-bit GEMM for long prefill chunks on tcgen05 (sm_100a), persistent and epilogue-overlapped.
+//
+//   owl_f16_gemm_persist : C[T,N] = X[T,K] . W[N,K]^T     X, W both fp16 or both bf16, C bf16, fp32 accumulate
+//
+// Tile 128 (tokens) x 256 (weight rows) x 64 (k): with a 128 x 128 tile one MMA step reads as many shared-memory
+// bytes per cycle as the SM can deliver, so the tensor pipe idles half of the time; 256 weight rows per tile
+// halve the operand bytes per flop. One CTA per SM walks the tiles (weight-tile major, so the CTAs that run
+// together share a weight tile through L2 and the weight matrix is read from HBM once):
+//   warp 0      TMA producer: X tile [128 x 64] and W tile [256 x 64] per stage, 128-byte swizzle, 4 stages
+//   warp 1      MMA issuer: 4 x tcgen05.mma (M128 N256 K16) per stage into one of two TMEM accumulators
+//               (2 x 256 columns), commit -> stage free; after the last stage of a tile commit -> accumulator full
+//   warps 2-5   epilogue of the previous tile while the next tile's MMAs run: tcgen05.ld 32 columns at a
+//               time -> bf16 -> global, then accumulator free
+// Every mbarrier wait is bounded; on a timeout the CTA records an error code, the roles leave their loops,
+// copies in flight are waited for (bounded) and TMEM is freed.
+//
+// Role in the reference: the cuBLAS GEMMs of the dequant -> GEMM prefill arm (crates/kernels/src/family/cublas.rs).
+#include <cuda.h>
+#include "common.cuh"
+
+namespace owl {
+
+__device__ int g_gemm_dense_status = 0;
+
+constexpr int GD_BM = 128, GD_BN = 256, GD_BK = 64, GD_STAGES = 4;
+constexpr int GD_A_BYTES = GD_BM * GD_BK * 2, GD_B_BYTES = GD_BN * GD_BK * 2;
+constexpr int GD_STAGE_BYTES = GD_A_BYTES + GD_B_BYTES;          // 48 KB
+constexpr int GD_THREADS = 192;
+constexpr int GD_SMEM = GD_STAGES * GD_STAGE_BYTES + 1024 + 256;
+
+struct GdParams {
+  __nv_bfloat16* out;
+  int T, N, K, ldo, fmt;
+  int m_tiles, n_tiles;
+};
+struct GdCtl {
+  uint64_t full[GD_STAGES], empty[GD_STAGES], acc_full[2], acc_empty[2];
+  uint32_t tmem_base;
+  volatile int abort_flag;
+};
+
+__device__ __forceinline__ bool gd_wait(uint64_t* bar, uint32_t parity, GdCtl* c, int code) {
+  for (uint32_t i = 0; i < (1u << 22); ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 255u) == 255u && c->abort_flag) return false;
+  }
+  c->abort_flag = 1;
+  atomicCAS(&g_gemm_dense_status, 0, code);
+  return false;
+}
+
+__global__ void __launch_bounds__(GD_THREADS, 1) gemm_dense_kernel(const __grid_constant__ CUtensorMap tmA,
+                                                                   const __grid_constant__ CUtensorMap tmB, GdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  GdCtl* ctl = reinterpret_cast<GdCtl*>(base + GD_STAGES * GD_STAGE_BYTES);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int KI = p.K / GD_BK;
+  const int n_tiles_total = p.m_tiles * p.n_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < GD_STAGES; ++s) { mbar_init(&ctl->full[s], 1); mbar_init(&ctl->empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&ctl->acc_full[a], 1); mbar_init(&ctl->acc_empty[a], 4); }
+    ctl->abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(&ctl->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = ctl->tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int it = 0;                                           // stage counter across tiles
+      for (int tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x) {
+        const int m0 = (tile % p.m_tiles) * GD_BM, n0 = (tile / p.m_tiles) * GD_BN;
+        for (int k = 0; k < KI; ++k, ++it) {
+          const int s = it % GD_STAGES;
+          if (!gd_wait(&ctl->empty[s], (((uint32_t)(it / GD_STAGES)) & 1u) ^ 1u, ctl, OWL_ERR_WAIT_MMA)) goto prod_done;
+          mbar_expect_tx(&ctl->full[s], GD_STAGE_BYTES);
+          uint8_t* st = base + (size_t)s * GD_STAGE_BYTES;
+          tma_load_2d(st, &tmA, &ctl->full[s], k * GD_BK, m0);
+          tma_load_2d(st + GD_A_BYTES, &tmB, &ctl->full[s], k * GD_BK, n0);
+        }
+      }
+    prod_done:
+      if (ctl->abort_flag) {
+        for (int i = max(0, it - GD_STAGES); i < it; ++i)
+          for (uint32_t n = 0; n < 256u; ++n)
+            if (mbar_try_wait(&ctl->full[i % GD_STAGES], ((uint32_t)(i / GD_STAGES)) & 1u)) break;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_f16(GD_BM, GD_BN, p.fmt);
+      int it = 0, lt = 0;                                   // stage counter, local tile counter
+      for (int tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x, ++lt) {
+        const int ab = lt & 1;
+        if (!gd_wait(&ctl->acc_empty[ab], (((uint32_t)(lt >> 1)) & 1u) ^ 1u, ctl, OWL_ERR_WAIT_EPI)) break;
+        tc_fence_after();
+        const uint32_t td = tmem + ab * GD_BN;
+        bool ok = true;
+        for (int k = 0; k < KI; ++k, ++it) {
+          const int s = it % GD_STAGES;
+          if (!gd_wait(&ctl->full[s], ((uint32_t)(it / GD_STAGES)) & 1u, ctl, OWL_ERR_WAIT_TMA)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(base + (size_t)s * GD_STAGE_BYTES);
+          const uint64_t da = umma_desc_k128(sa), db = umma_desc_k128(sa + GD_A_BYTES);
+#pragma unroll
+          for (int k4 = 0; k4 < GD_BK / 16; ++k4)
+            tc_mma_f16(td, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2), idesc, (k > 0 || k4 > 0) ? 1u : 0u);
+          tc_commit(&ctl->empty[s]);
+        }
+        if (!ok) break;
+        tc_commit(&ctl->acc_full[ab]);
+      }
+    }
+  } else {
+    const int q4 = warp & 3;                                // TMEM lane quarter of this warp
+    int lt = 0;
+    for (int tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x, ++lt) {
+      const int ab = lt & 1;
+      const int m0 = (tile % p.m_tiles) * GD_BM, n0 = (tile / p.m_tiles) * GD_BN;
+      if (!gd_wait(&ctl->acc_full[ab], ((uint32_t)(lt >> 1)) & 1u, ctl, OWL_ERR_WAIT_MMA)) break;
+      tc_fence_after();
+      const int row = m0 + q4 * 32 + lane;
+#pragma unroll 1
+      for (int c = 0; c < GD_BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(ab * GD_BN + c * 32), r);
+        tc_wait_ld();
+        if (row < p.T) {
+          __nv_bfloat16* o = p.out + (size_t)row * p.ldo + n0 + c * 32;
+          if (n0 + c * 32 + 32 <= p.N) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 pk;
+              pk.x = pack_bf16(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+              pk.y = pack_bf16(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+              pk.z = pack_bf16(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+              pk.w = pack_bf16(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+              *reinterpret_cast<uint4*>(o + v * 8) = pk;
+            }
+          } else {
+            for (int v = 0; v < 32; ++v)
+              if (n0 + c * 32 + v < p.N) o[v] = __float2bfloat16(__uint_as_float(r[v]));
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl->acc_empty[ab]);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn2)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn2 gd_encode() {
+  static EncodeTiledFn2 fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn2>(p);
+  }
+  return fn;
+}
+static int gd_map(CUtensorMap* m, const void* ptr, int rows, int K, int ld, int fmt, int box_rows) {
+  EncodeTiledFn2 enc = gd_encode();
+  if (!enc) return OWL_ERR_LAUNCH * 1000 - 1;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {GD_BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(m, fmt ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(ptr),
+                   dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? OWL_OK : OWL_ERR_LAUNCH * 1000 - (int)r;
+}
+
+}  // namespace owl
+using namespace owl;
+
+// x: [T][ldx], w: [N][ldw], both fp16 (fmt 0) or both bf16 (fmt 1); out bf16 [T][ldo]. K multiple of 64.
+OWL_API int owl_f16_gemm_persist(const void* x, int ldx, const void* w, int ldw, void* out, int T, int N, int K, int ldo,
+                                 int fmt, cudaStream_t st) {
+  if (T < 1 || N < 1 || K < 64 || (K & 63) || (ldx & 7) || (ldw & 7) || (ldo & 7) || (fmt != 0 && fmt != 1) ||
+      (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) ||
+      (reinterpret_cast<uintptr_t>(out) & 15))
+    return OWL_ERR_BAD_ARG;
+  CUtensorMap a, b;
+  int r = gd_map(&a, x, T, K, ldx, fmt, GD_BM);
+  if (r) return r;
+  r = gd_map(&b, w, N, K, ldw, fmt, GD_BN);
+  if (r) return r;
+  GdParams p = {};
+  p.out = (__nv_bfloat16*)out; p.T = T; p.N = N; p.K = K; p.ldo = ldo; p.fmt = fmt;
+  p.m_tiles = (T + GD_BM - 1) / GD_BM; p.n_tiles = (N + GD_BN - 1) / GD_BN;
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (cudaFuncSetAttribute(gemm_dense_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GD_SMEM) != cudaSuccess) {
+      sms = 0;
+      return OWL_ERR_LAUNCH * 1000;
+    }
+  }
+  const int tiles = p.m_tiles * p.n_tiles;
+  gemm_dense_kernel<<<tiles < sms ? tiles : sms, GD_THREADS, GD_SMEM, st>>>(a, b, p);
+  OWL_LAUNCH_CHECK();
+  return OWL_OK;
+}
+
+OWL_API int owl_gemm_dense_status() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_gemm_dense_status, sizeof(int)) != cudaSuccess) return -1;
+  if (v != 0) cudaMemcpyToSymbol(g_gemm_dense_status, &zero, sizeof(int));
+  return v;
+}

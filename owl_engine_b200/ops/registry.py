@@ -42,6 +42,8 @@ _T = [
     KernelSpec("owl_w4a16_gemm_tc", "gemm_tc.cu", "gemm", gen="tcgen05+tmem+tma"),
     KernelSpec("owl_f16_gemm_tc", "gemm_tc.cu", "gemm", gen="tcgen05+tmem+tma"),
     KernelSpec("owl_gemm_status", "gemm_tc.cu", "status", capture=False),
+    KernelSpec("owl_f16_gemm_persist", "gemm_dense.cu", "gemm", gen="tcgen05+tmem+tma"),
+    KernelSpec("owl_gemm_dense_status", "gemm_dense.cu", "status", capture=False),
     KernelSpec("owl_w4_dequant", "dequant.cu", "load"),
     KernelSpec("owl_nvfp4_gemv", "lowbit.cu", "gemv"),
     KernelSpec("owl_nvfp4_dequant", "lowbit.cu", "load"),

@@ -13,8 +13,10 @@ def gen(s):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("shape", [(128, 128, 64), (300, 256, 512), (77, 384, 192), (1024, 1024, 1024)])
+@pytest.mark.parametrize("shape", [(128, 128, 64), (300, 256, 512), (77, 384, 192), (1024, 1024, 1024), (300, 1000, 320),
+                                   (2048, 2304, 512), (257, 520, 64)])
 def test_dense_gemm(dtype, shape):
+    """Shapes with t >= 256 and n >= 512 run the persistent 128 x 256 kernel (ragged edges included)."""
     t, n, k = shape
     x = (torch.randn(t, k, generator=gen(1))).to(dtype)
     w = (torch.randn(n, k, generator=gen(2)) * 0.05).to(dtype)

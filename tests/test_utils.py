@@ -91,7 +91,7 @@ def test_kernel_registry_matches_sources_and_bindings():
     from owl_engine_b200.ops import registry as R
 
     assert R.cross_check() == []
-    assert {k.entry for k in R.admit("gemm")} == {"owl_w4a16_gemm_tc", "owl_f16_gemm_tc"}
+    assert {k.entry for k in R.admit("gemm")} == {"owl_w4a16_gemm_tc", "owl_f16_gemm_tc", "owl_f16_gemm_persist"}
     assert all("tcgen05" in k.gen for k in R.admit("gemm"))
 
 
