@@ -36,7 +36,8 @@ class TurnOpts:
     stop_ids: tuple = ()
     eos_ids: tuple = ()
     session: str | None = None
-    images: list = field(default_factory=list)
+    images: list = field(default_factory=list)      # [(merged embeddings, (t, gh, gw), fingerprint)] in prompt order
+    image_pad_id: int | None = None
 
 
 @dataclass
@@ -138,7 +139,7 @@ class RunningEngine:
     # -- step executors -------------------------------------------------------------------------
     def _do_begin(self, step) -> None:
         t = self.turns[step.turns[0]]
-        t.sid = self.e.add_sequence(t.tokens)
+        t.sid = self.e.add_sequence(t.tokens, images=t.opts.images or None, image_pad_id=t.opts.image_pad_id)
         seq = self.e.seqs[t.sid]
         t.plan = self.e.prefill_plan(t.sid)
         t.state = PREFILL

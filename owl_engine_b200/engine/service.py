@@ -49,7 +49,11 @@ class EngineService:
     def _main(self) -> None:
         build, max_batch, on_full, spec_runner = self._args
         try:
-            self.re = RunningEngine(build(), max_batch, on_full, spec_runner)
+            engine = build()
+            # a callable spec_runner is a factory: draft heads need the engine (its runner, weights, pools)
+            if callable(spec_runner) and not hasattr(spec_runner, "round"):
+                spec_runner = spec_runner(engine)
+            self.re = RunningEngine(engine, max_batch, on_full, spec_runner)
         except Exception as ex:
             self.boot_error = f"boot failed: {ex!r}\n{traceback.format_exc()}"
             self.exit = ServiceExit("fatal", 1, self.boot_error)

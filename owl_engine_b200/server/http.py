@@ -33,7 +33,7 @@ REASONS = {200: "OK", 400: "Bad Request", 404: "Not Found", 405: "Method Not All
 class App:
     def __init__(self, client, tokenizer, model_name: str, template: ChatTemplate | None = None,
                  default_sampling: SamplingParams | None = None, default_max_new: int = 4096, max_new_cap: int = 32768,
-                 queue_timeout_ms: int = 30000, keepalive_ms: int = 15000, max_concurrent: int = 8):
+                 queue_timeout_ms: int = 30000, keepalive_ms: int = 15000, max_concurrent: int = 8, vision=None):
         self.client, self.tok, self.model = client, tokenizer, model_name
         self.tpl = template or ChatTemplate()
         self.default_sampling = default_sampling or SamplingParams()
@@ -42,6 +42,7 @@ class App:
         self.permits = asyncio.Semaphore(max_concurrent)
         self.session_locks: dict[str, asyncio.Lock] = {}
         self.guard = RepeatGuard()
+        self.vision = vision      # Vision (tower + image cache + pad token id) or None: image parts are then refused
         self.started = time.time()
 
     # -- plumbing -------------------------------------------------------------------------------
@@ -167,9 +168,16 @@ class App:
             kwargs.setdefault("enable_thinking", False)
         prompt = self.tpl.render(req.messages, tools=req.tools, **kwargs)
         ids = self.tok.encode(prompt)
+        images = []
+        if req.images:
+            if self.vision is None:
+                raise BadRequest("this server was started without a vision tower; image parts are not accepted")
+            loop0 = asyncio.get_running_loop()
+            ids, images = await loop0.run_in_executor(None, self.vision.expand, ids, [im["data"] for im in req.images])
         max_new = min(req.max_tokens or self.default_max_new, self.max_new_cap)
         opts = TurnOpts(max_new=max_new, ignore_eos=req.ignore_eos, sampling=req.sampling(self.default_sampling),
-                        eos_ids=tuple(self.tok.eos_ids), session=req.session, images=req.images)
+                        eos_ids=tuple(self.tok.eos_ids), session=req.session, images=images,
+                        image_pad_id=self.vision.pad_id if self.vision else None)
         lock = self.session_locks.setdefault(req.session, asyncio.Lock()) if req.session else None
         try:
             await asyncio.wait_for(self.permits.acquire(), self.queue_timeout)
@@ -237,6 +245,31 @@ class App:
             if lock:
                 lock.release()
             self.permits.release()
+
+
+class Vision:
+    """Server-side image path: decode -> vision tower (cached by content) -> expand the single image-pad token the
+    chat template wrote per image into as many pad tokens as the image has merged patches."""
+
+    def __init__(self, tower, pad_id: int, cache_cap: int = 8):
+        from ..cli import png
+        from ..models.vision import ImageCache
+
+        self.tower, self.pad_id, self.cache, self.decode = tower, pad_id, ImageCache(cache_cap), png.decode_png
+
+    def expand(self, ids: list[int], blobs: list[bytes]):
+        images, out, k = [], [], 0
+        for t in ids:
+            if t == self.pad_id and k < len(blobs):
+                emb, grid, fp = self.cache.get(self.tower, blobs[k], self.decode)
+                images.append((emb, grid, fp))
+                out.extend([self.pad_id] * emb.shape[0])
+                k += 1
+            else:
+                out.append(t)
+        if k != len(blobs):
+            raise BadRequest(f"{len(blobs)} images but {k} image placeholders in the rendered prompt")
+        return out, images
 
 
 def _vram(re) -> dict:

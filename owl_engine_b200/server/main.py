@@ -38,6 +38,10 @@ def build_engine_factory(cfg: C.OwlConfig):
                             max_seqs=max(v["store.gdn"]["gdn_slots"], v["runtime"]["max_batch"]), max_seq=v["runtime"]["max_seq"],
                             prefill_chunk=v["runtime"]["prefill_chunk"], pdl=v["kernel"]["pdl"],
                             prefill_gemm=v["kernel"]["prefill_gemm"], host_cache_mb=v["store"]["host_cache_mb"])
+        if v["kernel"]["selfcheck"]:
+            from ..ops import selfcheck
+
+            selfcheck.assert_ok(torch.device("cuda:0"))       # refuse to serve on a build whose kernels disagree with the host oracles
         if v["model"]["format"] == "random" or not v["model"]["path"]:
             return Engine(ecfg)
         from ..formats.loader import load_model
@@ -46,6 +50,33 @@ def build_engine_factory(cfg: C.OwlConfig):
                                    group=v["model"]["group"], lm_head_int8=ecfg.lm_head_int8)
         return Engine(ecfg, spec=spec, weights=weights)
     return build
+
+
+def build_spec_factory(cfg: C.OwlConfig):
+    """``[spec]`` section -> a factory ``engine -> SpecRunner`` (None when speculative decoding is off)."""
+    sp = cfg.values["spec"]
+    if sp["kind"] == "none" and not sp["lookup"]:
+        return None
+    if sp["kind"] == "dflash2":
+        raise C.ConfigError("spec.kind = \"dflash2\": this draft head is not built; use \"mtp\" or lookup drafting")
+
+    def make(engine):
+        from ..engine.spec import LookupDraft, MtpDraft, SpecRunner
+        from ..models.mtp import MtpHead
+
+        lookup = LookupDraft(sp["lookup_nmin"], sp["lookup_nmax"]) if sp["lookup"] else None
+        if sp["kind"] == "mtp":
+            weights = None
+            if sp["draft_path"]:
+                from ..formats.safetensors import SafeDir
+
+                src = SafeDir(sp["draft_path"])
+                weights = {k: src.get(k) for k in src.keys()}
+            draft = MtpDraft(MtpHead(engine.runner, weights=weights), lookup)
+        else:
+            draft = lookup
+        return SpecRunner(draft, depth=max(1, min(7, sp["depth"] or 3)))
+    return make
 
 
 def main(argv=None) -> int:
@@ -84,18 +115,36 @@ def main(argv=None) -> int:
 
     METRICS.set_level(cfg.values["probes"]["perf_level"])
     v = cfg.values
-    svc = EngineService(build_engine_factory(cfg), max_batch=v["runtime"]["max_batch"], on_full=v["runtime"]["admission_on_full"])
+    svc = EngineService(build_engine_factory(cfg), max_batch=v["runtime"]["max_batch"], on_full=v["runtime"]["admission_on_full"],
+                        spec_runner=build_spec_factory(cfg))
     client = svc.boot()
     path = v["model"]["path"]
     try:
         tok = HfTokenizer(path) if path and v["model"]["format"] != "gguf" else ByteTokenizer()
     except Exception:
         tok = ByteTokenizer()
+    vision = None
+    if v["vision"]["enabled"]:
+        import torch
+
+        from ..models.spec import PRESETS
+        from ..models.vision import VisionSpec, VisionTower
+        from .http import Vision
+
+        hidden = PRESETS[v["model"]["name"]]().hidden if v["model"]["name"] in PRESETS else 5120
+        vspec = VisionSpec(out_hidden=hidden, max_pixels=v["vision"]["max_pixels"] or VisionSpec.max_pixels)
+        vweights = None
+        if v["vision"]["path"]:
+            from ..formats.safetensors import SafeDir
+
+            src = SafeDir(v["vision"]["path"])
+            vweights = {k.removeprefix("visual.").removeprefix("model.visual."): src.get(k) for k in src.keys() if "visual" in k or "blocks." in k or "merger." in k or "patch_embed" in k or "pos_embed" in k}
+        vision = Vision(VisionTower(vspec, vweights, device="cuda:0", dtype=torch.bfloat16), getattr(tok, "image_pad_id", None) or 0)
     s = v["sampling"]
     app = App(client, tok, v["model"]["name"], ChatTemplate(v["server"]["template_path"], v["server"]["template_vars"]),
               SamplingParams(s["mode"], s["temp"], s["topk"], s["topp"], s["rep_penalty"]), v["runtime"]["default_max_new"],
               v["runtime"]["max_new_cap"], v["server"]["queue_timeout_ms"], v["server"]["keepalive_ms"],
-              max_concurrent=v["store.gdn"]["gdn_slots"])
+              max_concurrent=v["store.gdn"]["gdn_slots"], vision=vision)
     host, _, port = v["server"]["bind"].rpartition(":")
 
     async def run():
