@@ -88,7 +88,7 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (result marked invalid)")
     ap.add_argument("--gemv", default="dp4a", choices=["dp4a", "tc"],
                     help="W4 decode arm: legacy streaming kernels or the tcgen05 streaming kernel")
-    ap.add_argument("--comm", default="fused", choices=["nccl", "fused"],
+    ap.add_argument("--comm", default="fused", choices=["nccl", "fused", "push"],
                     help="TP collectives: our symmetric-memory kernels (fused) or the NCCL baseline arm")
     args = ap.parse_args()
 

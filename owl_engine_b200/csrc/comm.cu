@@ -174,6 +174,89 @@ __global__ void __launch_bounds__(1024) ar_residual_norm_kernel(ArNormParams p) 
   }
 }
 
+// Consumer of the push protocol (gemv.cu, EPI_PUSH): every rank's GEMV has written its partial sums into slot
+// [src] of THIS rank's buffer and published a sequence number; this kernel waits for the numbers (bounded), adds the
+// slots in rank order (bit-identical h on every rank), then residual + RMSNorm + ActPack as above. It touches no
+// peer memory at all.
+struct PushNormParams {
+  const __nv_bfloat16* slots;  // local [world][push_rows][H]
+  const uint32_t* flags;       // local [world]: sequence numbers published by the peers' GEMVs
+  uint32_t* counters;          // private per-row sequence counters [rows]
+  __nv_bfloat16* h; const __nv_bfloat16* w; __nv_bfloat16* normed; uint4* xpack; float2* xs;
+  int H, G, world, push_rows, one_plus_w;
+  float eps;
+  uint32_t spin_limit;
+};
+__global__ void __launch_bounds__(1024) push_residual_norm_kernel(PushNormParams p) {
+  __shared__ float red[32];
+  __shared__ uint32_t s_seq;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x;
+  if (threadIdx.x == 0) { s_seq = p.counters[row] + 1; p.counters[row] = s_seq; }
+  __syncthreads();
+  if (threadIdx.x < p.world) {
+    bool got = false;
+    for (uint32_t i = 0; i < p.spin_limit; ++i) {
+      if ((int)(ld_acquire_sys(p.flags + threadIdx.x) - s_seq) >= 0) { got = true; break; }
+      if (i > 64) __nanosleep(64);
+    }
+    if (!got) atomicCAS(&g_comm_status, 0, OWL_ERR_WAIT_PEER);
+  }
+  __syncthreads();
+  const int nchunks = p.H >> 3;
+  __nv_bfloat16* hrow = p.h + (size_t)row * p.H;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < nchunks; c += blockDim.x) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int r = 0; r < p.world; ++r) {
+      // written by peers over NVLink: read past L1 (the acquire above orders the loads after the flag)
+      const uint4 u = ld_relaxed_sys_v4(reinterpret_cast<const uint4*>(p.slots + ((size_t)r * p.push_rows + row) * p.H) + c);
+      float v[8];
+      unpack_bf16x8(u, v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += v[i];
+    }
+    const uint4 hu = reinterpret_cast<const uint4*>(hrow)[c];
+    float hv[8];
+    unpack_bf16x8(hu, hv);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      hv[i] = __bfloat162float(__float2bfloat16(hv[i] + acc[i]));
+      ss += hv[i] * hv[i];
+    }
+    reinterpret_cast<uint4*>(hrow)[c] = pack_bf16x8(hv);
+  }
+  if (!p.w) return;
+  ss = block_sum(ss, red);
+  const float rinv = rsqrtf(ss / (float)p.H + p.eps);
+  const int nround = (nchunks + 31) & ~31;
+  const int tiles = p.G & ACT_TILES, gq = p.G & ~ACT_TILES, cpg = gq >> 3;
+  for (int c = threadIdx.x; c < nround; c += blockDim.x) {
+    float v[8];
+    const bool live = c < nchunks;
+    if (live) {
+      const uint4 a = reinterpret_cast<const uint4*>(hrow)[c];
+      unpack_bf16x8(a, v);
+      const uint4 wv = reinterpret_cast<const uint4*>(p.w)[c];
+      float wf[8];
+      unpack_bf16x8(wv, wf);
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        v[i] = __bfloat162float(__float2bfloat16(v[i] * rinv * (p.one_plus_w ? 1.f + wf[i] : wf[i])));
+      if (p.normed) reinterpret_cast<uint4*>(p.normed + (size_t)row * p.H)[c] = pack_bf16x8(v);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = 0.f;
+    }
+    if (p.xpack) {
+      float sx, xsum;
+      const uint4 pk = actpack_emit(v, cpg, sx, xsum);
+      if (live) actpack_store(p.xpack, p.xs, tiles, gq, row, c, nchunks, pk, sx, xsum);
+    }
+  }
+}
+
 // In-place sum over ranks of buf (bf16, n8 chunks of 8), every rank ends with the full sum.
 // Each CTA reduces a contiguous share and writes it back to its OWN buffer only; two barriers
 // (before reading, after reading) protect the in-place update.
@@ -273,6 +356,30 @@ OWL_API int owl_ar_residual_norm(const void* const* part_ptrs, const void* mc_pa
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
   cudaError_t e = cudaLaunchKernelEx(&cfg, ar_residual_norm_kernel, p);
+  if (e != cudaSuccess) return (int)OWL_ERR_LAUNCH * 1000 - (int)e;
+  return OWL_OK;
+}
+
+// slots: this rank's [world][push_rows][H] bf16 buffer; flags: this rank's [world] sequence words of the call site;
+// counters: private uint32 [M] (zero before the first call).
+OWL_API int owl_push_residual_norm(const void* slots, const void* flags, void* counters, void* h, const void* w,
+                                   void* normed, void* xpack, void* xs, int M, int H, int G, int world, int push_rows,
+                                   float eps, int one_plus_w, unsigned spin_limit, int pdl, cudaStream_t st) {
+  if (M < 1 || M > push_rows || (H & 127) || world < 2 || world > MAX_RANKS || !actpack_group_ok(G, M)) return OWL_ERR_BAD_ARG;
+  PushNormParams p = {};
+  p.slots = (const __nv_bfloat16*)slots; p.flags = (const uint32_t*)flags; p.counters = (uint32_t*)counters;
+  p.h = (__nv_bfloat16*)h; p.w = (const __nv_bfloat16*)w; p.normed = (__nv_bfloat16*)normed; p.xpack = (uint4*)xpack;
+  p.xs = (float2*)xs; p.H = H; p.G = G; p.world = world; p.push_rows = push_rows; p.one_plus_w = one_plus_w; p.eps = eps;
+  p.spin_limit = spin_limit;
+  int threads = ((H / 8 + 31) / 32) * 32;
+  if (threads > 1024) threads = 1024;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(M); cfg.blockDim = dim3(threads); cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, push_residual_norm_kernel, p);
   if (e != cudaSuccess) return (int)OWL_ERR_LAUNCH * 1000 - (int)e;
   return OWL_OK;
 }

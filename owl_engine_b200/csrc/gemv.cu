@@ -95,7 +95,8 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint3
                ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 
-enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SILU_MUL = 2, EPI_F32 = 3, EPI_SILU_PACK = 4 };
+enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SILU_MUL = 2, EPI_F32 = 3, EPI_SILU_PACK = 4, EPI_PUSH = 5 };
+constexpr int SK_MAX_RANKS = 8;
 enum { KIND_W4_G128 = 0, KIND_W4_G32 = 1, KIND_BF16 = 2, KIND_W8 = 3 };
 
 struct SkinnyParams {
@@ -113,6 +114,15 @@ struct SkinnyParams {
   int tiles_per_cta;     // contiguous row tiles per CTA
   int gout;              // EPI_SILU_PACK: group size of the produced ActPack (32 or 128)
   int force_mma;         // tests / A-B runs: use the tensor-core arm even for one token
+  // EPI_PUSH (tensor parallel, row-parallel projection): the partial sums go straight into every rank's
+  // reduction buffer (plain peer stores over NVLink), slot [rank] of [world][push_rows][ldo] bf16, so the
+  // transfer overlaps the streaming tile by tile; the CTA that finishes last publishes one sequence number per
+  // peer and the consumer kernel (comm.cu: owl_push_residual_norm) only reads local memory.
+  __nv_bfloat16* push_dst[SK_MAX_RANKS];   // base of the buffer on each rank (peer-mapped)
+  uint32_t* push_flag[SK_MAX_RANKS];       // flag word of this call site on each rank, indexed [src rank]
+  int* push_count;                         // local: CTAs of this launch that are done (returns to zero)
+  uint32_t* push_seq;                      // local: sequence number of this call site
+  int push_rank, push_world, push_rows;
 };
 
 constexpr int SK_WARPS = 8;    // warps per CTA = K slices of the record layout
@@ -455,6 +465,10 @@ __global__ void __launch_bounds__(SK_WARPS * 32, MT == 1 ? 4 : 2) skinny_stream_
             } else if (epi == EPI_F32) {
               float* o = reinterpret_cast<float*>(p.out) + (size_t)tok * p.ldo + nt * 16 + g;
               o[0] = v_lo; o[8] = v_hi;
+            } else if (epi == EPI_PUSH) {
+              const __nv_bfloat16 a = __float2bfloat16(v_lo), b = __float2bfloat16(v_hi);
+              const size_t off = ((size_t)p.push_rank * p.push_rows + tok) * p.ldo + nt * 16 + g;
+              for (int r = 0; r < p.push_world; ++r) { p.push_dst[r][off] = a; p.push_dst[r][off + 8] = b; }
             } else {
               __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)tok * p.ldo + nt * 16 + g;
               float a = v_lo, b = v_hi;
@@ -489,6 +503,22 @@ __global__ void __launch_bounds__(SK_WARPS * 32, MT == 1 ? 4 : 2) skinny_stream_
       }
     }
     ++item;
+  }
+  if (epi == EPI_PUSH) {
+    // every thread's peer stores are ordered before the count; the last CTA of the grid tells the peers
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      if (atomicAdd(p.push_count, 1) == (int)gridDim.x - 1) {
+        *p.push_count = 0;
+        const uint32_t seq = *p.push_seq + 1;
+        *p.push_seq = seq;
+        __threadfence_system();
+        for (int r = 0; r < p.push_world; ++r)
+          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.push_flag[r] + p.push_rank), "r"(seq) : "memory");
+      }
+    }
   }
   // Dependents are released when this CTA is done streaming: releasing them earlier only parks
   // their CTAs on SM resources this kernel still needs (measured slower).
@@ -561,6 +591,27 @@ OWL_API int owl_w4a16_skinny(const void* records, const void* xpack, const void*
   p.force_mma = (tiles_per_cta < 0);
   p.tiles_per_cta = pick_tiles_per_cta(p.n_tiles, epi, tiles_per_cta < 0 ? -tiles_per_cta - 1 : tiles_per_cta);
   return group == 128 ? dispatch_mt<KIND_W4_G128>(p, epi, pdl, st) : dispatch_mt<KIND_W4_G32>(p, epi, pdl, st);
+}
+
+// Tensor-parallel variant for row-parallel projections: the partial sums are written into every rank's
+// reduction buffer instead of a local output (see EPI_PUSH). dst_ptrs / flag_ptrs: host arrays of `world`
+// peer-mapped device pointers (buffer base [world][push_rows][ldo] bf16; flag words [world] uint32 of this call
+// site); count / seq: local device words (zero before the first call).
+OWL_API int owl_w4a16_skinny_push(const void* records, const void* xpack, const void* xsums, void* const* dst_ptrs,
+                                  void* const* flag_ptrs, void* count, void* seq, int M, int N, int K, int ldo, int group,
+                                  int rank, int world, int push_rows, int force_mma, int pdl, cudaStream_t st) {
+  if (M < 1 || M > 32 || M > push_rows || (N & 15) || (K & 127) || (group != 32 && group != 128) || world < 2 ||
+      world > SK_MAX_RANKS || rank < 0 || rank >= world || !count || !seq)
+    return OWL_ERR_BAD_ARG;
+  SkinnyParams p = {};
+  p.w = (const uint8_t*)records; p.x = (const uint4*)xpack; p.xs = (const float2*)xsums;
+  p.M = M; p.N = N; p.K = K; p.ldo = ldo; p.gout = 128;
+  p.n_tiles = N / 16;
+  p.force_mma = force_mma;
+  p.tiles_per_cta = pick_tiles_per_cta(p.n_tiles, EPI_PUSH, 0);
+  for (int r = 0; r < world; ++r) { p.push_dst[r] = (__nv_bfloat16*)dst_ptrs[r]; p.push_flag[r] = (uint32_t*)flag_ptrs[r]; }
+  p.push_count = (int*)count; p.push_seq = (uint32_t*)seq; p.push_rank = rank; p.push_world = world; p.push_rows = push_rows;
+  return group == 128 ? dispatch_mt<KIND_W4_G128>(p, EPI_PUSH, pdl, st) : dispatch_mt<KIND_W4_G32>(p, EPI_PUSH, pdl, st);
 }
 
 // w: dense bf16 records [N/16][K/64][2048 B].

@@ -33,6 +33,8 @@ class EngineConfig:
     n_slots: int = 8               # GDN state rows (= concurrency ceiling, like gdn_slots)
     n_snap_rows: int = 2           # extra state rows that hold prefix-boundary snapshots
     host_cache_mb: int = 0         # pinned-host KV tier (0 = off)
+    disk_cache_mb: int = 0         # disk KV tier behind the host tier (0 = off)
+    disk_dir: str = ""             # directory of the disk tier (block files + restart index)
     max_seqs: int = 8
     max_seq: int = 8192
     prefill_chunk: int = 2048
@@ -91,7 +93,13 @@ class Engine:
         self.states = StateStore(cfg.n_slots, cfg.n_snap_rows)
         self.host = HostTier(page_bytes(self.pool), cfg.host_cache_mb << 20) if cfg.host_cache_mb else None
         self.mover = Mover(self.pool, self.host) if self.host else None
-        self.host_slot_of: dict[int, int] = {}       # chain hash -> host slot (demoted blocks)
+        self.host_slot_of: dict[int, int] = {}       # chain hash -> host slot (demoted blocks), oldest first
+        self.disk = None
+        if cfg.disk_cache_mb and cfg.disk_dir and self.host is not None:
+            from ..store.tiers import DiskTier
+
+            self.disk = DiskTier(cfg.disk_dir, page_bytes(self.pool), cfg.disk_cache_mb << 20)
+        self.spilled = self.recalled = 0
         self.free_rows = list(range(cfg.max_seqs - 1, -1, -1))
         self.seqs: dict[int, Sequence] = {}
         self._next_sid = 0
@@ -111,19 +119,44 @@ class Engine:
         got = self.kv.alloc(n)
         if got is not None:
             return got
-        demote = self.host is not None and len(self.host.free) >= n
-        pages, hashes = self.kv.evict(need_free=n, demote=demote)
-        if demote:
+        free = self.kv.stats()["free_pages"]
+        short = n - free
+        room = 0
+        if self.host is not None:
+            if len(self.host.free) < short and self.disk is not None:
+                self._spill_host(short - len(self.host.free))
+            room = min(short, len(self.host.free))
+        if room:
+            pages, hashes = self.kv.evict(need_free=free + room, demote=True)
             for pg, h in zip(pages, hashes):
                 slot = self.host.alloc()
                 self.mover.copy_out(pg, slot)
                 self.kv.set_carrier(h, 1, slot)
                 self.host_slot_of[h] = slot
             self.mover.fence()
+        if room < short:
+            self.kv.evict(need_free=n, demote=False)           # no tier left to hold them: dropped
         got = self.kv.alloc(n)
         if got is None:
             raise RuntimeError("KV pool exhausted")
         return got
+
+    def _spill_host(self, n: int) -> None:
+        """Make room in the pinned-host tier: its oldest blocks go to disk files (carrier 2); when the disk tier is
+        full too they are dropped from the prefix tree."""
+        self._mover_sync()                                 # demotions into the slots about to be read have landed
+        for h in list(self.host_slot_of)[:n]:
+            slot = self.host_slot_of.pop(h)
+            if self.disk.spill(h, 0, (), self.host.slot(slot)):
+                self.kv.set_carrier(h, 2, 0)
+                self.spilled += 1
+            else:
+                self.kv.forget(h)
+            self.host.release(slot)
+
+    def _mover_sync(self) -> None:
+        if self.mover.stream is not None:
+            self.mover.stream.synchronize()
 
     def _ensure_pages(self, seq: Sequence, n_tokens: int) -> None:
         need = (n_tokens + PAGE - 1) // PAGE
@@ -186,6 +219,17 @@ class Engine:
             for i in range(keep):                              # promote demoted blocks of the kept prefix
                 if carriers[i] != 0:
                     h = int(seq.chain[i])
+                    if self.disk is not None and h in self.disk.index and h not in self.host_slot_of:
+                        # disk -> pinned host staging slot (then host -> device below)
+                        if not self.host.free:
+                            self._spill_host(1)
+                        slot = self.host.alloc()
+                        if slot is not None:
+                            self._mover_sync()                 # no copy still reads the recycled slot
+                            self.disk.fill(h, self.host.slot(slot))
+                            self.disk.drop(h)
+                            self.host_slot_of[h] = slot
+                            self.recalled += 1
                     pg = self.kv.alloc(1)
                     if pg is None or h not in self.host_slot_of:
                         keep = i

@@ -363,6 +363,14 @@ class HybridRunner:
         if self.comm is None or sp.tp_world == 1:
             self._gemv(w, xp, xs, self.h, m, residual=self.h, epi=K.EPI_RESIDUAL, pdl=self.pdl)
             self._norm(m, next_norm, want_xn=want_xn, want_pack=want_pack)
+        elif symm is not None and getattr(self.comm, "mode", "") == "push" and w.layout == "slice" and w.n == sp.hidden:
+            # fused arm: the GEMV's epilogue writes its partial sums into every rank's slots over NVLink while the
+            # rest of the matrix is still streaming; the consumer waits for the peers' sequence numbers and reduces
+            # local memory only
+            symm.gemv_push(which, w, xp, xs, m, pdl=self.pdl, force_mma=self.uniform_rows and m == 1)
+            symm.push_residual_norm(which, self.h, m, next_norm, normed=self.xn if want_xn else None,
+                                    xpack=self.xp_h if want_pack else None, xs=self.xs_h if want_pack else None,
+                                    group=self._grp(), eps=sp.eps, pdl=self.pdl)
         elif symm is not None:
             self._gemv(w, xp, xs, symm.partial(which), m, pdl=self.pdl)
             symm.ar_residual_norm(which, self.h, m, next_norm, normed=self.xn if want_xn else None,

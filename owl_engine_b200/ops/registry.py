@@ -73,6 +73,8 @@ _T = [
     # collectives over peer memory
     KernelSpec("owl_ar_residual_norm", "comm.cu", "comm", gen="p2p+multimem"),
     KernelSpec("owl_ar_inplace", "comm.cu", "comm", gen="p2p+multimem"),
+    KernelSpec("owl_push_residual_norm", "comm.cu", "comm", gen="p2p"),
+    KernelSpec("owl_w4a16_skinny_push", "gemv.cu", "gemv", gen="dp4a+mma.sync+bulk-copy+p2p"),
     KernelSpec("owl_argmax_merge", "comm.cu", "comm", gen="p2p"),
     KernelSpec("owl_comm_wait_probe", "comm.cu", "comm", gen="p2p"),
     KernelSpec("owl_comm_status", "comm.cu", "status", capture=False),
@@ -98,6 +100,7 @@ def cross_check() -> list[str]:
     """Mismatches between the sources, this table and the ctypes signatures (empty = consistent)."""
     from . import kernels as K
     from . import gemm_tc  # noqa: F401  (registers its signatures)
+    from ..parallel import symm  # noqa: F401
 
     problems = []
     decl = declared()

@@ -4,6 +4,10 @@ Two arms, selected per call site by ``mode``:
 
 * ``"nccl"``  -- the baseline: ``torch.distributed`` all-reduce (NCCL over NVLink / NVSwitch),
   capturable in CUDA graphs, followed by a separate residual add.
+* ``"push"``  -- ``"fused"`` plus the GEMV-fused transfer for decode: the row-parallel GEMV's epilogue writes
+  its partial sums into every rank's slot buffer over NVLink (peer stores, tile by tile while the matrix
+  streams) and the consumer kernel reduces local memory only (``csrc/gemv.cu`` EPI_PUSH +
+  ``owl_push_residual_norm``);
 * ``"fused"`` -- the product path: hand-written kernels over symmetric (peer-mapped) memory
   (``parallel/symm.py`` + ``csrc/comm.cu``): one-shot all-reduce fused with the residual add for
   decode-size payloads, reduce-scatter / all-gather fused into the GEMM epilogue / prologue for
@@ -28,7 +32,7 @@ class TpComm:
         self.rank, self.world, self.device, self.mode = rank, world, device, mode
         self.group = group
         self.symm = None
-        if mode == "fused" and world > 1:
+        if mode in ("fused", "push") and world > 1:
             from .symm import SymmetricWorkspace
 
             self.symm = SymmetricWorkspace(rank, world, device, group, hidden=hidden, big_elems=big_elems,

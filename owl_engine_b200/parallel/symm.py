@@ -11,6 +11,8 @@ Workspace layout (identical on every rank, so an offset is valid on all peers):
     part_a/b   : bf16[MAX_ROWS][hidden]         partial sums of the two row-parallel call sites
     exch       : uint2[MAX_ROWS][8]             vocab-split argmax exchange
     big        : bf16[big_elems]                prefill-size all-reduce payload
+    push_a/b   : bf16[world][MAX_ROWS][hidden]  slots the peers' GEMV epilogues write their partial sums into
+    push_flags : uint32[2][8]                   sequence numbers published by the peers' GEMVs
 
 Reference counterpart: VMM peer grant + staging header (``crates/backends/cuda/src/vmm.rs``,
 ``comm/ar.rs:38-175``), generalised from 2 threads in one process to 2/4/8 processes.
@@ -27,6 +29,8 @@ from ..ops import kernels as K
 _P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 K.register("owl_ar_residual_norm", [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, ctypes.c_uint,
                                     _I, _P])
+K.register("owl_w4a16_skinny_push", [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P])
+K.register("owl_push_residual_norm", [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, ctypes.c_uint, _I, _P])
 K.register("owl_ar_inplace", [_P, _P, _P, _P, ctypes.c_longlong, _I, _I, _I, _I, ctypes.c_uint, _P])
 K.register("owl_argmax_merge", [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, ctypes.c_uint, _I, _P])
 K.register("owl_comm_wait_probe", [_P, ctypes.c_uint, ctypes.c_uint, _P, _P])
@@ -55,7 +59,10 @@ class SymmetricWorkspace:
         self.off_exch = self.off_b + MAX_ROWS * hidden * 2
         self.off_big = (self.off_exch + MAX_ROWS * 8 * 8 + 255) // 256 * 256
         self.big_elems = big_elems
-        nbytes = self.off_big + big_elems * 2
+        self.off_push = (self.off_big + big_elems * 2 + 255) // 256 * 256
+        push_bytes = world * MAX_ROWS * hidden * 2
+        self.off_pflags = self.off_push + 2 * push_bytes
+        nbytes = self.off_pflags + 2 * 8 * 4
         self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
         self.buf.zero_()
         gname = (group or dist.group.WORLD).group_name
@@ -74,6 +81,13 @@ class SymmetricWorkspace:
         self.part_a = self.buf[self.off_a:self.off_b].view(torch.bfloat16).view(MAX_ROWS, hidden)
         self.part_b = self.buf[self.off_b:self.off_exch].view(torch.bfloat16).view(MAX_ROWS, hidden)
         self.big = self.buf[self.off_big:self.off_big + big_elems * 2].view(torch.bfloat16)
+        self.push_dst = [_ptr_array([b + self.off_push + w * push_bytes for b in base]) for w in range(2)]
+        self.push_flag = [_ptr_array([b + self.off_pflags + w * 32 for b in base]) for w in range(2)]
+        self.push_slots = [self.buf[self.off_push + w * push_bytes:self.off_push + (w + 1) * push_bytes] for w in range(2)]
+        self.push_flags_local = [self.buf[self.off_pflags + w * 32:self.off_pflags + (w + 1) * 32] for w in range(2)]
+        self.push_count = torch.zeros(2, dtype=torch.int32, device=device)
+        self.push_seq = torch.zeros(2, dtype=torch.int32, device=device)
+        self.push_counters = torch.zeros(2, MAX_ROWS, dtype=torch.int32, device=device)
         self.counters = torch.zeros(FLAG_SLOTS, dtype=torch.int32, device=device)
         self.scratch = torch.empty(big_elems, dtype=torch.bfloat16, device=device)
 
@@ -84,6 +98,20 @@ class SymmetricWorkspace:
         K.call("owl_ar_residual_norm", ptrs, mc, self.flag_ptrs, K.ptr(self.counters), K.ptr(h), K.ptr(norm_w),
                K.ptr(normed), K.ptr(xpack), K.ptr(xs), m, self.hidden, group, self.rank, self.world, slot0, eps, 1,
                SPIN_LIMIT, int(pdl), K.stream())
+
+    def gemv_push(self, which: int, w, xpack, xs, m: int, *, pdl: bool = False, force_mma: bool = False) -> None:
+        """Row-parallel W4 GEMV whose epilogue writes the partial sums into every rank's slot buffer (fused
+        GEMV + all-gather of partials over NVLink); pair with ``push_residual_norm``."""
+        assert w.layout == "slice"
+        K.call("owl_w4a16_skinny_push", K.ptr(w.records), K.ptr(xpack), K.ptr(xs), self.push_dst[which], self.push_flag[which],
+               K.ptr(self.push_count[which:]), K.ptr(self.push_seq[which:]), m, w.n, w.k, self.hidden, w.group, self.rank,
+               self.world, MAX_ROWS, int(force_mma), int(pdl), K.stream())
+
+    def push_residual_norm(self, which: int, h, m: int, norm_w, *, normed=None, xpack=None, xs=None, group: int = 128,
+                           eps: float = 1e-6, pdl: bool = False) -> None:
+        K.call("owl_push_residual_norm", K.ptr(self.push_slots[which]), K.ptr(self.push_flags_local[which]),
+               K.ptr(self.push_counters[which]), K.ptr(h), K.ptr(norm_w), K.ptr(normed), K.ptr(xpack), K.ptr(xs), m,
+               self.hidden, group, self.world, MAX_ROWS, eps, 1, SPIN_LIMIT, int(pdl), K.stream())
 
     def partial(self, which: int) -> torch.Tensor:
         return self.part_a if which == 0 else self.part_b

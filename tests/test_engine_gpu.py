@@ -34,6 +34,27 @@ def test_prefix_reuse_gives_same_tokens_as_cold_run():
     assert eng.generate(base, 6) == a and eng.prefix_hits >= 2
 
 
+def test_pressure_demotes_to_host_then_disk_and_recall_gives_same_tokens(tmp_path):
+    """A pool too small for the working set: published prefixes leave for the pinned-host tier, the host tier's oldest
+    blocks leave for disk files, and a returning prompt is served from disk -> host -> device with unchanged output."""
+    eng = Engine(EngineConfig(model="test-hybrid", n_pages=20, n_slots=4, n_snap_rows=8, max_seqs=4,
+                                                  max_seq=512, prefill_chunk=64, host_cache_mb=1,
+                                                  disk_cache_mb=4, disk_dir=str(tmp_path / "kv")))
+    keep = 4
+    eng.host.free = eng.host.free[-keep:]                      # a host tier of four blocks
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, eng.spec.vocab, (100,), generator=g).tolist() for _ in range(4)]
+    first = eng.generate(prompts[0], 5)
+    for p in prompts[1:]:
+        eng.generate(p, 5)
+    assert eng.spilled > 0 and len(eng.disk.index) > 0
+    assert eng.generate(prompts[0], 5) == first
+    assert eng.recalled > 0 and eng.prefix_hits >= 1
+    cold = Engine(EngineConfig(model="test-hybrid", n_pages=128, n_slots=4, n_snap_rows=2, max_seqs=4, max_seq=512,
+                               prefill_chunk=64))
+    assert cold.generate(prompts[0], 5) == first
+
+
 def test_running_engine_batches_and_events():
     re = RunningEngine(make_engine(), max_batch=4)
     g = torch.Generator().manual_seed(1)

@@ -34,7 +34,7 @@ def _worker(rank, world, port, mode, q):
     full = make_spec(n_layers=4, vocab=512)
     dense = init_weights(full, seed=3, std=0.05)
     spec = full.sharded(rank, world)
-    hw, _ = H.weights_from_dense(spec, dense, dev, vocab_split=(mode == "fused"))
+    hw, _ = H.weights_from_dense(spec, dense, dev, vocab_split=(mode in ("fused", "push")))
     pool = H.StatePool(spec, dev, n_pages=32, n_slots=2)
     run = H.HybridRunner(spec, hw, pool, max_seqs=2, max_blocks=16, comm=comm, prefill_gemm="tc")
     run.block_table[0, :8] = torch.arange(8, dtype=torch.int32, device=dev)
@@ -79,7 +79,7 @@ def _worker(rank, world, port, mode, q):
     os._exit(0)
 
 
-@pytest.mark.parametrize("mode", ["nccl", "fused"])
+@pytest.mark.parametrize("mode", ["nccl", "fused", "push"])
 def test_tp2_matches_and_is_rank_consistent(mode):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
