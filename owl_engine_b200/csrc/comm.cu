@@ -257,6 +257,104 @@ __global__ void __launch_bounds__(1024) push_residual_norm_kernel(PushNormParams
   }
 }
 
+// Owner side of the prefill reduce-scatter and the all-gather that follows it, one CTA per token row.
+// The row-parallel GEMMs of all ranks have written their partial sums of this rank's row tiles into
+// slots[source rank] (gemm_dense.cu, owl_f16_gemm_rs). Per row: wait for the sources' flags, add the slots
+// in rank order to the residual row (kept only on the owner), RMS-normalise, and store the normalised row
+// into EVERY rank's gathered-activation buffer with plain peer stores; the CTA that completes a row tile
+// publishes the tile's sequence number on every rank, where the next column-parallel GEMM
+// (owl_f16_gemm_ag) waits for it tile by tile. n_src = 0 seeds the pipeline (no slots: the residual rows
+// already hold the embeddings); w = null ends it (residual update only).
+struct RsNormAgParams {
+  const __nv_bfloat16* slots;  // local [world][max_local * 128][H]
+  const uint32_t* rs_flags;    // local [world][max_local]
+  __nv_bfloat16* h;            // local residual rows of the owned tiles [max_local * 128][H]
+  const __nv_bfloat16* w;
+  void* xdst[MAX_RANKS];       // each rank's gathered activations [T][H], fp16 or bf16
+  uint32_t* ag_flag[MAX_RANKS];// each rank's flag table [world][max_local]
+  int* rows_done;              // local [max_local]
+  int T, H, rank, world, max_local, n_src, one_plus_w, out_f16;
+  uint32_t rs_seq, ag_seq, spin_limit;
+  float eps;
+};
+__global__ void __launch_bounds__(256) rs_norm_ag_kernel(RsNormAgParams p) {
+  __shared__ float red[32];
+  __shared__ int s_fail;
+  const int lt = blockIdx.y, j = lt * p.world + p.rank;
+  const int grow = j * 128 + blockIdx.x;                       // global token row
+  if (grow >= p.T) return;
+  const int lrow = lt * 128 + blockIdx.x;
+  if (threadIdx.x == 0) s_fail = 0;
+  __syncthreads();
+  if ((int)threadIdx.x < p.n_src) {
+    bool got = false;
+    const uint32_t* f = p.rs_flags + threadIdx.x * p.max_local + lt;
+    for (uint32_t i = 0; i < p.spin_limit; ++i) {
+      if ((int)(ld_acquire_sys(f) - p.rs_seq) >= 0) { got = true; break; }
+      if (i > 16) __nanosleep(100);
+    }
+    if (!got) { atomicCAS(&g_comm_status, 0, OWL_ERR_WAIT_PEER); s_fail = 1; }
+  }
+  __syncthreads();
+  if (s_fail) return;                                          // the gather flag is never published: peers time out too
+  const int nchunks = p.H >> 3;
+  __nv_bfloat16* hrow = p.h + (size_t)lrow * p.H;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < nchunks; c += blockDim.x) {
+    float hv[8];
+    unpack_bf16x8(reinterpret_cast<const uint4*>(hrow)[c], hv);
+    if (p.n_src) {
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int r = 0; r < p.n_src; ++r) {
+        const uint4 u = ld_relaxed_sys_v4(reinterpret_cast<const uint4*>(p.slots + ((size_t)r * p.max_local * 128 + lrow) * p.H) + c);
+        float v[8];
+        unpack_bf16x8(u, v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += v[i];
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) hv[i] = __bfloat162float(__float2bfloat16(hv[i] + acc[i]));
+      reinterpret_cast<uint4*>(hrow)[c] = pack_bf16x8(hv);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += hv[i] * hv[i];
+  }
+  if (!p.w) return;
+  ss = block_sum(ss, red);
+  const float rinv = rsqrtf(ss / (float)p.H + p.eps);
+  for (int c = threadIdx.x; c < nchunks; c += blockDim.x) {
+    float v[8], wf[8];
+    unpack_bf16x8(reinterpret_cast<const uint4*>(hrow)[c], v);
+    unpack_bf16x8(reinterpret_cast<const uint4*>(p.w)[c], wf);
+    uint4 pk;
+    if (p.out_f16) {
+      __half2 q[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        q[i] = __floats2half2_rn(v[2 * i] * rinv * (p.one_plus_w ? 1.f + wf[2 * i] : wf[2 * i]),
+                                 v[2 * i + 1] * rinv * (p.one_plus_w ? 1.f + wf[2 * i + 1] : wf[2 * i + 1]));
+      pk = *reinterpret_cast<uint4*>(q);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = v[i] * rinv * (p.one_plus_w ? 1.f + wf[i] : wf[i]);
+      pk = pack_bf16x8(v);
+    }
+    for (int d = 0; d < p.world; ++d)
+      reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.xdst[d]) + (size_t)grow * p.H)[c] = pk;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int valid = min(128, p.T - j * 128);
+    const int old = atomicAdd(p.rows_done + lt, 1);
+    if (old == valid - 1) {
+      p.rows_done[lt] = 0;
+      __threadfence_system();
+      for (int d = 0; d < p.world; ++d) st_release_sys(p.ag_flag[d] + p.rank * p.max_local + lt, p.ag_seq);
+    }
+  }
+}
+
 // In-place sum over ranks of buf (bf16, n8 chunks of 8), every rank ends with the full sum.
 // Each CTA reduces a contiguous share and writes it back to its OWN buffer only; two barriers
 // (before reading, after reading) protect the in-place update.
@@ -381,6 +479,36 @@ OWL_API int owl_push_residual_norm(const void* slots, const void* flags, void* c
   cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
   cudaError_t e = cudaLaunchKernelEx(&cfg, push_residual_norm_kernel, p);
   if (e != cudaSuccess) return (int)OWL_ERR_LAUNCH * 1000 - (int)e;
+  return OWL_OK;
+}
+
+// slots / rs_flags / h / rows_done are this rank's own memory; xdst[r] / ag_flag[r] are every rank's gathered
+// activation buffer and flag table (peer-mapped). n_src = world (after a reduce-scatter GEMM) or 0 (seed).
+OWL_API int owl_rs_norm_ag(const void* slots, const void* rs_flags, void* h, const void* w, void* const* xdst,
+                           void* const* ag_flag, void* rows_done, int T, int H, int rank, int world, int max_local, int n_src,
+                           unsigned rs_seq, unsigned ag_seq, float eps, int one_plus_w, int out_f16, unsigned spin_limit,
+                           cudaStream_t st) {
+  if (T < 1 || (H & 7) || world < 1 || world > MAX_RANKS || rank < 0 || rank >= world || max_local < 1 ||
+      (n_src != 0 && n_src != world) || (T + 127) / 128 > world * max_local || !h || !rows_done || (n_src && (!slots || !rs_flags)))
+    return OWL_ERR_BAD_ARG;
+  RsNormAgParams p = {};
+  p.slots = (const __nv_bfloat16*)slots; p.rs_flags = (const uint32_t*)rs_flags; p.h = (__nv_bfloat16*)h;
+  p.w = (const __nv_bfloat16*)w; p.rows_done = (int*)rows_done; p.T = T; p.H = H; p.rank = rank; p.world = world;
+  p.max_local = max_local; p.n_src = n_src; p.one_plus_w = one_plus_w; p.out_f16 = out_f16; p.rs_seq = rs_seq;
+  p.ag_seq = ag_seq; p.spin_limit = spin_limit; p.eps = eps;
+  if (w) {
+    if (!xdst || !ag_flag) return OWL_ERR_BAD_ARG;
+    for (int r = 0; r < world; ++r) {
+      if (!xdst[r] || !ag_flag[r] || (reinterpret_cast<uintptr_t>(xdst[r]) & 15)) return OWL_ERR_BAD_ARG;
+      p.xdst[r] = xdst[r];
+      p.ag_flag[r] = (uint32_t*)ag_flag[r];
+    }
+  }
+  const int m_tiles = (T + 127) / 128;
+  const int mine = rank < m_tiles ? (m_tiles - rank + world - 1) / world : 0;   // row tiles this rank owns
+  if (mine == 0) return OWL_OK;
+  rs_norm_ag_kernel<<<dim3(128, mine), 256, 0, st>>>(p);
+  OWL_LAUNCH_CHECK();
   return OWL_OK;
 }
 

@@ -11,6 +11,17 @@
 //               (2 x 256 columns), commit -> stage free; after the last stage of a tile commit -> accumulator full
 //   warps 2-5   epilogue of the previous tile while the next tile's MMAs run: tcgen05.ld 32 columns at a
 //               time -> bf16 -> global, then accumulator free
+// Tensor-parallel forms of the same kernel (one process per GPU, peer-mapped symmetric memory):
+//   owl_f16_gemm_ag : column-parallel GEMM whose activation rows are produced by other ranks (all-gather by
+//                     peer stores into THIS GPU's memory). The producer warp waits, per 128-row tile, for the
+//                     owner rank's sequence flag before it issues the tile's first TMA load, so the GEMM
+//                     starts on the rows that have arrived while the rest are still in flight.
+//   owl_f16_gemm_rs : row-parallel GEMM whose epilogue is the reduce-scatter: each 128-row tile of partial
+//                     sums is written from TMEM straight into the slot [source rank] of the rank that owns
+//                     the tile (plain peer stores over NVLink), and the last weight-tile of a row tile
+//                     publishes a sequence flag there. The owner sums the slots in rank order (comm.cu).
+// Row tile j is owned by rank j % world and is its local tile j / world. TMA never reads peer memory here.
+//
 // Every mbarrier wait is bounded; on a timeout the CTA records an error code, the roles leave their loops,
 // copies in flight are waited for (bounded) and TMEM is freed.
 //
@@ -32,6 +43,13 @@ struct GdParams {
   __nv_bfloat16* out;
   int T, N, K, ldo, fmt;
   int m_tiles, n_tiles;
+  // tensor-parallel forms
+  int rank, world, max_local;        // max_local: row tiles a rank can own (slot and flag table extent)
+  const uint32_t* ag_flags;          // local [world][max_local]: sequence flags of arrived activation row tiles
+  uint32_t ag_seq, rs_seq, spin_limit;
+  __nv_bfloat16* rs_dst[8];          // each rank's slot buffer [world][max_local * 128][ldo]
+  uint32_t* rs_flag[8];              // each rank's flag table [world][max_local]
+  int* rs_done;                      // local [m_tiles]: weight tiles finished per row tile
 };
 struct GdCtl {
   uint64_t full[GD_STAGES], empty[GD_STAGES], acc_full[2], acc_empty[2];
@@ -49,6 +67,16 @@ __device__ __forceinline__ bool gd_wait(uint64_t* bar, uint32_t parity, GdCtl* c
   return false;
 }
 
+__device__ __forceinline__ void gd_st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t gd_ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+template <bool AG, bool RS>
 __global__ void __launch_bounds__(GD_THREADS, 1) gemm_dense_kernel(const __grid_constant__ CUtensorMap tmA,
                                                                    const __grid_constant__ CUtensorMap tmB, GdParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -80,6 +108,23 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gemm_dense_kernel(const __grid_
       int it = 0;                                           // stage counter across tiles
       for (int tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x) {
         const int m0 = (tile % p.m_tiles) * GD_BM, n0 = (tile / p.m_tiles) * GD_BN;
+        if (AG) {
+          // the rows of this tile are written by their owner rank; its flag says they have landed
+          const int j = tile % p.m_tiles;
+          const uint32_t* f = p.ag_flags + (j % p.world) * p.max_local + j / p.world;
+          bool got = false;
+          for (uint32_t i = 0; i < p.spin_limit; ++i) {
+            if ((int)(gd_ld_acquire_sys(f) - p.ag_seq) >= 0) { got = true; break; }
+            if (i > 16) __nanosleep(100);
+            if ((i & 255u) == 255u && ctl->abort_flag) break;
+          }
+          if (!got) {
+            ctl->abort_flag = 1;
+            atomicCAS(&g_gemm_dense_status, 0, OWL_ERR_WAIT_PEER);
+            goto prod_done;
+          }
+          asm volatile("fence.proxy.async;" ::: "memory");   // peer-written rows are read by the copy engine next
+        }
         for (int k = 0; k < KI; ++k, ++it) {
           const int s = it % GD_STAGES;
           if (!gd_wait(&ctl->empty[s], (((uint32_t)(it / GD_STAGES)) & 1u) ^ 1u, ctl, OWL_ERR_WAIT_MMA)) goto prod_done;
@@ -130,13 +175,18 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gemm_dense_kernel(const __grid_
       if (!gd_wait(&ctl->acc_full[ab], ((uint32_t)(lt >> 1)) & 1u, ctl, OWL_ERR_WAIT_MMA)) break;
       tc_fence_after();
       const int row = m0 + q4 * 32 + lane;
+      __nv_bfloat16* obase = p.out + (size_t)row * p.ldo;
+      const int jt = tile % p.m_tiles;
+      if (RS)   // slot [this rank] of the owner of row tile jt, at the tile's local position
+        obase = p.rs_dst[jt % p.world] +
+                ((size_t)p.rank * p.max_local * GD_BM + (size_t)(jt / p.world) * GD_BM + q4 * 32 + lane) * p.ldo;
 #pragma unroll 1
       for (int c = 0; c < GD_BN / 32; ++c) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(tmem + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(ab * GD_BN + c * 32), r);
         tc_wait_ld();
         if (row < p.T) {
-          __nv_bfloat16* o = p.out + (size_t)row * p.ldo + n0 + c * 32;
+          __nv_bfloat16* o = obase + n0 + c * 32;
           if (n0 + c * 32 + 32 <= p.N) {
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
@@ -156,6 +206,20 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gemm_dense_kernel(const __grid_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&ctl->acc_empty[ab]);
+      if (RS) {
+        // each warp fences its peer stores and counts itself; the warp that completes a row tile (4 warps x
+        // its weight tiles, over all CTAs) publishes the sequence number at the owner
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+          const int old = atomicAdd(p.rs_done + jt, 1);
+          if (old == p.n_tiles * 4 - 1) {
+            p.rs_done[jt] = 0;
+            __threadfence_system();
+            gd_st_release_sys(p.rs_flag[jt % p.world] + p.rank * p.max_local + jt / p.world, p.rs_seq);
+          }
+        }
+      }
     }
   }
   tc_fence_before();
@@ -196,35 +260,78 @@ static int gd_map(CUtensorMap* m, const void* ptr, int rows, int K, int ld, int 
 }  // namespace owl
 using namespace owl;
 
-// x: [T][ldx], w: [N][ldw], both fp16 (fmt 0) or both bf16 (fmt 1); out bf16 [T][ldo]. K multiple of 64.
-OWL_API int owl_f16_gemm_persist(const void* x, int ldx, const void* w, int ldw, void* out, int T, int N, int K, int ldo,
-                                 int fmt, cudaStream_t st) {
-  if (T < 1 || N < 1 || K < 64 || (K & 63) || (ldx & 7) || (ldw & 7) || (ldo & 7) || (fmt != 0 && fmt != 1) ||
-      (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) ||
-      (reinterpret_cast<uintptr_t>(out) & 15))
+static int gd_launch(const void* x, int ldx, const void* w, int ldw, GdParams& p, int mode, cudaStream_t st) {
+  if (p.T < 1 || p.N < 1 || p.K < 64 || (p.K & 63) || (ldx & 7) || (ldw & 7) || (p.ldo & 7) || (p.fmt != 0 && p.fmt != 1) ||
+      (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
     return OWL_ERR_BAD_ARG;
   CUtensorMap a, b;
-  int r = gd_map(&a, x, T, K, ldx, fmt, GD_BM);
+  int r = gd_map(&a, x, p.T, p.K, ldx, p.fmt, GD_BM);
   if (r) return r;
-  r = gd_map(&b, w, N, K, ldw, fmt, GD_BN);
+  r = gd_map(&b, w, p.N, p.K, ldw, p.fmt, GD_BN);
   if (r) return r;
-  GdParams p = {};
-  p.out = (__nv_bfloat16*)out; p.T = T; p.N = N; p.K = K; p.ldo = ldo; p.fmt = fmt;
-  p.m_tiles = (T + GD_BM - 1) / GD_BM; p.n_tiles = (N + GD_BN - 1) / GD_BN;
+  p.m_tiles = (p.T + GD_BM - 1) / GD_BM; p.n_tiles = (p.N + GD_BN - 1) / GD_BN;
   static int sms = 0;
   if (!sms) {
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (cudaFuncSetAttribute(gemm_dense_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GD_SMEM) != cudaSuccess) {
+    if (cudaFuncSetAttribute(gemm_dense_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GD_SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(gemm_dense_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GD_SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(gemm_dense_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GD_SMEM) != cudaSuccess) {
       sms = 0;
       return OWL_ERR_LAUNCH * 1000;
     }
   }
   const int tiles = p.m_tiles * p.n_tiles;
-  gemm_dense_kernel<<<tiles < sms ? tiles : sms, GD_THREADS, GD_SMEM, st>>>(a, b, p);
+  const int grid = tiles < sms ? tiles : sms;
+  if (mode == 0) gemm_dense_kernel<false, false><<<grid, GD_THREADS, GD_SMEM, st>>>(a, b, p);
+  else if (mode == 1) gemm_dense_kernel<true, false><<<grid, GD_THREADS, GD_SMEM, st>>>(a, b, p);
+  else gemm_dense_kernel<false, true><<<grid, GD_THREADS, GD_SMEM, st>>>(a, b, p);
   OWL_LAUNCH_CHECK();
   return OWL_OK;
+}
+
+// x: [T][ldx], w: [N][ldw], both fp16 (fmt 0) or both bf16 (fmt 1); out bf16 [T][ldo]. K multiple of 64.
+OWL_API int owl_f16_gemm_persist(const void* x, int ldx, const void* w, int ldw, void* out, int T, int N, int K, int ldo,
+                                 int fmt, cudaStream_t st) {
+  if (reinterpret_cast<uintptr_t>(out) & 15) return OWL_ERR_BAD_ARG;
+  GdParams p = {};
+  p.out = (__nv_bfloat16*)out; p.T = T; p.N = N; p.K = K; p.ldo = ldo; p.fmt = fmt;
+  return gd_launch(x, ldx, w, ldw, p, 0, st);
+}
+
+// Column-parallel GEMM over activation rows gathered from the ranks: x is THIS rank's copy of the gathered
+// rows [T][ldx]; row tile j is valid once ag_flags[(j % world) * max_local + j / world] >= seq.
+OWL_API int owl_f16_gemm_ag(const void* x, int ldx, const void* w, int ldw, void* out, int T, int N, int K, int ldo, int fmt,
+                            const void* ag_flags, unsigned seq, int world, int max_local, unsigned spin_limit,
+                            cudaStream_t st) {
+  if ((reinterpret_cast<uintptr_t>(out) & 15) || !ag_flags || world < 1 || world > 8 || max_local < 1 ||
+      (T + GD_BM - 1) / GD_BM > world * max_local)
+    return OWL_ERR_BAD_ARG;
+  GdParams p = {};
+  p.out = (__nv_bfloat16*)out; p.T = T; p.N = N; p.K = K; p.ldo = ldo; p.fmt = fmt;
+  p.world = world; p.max_local = max_local; p.ag_flags = (const uint32_t*)ag_flags; p.ag_seq = seq; p.spin_limit = spin_limit;
+  return gd_launch(x, ldx, w, ldw, p, 1, st);
+}
+
+// Row-parallel GEMM + reduce-scatter: the partial sums of row tile j go to slot [rank] of rank j % world
+// (dst[r] = base of rank r's slot buffer [world][max_local * 128][ldo], flag[r] = base of its flag table
+// [world][max_local]); done = local int[row tiles], zero before the first call.
+OWL_API int owl_f16_gemm_rs(const void* x, int ldx, const void* w, int ldw, int T, int N, int K, int ldo, int fmt,
+                            void* const* dst, void* const* flag, void* done, unsigned seq, int rank, int world, int max_local,
+                            cudaStream_t st) {
+  if (!dst || !flag || !done || world < 1 || world > 8 || rank < 0 || rank >= world || max_local < 1 ||
+      (T + GD_BM - 1) / GD_BM > world * max_local || N > ldo)
+    return OWL_ERR_BAD_ARG;
+  GdParams p = {};
+  p.T = T; p.N = N; p.K = K; p.ldo = ldo; p.fmt = fmt;
+  p.rank = rank; p.world = world; p.max_local = max_local; p.rs_seq = seq; p.rs_done = (int*)done;
+  for (int r = 0; r < world; ++r) {
+    if (!dst[r] || !flag[r] || (reinterpret_cast<uintptr_t>(dst[r]) & 15)) return OWL_ERR_BAD_ARG;
+    p.rs_dst[r] = (__nv_bfloat16*)dst[r];
+    p.rs_flag[r] = (uint32_t*)flag[r];
+  }
+  return gd_launch(x, ldx, w, ldw, p, 2, st);
 }
 
 OWL_API int owl_gemm_dense_status() {

@@ -320,6 +320,8 @@ class HybridRunner:
         self.uniform_rows = False       # per-row arithmetic independent of the number of rows in the step (speculative
                                         # verify must reproduce plain decoding bit for bit): one GEMV arm for 1..8 rows,
                                         # KV splits aligned to positions instead of to the row's length
+        self.pf_pipe = None             # explicit prefill pipe (parallel/symm.PrefillPipe); default: the communicator's
+        self.sp_prefill = False         # tensor-parallel prefill through the GEMM-fused reduce-scatter / all-gather path
         self.gdn_save = None            # (qkvz [n_gdn, M, nq], ab [n_gdn, M, ldab]): GDN inputs of the last step, kept for fold()
 
     # -- step inputs -------------------------------------------------------------------------
@@ -588,6 +590,9 @@ class HybridRunner:
 
         sp, pool = self.spec, self.pool
         t = ids.shape[0]
+        pipe = self._pipe()
+        if pipe is not None and t >= self.SP_FROM and t <= pipe.rows and self.prefill_gemm == "tc" and self.taps is None:
+            return self._prefill_chunk_sp(pipe, ids, pos0, seq_row, gdn_slot, pos3, want_logits, embeds)
         ws = self._prefill_ws(max(t, 16))
         h, x = ws["h"][:t], ws["x"][:t]
         if pos3 is None:
@@ -663,6 +668,112 @@ class HybridRunner:
         if not want_logits:
             return None
         self.h[:1].copy_(h[t - 1:t])
+        self._norm(1, self.w.final_norm, want_xn=True, want_pack=False)
+        self._head(1, sample=True)
+        return self.out_tok[:1]
+
+    SP_FROM = 256       # tokens per chunk from which the sequence-parallel fused path is used under tensor parallelism
+
+    def _pipe(self):
+        """The prefill pipe of the tensor-parallel communicator (or one set explicitly, e.g. a world of one)."""
+        if self.pf_pipe is not None:
+            return self.pf_pipe
+        symm = getattr(self.comm, "symm", None) if self.comm is not None else None
+        if symm is None or self.spec.tp_world == 1 or not self.sp_prefill:
+            return None
+        return getattr(symm, "prefill", None)
+
+    def _prefill_chunk_sp(self, pipe, ids, pos0: int, seq_row: int, gdn_slot: int, pos3, want_logits: bool, embeds):
+        """Tensor-parallel prefill chunk with the collectives inside the GEMMs: every row-parallel projection is a
+        tcgen05 GEMM whose epilogue scatters its partial row tiles to their owner ranks over NVLink; the owner adds
+        them to its share of the residual stream, normalises and stores the result into every rank's activation buffer;
+        the next column-parallel GEMM starts on the row tiles that have arrived. The residual stream of the chunk is
+        sharded by 128-row tiles over the ranks (sequence parallel) and never gathered.
+
+        Reference counterpart: all-reduce injection after every row-parallel node followed by a separate
+        fused_add_rmsnorm launch (crates/models/src/interpreters/eval.rs:1154-1419); no GEMM / collective overlap there."""
+        from ..ops import linear
+
+        sp, pool, dev = self.spec, self.pool, self.device
+        t = ids.shape[0]
+        ws = self._prefill_ws(t)
+        xd = torch.float16
+        dense = lambda w: linear.w4_dense(w, xd, dev)
+        if pos3 is None:
+            ws["pos3"][:, :t] = torch.arange(pos0, pos0 + t, dtype=torch.int32, device=dev)[None]
+        else:
+            ws["pos3"][:, :t] = pos3
+        pos3_v = ws["pos3"][:, :t].contiguous()
+        tpos = torch.arange(pos0, pos0 + t, device=dev)
+        pages = self.block_table[seq_row, (tpos // PAGE).long()]
+        kv_slot = (pages * PAGE + (tpos % PAGE).int()).int()
+        ng, tail = t // 8, t % 8
+        if ng:
+            ws["ctx"][:ng] = pos0 + 8 * torch.arange(1, ng + 1, dtype=torch.int32, device=dev)
+            ws["bt_row"][:ng] = seq_row
+        if tail:
+            ws["ctx"][ng] = pos0 + t
+            ws["bt_row"][ng] = seq_row
+        own = pipe.own_rows(t).clamp(max=t - 1)
+        if own.numel():
+            if embeds is None:
+                K.embed(ids[own].contiguous(), self.w.embed, pipe.h, own.numel())
+            else:
+                pipe.h[:own.numel()].copy_(embeds[own])
+        layers = self.w.layers
+        pipe.reduce_norm_gather(t, layers[0].ln1, out_dtype=xd, eps=sp.eps, seed=True)
+        fi = gi = 0
+        use_state = pos0 > 0
+        for i, lw in enumerate(layers):
+            x = pipe.x(t, xd)
+            if lw.kind == "gdn":
+                nq = sp.conv_dim + sp.value_dim
+                wide = ws["wide"].view(-1)[:t * nq].view(t, nq)
+                pipe.gemm_ag(dense(lw.qkvz), wide, t)
+                ab = ws["ab"][:t]
+                linear.dense_gemm(x, lw.ab_dense, ab, arm="tc")        # after the gathering GEMM: all rows are here
+                conv = ws["conv"][:t]
+                K.gdn_conv_fwd(wide, nq, lw.conv_w, pool.conv_state[gi], gdn_slot, conv, t, sp.nk, sp.nv, use_state)
+                mix = ws["mix"].view(-1)[:t * sp.value_dim].view(t, sp.value_dim)
+                K.gdn_scan(conv, wide[:, sp.conv_dim:], nq, ab, self.ldab, lw.a_log, lw.dt_bias, lw.gamma,
+                           pool.rec_state[gi], gdn_slot, mix, t, sp.nk, sp.nv, use_state, sp.eps)
+                pipe.gemm_rs(mix, dense(lw.out_proj), t)
+                gi += 1
+            else:
+                wide = ws["wide"].view(-1)[:t * self.qkv_n].view(t, self.qkv_n)
+                pipe.gemm_ag(dense(lw.qkv), wide, t)
+                qn = 2 * sp.hq * sp.hd
+                K.qknorm_rope_insert(wide, self.qkv_n, wide[:, qn:], self.qkv_n, wide[:, qn + sp.hkv * sp.hd:],
+                                     self.qkv_n, lw.q_norm, lw.k_norm, pos3_v, self.inv_freq, self.section, kv_slot,
+                                     ws["q"], pool.k_pool[fi], pool.v_pool[fi], t, sp.hq, sp.hkv, sp.hd, sp.rotary_dim,
+                                     sp.eps, self.rope_scale)
+                if ng:
+                    K.paged_attn(ws["q"], pool.k_pool[fi], pool.v_pool[fi], self.block_table, ws["bt_row"], ws["ctx"],
+                                 ws["part_o"], ws["part_ml"], ng, 8, sp.hq, sp.hkv, sp.hd, self.max_blocks, 1, self.scale)
+                if tail:
+                    off = ng * 8
+                    K.paged_attn(ws["q"][off:], pool.k_pool[fi], pool.v_pool[fi], self.block_table, ws["bt_row"][ng:],
+                                 ws["ctx"][ng:], ws["part_o"][off * sp.hq * sp.hd:], ws["part_ml"][off * sp.hq * 2:], 1,
+                                 tail, sp.hq, sp.hkv, sp.hd, self.max_blocks, 1, self.scale)
+                mix = ws["mix"].view(-1)[:t * sp.hq * sp.hd].view(t, sp.hq * sp.hd)
+                K.attn_reduce(ws["part_o"], ws["part_ml"], 1, wide, self.qkv_n, t, sp.hq, out=mix, group=self.G)
+                pipe.gemm_rs(mix, dense(lw.o_proj), t)
+                fi += 1
+            pipe.reduce_norm_gather(t, lw.ln2, out_dtype=xd, eps=sp.eps)
+            gu = ws["wide"].view(-1)[:t * 2 * sp.inter].view(t, 2 * sp.inter)
+            pipe.gemm_ag(dense(lw.gate_up), gu, t)
+            K.silu_mul(gu, t, sp.inter, out=ws["act"][:t], group=self.G)
+            pipe.gemm_rs(ws["act"][:t], dense(lw.down), t)
+            pipe.reduce_norm_gather(t, layers[i + 1].ln1 if i + 1 < len(layers) else None, out_dtype=xd, eps=sp.eps)
+        if not want_logits:
+            return None
+        owner, lrow = pipe.local_row(t - 1)
+        if pipe.rank == owner:
+            self.h[:1].copy_(pipe.h[lrow:lrow + 1])
+        else:
+            self.h[:1].zero_()
+        if pipe.world > 1:
+            self.comm.allreduce_prefill(self.h[:1])             # the other ranks hold zeros: a broadcast of the last row
         self._norm(1, self.w.final_norm, want_xn=True, want_pack=False)
         self._head(1, sample=True)
         return self.out_tok[:1]

@@ -57,6 +57,11 @@ def w4_gemm(w, x: torch.Tensor, out: torch.Tensor, arm: str = "tc") -> torch.Ten
     raise ValueError(f"unknown prefill GEMM arm {arm!r}")
 
 
+def w4_dense(w, dtype, device) -> torch.Tensor:
+    """The weight dequantised into the shared dense scratch matrix (valid until the next call on this stream)."""
+    return K.w4_dequant(w, _dense_scratch(w.n, w.k, device, dtype))
+
+
 _w16: dict = {}
 
 

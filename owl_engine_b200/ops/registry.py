@@ -43,6 +43,8 @@ _T = [
     KernelSpec("owl_f16_gemm_tc", "gemm_tc.cu", "gemm", gen="tcgen05+tmem+tma"),
     KernelSpec("owl_gemm_status", "gemm_tc.cu", "status", capture=False),
     KernelSpec("owl_f16_gemm_persist", "gemm_dense.cu", "gemm", gen="tcgen05+tmem+tma"),
+    KernelSpec("owl_f16_gemm_ag", "gemm_dense.cu", "gemm", gen="tcgen05+tmem+tma+p2p"),
+    KernelSpec("owl_f16_gemm_rs", "gemm_dense.cu", "gemm", gen="tcgen05+tmem+tma+p2p"),
     KernelSpec("owl_gemm_dense_status", "gemm_dense.cu", "status", capture=False),
     KernelSpec("owl_w4_dequant", "dequant.cu", "load"),
     KernelSpec("owl_nvfp4_gemv", "lowbit.cu", "gemv"),
@@ -74,6 +76,7 @@ _T = [
     KernelSpec("owl_ar_residual_norm", "comm.cu", "comm", gen="p2p+multimem"),
     KernelSpec("owl_ar_inplace", "comm.cu", "comm", gen="p2p+multimem"),
     KernelSpec("owl_push_residual_norm", "comm.cu", "comm", gen="p2p"),
+    KernelSpec("owl_rs_norm_ag", "comm.cu", "comm", gen="p2p"),
     KernelSpec("owl_w4a16_skinny_push", "gemv.cu", "gemv", gen="dp4a+mma.sync+bulk-copy+p2p"),
     KernelSpec("owl_argmax_merge", "comm.cu", "comm", gen="p2p"),
     KernelSpec("owl_comm_wait_probe", "comm.cu", "comm", gen="p2p"),

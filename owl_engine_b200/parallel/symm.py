@@ -13,6 +13,9 @@ Workspace layout (identical on every rank, so an offset is valid on all peers):
     big        : bf16[big_elems]                prefill-size all-reduce payload
     push_a/b   : bf16[world][MAX_ROWS][hidden]  slots the peers' GEMV epilogues write their partial sums into
     push_flags : uint32[2][8]                   sequence numbers published by the peers' GEMVs
+    pf_slots   : bf16[world][max_local*128][hidden]  prefill reduce-scatter slots (partial sums of this rank's row tiles)
+    pf_x       : 16-bit[pf_rows][hidden]        prefill all-gather target (normalised rows from every owner)
+    pf_flags   : uint32[2][world][max_local]    reduce-scatter / all-gather sequence flags per row tile
 
 Reference counterpart: VMM peer grant + staging header (``crates/backends/cuda/src/vmm.rs``,
 ``comm/ar.rs:38-175``), generalised from 2 threads in one process to 2/4/8 processes.
@@ -34,6 +37,10 @@ K.register("owl_push_residual_norm", [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I
 K.register("owl_ar_inplace", [_P, _P, _P, _P, ctypes.c_longlong, _I, _I, _I, _I, ctypes.c_uint, _P])
 K.register("owl_argmax_merge", [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, ctypes.c_uint, _I, _P])
 K.register("owl_comm_wait_probe", [_P, ctypes.c_uint, ctypes.c_uint, _P, _P])
+_U = ctypes.c_uint
+K.register("owl_f16_gemm_ag", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P, _U, _I, _I, _U, _P])
+K.register("owl_f16_gemm_rs", [_P, _I, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _U, _I, _I, _I, _P])
+K.register("owl_rs_norm_ag", [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _U, _U, _F, _I, _I, _U, _P])
 
 FLAG_SLOTS = 128
 MAX_ROWS = 32
@@ -45,6 +52,89 @@ def _ptr_array(ptrs):
     for i, p in enumerate(ptrs):
         arr[i] = p
     return arr
+
+
+class PrefillPipe:
+    """Sequence-parallel prefill plumbing of one rank: GEMM + reduce-scatter, owner-side sum + residual + RMSNorm +
+    all-gather, and the column-parallel GEMM that consumes the gathered rows tile by tile.
+
+    Token rows are cut into 128-row tiles; tile j is owned by rank ``j % world`` (its local tile ``j // world``). The
+    residual stream of a chunk lives only on the owners (``h``, local). All buffers are passed in, so a world of one
+    (plain device tensors) exercises the same kernels and flags on a single GPU."""
+
+    TILE = 128
+
+    def __init__(self, rank: int, world: int, hidden: int, rows: int, *, slots, x_bytes, rs_flags, ag_flags, x_ptrs, slot_ptrs,
+                 rs_flag_ptrs, ag_flag_ptrs, device):
+        self.rank, self.world, self.hidden, self.rows = rank, world, hidden, rows
+        self.max_local = self.max_local_for(rows, world)
+        self.slots, self.x_bytes, self.rs_flags, self.ag_flags = slots, x_bytes, rs_flags, ag_flags
+        self.x_ptrs, self.slot_ptrs = _ptr_array(x_ptrs), _ptr_array(slot_ptrs)
+        self.rs_flag_ptrs, self.ag_flag_ptrs = _ptr_array(rs_flag_ptrs), _ptr_array(ag_flag_ptrs)
+        self.h = torch.zeros(self.max_local * self.TILE, hidden, dtype=torch.bfloat16, device=device)
+        self.rs_done = torch.zeros((rows + self.TILE - 1) // self.TILE, dtype=torch.int32, device=device)
+        self.rows_done = torch.zeros(self.max_local, dtype=torch.int32, device=device)
+        self.rs_seq = self.ag_seq = 0
+        self.device = device
+
+    @classmethod
+    def max_local_for(cls, rows: int, world: int) -> int:
+        tiles = (rows + cls.TILE - 1) // cls.TILE
+        return (tiles + world - 1) // world
+
+    @classmethod
+    def local(cls, hidden: int, rows: int, device) -> "PrefillPipe":
+        """A world of one on plain device memory (single-GPU tests of the protocol)."""
+        ml = cls.max_local_for(rows, 1)
+        slots = torch.zeros(ml * cls.TILE, hidden, dtype=torch.bfloat16, device=device)
+        xb = torch.zeros(rows * hidden * 2, dtype=torch.uint8, device=device)
+        rf = torch.zeros(ml, dtype=torch.int32, device=device)
+        af = torch.zeros(ml, dtype=torch.int32, device=device)
+        return cls(0, 1, hidden, rows, slots=slots, x_bytes=xb, rs_flags=rf, ag_flags=af, x_ptrs=[xb.data_ptr()],
+                   slot_ptrs=[slots.data_ptr()], rs_flag_ptrs=[rf.data_ptr()], ag_flag_ptrs=[af.data_ptr()], device=device)
+
+    def x(self, t: int, dtype) -> torch.Tensor:
+        """This rank's copy of the gathered activation rows."""
+        return self.x_bytes[:t * self.hidden * 2].view(dtype).view(t, self.hidden)
+
+    def own_rows(self, t: int) -> torch.Tensor:
+        """Global row numbers of the rows this rank owns, in local order (padded tiles clipped to t)."""
+        tiles = (t + self.TILE - 1) // self.TILE
+        mine = torch.arange(self.rank, tiles, self.world)
+        rows = (mine[:, None] * self.TILE + torch.arange(self.TILE)[None]).reshape(-1)
+        return rows.to(self.device)
+
+    def local_row(self, row: int) -> tuple[int, int]:
+        """(owner rank, local row) of a global token row."""
+        j = row // self.TILE
+        return j % self.world, (j // self.world) * self.TILE + row % self.TILE
+
+    def gemm_rs(self, x: torch.Tensor, w: torch.Tensor, t: int) -> None:
+        """Partial sums of ``x[:t] @ w^T`` go to the owners' slots (row-parallel GEMM + reduce-scatter)."""
+        assert x.dtype == w.dtype and w.shape[0] == self.hidden and t <= self.rows
+        self.rs_seq += 1
+        K.call("owl_f16_gemm_rs", K.ptr(x), x.stride(0), K.ptr(w), w.stride(0), t, w.shape[0], x.shape[1], self.hidden,
+               1 if x.dtype == torch.bfloat16 else 0, self.slot_ptrs, self.rs_flag_ptrs, K.ptr(self.rs_done), self.rs_seq,
+               self.rank, self.world, self.max_local, K.stream())
+
+    def reduce_norm_gather(self, t: int, norm_w, *, out_dtype=torch.float16, eps: float = 1e-6, seed: bool = False,
+                           one_plus_w: bool = True) -> None:
+        """Owner side: residual rows += slots (unless ``seed``), then normalised rows to every rank (unless ``norm_w`` is
+        None, which only updates the residual)."""
+        if norm_w is not None:
+            self.ag_seq += 1
+        K.call("owl_rs_norm_ag", K.ptr(self.slots), K.ptr(self.rs_flags), K.ptr(self.h), K.ptr(norm_w), self.x_ptrs,
+               self.ag_flag_ptrs, K.ptr(self.rows_done), t, self.hidden, self.rank, self.world, self.max_local,
+               0 if seed else self.world, self.rs_seq, self.ag_seq, eps, int(one_plus_w), int(out_dtype == torch.float16),
+               SPIN_LIMIT, K.stream())
+
+    def gemm_ag(self, w: torch.Tensor, out: torch.Tensor, t: int) -> torch.Tensor:
+        """``out[:t] = gathered_x[:t] @ w^T``, starting on the row tiles that have arrived."""
+        x = self.x(t, w.dtype)
+        K.call("owl_f16_gemm_ag", K.ptr(x), x.stride(0), K.ptr(w), w.stride(0), K.ptr(out), t, w.shape[0], self.hidden,
+               out.stride(0), 1 if w.dtype == torch.bfloat16 else 0, K.ptr(self.ag_flags), self.ag_seq, self.world,
+               self.max_local, SPIN_LIMIT, K.stream())
+        return out
 
 
 class SymmetricWorkspace:
@@ -62,7 +152,13 @@ class SymmetricWorkspace:
         self.off_push = (self.off_big + big_elems * 2 + 255) // 256 * 256
         push_bytes = world * MAX_ROWS * hidden * 2
         self.off_pflags = self.off_push + 2 * push_bytes
-        nbytes = self.off_pflags + 2 * 8 * 4
+        pf_rows = big_elems // hidden
+        ml = PrefillPipe.max_local_for(pf_rows, world)
+        self.off_pf_slots = (self.off_pflags + 2 * 8 * 4 + 255) // 256 * 256
+        pf_slot_bytes = world * ml * PrefillPipe.TILE * hidden * 2
+        self.off_pf_x = self.off_pf_slots + pf_slot_bytes
+        self.off_pf_flags = self.off_pf_x + pf_rows * hidden * 2
+        nbytes = self.off_pf_flags + 2 * world * ml * 4
         self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
         self.buf.zero_()
         gname = (group or dist.group.WORLD).group_name
@@ -88,6 +184,14 @@ class SymmetricWorkspace:
         self.push_count = torch.zeros(2, dtype=torch.int32, device=device)
         self.push_seq = torch.zeros(2, dtype=torch.int32, device=device)
         self.push_counters = torch.zeros(2, MAX_ROWS, dtype=torch.int32, device=device)
+        fl = world * ml * 4
+        self.prefill = PrefillPipe(
+            rank, world, hidden, pf_rows, device=device,
+            slots=self.buf[self.off_pf_slots:self.off_pf_x].view(torch.bfloat16),
+            x_bytes=self.buf[self.off_pf_x:self.off_pf_flags],
+            rs_flags=self.buf[self.off_pf_flags:self.off_pf_flags + fl], ag_flags=self.buf[self.off_pf_flags + fl:self.off_pf_flags + 2 * fl],
+            x_ptrs=[b + self.off_pf_x for b in base], slot_ptrs=[b + self.off_pf_slots for b in base],
+            rs_flag_ptrs=[b + self.off_pf_flags for b in base], ag_flag_ptrs=[b + self.off_pf_flags + fl for b in base]) if pf_rows >= 128 else None
         self.counters = torch.zeros(FLAG_SLOTS, dtype=torch.int32, device=device)
         self.scratch = torch.empty(big_elems, dtype=torch.bfloat16, device=device)
 

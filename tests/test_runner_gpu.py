@@ -107,3 +107,34 @@ def test_batched_decode_and_self_feeding_graph(layout):
             # the graph feeds its own argmax forward: keep the reference on the same tokens
             ref_next[b] = got[b]
         assert v["ids"].cpu().tolist() == got
+
+
+def test_sequence_parallel_prefill_protocol_on_one_gpu():
+    """The tensor-parallel prefill path (GEMM + reduce-scatter epilogue, owner-side sum + norm + all-gather, GEMM that
+    waits per row tile) with a world of one on plain device memory: same kernels, flags and sequence numbers."""
+    from owl_engine_b200.ops import gemm_tc
+    from owl_engine_b200.parallel.symm import PrefillPipe, SymmetricWorkspace
+
+    spec, run, ref = build("tc")
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, spec.vocab, (250,), generator=g)
+    ids = prompt.to(torch.int32).to(DEV)
+    run.block_table[1, :16] = torch.arange(16, dtype=torch.int32, device=DEV)
+    run.prefill_chunk_forward(ids, 0, 1, 1)
+    torch.cuda.synchronize()
+    h_plain, l_plain = run.h[:1].float().cpu(), run.logits[:1].float().cpu()
+    run.pf_pipe = PrefillPipe.local(spec.hidden, 256, DEV)
+    run.SP_FROM = 128
+    outs = []
+    for slot in (2, 3):                         # twice: sequence numbers advance, flags are reused
+        run.prefill_chunk_forward(ids, 0, 1, slot)
+        torch.cuda.synchronize()
+        outs.append((run.h[:1].float().cpu(), run.logits[:1].float().cpu()))
+    assert gemm_tc.gemm_status() == 0 and SymmetricWorkspace.status() == 0
+    assert rel_err(outs[0][0], h_plain) < 0.02 and rel_err(outs[0][1], l_plain) < 0.02
+    assert torch.equal(outs[0][0], outs[1][0])
+    a, b = run.pool.rec_state[0][1].float(), run.pool.rec_state[0][2].float()
+    assert rel_err(b, a) < 0.02
+    st = ref.new_state()
+    hr = ref.forward(prompt, st)
+    assert rel_err(outs[0][0], hr[-1:]) < 0.05

@@ -106,3 +106,74 @@ def test_tp2_matches_and_is_rank_consistent(mode):
         import numpy as np
         for a, b in zip(l0, l1):
             assert np.array_equal(a, b), "ranks hold different logits"
+
+
+def _worker_sp(rank, world, port, q):
+    """A 250-token prefill chunk under TP: GEMM-fused reduce-scatter / all-gather path vs the all-reduce path."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+
+    from owl_engine_b200.models import hybrid as H
+    from owl_engine_b200.models.reference import init_weights
+    from owl_engine_b200.models.spec import test_hybrid as make_spec
+    from owl_engine_b200.ops import gemm_tc
+    from owl_engine_b200.parallel.comm import TpComm
+
+    comm = TpComm.from_env("fused", hidden=256, big_elems=256 * 256)
+    dev = comm.device
+    full = make_spec(n_layers=4, vocab=512)
+    dense = init_weights(full, seed=3, std=0.05)
+    spec = full.sharded(rank, world)
+    hw, _ = H.weights_from_dense(spec, dense, dev, vocab_split=True)
+    pool = H.StatePool(spec, dev, n_pages=32, n_slots=3)
+    run = H.HybridRunner(spec, hw, pool, max_seqs=2, max_blocks=16, comm=comm, prefill_gemm="tc")
+    run.SP_FROM = 128
+    run.block_table[0, :16] = torch.arange(16, dtype=torch.int32, device=dev)
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, full.vocab, (250,), generator=g).to(torch.int32).to(dev)
+    out = {}
+    for name, sp_on, slot in (("plain", False, 1), ("sp", True, 2), ("sp2", True, 1)):
+        run.sp_prefill = sp_on
+        run.prefill_chunk_forward(prompt, 0, 0, slot)
+        torch.cuda.synchronize()
+        out[name] = (int(run.out_tok[0]), run.h[:1].float().cpu().numpy().copy())
+    rec = (pool.rec_state[0][1].float() - pool.rec_state[0][2].float()).abs().max().item() / \
+        pool.rec_state[0][2].float().abs().max().clamp_min(1e-6).item()
+    status = comm.symm.status() or gemm_tc.gemm_status()
+    q.put((rank, out, rec, status))
+    q.close()
+    q.join_thread()
+    dist.barrier()
+    torch.cuda.synchronize()
+    os._exit(0)
+
+
+def test_tp2_sequence_parallel_prefill_matches_allreduce_prefill():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import numpy as np
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_sp, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    try:
+        res = sorted([q.get(timeout=120) for _ in procs], key=lambda x: x[0])
+        for p in procs:
+            p.join(timeout=30)
+    finally:
+        for p in procs:
+            if p.is_alive():
+                p.kill()
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    for rank, out, rec, status in res:
+        assert status == 0
+        h_plain, h_sp, h_sp2 = out["plain"][1], out["sp"][1], out["sp2"][1]
+        assert np.linalg.norm(h_sp - h_plain) / np.linalg.norm(h_plain) < 0.03
+        assert np.array_equal(h_sp, h_sp2), "the fused path is not reproducible call to call"
+        assert rec < 0.05
+    assert res[0][1]["sp"][0] == res[1][1]["sp"][0], "ranks disagree on the sampled token"
+    assert np.array_equal(res[0][1]["sp"][1], res[1][1]["sp"][1]), "ranks hold different last hidden rows"

@@ -91,7 +91,8 @@ def test_kernel_registry_matches_sources_and_bindings():
     from owl_engine_b200.ops import registry as R
 
     assert R.cross_check() == []
-    assert {k.entry for k in R.admit("gemm")} == {"owl_w4a16_gemm_tc", "owl_f16_gemm_tc", "owl_f16_gemm_persist"}
+    assert {k.entry for k in R.admit("gemm")} == {"owl_w4a16_gemm_tc", "owl_f16_gemm_tc", "owl_f16_gemm_persist",
+                                                     "owl_f16_gemm_ag", "owl_f16_gemm_rs"}
     assert all("tcgen05" in k.gen for k in R.admit("gemm"))
 
 
