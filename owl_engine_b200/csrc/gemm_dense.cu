@@ -1,6 +1,9 @@
 // Dense 16-bit GEMM for long prefill chunks on tcgen05 (sm_100a), persistent and epilogue-overlapped.
 //
 //   owl_f16_gemm_persist : C[T,N] = X[T,K] . W[N,K]^T     X, W both fp16 or both bf16, C bf16, fp32 accumulate
+//   owl_e4m3_gemm        : C[T,N] = (sx[t] sw[n]) Xq[T,K] . Wq[N,K]^T   both e4m3 with per-row fp32 scales (kind::f8f6f4,
+//                          twice the 16-bit rate): the tensor-core arm of W4A8 -- int4 weights dequantised once to e4m3
+//                          rows, activations quantised per token (owl_quant_e4m3_rows)
 //
 // Tile 128 (tokens) x 256 (weight rows) x 64 (k): with a 128 x 128 tile one MMA step reads as many shared-memory
 // bytes per cycle as the SM can deliver, so the tensor pipe idles half of the time; 256 weight rows per tile
@@ -50,6 +53,8 @@ struct GdParams {
   __nv_bfloat16* rs_dst[8];          // each rank's slot buffer [world][max_local * 128][ldo]
   uint32_t* rs_flag[8];              // each rank's flag table [world][max_local]
   int* rs_done;                      // local [m_tiles]: weight tiles finished per row tile
+  const float* a_scale;              // e4m3 form: per-token and per-weight-row scales
+  const float* b_scale;
 };
 struct GdCtl {
   uint64_t full[GD_STAGES], empty[GD_STAGES], acc_full[2], acc_empty[2];
@@ -76,14 +81,15 @@ __device__ __forceinline__ uint32_t gd_ld_acquire_sys(const uint32_t* p) {
   return v;
 }
 
-template <bool AG, bool RS>
+template <bool AG, bool RS, bool F8>
 __global__ void __launch_bounds__(GD_THREADS, 1) gemm_dense_kernel(const __grid_constant__ CUtensorMap tmA,
                                                                    const __grid_constant__ CUtensorMap tmB, GdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   GdCtl* ctl = reinterpret_cast<GdCtl*>(base + GD_STAGES * GD_STAGE_BYTES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int KI = p.K / GD_BK;
+  constexpr int BKE = F8 ? 2 * GD_BK : GD_BK;           // k elements per stage (128 bytes per row either way)
+  const int KI = p.K / BKE;
   const int n_tiles_total = p.m_tiles * p.n_tiles;
 
   if (threadIdx.x == 0) {
@@ -130,8 +136,8 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gemm_dense_kernel(const __grid_
           if (!gd_wait(&ctl->empty[s], (((uint32_t)(it / GD_STAGES)) & 1u) ^ 1u, ctl, OWL_ERR_WAIT_MMA)) goto prod_done;
           mbar_expect_tx(&ctl->full[s], GD_STAGE_BYTES);
           uint8_t* st = base + (size_t)s * GD_STAGE_BYTES;
-          tma_load_2d(st, &tmA, &ctl->full[s], k * GD_BK, m0);
-          tma_load_2d(st + GD_A_BYTES, &tmB, &ctl->full[s], k * GD_BK, n0);
+          tma_load_2d(st, &tmA, &ctl->full[s], k * BKE, m0);
+          tma_load_2d(st + GD_A_BYTES, &tmB, &ctl->full[s], k * BKE, n0);
         }
       }
     prod_done:
@@ -143,7 +149,7 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gemm_dense_kernel(const __grid_
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc = umma_idesc_f16(GD_BM, GD_BN, p.fmt);
+      const uint32_t idesc = F8 ? umma_idesc_e4m3(GD_BM, GD_BN) : umma_idesc_f16(GD_BM, GD_BN, p.fmt);
       int it = 0, lt = 0;                                   // stage counter, local tile counter
       for (int tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x, ++lt) {
         const int ab = lt & 1;
@@ -158,8 +164,10 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gemm_dense_kernel(const __grid_
           const uint32_t sa = smem_u32(base + (size_t)s * GD_STAGE_BYTES);
           const uint64_t da = umma_desc_k128(sa), db = umma_desc_k128(sa + GD_A_BYTES);
 #pragma unroll
-          for (int k4 = 0; k4 < GD_BK / 16; ++k4)
-            tc_mma_f16(td, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2), idesc, (k > 0 || k4 > 0) ? 1u : 0u);
+          for (int k4 = 0; k4 < GD_BK / 16; ++k4) {       // 32 bytes of k per instruction in both forms
+            if (F8) tc_mma_f8(td, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2), idesc, (k > 0 || k4 > 0) ? 1u : 0u);
+            else tc_mma_f16(td, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2), idesc, (k > 0 || k4 > 0) ? 1u : 0u);
+          }
           tc_commit(&ctl->empty[s]);
         }
         if (!ok) break;
@@ -185,6 +193,14 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gemm_dense_kernel(const __grid_
         uint32_t r[32];
         tmem_ld_32x32b_x32(tmem + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(ab * GD_BN + c * 32), r);
         tc_wait_ld();
+        if (F8 && row < p.T) {
+          const float sa = p.a_scale[row];
+#pragma unroll
+          for (int v = 0; v < 32; ++v) {
+            const int col = n0 + c * 32 + v;
+            r[v] = __float_as_uint(__uint_as_float(r[v]) * sa * (col < p.N ? p.b_scale[col] : 0.f));
+          }
+        }
         if (row < p.T) {
           __nv_bfloat16* o = obase + n0 + c * 32;
           if (n0 + c * 32 + 32 <= p.N) {
@@ -244,14 +260,14 @@ static EncodeTiledFn2 gd_encode() {
   }
   return fn;
 }
-static int gd_map(CUtensorMap* m, const void* ptr, int rows, int K, int ld, int fmt, int box_rows) {
+static int gd_map(CUtensorMap* m, const void* ptr, int rows, int K, int ld, int fmt, int box_rows) {   // fmt 2: e4m3 bytes
   EncodeTiledFn2 enc = gd_encode();
   if (!enc) return OWL_ERR_LAUNCH * 1000 - 1;
   cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {GD_BK, (cuuint32_t)box_rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * (fmt == 2 ? 1 : 2)};
+  cuuint32_t box[2] = {(cuuint32_t)(fmt == 2 ? 2 * GD_BK : GD_BK), (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(m, fmt ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(ptr),
+  CUresult r = enc(m, fmt == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : fmt ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(ptr),
                    dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? OWL_OK : OWL_ERR_LAUNCH * 1000 - (int)r;
@@ -261,8 +277,9 @@ static int gd_map(CUtensorMap* m, const void* ptr, int rows, int K, int ld, int 
 using namespace owl;
 
 static int gd_launch(const void* x, int ldx, const void* w, int ldw, GdParams& p, int mode, cudaStream_t st) {
-  if (p.T < 1 || p.N < 1 || p.K < 64 || (p.K & 63) || (ldx & 7) || (ldw & 7) || (p.ldo & 7) || (p.fmt != 0 && p.fmt != 1) ||
-      (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
+  const int kmask = p.fmt == 2 ? 127 : 63, ldmask = p.fmt == 2 ? 15 : 7;
+  if (p.T < 1 || p.N < 1 || p.K <= kmask || (p.K & kmask) || (ldx & ldmask) || (ldw & ldmask) || (p.ldo & 7) || p.fmt < 0 ||
+      p.fmt > 2 || (p.fmt == 2) != (mode == 3) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
     return OWL_ERR_BAD_ARG;
   CUtensorMap a, b;
   int r = gd_map(&a, x, p.T, p.K, ldx, p.fmt, GD_BM);
@@ -275,18 +292,20 @@ static int gd_launch(const void* x, int ldx, const void* w, int ldw, GdParams& p
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (cudaFuncSetAttribute(gemm_dense_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GD_SMEM) != cudaSuccess ||
-        cudaFuncSetAttribute(gemm_dense_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GD_SMEM) != cudaSuccess ||
-        cudaFuncSetAttribute(gemm_dense_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GD_SMEM) != cudaSuccess) {
+    if (cudaFuncSetAttribute(gemm_dense_kernel<false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GD_SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(gemm_dense_kernel<true, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GD_SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(gemm_dense_kernel<false, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GD_SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(gemm_dense_kernel<false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GD_SMEM) != cudaSuccess) {
       sms = 0;
       return OWL_ERR_LAUNCH * 1000;
     }
   }
   const int tiles = p.m_tiles * p.n_tiles;
   const int grid = tiles < sms ? tiles : sms;
-  if (mode == 0) gemm_dense_kernel<false, false><<<grid, GD_THREADS, GD_SMEM, st>>>(a, b, p);
-  else if (mode == 1) gemm_dense_kernel<true, false><<<grid, GD_THREADS, GD_SMEM, st>>>(a, b, p);
-  else gemm_dense_kernel<false, true><<<grid, GD_THREADS, GD_SMEM, st>>>(a, b, p);
+  if (mode == 0) gemm_dense_kernel<false, false, false><<<grid, GD_THREADS, GD_SMEM, st>>>(a, b, p);
+  else if (mode == 1) gemm_dense_kernel<true, false, false><<<grid, GD_THREADS, GD_SMEM, st>>>(a, b, p);
+  else if (mode == 2) gemm_dense_kernel<false, true, false><<<grid, GD_THREADS, GD_SMEM, st>>>(a, b, p);
+  else gemm_dense_kernel<false, false, true><<<grid, GD_THREADS, GD_SMEM, st>>>(a, b, p);
   OWL_LAUNCH_CHECK();
   return OWL_OK;
 }
@@ -298,6 +317,17 @@ OWL_API int owl_f16_gemm_persist(const void* x, int ldx, const void* w, int ldw,
   GdParams p = {};
   p.out = (__nv_bfloat16*)out; p.T = T; p.N = N; p.K = K; p.ldo = ldo; p.fmt = fmt;
   return gd_launch(x, ldx, w, ldw, p, 0, st);
+}
+
+// xq: e4m3 [T][ldx], wq: e4m3 [N][ldw] (bytes), sx fp32 [T], sw fp32 [N]; out bf16 [T][ldo] = sx[t] sw[n] (xq . wq^T).
+// K multiple of 128.
+OWL_API int owl_e4m3_gemm(const void* xq, int ldx, const void* sx, const void* wq, int ldw, const void* sw, void* out, int T,
+                          int N, int K, int ldo, cudaStream_t st) {
+  if ((reinterpret_cast<uintptr_t>(out) & 15) || !sx || !sw) return OWL_ERR_BAD_ARG;
+  GdParams p = {};
+  p.out = (__nv_bfloat16*)out; p.T = T; p.N = N; p.K = K; p.ldo = ldo; p.fmt = 2;
+  p.a_scale = (const float*)sx; p.b_scale = (const float*)sw;
+  return gd_launch(xq, ldx, wq, ldw, p, 3, st);
 }
 
 // Column-parallel GEMM over activation rows gathered from the ranks: x is THIS rank's copy of the gathered

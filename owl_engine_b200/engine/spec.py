@@ -144,6 +144,50 @@ class MtpDraft:
         self.ready[sid] = True
 
 
+class DFlash2Draft:
+    """The DFlash2 block draft as draft source (``models/dflash2.py``): the target's tap hiddens of every prompt chunk
+    and of every accepted row are encoded into the draft's ring KV; a proposal is one captured forward of the 8-row
+    block. One sequence at a time (the ring belongs to the sequence that was prefetched last)."""
+
+    def __init__(self, draft, runner, lookup: LookupDraft | None = None):
+        self.draft, self.lookup, self.sid = draft, lookup, None
+        dev, H = runner.device, runner.spec.hidden
+        runner.taps = {i: torch.zeros(runner.MAX_ROWS, H, dtype=torch.bfloat16, device=dev) for i in draft.spec.taps}
+        runner.taps["prefill"] = {}
+        runner.tap_sink = self._on_chunk
+        runner.graphs.clear()
+        self.runner = runner
+
+    def _on_chunk(self, pos0: int, t: int, taps: dict) -> None:
+        if pos0 < self.draft.n_seen or pos0 == 0:
+            self.draft.reset()
+        cat = torch.cat([taps[i] for i in self.draft.spec.taps], dim=1)
+        for o in range(0, t, self.draft.max_encode):
+            self.draft.encode(cat[o:o + self.draft.max_encode], pos0 + o)
+
+    def after_prefill(self, engine: Engine, sid: int) -> None:
+        self.sid = sid
+        if self.draft.graph is None:
+            self.draft.capture()
+
+    def propose(self, engine: Engine, sid: int, depth: int) -> list[int]:
+        if self.lookup is not None:
+            hit = self.lookup.propose(engine, sid, depth)
+            if len(hit) >= depth:
+                return hit
+        if sid != self.sid:
+            return []
+        seq = engine.seqs[sid]
+        return self.draft.propose(seq.tokens[-1], seq.n_cached, depth)
+
+    def observe(self, engine: Engine, sid: int, n_rows: int, emitted: list[int]) -> None:
+        if sid != self.sid:
+            return
+        seq = engine.seqs[sid]
+        cat = torch.cat([self.runner.taps[i][:n_rows] for i in self.draft.spec.taps], dim=1)
+        self.draft.encode(cat, seq.n_cached - n_rows)
+
+
 # ---- the round machine ------------------------------------------------------------------------
 @dataclass
 class SpecStats:

@@ -316,6 +316,7 @@ class HybridRunner:
         self.graphs: dict = {}
         self._pf = None   # lazily allocated prefill workspace
         self.taps: dict | None = None   # layer -> bf16 [M,H] buffers filled during decode/prefill for draft heads
+        self.tap_sink = None            # callable(pos0, t, {layer: [t, H]}) called after every prefill chunk when taps are on
         self.pre_hook = None            # callable(m): rewrites self.h after the embedding (draft heads mix in the target's hidden)
         self.uniform_rows = False       # per-row arithmetic independent of the number of rows in the step (speculative
                                         # verify must reproduce plain decoding bit for bit): one GEMV arm for 1..8 rows,
@@ -558,7 +559,7 @@ class HybridRunner:
         sp, dev = self.spec, self.device
         bf = lambda *s: torch.empty(*s, dtype=torch.bfloat16, device=dev)
         # GEMM inputs are fp16 on the tcgen05 arm (exact int4 dequant), bf16 on the baseline arm
-        xd = torch.float16 if self.prefill_gemm == "tc" else torch.bfloat16
+        xd = torch.float16 if self.prefill_gemm in ("tc", "tc8") else torch.bfloat16
         xa = lambda *s: torch.empty(*s, dtype=xd, device=dev)
         widest = max(2 * sp.inter, sp.conv_dim + sp.value_dim, self.qkv_n)
         ws = dict(t=t, h=bf(t, sp.hidden), x=xa(t, sp.hidden), wide=bf(t, widest), act=xa(t, sp.inter),
@@ -625,7 +626,7 @@ class HybridRunner:
                 wide = ws["wide"].view(-1)[:t * nq].view(t, nq)
                 self._gemm(lw.qkvz, x, wide)
                 ab = ws["ab"][:t]
-                linear.dense_gemm(x, lw.ab_dense, ab, arm=self.prefill_gemm)
+                linear.dense_gemm(x, lw.ab_dense, ab, arm="baseline" if self.prefill_gemm == "baseline" else "tc")
                 conv = ws["conv"][:t]
                 K.gdn_conv_fwd(wide, nq, lw.conv_w, pool.conv_state[gi], gdn_slot, conv, t, sp.nk, sp.nv, use_state)
                 mix = ws["mix"].view(-1)[:t * sp.value_dim].view(t, sp.value_dim)
@@ -665,6 +666,8 @@ class HybridRunner:
             h.add_(ws["y"][:t])
             if self.taps is not None and i in self.taps and "prefill" in self.taps:
                 self.taps["prefill"][i] = h.clone()
+        if self.taps is not None and self.tap_sink is not None and "prefill" in self.taps:
+            self.tap_sink(pos0, t, self.taps["prefill"])
         if not want_logits:
             return None
         self.h[:1].copy_(h[t - 1:t])

@@ -10,6 +10,28 @@ from . import kernels as K
 K.register("owl_w4a16_gemm_tc", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
 K.register("owl_f16_gemm_persist", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
 K.register("owl_f16_gemm_tc", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+K.register("owl_e4m3_gemm", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+K.register("owl_quant_e4m3_rows", [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p])
+
+
+def quant_e4m3_rows(x: torch.Tensor, out: torch.Tensor | None = None, scales: torch.Tensor | None = None):
+    """Per-row e4m3 quantisation of a 16-bit matrix: returns (bytes [R, K], fp32 scales [R]) with x ~= scale * q."""
+    assert x.dtype in (torch.float16, torch.bfloat16) and x.stride(-1) == 1
+    r, k = x.shape
+    out = torch.empty(r, k, dtype=torch.uint8, device=x.device) if out is None else out
+    scales = torch.empty(r, dtype=torch.float32, device=x.device) if scales is None else scales
+    K.call("owl_quant_e4m3_rows", K.ptr(x), x.stride(0), int(x.dtype == torch.float16), K.ptr(out), out.stride(0), K.ptr(scales),
+           r, k, K.stream())
+    return out, scales
+
+
+def e4m3_gemm(xq: torch.Tensor, sx: torch.Tensor, wq: torch.Tensor, sw: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[T, N] (bf16) = (sx[:, None] * sw[None]) * (xq @ wq^T) with e4m3 operands (``tcgen05.mma kind::f8f6f4``)."""
+    assert xq.dtype == torch.uint8 and wq.dtype == torch.uint8 and out.dtype == torch.bfloat16
+    t, k = xq.shape
+    K.call("owl_e4m3_gemm", K.ptr(xq), xq.stride(0), K.ptr(sx), K.ptr(wq), wq.stride(0), K.ptr(sw), K.ptr(out), t, wq.shape[0], k,
+           out.stride(0), K.stream())
+    return out
 
 
 def w4a16_gemm(w, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:

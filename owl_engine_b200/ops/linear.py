@@ -9,6 +9,12 @@ two arms:
                   scratch matrix (``csrc/dequant.cu``, runs at copy bandwidth) and the dense tcgen05 GEMM
                   multiplies it -- the in-kernel dequantisation repeats per 128-token tile and caps
                   the fused kernel near 300 TFLOP/s, the dense kernel runs at 750-1000;
+* ``"tc8"``       the W4A8 arm on tensor cores: like ``"tc"``, but for long chunks the dequantised weight is
+                  re-quantised per output row to e4m3 and the activations per token, and the product runs as
+                  ``tcgen05.mma kind::f8f6f4`` at twice the 16-bit rate (the reference's W4A8 arm quantises
+                  activations per token to int8 for IMMA, ``crates/kernels/cu/elems/quant_i8_act.cu:80-98``; int4
+                  values times a group scale do not survive an integer MMA without a per-group epilogue, an
+                  8-bit float product with per-row scales does);
 * ``"baseline"``  dequantise to a dense bf16 scratch matrix, then the library GEMM
                   (``torch.matmul`` = cuBLAS). This is the comparison arm, like the reference's
                   range-dequant -> cuBLAS arm (``crates/kernels/cu/gguf/gguf_smem.cu:415-552``).
@@ -33,12 +39,28 @@ def _dense_scratch(n: int, k: int, device, dtype=torch.bfloat16) -> torch.Tensor
     return buf[:n * k].view(n, k)
 
 
+def _fp8_scratch(tag: str, r: int, k: int, device):
+    key = (tag, str(device))
+    buf = _scratch.get(key)
+    if buf is None or buf[0].numel() < r * k or buf[1].numel() < r:
+        buf = (torch.empty(r * k, dtype=torch.uint8, device=device), torch.empty(r, dtype=torch.float32, device=device))
+        _scratch[key] = buf
+    return buf[0][:r * k].view(r, k), buf[1][:r]
+
+
 def w4_gemm(w, x: torch.Tensor, out: torch.Tensor, arm: str = "tc") -> torch.Tensor:
     if arm == "baseline":
         dense = K.w4_dequant(w, _dense_scratch(w.n, w.k, x.device))
         torch.matmul(x, dense.t(), out=out)
         return out
-    if arm == "tc":
+    if arm == "tc8" and x.shape[0] >= DEQUANT_FROM and w.k % 128 == 0:
+        from . import gemm_tc
+
+        dense = K.w4_dequant(w, _dense_scratch(w.n, w.k, x.device, torch.float16))
+        wq, sw = gemm_tc.quant_e4m3_rows(dense, *_fp8_scratch("w", w.n, w.k, x.device))
+        xq, sx = gemm_tc.quant_e4m3_rows(x, *_fp8_scratch("x", x.shape[0], w.k, x.device))
+        return gemm_tc.e4m3_gemm(xq, sx, wq, sw, out)
+    if arm in ("tc", "tc8"):
         from . import gemm_tc
 
         if x.shape[0] <= SKINNY_UPTO and w.layout == "slice":

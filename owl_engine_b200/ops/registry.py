@@ -45,8 +45,14 @@ _T = [
     KernelSpec("owl_f16_gemm_persist", "gemm_dense.cu", "gemm", gen="tcgen05+tmem+tma"),
     KernelSpec("owl_f16_gemm_ag", "gemm_dense.cu", "gemm", gen="tcgen05+tmem+tma+p2p"),
     KernelSpec("owl_f16_gemm_rs", "gemm_dense.cu", "gemm", gen="tcgen05+tmem+tma+p2p"),
+    KernelSpec("owl_e4m3_gemm", "gemm_dense.cu", "gemm", gen="tcgen05+tmem+tma"),
     KernelSpec("owl_gemm_dense_status", "gemm_dense.cu", "status", capture=False),
     KernelSpec("owl_w4_dequant", "dequant.cu", "load"),
+    KernelSpec("owl_quant_e4m3_rows", "dequant.cu", "load"),
+    KernelSpec("owl_dflash_conv", "dflash.cu", "draft"),
+    KernelSpec("owl_dflash_norm_rope", "dflash.cu", "draft"),
+    KernelSpec("owl_dflash_nc_attn", "dflash.cu", "draft"),
+    KernelSpec("owl_dflash_select", "dflash.cu", "draft"),
     KernelSpec("owl_nvfp4_gemv", "lowbit.cu", "gemv"),
     KernelSpec("owl_nvfp4_dequant", "lowbit.cu", "load"),
     KernelSpec("owl_nvfp4_quant_act", "lowbit.cu", "quant"),

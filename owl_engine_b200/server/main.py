@@ -58,9 +58,6 @@ def build_spec_factory(cfg: C.OwlConfig):
     sp = cfg.values["spec"]
     if sp["kind"] == "none" and not sp["lookup"]:
         return None
-    if sp["kind"] == "dflash2":
-        raise C.ConfigError("spec.kind = \"dflash2\": this draft head is not built; use \"mtp\" or lookup drafting")
-
     def make(engine):
         from ..engine.spec import LookupDraft, MtpDraft, SpecRunner
         from ..models.mtp import MtpHead
@@ -74,6 +71,24 @@ def build_spec_factory(cfg: C.OwlConfig):
                 src = SafeDir(sp["draft_path"])
                 weights = {k: src.get(k) for k in src.keys()}
             draft = MtpDraft(MtpHead(engine.runner, weights=weights), lookup)
+        elif sp["kind"] == "dflash2":
+            from ..engine.spec import DFlash2Draft
+            from ..models import dflash2 as D
+
+            ts = engine.spec
+            n = ts.n_layers
+            taps = D.DraftSpec.taps if n >= 62 else tuple(sorted({max(0, n * (2 * i + 1) // 10 - 1) for i in range(5)}))
+            dspec = D.DraftSpec(hidden=ts.hidden, vocab=ts.vocab, inter=ts.inter, taps=taps, mask_token_id=ts.vocab - 1,
+                                rope_theta=ts.rope_theta)
+            if sp["draft_path"]:
+                from ..formats.safetensors import SafeDir
+
+                src = SafeDir(sp["draft_path"])
+                dw = D.weights_from_dense(dspec, {k: src.get(k) for k in src.keys()}, engine.device)
+            else:
+                dw = D.random_weights(dspec, engine.device)
+            head = D.DFlash2(dspec, dw, engine.weights.embed, engine.weights.lm_head, engine.device)
+            draft = DFlash2Draft(head, engine.runner, lookup)
         else:
             draft = lookup
         return SpecRunner(draft, depth=max(1, min(7, sp["depth"] or 3)))
