@@ -43,6 +43,10 @@ class EngineConfig:
     decode_gemv: str = "dp4a"      # W4 decode arm: "dp4a" (legacy streaming kernels) or "tc" (tcgen05 streaming kernel)
     seed: int = 0
     n_layers: int | None = None    # override (tests / smoke)
+    kvmem_budget: int = 0          # tokens of KV a decode step may attend to (0 = everything): longer contexts attend to a
+                                   # view of sink + recent + best-scoring blocks, re-selected at every block boundary
+    kvmem_sink: int = 2
+    kvmem_recent: int = 4
 
 
 @dataclass
@@ -56,6 +60,9 @@ class Sequence:
     n_prompt: int = 0
     reused: int = 0                # prompt tokens served from the prefix cache
     chain: object = None           # block hashes of the prompt (numpy uint64)
+    meank: object = None           # KV selection: block means of de-rotated keys (last full-attention layer), float [blocks, hkv, hd]
+    meank_n: int = 0               # blocks indexed so far
+    view: list = None              # block indices of the current view (ascending, ends with the block being written)
     images: list = field(default_factory=list)    # [(first token index, merged embeddings [n, H], fingerprint)]
     pos3: object = None            # multimodal (t, h, w) position ids of the prompt, int32 [3, n_prompt] (None = text only)
     rope_delta: int = 0            # rope position of a decode token = its cache index + rope_delta
@@ -86,7 +93,7 @@ class Engine:
         self.pool = H.StatePool(self.spec, self.device, cfg.n_pages, cfg.n_slots + cfg.n_snap_rows + 1)
         self.spec_row = cfg.n_slots + cfg.n_snap_rows
         self.max_blocks = (cfg.max_seq + PAGE - 1) // PAGE
-        self.runner = H.HybridRunner(self.spec, self.weights, self.pool, max_seqs=cfg.max_seqs,
+        self.runner = H.HybridRunner(self.spec, self.weights, self.pool, max_seqs=cfg.max_seqs * (2 if cfg.kvmem_budget else 1),
                                      max_blocks=self.max_blocks, prefill_chunk=cfg.prefill_chunk, comm=comm,
                                      pdl=cfg.pdl, prefill_gemm=cfg.prefill_gemm)
         self.kv = KvStore(cfg.n_pages, PAGE)
@@ -100,6 +107,7 @@ class Engine:
 
             self.disk = DiskTier(cfg.disk_dir, page_bytes(self.pool), cfg.disk_cache_mb << 20)
         self.spilled = self.recalled = 0
+        self._last_rows: dict = {}
         self.free_rows = list(range(cfg.max_seqs - 1, -1, -1))
         self.seqs: dict[int, Sequence] = {}
         self._next_sid = 0
@@ -335,8 +343,13 @@ class Engine:
             hi[lay.ctx + i] = pos + 1
             hi[lay.gslot + i] = seq.slot
             hi[lay.bt_row + i] = seq.row
-            ctx_max = max(ctx_max, pos + 1)
+            if self.cfg.kvmem_budget and pos + 1 > self.cfg.kvmem_budget:
+                n_view = self._kvmem_view(seq, pos)
+                hi[lay.ctx + i] = (n_view - 1) * PAGE + pos % PAGE + 1
+                hi[lay.bt_row + i] = seq.row + self.cfg.max_seqs
+            ctx_max = max(ctx_max, int(hi[lay.ctx + i]))
         graph = self.runner.capture(b, 1, ctx_hint=self._ctx_bucket(ctx_max))
+        self._last_rows = {sid: i for i, sid in enumerate(sids)}     # whose query sits in which row of runner.q_rope
         n = lay.size
         self.runner.inp[:n].copy_(self.h_inp[:n], non_blocking=True)
         graph.replay()
@@ -352,6 +365,39 @@ class Engine:
             seq.tokens.append(t)
             out.append(t)
         return out
+
+    def _kvmem_view(self, seq: Sequence, pos: int) -> int:
+        """Bounded attention view of a long sequence: sink blocks + recent blocks + the best-scoring blocks of the rest,
+        re-selected whenever the write position enters a new block. The index (block means of de-rotated keys of the last
+        full-attention layer) grows incrementally; blocks are scored on the GPU against the sequence's query of the previous
+        step. The view's page table lives in a second block-table row of the sequence. Returns the number of view blocks."""
+        from ..store import select as S
+
+        cur = pos // PAGE                                  # block being written
+        if seq.view is not None and seq.view[-1] == cur:
+            return len(seq.view)
+        sp, run, dev = self.spec, self.runner, self.device
+        fi = sp.n_full - 1
+        if seq.meank is None:
+            seq.meank = torch.zeros(self.max_blocks, sp.hkv, sp.hd, dtype=torch.float32, device=dev)
+        if seq.meank_n < cur:                              # index the blocks completed since the last selection
+            ids = torch.arange(seq.meank_n, cur, dtype=torch.int32, device=dev)
+            pages = torch.tensor(seq.pages[seq.meank_n:cur], dtype=torch.int32, device=dev)
+            S.mean_k_blocks_gpu(self.pool.k_pool[fi], pages, ids * PAGE + seq.rope_delta, torch.full_like(ids, PAGE), run.inv_freq,
+                                sp.rotary_dim, seq.meank[seq.meank_n:cur])
+            seq.meank_n = cur
+        budget_blocks = max(self.cfg.kvmem_sink + self.cfg.kvmem_recent + 1, self.cfg.kvmem_budget // PAGE)
+        q_row = self._last_rows.get(seq.sid, -1)
+        if q_row >= 0 and cur > 0:
+            qpos = torch.tensor([pos - 1 + seq.rope_delta], dtype=torch.int32, device=dev)
+            scores = S.score_blocks_gpu(run.q_rope[q_row:q_row + 1], qpos, seq.meank[:cur], run.inv_freq, sp.rotary_dim).cpu()
+        else:
+            scores = torch.zeros(max(cur, 1))
+        scores = torch.cat([scores[:cur], torch.zeros(1)])          # the block being written is always "recent"
+        seq.view = S.select(scores, cur + 1, budget_blocks, self.cfg.kvmem_sink, self.cfg.kvmem_recent)
+        row = seq.row + self.cfg.max_seqs
+        run.block_table[row, :len(seq.view)] = torch.tensor([seq.pages[b] for b in seq.view], dtype=torch.int32, device=dev)
+        return len(seq.view)
 
     @staticmethod
     def _ctx_bucket(ctx: int) -> int:

@@ -287,6 +287,7 @@ def verify_step(engine: Engine, sid: int, rows: list[int]) -> list[int]:
         r.uniform_rows = True
         r.capture_fold(1)          # allocates fold_slot
     engine.pool.copy_slot(seq.slot, engine.spec_row)
+    engine._last_rows = {}          # the query buffer now holds verify rows, not decode rows
     lay = H.StepLayout(1, t)
     hi = engine.h_inp_np
     for i, tok in enumerate(rows):

@@ -49,6 +49,9 @@ _T = [
     KernelSpec("owl_gemm_dense_status", "gemm_dense.cu", "status", capture=False),
     KernelSpec("owl_w4_dequant", "dequant.cu", "load"),
     KernelSpec("owl_quant_e4m3_rows", "dequant.cu", "load"),
+    KernelSpec("owl_mean_k_block", "kvmem.cu", "select"),
+    KernelSpec("owl_kvscore", "kvmem.cu", "select"),
+    KernelSpec("owl_kvscore_softmax", "kvmem.cu", "select"),
     KernelSpec("owl_dflash_conv", "dflash.cu", "draft"),
     KernelSpec("owl_dflash_norm_rope", "dflash.cu", "draft"),
     KernelSpec("owl_dflash_nc_attn", "dflash.cu", "draft"),

@@ -61,3 +61,47 @@ def select(scores: torch.Tensor, n_blocks: int, budget_blocks: int, sink: int = 
 def view_table(block_table_row: torch.Tensor, kept: list[int]) -> torch.Tensor:
     """Page table of the selected blocks (what the attention kernel walks instead of the full row)."""
     return block_table_row[torch.tensor(kept, dtype=torch.long, device=block_table_row.device)]
+
+
+# ---- GPU index + scoring (csrc/kvmem.cu) ----------------------------------------------------------------------------
+def _K():
+    import ctypes
+
+    from ..ops import kernels as K
+
+    if "owl_mean_k_block" not in K._SIGS:
+        P, I, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+        K.register("owl_mean_k_block", [P, P, P, P, P, I, I, I, I, P, P])
+        K.register("owl_kvscore", [P, P, P, P, I, I, I, I, I, I, P, P])
+        K.register("owl_kvscore_softmax", [P, I, F, P, P])
+    return K
+
+
+def mean_k_blocks_gpu(k_pool_layer: torch.Tensor, pages: torch.Tensor, pos0: torch.Tensor, n_valid: torch.Tensor,
+                      inv_freq: torch.Tensor, rotary_dim: int, out: torch.Tensor) -> torch.Tensor:
+    """Block means of de-rotated keys straight from the paged e4m3 pool of one layer -> ``out[:len(pages)]``."""
+    K = _K()
+    _, _, hkv, hd = k_pool_layer.shape
+    n = pages.numel()
+    K.call("owl_mean_k_block", K.ptr(k_pool_layer), K.ptr(pages), K.ptr(pos0), K.ptr(n_valid), K.ptr(inv_freq), rotary_dim, n,
+           hkv, hd, K.ptr(out), K.stream())
+    return out[:n]
+
+
+def score_blocks_gpu(q: torch.Tensor, qpos: torch.Tensor, index: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int,
+                     out: torch.Tensor | None = None) -> torch.Tensor:
+    """Cosine-max block scores of rotated queries ``q`` bf16 [nq, hq, hd] against the index float [nb, hkv, hd]."""
+    K = _K()
+    nq, hq, hd = q.shape
+    nb, hkv, _ = index.shape
+    out = torch.empty(nb, dtype=torch.float32, device=q.device) if out is None else out
+    K.call("owl_kvscore", K.ptr(q), K.ptr(qpos), K.ptr(index), K.ptr(inv_freq), rotary_dim, nq, hq, hkv, hd, nb, K.ptr(out),
+           K.stream())
+    return out[:nb]
+
+
+def softmax_scores_gpu(scores: torch.Tensor, temp: float = 1.0) -> torch.Tensor:
+    K = _K()
+    out = torch.empty_like(scores)
+    K.call("owl_kvscore_softmax", K.ptr(scores), scores.numel(), float(temp), K.ptr(out), K.stream())
+    return out

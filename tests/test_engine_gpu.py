@@ -177,3 +177,45 @@ def test_image_prompt_embeds_positions_and_content_keyed_prefix_cache():
     c, r2 = run(png.BLUE)
     assert r0 == 0 and r1 >= 32 and a == b          # same pixels: cached prefix reused, same continuation
     assert r2 <= 0 + 16 * 0 and c != a              # other pixels: no reuse past the text head, other output
+
+
+def test_kv_selection_view_covers_everything_or_a_bounded_set():
+    """KV selection: with a budget above the context nothing changes; with a small budget decode steps attend to a
+    view of sink + recent + scored blocks whose page table sits in the sequence's second block-table row."""
+    from owl_engine_b200.store import select as S
+
+    g = torch.Generator().manual_seed(5)
+    base = EngineConfig(model="test-hybrid", n_pages=128, n_slots=4, n_snap_rows=2, max_seqs=4, max_seq=512, prefill_chunk=64)
+    prompt = torch.randint(0, 512, (150,), generator=g).tolist()
+    plain = Engine(base).generate(prompt, 20)
+    from dataclasses import replace
+    wide = Engine(replace(base, kvmem_budget=4096))
+    assert wide.generate(prompt, 20) == plain
+    eng = Engine(replace(base, kvmem_budget=96, kvmem_sink=1, kvmem_recent=2))
+    sid = eng.add_sequence(prompt)
+    eng.prefill(sid)
+    for _ in range(20):
+        eng.decode_step([sid])
+    seq = eng.seqs[sid]
+    cur = (seq.n_cached - 1) // 16
+    assert seq.view is not None and len(seq.view) == 6 and seq.view[0] == 0 and seq.view[-2:] == [cur - 1, cur]
+    assert seq.view == sorted(seq.view) and seq.meank_n == cur
+    row = eng.runner.block_table[seq.row + 4, :6].tolist()
+    assert row == [seq.pages[b] for b in seq.view]
+    # the GPU index equals the host formula on the pool's own keys
+    sp, fi = eng.spec, eng.spec.n_full - 1
+    k = eng.pool.k_pool[fi][seq.pages[2]].view(torch.float8_e4m3fn).float().cpu()          # [16, hkv, hd]
+    pos = torch.arange(32, 48).float()
+    inv = eng.runner.inv_freq.cpu()
+    ang = pos[:, None] * inv[None]
+    want = S.mean_k_index(S.derope(k, ang.cos(), ang.sin())[None])[0]
+    assert torch.allclose(seq.meank[2].cpu(), want, atol=2e-3, rtol=1e-3)
+    q = torch.randn(1, sp.hq, sp.hd, generator=g).bfloat16()
+    got = S.score_blocks_gpu(q.to(eng.device), torch.tensor([200], dtype=torch.int32, device=eng.device), seq.meank[:cur],
+                             eng.runner.inv_freq, sp.rotary_dim).cpu()
+    a200 = torch.tensor([200.0])[:, None] * inv[None]
+    ref = S.score_blocks(S.derope(q.float(), a200.cos(), a200.sin()), seq.meank[:cur].cpu())
+    assert torch.allclose(got, ref, atol=2e-3)
+    p = S.softmax_scores_gpu(got.to(eng.device), 4.0).cpu()
+    assert torch.allclose(p, torch.softmax(got * 4.0, 0), atol=1e-5)
+    eng.free_sequence(sid, publish=False)
