@@ -34,7 +34,8 @@ struct InsertParams {
   const unsigned char* section; // [rot/2] stream index per frequency
   const int* kv_slot;           // [rows] physical token index (page*16 + off); < 0 = skip write
   __nv_bfloat16* q_out;         // [rows][hq][hd]
-  uint8_t* k_pool; uint8_t* v_pool;  // [pages][16][hkv][hd] e4m3
+  uint8_t* k_pool; uint8_t* v_pool;  // [pages][16][hkv][hd] e4m3, or int8 when the scale pools are given
+  float* k_scale; float* v_scale;    // int8 pool: [pages][16][hkv] per (token, kv head) scales (null: e4m3 pool)
   int rows, hq, hkv, hd, rot;
   float eps, rope_scale;        // rope_scale multiplies cos/sin (YaRN attention factor)
 };
@@ -83,6 +84,11 @@ __global__ void __launch_bounds__(128) qknorm_rope_insert_kernel(InsertParams p)
       a = o[0]; b = o[1];
     }
   }
+  float amax = 0.f;
+  if (!is_q && p.k_scale) {    // int8 pool: one scale per (token, kv head), from the bf16-rounded values
+    const float av = e0 < hd ? fmaxf(fabsf(__bfloat162float(__float2bfloat16(a))), fabsf(__bfloat162float(__float2bfloat16(b)))) : 0.f;
+    amax = block_max(av, red);
+  }
   if (e0 >= hd) return;
   if (is_q) {
     *reinterpret_cast<uint32_t*>(p.q_out + ((size_t)row * p.hq + head) * hd + e0) = pack_bf16(a, b);
@@ -92,7 +98,14 @@ __global__ void __launch_bounds__(128) qknorm_rope_insert_kernel(InsertParams p)
     uint8_t* dst = (is_k ? p.k_pool : p.v_pool) + ((size_t)slot * p.hkv + kvh) * hd + e0;
     // values are rounded to bf16 first so the pool holds cast(bf16(x)) like a two-step pipeline
     const float ar = __bfloat162float(__float2bfloat16(a)), br = __bfloat162float(__float2bfloat16(b));
-    *reinterpret_cast<uint16_t*>(dst) = (uint16_t)f_to_fp8e4m3(ar) | ((uint16_t)f_to_fp8e4m3(br) << 8);
+    if (p.k_scale) {
+      const float sc = amax > 0.f ? amax / 127.f : 1.f, inv = 1.f / sc;
+      const int qa = max(-127, min(127, __float2int_rn(ar * inv))), qb = max(-127, min(127, __float2int_rn(br * inv)));
+      *reinterpret_cast<uint16_t*>(dst) = (uint16_t)(qa & 0xff) | ((uint16_t)(qb & 0xff) << 8);
+      if (tid == 0) (is_k ? p.k_scale : p.v_scale)[(size_t)slot * p.hkv + kvh] = sc;
+    } else {
+      *reinterpret_cast<uint16_t*>(dst) = (uint16_t)f_to_fp8e4m3(ar) | ((uint16_t)f_to_fp8e4m3(br) << 8);
+    }
   }
 }
 
@@ -104,6 +117,7 @@ __global__ void __launch_bounds__(128) qknorm_rope_insert_kernel(InsertParams p)
 struct AttnParams {
   const __nv_bfloat16* q;       // [groups*T][hq][hd]
   const uint8_t* k_pool; const uint8_t* v_pool;
+  const float* k_scale; const float* v_scale;   // int8 pool only
   const int* block_table;       // [seqs][max_blocks]
   const int* bt_row;            // [groups] -> block_table row (nullptr: identity)
   const int* ctx_len;           // [groups] tokens visible to the LAST row of the group
@@ -122,6 +136,16 @@ __device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t two_bytes) {
   __half2_raw r = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)two_bytes, __NV_E4M3);
   return *reinterpret_cast<uint32_t*>(&r);
 }
+// two int8 bytes -> f16x2, exact: (b ^ 0x80) placed under the exponent of 1024, minus 1152
+__device__ __forceinline__ uint32_t s8x2_to_f16x2(uint32_t two_bytes) {
+  const uint32_t w = __byte_perm(two_bytes ^ 0x8080u, 0x64646464u, 0x4140u);
+  const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&w), __half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480)));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+template <bool I8>
+__device__ __forceinline__ uint32_t kv2_to_f16x2(uint32_t two_bytes) {
+  return I8 ? s8x2_to_f16x2(two_bytes) : e4m3x2_to_f16x2(two_bytes);
+}
 __device__ __forceinline__ void mma16816(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
   asm volatile(
@@ -130,7 +154,7 @@ __device__ __forceinline__ void mma16816(float* c, uint32_t a0, uint32_t a1, uin
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int RG>
+template <int RG, bool I8>
 __global__ void __launch_bounds__(AT_WARPS * 32) paged_attn_kernel(AttnParams p) {
   constexpr int TS = AT_WARPS / RG;
   // cross-warp merge buffers (token splits of the same row group)
@@ -211,15 +235,24 @@ __global__ void __launch_bounds__(AT_WARPS * 32) paged_attn_kernel(AttnParams p)
           const uint32_t wb[4] = {kb[blk].x, kb[blk].y, kb[blk].z, kb[blk].w};
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            mma16816(s0, qa0[blk * 4 + j], 0u, qa2[blk * 4 + j], 0u, e4m3x2_to_f16x2(wa[j] & 0xffffu),
-                     e4m3x2_to_f16x2(wa[j] >> 16));
-            mma16816(s1, qa0[blk * 4 + j], 0u, qa2[blk * 4 + j], 0u, e4m3x2_to_f16x2(wb[j] & 0xffffu),
-                     e4m3x2_to_f16x2(wb[j] >> 16));
+            mma16816(s0, qa0[blk * 4 + j], 0u, qa2[blk * 4 + j], 0u, kv2_to_f16x2<I8>(wa[j] & 0xffffu),
+                     kv2_to_f16x2<I8>(wa[j] >> 16));
+            mma16816(s1, qa0[blk * 4 + j], 0u, qa2[blk * 4 + j], 0u, kv2_to_f16x2<I8>(wb[j] & 0xffffu),
+                     kv2_to_f16x2<I8>(wb[j] >> 16));
           }
         }
         // s0[0..1]: (row g, tokens tk0+2t, +1); s1[0..1]: (row g, tokens tk0+8+2t, +1)
         float sv[4] = {s0[0], s0[1], s1[0], s1[1]};
         const int tk[4] = {tk0 + 2 * t, tk0 + 2 * t + 1, tk0 + 8 + 2 * t, tk0 + 9 + 2 * t};
+        float vsc[4] = {1.f, 1.f, 1.f, 1.f};
+        if (I8) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const size_t si = ((size_t)page * PAGE + (tk[i] - tk0)) * p.hkv + kvh;
+            sv[i] *= p.k_scale[si];
+            vsc[i] = p.v_scale[si];
+          }
+        }
         float mx = -INFINITY;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -238,7 +271,7 @@ __global__ void __launch_bounds__(AT_WARPS * 32) paged_attn_kernel(AttnParams p)
         l_run = l_run * alpha + ps;
         m_run = m_new;
         // P^T as the B operand: b0 = (tokens 2t,2t+1 ; row g), b1 = (tokens 8+2t, 9+2t ; row g)
-        const uint32_t pb0 = pack_f16(sv[0], sv[1]), pb1 = pack_f16(sv[2], sv[3]);
+        const uint32_t pb0 = pack_f16(sv[0] * vsc[0], sv[1] * vsc[1]), pb1 = pack_f16(sv[2] * vsc[2], sv[3] * vsc[3]);
         // rescale factors for the O^T columns (rows 2t, 2t+1)
         const float al0 = __shfl_sync(0xffffffffu, alpha, (2 * t) * 4);
         const float al1 = __shfl_sync(0xffffffffu, alpha, (2 * t + 1) * 4);
@@ -251,10 +284,10 @@ __global__ void __launch_bounds__(AT_WARPS * 32) paged_attn_kernel(AttnParams p)
             // m-tile rows: g -> dim blk*32 + g*4 + ip*2, g+8 -> that + 1
             const uint32_t selA = ip ? 0x0062u : 0x0040u;  // bytes (x.b[2ip], y.b[2ip])
             const uint32_t selB = ip ? 0x0073u : 0x0051u;  // bytes (x.b[2ip+1], y.b[2ip+1])
-            const uint32_t a0 = e4m3x2_to_f16x2(__byte_perm(va[blk], vb[blk], selA) & 0xffffu);
-            const uint32_t a1 = e4m3x2_to_f16x2(__byte_perm(va[blk], vb[blk], selB) & 0xffffu);
-            const uint32_t a2 = e4m3x2_to_f16x2(__byte_perm(vc[blk], vd[blk], selA) & 0xffffu);
-            const uint32_t a3 = e4m3x2_to_f16x2(__byte_perm(vc[blk], vd[blk], selB) & 0xffffu);
+            const uint32_t a0 = kv2_to_f16x2<I8>(__byte_perm(va[blk], vb[blk], selA) & 0xffffu);
+            const uint32_t a1 = kv2_to_f16x2<I8>(__byte_perm(va[blk], vb[blk], selB) & 0xffffu);
+            const uint32_t a2 = kv2_to_f16x2<I8>(__byte_perm(vc[blk], vd[blk], selA) & 0xffffu);
+            const uint32_t a3 = kv2_to_f16x2<I8>(__byte_perm(vc[blk], vd[blk], selB) & 0xffffu);
             mma16816(c, a0, a1, a2, a3, pb0, pb1);
           }
         }
@@ -377,18 +410,18 @@ __global__ void __launch_bounds__(256) attn_reduce_kernel(const float* __restric
 }  // namespace owl
 using namespace owl;
 
-OWL_API int owl_qknorm_rope_insert(const void* qraw, int ldq, const void* kraw, int ldk, const void* vraw, int ldv,
-                                   const void* qnorm_w, const void* knorm_w, const void* pos3, const void* inv_freq,
-                                   const void* section, const void* kv_slot, void* q_out, void* k_pool, void* v_pool,
-                                   int rows, int hq, int hkv, int hd, int rot, float eps, float rope_scale, int pdl,
-                                   cudaStream_t st) {
+static int insert_launch(const void* qraw, int ldq, const void* kraw, int ldk, const void* vraw, int ldv, const void* qnorm_w,
+                         const void* knorm_w, const void* pos3, const void* inv_freq, const void* section, const void* kv_slot,
+                         void* q_out, void* k_pool, void* v_pool, void* k_scale, void* v_scale, int rows, int hq, int hkv, int hd,
+                         int rot, float eps, float rope_scale, int pdl, cudaStream_t st) {
   if (rows < 1 || hd > 256 || (hd & 1) || rot > hd || (rot & 3)) return OWL_ERR_BAD_ARG;
   InsertParams p;
   p.qraw = (const __nv_bfloat16*)qraw; p.ldq = ldq; p.kraw = (const __nv_bfloat16*)kraw; p.ldk = ldk;
   p.vraw = (const __nv_bfloat16*)vraw; p.ldv = ldv; p.qnorm_w = (const __nv_bfloat16*)qnorm_w;
   p.knorm_w = (const __nv_bfloat16*)knorm_w; p.pos3 = (const int*)pos3; p.inv_freq = (const float*)inv_freq;
   p.section = (const unsigned char*)section; p.kv_slot = (const int*)kv_slot; p.q_out = (__nv_bfloat16*)q_out;
-  p.k_pool = (uint8_t*)k_pool; p.v_pool = (uint8_t*)v_pool; p.rows = rows; p.hq = hq; p.hkv = hkv; p.hd = hd;
+  p.k_pool = (uint8_t*)k_pool; p.v_pool = (uint8_t*)v_pool; p.k_scale = (float*)k_scale; p.v_scale = (float*)v_scale;
+  p.rows = rows; p.hq = hq; p.hkv = hkv; p.hd = hd;
   p.rot = rot; p.eps = eps; p.rope_scale = rope_scale;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(rows, hq + 2 * hkv); cfg.blockDim = dim3(128); cfg.stream = st;
@@ -401,14 +434,35 @@ OWL_API int owl_qknorm_rope_insert(const void* qraw, int ldq, const void* kraw, 
   return OWL_OK;
 }
 
-// part_o: float[groups*T*hq*splits*256], part_ml: float[groups*T*hq*splits*2].
-OWL_API int owl_paged_attn(const void* q, const void* k_pool, const void* v_pool, const void* block_table,
-                           const void* bt_row, const void* ctx_len, void* part_o, void* part_ml, int groups, int T,
-                           int hq, int hkv, int hd, int max_blocks, int splits, int per_pages, float scale, int pdl,
-                           cudaStream_t st) {
+OWL_API int owl_qknorm_rope_insert(const void* qraw, int ldq, const void* kraw, int ldk, const void* vraw, int ldv,
+                                   const void* qnorm_w, const void* knorm_w, const void* pos3, const void* inv_freq,
+                                   const void* section, const void* kv_slot, void* q_out, void* k_pool, void* v_pool,
+                                   int rows, int hq, int hkv, int hd, int rot, float eps, float rope_scale, int pdl,
+                                   cudaStream_t st) {
+  return insert_launch(qraw, ldq, kraw, ldk, vraw, ldv, qnorm_w, knorm_w, pos3, inv_freq, section, kv_slot, q_out, k_pool, v_pool,
+                       nullptr, nullptr, rows, hq, hkv, hd, rot, eps, rope_scale, pdl, st);
+}
+
+// int8 KV pool: values rounded to int8 with one fp32 scale per (token, kv head) in k_scale / v_scale [pages][16][hkv].
+OWL_API int owl_qknorm_rope_insert_i8(const void* qraw, int ldq, const void* kraw, int ldk, const void* vraw, int ldv,
+                                      const void* qnorm_w, const void* knorm_w, const void* pos3, const void* inv_freq,
+                                      const void* section, const void* kv_slot, void* q_out, void* k_pool, void* v_pool,
+                                      void* k_scale, void* v_scale, int rows, int hq, int hkv, int hd, int rot, float eps,
+                                      float rope_scale, int pdl, cudaStream_t st) {
+  if (!k_scale || !v_scale) return OWL_ERR_BAD_ARG;
+  return insert_launch(qraw, ldq, kraw, ldk, vraw, ldv, qnorm_w, knorm_w, pos3, inv_freq, section, kv_slot, q_out, k_pool, v_pool,
+                       k_scale, v_scale, rows, hq, hkv, hd, rot, eps, rope_scale, pdl, st);
+}
+
+template <bool I8>
+static int attn_launch(const void* q, const void* k_pool, const void* v_pool, const void* k_scale, const void* v_scale,
+                       const void* block_table, const void* bt_row, const void* ctx_len, void* part_o, void* part_ml, int groups,
+                       int T, int hq, int hkv, int hd, int max_blocks, int splits, int per_pages, float scale, int pdl,
+                       cudaStream_t st) {
   if (hd != HD || groups < 1 || T < 1 || T > 8 || hq % hkv || hq / hkv > 8 || splits < 1) return OWL_ERR_BAD_ARG;
   AttnParams p;
   p.q = (const __nv_bfloat16*)q; p.k_pool = (const uint8_t*)k_pool; p.v_pool = (const uint8_t*)v_pool;
+  p.k_scale = (const float*)k_scale; p.v_scale = (const float*)v_scale;
   p.block_table = (const int*)block_table; p.bt_row = (const int*)bt_row; p.ctx_len = (const int*)ctx_len;
   p.part_o = (float*)part_o; p.part_ml = (float*)part_ml; p.T = T; p.hq = hq; p.hkv = hkv;
   p.max_blocks = max_blocks; p.splits = splits; p.per_pages = per_pages; p.scale_log2 = scale * 1.4426950408889634f;
@@ -420,12 +474,31 @@ OWL_API int owl_paged_attn(const void* q, const void* k_pool, const void* v_pool
   cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
   cudaError_t e;
   // per_pages > 0 asks for arithmetic that does not depend on T: one warp per row (no token split inside a CTA)
-  if (per_pages > 0) e = cudaLaunchKernelEx(&cfg, paged_attn_kernel<4>, p);
-  else if (T == 1) e = cudaLaunchKernelEx(&cfg, paged_attn_kernel<1>, p);
-  else if (T == 2) e = cudaLaunchKernelEx(&cfg, paged_attn_kernel<2>, p);
-  else e = cudaLaunchKernelEx(&cfg, paged_attn_kernel<4>, p);
+  if (per_pages > 0) e = cudaLaunchKernelEx(&cfg, paged_attn_kernel<4, I8>, p);
+  else if (T == 1) e = cudaLaunchKernelEx(&cfg, paged_attn_kernel<1, I8>, p);
+  else if (T == 2) e = cudaLaunchKernelEx(&cfg, paged_attn_kernel<2, I8>, p);
+  else e = cudaLaunchKernelEx(&cfg, paged_attn_kernel<4, I8>, p);
   if (e != cudaSuccess) return (int)OWL_ERR_LAUNCH * 1000 - (int)e;
   return OWL_OK;
+}
+
+// part_o: float[groups*T*hq*splits*256], part_ml: float[groups*T*hq*splits*2].
+OWL_API int owl_paged_attn(const void* q, const void* k_pool, const void* v_pool, const void* block_table,
+                           const void* bt_row, const void* ctx_len, void* part_o, void* part_ml, int groups, int T,
+                           int hq, int hkv, int hd, int max_blocks, int splits, int per_pages, float scale, int pdl,
+                           cudaStream_t st) {
+  return attn_launch<false>(q, k_pool, v_pool, nullptr, nullptr, block_table, bt_row, ctx_len, part_o, part_ml, groups, T, hq, hkv,
+                            hd, max_blocks, splits, per_pages, scale, pdl, st);
+}
+
+// The same attention over an int8 pool with per (token, kv head) scales.
+OWL_API int owl_paged_attn_i8(const void* q, const void* k_pool, const void* v_pool, const void* k_scale, const void* v_scale,
+                              const void* block_table, const void* bt_row, const void* ctx_len, void* part_o, void* part_ml,
+                              int groups, int T, int hq, int hkv, int hd, int max_blocks, int splits, int per_pages, float scale,
+                              int pdl, cudaStream_t st) {
+  if (!k_scale || !v_scale) return OWL_ERR_BAD_ARG;
+  return attn_launch<true>(q, k_pool, v_pool, k_scale, v_scale, block_table, bt_row, ctx_len, part_o, part_ml, groups, T, hq, hkv,
+                           hd, max_blocks, splits, per_pages, scale, pdl, st);
 }
 
 OWL_API int owl_attn_reduce(const void* part_o, const void* part_ml, int splits, const void* qraw, int ldq, void* out,

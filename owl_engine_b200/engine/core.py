@@ -43,6 +43,7 @@ class EngineConfig:
     decode_gemv: str = "dp4a"      # W4 decode arm: "dp4a" (legacy streaming kernels) or "tc" (tcgen05 streaming kernel)
     seed: int = 0
     n_layers: int | None = None    # override (tests / smoke)
+    kv_dtype: str = "fp8"          # KV pool format: "fp8" (e4m3) or "int8" (per token, per head scales)
     kvmem_budget: int = 0          # tokens of KV a decode step may attend to (0 = everything): longer contexts attend to a
                                    # view of sink + recent + best-scoring blocks, re-selected at every block boundary
     kvmem_sink: int = 2
@@ -90,7 +91,9 @@ class Engine:
                                                    lm_head_int8=cfg.lm_head_int8,
                                                    layout="block" if cfg.decode_gemv == "tc" else "slice")
         # GDN rows: one per sequence slot, the prefix-snapshot rows, and one scratch row for speculative rollback
-        self.pool = H.StatePool(self.spec, self.device, cfg.n_pages, cfg.n_slots + cfg.n_snap_rows + 1)
+        if cfg.kv_dtype != "fp8" and cfg.kvmem_budget:
+            raise ValueError("KV selection reads the e4m3 pool: kvmem_budget needs kv_dtype = \"fp8\"")
+        self.pool = H.StatePool(self.spec, self.device, cfg.n_pages, cfg.n_slots + cfg.n_snap_rows + 1, kv_dtype=cfg.kv_dtype)
         self.spec_row = cfg.n_slots + cfg.n_snap_rows
         self.max_blocks = (cfg.max_seq + PAGE - 1) // PAGE
         self.runner = H.HybridRunner(self.spec, self.weights, self.pool, max_seqs=cfg.max_seqs * (2 if cfg.kvmem_budget else 1),
@@ -224,31 +227,44 @@ class Engine:
             m, pages, carriers = self.kv.match(seq.chain)
             snap = self.states.find(seq.chain[:m]) if m else None
             keep = snap.n_tokens // PAGE if snap else 0
+            promoted = set()
+            keep0 = keep
             for i in range(keep):                              # promote demoted blocks of the kept prefix
-                if carriers[i] != 0:
-                    h = int(seq.chain[i])
-                    if self.disk is not None and h in self.disk.index and h not in self.host_slot_of:
-                        # disk -> pinned host staging slot (then host -> device below)
-                        if not self.host.free:
-                            self._spill_host(1)
-                        slot = self.host.alloc()
-                        if slot is not None:
-                            self._mover_sync()                 # no copy still reads the recycled slot
-                            self.disk.fill(h, self.host.slot(slot))
-                            self.disk.drop(h)
-                            self.host_slot_of[h] = slot
-                            self.recalled += 1
-                    pg = self.kv.alloc(1)
-                    if pg is None or h not in self.host_slot_of:
-                        keep = i
-                        break
-                    self.mover.copy_in(self.host_slot_of[h], pg[0])
-                    self.kv.set_carrier(h, 0, pg[0])
-                    self.host.release(self.host_slot_of.pop(h))
-                    pages[i] = pg[0]                           # alloc's reference is the sequence's
+                if carriers[i] == 0:
+                    continue
+                h = int(seq.chain[i])
+                try:
+                    pg = self._alloc_pages(1)                  # may push other cold blocks down a tier
+                except RuntimeError:
+                    pg = None
+                if pg is not None and h not in self.host_slot_of and self.disk is not None and h in self.disk.index:
+                    # disk -> pinned host staging slot (then host -> device below)
+                    if not self.host.free:
+                        self._spill_host(1)
+                    hslot = self.host.alloc()
+                    if hslot is not None:
+                        self._mover_sync()                     # no copy still reads the recycled slot
+                        self.disk.fill(h, self.host.slot(hslot))
+                        self.disk.drop(h)
+                        self.host_slot_of[h] = hslot
+                        self.recalled += 1
+                if pg is None or h not in self.host_slot_of:
+                    if pg is not None:
+                        self.kv.unref(pg)
+                    keep = i
+                    break
+                self.mover.copy_in(self.host_slot_of[h], pg[0])
+                self.kv.set_carrier(h, 0, pg[0])
+                self.host.release(self.host_slot_of.pop(h))
+                pages[i] = pg[0]                               # alloc's reference is the sequence's
+                promoted.add(i)
             if self.mover:
                 self.mover.fence()
-            self.kv.unref([p for p, c in zip(pages[keep:m], carriers[keep:m]) if c == 0])
+            if keep < keep0:
+                # the recurrent state must match the KV prefix: fall back to the longest snapshot inside what is resident
+                snap = self.states.find(seq.chain[:keep]) if keep else None
+                keep = snap.n_tokens // PAGE if snap else 0
+            self.kv.unref([p for j, (p, c) in enumerate(zip(pages[:m], carriers[:m])) if j >= keep and (c == 0 or j in promoted)])
             if keep:
                 seq.pages = pages[:keep]
                 self.runner.block_table[seq.row, :keep] = torch.tensor(seq.pages, dtype=torch.int32, device=self.device)

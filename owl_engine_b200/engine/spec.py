@@ -116,13 +116,35 @@ class OracleDraft:
 class MtpDraft:
     """The MTP head as draft source (``models/mtp.py``); optionally overridden by a suffix lookup."""
 
-    def __init__(self, head, lookup: LookupDraft | None = None):
-        self.head, self.lookup = head, lookup
+    def __init__(self, head, lookup: LookupDraft | None = None, window: int = 8192):
+        self.head, self.lookup, self.window = head, lookup, window
         self.ready: dict = {}        # sid -> True once the head has absorbed the row before the anchor
+        self._chunks: list = []      # (pos0, t, last-layer hiddens) of the prompt chunks just prefetched
+        t = head.target
+        self._tap = t.spec.n_layers - 1
+        if t.taps is None:
+            t.taps = {}
+        t.taps.setdefault("prefill", {})
+        t.taps.setdefault(self._tap, torch.zeros(t.MAX_ROWS, t.spec.hidden, dtype=torch.bfloat16, device=t.device))
+        t.tap_sink = self._on_chunk
+        t.graphs.clear()
+
+    def _on_chunk(self, pos0: int, t: int, taps: dict) -> None:
+        """Keep the target's final hiddens of the prompt chunks (the most recent ``window`` positions)."""
+        self._chunks.append((pos0, t, taps[self._tap]))
+        while len(self._chunks) > 1 and sum(c[1] for c in self._chunks[1:]) >= self.window:
+            self._chunks.pop(0)
 
     def after_prefill(self, engine: Engine, sid: int) -> None:
-        """Absorb the last prompt row: (first generated token, hidden of the last prompt position)."""
+        """Fill the head's KV for the prompt (every row but the last, chunk by chunk on the GEMM path), then absorb the
+        last prompt row: (first generated token, hidden of the last prompt position)."""
         seq = engine.seqs[sid]
+        for pos0, t, h in self._chunks:
+            n = t - 1 if pos0 + t >= seq.n_cached else t
+            if n > 0 and pos0 + n < len(seq.tokens):
+                nxt = torch.tensor(seq.tokens[pos0 + 1:pos0 + n + 1], dtype=torch.int32, device=engine.device)
+                self.head.absorb_prefill(nxt, h[:n], pos0, seq.row)
+        self._chunks.clear()
         q = seq.n_cached - 1
         self.head.absorb([seq.tokens[-1]], engine.runner.h[:1], q, seq.row, seq.pages)
         self.ready[sid] = True

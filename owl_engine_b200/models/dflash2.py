@@ -218,7 +218,7 @@ class DraftLayer:
     conv_a_proj: Q.DenseSkinny
     conv_m_base: torch.Tensor
     conv_m_proj: Q.DenseSkinny
-    gate_up: Q.DenseSkinny
+    gate_up: Q.DenseSkinny        # gate / up rows interleaved in eights (the order the activation kernel reads)
     down: Q.DenseSkinny
 
 
@@ -255,7 +255,7 @@ def weights_from_dense(spec: DraftSpec, w: dict, device) -> DraftWeights:
             q_norm=bf(w[p + "self_attn.q_norm.weight"]), k_norm=bf(w[p + "self_attn.k_norm.weight"]),
             conv_a_base=bf(w[p + "attention_conv.base_kernel"]), conv_a_proj=rec(w[p + "attention_conv.kernel_projection.weight"]),
             conv_m_base=bf(w[p + "mlp_conv.base_kernel"]), conv_m_proj=rec(w[p + "mlp_conv.kernel_projection.weight"]),
-            gate_up=rec(torch.cat([w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"]], 0)),
+            gate_up=rec(Q.interleave_gate_up(w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"])),   # order of silu_mul
             down=rec(w[p + "mlp.down_proj.weight"])))
     out.sel_proj = rec(w["selector.hidden_projection.weight"])
     out.a_tab, out.b_tab = bf(w["selector.predecessor_codebook"]), bf(w["selector.successor_codebook"])
@@ -345,14 +345,17 @@ class DFlash2:
         else:
             gemm_tc.f16_gemm(taps, w.fc, mem)
         K.rmsnorm_pack(mem, w.hidden_norm, normed=memn, m=t, k=sp.hidden, eps=sp.eps, one_plus_w=False)
-        self.e_pos[:t] = torch.arange(pos0, pos0 + t, dtype=torch.int32, device=self.device)
-        self.e_slot[:t] = self.e_pos[:t] % sp.window
+        lo = max(0, t - sp.window)          # rows older than the window would only race with their successors for a slot
+        n = t - lo
+        self.e_pos[:n] = torch.arange(pos0 + lo, pos0 + t, dtype=torch.int32, device=self.device)
+        self.e_slot[:n] = self.e_pos[:n] % sp.window
         nk = sp.hkv * sp.hd
+        kv = kv[:n]
         for i, lw in enumerate(w.layers):
-            gemm_tc.f16_gemm(memn, lw.kv_dense, kv, force_small=True)
+            gemm_tc.f16_gemm(memn[lo:], lw.kv_dense, kv, force_small=True)
             K.call("owl_dflash_norm_rope", K.ptr(kv), kv.stride(0), K.ptr(kv[:, nk:]), kv.stride(0), K.ptr(lw.k_norm),
                    K.ptr(self.e_pos), K.ptr(self.inv_freq), None, K.ptr(self.ring_k[i]), K.ptr(self.ring_v[i]),
-                   K.ptr(self.e_slot), t, sp.hkv, sp.eps, 0, K.stream())
+                   K.ptr(self.e_slot), n, sp.hkv, sp.eps, 0, K.stream())
         self.n_seen = pos0 + t
         self.prefix_len.fill_(min(self.n_seen, sp.window))
 

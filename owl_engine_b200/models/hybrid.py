@@ -216,11 +216,18 @@ class StatePool:
     """Device state: paged fp8 KV (``[layer][page][16][hkv][hd]`` e4m3, zero-initialised so that
     masked slots never hold NaN encodings), GDN convolution history and recurrent state rows."""
 
-    def __init__(self, spec: ModelSpec, device, n_pages: int, n_slots: int, ledger=None):
-        self.spec, self.device, self.n_pages, self.n_slots = spec, device, n_pages, n_slots
+    def __init__(self, spec: ModelSpec, device, n_pages: int, n_slots: int, ledger=None, kv_dtype: str = "fp8"):
+        """``kv_dtype`` "fp8": e4m3 values (no scales); "int8": int8 values with one fp32 scale per (token, kv head) in
+        ``k_scale`` / ``v_scale`` (the reference's int8 KV family, crates/kernels/cu/attn int8 kernels)."""
+        assert kv_dtype in ("fp8", "int8")
+        self.spec, self.device, self.n_pages, self.n_slots, self.kv_dtype = spec, device, n_pages, n_slots, kv_dtype
         nf, ng = spec.n_full, spec.n_gdn
         self.k_pool = torch.zeros(nf, n_pages, PAGE, spec.hkv, spec.hd, dtype=torch.uint8, device=device)
         self.v_pool = torch.zeros(nf, n_pages, PAGE, spec.hkv, spec.hd, dtype=torch.uint8, device=device)
+        self.k_scale = self.v_scale = None
+        if kv_dtype == "int8":
+            self.k_scale = torch.zeros(nf, n_pages, PAGE, spec.hkv, dtype=torch.float32, device=device)
+            self.v_scale = torch.zeros(nf, n_pages, PAGE, spec.hkv, dtype=torch.float32, device=device)
         self.conv_state = torch.zeros(ng, n_slots, spec.conv_dim, spec.conv_k - 1, dtype=torch.float32, device=device)
         self.rec_state = torch.zeros(ng, n_slots, spec.nv, spec.kd, spec.vd, dtype=torch.float32, device=device)
         if ledger is not None:
@@ -234,6 +241,10 @@ class StatePool:
     @staticmethod
     def bytes_per_slot(spec: ModelSpec) -> int:
         return spec.gdn_state_bytes()
+
+    def scales(self, layer: int):
+        """(k_scale, v_scale) of one full-attention layer for the int8 pool, None for the e4m3 pool."""
+        return None if self.k_scale is None else (self.k_scale[layer], self.v_scale[layer])
 
     def reset_slot(self, slot: int) -> None:
         self.conv_state[:, slot].zero_()
@@ -424,10 +435,10 @@ class HybridRunner:
         K.qknorm_rope_insert(self.qkv_out, self.qkv_n, kraw, self.qkv_n, vraw, self.qkv_n, lw.q_norm, lw.k_norm,
                              v["pos3"], self.inv_freq, self.section, v["kv_slot"], self.q_rope, self.pool.k_pool[li],
                              self.pool.v_pool[li], m, sp.hq, sp.hkv, sp.hd, sp.rotary_dim, sp.eps, self.rope_scale,
-                             pdl=self.pdl)
+                             pdl=self.pdl, scales=self.pool.scales(li))
         K.paged_attn(self.q_rope, self.pool.k_pool[li], self.pool.v_pool[li], self.block_table, v["bt_row"], v["ctx"],
                      self.part_o, self.part_ml, lay.b, lay.t, sp.hq, sp.hkv, sp.hd, self.max_blocks, splits, self.scale,
-                     pdl=self.pdl,
+                     pdl=self.pdl, scales=self.pool.scales(li),
                      per_pages=((ctx_hint + PAGE - 1) // PAGE + splits - 1) // splits if self.uniform_rows and ctx_hint else 0)
         K.attn_reduce(self.part_o, self.part_ml, splits, self.qkv_out, self.qkv_n, m, sp.hq, xpack=self.xp_a,
                       xs=self.xs_a, group=self._grp(), pdl=self.pdl)
@@ -641,15 +652,16 @@ class HybridRunner:
                 K.qknorm_rope_insert(wide, self.qkv_n, wide[:, qn:], self.qkv_n, wide[:, qn + sp.hkv * sp.hd:],
                                      self.qkv_n, lw.q_norm, lw.k_norm, pos3_v, self.inv_freq, self.section, kv_slot,
                                      ws["q"], pool.k_pool[fi], pool.v_pool[fi], t, sp.hq, sp.hkv, sp.hd, sp.rotary_dim,
-                                     sp.eps, self.rope_scale)
+                                     sp.eps, self.rope_scale, scales=pool.scales(fi))
                 if ng:
                     K.paged_attn(ws["q"], pool.k_pool[fi], pool.v_pool[fi], self.block_table, ws["bt_row"], ws["ctx"],
-                                 ws["part_o"], ws["part_ml"], ng, 8, sp.hq, sp.hkv, sp.hd, self.max_blocks, 1, self.scale)
+                                 ws["part_o"], ws["part_ml"], ng, 8, sp.hq, sp.hkv, sp.hd, self.max_blocks, 1, self.scale,
+                                 scales=pool.scales(fi))
                 if tail:
                     off = ng * 8
                     K.paged_attn(ws["q"][off:], pool.k_pool[fi], pool.v_pool[fi], self.block_table, ws["bt_row"][ng:],
                                  ws["ctx"][ng:], ws["part_o"][off * sp.hq * sp.hd:], ws["part_ml"][off * sp.hq * 2:], 1,
-                                 tail, sp.hq, sp.hkv, sp.hd, self.max_blocks, 1, self.scale)
+                                 tail, sp.hq, sp.hkv, sp.hd, self.max_blocks, 1, self.scale, scales=pool.scales(fi))
                 mix = ws["mix"].view(-1)[:t * sp.hq * sp.hd].view(t, sp.hq * sp.hd)
                 K.attn_reduce(ws["part_o"], ws["part_ml"], 1, wide, self.qkv_n, t, sp.hq, out=mix, group=self.G)
                 self._gemm(lw.o_proj, mix, ws["y"][:t])
@@ -749,15 +761,16 @@ class HybridRunner:
                 K.qknorm_rope_insert(wide, self.qkv_n, wide[:, qn:], self.qkv_n, wide[:, qn + sp.hkv * sp.hd:],
                                      self.qkv_n, lw.q_norm, lw.k_norm, pos3_v, self.inv_freq, self.section, kv_slot,
                                      ws["q"], pool.k_pool[fi], pool.v_pool[fi], t, sp.hq, sp.hkv, sp.hd, sp.rotary_dim,
-                                     sp.eps, self.rope_scale)
+                                     sp.eps, self.rope_scale, scales=pool.scales(fi))
                 if ng:
                     K.paged_attn(ws["q"], pool.k_pool[fi], pool.v_pool[fi], self.block_table, ws["bt_row"], ws["ctx"],
-                                 ws["part_o"], ws["part_ml"], ng, 8, sp.hq, sp.hkv, sp.hd, self.max_blocks, 1, self.scale)
+                                 ws["part_o"], ws["part_ml"], ng, 8, sp.hq, sp.hkv, sp.hd, self.max_blocks, 1, self.scale,
+                                 scales=pool.scales(fi))
                 if tail:
                     off = ng * 8
                     K.paged_attn(ws["q"][off:], pool.k_pool[fi], pool.v_pool[fi], self.block_table, ws["bt_row"][ng:],
                                  ws["ctx"][ng:], ws["part_o"][off * sp.hq * sp.hd:], ws["part_ml"][off * sp.hq * 2:], 1,
-                                 tail, sp.hq, sp.hkv, sp.hd, self.max_blocks, 1, self.scale)
+                                 tail, sp.hq, sp.hkv, sp.hd, self.max_blocks, 1, self.scale, scales=pool.scales(fi))
                 mix = ws["mix"].view(-1)[:t * sp.hq * sp.hd].view(t, sp.hq * sp.hd)
                 K.attn_reduce(ws["part_o"], ws["part_ml"], 1, wide, self.qkv_n, t, sp.hq, out=mix, group=self.G)
                 pipe.gemm_rs(mix, dense(lw.o_proj), t)

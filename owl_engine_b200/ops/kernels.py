@@ -34,6 +34,9 @@ _SIGS = {
     "owl_qknorm_rope_insert": [_P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F,
                                _F, _I, _P],
     "owl_paged_attn": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+    "owl_qknorm_rope_insert_i8": [_P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F,
+                                  _F, _I, _P],
+    "owl_paged_attn_i8": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "owl_decode_advance": [_P, _P, _P, _I, _I, _I, _P],
     "owl_w4_dequant": [_P, _P, _I, _I, _I, _I, _I, _P],
     "owl_attn_reduce": [_P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _P],
@@ -224,15 +227,27 @@ def gdn_scan(qkv, z, ldz: int, ab, ldab: int, a_log, dt_bias, gamma, state, slot
 
 def qknorm_rope_insert(qraw, ldq: int, kraw, ldk: int, vraw, ldv: int, qnorm_w, knorm_w, pos3, inv_freq, section,
                        kv_slot, q_out, k_pool, v_pool, rows: int, hq: int, hkv: int, hd: int, rot: int,
-                       eps: float = 1e-6, rope_scale: float = 1.0, pdl: bool = False) -> None:
+                       eps: float = 1e-6, rope_scale: float = 1.0, pdl: bool = False, scales=None) -> None:
+    """``scales`` = (k_scale, v_scale) fp32 [pages, 16, hkv] selects the int8 pool form."""
+    if scales is not None:
+        call("owl_qknorm_rope_insert_i8", ptr(qraw), ldq, ptr(kraw), ldk, ptr(vraw), ldv, ptr(qnorm_w), ptr(knorm_w),
+             ptr(pos3), ptr(inv_freq), ptr(section), ptr(kv_slot), ptr(q_out), ptr(k_pool), ptr(v_pool), ptr(scales[0]),
+             ptr(scales[1]), rows, hq, hkv, hd, rot, eps, rope_scale, int(pdl), stream())
+        return
     call("owl_qknorm_rope_insert", ptr(qraw), ldq, ptr(kraw), ldk, ptr(vraw), ldv, ptr(qnorm_w), ptr(knorm_w),
          ptr(pos3), ptr(inv_freq), ptr(section), ptr(kv_slot), ptr(q_out), ptr(k_pool), ptr(v_pool), rows, hq, hkv,
          hd, rot, eps, rope_scale, int(pdl), stream())
 
 
 def paged_attn(q, k_pool, v_pool, block_table, bt_row, ctx_len, part_o, part_ml, groups: int, t: int, hq: int,
-               hkv: int, hd: int, max_blocks: int, splits: int, scale: float, pdl: bool = False, per_pages: int = 0) -> None:
+               hkv: int, hd: int, max_blocks: int, splits: int, scale: float, pdl: bool = False, per_pages: int = 0,
+               scales=None) -> None:
     """``per_pages`` > 0 fixes the pages per KV split (must satisfy splits * per_pages >= pages of the longest row)."""
+    if scales is not None:
+        call("owl_paged_attn_i8", ptr(q), ptr(k_pool), ptr(v_pool), ptr(scales[0]), ptr(scales[1]), ptr(block_table),
+             ptr(bt_row), ptr(ctx_len), ptr(part_o), ptr(part_ml), groups, t, hq, hkv, hd, max_blocks, splits, per_pages, scale,
+             int(pdl), stream())
+        return
     call("owl_paged_attn", ptr(q), ptr(k_pool), ptr(v_pool), ptr(block_table), ptr(bt_row), ptr(ctx_len), ptr(part_o),
          ptr(part_ml), groups, t, hq, hkv, hd, max_blocks, splits, per_pages, scale, int(pdl), stream())
 

@@ -84,9 +84,6 @@ def w4_dense(w, dtype, device) -> torch.Tensor:
     return K.w4_dequant(w, _dense_scratch(w.n, w.k, device, dtype))
 
 
-_w16: dict = {}
-
-
 def dense_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, arm: str = "tc") -> torch.Tensor:
     """out[T, N] (bf16) = x @ w^T for a small dense bf16 weight (GDN a/b projections, draft heads)."""
     if arm == "baseline":
@@ -95,10 +92,11 @@ def dense_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, arm: str = "
     from . import gemm_tc
 
     if x.dtype != w.dtype:
-        key = (w.data_ptr(), x.dtype)
-        wc = _w16.get(key)
-        if wc is None:
-            wc = w.to(x.dtype)
-            _w16[key] = wc
-        w = wc
+        # the converted copy lives on the weight tensor itself (a cache keyed by address would hand a stale copy to the
+        # next tensor allocated at that address)
+        cache = getattr(w, "_owl_cast", None)
+        if cache is None or cache.dtype != x.dtype:
+            cache = w.to(x.dtype)
+            w._owl_cast = cache
+        w = cache
     return gemm_tc.f16_gemm(x, w, out)

@@ -38,7 +38,8 @@ def build_engine_factory(cfg: C.OwlConfig):
                             max_seqs=max(v["store.gdn"]["gdn_slots"], v["runtime"]["max_batch"]), max_seq=v["runtime"]["max_seq"],
                             prefill_chunk=v["runtime"]["prefill_chunk"], pdl=v["kernel"]["pdl"],
                             prefill_gemm=v["kernel"]["prefill_gemm"], host_cache_mb=v["store"]["host_cache_mb"],
-                            disk_cache_mb=v["store"]["disk_cache_mb"], disk_dir=v["store"]["disk_dir"])
+                            disk_cache_mb=v["store"]["disk_cache_mb"], disk_dir=v["store"]["disk_dir"],
+                            kv_dtype=v["store.kv"]["kv_dtype"])
         if v["kernel"]["selfcheck"]:
             from ..ops import selfcheck
 

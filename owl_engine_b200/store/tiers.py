@@ -51,13 +51,17 @@ class HostTier:
 
 
 def page_views(pool, page: int):
-    """The device slabs of one KV page: (k_pool[:, page], v_pool[:, page]) as byte views."""
-    return pool.k_pool[:, page].reshape(pool.k_pool.shape[0], -1), pool.v_pool[:, page].reshape(pool.v_pool.shape[0], -1)
+    """The device slabs of one KV page as byte views: k_pool[:, page], v_pool[:, page] and, for the int8 pool, the
+    page's scale slabs."""
+    views = [pool.k_pool[:, page].reshape(pool.k_pool.shape[0], -1), pool.v_pool[:, page].reshape(pool.v_pool.shape[0], -1)]
+    for sc in (getattr(pool, "k_scale", None), getattr(pool, "v_scale", None)):
+        if sc is not None:
+            views.append(sc[:, page].reshape(sc.shape[0], -1).view(torch.uint8))
+    return views
 
 
 def page_bytes(pool) -> int:
-    k, v = page_views(pool, 0)
-    return int(k.numel() + v.numel())
+    return int(sum(v.numel() for v in page_views(pool, 0)))
 
 
 class Mover:
@@ -69,26 +73,26 @@ class Mover:
         self.bytes_out = self.bytes_in = 0
 
     def copy_out(self, page: int, slot: int) -> None:
-        k, v = page_views(self.pool, page)
         dst = self.host.slot(slot)
-        nk = k.numel()
         ctx = torch.cuda.stream(self.stream) if self.stream else _null()
         with ctx:
             if self.stream:
                 self.stream.wait_stream(torch.cuda.current_stream())
-            dst[:nk].view_as(k).copy_(k, non_blocking=True)
-            dst[nk:nk + v.numel()].view_as(v).copy_(v, non_blocking=True)
-        self.bytes_out += nk + v.numel()
+            off = 0
+            for v in page_views(self.pool, page):
+                dst[off:off + v.numel()].view_as(v).copy_(v, non_blocking=True)
+                off += v.numel()
+        self.bytes_out += off
 
     def copy_in(self, slot: int, page: int) -> None:
-        k, v = page_views(self.pool, page)
         src = self.host.slot(slot)
-        nk = k.numel()
         ctx = torch.cuda.stream(self.stream) if self.stream else _null()
         with ctx:
-            k.copy_(src[:nk].view_as(k), non_blocking=True)
-            v.copy_(src[nk:nk + v.numel()].view_as(v), non_blocking=True)
-        self.bytes_in += nk + v.numel()
+            off = 0
+            for v in page_views(self.pool, page):
+                v.copy_(src[off:off + v.numel()].view_as(v), non_blocking=True)
+                off += v.numel()
+        self.bytes_in += off
 
     def fence(self) -> None:
         """Make the compute stream wait for all moves issued so far (call before pages are reused)."""

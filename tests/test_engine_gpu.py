@@ -16,7 +16,16 @@ def make_engine(**kw):
     return Engine(cfg)
 
 
-def test_prefix_reuse_gives_same_tokens_as_cold_run():
+@pytest.fixture
+def uniform_tail(monkeypatch):
+    """Bit-equality of a warm and a cold prefill needs the same GEMM arithmetic for every chunk length: keep the
+    few-row tail chunks on the GEMM kernel instead of the (integer-activation) weight-streaming kernel."""
+    from owl_engine_b200.ops import linear
+
+    monkeypatch.setattr(linear, "SKINNY_UPTO", 0)
+
+
+def test_prefix_reuse_gives_same_tokens_as_cold_run(uniform_tail):
     eng = make_engine()
     g = torch.Generator().manual_seed(0)
     base = torch.randint(0, eng.spec.vocab, (100,), generator=g).tolist()
@@ -34,7 +43,7 @@ def test_prefix_reuse_gives_same_tokens_as_cold_run():
     assert eng.generate(base, 6) == a and eng.prefix_hits >= 2
 
 
-def test_pressure_demotes_to_host_then_disk_and_recall_gives_same_tokens(tmp_path):
+def test_pressure_demotes_to_host_then_disk_and_recall_gives_same_tokens(tmp_path, uniform_tail):
     """A pool too small for the working set: published prefixes leave for the pinned-host tier, the host tier's oldest
     blocks leave for disk files, and a returning prompt is served from disk -> host -> device with unchanged output."""
     eng = Engine(EngineConfig(model="test-hybrid", n_pages=20, n_slots=4, n_snap_rows=8, max_seqs=4,

@@ -10,13 +10,13 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-def build(arm="baseline", n_layers=4, group=128, layout="slice"):
+def build(arm="baseline", n_layers=4, group=128, layout="slice", kv_dtype="fp8"):
     spec = make_spec(n_layers=n_layers)
     dense = init_weights(spec, seed=3, std=0.05)
     hw, equiv = H.weights_from_dense(spec, dense, DEV, group=group, layout=layout)
-    pool = H.StatePool(spec, DEV, n_pages=32, n_slots=4)
+    pool = H.StatePool(spec, DEV, n_pages=32, n_slots=4, kv_dtype=kv_dtype)
     run = H.HybridRunner(spec, hw, pool, max_seqs=4, max_blocks=16, prefill_gemm=arm, pdl=True)
-    ref = RefModel(spec, equiv, kv_fp8=True)
+    ref = RefModel(spec, equiv, kv_fp8=kv_dtype == "fp8")
     return spec, run, ref
 
 
@@ -138,3 +138,43 @@ def test_sequence_parallel_prefill_protocol_on_one_gpu():
     st = ref.new_state()
     hr = ref.forward(prompt, st)
     assert rel_err(outs[0][0], hr[-1:]) < 0.05
+
+
+def test_int8_kv_pool_matches_reference():
+    """int8 KV pool (per token, per head scales): prefill in two chunks, then eager and graph decode steps against the
+    fp32 model with an unquantised cache; the stored bytes dequantise to the keys the kernel was given."""
+    spec, run, ref = build("tc", kv_dtype="int8")
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, spec.vocab, (37,), generator=g)
+    seq_row, slot = 1, 2
+    run.block_table[seq_row, :8] = torch.tensor([5, 9, 2, 30, 11, 12, 13, 14], dtype=torch.int32, device=DEV)
+    ids = prompt.to(torch.int32).to(DEV)
+    run.prefill_chunk_forward(ids[:21], 0, seq_row, slot, want_logits=False)
+    run.prefill_chunk_forward(ids[21:], 21, seq_row, slot)
+    torch.cuda.synchronize()
+    st = ref.new_state()
+    hr = ref.forward(prompt, st)
+    want = ref.logits(hr[-1:])
+    assert rel_err(run.logits[:1].float().cpu(), want) < 0.05
+    ks = run.pool.k_scale[0, 5]                              # page 5 holds positions 0..15
+    assert (ks > 0).all() and (run.pool.k_pool[0, 5].view(torch.int8).abs().amax(-1) == 127).all()
+    lay = H.StepLayout(1, 1)
+    v = run.views(lay)
+    nxt = int(want.argmax(-1))
+    for step in range(4):
+        pos = 37 + step
+        v["ids"][0] = nxt
+        v["pos3"][:] = pos
+        v["kv_slot"][0] = int(run.block_table[seq_row, pos // 16]) * 16 + pos % 16
+        v["ctx"][0] = pos + 1
+        v["gslot"][0] = slot
+        v["bt_row"][0] = seq_row
+        if step < 2:
+            run.step_forward(lay, ctx_hint=64)
+        else:
+            run.capture(1, 1, ctx_hint=64).replay()
+        torch.cuda.synchronize()
+        hr = ref.forward(torch.tensor([nxt]), st)
+        want = ref.logits(hr)
+        assert rel_err(run.logits[:1].float().cpu(), want) < 0.05, step
+        nxt = int(want.argmax(-1))
