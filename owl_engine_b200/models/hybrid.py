@@ -333,7 +333,7 @@ class HybridRunner:
                                         # verify must reproduce plain decoding bit for bit): one GEMV arm for 1..8 rows,
                                         # KV splits aligned to positions instead of to the row's length
         self.pf_pipe = None             # explicit prefill pipe (parallel/symm.PrefillPipe); default: the communicator's
-        self.sp_prefill = False         # tensor-parallel prefill through the GEMM-fused reduce-scatter / all-gather path
+        self.sp_prefill = True          # tensor-parallel prefill through the GEMM-fused reduce-scatter / all-gather path
         self.gdn_save = None            # (qkvz [n_gdn, M, nq], ab [n_gdn, M, ldab]): GDN inputs of the last step, kept for fold()
 
     # -- step inputs -------------------------------------------------------------------------
