@@ -40,7 +40,8 @@ __device__ __forceinline__ uint32_t float_to_e2m1(float x) {       // round to n
 template <int MT>
 __global__ void __launch_bounds__(256) nvfp4_gemv_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ sf,
                                                          float alpha, const __nv_bfloat16* __restrict__ x, int ldx,
-                                                         __nv_bfloat16* out, int ldo, int M, int N, int K) {
+                                                         __nv_bfloat16* out, int ldo, const __nv_bfloat16* residual, int M,
+                                                         int N, int K) {
   const int lane = threadIdx.x & 31, n = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (n >= N) return;
   float acc[MT];
@@ -71,8 +72,28 @@ __global__ void __launch_bounds__(256) nvfp4_gemv_kernel(const uint8_t* __restri
 #pragma unroll
   for (int m = 0; m < MT; ++m) {
     const float v = warp_sum(acc[m]);
-    if (lane == 0 && m < M) out[(size_t)m * ldo + n] = __float2bfloat16(v * alpha);
+    if (lane == 0 && m < M)
+      out[(size_t)m * ldo + n] = __float2bfloat16(v * alpha + (residual ? __bfloat162float(residual[(size_t)m * ldo + n]) : 0.f));
   }
+}
+
+// x = sx * (128 h + l) per element; chunk byte order as written by actpack_emit
+__global__ void __launch_bounds__(256) act_unpack_kernel(const uint4* __restrict__ xpack, const float2* __restrict__ xs,
+                                                         __nv_bfloat16* __restrict__ out, int ldo, int nchunks, int cpg) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x, row = blockIdx.y;
+  if (c >= nchunks) return;
+  const uint4 pk = xpack[(size_t)row * nchunks + c];
+  const float sx = xs[(size_t)row * (nchunks / cpg) + c / cpg].x;
+  const int klo[4] = {0, 4, 1, 5}, khi[4] = {2, 6, 3, 7};
+  float v[8];
+#pragma unroll
+  for (int b = 0; b < 4; ++b) {
+    const int hl = (int)(int8_t)((pk.x >> (8 * b)) & 0xff), ll = (int)((pk.y >> (8 * b)) & 0x7f);
+    const int hb = (int)(int8_t)((pk.z >> (8 * b)) & 0xff), lb = (int)((pk.w >> (8 * b)) & 0x7f);
+    v[klo[b]] = sx * (float)(hl * 128 + ll);
+    v[khi[b]] = sx * (float)(hb * 128 + lb);
+  }
+  *reinterpret_cast<uint4*>(out + (size_t)row * ldo + c * 8) = pack_bf16x8(v);
 }
 
 __global__ void __launch_bounds__(256) nvfp4_dequant_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ sf,
@@ -230,13 +251,34 @@ __global__ void __launch_bounds__(256) gguf_gemv_kernel(const uint8_t* __restric
 }  // namespace owl
 using namespace owl;
 
-OWL_API int owl_nvfp4_gemv(const void* codes, const void* sf, float alpha, const void* x, int ldx, void* out, int ldo,
-                           int M, int N, int K, cudaStream_t st) {
+static int nvfp4_gemv_launch(const void* codes, const void* sf, float alpha, const void* x, int ldx, void* out, int ldo,
+                             const void* residual, int M, int N, int K, cudaStream_t st) {
   if (M < 1 || M > 8 || N < 1 || (K & 15) || (ldx & 7)) return OWL_ERR_BAD_ARG;
   const dim3 grid((N + 7) / 8);
-  if (M == 1) nvfp4_gemv_kernel<1><<<grid, 256, 0, st>>>((const uint8_t*)codes, (const uint8_t*)sf, alpha, (const __nv_bfloat16*)x, ldx, (__nv_bfloat16*)out, ldo, M, N, K);
-  else if (M <= 4) nvfp4_gemv_kernel<4><<<grid, 256, 0, st>>>((const uint8_t*)codes, (const uint8_t*)sf, alpha, (const __nv_bfloat16*)x, ldx, (__nv_bfloat16*)out, ldo, M, N, K);
-  else nvfp4_gemv_kernel<8><<<grid, 256, 0, st>>>((const uint8_t*)codes, (const uint8_t*)sf, alpha, (const __nv_bfloat16*)x, ldx, (__nv_bfloat16*)out, ldo, M, N, K);
+  const auto *c = (const uint8_t*)codes, *f = (const uint8_t*)sf;
+  const auto *xx = (const __nv_bfloat16*)x, *r = (const __nv_bfloat16*)residual;
+  if (M == 1) nvfp4_gemv_kernel<1><<<grid, 256, 0, st>>>(c, f, alpha, xx, ldx, (__nv_bfloat16*)out, ldo, r, M, N, K);
+  else if (M <= 4) nvfp4_gemv_kernel<4><<<grid, 256, 0, st>>>(c, f, alpha, xx, ldx, (__nv_bfloat16*)out, ldo, r, M, N, K);
+  else nvfp4_gemv_kernel<8><<<grid, 256, 0, st>>>(c, f, alpha, xx, ldx, (__nv_bfloat16*)out, ldo, r, M, N, K);
+  OWL_LAUNCH_CHECK();
+  return OWL_OK;
+}
+OWL_API int owl_nvfp4_gemv(const void* codes, const void* sf, float alpha, const void* x, int ldx, void* out, int ldo,
+                           int M, int N, int K, cudaStream_t st) {
+  return nvfp4_gemv_launch(codes, sf, alpha, x, ldx, out, ldo, nullptr, M, N, K, st);
+}
+// out = residual + alpha * x . W^T (residual bf16 [M][ldo], may alias out).
+OWL_API int owl_nvfp4_gemv_res(const void* codes, const void* sf, float alpha, const void* x, int ldx, void* out, int ldo,
+                               const void* residual, int M, int N, int K, cudaStream_t st) {
+  if (!residual) return OWL_ERR_BAD_ARG;
+  return nvfp4_gemv_launch(codes, sf, alpha, x, ldx, out, ldo, residual, M, N, K, st);
+}
+// ActPack rows (15-bit fixed point + per-group scale, row layout) back to bf16 [M][ldo]: the input of the float GEMV arms.
+OWL_API int owl_act_unpack(const void* xpack, const void* xs, void* out, int ldo, int M, int K, int G, cudaStream_t st) {
+  if (M < 1 || (K & 7) || (G != 32 && G != 128) || (K % G) || (ldo & 7)) return OWL_ERR_BAD_ARG;
+  const int nchunks = K / 8;
+  act_unpack_kernel<<<dim3((nchunks + 255) / 256, M), 256, 0, st>>>((const uint4*)xpack, (const float2*)xs, (__nv_bfloat16*)out, ldo,
+                                                                     nchunks, G >> 3);
   OWL_LAUNCH_CHECK();
   return OWL_OK;
 }

@@ -87,7 +87,7 @@ def _pad16_rows(w: torch.Tensor) -> torch.Tensor:
 
 
 def weights_from_dense(spec: ModelSpec, dense: dict, device, group: int = 128, lm_head_int8: bool = False, layout: str = "slice",
-                       vocab_split: bool = False):
+                       vocab_split: bool = False, quant: str = "w4a16"):
     """Build device weights from HF-named dense tensors (full, unsharded model; ``spec`` may be
     a TP shard, in which case rows / columns are cut with ``parallel.plan``). Returns
     ``(HybridWeights, dense_equiv)`` where ``dense_equiv`` holds the dequantised weights under
@@ -99,6 +99,16 @@ def weights_from_dense(spec: ModelSpec, dense: dict, device, group: int = 128, l
 
     def w4(name_or_tensor, names=None):
         w = name_or_tensor.float()
+        if quant == "nvfp4":
+            from ..formats import nvfp4
+
+            q4 = nvfp4.quantize(w)
+            deq = nvfp4.dequantize(q4)
+            off = 0
+            for nm, rows in names or []:
+                equiv[nm] = deq[off:off + rows]
+                off += rows
+            return Q.NvFp4Linear(q4.codes.to(device), q4.scales.to(device), q4.global_scale, w.shape[0], w.shape[1], group)
         c = Q.quantize_w4(w, group)
         if names:
             deq = c.dequant()
@@ -115,11 +125,19 @@ def weights_from_dense(spec: ModelSpec, dense: dict, device, group: int = 128, l
         p = f"model.layers.{i}."
         m = p + "mlp."
         gu = Q.interleave_gate_up(dense[m + "gate_proj.weight"].float(), dense[m + "up_proj.weight"].float())
-        cgu = Q.quantize_w4(gu, group)
-        ge, ue = Q.deinterleave_gate_up(cgu.dequant().t())
+        if quant == "nvfp4":
+            from ..formats import nvfp4
+
+            qgu = nvfp4.quantize(gu)
+            gu_dev = Q.NvFp4Linear(qgu.codes.to(device), qgu.scales.to(device), qgu.global_scale, gu.shape[0], gu.shape[1], group)
+            gu_deq = nvfp4.dequantize(qgu)
+        else:
+            cgu = Q.quantize_w4(gu, group)
+            gu_dev, gu_deq = Q.pack_skinny(cgu, layout).to(device), cgu.dequant()
+        ge, ue = Q.deinterleave_gate_up(gu_deq.t())
         equiv[m + "gate_proj.weight"], equiv[m + "up_proj.weight"] = ge.t().contiguous(), ue.t().contiguous()
         lw = LayerWeights(kind="full" if spec.is_full(i) else "gdn", ln1=bf(dense[p + "input_layernorm.weight"]),
-                          ln2=bf(dense[p + "post_attention_layernorm.weight"]), gate_up=Q.pack_skinny(cgu, layout).to(device),
+                          ln2=bf(dense[p + "post_attention_layernorm.weight"]), gate_up=gu_dev,
                           down=w4(dense[m + "down_proj.weight"], [(m + "down_proj.weight", spec.hidden)]))
         if lw.kind == "gdn":
             a = p + "linear_attn."
@@ -165,8 +183,18 @@ def weights_from_dense(spec: ModelSpec, dense: dict, device, group: int = 128, l
 
 
 def random_weights(spec: ModelSpec, device, group: int = 128, seed: int = 0, lm_head_int8: bool = False, layout: str = "slice",
-                   std: float = 0.02, vocab_split: bool = True) -> HybridWeights:
+                   std: float = 0.02, vocab_split: bool = True, quant: str = "w4a16") -> HybridWeights:
     """Random-init weights generated directly in the device layouts (benchmarks: no dense copy)."""
+    if quant == "nvfp4":
+        class _Q4:                      # same call shape as Q.random_skinny, NVFP4 storage
+            @staticmethod
+            def random_skinny(n, k, group, device, std, seed, layout):
+                return Q.random_nvfp4(n, k, device, std, seed, group)
+        return _random_weights(spec, device, group, seed, lm_head_int8, "nvfp4", std, vocab_split, _Q4)
+    return _random_weights(spec, device, group, seed, lm_head_int8, layout, std, vocab_split, Q)
+
+
+def _random_weights(spec, device, group, seed, lm_head_int8, layout, std, vocab_split, QW) -> HybridWeights:
     gen = torch.Generator(device=device).manual_seed(seed)
     rnd = lambda *s: (torch.randn(*s, device=device, generator=gen) * std)
     H = spec.hidden
@@ -176,21 +204,21 @@ def random_weights(spec: ModelSpec, device, group: int = 128, seed: int = 0, lm_
         sd += 17
         lw = LayerWeights(kind="full" if spec.is_full(i) else "gdn", ln1=rnd(H).to(torch.bfloat16),
                           ln2=rnd(H).to(torch.bfloat16),
-                          gate_up=Q.random_skinny(2 * spec.inter, H, group, device, std, sd + 1, layout),
-                          down=Q.random_skinny(H, spec.inter, group, device, std, sd + 2, layout))
+                          gate_up=QW.random_skinny(2 * spec.inter, H, group, device, std, sd + 1, layout),
+                          down=QW.random_skinny(H, spec.inter, group, device, std, sd + 2, layout))
         if lw.kind == "gdn":
-            lw.qkvz = Q.random_skinny(spec.conv_dim + spec.value_dim, H, group, device, std, sd + 3, layout)
+            lw.qkvz = QW.random_skinny(spec.conv_dim + spec.value_dim, H, group, device, std, sd + 3, layout)
             lw.ab_dense = _pad16_rows(rnd(2 * spec.nv, H).to(torch.bfloat16))
             lw.ab = Q.dense_skinny(lw.ab_dense, device)
             lw.conv_w = (torch.randn(spec.conv_dim, spec.conv_k, device=device, generator=gen) * 0.2)
             lw.a_log = torch.log(torch.empty(spec.nv, device=device).uniform_(1.0, 16.0, generator=gen))
             lw.dt_bias = torch.ones(spec.nv, device=device)
             lw.gamma = torch.ones(spec.vd, device=device)
-            lw.out_proj = Q.random_skinny(H, spec.value_dim, group, device, std, sd + 4, layout)
+            lw.out_proj = QW.random_skinny(H, spec.value_dim, group, device, std, sd + 4, layout)
         else:
-            lw.qkv = Q.random_skinny(2 * spec.hq * spec.hd + 2 * spec.hkv * spec.hd, H, group, device, std, sd + 5, layout)
+            lw.qkv = QW.random_skinny(2 * spec.hq * spec.hd + 2 * spec.hkv * spec.hd, H, group, device, std, sd + 5, layout)
             lw.q_norm, lw.k_norm = rnd(spec.hd).to(torch.bfloat16), rnd(spec.hd).to(torch.bfloat16)
-            lw.o_proj = Q.random_skinny(H, spec.hq * spec.hd, group, device, std, sd + 6, layout)
+            lw.o_proj = QW.random_skinny(H, spec.hq * spec.hd, group, device, std, sd + 6, layout)
         layers.append(lw)
     emb = rnd(spec.vocab, H).to(torch.bfloat16)
     hw = HybridWeights(spec=spec, embed=emb, final_norm=torch.zeros(H, dtype=torch.bfloat16, device=device),
@@ -327,6 +355,7 @@ class HybridRunner:
         self.graphs: dict = {}
         self._pf = None   # lazily allocated prefill workspace
         self.taps: dict | None = None   # layer -> bf16 [M,H] buffers filled during decode/prefill for draft heads
+        self._x16 = self._gu16 = None   # bf16 staging of the NVFP4 GEMV arm (allocated on first use)
         self.tap_sink = None            # callable(pos0, t, {layer: [t, H]}) called after every prefill chunk when taps are on
         self.pre_hook = None            # callable(m): rewrites self.h after the embedding (draft heads mix in the target's hidden)
         self.uniform_rows = False       # per-row arithmetic independent of the number of rows in the step (speculative
@@ -350,6 +379,9 @@ class HybridRunner:
 
     def _gemv(self, w, xp, xs, out, m: int, *, residual=None, epi: int = K.EPI_STORE, ldo=None, pdl: bool = False) -> None:
         """out[m] = W x on the weight-streaming kernel that matches the weight's record layout."""
+        if w.layout == "nvfp4":
+            self._gemv_nvfp4(w, xp, xs, out, m, residual, epi, ldo)
+            return
         if w.layout != "block":
             K.w4a16_skinny(w, xp, xs, out, m, residual=residual, epi=epi, ldo=ldo, pdl=pdl,
                            force_mma=self.uniform_rows and m == 1)
@@ -360,6 +392,29 @@ class HybridRunner:
             K.w4a16_stream_tc(w, xp.view(-1)[(r0 // 8) * tb:], out[r0:], rows, self.tc_ws,
                               residual=None if residual is None else residual[r0:], epi=epi,
                               ldo=ldo if ldo is not None else out.shape[-1], pdl=pdl)
+
+    def _gemv_nvfp4(self, w, xp, xs, out, m: int, residual, epi: int, ldo) -> None:
+        """NVFP4 weights as stored in the checkpoint (e2m1 codes + e4m3 block scales): the activations come back from
+        ActPack to bf16 (15 bits of fixed point: nothing is lost on the way to bf16), the streaming dequant GEMV runs 8 rows
+        per pass, and the gate / up activation is the stand-alone kernel."""
+        sp = self.spec
+        if self._x16 is None:
+            kmax = max(sp.hidden, sp.inter, sp.value_dim, sp.hq * sp.hd)
+            self._x16 = torch.empty(self.MAX_ROWS, kmax, dtype=torch.bfloat16, device=self.device)
+            self._gu16 = torch.empty(self.MAX_ROWS, 2 * sp.inter, dtype=torch.bfloat16, device=self.device)
+        x = self._x16[:, :w.k]
+        K.act_unpack(xp, xs, x, m, w.k, self.G)
+        dst = self._gu16 if epi == K.EPI_SILU_MUL else (out if ldo is None else out.view(-1)[:out.shape[0] * ldo].view(out.shape[0], ldo))
+        for r0 in range(0, m, 8):
+            rows = min(8, m - r0)
+            if epi == K.EPI_RESIDUAL:
+                K.nvfp4_gemv_res(w.codes, w.scales, w.alpha, x[r0:], dst[r0:], residual[r0:], rows)
+            else:
+                K.nvfp4_gemv(w.codes, w.scales, w.alpha, x[r0:], dst[r0:], rows)
+        if epi == K.EPI_SILU_MUL:
+            K.silu_mul(self._gu16, m, w.n // 2, out=out, pdl=False)
+        elif epi not in (K.EPI_STORE, K.EPI_RESIDUAL):
+            raise ValueError(f"NVFP4 arm: epilogue {epi} is not built")
 
     def _norm(self, m: int, w, *, want_xn: bool, want_pack: bool = True) -> None:
         sp = self.spec
@@ -590,6 +645,8 @@ class HybridRunner:
         """out[T, N] = x[T, K] @ dequant(w)^T for a prefill chunk."""
         from ..ops import linear
 
+        if w.layout == "nvfp4":
+            return linear.nvfp4_gemm(w, x, out, arm=self.prefill_gemm)
         return linear.w4_gemm(w, x, out, arm=self.prefill_gemm)
 
     def prefill_chunk_forward(self, ids: torch.Tensor, pos0: int, seq_row: int, gdn_slot: int, *,

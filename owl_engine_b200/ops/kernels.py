@@ -289,6 +289,8 @@ def topk_merge(cand_val, cand_idx, k: int):
 
 
 register("owl_nvfp4_gemv", [_P, _P, _F, _P, _I, _P, _I, _I, _I, _I, _P])
+register("owl_nvfp4_gemv_res", [_P, _P, _F, _P, _I, _P, _I, _P, _I, _I, _I, _P])
+register("owl_act_unpack", [_P, _P, _P, _I, _I, _I, _I, _P])
 register("owl_nvfp4_dequant", [_P, _P, _F, _P, c_longlong, _P])
 register("owl_nvfp4_quant_act", [_P, _F, _P, _P, c_longlong, _P])
 register("owl_gguf_dequant", [_P, _I, _I, _P, _I, _P, _P])
@@ -299,6 +301,18 @@ def nvfp4_gemv(codes, scales, alpha: float, x, out, m: int) -> None:
     """out[m, N] = alpha * x . dequant(NVFP4 W)^T for m <= 8 (``csrc/lowbit.cu``). codes uint8 [N, K/2], scales e4m3 bytes [N, K/16]."""
     n, k = codes.shape[0], codes.shape[1] * 2
     call("owl_nvfp4_gemv", ptr(codes), ptr(scales), float(alpha), ptr(x), x.stride(0), ptr(out), out.stride(0), m, n, k, stream())
+
+
+def nvfp4_gemv_res(codes, scales, alpha: float, x, out, residual, m: int) -> None:
+    """out = residual + alpha * x . dequant(W)^T (m <= 8); ``residual`` may be ``out``."""
+    n, k = codes.shape[0], codes.shape[1] * 2
+    call("owl_nvfp4_gemv_res", ptr(codes), ptr(scales), float(alpha), ptr(x), x.stride(0), ptr(out), out.stride(0), ptr(residual),
+         m, n, k, stream())
+
+
+def act_unpack(xpack, xs, out, m: int, k: int, group: int = 128) -> None:
+    """ActPack rows (row layout) -> bf16 ``out[:m, :k]``."""
+    call("owl_act_unpack", ptr(xpack), ptr(xs), ptr(out), out.stride(0), m, k, group, stream())
 
 
 def nvfp4_dequant(codes, scales, alpha: float, out=None):

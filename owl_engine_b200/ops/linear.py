@@ -79,6 +79,27 @@ def w4_gemm(w, x: torch.Tensor, out: torch.Tensor, arm: str = "tc") -> torch.Ten
     raise ValueError(f"unknown prefill GEMM arm {arm!r}")
 
 
+def nvfp4_gemm(w, x: torch.Tensor, out: torch.Tensor, arm: str = "tc") -> torch.Tensor:
+    """out[T, N] = x @ dequant(NVFP4 w)^T for a prefill chunk: the weight is dequantised once (bf16) and multiplied on the
+    dense tcgen05 GEMM; ``"tc8"`` re-quantises rows to e4m3 and runs the 8-bit float product at twice the rate; a handful of
+    rows take the streaming GEMV."""
+    from . import gemm_tc
+
+    t = x.shape[0]
+    if arm != "baseline" and t <= 8:
+        K.nvfp4_gemv(w.codes, w.scales, w.alpha, x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16), out, t)
+        return out
+    dense = K.nvfp4_dequant(w.codes, w.scales, w.alpha, _dense_scratch(w.n, w.k, x.device, torch.bfloat16))
+    if arm == "baseline":
+        torch.matmul(x.to(torch.bfloat16), dense.t(), out=out)
+        return out
+    if arm == "tc8" and t >= DEQUANT_FROM and w.k % 128 == 0:
+        wq, sw = gemm_tc.quant_e4m3_rows(dense, *_fp8_scratch("w", w.n, w.k, x.device))
+        xq, sx = gemm_tc.quant_e4m3_rows(x, *_fp8_scratch("x", t, w.k, x.device))
+        return gemm_tc.e4m3_gemm(xq, sx, wq, sw, out)
+    return gemm_tc.f16_gemm(x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16), dense, out)
+
+
 def w4_dense(w, dtype, device) -> torch.Tensor:
     """The weight dequantised into the shared dense scratch matrix (valid until the next call on this stream)."""
     return K.w4_dequant(w, _dense_scratch(w.n, w.k, device, dtype))

@@ -140,6 +140,42 @@ class W4Skinny:
         return 1024 + 64 * (128 // self.group)
 
 
+@dataclass
+class NvFp4Linear:
+    """Device-ready NVFP4 weight as stored in the checkpoint: e2m1 codes ``[N, K/2]`` (two per byte, low nibble first),
+    e4m3 block scales ``[N, K/16]`` and the per-tensor scale ``alpha``. Row order is the model's (gate / up rows interleaved
+    in eights for the merged MLP projection, like every other weight format here)."""
+    codes: torch.Tensor
+    scales: torch.Tensor
+    alpha: float
+    n: int
+    k: int
+    group: int = 128          # ActPack group of the activations this weight is fed from
+    layout: str = "nvfp4"
+
+    @property
+    def nbytes(self) -> int:
+        return self.codes.numel() + self.scales.numel()
+
+
+def nvfp4_linear(w: torch.Tensor, device, group: int = 128) -> NvFp4Linear:
+    """Quantise a dense ``[N, K]`` weight to NVFP4 (CPU oracle codec) and move it to the device."""
+    from ..formats import nvfp4
+
+    q = nvfp4.quantize(w.float())
+    return NvFp4Linear(q.codes.to(device), q.scales.to(device), q.global_scale, w.shape[0], w.shape[1], group)
+
+
+def random_nvfp4(n: int, k: int, device, std: float = 0.02, seed: int = 0, group: int = 128) -> NvFp4Linear:
+    """Random NVFP4 weight generated directly on the device (benchmark initialisation): uniform codes, block scales near one
+    e4m3 value, ``alpha`` chosen so that the dequantised values have standard deviation about ``std``."""
+    gen = torch.Generator(device=device).manual_seed(seed)
+    codes = torch.randint(0, 256, (n, k // 2), device=device, generator=gen, dtype=torch.uint8)
+    sc = (torch.rand(n, k // 16, device=device, generator=gen) * 64.0 + 192.0).to(torch.float8_e4m3fn).view(torch.uint8)
+    # e2m1 magnitudes {0, .5, 1, 1.5, 2, 3, 4, 6}: rms 2.97; mean block scale 224
+    return NvFp4Linear(codes, sc, std / (2.97 * 224.0), n, k, group)
+
+
 def to_block_major(rec: torch.Tensor) -> torch.Tensor:
     """[NT, KT, REC] -> flat bytes ordered [row block][kt][row tile in block (8)], zero records appended
     so that NT becomes a multiple of 8."""
