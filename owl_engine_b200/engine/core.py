@@ -89,7 +89,8 @@ class Engine:
         self.spec = full.sharded(rank, world) if world > 1 and full.tp_world == 1 else full
         self.weights = weights or H.random_weights(self.spec, self.device, group=cfg.group, seed=cfg.seed + rank * 7919,
                                                    lm_head_int8=cfg.lm_head_int8,
-                                                   layout="block" if cfg.decode_gemv == "tc" else "slice")
+                                                   layout="block" if cfg.decode_gemv == "tc" else "slice",
+                                                   quant="nvfp4" if cfg.quant == "nvfp4" else "w4a16")
         # GDN rows: one per sequence slot, the prefix-snapshot rows, and one scratch row for speculative rollback
         if cfg.kv_dtype != "fp8" and cfg.kvmem_budget:
             raise ValueError("KV selection reads the e4m3 pool: kvmem_budget needs kv_dtype = \"fp8\"")

@@ -660,7 +660,8 @@ class HybridRunner:
         sp, pool = self.spec, self.pool
         t = ids.shape[0]
         pipe = self._pipe()
-        if pipe is not None and t >= self.SP_FROM and t <= pipe.rows and self.prefill_gemm == "tc" and self.taps is None:
+        if pipe is not None and t >= self.SP_FROM and t <= pipe.rows and self.prefill_gemm == "tc" and self.taps is None \
+                and self.w.layout != "nvfp4":
             return self._prefill_chunk_sp(pipe, ids, pos0, seq_row, gdn_slot, pos3, want_logits, embeds)
         ws = self._prefill_ws(max(t, 16))
         h, x = ws["h"][:t], ws["x"][:t]

@@ -10,10 +10,10 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-def build(arm="baseline", n_layers=4, group=128, layout="slice", kv_dtype="fp8"):
+def build(arm="baseline", n_layers=4, group=128, layout="slice", kv_dtype="fp8", quant="w4a16"):
     spec = make_spec(n_layers=n_layers)
     dense = init_weights(spec, seed=3, std=0.05)
-    hw, equiv = H.weights_from_dense(spec, dense, DEV, group=group, layout=layout)
+    hw, equiv = H.weights_from_dense(spec, dense, DEV, group=group, layout=layout, quant=quant)
     pool = H.StatePool(spec, DEV, n_pages=32, n_slots=4, kv_dtype=kv_dtype)
     run = H.HybridRunner(spec, hw, pool, max_seqs=4, max_blocks=16, prefill_gemm=arm, pdl=True)
     ref = RefModel(spec, equiv, kv_fp8=kv_dtype == "fp8")
@@ -178,3 +178,60 @@ def test_int8_kv_pool_matches_reference():
         want = ref.logits(hr)
         assert rel_err(run.logits[:1].float().cpu(), want) < 0.05, step
         nxt = int(want.argmax(-1))
+
+
+@pytest.mark.parametrize("arm", ["tc", "tc8"])
+def test_nvfp4_weights_prefill_and_decode_match_reference(arm):
+    """NVFP4 weights as stored (e2m1 codes, e4m3 block scales, per-tensor scale): prefill through the dequantise-once
+    GEMM (bf16, or re-quantised e4m3 rows), decode through ActPack -> bf16 -> streaming NVFP4 GEMV, against the fp32 model
+    running on the dequantised weights."""
+    spec, run, ref = build(arm, quant="nvfp4")
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, spec.vocab, (150,), generator=g)
+    seq_row, slot = 1, 2
+    run.block_table[seq_row, :12] = torch.arange(3, 15, dtype=torch.int32, device=DEV)
+    ids = prompt.to(torch.int32).to(DEV)
+    run.prefill_chunk_forward(ids[:128], 0, seq_row, slot, want_logits=False)      # 128 rows: the dense / e4m3 GEMM
+    run.prefill_chunk_forward(ids[128:], 128, seq_row, slot)                        # 22 rows
+    torch.cuda.synchronize()
+    st = ref.new_state()
+    hr = ref.forward(prompt, st)
+    want = ref.logits(hr[-1:])
+    tol = 0.05 if arm == "tc" else 0.12
+    assert rel_err(run.logits[:1].float().cpu(), want) < tol
+    lay = H.StepLayout(1, 1)
+    v = run.views(lay)
+    nxt = int(want.argmax(-1))
+    for step in range(3):
+        pos = 150 + step
+        v["ids"][0] = nxt
+        v["pos3"][:] = pos
+        v["kv_slot"][0] = int(run.block_table[seq_row, pos // 16]) * 16 + pos % 16
+        v["ctx"][0] = pos + 1
+        v["gslot"][0] = slot
+        v["bt_row"][0] = seq_row
+        if step < 2:
+            run.step_forward(lay, ctx_hint=256)
+        else:
+            run.capture(1, 1, ctx_hint=256).replay()
+        torch.cuda.synchronize()
+        hr = ref.forward(torch.tensor([nxt]), st)
+        want = ref.logits(hr)
+        assert rel_err(run.logits[:1].float().cpu(), want) < tol, step
+        nxt = int(want.argmax(-1))
+
+
+def test_act_unpack_inverts_act_pack():
+    from owl_engine_b200.ops import kernels as K
+
+    g = torch.Generator().manual_seed(9)
+    m, k = 5, 512
+    x = (torch.randn(m, k, generator=g) * 3).bfloat16().to(DEV)
+    for group in (128, 32):
+        xp = torch.empty(m, 2 * k, dtype=torch.uint8, device=DEV)
+        xs = torch.empty(m, k // group, 2, dtype=torch.float32, device=DEV)
+        K.act_pack(x, xp, xs, m, k, group)
+        out = torch.zeros(m, k, dtype=torch.bfloat16, device=DEV)
+        K.act_unpack(xp, xs, out, m, k, group)
+        torch.cuda.synchronize()
+        assert rel_err(out.float().cpu(), x.float().cpu()) < 3e-3
