@@ -40,8 +40,8 @@ __device__ __forceinline__ uint32_t float_to_e2m1(float x) {       // round to n
 template <int MT>
 __global__ void __launch_bounds__(256) nvfp4_gemv_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ sf,
                                                          float alpha, const __nv_bfloat16* __restrict__ x, int ldx,
-                                                         __nv_bfloat16* out, int ldo, const __nv_bfloat16* residual, int M,
-                                                         int N, int K) {
+                                                         __nv_bfloat16* out, int ldo, const __nv_bfloat16* residual,
+                                                         const float* __restrict__ row_scale, int M, int N, int K) {
   const int lane = threadIdx.x & 31, n = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (n >= N) return;
   float acc[MT];
@@ -69,11 +69,12 @@ __global__ void __launch_bounds__(256) nvfp4_gemv_kernel(const uint8_t* __restri
       for (int i = 0; i < 16; ++i) acc[m] = fmaf(w[i], xv[i], acc[m]);
     }
   }
+  const float a = row_scale ? alpha * row_scale[n] : alpha;     // merged projections keep one per-tensor scale per row
 #pragma unroll
   for (int m = 0; m < MT; ++m) {
     const float v = warp_sum(acc[m]);
     if (lane == 0 && m < M)
-      out[(size_t)m * ldo + n] = __float2bfloat16(v * alpha + (residual ? __bfloat162float(residual[(size_t)m * ldo + n]) : 0.f));
+      out[(size_t)m * ldo + n] = __float2bfloat16(v * a + (residual ? __bfloat162float(residual[(size_t)m * ldo + n]) : 0.f));
   }
 }
 
@@ -97,11 +98,12 @@ __global__ void __launch_bounds__(256) act_unpack_kernel(const uint4* __restrict
 }
 
 __global__ void __launch_bounds__(256) nvfp4_dequant_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ sf,
-                                                            float alpha, __nv_bfloat16* out, size_t n_blocks) {
+                                                            float alpha, __nv_bfloat16* out, size_t n_blocks,
+                                                            const float* __restrict__ row_scale, int blocks_per_row) {
   const size_t b = (size_t)blockIdx.x * 256 + threadIdx.x;     // one 16-element block per thread
   if (b >= n_blocks) return;
   const uint2 q = *reinterpret_cast<const uint2*>(codes + b * 8);
-  const float s = e4m3_to_float(sf[b]) * alpha;
+  const float s = e4m3_to_float(sf[b]) * alpha * (row_scale ? row_scale[b / blocks_per_row] : 1.f);
   float w[16];
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
@@ -252,14 +254,15 @@ __global__ void __launch_bounds__(256) gguf_gemv_kernel(const uint8_t* __restric
 using namespace owl;
 
 static int nvfp4_gemv_launch(const void* codes, const void* sf, float alpha, const void* x, int ldx, void* out, int ldo,
-                             const void* residual, int M, int N, int K, cudaStream_t st) {
+                             const void* residual, int M, int N, int K, cudaStream_t st, const void* row_scale = nullptr) {
   if (M < 1 || M > 8 || N < 1 || (K & 15) || (ldx & 7)) return OWL_ERR_BAD_ARG;
   const dim3 grid((N + 7) / 8);
   const auto *c = (const uint8_t*)codes, *f = (const uint8_t*)sf;
   const auto *xx = (const __nv_bfloat16*)x, *r = (const __nv_bfloat16*)residual;
-  if (M == 1) nvfp4_gemv_kernel<1><<<grid, 256, 0, st>>>(c, f, alpha, xx, ldx, (__nv_bfloat16*)out, ldo, r, M, N, K);
-  else if (M <= 4) nvfp4_gemv_kernel<4><<<grid, 256, 0, st>>>(c, f, alpha, xx, ldx, (__nv_bfloat16*)out, ldo, r, M, N, K);
-  else nvfp4_gemv_kernel<8><<<grid, 256, 0, st>>>(c, f, alpha, xx, ldx, (__nv_bfloat16*)out, ldo, r, M, N, K);
+  const float* rs = (const float*)row_scale;
+  if (M == 1) nvfp4_gemv_kernel<1><<<grid, 256, 0, st>>>(c, f, alpha, xx, ldx, (__nv_bfloat16*)out, ldo, r, rs, M, N, K);
+  else if (M <= 4) nvfp4_gemv_kernel<4><<<grid, 256, 0, st>>>(c, f, alpha, xx, ldx, (__nv_bfloat16*)out, ldo, r, rs, M, N, K);
+  else nvfp4_gemv_kernel<8><<<grid, 256, 0, st>>>(c, f, alpha, xx, ldx, (__nv_bfloat16*)out, ldo, r, rs, M, N, K);
   OWL_LAUNCH_CHECK();
   return OWL_OK;
 }
@@ -273,6 +276,22 @@ OWL_API int owl_nvfp4_gemv_res(const void* codes, const void* sf, float alpha, c
   if (!residual) return OWL_ERR_BAD_ARG;
   return nvfp4_gemv_launch(codes, sf, alpha, x, ldx, out, ldo, residual, M, N, K, st);
 }
+// Per-row scales (fp32 [N], multiplied with alpha): rows of a merged projection keep their tensors' own scales.
+// residual may be null.
+OWL_API int owl_nvfp4_gemv_rows(const void* codes, const void* sf, float alpha, const void* row_scale, const void* x, int ldx,
+                                void* out, int ldo, const void* residual, int M, int N, int K, cudaStream_t st) {
+  if (!row_scale) return OWL_ERR_BAD_ARG;
+  return nvfp4_gemv_launch(codes, sf, alpha, x, ldx, out, ldo, residual, M, N, K, st, row_scale);
+}
+OWL_API int owl_nvfp4_dequant_rows(const void* codes, const void* sf, float alpha, const void* row_scale, int K, void* out,
+                                   long long n_elems, cudaStream_t st) {
+  if (n_elems < 16 || (n_elems & 15) || !row_scale || K < 16 || (K & 15)) return OWL_ERR_BAD_ARG;
+  const size_t nb = (size_t)n_elems / 16;
+  nvfp4_dequant_kernel<<<(unsigned)((nb + 255) / 256), 256, 0, st>>>((const uint8_t*)codes, (const uint8_t*)sf, alpha,
+                                                                     (__nv_bfloat16*)out, nb, (const float*)row_scale, K / 16);
+  OWL_LAUNCH_CHECK();
+  return OWL_OK;
+}
 // ActPack rows (15-bit fixed point + per-group scale, row layout) back to bf16 [M][ldo]: the input of the float GEMV arms.
 OWL_API int owl_act_unpack(const void* xpack, const void* xs, void* out, int ldo, int M, int K, int G, cudaStream_t st) {
   if (M < 1 || (K & 7) || (G != 32 && G != 128) || (K % G) || (ldo & 7)) return OWL_ERR_BAD_ARG;
@@ -285,7 +304,8 @@ OWL_API int owl_act_unpack(const void* xpack, const void* xs, void* out, int ldo
 OWL_API int owl_nvfp4_dequant(const void* codes, const void* sf, float alpha, void* out, long long n_elems, cudaStream_t st) {
   if (n_elems < 16 || (n_elems & 15)) return OWL_ERR_BAD_ARG;
   const size_t nb = (size_t)n_elems / 16;
-  nvfp4_dequant_kernel<<<(unsigned)((nb + 255) / 256), 256, 0, st>>>((const uint8_t*)codes, (const uint8_t*)sf, alpha, (__nv_bfloat16*)out, nb);
+  nvfp4_dequant_kernel<<<(unsigned)((nb + 255) / 256), 256, 0, st>>>((const uint8_t*)codes, (const uint8_t*)sf, alpha, (__nv_bfloat16*)out, nb,
+                                                                     nullptr, 1);
   OWL_LAUNCH_CHECK();
   return OWL_OK;
 }

@@ -26,5 +26,9 @@ for (n,k) in [(34816,5120),(5120,17408),(16384,5120),(5120,6144)]:
         c=t(lambda: gemm_tc.f16_gemm(xb,dense,out))
         c0=t(lambda: gemm_tc.f16_gemm(xb,dense,out,force_small=True))
         d=t(lambda: torch.matmul(xb,dense.t(),out=out))
-        print(f"N={n} K={k} T={T}: w4 fused {a:.3f} ms ({fl/a/1e9:.0f} TF)  dequant {b:.3f} ms  dense persist {c:.3f} ms ({fl/c/1e9:.0f} TF) small-tile {c0:.3f} ms  cublas {d:.3f} ms ({fl/d/1e9:.0f} TF)", flush=True)
+        # W4A8 arm: rows re-quantised to e4m3, product on kind::f8f6f4
+        wq,sw=gemm_tc.quant_e4m3_rows(dense); xq,sx=gemm_tc.quant_e4m3_rows(xb)
+        e=t(lambda: gemm_tc.e4m3_gemm(xq,sx,wq,sw,out))
+        qw=t(lambda: gemm_tc.quant_e4m3_rows(dense,wq,sw)); qx=t(lambda: gemm_tc.quant_e4m3_rows(xb,xq,sx))
+        print(f"N={n} K={k} T={T}: w4 fused {a:.3f} ms ({fl/a/1e9:.0f} TF)  dequant {b:.3f} ms  dense persist {c:.3f} ms ({fl/c/1e9:.0f} TF) small-tile {c0:.3f} ms  cublas {d:.3f} ms ({fl/d/1e9:.0f} TF)  e4m3 {e:.3f} ms ({fl/e/1e9:.0f} TF; quant w {qw:.3f} x {qx:.3f} ms)", flush=True)
 print(gemm_tc.gemm_status())

@@ -15,6 +15,7 @@ removed). Reference counterpart: ``crates/engine/src/loader.rs``, ``crates/model
 from __future__ import annotations
 
 import json
+from dataclasses import dataclass
 from pathlib import Path
 
 import torch
@@ -128,39 +129,80 @@ class GgufProvider:
         return Q.quantize_w4(self.f.dequant(g).float(), 32)
 
 
+@dataclass
+class NvCanonical:
+    """NVFP4 tensor as stored (ModelOpt layout): e2m1 codes ``[N, K/2]`` (two per byte), e4m3 block scales ``[N, K/16]`` and one
+    fp32 scale per ROW (a per-tensor scale broadcast, so that rows of different tensors can be stacked)."""
+    codes: torch.Tensor
+    scales: torch.Tensor
+    row_scale: torch.Tensor
+    group: int = 128
+
+    @property
+    def shape(self):
+        return (self.codes.shape[0], self.codes.shape[1] * 2)
+
+
+class NvFp4Provider(DenseProvider):
+    """ModelOpt NVFP4 checkpoints: ``<name>`` uint8 packed codes, ``<name>_scale`` e4m3 block scales, ``<name>_scale_2`` the
+    fp32 per-tensor scale (``crates/models/src/formats`` NVFP4 source in the reference); everything else is 16-bit."""
+
+    def w4(self, name: str) -> NvCanonical:
+        codes = self._get(name)
+        if codes.dtype not in (torch.uint8, torch.int8):
+            from . import nvfp4
+
+            q = nvfp4.quantize(codes.float())                # an unquantised tensor inside a quantised checkpoint
+            return NvCanonical(q.codes, q.scales, torch.full((codes.shape[0],), q.global_scale), self.group)
+        sc = self._get(name + "_scale")
+        g2 = self._get(name + "_scale_2").float().reshape(-1)
+        return NvCanonical(codes.view(torch.uint8), sc.view(torch.uint8), g2.expand(codes.shape[0]).contiguous(), self.group)
+
+
 def open_source(path: str | Path, group: int = 128):
     kind = detect_kind(path)
     if kind == "gguf":
         f = gguf.GgufFile(path)
         return kind, GgufProvider(f), f
     d = SafeDir(path)
+    if kind == "nvfp4":
+        return kind, NvFp4Provider(d, group), d
     return kind, (AwqProvider(d, group) if kind == "awq" else DenseProvider(d, group)), d
 
 
 # ---- canonical-form surgery --------------------------------------------------------------------
-def cat_rows(parts: list[Q.W4Canonical]) -> Q.W4Canonical:
+def cat_rows(parts: list):
+    if isinstance(parts[0], NvCanonical):
+        return NvCanonical(torch.cat([p.codes for p in parts]), torch.cat([p.scales for p in parts]),
+                           torch.cat([p.row_scale for p in parts]), parts[0].group)
     g = parts[0].group
     assert all(p.group == g and p.q.shape[1] == parts[0].q.shape[1] for p in parts)
     return Q.W4Canonical(torch.cat([p.q for p in parts]), torch.cat([p.scales for p in parts]),
                          torch.cat([p.zeros for p in parts]), g)
 
 
-def rows(c: Q.W4Canonical, idx) -> Q.W4Canonical:
+def rows(c, idx):
+    if isinstance(c, NvCanonical):
+        return NvCanonical(c.codes[idx].contiguous(), c.scales[idx].contiguous(), c.row_scale[idx].contiguous(), c.group)
     return Q.W4Canonical(c.q[idx].contiguous(), c.scales[idx].contiguous(), c.zeros[idx].contiguous(), c.group)
 
 
-def cols(c: Q.W4Canonical, lo: int, hi: int) -> Q.W4Canonical:
+def cols(c, lo: int, hi: int):
+    if isinstance(c, NvCanonical):
+        assert lo % 16 == 0 and hi % 16 == 0, "column cut must fall on a scale block boundary"
+        return NvCanonical(c.codes[:, lo // 2:hi // 2].contiguous(), c.scales[:, lo // 16:hi // 16].contiguous(), c.row_scale,
+                           c.group)
     g = c.group
     assert lo % g == 0 and hi % g == 0, "column cut must fall on a quantisation group boundary"
     return Q.W4Canonical(c.q[:, lo:hi].contiguous(), c.scales[:, lo // g:hi // g].contiguous(),
                          c.zeros[:, lo // g:hi // g].contiguous(), g)
 
 
-def shard_w4(name: str, c: Q.W4Canonical, full: ModelSpec, plan: TpPlan) -> Q.W4Canonical:
+def shard_w4(name: str, c, full: ModelSpec, plan: TpPlan):
     if plan.world == 1:
         return c
     r = rule_of(name)
-    n, k = c.q.shape
+    n, k = c.shape
     if r is Rule.COL:
         lo, hi = plan.shard_range(n)
         return rows(c, slice(lo, hi))
@@ -183,10 +225,13 @@ def shard_w4(name: str, c: Q.W4Canonical, full: ModelSpec, plan: TpPlan) -> Q.W4
     return c
 
 
-def interleave_rows(gate: Q.W4Canonical, up: Q.W4Canonical) -> Q.W4Canonical:
+def interleave_rows(gate, up):
     def il(a, b):
         i = a.shape[0]
         return torch.stack([a.view(i // 8, 8, -1), b.view(i // 8, 8, -1)], dim=1).reshape(2 * i, -1)
+    if isinstance(gate, NvCanonical):
+        return NvCanonical(il(gate.codes, up.codes), il(gate.scales, up.scales),
+                           il(gate.row_scale[:, None], up.row_scale[:, None]).reshape(-1), gate.group)
     return Q.W4Canonical(il(gate.q, up.q), il(gate.scales, up.scales), il(gate.zeros, up.zeros), gate.group)
 
 
@@ -201,7 +246,11 @@ def build_weights(full: ModelSpec, provider, device, rank: int = 0, world: int =
     f32 = lambda t: t.float().to(device)
     dn = lambda name: shard_tensor(name, provider.dense(name), full, plan)
     w4 = lambda name: shard_w4(name, provider.w4(name), full, plan)
-    pack = lambda c: Q.pack_skinny(c).to(device)
+    def pack(c):
+        if isinstance(c, NvCanonical):
+            n, k = c.shape
+            return Q.NvFp4Linear(c.codes.to(device), c.scales.to(device), 1.0, n, k, c.group, "nvfp4", c.row_scale.float().to(device))
+        return Q.pack_skinny(c).to(device)
     layers, group = [], None
     for i in range(full.n_layers):
         p = f"model.layers.{i}."

@@ -407,10 +407,7 @@ class HybridRunner:
         dst = self._gu16 if epi == K.EPI_SILU_MUL else (out if ldo is None else out.view(-1)[:out.shape[0] * ldo].view(out.shape[0], ldo))
         for r0 in range(0, m, 8):
             rows = min(8, m - r0)
-            if epi == K.EPI_RESIDUAL:
-                K.nvfp4_gemv_res(w.codes, w.scales, w.alpha, x[r0:], dst[r0:], residual[r0:], rows)
-            else:
-                K.nvfp4_gemv(w.codes, w.scales, w.alpha, x[r0:], dst[r0:], rows)
+            K.nvfp4_linear_gemv(w, x[r0:], dst[r0:], rows, residual=residual[r0:] if epi == K.EPI_RESIDUAL else None)
         if epi == K.EPI_SILU_MUL:
             K.silu_mul(self._gu16, m, w.n // 2, out=out, pdl=False)
         elif epi not in (K.EPI_STORE, K.EPI_RESIDUAL):
@@ -625,7 +622,7 @@ class HybridRunner:
         sp, dev = self.spec, self.device
         bf = lambda *s: torch.empty(*s, dtype=torch.bfloat16, device=dev)
         # GEMM inputs are fp16 on the tcgen05 arm (exact int4 dequant), bf16 on the baseline arm
-        xd = torch.float16 if self.prefill_gemm in ("tc", "tc8") else torch.bfloat16
+        xd = torch.float16 if self.prefill_gemm != "baseline" else torch.bfloat16
         xa = lambda *s: torch.empty(*s, dtype=xd, device=dev)
         widest = max(2 * sp.inter, sp.conv_dim + sp.value_dim, self.qkv_n)
         ws = dict(t=t, h=bf(t, sp.hidden), x=xa(t, sp.hidden), wide=bf(t, widest), act=xa(t, sp.inter),
@@ -660,7 +657,7 @@ class HybridRunner:
         sp, pool = self.spec, self.pool
         t = ids.shape[0]
         pipe = self._pipe()
-        if pipe is not None and t >= self.SP_FROM and t <= pipe.rows and self.prefill_gemm == "tc" and self.taps is None \
+        if pipe is not None and t >= self.SP_FROM and t <= pipe.rows and self.prefill_gemm in ("tc", "tcr") and self.taps is None \
                 and self.w.layout != "nvfp4":
             return self._prefill_chunk_sp(pipe, ids, pos0, seq_row, gdn_slot, pos3, want_logits, embeds)
         ws = self._prefill_ws(max(t, 16))
@@ -771,7 +768,7 @@ class HybridRunner:
         t = ids.shape[0]
         ws = self._prefill_ws(t)
         xd = torch.float16
-        dense = lambda w: linear.w4_dense(w, xd, dev)
+        dense = lambda w: linear.w4_dense(w, xd, dev, resident=self.prefill_gemm == "tcr")
         if pos3 is None:
             ws["pos3"][:, :t] = torch.arange(pos0, pos0 + t, dtype=torch.int32, device=dev)[None]
         else:

@@ -290,6 +290,8 @@ def topk_merge(cand_val, cand_idx, k: int):
 
 register("owl_nvfp4_gemv", [_P, _P, _F, _P, _I, _P, _I, _I, _I, _I, _P])
 register("owl_nvfp4_gemv_res", [_P, _P, _F, _P, _I, _P, _I, _P, _I, _I, _I, _P])
+register("owl_nvfp4_gemv_rows", [_P, _P, _F, _P, _P, _I, _P, _I, _P, _I, _I, _I, _P])
+register("owl_nvfp4_dequant_rows", [_P, _P, _F, _P, _I, _P, c_longlong, _P])
 register("owl_act_unpack", [_P, _P, _P, _I, _I, _I, _I, _P])
 register("owl_nvfp4_dequant", [_P, _P, _F, _P, c_longlong, _P])
 register("owl_nvfp4_quant_act", [_P, _F, _P, _P, c_longlong, _P])
@@ -308,6 +310,26 @@ def nvfp4_gemv_res(codes, scales, alpha: float, x, out, residual, m: int) -> Non
     n, k = codes.shape[0], codes.shape[1] * 2
     call("owl_nvfp4_gemv_res", ptr(codes), ptr(scales), float(alpha), ptr(x), x.stride(0), ptr(out), out.stride(0), ptr(residual),
          m, n, k, stream())
+
+
+def nvfp4_linear_gemv(w, x, out, m: int, residual=None) -> None:
+    """``out[:m] = (residual +) x . dequant(w)^T`` for an ``NvFp4Linear`` (m <= 8), per-row scales included."""
+    if w.row_scale is not None:
+        call("owl_nvfp4_gemv_rows", ptr(w.codes), ptr(w.scales), float(w.alpha), ptr(w.row_scale), ptr(x), x.stride(0), ptr(out),
+             out.stride(0), ptr(residual), m, w.n, w.k, stream())
+    elif residual is not None:
+        nvfp4_gemv_res(w.codes, w.scales, w.alpha, x, out, residual, m)
+    else:
+        nvfp4_gemv(w.codes, w.scales, w.alpha, x, out, m)
+
+
+def nvfp4_linear_dequant(w, out):
+    """Dense bf16 ``[N, K]`` copy of an ``NvFp4Linear``."""
+    if w.row_scale is not None:
+        call("owl_nvfp4_dequant_rows", ptr(w.codes), ptr(w.scales), float(w.alpha), ptr(w.row_scale), w.k, ptr(out), w.n * w.k,
+             stream())
+        return out
+    return nvfp4_dequant(w.codes, w.scales, w.alpha, out)
 
 
 def act_unpack(xpack, xs, out, m: int, k: int, group: int = 128) -> None:

@@ -15,6 +15,9 @@ two arms:
                   activations per token to int8 for IMMA, ``crates/kernels/cu/elems/quant_i8_act.cu:80-98``; int4
                   values times a group scale do not survive an integer MMA without a per-group epilogue, an
                   8-bit float product with per-row scales does);
+* ``"tcr"`` / ``"tc8r"``  the same two arms with the dequantised (fp16) resp. re-quantised (e4m3) weight kept RESIDENT
+                  on the weight object after its first use: 4 resp. 2 extra bytes per weight in HBM (54 / 27 GB for the
+                  27B model on one GPU, which 180 GB leave room for) buy back the per-call dequantisation pass;
 * ``"baseline"``  dequantise to a dense bf16 scratch matrix, then the library GEMM
                   (``torch.matmul`` = cuBLAS). This is the comparison arm, like the reference's
                   range-dequant -> cuBLAS arm (``crates/kernels/cu/gguf/gguf_smem.cu:415-552``).
@@ -53,14 +56,20 @@ def w4_gemm(w, x: torch.Tensor, out: torch.Tensor, arm: str = "tc") -> torch.Ten
         dense = K.w4_dequant(w, _dense_scratch(w.n, w.k, x.device))
         torch.matmul(x, dense.t(), out=out)
         return out
-    if arm == "tc8" and x.shape[0] >= DEQUANT_FROM and w.k % 128 == 0:
+    resident = arm in ("tcr", "tc8r")
+    if arm in ("tc8", "tc8r") and x.shape[0] >= DEQUANT_FROM and w.k % 128 == 0:
         from . import gemm_tc
 
-        dense = K.w4_dequant(w, _dense_scratch(w.n, w.k, x.device, torch.float16))
-        wq, sw = gemm_tc.quant_e4m3_rows(dense, *_fp8_scratch("w", w.n, w.k, x.device))
+        cached = getattr(w, "_owl_e4m3", None) if resident else None
+        if cached is None:
+            dense = K.w4_dequant(w, _dense_scratch(w.n, w.k, x.device, torch.float16))
+            cached = gemm_tc.quant_e4m3_rows(dense) if resident else gemm_tc.quant_e4m3_rows(dense, *_fp8_scratch("w", w.n, w.k, x.device))
+            if resident:
+                w._owl_e4m3 = cached
+        wq, sw = cached
         xq, sx = gemm_tc.quant_e4m3_rows(x, *_fp8_scratch("x", x.shape[0], w.k, x.device))
         return gemm_tc.e4m3_gemm(xq, sx, wq, sw, out)
-    if arm in ("tc", "tc8"):
+    if arm in ("tc", "tc8", "tcr", "tc8r"):
         from . import gemm_tc
 
         if x.shape[0] <= SKINNY_UPTO and w.layout == "slice":
@@ -73,8 +82,7 @@ def w4_gemm(w, x: torch.Tensor, out: torch.Tensor, arm: str = "tc") -> torch.Ten
             K.w4a16_skinny(w, xp, xs, out, t, ldo=out.stride(0))
             return out
         if x.shape[0] >= DEQUANT_FROM:
-            dense = K.w4_dequant(w, _dense_scratch(w.n, w.k, x.device, x.dtype))
-            return gemm_tc.f16_gemm(x, dense, out)
+            return gemm_tc.f16_gemm(x, w4_dense(w, x.dtype, x.device, resident=resident), out)
         return gemm_tc.w4a16_gemm(w, x, out)
     raise ValueError(f"unknown prefill GEMM arm {arm!r}")
 
@@ -85,11 +93,12 @@ def nvfp4_gemm(w, x: torch.Tensor, out: torch.Tensor, arm: str = "tc") -> torch.
     rows take the streaming GEMV."""
     from . import gemm_tc
 
+    arm = {"tcr": "tc", "tc8r": "tc8"}.get(arm, arm)       # no resident copies on this path
     t = x.shape[0]
     if arm != "baseline" and t <= 8:
-        K.nvfp4_gemv(w.codes, w.scales, w.alpha, x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16), out, t)
+        K.nvfp4_linear_gemv(w, x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16), out, t)
         return out
-    dense = K.nvfp4_dequant(w.codes, w.scales, w.alpha, _dense_scratch(w.n, w.k, x.device, torch.bfloat16))
+    dense = K.nvfp4_linear_dequant(w, _dense_scratch(w.n, w.k, x.device, torch.bfloat16))
     if arm == "baseline":
         torch.matmul(x.to(torch.bfloat16), dense.t(), out=out)
         return out
@@ -100,8 +109,15 @@ def nvfp4_gemm(w, x: torch.Tensor, out: torch.Tensor, arm: str = "tc") -> torch.
     return gemm_tc.f16_gemm(x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16), dense, out)
 
 
-def w4_dense(w, dtype, device) -> torch.Tensor:
-    """The weight dequantised into the shared dense scratch matrix (valid until the next call on this stream)."""
+def w4_dense(w, dtype, device, resident: bool = False) -> torch.Tensor:
+    """The weight dequantised into the shared dense scratch matrix (valid until the next call on this stream), or, with
+    ``resident``, into a matrix of its own that stays attached to the weight."""
+    if resident:
+        d = getattr(w, "_owl_dense", None)
+        if d is None or d.dtype != dtype:
+            d = K.w4_dequant(w, torch.empty(w.n, w.k, dtype=dtype, device=device))
+            w._owl_dense = d
+        return d
     return K.w4_dequant(w, _dense_scratch(w.n, w.k, device, dtype))
 
 

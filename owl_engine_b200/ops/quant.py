@@ -152,6 +152,7 @@ class NvFp4Linear:
     k: int
     group: int = 128          # ActPack group of the activations this weight is fed from
     layout: str = "nvfp4"
+    row_scale: torch.Tensor = None   # fp32 [N] (multiplied with alpha): set when rows of several tensors were merged
 
     @property
     def nbytes(self) -> int:

@@ -58,6 +58,8 @@ _T = [
     KernelSpec("owl_dflash_select", "dflash.cu", "draft"),
     KernelSpec("owl_nvfp4_gemv", "lowbit.cu", "gemv"),
     KernelSpec("owl_nvfp4_gemv_res", "lowbit.cu", "gemv"),
+    KernelSpec("owl_nvfp4_gemv_rows", "lowbit.cu", "gemv"),
+    KernelSpec("owl_nvfp4_dequant_rows", "lowbit.cu", "load"),
     KernelSpec("owl_act_unpack", "lowbit.cu", "elem"),
     KernelSpec("owl_nvfp4_dequant", "lowbit.cu", "load"),
     KernelSpec("owl_nvfp4_quant_act", "lowbit.cu", "quant"),

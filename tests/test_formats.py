@@ -122,3 +122,35 @@ def test_awq_forge_converts_a_dense_checkpoint(tmp_path):
     e_rtn = (x @ c.dequant().t() - ref).pow(2).mean()
     e_awq = ((x * sinv) @ c2.dequant().t() - ref).pow(2).mean()
     assert e_awq <= e_rtn * 1.02
+
+
+def test_nvfp4_checkpoint_source_and_row_surgery():
+    """ModelOpt-style NVFP4 tensors (packed codes, e4m3 block scales, fp32 per-tensor scale) keep their values through the
+    loader's row / column / interleave surgery: the per-tensor scale travels as a per-row scale."""
+    import torch
+
+    from owl_engine_b200.formats import loader as L, nvfp4
+
+    g = torch.Generator().manual_seed(0)
+    dense = {n: torch.randn(r, 64, generator=g) * s for n, r, s in (("q.weight", 32, 0.05), ("k.weight", 16, 0.2), ("g.weight", 16, 0.1),
+                                                                    ("u.weight", 16, 0.4))}
+    src = {}
+    for n, w in dense.items():
+        q = nvfp4.quantize(w)
+        src[n], src[n + "_scale"] = q.codes, q.scales.view(torch.float8_e4m3fn)
+        src[n + "_scale_2"] = torch.tensor(q.global_scale)
+        dense[n] = nvfp4.dequantize(q)
+    prov = L.NvFp4Provider(src, 128)
+
+    def deq(c):
+        n, k = c.shape
+        q = nvfp4.NvFp4(c.codes, c.scales, 1.0, (n, k))
+        return nvfp4.dequantize(q) * c.row_scale[:, None]
+
+    qk = L.cat_rows([prov.w4("q.weight"), prov.w4("k.weight")])
+    assert torch.allclose(deq(qk), torch.cat([dense["q.weight"], dense["k.weight"]]), rtol=1e-6, atol=1e-8)
+    assert torch.allclose(deq(L.cols(qk, 16, 48)), torch.cat([dense["q.weight"], dense["k.weight"]])[:, 16:48], rtol=1e-6, atol=1e-8)
+    assert torch.allclose(deq(L.rows(qk, slice(8, 40))), torch.cat([dense["q.weight"], dense["k.weight"]])[8:40], rtol=1e-6, atol=1e-8)
+    gu = L.interleave_rows(prov.w4("g.weight"), prov.w4("u.weight"))
+    from owl_engine_b200.ops import quant as Q
+    assert torch.allclose(deq(gu), Q.interleave_gate_up(dense["g.weight"], dense["u.weight"]), rtol=1e-6, atol=1e-8)

@@ -235,3 +235,30 @@ def test_act_unpack_inverts_act_pack():
         K.act_unpack(xp, xs, out, m, k, group)
         torch.cuda.synchronize()
         assert rel_err(out.float().cpu(), x.float().cpu()) < 3e-3
+
+
+def test_nvfp4_checkpoint_loader_weights_run_through_the_per_row_scale_kernels():
+    """Weights built by the checkpoint loader from an NVFP4 source (merged projections carry one scale per row) give the
+    same prefill logits as the directly quantised model, up to the difference between per-tensor and merged scales."""
+    from owl_engine_b200.formats import loader as L
+
+    spec = make_spec(n_layers=4)
+    dense = init_weights(spec, seed=3, std=0.05)
+    hw = L.build_weights(spec, L.NvFp4Provider(dense, 128), DEV)
+    assert hw.layers[0].gate_up.layout == "nvfp4" and hw.layers[0].gate_up.row_scale is not None
+    pool = H.StatePool(spec, DEV, n_pages=32, n_slots=4)
+    run = H.HybridRunner(spec, hw, pool, max_seqs=4, max_blocks=16, prefill_gemm="tc")
+    _, run2, _ = build("tc", quant="nvfp4")
+    ids = torch.randint(0, spec.vocab, (140,), generator=torch.Generator().manual_seed(2)).to(torch.int32).to(DEV)
+    outs = []
+    for r in (run, run2):
+        r.block_table[1, :12] = torch.arange(3, 15, dtype=torch.int32, device=DEV)
+        r.prefill_chunk_forward(ids, 0, 1, 2)
+        lay = H.StepLayout(1, 1)
+        v = r.views(lay)
+        v["ids"][0] = 5; v["pos3"][:] = 140; v["kv_slot"][0] = int(r.block_table[1, 140 // 16]) * 16 + 140 % 16
+        v["ctx"][0] = 141; v["gslot"][0] = 2; v["bt_row"][0] = 1
+        r.step_forward(lay, ctx_hint=256)
+        torch.cuda.synchronize()
+        outs.append(r.logits[:1].float().cpu())
+    assert rel_err(outs[0], outs[1]) < 0.15
