@@ -38,6 +38,28 @@ def test_nvfp4_gemv_dequant_and_act_quant(m):
     assert (ac.cpu() == a.codes).float().mean() > 0.98
 
 
+def test_nvfp4_per_row_scales_residual_form_and_act_unpack():
+    """Merged projections: rows keep their own tensors' scales; the residual form adds in the epilogue."""
+    from owl_engine_b200.ops import quant as Q
+
+    n, k, m = 96, 256, 5
+    parts = [torch.randn(32, k, generator=gen(3)) * s for s in (0.02, 0.3, 0.08)]
+    qs = [NV.quantize(p) for p in parts]
+    ref = torch.cat([NV.dequantize(q) for q in qs])
+    w = Q.NvFp4Linear(torch.cat([q.codes for q in qs]).to(DEV), torch.cat([q.scales for q in qs]).to(DEV), 1.0, n, k, 128, "nvfp4",
+                      torch.cat([torch.full((32,), q.global_scale) for q in qs]).to(DEV))
+    deq = K.nvfp4_linear_dequant(w, torch.empty(n, k, dtype=torch.bfloat16, device=DEV))
+    torch.testing.assert_close(deq.float().cpu(), ref, rtol=1e-2, atol=1e-5)
+    x = torch.randn(m, k, generator=gen(4)).to(torch.bfloat16)
+    res = torch.randn(m, n, generator=gen(5)).to(torch.bfloat16)
+    out = torch.zeros(m, n, dtype=torch.bfloat16, device=DEV)
+    K.nvfp4_linear_gemv(w, x.to(DEV), out, m)
+    want = x.float() @ ref.t()
+    torch.testing.assert_close(out.float().cpu(), want, rtol=2e-2, atol=2e-2 * want.abs().max().item())
+    K.nvfp4_linear_gemv(w, x.to(DEV), out, m, residual=res.to(DEV))
+    torch.testing.assert_close(out.float().cpu(), want + res.float(), rtol=2e-2, atol=2e-2 * (want + res.float()).abs().max().item())
+
+
 @pytest.mark.parametrize("tname", ["Q8_0", "Q4_0", "IQ4_NL", "Q4_K", "Q5_K", "Q6_K", "IQ4_XS"])
 def test_gguf_dequant_and_gemv(tname):
     n, k = 24, 512
