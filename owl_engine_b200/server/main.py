@@ -31,7 +31,11 @@ def build_engine_factory(cfg: C.OwlConfig):
 
         torch.cuda.set_device(0)
         est = estimate(cfg)
+        km = v["kvmem"]
         ecfg = EngineConfig(model=v["model"]["name"], group=v["model"]["group"],
+                            quant="nvfp4" if v["model"]["quant"] == "nvfp4" else "w4a16",
+                            kvmem_budget=km["workspace_per_req"] if km["select_decode"] else 0,
+                            kvmem_sink=km["select_sink"], kvmem_recent=km["select_recent"],
                             lm_head_int8=v["model"]["head_quant"] != "bf16",
                             n_pages=min(est["kv_pages"], max(1024, (v["runtime"]["max_seq"] // 16 + 64) * v["store.gdn"]["gdn_slots"])),
                             n_slots=v["store.gdn"]["gdn_slots"], n_snap_rows=max(2, v["store.gdn"]["snap_max"]),
