@@ -596,6 +596,17 @@ OWL_API int owl_gdn_scan(const void* qkv, const void* z, int ldz, const void* ab
 
 // Same contract as owl_gdn_scan with a caller-provided fp32 scratch of T * nv * 128 floats: the column-split
 // scan (4 CTAs per head) followed by the gated RMSNorm kernel. conv_dim must be a multiple of 8 elements.
+// The gated RMSNorm alone: raw float [T][nv * 128] (un-normalised scan outputs) -> out[r][h] = rmsnorm(raw) * gamma * silu(z).
+OWL_API int owl_gdn_norm_gate(const void* raw, const void* z, int ldz, const void* gamma, void* out, int T, int nv, float eps,
+                              int out_f16, cudaStream_t st) {
+  if (T < 1 || nv < 1 || (ldz & 3) || !raw || !out) return OWL_ERR_BAD_ARG;
+  const long long warps = (long long)T * nv;
+  gdn_norm_gate_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, st>>>((const float*)raw, (const __nv_bfloat16*)z, ldz,
+                                                                   (const float*)gamma, (__nv_bfloat16*)out, T, nv, eps, out_f16);
+  OWL_LAUNCH_CHECK();
+  return OWL_OK;
+}
+
 OWL_API int owl_gdn_scan_split(const void* qkv, const void* z, int ldz, const void* ab, int ldab, const void* a_log,
                                const void* dt_bias, const void* gamma, void* state, int slot, void* out, void* scratch,
                                int T, int nk, int nv, int use_state, float eps, int out_f16, cudaStream_t st) {

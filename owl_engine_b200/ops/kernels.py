@@ -204,14 +204,36 @@ def gdn_conv_fwd(x, ld: int, conv_w, conv_state, slot: int, out, t: int, nk: int
 register("owl_gdn_scan_split", [_P, _P, _I, _P, _I, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _F, _I, _P])
 _scan_scratch: dict = {}
 GDN_SPLIT_FROM = 32      # tokens from which the column-split scan (4 CTAs per head + norm kernel) is used
+GDN_CHUNKED_FROM = 128   # tokens from which the chunked (WY) tensor-core scan is used (0 = never)
+register("owl_gdn_chunk_work_bytes", [_I, _I, _P])
+register("owl_gdn_chunk_scan", [_P, _P, _I, _P, _P, _P, _I, _P, _P, c_longlong, _I, _I, _I, _I, _P])
+register("owl_gdn_norm_gate", [_P, _P, _I, _P, _P, _I, _I, _F, _I, _P])
+_chunk_work: dict = {}
 
 
 def gdn_scan(qkv, z, ldz: int, ab, ldab: int, a_log, dt_bias, gamma, state, slot: int, out, t: int, nk: int, nv: int,
              use_state: bool, eps: float = 1e-6, split: bool | None = None) -> None:
     """Gated delta rule over ``t`` tokens of one sequence (prefill). Long chunks run the column-split kernel,
     which needs a fp32 scratch of t * nv * 128 floats (cached per device)."""
+    if split is None and GDN_CHUNKED_FROM and t >= GDN_CHUNKED_FROM:
+        split = "chunked"
     if split is None:
         split = t >= GDN_SPLIT_FROM
+    if split == "chunked":
+        # chunk-64 WY form on tensor cores (csrc/gdn_chunk.cu): prep kernel over all chunks, recurrence over chunks, gated norm
+        key = str(qkv.device)
+        nb = c_longlong(0)
+        call("owl_gdn_chunk_work_bytes", t, nv, ctypes.addressof(nb))
+        need = int(nb.value)
+        raw, work = _chunk_work.get(key, (None, None))
+        if raw is None or raw.numel() < t * nv * 128 or work.numel() < need:
+            raw = torch.empty(max(t * nv * 128, 0 if raw is None else raw.numel()), dtype=torch.float32, device=qkv.device)
+            work = torch.empty(max(need, 0 if work is None else work.numel()), dtype=torch.uint8, device=qkv.device)
+            _chunk_work[key] = (raw, work)
+        call("owl_gdn_chunk_scan", ptr(qkv), ptr(ab), ldab, ptr(a_log), ptr(dt_bias), ptr(state), slot, ptr(raw), ptr(work),
+             work.numel(), t, nk, nv, int(use_state), stream())
+        call("owl_gdn_norm_gate", ptr(raw), ptr(z), ldz, ptr(gamma), ptr(out), t, nv, eps, _is_f16(out), stream())
+        return
     if not split:
         call("owl_gdn_scan", ptr(qkv), ptr(z), ldz, ptr(ab), ldab, ptr(a_log), ptr(dt_bias), ptr(gamma), ptr(state), slot,
              ptr(out), t, nk, nv, int(use_state), eps, _is_f16(out), stream())

@@ -230,8 +230,11 @@ def test_gdn_decode(nk, nv, t):
     torch.testing.assert_close(xs.cpu(), ws, rtol=1e-5, atol=1e-3)
 
 
-@pytest.mark.parametrize("t,use_state", [(70, True), (33, False), (5, False), (2, True)])
-def test_gdn_prefill_conv_and_scan(t, use_state):
+@pytest.mark.parametrize("t,use_state,split", [(70, True, None), (33, False, None), (5, False, None), (2, True, None),
+                                               (64, False, "chunked"), (70, True, "chunked"), (200, True, None),
+                                               (333, False, None)])
+def test_gdn_prefill_conv_and_scan(t, use_state, split):
+    """t >= 128 (or split="chunked") runs the chunk-64 WY scan on tensor cores, 32 <= t < 128 the column-split serial scan."""
     nk, nv = 2, 6
     s = _gdn_setup(nk, nv, t, 1, 21)
     if not use_state:
@@ -245,7 +248,7 @@ def test_gdn_prefill_conv_and_scan(t, use_state):
     out = torch.empty(t, s["vdim"], dtype=torch.bfloat16, device=DEV)
     z = d["qkvz"][:, s["conv_dim"]:]
     K.gdn_scan(conv_out, z, ld, d["ab"], 2 * nv, d["a_log"], d["dt_bias"], d["gamma"], d["state"], slot, out, t, nk, nv,
-               use_state)
+               use_state, split=split)
     torch.cuda.synchronize()
     want, st, hist = _gdn_ref(s, slice(0, t), slot, t)
     torch.testing.assert_close(out.float().cpu(), want, rtol=3e-2, atol=3e-2)
