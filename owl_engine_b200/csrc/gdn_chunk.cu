@@ -26,6 +26,7 @@ constexpr int CK_C = 64;            // chunk length
 constexpr int CK_D = 128;           // head dim (k and v)
 constexpr int CK_LD = CK_D + 8;     // row stride of [64][128] bf16 tiles (68 words: conflict-free fragment loads)
 constexpr int CK_LT = CK_C + 8;     // row stride of [*][64] bf16 tiles
+constexpr int CK_NC = 64;           // value columns per CTA of the recurrence kernel
 
 __device__ __forceinline__ void mma_bf16(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
   asm volatile(
@@ -55,7 +56,7 @@ struct GdnChunkParams {
   float* state;                 // [slots][nv][128 k][128 v]
   float* raw;                   // [T][nv * 128] un-normalised outputs
   __nv_bfloat16* w;             // [Tpad][nv][128]
-  __nv_bfloat16* u;             // [Tpad][nv][128]
+  float* u;                     // [Tpad][nv][128] (fp32: v' = u - w S cancels)
   __nv_bfloat16* qg;            // [Tpad][nv][128]   scale e^{gc} q
   __nv_bfloat16* kdT;           // [nv][chunks][128][64]   (e^{gc_last - gc} k)^T
   __nv_bfloat16* attn;          // [nv][chunks][64][64]
@@ -216,20 +217,19 @@ __global__ void __launch_bounds__(256) gdn_chunk_prep_kernel(GdnChunkParams p) {
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         const size_t o = ((size_t)(r0 + m0 + g + half * 8) * p.nv + h) * CK_D + nh + n * 8 + 2 * t4;
-        *reinterpret_cast<uint32_t*>(p.u + o) = pack_bf16(uu[n][half * 2], uu[n][half * 2 + 1]);
+        *reinterpret_cast<float2*>(p.u + o) = make_float2(uu[n][half * 2], uu[n][half * 2 + 1]);
         *reinterpret_cast<uint32_t*>(p.w + o) = pack_bf16(ww[n][half * 2], ww[n][half * 2 + 1]);
       }
   }
 }
 
 // ---- the recurrence over chunks: one CTA per (v-head, 64 value columns), 256 threads ----------------------------------
-constexpr int CK_NC = 64;           // value columns per CTA
 struct ScanBuf {
   __nv_bfloat16 w[CK_C][CK_LD];
   __nv_bfloat16 qg[CK_C][CK_LD];
   __nv_bfloat16 kdT[CK_D][CK_LT];
   __nv_bfloat16 attn[CK_C][CK_LT];
-  __nv_bfloat16 u[CK_C][CK_LT];     // this CTA's 64 columns
+  float u[CK_C][CK_NC + 4];         // this CTA's 64 columns (fp32)
 };
 struct ScanSmem {
   ScanBuf buf[2];
@@ -264,8 +264,11 @@ __global__ void __launch_bounds__(256) gdn_chunk_scan_kernel(GdnChunkParams p) {
       }
       for (int i = tid; i < CK_C * 8; i += 256) {
         const int t = i >> 3, piece = (i & 7) * 8;
-        ck_cp16(&b.u[t][piece], p.u + ((size_t)(r0 + t) * p.nv + h) * CK_D + cb + piece);
         ck_cp16(&b.attn[t][piece], p.attn + (((size_t)h * p.chunks + c) * CK_C + t) * CK_C + piece);
+      }
+      for (int i = tid; i < CK_C * 16; i += 256) {
+        const int t = i >> 4, piece = (i & 15) * 4;
+        ck_cp16(&b.u[t][piece], p.u + ((size_t)(r0 + t) * p.nv + h) * CK_D + cb + piece);
       }
       for (int i = tid; i < CK_D * 8; i += 256) {
         const int d = i >> 3, piece = (i & 7) * 8;
@@ -315,9 +318,9 @@ __global__ void __launch_bounds__(256) gdn_chunk_scan_kernel(GdnChunkParams p) {
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         const int i = m0 + g + half * 8, col = nh + n * 8 + 2 * t4;
-        const uint32_t uw = *reinterpret_cast<const uint32_t*>(&b.u[i][col]);
-        sm.vnT[col][i] = __float2bfloat16(bf16_lo(uw) - pv[n][half * 2]);
-        sm.vnT[col + 1][i] = __float2bfloat16(bf16_hi(uw) - pv[n][half * 2 + 1]);
+        const float2 uw = *reinterpret_cast<const float2*>(&b.u[i][col]);
+        sm.vnT[col][i] = __float2bfloat16(uw.x - pv[n][half * 2]);
+        sm.vnT[col + 1][i] = __float2bfloat16(uw.y - pv[n][half * 2 + 1]);
       }
     __syncthreads();
     // o += attn v'  (K = 64 tokens)
@@ -375,7 +378,7 @@ using namespace owl;
 
 static long long ck_work_bytes(int T, int nv) {
   const long long chunks = (T + CK_C - 1) / CK_C, tpad = chunks * CK_C;
-  return tpad * nv * CK_D * 2 * 3 + (long long)nv * chunks * CK_D * CK_C * 2 + (long long)nv * chunks * CK_C * CK_C * 2 +
+  return tpad * nv * CK_D * 2 * 4 + (long long)nv * chunks * CK_D * CK_C * 2 + (long long)nv * chunks * CK_C * CK_C * 2 +
          (long long)nv * chunks * 4 + 1024;
 }
 // Bytes of the work buffer for T tokens and nv value heads -> *out_bytes (long long).
@@ -405,8 +408,9 @@ OWL_API int owl_gdn_chunk_scan(const void* qkv, const void* ab, int ldab, const 
   p.chunks = (T + CK_C - 1) / CK_C;
   const size_t tpad = (size_t)p.chunks * CK_C, rows = tpad * nv * CK_D;
   auto* base = reinterpret_cast<__nv_bfloat16*>(work);
-  p.w = base; p.u = base + rows; p.qg = base + 2 * rows;
-  p.kdT = base + 3 * rows;
+  p.u = reinterpret_cast<float*>(base);                 // 2 * rows bf16-sized elements
+  p.w = base + 2 * rows; p.qg = base + 3 * rows;
+  p.kdT = base + 4 * rows;
   p.attn = p.kdT + (size_t)nv * p.chunks * CK_D * CK_C;
   p.eglast = reinterpret_cast<float*>(p.attn + (size_t)nv * p.chunks * CK_C * CK_C);
   gdn_chunk_prep_kernel<<<dim3(p.chunks, nv), 256, sizeof(PrepSmem), st>>>(p);

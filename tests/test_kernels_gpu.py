@@ -251,8 +251,15 @@ def test_gdn_prefill_conv_and_scan(t, use_state, split):
                use_state, split=split)
     torch.cuda.synchronize()
     want, st, hist = _gdn_ref(s, slice(0, t), slot, t)
-    torch.testing.assert_close(out.float().cpu(), want, rtol=3e-2, atol=3e-2)
-    torch.testing.assert_close(d["state"][slot].cpu(), st, rtol=2e-2, atol=2e-2)
+    if split == "chunked" or t >= K.GDN_CHUNKED_FROM:
+        # bf16 operands of the chunk products: judged on the norm, with a loose bound on any single element
+        got = out.float().cpu()
+        assert (got - want).norm() / want.norm() < 1e-2
+        torch.testing.assert_close(got, want, rtol=1e-1, atol=1e-1)
+        assert (d["state"][slot].cpu() - st).norm() / st.norm() < 1e-2
+    else:
+        torch.testing.assert_close(out.float().cpu(), want, rtol=3e-2, atol=3e-2)
+        torch.testing.assert_close(d["state"][slot].cpu(), st, rtol=2e-2, atol=2e-2)
     torch.testing.assert_close(d["conv_state"][slot].cpu(), hist, rtol=0, atol=0)
 
 
