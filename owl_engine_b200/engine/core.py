@@ -43,6 +43,7 @@ class EngineConfig:
     decode_gemv: str = "dp4a"      # W4 decode arm: "dp4a" (legacy streaming kernels) or "tc" (tcgen05 streaming kernel)
     seed: int = 0
     n_layers: int | None = None    # override (tests / smoke)
+    snap_cut: bool = False         # cut a separate chunk at the prompt's last block boundary instead of snapshotting inside a chunk
     kv_dtype: str = "fp8"          # KV pool format: "fp8" (e4m3) or "int8" (per token, per head scales)
     kvmem_budget: int = 0          # tokens of KV a decode step may attend to (0 = everything): longer contexts attend to a
                                    # view of sink + recent + best-scoring blocks, re-selected at every block boundary
@@ -305,11 +306,18 @@ class Engine:
                 if lo < hi:
                     embeds[lo - start:hi - start] = emb[lo - first:hi - first].to(self.device, torch.bfloat16)
             pos3 = seq.pos3[:, start:end].to(self.device)
-        tok = self.runner.prefill_chunk_forward(ids, start, seq.row, seq.slot, want_logits=want_token, embeds=embeds,
-                                                pos3=pos3)
-        seq.n_cached = end
         boundary = (seq.n_prompt - 1) // PAGE * PAGE
-        if end == boundary and boundary > seq.reused and seq.chain is not None and len(seq.chain):
+        can_snap = boundary > seq.reused and seq.chain is not None and len(seq.chain)
+        snap = None
+        if can_snap and start < boundary < end:
+            # the last block boundary lies inside this chunk: the runner leaves the GDN state of that point in the snapshot row
+            row = self.states.snapshot(int(seq.chain[boundary // PAGE - 1]), boundary)
+            if row is not None:
+                snap = (boundary - start, row)
+        tok = self.runner.prefill_chunk_forward(ids, start, seq.row, seq.slot, want_logits=want_token, embeds=embeds,
+                                                pos3=pos3, snap=snap)
+        seq.n_cached = end
+        if end == boundary and can_snap:
             row = self.states.snapshot(int(seq.chain[boundary // PAGE - 1]), boundary)
             if row is not None:
                 self.pool.copy_slot(seq.slot, row)
@@ -320,12 +328,14 @@ class Engine:
         return None
 
     def prefill_plan(self, sid: int) -> list[tuple[int, int]]:
-        """Chunk boundaries for the rest of the prompt: multiples of prefill_chunk plus a cut at the
-        last block boundary (where the GDN snapshot is taken)."""
+        """Chunk boundaries for the rest of the prompt: multiples of prefill_chunk. The GDN snapshot at the last block
+        boundary is taken inside the chunk that contains it (``snap`` of the runner), so no few-row tail chunk is cut
+        off; ``cfg.snap_cut`` restores the separate cut."""
         seq = self.seqs[sid]
         n, c = seq.n_prompt, self.cfg.prefill_chunk
         boundary = (n - 1) // PAGE * PAGE
-        cuts = sorted({min(n, x) for x in range(seq.n_cached + c, n + c, c)} | ({boundary} if boundary > seq.n_cached else set()) | {n})
+        extra = {boundary} if (self.cfg.snap_cut and boundary > seq.n_cached) else set()
+        cuts = sorted({min(n, x) for x in range(seq.n_cached + c, n + c, c)} | extra | {n})
         out, lo = [], seq.n_cached
         for hi in cuts:
             if hi > lo:

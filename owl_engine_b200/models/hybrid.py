@@ -646,12 +646,28 @@ class HybridRunner:
             return linear.nvfp4_gemm(w, x, out, arm=self.prefill_gemm)
         return linear.w4_gemm(w, x, out, arm=self.prefill_gemm)
 
+    def _gdn_prefill(self, lw, gi: int, wide, nq: int, ab, conv, mix, t: int, gdn_slot: int, use_state: bool, snap) -> None:
+        """Convolution + delta-rule scan of one GDN layer over the chunk's rows. With ``snap = (rows, state_row)`` the
+        scan stops after ``rows`` rows, the layer's convolution history and recurrent state are copied to ``state_row``
+        (the prefix snapshot at a block boundary inside the chunk) and the remaining rows follow."""
+        sp, pool = self.spec, self.pool
+        parts = [(0, t)] if snap is None else [(0, snap[0]), (snap[0], t)]
+        for a, b in parts:
+            st = use_state or a > 0
+            K.gdn_conv_fwd(wide[a:], nq, lw.conv_w, pool.conv_state[gi], gdn_slot, conv[a:], b - a, sp.nk, sp.nv, st)
+            K.gdn_scan(conv[a:], wide[a:, sp.conv_dim:], nq, ab[a:], self.ldab, lw.a_log, lw.dt_bias, lw.gamma,
+                       pool.rec_state[gi], gdn_slot, mix[a:], b - a, sp.nk, sp.nv, st, sp.eps)
+            if snap is not None and b == snap[0]:
+                pool.conv_state[gi, snap[1]].copy_(pool.conv_state[gi, gdn_slot])
+                pool.rec_state[gi, snap[1]].copy_(pool.rec_state[gi, gdn_slot])
+
     def prefill_chunk_forward(self, ids: torch.Tensor, pos0: int, seq_row: int, gdn_slot: int, *,
                               pos3: torch.Tensor | None = None, want_logits: bool = True,
-                              embeds: torch.Tensor | None = None):
+                              embeds: torch.Tensor | None = None, snap: tuple | None = None):
         """Run one prefill chunk (eager). ``ids`` int32 [T] on device; KV pages for positions
         pos0..pos0+T-1 must already be in ``block_table[seq_row]``. Returns the argmax token of
-        the last row when ``want_logits``."""
+        the last row when ``want_logits``. ``snap = (rows, state_row)``: also leave the GDN state after the first
+        ``rows`` rows of the chunk in ``state_row`` (0 < rows < T)."""
         from ..ops import linear
 
         sp, pool = self.spec, self.pool
@@ -659,7 +675,7 @@ class HybridRunner:
         pipe = self._pipe()
         if pipe is not None and t >= self.SP_FROM and t <= pipe.rows and self.prefill_gemm in ("tc", "tcr") and self.taps is None \
                 and self.w.layout != "nvfp4":
-            return self._prefill_chunk_sp(pipe, ids, pos0, seq_row, gdn_slot, pos3, want_logits, embeds)
+            return self._prefill_chunk_sp(pipe, ids, pos0, seq_row, gdn_slot, pos3, want_logits, embeds, snap)
         ws = self._prefill_ws(max(t, 16))
         h, x = ws["h"][:t], ws["x"][:t]
         if pos3 is None:
@@ -693,11 +709,8 @@ class HybridRunner:
                 self._gemm(lw.qkvz, x, wide)
                 ab = ws["ab"][:t]
                 linear.dense_gemm(x, lw.ab_dense, ab, arm="baseline" if self.prefill_gemm == "baseline" else "tc")
-                conv = ws["conv"][:t]
-                K.gdn_conv_fwd(wide, nq, lw.conv_w, pool.conv_state[gi], gdn_slot, conv, t, sp.nk, sp.nv, use_state)
                 mix = ws["mix"].view(-1)[:t * sp.value_dim].view(t, sp.value_dim)
-                K.gdn_scan(conv, wide[:, sp.conv_dim:], nq, ab, self.ldab, lw.a_log, lw.dt_bias, lw.gamma,
-                           pool.rec_state[gi], gdn_slot, mix, t, sp.nk, sp.nv, use_state, sp.eps)
+                self._gdn_prefill(lw, gi, wide, nq, ab, ws["conv"][:t], mix, t, gdn_slot, use_state, snap)
                 self._gemm(lw.out_proj, mix, ws["y"][:t])
                 gi += 1
             else:
@@ -753,7 +766,7 @@ class HybridRunner:
             return None
         return getattr(symm, "prefill", None)
 
-    def _prefill_chunk_sp(self, pipe, ids, pos0: int, seq_row: int, gdn_slot: int, pos3, want_logits: bool, embeds):
+    def _prefill_chunk_sp(self, pipe, ids, pos0: int, seq_row: int, gdn_slot: int, pos3, want_logits: bool, embeds, snap=None):
         """Tensor-parallel prefill chunk with the collectives inside the GEMMs: every row-parallel projection is a
         tcgen05 GEMM whose epilogue scatters its partial row tiles to their owner ranks over NVLink; the owner adds
         them to its share of the residual stream, normalises and stores the result into every rank's activation buffer;
@@ -802,11 +815,8 @@ class HybridRunner:
                 pipe.gemm_ag(dense(lw.qkvz), wide, t)
                 ab = ws["ab"][:t]
                 linear.dense_gemm(x, lw.ab_dense, ab, arm="tc")        # after the gathering GEMM: all rows are here
-                conv = ws["conv"][:t]
-                K.gdn_conv_fwd(wide, nq, lw.conv_w, pool.conv_state[gi], gdn_slot, conv, t, sp.nk, sp.nv, use_state)
                 mix = ws["mix"].view(-1)[:t * sp.value_dim].view(t, sp.value_dim)
-                K.gdn_scan(conv, wide[:, sp.conv_dim:], nq, ab, self.ldab, lw.a_log, lw.dt_bias, lw.gamma,
-                           pool.rec_state[gi], gdn_slot, mix, t, sp.nk, sp.nv, use_state, sp.eps)
+                self._gdn_prefill(lw, gi, wide, nq, ab, ws["conv"][:t], mix, t, gdn_slot, use_state, snap)
                 pipe.gemm_rs(mix, dense(lw.out_proj), t)
                 gi += 1
             else:
