@@ -115,7 +115,7 @@ def test_speculative_decoding_with_the_block_draft_reproduces_greedy():
     from owl_engine_b200.engine import spec as S
     from owl_engine_b200.engine.core import Engine, EngineConfig
 
-    cfg = EngineConfig(model="test-hybrid", n_pages=128, n_slots=4, n_snap_rows=2, max_seqs=4, max_seq=512, prefill_chunk=64)
+    cfg = EngineConfig(model="test-hybrid", snap_cut=True, n_pages=128, n_slots=4, n_snap_rows=2, max_seqs=4, max_seq=512, prefill_chunk=64)
     eng = Engine(cfg)
     eng.runner.uniform_rows = True      # the plain baseline uses the arithmetic a speculating engine switches to
     g = torch.Generator().manual_seed(7)

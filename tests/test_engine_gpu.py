@@ -10,8 +10,11 @@ from owl_engine_b200.engine.service import EngineService
 pytestmark = pytest.mark.gpu
 
 
+# snap_cut=True: these tests compare a cold prefill with a prefix-reusing one token for token, which needs the rows after
+# the last block boundary to go through the same kernels in both (a chunk of their own); the default takes the snapshot
+# inside the chunk instead (test_snapshot_inside_a_chunk_equals_the_cut_chunk covers that path).
 def make_engine(**kw):
-    cfg = EngineConfig(model="test-hybrid", n_pages=128, n_slots=4, n_snap_rows=2, max_seqs=4, max_seq=512,
+    cfg = EngineConfig(model="test-hybrid", snap_cut=True, n_pages=128, n_slots=4, n_snap_rows=2, max_seqs=4, max_seq=512,
                        prefill_chunk=64, **kw)
     return Engine(cfg)
 
@@ -46,7 +49,7 @@ def test_prefix_reuse_gives_same_tokens_as_cold_run(uniform_tail):
 def test_pressure_demotes_to_host_then_disk_and_recall_gives_same_tokens(tmp_path, uniform_tail):
     """A pool too small for the working set: published prefixes leave for the pinned-host tier, the host tier's oldest
     blocks leave for disk files, and a returning prompt is served from disk -> host -> device with unchanged output."""
-    eng = Engine(EngineConfig(model="test-hybrid", n_pages=20, n_slots=4, n_snap_rows=8, max_seqs=4,
+    eng = Engine(EngineConfig(model="test-hybrid", snap_cut=True, n_pages=20, n_slots=4, n_snap_rows=8, max_seqs=4,
                                                   max_seq=512, prefill_chunk=64, host_cache_mb=1,
                                                   disk_cache_mb=4, disk_dir=str(tmp_path / "kv")))
     keep = 4
@@ -59,7 +62,7 @@ def test_pressure_demotes_to_host_then_disk_and_recall_gives_same_tokens(tmp_pat
     assert eng.spilled > 0 and len(eng.disk.index) > 0
     assert eng.generate(prompts[0], 5) == first
     assert eng.recalled > 0 and eng.prefix_hits >= 1
-    cold = Engine(EngineConfig(model="test-hybrid", n_pages=128, n_slots=4, n_snap_rows=2, max_seqs=4, max_seq=512,
+    cold = Engine(EngineConfig(model="test-hybrid", snap_cut=True, n_pages=128, n_slots=4, n_snap_rows=2, max_seqs=4, max_seq=512,
                                prefill_chunk=64))
     assert cold.generate(prompts[0], 5) == first
 
@@ -194,7 +197,7 @@ def test_kv_selection_view_covers_everything_or_a_bounded_set():
     from owl_engine_b200.store import select as S
 
     g = torch.Generator().manual_seed(5)
-    base = EngineConfig(model="test-hybrid", n_pages=128, n_slots=4, n_snap_rows=2, max_seqs=4, max_seq=512, prefill_chunk=64)
+    base = EngineConfig(model="test-hybrid", snap_cut=True, n_pages=128, n_slots=4, n_snap_rows=2, max_seqs=4, max_seq=512, prefill_chunk=64)
     prompt = torch.randint(0, 512, (150,), generator=g).tolist()
     plain = Engine(base).generate(prompt, 20)
     from dataclasses import replace
@@ -228,3 +231,27 @@ def test_kv_selection_view_covers_everything_or_a_bounded_set():
     p = S.softmax_scores_gpu(got.to(eng.device), 4.0).cpu()
     assert torch.allclose(p, torch.softmax(got * 4.0, 0), atol=1e-5)
     eng.free_sequence(sid, publish=False)
+
+
+def test_snapshot_inside_a_chunk_equals_the_cut_chunk(uniform_tail):
+    """The GDN snapshot taken inside the chunk that contains the last block boundary holds the same state as the one taken
+    after a chunk cut at the boundary, and a request that reuses it continues identically."""
+    g = torch.Generator().manual_seed(11)
+    prompt = torch.randint(0, 512, (150,), generator=g).tolist()
+    outs, snaps = [], []
+    for cut in (True, False):
+        eng = Engine(EngineConfig(model="test-hybrid", n_pages=128, n_slots=4, n_snap_rows=2, max_seqs=4, max_seq=512,
+                                  prefill_chunk=256, snap_cut=cut))
+        sid = eng.add_sequence(prompt)
+        assert eng.prefill_plan(sid) == ([(0, 144), (144, 150)] if cut else [(0, 150)])
+        eng.prefill(sid)
+        first = eng.runner.logits[:1].float().cpu().clone()
+        snap = eng.states.find(eng.seqs[sid].chain)
+        assert snap is not None and snap.n_tokens == 144
+        snaps.append((eng.pool.rec_state[:, snap.row].clone(), eng.pool.conv_state[:, snap.row].clone()))
+        eng.free_sequence(sid)
+        outs.append((first, eng.generate(prompt + [7, 8, 9], 6), eng.prefix_hits))
+    assert torch.equal(snaps[0][1], snaps[1][1])
+    assert (snaps[0][0] - snaps[1][0]).norm() / snaps[0][0].norm() < 1e-3          # 144 rows vs 144 rows: same chunked scan
+    assert (outs[0][0] - outs[1][0]).norm() / outs[0][0].norm() < 1e-2
+    assert outs[0][2] >= 1 and outs[1][2] >= 1 and len(outs[0][1]) == len(outs[1][1]) == 6

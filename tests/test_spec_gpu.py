@@ -11,7 +11,7 @@ pytestmark = pytest.mark.gpu
 
 
 def make_engine():
-    eng = Engine(EngineConfig(model="test-hybrid", n_pages=128, n_slots=4, n_snap_rows=2, max_seqs=4, max_seq=512,
+    eng = Engine(EngineConfig(model="test-hybrid", snap_cut=True, n_pages=128, n_slots=4, n_snap_rows=2, max_seqs=4, max_seq=512,
                               prefill_chunk=64))
     # the plain baseline uses the same row-count-independent arithmetic a speculating engine switches to
     eng.runner.uniform_rows = True
