@@ -94,6 +94,9 @@ def main() -> None:
     ap.add_argument("--prefill-gemm", default="tc", choices=["tc", "tcr", "tc8", "tc8r", "baseline"],
                     help="prefill GEMM arm: 16-bit tcgen05 (tc), e4m3 tcgen05 W4A8 (tc8), the same with resident dequantised "
                          "weights (tcr, tc8r), dequant + library GEMM (baseline)")
+    ap.add_argument("--head", default="int8", choices=["int8", "bf16"],
+                    help="lm_head storage: per-row int8 (W8A16; the reference's default, profiles/full.toml:144 "
+                         "head_quant = rtn-int8-row) or bf16")
     ap.add_argument("--comm", default="fused", choices=["nccl", "fused", "push"],
                     help="TP collectives: our symmetric-memory kernels (fused) or the NCCL baseline arm")
     args = ap.parse_args()
@@ -122,7 +125,7 @@ def main() -> None:
 
     cfg = EngineConfig(model="qwen3.8-27b", group=128, n_pages=1024, n_slots=2, max_seqs=2,
                        max_seq=args.prompt_len + 2 * (warmup + steps) + 64, n_layers=args.layers,
-                       decode_gemv=args.gemv, prefill_gemm=args.prefill_gemm)
+                       decode_gemv=args.gemv, prefill_gemm=args.prefill_gemm, lm_head_int8=args.head == "int8")
     eng = Engine(cfg, comm=comm)
     if args.sp_prefill >= 0:
         eng.runner.sp_prefill = bool(args.sp_prefill)
@@ -236,7 +239,8 @@ def main() -> None:
             "impl": "ours",
             "config": {"model": "qwen3.8-27b hybrid (64 layers, hidden 5120, vocab 151936)", "global_batch": 1,
                        "seq_len": args.prompt_len, "generated": steps, "parallelism": f"tp{world}",
-                       "weights": "int4 g128 asym (W4A16)", "kv": "fp8 e4m3 paged, block 16",
+                       "weights": "int4 g128 asym (W4A16)",
+                       "lm_head": "int8 per row, W8A16 (reference default head_quant = rtn-int8-row)" if args.head == "int8" else "bf16", "kv": "fp8 e4m3 paged, block 16",
                        "l2": "inputs larger than L2: every step streams the full weight set "
                              f"({eng.weights.streamed_bytes() / 1e9:.1f} GB per rank)",
                        "comm": args.comm if world > 1 else "none",
