@@ -594,6 +594,15 @@ class HybridRunner:
         if g is not None:
             return g
         lay = StepLayout(b, t)
+        if self.comm is not None and not getattr(self.comm, "capturable", True):
+            # a transport that crosses the host (relay fallback) cannot be captured: the "graph" is the eager step
+            runner = self
+
+            class _Eager:
+                def replay(self_inner):
+                    runner.step_forward(lay, ctx_hint=ctx_hint, advance=advance, sample=sample)
+            self.graphs[key] = _Eager()
+            return self.graphs[key]
         stream = torch.cuda.Stream(device=self.device)
         stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(stream):

@@ -8,6 +8,8 @@ Two arms, selected per call site by ``mode``:
   its partial sums into every rank's slot buffer over NVLink (peer stores, tile by tile while the matrix
   streams) and the consumer kernel reduces local memory only (``csrc/gemv.cu`` EPI_PUSH +
   ``owl_push_residual_norm``);
+* ``"host"``  -- the fallback for GPU pairs that may not map each other's memory (``parallel/peer.py``): payloads
+  cross through pinned host memory and a ``gloo`` all-reduce; not capturable, the runner steps eagerly;
 * ``"fused"`` -- the product path: hand-written kernels over symmetric (peer-mapped) memory
   (``parallel/symm.py`` + ``csrc/comm.cu``): one-shot all-reduce fused with the residual add for
   decode-size payloads, reduce-scatter / all-gather fused into the GEMM epilogue / prologue for
@@ -32,6 +34,12 @@ class TpComm:
         self.rank, self.world, self.device, self.mode = rank, world, device, mode
         self.group = group
         self.symm = None
+        self.relay = None
+        self.capturable = mode != "host"
+        if mode == "host" and world > 1:
+            from .peer import HostRelay
+
+            self.relay = HostRelay()
         if mode in ("fused", "push") and world > 1:
             from .symm import SymmetricWorkspace
 
@@ -56,12 +64,19 @@ class TpComm:
         if self.symm is not None:
             self.symm.allreduce_add_residual(partial, h, m)
             return
+        if self.relay is not None:
+            self.relay.allreduce_(partial[:m])
+            h[:m].add_(partial[:m])
+            return
         dist.all_reduce(partial[:m], group=self.group)
         h[:m].add_(partial[:m])
 
     def allreduce_prefill(self, y: torch.Tensor) -> None:
         if self.symm is not None and self.symm.can_reduce(y):
             self.symm.allreduce_(y)
+            return
+        if self.relay is not None:
+            self.relay.allreduce_(y)
             return
         dist.all_reduce(y, group=self.group)
 

@@ -52,7 +52,7 @@ SCHEMA: dict = {
     "runtime": {"admission_on_full": str, "default_max_new": int, "max_new_cap": int, "max_seq": int,
                 "prefill_chunk": int, "max_batch": int},
     "parallel": {"mode": Enum("single", "tp", "layer"), "device": ListOf(str, lengths=(0, 1, 2, 4, 8)),
-                 "tp_ar": Enum("nccl", "fused", "multimem"), "tp_ar_f8": bool, "tp_comm": Enum("p2p", "nccl"),
+                 "tp_ar": Enum("nccl", "fused", "push", "multimem"), "tp_ar_f8": bool, "tp_comm": Enum("p2p", "nccl", "host"),
                  "tp_vocab_split": bool, "tp_fused_gemm": bool},
     "model": {"name": str, "path": str, "format": Enum("safetensors", "awq", "w4a16", "nvfp4", "gguf", "random"),
               "quant": Enum("bf16", "w4a16", "w4a8", "nvfp4", "gguf"), "group": Enum(32, 128),

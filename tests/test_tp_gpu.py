@@ -79,7 +79,7 @@ def _worker(rank, world, port, mode, q):
     os._exit(0)
 
 
-@pytest.mark.parametrize("mode", ["nccl", "fused", "push"])
+@pytest.mark.parametrize("mode", ["nccl", "fused", "push", "host"])
 def test_tp2_matches_and_is_rank_consistent(mode):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
