@@ -91,7 +91,7 @@ def main() -> None:
     ap.add_argument("--sp-prefill", type=int, default=-1, choices=[-1, 0, 1],
                     help="N > 1: prefill through the GEMM-fused reduce-scatter / all-gather path (1), the all-reduce path (0), "
                          "or the runner's default (-1)")
-    ap.add_argument("--prefill-gemm", default="tc", choices=["tc", "tcr", "tc8", "tc8r", "baseline"],
+    ap.add_argument("--prefill-gemm", default="tcr", choices=["tc", "tcr", "tc8", "tc8r", "baseline"],
                     help="prefill GEMM arm: 16-bit tcgen05 (tc), e4m3 tcgen05 W4A8 (tc8), the same with resident dequantised "
                          "weights (tcr, tc8r), dequant + library GEMM (baseline)")
     ap.add_argument("--head", default="int8", choices=["int8", "bf16"],
