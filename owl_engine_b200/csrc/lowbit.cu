@@ -80,7 +80,7 @@ __global__ void __launch_bounds__(256) nvfp4_gemv_kernel(const uint8_t* __restri
 
 // x = sx * (128 h + l) per element; chunk byte order as written by actpack_emit
 __global__ void __launch_bounds__(256) act_unpack_kernel(const uint4* __restrict__ xpack, const float2* __restrict__ xs,
-                                                         __nv_bfloat16* __restrict__ out, int ldo, int nchunks, int cpg) {
+                                                         __nv_bfloat16* __restrict__ out, int ldo, int nchunks, int cpg, int out_f16) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x, row = blockIdx.y;
   if (c >= nchunks) return;
   const uint4 pk = xpack[(size_t)row * nchunks + c];
@@ -94,7 +94,24 @@ __global__ void __launch_bounds__(256) act_unpack_kernel(const uint4* __restrict
     v[klo[b]] = sx * (float)(hl * 128 + ll);
     v[khi[b]] = sx * (float)(hb * 128 + lb);
   }
-  *reinterpret_cast<uint4*>(out + (size_t)row * ldo + c * 8) = pack_bf16x8(v);
+  if (out_f16) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = clamp_h(v[i]);
+  }
+  *reinterpret_cast<uint4*>(out + (size_t)row * ldo + c * 8) = out_f16 ? pack_f16x8(v) : pack_bf16x8(v);
+}
+
+// out[m][n] = a[m][n] + b[m][n] (bf16 rows with leading dimensions; the residual epilogue of the GEMM arms)
+__global__ void __launch_bounds__(256) add_rows_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfloat16* __restrict__ b,
+                                                       int ldb, __nv_bfloat16* __restrict__ out, int ldo, int n8) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x, row = blockIdx.y;
+  if (c >= n8) return;
+  float x[8], y[8];
+  unpack_bf16x8(*reinterpret_cast<const uint4*>(a + (size_t)row * lda + c * 8), x);
+  unpack_bf16x8(*reinterpret_cast<const uint4*>(b + (size_t)row * ldb + c * 8), y);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) x[i] += y[i];
+  *reinterpret_cast<uint4*>(out + (size_t)row * ldo + c * 8) = pack_bf16x8(x);
 }
 
 __global__ void __launch_bounds__(256) nvfp4_dequant_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ sf,
@@ -293,11 +310,20 @@ OWL_API int owl_nvfp4_dequant_rows(const void* codes, const void* sf, float alph
   return OWL_OK;
 }
 // ActPack rows (15-bit fixed point + per-group scale, row layout) back to bf16 [M][ldo]: the input of the float GEMV arms.
-OWL_API int owl_act_unpack(const void* xpack, const void* xs, void* out, int ldo, int M, int K, int G, cudaStream_t st) {
+// out: bf16 (out_f16 = 0) or fp16 (out_f16 = 1) [M][ldo].
+OWL_API int owl_act_unpack(const void* xpack, const void* xs, void* out, int ldo, int M, int K, int G, int out_f16, cudaStream_t st) {
   if (M < 1 || (K & 7) || (G != 32 && G != 128) || (K % G) || (ldo & 7)) return OWL_ERR_BAD_ARG;
   const int nchunks = K / 8;
   act_unpack_kernel<<<dim3((nchunks + 255) / 256, M), 256, 0, st>>>((const uint4*)xpack, (const float2*)xs, (__nv_bfloat16*)out, ldo,
-                                                                     nchunks, G >> 3);
+                                                                     nchunks, G >> 3, out_f16);
+  OWL_LAUNCH_CHECK();
+  return OWL_OK;
+}
+// out = a + b over M rows of N bf16 values (N multiple of 8; out may alias a or b).
+OWL_API int owl_add_rows(const void* a, int lda, const void* b, int ldb, void* out, int ldo, int M, int N, cudaStream_t st) {
+  if (M < 1 || N < 8 || (N & 7) || (lda & 7) || (ldb & 7) || (ldo & 7)) return OWL_ERR_BAD_ARG;
+  add_rows_kernel<<<dim3((N / 8 + 255) / 256, M), 256, 0, st>>>((const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)b, ldb,
+                                                               (__nv_bfloat16*)out, ldo, N / 8);
   OWL_LAUNCH_CHECK();
   return OWL_OK;
 }

@@ -356,6 +356,7 @@ class HybridRunner:
         self._pf = None   # lazily allocated prefill workspace
         self.taps: dict | None = None   # layer -> bf16 [M,H] buffers filled during decode/prefill for draft heads
         self._x16 = self._gu16 = None   # bf16 staging of the NVFP4 GEMV arm (allocated on first use)
+        self._x16h = self._y16 = None   # fp16 activations / bf16 outputs of the batched dense-GEMM arm
         self.tap_sink = None            # callable(pos0, t, {layer: [t, H]}) called after every prefill chunk when taps are on
         self.pre_hook = None            # callable(m): rewrites self.h after the embedding (draft heads mix in the target's hidden)
         self.uniform_rows = False       # per-row arithmetic independent of the number of rows in the step (speculative
@@ -382,6 +383,9 @@ class HybridRunner:
         if w.layout == "nvfp4":
             self._gemv_nvfp4(w, xp, xs, out, m, residual, epi, ldo)
             return
+        if m >= self.BATCH_GEMM_FROM and self.prefill_gemm == "tcr" and w.layout == "slice" and epi in (K.EPI_STORE, K.EPI_RESIDUAL, K.EPI_SILU_MUL):
+            self._gemv_dense16(w, xp, xs, out, m, residual, epi, ldo)
+            return
         if w.layout != "block":
             K.w4a16_skinny(w, xp, xs, out, m, residual=residual, epi=epi, ldo=ldo, pdl=pdl,
                            force_mma=self.uniform_rows and m == 1)
@@ -392,6 +396,34 @@ class HybridRunner:
             K.w4a16_stream_tc(w, xp.view(-1)[(r0 // 8) * tb:], out[r0:], rows, self.tc_ws,
                               residual=None if residual is None else residual[r0:], epi=epi,
                               ldo=ldo if ldo is not None else out.shape[-1], pdl=pdl)
+
+    BATCH_GEMM_FROM = 16   # rows from which a batched step multiplies the resident fp16 weight copy on the dense tcgen05 GEMM
+
+    def _gemv_dense16(self, w, xp, xs, out, m: int, residual, epi: int, ldo) -> None:
+        """Wide batched steps (16+ rows) with a resident fp16 copy of the weights (``prefill_gemm = "tcr"``): the integer
+        weight-streaming arms run on warp-level MMA and grow linearly with the row count from 8 rows on, while the dense
+        tcgen05 GEMM streams the 4x larger fp16 matrix once for all rows -- at 32 rows that is the faster side."""
+        from ..ops import gemm_tc, linear
+
+        sp = self.spec
+        if self._x16h is None:
+            kmax = max(sp.hidden, sp.inter, sp.value_dim, sp.hq * sp.hd)
+            nmax = max(2 * sp.inter, sp.conv_dim + sp.value_dim, self.qkv_n, sp.hidden)
+            self._x16h = torch.empty(self.MAX_ROWS, kmax, dtype=torch.float16, device=self.device)
+            self._y16 = torch.empty(self.MAX_ROWS * nmax, dtype=torch.bfloat16, device=self.device)
+        x = self._x16h[:m, :w.k]
+        K.act_unpack(xp, xs, x, m, w.k, self.G)
+        dense = linear.w4_dense(w, torch.float16, self.device, resident=True)
+        direct = epi == K.EPI_STORE
+        ld = (ldo if ldo is not None else out.shape[-1]) if direct else w.n
+        y = (out.view(-1)[:m * ld] if direct and out.is_contiguous() and (ldo is None or ldo == out.shape[-1]) else self._y16[:m * ld]).view(m, ld)
+        gemm_tc.f16_gemm(x, dense, y, force_small=True)
+        if epi == K.EPI_RESIDUAL:
+            K.add_rows(residual, y, out, m, w.n)
+        elif epi == K.EPI_SILU_MUL:
+            K.silu_mul(y, m, w.n // 2, out=out, pdl=False)
+        elif y.data_ptr() != out.data_ptr():
+            out[:m, :w.n].copy_(y[:, :w.n])
 
     def _gemv_nvfp4(self, w, xp, xs, out, m: int, residual, epi: int, ldo) -> None:
         """NVFP4 weights as stored in the checkpoint (e2m1 codes + e4m3 block scales): the activations come back from

@@ -314,7 +314,8 @@ register("owl_nvfp4_gemv", [_P, _P, _F, _P, _I, _P, _I, _I, _I, _I, _P])
 register("owl_nvfp4_gemv_res", [_P, _P, _F, _P, _I, _P, _I, _P, _I, _I, _I, _P])
 register("owl_nvfp4_gemv_rows", [_P, _P, _F, _P, _P, _I, _P, _I, _P, _I, _I, _I, _P])
 register("owl_nvfp4_dequant_rows", [_P, _P, _F, _P, _I, _P, c_longlong, _P])
-register("owl_act_unpack", [_P, _P, _P, _I, _I, _I, _I, _P])
+register("owl_act_unpack", [_P, _P, _P, _I, _I, _I, _I, _I, _P])
+register("owl_add_rows", [_P, _I, _P, _I, _P, _I, _I, _I, _P])
 register("owl_nvfp4_dequant", [_P, _P, _F, _P, c_longlong, _P])
 register("owl_nvfp4_quant_act", [_P, _F, _P, _P, c_longlong, _P])
 register("owl_gguf_dequant", [_P, _I, _I, _P, _I, _P, _P])
@@ -355,8 +356,13 @@ def nvfp4_linear_dequant(w, out):
 
 
 def act_unpack(xpack, xs, out, m: int, k: int, group: int = 128) -> None:
-    """ActPack rows (row layout) -> bf16 ``out[:m, :k]``."""
-    call("owl_act_unpack", ptr(xpack), ptr(xs), ptr(out), out.stride(0), m, k, group, stream())
+    """ActPack rows (row layout) -> bf16 or fp16 (by ``out.dtype``) ``out[:m, :k]``."""
+    call("owl_act_unpack", ptr(xpack), ptr(xs), ptr(out), out.stride(0), m, k, group, _is_f16(out), stream())
+
+
+def add_rows(a, b, out, m: int, n: int) -> None:
+    """``out[:m, :n] = a[:m, :n] + b[:m, :n]`` (bf16)."""
+    call("owl_add_rows", ptr(a), a.stride(0), ptr(b), b.stride(0), ptr(out), out.stride(0), m, n, stream())
 
 
 def nvfp4_dequant(codes, scales, alpha: float, out=None):

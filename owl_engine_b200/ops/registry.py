@@ -61,6 +61,7 @@ _T = [
     KernelSpec("owl_nvfp4_gemv_rows", "lowbit.cu", "gemv"),
     KernelSpec("owl_nvfp4_dequant_rows", "lowbit.cu", "load"),
     KernelSpec("owl_act_unpack", "lowbit.cu", "elem"),
+    KernelSpec("owl_add_rows", "lowbit.cu", "elem"),
     KernelSpec("owl_nvfp4_dequant", "lowbit.cu", "load"),
     KernelSpec("owl_nvfp4_quant_act", "lowbit.cu", "quant"),
     KernelSpec("owl_gguf_dequant", "lowbit.cu", "load"),

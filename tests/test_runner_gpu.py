@@ -264,3 +264,29 @@ def test_nvfp4_checkpoint_loader_weights_run_through_the_per_row_scale_kernels()
         torch.cuda.synchronize()
         outs.append(r.logits[:1].float().cpu())
     assert torch.isfinite(outs[0]).all() and rel_err(outs[0], outs[1]) < 0.5
+
+
+def test_wide_batched_step_on_the_resident_dense_weights_matches_the_streaming_arm():
+    """16+ rows with prefill_gemm = "tcr": the step multiplies the resident fp16 weight copy on the dense tcgen05 GEMM;
+    logits agree with the integer weight-streaming arm on the same rows."""
+    spec, run, _ = build("tcr")
+    _, run_ref, _ = build("tc")
+    b = 16
+    g = torch.Generator().manual_seed(4)
+    outs = []
+    for r in (run, run_ref):
+        lay = H.StepLayout(b, 1)
+        v = r.views(lay)
+        for i in range(b):
+            r.block_table[i % 4, :2] = torch.tensor([2 * (i % 4), 2 * (i % 4) + 1], dtype=torch.int32, device=DEV)
+        v["ids"].copy_(torch.randint(0, spec.vocab, (b,), generator=torch.Generator().manual_seed(4)).to(torch.int32))
+        v["pos3"][:] = 0
+        v["kv_slot"].copy_(torch.arange(b, dtype=torch.int32) % 4 * 32)
+        v["ctx"][:] = 1
+        v["gslot"].copy_(torch.arange(b, dtype=torch.int32) % 4)
+        v["bt_row"].copy_(torch.arange(b, dtype=torch.int32) % 4)
+        r.step_forward(lay, ctx_hint=64)
+        torch.cuda.synchronize()
+        outs.append(r.logits[:b].float().cpu())
+    assert run._x16h is not None and run_ref._x16h is None
+    assert rel_err(outs[0], outs[1]) < 0.03
