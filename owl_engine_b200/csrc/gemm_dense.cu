@@ -55,6 +55,9 @@ struct GdParams {
   int* rs_done;                      // local [m_tiles]: weight tiles finished per row tile
   const float* a_scale;              // e4m3 form: per-token and per-weight-row scales
   const float* b_scale;
+  int ksplit;                        // > 1: the k range is cut in ksplit parts, fp32 partial tiles go to `partial`
+  float* partial;                    // [ksplit][T][ldp]
+  int ldp;
 };
 struct GdCtl {
   uint64_t full[GD_STAGES], empty[GD_STAGES], acc_full[2], acc_empty[2];
@@ -90,7 +93,8 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gemm_dense_kernel(const __grid_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int BKE = F8 ? 2 * GD_BK : GD_BK;           // k elements per stage (128 bytes per row either way)
   const int KI = p.K / BKE;
-  const int n_tiles_total = p.m_tiles * p.n_tiles;
+  const int KS = p.ksplit > 1 ? p.ksplit : 1;
+  const int n_tiles_total = p.m_tiles * p.n_tiles * KS;     // tile index = (m + m_tiles * n) * KS + k part
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < GD_STAGES; ++s) { mbar_init(&ctl->full[s], 1); mbar_init(&ctl->empty[s], 1); }
@@ -113,10 +117,12 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gemm_dense_kernel(const __grid_
     if (lane == 0) {
       int it = 0;                                           // stage counter across tiles
       for (int tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x) {
-        const int m0 = (tile % p.m_tiles) * GD_BM, n0 = (tile / p.m_tiles) * GD_BN;
+        const int mn = tile / KS, ks = tile % KS;
+        const int m0 = (mn % p.m_tiles) * GD_BM, n0 = (mn / p.m_tiles) * GD_BN;
+        const int kb = ks * KI / KS, ke = (ks + 1) * KI / KS;
         if (AG) {
           // the rows of this tile are written by their owner rank; its flag says they have landed
-          const int j = tile % p.m_tiles;
+          const int j = mn % p.m_tiles;
           const uint32_t* f = p.ag_flags + (j % p.world) * p.max_local + j / p.world;
           bool got = false;
           for (uint32_t i = 0; i < p.spin_limit; ++i) {
@@ -131,7 +137,7 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gemm_dense_kernel(const __grid_
           }
           asm volatile("fence.proxy.async;" ::: "memory");   // peer-written rows are read by the copy engine next
         }
-        for (int k = 0; k < KI; ++k, ++it) {
+        for (int k = kb; k < ke; ++k, ++it) {
           const int s = it % GD_STAGES;
           if (!gd_wait(&ctl->empty[s], (((uint32_t)(it / GD_STAGES)) & 1u) ^ 1u, ctl, OWL_ERR_WAIT_MMA)) goto prod_done;
           mbar_expect_tx(&ctl->full[s], GD_STAGE_BYTES);
@@ -157,7 +163,8 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gemm_dense_kernel(const __grid_
         tc_fence_after();
         const uint32_t td = tmem + ab * GD_BN;
         bool ok = true;
-        for (int k = 0; k < KI; ++k, ++it) {
+        const int kb = (tile % KS) * KI / KS, ke = (tile % KS + 1) * KI / KS;
+        for (int k = kb; k < ke; ++k, ++it) {
           const int s = it % GD_STAGES;
           if (!gd_wait(&ctl->full[s], ((uint32_t)(it / GD_STAGES)) & 1u, ctl, OWL_ERR_WAIT_TMA)) { ok = false; break; }
           tc_fence_after();
@@ -165,8 +172,8 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gemm_dense_kernel(const __grid_
           const uint64_t da = umma_desc_k128(sa), db = umma_desc_k128(sa + GD_A_BYTES);
 #pragma unroll
           for (int k4 = 0; k4 < GD_BK / 16; ++k4) {       // 32 bytes of k per instruction in both forms
-            if (F8) tc_mma_f8(td, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2), idesc, (k > 0 || k4 > 0) ? 1u : 0u);
-            else tc_mma_f16(td, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2), idesc, (k > 0 || k4 > 0) ? 1u : 0u);
+            if (F8) tc_mma_f8(td, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2), idesc, (k > kb || k4 > 0) ? 1u : 0u);
+            else tc_mma_f16(td, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2), idesc, (k > kb || k4 > 0) ? 1u : 0u);
           }
           tc_commit(&ctl->empty[s]);
         }
@@ -179,12 +186,13 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gemm_dense_kernel(const __grid_
     int lt = 0;
     for (int tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x, ++lt) {
       const int ab = lt & 1;
-      const int m0 = (tile % p.m_tiles) * GD_BM, n0 = (tile / p.m_tiles) * GD_BN;
+      const int mn = tile / KS;
+      const int m0 = (mn % p.m_tiles) * GD_BM, n0 = (mn / p.m_tiles) * GD_BN;
       if (!gd_wait(&ctl->acc_full[ab], ((uint32_t)(lt >> 1)) & 1u, ctl, OWL_ERR_WAIT_MMA)) break;
       tc_fence_after();
       const int row = m0 + q4 * 32 + lane;
       __nv_bfloat16* obase = p.out + (size_t)row * p.ldo;
-      const int jt = tile % p.m_tiles;
+      const int jt = mn % p.m_tiles;
       if (RS)   // slot [this rank] of the owner of row tile jt, at the tile's local position
         obase = p.rs_dst[jt % p.world] +
                 ((size_t)p.rank * p.max_local * GD_BM + (size_t)(jt / p.world) * GD_BM + q4 * 32 + lane) * p.ldo;
@@ -201,7 +209,15 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gemm_dense_kernel(const __grid_
             r[v] = __float_as_uint(__uint_as_float(r[v]) * sa * (col < p.N ? p.b_scale[col] : 0.f));
           }
         }
-        if (row < p.T) {
+        if (!AG && !RS && KS > 1) {
+          // k-split: fp32 partial tile (scaled already in the e4m3 form); the reduce kernel sums the parts
+          if (row < p.T) {
+            float* po = p.partial + ((size_t)(tile % KS) * p.T + row) * p.ldp + n0 + c * 32;
+#pragma unroll
+            for (int v = 0; v < 8; ++v)
+              *reinterpret_cast<uint4*>(po + v * 4) = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
+          }
+        } else if (row < p.T) {
           __nv_bfloat16* o = obase + n0 + c * 32;
           if (n0 + c * 32 + 32 <= p.N) {
 #pragma unroll
@@ -243,6 +259,25 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gemm_dense_kernel(const __grid_
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
+  }
+}
+
+// out[row][col] = bf16(sum over parts): grid (ceil(N / 1024), T), 256 threads x 4 columns
+__global__ void __launch_bounds__(256) gemm_ksplit_reduce_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
+                                                                 int T, int N, int ldp, int ldo, int ks) {
+  const int row = blockIdx.y, col = (blockIdx.x * 256 + threadIdx.x) * 4;
+  if (col >= N) return;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int s = 0; s < ks; ++s) {
+    const float4 v = *reinterpret_cast<const float4*>(partial + ((size_t)s * T + row) * ldp + col);
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  }
+  __nv_bfloat16* o = out + (size_t)row * ldo + col;
+  if (col + 4 <= N) {
+    *reinterpret_cast<uint2*>(o) = make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
+  } else {
+    const float a[4] = {acc.x, acc.y, acc.z, acc.w};
+    for (int i = 0; i < 4 && col + i < N; ++i) o[i] = __float2bfloat16(a[i]);
   }
 }
 
@@ -300,13 +335,34 @@ static int gd_launch(const void* x, int ldx, const void* w, int ldw, GdParams& p
       return OWL_ERR_LAUNCH * 1000;
     }
   }
-  const int tiles = p.m_tiles * p.n_tiles;
+  int tiles = p.m_tiles * p.n_tiles;
+  // few output tiles (small T and a narrow weight): cut k so that every SM streams a share of the weight; the fp32
+  // partial tiles (at most 148 tiles of 128 x 256 floats = 19.4 MB) live in a per-process scratch allocated on first use
+  // (outside any stream capture: the warm-up call of a captured step comes first)
+  static float* ks_scratch = nullptr;
+  constexpr size_t KS_SCRATCH = (size_t)160 * GD_BM * GD_BN * sizeof(float);
+  p.ksplit = 1;
+  const int KIs = p.K / (p.fmt == 2 ? 2 * GD_BK : GD_BK);
+  if ((mode == 0 || mode == 3) && tiles * 2 <= sms && KIs >= 8) {
+    int ks = sms / tiles;
+    if (ks > KIs / 4) ks = KIs / 4;
+    if (ks > 16) ks = 16;
+    p.ldp = p.n_tiles * GD_BN;
+    if (ks > 1 && (size_t)ks * p.T * p.ldp * sizeof(float) <= KS_SCRATCH) {
+      if (!ks_scratch && cudaMalloc(&ks_scratch, KS_SCRATCH) != cudaSuccess) ks_scratch = nullptr;
+      if (ks_scratch) { p.ksplit = ks; p.partial = ks_scratch; tiles *= ks; }
+    }
+  }
   const int grid = tiles < sms ? tiles : sms;
   if (mode == 0) gemm_dense_kernel<false, false, false><<<grid, GD_THREADS, GD_SMEM, st>>>(a, b, p);
   else if (mode == 1) gemm_dense_kernel<true, false, false><<<grid, GD_THREADS, GD_SMEM, st>>>(a, b, p);
   else if (mode == 2) gemm_dense_kernel<false, true, false><<<grid, GD_THREADS, GD_SMEM, st>>>(a, b, p);
   else gemm_dense_kernel<false, false, true><<<grid, GD_THREADS, GD_SMEM, st>>>(a, b, p);
   OWL_LAUNCH_CHECK();
+  if (p.ksplit > 1) {
+    gemm_ksplit_reduce_kernel<<<dim3((p.N + 1023) / 1024, p.T), 256, 0, st>>>(p.partial, p.out, p.T, p.N, p.ldp, p.ldo, p.ksplit);
+    OWL_LAUNCH_CHECK();
+  }
   return OWL_OK;
 }
 

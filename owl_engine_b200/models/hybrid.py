@@ -356,7 +356,7 @@ class HybridRunner:
         self._pf = None   # lazily allocated prefill workspace
         self.taps: dict | None = None   # layer -> bf16 [M,H] buffers filled during decode/prefill for draft heads
         self._x16 = self._gu16 = None   # bf16 staging of the NVFP4 GEMV arm (allocated on first use)
-        self._x16h = self._y16 = None   # fp16 activations / bf16 outputs of the batched dense-GEMM arm
+        self._x16h = self._y16 = self._xq8 = None   # fp16 / e4m3 activations and bf16 outputs of the batched dense-GEMM arm
         self.tap_sink = None            # callable(pos0, t, {layer: [t, H]}) called after every prefill chunk when taps are on
         self.pre_hook = None            # callable(m): rewrites self.h after the embedding (draft heads mix in the target's hidden)
         self.uniform_rows = False       # per-row arithmetic independent of the number of rows in the step (speculative
@@ -383,7 +383,8 @@ class HybridRunner:
         if w.layout == "nvfp4":
             self._gemv_nvfp4(w, xp, xs, out, m, residual, epi, ldo)
             return
-        if m >= self.BATCH_GEMM_FROM and self.prefill_gemm == "tcr" and w.layout == "slice" and epi in (K.EPI_STORE, K.EPI_RESIDUAL, K.EPI_SILU_MUL):
+        if m >= self.BATCH_GEMM_FROM and self.prefill_gemm in ("tcr", "tc8r") and w.layout == "slice" and w.k % 128 == 0 \
+                and epi in (K.EPI_STORE, K.EPI_RESIDUAL, K.EPI_SILU_MUL):
             self._gemv_dense16(w, xp, xs, out, m, residual, epi, ldo)
             return
         if w.layout != "block":
@@ -397,12 +398,13 @@ class HybridRunner:
                               residual=None if residual is None else residual[r0:], epi=epi,
                               ldo=ldo if ldo is not None else out.shape[-1], pdl=pdl)
 
-    BATCH_GEMM_FROM = 16   # rows from which a batched step multiplies the resident fp16 weight copy on the dense tcgen05 GEMM
+    BATCH_GEMM_FROM = 16   # rows from which a batched step multiplies the resident dense weight copy on the tcgen05 GEMM
 
     def _gemv_dense16(self, w, xp, xs, out, m: int, residual, epi: int, ldo) -> None:
-        """Wide batched steps (16+ rows) with a resident fp16 copy of the weights (``prefill_gemm = "tcr"``): the integer
-        weight-streaming arms run on warp-level MMA and grow linearly with the row count from 8 rows on, while the dense
-        tcgen05 GEMM streams the 4x larger fp16 matrix once for all rows -- at 32 rows that is the faster side."""
+        """Wide batched steps (16+ rows) with a resident dense copy of the weights (``prefill_gemm = "tcr"``: fp16, 4x the
+        int4 bytes; ``"tc8r"``: e4m3 rows, 2x, activations quantised per token): the integer weight-streaming arms run on
+        warp-level MMA and grow linearly with the row count from 8 rows on, while the persistent tcgen05 GEMM streams the
+        dense matrix once for all rows."""
         from ..ops import gemm_tc, linear
 
         sp = self.spec
@@ -413,11 +415,18 @@ class HybridRunner:
             self._y16 = torch.empty(self.MAX_ROWS * nmax, dtype=torch.bfloat16, device=self.device)
         x = self._x16h[:m, :w.k]
         K.act_unpack(xp, xs, x, m, w.k, self.G)
-        dense = linear.w4_dense(w, torch.float16, self.device, resident=True)
         direct = epi == K.EPI_STORE
         ld = (ldo if ldo is not None else out.shape[-1]) if direct else w.n
         y = (out.view(-1)[:m * ld] if direct and out.is_contiguous() and (ldo is None or ldo == out.shape[-1]) else self._y16[:m * ld]).view(m, ld)
-        gemm_tc.f16_gemm(x, dense, y, force_small=True)
+        if self.prefill_gemm == "tc8r":
+            wq, sw = linear.w4_e4m3(w, self.device)
+            if self._xq8 is None:
+                self._xq8 = (torch.empty(self.MAX_ROWS * self._x16h.shape[1], dtype=torch.uint8, device=self.device),
+                             torch.empty(self.MAX_ROWS, dtype=torch.float32, device=self.device))
+            xq, sx = gemm_tc.quant_e4m3_rows(x, self._xq8[0][:m * w.k].view(m, w.k), self._xq8[1][:m])
+            gemm_tc.e4m3_gemm(xq, sx, wq, sw, y)
+        else:
+            gemm_tc.f16_gemm(x, linear.w4_dense(w, torch.float16, self.device, resident=True), y, force_persist=True)
         if epi == K.EPI_RESIDUAL:
             K.add_rows(residual, y, out, m, w.n)
         elif epi == K.EPI_SILU_MUL:

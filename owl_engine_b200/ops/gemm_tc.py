@@ -43,12 +43,12 @@ def w4a16_gemm(w, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def f16_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, force_small: bool = False) -> torch.Tensor:
+def f16_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, force_small: bool = False, force_persist: bool = False) -> torch.Tensor:
     """out[T, N] (bf16) = x[T, K] @ w[N, K]^T with fp16 or bf16 operands on the tcgen05 path."""
     assert x.dtype == w.dtype and x.dtype in (torch.float16, torch.bfloat16) and out.dtype == torch.bfloat16
     t, k = x.shape
     # long chunks x wide weights: the persistent 128 x 256 kernel; otherwise the 128 x 128 kernel (two CTAs per SM)
-    entry = "owl_f16_gemm_persist" if (t >= 256 and w.shape[0] >= 512 and not force_small) else "owl_f16_gemm_tc"
+    entry = "owl_f16_gemm_persist" if (force_persist or (t >= 256 and w.shape[0] >= 512 and not force_small)) else "owl_f16_gemm_tc"
     K.call(entry, K.ptr(x), x.stride(0), K.ptr(w), w.stride(0), K.ptr(out), t, w.shape[0], k, out.stride(0),
            1 if x.dtype == torch.bfloat16 else 0, K.stream())
     return out

@@ -109,6 +109,18 @@ def nvfp4_gemm(w, x: torch.Tensor, out: torch.Tensor, arm: str = "tc") -> torch.
     return gemm_tc.f16_gemm(x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16), dense, out)
 
 
+def w4_e4m3(w, device):
+    """Resident per-row e4m3 copy of a W4 weight: (bytes [N, K], fp32 row scales [N]), created on first use."""
+    from . import gemm_tc
+
+    cached = getattr(w, "_owl_e4m3", None)
+    if cached is None:
+        dense = K.w4_dequant(w, _dense_scratch(w.n, w.k, device, torch.float16))
+        cached = gemm_tc.quant_e4m3_rows(dense)
+        w._owl_e4m3 = cached
+    return cached
+
+
 def w4_dense(w, dtype, device, resident: bool = False) -> torch.Tensor:
     """The weight dequantised into the shared dense scratch matrix (valid until the next call on this stream), or, with
     ``resident``, into a matrix of its own that stays attached to the weight."""
