@@ -398,7 +398,7 @@ class HybridRunner:
                               residual=None if residual is None else residual[r0:], epi=epi,
                               ldo=ldo if ldo is not None else out.shape[-1], pdl=pdl)
 
-    BATCH_GEMM_FROM = 16   # rows from which a batched step multiplies the resident dense weight copy on the tcgen05 GEMM
+    BATCH_GEMM_FROM = 24   # rows from which a batched step multiplies the resident dense weight copy on the tcgen05 GEMM
 
     def _gemv_dense16(self, w, xp, xs, out, m: int, residual, epi: int, ldo) -> None:
         """Wide batched steps (16+ rows) with a resident dense copy of the weights (``prefill_gemm = "tcr"``: fp16, 4x the

@@ -45,7 +45,7 @@ def test_w4a16_gemm(group, shape):
     assert err < 4e-3, err
 
 
-@pytest.mark.parametrize("shape", [(300, 512, 1024), (128, 256, 128), (1024, 1000, 2176)])
+@pytest.mark.parametrize("shape", [(300, 512, 1024), (128, 256, 128), (1024, 1000, 2176), (16, 512, 1024), (32, 5120, 2176)])
 def test_e4m3_gemm_and_row_quantisation(shape):
     """kind::f8f6f4 product of row-quantised operands: exact against the dequantised operands, close to the 16-bit product."""
     t, n, k = shape
