@@ -65,6 +65,7 @@ class Sequence:
     meank: object = None           # KV selection: block means of de-rotated keys (last full-attention layer), float [blocks, hkv, hd]
     meank_n: int = 0               # blocks indexed so far
     view: list = None              # block indices of the current view (ascending, ends with the block being written)
+    gap_from: int = None           # first token index after which the KV is carried memory (leave-gap deletions); None = exact
     images: list = field(default_factory=list)    # [(first token index, merged embeddings [n, H], fingerprint)]
     pos3: object = None            # multimodal (t, h, w) position ids of the prompt, int32 [3, n_prompt] (None = text only)
     rope_delta: int = 0            # rope position of a decode token = its cache index + rope_delta
@@ -281,12 +282,67 @@ class Engine:
         references) and give pages, row and state row back."""
         seq = self.seqs.pop(sid)
         if publish and seq.n_cached >= PAGE:
-            nb = min(seq.n_cached // PAGE, len(seq.pages))
+            exact = seq.n_cached if seq.gap_from is None else min(seq.n_cached, seq.gap_from)
+            nb = min(exact // PAGE, len(seq.pages))
             chain = self.kv.chain(self._hash_tokens(seq.tokens, seq.images)[:nb * PAGE])
             self.kv.publish(chain, seq.pages[:nb])
         self.kv.unref(seq.pages)
         self.free_rows.append(seq.row)
         self.states.give_back(sid)
+
+    # -- live-sequence surgery (agent sessions) --------------------------------------------------
+    def drop_ranges(self, sid: int, ranges: list) -> int:
+        """Leave-gap deletion on a live sequence: unlink the pages of the page-aligned token ranges ``[lo, hi)`` (all inside
+        the cached part). Survivors keep their KV and their rotary positions; the position ledger keeps the hole
+        (``rope_delta`` grows by the removed length, so new tokens continue from the old maximum position + 1). Returns the
+        number of tokens removed. What precedes the first range stays content-addressable; what follows it is carried
+        memory and is no longer published to the prefix tree (``engine/img_evict.py`` has the host-side rules)."""
+        from .img_evict import page_map
+
+        seq = self.seqs[sid]
+        ranges = sorted(ranges)
+        assert all(lo % PAGE == 0 and hi % PAGE == 0 and 0 <= lo < hi <= seq.n_cached for lo, hi in ranges)
+        keep = page_map(len(seq.pages) * PAGE, ranges, PAGE)
+        gone = [p for i, p in enumerate(seq.pages) if i not in set(keep)]
+        seq.pages = [seq.pages[i] for i in keep]
+        self.kv.unref(gone)
+        row = torch.zeros(self.max_blocks, dtype=torch.int32)
+        row[:len(seq.pages)] = torch.tensor(seq.pages, dtype=torch.int32)
+        self.runner.block_table[seq.row].copy_(row.to(self.device))
+        removed = 0
+        for lo, hi in reversed(ranges):
+            del seq.tokens[lo:hi]
+            removed += hi - lo
+        if seq.pos3 is not None:
+            keep_tok = torch.ones(seq.pos3.shape[1], dtype=torch.bool)
+            for lo, hi in ranges:
+                keep_tok[lo:hi] = False
+            seq.pos3 = seq.pos3[:, keep_tok]
+        shifted = []
+        for first, emb, fp in seq.images:
+            if any(lo <= first < hi for lo, hi in ranges):
+                continue
+            shifted.append((first - sum(hi - lo for lo, hi in ranges if hi <= first), emb, fp))
+        seq.images = shifted
+        seq.n_cached -= removed
+        seq.n_prompt = max(0, seq.n_prompt - removed)
+        seq.rope_delta += removed
+        seq.gap_from = min(ranges[0][0], seq.gap_from if seq.gap_from is not None else ranges[0][0])
+        seq.chain = None
+        seq.meank_n, seq.view = min(seq.meank_n, ranges[0][0] // PAGE), None
+        return removed
+
+    def extend_sequence(self, sid: int, new_tokens: list) -> int:
+        """Continue a live sequence with more prompt tokens (the next turn of an agent session on its parked sequence): the
+        not-yet-cached tail (the last sampled token and ``new_tokens``) is prefilled from the sequence's current position;
+        returns the next token."""
+        seq = self.seqs[sid]
+        seq.tokens.extend(int(t) for t in new_tokens)
+        seq.n_prompt = len(seq.tokens)
+        if seq.gap_from is None:
+            usable = (seq.n_prompt - 1) // PAGE * PAGE        # the longer prompt has its own block identities
+            seq.chain = self.kv.chain(self._hash_tokens(seq.tokens, seq.images)[:usable]) if usable else None
+        return self.prefill(sid)
 
     # -- prefill ------------------------------------------------------------------------------
     def prefill_range(self, sid: int, start: int, end: int, want_token: bool):
@@ -306,6 +362,9 @@ class Engine:
                 if lo < hi:
                     embeds[lo - start:hi - start] = emb[lo - first:hi - first].to(self.device, torch.bfloat16)
             pos3 = seq.pos3[:, start:end].to(self.device)
+        elif seq.rope_delta:
+            # positions after a leave-gap deletion: cache index + the removed length
+            pos3 = torch.arange(start + seq.rope_delta, end + seq.rope_delta, dtype=torch.int32, device=self.device).repeat(3, 1)
         boundary = (seq.n_prompt - 1) // PAGE * PAGE
         can_snap = boundary > seq.reused and seq.chain is not None and len(seq.chain)
         snap = None

@@ -255,3 +255,53 @@ def test_snapshot_inside_a_chunk_equals_the_cut_chunk(uniform_tail):
     assert (snaps[0][0] - snaps[1][0]).norm() / snaps[0][0].norm() < 1e-3          # 144 rows vs 144 rows: same chunked scan
     assert (outs[0][0] - outs[1][0]).norm() / outs[0][0].norm() < 1e-2
     assert outs[0][2] >= 1 and outs[1][2] >= 1 and len(outs[0][1]) == len(outs[1][1]) == 6
+
+
+def test_leave_gap_deletion_and_extension_of_a_live_sequence():
+    """An agent session on a live sequence: a page-aligned segment in the middle of the history is unlinked (pages freed, block
+    table compacted, survivors keep KV and positions, the position ledger keeps the hole), decoding continues, and the next turn's
+    tokens are appended from the old maximum position + 1. Before the hole everything is exact: the same steps on a sequence
+    that never had the segment after it agree token for token up to the deletion point's first new token only in mechanics,
+    so the checks are the ledgers and that the carried context is the one attended to."""
+    from owl_engine_b200.engine import img_evict as E
+
+    eng = make_engine()
+    g = torch.Generator().manual_seed(9)
+    a = torch.randint(0, 500, (27,), generator=g).tolist()
+    img = torch.randint(0, 500, (40,), generator=g).tolist()
+    b = torch.randint(0, 500, (13,), generator=g).tolist()
+    seq0 = E.pad_rule(a + img + b, [(27, 67)], 16, 511)
+    sp = seq0.spans[0]
+    assert sp.start == 32 and sp.hi == 80
+    free0 = eng.kv.stats()["free_pages"]
+    sid = eng.add_sequence(seq0.ids)
+    eng.prefill(sid)
+    for _ in range(3):
+        eng.decode_step([sid])
+    seq = eng.seqs[sid]
+    n_before, pages_before = seq.n_cached, list(seq.pages)
+    ranges, suffix = E.detect_deletions(seq0, a + b + [5, 6, 7])
+    assert ranges == [(32, 80)] and suffix == [5, 6, 7]
+    removed = eng.drop_ranges(sid, ranges)
+    assert removed == 48 and seq.n_cached == n_before - 48 and seq.rope_delta == 48 and seq.gap_from == 32
+    assert seq.pages == pages_before[:2] + pages_before[5:]
+    assert eng.runner.block_table[seq.row, :len(seq.pages)].tolist() == seq.pages
+    assert eng.kv.stats()["free_pages"] == free0 - len(seq.pages)
+    assert seq.tokens[:32] == seq0.ids[:32] and seq.tokens[32:32 + len(seq0.ids) - 80] == seq0.ids[80:]
+    t1 = eng.decode_step([sid])[0]                                  # position = cache index + 48
+    assert int(eng.h_inp_np[H_pos_index(eng)]) == seq.n_cached - 1 + 48
+    nxt = eng.extend_sequence(sid, suffix)
+    assert 0 <= nxt < eng.spec.vocab and seq.n_cached == len(seq.tokens) - 1
+    out = [eng.decode_step([sid])[0] for _ in range(4)]
+    assert all(0 <= t < eng.spec.vocab for t in [t1] + out)
+    # only the exact part is published
+    eng.free_sequence(sid)
+    sid2 = eng.add_sequence(seq0.ids[:32] + [1, 2, 3])
+    assert eng.seqs[sid2].reused in (0, 16, 32)
+    eng.free_sequence(sid2, publish=False)
+
+
+def H_pos_index(eng):
+    from owl_engine_b200.models import hybrid as H
+
+    return H.StepLayout(1, 1).pos3
