@@ -38,6 +38,7 @@ class TurnOpts:
     session: str | None = None
     images: list = field(default_factory=list)      # [(merged embeddings, (t, gh, gw), fingerprint)] in prompt order
     image_pad_id: int | None = None
+    evict_spans: list = field(default_factory=list)  # [(start, end)] client-coordinate segments that may be dropped later
 
 
 @dataclass
@@ -56,8 +57,16 @@ class Turn:
 
 
 class RunningEngine:
-    def __init__(self, engine: Engine, max_batch: int = 8, on_full: str = "reject", spec_runner=None):
+    def __init__(self, engine: Engine, max_batch: int = 8, on_full: str = "reject", spec_runner=None,
+                 park_sessions: bool = False, max_parked: int = 2, evict_pad_id: int = 0):
+        """``park_sessions``: a finished turn of a named session keeps its sequence alive (pages + GDN row) so that the next
+        turn continues it: droppable segments the client removed are unlinked in place (leave-gap, ``engine/img_evict.py``) and
+        only the new tokens are prefilled. At most ``max_parked`` sequences wait; the oldest is released (and published) when
+        a row is needed."""
         self.e = engine
+        self.park_sessions, self.max_parked, self.evict_pad_id = park_sessions, max_parked, evict_pad_id
+        self.parked: dict = {}       # session -> (engine sequence id, PaddedSeq of everything in the sequence, tick)
+        self.resumed = self.gap_drops = 0
         self.sched = Scheduler(max_batch, engine.cfg.prefill_chunk, on_full)
         self.turns: dict[int, Turn] = {}
         self.reservations = B.Reservations()
@@ -137,9 +146,66 @@ class RunningEngine:
             n += 1
 
     # -- step executors -------------------------------------------------------------------------
+    def _release_parked(self, session: str, publish: bool = True) -> None:
+        sid, _, _ = self.parked.pop(session)
+        if sid in self.e.seqs:
+            self.e.free_sequence(sid, publish=publish)
+
+    def _try_resume(self, t: Turn) -> bool:
+        """Continue the session's parked sequence when the new prompt is its history with whole droppable segments removed
+        and text appended (no new images in the appended part)."""
+        from . import img_evict as E
+
+        ent = self.parked.get(t.opts.session)
+        if ent is None or t.opts.images:
+            return False
+        sid, hist, _ = ent
+        r = E.detect_deletions(hist, t.tokens) if sid in self.e.seqs else None
+        if r is None or not r[1]:
+            return False
+        ranges, suffix = r
+        seq = self.e.seqs[sid]
+        cached_client = len(E.unpad(hist))
+        if ranges:
+            if any(hi > seq.n_cached for _, hi in ranges):
+                return False
+            self.e.drop_ranges(sid, ranges)
+            hist = E.apply_deletions(hist, ranges)
+            self.gap_drops += len(ranges)
+        del self.parked[t.opts.session]
+        # the sequence's last sampled token is history too (already in seq.tokens, not yet cached)
+        seq.tokens.extend(int(x) for x in suffix)
+        seq.n_prompt = len(seq.tokens)
+        if seq.gap_from is None:
+            usable = (seq.n_prompt - 1) // PAGE * PAGE
+            seq.chain = self.e.kv.chain(self.e._hash_tokens(seq.tokens, seq.images)[:usable]) if usable else None
+        seq.reused = min(seq.n_cached, cached_client)
+        t.sid, t.padded = sid, E.PaddedSeq(hist.ids + list(suffix), hist.spans, hist.pads)
+        self.resumed += 1
+        return True
+
     def _do_begin(self, step) -> None:
         t = self.turns[step.turns[0]]
-        t.sid = self.e.add_sequence(t.tokens, images=t.opts.images or None, image_pad_id=t.opts.image_pad_id)
+        from . import img_evict as E
+
+        t.padded = None
+        if not (self.park_sessions and t.opts.session and self._try_resume(t)):
+            if t.opts.session in self.parked:
+                self._release_parked(t.opts.session)
+            prompt = t.tokens
+            if self.park_sessions and t.opts.evict_spans and not t.opts.images:
+                t.padded = E.pad_rule(t.tokens, sorted(t.opts.evict_spans), PAGE, self.evict_pad_id)
+                prompt = t.padded.ids
+            elif self.park_sessions and t.opts.session:
+                t.padded = E.PaddedSeq(list(t.tokens))
+            while True:
+                try:
+                    t.sid = self.e.add_sequence(prompt, images=t.opts.images or None, image_pad_id=t.opts.image_pad_id)
+                    break
+                except RuntimeError:
+                    if not self.parked:
+                        raise
+                    self._release_parked(min(self.parked, key=lambda k: self.parked[k][2]))
         seq = self.e.seqs[t.sid]
         t.plan = self.e.prefill_plan(t.sid)
         t.state = PREFILL
@@ -216,7 +282,19 @@ class RunningEngine:
         usage = {"prompt_tokens": len(t.tokens), "completion_tokens": t.n_out, "cached_tokens": 0}
         if t.sid is not None and t.sid in self.e.seqs:
             usage["cached_tokens"] = self.e.seqs[t.sid].reused
-            self.e.free_sequence(t.sid, publish=True)     # cancelled turns publish their written prefix too
+            padded = getattr(t, "padded", None)
+            if self.park_sessions and t.opts.session and padded is not None and reason in ("stop", "length", "eos") \
+                    and self.spec_runner is None:
+                # park: the sequence (pages, GDN row) waits for the session's next turn
+                from . import img_evict as E
+
+                seq = self.e.seqs[t.sid]
+                gen = seq.tokens[len(padded.ids):]
+                self.parked[t.opts.session] = (t.sid, E.PaddedSeq(padded.ids + gen, padded.spans, padded.pads), self._tick)
+                while len(self.parked) > self.max_parked:
+                    self._release_parked(min(self.parked, key=lambda k: self.parked[k][2]))
+            else:
+                self.e.free_sequence(t.sid, publish=True)     # cancelled turns publish their written prefix too
         self.reservations.release(t.turn)
         t.state = DONE
         self.completed += 1

@@ -305,3 +305,31 @@ def H_pos_index(eng):
     from owl_engine_b200.models import hybrid as H
 
     return H.StepLayout(1, 1).pos3
+
+
+def test_parked_session_resumes_with_a_dropped_screenshot():
+    """Agent session over the running engine: turn 1 has a droppable segment, turn 2 arrives without it and with new text:
+    the parked sequence is continued (segment unlinked in place, only the new tokens prefilled); turn 3 appends again."""
+    eng = make_engine()
+    re_ = RunningEngine(eng, max_batch=2, park_sessions=True, max_parked=1, evict_pad_id=511)
+    g = torch.Generator().manual_seed(13)
+    a = torch.randint(0, 500, (27,), generator=g).tolist()
+    img = torch.randint(0, 500, (40,), generator=g).tolist()
+    b = torch.randint(0, 500, (13,), generator=g).tolist()
+    o1 = re_.generate(a + img + b, TurnOpts(max_new=4, ignore_eos=True, session="s", evict_spans=[(27, 67)]))
+    assert len(o1) == 4 and "s" in re_.parked and len(eng.seqs) == 1
+    pages1 = len(next(iter(eng.seqs.values())).pages)
+    t2 = a + b + o1 + [3, 4, 5]
+    o2 = re_.generate(t2, TurnOpts(max_new=4, ignore_eos=True, session="s"))
+    assert re_.resumed == 1 and re_.gap_drops == 1 and len(o2) == 4
+    seq = next(iter(eng.seqs.values()))
+    assert seq.rope_delta == 48 and len(seq.pages) <= pages1 - 2
+    assert re_.trace[-1]["cached_tokens"] > 0
+    o3 = re_.generate(t2 + o2 + [9, 9], TurnOpts(max_new=3, ignore_eos=True, session="s"))
+    assert re_.resumed == 2 and len(o3) == 3
+    # another session parks too: the older parked sequence is released
+    re_.generate(a, TurnOpts(max_new=2, ignore_eos=True, session="other"))
+    assert list(re_.parked) == ["other"] and len(eng.seqs) == 1
+    # a prompt that is not a continuation starts over
+    re_.generate(b + a, TurnOpts(max_new=2, ignore_eos=True, session="other"))
+    assert re_.resumed == 2
