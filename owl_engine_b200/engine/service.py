@@ -28,8 +28,10 @@ class ServiceExit:
 
 
 class EngineService:
-    def __init__(self, build_engine, max_batch: int = 8, on_full: str = "reject", spec_runner=None):
-        """``build_engine()`` is called on the engine thread and returns an ``Engine``."""
+    def __init__(self, build_engine, max_batch: int = 8, on_full: str = "reject", spec_runner=None, running_kw: dict | None = None):
+        """``build_engine()`` is called on the engine thread and returns an ``Engine``; ``running_kw`` goes to
+        ``RunningEngine`` (session parking for droppable image segments)."""
+        self._running_kw = running_kw or {}
         self.inbox: queue.Queue = queue.Queue(maxsize=64)
         self.ready = threading.Event()
         self.exit: ServiceExit | None = None
@@ -53,7 +55,7 @@ class EngineService:
             # a callable spec_runner is a factory: draft heads need the engine (its runner, weights, pools)
             if callable(spec_runner) and not hasattr(spec_runner, "round"):
                 spec_runner = spec_runner(engine)
-            self.re = RunningEngine(engine, max_batch, on_full, spec_runner)
+            self.re = RunningEngine(engine, max_batch, on_full, spec_runner, **self._running_kw)
         except Exception as ex:
             self.boot_error = f"boot failed: {ex!r}\n{traceback.format_exc()}"
             self.exit = ServiceExit("fatal", 1, self.boot_error)

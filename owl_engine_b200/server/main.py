@@ -137,7 +137,8 @@ def main(argv=None) -> int:
     METRICS.set_level(cfg.values["probes"]["perf_level"])
     v = cfg.values
     svc = EngineService(build_engine_factory(cfg), max_batch=v["runtime"]["max_batch"], on_full=v["runtime"]["admission_on_full"],
-                        spec_runner=build_spec_factory(cfg))
+                        spec_runner=build_spec_factory(cfg),
+                        running_kw={"park_sessions": bool(v["vision"]["image_evict"]), "max_parked": max(1, v["store.gdn"]["gdn_slots"] // 2)})
     client = svc.boot()
     path = v["model"]["path"]
     try:
