@@ -95,7 +95,7 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint3
                ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 
-enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SILU_MUL = 2, EPI_F32 = 3, EPI_SILU_PACK = 4, EPI_PUSH = 5 };
+enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SILU_MUL = 2, EPI_F32 = 3, EPI_SILU_PACK = 4, EPI_PUSH = 5, EPI_RESIDUAL_NORM = 6 };
 constexpr int SK_MAX_RANKS = 8;
 enum { KIND_W4_G128 = 0, KIND_W4_G32 = 1, KIND_BF16 = 2, KIND_W8 = 3 };
 
@@ -123,6 +123,13 @@ struct SkinnyParams {
   int* push_count;                         // local: CTAs of this launch that are done (returns to zero)
   uint32_t* push_seq;                      // local: sequence number of this call site
   int push_rank, push_world, push_rows;
+  // EPI_RESIDUAL_NORM: out = residual + y, and the CTA that finishes last (push_count) RMS-normalises the M finished rows
+  // and packs them for the next projection: the separate norm launch of the step disappears
+  const __nv_bfloat16* norm_w;             // [N]
+  __nv_bfloat16* normed;                   // optional bf16 [M][N]
+  uint4* norm_pack; float2* norm_xs;       // optional ActPack of the normalised rows (row layout or tiles, by norm_g)
+  int norm_g, norm_one_plus;
+  float norm_eps;
 };
 
 constexpr int SK_WARPS = 8;    // warps per CTA = K slices of the record layout
@@ -472,7 +479,7 @@ __global__ void __launch_bounds__(SK_WARPS * 32, MT == 1 ? 4 : 2) skinny_stream_
             } else {
               __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)tok * p.ldo + nt * 16 + g;
               float a = v_lo, b = v_hi;
-              if (epi == EPI_RESIDUAL) {
+              if (epi == EPI_RESIDUAL || epi == EPI_RESIDUAL_NORM) {
                 const __nv_bfloat16* rr = p.residual + (size_t)tok * p.ldo + nt * 16 + g;
                 a += __bfloat162float(rr[0]); b += __bfloat162float(rr[8]);
               }
@@ -517,6 +524,58 @@ __global__ void __launch_bounds__(SK_WARPS * 32, MT == 1 ? 4 : 2) skinny_stream_
         __threadfence_system();
         for (int r = 0; r < p.push_world; ++r)
           asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.push_flag[r] + p.push_rank), "r"(seq) : "memory");
+      }
+    }
+  }
+  if (epi == EPI_RESIDUAL_NORM) {
+    __shared__ int s_last;
+    __shared__ float s_red[32];
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const int last = atomicAdd(p.push_count, 1) == (int)gridDim.x - 1;
+      if (last) *p.push_count = 0;
+      s_last = last;
+      __threadfence();
+    }
+    __syncthreads();
+    if (s_last) {
+      // every CTA's rows are in global memory (fence + count): read them past L1
+      const int nchunks = p.N >> 3, tiles = p.norm_g & ACT_TILES, gq = p.norm_g & ~ACT_TILES, cpg = gq >> 3;
+      const int nround = (nchunks + 31) & ~31;
+      const __nv_bfloat16* hb = reinterpret_cast<const __nv_bfloat16*>(p.out);
+      for (int row = 0; row < p.M; ++row) {
+        const uint4* hp = reinterpret_cast<const uint4*>(hb + (size_t)row * p.ldo);
+        float ss = 0.f;
+        for (int c = threadIdx.x; c < nchunks; c += blockDim.x) {
+          float v[8];
+          unpack_bf16x8(__ldcg(hp + c), v);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
+        }
+        ss = block_sum(ss, s_red);
+        const float rinv = rsqrtf(ss / (float)p.N + p.norm_eps);
+        for (int c = threadIdx.x; c < nround; c += blockDim.x) {
+          float v[8];
+          const bool live = c < nchunks;
+          if (live) {
+            float wf[8];
+            unpack_bf16x8(__ldcg(hp + c), v);
+            unpack_bf16x8(reinterpret_cast<const uint4*>(p.norm_w)[c], wf);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              v[i] = __bfloat162float(__float2bfloat16(v[i] * rinv * (p.norm_one_plus ? 1.f + wf[i] : wf[i])));
+            if (p.normed) reinterpret_cast<uint4*>(p.normed + (size_t)row * p.N)[c] = pack_bf16x8(v);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = 0.f;
+          }
+          if (p.norm_pack) {
+            float sx, xsum;
+            const uint4 pk = actpack_emit(v, cpg, sx, xsum);
+            if (live) actpack_store(p.norm_pack, p.norm_xs, tiles, gq, row, c, nchunks, pk, sx, xsum);
+          }
+        }
       }
     }
   }
@@ -591,6 +650,27 @@ OWL_API int owl_w4a16_skinny(const void* records, const void* xpack, const void*
   p.force_mma = (tiles_per_cta < 0);
   p.tiles_per_cta = pick_tiles_per_cta(p.n_tiles, epi, tiles_per_cta < 0 ? -tiles_per_cta - 1 : tiles_per_cta);
   return group == 128 ? dispatch_mt<KIND_W4_G128>(p, epi, pdl, st) : dispatch_mt<KIND_W4_G32>(p, epi, pdl, st);
+}
+
+// Row projection with the residual add AND the following RMSNorm + activation packing in one launch (EPI_RESIDUAL_NORM):
+// out = residual + W x; the last CTA to finish normalises the M rows of `out` with norm_w and writes `normed` (bf16, optional)
+// and / or the ActPack (norm_pack / norm_xs, group norm_g, optionally | ACT_TILES). count: local int, zero before the first call.
+OWL_API int owl_w4a16_skinny_norm(const void* records, const void* xpack, const void* xsums, void* out, const void* residual,
+                                  const void* norm_w, void* normed, void* norm_pack, void* norm_xs, void* count, int M, int N,
+                                  int K, int ldo, int group, int norm_g, float eps, int one_plus_w, int force_mma, int pdl,
+                                  cudaStream_t st) {
+  if (M < 1 || M > 32 || (N & 127) || (K & 127) || (group != 32 && group != 128) || !out || !residual || !norm_w || !count ||
+      ldo != N || !actpack_group_ok(norm_g, M) || (!normed && !norm_pack) || (norm_pack && !norm_xs && !(norm_g & ACT_TILES)))
+    return OWL_ERR_BAD_ARG;
+  SkinnyParams p = {};
+  p.w = (const uint8_t*)records; p.x = (const uint4*)xpack; p.xs = (const float2*)xsums;
+  p.out = out; p.residual = (const __nv_bfloat16*)residual;
+  p.M = M; p.N = N; p.K = K; p.ldo = ldo; p.n_tiles = N / 16; p.force_mma = force_mma;
+  p.tiles_per_cta = pick_tiles_per_cta(p.n_tiles, EPI_RESIDUAL, 0);
+  p.push_count = (int*)count;
+  p.norm_w = (const __nv_bfloat16*)norm_w; p.normed = (__nv_bfloat16*)normed; p.norm_pack = (uint4*)norm_pack;
+  p.norm_xs = (float2*)norm_xs; p.norm_g = norm_g; p.norm_one_plus = one_plus_w; p.norm_eps = eps;
+  return group == 128 ? dispatch_mt<KIND_W4_G128>(p, EPI_RESIDUAL_NORM, pdl, st) : dispatch_mt<KIND_W4_G32>(p, EPI_RESIDUAL_NORM, pdl, st);
 }
 
 // Tensor-parallel variant for row-parallel projections: the partial sums are written into every rank's

@@ -19,6 +19,7 @@ _F = c_float
 
 _SIGS = {
     "owl_w4a16_skinny": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "owl_w4a16_skinny_norm": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
     "owl_w4a16_stream_tc": [_P, _P, _P, _P, _P, c_longlong, _P, c_longlong, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "owl_bf16_skinny": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "owl_w8a16_skinny": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
@@ -90,6 +91,18 @@ def w4a16_skinny(w, xpack, xs, out, m: int, *, residual=None, epi: int = EPI_STO
         tiles_per_cta = -tiles_per_cta - 1
     call("owl_w4a16_skinny", ptr(w.records), ptr(xpack), ptr(xs), ptr(out), ptr(residual), ptr(out_pack), ptr(out_xs),
          m, w.n, w.k, ldo, w.group, epi, gout, tiles_per_cta, int(pdl), stream())
+
+
+def w4a16_skinny_norm(w, xpack, xs, h, norm_w, count, m: int, *, normed=None, norm_pack=None, norm_xs=None,
+                      group: int = 128, eps: float = 1e-6, one_plus_w: bool = True, pdl: bool = False,
+                      force_mma: bool = False) -> None:
+    """h[m, :] += dequant(w) @ x, and the CTA that finishes last writes rmsnorm(h) * (norm_w or 1 + norm_w) as bf16
+    (``normed``) and / or ActPack (``norm_pack`` / ``norm_xs``): the row projection, the residual add and the next
+    block's norm in one launch. ``count``: one int32 on the device, zero before the first call (the kernel zeroes it)."""
+    assert w.layout == "slice" and h.shape[-1] == w.n and h.is_contiguous()
+    call("owl_w4a16_skinny_norm", ptr(w.records), ptr(xpack), ptr(xs), ptr(h), ptr(h), ptr(norm_w), ptr(normed),
+         ptr(norm_pack), ptr(norm_xs), ptr(count), m, w.n, w.k, w.n, w.group, group, eps, int(one_plus_w), int(force_mma),
+         int(pdl), stream())
 
 
 class StreamTcWorkspace:

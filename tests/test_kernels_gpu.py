@@ -110,6 +110,40 @@ def test_w4a16_skinny_fused_silu_pack(m, gout):
     torch.testing.assert_close(oxs.cpu(), ws, rtol=1e-5, atol=1e-3)
 
 
+@pytest.mark.parametrize("m,group", [(1, 128), (3, 32), (8, 128), (20, 128)])
+def test_w4a16_skinny_fused_residual_norm(m, group):
+    """Projection + residual + RMSNorm + ActPack in one launch against the two-launch path (same rows, same packing)."""
+    n, k = 5120, 1024
+    c = Q.quantize_w4(torch.randn(n, k, generator=gen(60)) * 0.05, group)
+    s = Q.pack_skinny(c).to(DEV)
+    x = bf(torch.randn(m, k, generator=gen(61)))
+    xp = torch.empty(m, 2 * k, dtype=torch.uint8, device=DEV)
+    xs = torch.empty(m, k // group, 2, dtype=torch.float32, device=DEV)
+    K.act_pack(x.to(DEV), xp, xs, m, k, group)
+    res = bf(torch.randn(m, n, generator=gen(62))).to(DEV)
+    nw = bf(torch.randn(n, generator=gen(63)) * 0.1).to(DEV)
+    count = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for it in range(2):          # the second call checks that the counter went back to zero
+        h2 = res.clone()
+        K.w4a16_skinny(s, xp, xs, h2, m, residual=h2, epi=K.EPI_RESIDUAL)
+        xn2 = torch.zeros(m, n, dtype=torch.bfloat16, device=DEV)
+        p2 = torch.zeros(m, 2 * n, dtype=torch.uint8, device=DEV)
+        s2 = torch.zeros(m, n // 128, 2, dtype=torch.float32, device=DEV)
+        K.rmsnorm_pack(h2, nw, normed=xn2, xpack=p2, xs=s2, m=m, k=n, group=128)
+        h1 = res.clone()
+        xn1, p1, s1 = torch.zeros_like(xn2), torch.zeros_like(p2), torch.zeros_like(s2)
+        K.w4a16_skinny_norm(s, xp, xs, h1, nw, count, m, normed=xn1, norm_pack=p1, norm_xs=s1, group=128)
+        torch.cuda.synchronize()
+        assert torch.equal(h1, h2)
+        assert int(count.item()) == 0
+        torch.testing.assert_close(xn1.float(), xn2.float(), rtol=1e-2, atol=1e-2)
+        want = R.rmsnorm(h2.float().cpu(), nw.float().cpu(), 1e-6)
+        torch.testing.assert_close(xn1.float().cpu(), want, rtol=2e-2, atol=2e-2)
+        wp, ws = Q.act_pack_ref(xn1.float().cpu(), 128)
+        assert torch.equal(p1.cpu(), wp)
+        torch.testing.assert_close(s1.cpu(), ws, rtol=1e-5, atol=1e-3)
+
+
 @pytest.mark.parametrize("m", [1, 5, 16])
 def test_bf16_and_w8_skinny(m):
     n, k = 272, 1024
