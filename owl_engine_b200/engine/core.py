@@ -332,17 +332,48 @@ class Engine:
         seq.meank_n, seq.view = min(seq.meank_n, ranges[0][0] // PAGE), None
         return removed
 
-    def extend_sequence(self, sid: int, new_tokens: list) -> int:
+    def extend_sequence(self, sid: int, new_tokens: list, images: list | None = None, image_pad_id: int | None = None) -> int:
         """Continue a live sequence with more prompt tokens (the next turn of an agent session on its parked sequence): the
-        not-yet-cached tail (the last sampled token and ``new_tokens``) is prefilled from the sequence's current position;
-        returns the next token."""
+        not-yet-cached tail (the last sampled token and ``new_tokens``, new images included) is prefilled from the sequence's
+        current position; returns the next token."""
+        self.append_tokens(sid, new_tokens, images, image_pad_id)
+        return self.prefill(sid)
+
+    def _pos3_cover(self, seq, upto: int) -> None:
+        """The (t, h, w) position ledger covers the prompt it was built for; tokens after it (sampled ones, appended text)
+        sit at cache index + ``rope_delta`` in all three components."""
+        n = seq.pos3.shape[1]
+        if n < upto:
+            ext = torch.arange(n + seq.rope_delta, upto + seq.rope_delta, dtype=torch.int32).repeat(3, 1)
+            seq.pos3 = torch.cat([seq.pos3, ext], 1)
+
+    def append_tokens(self, sid: int, new_tokens: list, images: list | None = None, image_pad_id: int | None = None) -> None:
+        """More prompt for a live sequence, without running it. ``images`` (same triples as ``add_sequence``) belong to the
+        image-pad runs inside ``new_tokens``: their (t, h, w) blocks start at the sequence's next position."""
         seq = self.seqs[sid]
-        seq.tokens.extend(int(t) for t in new_tokens)
+        new_tokens = [int(t) for t in new_tokens]
+        base = len(seq.tokens)
+        if images:
+            from ..models.vision import mrope_positions
+
+            if seq.pos3 is None:
+                seq.pos3 = torch.zeros(3, 0, dtype=torch.int32)
+            self._pos3_cover(seq, base)
+            p0 = base + seq.rope_delta
+            pos, nxt = mrope_positions(new_tokens, image_pad_id, [g for _, g, _ in images], 2)
+            seq.pos3 = torch.cat([seq.pos3, pos + p0], 1)
+            i = 0
+            for emb, grid, fp in images:
+                while new_tokens[i] != image_pad_id:
+                    i += 1
+                seq.images.append((base + i, emb, fp))
+                i += emb.shape[0]
+            seq.rope_delta = p0 + nxt - (base + len(new_tokens))
+        seq.tokens.extend(new_tokens)
         seq.n_prompt = len(seq.tokens)
         if seq.gap_from is None:
             usable = (seq.n_prompt - 1) // PAGE * PAGE        # the longer prompt has its own block identities
             seq.chain = self.kv.chain(self._hash_tokens(seq.tokens, seq.images)[:usable]) if usable else None
-        return self.prefill(sid)
 
     # -- prefill ------------------------------------------------------------------------------
     def prefill_range(self, sid: int, start: int, end: int, want_token: bool):
@@ -361,6 +392,7 @@ class Engine:
                 lo, hi = max(first, start), min(first + emb.shape[0], end)
                 if lo < hi:
                     embeds[lo - start:hi - start] = emb[lo - first:hi - first].to(self.device, torch.bfloat16)
+            self._pos3_cover(seq, end)
             pos3 = seq.pos3[:, start:end].to(self.device)
         elif seq.rope_delta:
             # positions after a leave-gap deletion: cache index + the removed length

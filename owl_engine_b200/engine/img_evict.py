@@ -42,25 +42,44 @@ class PaddedSeq:
     pads: list = field(default_factory=list)           # (lo, hi) of pad runs left behind by deleted segments (their front pads)
 
 
-def pad_rule(ids: list, spans: list, page: int, pad_id: int) -> PaddedSeq:
+def pad_rule(ids: list, spans: list, page: int, pad_id: int, base: int = 0) -> PaddedSeq:
     """``spans``: ``(start, end)`` of the removable segments in CLIENT coordinates, ascending and disjoint. Pads go in front
     of a segment so that it starts on a page boundary and behind it so that it ends on one; applying the rule to an
-    already padded prefix changes nothing (position differences are whole pages)."""
+    already padded prefix changes nothing (position differences are whole pages). ``base``: cache index of ``ids[0]`` when
+    the tokens continue a live sequence; the returned spans are then in the sequence's coordinates (``ids`` stay relative)."""
     out, res, cur = [], [], 0
     for s, e in spans:
         assert cur <= s < e <= len(ids)
         out.extend(ids[cur:s])
-        before = (-len(out)) % page
+        before = (-(base + len(out))) % page
         out.extend([pad_id] * before)
-        start = len(out)
+        start = base + len(out)
         out.extend(ids[s:e])
-        end = len(out)
+        end = base + len(out)
         after = (-end) % page
         out.extend([pad_id] * after)
         res.append(ImgSpan(start, end, before, after))
         cur = e
     out.extend(ids[cur:])
     return PaddedSeq(out, res)
+
+
+def identity_ids(ids: list, image_pad_id, fingerprints: list) -> list:
+    """Token list in which the k-th run of image-pad tokens is replaced by a marker of that image's content fingerprint
+    (a negative number: no vocabulary id), so that two screenshots of the same size are different segments when two client
+    histories are compared."""
+    if image_pad_id is None or not fingerprints:
+        return list(ids)
+    out, k, prev = [], -1, None
+    for t in ids:
+        if t == image_pad_id:
+            if prev != image_pad_id:
+                k += 1
+            out.append(-1 - (int(fingerprints[min(k, len(fingerprints) - 1)]) & 0x7FFFFFFF))
+        else:
+            out.append(t)
+        prev = t
+    return out
 
 
 def _pad_runs(seq: PaddedSeq) -> list:

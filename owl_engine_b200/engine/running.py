@@ -78,6 +78,11 @@ class RunningEngine:
 
     # -- API ------------------------------------------------------------------------------------
     def submit(self, tokens: list[int], opts: TurnOpts | None = None, sink=None) -> int:
+        if opts is not None and opts.evict_spans and not self.park_sessions:
+            # a droppable mark nobody honours would silently re-prefill the whole history every turn: refuse loudly
+            # (reference: crates/engine/src/running.rs:1400-1409)
+            raise ValueError("rejected: segments are marked droppable (owl_evict) but image_evict is off in this profile; "
+                             "enable [vision] image_evict or remove the marks")
         t = Turn(self._next, list(tokens), opts or TurnOpts(), sink or queue.Queue(), arrival=self._tick)
         self._next += 1
         self.turns[t.turn] = t
@@ -151,20 +156,29 @@ class RunningEngine:
         if sid in self.e.seqs:
             self.e.free_sequence(sid, publish=publish)
 
+    def _ident(self, t: Turn) -> list:
+        """The turn's client tokens with every image-pad run marked by its image's fingerprint (what histories are compared by)."""
+        from . import img_evict as E
+
+        return E.identity_ids(t.tokens, t.opts.image_pad_id, [fp for _, _, fp in t.opts.images])
+
     def _try_resume(self, t: Turn) -> bool:
         """Continue the session's parked sequence when the new prompt is its history with whole droppable segments removed
-        and text appended (no new images in the appended part)."""
+        and anything appended (text, and new images with their own droppable marks)."""
         from . import img_evict as E
 
         ent = self.parked.get(t.opts.session)
-        if ent is None or t.opts.images:
+        if ent is None:
             return False
         sid, hist, _ = ent
-        r = E.detect_deletions(hist, t.tokens) if sid in self.e.seqs else None
+        ident = self._ident(t)
+        r = E.detect_deletions(hist, ident) if sid in self.e.seqs else None
         if r is None or not r[1]:
             return False
         ranges, suffix = r
         seq = self.e.seqs[sid]
+        if len(hist.ids) != len(seq.tokens):
+            return False
         cached_client = len(E.unpad(hist))
         if ranges:
             if any(hi > seq.n_cached for _, hi in ranges):
@@ -173,14 +187,18 @@ class RunningEngine:
             hist = E.apply_deletions(hist, ranges)
             self.gap_drops += len(ranges)
         del self.parked[t.opts.session]
-        # the sequence's last sampled token is history too (already in seq.tokens, not yet cached)
-        seq.tokens.extend(int(x) for x in suffix)
-        seq.n_prompt = len(seq.tokens)
-        if seq.gap_from is None:
-            usable = (seq.n_prompt - 1) // PAGE * PAGE
-            seq.chain = self.e.kv.chain(self.e._hash_tokens(seq.tokens, seq.images)[:usable]) if usable else None
+        # the appended part: its real tokens, the images whose pad runs lie in it, and its droppable segments padded from
+        # the sequence's current length (the sequence's last sampled token is history too: in seq.tokens, not yet cached)
+        cut = len(t.tokens) - len(suffix)
+        real = list(t.tokens[cut:])
+        new_imgs = t.opts.images[len(seq.images):] if t.opts.images else []
+        spans = sorted((s - cut, e - cut) for s, e in t.opts.evict_spans if s >= cut)
+        base = len(seq.tokens)
+        ps_real = E.pad_rule(real, spans, PAGE, self.evict_pad_id, base)
+        ps_id = E.pad_rule(list(suffix), spans, PAGE, self.evict_pad_id, base)
+        self.e.append_tokens(sid, ps_real.ids, new_imgs or None, t.opts.image_pad_id)
         seq.reused = min(seq.n_cached, cached_client)
-        t.sid, t.padded = sid, E.PaddedSeq(hist.ids + list(suffix), hist.spans, hist.pads)
+        t.sid, t.padded = sid, E.PaddedSeq(hist.ids + ps_id.ids, hist.spans + ps_id.spans, hist.pads)
         self.resumed += 1
         return True
 
@@ -193,11 +211,12 @@ class RunningEngine:
             if t.opts.session in self.parked:
                 self._release_parked(t.opts.session)
             prompt = t.tokens
-            if self.park_sessions and t.opts.evict_spans and not t.opts.images:
-                t.padded = E.pad_rule(t.tokens, sorted(t.opts.evict_spans), PAGE, self.evict_pad_id)
-                prompt = t.padded.ids
+            if self.park_sessions and t.opts.evict_spans:
+                spans = sorted(t.opts.evict_spans)
+                prompt = E.pad_rule(t.tokens, spans, PAGE, self.evict_pad_id).ids
+                t.padded = E.pad_rule(self._ident(t), spans, PAGE, self.evict_pad_id)     # what later histories are compared with
             elif self.park_sessions and t.opts.session:
-                t.padded = E.PaddedSeq(list(t.tokens))
+                t.padded = E.PaddedSeq(self._ident(t))
             while True:
                 try:
                     t.sid = self.e.add_sequence(prompt, images=t.opts.images or None, image_pad_id=t.opts.image_pad_id)

@@ -87,7 +87,10 @@ class EngineService:
                 return True
             if kind == "submit":
                 _, tokens, opts, sink, reply = msg
-                reply.put(self.re.submit(tokens, opts, sink))
+                try:
+                    reply.put(self.re.submit(tokens, opts, sink))
+                except ValueError as ex:          # refused at the submit boundary: the caller gets the reason
+                    reply.put(ex)
             elif kind == "cancel":
                 self.re.cancel_turn(msg[1])
             elif kind == "query":
@@ -112,7 +115,10 @@ class EngineClient:
         sink: queue.Queue = queue.Queue(maxsize=4096)
         reply: queue.Queue = queue.Queue()
         self.svc.inbox.put(("submit", tokens, opts, sink, reply))
-        return reply.get(timeout=60), sink
+        turn = reply.get(timeout=60)
+        if isinstance(turn, Exception):
+            raise turn
+        return turn, sink
 
     def cancel(self, turn: int) -> None:
         self.svc.inbox.put(("cancel", turn))

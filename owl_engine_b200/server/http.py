@@ -161,6 +161,17 @@ class App:
             return await self._send(w, 200, {"loaded": self.model})
         await self._send(w, 404, {"error": "unknown debug endpoint"})
 
+    def vision_wrap(self) -> tuple:
+        """Token ids of the markers the chat template writes around an image placeholder (None when the tokenizer has
+        no single token for them)."""
+        if getattr(self, "_vwrap", None) is None:
+            ids = []
+            for text in ("<|vision_start|>", "<|vision_end|>"):
+                e = self.tok.encode(text)
+                ids.append(e[0] if len(e) == 1 else None)
+            self._vwrap = tuple(ids) if None not in ids else (None, None)
+        return self._vwrap
+
     async def chat(self, body, reader, w) -> None:
         req = ChatRequest.parse(body)
         kwargs = dict(req.chat_template_kwargs)
@@ -168,16 +179,18 @@ class App:
             kwargs.setdefault("enable_thinking", False)
         prompt = self.tpl.render(req.messages, tools=req.tools, **kwargs)
         ids = self.tok.encode(prompt)
-        images = []
+        images, evict_spans = [], []
         if req.images:
             if self.vision is None:
                 raise BadRequest("this server was started without a vision tower; image parts are not accepted")
             loop0 = asyncio.get_running_loop()
-            ids, images = await loop0.run_in_executor(None, self.vision.expand, ids, [im["data"] for im in req.images])
+            ids, images, evict_spans = await loop0.run_in_executor(
+                None, self.vision.expand, ids, [im["data"] for im in req.images], [im["evict"] for im in req.images],
+                self.vision_wrap())
         max_new = min(req.max_tokens or self.default_max_new, self.max_new_cap)
         opts = TurnOpts(max_new=max_new, ignore_eos=req.ignore_eos, sampling=req.sampling(self.default_sampling),
                         eos_ids=tuple(self.tok.eos_ids), session=req.session, images=images,
-                        image_pad_id=self.vision.pad_id if self.vision else None)
+                        image_pad_id=self.vision.pad_id if self.vision else None, evict_spans=evict_spans)
         lock = self.session_locks.setdefault(req.session, asyncio.Lock()) if req.session else None
         try:
             await asyncio.wait_for(self.permits.acquire(), self.queue_timeout)
@@ -188,7 +201,10 @@ class App:
         turn = None
         try:
             loop = asyncio.get_running_loop()
-            turn, sink = await loop.run_in_executor(None, self.client.chat, ids, opts)
+            try:
+                turn, sink = await loop.run_in_executor(None, self.client.chat, ids, opts)
+            except ValueError as e:              # refused at the submit boundary (e.g. droppable marks with image_evict off)
+                raise BadRequest(str(e)) from None
             streamer = Streamer(self.model, StreamDecoder(self.tok), req.stop,
                                 start_in_think=prompt.rstrip().endswith("<think>"))
             if req.stream:
@@ -257,19 +273,28 @@ class Vision:
 
         self.tower, self.pad_id, self.cache, self.decode = tower, pad_id, ImageCache(cache_cap), png.decode_png
 
-    def expand(self, ids: list[int], blobs: list[bytes]):
-        images, out, k = [], [], 0
-        for t in ids:
+    def expand(self, ids: list[int], blobs: list[bytes], evict: list | None = None, wrap: tuple = (None, None)):
+        """Returns the expanded ids, the image triples and, for the images whose ``evict`` entry is true, the token spans a
+        client may later drop: the pad run together with the vision-start / vision-end tokens (``wrap``) around it when
+        they are there, i.e. exactly what disappears from the rendered prompt when the image part is removed."""
+        images, out, spans, k = [], [], [], 0
+        for j, t in enumerate(ids):
             if t == self.pad_id and k < len(blobs):
                 emb, grid, fp = self.cache.get(self.tower, blobs[k], self.decode)
                 images.append((emb, grid, fp))
+                lo = len(out)
                 out.extend([self.pad_id] * emb.shape[0])
+                if evict and evict[k]:
+                    hi = len(out)
+                    if wrap[0] is not None and j > 0 and ids[j - 1] == wrap[0] and j + 1 < len(ids) and ids[j + 1] == wrap[1]:
+                        lo, hi = lo - 1, hi + 1
+                    spans.append((lo, hi))
                 k += 1
             else:
                 out.append(t)
         if k != len(blobs):
             raise BadRequest(f"{len(blobs)} images but {k} image placeholders in the rendered prompt")
-        return out, images
+        return out, images, spans
 
 
 def _vram(re) -> dict:

@@ -333,3 +333,59 @@ def test_parked_session_resumes_with_a_dropped_screenshot():
     # a prompt that is not a continuation starts over
     re_.generate(b + a, TurnOpts(max_new=2, ignore_eos=True, session="other"))
     assert re_.resumed == 2
+
+
+def test_parked_session_with_screenshots_drops_one_and_takes_a_new_one():
+    """The screenshot loop of a GUI agent: turn 1 carries two same-sized droppable images; turn 2 arrives without the FIRST one and
+    with a new image behind the history; turn 3 drops the second. Each turn continues the parked sequence: the dropped image's pages
+    are unlinked, the kept image stays (identified by content, not by size), the new image's (t, h, w) block starts at the
+    sequence's next position and is droppable itself."""
+    from owl_engine_b200.cli import png
+    from owl_engine_b200.models import vision as V
+
+    eng = make_engine()
+    tower, cache = V.VisionTower(V.tiny_vision(out_hidden=eng.spec.hidden)), V.ImageCache()
+    pad = 500
+    re_ = RunningEngine(eng, max_batch=2, park_sessions=True, max_parked=1, evict_pad_id=511)
+
+    def img(rgb):
+        emb, grid, fp = cache.get(tower, png.encode_png(96, 64, rgb), png.decode_png)
+        return (emb * 20, grid, fp)
+
+    red, blue, green = img(png.RED), img(png.BLUE), img((0, 255, 0))
+    n = red[0].shape[0]
+    g = torch.Generator().manual_seed(21)
+    a, b, c = (torch.randint(0, 400, (k,), generator=g).tolist() for k in (11, 7, 9))
+    t1 = a + [pad] * n + b + [pad] * n + c
+    s1 = [(len(a), len(a) + n), (len(a) + n + len(b), len(a) + 2 * n + len(b))]
+    o1 = re_.generate(t1, TurnOpts(max_new=3, ignore_eos=True, session="s", images=[red, blue], image_pad_id=pad, evict_spans=s1))
+    assert len(o1) == 3 and "s" in re_.parked
+    seq = next(iter(eng.seqs.values()))
+    assert [fp for _, _, fp in seq.images] == [red[2], blue[2]] and all(f % 16 == 0 for f, _, _ in seq.images)
+    pages1 = len(seq.pages)
+    # turn 2: red is gone, a new (green) screenshot follows the history
+    d = [5, 6, 7]
+    t2 = a + b + [pad] * n + c + o1 + d + [pad] * n + [8]
+    lo = len(a) + len(b) + n + len(c) + len(o1) + len(d)
+    o2 = re_.generate(t2, TurnOpts(max_new=3, ignore_eos=True, session="s", images=[blue, green], image_pad_id=pad,
+                                   evict_spans=[(len(a) + len(b), len(a) + len(b) + n), (lo, lo + n)]))
+    assert re_.resumed == 1 and re_.gap_drops == 1 and len(o2) == 3
+    assert [fp for _, _, fp in seq.images] == [blue[2], green[2]] and seq.images[1][0] % 16 == 0
+    assert seq.pos3.shape[1] >= seq.images[1][0] + n
+    p = seq.pos3[:, seq.images[1][0]:seq.images[1][0] + n]
+    assert int(p[0].max()) == int(p[0].min()) and int(p[1].max() - p[1].min()) == 1 and int(p[2].max() - p[2].min()) == 2
+    assert int(seq.pos3[0, seq.images[1][0] - 1]) < int(p[0].min())            # the block starts after everything before it
+    assert len(seq.tokens) + seq.rope_delta > int(seq.pos3.max())               # decode positions continue past every used id
+    # turn 3: blue is gone as well
+    t3 = a + b + c + o1 + d + [pad] * n + [8] + o2 + [9]
+    lo3 = len(a) + len(b) + len(c) + len(o1) + len(d)
+    o3 = re_.generate(t3, TurnOpts(max_new=2, ignore_eos=True, session="s", images=[green], image_pad_id=pad, evict_spans=[(lo3, lo3 + n)]))
+    assert re_.resumed == 2 and re_.gap_drops == 2 and len(o3) == 2
+    assert [fp for _, _, fp in seq.images] == [green[2]] and len(seq.pages) <= pages1 + 2
+    # same-sized image with other content in the kept slot is NOT a continuation
+    t4 = [x for x in t3]
+    re_.generate(t4 + o3 + [1], TurnOpts(max_new=1, ignore_eos=True, session="s", images=[red], image_pad_id=pad))
+    assert re_.resumed == 2
+    # droppable marks while sessions are not parked are refused
+    with pytest.raises(ValueError):
+        RunningEngine(eng, max_batch=2).submit(a, TurnOpts(evict_spans=[(0, 4)]))

@@ -57,3 +57,50 @@ def test_position_ledger_keeps_holes():
     assert kept == list(range(32)) + list(range(64, 100)) and nxt == 100
     kept2, nxt2 = E.positions_after_splice(kept + [100, 101], [(48, 64)])            # a second deletion later on
     assert nxt2 == 102 and len(kept2) == len(kept) + 2 - 16
+
+
+def test_pad_rule_continues_a_live_sequence_from_its_cache_index():
+    """A suffix appended at cache index 37: its droppable segment starts and ends on page boundaries of the SEQUENCE."""
+    suffix = list(range(100, 130))
+    ps = E.pad_rule(suffix, [(5, 17)], 16, 0, base=37)
+    sp = ps.spans[0]
+    assert sp.start % 16 == 0 and sp.hi % 16 == 0 and sp.start == 48 and sp.end == 60 and sp.hi == 64
+    assert ps.ids[:5] == suffix[:5] and ps.ids[5:11] == [0] * 6 and ps.ids[11:23] == suffix[5:17]
+    whole = E.PaddedSeq(list(range(37)) + ps.ids, ps.spans)
+    assert E.unpad(whole) == list(range(37)) + suffix
+    r, tail = E.detect_deletions(whole, list(range(37)) + suffix[:5] + suffix[17:] + [7])
+    assert r == [(48, 64)] and tail == [7]
+
+
+def test_identity_ids_tell_same_sized_images_apart():
+    pad = 9
+    ids = [1, 2, pad, pad, pad, 3, pad, pad, pad, 4]
+    a = E.identity_ids(ids, pad, [111, 222])
+    assert a[0:2] == [1, 2] and a[5] == 3 and a[9] == 4 and len(set(a[2:5])) == 1 and len(set(a[6:9])) == 1 and a[2] != a[6]
+    assert all(t < 0 for t in a[2:5] + a[6:9])
+    old = E.pad_rule(a, [(2, 5), (6, 9)], 4, 0)
+    # the client drops the FIRST image: with plain pad tokens the two histories would also match "second image dropped"
+    new = E.identity_ids([1, 2, 3, pad, pad, pad, 4, 5], pad, [222])
+    r, tail = E.detect_deletions(old, new)
+    assert r == [(old.spans[0].start, old.spans[0].hi)] and tail == [5]
+    assert E.identity_ids(ids, None, []) == ids
+
+
+def test_vision_expand_reports_droppable_spans_with_their_markers():
+    import torch
+
+    from owl_engine_b200.cli import png
+    from owl_engine_b200.models import vision as V
+    from owl_engine_b200.server.http import Vision
+
+    tower = V.VisionTower(V.tiny_vision(out_hidden=64))
+    vis = Vision(tower, pad_id=500)
+    red, blue = png.encode_png(96, 64, png.RED), png.encode_png(96, 64, png.BLUE)
+    ids = [1, 2, 70, 500, 71, 3, 70, 500, 71, 4]
+    out, images, spans = vis.expand(ids, [red, blue], [True, False], (70, 71))
+    n = images[0][0].shape[0]
+    assert out == [1, 2, 70] + [500] * n + [71, 3, 70] + [500] * n + [71, 4] and len(images) == 2
+    assert spans == [(2, 2 + n + 2)]
+    out2, _, spans2 = vis.expand(ids, [red, blue], [True, True])        # no marker ids known: the pad runs alone
+    assert spans2 == [(3, 3 + n), (3 + n + 3, 3 + 2 * n + 3)] and out2 == out
+    assert torch.equal(images[0][0], vis.expand(ids, [red, blue])[1][0][0])
