@@ -243,8 +243,9 @@ def main() -> None:
                        "lm_head": "int8 per row, W8A16 (reference default head_quant = rtn-int8-row)" if args.head == "int8" else "bf16", "kv": "fp8 e4m3 paged, block 16",
                        "l2": "inputs larger than L2: every step streams the full weight set "
                              f"({eng.weights.streamed_bytes() / 1e9:.1f} GB per rank)",
-                       "comm": args.comm if world > 1 else "none",
-                       "sp_prefill": bool(eng.runner.sp_prefill and world > 1), "cuda_graph": True, "decode_gemv": args.gemv,
+                       "comm": comm.mode if world > 1 else "none",
+                       "comm_proof": (getattr(comm, "proof", {}).get("ok") if world > 1 else None),
+                       "sp_prefill": bool(world > 1 and eng.runner._pipe() is not None), "cuda_graph": True, "decode_gemv": args.gemv,
                        "prefill_gemm": args.prefill_gemm},
             "e2e": {"value": round(e2e_value, 2), "unit": "tokens/s",
                     "h2d_bytes_per_step": (eng.h2d_bytes - h2d0) // steps,

@@ -31,6 +31,8 @@ def _worker(rank, world, port, mode, q):
 
     comm = TpComm.from_env(mode, hidden=256, big_elems=64 * 256)
     dev = comm.device
+    if mode in ("fused", "push"):       # the post-assembly proof ran, passed, and left the own kernels in place
+        assert comm.proof["ok"] and comm.symm is not None and comm.mode == mode, comm.proof
     full = make_spec(n_layers=4, vocab=512)
     dense = init_weights(full, seed=3, std=0.05)
     spec = full.sharded(rank, world)
@@ -122,6 +124,7 @@ def _worker_sp(rank, world, port, q):
 
     comm = TpComm.from_env("fused", hidden=256, big_elems=256 * 256)
     dev = comm.device
+    assert comm.proof["ok"] and "sp_gemm" in comm.proof and comm.symm is not None, comm.proof
     full = make_spec(n_layers=4, vocab=512)
     dense = init_weights(full, seed=3, std=0.05)
     spec = full.sharded(rank, world)
