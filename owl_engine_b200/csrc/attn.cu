@@ -36,6 +36,7 @@ struct InsertParams {
   __nv_bfloat16* q_out;         // [rows][hq][hd]
   uint8_t* k_pool; uint8_t* v_pool;  // [pages][16][hkv][hd] e4m3, or int8 when the scale pools are given
   float* k_scale; float* v_scale;    // int8 pool: [pages][16][hkv] per (token, kv head) scales (null: e4m3 pool)
+  int kv16;                          // 16-bit pool: fp16 words holding the bf16-rounded values (exact inside the fp16 range)
   int rows, hq, hkv, hd, rot;
   float eps, rope_scale;        // rope_scale multiplies cos/sin (YaRN attention factor)
 };
@@ -98,6 +99,11 @@ __global__ void __launch_bounds__(128) qknorm_rope_insert_kernel(InsertParams p)
     uint8_t* dst = (is_k ? p.k_pool : p.v_pool) + ((size_t)slot * p.hkv + kvh) * hd + e0;
     // values are rounded to bf16 first so the pool holds cast(bf16(x)) like a two-step pipeline
     const float ar = __bfloat162float(__float2bfloat16(a)), br = __bfloat162float(__float2bfloat16(b));
+    if (p.kv16) {
+      __half2* d16 = reinterpret_cast<__half2*>((is_k ? p.k_pool : p.v_pool) + (((size_t)slot * p.hkv + kvh) * hd + e0) * 2);
+      *d16 = __floats2half2_rn(fminf(fmaxf(ar, -65504.f), 65504.f), fminf(fmaxf(br, -65504.f), 65504.f));
+      return;
+    }
     if (p.k_scale) {
       const float sc = amax > 0.f ? amax / 127.f : 1.f, inv = 1.f / sc;
       const int qa = max(-127, min(127, __float2int_rn(ar * inv))), qb = max(-127, min(127, __float2int_rn(br * inv)));
@@ -142,9 +148,11 @@ __device__ __forceinline__ uint32_t s8x2_to_f16x2(uint32_t two_bytes) {
   const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&w), __half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480)));
   return *reinterpret_cast<const uint32_t*>(&r);
 }
-template <bool I8>
+// pool formats of the attention kernel
+enum { KV_E4M3 = 0, KV_I8 = 1, KV_F16 = 2 };
+template <int KV>
 __device__ __forceinline__ uint32_t kv2_to_f16x2(uint32_t two_bytes) {
-  return I8 ? s8x2_to_f16x2(two_bytes) : e4m3x2_to_f16x2(two_bytes);
+  return KV == KV_I8 ? s8x2_to_f16x2(two_bytes) : e4m3x2_to_f16x2(two_bytes);
 }
 __device__ __forceinline__ void mma16816(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
@@ -154,9 +162,11 @@ __device__ __forceinline__ void mma16816(float* c, uint32_t a0, uint32_t a1, uin
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int RG, bool I8>
+template <int RG, int KV>
 __global__ void __launch_bounds__(AT_WARPS * 32) paged_attn_kernel(AttnParams p) {
   constexpr int TS = AT_WARPS / RG;
+  constexpr bool I8 = KV == KV_I8, F16 = KV == KV_F16;
+  constexpr int ESZ = F16 ? 2 : 1;             // bytes per pool element
   // cross-warp merge buffers (token splits of the same row group)
   __shared__ float mo[AT_WARPS][8][HD + 1];   // O by [row][dim]
   __shared__ float mml[AT_WARPS][8][2];
@@ -209,25 +219,39 @@ __global__ void __launch_bounds__(AT_WARPS * 32) paged_attn_kernel(AttnParams p)
         const int tk0 = pg * PAGE;
         if (tk0 >= limit) break;
         const int page = bt[pg];
-        const uint8_t* kp = p.k_pool + (((size_t)page * PAGE) * p.hkv + kvh) * HD;
-        const uint8_t* vp = p.v_pool + (((size_t)page * PAGE) * p.hkv + kvh) * HD;
-        const size_t tstride = (size_t)p.hkv * HD;
+        const uint8_t* kp = p.k_pool + (((size_t)page * PAGE) * p.hkv + kvh) * HD * ESZ;
+        const uint8_t* vp = p.v_pool + (((size_t)page * PAGE) * p.hkv + kvh) * HD * ESZ;
+        const size_t tstride = (size_t)p.hkv * HD * ESZ;
         // ---- S = Q K^T for tokens tk0+g (s0) and tk0+8+g (s1) -----------------------------
         float s0[4] = {0, 0, 0, 0}, s1[4] = {0, 0, 0, 0};
         uint4 ka[4], kb[4];
+        uint4 ka2[F16 ? 4 : 1], kb2[F16 ? 4 : 1];   // 16-bit pool: the second 8 of the lane's 16 dims per block
 #pragma unroll
         for (int blk = 0; blk < 4; ++blk) {
-          ka[blk] = ldg_stream(reinterpret_cast<const uint4*>(kp + (size_t)g * tstride + blk * 64 + t * 16));
-          kb[blk] = ldg_stream(reinterpret_cast<const uint4*>(kp + (size_t)(g + 8) * tstride + blk * 64 + t * 16));
+          ka[blk] = ldg_stream(reinterpret_cast<const uint4*>(kp + (size_t)g * tstride + (blk * 64 + t * 16) * ESZ));
+          kb[blk] = ldg_stream(reinterpret_cast<const uint4*>(kp + (size_t)(g + 8) * tstride + (blk * 64 + t * 16) * ESZ));
+          if constexpr (F16) {
+            ka2[blk] = ldg_stream(reinterpret_cast<const uint4*>(kp + (size_t)g * tstride + (blk * 64 + t * 16) * ESZ + 16));
+            kb2[blk] = ldg_stream(reinterpret_cast<const uint4*>(kp + (size_t)(g + 8) * tstride + (blk * 64 + t * 16) * ESZ + 16));
+          }
         }
         // V words for tokens tk0 + {2t, 2t+1, 2t+8, 2t+9}, dims blk*32 + g*4 .. +3
+        // (16-bit pool: two words per token and block, x = dims 0,1 and y = dims 2,3 of the lane's four)
         uint32_t va[8], vb[8], vc[8], vd[8];
+        uint32_t va2[F16 ? 8 : 1], vb2[F16 ? 8 : 1], vc2[F16 ? 8 : 1], vd2[F16 ? 8 : 1];
 #pragma unroll
         for (int blk = 0; blk < 8; ++blk) {
-          va[blk] = ldg_stream_u32(reinterpret_cast<const uint32_t*>(vp + (size_t)(2 * t) * tstride + blk * 32 + g * 4));
-          vb[blk] = ldg_stream_u32(reinterpret_cast<const uint32_t*>(vp + (size_t)(2 * t + 1) * tstride + blk * 32 + g * 4));
-          vc[blk] = ldg_stream_u32(reinterpret_cast<const uint32_t*>(vp + (size_t)(2 * t + 8) * tstride + blk * 32 + g * 4));
-          vd[blk] = ldg_stream_u32(reinterpret_cast<const uint32_t*>(vp + (size_t)(2 * t + 9) * tstride + blk * 32 + g * 4));
+          const size_t doff = (size_t)(blk * 32 + g * 4) * ESZ;
+          va[blk] = ldg_stream_u32(reinterpret_cast<const uint32_t*>(vp + (size_t)(2 * t) * tstride + doff));
+          vb[blk] = ldg_stream_u32(reinterpret_cast<const uint32_t*>(vp + (size_t)(2 * t + 1) * tstride + doff));
+          vc[blk] = ldg_stream_u32(reinterpret_cast<const uint32_t*>(vp + (size_t)(2 * t + 8) * tstride + doff));
+          vd[blk] = ldg_stream_u32(reinterpret_cast<const uint32_t*>(vp + (size_t)(2 * t + 9) * tstride + doff));
+          if constexpr (F16) {
+            va2[blk] = ldg_stream_u32(reinterpret_cast<const uint32_t*>(vp + (size_t)(2 * t) * tstride + doff + 4));
+            vb2[blk] = ldg_stream_u32(reinterpret_cast<const uint32_t*>(vp + (size_t)(2 * t + 1) * tstride + doff + 4));
+            vc2[blk] = ldg_stream_u32(reinterpret_cast<const uint32_t*>(vp + (size_t)(2 * t + 8) * tstride + doff + 4));
+            vd2[blk] = ldg_stream_u32(reinterpret_cast<const uint32_t*>(vp + (size_t)(2 * t + 9) * tstride + doff + 4));
+          }
         }
 #pragma unroll
         for (int blk = 0; blk < 4; ++blk) {
@@ -235,10 +259,17 @@ __global__ void __launch_bounds__(AT_WARPS * 32) paged_attn_kernel(AttnParams p)
           const uint32_t wb[4] = {kb[blk].x, kb[blk].y, kb[blk].z, kb[blk].w};
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            mma16816(s0, qa0[blk * 4 + j], 0u, qa2[blk * 4 + j], 0u, kv2_to_f16x2<I8>(wa[j] & 0xffffu),
-                     kv2_to_f16x2<I8>(wa[j] >> 16));
-            mma16816(s1, qa0[blk * 4 + j], 0u, qa2[blk * 4 + j], 0u, kv2_to_f16x2<I8>(wb[j] & 0xffffu),
-                     kv2_to_f16x2<I8>(wb[j] >> 16));
+            if constexpr (F16) {     // fp16 words as stored: dims j*4 + {0,1} and {2,3}
+              const uint32_t xa[8] = {wa[0], wa[1], wa[2], wa[3], ka2[blk].x, ka2[blk].y, ka2[blk].z, ka2[blk].w};
+              const uint32_t xb[8] = {wb[0], wb[1], wb[2], wb[3], kb2[blk].x, kb2[blk].y, kb2[blk].z, kb2[blk].w};
+              mma16816(s0, qa0[blk * 4 + j], 0u, qa2[blk * 4 + j], 0u, xa[2 * j], xa[2 * j + 1]);
+              mma16816(s1, qa0[blk * 4 + j], 0u, qa2[blk * 4 + j], 0u, xb[2 * j], xb[2 * j + 1]);
+            } else {
+              mma16816(s0, qa0[blk * 4 + j], 0u, qa2[blk * 4 + j], 0u, kv2_to_f16x2<KV>(wa[j] & 0xffffu),
+                       kv2_to_f16x2<KV>(wa[j] >> 16));
+              mma16816(s1, qa0[blk * 4 + j], 0u, qa2[blk * 4 + j], 0u, kv2_to_f16x2<KV>(wb[j] & 0xffffu),
+                       kv2_to_f16x2<KV>(wb[j] >> 16));
+            }
           }
         }
         // s0[0..1]: (row g, tokens tk0+2t, +1); s1[0..1]: (row g, tokens tk0+8+2t, +1)
@@ -284,10 +315,18 @@ __global__ void __launch_bounds__(AT_WARPS * 32) paged_attn_kernel(AttnParams p)
             // m-tile rows: g -> dim blk*32 + g*4 + ip*2, g+8 -> that + 1
             const uint32_t selA = ip ? 0x0062u : 0x0040u;  // bytes (x.b[2ip], y.b[2ip])
             const uint32_t selB = ip ? 0x0073u : 0x0051u;  // bytes (x.b[2ip+1], y.b[2ip+1])
-            const uint32_t a0 = kv2_to_f16x2<I8>(__byte_perm(va[blk], vb[blk], selA) & 0xffffu);
-            const uint32_t a1 = kv2_to_f16x2<I8>(__byte_perm(va[blk], vb[blk], selB) & 0xffffu);
-            const uint32_t a2 = kv2_to_f16x2<I8>(__byte_perm(vc[blk], vd[blk], selA) & 0xffffu);
-            const uint32_t a3 = kv2_to_f16x2<I8>(__byte_perm(vc[blk], vd[blk], selB) & 0xffffu);
+            uint32_t a0, a1, a2, a3;
+            if constexpr (F16) {     // word ip of each token holds dims (2ip, 2ip+1): low halves -> row g, high halves -> row g+8
+              const uint32_t wa_ = ip ? va2[blk] : va[blk], wb_ = ip ? vb2[blk] : vb[blk];
+              const uint32_t wc_ = ip ? vc2[blk] : vc[blk], wd_ = ip ? vd2[blk] : vd[blk];
+              a0 = __byte_perm(wa_, wb_, 0x5410u); a1 = __byte_perm(wa_, wb_, 0x7632u);
+              a2 = __byte_perm(wc_, wd_, 0x5410u); a3 = __byte_perm(wc_, wd_, 0x7632u);
+            } else {
+              a0 = kv2_to_f16x2<KV>(__byte_perm(va[blk], vb[blk], selA) & 0xffffu);
+              a1 = kv2_to_f16x2<KV>(__byte_perm(va[blk], vb[blk], selB) & 0xffffu);
+              a2 = kv2_to_f16x2<KV>(__byte_perm(vc[blk], vd[blk], selA) & 0xffffu);
+              a3 = kv2_to_f16x2<KV>(__byte_perm(vc[blk], vd[blk], selB) & 0xffffu);
+            }
             mma16816(c, a0, a1, a2, a3, pb0, pb1);
           }
         }
@@ -413,7 +452,7 @@ using namespace owl;
 static int insert_launch(const void* qraw, int ldq, const void* kraw, int ldk, const void* vraw, int ldv, const void* qnorm_w,
                          const void* knorm_w, const void* pos3, const void* inv_freq, const void* section, const void* kv_slot,
                          void* q_out, void* k_pool, void* v_pool, void* k_scale, void* v_scale, int rows, int hq, int hkv, int hd,
-                         int rot, float eps, float rope_scale, int pdl, cudaStream_t st) {
+                         int rot, float eps, float rope_scale, int pdl, cudaStream_t st, int kv16 = 0) {
   if (rows < 1 || hd > 256 || (hd & 1) || rot > hd || (rot & 3)) return OWL_ERR_BAD_ARG;
   InsertParams p;
   p.qraw = (const __nv_bfloat16*)qraw; p.ldq = ldq; p.kraw = (const __nv_bfloat16*)kraw; p.ldk = ldk;
@@ -421,7 +460,7 @@ static int insert_launch(const void* qraw, int ldq, const void* kraw, int ldk, c
   p.knorm_w = (const __nv_bfloat16*)knorm_w; p.pos3 = (const int*)pos3; p.inv_freq = (const float*)inv_freq;
   p.section = (const unsigned char*)section; p.kv_slot = (const int*)kv_slot; p.q_out = (__nv_bfloat16*)q_out;
   p.k_pool = (uint8_t*)k_pool; p.v_pool = (uint8_t*)v_pool; p.k_scale = (float*)k_scale; p.v_scale = (float*)v_scale;
-  p.rows = rows; p.hq = hq; p.hkv = hkv; p.hd = hd;
+  p.rows = rows; p.hq = hq; p.hkv = hkv; p.hd = hd; p.kv16 = kv16;
   p.rot = rot; p.eps = eps; p.rope_scale = rope_scale;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(rows, hq + 2 * hkv); cfg.blockDim = dim3(128); cfg.stream = st;
@@ -454,7 +493,17 @@ OWL_API int owl_qknorm_rope_insert_i8(const void* qraw, int ldq, const void* kra
                        k_scale, v_scale, rows, hq, hkv, hd, rot, eps, rope_scale, pdl, st);
 }
 
-template <bool I8>
+// 16-bit KV pool: fp16 words holding the bf16-rounded values (what a bf16 pool holds, readable by the fp16 MMA as stored).
+OWL_API int owl_qknorm_rope_insert_f16(const void* qraw, int ldq, const void* kraw, int ldk, const void* vraw, int ldv,
+                                       const void* qnorm_w, const void* knorm_w, const void* pos3, const void* inv_freq,
+                                       const void* section, const void* kv_slot, void* q_out, void* k_pool, void* v_pool,
+                                       int rows, int hq, int hkv, int hd, int rot, float eps, float rope_scale, int pdl,
+                                       cudaStream_t st) {
+  return insert_launch(qraw, ldq, kraw, ldk, vraw, ldv, qnorm_w, knorm_w, pos3, inv_freq, section, kv_slot, q_out, k_pool, v_pool,
+                       nullptr, nullptr, rows, hq, hkv, hd, rot, eps, rope_scale, pdl, st, 1);
+}
+
+template <int KV>
 static int attn_launch(const void* q, const void* k_pool, const void* v_pool, const void* k_scale, const void* v_scale,
                        const void* block_table, const void* bt_row, const void* ctx_len, void* part_o, void* part_ml, int groups,
                        int T, int hq, int hkv, int hd, int max_blocks, int splits, int per_pages, float scale, int pdl,
@@ -474,10 +523,10 @@ static int attn_launch(const void* q, const void* k_pool, const void* v_pool, co
   cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
   cudaError_t e;
   // per_pages > 0 asks for arithmetic that does not depend on T: one warp per row (no token split inside a CTA)
-  if (per_pages > 0) e = cudaLaunchKernelEx(&cfg, paged_attn_kernel<4, I8>, p);
-  else if (T == 1) e = cudaLaunchKernelEx(&cfg, paged_attn_kernel<1, I8>, p);
-  else if (T == 2) e = cudaLaunchKernelEx(&cfg, paged_attn_kernel<2, I8>, p);
-  else e = cudaLaunchKernelEx(&cfg, paged_attn_kernel<4, I8>, p);
+  if (per_pages > 0) e = cudaLaunchKernelEx(&cfg, paged_attn_kernel<4, KV>, p);
+  else if (T == 1) e = cudaLaunchKernelEx(&cfg, paged_attn_kernel<1, KV>, p);
+  else if (T == 2) e = cudaLaunchKernelEx(&cfg, paged_attn_kernel<2, KV>, p);
+  else e = cudaLaunchKernelEx(&cfg, paged_attn_kernel<4, KV>, p);
   if (e != cudaSuccess) return (int)OWL_ERR_LAUNCH * 1000 - (int)e;
   return OWL_OK;
 }
@@ -487,7 +536,7 @@ OWL_API int owl_paged_attn(const void* q, const void* k_pool, const void* v_pool
                            const void* bt_row, const void* ctx_len, void* part_o, void* part_ml, int groups, int T,
                            int hq, int hkv, int hd, int max_blocks, int splits, int per_pages, float scale, int pdl,
                            cudaStream_t st) {
-  return attn_launch<false>(q, k_pool, v_pool, nullptr, nullptr, block_table, bt_row, ctx_len, part_o, part_ml, groups, T, hq, hkv,
+  return attn_launch<KV_E4M3>(q, k_pool, v_pool, nullptr, nullptr, block_table, bt_row, ctx_len, part_o, part_ml, groups, T, hq, hkv,
                             hd, max_blocks, splits, per_pages, scale, pdl, st);
 }
 
@@ -497,8 +546,17 @@ OWL_API int owl_paged_attn_i8(const void* q, const void* k_pool, const void* v_p
                               int groups, int T, int hq, int hkv, int hd, int max_blocks, int splits, int per_pages, float scale,
                               int pdl, cudaStream_t st) {
   if (!k_scale || !v_scale) return OWL_ERR_BAD_ARG;
-  return attn_launch<true>(q, k_pool, v_pool, k_scale, v_scale, block_table, bt_row, ctx_len, part_o, part_ml, groups, T, hq, hkv,
+  return attn_launch<KV_I8>(q, k_pool, v_pool, k_scale, v_scale, block_table, bt_row, ctx_len, part_o, part_ml, groups, T, hq, hkv,
                            hd, max_blocks, splits, per_pages, scale, pdl, st);
+}
+
+// The same attention over a 16-bit pool (fp16 words holding bf16-rounded values, written by owl_qknorm_rope_insert_f16).
+OWL_API int owl_paged_attn_f16(const void* q, const void* k_pool, const void* v_pool, const void* block_table,
+                               const void* bt_row, const void* ctx_len, void* part_o, void* part_ml, int groups, int T,
+                               int hq, int hkv, int hd, int max_blocks, int splits, int per_pages, float scale, int pdl,
+                               cudaStream_t st) {
+  return attn_launch<KV_F16>(q, k_pool, v_pool, nullptr, nullptr, block_table, bt_row, ctx_len, part_o, part_ml, groups, T, hq, hkv,
+                             hd, max_blocks, splits, per_pages, scale, pdl, st);
 }
 
 OWL_API int owl_attn_reduce(const void* part_o, const void* part_ml, int splits, const void* qraw, int ldq, void* out,

@@ -44,7 +44,7 @@ class EngineConfig:
     seed: int = 0
     n_layers: int | None = None    # override (tests / smoke)
     snap_cut: bool = False         # cut a separate chunk at the prompt's last block boundary instead of snapshotting inside a chunk
-    kv_dtype: str = "fp8"          # KV pool format: "fp8" (e4m3) or "int8" (per token, per head scales)
+    kv_dtype: str = "fp8"          # KV pool format: "fp8" (e4m3), "int8" (per token, per head scales), "bf16" / "f16" (16-bit)
     kvmem_budget: int = 0          # tokens of KV a decode step may attend to (0 = everything): longer contexts attend to a
                                    # view of sink + recent + best-scoring blocks, re-selected at every block boundary
     kvmem_sink: int = 2

@@ -248,11 +248,14 @@ class StatePool:
     def __init__(self, spec: ModelSpec, device, n_pages: int, n_slots: int, ledger=None, kv_dtype: str = "fp8"):
         """``kv_dtype`` "fp8": e4m3 values (no scales); "int8": int8 values with one fp32 scale per (token, kv head) in
         ``k_scale`` / ``v_scale`` (the reference's int8 KV family, crates/kernels/cu/attn int8 kernels)."""
-        assert kv_dtype in ("fp8", "int8")
+        assert kv_dtype in ("fp8", "int8", "bf16", "f16")
         self.spec, self.device, self.n_pages, self.n_slots, self.kv_dtype = spec, device, n_pages, n_slots, kv_dtype
         nf, ng = spec.n_full, spec.n_gdn
-        self.k_pool = torch.zeros(nf, n_pages, PAGE, spec.hkv, spec.hd, dtype=torch.uint8, device=device)
-        self.v_pool = torch.zeros(nf, n_pages, PAGE, spec.hkv, spec.hd, dtype=torch.uint8, device=device)
+        # "bf16" / "f16": a 16-bit pool of fp16 words that hold the bf16-rounded K / V values (exact inside the fp16 range,
+        # clamped outside), which the attention kernel feeds to the fp16 MMA as stored; the kernels tell the pools apart by dtype
+        pdt = torch.float16 if kv_dtype in ("bf16", "f16") else torch.uint8
+        self.k_pool = torch.zeros(nf, n_pages, PAGE, spec.hkv, spec.hd, dtype=pdt, device=device)
+        self.v_pool = torch.zeros(nf, n_pages, PAGE, spec.hkv, spec.hd, dtype=pdt, device=device)
         self.k_scale = self.v_scale = None
         if kv_dtype == "int8":
             self.k_scale = torch.zeros(nf, n_pages, PAGE, spec.hkv, dtype=torch.float32, device=device)
@@ -260,12 +263,12 @@ class StatePool:
         self.conv_state = torch.zeros(ng, n_slots, spec.conv_dim, spec.conv_k - 1, dtype=torch.float32, device=device)
         self.rec_state = torch.zeros(ng, n_slots, spec.nv, spec.kd, spec.vd, dtype=torch.float32, device=device)
         if ledger is not None:
-            ledger.record("kv_pool", "pool", self.k_pool.numel() * 2)
+            ledger.record("kv_pool", "pool", self.k_pool.numel() * self.k_pool.element_size() * 2)
             ledger.record("gdn_state", "pool", self.conv_state.numel() * 4 + self.rec_state.numel() * 4)
 
     @staticmethod
-    def bytes_per_page(spec: ModelSpec) -> int:
-        return spec.n_full * 2 * PAGE * spec.hkv * spec.hd
+    def bytes_per_page(spec: ModelSpec, kv_dtype: str = "fp8") -> int:
+        return spec.n_full * 2 * PAGE * spec.hkv * spec.hd * (2 if kv_dtype in ("bf16", "f16") else 1)
 
     @staticmethod
     def bytes_per_slot(spec: ModelSpec) -> int:

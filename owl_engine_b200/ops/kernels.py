@@ -35,6 +35,9 @@ _SIGS = {
     "owl_qknorm_rope_insert": [_P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F,
                                _F, _I, _P],
     "owl_paged_attn": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+    "owl_qknorm_rope_insert_f16": [_P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F,
+                                   _F, _I, _P],
+    "owl_paged_attn_f16": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "owl_qknorm_rope_insert_i8": [_P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F,
                                   _F, _I, _P],
     "owl_paged_attn_i8": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
@@ -264,6 +267,11 @@ def qknorm_rope_insert(qraw, ldq: int, kraw, ldk: int, vraw, ldv: int, qnorm_w, 
                        kv_slot, q_out, k_pool, v_pool, rows: int, hq: int, hkv: int, hd: int, rot: int,
                        eps: float = 1e-6, rope_scale: float = 1.0, pdl: bool = False, scales=None) -> None:
     """``scales`` = (k_scale, v_scale) fp32 [pages, 16, hkv] selects the int8 pool form."""
+    if k_pool.dtype == torch.float16:
+        call("owl_qknorm_rope_insert_f16", ptr(qraw), ldq, ptr(kraw), ldk, ptr(vraw), ldv, ptr(qnorm_w), ptr(knorm_w),
+             ptr(pos3), ptr(inv_freq), ptr(section), ptr(kv_slot), ptr(q_out), ptr(k_pool), ptr(v_pool), rows, hq, hkv,
+             hd, rot, eps, rope_scale, int(pdl), stream())
+        return
     if scales is not None:
         call("owl_qknorm_rope_insert_i8", ptr(qraw), ldq, ptr(kraw), ldk, ptr(vraw), ldv, ptr(qnorm_w), ptr(knorm_w),
              ptr(pos3), ptr(inv_freq), ptr(section), ptr(kv_slot), ptr(q_out), ptr(k_pool), ptr(v_pool), ptr(scales[0]),
@@ -278,6 +286,10 @@ def paged_attn(q, k_pool, v_pool, block_table, bt_row, ctx_len, part_o, part_ml,
                hkv: int, hd: int, max_blocks: int, splits: int, scale: float, pdl: bool = False, per_pages: int = 0,
                scales=None) -> None:
     """``per_pages`` > 0 fixes the pages per KV split (must satisfy splits * per_pages >= pages of the longest row)."""
+    if k_pool.dtype == torch.float16:
+        call("owl_paged_attn_f16", ptr(q), ptr(k_pool), ptr(v_pool), ptr(block_table), ptr(bt_row), ptr(ctx_len), ptr(part_o),
+             ptr(part_ml), groups, t, hq, hkv, hd, max_blocks, splits, per_pages, scale, int(pdl), stream())
+        return
     if scales is not None:
         call("owl_paged_attn_i8", ptr(q), ptr(k_pool), ptr(v_pool), ptr(scales[0]), ptr(scales[1]), ptr(block_table),
              ptr(bt_row), ptr(ctx_len), ptr(part_o), ptr(part_ml), groups, t, hq, hkv, hd, max_blocks, splits, per_pages, scale,

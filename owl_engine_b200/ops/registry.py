@@ -91,6 +91,8 @@ _T = [
     KernelSpec("owl_paged_attn", "attn.cu", "attn", gen="mma.sync"),
     KernelSpec("owl_qknorm_rope_insert_i8", "attn.cu", "attn"),
     KernelSpec("owl_paged_attn_i8", "attn.cu", "attn", gen="mma.sync"),
+    KernelSpec("owl_qknorm_rope_insert_f16", "attn.cu", "attn"),
+    KernelSpec("owl_paged_attn_f16", "attn.cu", "attn", gen="mma.sync"),
     KernelSpec("owl_attn_reduce", "attn.cu", "attn"),
     # collectives over peer memory
     KernelSpec("owl_ar_residual_norm", "comm.cu", "comm", gen="p2p+multimem"),

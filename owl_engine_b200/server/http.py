@@ -305,7 +305,7 @@ def _vram(re) -> dict:
     free, total = torch.cuda.mem_get_info(re.e.device)
     led = Ledger()
     led.record("weights", "weights", re.e.weights.nbytes())
-    led.record("kv_pool", "kv pool", re.e.pool.k_pool.numel() * 2)
+    led.record("kv_pool", "kv pool", re.e.pool.k_pool.numel() * re.e.pool.k_pool.element_size() * 2)
     led.record("gdn_rows", "gdn state", re.e.pool.conv_state.numel() * 4 + re.e.pool.rec_state.numel() * 4)
     return led.view(total, free)
 

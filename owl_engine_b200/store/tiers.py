@@ -53,7 +53,8 @@ class HostTier:
 def page_views(pool, page: int):
     """The device slabs of one KV page as byte views: k_pool[:, page], v_pool[:, page] and, for the int8 pool, the
     page's scale slabs."""
-    views = [pool.k_pool[:, page].reshape(pool.k_pool.shape[0], -1), pool.v_pool[:, page].reshape(pool.v_pool.shape[0], -1)]
+    views = [t[:, page].reshape(t.shape[0], -1) for t in (pool.k_pool, pool.v_pool)]
+    views = [v if v.dtype == torch.uint8 else v.view(torch.uint8) for v in views]          # 16-bit pool: fp16 words as bytes
     for sc in (getattr(pool, "k_scale", None), getattr(pool, "v_scale", None)):
         if sc is not None:
             views.append(sc[:, page].reshape(sc.shape[0], -1).view(torch.uint8))

@@ -62,7 +62,7 @@ SCHEMA: dict = {
     "store": {"prefix_cache": bool, "host_cache_mb": int, "snap_host_mb": int, "disk_cache_mb": int,
               "snap_disk_mb": int, "disk_dir": str, "vram_budget": float, "vram_reserve_mb": int, "no_reclaim": bool,
               "block_tokens": Enum(16, 32), "evict_policy": Enum("lru", "lrfu")},
-    "store.kv": {"kv_dtype": Enum("fp8", "int8"), "draft_kv_dtype": Enum("bf16", "fp8")},
+    "store.kv": {"kv_dtype": Enum("fp8", "int8", "bf16", "f16"), "draft_kv_dtype": Enum("bf16", "fp8")},
     "store.gdn": {"gdn_slots": int, "snap_decode_stride": int, "snap_max": int, "snap_msg_min_gap": int,
                   "snap_msg_recent": int, "snap_session_cap": int, "snap_structural_reserve": int},
     "spec": {"depth": int, "draft_path": str, "kind": Enum("none", "mtp", "dflash2"), "lookup": bool, "lookup_nmin": int,

@@ -40,7 +40,7 @@ def estimate(cfg) -> dict:
     rspec = spec.sharded(0, world) if world > 1 else spec
     total = B200_HBM_BYTES
     avail = int(total * v["store"]["vram_budget"]) - (v["store"]["vram_reserve_mb"] << 20)
-    kv_elem = {"fp8": 1, "int8": 1, "bf16": 2}[v["store.kv"]["kv_dtype"]]
+    kv_elem = {"fp8": 1, "int8": 1, "bf16": 2, "f16": 2}[v["store.kv"]["kv_dtype"]]
     w = weight_bytes(rspec, v["model"]["quant"], v["model"]["group"], v["model"]["head_quant"] != "bf16")
     slots = v["store.gdn"]["gdn_slots"] + v["store.gdn"]["snap_max"]
     gdn = slots * rspec.gdn_state_bytes()

@@ -346,6 +346,35 @@ def test_paged_attention(t, ctx_lens, splits):
         torch.testing.assert_close(got, want, rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("t,ctx_lens,splits", [(1, [37, 200], 3), (4, [50, 130], 2), (8, [97, 8], 1)])
+def test_paged_attention_16bit_pool(t, ctx_lens, splits):
+    """The same attention over a 16-bit pool (fp16 words): K / V are used as stored, so the fp32 reference on the
+    fp16-rounded values is matched more tightly than with the 8-bit pools."""
+    hq, hkv, hd = 6, 1, 256
+    batch = len(ctx_lens)
+    q, k8, v8, bt, ks, vs, max_blocks = _attn_case(batch, t, ctx_lens)
+    k_pool = k8.view(torch.float8_e4m3fn).float().half()        # the case's values (exact in fp16), as a 16-bit pool
+    v_pool = v8.view(torch.float8_e4m3fn).float().half()
+    rows = batch * t
+    part_o = torch.zeros(rows * hq * splits * hd, dtype=torch.float32, device=DEV)
+    part_ml = torch.zeros(rows * hq * splits * 2, dtype=torch.float32, device=DEV)
+    ctx = torch.tensor(ctx_lens, dtype=torch.int32, device=DEV)
+    K.paged_attn(q.to(DEV), k_pool.to(DEV), v_pool.to(DEV), bt.to(DEV), None, ctx, part_o, part_ml, batch, t, hq, hkv, hd,
+                 max_blocks, splits, 1.0 / math.sqrt(hd))
+    out = torch.empty(rows, hq * hd, dtype=torch.bfloat16, device=DEV)
+    K.attn_reduce(part_o, part_ml, splits, None, 0, rows, hq, out=out)
+    o8 = torch.empty_like(out)
+    K.paged_attn(q.to(DEV), k8.to(DEV), v8.to(DEV), bt.to(DEV), None, ctx, part_o, part_ml, batch, t, hq, hkv, hd,
+                 max_blocks, splits, 1.0 / math.sqrt(hd))
+    K.attn_reduce(part_o, part_ml, splits, None, 0, rows, hq, out=o8)
+    torch.cuda.synchronize()
+    assert torch.equal(out, o8)          # same values in both pools: the two formats feed the MMA identical fp16 operands
+    for b in range(batch):
+        want = R.gqa_attention(q[b * t:(b + 1) * t].float(), ks[b], vs[b], ctx_lens[b] - t)
+        got = out[b * t:(b + 1) * t].float().cpu().view(t, hq, hd)
+        torch.testing.assert_close(got, want, rtol=2e-2, atol=2e-2)
+
+
 def test_qknorm_rope_insert():
     rows, hq, hkv, hd, rot = 5, 6, 2, 256, 64
     g = gen(40)
@@ -379,6 +408,21 @@ def test_qknorm_rope_insert():
         torch.testing.assert_close(kp[s], want_k[r], rtol=0.07, atol=0.02)
         torch.testing.assert_close(vp[s], vraw[r].float().view(hkv, hd), rtol=0.07, atol=0.02)
     assert torch.count_nonzero(kp[1]) == 0
+    # 16-bit pool: fp16 words holding the bf16-rounded values
+    k16 = torch.zeros(4, 16, hkv, hd, dtype=torch.float16, device=DEV)
+    v16 = torch.zeros_like(k16)
+    K.qknorm_rope_insert(qraw.to(DEV), hq * 2 * hd, kraw.to(DEV), hkv * hd, vraw.to(DEV), hkv * hd, qw.to(DEV),
+                         kw.to(DEV), pos3.to(DEV), inv.to(DEV), torch.tensor(section, dtype=torch.uint8, device=DEV),
+                         kv_slot.to(DEV), q_out, k16, v16, rows, hq, hkv, hd, rot)
+    torch.cuda.synchronize()
+    kp, vp = k16.view(-1, hkv, hd).float().cpu(), v16.view(-1, hkv, hd).float().cpu()
+    for r in range(rows):
+        s = int(kv_slot[r])
+        if s < 0:
+            continue
+        torch.testing.assert_close(kp[s], want_k[r], rtol=1e-2, atol=1e-2)
+        assert torch.equal(vp[s], vraw[r].float().view(hkv, hd))                 # bf16 inputs are stored exactly
+    assert torch.count_nonzero(kp[1]) == 0 and torch.equal(kp, kp.bfloat16().float())
 
 
 def test_zz_skinny_status_clean_after_all():

@@ -140,10 +140,12 @@ def test_sequence_parallel_prefill_protocol_on_one_gpu():
     assert rel_err(outs[0][0], hr[-1:]) < 0.05
 
 
-def test_int8_kv_pool_matches_reference():
-    """int8 KV pool (per token, per head scales): prefill in two chunks, then eager and graph decode steps against the
-    fp32 model with an unquantised cache; the stored bytes dequantise to the keys the kernel was given."""
-    spec, run, ref = build("tc", kv_dtype="int8")
+@pytest.mark.parametrize("kv_dtype", ["int8", "bf16"])
+def test_int8_and_16bit_kv_pools_match_reference(kv_dtype):
+    """int8 KV pool (per token, per head scales) and the 16-bit pool (fp16 words holding bf16-rounded values): prefill in two
+    chunks, then eager and graph decode steps against the fp32 model with an unquantised cache; the stored values are the keys
+    the kernel was given."""
+    spec, run, ref = build("tc", kv_dtype=kv_dtype)
     g = torch.Generator().manual_seed(0)
     prompt = torch.randint(0, spec.vocab, (37,), generator=g)
     seq_row, slot = 1, 2
@@ -156,8 +158,13 @@ def test_int8_kv_pool_matches_reference():
     hr = ref.forward(prompt, st)
     want = ref.logits(hr[-1:])
     assert rel_err(run.logits[:1].float().cpu(), want) < 0.05
-    ks = run.pool.k_scale[0, 5]                              # page 5 holds positions 0..15
-    assert (ks > 0).all() and (run.pool.k_pool[0, 5].view(torch.int8).abs().amax(-1) == 127).all()
+    if kv_dtype == "int8":
+        ks = run.pool.k_scale[0, 5]                              # page 5 holds positions 0..15
+        assert (ks > 0).all() and (run.pool.k_pool[0, 5].view(torch.int8).abs().amax(-1) == 127).all()
+    else:
+        kp = run.pool.k_pool[0, 5]                               # fp16 words, every one exactly a bf16 value
+        assert kp.dtype == torch.float16 and torch.equal(kp.float(), kp.float().bfloat16().float()) and kp.abs().max() > 0
+        assert rel_err(run.logits[:1].float().cpu(), want) < 0.03
     lay = H.StepLayout(1, 1)
     v = run.views(lay)
     nxt = int(want.argmax(-1))
