@@ -19,22 +19,34 @@ __device__ __forceinline__ float e4m3_to_f(uint8_t v) {
   return __half2float(__half(__nv_cvt_fp8_to_halfraw(v, __NV_E4M3)));
 }
 
+// pool element d of a token row: FMT 0 e4m3, 1 int8 (scaled by the token's scale afterwards), 2 fp16 words
+template <int FMT>
+__device__ __forceinline__ float kv_elem(const uint8_t* row, int d) {
+  if (FMT == 2) return __half2float(reinterpret_cast<const __half*>(row)[d]);
+  if (FMT == 1) return (float)reinterpret_cast<const int8_t*>(row)[d];
+  return e4m3_to_f(row[d]);
+}
+
 // grid (blocks, hkv), hd threads.
-__global__ void mean_k_block_kernel(const uint8_t* __restrict__ k_pool, const int* __restrict__ pages, const int* __restrict__ pos0,
+template <int FMT>
+__global__ void mean_k_block_kernel(const uint8_t* __restrict__ k_pool, const float* __restrict__ k_scale,
+                                    const int* __restrict__ pages, const int* __restrict__ pos0,
                                     const int* __restrict__ n_valid, const float* __restrict__ inv_freq, int rotary_dim, int hkv,
                                     int hd, float* __restrict__ out) {
+  constexpr int ESZ = FMT == 2 ? 2 : 1;
   const int b = blockIdx.x, h = blockIdx.y, d = threadIdx.x, half = rotary_dim / 2;
   const int n = min(max(n_valid[b], 1), KVM_PAGE);
-  const uint8_t* base = k_pool + (((size_t)pages[b] * KVM_PAGE) * hkv + h) * hd;
+  const uint8_t* base = k_pool + (((size_t)pages[b] * KVM_PAGE) * hkv + h) * hd * ESZ;
   float acc = 0.f;
   for (int i = 0; i < n; ++i) {
-    const uint8_t* kp = base + (size_t)i * hkv * hd;
-    float v = e4m3_to_f(kp[d]);
+    const uint8_t* kp = base + (size_t)i * hkv * hd * ESZ;
+    const float sc = FMT == 1 ? k_scale[((size_t)pages[b] * KVM_PAGE + i) * hkv + h] : 1.f;
+    float v = kv_elem<FMT>(kp, d) * sc;
     if (d < rotary_dim) {
       const int j = d < half ? d : d - half;
       float sn, cs;
       sincosf((float)(pos0[b] + i) * inv_freq[j], &sn, &cs);
-      const float o = e4m3_to_f(kp[d < half ? d + half : d - half]);
+      const float o = kv_elem<FMT>(kp, d < half ? d + half : d - half) * sc;
       v = d < half ? v * cs + o * sn : v * cs - o * sn;       // inverse rotation
     }
     acc += v;
@@ -96,8 +108,30 @@ using namespace owl;
 OWL_API int owl_mean_k_block(const void* k_pool, const void* pages, const void* pos0, const void* n_valid, const void* inv_freq,
                              int rotary_dim, int blocks, int hkv, int hd, void* out, cudaStream_t st) {
   if (blocks < 1 || hkv < 1 || hd < 32 || hd > 1024 || rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1)) return OWL_ERR_BAD_ARG;
-  mean_k_block_kernel<<<dim3(blocks, hkv), hd, 0, st>>>((const uint8_t*)k_pool, (const int*)pages, (const int*)pos0,
-                                                       (const int*)n_valid, (const float*)inv_freq, rotary_dim, hkv, hd, (float*)out);
+  mean_k_block_kernel<0><<<dim3(blocks, hkv), hd, 0, st>>>((const uint8_t*)k_pool, nullptr, (const int*)pages, (const int*)pos0,
+                                                          (const int*)n_valid, (const float*)inv_freq, rotary_dim, hkv, hd,
+                                                          (float*)out);
+  OWL_LAUNCH_CHECK();
+  return OWL_OK;
+}
+
+// The same index over the other pool formats: fmt 1 = int8 with k_scale float [pages][16][hkv], fmt 2 = fp16 words.
+OWL_API int owl_mean_k_block_fmt(const void* k_pool, const void* k_scale, int fmt, const void* pages, const void* pos0,
+                                 const void* n_valid, const void* inv_freq, int rotary_dim, int blocks, int hkv, int hd, void* out,
+                                 cudaStream_t st) {
+  if (blocks < 1 || hkv < 1 || hd < 32 || hd > 1024 || rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1) || fmt < 0 || fmt > 2 ||
+      (fmt == 1 && !k_scale))
+    return OWL_ERR_BAD_ARG;
+  const dim3 grid(blocks, hkv);
+  if (fmt == 0)
+    mean_k_block_kernel<0><<<grid, hd, 0, st>>>((const uint8_t*)k_pool, nullptr, (const int*)pages, (const int*)pos0,
+                                                (const int*)n_valid, (const float*)inv_freq, rotary_dim, hkv, hd, (float*)out);
+  else if (fmt == 1)
+    mean_k_block_kernel<1><<<grid, hd, 0, st>>>((const uint8_t*)k_pool, (const float*)k_scale, (const int*)pages, (const int*)pos0,
+                                                (const int*)n_valid, (const float*)inv_freq, rotary_dim, hkv, hd, (float*)out);
+  else
+    mean_k_block_kernel<2><<<grid, hd, 0, st>>>((const uint8_t*)k_pool, nullptr, (const int*)pages, (const int*)pos0,
+                                                (const int*)n_valid, (const float*)inv_freq, rotary_dim, hkv, hd, (float*)out);
   OWL_LAUNCH_CHECK();
   return OWL_OK;
 }

@@ -94,8 +94,6 @@ class Engine:
                                                    layout="block" if cfg.decode_gemv == "tc" else "slice",
                                                    quant="nvfp4" if cfg.quant == "nvfp4" else "w4a16")
         # GDN rows: one per sequence slot, the prefix-snapshot rows, and one scratch row for speculative rollback
-        if cfg.kv_dtype != "fp8" and cfg.kvmem_budget:
-            raise ValueError("KV selection reads the e4m3 pool: kvmem_budget needs kv_dtype = \"fp8\"")
         self.pool = H.StatePool(self.spec, self.device, cfg.n_pages, cfg.n_slots + cfg.n_snap_rows + 1, kv_dtype=cfg.kv_dtype)
         self.spec_row = cfg.n_slots + cfg.n_snap_rows
         self.max_blocks = (cfg.max_seq + PAGE - 1) // PAGE
@@ -502,7 +500,8 @@ class Engine:
             ids = torch.arange(seq.meank_n, cur, dtype=torch.int32, device=dev)
             pages = torch.tensor(seq.pages[seq.meank_n:cur], dtype=torch.int32, device=dev)
             S.mean_k_blocks_gpu(self.pool.k_pool[fi], pages, ids * PAGE + seq.rope_delta, torch.full_like(ids, PAGE), run.inv_freq,
-                                sp.rotary_dim, seq.meank[seq.meank_n:cur])
+                                sp.rotary_dim, seq.meank[seq.meank_n:cur],
+                                k_scale=None if self.pool.k_scale is None else self.pool.k_scale[fi])
             seq.meank_n = cur
         budget_blocks = max(self.cfg.kvmem_sink + self.cfg.kvmem_recent + 1, self.cfg.kvmem_budget // PAGE)
         q_row = self._last_rows.get(seq.sid, -1)

@@ -51,6 +51,7 @@ _T = [
     KernelSpec("owl_w4_dequant", "dequant.cu", "load"),
     KernelSpec("owl_quant_e4m3_rows", "dequant.cu", "load"),
     KernelSpec("owl_mean_k_block", "kvmem.cu", "select"),
+    KernelSpec("owl_mean_k_block_fmt", "kvmem.cu", "select"),
     KernelSpec("owl_kvscore", "kvmem.cu", "select"),
     KernelSpec("owl_kvscore_softmax", "kvmem.cu", "select"),
     KernelSpec("owl_dflash_conv", "dflash.cu", "draft"),

@@ -72,19 +72,22 @@ def _K():
     if "owl_mean_k_block" not in K._SIGS:
         P, I, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
         K.register("owl_mean_k_block", [P, P, P, P, P, I, I, I, I, P, P])
+        K.register("owl_mean_k_block_fmt", [P, P, I, P, P, P, P, I, I, I, I, P, P])
         K.register("owl_kvscore", [P, P, P, P, I, I, I, I, I, I, P, P])
         K.register("owl_kvscore_softmax", [P, I, F, P, P])
     return K
 
 
 def mean_k_blocks_gpu(k_pool_layer: torch.Tensor, pages: torch.Tensor, pos0: torch.Tensor, n_valid: torch.Tensor,
-                      inv_freq: torch.Tensor, rotary_dim: int, out: torch.Tensor) -> torch.Tensor:
-    """Block means of de-rotated keys straight from the paged e4m3 pool of one layer -> ``out[:len(pages)]``."""
+                      inv_freq: torch.Tensor, rotary_dim: int, out: torch.Tensor, k_scale: torch.Tensor | None = None) -> torch.Tensor:
+    """Block means of de-rotated keys straight from the paged pool of one layer -> ``out[:len(pages)]``. The pool format is
+    read off the tensors: fp16 words (16-bit pool), int8 with ``k_scale`` [pages, 16, hkv], else e4m3."""
     K = _K()
     _, _, hkv, hd = k_pool_layer.shape
     n = pages.numel()
-    K.call("owl_mean_k_block", K.ptr(k_pool_layer), K.ptr(pages), K.ptr(pos0), K.ptr(n_valid), K.ptr(inv_freq), rotary_dim, n,
-           hkv, hd, K.ptr(out), K.stream())
+    fmt = 2 if k_pool_layer.dtype == torch.float16 else (1 if k_scale is not None else 0)
+    K.call("owl_mean_k_block_fmt", K.ptr(k_pool_layer), K.ptr(k_scale), fmt, K.ptr(pages), K.ptr(pos0), K.ptr(n_valid),
+           K.ptr(inv_freq), rotary_dim, n, hkv, hd, K.ptr(out), K.stream())
     return out[:n]
 
 

@@ -389,3 +389,34 @@ def test_parked_session_with_screenshots_drops_one_and_takes_a_new_one():
     # droppable marks while sessions are not parked are refused
     with pytest.raises(ValueError):
         RunningEngine(eng, max_batch=2).submit(a, TurnOpts(evict_spans=[(0, 4)]))
+
+
+@pytest.mark.parametrize("kv_dtype", ["int8", "bf16"])
+def test_kv_selection_index_over_int8_and_16bit_pools(kv_dtype):
+    """KV selection with the other pool formats: the block index is the mean of the de-rotated keys AS STORED (int8 values times
+    their token scale; fp16 words), and a bounded view is selected and attended to."""
+    from dataclasses import replace
+
+    from owl_engine_b200.store import select as S
+
+    g = torch.Generator().manual_seed(5)
+    base = EngineConfig(model="test-hybrid", snap_cut=True, n_pages=128, n_slots=4, n_snap_rows=2, max_seqs=4, max_seq=512,
+                        prefill_chunk=64, kv_dtype=kv_dtype)
+    prompt = torch.randint(0, 512, (150,), generator=g).tolist()
+    eng = Engine(replace(base, kvmem_budget=96, kvmem_sink=1, kvmem_recent=2))
+    sid = eng.add_sequence(prompt)
+    eng.prefill(sid)
+    out = [eng.decode_step([sid])[0] for _ in range(8)]
+    seq = eng.seqs[sid]
+    assert seq.view is not None and len(seq.view) == 6 and all(0 <= t < eng.spec.vocab for t in out)
+    fi = eng.spec.n_full - 1
+    page = seq.pages[2]
+    if kv_dtype == "int8":
+        k = eng.pool.k_pool[fi][page].view(torch.int8).float().cpu() * eng.pool.k_scale[fi][page].cpu()[..., None]
+    else:
+        k = eng.pool.k_pool[fi][page].float().cpu()
+    inv = eng.runner.inv_freq.cpu()
+    ang = torch.arange(32, 48).float()[:, None] * inv[None]
+    want = S.mean_k_index(S.derope(k, ang.cos(), ang.sin())[None])[0]
+    assert torch.allclose(seq.meank[2].cpu(), want, atol=2e-3, rtol=1e-3)
+    eng.free_sequence(sid, publish=False)
