@@ -317,6 +317,13 @@ class HybridRunner:
         # path, while the separate norm kernel's launch is hidden by programmatic dependent launch
         self.fuse_norm = os.environ.get("OWL_FUSE_NORM", "0") == "1"
         self._norm_count = None
+        # L2 prefetch of the next projection's weights on a side branch of the step graph (MB per projection, 0 = off) and
+        # where the branch forks: "before" the current projection (concurrent with it) or "after" it (in the gap that follows)
+        self.l2_prefetch_mb = float(os.environ.get("OWL_L2_PREFETCH_MB", "0"))
+        self.l2_prefetch_at = os.environ.get("OWL_L2_PREFETCH_AT", "after")
+        self._pf_rec = None          # warm-up pass of a capture: the weight tensors in launch order
+        self._pf_play = None         # capture pass: (schedule, side stream, capture stream)
+        self._pf_i = 0
         self.prefill_gemm = prefill_gemm
         self.G = weights.group
         dev, H, M = self.device, spec.hidden, self.MAX_ROWS
@@ -387,8 +394,35 @@ class HybridRunner:
         """``group`` argument for the ActPack producers: the tile layout when the tcgen05 streaming kernel consumes it."""
         return self.G | K.ACT_TILES if self.tiles else self.G
 
+    def _pf_hook(self, w, after: bool) -> None:
+        """Weight-stream bookkeeping around a projection: the warm-up pass of a capture records the weight tensors in launch
+        order; the capture pass forks a side branch that prefetches the front of the NEXT projection's weights into L2 (the
+        last projection of a step prefetches the first one of the next step)."""
+        if self._pf_rec is not None:
+            if not after:
+                self._pf_rec.append(getattr(w, "records", None))
+            return
+        if self._pf_play is None:
+            return
+        if not after:
+            self._pf_cur, self._pf_i = self._pf_i, self._pf_i + 1
+        if after != (self.l2_prefetch_at == "after"):
+            return
+        sched, side, cur = self._pf_play
+        nxt = sched[(self._pf_cur + 1) % len(sched)]
+        if nxt is None:
+            return
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            K.l2_prefetch(nxt, int(self.l2_prefetch_mb * (1 << 20)))
+
     def _gemv(self, w, xp, xs, out, m: int, *, residual=None, epi: int = K.EPI_STORE, ldo=None, pdl: bool = False) -> None:
         """out[m] = W x on the weight-streaming kernel that matches the weight's record layout."""
+        self._pf_hook(w, False)
+        self._gemv_inner(w, xp, xs, out, m, residual=residual, epi=epi, ldo=ldo, pdl=pdl)
+        self._pf_hook(w, True)
+
+    def _gemv_inner(self, w, xp, xs, out, m: int, *, residual=None, epi: int = K.EPI_STORE, ldo=None, pdl: bool = False) -> None:
         if w.layout == "nvfp4":
             self._gemv_nvfp4(w, xp, xs, out, m, residual, epi, ldo)
             return
@@ -558,7 +592,9 @@ class HybridRunner:
         """lm_head over ``self.xn`` (the final norm is produced by the last row-parallel step) and the
         greedy sample; with a vocab-split head the per-rank winners are merged across ranks."""
         w = self.w
+        self._pf_hook(w.lm_head, False)
         K.dense_skinny(w.lm_head, self.xn, self.logits, m, pdl=self.pdl)
+        self._pf_hook(w.lm_head, True)
         if not sample:
             return
         symm = getattr(self.comm, "symm", None) if self.comm is not None else None
@@ -672,11 +708,22 @@ class HybridRunner:
             v["kv_slot"].fill_(-1)
             v["ctx"].fill_(1)
             v["bt_row"].zero_()
+            prefetch = self.l2_prefetch_mb > 0 and b * t < self.BATCH_GEMM_FROM
+            self._pf_rec = [] if prefetch else None
             self.step_forward(lay, ctx_hint=ctx_hint, advance=False, sample=sample)
+            sched, self._pf_rec = self._pf_rec, None
             stream.synchronize()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
-                self.step_forward(lay, ctx_hint=ctx_hint, advance=advance, sample=sample)
+                if prefetch and sched:
+                    side = torch.cuda.Stream(device=self.device)
+                    self._pf_play, self._pf_i = (sched, side, stream), 0
+                try:
+                    self.step_forward(lay, ctx_hint=ctx_hint, advance=advance, sample=sample)
+                finally:
+                    if self._pf_play is not None:
+                        stream.wait_stream(self._pf_play[1])       # join the prefetch branch before the capture ends
+                        self._pf_play = None
             self.inp.copy_(saved)
         torch.cuda.current_stream().wait_stream(stream)
         self.graphs[key] = graph

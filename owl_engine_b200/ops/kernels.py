@@ -179,6 +179,15 @@ def rmsnorm_pack(h, w, *, delta=None, out_h=None, normed=None, xpack=None, xs=No
          eps, int(one_plus_w), _is_f16(normed), int(pdl), stream())
 
 
+register("owl_l2_prefetch", [_P, c_longlong, _I, _P])
+
+
+def l2_prefetch(t: torch.Tensor, nbytes: int | None = None, ctas: int = 0) -> None:
+    """Ask the memory system to bring the first ``nbytes`` of ``t`` into L2 (fire and forget, current stream)."""
+    total = t.numel() * t.element_size()
+    call("owl_l2_prefetch", ptr(t), min(total, nbytes) if nbytes is not None else total, ctas, stream())
+
+
 def act_pack(x, xpack, xs, m: int, k: int, group: int = 128, ldx: int | None = None, pdl: bool = False) -> None:
     call("owl_act_pack", ptr(x), ldx if ldx is not None else k, ptr(xpack), ptr(xs), m, k, group, int(pdl), stream())
 

@@ -87,6 +87,7 @@ _T = [
     KernelSpec("owl_gdn_norm_gate", "gdn.cu", "gdn"),
     KernelSpec("owl_gdn_chunk_scan", "gdn_chunk.cu", "gdn", gen="mma.sync+cp.async"),
     KernelSpec("owl_gdn_chunk_work_bytes", "gdn_chunk.cu", "status", capture=False),
+    KernelSpec("owl_l2_prefetch", "prefetch.cu", "elem", gen="bulk-prefetch"),
     # attention / KV
     KernelSpec("owl_qknorm_rope_insert", "attn.cu", "attn"),
     KernelSpec("owl_paged_attn", "attn.cu", "attn", gen="mma.sync"),
