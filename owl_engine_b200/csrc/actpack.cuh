@@ -39,7 +39,13 @@ __device__ __forceinline__ float clamp_h(float x) { return fminf(fmaxf(x, -65504
 // Packs 8 consecutive activations. Every lane of the warp must call this; the `cpg` (4 or 16)
 // consecutive lanes that hold the chunks of one group cooperate through shuffles. Returns the
 // chunk; (sx, xsum) are valid in every lane of the group.
+// With ACT_A8 in the producer's group argument (it arrives here as bit ACT_A8 >> 3 of `cpg`) the activations are rounded to
+// 8 bits instead of 15: h = round(x * 127 / amax), l = 0 and sx = amax / (127 * 128), so every consumer reads the same
+// format and the W4A8 arm of the streaming kernel may skip the low plane.
+constexpr int ACT_A8 = 0x2000;
 __device__ __forceinline__ uint4 actpack_emit(const float* v, int cpg, float& sx, float& xsum) {
+  const bool a8 = (cpg & (ACT_A8 >> 3)) != 0;
+  cpg &= (ACT_A8 >> 3) - 1;
   float pb[4], pl[4];   // pl: activations of the low nibbles, pb: of the high nibbles
   const int klo[4] = {0, 4, 1, 5}, khi[4] = {2, 6, 3, 7};
   float amax = 0.f;
@@ -54,6 +60,22 @@ __device__ __forceinline__ uint4 actpack_emit(const float* v, int cpg, float& sx
   for (int o = cpg >> 1; o > 0; o >>= 1) {
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     xsum += __shfl_xor_sync(0xffffffffu, xsum, o);
+  }
+  if (a8) {
+    const float s8 = fmaxf(amax, 1e-30f) * (1.f / 127.f), inv8 = 1.f / s8;
+    uint32_t hb8 = 0, hl8 = 0;
+    int qsum = 0;
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const int qb = __float2int_rn(pb[b] * inv8), ql = __float2int_rn(pl[b] * inv8);
+      hb8 |= (uint32_t)(qb & 0xff) << (8 * b);
+      hl8 |= (uint32_t)(ql & 0xff) << (8 * b);
+      qsum += qb + ql;
+    }
+    for (int o = cpg >> 1; o > 0; o >>= 1) qsum += __shfl_xor_sync(0xffffffffu, qsum, o);
+    xsum = s8 * (float)qsum;      // the zero-point term uses the ROUNDED activations: the product is exact for them
+    sx = s8 * (1.f / 128.f);
+    return make_uint4(hl8, 0u, hb8, 0u);
   }
   sx = fmaxf(amax, 1e-30f) * (1.f / ACT_QMAX);
   const float inv = 1.f / sx;
@@ -84,13 +106,14 @@ __host__ __device__ constexpr int actpack_tile_bytes(int G) { return 2048 + 64 *
 
 // Group argument check of the producers' launchers: 32 / 128, optionally | ACT_TILES.
 inline bool actpack_group_ok(int G, int tokens) {
-  const int g = G & ~ACT_TILES;
+  const int g = G & ~(ACT_TILES | 0x2000);       // 0x2000: ACT_A8
   (void)tokens;
   return g == 32 || g == 128;
 }
 
 __device__ __forceinline__ void actpack_store(uint4* xpack, float2* xs, int tiles, int G, int token, int c8, int nchunks,
                                               const uint4& pk, float sx, float xsum) {
+  G &= ~ACT_A8;
   const int cpg = G >> 3;
   if (!tiles) {
     xpack[(size_t)token * nchunks + c8] = pk;

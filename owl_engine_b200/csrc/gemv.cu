@@ -114,6 +114,7 @@ struct SkinnyParams {
   int tiles_per_cta;     // contiguous row tiles per CTA
   int gout;              // EPI_SILU_PACK: group size of the produced ActPack (32 or 128)
   int force_mma;         // tests / A-B runs: use the tensor-core arm even for one token
+  int a8;                // activations were packed with ACT_A8 (low plane all zero): skip its products (W4A8 arm)
   // EPI_PUSH (tensor parallel, row-parallel projection): the partial sums go straight into every rank's
   // reduction buffer (plain peer stores over NVLink), slot [rank] of [world][push_rows][ldo] bf16, so the
   // transfer overlaps the streaming tile by tile; the CTA that finishes last publishes one sequence number per
@@ -167,7 +168,7 @@ __device__ __forceinline__ void mma_f16_16816_z(float* c, uint32_t a0, uint32_t 
 // warp-level tensor-core path. On sm_100 the legacy mma.sync path issues one m16n8k16/k32 MMA per
 // ~34 cycles per SM sub-core, which caps a W4 stream at ~4 TB/s (8 MMAs per 1088-byte record
 // whatever the token count); for one token 32 dp4a per lane per record are cheaper than that.
-template <int MT, int KIND, bool SIMT>
+template <int MT, int KIND, bool SIMT, bool A8>
 __global__ void __launch_bounds__(SK_WARPS * 32, MT == 1 ? 4 : 2) skinny_stream_kernel(SkinnyParams p, int epi) {
   constexpr int REC = RecInfo<KIND>::BYTES, KREC = RecInfo<KIND>::KREC;
   constexpr bool W4 = KIND == KIND_W4_G128 || KIND == KIND_W4_G32;
@@ -295,11 +296,20 @@ __global__ void __launch_bounds__(SK_WARPS * 32, MT == 1 ? 4 : 2) skinny_stream_
           for (int q = 0; q < GPT; ++q) {
             int h0 = 0, l0 = 0, h1 = 0, l1 = 0;
 #pragma unroll
-            for (int w = (G == 128 ? 0 : q); w < (G == 128 ? 4 : q + 1); ++w) {
-              h0 = dp4a_us(nl[w], xb[0][w].x, h0); l0 = dp4a_uu(nl[w], xb[0][w].y, l0);
-              h0 = dp4a_us(ul[w], xb[0][w].z, h0); l0 = dp4a_uu(ul[w], xb[0][w].w, l0);
-              h1 = dp4a_us(nh[w], xb[0][w].x, h1); l1 = dp4a_uu(nh[w], xb[0][w].y, l1);
-              h1 = dp4a_us(uh[w], xb[0][w].z, h1); l1 = dp4a_uu(uh[w], xb[0][w].w, l1);
+            if (A8) {      // 8-bit activations: the low plane is zero, half the products
+#pragma unroll
+              for (int w = (G == 128 ? 0 : q); w < (G == 128 ? 4 : q + 1); ++w) {
+                h0 = dp4a_us(nl[w], xb[0][w].x, h0); h0 = dp4a_us(ul[w], xb[0][w].z, h0);
+                h1 = dp4a_us(nh[w], xb[0][w].x, h1); h1 = dp4a_us(uh[w], xb[0][w].z, h1);
+              }
+            } else {
+#pragma unroll
+              for (int w = (G == 128 ? 0 : q); w < (G == 128 ? 4 : q + 1); ++w) {
+                h0 = dp4a_us(nl[w], xb[0][w].x, h0); l0 = dp4a_uu(nl[w], xb[0][w].y, l0);
+                h0 = dp4a_us(ul[w], xb[0][w].z, h0); l0 = dp4a_uu(ul[w], xb[0][w].w, l0);
+                h1 = dp4a_us(nh[w], xb[0][w].x, h1); l1 = dp4a_uu(nh[w], xb[0][w].y, l1);
+                h1 = dp4a_us(uh[w], xb[0][w].z, h1); l1 = dp4a_uu(uh[w], xb[0][w].w, l1);
+              }
             }
             const __half2 hh0 = *reinterpret_cast<const __half2*>(&su0[q]);
             const __half2 hh1 = *reinterpret_cast<const __half2*>(&su1[q]);
@@ -316,9 +326,11 @@ __global__ void __launch_bounds__(SK_WARPS * 32, MT == 1 ? 4 : 2) skinny_stream_
 #pragma unroll
             for (int i = 0; i < 2; ++i) {   // one k32-byte MMA covers words 2i and 2i+1
               imma_u8s8(ch, nl[2 * i], nh[2 * i], nl[2 * i + 1], nh[2 * i + 1], xb[m][2 * i].x, xb[m][2 * i + 1].x);
-              imma_u8u8(cl, nl[2 * i], nh[2 * i], nl[2 * i + 1], nh[2 * i + 1], xb[m][2 * i].y, xb[m][2 * i + 1].y);
               imma_u8s8(ch, ul[2 * i], uh[2 * i], ul[2 * i + 1], uh[2 * i + 1], xb[m][2 * i].z, xb[m][2 * i + 1].z);
-              imma_u8u8(cl, ul[2 * i], uh[2 * i], ul[2 * i + 1], uh[2 * i + 1], xb[m][2 * i].w, xb[m][2 * i + 1].w);
+              if (!A8) {
+                imma_u8u8(cl, nl[2 * i], nh[2 * i], nl[2 * i + 1], nh[2 * i + 1], xb[m][2 * i].y, xb[m][2 * i + 1].y);
+                imma_u8u8(cl, ul[2 * i], uh[2 * i], ul[2 * i + 1], uh[2 * i + 1], xb[m][2 * i].w, xb[m][2 * i + 1].w);
+              }
             }
             const __half2 h0 = *reinterpret_cast<const __half2*>(&su0[0]);
             const __half2 h1 = *reinterpret_cast<const __half2*>(&su1[0]);
@@ -343,9 +355,11 @@ __global__ void __launch_bounds__(SK_WARPS * 32, MT == 1 ? 4 : 2) skinny_stream_
             for (int m = 0; m < MT; ++m) {
               int ch[4] = {0, 0, 0, 0}, cl[4] = {0, 0, 0, 0};
               imma_u8s8(ch, nl[q], nh[q], 0u, 0u, xb[m][q].x, 0u);
-              imma_u8u8(cl, nl[q], nh[q], 0u, 0u, xb[m][q].y, 0u);
               imma_u8s8(ch, ul[q], uh[q], 0u, 0u, xb[m][q].z, 0u);
-              imma_u8u8(cl, ul[q], uh[q], 0u, 0u, xb[m][q].w, 0u);
+              if (!A8) {
+                imma_u8u8(cl, nl[q], nh[q], 0u, 0u, xb[m][q].y, 0u);
+                imma_u8u8(cl, ul[q], uh[q], 0u, 0u, xb[m][q].w, 0u);
+              }
               const float f0 = (float)(ch[0] * 128 + cl[0]), f1 = (float)(ch[1] * 128 + cl[1]);
               const float f2 = (float)(ch[2] * 128 + cl[2]), f3 = (float)(ch[3] * 128 + cl[3]);
               acc[m][0] = fmaf(sc0, fmaf(sa[m][q].x, f0, -z0 * sa[m][q].y), acc[m][0]);
@@ -584,9 +598,9 @@ __global__ void __launch_bounds__(SK_WARPS * 32, MT == 1 ? 4 : 2) skinny_stream_
   pdl_launch_dependents();
 }
 
-template <int MT, int KIND, bool SIMT = false>
+template <int MT, int KIND, bool SIMT = false, bool A8 = false>
 static int launch_skinny(const SkinnyParams& p, int epi, int pdl, cudaStream_t st) {
-  auto kernel = skinny_stream_kernel<MT, KIND, SIMT>;
+  auto kernel = skinny_stream_kernel<MT, KIND, SIMT, A8>;
   constexpr int smem = skinny_smem_bytes<MT, KIND>();
   static bool attr_done = false;
   if (!attr_done) {
@@ -622,6 +636,14 @@ template <int KIND>
 static int dispatch_mt(const SkinnyParams& p, int epi, int pdl, cudaStream_t st) {
   const int mt = (p.M + 7) / 8;
   constexpr bool W4K = KIND == KIND_W4_G128 || KIND == KIND_W4_G32;
+  if constexpr (W4K) {
+    if (p.a8) {      // W4A8 arm: its own instantiations, so the 15-bit kernels keep their code
+      if (p.M == 1 && !p.force_mma) return launch_skinny<1, KIND, true, true>(p, epi, pdl, st);
+      if (mt == 1) return launch_skinny<1, KIND, false, true>(p, epi, pdl, st);
+      if (mt == 2) return launch_skinny<2, KIND, false, true>(p, epi, pdl, st);
+      return launch_skinny<4, KIND, false, true>(p, epi, pdl, st);
+    }
+  }
   if (W4K && p.M == 1 && !p.force_mma) return launch_skinny<1, KIND, W4K>(p, epi, pdl, st);
   if (mt == 1) return launch_skinny<1, KIND>(p, epi, pdl, st);
   if (mt == 2) return launch_skinny<2, KIND>(p, epi, pdl, st);
@@ -649,6 +671,20 @@ OWL_API int owl_w4a16_skinny(const void* records, const void* xpack, const void*
   p.n_tiles = N / 16;
   p.force_mma = (tiles_per_cta < 0);
   p.tiles_per_cta = pick_tiles_per_cta(p.n_tiles, epi, tiles_per_cta < 0 ? -tiles_per_cta - 1 : tiles_per_cta);
+  return group == 128 ? dispatch_mt<KIND_W4_G128>(p, epi, pdl, st) : dispatch_mt<KIND_W4_G32>(p, epi, pdl, st);
+}
+
+// W4A8 arm: the same launch for activations packed with ACT_A8 (8-bit, low plane zero): half the integer products.
+OWL_API int owl_w4a16_skinny_a8(const void* records, const void* xpack, const void* xsums, void* out, const void* residual,
+                                int M, int N, int K, int ldo, int group, int epi, int force_mma, int pdl, cudaStream_t st) {
+  if (M < 1 || M > 32 || (N & 15) || (K & 127) || (group != 32 && group != 128) || !out) return OWL_ERR_BAD_ARG;
+  if (epi != EPI_STORE && epi != EPI_RESIDUAL && epi != EPI_SILU_MUL && epi != EPI_F32) return OWL_ERR_BAD_ARG;
+  if (epi == EPI_RESIDUAL && !residual) return OWL_ERR_BAD_ARG;
+  SkinnyParams p = {};
+  p.w = (const uint8_t*)records; p.x = (const uint4*)xpack; p.xs = (const float2*)xsums;
+  p.out = out; p.residual = (const __nv_bfloat16*)residual;
+  p.M = M; p.N = N; p.K = K; p.ldo = ldo; p.n_tiles = N / 16; p.force_mma = force_mma; p.a8 = 1;
+  p.tiles_per_cta = pick_tiles_per_cta(p.n_tiles, epi, 0);
   return group == 128 ? dispatch_mt<KIND_W4_G128>(p, epi, pdl, st) : dispatch_mt<KIND_W4_G32>(p, epi, pdl, st);
 }
 

@@ -40,6 +40,7 @@ class EngineConfig:
     prefill_chunk: int = 2048
     pdl: bool = True
     prefill_gemm: str = "tc"
+    act_bits: int = 15             # decode activations: 15-bit fixed point, or 8 (the W4A8 decode arm, `[model] quant = "w4a8"`)
     decode_gemv: str = "dp4a"      # W4 decode arm: "dp4a" (legacy streaming kernels) or "tc" (tcgen05 streaming kernel)
     seed: int = 0
     n_layers: int | None = None    # override (tests / smoke)
@@ -100,6 +101,9 @@ class Engine:
         self.runner = H.HybridRunner(self.spec, self.weights, self.pool, max_seqs=cfg.max_seqs * (2 if cfg.kvmem_budget else 1),
                                      max_blocks=self.max_blocks, prefill_chunk=cfg.prefill_chunk, comm=comm,
                                      pdl=cfg.pdl, prefill_gemm=cfg.prefill_gemm)
+        if cfg.act_bits != 15:
+            assert cfg.act_bits == 8, "act_bits is 15 or 8"
+            self.runner.act_bits = 8
         self.kv = KvStore(cfg.n_pages, PAGE)
         self.states = StateStore(cfg.n_slots, cfg.n_snap_rows)
         self.host = HostTier(page_bytes(self.pool), cfg.host_cache_mb << 20) if cfg.host_cache_mb else None

@@ -317,6 +317,9 @@ class HybridRunner:
         # path, while the separate norm kernel's launch is hidden by programmatic dependent launch
         self.fuse_norm = os.environ.get("OWL_FUSE_NORM", "0") == "1"
         self._norm_count = None
+        # decode activations: 15-bit fixed point (exact for bf16 inputs up to rounding at 2^-14 of the group maximum), or 8
+        # bits per group (the W4A8 decode arm: half the integer products per weight byte)
+        self.act_bits = int(os.environ.get("OWL_ACT_BITS", "15"))
         # L2 prefetch of the next projection's weights on a side branch of the step graph (MB per projection, 0 = off) and
         # where the branch forks: "before" the current projection (concurrent with it) or "after" it (in the gap that follows)
         self.l2_prefetch_mb = float(os.environ.get("OWL_L2_PREFETCH_MB", "0"))
@@ -392,7 +395,8 @@ class HybridRunner:
     # -- building blocks ---------------------------------------------------------------------
     def _grp(self) -> int:
         """``group`` argument for the ActPack producers: the tile layout when the tcgen05 streaming kernel consumes it."""
-        return self.G | K.ACT_TILES if self.tiles else self.G
+        g = (self.G | K.ACT_TILES) if self.tiles else self.G
+        return g | K.ACT_A8 if self.act_bits == 8 else g
 
     def _pf_hook(self, w, after: bool) -> None:
         """Weight-stream bookkeeping around a projection: the warm-up pass of a capture records the weight tensors in launch
@@ -432,7 +436,8 @@ class HybridRunner:
             return
         if w.layout != "block":
             K.w4a16_skinny(w, xp, xs, out, m, residual=residual, epi=epi, ldo=ldo, pdl=pdl,
-                           force_mma=self.uniform_rows and m == 1)
+                           force_mma=self.uniform_rows and m == 1,
+                           a8=self.act_bits == 8 and epi in (K.EPI_STORE, K.EPI_RESIDUAL, K.EPI_SILU_MUL, K.EPI_F32))
             return
         tb = K.act_tile_bytes(w.k, w.group)
         for r0 in range(0, m, 8):       # 8 tokens per pass (one activation tile buffer each)

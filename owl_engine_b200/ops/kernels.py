@@ -19,6 +19,7 @@ _F = c_float
 
 _SIGS = {
     "owl_w4a16_skinny": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "owl_w4a16_skinny_a8": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "owl_w4a16_skinny_norm": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
     "owl_w4a16_stream_tc": [_P, _P, _P, _P, _P, c_longlong, _P, c_longlong, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "owl_bf16_skinny": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
@@ -84,12 +85,17 @@ EPI_STORE, EPI_RESIDUAL, EPI_SILU_MUL, EPI_F32, EPI_SILU_PACK = 0, 1, 2, 3, 4
 
 def w4a16_skinny(w, xpack, xs, out, m: int, *, residual=None, epi: int = EPI_STORE, ldo: int | None = None,
                  out_pack=None, out_xs=None, gout: int = 128, tiles_per_cta: int = 0, pdl: bool = False,
-                 force_mma: bool = False) -> None:
+                 force_mma: bool = False, a8: bool = False) -> None:
     """out[m, :] = dequant(w) @ x for m <= 32 rows. ``w`` is a ``W4Skinny``. One token runs on the
-    dp4a arm unless ``force_mma`` (A/B runs and tests of the tensor-core arm)."""
+    dp4a arm unless ``force_mma`` (A/B runs and tests of the tensor-core arm). ``a8``: the activations were packed with
+    ``ACT_A8`` (8-bit), the kernel skips the all-zero low plane (the W4A8 arm)."""
     if ldo is None:
         ldo = out.shape[-1] if out is not None else w.n
     assert w.layout == "slice", "w4a16_skinny reads slice-major records"
+    if a8:
+        call("owl_w4a16_skinny_a8", ptr(w.records), ptr(xpack), ptr(xs), ptr(out), ptr(residual), m, w.n, w.k, ldo, w.group,
+             epi, int(force_mma), int(pdl), stream())
+        return
     if force_mma:
         tiles_per_cta = -tiles_per_cta - 1
     call("owl_w4a16_skinny", ptr(w.records), ptr(xpack), ptr(xs), ptr(out), ptr(residual), ptr(out_pack), ptr(out_xs),
@@ -123,6 +129,7 @@ class StreamTcWorkspace:
 
 
 ACT_TILES = 0x1000     # OR into a producer's ``group`` argument: write ActPack in the tile layout
+ACT_A8 = 0x2000        # OR into a producer's ``group`` argument: round the activations to 8 bits (low plane zero)
 
 
 def act_tile_bytes(k: int, group: int) -> int:

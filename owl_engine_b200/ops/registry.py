@@ -35,6 +35,7 @@ _T = [
     # weight streaming / GEMM
     KernelSpec("owl_w4a16_skinny", "gemv.cu", "gemv", gen="dp4a+mma.sync+bulk-copy"),
     KernelSpec("owl_w4a16_skinny_norm", "gemv.cu", "gemv", gen="dp4a+mma.sync+bulk-copy"),
+    KernelSpec("owl_w4a16_skinny_a8", "gemv.cu", "gemv", gen="dp4a+mma.sync+bulk-copy"),
     KernelSpec("owl_bf16_skinny", "gemv.cu", "gemv", gen="mma.sync+bulk-copy"),
     KernelSpec("owl_w8a16_skinny", "gemv.cu", "gemv", gen="mma.sync+bulk-copy"),
     KernelSpec("owl_skinny_status", "gemv.cu", "status", capture=False),

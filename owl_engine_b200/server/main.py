@@ -34,6 +34,7 @@ def build_engine_factory(cfg: C.OwlConfig):
         km = v["kvmem"]
         ecfg = EngineConfig(model=v["model"]["name"], group=v["model"]["group"],
                             quant="nvfp4" if v["model"]["quant"] == "nvfp4" else "w4a16",
+                            act_bits=8 if v["model"]["quant"] == "w4a8" else 15,
                             kvmem_budget=km["workspace_per_req"] if km["select_decode"] else 0,
                             kvmem_sink=km["select_sink"], kvmem_recent=km["select_recent"],
                             lm_head_int8=v["model"]["head_quant"] != "bf16",

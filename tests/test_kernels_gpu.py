@@ -65,6 +65,39 @@ def test_w4a16_skinny(m, group, shape):
     assert err < 5e-3, err
 
 
+@pytest.mark.parametrize("m,group", [(1, 128), (1, 32), (5, 128), (20, 32)])
+def test_w4a8_arm_skips_the_low_plane(m, group):
+    """Activations packed with ACT_A8 are 8-bit (low plane zero, same container): the W4A8 arm, which skips the low-plane
+    products, equals the full kernel on the same pack bit for bit, and both match the fp32 product of the dequantised weights
+    with the 8-bit activations."""
+    n, k = 512, 1024
+    c = Q.quantize_w4(torch.randn(n, k, generator=gen(70)) * 0.05, group)
+    s = Q.pack_skinny(c).to(DEV)
+    x = bf(torch.randn(m, k, generator=gen(71)))
+    xp = torch.empty(m, 2 * k, dtype=torch.uint8, device=DEV)
+    xs = torch.empty(m, k // group, 2, dtype=torch.float32, device=DEV)
+    K.act_pack(x.to(DEV), xp, xs, m, k, group | K.ACT_A8)
+    planes = xp.view(m, k // 8, 16).cpu()
+    assert int(planes[:, :, 4:8].max()) == 0 and int(planes[:, :, 12:16].max()) == 0        # low planes
+    full = torch.zeros(m, n, dtype=torch.bfloat16, device=DEV)
+    a8 = torch.zeros_like(full)
+    K.w4a16_skinny(s, xp, xs, full, m)
+    K.w4a16_skinny(s, xp, xs, a8, m, a8=True)
+    assert torch.equal(full, a8)
+    if m == 1:
+        mm = torch.zeros_like(full)
+        K.w4a16_skinny(s, xp, xs, mm, m, a8=True, force_mma=True)
+        torch.testing.assert_close(mm.float(), a8.float(), rtol=1e-2, atol=1e-3)
+    xg = x.float().view(m, k // group, group)
+    sc = xg.abs().amax(-1, keepdim=True).clamp_min(1e-30) / 127.0
+    x8 = (torch.round(xg / sc).clamp(-127, 127) * sc).view(m, k)
+    want = x8 @ c.dequant().t()
+    err = (a8.float().cpu() - want).norm() / want.norm()
+    assert err < 5e-3, err
+    exact = x.float() @ c.dequant().t()
+    assert (a8.float().cpu() - exact).norm() / exact.norm() < 2e-2       # 8-bit activations: ~1 % of the product's norm
+
+
 @pytest.mark.parametrize("ks", [1, 2, 4, 8])
 def test_w4a16_skinny_splitk_and_epilogues(ks):
     m, n, k, group = 2, 128, 2048, 128

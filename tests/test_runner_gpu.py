@@ -140,6 +140,39 @@ def test_sequence_parallel_prefill_protocol_on_one_gpu():
     assert rel_err(outs[0][0], hr[-1:]) < 0.05
 
 
+def test_w4a8_decode_arm_tracks_the_reference():
+    """8-bit decode activations (``act_bits = 8``): greedy decode steps stay close to the fp32 model (looser than the 15-bit
+    arm), eager and captured."""
+    spec, run, ref = build("tc")
+    run.act_bits = 8
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, spec.vocab, (37,), generator=g)
+    seq_row, slot = 1, 2
+    run.block_table[seq_row, :8] = torch.tensor([5, 9, 2, 30, 11, 12, 13, 14], dtype=torch.int32, device=DEV)
+    run.prefill_chunk_forward(prompt.to(torch.int32).to(DEV), 0, seq_row, slot)
+    st = ref.new_state()
+    want = ref.logits(ref.forward(prompt, st)[-1:])
+    lay = H.StepLayout(1, 1)
+    v = run.views(lay)
+    nxt = int(want.argmax(-1))
+    for step in range(4):
+        pos = 37 + step
+        v["ids"][0] = nxt
+        v["pos3"][:] = pos
+        v["kv_slot"][0] = int(run.block_table[seq_row, pos // 16]) * 16 + pos % 16
+        v["ctx"][0] = pos + 1
+        v["gslot"][0] = slot
+        v["bt_row"][0] = seq_row
+        if step < 2:
+            run.step_forward(lay, ctx_hint=64)
+        else:
+            run.capture(1, 1, ctx_hint=64).replay()
+        torch.cuda.synchronize()
+        want = ref.logits(ref.forward(torch.tensor([nxt]), st))
+        assert rel_err(run.logits[:1].float().cpu(), want) < 0.12, step
+        nxt = int(want.argmax(-1))
+
+
 @pytest.mark.parametrize("kv_dtype", ["int8", "bf16"])
 def test_int8_and_16bit_kv_pools_match_reference(kv_dtype):
     """int8 KV pool (per token, per head scales) and the 16-bit pool (fp16 words holding bf16-rounded values): prefill in two
