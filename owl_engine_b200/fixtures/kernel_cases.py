@@ -2,7 +2,7 @@
 L2 but well under a few GB, then exits.
 
 ``python -m owl_engine_b200.fixtures.kernel_cases <case>`` with case in
-``gemm16 gemm8 gemm_w4 gemv attn gdn_decode gdn_scan dflash_attn`` (prints the CUDA-event time per launch).
+``gemm16 gemm8 gemm_w4 gemv attn attn16 gdn_decode gdn_scan dflash_attn`` (prints the CUDA-event time per launch).
 """
 import math
 import sys
@@ -71,11 +71,15 @@ def gemv():
     return ms, f"{ws[0].records.numel() / ms / 1e9:.2f} TB/s"
 
 
-def attn():
+def attn(kv16: bool = False):
     hq, hkv, hd, ctx, b = 24, 4, 256, 32768, 4                              # 4 sequences x 32k tokens: 268 MB of fp8 KV
     pages = b * ctx // 16
-    kp = torch.randint(0, 120, (pages, 16, hkv, hd), dtype=torch.uint8, device=dev)
-    vp = torch.randint(0, 120, (pages, 16, hkv, hd), dtype=torch.uint8, device=dev)
+    if kv16:                                                                # the 16-bit pool: 537 MB of fp16 words
+        kp = torch.randn(pages, 16, hkv, hd, device=dev).half()
+        vp = torch.randn(pages, 16, hkv, hd, device=dev).half()
+    else:
+        kp = torch.randint(0, 120, (pages, 16, hkv, hd), dtype=torch.uint8, device=dev)
+        vp = torch.randint(0, 120, (pages, 16, hkv, hd), dtype=torch.uint8, device=dev)
     bt = torch.arange(pages, dtype=torch.int32, device=dev).view(b, -1).contiguous()
     q = torch.randn(b, hq, hd, device=dev).bfloat16()
     splits = 32
@@ -84,7 +88,11 @@ def attn():
     ctxs = torch.full((b,), ctx, dtype=torch.int32, device=dev)
     rows = torch.arange(b, dtype=torch.int32, device=dev)
     ms = timed(lambda: K.paged_attn(q, kp, vp, bt, rows, ctxs, po, pml, b, 1, hq, hkv, hd, bt.shape[1], splits, 1 / math.sqrt(hd)))
-    return ms, f"{2 * kp.numel() / ms / 1e9:.2f} TB/s of KV"
+    return ms, f"{2 * kp.numel() * kp.element_size() / ms / 1e9:.2f} TB/s of KV"
+
+
+def attn16():
+    return attn(True)
 
 
 def gdn_decode():
