@@ -93,3 +93,55 @@ def test_http_surface():
             st, _, _ = await request(port, "GET", "/nope")
             assert st == 404
     asyncio.run(main())
+
+
+def test_owl_evict_marks_become_droppable_spans_and_refusals_are_400():
+    """An image part with ``owl_evict: true`` reaches the engine as a token span that covers the image's pad run and its
+    vision-start / vision-end markers; an engine that refuses the marks (image_evict off) yields a 400 with the reason."""
+    import base64
+
+    from owl_engine_b200.cli import png
+    from owl_engine_b200.models import vision as V
+    from owl_engine_b200.server.http import Vision
+
+    class Recorder(FakeClient):
+        def __init__(self, tok, script, refuse=False):
+            super().__init__(tok, script)
+            self.seen, self.refuse = [], refuse
+
+        def chat(self, tokens, opts):
+            if self.refuse and opts.evict_spans:
+                raise ValueError("rejected: segments are marked droppable (owl_evict) but image_evict is off in this profile")
+            self.seen.append((list(tokens), opts))
+            return super().chat(tokens, opts)
+
+    async def main():
+        tok = ByteTokenizer()
+        vis = Vision(V.VisionTower(V.tiny_vision(out_hidden=64)), tok.image_pad_id)
+        url = "data:image/png;base64," + base64.b64encode(png.encode_png(96, 64, png.RED)).decode()
+        body = {"model": "m", "max_tokens": 4, "messages": [{"role": "user", "content": [
+            {"type": "text", "text": "look"}, {"type": "image_url", "image_url": {"url": url}, "owl_evict": True},
+            {"type": "image_url", "image_url": {"url": url}}, {"type": "text", "text": "done"}]}]}
+        out = {}
+        for name, refuse in (("ok", False), ("refused", True)):
+            client = Recorder(tok, "hi", refuse)
+            app = App(client, tok, "test-model", vision=vis)
+            server = await serve(app, "127.0.0.1", 0)
+            port = server.sockets[0].getsockname()[1]
+            out[name] = (await request(port, "POST", "/v1/chat/completions", body), client)
+            server.close()
+            await server.wait_closed()
+        return out
+
+    out = asyncio.run(main())
+    (code, _, payload), client = out["ok"]
+    assert code == 200, payload
+    tokens, opts = client.seen[0]
+    tok = ByteTokenizer()
+    assert len(opts.images) == 2 and len(opts.evict_spans) == 1                  # only the marked image is droppable
+    lo, hi = opts.evict_spans[0]
+    n = opts.images[0][0].shape[0]
+    assert hi - lo == n + 2 and tokens[lo] == tok.special_ids["<|vision_start|>"] and tokens[hi - 1] == tok.special_ids["<|vision_end|>"]
+    assert tokens[lo + 1:hi - 1] == [tok.image_pad_id] * n and opts.image_pad_id == tok.image_pad_id
+    (code, _, payload), _ = out["refused"]
+    assert code == 400 and b"image_evict" in payload
