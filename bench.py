@@ -123,7 +123,9 @@ def main() -> None:
     warmup = max(3, args.warmup)
     steps = args.steps
 
-    cfg = EngineConfig(model="qwen3.8-27b", group=128, n_pages=1024, n_slots=2, max_seqs=2,
+    # pages for the warm-up prompt and the timed prompt side by side, plus the generated tokens
+    n_pages = max(1024, 2 * (args.prompt_len + 2 * (warmup + steps) + 64) // 16 + 64)
+    cfg = EngineConfig(model="qwen3.8-27b", group=128, n_pages=n_pages, n_slots=2, max_seqs=2,
                        max_seq=args.prompt_len + 2 * (warmup + steps) + 64, n_layers=args.layers,
                        decode_gemv=args.gemv, prefill_gemm=args.prefill_gemm, lm_head_int8=args.head == "int8")
     eng = Engine(cfg, comm=comm)
