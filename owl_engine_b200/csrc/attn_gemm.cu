@@ -1,0 +1,137 @@
+// Helpers of the GEMM-form prefill attention (long prompts): the two contractions of causal attention run as tcgen05 GEMMs
+// (gemm_dense.cu), these kernels do what lies between them.
+//
+//   owl_kv_gather       paged K / V of one sequence and layer (e4m3, int8 + scales, or fp16 words)
+//                         -> K  bf16 [hkv][ctx_pad][hd]   (rows = keys: the B operand of S = Q K^T, k-major)
+//                            Vt fp16 [hkv][hd][ctx_pad]   (rows = dims: the B operand of O = P V,   k-major)
+//                       ctx_pad is a multiple of 64; the padding columns / rows are written as zeros
+//   owl_causal_softmax  S fp16 [rows][ld] -> P fp16 in place: row r sees keys < pos0 + r + 1, softmax(scale * s), zeros elsewhere
+//
+// Role in the reference: the FlashInfer prefill kernels of crates/kernels/cu/attn (fused form); on this part the tensor cores
+// are reached through tcgen05 GEMMs, and below a few thousand keys the fused warp-level kernel of attn.cu stays in use.
+#include <cuda_fp8.h>
+#include "common.cuh"
+
+namespace owl {
+
+constexpr int AG_PAGE = 16;
+
+template <int FMT>   // 0 e4m3, 1 int8 (+ scale), 2 fp16 words
+__device__ __forceinline__ float ag_elem(const uint8_t* row, int d) {
+  if (FMT == 2) return __half2float(reinterpret_cast<const __half*>(row)[d]);
+  if (FMT == 1) return (float)reinterpret_cast<const int8_t*>(row)[d];
+  __nv_fp8_e4m3 v;
+  v.__x = row[d];
+  return (float)v;
+}
+
+// grid (ctx_pad / 16, hkv), block 256 = 16 tokens x 16 lanes of 16 dims (hd = 256). The V tile goes through shared memory so
+// that both the pool reads and the transposed stores are contiguous.
+template <int FMT>
+__global__ void __launch_bounds__(256) kv_gather_kernel(const uint8_t* __restrict__ k_pool, const uint8_t* __restrict__ v_pool,
+                                                        const float* __restrict__ k_scale, const float* __restrict__ v_scale,
+                                                        const int* __restrict__ bt, int ctx, int ctx_pad, int hkv,
+                                                        __nv_bfloat16* __restrict__ kout, __half* __restrict__ vt) {
+  constexpr int HD = 256, ESZ = FMT == 2 ? 2 : 1;
+  __shared__ __half vs[16][HD + 2];
+  const int pg = blockIdx.x, h = blockIdx.y, tok = threadIdx.x >> 4, l16 = threadIdx.x & 15;
+  const int key = pg * AG_PAGE + tok;
+  const bool live = key < ctx;
+  const int page = live ? bt[pg] : 0;
+  const size_t slot = (size_t)page * AG_PAGE + tok;
+  const uint8_t* kp = k_pool + (slot * hkv + h) * HD * ESZ;
+  const uint8_t* vp = v_pool + (slot * hkv + h) * HD * ESZ;
+  const float ks = (FMT == 1 && live) ? k_scale[slot * hkv + h] : 1.f;
+  const float vsc = (FMT == 1 && live) ? v_scale[slot * hkv + h] : 1.f;
+  __nv_bfloat16* ko = kout + ((size_t)h * ctx_pad + key) * HD;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int d = l16 * 16 + i;
+    ko[d] = __float2bfloat16(live ? ag_elem<FMT>(kp, d) * ks : 0.f);
+    vs[tok][d] = __float2half_rn(live ? ag_elem<FMT>(vp, d) * vsc : 0.f);
+  }
+  __syncthreads();
+  // transposed store: thread -> (dim, 16 consecutive keys)
+  const int d = threadIdx.x;
+  __half* vo = vt + ((size_t)h * HD + d) * ctx_pad + (size_t)pg * AG_PAGE;
+  __align__(16) __half tmp[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) tmp[i] = vs[i][d];
+  reinterpret_cast<uint4*>(vo)[0] = reinterpret_cast<const uint4*>(tmp)[0];
+  reinterpret_cast<uint4*>(vo)[1] = reinterpret_cast<const uint4*>(tmp)[1];
+}
+
+// one CTA (256 threads) per score row; three passes over the row (max, sum, write)
+__global__ void __launch_bounds__(256) causal_softmax_kernel(__half* __restrict__ s, int ld, int ncols, int pos0, float scale_log2) {
+  __shared__ float red[32];
+  const int r = blockIdx.x;
+  __half* row = s + (size_t)r * ld;
+  const int limit = min(pos0 + r + 1, ncols);
+  float mx = -INFINITY;
+  for (int c = threadIdx.x; c < limit; c += blockDim.x) mx = fmaxf(mx, __half2float(row[c]));
+  mx = block_max(mx, red);
+  float sum = 0.f;
+  for (int c = threadIdx.x; c < limit; c += blockDim.x) sum += exp2f((__half2float(row[c]) - mx) * scale_log2);
+  sum = block_sum(sum, red);
+  const float inv = 1.f / sum;
+  for (int c = threadIdx.x; c < ncols; c += blockDim.x)
+    row[c] = __float2half_rn(c < limit ? exp2f((__half2float(row[c]) - mx) * scale_log2) * inv : 0.f);
+}
+
+// y = o * sigmoid(gate): o bf16 [rows][HD], gate from the q projection output ([q_h | gate_h] per head, row stride ldq); y bf16 or
+// fp16 [rows][HD]. grid (HD / 8 / 256 rounded up, rows).
+__global__ void __launch_bounds__(256) attn_gate_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ qraw,
+                                                        int ldq, int D, void* __restrict__ out, int HD, int out_f16) {
+  const int row = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= (HD >> 3)) return;
+  const int e = c * 8, head = e / D, off = e % D;
+  const uint4 a = reinterpret_cast<const uint4*>(o + (size_t)row * HD)[c];
+  const uint4 g = *reinterpret_cast<const uint4*>(qraw + (size_t)row * ldq + (size_t)head * 2 * D + D + off);
+  const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
+  uint32_t r[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float y0 = bf16_lo(aw[i]) / (1.f + __expf(-bf16_lo(gw[i]))), y1 = bf16_hi(aw[i]) / (1.f + __expf(-bf16_hi(gw[i])));
+    r[i] = out_f16 ? pack_f16(y0, y1) : pack_bf16(y0, y1);
+  }
+  reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(out) + (size_t)row * HD)[c] = make_uint4(r[0], r[1], r[2], r[3]);
+}
+
+}  // namespace owl
+using namespace owl;
+
+OWL_API int owl_attn_gate(const void* o, const void* qraw, int ldq, int D, void* out, int rows, int HD, int out_f16, cudaStream_t st) {
+  if (rows < 1 || (HD & 7) || (D & 7) || (ldq & 7) || !o || !qraw || !out) return OWL_ERR_BAD_ARG;
+  attn_gate_kernel<<<dim3((HD / 8 + 255) / 256, rows), 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)qraw, ldq, D, out,
+                                                                   HD, out_f16);
+  OWL_LAUNCH_CHECK();
+  return OWL_OK;
+}
+
+// bt: the sequence's block-table row (int32 page numbers). fmt: 0 e4m3, 1 int8 with k_scale / v_scale [pages][16][hkv], 2 fp16.
+OWL_API int owl_kv_gather(const void* k_pool, const void* v_pool, const void* k_scale, const void* v_scale, int fmt, const void* bt,
+                          int ctx, int ctx_pad, int hkv, int hd, void* k_out, void* vt_out, cudaStream_t st) {
+  if (hd != 256 || ctx < 1 || ctx_pad < ctx || (ctx_pad & 63) || hkv < 1 || fmt < 0 || fmt > 2 || (fmt == 1 && (!k_scale || !v_scale)))
+    return OWL_ERR_BAD_ARG;
+  const dim3 grid(ctx_pad / AG_PAGE, hkv);
+  if (fmt == 0)
+    kv_gather_kernel<0><<<grid, 256, 0, st>>>((const uint8_t*)k_pool, (const uint8_t*)v_pool, nullptr, nullptr, (const int*)bt, ctx,
+                                              ctx_pad, hkv, (__nv_bfloat16*)k_out, (__half*)vt_out);
+  else if (fmt == 1)
+    kv_gather_kernel<1><<<grid, 256, 0, st>>>((const uint8_t*)k_pool, (const uint8_t*)v_pool, (const float*)k_scale,
+                                              (const float*)v_scale, (const int*)bt, ctx, ctx_pad, hkv, (__nv_bfloat16*)k_out,
+                                              (__half*)vt_out);
+  else
+    kv_gather_kernel<2><<<grid, 256, 0, st>>>((const uint8_t*)k_pool, (const uint8_t*)v_pool, nullptr, nullptr, (const int*)bt, ctx,
+                                              ctx_pad, hkv, (__nv_bfloat16*)k_out, (__half*)vt_out);
+  OWL_LAUNCH_CHECK();
+  return OWL_OK;
+}
+
+// s: fp16 [rows][ld]; columns [0, ncols) are rewritten (probabilities, zeros past the causal limit pos0 + r + 1).
+OWL_API int owl_causal_softmax(void* s, int rows, int ld, int ncols, int pos0, float scale, cudaStream_t st) {
+  if (rows < 1 || ncols < 1 || ld < ncols || pos0 < 0) return OWL_ERR_BAD_ARG;
+  causal_softmax_kernel<<<rows, 256, 0, st>>>((__half*)s, ld, ncols, pos0, scale * 1.4426950408889634f);
+  OWL_LAUNCH_CHECK();
+  return OWL_OK;
+}

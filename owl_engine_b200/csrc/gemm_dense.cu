@@ -55,6 +55,7 @@ struct GdParams {
   int* rs_done;                      // local [m_tiles]: weight tiles finished per row tile
   const float* a_scale;              // e4m3 form: per-token and per-weight-row scales
   const float* b_scale;
+  int out_f16;                       // direct epilogue writes fp16 instead of bf16 (attention scores); never split-k
   int ksplit;                        // > 1: the k range is cut in ksplit parts, fp32 partial tiles go to `partial`
   float* partial;                    // [ksplit][T][ldp]
   int ldp;
@@ -223,15 +224,25 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gemm_dense_kernel(const __grid_
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
               uint4 pk;
-              pk.x = pack_bf16(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
-              pk.y = pack_bf16(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
-              pk.z = pack_bf16(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
-              pk.w = pack_bf16(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+              if (p.out_f16) {
+                pk.x = pack_f16(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+                pk.y = pack_f16(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+                pk.z = pack_f16(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+                pk.w = pack_f16(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+              } else {
+                pk.x = pack_bf16(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+                pk.y = pack_bf16(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+                pk.z = pack_bf16(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+                pk.w = pack_bf16(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+              }
               *reinterpret_cast<uint4*>(o + v * 8) = pk;
             }
           } else {
             for (int v = 0; v < 32; ++v)
-              if (n0 + c * 32 + v < p.N) o[v] = __float2bfloat16(__uint_as_float(r[v]));
+              if (n0 + c * 32 + v < p.N) {
+                if (p.out_f16) reinterpret_cast<__half*>(o)[v] = __float2half_rn(__uint_as_float(r[v]));
+                else o[v] = __float2bfloat16(__uint_as_float(r[v]));
+              }
           }
         }
       }
@@ -343,7 +354,7 @@ static int gd_launch(const void* x, int ldx, const void* w, int ldw, GdParams& p
   constexpr size_t KS_SCRATCH = (size_t)160 * GD_BM * GD_BN * sizeof(float);
   p.ksplit = 1;
   const int KIs = p.K / (p.fmt == 2 ? 2 * GD_BK : GD_BK);
-  if ((mode == 0 || mode == 3) && tiles * 2 <= sms && KIs >= 8) {
+  if ((mode == 0 || mode == 3) && !p.out_f16 && tiles * 2 <= sms && KIs >= 8) {
     int ks = sms / tiles;
     if (ks > KIs / 4) ks = KIs / 4;
     if (ks > 16) ks = 16;
@@ -372,6 +383,15 @@ OWL_API int owl_f16_gemm_persist(const void* x, int ldx, const void* w, int ldw,
   if (reinterpret_cast<uintptr_t>(out) & 15) return OWL_ERR_BAD_ARG;
   GdParams p = {};
   p.out = (__nv_bfloat16*)out; p.T = T; p.N = N; p.K = K; p.ldo = ldo; p.fmt = fmt;
+  return gd_launch(x, ldx, w, ldw, p, 0, st);
+}
+
+// The same product with an fp16 result (attention scores of the GEMM-form prefill attention): 11 mantissa bits.
+OWL_API int owl_f16_gemm_persist_f16out(const void* x, int ldx, const void* w, int ldw, void* out, int T, int N, int K, int ldo,
+                                        int fmt, cudaStream_t st) {
+  if (reinterpret_cast<uintptr_t>(out) & 15) return OWL_ERR_BAD_ARG;
+  GdParams p = {};
+  p.out = (__nv_bfloat16*)out; p.T = T; p.N = N; p.K = K; p.ldo = ldo; p.fmt = fmt; p.out_f16 = 1;
   return gd_launch(x, ldx, w, ldw, p, 0, st);
 }
 

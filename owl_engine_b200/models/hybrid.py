@@ -317,6 +317,7 @@ class HybridRunner:
         # path, while the separate norm kernel's launch is hidden by programmatic dependent launch
         self.fuse_norm = os.environ.get("OWL_FUSE_NORM", "0") == "1"
         self._norm_count = None
+        self._attn_ws = None         # scratch of the GEMM-form prefill attention
         # decode activations: 15-bit fixed point (exact for bf16 inputs up to rounding at 2^-14 of the group maximum), or 8
         # bits per group (the W4A8 decode arm: half the integer products per weight byte)
         self.act_bits = int(os.environ.get("OWL_ACT_BITS", "15"))
@@ -840,17 +841,8 @@ class HybridRunner:
                                      self.qkv_n, lw.q_norm, lw.k_norm, pos3_v, self.inv_freq, self.section, kv_slot,
                                      ws["q"], pool.k_pool[fi], pool.v_pool[fi], t, sp.hq, sp.hkv, sp.hd, sp.rotary_dim,
                                      sp.eps, self.rope_scale, scales=pool.scales(fi))
-                if ng:
-                    K.paged_attn(ws["q"], pool.k_pool[fi], pool.v_pool[fi], self.block_table, ws["bt_row"], ws["ctx"],
-                                 ws["part_o"], ws["part_ml"], ng, 8, sp.hq, sp.hkv, sp.hd, self.max_blocks, 1, self.scale,
-                                 scales=pool.scales(fi))
-                if tail:
-                    off = ng * 8
-                    K.paged_attn(ws["q"][off:], pool.k_pool[fi], pool.v_pool[fi], self.block_table, ws["bt_row"][ng:],
-                                 ws["ctx"][ng:], ws["part_o"][off * sp.hq * sp.hd:], ws["part_ml"][off * sp.hq * 2:], 1,
-                                 tail, sp.hq, sp.hkv, sp.hd, self.max_blocks, 1, self.scale, scales=pool.scales(fi))
                 mix = ws["mix"].view(-1)[:t * sp.hq * sp.hd].view(t, sp.hq * sp.hd)
-                K.attn_reduce(ws["part_o"], ws["part_ml"], 1, wide, self.qkv_n, t, sp.hq, out=mix, group=self.G)
+                self._prefill_attention(ws, pool, fi, wide, mix, t, pos0, seq_row, ng, tail)
                 self._gemm(lw.o_proj, mix, ws["y"][:t])
                 fi += 1
             if self.comm is not None and sp.tp_world > 1:
@@ -875,6 +867,33 @@ class HybridRunner:
         return self.out_tok[:1]
 
     SP_FROM = 256       # tokens per chunk from which the sequence-parallel fused path is used under tensor parallelism
+
+    ATTN_GEMM_FROM = 4096      # keys from which a prefill chunk's attention runs as tcgen05 GEMMs (0: never)
+
+    def _prefill_attention(self, ws, pool, fi: int, wide, mix, t: int, pos0: int, seq_row: int, ng: int, tail: int) -> None:
+        """Causal attention of a prefill chunk over the sequence's pages. Short contexts: the fused warp-level kernel (8 query
+        rows per group). Long contexts: gather the pages once, S = Q K^T and O = P V as tcgen05 GEMMs with a causal softmax
+        between them (``K.attn_gemm_prefill``): the fused kernel's tensor path tops out near 60 TFLOP/s of attention work."""
+        sp = self.spec
+        ctx = pos0 + t
+        if self.ATTN_GEMM_FROM and ctx >= self.ATTN_GEMM_FROM and t >= 128 and sp.hd == 256:
+            aw = self._attn_ws
+            if aw is None or aw["t"] < t or aw["ctx"] < ctx:
+                cap = max(ctx, 2 * (aw["ctx"] if aw else 0), 8192)
+                self._attn_ws = aw = K.attn_gemm_ws(self.device, max(t, aw["t"] if aw else 0), cap, sp.hq, sp.hkv, sp.hd)
+            K.attn_gemm_prefill(ws["q"], pool.k_pool[fi], pool.v_pool[fi], pool.scales(fi), self.block_table[seq_row], pos0, t,
+                                sp.hq, sp.hkv, sp.hd, self.scale, aw, wide, self.qkv_n, mix)
+            return
+        if ng:
+            K.paged_attn(ws["q"], pool.k_pool[fi], pool.v_pool[fi], self.block_table, ws["bt_row"], ws["ctx"],
+                         ws["part_o"], ws["part_ml"], ng, 8, sp.hq, sp.hkv, sp.hd, self.max_blocks, 1, self.scale,
+                         scales=pool.scales(fi))
+        if tail:
+            off = ng * 8
+            K.paged_attn(ws["q"][off:], pool.k_pool[fi], pool.v_pool[fi], self.block_table, ws["bt_row"][ng:],
+                         ws["ctx"][ng:], ws["part_o"][off * sp.hq * sp.hd:], ws["part_ml"][off * sp.hq * 2:], 1,
+                         tail, sp.hq, sp.hkv, sp.hd, self.max_blocks, 1, self.scale, scales=pool.scales(fi))
+        K.attn_reduce(ws["part_o"], ws["part_ml"], 1, wide, self.qkv_n, t, sp.hq, out=mix, group=self.G)
 
     def _pipe(self):
         """The prefill pipe of the tensor-parallel communicator (or one set explicitly, e.g. a world of one)."""
@@ -946,17 +965,8 @@ class HybridRunner:
                                      self.qkv_n, lw.q_norm, lw.k_norm, pos3_v, self.inv_freq, self.section, kv_slot,
                                      ws["q"], pool.k_pool[fi], pool.v_pool[fi], t, sp.hq, sp.hkv, sp.hd, sp.rotary_dim,
                                      sp.eps, self.rope_scale, scales=pool.scales(fi))
-                if ng:
-                    K.paged_attn(ws["q"], pool.k_pool[fi], pool.v_pool[fi], self.block_table, ws["bt_row"], ws["ctx"],
-                                 ws["part_o"], ws["part_ml"], ng, 8, sp.hq, sp.hkv, sp.hd, self.max_blocks, 1, self.scale,
-                                 scales=pool.scales(fi))
-                if tail:
-                    off = ng * 8
-                    K.paged_attn(ws["q"][off:], pool.k_pool[fi], pool.v_pool[fi], self.block_table, ws["bt_row"][ng:],
-                                 ws["ctx"][ng:], ws["part_o"][off * sp.hq * sp.hd:], ws["part_ml"][off * sp.hq * 2:], 1,
-                                 tail, sp.hq, sp.hkv, sp.hd, self.max_blocks, 1, self.scale, scales=pool.scales(fi))
                 mix = ws["mix"].view(-1)[:t * sp.hq * sp.hd].view(t, sp.hq * sp.hd)
-                K.attn_reduce(ws["part_o"], ws["part_ml"], 1, wide, self.qkv_n, t, sp.hq, out=mix, group=self.G)
+                self._prefill_attention(ws, pool, fi, wide, mix, t, pos0, seq_row, ng, tail)
                 pipe.gemm_rs(mix, dense(lw.o_proj), t)
                 fi += 1
             pipe.reduce_norm_gather(t, lw.ln2, out_dtype=xd, eps=sp.eps)

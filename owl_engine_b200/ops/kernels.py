@@ -321,6 +321,44 @@ def attn_reduce(part_o, part_ml, splits: int, qraw, ldq: int, rows: int, hq: int
          group, _is_f16(out), int(pdl), stream())
 
 
+register("owl_kv_gather", [_P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P, _P, _P])
+register("owl_causal_softmax", [_P, _I, _I, _I, _I, _F, _P])
+register("owl_attn_gate", [_P, _P, _I, _I, _P, _I, _I, _I, _P])
+register("owl_f16_gemm_persist_f16out", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P])
+
+
+def attn_gemm_prefill(q, k_pool, v_pool, scales, bt_row, pos0: int, t: int, hq: int, hkv: int, hd: int, scale: float, ws: dict,
+                      qraw, ldq: int, out) -> None:
+    """Causal attention of a prefill chunk as tcgen05 GEMMs (long contexts): the sequence's paged K / V are gathered once into
+    dense k-major operands (K bf16, V transposed fp16), then per q head S = Q K^T (fp16 scores), a causal softmax in place,
+    O = P V; the sigmoid gate of the q projection closes it. ``q``: bf16 [t, hq, hd] after norm and rotary; ``bt_row``: the
+    sequence's block-table row; ``ws``: scratch tensors kept by the caller (``attn_gemm_ws``); ``out``: [t, hq * hd] bf16 / fp16."""
+    ctx = pos0 + t
+    ctx_pad = (ctx + 63) // 64 * 64
+    fmt = 2 if k_pool.dtype == torch.float16 else (1 if scales is not None else 0)
+    kb, vt, s, o = ws["k"][:hkv * ctx_pad * hd], ws["vt"][:hkv * hd * ctx_pad], ws["s"][:t * ctx_pad], ws["o"][:t * hq * hd]
+    call("owl_kv_gather", ptr(k_pool), ptr(v_pool), ptr(scales[0]) if scales else None, ptr(scales[1]) if scales else None, fmt,
+         ptr(bt_row), ctx, ctx_pad, hkv, hd, ptr(kb), ptr(vt), stream())
+    gq, st = hq // hkv, stream()
+    for h in range(hq):
+        kh = h // gq
+        call("owl_f16_gemm_persist_f16out", q.data_ptr() + h * hd * 2, hq * hd, kb.data_ptr() + kh * ctx_pad * hd * 2, hd, ptr(s),
+             t, ctx_pad, hd, ctx_pad, 1, st)
+        call("owl_causal_softmax", ptr(s), t, ctx_pad, ctx_pad, pos0, scale, st)
+        call("owl_f16_gemm_persist", ptr(s), ctx_pad, vt.data_ptr() + kh * hd * ctx_pad * 2, ctx_pad, o.data_ptr() + h * hd * 2,
+             t, hd, ctx_pad, hq * hd, 0, st)
+    call("owl_attn_gate", ptr(o), ptr(qraw), ldq, hd, ptr(out), t, hq * hd, _is_f16(out), st)
+
+
+def attn_gemm_ws(device, t: int, max_ctx: int, hq: int, hkv: int, hd: int) -> dict:
+    """Scratch of ``attn_gemm_prefill`` for chunks of up to ``t`` rows over up to ``max_ctx`` keys."""
+    cp = (max_ctx + 63) // 64 * 64
+    return {"k": torch.zeros(hkv * cp * hd, dtype=torch.bfloat16, device=device),
+            "vt": torch.zeros(hkv * hd * cp, dtype=torch.float16, device=device),
+            "s": torch.zeros(t * cp, dtype=torch.float16, device=device),
+            "o": torch.zeros(t * hq * hd, dtype=torch.bfloat16, device=device), "t": t, "ctx": cp}
+
+
 register("owl_topk", [_P, _I, _I, _I, _I, _P, _P, _I, _F, _I, _P, _P, _I, _P, _P, _P])
 register("owl_topk_merge", [_P, _P, _I, _I, _I, _P, _P, _P])
 

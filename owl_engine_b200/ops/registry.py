@@ -45,6 +45,7 @@ _T = [
     KernelSpec("owl_f16_gemm_tc", "gemm_tc.cu", "gemm", gen="tcgen05+tmem+tma"),
     KernelSpec("owl_gemm_status", "gemm_tc.cu", "status", capture=False),
     KernelSpec("owl_f16_gemm_persist", "gemm_dense.cu", "gemm", gen="tcgen05+tmem+tma"),
+    KernelSpec("owl_f16_gemm_persist_f16out", "gemm_dense.cu", "gemm", gen="tcgen05+tmem+tma"),
     KernelSpec("owl_f16_gemm_ag", "gemm_dense.cu", "gemm", gen="tcgen05+tmem+tma+p2p"),
     KernelSpec("owl_f16_gemm_rs", "gemm_dense.cu", "gemm", gen="tcgen05+tmem+tma+p2p"),
     KernelSpec("owl_e4m3_gemm", "gemm_dense.cu", "gemm", gen="tcgen05+tmem+tma"),
@@ -97,6 +98,9 @@ _T = [
     KernelSpec("owl_qknorm_rope_insert_f16", "attn.cu", "attn"),
     KernelSpec("owl_paged_attn_f16", "attn.cu", "attn", gen="mma.sync"),
     KernelSpec("owl_attn_reduce", "attn.cu", "attn"),
+    KernelSpec("owl_kv_gather", "attn_gemm.cu", "attn"),
+    KernelSpec("owl_causal_softmax", "attn_gemm.cu", "attn"),
+    KernelSpec("owl_attn_gate", "attn_gemm.cu", "attn"),
     # collectives over peer memory
     KernelSpec("owl_ar_residual_norm", "comm.cu", "comm", gen="p2p+multimem"),
     KernelSpec("owl_ar_inplace", "comm.cu", "comm", gen="p2p+multimem"),

@@ -140,6 +140,33 @@ def test_sequence_parallel_prefill_protocol_on_one_gpu():
     assert rel_err(outs[0][0], hr[-1:]) < 0.05
 
 
+@pytest.mark.parametrize("kv_dtype", ["fp8", "int8", "bf16"])
+def test_gemm_form_prefill_attention_matches_the_fused_kernel_and_the_reference(kv_dtype):
+    """Long-context prefill attention as tcgen05 GEMMs (page gather -> S = Q K^T -> causal softmax -> O = P V -> gate) against
+    the fused warp-level kernel on the same pool and against the fp32 model; two chunks, so the second one attends to pages
+    written by the first."""
+    g = torch.Generator().manual_seed(0)
+    outs = {}
+    for arm in ("gemm", "fused"):
+        spec, run, ref = build("tc", kv_dtype=kv_dtype)
+        run.ATTN_GEMM_FROM = 128 if arm == "gemm" else 0
+        prompt = torch.randint(0, spec.vocab, (256,), generator=torch.Generator().manual_seed(1))
+        seq_row, slot = 1, 2
+        run.block_table[seq_row, :16] = torch.arange(16, 32, dtype=torch.int32, device=DEV).flip(0)
+        ids = prompt.to(torch.int32).to(DEV)
+        run.prefill_chunk_forward(ids[:128], 0, seq_row, slot, want_logits=False)
+        run.prefill_chunk_forward(ids[128:], 128, seq_row, slot)
+        torch.cuda.synchronize()
+        outs[arm] = run.logits[:1].float().cpu()
+        if arm == "gemm":
+            assert run._attn_ws is not None
+            from owl_engine_b200.ops import gemm_tc
+            assert gemm_tc.gemm_status() == 0
+    want = ref.logits(ref.forward(prompt, ref.new_state())[-1:])
+    assert rel_err(outs["gemm"], outs["fused"]) < 0.02
+    assert rel_err(outs["gemm"], want) < 0.05
+
+
 def test_w4a8_decode_arm_tracks_the_reference():
     """8-bit decode activations (``act_bits = 8``): greedy decode steps stay close to the fp32 model (looser than the 15-bit
     arm), eager and captured."""
