@@ -78,6 +78,57 @@ __global__ void __launch_bounds__(256) causal_softmax_kernel(__half* __restrict_
     row[c] = __float2half_rn(c < limit ? exp2f((__half2float(row[c]) - mx) * scale_log2) * inv : 0.f);
 }
 
+// The same with the row staged in shared memory (rows up to ~110 k keys): one vectorised read of the scores, one exponential per
+// element, one vectorised write. ld and ncols are multiples of 8; dynamic shared memory = ncols halves.
+__global__ void __launch_bounds__(512) causal_softmax_smem_kernel(__half* __restrict__ s, int ld, int ncols, int pos0, float scale_log2) {
+  extern __shared__ __align__(16) __half srow[];
+  __shared__ float red[32];
+  const int r = blockIdx.x;
+  __half* row = s + (size_t)r * ld;
+  const int limit = min(pos0 + r + 1, ncols);
+  const int nv = (limit + 7) >> 3, nv_all = ncols >> 3;       // uint4 chunks that hold visible keys / all chunks
+  float mx = -INFINITY;
+  for (int c = threadIdx.x; c < nv; c += blockDim.x) {
+    const uint4 u = reinterpret_cast<const uint4*>(row)[c];
+    reinterpret_cast<uint4*>(srow)[c] = u;
+    const __half2* h2 = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(h2[i]);
+      if (c * 8 + 2 * i < limit) mx = fmaxf(mx, f.x);
+      if (c * 8 + 2 * i + 1 < limit) mx = fmaxf(mx, f.y);
+    }
+  }
+  mx = block_max(mx, red);
+  float sum = 0.f;
+  for (int c = threadIdx.x; c < nv; c += blockDim.x) {
+    __half2* h2 = reinterpret_cast<__half2*>(srow) + c * 4;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(h2[i]);
+      const float e0 = c * 8 + 2 * i < limit ? exp2f((f.x - mx) * scale_log2) : 0.f;
+      const float e1 = c * 8 + 2 * i + 1 < limit ? exp2f((f.y - mx) * scale_log2) : 0.f;
+      sum += e0 + e1;
+      h2[i] = __floats2half2_rn(e0, e1);
+    }
+  }
+  sum = block_sum(sum, red);
+  const float inv = 1.f / sum;
+  for (int c = threadIdx.x; c < nv_all; c += blockDim.x) {
+    uint4 u = make_uint4(0u, 0u, 0u, 0u);
+    if (c < nv) {
+      u = reinterpret_cast<const uint4*>(srow)[c];
+      __half2* h2 = reinterpret_cast<__half2*>(&u);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(h2[i]);
+        h2[i] = __floats2half2_rn(f.x * inv, f.y * inv);
+      }
+    }
+    reinterpret_cast<uint4*>(row)[c] = u;
+  }
+}
+
 // y = o * sigmoid(gate): o bf16 [rows][HD], gate from the q projection output ([q_h | gate_h] per head, row stride ldq); y bf16 or
 // fp16 [rows][HD]. grid (HD / 8 / 256 rounded up, rows).
 __global__ void __launch_bounds__(256) attn_gate_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ qraw,
@@ -131,7 +182,18 @@ OWL_API int owl_kv_gather(const void* k_pool, const void* v_pool, const void* k_
 // s: fp16 [rows][ld]; columns [0, ncols) are rewritten (probabilities, zeros past the causal limit pos0 + r + 1).
 OWL_API int owl_causal_softmax(void* s, int rows, int ld, int ncols, int pos0, float scale, cudaStream_t st) {
   if (rows < 1 || ncols < 1 || ld < ncols || pos0 < 0) return OWL_ERR_BAD_ARG;
-  causal_softmax_kernel<<<rows, 256, 0, st>>>((__half*)s, ld, ncols, pos0, scale * 1.4426950408889634f);
+  const size_t smem = (size_t)ncols * 2;
+  if (!(ld & 7) && !(ncols & 7) && !(reinterpret_cast<uintptr_t>(s) & 15) && smem <= 200 * 1024) {
+    static bool attr_done = false;
+    if (!attr_done) {
+      if (cudaFuncSetAttribute(causal_softmax_smem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+        return OWL_ERR_LAUNCH * 1000;
+      attr_done = true;
+    }
+    causal_softmax_smem_kernel<<<rows, 512, smem, st>>>((__half*)s, ld, ncols, pos0, scale * 1.4426950408889634f);
+  } else {
+    causal_softmax_kernel<<<rows, 256, 0, st>>>((__half*)s, ld, ncols, pos0, scale * 1.4426950408889634f);
+  }
   OWL_LAUNCH_CHECK();
   return OWL_OK;
 }
