@@ -62,11 +62,12 @@ __global__ void __launch_bounds__(256) kv_gather_kernel(const uint8_t* __restric
 }
 
 // one CTA (256 threads) per score row; three passes over the row (max, sum, write)
-__global__ void __launch_bounds__(256) causal_softmax_kernel(__half* __restrict__ s, int ld, int ncols, int pos0, float scale_log2) {
+__global__ void __launch_bounds__(256) causal_softmax_kernel(__half* __restrict__ s, int ld, int ncols, int pos0, float scale_log2,
+                                                             int rpt) {
   __shared__ float red[32];
   const int r = blockIdx.x;
   __half* row = s + (size_t)r * ld;
-  const int limit = min(pos0 + r + 1, ncols);
+  const int limit = min(pos0 + r / rpt + 1, ncols);
   float mx = -INFINITY;
   for (int c = threadIdx.x; c < limit; c += blockDim.x) mx = fmaxf(mx, __half2float(row[c]));
   mx = block_max(mx, red);
@@ -80,12 +81,13 @@ __global__ void __launch_bounds__(256) causal_softmax_kernel(__half* __restrict_
 
 // The same with the row staged in shared memory (rows up to ~110 k keys): one vectorised read of the scores, one exponential per
 // element, one vectorised write. ld and ncols are multiples of 8; dynamic shared memory = ncols halves.
-__global__ void __launch_bounds__(512) causal_softmax_smem_kernel(__half* __restrict__ s, int ld, int ncols, int pos0, float scale_log2) {
+__global__ void __launch_bounds__(512) causal_softmax_smem_kernel(__half* __restrict__ s, int ld, int ncols, int pos0, float scale_log2,
+                                                                  int rpt) {
   extern __shared__ __align__(16) __half srow[];
   __shared__ float red[32];
   const int r = blockIdx.x;
   __half* row = s + (size_t)r * ld;
-  const int limit = min(pos0 + r + 1, ncols);
+  const int limit = min(pos0 + r / rpt + 1, ncols);
   const int nv = (limit + 7) >> 3, nv_all = ncols >> 3;       // uint4 chunks that hold visible keys / all chunks
   float mx = -INFINITY;
   for (int c = threadIdx.x; c < nv; c += blockDim.x) {
@@ -132,11 +134,14 @@ __global__ void __launch_bounds__(512) causal_softmax_smem_kernel(__half* __rest
 // y = o * sigmoid(gate): o bf16 [rows][HD], gate from the q projection output ([q_h | gate_h] per head, row stride ldq); y bf16 or
 // fp16 [rows][HD]. grid (HD / 8 / 256 rounded up, rows).
 __global__ void __launch_bounds__(256) attn_gate_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ qraw,
-                                                        int ldq, int D, void* __restrict__ out, int HD, int out_f16) {
+                                                        int ldq, int D, void* __restrict__ out, int HD, int out_f16, int gq) {
   const int row = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= (HD >> 3)) return;
   const int e = c * 8, head = e / D, off = e % D;
-  const uint4 a = reinterpret_cast<const uint4*>(o + (size_t)row * HD)[c];
+  // gq > 0: o is stacked per kv head, [hkv][rows][gq][D] (the grouped GEMM's output); else [rows][HD]
+  const __nv_bfloat16* src = gq > 0 ? o + ((((size_t)(head / gq) * gridDim.y + row) * gq + head % gq) * D + off)
+                                    : o + (size_t)row * HD + e;
+  const uint4 a = *reinterpret_cast<const uint4*>(src);
   const uint4 g = *reinterpret_cast<const uint4*>(qraw + (size_t)row * ldq + (size_t)head * 2 * D + D + off);
   const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
   uint32_t r[4];
@@ -151,10 +156,28 @@ __global__ void __launch_bounds__(256) attn_gate_kernel(const __nv_bfloat16* __r
 }  // namespace owl
 using namespace owl;
 
-OWL_API int owl_attn_gate(const void* o, const void* qraw, int ldq, int D, void* out, int rows, int HD, int out_f16, cudaStream_t st) {
-  if (rows < 1 || (HD & 7) || (D & 7) || (ldq & 7) || !o || !qraw || !out) return OWL_ERR_BAD_ARG;
+// q bf16 [rows][hq][D] -> qg [hkv][rows][gq][D]: the q heads of one kv head become consecutive rows of one GEMM operand.
+__global__ void __launch_bounds__(256) q_group_kernel(const uint4* __restrict__ q, uint4* __restrict__ qg, int hq, int gq, int cpd) {
+  const int row = blockIdx.y, rows = gridDim.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= hq * cpd) return;
+  const int head = c / cpd, off = c % cpd;
+  qg[(((size_t)(head / gq) * rows + row) * gq + head % gq) * cpd + off] = q[(size_t)row * hq * cpd + c];
+}
+
+OWL_API int owl_q_group(const void* q, void* qg, int rows, int hq, int hkv, int D, cudaStream_t st) {
+  if (rows < 1 || hkv < 1 || hq % hkv || (D & 7) || !q || !qg) return OWL_ERR_BAD_ARG;
+  const int cpd = D / 8;
+  q_group_kernel<<<dim3((hq * cpd + 255) / 256, rows), 256, 0, st>>>((const uint4*)q, (uint4*)qg, hq, hq / hkv, cpd);
+  OWL_LAUNCH_CHECK();
+  return OWL_OK;
+}
+
+// gq > 0: `o` is the grouped layout [hkv][rows][gq][D]; gq = 0: [rows][HD].
+OWL_API int owl_attn_gate(const void* o, const void* qraw, int ldq, int D, void* out, int rows, int HD, int out_f16, int gq,
+                          cudaStream_t st) {
+  if (rows < 1 || (HD & 7) || (D & 7) || (ldq & 7) || !o || !qraw || !out || gq < 0) return OWL_ERR_BAD_ARG;
   attn_gate_kernel<<<dim3((HD / 8 + 255) / 256, rows), 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)qraw, ldq, D, out,
-                                                                   HD, out_f16);
+                                                                   HD, out_f16, gq);
   OWL_LAUNCH_CHECK();
   return OWL_OK;
 }
@@ -180,8 +203,9 @@ OWL_API int owl_kv_gather(const void* k_pool, const void* v_pool, const void* k_
 }
 
 // s: fp16 [rows][ld]; columns [0, ncols) are rewritten (probabilities, zeros past the causal limit pos0 + r + 1).
-OWL_API int owl_causal_softmax(void* s, int rows, int ld, int ncols, int pos0, float scale, cudaStream_t st) {
-  if (rows < 1 || ncols < 1 || ld < ncols || pos0 < 0) return OWL_ERR_BAD_ARG;
+// rows_per_tok consecutive rows belong to one query token (the q heads of a kv head stacked per token).
+OWL_API int owl_causal_softmax(void* s, int rows, int ld, int ncols, int pos0, float scale, int rows_per_tok, cudaStream_t st) {
+  if (rows < 1 || ncols < 1 || ld < ncols || pos0 < 0 || rows_per_tok < 1) return OWL_ERR_BAD_ARG;
   const size_t smem = (size_t)ncols * 2;
   if (!(ld & 7) && !(ncols & 7) && !(reinterpret_cast<uintptr_t>(s) & 15) && smem <= 200 * 1024) {
     static bool attr_done = false;
@@ -190,9 +214,9 @@ OWL_API int owl_causal_softmax(void* s, int rows, int ld, int ncols, int pos0, f
         return OWL_ERR_LAUNCH * 1000;
       attr_done = true;
     }
-    causal_softmax_smem_kernel<<<rows, 512, smem, st>>>((__half*)s, ld, ncols, pos0, scale * 1.4426950408889634f);
+    causal_softmax_smem_kernel<<<rows, 512, smem, st>>>((__half*)s, ld, ncols, pos0, scale * 1.4426950408889634f, rows_per_tok);
   } else {
-    causal_softmax_kernel<<<rows, 256, 0, st>>>((__half*)s, ld, ncols, pos0, scale * 1.4426950408889634f);
+    causal_softmax_kernel<<<rows, 256, 0, st>>>((__half*)s, ld, ncols, pos0, scale * 1.4426950408889634f, rows_per_tok);
   }
   OWL_LAUNCH_CHECK();
   return OWL_OK;

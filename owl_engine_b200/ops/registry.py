@@ -101,6 +101,7 @@ _T = [
     KernelSpec("owl_kv_gather", "attn_gemm.cu", "attn"),
     KernelSpec("owl_causal_softmax", "attn_gemm.cu", "attn"),
     KernelSpec("owl_attn_gate", "attn_gemm.cu", "attn"),
+    KernelSpec("owl_q_group", "attn_gemm.cu", "attn"),
     # collectives over peer memory
     KernelSpec("owl_ar_residual_norm", "comm.cu", "comm", gen="p2p+multimem"),
     KernelSpec("owl_ar_inplace", "comm.cu", "comm", gen="p2p+multimem"),
