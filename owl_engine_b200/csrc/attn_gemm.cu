@@ -63,7 +63,7 @@ __global__ void __launch_bounds__(256) kv_gather_kernel(const uint8_t* __restric
 
 // one CTA (256 threads) per score row; three passes over the row (max, sum, write)
 __global__ void __launch_bounds__(256) causal_softmax_kernel(__half* __restrict__ s, int ld, int ncols, int pos0, float scale_log2,
-                                                             int rpt) {
+                                                             int rpt, float* __restrict__ inv_sum) {
   __shared__ float red[32];
   const int r = blockIdx.x;
   __half* row = s + (size_t)r * ld;
@@ -74,67 +74,71 @@ __global__ void __launch_bounds__(256) causal_softmax_kernel(__half* __restrict_
   float sum = 0.f;
   for (int c = threadIdx.x; c < limit; c += blockDim.x) sum += exp2f((__half2float(row[c]) - mx) * scale_log2);
   sum = block_sum(sum, red);
-  const float inv = 1.f / sum;
   for (int c = threadIdx.x; c < ncols; c += blockDim.x)
-    row[c] = __float2half_rn(c < limit ? exp2f((__half2float(row[c]) - mx) * scale_log2) * inv : 0.f);
+    row[c] = __float2half_rn(c < limit ? exp2f((__half2float(row[c]) - mx) * scale_log2) : 0.f);
+  if (threadIdx.x == 0) inv_sum[r] = 1.f / sum;
 }
 
-// The same with the row staged in shared memory (rows up to ~110 k keys): one vectorised read of the scores, one exponential per
-// element, one vectorised write. ld and ncols are multiples of 8; dynamic shared memory = ncols halves.
+// The row staged in shared memory (rows up to ~100 k keys): one vectorised read of the scores, one exponential per element, one
+// vectorised write. The probabilities are left UNNORMALISED (largest = 1, which keeps them in the fp16 normal range however many
+// keys a row sees); 1 / sum goes to inv_sum[row] and is applied to the output row after O = P V. ld and ncols are multiples of
+// 8; dynamic shared memory = ncols halves.
 __global__ void __launch_bounds__(512) causal_softmax_smem_kernel(__half* __restrict__ s, int ld, int ncols, int pos0, float scale_log2,
-                                                                  int rpt) {
+                                                                  int rpt, float* __restrict__ inv_sum) {
   extern __shared__ __align__(16) __half srow[];
   __shared__ float red[32];
   const int r = blockIdx.x;
   __half* row = s + (size_t)r * ld;
   const int limit = min(pos0 + r / rpt + 1, ncols);
-  const int nv = (limit + 7) >> 3, nv_all = ncols >> 3;       // uint4 chunks that hold visible keys / all chunks
-  float mx = -INFINITY;
+  const int nfull = limit >> 3, nv = (limit + 7) >> 3, nv_all = ncols >> 3;   // fully visible chunks / chunks with a visible key / all
+  __half2 m2 = __float2half2_rn(-65504.f);
   for (int c = threadIdx.x; c < nv; c += blockDim.x) {
     const uint4 u = reinterpret_cast<const uint4*>(row)[c];
     reinterpret_cast<uint4*>(srow)[c] = u;
     const __half2* h2 = reinterpret_cast<const __half2*>(&u);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float2 f = __half22float2(h2[i]);
-      if (c * 8 + 2 * i < limit) mx = fmaxf(mx, f.x);
-      if (c * 8 + 2 * i + 1 < limit) mx = fmaxf(mx, f.y);
+    if (c < nfull) {
+      m2 = __hmax2(m2, __hmax2(__hmax2(h2[0], h2[1]), __hmax2(h2[2], h2[3])));
+    } else {
+      const __half* h = reinterpret_cast<const __half*>(&u);
+      for (int i = 0; i < limit - c * 8; ++i) m2 = __hmax2(m2, __half2half2(h[i]));
     }
   }
-  mx = block_max(mx, red);
+  const float mx = block_max(fmaxf(__low2float(m2), __high2float(m2)), red);
+  const float bias = -mx * scale_log2;
   float sum = 0.f;
-  for (int c = threadIdx.x; c < nv; c += blockDim.x) {
-    __half2* h2 = reinterpret_cast<__half2*>(srow) + c * 4;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float2 f = __half22float2(h2[i]);
-      const float e0 = c * 8 + 2 * i < limit ? exp2f((f.x - mx) * scale_log2) : 0.f;
-      const float e1 = c * 8 + 2 * i + 1 < limit ? exp2f((f.y - mx) * scale_log2) : 0.f;
-      sum += e0 + e1;
-      h2[i] = __floats2half2_rn(e0, e1);
-    }
-  }
-  sum = block_sum(sum, red);
-  const float inv = 1.f / sum;
   for (int c = threadIdx.x; c < nv_all; c += blockDim.x) {
     uint4 u = make_uint4(0u, 0u, 0u, 0u);
     if (c < nv) {
       u = reinterpret_cast<const uint4*>(srow)[c];
       __half2* h2 = reinterpret_cast<__half2*>(&u);
+      if (c < nfull) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float2 f = __half22float2(h2[i]);
-        h2[i] = __floats2half2_rn(f.x * inv, f.y * inv);
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __half22float2(h2[i]);
+          const float e0 = exp2f(fmaf(f.x, scale_log2, bias)), e1 = exp2f(fmaf(f.y, scale_log2, bias));
+          sum += e0 + e1;
+          h2[i] = __floats2half2_rn(e0, e1);
+        }
+      } else {
+        __half* h = reinterpret_cast<__half*>(&u);
+        for (int i = 0; i < 8; ++i) {
+          const float e = c * 8 + i < limit ? exp2f(fmaf(__half2float(h[i]), scale_log2, bias)) : 0.f;
+          sum += e;
+          h[i] = __float2half_rn(e);
+        }
       }
     }
     reinterpret_cast<uint4*>(row)[c] = u;
   }
+  sum = block_sum(sum, red);
+  if (threadIdx.x == 0) inv_sum[r] = 1.f / sum;
 }
 
 // y = o * sigmoid(gate): o bf16 [rows][HD], gate from the q projection output ([q_h | gate_h] per head, row stride ldq); y bf16 or
 // fp16 [rows][HD]. grid (HD / 8 / 256 rounded up, rows).
 __global__ void __launch_bounds__(256) attn_gate_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ qraw,
-                                                        int ldq, int D, void* __restrict__ out, int HD, int out_f16, int gq) {
+                                                        int ldq, int D, void* __restrict__ out, int HD, int out_f16, int gq,
+                                                        const float* __restrict__ inv_sum) {
   const int row = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= (HD >> 3)) return;
   const int e = c * 8, head = e / D, off = e % D;
@@ -142,12 +146,15 @@ __global__ void __launch_bounds__(256) attn_gate_kernel(const __nv_bfloat16* __r
   const __nv_bfloat16* src = gq > 0 ? o + ((((size_t)(head / gq) * gridDim.y + row) * gq + head % gq) * D + off)
                                     : o + (size_t)row * HD + e;
   const uint4 a = *reinterpret_cast<const uint4*>(src);
+  // softmax denominator of this (token, head): same stacking as the grouped rows, or [head][rows] for the flat layout
+  const float nrm = !inv_sum ? 1.f : gq > 0 ? inv_sum[((size_t)(head / gq) * gridDim.y + row) * gq + head % gq]
+                                            : inv_sum[(size_t)head * gridDim.y + row];
   const uint4 g = *reinterpret_cast<const uint4*>(qraw + (size_t)row * ldq + (size_t)head * 2 * D + D + off);
   const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
   uint32_t r[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const float y0 = bf16_lo(aw[i]) / (1.f + __expf(-bf16_lo(gw[i]))), y1 = bf16_hi(aw[i]) / (1.f + __expf(-bf16_hi(gw[i])));
+    const float y0 = nrm * bf16_lo(aw[i]) / (1.f + __expf(-bf16_lo(gw[i]))), y1 = nrm * bf16_hi(aw[i]) / (1.f + __expf(-bf16_hi(gw[i])));
     r[i] = out_f16 ? pack_f16(y0, y1) : pack_bf16(y0, y1);
   }
   reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(out) + (size_t)row * HD)[c] = make_uint4(r[0], r[1], r[2], r[3]);
@@ -174,10 +181,10 @@ OWL_API int owl_q_group(const void* q, void* qg, int rows, int hq, int hkv, int 
 
 // gq > 0: `o` is the grouped layout [hkv][rows][gq][D]; gq = 0: [rows][HD].
 OWL_API int owl_attn_gate(const void* o, const void* qraw, int ldq, int D, void* out, int rows, int HD, int out_f16, int gq,
-                          cudaStream_t st) {
+                          const void* inv_sum, cudaStream_t st) {
   if (rows < 1 || (HD & 7) || (D & 7) || (ldq & 7) || !o || !qraw || !out || gq < 0) return OWL_ERR_BAD_ARG;
   attn_gate_kernel<<<dim3((HD / 8 + 255) / 256, rows), 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)qraw, ldq, D, out,
-                                                                   HD, out_f16, gq);
+                                                                   HD, out_f16, gq, (const float*)inv_sum);
   OWL_LAUNCH_CHECK();
   return OWL_OK;
 }
@@ -204,8 +211,10 @@ OWL_API int owl_kv_gather(const void* k_pool, const void* v_pool, const void* k_
 
 // s: fp16 [rows][ld]; columns [0, ncols) are rewritten (probabilities, zeros past the causal limit pos0 + r + 1).
 // rows_per_tok consecutive rows belong to one query token (the q heads of a kv head stacked per token).
-OWL_API int owl_causal_softmax(void* s, int rows, int ld, int ncols, int pos0, float scale, int rows_per_tok, cudaStream_t st) {
-  if (rows < 1 || ncols < 1 || ld < ncols || pos0 < 0 || rows_per_tok < 1) return OWL_ERR_BAD_ARG;
+// The probabilities are written unnormalised (row maximum = 1); inv_sum[row] = 1 / (row sum) scales the row of O = P V.
+OWL_API int owl_causal_softmax(void* s, int rows, int ld, int ncols, int pos0, float scale, int rows_per_tok, void* inv_sum,
+                               cudaStream_t st) {
+  if (rows < 1 || ncols < 1 || ld < ncols || pos0 < 0 || rows_per_tok < 1 || !inv_sum) return OWL_ERR_BAD_ARG;
   const size_t smem = (size_t)ncols * 2;
   if (!(ld & 7) && !(ncols & 7) && !(reinterpret_cast<uintptr_t>(s) & 15) && smem <= 200 * 1024) {
     static bool attr_done = false;
@@ -214,9 +223,10 @@ OWL_API int owl_causal_softmax(void* s, int rows, int ld, int ncols, int pos0, f
         return OWL_ERR_LAUNCH * 1000;
       attr_done = true;
     }
-    causal_softmax_smem_kernel<<<rows, 512, smem, st>>>((__half*)s, ld, ncols, pos0, scale * 1.4426950408889634f, rows_per_tok);
+    causal_softmax_smem_kernel<<<rows, 512, smem, st>>>((__half*)s, ld, ncols, pos0, scale * 1.4426950408889634f, rows_per_tok,
+                                                        (float*)inv_sum);
   } else {
-    causal_softmax_kernel<<<rows, 256, 0, st>>>((__half*)s, ld, ncols, pos0, scale * 1.4426950408889634f, rows_per_tok);
+    causal_softmax_kernel<<<rows, 256, 0, st>>>((__half*)s, ld, ncols, pos0, scale * 1.4426950408889634f, rows_per_tok, (float*)inv_sum);
   }
   OWL_LAUNCH_CHECK();
   return OWL_OK;

@@ -2,7 +2,7 @@
 L2 but well under a few GB, then exits.
 
 ``python -m owl_engine_b200.fixtures.kernel_cases <case>`` with case in
-``gemm16 gemm8 gemm_w4 gemv attn attn16 gdn_decode gdn_scan dflash_attn`` (prints the CUDA-event time per launch).
+``gemm16 gemm8 gemm_w4 gemv attn attn16 attn_prefill_gemm attn_prefill_fused gdn_decode gdn_scan dflash_attn`` (prints the CUDA-event time per launch).
 """
 import math
 import sys
@@ -93,6 +93,46 @@ def attn(kv16: bool = False):
 
 def attn16():
     return attn(True)
+
+
+def _prefill_attn_case(ctx: int, t: int):
+    hq, hkv, hd = 24, 4, 256
+    pages = ctx // 16
+    kp = torch.randint(0, 120, (pages, 16, hkv, hd), dtype=torch.uint8, device=dev)
+    vp = torch.randint(0, 120, (pages, 16, hkv, hd), dtype=torch.uint8, device=dev)
+    bt = torch.arange(pages, dtype=torch.int32, device=dev).view(1, -1).contiguous()
+    q = torch.randn(t, hq, hd, device=dev).bfloat16()
+    qraw = torch.randn(t, hq * 2 * hd, device=dev).bfloat16()
+    return hq, hkv, hd, kp, vp, bt, q, qraw
+
+
+def attn_prefill_gemm(ctx: int = 8192, t: int = 2048):
+    """The last 2048-row chunk of an 8192-token prompt, attention only, GEMM form (gather + 4 x (GEMM, softmax, GEMM) + gate)."""
+    hq, hkv, hd, kp, vp, bt, q, qraw = _prefill_attn_case(ctx, t)
+    ws = K.attn_gemm_ws(dev, t, ctx, hq, hkv, hd)
+    out = torch.empty(t, hq * hd, dtype=torch.float16, device=dev)
+    ms = timed(lambda: K.attn_gemm_prefill(q, kp, vp, None, bt[0], ctx - t, t, hq, hkv, hd, 1 / math.sqrt(hd), ws, qraw,
+                                           hq * 2 * hd, out))
+    flops = 4 * hq * hd * (t * (ctx - t) + t * t / 2)
+    return ms, f"{flops / ms / 1e9:.0f} TFLOP/s of causal attention work"
+
+
+def attn_prefill_fused(ctx: int = 8192, t: int = 2048):
+    """The same chunk on the fused warp-level kernel (8 query rows per group, one KV split)."""
+    hq, hkv, hd, kp, vp, bt, q, qraw = _prefill_attn_case(ctx, t)
+    ng = t // 8
+    po = torch.empty(t * hq * hd, device=dev)
+    pml = torch.empty(t * hq * 2, device=dev)
+    ctxs = (torch.arange(ng, dtype=torch.int32, device=dev) * 8 + (ctx - t) + 8).contiguous()
+    rows = torch.zeros(ng, dtype=torch.int32, device=dev)
+    out = torch.empty(t, hq * hd, dtype=torch.float16, device=dev)
+
+    def f():
+        K.paged_attn(q, kp, vp, bt, rows, ctxs, po, pml, ng, 8, hq, hkv, hd, bt.shape[1], 1, 1 / math.sqrt(hd))
+        K.attn_reduce(po, pml, 1, qraw, hq * 2 * hd, t, hq, out=out)
+    ms = timed(f)
+    flops = 4 * hq * hd * (t * (ctx - t) + t * t / 2)
+    return ms, f"{flops / ms / 1e9:.0f} TFLOP/s of causal attention work"
 
 
 def gdn_decode():

@@ -322,8 +322,8 @@ def attn_reduce(part_o, part_ml, splits: int, qraw, ldq: int, rows: int, hq: int
 
 
 register("owl_kv_gather", [_P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P, _P, _P])
-register("owl_causal_softmax", [_P, _I, _I, _I, _I, _F, _I, _P])
-register("owl_attn_gate", [_P, _P, _I, _I, _P, _I, _I, _I, _I, _P])
+register("owl_causal_softmax", [_P, _I, _I, _I, _I, _F, _I, _P, _P])
+register("owl_attn_gate", [_P, _P, _I, _I, _P, _I, _I, _I, _I, _P, _P])
 register("owl_q_group", [_P, _P, _I, _I, _I, _I, _P])
 register("owl_f16_gemm_persist_f16out", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P])
 
@@ -341,6 +341,7 @@ def attn_gemm_prefill(q, k_pool, v_pool, scales, bt_row, pos0: int, t: int, hq: 
     call("owl_kv_gather", ptr(k_pool), ptr(v_pool), ptr(scales[0]) if scales else None, ptr(scales[1]) if scales else None, fmt,
          ptr(bt_row), ctx, ctx_pad, hkv, hd, ptr(kb), ptr(vt), stream())
     gq, st = hq // hkv, stream()
+    inv = ws["inv"][:hq * t]            # 1 / softmax denominator per (head, token), applied with the gate
     if ws.get("grouped", True):
         # the gq q heads of a kv head as consecutive rows: one GEMM pair per kv head, K and V^T read once for all of them
         qg, og = ws["qg"][:hq * t * hd], ws["og"][:hq * t * hd]
@@ -349,19 +350,19 @@ def attn_gemm_prefill(q, k_pool, v_pool, scales, bt_row, pos0: int, t: int, hq: 
         for kh in range(hkv):
             call("owl_f16_gemm_persist_f16out", qg.data_ptr() + kh * t * gq * hd * 2, hd, kb.data_ptr() + kh * ctx_pad * hd * 2, hd,
                  ptr(s), t * gq, ctx_pad, hd, ctx_pad, 1, st)
-            call("owl_causal_softmax", ptr(s), t * gq, ctx_pad, ctx_pad, pos0, scale, gq, st)
+            call("owl_causal_softmax", ptr(s), t * gq, ctx_pad, ctx_pad, pos0, scale, gq, inv.data_ptr() + kh * t * gq * 4, st)
             call("owl_f16_gemm_persist", ptr(s), ctx_pad, vt.data_ptr() + kh * hd * ctx_pad * 2, ctx_pad,
                  og.data_ptr() + kh * t * gq * hd * 2, t * gq, hd, ctx_pad, hd, 0, st)
-        call("owl_attn_gate", ptr(og), ptr(qraw), ldq, hd, ptr(out), t, hq * hd, _is_f16(out), gq, st)
+        call("owl_attn_gate", ptr(og), ptr(qraw), ldq, hd, ptr(out), t, hq * hd, _is_f16(out), gq, ptr(inv), st)
         return
     for h in range(hq):
         kh = h // gq
         call("owl_f16_gemm_persist_f16out", q.data_ptr() + h * hd * 2, hq * hd, kb.data_ptr() + kh * ctx_pad * hd * 2, hd, ptr(s),
              t, ctx_pad, hd, ctx_pad, 1, st)
-        call("owl_causal_softmax", ptr(s), t, ctx_pad, ctx_pad, pos0, scale, 1, st)
+        call("owl_causal_softmax", ptr(s), t, ctx_pad, ctx_pad, pos0, scale, 1, inv.data_ptr() + h * t * 4, st)
         call("owl_f16_gemm_persist", ptr(s), ctx_pad, vt.data_ptr() + kh * hd * ctx_pad * 2, ctx_pad, o.data_ptr() + h * hd * 2,
              t, hd, ctx_pad, hq * hd, 0, st)
-    call("owl_attn_gate", ptr(o), ptr(qraw), ldq, hd, ptr(out), t, hq * hd, _is_f16(out), 0, st)
+    call("owl_attn_gate", ptr(o), ptr(qraw), ldq, hd, ptr(out), t, hq * hd, _is_f16(out), 0, ptr(inv), st)
 
 
 def attn_gemm_ws(device, t: int, max_ctx: int, hq: int, hkv: int, hd: int) -> dict:
@@ -372,7 +373,8 @@ def attn_gemm_ws(device, t: int, max_ctx: int, hq: int, hkv: int, hd: int) -> di
             "s": torch.zeros(t * (hq // hkv) * cp, dtype=torch.float16, device=device),
             "o": torch.zeros(t * hq * hd, dtype=torch.bfloat16, device=device),
             "qg": torch.zeros(t * hq * hd, dtype=torch.bfloat16, device=device),
-            "og": torch.zeros(t * hq * hd, dtype=torch.bfloat16, device=device), "t": t, "ctx": cp, "grouped": True}
+            "og": torch.zeros(t * hq * hd, dtype=torch.bfloat16, device=device),
+            "inv": torch.zeros(t * hq, dtype=torch.float32, device=device), "t": t, "ctx": cp, "grouped": True}
 
 
 register("owl_topk", [_P, _I, _I, _I, _I, _P, _P, _I, _F, _I, _P, _P, _I, _P, _P, _P])

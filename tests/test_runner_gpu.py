@@ -3,6 +3,7 @@ import pytest
 import torch
 
 from owl_engine_b200.models import hybrid as H
+from owl_engine_b200.ops import kernels as K
 from owl_engine_b200.models.reference import RefModel, init_weights
 from owl_engine_b200.models.spec import test_hybrid as make_spec
 
@@ -147,9 +148,12 @@ def test_gemm_form_prefill_attention_matches_the_fused_kernel_and_the_reference(
     written by the first."""
     g = torch.Generator().manual_seed(0)
     outs = {}
-    for arm in ("gemm", "fused"):
+    for arm in ("gemm", "gemm_flat", "fused"):
         spec, run, ref = build("tc", kv_dtype=kv_dtype)
-        run.ATTN_GEMM_FROM = 128 if arm == "gemm" else 0
+        run.ATTN_GEMM_FROM = 128 if arm != "fused" else 0
+        if arm == "gemm_flat":       # one GEMM pair per q head instead of per kv head
+            run._attn_ws = K.attn_gemm_ws(DEV, 128, 256, spec.hq, spec.hkv, spec.hd)
+            run._attn_ws["grouped"] = False
         prompt = torch.randint(0, spec.vocab, (256,), generator=torch.Generator().manual_seed(1))
         seq_row, slot = 1, 2
         run.block_table[seq_row, :16] = torch.arange(16, 32, dtype=torch.int32, device=DEV).flip(0)
@@ -158,12 +162,12 @@ def test_gemm_form_prefill_attention_matches_the_fused_kernel_and_the_reference(
         run.prefill_chunk_forward(ids[128:], 128, seq_row, slot)
         torch.cuda.synchronize()
         outs[arm] = run.logits[:1].float().cpu()
-        if arm == "gemm":
+        if arm != "fused":
             assert run._attn_ws is not None
             from owl_engine_b200.ops import gemm_tc
             assert gemm_tc.gemm_status() == 0
     want = ref.logits(ref.forward(prompt, ref.new_state())[-1:])
-    assert rel_err(outs["gemm"], outs["fused"]) < 0.02
+    assert rel_err(outs["gemm"], outs["fused"]) < 0.02 and rel_err(outs["gemm_flat"], outs["fused"]) < 0.02
     assert rel_err(outs["gemm"], want) < 0.05
 
 
