@@ -869,7 +869,7 @@ class HybridRunner:
     SP_FROM = 256       # tokens per chunk from which the sequence-parallel fused path is used under tensor parallelism
 
     # keys from which a prefill chunk's attention runs as tcgen05 GEMMs (0: never)
-    ATTN_GEMM_FROM = int(os.environ.get("OWL_ATTN_GEMM_FROM", "4096"))
+    ATTN_GEMM_FROM = int(os.environ.get("OWL_ATTN_GEMM_FROM", "2048"))
 
     def _prefill_attention(self, ws, pool, fi: int, wide, mix, t: int, pos0: int, seq_row: int, ng: int, tail: int) -> None:
         """Causal attention of a prefill chunk over the sequence's pages. Short contexts: the fused warp-level kernel (8 query
