@@ -877,7 +877,7 @@ class HybridRunner:
         between them (``K.attn_gemm_prefill``): the fused kernel's tensor path tops out near 60 TFLOP/s of attention work."""
         sp = self.spec
         ctx = pos0 + t
-        if self.ATTN_GEMM_FROM and ctx >= self.ATTN_GEMM_FROM and t >= 128 and sp.hd == 256:
+        if self.ATTN_GEMM_FROM and ctx >= self.ATTN_GEMM_FROM and t >= 32 and sp.hd == 256:
             aw = self._attn_ws
             if aw is None or aw["t"] < t or aw["ctx"] < ctx:
                 cap = max(ctx, 2 * (aw["ctx"] if aw else 0), 8192)

@@ -152,14 +152,14 @@ def test_gemm_form_prefill_attention_matches_the_fused_kernel_and_the_reference(
         spec, run, ref = build("tc", kv_dtype=kv_dtype)
         run.ATTN_GEMM_FROM = 128 if arm != "fused" else 0
         if arm == "gemm_flat":       # one GEMM pair per q head instead of per kv head
-            run._attn_ws = K.attn_gemm_ws(DEV, 128, 256, spec.hq, spec.hkv, spec.hd)
+            run._attn_ws = K.attn_gemm_ws(DEV, 216, 256, spec.hq, spec.hkv, spec.hd)
             run._attn_ws["grouped"] = False
         prompt = torch.randint(0, spec.vocab, (256,), generator=torch.Generator().manual_seed(1))
         seq_row, slot = 1, 2
         run.block_table[seq_row, :16] = torch.arange(16, 32, dtype=torch.int32, device=DEV).flip(0)
         ids = prompt.to(torch.int32).to(DEV)
-        run.prefill_chunk_forward(ids[:128], 0, seq_row, slot, want_logits=False)
-        run.prefill_chunk_forward(ids[128:], 128, seq_row, slot)
+        run.prefill_chunk_forward(ids[:216], 0, seq_row, slot, want_logits=False)
+        run.prefill_chunk_forward(ids[216:], 216, seq_row, slot)           # a 40-row tail chunk over 256 keys
         torch.cuda.synchronize()
         outs[arm] = run.logits[:1].float().cpu()
         if arm != "fused":
