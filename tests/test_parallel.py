@@ -69,3 +69,21 @@ def test_host_relay_allreduce_between_two_cpu_ranks():
     for p in procs:
         p.join(timeout=30)
     assert res == [(0, 96.0), (1, 96.0)]
+
+
+def test_27b_shards_meet_the_kernel_alignments_at_2_4_8_ranks():
+    """Per-rank shapes of the 27B preset at every supported world size: record widths (k multiples of 128), GEMM tile widths and
+    whole head groups, which the weight-streaming and tcgen05 kernels require; kv heads are replicated past 4 ranks."""
+    from owl_engine_b200.models.spec import qwen_27b
+
+    full = qwen_27b()
+    for world in (2, 4, 8):
+        for rank in (0, world - 1):
+            sp = full.sharded(rank, world)
+            assert sp.tp_world == world and sp.tp_rank == rank and sp.hidden == full.hidden
+            assert sp.inter * world == full.inter and sp.inter % 128 == 0            # down-proj k, gate/up rows
+            assert sp.hq * world == full.hq and sp.hq % sp.hkv == 0 and sp.hq // sp.hkv <= 8
+            assert sp.hkv == max(1, full.hkv // world) and sp.kv_replicas == max(1, world // full.hkv)
+            assert (sp.hq * sp.hd) % 128 == 0                                       # o-proj k
+            assert sp.nk * world == full.nk and sp.nv * world == full.nv and sp.nv % sp.nk == 0
+            assert sp.value_dim % 128 == 0 and (sp.conv_dim + sp.value_dim) % 16 == 0
