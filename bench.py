@@ -86,8 +86,9 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--prompt-len", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (result marked invalid)")
-    ap.add_argument("--gemv", default="dp4a", choices=["dp4a", "tc"],
-                    help="W4 decode arm: legacy streaming kernels or the tcgen05 streaming kernel")
+    ap.add_argument("--gemv", default="fma", choices=["fma", "dp4a", "tc"],
+                    help="W4 decode arm: the half-precision FMA projection with fused norm / residual / activation (fma), the "
+                         "integer streaming kernels (dp4a) or the tcgen05 streaming kernel (tc)")
     ap.add_argument("--sp-prefill", type=int, default=-1, choices=[-1, 0, 1],
                     help="N > 1: prefill through the GEMM-fused reduce-scatter / all-gather path (1), the all-reduce path (0), "
                          "or the runner's default (-1)")
@@ -227,7 +228,11 @@ def main() -> None:
     if comm:
         dev_ms = comm.max_over_ranks(dev_ms)
 
-    status = K.skinny_status()
+    # every bounded-wait status word of the native library (0 = no wait ran out anywhere), worst over the ranks
+    status = K.all_status()
+    if comm:
+        status = {k: int(comm.max_over_ranks(float(abs(v)))) for k, v in status.items()}
+    bad_status = {k: v for k, v in status.items() if v}
     if rank == 0:
         ms_per_step = dev_ms / steps
         value = 1000.0 / ms_per_step
@@ -261,6 +266,8 @@ def main() -> None:
         }
         if args.layers is not None:
             out["invalid"] = "debug run with fewer layers"
+        if bad_status:
+            out["invalid"] = f"a bounded wait ran out inside a kernel: {bad_status}"
         print(json.dumps(out))
     if comm:
         import torch.distributed as dist

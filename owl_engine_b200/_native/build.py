@@ -106,7 +106,7 @@ def build_host(force: bool = False) -> Path | None:
         return HOST_LIB
     OBJ.mkdir(exist_ok=True)
     cxx = shutil.which("g++") or "g++"
-    _run([cxx, *CXX_FLAGS, "-shared", "-I", str(CSRC / "host"), "-o", str(HOST_LIB), *map(str, srcs)])
+    _run([cxx, *CXX_FLAGS, "-shared", "-I", str(CSRC / "host"), "-o", str(HOST_LIB), *map(str, srcs), "-lrt"])
     stamp.write_text(dig)
     return HOST_LIB
 

@@ -41,7 +41,9 @@ class EngineConfig:
     pdl: bool = True
     prefill_gemm: str = "tc"
     act_bits: int = 15             # decode activations: 15-bit fixed point, or 8 (the W4A8 decode arm, `[model] quant = "w4a8"`)
-    decode_gemv: str = "dp4a"      # W4 decode arm: "dp4a" (legacy streaming kernels) or "tc" (tcgen05 streaming kernel)
+    decode_gemv: str = "fma"       # W4 decode arm: "fma" (one-token steps on the half-precision FMA projection with fused norm /
+                                   # residual / activation; other row counts on the integer arm), "dp4a" (integer arm only) or
+                                   # "tc" (tcgen05 streaming kernel, block-major records)
     seed: int = 0
     n_layers: int | None = None    # override (tests / smoke)
     snap_cut: bool = False         # cut a separate chunk at the prompt's last block boundary instead of snapshotting inside a chunk
@@ -50,6 +52,7 @@ class EngineConfig:
                                    # view of sink + recent + best-scoring blocks, re-selected at every block boundary
     kvmem_sink: int = 2
     kvmem_recent: int = 4
+    vocab_split: bool = True       # tensor parallel: each rank holds vocab / world lm_head rows and the winners are merged
 
 
 @dataclass
@@ -93,6 +96,7 @@ class Engine:
         self.weights = weights or H.random_weights(self.spec, self.device, group=cfg.group, seed=cfg.seed + rank * 7919,
                                                    lm_head_int8=cfg.lm_head_int8,
                                                    layout="block" if cfg.decode_gemv == "tc" else "slice",
+                                                   vocab_split=cfg.vocab_split,
                                                    quant="nvfp4" if cfg.quant == "nvfp4" else "w4a16")
         # GDN rows: one per sequence slot, the prefix-snapshot rows, and one scratch row for speculative rollback
         self.pool = H.StatePool(self.spec, self.device, cfg.n_pages, cfg.n_slots + cfg.n_snap_rows + 1, kv_dtype=cfg.kv_dtype)
@@ -101,6 +105,7 @@ class Engine:
         self.runner = H.HybridRunner(self.spec, self.weights, self.pool, max_seqs=cfg.max_seqs * (2 if cfg.kvmem_budget else 1),
                                      max_blocks=self.max_blocks, prefill_chunk=cfg.prefill_chunk, comm=comm,
                                      pdl=cfg.pdl, prefill_gemm=cfg.prefill_gemm)
+        self.runner.decode_gemv = cfg.decode_gemv
         if cfg.act_bits != 15:
             assert cfg.act_bits == 8, "act_bits is 15 or 8"
             self.runner.act_bits = 8
@@ -477,6 +482,7 @@ class Engine:
         torch.cuda.current_stream().synchronize()
         self.h2d_bytes += n * 4
         self.d2h_bytes += b * 4
+        self._check_status()
         out = []
         for i, sid in enumerate(sids):
             seq = self.seqs[sid]
@@ -485,6 +491,32 @@ class Engine:
             seq.tokens.append(t)
             out.append(t)
         return out
+
+    STATUS_EVERY = 16      # steps between reads of the kernels' bounded-wait status words on a tensor-parallel rank
+
+    def _check_status(self, force: bool = False) -> None:
+        """Read the native library's bounded-wait status words at the step's existing host sync point. A kernel whose wait
+        for a copy, an MMA or a peer flag ran out finishes on stale data, so the tokens of such a step must not be emitted:
+        the step raises, its turns fail, and under tensor parallelism the rank leaves the hand-written collectives for the
+        library arm (every rank runs the same check on the same step count, so they switch together). Single-GPU steps
+        check every ``STATUS_EVERY`` x 8 steps (only copy / MMA waits exist there), tensor-parallel ones every
+        ``STATUS_EVERY``."""
+        self._status_tick = getattr(self, "_status_tick", 0) + 1
+        every = self.STATUS_EVERY * (1 if self.comm is not None else 8)
+        if not force and self._status_tick % every:
+            return
+        bad = {k: v for k, v in K.all_status().items() if v}
+        if not bad:
+            return
+        if self.comm is not None and getattr(self.comm, "symm", None) is not None:
+            self.comm.symm, self.comm.mode = None, "nccl"
+            self.runner.graphs.clear()
+        raise RuntimeError(f"a bounded wait ran out inside a kernel ({bad}): the step's output is discarded")
+
+    def set_last_token(self, sid: int, tok: int) -> None:
+        """Replace the sequence's newest token (the host sampled something other than the device's argmax). The next
+        step reads it as its input, so under tensor parallelism this call is mirrored to every rank."""
+        self.seqs[sid].tokens[-1] = int(tok)
 
     def _kvmem_view(self, seq: Sequence, pos: int) -> int:
         """Bounded attention view of a long sequence: sink blocks + recent blocks + the best-scoring blocks of the rest,

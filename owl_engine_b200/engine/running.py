@@ -111,7 +111,10 @@ class RunningEngine:
                 continue
             fed = self.e.seqs[t.sid].n_cached if t.sid is not None else 0
             need = (len(t.tokens) + t.opts.max_new + PAGE - 1) // PAGE
-            out.append(TurnView(t.turn, t.state, len(t.tokens), fed, need, self.spec_runner is not None, t.arrival))
+            # the speculative round accepts by greedy agreement: sampled turns decode plainly so that temperature / top-p /
+            # seed keep their meaning
+            spec = self.spec_runner is not None and t.opts.sampling.mode == "greedy"
+            out.append(TurnView(t.turn, t.state, len(t.tokens), fed, need, spec, t.arrival))
         return out
 
     def pump(self) -> bool:
@@ -127,7 +130,7 @@ class RunningEngine:
                                              self.reservations.outstanding, self.e.cfg.n_pages,
                                              min(len(self.e.states.free_rows), len(self.e.free_rows)))
         for r in rejected:
-            t = self.turns[r]
+            t = self.turns.pop(r)          # terminal: the ledger forgets the turn once its last event is out
             t.state = DONE
             t.sink.put(("failed", r, "rejected: the request does not fit the KV pool / no free slot"))
         if step.kind == "idle":
@@ -138,8 +141,8 @@ class RunningEngine:
         except Exception as ex:  # a failed step fails its turns, the engine keeps serving
             log.error("engine.pump", f"{step.kind} failed: {ex!r}")
             for tid in step.turns:
-                t = self.turns[tid]
-                if t.state != DONE:
+                t = self.turns.get(tid)
+                if t is not None and t.state != DONE:
                     self._finish(t, "failed", error=repr(ex))
         return True
 
@@ -241,6 +244,10 @@ class RunningEngine:
             t.state = DECODE
             if self.spec_runner is not None:
                 self.spec_runner.after_prefill(self.e, t.sid)
+            if t.opts.sampling.mode != "greedy":
+                # the prefill returns the argmax of its last row; a sampled turn draws its first token from the same logits
+                tok = self._resample(t, 0)
+                self.e.set_last_token(t.sid, tok)
             self._emit(t, tok)
 
     def _do_decode(self, step) -> None:
@@ -251,7 +258,7 @@ class RunningEngine:
             tok = toks[i]
             if t.opts.sampling.mode != "greedy":
                 tok = self._resample(t, i)
-                self.e.seqs[t.sid].tokens[-1] = tok
+                self.e.set_last_token(t.sid, tok)
             self._emit(t, tok)
 
     def _do_spec(self, step) -> None:
@@ -267,6 +274,10 @@ class RunningEngine:
         from ..ops import kernels as K
 
         r = self.e.runner
+        if r.vocab_split:
+            # every rank holds a slice of the logits: a per-rank draw would send the ranks down different sequences
+            raise RuntimeError("sampling modes other than greedy need the full logits on one rank: serve this profile with "
+                               "[parallel] vocab_split = false, or use greedy decoding")
         if not hasattr(self, "_topk"):
             self._topk = K.TopK(r.device, max_rows=r.MAX_ROWS, k=min(32, r.vocab_local))
             self._hist = torch.zeros(r.MAX_ROWS, 4096, dtype=torch.int32, device=r.device)
@@ -323,11 +334,14 @@ class RunningEngine:
             t.sink.put(("failed", t.turn, error or "failed"))
         else:
             t.sink.put(("completed", t.turn, reason, usage))
+        # terminal event is out: drop the turn (tokens, history set, sink) so that a long-running server neither grows nor
+        # walks finished turns on every step; cancel_turn tolerates an unknown id
+        self.turns.pop(t.turn, None)
 
     # -- convenience ----------------------------------------------------------------------------
     def generate(self, tokens: list[int], opts: TurnOpts | None = None) -> list[int]:
         tid = self.submit(tokens, opts)
-        t = self.turns[tid]
+        t = self.turns[tid]             # held here: the ledger drops the turn when it finishes
         self.run_until_idle()
         out = []
         while not t.sink.empty():

@@ -55,6 +55,12 @@ class EngineService:
             # a callable spec_runner is a factory: draft heads need the engine (its runner, weights, pools)
             if callable(spec_runner) and not hasattr(spec_runner, "round"):
                 spec_runner = spec_runner(engine)
+            ring = getattr(engine, "_ring", None)
+            if ring is not None and spec_runner is not None:
+                # tensor-parallel leader: speculative rounds are mirrored to the follower ranks as whole calls
+                from .tp_serve import MirroredSpec
+
+                spec_runner = MirroredSpec(spec_runner, ring)
             self.re = RunningEngine(engine, max_batch, on_full, spec_runner, **self._running_kw)
         except Exception as ex:
             self.boot_error = f"boot failed: {ex!r}\n{traceback.format_exc()}"
@@ -75,6 +81,9 @@ class EngineService:
         except Exception as ex:
             log.error("engine.service", traceback.format_exc())
             self.exit = ServiceExit("panic", 70, repr(ex))
+        finally:
+            if hasattr(self.re.e, "shutdown"):
+                self.re.e.shutdown()          # tensor-parallel leader: release the follower ranks, whatever ended the loop
 
     def _drain(self) -> bool:
         while True:

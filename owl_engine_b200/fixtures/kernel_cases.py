@@ -71,6 +71,37 @@ def gemv():
     return ms, f"{ws[0].records.numel() / ms / 1e9:.2f} TB/s"
 
 
+def gemv_fma(k: int = 5120, n: int = 34816, norm: bool = True):
+    """One-token W4A16 projection on the half-precision FMA arm: the gate / up shape with the fused RMSNorm prologue and the
+    silu * up epilogue (three weight copies, so every launch misses L2)."""
+    ws = [Q.random_skinny(n, k, 128, dev, seed=i) for i in range(3)]
+    h = torch.randn(k, device=dev).bfloat16()
+    nw = (torch.randn(k, device=dev) * 0.1).bfloat16()
+    out = torch.zeros(n // 2, dtype=torch.bfloat16, device=dev)
+    i = [0]
+
+    def f():
+        K.w4_fma(ws[i[0] % 3], h, out, norm_w=nw if norm else None, epi=K.EPI_SILU_MUL)
+        i[0] += 1
+    ms = timed(f)
+    return ms, f"{ws[0].records.numel() / ms / 1e9:.2f} TB/s"
+
+
+def gemv_fma_down():
+    """The down-projection shape (17408 -> 5120) with the residual epilogue."""
+    n, k = 5120, 17408
+    ws = [Q.random_skinny(n, k, 128, dev, seed=i) for i in range(4)]
+    x = torch.randn(k, device=dev).bfloat16()
+    hbuf = torch.zeros(n, dtype=torch.bfloat16, device=dev)
+    i = [0]
+
+    def f():
+        K.w4_fma(ws[i[0] % 4], x, hbuf, residual=hbuf, epi=K.EPI_RESIDUAL)
+        i[0] += 1
+    ms = timed(f)
+    return ms, f"{ws[0].records.numel() / ms / 1e9:.2f} TB/s"
+
+
 def attn(kv16: bool = False):
     hq, hkv, hd, ctx, b = 24, 4, 256, 32768, 4                              # 4 sequences x 32k tokens: 268 MB of fp8 KV
     pages = b * ctx // 16

@@ -385,6 +385,10 @@ class HybridRunner:
         self.pf_pipe = None             # explicit prefill pipe (parallel/symm.PrefillPipe); default: the communicator's
         self.sp_prefill = True          # tensor-parallel prefill through the GEMM-fused reduce-scatter / all-gather path
         self.gdn_save = None            # (qkvz [n_gdn, M, nq], ab [n_gdn, M, ldab]): GDN inputs of the last step, kept for fold()
+        # one-token steps: "fma" = the half-precision FMA projection with the norm / residual / activation glue folded in
+        # (5 launches per GDN layer, 7 per attention layer); "dp4a" = the integer arm with separate norm and pack launches
+        self.decode_gemv = "fma"
+        self.mix = bf(M, max(spec.value_dim, spec.hq * spec.hd))   # mixer output (GDN / attention) of the fused one-token path
 
     # -- step inputs -------------------------------------------------------------------------
     def views(self, lay: StepLayout):
@@ -612,6 +616,53 @@ class HybridRunner:
             K.argmax(self.logits, m, self.vocab_local, self.vocab_local, self.am_val, self.am_idx, self.am_parts,
                      self.out_tok, w.vocab_offset, pdl=self.pdl)
 
+    # -- one-token step on the FMA arm -----------------------------------------------------------
+    def _fma_ok(self, lay: StepLayout) -> bool:
+        """The fused one-token path applies: one row, slice-major group-128 int4 weights, 15-bit-equivalent activations, and no
+        mode that needs row-count-independent arithmetic (speculative verify reproduces plain decoding bit for bit on the
+        integer arm)."""
+        w0 = self.w.layers[0].gate_up if self.w.layers else None
+        return (self.decode_gemv == "fma" and lay.m == 1 and not self.uniform_rows and self.act_bits == 15
+                and getattr(w0, "layout", "") == "slice" and getattr(w0, "group", 0) == 128
+                and (self.comm is None or self.spec.tp_world == 1))
+
+    def _step_forward_fma(self, lay: StepLayout, v: dict, splits: int, ctx_hint: int) -> None:
+        """Layers of a one-token step with every projection on ``K.w4_fma``: the RMSNorm is the prologue of the column
+        projections, the residual add / silu * up their epilogue, the GDN a / b rows ride in the qkvz launch."""
+        sp, pdl = self.spec, self.pdl
+        h, mix, act = self.h[0], self.mix[0], self.act[0]
+        fi = gi = 0
+        for i, lw in enumerate(self.w.layers):
+            if lw.kind == "gdn":
+                qo, ao = (self.qkvz_out, self.ab_out) if self.gdn_save is None else (self.gdn_save[0][gi], self.gdn_save[1][gi])
+                K.w4_fma(lw.qkvz, h, qo[0], norm_w=lw.ln1, ab_w=lw.ab_dense, ab_out=ao[0], ab_rows=lw.ab_dense.shape[0],
+                         eps=sp.eps, pdl=pdl)
+                K.gdn_decode(qo, qo.shape[1], ao, self.ldab, lw.conv_w, lw.a_log, lw.dt_bias, lw.gamma,
+                             self.pool.conv_state[gi], self.pool.rec_state[gi], v["gslot"], out=self.mix, batch=lay.b, t=lay.t,
+                             nk=sp.nk, nv=sp.nv, group=self.G, eps=sp.eps, pdl=pdl)
+                K.w4_fma(lw.out_proj, mix, h, residual=h, epi=K.EPI_RESIDUAL, pdl=pdl)
+                gi += 1
+            else:
+                K.w4_fma(lw.qkv, h, self.qkv_out[0], norm_w=lw.ln1, eps=sp.eps, pdl=pdl)
+                qn = 2 * sp.hq * sp.hd
+                kraw, vraw = self.qkv_out[:, qn:], self.qkv_out[:, qn + sp.hkv * sp.hd:]
+                K.qknorm_rope_insert(self.qkv_out, self.qkv_n, kraw, self.qkv_n, vraw, self.qkv_n, lw.q_norm, lw.k_norm,
+                                     v["pos3"], self.inv_freq, self.section, v["kv_slot"], self.q_rope, self.pool.k_pool[fi],
+                                     self.pool.v_pool[fi], 1, sp.hq, sp.hkv, sp.hd, sp.rotary_dim, sp.eps, self.rope_scale,
+                                     pdl=pdl, scales=self.pool.scales(fi))
+                K.paged_attn(self.q_rope, self.pool.k_pool[fi], self.pool.v_pool[fi], self.block_table, v["bt_row"], v["ctx"],
+                             self.part_o, self.part_ml, lay.b, lay.t, sp.hq, sp.hkv, sp.hd, self.max_blocks, splits, self.scale,
+                             pdl=pdl, scales=self.pool.scales(fi))
+                K.attn_reduce(self.part_o, self.part_ml, splits, self.qkv_out, self.qkv_n, 1, sp.hq, out=self.mix,
+                              group=self.G, pdl=pdl)
+                K.w4_fma(lw.o_proj, mix, h, residual=h, epi=K.EPI_RESIDUAL, pdl=pdl)
+                fi += 1
+            K.w4_fma(lw.gate_up, h, act, norm_w=lw.ln2, epi=K.EPI_SILU_MUL, eps=sp.eps, pdl=pdl)
+            K.w4_fma(lw.down, act, h, residual=h, epi=K.EPI_RESIDUAL, pdl=pdl)
+            if self.taps is not None and i in self.taps:
+                self.taps[i][:1].copy_(self.h[:1])
+        self._norm(1, self.w.final_norm, want_xn=True, want_pack=False)
+
     # -- decode / verify step ------------------------------------------------------------------
     def step_forward(self, lay: StepLayout, *, ctx_hint: int = 2048, advance: bool = False, sample: bool = True) -> None:
         """One forward over ``lay.m`` rows whose inputs sit in ``self.inp``. Capturable."""
@@ -622,7 +673,11 @@ class HybridRunner:
         if self.pre_hook is not None:
             self.pre_hook(m)
         layers = self.w.layers
-        self._norm(m, layers[0].ln1, want_xn=layers[0].kind == "gdn")
+        if self._fma_ok(lay):
+            self._step_forward_fma(lay, v, splits, ctx_hint)
+            layers = ()
+        else:
+            self._norm(m, layers[0].ln1, want_xn=layers[0].kind == "gdn")
         fi = gi = 0
         for i, lw in enumerate(layers):
             if lw.kind == "gdn":

@@ -168,6 +168,45 @@ def dense_skinny(w, x, out, m: int, *, residual=None, epi: int = EPI_STORE, ldo:
              int(pdl), stream())
 
 
+register("owl_w4_fma", [_P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P])
+
+
+def w4_fma(w, x, out, *, norm_w=None, residual=None, epi: int = EPI_STORE, ab_w=None, ab_out=None, ab_rows: int = 0, x_out=None,
+           eps: float = 1e-6, one_plus_w: bool = True, groups_per_cta: int = 0, pdl: bool = False) -> None:
+    """One token: ``out = epilogue(dequant(w) @ prologue(x))`` on the half-precision FMA arm (``csrc/gemv_fma.cu``).
+
+    ``x`` bf16 ``[K]``: the activations, or with ``norm_w`` the residual stream, which the kernel RMS-normalises itself
+    (``* (1 + norm_w)``). ``epi``: ``EPI_STORE``, ``EPI_RESIDUAL`` (``out = residual + y``) or ``EPI_SILU_MUL`` (``out[N/2]``).
+    ``ab_w`` bf16 ``[ab_rows, K]``: dense rows multiplied with the same activations into ``ab_out``. ``x_out`` bf16 ``[K]``
+    receives the activations the kernel consumed (the normalised row)."""
+    assert w.layout == "slice" and w.group == 128, "w4_fma reads slice-major group-128 records"
+    call("owl_w4_fma", ptr(w.records), ptr(x), ptr(norm_w), ptr(out), ptr(residual), ptr(ab_w), ptr(ab_out), ab_rows,
+         ptr(x_out), w.n, w.k, int(norm_w is not None), epi, eps, int(one_plus_w), groups_per_cta, int(pdl), stream())
+
+
+def fma_status() -> int:
+    """First bounded-wait failure recorded by the FMA-arm projection kernels (0 = none); clears it."""
+    f = fn("owl_fma_status")
+    f.argtypes = []
+    return f()
+
+
+_STATUS_WORDS = {"skinny": "owl_skinny_status", "fma": "owl_fma_status", "stream_tc": "owl_stream_tc_status",
+                 "gemm": "owl_gemm_status", "gemm_dense": "owl_gemm_dense_status", "comm": "owl_comm_status"}
+
+
+def all_status() -> dict:
+    """Every bounded-wait status word of the native library, read and cleared: ``{name: code}`` with 0 = no wait ran out
+    since the last read. A non-zero word means a kernel gave up on a copy, an MMA or a peer flag and finished on stale
+    data, so whatever that step produced must be discarded."""
+    out = {}
+    for name, sym in _STATUS_WORDS.items():
+        f = fn(sym)
+        f.argtypes = []
+        out[name] = int(f())
+    return out
+
+
 def skinny_status() -> int:
     """First bounded-wait failure recorded by a weight-streaming kernel (0 = none); clears it."""
     f = fn("owl_skinny_status")

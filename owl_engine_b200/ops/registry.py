@@ -39,6 +39,8 @@ _T = [
     KernelSpec("owl_bf16_skinny", "gemv.cu", "gemv", gen="mma.sync+bulk-copy"),
     KernelSpec("owl_w8a16_skinny", "gemv.cu", "gemv", gen="mma.sync+bulk-copy"),
     KernelSpec("owl_skinny_status", "gemv.cu", "status", capture=False),
+    KernelSpec("owl_w4_fma", "gemv_fma.cu", "gemv", gen="hfma2+bulk-copy"),
+    KernelSpec("owl_fma_status", "gemv_fma.cu", "status", capture=False),
     KernelSpec("owl_w4a16_stream_tc", "gemv_tc.cu", "gemv", gen="tcgen05+tmem+bulk-copy"),
     KernelSpec("owl_stream_tc_status", "gemv_tc.cu", "status", capture=False),
     KernelSpec("owl_w4a16_gemm_tc", "gemm_tc.cu", "gemm", gen="tcgen05+tmem+tma"),

@@ -260,6 +260,9 @@ class App:
         finally:
             if lock:
                 lock.release()
+                # an idle session keeps no lock object: nobody holds it and nobody waits for it
+                if not lock.locked() and not getattr(lock, "_waiters", None) and self.session_locks.get(req.session) is lock:
+                    del self.session_locks[req.session]
             self.permits.release()
 
 

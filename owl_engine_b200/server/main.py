@@ -20,8 +20,47 @@ from ..utils import log
 from ..utils.memory import estimate
 
 
-def build_engine_factory(cfg: C.OwlConfig):
+def parallel_plan(cfg: C.OwlConfig, env=None) -> dict:
+    """``[parallel]`` against the launch environment: which rank this process is, which communicator arm it builds.
+    Every key is either honoured or refused here, before anything is allocated (the rule of the reference's profile
+    loader: refuse, never ignore). ``mode = "tp"`` needs one process per GPU (``torchrun --nproc-per-node N``)."""
+    import os
+
+    env = os.environ if env is None else env
+    p = cfg.values["parallel"]
+    world, rank = int(env.get("WORLD_SIZE", "1")), int(env.get("RANK", "0"))
+    local = int(env.get("LOCAL_RANK", rank))
+    if p["mode"] == "layer":
+        raise C.ConfigError("parallel.mode = \"layer\" is reserved: layer-split serving is not built")
+    if p["mode"] == "single":
+        if world > 1:
+            raise C.ConfigError(f"parallel.mode = \"single\" but the launcher started {world} ranks; use a tp profile "
+                                "or start one process")
+        return {"world": 1, "rank": 0, "local": 0, "comm_mode": None}
+    want = len(p["device"]) or world
+    if world == 1:
+        raise C.ConfigError(f"parallel.mode = \"tp\" serves with one process per GPU: start it as "
+                            f"python -m torch.distributed.run --nproc-per-node {max(want, 2)} --master-addr 127.0.0.1 "
+                            "-m owl_engine_b200.server.main -p <profile>")
+    if want != world:
+        raise C.ConfigError(f"parallel.device names {want} GPUs but the launcher started {world} ranks")
+    if world not in (2, 4, 8):
+        raise C.ConfigError(f"tensor parallelism is built for 2, 4 or 8 ranks, not {world}")
+    if p["tp_ar_f8"]:
+        raise C.ConfigError("parallel.tp_ar_f8 = true: the e4m3-payload all-reduce is not built; set it to false")
+    if p["tp_comm"] == "host":
+        comm_mode = "host"          # staged through pinned host memory (GPU pairs without peer access)
+    elif p["tp_comm"] == "nccl" or p["tp_ar"] == "nccl":
+        comm_mode = "nccl"
+    else:
+        comm_mode = "push" if p["tp_ar"] == "push" else "fused"
+    return {"world": world, "rank": rank, "local": local, "comm_mode": comm_mode, "multimem": p["tp_ar"] == "multimem",
+            "vocab_split": bool(p["tp_vocab_split"]), "fused_gemm": bool(p["tp_fused_gemm"])}
+
+
+def build_engine_factory(cfg: C.OwlConfig, plan: dict | None = None):
     v = cfg.values
+    plan = plan or {"world": 1, "rank": 0, "local": 0, "comm_mode": None}
 
     def build():
         import torch
@@ -29,7 +68,16 @@ def build_engine_factory(cfg: C.OwlConfig):
         from ..engine.core import Engine, EngineConfig
         from ..models.spec import PRESETS
 
-        torch.cuda.set_device(0)
+        comm = None
+        if plan["world"] > 1:
+            from ..parallel.comm import TpComm
+
+            hidden = PRESETS[v["model"]["name"]]().hidden if v["model"]["name"] in PRESETS else 5120
+            comm = TpComm.from_env(plan["comm_mode"], hidden=hidden, big_elems=v["runtime"]["prefill_chunk"] * hidden,
+                                   use_multimem=plan["multimem"])
+        else:
+            torch.cuda.set_device(plan["local"])
+        dev = torch.device(f"cuda:{torch.cuda.current_device()}")
         est = estimate(cfg)
         km = v["kvmem"]
         ecfg = EngineConfig(model=v["model"]["name"], group=v["model"]["group"],
@@ -44,18 +92,27 @@ def build_engine_factory(cfg: C.OwlConfig):
                             prefill_chunk=v["runtime"]["prefill_chunk"], pdl=v["kernel"]["pdl"],
                             prefill_gemm=v["kernel"]["prefill_gemm"], host_cache_mb=v["store"]["host_cache_mb"],
                             disk_cache_mb=v["store"]["disk_cache_mb"], disk_dir=v["store"]["disk_dir"],
-                            kv_dtype=v["store.kv"]["kv_dtype"])
+                            kv_dtype=v["store.kv"]["kv_dtype"], vocab_split=plan.get("vocab_split", True))
         if v["kernel"]["selfcheck"]:
             from ..ops import selfcheck
 
-            selfcheck.assert_ok(torch.device("cuda:0"))       # refuse to serve on a build whose kernels disagree with the host oracles
+            selfcheck.assert_ok(dev)       # refuse to serve on a build whose kernels disagree with the host oracles
         if v["model"]["format"] == "random" or not v["model"]["path"]:
-            return Engine(ecfg)
-        from ..formats.loader import load_model
+            eng = Engine(ecfg, comm=comm)
+        else:
+            from ..formats.loader import load_model
 
-        spec, weights = load_model(v["model"]["path"], torch.device("cuda:0"), spec=PRESETS.get(v["model"]["name"], lambda: None)(),
-                                   group=v["model"]["group"], lm_head_int8=ecfg.lm_head_int8)
-        return Engine(ecfg, spec=spec, weights=weights)
+            spec, weights = load_model(v["model"]["path"], dev, spec=PRESETS.get(v["model"]["name"], lambda: None)(),
+                                       rank=plan["rank"], world=plan["world"], group=v["model"]["group"],
+                                       lm_head_int8=ecfg.lm_head_int8, vocab_split=plan.get("vocab_split", True))
+            eng = Engine(ecfg, spec=spec, weights=weights, comm=comm)
+        if comm is not None:
+            eng.runner.sp_prefill = plan["fused_gemm"]
+            if plan["rank"] == 0:
+                from ..engine.tp_serve import MirroredEngine, leader_ring
+
+                return MirroredEngine(eng, leader_ring(plan["world"]))
+        return eng
     return build
 
 
@@ -101,6 +158,27 @@ def build_spec_factory(cfg: C.OwlConfig):
     return make
 
 
+def _leave_group(engine) -> None:
+    """End of a tensor-parallel rank: drop the captured graphs and the symmetric workspace, then leave the process group
+    together with the other ranks (no rank exits while a peer may still touch its memory)."""
+    comm = getattr(engine, "comm", None)
+    if comm is None:
+        return
+    import torch
+    import torch.distributed as dist
+
+    engine.runner.graphs.clear()
+    torch.cuda.synchronize()
+    try:
+        comm.barrier()
+    except Exception:    # noqa: BLE001  (a peer that already died cannot be waited for)
+        pass
+    comm.symm = None
+    torch.cuda.synchronize()
+    if dist.is_initialized():
+        dist.destroy_process_group()
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="owl-b200-server")
     ap.add_argument("-p", "--profile", required=True)
@@ -126,6 +204,11 @@ def main(argv=None) -> int:
         print(json.dumps(estimate(cfg), indent=1))
     if a.explain or a.print_config or a.check:
         return 0
+    try:
+        plan = parallel_plan(cfg)
+    except C.ConfigError as e:
+        print(f"config error: {e}", file=sys.stderr)
+        return 2
     lv = cfg.values["log"]
     log.LOG.configure(a.log_level or lv["level"], lv["tags_allow"], lv["tags_deny"], lv["timestamp"])
     from ..engine.sampler import SamplingParams
@@ -137,7 +220,20 @@ def main(argv=None) -> int:
 
     METRICS.set_level(cfg.values["probes"]["perf_level"])
     v = cfg.values
-    svc = EngineService(build_engine_factory(cfg), max_batch=v["runtime"]["max_batch"], on_full=v["runtime"]["admission_on_full"],
+    if plan["rank"] > 0:
+        # follower rank of a tensor-parallel job: no listener, no scheduler; apply the leader's step descriptors
+        from ..engine.tp_serve import follower_loop, follower_ring
+
+        engine = build_engine_factory(cfg, plan)()
+        make_spec = build_spec_factory(cfg)
+        spec_runner = make_spec(engine) if make_spec else None
+        ring = follower_ring(plan["rank"])
+        n = follower_loop(engine, ring, spec_runner)
+        log.info("tp.follower", f"rank {plan['rank']}: applied {n} descriptors, leaving")
+        ring.free()
+        _leave_group(engine)
+        return 0
+    svc = EngineService(build_engine_factory(cfg, plan), max_batch=v["runtime"]["max_batch"], on_full=v["runtime"]["admission_on_full"],
                         spec_runner=build_spec_factory(cfg),
                         running_kw={"park_sessions": bool(v["vision"]["image_evict"]), "max_parked": max(1, v["store.gdn"]["gdn_slots"] // 2)})
     client = svc.boot()
@@ -181,6 +277,8 @@ def main(argv=None) -> int:
     except KeyboardInterrupt:
         pass
     ex = svc.shutdown()
+    if svc.re is not None:
+        _leave_group(svc.re.e)
     if a.perf_dump:
         import os
         os.makedirs(a.perf_dump, exist_ok=True)

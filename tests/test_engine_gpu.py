@@ -72,10 +72,14 @@ def test_running_engine_batches_and_events():
     g = torch.Generator().manual_seed(1)
     prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (20, 70, 33)]
     solo = [RunningEngine(make_engine()).generate(p, TurnOpts(max_new=5)) for p in prompts]
-    tids = [re.submit(p, TurnOpts(max_new=5)) for p in prompts]
+    import queue
+
+    sinks = [queue.Queue() for _ in prompts]
+    tids = [re.submit(p, TurnOpts(max_new=5), sink=q) for p, q in zip(prompts, sinks)]
     re.run_until_idle()
-    for tid, want in zip(tids, solo):
-        evs = list(re.turns[tid].sink.queue)
+    assert not re.turns          # finished turns leave the ledger
+    for tid, want, q in zip(tids, solo, sinks):
+        evs = list(q.queue)
         toks = [e[2] for e in evs if e[0] == "token"]
         assert toks == want and evs[-1][0] == "completed" and evs[-1][2] == "length"
         assert evs[0][0] == "prefill"
@@ -89,12 +93,15 @@ def test_sampling_is_seeded_and_cancel_publishes():
     a = re.generate(p, o)
     b = re.generate(p, o)
     assert a == b and len(a) == 8
-    tid = re.submit(list(range(100, 180)), TurnOpts(max_new=50))
+    import queue
+
+    q = queue.Queue()
+    tid = re.submit(list(range(100, 180)), TurnOpts(max_new=50), sink=q)
     for _ in range(4):
         re.pump()
     re.cancel_turn(tid)
     re.run_until_idle()
-    assert list(re.turns[tid].sink.queue)[-1][2] == "cancelled"
+    assert list(q.queue)[-1][2] == "cancelled" and tid not in re.turns
     assert re.e.kv.stats()["nodes"] >= 4
 
 
