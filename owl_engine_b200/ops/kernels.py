@@ -6,6 +6,7 @@ failure. There is no fallback: CPU numerics live in ``ops/reference.py``.
 """
 from __future__ import annotations
 
+import collections
 import ctypes
 from ctypes import c_longlong, c_float, c_int, c_void_p
 
@@ -74,10 +75,28 @@ def stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+# Ring of the most recent native launches (entry name + raw arguments), formatted on demand by ``recent_launches``:
+# what ran last is the first question after a wrong token or a status word, and a captured graph hides it from the host.
+_LAUNCHES: collections.deque = collections.deque(maxlen=2048)
+_launch_seq = 0
+
+
 def call(name: str, *args) -> None:
+    global _launch_seq
     rc = fn(name)(*args)
+    _launch_seq += 1
+    _LAUNCHES.append((_launch_seq, name, args))
     if rc != 0:
         _native.check(rc, name)
+
+
+def recent_launches(n: int = 256) -> list[dict]:
+    """The last ``n`` launches: sequence number, entry, stream handle and the small integer arguments (shapes, modes)."""
+    out = []
+    for seq, name, args in list(_LAUNCHES)[-n:]:
+        ints = [a for a in args[:-1] if type(a) is int and -(1 << 31) <= a < (1 << 31)]
+        out.append({"seq": seq, "entry": name, "stream": args[-1] if args and isinstance(args[-1], int) else None, "ints": ints})
+    return out
 
 
 EPI_STORE, EPI_RESIDUAL, EPI_SILU_MUL, EPI_F32, EPI_SILU_PACK = 0, 1, 2, 3, 4

@@ -11,6 +11,7 @@ Reference counterpart: ``apps/server/src/{http,main,debug,agent_trace,load}.rs``
 from __future__ import annotations
 
 import asyncio
+import collections
 import json
 import queue as pyqueue
 import time
@@ -44,6 +45,7 @@ class App:
         self.guard = RepeatGuard()
         self.vision = vision      # Vision (tower + image cache + pad token id) or None: image parts are then refused
         self.started = time.time()
+        self.agent_trace: collections.deque = collections.deque(maxlen=64)   # per turn: the output splitter's structural trace
 
     # -- plumbing -------------------------------------------------------------------------------
     async def handle(self, reader: asyncio.StreamReader, writer: asyncio.StreamWriter) -> None:
@@ -153,10 +155,18 @@ class App:
         if parts[0] == "agent":
             if parts[1:] == ["clear"] and method == "POST":
                 q(lambda re: re.trace.clear())
+            if parts[1:] == ["clear"] and method == "POST":
+                self.agent_trace.clear()
             n = int(parts[1]) if len(parts) > 1 and parts[1].isdigit() else 64
+            if parts[1:2] == ["splitter"]:
+                return await self._send(w, 200, list(self.agent_trace)[-n:])
             return await self._send(w, 200, q(lambda re: re.trace[-n:]))
         if parts[0] == "launches":
-            return await self._send(w, 200, q(lambda re: {"graphs": [list(k) for k in re.e.runner.graphs.keys()]}))
+            n = int(parts[1]) if len(parts) > 1 and parts[1].isdigit() else 256
+            from ..ops import kernels as K
+
+            return await self._send(w, 200, q(lambda re: {"graphs": [list(k) for k in re.e.runner.graphs.keys()],
+                                                           "launches": K.recent_launches(n), "status": K.all_status()}))
         if parts[0] == "load" and method == "POST":
             return await self._send(w, 200, {"loaded": self.model})
         await self._send(w, 404, {"error": "unknown debug endpoint"})
@@ -206,7 +216,7 @@ class App:
             except ValueError as e:              # refused at the submit boundary (e.g. droppable marks with image_evict off)
                 raise BadRequest(str(e)) from None
             streamer = Streamer(self.model, StreamDecoder(self.tok), req.stop,
-                                start_in_think=prompt.rstrip().endswith("<think>"))
+                                start_in_think=prompt.rstrip().endswith("<think>"), tools=req.tools)
             if req.stream:
                 await self._sse_open(w)
             last_io, t_submit = time.time(), time.time()
@@ -252,6 +262,11 @@ class App:
             else:
                 streamer.drain()
                 await self._send(w, 200, streamer.full_response(reason, usage))
+            sp = streamer.splitter
+            self.agent_trace.append({"id": streamer.id, "session": req.session, "tool_calls": sp.n_calls, "malformed": sp.malformed,
+                                     "strays": sp.strays, "reasoning_tokens": sp.reasoning_steps, "trace": sp.trace()})
+            for m in streamer.malformed:
+                log.warn("server.toolcall", f"{streamer.id}: malformed tool block ({m['kind']}, {len(m['raw'])} B): {m['raw'][:2048]!r}")
             METRICS.event("server.turn", ms=(time.time() - t_submit) * 1e3, tokens=usage["completion_tokens"])
         except (ConnectionError, asyncio.IncompleteReadError):
             if turn is not None:

@@ -104,10 +104,11 @@ class ChatRequest:
 class Streamer:
     """Engine tokens -> OpenAI chunks. One instance per response."""
 
-    def __init__(self, model: str, decoder, stop: list[str], start_in_think: bool = False):
+    def __init__(self, model: str, decoder, stop: list[str], start_in_think: bool = False, tools=None):
         self.id = "chatcmpl-" + uuid.uuid4().hex[:24]
         self.model, self.created = model, int(time.time())
-        self.decoder, self.splitter = decoder, ChannelSplitter(start_in_think)
+        self.decoder, self.splitter = decoder, ChannelSplitter(start_in_think, tools=tools)
+        self.malformed: list = []        # tool blocks that could not be parsed (logged by the server, never emitted as text)
         self.stop, self.text_tail, self.stopped = stop, "", False
         self.content, self.reasoning, self.tool_calls = [], [], []
         self.first = True
@@ -136,6 +137,8 @@ class Streamer:
             elif ev[0] == "reasoning":
                 self.reasoning.append(ev[1])
                 delta["reasoning_content"] = ev[1]
+            elif ev[0] == "malformed":
+                self.malformed.append(ev[1])
             else:
                 i = len(self.tool_calls)
                 self.tool_calls.append(ev[1])
@@ -186,11 +189,11 @@ class Streamer:
         if not self.stopped:
             self._events_to_chunks(self._flush_tail())
 
-    @staticmethod
-    def usage(u: dict) -> dict:
+    def usage(self, u: dict) -> dict:
         return {"prompt_tokens": u["prompt_tokens"], "completion_tokens": u["completion_tokens"],
                 "total_tokens": u["prompt_tokens"] + u["completion_tokens"],
-                "prompt_tokens_details": {"cached_tokens": u.get("cached_tokens", 0)}}
+                "prompt_tokens_details": {"cached_tokens": u.get("cached_tokens", 0)},
+                "completion_tokens_details": {"reasoning_tokens": self.splitter.reasoning_steps}}
 
     def full_response(self, reason: str, usage: dict) -> dict:
         msg = {"role": "assistant", "content": "".join(self.content)}
