@@ -182,8 +182,9 @@ struct PushNormParams {
   const __nv_bfloat16* slots;  // local [world][push_rows][H]
   const uint32_t* flags;       // local [world]: sequence numbers published by the peers' GEMVs
   uint32_t* counters;          // private per-row sequence counters [rows]
+  const uint32_t* seq_src;     // when set: the expected sequence number is read here (the local producer's word) instead
   __nv_bfloat16* h; const __nv_bfloat16* w; __nv_bfloat16* normed; uint4* xpack; float2* xs;
-  int H, G, world, push_rows, one_plus_w;
+  int H, G, world, ranks, push_rows, one_plus_w;    // world: slots to add (ranks x k parts); ranks: flags to wait for
   float eps;
   uint32_t spin_limit;
 };
@@ -193,9 +194,12 @@ __global__ void __launch_bounds__(1024) push_residual_norm_kernel(PushNormParams
   pdl_launch_dependents();
   pdl_wait();
   const int row = blockIdx.x;
-  if (threadIdx.x == 0) { s_seq = p.counters[row] + 1; p.counters[row] = s_seq; }
+  if (threadIdx.x == 0) {
+    if (p.seq_src) { s_seq = *p.seq_src; }
+    else { s_seq = p.counters[row] + 1; p.counters[row] = s_seq; }
+  }
   __syncthreads();
-  if (threadIdx.x < p.world) {
+  if (threadIdx.x < p.ranks) {
     bool got = false;
     for (uint32_t i = 0; i < p.spin_limit; ++i) {
       if ((int)(ld_acquire_sys(p.flags + threadIdx.x) - s_seq) >= 0) { got = true; break; }
@@ -462,9 +466,14 @@ OWL_API int owl_ar_residual_norm(const void* const* part_ptrs, const void* mc_pa
 // counters: private uint32 [M] (zero before the first call).
 OWL_API int owl_push_residual_norm(const void* slots, const void* flags, void* counters, void* h, const void* w,
                                    void* normed, void* xpack, void* xs, int M, int H, int G, int world, int push_rows,
-                                   float eps, int one_plus_w, unsigned spin_limit, int pdl, cudaStream_t st) {
-  if (M < 1 || M > push_rows || (H & 127) || world < 2 || world > MAX_RANKS || !actpack_group_ok(G, M)) return OWL_ERR_BAD_ARG;
+                                   float eps, int one_plus_w, unsigned spin_limit, const void* seq_src, int kparts, int pdl,
+                                   cudaStream_t st) {
+  if (M < 1 || M > push_rows || (H & 127) || world < 1 || kparts < 1 || world * kparts > MAX_RANKS || !actpack_group_ok(G, M))
+    return OWL_ERR_BAD_ARG;
   PushNormParams p = {};
+  p.seq_src = (const uint32_t*)seq_src;
+  p.ranks = world;
+  world *= kparts;          // slots [rank * kparts + part]
   p.slots = (const __nv_bfloat16*)slots; p.flags = (const uint32_t*)flags; p.counters = (uint32_t*)counters;
   p.h = (__nv_bfloat16*)h; p.w = (const __nv_bfloat16*)w; p.normed = (__nv_bfloat16*)normed; p.xpack = (uint4*)xpack;
   p.xs = (float2*)xs; p.H = H; p.G = G; p.world = world; p.push_rows = push_rows; p.one_plus_w = one_plus_w; p.eps = eps;

@@ -322,6 +322,10 @@ static int gd_map(CUtensorMap* m, const void* ptr, int rows, int K, int ld, int 
 }  // namespace owl
 using namespace owl;
 
+constexpr int GD_MAX_DEV = 64;
+static float* g_ks_scratch[GD_MAX_DEV] = {nullptr};
+static size_t g_ks_scratch_bytes[GD_MAX_DEV] = {0};
+
 static int gd_launch(const void* x, int ldx, const void* w, int ldw, GdParams& p, int mode, cudaStream_t st) {
   const int kmask = p.fmt == 2 ? 127 : 63, ldmask = p.fmt == 2 ? 15 : 7;
   if (p.T < 1 || p.N < 1 || p.K <= kmask || (p.K & kmask) || (ldx & ldmask) || (ldw & ldmask) || (p.ldo & 7) || p.fmt < 0 ||
@@ -348,10 +352,12 @@ static int gd_launch(const void* x, int ldx, const void* w, int ldw, GdParams& p
   }
   int tiles = p.m_tiles * p.n_tiles;
   // few output tiles (small T and a narrow weight): cut k so that every SM streams a share of the weight; the fp32
-  // partial tiles (at most 148 tiles of 128 x 256 floats = 19.4 MB) live in a per-process scratch allocated on first use
-  // (outside any stream capture: the warm-up call of a captured step comes first)
-  static float* ks_scratch = nullptr;
-  constexpr size_t KS_SCRATCH = (size_t)160 * GD_BM * GD_BN * sizeof(float);
+  // partial tiles (at most 148 tiles of 128 x 256 floats = 19.4 MB) live in a scratch buffer the CALLER registers per
+  // device (owl_gemm_dense_set_scratch): this launcher never allocates; without a scratch the product runs unsplit
+  int dev_id = 0;
+  cudaGetDevice(&dev_id);
+  float* ks_scratch = (dev_id >= 0 && dev_id < GD_MAX_DEV) ? g_ks_scratch[dev_id] : nullptr;
+  const size_t KS_SCRATCH = (dev_id >= 0 && dev_id < GD_MAX_DEV) ? g_ks_scratch_bytes[dev_id] : 0;
   p.ksplit = 1;
   const int KIs = p.K / (p.fmt == 2 ? 2 * GD_BK : GD_BK);
   if ((mode == 0 || mode == 3) && !p.out_f16 && tiles * 2 <= sms && KIs >= 8) {
@@ -360,7 +366,6 @@ static int gd_launch(const void* x, int ldx, const void* w, int ldw, GdParams& p
     if (ks > 16) ks = 16;
     p.ldp = p.n_tiles * GD_BN;
     if (ks > 1 && (size_t)ks * p.T * p.ldp * sizeof(float) <= KS_SCRATCH) {
-      if (!ks_scratch && cudaMalloc(&ks_scratch, KS_SCRATCH) != cudaSuccess) ks_scratch = nullptr;
       if (ks_scratch) { p.ksplit = ks; p.partial = ks_scratch; tiles *= ks; }
     }
   }
@@ -438,6 +443,17 @@ OWL_API int owl_f16_gemm_rs(const void* x, int ldx, const void* w, int ldw, int 
     p.rs_flag[r] = (uint32_t*)flag[r];
   }
   return gd_launch(x, ldx, w, ldw, p, 2, st);
+}
+
+// Registers (or with a null pointer removes) the split-K scratch of the current device: caller-owned device memory of at
+// least `bytes` bytes that lives as long as dense GEMMs may run. Recommended size: 160 tiles x 128 x 256 floats (21 MB).
+OWL_API int owl_gemm_dense_set_scratch(void* ptr, long long bytes) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= GD_MAX_DEV || bytes < 0) return OWL_ERR_BAD_ARG;
+  if (ptr && (reinterpret_cast<uintptr_t>(ptr) & 15)) return OWL_ERR_BAD_ARG;
+  g_ks_scratch[dev] = (float*)ptr;
+  g_ks_scratch_bytes[dev] = ptr ? (size_t)bytes : 0;
+  return OWL_OK;
 }
 
 OWL_API int owl_gemm_dense_status() {

@@ -36,13 +36,12 @@ namespace owl {
 
 __device__ int g_fma_status = 0;   // first bounded-wait failure of this file's kernels (0 = none)
 
-enum { FMA_PLAIN = 0, FMA_NORM = 1 };
-enum { FEPI_STORE = 0, FEPI_RESIDUAL = 1, FEPI_SILU_MUL = 2 };
+enum { FMA_PLAIN = 0, FMA_NORM = 1, FMA_PULL = 2 };
+enum { FEPI_STORE = 0, FEPI_RESIDUAL = 1, FEPI_SILU_MUL = 2, FEPI_PUSH = 3 };
+constexpr int FM_MAX_RANKS = 8;
 
 constexpr int FM_REC = 1088;          // bytes per record (g128)
-constexpr int FM_SLOTS = 2;           // chunks in flight per warp
-constexpr int FM_CH = 2;              // records per chunk (one bulk copy, one mbarrier)
-constexpr int FM_SLOT_BYTES = FM_CH * FM_REC;
+constexpr int FM_STAGES = 4;          // records per warp ring: three in flight while one is consumed
 constexpr int FM_WARPS = 8;           // warps per group = k slices of the record order
 
 struct FmaParams {
@@ -58,7 +57,39 @@ struct FmaParams {
   int N, K, n_tiles;
   float eps;
   int one_plus;
+  int kparts;                       // FEPI_PUSH: every row tile is cut into this many k parts, each a unit of work of its own
+  // FEPI_PUSH (row-parallel projection): the partial sums of k part q go into slot [push_rank * kparts + q] of every
+  // rank's reduction buffer [world * kparts][push_rows][N] bf16 with plain (peer) stores while the matrix streams; the CTA
+  // that finishes last bumps the call site's sequence number and publishes it in every rank's flag word [push_rank]. With
+  // one rank this is a local split of the k range: a projection with few row tiles (N = hidden) gets kparts times as many
+  // units of work, and the consumer's prologue adds the parts.
+  __nv_bfloat16* push_dst[FM_MAX_RANKS];
+  uint32_t* push_flag[FM_MAX_RANKS];
+  int* push_count;                  // local: finished CTAs of this launch (returns to zero)
+  uint32_t* push_seq;               // local: sequence number of this call site
+  int push_rank, push_world, push_rows;
+  // FMA_PULL (the column-parallel projection that follows): wait until every rank's flag reached the local sequence
+  // number, x = residual stream + the slots in rank order (the same sum, bit for bit, on every rank), then the norm as in
+  // FMA_NORM. CTA 0 stores the new residual stream into h_out, a buffer other than x (the other CTAs still read x).
+  const __nv_bfloat16* pull_slots;  // local [world][pull_rows][K]
+  const uint32_t* pull_flags;       // local [world]
+  const uint32_t* pull_seq;         // local: the sequence number the local producer published last
+  __nv_bfloat16* h_out;
+  int pull_world, pull_ranks, pull_rows;      // slots to add (ranks x k parts), ranks whose flags to wait for
+  uint32_t spin_limit;
 };
+
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_relaxed_sys_u4(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
 
 __device__ __forceinline__ uint32_t hfma2_u(uint32_t a, uint32_t b, uint32_t c) {
   uint32_t d;
@@ -69,10 +100,13 @@ __device__ __forceinline__ float h2_sum(uint32_t v) {
   const __half2 h = *reinterpret_cast<const __half2*>(&v);
   return __low2float(h) + __high2float(h);
 }
-__device__ __forceinline__ void bulk_g2s_f(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+// 16-byte asynchronous copy global -> shared that bypasses L1 (every weight byte is read once).
+__device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gsrc) : "memory");
 }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 // Named barrier of one 8-warp group; the id is an immediate so that the CTA reserves only the barriers it uses.
 template <int VC>
 __device__ __forceinline__ void group_barrier(int vc) {
@@ -87,58 +121,67 @@ __device__ __forceinline__ void bf16x8_to_f(const uint4& a, float* v) {
 }
 
 __host__ __device__ constexpr int fma_smem_bytes(int vc, int k) {
-  return vc * FM_WARPS * FM_SLOTS * FM_SLOT_BYTES + vc * FM_WARPS * FM_SLOTS * 8 + k * 2 + (k / 128) * 4 +
-         vc * 2 * FM_WARPS * 16 * 4 + 2 * 32 * 4 + 64;
+  return vc * FM_WARPS * FM_STAGES * FM_REC + k * 2 + (k / 128) * 4 + vc * 2 * FM_WARPS * 16 * 4 + 2 * 32 * 4 + 64;
 }
 
 // VC groups of eight warps per CTA; the groups share the activation vector and nothing else.
 template <int VC, int MODE, int EPI>
 __global__ void __launch_bounds__(VC * FM_WARPS * 32, 4 / VC) w4_fma_kernel(FmaParams p) {
   constexpr int NT = VC * FM_WARPS * 32;
-  constexpr int FM_CACHE = MODE == FMA_NORM ? 2 : 3;   // activation chunks (8 values) kept in registers between the two prologue passes
+  constexpr bool NORMED = MODE != FMA_PLAIN;
+  constexpr int FM_CACHE = NORMED ? 2 : 3;   // activation chunks (8 values) kept in registers between the two prologue passes
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* ring_all = smem;
-  uint64_t* bars_all = reinterpret_cast<uint64_t*>(smem + VC * FM_WARPS * FM_SLOTS * FM_SLOT_BYTES);
-  uint4* xh4 = reinterpret_cast<uint4*>(bars_all + VC * FM_WARPS * FM_SLOTS);      // fp16 x' [K]
+  uint4* xh4 = reinterpret_cast<uint4*>(smem + VC * FM_WARPS * FM_STAGES * FM_REC);   // fp16 x' [K]
   float* xg = reinterpret_cast<float*>(xh4 + p.K / 8);                             // per 128-k group: sum(x') * 2^-24
   float* red = xg + p.K / 128;                                                     // [VC][2][8 warps][16 rows]
   float* pro = red + VC * 2 * FM_WARPS * 16;                                       // prologue reductions [2][32]
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int vc = warp / FM_WARPS, wi = warp % FM_WARPS, g = lane >> 2, t = lane & 3;
-  uint8_t* ring = ring_all + (size_t)warp * FM_SLOTS * FM_SLOT_BYTES;
-  uint64_t* bars = bars_all + warp * FM_SLOTS;
+  uint8_t* ring = ring_all + (size_t)warp * FM_STAGES * FM_REC;
 
-  // ---- this warp's stream: k slice wi of the row tiles of its group -----------------------------------------
+  // ---- this warp's stream -----------------------------------------------------------------------------------------
+  // Warp wi streams k slice wi: records [tile][record in slice], one contiguous run for the whole matrix. A unit of work
+  // is one row tile (or, with kparts > 1, one of the k parts of a tile: records [q * rpi / P, (q + 1) * rpi / P) of the
+  // tile in every slice); the groups of the grid take contiguous, equally long runs of units.
   const int KT = p.K / 128;
   const int n_groups = gridDim.x * VC, grp = blockIdx.x * VC + vc;
-  const int nt0 = (int)((long long)grp * p.n_tiles / n_groups);
-  const int n_items = (int)((long long)(grp + 1) * p.n_tiles / n_groups) - nt0;
   const int kt0 = (int)((long long)wi * KT / FM_WARPS), kt1 = (int)((long long)(wi + 1) * KT / FM_WARPS);
   const int rpi = kt1 - kt0;
-  const int total = rpi * n_items;
-  const uint8_t* wsrc = p.w + ((size_t)p.n_tiles * kt0 + (size_t)nt0 * rpi) * FM_REC;
-  const int n_chunks = (total + FM_CH - 1) / FM_CH;
+  const int P = EPI == FEPI_PUSH ? p.kparts : 1;
+  const int n_units = p.n_tiles * P;
+  const int u0 = (int)((long long)grp * n_units / n_groups), u1 = (int)((long long)(grp + 1) * n_units / n_groups);
+  // record index (within the slice) where unit u starts
+  auto unit_start = [&](int u) { return (u / P) * rpi + (u % P) * rpi / P; };
+  const int R0 = unit_start(u0), total = unit_start(u1) - R0;
+  const uint8_t* gsrc = p.w + ((size_t)p.n_tiles * kt0 + (size_t)R0) * FM_REC + lane * 16;   // next record to fetch, this lane's word
+  const uint32_t ring_s = smem_u32(ring) + lane * 16;
+  int to_issue = total;
 
-  if (lane == 0) {
-    for (int s = 0; s < FM_SLOTS; ++s) mbar_init(&bars[s], 1);
-    mbar_fence_init();
-  }
-  __syncwarp();
-  if (lane == 0) {      // weights do not depend on the previous kernel: start the stream before the dependency wait
-    for (int c = 0; c < FM_SLOTS && c < n_chunks; ++c) {
-      const uint32_t bytes = (uint32_t)min(FM_CH, total - c * FM_CH) * FM_REC;
-      mbar_expect_tx(&bars[c], bytes);
-      bulk_g2s_f(ring + (size_t)c * FM_SLOT_BYTES, wsrc + (size_t)c * FM_SLOT_BYTES, bytes, &bars[c]);
+  // Record j of the stream lives in ring stage j % FM_STAGES; lane L copies the 16-byte words it reads itself (L and
+  // 32 + L), lanes 0..3 the scale / zero words. One commit group per record, also past the end, so that the group count
+  // stays uniform and "all but the two newest groups are complete" always means "the record about to be read landed".
+  auto issue = [&](uint32_t stage_off) {
+    if (to_issue > 0) {
+      cp_async16(ring_s + stage_off, gsrc);
+      cp_async16(ring_s + stage_off + 512, gsrc + 512);
+      if (lane < 4) cp_async16(ring_s + stage_off + 1024, gsrc + 1024);
+      gsrc += FM_REC;
     }
-  }
+    --to_issue;
+    cp_async_commit();
+  };
+  // weights do not depend on the previous kernel: start the stream before the dependency wait
+#pragma unroll
+  for (int j = 0; j < FM_STAGES - 1; ++j) issue(j * FM_REC);
 
   // ---- prologue: the activation vector as scaled fp16 in shared memory -------------------------------------
   const int nchunks = p.K / 8;
   const uint4* x4 = reinterpret_cast<const uint4*>(p.x);
   const uint4* w4 = reinterpret_cast<const uint4*>(p.norm_w);
   uint4 wc[FM_CACHE], hc[FM_CACHE];
-  if (MODE == FMA_NORM) {
+  if (NORMED) {
 #pragma unroll
     for (int i = 0; i < FM_CACHE; ++i) {
       const int c = tid + i * NT;
@@ -146,11 +189,41 @@ __global__ void __launch_bounds__(VC * FM_WARPS * 32, 4 / VC) w4_fma_kernel(FmaP
     }
   }
   pdl_wait();
+  if (MODE == FMA_PULL) {
+    // every rank's partial sums of the preceding row-parallel projection must have landed in the local slots
+    if (tid < p.pull_ranks) {
+      const uint32_t want = *p.pull_seq;
+      bool got = false;
+      for (uint32_t i = 0; i < p.spin_limit; ++i) {
+        if ((int)(ld_acquire_sys_u32(p.pull_flags + tid) - want) >= 0) { got = true; break; }
+        if (i > 64) __nanosleep(32);
+      }
+      if (!got) atomicCAS(&g_fma_status, 0, OWL_ERR_WAIT_PEER);
+    }
+    __syncthreads();
+  }
+  // one chunk (8 values) of the input row; FMA_PULL adds the ranks' slots in rank order and rounds to bf16 once
+  auto load_x = [&](int c) -> uint4 {
+    const uint4 hv = __ldcg(x4 + c);
+    if (MODE != FMA_PULL) return hv;
+    float a[8], v[8];
+    bf16x8_to_f(hv, a);
+    float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < p.pull_world; ++r) {
+      bf16x8_to_f(ld_relaxed_sys_u4(reinterpret_cast<const uint4*>(p.pull_slots + (size_t)r * p.pull_rows * p.K) + c), v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) sum[i] += v[i];
+    }
+    const uint4 o = make_uint4(pack_bf16(a[0] + sum[0], a[1] + sum[1]), pack_bf16(a[2] + sum[2], a[3] + sum[3]),
+                               pack_bf16(a[4] + sum[4], a[5] + sum[5]), pack_bf16(a[6] + sum[6], a[7] + sum[7]));
+    if (blockIdx.x == 0) reinterpret_cast<uint4*>(p.h_out)[c] = o;
+    return o;
+  };
   float ss = 0.f, mx = 0.f;
   auto scan = [&](const uint4& hv, const uint4& wv) {
     float h[8], wf[8];
     bf16x8_to_f(hv, h);
-    if (MODE == FMA_NORM) {
+    if (NORMED) {
       bf16x8_to_f(wv, wf);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
@@ -165,26 +238,26 @@ __global__ void __launch_bounds__(VC * FM_WARPS * 32, 4 / VC) w4_fma_kernel(FmaP
 #pragma unroll
   for (int i = 0; i < FM_CACHE; ++i) {
     const int c = tid + i * NT;
-    hc[i] = c < nchunks ? __ldcg(x4 + c) : make_uint4(0, 0, 0, 0);
+    hc[i] = c < nchunks ? load_x(c) : make_uint4(0, 0, 0, 0);
   }
 #pragma unroll
   for (int i = 0; i < FM_CACHE; ++i) scan(hc[i], wc[i]);
-  for (int c = tid + FM_CACHE * NT; c < nchunks; c += NT)
-    scan(__ldcg(x4 + c), MODE == FMA_NORM ? __ldg(w4 + c) : make_uint4(0, 0, 0, 0));
+  for (int c = tid + FM_CACHE * NT; c < nchunks; c += NT)      // (FMA_PULL rows fit the register cache: checked by the launcher)
+    scan(__ldcg(x4 + c), NORMED ? __ldg(w4 + c) : make_uint4(0, 0, 0, 0));
   ss = warp_sum(ss);
   mx = warp_max(mx);
   if (lane == 0) { pro[warp] = ss; pro[32 + warp] = mx; }
   __syncthreads();
   ss = warp_sum(lane < VC * FM_WARPS ? pro[lane] : 0.f);
   mx = warp_max(lane < VC * FM_WARPS ? pro[32 + lane] : 0.f);
-  const float rinv = MODE == FMA_NORM ? rsqrtf(ss / (float)p.K + p.eps) : 1.f;
+  const float rinv = NORMED ? rsqrtf(ss / (float)p.K + p.eps) : 1.f;
   // power-of-two scale: 8192 < max |x'| <= 16384
   const float sx = __uint_as_float(__float_as_uint(16384.f / fmaxf(mx * rinv, 1e-30f)) & 0x7f800000u);
   const float unscale = 16777216.f / sx;      // products carry 2^-24 (subnormal nibbles) and sx
   auto emit = [&](int c, const uint4& hv, const uint4& wv) {       // warp-uniform call: c - lane is the same in all lanes
     float h[8], wf[8], s8 = 0.f;
     bf16x8_to_f(hv, h);
-    if (MODE == FMA_NORM) {
+    if (NORMED) {
       bf16x8_to_f(wv, wf);
 #pragma unroll
       for (int i = 0; i < 8; ++i)
@@ -215,7 +288,7 @@ __global__ void __launch_bounds__(VC * FM_WARPS * 32, 4 / VC) w4_fma_kernel(FmaP
   for (int c = tid + FM_CACHE * NT; c - lane < nchunks; c += NT) {
     const bool in = c < nchunks;
     emit(c, in ? __ldcg(x4 + c) : make_uint4(0, 0, 0, 0),
-         (MODE == FMA_NORM && in) ? __ldg(w4 + c) : make_uint4(0, 0, 0, 0));
+         (NORMED && in) ? __ldg(w4 + c) : make_uint4(0, 0, 0, 0));
   }
   __syncthreads();
 
@@ -246,27 +319,29 @@ __global__ void __launch_bounds__(VC * FM_WARPS * 32, 4 / VC) w4_fma_kernel(FmaP
 
   // ---- main loop ----------------------------------------------------------------------------------------------
   float acc0 = 0.f, acc1 = 0.f;      // rows g and g + 8 of the current tile, this lane's k runs
-  bool failed = false;
-  int item = 0, kk = 0, chunk = 0, in_chunk = 0, slot = 0;
-  uint32_t parity = 0;
-  const uint8_t* rec_b = ring;
   const uint32_t sixteenth = 0x2C002C00u;       // (1/16, 1/16)
-  for (int j = 0; j < total || item < n_items; ++j) {
-    if (j < total) {
-      const int krec = kt0 + kk;
-      const uint4* xr = xh4 + krec * 16 + t;
+  uint32_t st_c = 0, st_i = (FM_STAGES - 1) * FM_REC;        // ring offsets of the record consumed / fetched next
+  const uint8_t* ring_l = ring + lane * 16;                   // this lane's weight words of stage 0
+  const uint8_t* ring_z = ring + 1024 + g * 4;                // and its rows' (scale, zero) pairs
+  const uint4* x_slice = xh4 + kt0 * 16 + t;                  // this lane's activations of the slice's first record
+  const float* g_slice = xg + kt0;
+  for (int u = u0, item = 0; u < u1; ++u, ++item) {
+    const int q = u % P;
+    const int ka = q * rpi / P, kb = (q + 1) * rpi / P;
+    const uint4* xr = x_slice + ka * 16;
+    const float* xs = g_slice + ka;
+    for (int kk = ka; kk < kb; ++kk) {
       const uint4 x0 = xr[0], x1 = xr[4], x2 = xr[8], x3 = xr[12];
-      const float xsum = xg[krec];
-      if (in_chunk == 0) {
-        if (!failed && !mbar_wait(&bars[slot], parity, 1u << 22)) {
-          failed = true;
-          atomicCAS(&g_fma_status, 0, OWL_ERR_WAIT_TMA);
-        }
-      }
-      const uint4* rec = reinterpret_cast<const uint4*>(rec_b);
-      const uint4 lo = rec[lane], hi = rec[32 + lane];
-      const uint32_t* szr = reinterpret_cast<const uint32_t*>(rec + 64);
-      const uint32_t su0 = szr[g], su1 = szr[8 + g];
+      const float xsum = *xs;
+      xr += 16;
+      ++xs;
+      cp_async_wait<FM_STAGES - 2>();           // this lane's copies of the record have landed
+      __syncwarp();                             // and everybody's (scale words), and everybody left the previous record
+      issue(st_i);                              // refill the stage the previous record occupied
+      st_i = st_i == (FM_STAGES - 1) * FM_REC ? 0u : st_i + FM_REC;
+      const uint4 lo = *reinterpret_cast<const uint4*>(ring_l + st_c), hi = *reinterpret_cast<const uint4*>(ring_l + st_c + 512);
+      const uint32_t su0 = *reinterpret_cast<const uint32_t*>(ring_z + st_c), su1 = *reinterpret_cast<const uint32_t*>(ring_z + st_c + 32);
+      st_c = st_c == (FM_STAGES - 1) * FM_REC ? 0u : st_c + FM_REC;
       uint32_t a0 = 0u, b0 = 0u, a1 = 0u, b1 = 0u;
 #define OWL_FMA_WORD(Q0, Q1, XV)                                                           \
       {                                                                                    \
@@ -282,29 +357,14 @@ __global__ void __launch_bounds__(VC * FM_WARPS * 32, 4 / VC) w4_fma_kernel(FmaP
       OWL_FMA_WORD(lo.z, hi.z, x2)
       OWL_FMA_WORD(lo.w, hi.w, x3)
 #undef OWL_FMA_WORD
-      {
-        const float f0 = h2_sum(hfma2_u(b0, sixteenth, a0)), f1 = h2_sum(hfma2_u(b1, sixteenth, a1));
-        const __half2 s0 = *reinterpret_cast<const __half2*>(&su0), s1 = *reinterpret_cast<const __half2*>(&su1);
-        acc0 = fmaf(__low2float(s0), fmaf(-__high2float(s0), xsum * 0.25f, f0), acc0);   // four t lanes share z * sum
-        acc1 = fmaf(__low2float(s1), fmaf(-__high2float(s1), xsum * 0.25f, f1), acc1);
-      }
-      rec_b += FM_REC;
-      if (++in_chunk == FM_CH || j + 1 == total) {
-        __syncwarp();
-        const int nc = chunk + FM_SLOTS;
-        if (lane == 0 && nc < n_chunks) {
-          const uint32_t bytes = (uint32_t)min(FM_CH, total - nc * FM_CH) * FM_REC;
-          mbar_expect_tx(&bars[slot], bytes);
-          bulk_g2s_f(ring + (size_t)slot * FM_SLOT_BYTES, wsrc + (size_t)nc * FM_SLOT_BYTES, bytes, &bars[slot]);
-        }
-        ++chunk; in_chunk = 0;
-        if (++slot == FM_SLOTS) { slot = 0; parity ^= 1u; }
-        rec_b = ring + (size_t)slot * FM_SLOT_BYTES;
-      }
-      if (++kk < rpi) continue;
-      kk = 0;
+      const float f0 = h2_sum(hfma2_u(b0, sixteenth, a0)), f1 = h2_sum(hfma2_u(b1, sixteenth, a1));
+      const float2 s0 = __half22float2(*reinterpret_cast<const __half2*>(&su0));
+      const float2 s1 = __half22float2(*reinterpret_cast<const __half2*>(&su1));
+      const float xq = xsum * 0.25f;            // four t lanes share z * sum
+      acc0 = fmaf(s0.x, fmaf(-s0.y, xq, f0), acc0);
+      acc1 = fmaf(s1.x, fmaf(-s1.y, xq, f1), acc1);
     }
-    // ---- end of a row tile: 4 t lanes, then the 8 k slices through shared memory ------------------------------
+    // ---- end of the unit: 4 t lanes, then the 8 k slices through shared memory -------------------------------------
     acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
     acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
     acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
@@ -314,7 +374,7 @@ __global__ void __launch_bounds__(VC * FM_WARPS * 32, 4 / VC) w4_fma_kernel(FmaP
     acc0 = acc1 = 0.f;
     group_barrier<VC>(vc);
     if (wi == (item & (FM_WARPS - 1))) {
-      const int nt = nt0 + item;
+      const int nt = u / P;
       float v = 0.f;
       if (lane < 16) {
 #pragma unroll
@@ -324,12 +384,34 @@ __global__ void __launch_bounds__(VC * FM_WARPS * 32, 4 / VC) w4_fma_kernel(FmaP
       if (EPI == FEPI_SILU_MUL) {
         const float up = __shfl_down_sync(0xffffffffu, v, 8);
         if (lane < 8) p.out[nt * 8 + lane] = __float2bfloat16(silu_f(v) * up);
+      } else if (EPI == FEPI_PUSH) {
+        if (lane < 16) {
+          const __nv_bfloat16 bv = __float2bfloat16(v);
+          const size_t off = (size_t)(p.push_rank * P + q) * p.push_rows * p.N + nt * 16 + lane;
+          for (int r = 0; r < p.push_world; ++r) p.push_dst[r][off] = bv;
+        }
       } else if (lane < 16) {
         if (EPI == FEPI_RESIDUAL) v += __bfloat162float(p.residual[nt * 16 + lane]);
         p.out[nt * 16 + lane] = __float2bfloat16(v);
       }
     }
-    ++item;
+  }
+  cp_async_wait<0>();
+  if (EPI == FEPI_PUSH) {
+    // every thread's peer stores are ordered before the count; the last CTA of the grid tells the ranks
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0) {
+      __threadfence_system();
+      if (atomicAdd(p.push_count, 1) == (int)gridDim.x - 1) {
+        *p.push_count = 0;
+        const uint32_t seq = *p.push_seq + 1;
+        *p.push_seq = seq;
+        __threadfence_system();
+        for (int r = 0; r < p.push_world; ++r)
+          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.push_flag[r] + p.push_rank), "r"(seq) : "memory");
+      }
+    }
   }
   pdl_launch_dependents();
 }
@@ -364,7 +446,9 @@ template <int VC>
 static int dispatch_fma(const FmaParams& p, int mode, int epi, int grid, int pdl, cudaStream_t st) {
 #define OWL_FMA_CASE(M, E) if (mode == M && epi == E) return launch_fma<VC, M, E>(p, grid, pdl, st);
   OWL_FMA_CASE(FMA_PLAIN, FEPI_STORE) OWL_FMA_CASE(FMA_PLAIN, FEPI_RESIDUAL) OWL_FMA_CASE(FMA_PLAIN, FEPI_SILU_MUL)
+  OWL_FMA_CASE(FMA_PLAIN, FEPI_PUSH)
   OWL_FMA_CASE(FMA_NORM, FEPI_STORE) OWL_FMA_CASE(FMA_NORM, FEPI_RESIDUAL) OWL_FMA_CASE(FMA_NORM, FEPI_SILU_MUL)
+  OWL_FMA_CASE(FMA_PULL, FEPI_STORE) OWL_FMA_CASE(FMA_PULL, FEPI_SILU_MUL)
 #undef OWL_FMA_CASE
   return OWL_ERR_BAD_ARG;
 }
@@ -408,6 +492,50 @@ OWL_API int owl_w4_fma(const void* records, const void* x, const void* norm_w, v
   const int grid = fma_sm_count() * (4 / vc);
   if (p.ab_rows > grid * vc * FM_WARPS) return OWL_ERR_BAD_ARG;
   return vc == 4 ? dispatch_fma<4>(p, mode, epi, grid, pdl, st) : dispatch_fma<2>(p, mode, epi, grid, pdl, st);
+}
+
+// Split forms of the same launch (one token), across ranks and / or across k parts. push != 0: a row-parallel projection
+// whose partial sums are stored into slot [rank * kparts + part] of every rank's buffer (dst_ptrs: `world` peer-mapped bases
+// of [world * kparts][rows][N] bf16; flag_ptrs: `world` peer-mapped flag arrays [world] uint32; count / seq: local words,
+// zero before the first call); x is the plain activation vector. world * kparts <= 8; world = 1 is a local k split. push == 0: the column-parallel projection that consumes such a buffer: x is the residual stream,
+// pull_slots / pull_flags / pull_seq are the LOCAL slot buffer, flag array and producer sequence word, h_out (a buffer
+// other than x) receives x + sum of the slots, and the kernel multiplies by rmsnorm(h_out) * (norm_w or 1 + norm_w);
+// epi 0 or 2 as in owl_w4_fma.
+OWL_API int owl_w4_fma_tp(const void* records, const void* x, const void* norm_w, void* out, int N, int K, int epi, float eps,
+                          int one_plus_w, int push, void* const* dst_ptrs, void* const* flag_ptrs, void* count, void* seq,
+                          const void* pull_slots, const void* pull_flags, const void* pull_seq, void* h_out, const void* ab_w,
+                          void* ab_out, int ab_rows, int rank, int world, int rows, int kparts, unsigned spin_limit,
+                          int groups_per_cta, int pdl, cudaStream_t st) {
+  if (!records || !x || (N & 15) || (K & 127) || K < 128 || K > 32768 || world < 1 || world > FM_MAX_RANKS || rank < 0 ||
+      rank >= world || rows < 1)
+    return OWL_ERR_BAD_ARG;
+  FmaParams p = {};
+  p.w = (const uint8_t*)records; p.x = (const __nv_bfloat16*)x; p.norm_w = (const __nv_bfloat16*)norm_w;
+  p.out = (__nv_bfloat16*)out; p.N = N; p.K = K; p.n_tiles = N / 16; p.eps = eps; p.one_plus = one_plus_w;
+  p.ab_w = (const __nv_bfloat16*)ab_w; p.ab_out = (__nv_bfloat16*)ab_out; p.ab_rows = ab_rows;
+  const int vc = groups_per_cta ? groups_per_cta : (K > 8192 ? 4 : 2);
+  if (vc != 2 && vc != 4) return OWL_ERR_BAD_ARG;
+  const int grid = fma_sm_count() * (4 / vc);
+  if (ab_rows < 0 || (ab_rows > 0 && (!ab_w || !ab_out)) || ab_rows > grid * vc * FM_WARPS) return OWL_ERR_BAD_ARG;
+  if (kparts < 1 || world * kparts > FM_MAX_RANKS) return OWL_ERR_BAD_ARG;
+  p.kparts = kparts;
+  if (push) {
+    if (!dst_ptrs || !flag_ptrs || !count || !seq) return OWL_ERR_BAD_ARG;
+    for (int r = 0; r < world; ++r) {
+      p.push_dst[r] = (__nv_bfloat16*)dst_ptrs[r];
+      p.push_flag[r] = (uint32_t*)flag_ptrs[r];
+      if (!p.push_dst[r] || !p.push_flag[r]) return OWL_ERR_BAD_ARG;
+    }
+    p.push_count = (int*)count; p.push_seq = (uint32_t*)seq; p.push_rank = rank; p.push_world = world; p.push_rows = rows;
+    return vc == 4 ? launch_fma<4, FMA_PLAIN, FEPI_PUSH>(p, grid, pdl, st) : launch_fma<2, FMA_PLAIN, FEPI_PUSH>(p, grid, pdl, st);
+  }
+  if (!out || !norm_w || !pull_slots || !pull_flags || !pull_seq || !h_out || h_out == x || (epi != FEPI_STORE && epi != FEPI_SILU_MUL))
+    return OWL_ERR_BAD_ARG;
+  if (K / 8 > 2 * vc * FM_WARPS * 32) return OWL_ERR_BAD_ARG;      // the pulled row must fit the prologue's register cache
+  p.pull_slots = (const __nv_bfloat16*)pull_slots; p.pull_flags = (const uint32_t*)pull_flags;
+  p.pull_seq = (const uint32_t*)pull_seq; p.h_out = (__nv_bfloat16*)h_out; p.pull_world = world * kparts; p.pull_ranks = world; p.pull_rows = rows;
+  p.spin_limit = spin_limit ? spin_limit : (1u << 22);
+  return vc == 4 ? dispatch_fma<4>(p, FMA_PULL, epi, grid, pdl, st) : dispatch_fma<2>(p, FMA_PULL, epi, grid, pdl, st);
 }
 
 // First bounded-wait failure recorded by this file's kernels since the last call (0 = none); clears it.

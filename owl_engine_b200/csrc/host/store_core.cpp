@@ -229,6 +229,22 @@ API int owl_kv_set_carrier(void* h, uint64_t hash, int carrier, int slot) {
   return 0;
 }
 
+// Insert a node that lives below the device (restart adoption of the disk tier's index, or a block written by another
+// process): carrier HOST with its slot, or DISK. Parents must be adopted before their children for the child counts to
+// be right; a node whose parent is unknown is still inserted (it can only be reached through a chain that matches the
+// parent first, so it stays unreachable until the parent arrives). Returns 1 when inserted, 0 when the hash was known.
+API int owl_kv_adopt(void* h, uint64_t hash, uint64_t parent, int carrier, int slot, uint64_t tag) {
+  Store* s = static_cast<Store*>(h);
+  if (carrier == DEVICE || hash == 0 || s->nodes.count(hash)) return 0;
+  Node nd{};
+  nd.hash = hash; nd.parent = parent; nd.page = slot; nd.carrier = (int8_t)carrier; nd.tag = tag;
+  nd.children = 0; nd.dev_children = 0; nd.in_lru = false; nd.last_use = ++s->tick;
+  s->nodes.emplace(hash, nd);
+  auto pit = s->nodes.find(parent);
+  if (pit != s->nodes.end()) pit->second.children++;
+  return 1;
+}
+
 // Remove a non-device node for good (tier overflow). Fails (-1) when it still has children.
 API int owl_kv_forget(void* h, uint64_t hash) {
   Store* s = static_cast<Store*>(h);

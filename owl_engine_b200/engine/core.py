@@ -52,6 +52,8 @@ class EngineConfig:
                                    # view of sink + recent + best-scoring blocks, re-selected at every block boundary
     kvmem_sink: int = 2
     kvmem_recent: int = 4
+    recall_mode: str = "sync"      # recall of demoted prefix blocks: "sync" (host and disk), "host" (host only), "resident" (none)
+    workspace_reserve_mb: int = 3072   # n_pages = 0: device memory the boot plan leaves for graphs, prefill workspace, scratch
     vocab_split: bool = True       # tensor parallel: each rank holds vocab / world lm_head rows and the winners are merged
 
 
@@ -77,10 +79,12 @@ class Sequence:
 
 class Engine:
     def __init__(self, cfg: EngineConfig, *, spec: ModelSpec | None = None, weights: H.HybridWeights | None = None,
-                 comm=None, device=None):
+                 comm=None, device=None, ledger=None):
         from ..store.kv import KvStore
+        from ..store.rel import Rel
         from ..store.state import StateStore
         from ..store.tiers import HostTier, Mover, page_bytes
+        from ..utils.ledger import ledger_for
 
         self.cfg = cfg
         self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
@@ -89,6 +93,7 @@ class Engine:
             from dataclasses import replace
             full = replace(full, n_layers=cfg.n_layers)
         self.full_spec = full
+        self.ledger = ledger if ledger is not None else ledger_for(self.device)
         self.comm = comm
         world = comm.world if comm is not None else 1
         rank = comm.rank if comm is not None else 0
@@ -98,8 +103,19 @@ class Engine:
                                                    layout="block" if cfg.decode_gemv == "tc" else "slice",
                                                    vocab_split=cfg.vocab_split,
                                                    quant="nvfp4" if cfg.quant == "nvfp4" else "w4a16")
+        self.ledger.track_tree("weights", "weights", self.weights)
+        n_rows = cfg.n_slots + cfg.n_snap_rows + 1
+        if cfg.n_pages <= 0:
+            cfg.n_pages = self._plan_pages(cfg, n_rows)
+        self.ledger.check("kv pool + gdn state", cfg.n_pages * H.StatePool.bytes_per_page(self.spec, cfg.kv_dtype)
+                          + n_rows * H.StatePool.bytes_per_slot(self.spec))
         # GDN rows: one per sequence slot, the prefix-snapshot rows, and one scratch row for speculative rollback
-        self.pool = H.StatePool(self.spec, self.device, cfg.n_pages, cfg.n_slots + cfg.n_snap_rows + 1, kv_dtype=cfg.kv_dtype)
+        self.pool = H.StatePool(self.spec, self.device, cfg.n_pages, n_rows, kv_dtype=cfg.kv_dtype)
+        for nm in ("k_pool", "v_pool", "k_scale", "v_scale"):
+            if getattr(self.pool, nm, None) is not None:
+                self.ledger.track("pool." + nm, "kv pool", getattr(self.pool, nm))
+        self.ledger.track("pool.conv_state", "gdn state", self.pool.conv_state)
+        self.ledger.track("pool.rec_state", "gdn state", self.pool.rec_state)
         self.spec_row = cfg.n_slots + cfg.n_snap_rows
         self.max_blocks = (cfg.max_seq + PAGE - 1) // PAGE
         self.runner = H.HybridRunner(self.spec, self.weights, self.pool, max_seqs=cfg.max_seqs * (2 if cfg.kvmem_budget else 1),
@@ -109,17 +125,21 @@ class Engine:
         if cfg.act_bits != 15:
             assert cfg.act_bits == 8, "act_bits is 15 or 8"
             self.runner.act_bits = 8
+        self.ledger.track_tree("runner", "workspace", {k: v for k, v in vars(self.runner).items() if k not in ("w", "pool", "comm")})
+        if comm is not None and getattr(comm, "symm", None) is not None:
+            self.ledger.track("symmetric workspace", "symmetric", comm.symm.buf)
         self.kv = KvStore(cfg.n_pages, PAGE)
         self.states = StateStore(cfg.n_slots, cfg.n_snap_rows)
         self.host = HostTier(page_bytes(self.pool), cfg.host_cache_mb << 20) if cfg.host_cache_mb else None
         self.mover = Mover(self.pool, self.host) if self.host else None
-        self.host_slot_of: dict[int, int] = {}       # chain hash -> host slot (demoted blocks), oldest first
         self.disk = None
         if cfg.disk_cache_mb and cfg.disk_dir and self.host is not None:
             from ..store.tiers import DiskTier
 
             self.disk = DiskTier(cfg.disk_dir, page_bytes(self.pool), cfg.disk_cache_mb << 20)
-        self.spilled = self.recalled = 0
+        # every move between the device pool, the host tier and the disk tier goes through the relocation facade
+        self.rel = Rel(self.kv, self.states, self.pool, self.host, self.mover, self.disk, PAGE)
+        self.adopted = self.rel.adopt() if self.disk is not None else {"blocks": 0, "states": 0}
         self._last_rows: dict = {}
         self.free_rows = list(range(cfg.max_seqs - 1, -1, -1))
         self.seqs: dict[int, Sequence] = {}
@@ -133,6 +153,51 @@ class Engine:
         self.d2h_bytes = 0
         self.prefix_hits = self.prefix_lookups = 0
 
+    # counters that used to live on the engine (kept for callers and tests)
+    @property
+    def spilled(self) -> int:
+        return self.rel.spilled
+
+    @property
+    def recalled(self) -> int:
+        return self.rel.recalled
+
+    @property
+    def host_slot_of(self) -> dict:
+        return self.rel.host_slot_of
+
+    def _plan_pages(self, cfg: EngineConfig, n_rows: int) -> int:
+        """``n_pages = 0``: the KV pool takes what the declared budget leaves after the weights (already on the device and
+        in the ledger), the recurrent-state rows and the workspace reserve; the boot refuses when that is not enough for
+        one sequence of ``max_seq`` tokens."""
+        from ..store.budget import BudgetError, MemoryPlan
+
+        led = self.ledger
+        plan = MemoryPlan(total=led._total(), budget_frac=led.budget_frac, reserve=led.reserve, weights=led.used(),
+                          gdn_rows=n_rows * H.StatePool.bytes_per_slot(self.spec), workspace=cfg.workspace_reserve_mb << 20,
+                          page_bytes=H.StatePool.bytes_per_page(self.spec, cfg.kv_dtype))
+        plan.check(min_pages=(cfg.max_seq + PAGE - 1) // PAGE + 8)
+        cap = ((cfg.max_seq + PAGE - 1) // PAGE + 8) * max(cfg.n_slots, 1) * 2        # no point in more than every slot twice over
+        self.memory_plan = plan
+        if plan.kv_pages <= 0:
+            raise BudgetError("no room for a KV pool")
+        return int(min(plan.kv_pages, cap))
+
+    def checkpoint(self, include_device: bool = True) -> dict:
+        """Write the cached prefix blocks and their state snapshots through to the disk tier and save the restart index
+        (called when the server goes idle and at shutdown)."""
+        return self.rel.checkpoint(include_device)
+
+    def relieve(self) -> int:
+        """Watermark relief between steps (``store/rel.py``): demote cold prefix blocks before an admission needs the room."""
+        return self.rel.relieve()
+
+    def close(self) -> None:
+        """Orderly end: checkpoint when a disk tier is configured, stop its writer."""
+        if self.disk is not None:
+            self.rel.checkpoint()
+            self.disk.close()
+
     # -- pages ----------------------------------------------------------------------------------
     def _alloc_pages(self, n: int) -> list[int]:
         """Pages from the pool; under pressure the prefix tree gives up leaf-LRU blocks (demoted to the
@@ -140,44 +205,15 @@ class Engine:
         got = self.kv.alloc(n)
         if got is not None:
             return got
-        free = self.kv.stats()["free_pages"]
-        short = n - free
-        room = 0
-        if self.host is not None:
-            if len(self.host.free) < short and self.disk is not None:
-                self._spill_host(short - len(self.host.free))
-            room = min(short, len(self.host.free))
-        if room:
-            pages, hashes = self.kv.evict(need_free=free + room, demote=True)
-            for pg, h in zip(pages, hashes):
-                slot = self.host.alloc()
-                self.mover.copy_out(pg, slot)
-                self.kv.set_carrier(h, 1, slot)
-                self.host_slot_of[h] = slot
-            self.mover.fence()
-        if room < short:
-            self.kv.evict(need_free=n, demote=False)           # no tier left to hold them: dropped
+        self.rel.make_room(n)
         got = self.kv.alloc(n)
         if got is None:
             raise RuntimeError("KV pool exhausted")
         return got
 
-    def _spill_host(self, n: int) -> None:
-        """Make room in the pinned-host tier: its oldest blocks go to disk files (carrier 2); when the disk tier is
-        full too they are dropped from the prefix tree."""
-        self._mover_sync()                                 # demotions into the slots about to be read have landed
-        for h in list(self.host_slot_of)[:n]:
-            slot = self.host_slot_of.pop(h)
-            if self.disk.spill(h, 0, (), self.host.slot(slot)):
-                self.kv.set_carrier(h, 2, 0)
-                self.spilled += 1
-            else:
-                self.kv.forget(h)
-            self.host.release(slot)
-
     def _mover_sync(self) -> None:
-        if self.mover.stream is not None:
-            self.mover.stream.synchronize()
+        if self.mover is not None:
+            self.mover.sync()
 
     def _ensure_pages(self, seq: Sequence, n_tokens: int) -> None:
         need = (n_tokens + PAGE - 1) // PAGE
@@ -235,44 +271,20 @@ class Engine:
         if seq.chain is not None and len(seq.chain):
             self.prefix_lookups += 1
             m, pages, carriers = self.kv.match(seq.chain)
-            snap = self.states.find(seq.chain[:m]) if m else None
+            snap = self.rel.find_snapshot(seq.chain[:m]) if m else None
             keep = snap.n_tokens // PAGE if snap else 0
-            promoted = set()
             keep0 = keep
-            for i in range(keep):                              # promote demoted blocks of the kept prefix
-                if carriers[i] == 0:
-                    continue
-                h = int(seq.chain[i])
+
+            def one_page():
                 try:
-                    pg = self._alloc_pages(1)                  # may push other cold blocks down a tier
+                    return self._alloc_pages(1)[0]              # may push other cold blocks down a tier
                 except RuntimeError:
-                    pg = None
-                if pg is not None and h not in self.host_slot_of and self.disk is not None and h in self.disk.index:
-                    # disk -> pinned host staging slot (then host -> device below)
-                    if not self.host.free:
-                        self._spill_host(1)
-                    hslot = self.host.alloc()
-                    if hslot is not None:
-                        self._mover_sync()                     # no copy still reads the recycled slot
-                        self.disk.fill(h, self.host.slot(hslot))
-                        self.disk.drop(h)
-                        self.host_slot_of[h] = hslot
-                        self.recalled += 1
-                if pg is None or h not in self.host_slot_of:
-                    if pg is not None:
-                        self.kv.unref(pg)
-                    keep = i
-                    break
-                self.mover.copy_in(self.host_slot_of[h], pg[0])
-                self.kv.set_carrier(h, 0, pg[0])
-                self.host.release(self.host_slot_of.pop(h))
-                pages[i] = pg[0]                               # alloc's reference is the sequence's
-                promoted.add(i)
-            if self.mover:
-                self.mover.fence()
+                    return None
+            keep, promoted = self.rel.promote(seq.chain, keep, pages, carriers, one_page, mode=self.cfg.recall_mode) \
+                if any(c != 0 for c in carriers[:keep]) else (keep, set())
             if keep < keep0:
                 # the recurrent state must match the KV prefix: fall back to the longest snapshot inside what is resident
-                snap = self.states.find(seq.chain[:keep]) if keep else None
+                snap = self.rel.find_snapshot(seq.chain[:keep]) if keep else None
                 keep = snap.n_tokens // PAGE if snap else 0
             self.kv.unref([p for j, (p, c) in enumerate(zip(pages[:m], carriers[:m])) if j >= keep and (c == 0 or j in promoted)])
             if keep:
@@ -291,8 +303,11 @@ class Engine:
         if publish and seq.n_cached >= PAGE:
             exact = seq.n_cached if seq.gap_from is None else min(seq.n_cached, seq.gap_from)
             nb = min(exact // PAGE, len(seq.pages))
-            chain = self.kv.chain(self._hash_tokens(seq.tokens, seq.images)[:nb * PAGE])
+            hashed = self._hash_tokens(seq.tokens, seq.images)[:nb * PAGE]
+            chain = self.kv.chain(hashed)
             self.kv.publish(chain, seq.pages[:nb])
+            if self.disk is not None:
+                self.rel.note_published(chain, hashed)
         self.kv.unref(seq.pages)
         self.free_rows.append(seq.row)
         self.states.give_back(sid)

@@ -124,6 +124,8 @@ class RunningEngine:
         for t in list(self.turns.values()):
             if t.cancelled and t.state != DONE:
                 self._finish(t, "cancelled")
+        if self._tick % 16 == 0 and self.e.host is not None:
+            self.e.relieve()                 # watermark relief: cold prefix blocks leave the pool before a turn needs the room
         kvs = self.e.kv.stats()
         evictable = kvs["lru_len"]
         step, rejected = self.sched.schedule(self._views(), self.e.kv.free_pages, evictable,

@@ -39,6 +39,7 @@ class EngineService:
         self._args = (build_engine, max_batch, on_full, spec_runner)
         self.thread = threading.Thread(target=self._main, name="owl-engine", daemon=True)
         self.boot_error: str | None = None
+        self.idle_checkpoint_s = 5.0
 
     def boot(self, timeout: float = 600.0) -> "EngineClient":
         self.thread.start()
@@ -68,6 +69,7 @@ class EngineService:
             self.ready.set()
             return
         self.ready.set()
+        idle_since, checkpointed = None, False
         try:
             while True:
                 stop = self._drain()
@@ -75,13 +77,24 @@ class EngineService:
                     self.exit = ServiceExit("normal", 0)
                     return
                 if not self.re.pump():
+                    # idle: after a quiet spell write the cache through to the disk tier once (restart recall)
+                    idle_since = idle_since or time.monotonic()
+                    if not checkpointed and self.re.e.disk is not None and time.monotonic() - idle_since > self.idle_checkpoint_s:
+                        self.re.e.checkpoint()
+                        checkpointed = True
                     time.sleep(0.0005)
+                else:
+                    idle_since, checkpointed = None, False
         except MemoryError as ex:
             self.exit = ServiceExit("fatal", 1, repr(ex))
         except Exception as ex:
             log.error("engine.service", traceback.format_exc())
             self.exit = ServiceExit("panic", 70, repr(ex))
         finally:
+            try:
+                self.re.e.close()             # checkpoint + stop the disk writer (mirrored to the follower ranks)
+            except Exception:                 # noqa: BLE001
+                log.error("engine.service", traceback.format_exc())
             if hasattr(self.re.e, "shutdown"):
                 self.re.e.shutdown()          # tensor-parallel leader: release the follower ranks, whatever ended the loop
 

@@ -8,7 +8,7 @@ function of its call sequence (page allocation, prefix matches, tier moves), so 
 exchanging anything else, and they meet on the device inside the kernels' collectives. NCCL carries no step traffic.
 
 Mirrored: ``add_sequence``, ``free_sequence``, ``drop_ranges``, ``append_tokens``, ``extend_sequence``,
-``prefill_range``, ``decode_step``, ``set_last_token``, the speculative runner's ``after_prefill`` / ``round``, and
+``prefill_range``, ``decode_step``, ``set_last_token``, ``relieve``, ``checkpoint``, ``close``, the speculative runner's ``after_prefill`` / ``round``, and
 ``shutdown``. Everything else (statistics, plans, sequence lookups) is read-only and stays local.
 
 Reference counterpart: ``TpEngine::assemble / run`` and the ``mirror2!`` call sites
@@ -23,7 +23,7 @@ from ..parallel.ring import RingClosed, StepRing, ring_name
 from ..utils import log
 
 MIRRORED = ("add_sequence", "free_sequence", "drop_ranges", "append_tokens", "extend_sequence", "prefill_range",
-            "decode_step", "set_last_token")
+            "decode_step", "set_last_token", "relieve", "checkpoint", "close")
 
 
 class MirroredEngine:
@@ -66,6 +66,15 @@ class MirroredEngine:
 
     def set_last_token(self, *a, **kw):
         return self._mirror("set_last_token", *a, **kw)
+
+    def relieve(self, *a, **kw):
+        return self._mirror("relieve", *a, **kw)
+
+    def checkpoint(self, *a, **kw):
+        return self._mirror("checkpoint", *a, **kw)
+
+    def close(self, *a, **kw):
+        return self._mirror("close", *a, **kw)
 
     # composite calls are expressed through the mirrored primitives so that the followers see the same sequence
     def prefill(self, sid: int) -> int:

@@ -389,6 +389,9 @@ class HybridRunner:
         # (5 launches per GDN layer, 7 per attention layer); "dp4a" = the integer arm with separate norm and pack launches
         self.decode_gemv = "fma"
         self.mix = bf(M, max(spec.value_dim, spec.hq * spec.hd))   # mixer output (GDN / attention) of the fused one-token path
+        self.h_alt = bf(M, H)           # second residual-stream buffer of the one-token path with split projections
+        self.ksplit = int(os.environ.get("OWL_FMA_KSPLIT", "4"))    # one GPU: k parts of the projections into the hidden size (0 = off)
+        self._local_split = None
 
     # -- step inputs -------------------------------------------------------------------------
     def views(self, lay: StepLayout):
@@ -620,30 +623,68 @@ class HybridRunner:
     def _fma_ok(self, lay: StepLayout) -> bool:
         """The fused one-token path applies: one row, slice-major group-128 int4 weights, 15-bit-equivalent activations, and no
         mode that needs row-count-independent arithmetic (speculative verify reproduces plain decoding bit for bit on the
-        integer arm)."""
+        integer arm). Under tensor parallelism it needs the symmetric workspace (the collective lives inside the
+        projections) and no hidden-state taps (the residual stream is only materialised inside the next projection)."""
         w0 = self.w.layers[0].gate_up if self.w.layers else None
-        return (self.decode_gemv == "fma" and lay.m == 1 and not self.uniform_rows and self.act_bits == 15
-                and getattr(w0, "layout", "") == "slice" and getattr(w0, "group", 0) == 128
-                and (self.comm is None or self.spec.tp_world == 1))
+        if not (self.decode_gemv == "fma" and lay.m == 1 and not self.uniform_rows and self.act_bits == 15
+                and getattr(w0, "layout", "") == "slice" and getattr(w0, "group", 0) == 128):
+            return False
+        if self.comm is None or self.spec.tp_world == 1:
+            return True
+        return getattr(self.comm, "symm", None) is not None and self.taps is None and self.spec.hidden // 8 <= 1024
 
     def _step_forward_fma(self, lay: StepLayout, v: dict, splits: int, ctx_hint: int) -> None:
-        """Layers of a one-token step with every projection on ``K.w4_fma``: the RMSNorm is the prologue of the column
-        projections, the residual add / silu * up their epilogue, the GDN a / b rows ride in the qkvz launch."""
+        """Layers of a one-token step with every projection on the FMA arm: the RMSNorm is the prologue of the column
+        projections, the residual add / silu * up their epilogue, the GDN a / b rows ride in the qkvz launch.
+
+        Tensor parallel: a row-parallel projection stores its partial sums into every rank's slot buffer while it streams
+        (``fma_push``), and the next column-parallel projection waits for the ranks' flags, adds the slots to the residual
+        stream and normalises in its own prologue (``fma_pull``): the all-reduce costs no launch of its own. The residual
+        stream alternates between two buffers, because the CTA that stores the new row must not overwrite what the other
+        CTAs of the same launch still read."""
         sp, pdl = self.spec, self.pdl
-        h, mix, act = self.h[0], self.mix[0], self.act[0]
+        symm = getattr(self.comm, "symm", None) if (self.comm is not None and sp.tp_world > 1) else None
+        if symm is None and self.ksplit and self.taps is None and sp.hidden // 8 <= 1024:
+            # one GPU: the projections into the hidden size have few row tiles; cut their k range into parts that land in
+            # local slots (the same push / pull kernels with a world of one)
+            if self._local_split is None:
+                from ..parallel.symm import LocalSplit
+
+                self._local_split = LocalSplit(self.device, sp.hidden, kparts=self.ksplit)
+            symm = self._local_split
+        st = {"cur": self.h, "alt": self.h_alt, "pending": None}
+        if symm is not None and (2 * len(self.w.layers) - 1) % 2 == 1:
+            # an odd number of buffer swaps follows: start in the alternate buffer so that the step ends in self.h
+            self.h_alt[:1].copy_(self.h[:1])
+            st["cur"], st["alt"] = self.h_alt, self.h
+        mix, act = self.mix[0], self.act[0]
+
+        def col(w, out, norm_w, epi=K.EPI_STORE, **ab):
+            if st["pending"] is None:
+                K.w4_fma(w, st["cur"][0], out, norm_w=norm_w, epi=epi, eps=sp.eps, pdl=pdl, **ab)
+                return
+            symm.fma_pull(st["pending"], w, st["cur"][0], st["alt"][0], norm_w, out, epi=epi, eps=sp.eps, pdl=pdl, **ab)
+            st["cur"], st["alt"], st["pending"] = st["alt"], st["cur"], None
+
+        def row(which, w, x):
+            if symm is None:
+                K.w4_fma(w, x, st["cur"][0], residual=st["cur"][0], epi=K.EPI_RESIDUAL, pdl=pdl)
+            else:
+                symm.fma_push(which, w, x, pdl=pdl)
+                st["pending"] = which
+
         fi = gi = 0
         for i, lw in enumerate(self.w.layers):
             if lw.kind == "gdn":
                 qo, ao = (self.qkvz_out, self.ab_out) if self.gdn_save is None else (self.gdn_save[0][gi], self.gdn_save[1][gi])
-                K.w4_fma(lw.qkvz, h, qo[0], norm_w=lw.ln1, ab_w=lw.ab_dense, ab_out=ao[0], ab_rows=lw.ab_dense.shape[0],
-                         eps=sp.eps, pdl=pdl)
+                col(lw.qkvz, qo[0], lw.ln1, ab_w=lw.ab_dense, ab_out=ao[0], ab_rows=lw.ab_dense.shape[0])
                 K.gdn_decode(qo, qo.shape[1], ao, self.ldab, lw.conv_w, lw.a_log, lw.dt_bias, lw.gamma,
                              self.pool.conv_state[gi], self.pool.rec_state[gi], v["gslot"], out=self.mix, batch=lay.b, t=lay.t,
                              nk=sp.nk, nv=sp.nv, group=self.G, eps=sp.eps, pdl=pdl)
-                K.w4_fma(lw.out_proj, mix, h, residual=h, epi=K.EPI_RESIDUAL, pdl=pdl)
+                row(0, lw.out_proj, mix)
                 gi += 1
             else:
-                K.w4_fma(lw.qkv, h, self.qkv_out[0], norm_w=lw.ln1, eps=sp.eps, pdl=pdl)
+                col(lw.qkv, self.qkv_out[0], lw.ln1)
                 qn = 2 * sp.hq * sp.hd
                 kraw, vraw = self.qkv_out[:, qn:], self.qkv_out[:, qn + sp.hkv * sp.hd:]
                 K.qknorm_rope_insert(self.qkv_out, self.qkv_n, kraw, self.qkv_n, vraw, self.qkv_n, lw.q_norm, lw.k_norm,
@@ -655,13 +696,18 @@ class HybridRunner:
                              pdl=pdl, scales=self.pool.scales(fi))
                 K.attn_reduce(self.part_o, self.part_ml, splits, self.qkv_out, self.qkv_n, 1, sp.hq, out=self.mix,
                               group=self.G, pdl=pdl)
-                K.w4_fma(lw.o_proj, mix, h, residual=h, epi=K.EPI_RESIDUAL, pdl=pdl)
+                row(0, lw.o_proj, mix)
                 fi += 1
-            K.w4_fma(lw.gate_up, h, act, norm_w=lw.ln2, epi=K.EPI_SILU_MUL, eps=sp.eps, pdl=pdl)
-            K.w4_fma(lw.down, act, h, residual=h, epi=K.EPI_RESIDUAL, pdl=pdl)
+            col(lw.gate_up, act, lw.ln2, epi=K.EPI_SILU_MUL)
+            row(1, lw.down, act)
             if self.taps is not None and i in self.taps:
                 self.taps[i][:1].copy_(self.h[:1])
-        self._norm(1, self.w.final_norm, want_xn=True, want_pack=False)
+        if st["pending"] is not None:
+            assert st["cur"] is self.h
+            symm.push_residual_norm(st["pending"], self.h, 1, self.w.final_norm, normed=self.xn, group=self.G, eps=sp.eps, pdl=pdl,
+                                    fma=True)
+        else:
+            self._norm(1, self.w.final_norm, want_xn=True, want_pack=False)
 
     # -- decode / verify step ------------------------------------------------------------------
     def step_forward(self, lay: StepLayout, *, ctx_hint: int = 2048, advance: bool = False, sample: bool = True) -> None:

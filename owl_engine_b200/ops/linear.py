@@ -37,16 +37,28 @@ def _dense_scratch(n: int, k: int, device, dtype=torch.bfloat16) -> torch.Tensor
     key = (str(device), dtype)
     buf = _scratch.get(key)
     if buf is None or buf.numel() < n * k:
-        buf = torch.empty(n * k, dtype=dtype, device=device)
+        led = _ledger(device)
+        led.release(f"dequant scratch {dtype}")
+        _scratch.pop(key, None)
+        buf = None
+        buf = led.alloc(f"dequant scratch {dtype}", "workspace", (n * k,), dtype)
         _scratch[key] = buf
     return buf[:n * k].view(n, k)
+
+
+def _ledger(device):
+    from ..utils.ledger import ledger_for
+
+    return ledger_for(device)
 
 
 def _fp8_scratch(tag: str, r: int, k: int, device):
     key = (tag, str(device))
     buf = _scratch.get(key)
     if buf is None or buf[0].numel() < r * k or buf[1].numel() < r:
-        buf = (torch.empty(r * k, dtype=torch.uint8, device=device), torch.empty(r, dtype=torch.float32, device=device))
+        led = _ledger(device)
+        led.release(f"e4m3 scratch {tag}")
+        buf = (led.alloc(f"e4m3 scratch {tag}", "workspace", (r * k,), torch.uint8), torch.empty(r, dtype=torch.float32, device=device))
         _scratch[key] = buf
     return buf[0][:r * k].view(r, k), buf[1][:r]
 
@@ -65,6 +77,7 @@ def w4_gemm(w, x: torch.Tensor, out: torch.Tensor, arm: str = "tc") -> torch.Ten
             dense = K.w4_dequant(w, _dense_scratch(w.n, w.k, x.device, torch.float16))
             cached = gemm_tc.quant_e4m3_rows(dense) if resident else gemm_tc.quant_e4m3_rows(dense, *_fp8_scratch("w", w.n, w.k, x.device))
             if resident:
+                _ledger(x.device).track("resident e4m3 weight copy", "resident copies", cached[0])
                 w._owl_e4m3 = cached
         wq, sw = cached
         xq, sx = gemm_tc.quant_e4m3_rows(x, *_fp8_scratch("x", x.shape[0], w.k, x.device))
@@ -116,7 +129,9 @@ def w4_e4m3(w, device):
     cached = getattr(w, "_owl_e4m3", None)
     if cached is None:
         dense = K.w4_dequant(w, _dense_scratch(w.n, w.k, device, torch.float16))
+        _ledger(device).check("resident e4m3 weight copy", w.n * w.k)
         cached = gemm_tc.quant_e4m3_rows(dense)
+        _ledger(device).track("resident e4m3 weight copy", "resident copies", cached[0])
         w._owl_e4m3 = cached
     return cached
 
@@ -127,7 +142,9 @@ def w4_dense(w, dtype, device, resident: bool = False) -> torch.Tensor:
     if resident:
         d = getattr(w, "_owl_dense", None)
         if d is None or d.dtype != dtype:
-            d = K.w4_dequant(w, torch.empty(w.n, w.k, dtype=dtype, device=device))
+            # 4x the int4 bytes: a named, budget-checked entry of the device ledger (a profile whose budget cannot hold
+            # the copies is refused here, at the first chunk, instead of running the device out of memory later)
+            d = K.w4_dequant(w, _ledger(device).alloc("resident dense weight copy", "resident copies", (w.n, w.k), dtype))
             w._owl_dense = d
         return d
     return K.w4_dequant(w, _dense_scratch(w.n, w.k, device, dtype))

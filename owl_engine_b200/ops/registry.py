@@ -40,6 +40,7 @@ _T = [
     KernelSpec("owl_w8a16_skinny", "gemv.cu", "gemv", gen="mma.sync+bulk-copy"),
     KernelSpec("owl_skinny_status", "gemv.cu", "status", capture=False),
     KernelSpec("owl_w4_fma", "gemv_fma.cu", "gemv", gen="hfma2+bulk-copy"),
+    KernelSpec("owl_w4_fma_tp", "gemv_fma.cu", "gemv", gen="hfma2+bulk-copy+p2p"),
     KernelSpec("owl_fma_status", "gemv_fma.cu", "status", capture=False),
     KernelSpec("owl_w4a16_stream_tc", "gemv_tc.cu", "gemv", gen="tcgen05+tmem+bulk-copy"),
     KernelSpec("owl_stream_tc_status", "gemv_tc.cu", "status", capture=False),
@@ -52,8 +53,11 @@ _T = [
     KernelSpec("owl_f16_gemm_rs", "gemm_dense.cu", "gemm", gen="tcgen05+tmem+tma+p2p"),
     KernelSpec("owl_e4m3_gemm", "gemm_dense.cu", "gemm", gen="tcgen05+tmem+tma"),
     KernelSpec("owl_gemm_dense_status", "gemm_dense.cu", "status", capture=False),
+    KernelSpec("owl_gemm_dense_set_scratch", "gemm_dense.cu", "status", capture=False),
     KernelSpec("owl_w4_dequant", "dequant.cu", "load"),
     KernelSpec("owl_quant_e4m3_rows", "dequant.cu", "load"),
+    KernelSpec("owl_kv_pages_gather", "kvmove.cu", "store"),
+    KernelSpec("owl_kv_pages_scatter", "kvmove.cu", "store"),
     KernelSpec("owl_mean_k_block", "kvmem.cu", "select"),
     KernelSpec("owl_mean_k_block_fmt", "kvmem.cu", "select"),
     KernelSpec("owl_kvscore", "kvmem.cu", "select"),

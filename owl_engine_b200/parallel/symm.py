@@ -33,7 +33,9 @@ _P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 K.register("owl_ar_residual_norm", [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, ctypes.c_uint,
                                     _I, _P])
 K.register("owl_w4a16_skinny_push", [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P])
-K.register("owl_push_residual_norm", [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, ctypes.c_uint, _I, _P])
+K.register("owl_push_residual_norm", [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, ctypes.c_uint, _P, _I, _I, _P])
+K.register("owl_w4_fma_tp", [_P, _P, _P, _P, _I, _I, _I, _F, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I,
+                             ctypes.c_uint, _I, _I, _P])
 K.register("owl_ar_inplace", [_P, _P, _P, _P, ctypes.c_longlong, _I, _I, _I, _I, ctypes.c_uint, _P])
 K.register("owl_argmax_merge", [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, ctypes.c_uint, _I, _P])
 K.register("owl_comm_wait_probe", [_P, ctypes.c_uint, ctypes.c_uint, _P, _P])
@@ -137,6 +139,28 @@ class PrefillPipe:
         return out
 
 
+class LocalSplit:
+    """The push / pull pairing of the one-token projections on ONE GPU (no peers): a row-parallel projection with few row
+    tiles is cut into ``kparts`` k parts whose partial sums land in slots of a plain device buffer, and the next
+    column-parallel projection adds them in its prologue. Same kernels, flags and sequence numbers as the tensor-parallel
+    form with a world of one, so a single GPU exercises the protocol."""
+
+    def __init__(self, device, hidden: int, kparts: int = 4):
+        self.rank, self.world, self.device, self.hidden, self.kparts = 0, 1, device, hidden, kparts
+        from ..utils.ledger import ledger_for
+
+        led = ledger_for(device)
+        self.buf = led.alloc("k-split slots", "workspace", (2, 8, MAX_ROWS, hidden), torch.bfloat16, zero=True)
+        self.flags = torch.zeros(2, 8, dtype=torch.int32, device=device)
+        self.push_slots = [self.buf[0], self.buf[1]]
+        self.push_flags_local = [self.flags[0], self.flags[1]]
+        self.push_dst = [_ptr_array([self.buf[w].data_ptr()]) for w in range(2)]
+        self.push_flag = [_ptr_array([self.flags[w].data_ptr()]) for w in range(2)]
+        self.push_count = torch.zeros(2, dtype=torch.int32, device=device)
+        self.push_seq = torch.zeros(2, dtype=torch.int32, device=device)
+        self.push_counters = torch.zeros(2, MAX_ROWS, dtype=torch.int32, device=device)
+
+
 class SymmetricWorkspace:
     def __init__(self, rank: int, world: int, device, group=None, hidden: int = 5120, big_elems: int = 2048 * 5120,
                  use_multimem: bool = False):
@@ -150,7 +174,8 @@ class SymmetricWorkspace:
         self.off_big = (self.off_exch + MAX_ROWS * 8 * 8 + 255) // 256 * 256
         self.big_elems = big_elems
         self.off_push = (self.off_big + big_elems * 2 + 255) // 256 * 256
-        push_bytes = world * MAX_ROWS * hidden * 2
+        self.kparts = max(1, min(4, 8 // world))       # k parts of the one-token row-parallel projections (ranks x parts <= 8)
+        push_bytes = 8 * MAX_ROWS * hidden * 2
         self.off_pflags = self.off_push + 2 * push_bytes
         pf_rows = big_elems // hidden
         ml = PrefillPipe.max_local_for(pf_rows, world)
@@ -212,10 +237,30 @@ class SymmetricWorkspace:
                self.world, MAX_ROWS, int(force_mma), int(pdl), K.stream())
 
     def push_residual_norm(self, which: int, h, m: int, norm_w, *, normed=None, xpack=None, xs=None, group: int = 128,
-                           eps: float = 1e-6, pdl: bool = False) -> None:
+                           eps: float = 1e-6, pdl: bool = False, fma: bool = False) -> None:
+        """Consumer of ``gemv_push`` / ``fma_push``: waits until every rank's flag reached the sequence number the LOCAL
+        producer of this call site published last (one number series per call site, whichever producer or consumer kernel
+        a step uses), then residual + norm. ``fma``: the producer was ``fma_push`` (slots are [rank][k part])."""
         K.call("owl_push_residual_norm", K.ptr(self.push_slots[which]), K.ptr(self.push_flags_local[which]),
                K.ptr(self.push_counters[which]), K.ptr(h), K.ptr(norm_w), K.ptr(normed), K.ptr(xpack), K.ptr(xs), m,
-               self.hidden, group, self.world, MAX_ROWS, eps, 1, SPIN_LIMIT, int(pdl), K.stream())
+               self.hidden, group, self.world, MAX_ROWS, eps, 1, SPIN_LIMIT,
+               K.ptr(self.push_seq[which:]), self.kparts if fma else 1, int(pdl), K.stream())
+
+    # -- one-token projections on the FMA arm with the collective inside (csrc/gemv_fma.cu) ------------------------------
+    def fma_push(self, which: int, w, x, *, pdl: bool = False, groups_per_cta: int = 0) -> None:
+        """Row-parallel projection of one token: the partial sums go straight into slot [rank] of every rank's buffer."""
+        K.call("owl_w4_fma_tp", K.ptr(w.records), K.ptr(x), None, None, w.n, w.k, 0, 0.0, 1, 1, self.push_dst[which],
+               self.push_flag[which], K.ptr(self.push_count[which:]), K.ptr(self.push_seq[which:]), None, None, None, None,
+               None, None, 0, self.rank, self.world, MAX_ROWS, self.kparts, SPIN_LIMIT, groups_per_cta, int(pdl), K.stream())
+
+    def fma_pull(self, which: int, w, h_in, h_out, norm_w, out, *, epi: int = 0, eps: float = 1e-6, ab_w=None, ab_out=None,
+                 ab_rows: int = 0, pdl: bool = False, groups_per_cta: int = 0) -> None:
+        """Column-parallel projection of one token that first completes the all-reduce of call site ``which``:
+        ``h_out = h_in + sum of the ranks' slots`` (stored by one CTA), ``out = epilogue(W . rmsnorm(h_out))``."""
+        K.call("owl_w4_fma_tp", K.ptr(w.records), K.ptr(h_in), K.ptr(norm_w), K.ptr(out), w.n, w.k, epi, eps, 1, 0, None, None,
+               None, None, K.ptr(self.push_slots[which]), K.ptr(self.push_flags_local[which]), K.ptr(self.push_seq[which:]),
+               K.ptr(h_out), K.ptr(ab_w), K.ptr(ab_out), ab_rows, self.rank, self.world, MAX_ROWS, self.kparts, SPIN_LIMIT,
+               groups_per_cta, int(pdl), K.stream())
 
     def partial(self, which: int) -> torch.Tensor:
         return self.part_a if which == 0 else self.part_b
@@ -240,3 +285,9 @@ class SymmetricWorkspace:
         f = K.fn("owl_comm_status")
         f.argtypes = []
         return f()
+
+
+# the world-of-one form shares the launch wrappers
+LocalSplit.fma_push = SymmetricWorkspace.fma_push
+LocalSplit.fma_pull = SymmetricWorkspace.fma_pull
+LocalSplit.push_residual_norm = SymmetricWorkspace.push_residual_norm

@@ -316,16 +316,10 @@ class Vision:
 
 
 def _vram(re) -> dict:
-    import torch
-
-    from ..store.budget import Ledger
-
-    free, total = torch.cuda.mem_get_info(re.e.device)
-    led = Ledger()
-    led.record("weights", "weights", re.e.weights.nbytes())
-    led.record("kv_pool", "kv pool", re.e.pool.k_pool.numel() * re.e.pool.k_pool.element_size() * 2)
-    led.record("gdn_rows", "gdn state", re.e.pool.conv_state.numel() * 4 + re.e.pool.rec_state.numel() * 4)
-    return led.view(total, free)
+    """The engine's allocation ledger as mutually exclusive buckets that close to the driver's total (``utils/ledger.py``)."""
+    v = re.e.ledger.view()
+    v["tiers"] = re.e.rel.facts()
+    return v
 
 
 async def serve(app: App, host: str, port: int):

@@ -42,6 +42,7 @@ def lib():
         l.owl_kv_evict.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int]
         l.owl_kv_set_carrier.argtypes = [c_void_p, c_uint64, c_int, c_int]
         l.owl_kv_forget.argtypes = [c_void_p, c_uint64]
+        l.owl_kv_adopt.argtypes = [c_void_p, c_uint64, c_uint64, c_int, c_int, c_uint64]
         l.owl_kv_node.argtypes = [c_void_p, c_uint64, c_void_p, c_void_p, c_void_p, c_void_p]
         l.owl_kv_stats.argtypes = [c_void_p, c_void_p]
         l.owl_kv_list.argtypes = [c_void_p, c_int, c_void_p, c_int]
@@ -117,6 +118,10 @@ class KvStore:
     def set_carrier(self, h: int, carrier: int, slot: int) -> None:
         if lib().owl_kv_set_carrier(self.h, h, carrier, slot) != 0:
             raise KeyError(h)
+
+    def adopt(self, h: int, parent: int, carrier: int, slot: int = 0, tag: int = 0) -> bool:
+        """Insert a node that lives on the host (carrier 1, ``slot``) or on disk (carrier 2): restart adoption."""
+        return lib().owl_kv_adopt(self.h, h, parent, carrier, slot, tag) == 1
 
     def forget(self, h: int) -> bool:
         return lib().owl_kv_forget(self.h, h) == 0

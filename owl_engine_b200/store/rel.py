@@ -1,0 +1,298 @@
+"""Rel: the relocation facade of the KV store. One object plans and executes every move of a KV block between its
+carriers (device pool, pinned host tier, disk tier) and keeps the recurrent-state snapshots that make a cached prefix
+usable on a hybrid model.
+
+* ``make_room(n)``     need-driven pressure path: ``plan_capacity`` decides how many leaf-LRU blocks leave the device
+                       and whether they go to the host tier, through it to disk, or are dropped; the copies are batched
+                       (``Mover.copy_out_many``).
+* ``relieve()``        watermark-driven: when free pages fall under the policy's low mark, demote up to the high mark
+                       (called between steps, so the next admission finds room without moving anything).
+* ``promote(...)``     recall of a matched prefix whose blocks live on the host or on disk. Modes: ``"sync"`` (bring
+                       everything back, the caller waits on the mover fence), ``"resident"`` (use only what is on the
+                       device: a miss from the first demoted block on, nothing moves), ``"host"`` (host-resident blocks
+                       come back, disk-resident ones end the prefix).
+* ``checkpoint()``     write-through for restarts: every block of the host tier, the device-resident blocks of the prefix
+                       tree (optional) and the durable state snapshots are written to the disk tier, then the index.
+* ``adopt()``          at boot: the disk tier's index becomes prefix-tree nodes with the disk carrier, and the snapshot
+                       files become lazily loadable snapshots, so the first request after a restart can hit the cache.
+
+Reference counterpart: ``crates/store/src/rel.rs`` (the Rel facade, ``adopt_disk*`` at 1221-1290), ``hooks.rs:263``
+(``plan_capacity``), ``pressure.rs``, ``crates/engine/src/mem/disk_runtime.rs``.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from . import budget as B
+
+DEVICE, HOST, DISK = 0, 1, 2
+
+
+class Rel:
+    def __init__(self, kv, states, pool, host=None, mover=None, disk=None, block_tokens: int = 16, policy: B.PressurePolicy | None = None):
+        self.kv, self.states, self.pool = kv, states, pool
+        self.host, self.mover, self.disk = host, mover, disk
+        self.block_tokens = block_tokens
+        self.policy = policy or B.PressurePolicy()
+        self.host_slot_of: dict[int, int] = {}        # chain hash -> host slot, oldest first
+        self.meta: dict[int, tuple] = {}              # chain hash -> (parent hash, tag, tokens as int32 array): what the index stores
+        self.disk_snaps: dict[int, int] = {}          # prefix hash -> n_tokens of a snapshot that exists only on disk
+        self.spilled = self.recalled = self.demoted = self.dropped = self.adopted = 0
+        self.last_verdict: B.Verdict | None = None
+
+    # -- bookkeeping at publish time ----------------------------------------------------------------------------------------
+    def note_published(self, chain, tokens, tags=None) -> None:
+        """Remember parent / tokens of freshly published blocks (the restart index stores them)."""
+        bt = self.block_tokens
+        toks = np.asarray(tokens, dtype=np.int32)
+        parent = 0
+        for i, h in enumerate(chain):
+            h = int(h)
+            if h not in self.meta:
+                self.meta[h] = (parent, int(tags[i]) if tags is not None else 0, toks[i * bt:(i + 1) * bt].copy())
+            parent = h
+
+    def _meta(self, h: int) -> tuple:
+        m = self.meta.get(h)
+        if m is not None:
+            return m
+        nd = self.kv.node(h)
+        return ((nd or {}).get("parent", 0), (nd or {}).get("tag", 0), np.zeros(0, dtype=np.int32))
+
+    # -- pressure -------------------------------------------------------------------------------------------------------
+    def host_free(self) -> int:
+        return len(self.host.free) if self.host is not None else 0
+
+    def disk_free(self) -> int:
+        if self.disk is None or self.host is None:
+            return 0
+        return max(0, (self.disk.capacity - self.disk.used) // self.disk.page_bytes)
+
+    def make_room(self, need: int) -> None:
+        """Free device pages until ``need`` are available, cheapest sink first."""
+        st = self.kv.stats()
+        # leaves expose their parents as they go, so every device-resident tree block is a candidate in the end
+        free, evictable = st["free_pages"], st["device_nodes"]
+        v = B.plan_capacity(need, free, evictable, self.host_free(), self.disk_free())
+        self.last_verdict = v
+        if v.evict_pages <= 0:
+            return
+        remaining = need - free
+        while remaining > 0 and self.host is not None:
+            room = self.host_free()
+            if room == 0 and self.disk is not None and self.host_slot_of:
+                self.spill_host(min(remaining, len(self.host_slot_of)))      # host tier full: its oldest blocks go down to disk
+                room = self.host_free()
+            if room == 0:
+                break
+            n = self._demote(self.kv.free_pages + min(remaining, room))
+            if n == 0:
+                break
+            remaining -= n
+        if remaining > 0:
+            pages, hashes = self.kv.evict(need_free=need, demote=False)       # no tier left to hold them
+            self.dropped += len(pages)
+            for h in hashes:
+                self.meta.pop(int(h), None)
+
+    def _demote(self, need_free: int) -> int:
+        pages, hashes = self.kv.evict(need_free=need_free, demote=True)
+        slots = [self.host.alloc() for _ in pages]
+        self.mover.copy_out_many(pages, slots)
+        for h, slot in zip(hashes, slots):
+            self.kv.set_carrier(int(h), HOST, slot)
+            self.host_slot_of[int(h)] = slot
+        self.mover.fence()
+        self.demoted += len(pages)
+        return len(pages)
+
+    def relieve(self) -> int:
+        """Watermark relief between steps. Returns the number of pages demoted."""
+        if self.host is None:
+            return 0
+        free = self.kv.free_pages
+        target = self.policy.target(free, self.kv.n_pages)
+        if target <= 0:
+            return 0
+        room = self.host_free()
+        if room < target and self.disk is not None:
+            self.spill_host(min(target - room, len(self.host_slot_of)))
+            room = self.host_free()
+        n = min(target, room, self.kv.stats()["device_nodes"])
+        return self._demote(free + n) if n > 0 else 0
+
+    def spill_host(self, n: int) -> None:
+        """Make room in the pinned-host tier: its oldest blocks go to disk files; when the disk tier is full they leave
+        the prefix tree."""
+        if n <= 0:
+            return
+        self.mover.sync()                                  # demotions into the slots about to be read have landed
+        for h in list(self.host_slot_of)[:n]:
+            slot = self.host_slot_of.pop(h)
+            parent, tag, toks = self._meta(h)
+            if self.disk is not None and self.disk.spill(h, parent, toks, self.host.slot(slot), tag):
+                self.kv.set_carrier(h, DISK, 0)
+                self.spilled += 1
+            else:
+                self.kv.forget(h)
+                self.meta.pop(h, None)
+                self.dropped += 1
+            self.host.release(slot)
+
+    # -- recall ---------------------------------------------------------------------------------------------------------
+    def promote(self, chain, keep: int, pages: list, carriers: list, alloc_page, mode: str = "sync") -> tuple[int, set]:
+        """Bring the first ``keep`` matched blocks back to the device. ``alloc_page()`` returns one device page (it may run
+        the pressure path) or None. Returns (blocks usable from the start of the chain, indices that were promoted);
+        ``pages`` is updated in place with the new device pages."""
+        promoted: set = set()
+        if mode == "resident":
+            for i in range(keep):
+                if carriers[i] != DEVICE:
+                    return i, promoted
+            return keep, promoted
+        batch: list = []
+
+        def flush():
+            """Execute the recalls collected so far (one batched copy) and give their host slots back."""
+            if batch:
+                self.mover.copy_in_many([b[2] for b in batch], [b[3] for b in batch])
+                if self.mover.stream is not None:
+                    self.mover.sync()                  # the slots are reused at once: the copies must have read them
+                for _, hh, slot, pg in batch:
+                    self.kv.set_carrier(hh, DEVICE, pg)
+                    self.host.release(slot)
+                batch.clear()
+        usable = keep
+        for i in range(keep):
+            if carriers[i] == DEVICE:
+                continue
+            h = int(chain[i])
+            if h not in self.host_slot_of:
+                if mode == "host" or self.disk is None or h not in self.disk.index or self.host is None:
+                    usable = i
+                    break
+                if not self.host.free:
+                    flush()                            # staging slots of this very recall come back first
+                if not self.host.free:
+                    self.spill_host(1)
+                hslot = self.host.alloc()
+                if hslot is None:
+                    usable = i
+                    break
+                self.mover.sync()                          # no copy still reads the recycled slot
+                self.disk.fill(h, self.host.slot(hslot))
+                self.disk.drop(h)
+                self.host_slot_of[h] = hslot
+                self.recalled += 1
+            slot = self.host_slot_of.pop(h)            # pinned: the pressure path below must not spill what is being recalled
+            pg = alloc_page()
+            if pg is None:
+                self.host_slot_of[h] = slot
+                usable = i
+                break
+            batch.append((i, h, slot, pg))
+            pages[i] = pg
+            promoted.add(i)
+        if batch:
+            self.mover.copy_in_many([b[2] for b in batch], [b[3] for b in batch])
+            for _, hh, slot, pg in batch:
+                self.kv.set_carrier(hh, DEVICE, pg)
+                self.host.release(slot)
+        if self.mover is not None:
+            self.mover.fence()
+        return usable, promoted
+
+    # -- recurrent-state snapshots ----------------------------------------------------------------------------------------
+    def _state_bytes(self, row: int) -> torch.Tensor:
+        return torch.cat([self.pool.conv_state[:, row].reshape(-1).view(torch.uint8),
+                          self.pool.rec_state[:, row].reshape(-1).view(torch.uint8)])
+
+    def _state_load(self, row: int, raw: torch.Tensor) -> None:
+        nc = self.pool.conv_state[:, row].numel() * 4
+        self.pool.conv_state[:, row].copy_(raw[:nc].view(torch.float32).view_as(self.pool.conv_state[:, row]))
+        self.pool.rec_state[:, row].copy_(raw[nc:].view(torch.float32).view_as(self.pool.rec_state[:, row]))
+
+    def find_snapshot(self, chain):
+        """Deepest snapshot along a chain: live ones first; a snapshot that only exists on disk is loaded into a snapshot
+        row (evicting the least recently used one) and becomes live."""
+        snap = self.states.find(chain)
+        if not self.disk_snaps:
+            return snap
+        for i in range(len(chain) - 1, -1, -1):
+            h = int(chain[i])
+            if snap is not None and snap.chain_hash == h:
+                return snap
+            if h in self.disk_snaps:
+                n_tok = self.disk_snaps[h]
+                row = self.states.snapshot(h, n_tok)
+                if row is None:
+                    return snap
+                self._state_load(row, self.disk.get_state(h).to(self.pool.conv_state.device))
+                del self.disk_snaps[h]
+                self.recalled += 1
+                return self.states.snaps[h]
+        return snap
+
+    # -- checkpoint / adoption --------------------------------------------------------------------------------------------
+    def checkpoint(self, include_device: bool = True) -> dict:
+        """Write-through for a restart: host-tier blocks (and the device-resident tree blocks) are copied to the disk tier
+        without leaving their carrier, durable state snapshots too, then the index is saved."""
+        if self.disk is None:
+            return {"blocks": 0, "states": 0}
+        wrote = 0
+        if self.mover is not None:
+            self.mover.sync()
+        for h, slot in list(self.host_slot_of.items()):
+            parent, tag, toks = self._meta(h)
+            wrote += self.disk.spill(h, parent, toks, self.host.slot(slot), tag) and 1
+        if include_device and self.host is not None:
+            from .tiers import page_views
+
+            for h in self.kv.list(DEVICE):
+                if h in self.disk.index or h not in self.meta:
+                    continue
+                if self.disk.used + self.disk.page_bytes > self.disk.capacity:
+                    break
+                nd = self.kv.node(h)
+                data = torch.cat([v.reshape(-1) for v in page_views(self.pool, nd["page"])]).cpu()
+                parent, tag, toks = self._meta(h)
+                wrote += self.disk.spill(h, parent, toks, data, tag) and 1
+        n_states = 0
+        for h, s in list(self.states.snaps.items()):
+            if s.klass == "durable" and h not in self.disk.states:
+                n_states += self.disk.put_state(h, s.n_tokens, self._state_bytes(s.row)) and 1
+        n = self.disk.save_index(self.block_tokens)
+        return {"blocks": wrote, "states": n_states, "indexed": n}
+
+    def adopt(self) -> dict:
+        """Rebuild prefix-tree nodes (disk carrier) and lazily loadable snapshots from the disk tier's index."""
+        if self.disk is None:
+            return {"blocks": 0, "states": 0}
+        n = self.disk.load_index()
+        if n and getattr(self.disk, "index_block_tokens", self.block_tokens) != self.block_tokens:
+            self.disk.index.clear()
+            self.disk.states.clear()
+            return {"blocks": 0, "states": 0, "refused": "block size of the index differs from this profile's"}
+        bad = 0
+        for h in self.disk.chain_order():
+            rec = self.disk.index[h]
+            toks = np.asarray(rec["tokens"], dtype=np.int32)
+            # the hash must follow from the parent and the tokens: a file that does not belong to its chain is refused
+            if len(toks) == self.block_tokens and int(self.kv.chain(toks, root=rec["parent"], tags=[rec.get("tag", 0)])[0]) != h:
+                bad += 1
+                self.disk.drop(h)
+                continue
+            if self.kv.adopt(h, rec["parent"], DISK, 0, rec.get("tag", 0)):
+                self.meta[h] = (rec["parent"], rec.get("tag", 0), toks)
+                self.adopted += 1
+        for h, st in self.disk.states.items():
+            self.disk_snaps[h] = st["n_tokens"]
+        return {"blocks": self.adopted, "states": len(self.disk_snaps), "refused_blocks": bad}
+
+    def facts(self) -> dict:
+        return {"host_used": self.host.used if self.host else 0, "host_slots": self.host.n_slots if self.host else 0,
+                "disk_blocks": len(self.disk.index) if self.disk else 0, "disk_states": len(self.disk.states) if self.disk else 0,
+                "demoted": self.demoted, "spilled": self.spilled, "recalled": self.recalled, "dropped": self.dropped,
+                "adopted": self.adopted, "mover_copies": self.mover.copies if self.mover else 0,
+                "last_verdict": None if self.last_verdict is None else vars(self.last_verdict)}

@@ -105,3 +105,55 @@ def test_w4_fma_rejects_bad_shapes():
         K.w4_fma(s, x, out, epi=K.EPI_RESIDUAL)          # residual missing
     with pytest.raises(Exception):
         K.w4_fma(s, x, out, groups_per_cta=3)
+
+
+@pytest.mark.parametrize("parts", [1, 4])
+def test_w4_fma_push_pull_protocol_world_of_one(parts):
+    """``parts`` > 1 also cuts every row tile of the row-parallel launch into k parts that land in slots of their own.
+    The tensor-parallel pairing on one GPU: the row-parallel launch stores its partial sums into slot 0 of a local
+    buffer and publishes sequence numbers; the column-parallel launch waits for them, adds the slot to the residual stream
+    (stored into a second buffer) and normalises in its prologue. Two rounds, so the sequence numbers advance."""
+    import ctypes
+
+    from owl_engine_b200.parallel import symm  # noqa: F401  (registers the signature)
+
+    hdim, kdim, n2, rows = 5120, 2176, 1024, 32
+    cr, wr = _weight(hdim, kdim, 21)          # row-parallel: kdim -> hidden
+    cc, wc = _weight(n2, hdim, 22)            # column-parallel: hidden -> n2
+    slots = torch.zeros(parts, rows, hdim, dtype=torch.bfloat16, device=DEV)
+    flags = torch.zeros(8, dtype=torch.int32, device=DEV)
+    count = torch.zeros(1, dtype=torch.int32, device=DEV)
+    seq = torch.zeros(1, dtype=torch.int32, device=DEV)
+    arr = lambda t: (ctypes.c_void_p * 8)(t.data_ptr())
+    nw = (torch.randn(hdim, generator=gen(23)) * 0.1).to(torch.bfloat16).to(DEV)
+    h = torch.randn(hdim, generator=gen(24)).to(torch.bfloat16)
+    h_in, h_out = h.clone().to(DEV), torch.zeros(hdim, dtype=torch.bfloat16, device=DEV)
+    want_h = h.float()
+    for rnd in range(2):
+        x = torch.randn(kdim, generator=gen(30 + rnd)).to(torch.bfloat16)
+        out = torch.zeros(n2, dtype=torch.bfloat16, device=DEV)
+        K.call("owl_w4_fma_tp", K.ptr(wr.records), K.ptr(x.to(DEV)), None, None, hdim, kdim, 0, 0.0, 1, 1, arr(slots), arr(flags),
+               K.ptr(count), K.ptr(seq), None, None, None, None, None, None, 0, 0, 1, rows, parts, 1 << 20, 0, 0, K.stream())
+        K.call("owl_w4_fma_tp", K.ptr(wc.records), K.ptr(h_in), K.ptr(nw), K.ptr(out), n2, hdim, 0, 1e-6, 1, 0, None, None, None,
+               None, K.ptr(slots), K.ptr(flags), K.ptr(seq), K.ptr(h_out), None, None, 0, 0, 1, rows, parts, 1 << 20, 0, 0, K.stream())
+        torch.cuda.synchronize()
+        assert int(seq.item()) == rnd + 1 and int(flags[0].item()) == rnd + 1 and int(count.item()) == 0
+        part = cr.dequant() @ x.float()
+        want_h = (want_h + part).to(torch.bfloat16).float()
+        torch.testing.assert_close(h_out.float().cpu(), want_h, rtol=2e-2, atol=6e-2)
+        hn = h_out.float().cpu()
+        xn = (hn * torch.rsqrt((hn * hn).mean() + 1e-6) * (1.0 + nw.float().cpu())).to(torch.bfloat16).float()
+        want = cc.dequant() @ xn
+        err = (out.float().cpu() - want).norm() / want.norm()
+        assert err < 5e-3, err
+        h_in, h_out = h_out, h_in
+        want_h = h_in.float().cpu()
+    assert K.fma_status() == 0
+    # a flag nobody raises: the bounded wait runs out, the kernel finishes and reports it (nothing hangs)
+    seq.fill_(99)
+    out = torch.zeros(n2, dtype=torch.bfloat16, device=DEV)
+    K.call("owl_w4_fma_tp", K.ptr(wc.records), K.ptr(h_in), K.ptr(nw), K.ptr(out), n2, hdim, 0, 1e-6, 1, 0, None, None, None,
+           None, K.ptr(slots), K.ptr(flags), K.ptr(seq), K.ptr(h_out), None, None, 0, 0, 1, rows, parts, 2000, 0, 0, K.stream())
+    torch.cuda.synchronize()
+    assert K.fma_status() == 3        # OWL_ERR_WAIT_PEER
+    assert K.fma_status() == 0        # read clears it
