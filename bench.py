@@ -98,6 +98,11 @@ def main() -> None:
     ap.add_argument("--head", default="int8", choices=["int8", "bf16"],
                     help="lm_head storage: per-row int8 (W8A16; the reference's default, profiles/full.toml:144 "
                          "head_quant = rtn-int8-row) or bf16")
+    ap.add_argument("--sessions", type=int, default=32,
+                    help="after the single-stream measurement, run this many concurrent sessions (random prompts of 1k-8k tokens, "
+                         "--session-out tokens each) through the serving path and report the aggregate rate under \"extra\" "
+                         "(0 = skip)")
+    ap.add_argument("--session-out", type=int, default=256)
     ap.add_argument("--comm", default="fused", choices=["nccl", "fused", "push"],
                     help="TP collectives: our symmetric-memory kernels (fused) or the NCCL baseline arm")
     args = ap.parse_args()
@@ -126,8 +131,13 @@ def main() -> None:
 
     # pages for the warm-up prompt and the timed prompt side by side, plus the generated tokens
     n_pages = max(1024, 2 * (args.prompt_len + 2 * (warmup + steps) + 64) // 16 + 64)
-    cfg = EngineConfig(model="qwen3.8-27b", group=128, n_pages=n_pages, n_slots=2, max_seqs=2,
-                       max_seq=args.prompt_len + 2 * (warmup + steps) + 64, n_layers=args.layers,
+    n_slots, max_seq = 2, args.prompt_len + 2 * (warmup + steps) + 64
+    if args.sessions > 0:        # room for the concurrent-session run that follows the headline measurement
+        n_slots = max(2, args.sessions)
+        max_seq = max(max_seq, 8192 + args.session_out + 64)
+        n_pages = max(n_pages, args.sessions * (8192 + args.session_out + 64) // 16 + 256)
+    cfg = EngineConfig(model="qwen3.8-27b", group=128, n_pages=n_pages, n_slots=n_slots, max_seqs=n_slots,
+                       max_seq=max_seq, n_layers=args.layers,
                        decode_gemv=args.gemv, prefill_gemm=args.prefill_gemm, lm_head_int8=args.head == "int8")
     eng = Engine(cfg, comm=comm)
     if args.sp_prefill >= 0:
@@ -228,6 +238,20 @@ def main() -> None:
     if comm:
         dev_ms = comm.max_over_ranks(dev_ms)
 
+    # ---- throughput: concurrent sessions through the serving path (does not change `value`) ---------------------------
+    extra = None
+    if args.sessions > 0:
+        from owl_engine_b200.fixtures.sessions_bench import run_sessions
+
+        eng.free_sequence(sid, publish=False)
+        extra = run_sessions(eng, args.sessions, 1024, 8192, args.session_out, max_batch=min(32, args.sessions))
+        if comm:
+            extra["seconds"] = round(comm.max_over_ranks(extra["seconds"]), 3)
+            extra["output_tok_s"] = round(extra["output_tokens"] / extra["seconds"], 1)
+            extra["total_tok_s"] = round((extra["output_tokens"] + extra["prompt_tokens"]) / extra["seconds"], 1)
+        extra["what"] = (f"{args.sessions} concurrent sessions, random prompts of 1024-8192 tokens, {args.session_out} output tokens "
+                         "each, through RunningEngine (admission, chunked prefill, batched decode); host-timed, max over ranks")
+
     # every bounded-wait status word of the native library (0 = no wait ran out anywhere), worst over the ranks
     status = K.all_status()
     if comm:
@@ -263,6 +287,7 @@ def main() -> None:
             "launches_per_step": launches_per_step,
             "clocks": clocks,
             "kernel_status": status,
+            "extra": extra,
         }
         if args.layers is not None:
             out["invalid"] = "debug run with fewer layers"

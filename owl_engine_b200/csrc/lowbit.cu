@@ -4,7 +4,7 @@
 //                          output row streams 16 codes + 1 scale per lane step, fp32 accumulate
 //   owl_nvfp4_dequant     W -> bf16 [N,K] (prefill: feeds the dense tcgen05 GEMM; load-time checks)
 //   owl_nvfp4_quant_act   x bf16 [M,K] -> codes + e4m3 block scales with a given global scale (W4A4 operand)
-//   owl_gguf_dequant      GGUF blocks (Q8_0, Q4_0, Q4_K, Q5_K, Q6_K, IQ4_NL, IQ4_XS) -> bf16; with a row index
+//   owl_gguf_dequant      GGUF blocks (Q8_0, Q4_0/1, Q5_0/1, Q2_K .. Q6_K, IQ4_NL, IQ4_XS, IQ3_XXS, IQ3_S) -> bf16; with a row index
 //                          list it is the quantised embedding-table lookup
 //   owl_gguf_gemv         out[M,N] = x[M,K] . dequant(blocks)[N,K]^T for M <= 8: one warp per output row,
 //                          dequantisation in registers (no dense copy of the weight)
@@ -158,7 +158,13 @@ __global__ void __launch_bounds__(256) nvfp4_quant_kernel(const __nv_bfloat16* _
 }
 
 // ---- GGUF blocks ------------------------------------------------------------------------------------
-enum { GG_Q8_0 = 8, GG_Q4_0 = 2, GG_Q4_K = 12, GG_Q5_K = 13, GG_Q6_K = 14, GG_IQ4_NL = 20, GG_IQ4_XS = 23 };
+enum { GG_Q8_0 = 8, GG_Q4_0 = 2, GG_Q4_1 = 3, GG_Q5_0 = 6, GG_Q5_1 = 7, GG_Q2_K = 10, GG_Q3_K = 11, GG_Q4_K = 12, GG_Q5_K = 13,
+       GG_Q6_K = 14, GG_IQ3_XXS = 18, GG_IQ4_NL = 20, GG_IQ3_S = 21, GG_IQ4_XS = 23 };
+
+// Codebooks of the IQ3 types (four magnitudes per entry), uploaded once by owl_gguf_set_grids from the host tables.
+__device__ uint32_t g_iq3xxs_grid[256];
+__device__ uint32_t g_iq3s_grid[512];
+__device__ __forceinline__ uint8_t ksign7(int i) { return (uint8_t)(i | ((__popc(i) & 1) << 7)); }   // 7 sign bits + even parity
 
 __device__ __constant__ int8_t c_iq4nl[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
 
@@ -175,6 +181,13 @@ __host__ __device__ __forceinline__ bool gguf_geom(int type, int& elems, int& by
     case GG_Q8_0: elems = 32; bytes = 34; return true;
     case GG_Q4_0: elems = 32; bytes = 18; return true;
     case GG_IQ4_NL: elems = 32; bytes = 18; return true;
+    case GG_Q4_1: elems = 32; bytes = 20; return true;
+    case GG_Q5_0: elems = 32; bytes = 22; return true;
+    case GG_Q5_1: elems = 32; bytes = 24; return true;
+    case GG_Q2_K: elems = 256; bytes = 84; return true;
+    case GG_Q3_K: elems = 256; bytes = 110; return true;
+    case GG_IQ3_XXS: elems = 256; bytes = 98; return true;
+    case GG_IQ3_S: elems = 256; bytes = 110; return true;
     case GG_Q4_K: elems = 256; bytes = 144; return true;
     case GG_Q5_K: elems = 256; bytes = 176; return true;
     case GG_Q6_K: elems = 256; bytes = 210; return true;
@@ -189,6 +202,49 @@ __device__ __forceinline__ float gguf_elem(int type, const uint8_t* b, int e) {
     case GG_Q8_0: return f16_at(b) * (float)(int8_t)b[2 + e];
     case GG_Q4_0: { const uint8_t q = b[2 + (e & 15)]; return f16_at(b) * (float)((int)(e < 16 ? (q & 0xF) : (q >> 4)) - 8); }
     case GG_IQ4_NL: { const uint8_t q = b[2 + (e & 15)]; return f16_at(b) * (float)c_iq4nl[e < 16 ? (q & 0xF) : (q >> 4)]; }
+    case GG_Q4_1: { const uint8_t q = b[4 + (e & 15)]; return f16_at(b) * (float)(e < 16 ? (q & 0xF) : (q >> 4)) + f16_at(b + 2); }
+    case GG_Q5_0:
+    case GG_Q5_1: {
+      const int off = type == GG_Q5_0 ? 2 : 4;
+      const uint32_t qh = b[off] | (b[off + 1] << 8) | (b[off + 2] << 16) | ((uint32_t)b[off + 3] << 24);
+      const uint8_t q = b[off + 4 + (e & 15)];
+      const int v = (e < 16 ? (q & 0xF) : (q >> 4)) | (((qh >> e) & 1) << 4);
+      return type == GG_Q5_0 ? f16_at(b) * (float)(v - 16) : f16_at(b) * (float)v + f16_at(b + 2);
+    }
+    case GG_Q2_K: {
+      // element e: half h (128), shift pair j, 16-run `half16`; scales[h*8 + j*2 + half16], qs[h*32 + l] >> 2j
+      const int h = e >> 7, r = e & 127, j = r >> 5, l = r & 31;
+      const uint8_t sc = b[h * 8 + j * 2 + (l >> 4)];
+      const int q = (b[16 + h * 32 + l] >> (2 * j)) & 3;
+      return f16_at(b + 80) * (float)(sc & 0xF) * (float)q - f16_at(b + 82) * (float)(sc >> 4);
+    }
+    case GG_Q3_K: {
+      const int h = e >> 7, r = e & 127, j = r >> 5, l = r & 31;
+      const int is = h * 8 + j * 2 + (l >> 4);                      // one of sixteen 6-bit scales
+      const uint8_t* sc = b + 96;
+      const int low4 = is < 8 ? (sc[is] & 0xF) : (sc[is - 8] >> 4);
+      const int hi2 = (sc[8 + (is & 3)] >> (2 * (is >> 2))) & 3;
+      const int scale = (low4 | (hi2 << 4)) - 32;
+      const int q = ((b[32 + h * 32 + l] >> (2 * j)) & 3) - ((b[l] & (1 << (h * 4 + j))) ? 0 : 4);
+      return f16_at(b + 108) * (float)scale * (float)q;
+    }
+    case GG_IQ3_XXS: {
+      const int ib = e >> 5, r = e & 31, l = r >> 3, jj = r & 7;   // sub-block ib, 8-run l, element jj
+      const uint8_t* gas = b + 66 + ib * 4;
+      const uint32_t aux = gas[0] | (gas[1] << 8) | (gas[2] << 16) | ((uint32_t)gas[3] << 24);
+      const uint32_t grid = g_iq3xxs_grid[b[2 + ib * 8 + 2 * l + (jj >> 2)]];
+      const float mag = (float)((grid >> (8 * (jj & 3))) & 0xFF);
+      const uint8_t signs = ksign7((aux >> (7 * l)) & 127);
+      return f16_at(b) * (0.5f + (float)(aux >> 28)) * 0.5f * mag * ((signs >> jj) & 1 ? -1.f : 1.f);
+    }
+    case GG_IQ3_S: {
+      const int ib = e >> 5, r = e & 31, l = r >> 3, jj = r & 7;
+      const int qh = b[66 + ib];
+      const int idx = b[2 + ib * 8 + 2 * l + (jj >> 2)] | ((jj < 4 ? (qh << (8 - 2 * l)) : (qh << (7 - 2 * l))) & 256);
+      const float mag = (float)((g_iq3s_grid[idx] >> (8 * (jj & 3))) & 0xFF);
+      const float d = f16_at(b) * (float)(1 + 2 * ((b[106 + (ib >> 1)] >> (4 * (ib & 1))) & 0xF));
+      return d * mag * ((b[74 + ib * 4 + l] >> jj) & 1 ? -1.f : 1.f);
+    }
     case GG_Q4_K: {
       const int j = e >> 5, l = e & 31;                 // sub-block j (32 elements): pair (j/2), low nibbles for even j
       float s, m; k_scale_min(b + 4, j, s, m);
@@ -342,6 +398,14 @@ OWL_API int owl_nvfp4_quant_act(const void* x, float global_scale, void* codes, 
   OWL_LAUNCH_CHECK();
   return OWL_OK;
 }
+// Uploads the IQ3 codebooks (host tables: 256 and 512 little-endian uint32 entries of four magnitudes) to the current device.
+OWL_API int owl_gguf_set_grids(const void* iq3xxs, const void* iq3s) {
+  if (!iq3xxs || !iq3s) return OWL_ERR_BAD_ARG;
+  if (cudaMemcpyToSymbol(g_iq3xxs_grid, iq3xxs, sizeof(uint32_t) * 256) != cudaSuccess) return OWL_ERR_LAUNCH * 1000;
+  if (cudaMemcpyToSymbol(g_iq3s_grid, iq3s, sizeof(uint32_t) * 512) != cudaSuccess) return OWL_ERR_LAUNCH * 1000;
+  return OWL_OK;
+}
+
 // blocks: [n_src_rows][K / elems] GGUF blocks of `type` (ggml type id). rows: optional int32 [R] source rows.
 OWL_API int owl_gguf_dequant(const void* blocks, int type, int K, const void* rows, int R, void* out, cudaStream_t st) {
   int elems, bytes;

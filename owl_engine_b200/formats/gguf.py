@@ -1,8 +1,8 @@
 """GGUF container reader, block codecs (CPU oracles), writer for tests, meta -> ModelSpec.
 
-Supported tensor types: F32, F16, BF16, Q8_0, Q4_0, Q4_K, Q5_K, Q6_K, IQ4_NL, IQ4_XS. The IQ2 / IQ3
-families need large codebook grids that are not bundled here; such tensors raise
-``UnsupportedGgufType`` with the type name instead of decoding wrongly.
+Supported tensor types: F32, F16, BF16, Q8_0, Q4_0, Q4_1, Q5_0, Q5_1, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K, IQ4_NL, IQ4_XS,
+IQ3_XXS, IQ3_S (codebooks in ``gguf_grids.py``). The IQ2 / IQ1 families need further grids that are not bundled;
+such tensors raise ``UnsupportedGgufType`` with the type name instead of decoding wrongly.
 
 ``q4k_to_w4`` maps Q4_K super-blocks onto the engine's int4 form without dequantising: every
 32-value sub-block becomes a group with scale ``d * sc`` and (fractional) zero point
@@ -28,8 +28,9 @@ GGML_TYPES = {0: "F32", 1: "F16", 2: "Q4_0", 3: "Q4_1", 6: "Q5_0", 7: "Q5_1", 8:
               27: "I64", 28: "F64", 29: "IQ1_M", 30: "BF16"}
 TYPE_ID = {v: k for k, v in GGML_TYPES.items()}
 # name -> (elements per block, bytes per block)
-BLOCK = {"F32": (1, 4), "F16": (1, 2), "BF16": (1, 2), "Q8_0": (32, 34), "Q4_0": (32, 18), "Q4_K": (256, 144),
-         "Q5_K": (256, 176), "Q6_K": (256, 210), "IQ4_NL": (32, 18), "IQ4_XS": (256, 136), "I8": (1, 1), "I32": (1, 4)}
+BLOCK = {"F32": (1, 4), "F16": (1, 2), "BF16": (1, 2), "Q8_0": (32, 34), "Q4_0": (32, 18), "Q4_1": (32, 20), "Q5_0": (32, 22),
+         "Q5_1": (32, 24), "Q2_K": (256, 84), "Q3_K": (256, 110), "Q4_K": (256, 144), "Q5_K": (256, 176), "Q6_K": (256, 210),
+         "IQ4_NL": (32, 18), "IQ4_XS": (256, 136), "IQ3_XXS": (256, 98), "IQ3_S": (256, 110), "I8": (1, 1), "I32": (1, 4)}
 KVALUES_IQ4NL = np.array([-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113], dtype=np.float32)
 
 
@@ -151,6 +152,102 @@ def dequantize(raw: np.ndarray, tname: str, n: int) -> np.ndarray:
         qs = b[:, 2:]
         x = np.concatenate([(qs & 0xF).astype(np.float32) - 8, (qs >> 4).astype(np.float32) - 8], axis=1)
         return (x * d).reshape(-1)
+    if tname == "Q4_1":
+        d, m = _f16(b[:, 0:2].copy()), _f16(b[:, 2:4].copy())
+        qs = b[:, 4:]
+        x = np.concatenate([(qs & 0xF).astype(np.float32), (qs >> 4).astype(np.float32)], axis=1)
+        return (x * d + m).reshape(-1)
+    if tname in ("Q5_0", "Q5_1"):
+        off = 2 if tname == "Q5_0" else 4
+        d = _f16(b[:, 0:2].copy())
+        qh = b[:, off:off + 4].copy().view(np.uint32)                       # [nb, 1]: bit j = fifth bit of element j
+        qs = b[:, off + 4:]
+        j = np.arange(16, dtype=np.uint32)
+        lo = (qs & 0xF).astype(np.int32) | ((((qh >> j) & 1) << 4).astype(np.int32))
+        hi = (qs >> 4).astype(np.int32) | ((((qh >> (j + 16)) & 1) << 4).astype(np.int32))
+        x = np.concatenate([lo, hi], axis=1).astype(np.float32)
+        if tname == "Q5_0":
+            return ((x - 16.0) * d).reshape(-1)
+        return (x * d + _f16(b[:, 2:4].copy())).reshape(-1)
+    if tname == "Q2_K":
+        # scales[16] (low nibble scale, high nibble min) | qs[64] (2 bits) | d | dmin; two halves of 128, each 4 shifts x 2 x 16
+        sc = b[:, 0:16]
+        qs = b[:, 16:80].reshape(nb, 2, 32)
+        d, dmin = _f16(b[:, 80:82].copy()), _f16(b[:, 82:84].copy())
+        out = np.zeros((nb, 2, 4, 32), dtype=np.float32)
+        for h in range(2):
+            for j in range(4):
+                q = ((qs[:, h] >> (2 * j)) & 3).astype(np.float32)             # [nb, 32]
+                for half in range(2):
+                    s8 = sc[:, h * 8 + j * 2 + half]
+                    dl = d[:, 0] * (s8 & 0xF)
+                    ml = dmin[:, 0] * (s8 >> 4)
+                    out[:, h, j, half * 16:(half + 1) * 16] = dl[:, None] * q[:, half * 16:(half + 1) * 16] - ml[:, None]
+        return out.reshape(-1)
+    if tname == "Q3_K":
+        # hmask[32] | qs[64] | scales[12] (sixteen 6-bit scales) | d
+        hm = b[:, 0:32]
+        qs = b[:, 32:96].reshape(nb, 2, 32)
+        sc12 = b[:, 96:108].astype(np.uint32)
+        d = _f16(b[:, 108:110].copy())[:, 0]
+        aux = sc12[:, 0:4] | (sc12[:, 4:8] << 8)
+        a0 = sc12[:, 0] | (sc12[:, 1] << 8) | (sc12[:, 2] << 16) | (sc12[:, 3] << 24)
+        a1 = sc12[:, 4] | (sc12[:, 5] << 8) | (sc12[:, 6] << 16) | (sc12[:, 7] << 24)
+        tmp = sc12[:, 8] | (sc12[:, 9] << 8) | (sc12[:, 10] << 16) | (sc12[:, 11] << 24)
+        k1, k2 = np.uint32(0x03030303), np.uint32(0x0f0f0f0f)
+        w = [(a0 & k2) | (((tmp >> 0) & k1) << 4), (a1 & k2) | (((tmp >> 2) & k1) << 4),
+             ((a0 >> 4) & k2) | (((tmp >> 4) & k1) << 4), ((a1 >> 4) & k2) | (((tmp >> 6) & k1) << 4)]
+        scales = np.stack([((w[i] >> (8 * j)) & 0xFF) for i in range(4) for j in range(4)], axis=1).astype(np.int32) - 32   # [nb, 16]
+        del aux
+        out = np.zeros((nb, 2, 4, 32), dtype=np.float32)
+        is_ = 0
+        for h in range(2):
+            for j in range(4):
+                m = np.uint8(1 << (h * 4 + j))
+                q = ((qs[:, h] >> (2 * j)) & 3).astype(np.int32) - np.where(hm & m, 0, 4)
+                for half in range(2):
+                    dl = d * scales[:, is_]
+                    is_ += 1
+                    out[:, h, j, half * 16:(half + 1) * 16] = dl[:, None] * q[:, half * 16:(half + 1) * 16]
+        return out.reshape(-1)
+    if tname == "IQ3_XXS":
+        # d | qs[64] (grid indices, 8 per 32 values) | 8 x u32 (four 7-bit sign fields, top 4 bits = sub-block scale)
+        from .gguf_grids import IQ3XXS_GRID, KSIGNS
+
+        d = _f16(b[:, 0:2].copy())[:, 0]
+        q3 = b[:, 2:66].reshape(nb, 8, 8)
+        aux = b[:, 66:98].copy().view(np.uint32).reshape(nb, 8)
+        out = np.zeros((nb, 8, 4, 8), dtype=np.float32)
+        bit = (1 << np.arange(8)).astype(np.uint8)
+        for ib in range(8):
+            db = d * (0.5 + (aux[:, ib] >> 28).astype(np.float32)) * 0.5
+            for l in range(4):
+                signs = KSIGNS[(aux[:, ib] >> (7 * l)) & 127]                       # [nb]
+                g = np.concatenate([IQ3XXS_GRID[q3[:, ib, 2 * l]], IQ3XXS_GRID[q3[:, ib, 2 * l + 1]]], axis=1).astype(np.float32)
+                sg = np.where(signs[:, None] & bit[None, :], -1.0, 1.0)
+                out[:, ib, l] = db[:, None] * g * sg
+        return out.reshape(-1)
+    if tname == "IQ3_S":
+        # d | qs[64] | qh[8] | signs[32] | scales[4]
+        from .gguf_grids import IQ3S_GRID
+
+        d = _f16(b[:, 0:2].copy())[:, 0]
+        qs = b[:, 2:66].reshape(nb, 8, 8).astype(np.int32)
+        qh = b[:, 66:74].astype(np.int32)
+        signs = b[:, 74:106].reshape(nb, 8, 4)
+        scl = b[:, 106:110]
+        out = np.zeros((nb, 8, 4, 8), dtype=np.float32)
+        bit = (1 << np.arange(8)).astype(np.uint8)
+        for ib in range(8):
+            nib = (scl[:, ib // 2] >> (4 * (ib % 2))) & 0xF
+            db = d * (1 + 2 * nib.astype(np.float32))
+            for l in range(4):
+                i1 = qs[:, ib, 2 * l] | ((qh[:, ib] << (8 - 2 * l)) & 256)
+                i2 = qs[:, ib, 2 * l + 1] | ((qh[:, ib] << (7 - 2 * l)) & 256)
+                g = np.concatenate([IQ3S_GRID[i1], IQ3S_GRID[i2]], axis=1).astype(np.float32)
+                sg = np.where(signs[:, ib, l][:, None] & bit[None, :], -1.0, 1.0)
+                out[:, ib, l] = db[:, None] * g * sg
+        return out.reshape(-1)
     if tname == "IQ4_NL":
         d = _f16(b[:, :2].copy())
         qs = b[:, 2:]

@@ -379,6 +379,8 @@ def attn_reduce(part_o, part_ml, splits: int, qraw, ldq: int, rows: int, hq: int
          group, _is_f16(out), int(pdl), stream())
 
 
+register("owl_kv_pages_gather", [_P, _P, _P, _I, _I, _P, _I, _P, _P])
+register("owl_kv_pages_scatter", [_P, _P, _P, _I, _I, _P, _I, _P, _P])
 register("owl_kv_gather", [_P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P, _P, _P])
 register("owl_causal_softmax", [_P, _I, _I, _I, _I, _F, _I, _P, _P])
 register("owl_attn_gate", [_P, _P, _I, _I, _P, _I, _I, _I, _I, _P, _P])
@@ -537,8 +539,26 @@ def nvfp4_quant_act(x, global_scale: float):
     return codes, sf
 
 
+register("owl_gguf_set_grids", [_P, _P])
+_gguf_grids_on: set = set()
+
+
+def _gguf_grids(device) -> None:
+    """Upload the IQ3 codebooks to ``device`` once (the kernels index them by the blocks' grid numbers)."""
+    key = str(device)
+    if key in _gguf_grids_on:
+        return
+    from ..formats.gguf_grids import IQ3S_GRID, IQ3XXS_GRID
+
+    a, b = IQ3XXS_GRID.tobytes(), IQ3S_GRID.tobytes()
+    with torch.cuda.device(device):
+        call("owl_gguf_set_grids", ctypes.cast(ctypes.c_char_p(a), c_void_p), ctypes.cast(ctypes.c_char_p(b), c_void_p))
+    _gguf_grids_on.add(key)
+
+
 def gguf_dequant(blocks, type_id: int, k: int, n_rows: int, rows=None, out=None):
     """GGUF blocks (uint8, ``n_src_rows * K / elems`` blocks) -> bf16 [R, K]; ``rows`` int32 picks source rows (embedding lookup)."""
+    _gguf_grids(blocks.device)
     r = n_rows if rows is None else rows.numel()
     if out is None:
         out = torch.empty(r, k, dtype=torch.bfloat16, device=blocks.device)
@@ -547,6 +567,7 @@ def gguf_dequant(blocks, type_id: int, k: int, n_rows: int, rows=None, out=None)
 
 
 def gguf_gemv(blocks, type_id: int, n: int, k: int, x, out, m: int) -> None:
+    _gguf_grids(blocks.device)
     call("owl_gguf_gemv", ptr(blocks), type_id, ptr(x), x.stride(0), ptr(out), out.stride(0), m, n, k, stream())
 
 

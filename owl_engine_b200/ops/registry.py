@@ -75,6 +75,7 @@ _T = [
     KernelSpec("owl_nvfp4_dequant", "lowbit.cu", "load"),
     KernelSpec("owl_nvfp4_quant_act", "lowbit.cu", "quant"),
     KernelSpec("owl_gguf_dequant", "lowbit.cu", "load"),
+    KernelSpec("owl_gguf_set_grids", "lowbit.cu", "load", capture=False),
     KernelSpec("owl_gguf_gemv", "lowbit.cu", "gemv"),
     # elementwise / norms / sampling
     KernelSpec("owl_rmsnorm_pack", "elem.cu", "norm"),
@@ -139,7 +140,12 @@ def cross_check() -> list[str]:
     """Mismatches between the sources, this table and the ctypes signatures (empty = consistent)."""
     from . import kernels as K
     from . import gemm_tc  # noqa: F401  (registers its signatures)
+    from ..models import dflash2  # noqa: F401
     from ..parallel import symm  # noqa: F401
+    from ..store import select
+
+    select._K()
+    K.register("owl_argmax_noalloc", [K._P, K._I, K._I, K._I, K._P, K._I, K._P])     # bound by its own test through the C symbol
 
     problems = []
     decl = declared()
@@ -153,6 +159,9 @@ def cross_check() -> list[str]:
         sig = K._SIGS.get(name)
         if sig is not None and len(sig) != n:
             problems.append(f"{name}: ctypes signature has {len(sig)} parameters, the C declaration {n}")
+        if sig is None and n > 0:
+            # without argtypes ctypes passes Python ints as 32-bit C ints: a device pointer would be cut in half
+            problems.append(f"{name}: {n} parameters but no ctypes signature registered")
     for name in TABLE:
         if name not in decl:
             problems.append(f"{name}: registry row without an exported symbol")

@@ -174,7 +174,7 @@ class SymmetricWorkspace:
         self.off_big = (self.off_exch + MAX_ROWS * 8 * 8 + 255) // 256 * 256
         self.big_elems = big_elems
         self.off_push = (self.off_big + big_elems * 2 + 255) // 256 * 256
-        self.kparts = max(1, min(4, 8 // world))       # k parts of the one-token row-parallel projections (ranks x parts <= 8)
+        self.kparts = 1          # k parts of the one-token row-parallel projections (ranks x parts <= 8; one: whole tiles)
         push_bytes = 8 * MAX_ROWS * hidden * 2
         self.off_pflags = self.off_push + 2 * push_bytes
         pf_rows = big_elems // hidden

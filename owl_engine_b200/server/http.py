@@ -14,6 +14,7 @@ import asyncio
 import collections
 import json
 import queue as pyqueue
+import threading
 import time
 
 from ..engine.running import TurnOpts
@@ -45,6 +46,7 @@ class App:
         self.guard = RepeatGuard()
         self.vision = vision      # Vision (tower + image cache + pad token id) or None: image parts are then refused
         self.started = time.time()
+        self.stop = threading.Event()
         self.agent_trace: collections.deque = collections.deque(maxlen=64)   # per turn: the output splitter's structural trace
 
     # -- plumbing -------------------------------------------------------------------------------
@@ -167,6 +169,10 @@ class App:
 
             return await self._send(w, 200, q(lambda re: {"graphs": [list(k) for k in re.e.runner.graphs.keys()],
                                                            "launches": K.recent_launches(n), "status": K.all_status()}))
+        if parts[0] == "shutdown" and method == "POST":
+            # orderly stop (tests, supervisors): the listener loop sees the flag, the engine thread checkpoints and exits
+            self.stop.set()
+            return await self._send(w, 200, {"stopping": True})
         if parts[0] == "load" and method == "POST":
             return await self._send(w, 200, {"loaded": self.model})
         await self._send(w, 404, {"error": "unknown debug endpoint"})

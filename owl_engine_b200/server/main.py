@@ -269,8 +269,8 @@ def main(argv=None) -> int:
     async def run():
         server = await serve(app, host or "0.0.0.0", int(port))
         async with server:
-            while svc.exit is None:
-                await asyncio.sleep(0.5)
+            while svc.exit is None and not app.stop.is_set():
+                await asyncio.sleep(0.2)
 
     try:
         asyncio.run(run())

@@ -85,7 +85,112 @@ def test_gguf_other_codecs_shapes():
         out = gguf.dequantize(raw, t, be * 4)
         assert out.shape == (be * 4,) and np.isfinite(out).all()
     with pytest.raises(gguf.UnsupportedGgufType):
-        gguf.dequantize(np.zeros(10, dtype=np.uint8), "IQ3_S", 256)
+        gguf.dequantize(np.zeros(10, dtype=np.uint8), "IQ2_XS", 256)
+
+
+def _scalar_decode(raw, t):
+    """Element-by-element decoders written straight from the block layouts (independent of the vectorised codecs)."""
+    from owl_engine_b200.formats.gguf_grids import IQ3S_GRID, IQ3XXS_GRID, KSIGNS
+
+    f16 = lambda b: float(np.frombuffer(bytes(b), dtype=np.float16)[0])
+    be, bb = gguf.BLOCK[t]
+    out = []
+    for blk in raw.reshape(-1, bb):
+        b = [int(x) for x in blk]
+        y = [0.0] * be
+        if t == "Q4_1":
+            d, m = f16(blk[0:2]), f16(blk[2:4])
+            for j in range(16):
+                y[j], y[j + 16] = d * (b[4 + j] & 15) + m, d * (b[4 + j] >> 4) + m
+        elif t in ("Q5_0", "Q5_1"):
+            o = 2 if t == "Q5_0" else 4
+            d = f16(blk[0:2])
+            qh = b[o] | (b[o + 1] << 8) | (b[o + 2] << 16) | (b[o + 3] << 24)
+            for j in range(16):
+                lo = (b[o + 4 + j] & 15) | (((qh >> j) & 1) << 4)
+                hi = (b[o + 4 + j] >> 4) | (((qh >> (j + 16)) & 1) << 4)
+                if t == "Q5_0":
+                    y[j], y[j + 16] = d * (lo - 16), d * (hi - 16)
+                else:
+                    m = f16(blk[2:4])
+                    y[j], y[j + 16] = d * lo + m, d * hi + m
+        elif t == "Q2_K":
+            d, dmin = f16(blk[80:82]), f16(blk[82:84])
+            i, is_ = 0, 0
+            for h in range(2):
+                q = b[16 + 32 * h:16 + 32 * h + 32]
+                for j in range(4):
+                    for half in range(2):
+                        sc = b[is_]
+                        is_ += 1
+                        for l in range(16):
+                            y[i] = d * (sc & 15) * ((q[half * 16 + l] >> (2 * j)) & 3) - dmin * (sc >> 4)
+                            i += 1
+        elif t == "Q3_K":
+            d = f16(blk[108:110])
+            sc = b[96:108]
+            scales = []
+            for k in range(16):
+                low = (sc[k] & 15) if k < 8 else (sc[k - 8] >> 4)
+                hi = (sc[8 + k % 4] >> (2 * (k // 4))) & 3
+                scales.append((low | (hi << 4)) - 32)
+            i, is_, m = 0, 0, 1
+            for h in range(2):
+                q = b[32 + 32 * h:32 + 32 * h + 32]
+                for j in range(4):
+                    for half in range(2):
+                        dl = d * scales[is_]
+                        is_ += 1
+                        for l in range(16):
+                            ll = half * 16 + l
+                            y[i] = dl * (((q[ll] >> (2 * j)) & 3) - (0 if b[ll] & m else 4))
+                            i += 1
+                    m <<= 1
+        elif t == "IQ3_XXS":
+            d = f16(blk[0:2])
+            for ib in range(8):
+                aux = b[66 + 4 * ib] | (b[67 + 4 * ib] << 8) | (b[68 + 4 * ib] << 16) | (b[69 + 4 * ib] << 24)
+                db = d * (0.5 + (aux >> 28)) * 0.5
+                for l in range(4):
+                    signs = int(KSIGNS[(aux >> (7 * l)) & 127])
+                    g = list(IQ3XXS_GRID[b[2 + 8 * ib + 2 * l]]) + list(IQ3XXS_GRID[b[2 + 8 * ib + 2 * l + 1]])
+                    for j in range(8):
+                        y[32 * ib + 8 * l + j] = db * int(g[j]) * (-1 if signs & (1 << j) else 1)
+        elif t == "IQ3_S":
+            d = f16(blk[0:2])
+            for ib in range(8):
+                db = d * (1 + 2 * ((b[106 + ib // 2] >> (4 * (ib % 2))) & 15))
+                qh = b[66 + ib]
+                for l in range(4):
+                    i1 = b[2 + 8 * ib + 2 * l] | ((qh << (8 - 2 * l)) & 256)
+                    i2 = b[2 + 8 * ib + 2 * l + 1] | ((qh << (7 - 2 * l)) & 256)
+                    g = list(IQ3S_GRID[i1]) + list(IQ3S_GRID[i2])
+                    signs = b[74 + 4 * ib + l]
+                    for j in range(8):
+                        y[32 * ib + 8 * l + j] = db * int(g[j]) * (-1 if signs & (1 << j) else 1)
+        out += y
+    return np.asarray(out, dtype=np.float32)
+
+
+@pytest.mark.parametrize("t", ["Q4_1", "Q5_0", "Q5_1", "Q2_K", "Q3_K", "IQ3_XXS", "IQ3_S"])
+def test_gguf_new_codecs_against_scalar_decoders(t):
+    be, bb = gguf.BLOCK[t]
+    rng = np.random.default_rng(11)
+    raw = rng.integers(0, 256, size=(6, bb), dtype=np.uint8)
+    for col in {"Q4_1": (0, 2), "Q5_0": (0,), "Q5_1": (0, 2), "Q2_K": (80, 82), "Q3_K": (108,), "IQ3_XXS": (0,), "IQ3_S": (0,)}[t]:
+        raw[:, col:col + 2] = rng.uniform(0.01, 0.1, size=(6,)).astype(np.float16).view(np.uint8).reshape(-1, 2)
+    got = gguf.dequantize(raw.reshape(-1), t, 6 * be)
+    want = _scalar_decode(raw, t)
+    np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-6)
+
+
+def test_iq3_grids_are_well_formed():
+    from owl_engine_b200.formats import gguf_grids as GR
+
+    assert GR.IQ3XXS_GRID.shape == (256, 4) and set(np.unique(GR.IQ3XXS_GRID)) == {4, 12, 20, 28, 36, 44, 52, 62}
+    assert GR.IQ3S_GRID.shape == (512, 4) and set(np.unique(GR.IQ3S_GRID)) == {1, 3, 5, 7, 9, 11, 13, 15}
+    assert len({bytes(r) for r in GR.IQ3XXS_GRID}) == 256 and len({bytes(r) for r in GR.IQ3S_GRID}) == 512     # no duplicate entry
+    assert all(bin(int(v)).count("1") % 2 == 0 for v in GR.KSIGNS)
 
 
 def test_awq_forge_converts_a_dense_checkpoint(tmp_path):

@@ -60,7 +60,8 @@ def test_nvfp4_per_row_scales_residual_form_and_act_unpack():
     torch.testing.assert_close(out.float().cpu(), want + res.float(), rtol=2e-2, atol=2e-2 * (want + res.float()).abs().max().item())
 
 
-@pytest.mark.parametrize("tname", ["Q8_0", "Q4_0", "IQ4_NL", "Q4_K", "Q5_K", "Q6_K", "IQ4_XS"])
+@pytest.mark.parametrize("tname", ["Q8_0", "Q4_0", "Q4_1", "Q5_0", "Q5_1", "IQ4_NL", "Q2_K", "Q3_K", "Q4_K", "Q5_K", "Q6_K", "IQ4_XS",
+                                   "IQ3_XXS", "IQ3_S"])
 def test_gguf_dequant_and_gemv(tname):
     n, k = 24, 512
     be, bb = G.BLOCK[tname]
@@ -69,10 +70,14 @@ def test_gguf_dequant_and_gemv(tname):
     # keep the fp16 scale fields finite and moderate
     def set_f16(col, lo=0.001, hi=0.02):
         raw[:, col:col + 2] = rng.uniform(lo, hi, size=(raw.shape[0],)).astype(np.float16).view(np.uint8).reshape(-1, 2)
-    if tname in ("Q8_0", "Q4_0", "IQ4_NL", "IQ4_XS"):
+    if tname in ("Q8_0", "Q4_0", "Q5_0", "IQ4_NL", "IQ4_XS", "IQ3_XXS", "IQ3_S"):
         set_f16(0)
-    elif tname in ("Q4_K", "Q5_K"):
+    elif tname in ("Q4_K", "Q5_K", "Q4_1", "Q5_1"):
         set_f16(0); set_f16(2)
+    elif tname == "Q2_K":
+        set_f16(80); set_f16(82)
+    elif tname == "Q3_K":
+        set_f16(108)
     else:
         set_f16(208)
     want = torch.from_numpy(G.dequantize(raw.reshape(-1), tname, n * k)).view(n, k)
