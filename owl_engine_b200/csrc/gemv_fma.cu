@@ -43,6 +43,7 @@ constexpr int FM_MAX_RANKS = 8;
 constexpr int FM_REC = 1088;          // bytes per record (g128)
 constexpr int FM_STAGES = 4;          // records per warp ring: three in flight while one is consumed
 constexpr int FM_WARPS = 8;           // warps per group = k slices of the record order
+constexpr int FM_RED = 8;             // units of work whose partial sums wait in shared memory for one common barrier
 
 struct FmaParams {
   const uint8_t* w;                 // slice-major record stream
@@ -121,7 +122,7 @@ __device__ __forceinline__ void bf16x8_to_f(const uint4& a, float* v) {
 }
 
 __host__ __device__ constexpr int fma_smem_bytes(int vc, int k) {
-  return vc * FM_WARPS * FM_STAGES * FM_REC + k * 2 + (k / 128) * 4 + vc * 2 * FM_WARPS * 16 * 4 + 2 * 32 * 4 + 64;
+  return vc * FM_WARPS * FM_STAGES * FM_REC + k * 2 + (k / 128) * 4 + vc * FM_RED * FM_WARPS * 16 * 4 + 2 * 32 * 4 + 64;
 }
 
 // VC groups of eight warps per CTA; the groups share the activation vector and nothing else.
@@ -134,8 +135,8 @@ __global__ void __launch_bounds__(VC * FM_WARPS * 32, 4 / VC) w4_fma_kernel(FmaP
   uint8_t* ring_all = smem;
   uint4* xh4 = reinterpret_cast<uint4*>(smem + VC * FM_WARPS * FM_STAGES * FM_REC);   // fp16 x' [K]
   float* xg = reinterpret_cast<float*>(xh4 + p.K / 8);                             // per 128-k group: sum(x') * 2^-24
-  float* red = xg + p.K / 128;                                                     // [VC][2][8 warps][16 rows]
-  float* pro = red + VC * 2 * FM_WARPS * 16;                                       // prologue reductions [2][32]
+  float* red = xg + p.K / 128;                                                     // [VC][FM_RED units][8 warps][16 rows]
+  float* pro = red + VC * FM_RED * FM_WARPS * 16;                                  // prologue reductions [2][32]
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int vc = warp / FM_WARPS, wi = warp % FM_WARPS, g = lane >> 2, t = lane & 3;
@@ -364,21 +365,28 @@ __global__ void __launch_bounds__(VC * FM_WARPS * 32, 4 / VC) w4_fma_kernel(FmaP
       acc0 = fmaf(s0.x, fmaf(-s0.y, xq, f0), acc0);
       acc1 = fmaf(s1.x, fmaf(-s1.y, xq, f1), acc1);
     }
-    // ---- end of the unit: 4 t lanes, then the 8 k slices through shared memory -------------------------------------
+    // ---- end of the unit: the 4 t lanes, then this warp's 16 sums wait in shared memory for the other k slices ---------
     acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
     acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
     acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
     acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
-    float* rbuf = red + (size_t)((vc * 2 + (item & 1)) * FM_WARPS) * 16;
-    if (t == 0) { rbuf[wi * 16 + g] = acc0; rbuf[wi * 16 + 8 + g] = acc1; }
+    const int bi = item % FM_RED;                 // slot of this unit in the current batch
+    float* rmine = red + (size_t)((vc * FM_RED + bi) * FM_WARPS + wi) * 16;
+    if (t == 0) { rmine[g] = acc0; rmine[8 + g] = acc1; }
     acc0 = acc1 = 0.f;
+    if (bi + 1 < FM_RED && u + 1 < u1) continue;
+    // ---- a batch of units is complete (or the group is done): ONE barrier for the whole batch, then the 8 warps share
+    // the finishing work. The k slices of a group run unsynchronised in between (a barrier per 5-record tile would keep
+    // every warp waiting for the slowest one all the time).
     group_barrier<VC>(vc);
-    if (wi == (item & (FM_WARPS - 1))) {
-      const int nt = u / P;
+    const int n_batch = bi + 1, ub = u - bi;
+    for (int i = wi; i < n_batch; i += FM_WARPS) {
+      const float* rb = red + (size_t)((vc * FM_RED + i) * FM_WARPS) * 16;
+      const int uu = ub + i, nt = uu / P, qq = uu % P;
       float v = 0.f;
       if (lane < 16) {
 #pragma unroll
-        for (int s = 0; s < FM_WARPS; ++s) v += rbuf[s * 16 + lane];
+        for (int sl = 0; sl < FM_WARPS; ++sl) v += rb[sl * 16 + lane];
         v *= unscale;
       }
       if (EPI == FEPI_SILU_MUL) {
@@ -387,7 +395,7 @@ __global__ void __launch_bounds__(VC * FM_WARPS * 32, 4 / VC) w4_fma_kernel(FmaP
       } else if (EPI == FEPI_PUSH) {
         if (lane < 16) {
           const __nv_bfloat16 bv = __float2bfloat16(v);
-          const size_t off = (size_t)(p.push_rank * P + q) * p.push_rows * p.N + nt * 16 + lane;
+          const size_t off = (size_t)(p.push_rank * P + qq) * p.push_rows * p.N + nt * 16 + lane;
           for (int r = 0; r < p.push_world; ++r) p.push_dst[r][off] = bv;
         }
       } else if (lane < 16) {
@@ -395,6 +403,7 @@ __global__ void __launch_bounds__(VC * FM_WARPS * 32, 4 / VC) w4_fma_kernel(FmaP
         p.out[nt * 16 + lane] = __float2bfloat16(v);
       }
     }
+    if (u + 1 < u1) group_barrier<VC>(vc);        // the next batch reuses the slots
   }
   cp_async_wait<0>();
   if (EPI == FEPI_PUSH) {
