@@ -182,7 +182,10 @@ struct PushNormParams {
   const __nv_bfloat16* slots;  // local [world][push_rows][H]
   const uint32_t* flags;       // local [world]: sequence numbers published by the peers' GEMVs
   uint32_t* counters;          // private per-row sequence counters [rows]
-  const uint32_t* seq_src;     // when set: the expected sequence number is read here (the local producer's word) instead
+  uint32_t* seq_src;           // when set: the expected sequence number is read here (the local producer's word) instead
+  const uint2* ll;             // when set (one row only): the producer was the FMA projection, whose slots are 8-byte words
+                               // (two sums + the exchange's number = *seq_src + 1) [world][H / 2]; no flags are used, every
+                               // thread polls the words it adds (bounded), and the CTA writes the number back to *seq_src
   __nv_bfloat16* h; const __nv_bfloat16* w; __nv_bfloat16* normed; uint4* xpack; float2* xs;
   int H, G, world, ranks, push_rows, one_plus_w;    // world: slots to add (ranks x k parts); ranks: flags to wait for
   float eps;
@@ -195,11 +198,12 @@ __global__ void __launch_bounds__(1024) push_residual_norm_kernel(PushNormParams
   pdl_wait();
   const int row = blockIdx.x;
   if (threadIdx.x == 0) {
-    if (p.seq_src) { s_seq = *p.seq_src; }
+    if (p.ll) { s_seq = *p.seq_src + 1u; }
+    else if (p.seq_src) { s_seq = *p.seq_src; }
     else { s_seq = p.counters[row] + 1; p.counters[row] = s_seq; }
   }
   __syncthreads();
-  if (threadIdx.x < p.ranks) {
+  if (!p.ll && threadIdx.x < p.ranks) {
     bool got = false;
     for (uint32_t i = 0; i < p.spin_limit; ++i) {
       if ((int)(ld_acquire_sys(p.flags + threadIdx.x) - s_seq) >= 0) { got = true; break; }
@@ -213,7 +217,19 @@ __global__ void __launch_bounds__(1024) push_residual_norm_kernel(PushNormParams
   float ss = 0.f;
   for (int c = threadIdx.x; c < nchunks; c += blockDim.x) {
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int r = 0; r < p.world; ++r) {
+    for (int r = 0; p.ll && r < p.world; ++r) {
+      const uint4* src = reinterpret_cast<const uint4*>(p.ll + (size_t)r * (p.H >> 1)) + 2 * c;
+      const uint32_t want = s_seq;
+      uint4 u = ld_relaxed_sys_v4(src), v = ld_relaxed_sys_v4(src + 1);
+      for (uint32_t i = 0; u.y != want || u.w != want || v.y != want || v.w != want;) {
+        if (++i >= p.spin_limit) { atomicCAS(&g_comm_status, 0, OWL_ERR_WAIT_PEER); break; }
+        if (i > 64) __nanosleep(32);
+        u = ld_relaxed_sys_v4(src); v = ld_relaxed_sys_v4(src + 1);
+      }
+      acc[0] += bf16_lo(u.x); acc[1] += bf16_hi(u.x); acc[2] += bf16_lo(u.z); acc[3] += bf16_hi(u.z);
+      acc[4] += bf16_lo(v.x); acc[5] += bf16_hi(v.x); acc[6] += bf16_lo(v.z); acc[7] += bf16_hi(v.z);
+    }
+    for (int r = 0; !p.ll && r < p.world; ++r) {
       // written by peers over NVLink: read past L1 (the acquire above orders the loads after the flag)
       const uint4 u = ld_relaxed_sys_v4(reinterpret_cast<const uint4*>(p.slots + ((size_t)r * p.push_rows + row) * p.H) + c);
       float v[8];
@@ -231,6 +247,7 @@ __global__ void __launch_bounds__(1024) push_residual_norm_kernel(PushNormParams
     }
     reinterpret_cast<uint4*>(hrow)[c] = pack_bf16x8(hv);
   }
+  if (p.ll && threadIdx.x == 0) *p.seq_src = s_seq;      // one CTA in this form: every thread took the number from shared memory
   if (!p.w) return;
   ss = block_sum(ss, red);
   const float rinv = rsqrtf(ss / (float)p.H + p.eps);
@@ -463,15 +480,18 @@ OWL_API int owl_ar_residual_norm(const void* const* part_ptrs, const void* mc_pa
 }
 
 // slots: this rank's [world][push_rows][H] bf16 buffer; flags: this rank's [world] sequence words of the call site;
-// counters: private uint32 [M] (zero before the first call).
+// counters: private uint32 [M] (zero before the first call). ll (optional, M = 1, seq_src required): the word buffer of the
+// FMA projection's exchange [world * kparts][H / 2] instead of slots and flags.
 OWL_API int owl_push_residual_norm(const void* slots, const void* flags, void* counters, void* h, const void* w,
                                    void* normed, void* xpack, void* xs, int M, int H, int G, int world, int push_rows,
-                                   float eps, int one_plus_w, unsigned spin_limit, const void* seq_src, int kparts, int pdl,
-                                   cudaStream_t st) {
+                                   float eps, int one_plus_w, unsigned spin_limit, void* seq_src, int kparts, const void* ll,
+                                   int pdl, cudaStream_t st) {
   if (M < 1 || M > push_rows || (H & 127) || world < 1 || kparts < 1 || world * kparts > MAX_RANKS || !actpack_group_ok(G, M))
     return OWL_ERR_BAD_ARG;
+  if (ll && (M != 1 || !seq_src || (reinterpret_cast<uintptr_t>(ll) & 15))) return OWL_ERR_BAD_ARG;
   PushNormParams p = {};
-  p.seq_src = (const uint32_t*)seq_src;
+  p.seq_src = (uint32_t*)seq_src;
+  p.ll = (const uint2*)ll;
   p.ranks = world;
   world *= kparts;          // slots [rank * kparts + part]
   p.slots = (const __nv_bfloat16*)slots; p.flags = (const uint32_t*)flags; p.counters = (uint32_t*)counters;

@@ -60,23 +60,24 @@ struct FmaParams {
   int one_plus;
   int kparts;                       // FEPI_PUSH: every row tile is cut into this many k parts, each a unit of work of its own
   // FEPI_PUSH (row-parallel projection): the partial sums of k part q go into slot [push_rank * kparts + q] of every
-  // rank's reduction buffer [world * kparts][push_rows][N] bf16 with plain (peer) stores while the matrix streams; the CTA
-  // that finishes last bumps the call site's sequence number and publishes it in every rank's flag word [push_rank]. With
-  // one rank this is a local split of the k range: a projection with few row tiles (N = hidden) gets kparts times as many
-  // units of work, and the consumer's prologue adds the parts.
-  __nv_bfloat16* push_dst[FM_MAX_RANKS];
-  uint32_t* push_flag[FM_MAX_RANKS];
-  int* push_count;                  // local: finished CTAs of this launch (returns to zero)
-  uint32_t* push_seq;               // local: sequence number of this call site
-  int push_rank, push_world, push_rows;
-  // FMA_PULL (the column-parallel projection that follows): wait until every rank's flag reached the local sequence
-  // number, x = residual stream + the slots in rank order (the same sum, bit for bit, on every rank), then the norm as in
-  // FMA_NORM. CTA 0 stores the new residual stream into h_out, a buffer other than x (the other CTAs still read x).
-  const __nv_bfloat16* pull_slots;  // local [world][pull_rows][K]
-  const uint32_t* pull_flags;       // local [world]
-  const uint32_t* pull_seq;         // local: the sequence number the local producer published last
+  // rank's word buffer [world * kparts][N / 2] with plain (peer) stores while the matrix streams. A word is 8 bytes: two
+  // bf16 sums and the sequence number of this exchange (the call site's word + 1). An aligned 8-byte store arrives whole,
+  // so the consumer needs no flag, the producer no fence and no count of finished CTAs: a word whose number matches is
+  // valid. With one rank this is a local split of the k range: a projection with few row tiles (N = hidden) gets kparts
+  // times as many units of work, and the consumer's prologue adds the parts.
+  uint2* push_ll[FM_MAX_RANKS];
+  const uint32_t* push_seq;         // local: number of the call site's last completed exchange
+  int push_rank, push_world;
+  // FMA_PULL (the column-parallel projection that follows): every thread polls the words of the chunks it loads until they
+  // carry the awaited number (bounded), x = residual stream + the slots in rank order (the same sum, bit for bit, on every
+  // rank), then the norm as in FMA_NORM. CTA 0 stores the new residual stream into h_out, a buffer other than x (the
+  // other CTAs still read x). The CTA that leaves last writes the awaited number into the call site's word: every CTA of
+  // this grid read the word before that, and the next producer of the call site starts after this grid.
+  const uint2* pull_ll;             // local [world * kparts][K / 2]
+  uint32_t* pull_seq;               // local: the call site's word (the same the producer read)
+  int* pull_count;                  // local: CTAs of this launch that left (returns to zero)
   __nv_bfloat16* h_out;
-  int pull_world, pull_ranks, pull_rows;      // slots to add (ranks x k parts), ranks whose flags to wait for
+  int pull_world;                   // slots to add (ranks x k parts)
   uint32_t spin_limit;
 };
 
@@ -190,30 +191,31 @@ __global__ void __launch_bounds__(VC * FM_WARPS * 32, 4 / VC) w4_fma_kernel(FmaP
     }
   }
   pdl_wait();
-  if (MODE == FMA_PULL) {
-    // every rank's partial sums of the preceding row-parallel projection must have landed in the local slots
-    if (tid < p.pull_ranks) {
-      const uint32_t want = *p.pull_seq;
-      bool got = false;
-      for (uint32_t i = 0; i < p.spin_limit; ++i) {
-        if ((int)(ld_acquire_sys_u32(p.pull_flags + tid) - want) >= 0) { got = true; break; }
-        if (i > 64) __nanosleep(32);
-      }
-      if (!got) atomicCAS(&g_fma_status, 0, OWL_ERR_WAIT_PEER);
-    }
-    __syncthreads();
-  }
+  uint32_t want = 0, seq = 0;
+  bool dead = false;                      // a wait of this thread ran out: do not wait again
+  if (MODE == FMA_PULL) want = __ldcg(p.pull_seq) + 1u;
+  if (EPI == FEPI_PUSH) seq = __ldcg(p.push_seq) + 1u;
   // one chunk (8 values) of the input row; FMA_PULL adds the ranks' slots in rank order and rounds to bf16 once
   auto load_x = [&](int c) -> uint4 {
     const uint4 hv = __ldcg(x4 + c);
     if (MODE != FMA_PULL) return hv;
-    float a[8], v[8];
+    float a[8];
     bf16x8_to_f(hv, a);
     float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int r = 0; r < p.pull_world; ++r) {
-      bf16x8_to_f(ld_relaxed_sys_u4(reinterpret_cast<const uint4*>(p.pull_slots + (size_t)r * p.pull_rows * p.K) + c), v);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) sum[i] += v[i];
+      // four words of this chunk: (2 sums, number) x 4, valid once all four numbers match
+      const uint4* src = reinterpret_cast<const uint4*>(p.pull_ll + (size_t)r * (p.K >> 1)) + 2 * c;
+      uint4 u = ld_relaxed_sys_u4(src), v = ld_relaxed_sys_u4(src + 1);
+      if (!dead) {
+        uint32_t i = 0;
+        while (u.y != want || u.w != want || v.y != want || v.w != want) {
+          if (++i >= p.spin_limit) { dead = true; atomicCAS(&g_fma_status, 0, OWL_ERR_WAIT_PEER); break; }
+          if (i > 64) __nanosleep(32);
+          u = ld_relaxed_sys_u4(src); v = ld_relaxed_sys_u4(src + 1);
+        }
+      }
+      sum[0] += bf16_lo(u.x); sum[1] += bf16_hi(u.x); sum[2] += bf16_lo(u.z); sum[3] += bf16_hi(u.z);
+      sum[4] += bf16_lo(v.x); sum[5] += bf16_hi(v.x); sum[6] += bf16_lo(v.z); sum[7] += bf16_hi(v.z);
     }
     const uint4 o = make_uint4(pack_bf16(a[0] + sum[0], a[1] + sum[1]), pack_bf16(a[2] + sum[2], a[3] + sum[3]),
                                pack_bf16(a[4] + sum[4], a[5] + sum[5]), pack_bf16(a[6] + sum[6], a[7] + sum[7]));
@@ -393,10 +395,12 @@ __global__ void __launch_bounds__(VC * FM_WARPS * 32, 4 / VC) w4_fma_kernel(FmaP
         const float up = __shfl_down_sync(0xffffffffu, v, 8);
         if (lane < 8) p.out[nt * 8 + lane] = __float2bfloat16(silu_f(v) * up);
       } else if (EPI == FEPI_PUSH) {
-        if (lane < 16) {
-          const __nv_bfloat16 bv = __float2bfloat16(v);
-          const size_t off = (size_t)(p.push_rank * P + qq) * p.push_rows * p.N + nt * 16 + lane;
-          for (int r = 0; r < p.push_world; ++r) p.push_dst[r][off] = bv;
+        const float hi = __shfl_down_sync(0xffffffffu, v, 1);
+        if (lane < 16 && !(lane & 1)) {
+          const uint32_t pk = pack_bf16(v, hi);
+          const size_t off = (size_t)(p.push_rank * P + qq) * (p.N >> 1) + nt * 8 + (lane >> 1);
+          for (int r = 0; r < p.push_world; ++r)
+            asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p.push_ll[r] + off), "r"(pk), "r"(seq) : "memory");
         }
       } else if (lane < 16) {
         if (EPI == FEPI_RESIDUAL) v += __bfloat162float(p.residual[nt * 16 + lane]);
@@ -406,20 +410,10 @@ __global__ void __launch_bounds__(VC * FM_WARPS * 32, 4 / VC) w4_fma_kernel(FmaP
     if (u + 1 < u1) group_barrier<VC>(vc);        // the next batch reuses the slots
   }
   cp_async_wait<0>();
-  if (EPI == FEPI_PUSH) {
-    // every thread's peer stores are ordered before the count; the last CTA of the grid tells the ranks
-    __threadfence_system();
-    __syncthreads();
-    if (tid == 0) {
-      __threadfence_system();
-      if (atomicAdd(p.push_count, 1) == (int)gridDim.x - 1) {
-        *p.push_count = 0;
-        const uint32_t seq = *p.push_seq + 1;
-        *p.push_seq = seq;
-        __threadfence_system();
-        for (int r = 0; r < p.push_world; ++r)
-          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.push_flag[r] + p.push_rank), "r"(seq) : "memory");
-      }
+  if (MODE == FMA_PULL && tid == 0) {
+    if (atomicAdd(p.pull_count, 1) == (int)gridDim.x - 1) {
+      *p.pull_count = 0;
+      *p.pull_seq = want;
     }
   }
   pdl_launch_dependents();
@@ -504,19 +498,19 @@ OWL_API int owl_w4_fma(const void* records, const void* x, const void* norm_w, v
 }
 
 // Split forms of the same launch (one token), across ranks and / or across k parts. push != 0: a row-parallel projection
-// whose partial sums are stored into slot [rank * kparts + part] of every rank's buffer (dst_ptrs: `world` peer-mapped bases
-// of [world * kparts][rows][N] bf16; flag_ptrs: `world` peer-mapped flag arrays [world] uint32; count / seq: local words,
-// zero before the first call); x is the plain activation vector. world * kparts <= 8; world = 1 is a local k split. push == 0: the column-parallel projection that consumes such a buffer: x is the residual stream,
-// pull_slots / pull_flags / pull_seq are the LOCAL slot buffer, flag array and producer sequence word, h_out (a buffer
-// other than x) receives x + sum of the slots, and the kernel multiplies by rmsnorm(h_out) * (norm_w or 1 + norm_w);
-// epi 0 or 2 as in owl_w4_fma.
+// whose partial sums are stored into slot [rank * kparts + part] of every rank's word buffer (ll_ptrs: `world` peer-mapped
+// bases of [world * kparts][N / 2] 8-byte words, zero before the first call; seq: the call site's local sequence word, zero
+// before the first call); x is the plain activation vector. world * kparts <= 8; world = 1 is a local k split.
+// push == 0: the column-parallel projection that consumes such a buffer: x is the residual stream, pull_ll the LOCAL word
+// buffer, seq the same local word, pull_count a local int (zero before the first call), h_out (a buffer other than x)
+// receives x + sum of the slots, and the kernel multiplies by rmsnorm(h_out) * (norm_w or 1 + norm_w); epi 0 or 2 as in
+// owl_w4_fma.
 OWL_API int owl_w4_fma_tp(const void* records, const void* x, const void* norm_w, void* out, int N, int K, int epi, float eps,
-                          int one_plus_w, int push, void* const* dst_ptrs, void* const* flag_ptrs, void* count, void* seq,
-                          const void* pull_slots, const void* pull_flags, const void* pull_seq, void* h_out, const void* ab_w,
-                          void* ab_out, int ab_rows, int rank, int world, int rows, int kparts, unsigned spin_limit,
-                          int groups_per_cta, int pdl, cudaStream_t st) {
+                          int one_plus_w, int push, void* const* ll_ptrs, void* seq, const void* pull_ll, void* pull_count,
+                          void* h_out, const void* ab_w, void* ab_out, int ab_rows, int rank, int world, int kparts,
+                          unsigned spin_limit, int groups_per_cta, int pdl, cudaStream_t st) {
   if (!records || !x || (N & 15) || (K & 127) || K < 128 || K > 32768 || world < 1 || world > FM_MAX_RANKS || rank < 0 ||
-      rank >= world || rows < 1)
+      rank >= world || !seq)
     return OWL_ERR_BAD_ARG;
   FmaParams p = {};
   p.w = (const uint8_t*)records; p.x = (const __nv_bfloat16*)x; p.norm_w = (const __nv_bfloat16*)norm_w;
@@ -529,20 +523,20 @@ OWL_API int owl_w4_fma_tp(const void* records, const void* x, const void* norm_w
   if (kparts < 1 || world * kparts > FM_MAX_RANKS) return OWL_ERR_BAD_ARG;
   p.kparts = kparts;
   if (push) {
-    if (!dst_ptrs || !flag_ptrs || !count || !seq) return OWL_ERR_BAD_ARG;
+    if (!ll_ptrs) return OWL_ERR_BAD_ARG;
     for (int r = 0; r < world; ++r) {
-      p.push_dst[r] = (__nv_bfloat16*)dst_ptrs[r];
-      p.push_flag[r] = (uint32_t*)flag_ptrs[r];
-      if (!p.push_dst[r] || !p.push_flag[r]) return OWL_ERR_BAD_ARG;
+      p.push_ll[r] = (uint2*)ll_ptrs[r];
+      if (!p.push_ll[r] || (reinterpret_cast<uintptr_t>(p.push_ll[r]) & 15)) return OWL_ERR_BAD_ARG;
     }
-    p.push_count = (int*)count; p.push_seq = (uint32_t*)seq; p.push_rank = rank; p.push_world = world; p.push_rows = rows;
+    p.push_seq = (const uint32_t*)seq; p.push_rank = rank; p.push_world = world;
     return vc == 4 ? launch_fma<4, FMA_PLAIN, FEPI_PUSH>(p, grid, pdl, st) : launch_fma<2, FMA_PLAIN, FEPI_PUSH>(p, grid, pdl, st);
   }
-  if (!out || !norm_w || !pull_slots || !pull_flags || !pull_seq || !h_out || h_out == x || (epi != FEPI_STORE && epi != FEPI_SILU_MUL))
+  if (!out || !norm_w || !pull_ll || !pull_count || !h_out || h_out == x || (epi != FEPI_STORE && epi != FEPI_SILU_MUL) ||
+      (reinterpret_cast<uintptr_t>(pull_ll) & 15))
     return OWL_ERR_BAD_ARG;
   if (K / 8 > 2 * vc * FM_WARPS * 32) return OWL_ERR_BAD_ARG;      // the pulled row must fit the prologue's register cache
-  p.pull_slots = (const __nv_bfloat16*)pull_slots; p.pull_flags = (const uint32_t*)pull_flags;
-  p.pull_seq = (const uint32_t*)pull_seq; p.h_out = (__nv_bfloat16*)h_out; p.pull_world = world * kparts; p.pull_ranks = world; p.pull_rows = rows;
+  p.pull_ll = (const uint2*)pull_ll; p.pull_seq = (uint32_t*)seq; p.pull_count = (int*)pull_count;
+  p.h_out = (__nv_bfloat16*)h_out; p.pull_world = world * kparts;
   p.spin_limit = spin_limit ? spin_limit : (1u << 22);
   return vc == 4 ? dispatch_fma<4>(p, FMA_PULL, epi, grid, pdl, st) : dispatch_fma<2>(p, FMA_PULL, epi, grid, pdl, st);
 }

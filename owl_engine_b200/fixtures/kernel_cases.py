@@ -2,7 +2,7 @@
 L2 but well under a few GB, then exits.
 
 ``python -m owl_engine_b200.fixtures.kernel_cases <case>`` with case in
-``gemm16 gemm8 gemm_w4 gemv attn attn16 attn_prefill_gemm attn_prefill_fused gdn_decode gdn_scan dflash_attn`` (prints the CUDA-event time per launch).
+``gemm16 gemm8 gemm_nvfp4 quant_nvfp4 gemm_w4 gemv attn attn16 attn_prefill_gemm attn_prefill_fused gdn_decode gdn_scan dflash_attn`` (prints the CUDA-event time per launch).
 """
 import math
 import sys
@@ -45,6 +45,29 @@ def gemm8():
     out = torch.empty(t, n, dtype=torch.bfloat16, device=dev)
     ms = timed(lambda: gemm_tc.e4m3_gemm(xq, sx, wq, sw, out))
     return ms, f"{2 * t * n * k / ms / 1e9:.0f} TFLOP/s"
+
+
+def gemm_nvfp4(t: int = 2048, n: int = 34816, k: int = 5120):
+    """The merged gate / up projection of a 2048-token chunk, both operands NVFP4 (block-scaled tensor-core path)."""
+    from owl_engine_b200.ops import nvfp4_tc
+
+    w = Q.random_nvfp4(n, k, dev)
+    x = torch.randn(t, k, device=dev).bfloat16()
+    xq = nvfp4_tc.quant_rows(x)
+    out = torch.empty(t, n, dtype=torch.bfloat16, device=dev)
+    nvfp4_tc.weight_atoms(w)
+    ms = timed(lambda: nvfp4_tc.gemm(w, x, out, xq=xq))
+    return ms, f"{2 * t * n * k / ms / 1e9:.0f} TFLOP/s (status {nvfp4_tc.status()})"
+
+
+def quant_nvfp4(t: int = 2048, k: int = 17408):
+    """Activation quantisation of the same path: bf16 rows -> e2m1 codes, e4m3 scale atoms, fp32 row scales."""
+    from owl_engine_b200.ops import nvfp4_tc
+
+    x = torch.randn(t, k, device=dev).bfloat16()
+    bufs = nvfp4_tc.quant_rows(x)
+    ms = timed(lambda: nvfp4_tc.quant_rows(x, *bufs))
+    return ms, f"{(t * k * 2 + t * k // 2 + t * k // 16) / ms / 1e9:.3f} TB/s"
 
 
 def gemm_w4():

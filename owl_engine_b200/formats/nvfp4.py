@@ -62,13 +62,27 @@ def quantize_act(x: torch.Tensor) -> NvFp4:
     return quantize(x)
 
 
+def pack_sf_atoms(scales: torch.Tensor) -> torch.Tensor:
+    """Scale-factor layout of the block-scaled MMA (``tcgen05.mma kind::mxf4nvf4 block16``). ``scales``: e4m3 bytes
+    ``[R, K/16]``. The scales of a 128-row x 4-block (64 k) tile are one 512-byte atom, row r / block b of the tile at byte
+    ``(r % 32) * 16 + (r // 32) * 4 + b``; atoms are ordered ``[ceil(R/128)][4 * ceil(K/256)]``, rows and k padded with zero
+    bytes (e4m3 +0: a padded block contributes nothing). Works on any device; returns uint8 ``[blocks, atoms, 512]``."""
+    r, nb = scales.shape
+    rb, ka = (r + 127) // 128, 4 * ((nb + 15) // 16)
+    s = torch.zeros(rb * 128, ka * 4, dtype=torch.uint8, device=scales.device)
+    s[:r, :nb] = scales.view(torch.uint8)
+    s = s.view(rb, 4, 32, ka, 4)                               # [block, r//32, r%32, atom, b]
+    return s.permute(0, 3, 2, 1, 4).contiguous().view(rb, ka, 512)
+
+
 def pack_for_mma(q: NvFp4):
-    """Scale-factor layout of the block-scaled MMA (``tcgen05.mma kind::mxf4nvf4 block16``): scales
-    of a 128-row x 4-block tile are stored as 32 rows x 16 bytes (row r of the tile at
-    ``[r % 32][(r // 32) * 4 + block]``), tiles ordered [N/128][K/64]. Codes stay row-major."""
-    n, k = q.shape
-    nb = k // 16
-    assert n % 128 == 0 and nb % 4 == 0
-    s = q.scales.view(n // 128, 4, 32, nb // 4, 4)             # [tile, r//32, r%32, kb, blk]
-    s = s.permute(0, 3, 2, 1, 4).contiguous()                  # [tile, kb, r%32, r//32, blk]
-    return q.codes, s.view(n // 128, nb // 4, 512)
+    """(codes, scale atoms) of a quantised matrix for the block-scaled GEMM; codes stay row-major."""
+    return q.codes, pack_sf_atoms(q.scales)
+
+
+def quantize_rows(x: torch.Tensor):
+    """Activation quantisation of the block-scaled GEMM (host oracle of ``owl_nvfp4_quant_rows``): every row has its own
+    fp32 scale ``amax_row / (6 * 448)``. Returns (codes ``[T, K/2]``, e4m3 bytes ``[T, K/16]``, fp32 scales ``[T]``)."""
+    qs = [quantize(x[t:t + 1]) for t in range(x.shape[0])]
+    return (torch.cat([q.codes for q in qs]), torch.cat([q.scales for q in qs]),
+            torch.tensor([q.global_scale for q in qs], dtype=torch.float32))

@@ -211,7 +211,7 @@ def fma_status() -> int:
 
 
 _STATUS_WORDS = {"skinny": "owl_skinny_status", "fma": "owl_fma_status", "stream_tc": "owl_stream_tc_status",
-                 "gemm": "owl_gemm_status", "gemm_dense": "owl_gemm_dense_status", "comm": "owl_comm_status"}
+                 "gemm": "owl_gemm_status", "gemm_dense": "owl_gemm_dense_status", "gemm_nvfp4": "owl_gemm_nvfp4_status", "comm": "owl_comm_status"}
 
 
 def all_status() -> dict:

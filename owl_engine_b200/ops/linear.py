@@ -64,6 +64,7 @@ def _fp8_scratch(tag: str, r: int, k: int, device):
 
 
 def w4_gemm(w, x: torch.Tensor, out: torch.Tensor, arm: str = "tc") -> torch.Tensor:
+    arm = "tc" if arm == "tc4" else arm                    # the 4-bit float product exists for NVFP4 weights only
     if arm == "baseline":
         dense = K.w4_dequant(w, _dense_scratch(w.n, w.k, x.device))
         torch.matmul(x, dense.t(), out=out)
@@ -102,12 +103,19 @@ def w4_gemm(w, x: torch.Tensor, out: torch.Tensor, arm: str = "tc") -> torch.Ten
 
 def nvfp4_gemm(w, x: torch.Tensor, out: torch.Tensor, arm: str = "tc") -> torch.Tensor:
     """out[T, N] = x @ dequant(NVFP4 w)^T for a prefill chunk: the weight is dequantised once (bf16) and multiplied on the
-    dense tcgen05 GEMM; ``"tc8"`` re-quantises rows to e4m3 and runs the 8-bit float product at twice the rate; a handful of
-    rows take the streaming GEMV."""
+    dense tcgen05 GEMM; ``"tc8"`` re-quantises rows to e4m3 and runs the 8-bit float product at twice the rate; ``"tc4"``
+    (W4A4) quantises the chunk's activations to NVFP4 with one scale per token and multiplies codes by codes on the
+    block-scaled tensor-core path (``ops/nvfp4_tc.py``), with no dense copy of the weight at all; a handful of rows take the
+    streaming GEMV."""
     from . import gemm_tc
 
-    arm = {"tcr": "tc", "tc8r": "tc8"}.get(arm, arm)       # no resident copies on this path
     t = x.shape[0]
+    if arm == "tc4":
+        from . import nvfp4_tc
+
+        if t >= nvfp4_tc.MIN_ROWS and w.k % 64 == 0:
+            return nvfp4_tc.gemm(w, x, out)
+    arm = {"tcr": "tc", "tc8r": "tc8", "tc4": "tc"}.get(arm, arm)       # no resident copies on this path
     if arm != "baseline" and t <= 8:
         K.nvfp4_linear_gemv(w, x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16), out, t)
         return out

@@ -54,6 +54,9 @@ _T = [
     KernelSpec("owl_e4m3_gemm", "gemm_dense.cu", "gemm", gen="tcgen05+tmem+tma"),
     KernelSpec("owl_gemm_dense_status", "gemm_dense.cu", "status", capture=False),
     KernelSpec("owl_gemm_dense_set_scratch", "gemm_dense.cu", "status", capture=False),
+    KernelSpec("owl_nvfp4_gemm", "gemm_nvfp4.cu", "gemm", gen="tcgen05.block_scale+tmem+tma"),
+    KernelSpec("owl_nvfp4_quant_rows", "gemm_nvfp4.cu", "quant"),
+    KernelSpec("owl_gemm_nvfp4_status", "gemm_nvfp4.cu", "status", capture=False),
     KernelSpec("owl_w4_dequant", "dequant.cu", "load"),
     KernelSpec("owl_quant_e4m3_rows", "dequant.cu", "load"),
     KernelSpec("owl_kv_pages_gather", "kvmove.cu", "store"),
@@ -139,7 +142,7 @@ def declared() -> dict[str, tuple[str, int]]:
 def cross_check() -> list[str]:
     """Mismatches between the sources, this table and the ctypes signatures (empty = consistent)."""
     from . import kernels as K
-    from . import gemm_tc  # noqa: F401  (registers its signatures)
+    from . import gemm_tc, nvfp4_tc  # noqa: F401  (register their signatures)
     from ..models import dflash2  # noqa: F401
     from ..parallel import symm  # noqa: F401
     from ..store import select

@@ -13,6 +13,7 @@ Workspace layout (identical on every rank, so an offset is valid on all peers):
     big        : bf16[big_elems]                prefill-size all-reduce payload
     push_a/b   : bf16[world][MAX_ROWS][hidden]  slots the peers' GEMV epilogues write their partial sums into
     push_flags : uint32[2][8]                   sequence numbers published by the peers' GEMVs
+    push_ll    : uint2[2][8][hidden/2]          one-token exchange of the FMA projections: (two bf16 sums, exchange number) words
     pf_slots   : bf16[world][max_local*128][hidden]  prefill reduce-scatter slots (partial sums of this rank's row tiles)
     pf_x       : 16-bit[pf_rows][hidden]        prefill all-gather target (normalised rows from every owner)
     pf_flags   : uint32[2][world][max_local]    reduce-scatter / all-gather sequence flags per row tile
@@ -33,8 +34,8 @@ _P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 K.register("owl_ar_residual_norm", [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, ctypes.c_uint,
                                     _I, _P])
 K.register("owl_w4a16_skinny_push", [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P])
-K.register("owl_push_residual_norm", [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, ctypes.c_uint, _P, _I, _I, _P])
-K.register("owl_w4_fma_tp", [_P, _P, _P, _P, _I, _I, _I, _F, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I,
+K.register("owl_push_residual_norm", [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, ctypes.c_uint, _P, _I, _P, _I, _P])
+K.register("owl_w4_fma_tp", [_P, _P, _P, _P, _I, _I, _I, _F, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I,
                              ctypes.c_uint, _I, _I, _P])
 K.register("owl_ar_inplace", [_P, _P, _P, _P, ctypes.c_longlong, _I, _I, _I, _I, ctypes.c_uint, _P])
 K.register("owl_argmax_merge", [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, ctypes.c_uint, _I, _P])
@@ -159,6 +160,10 @@ class LocalSplit:
         self.push_count = torch.zeros(2, dtype=torch.int32, device=device)
         self.push_seq = torch.zeros(2, dtype=torch.int32, device=device)
         self.push_counters = torch.zeros(2, MAX_ROWS, dtype=torch.int32, device=device)
+        self.ll = led.alloc("k-split words", "workspace", (2, 8, hidden // 2, 2), torch.int32, zero=True)
+        self.push_ll_local = [self.ll[0], self.ll[1]]
+        self.push_ll = [_ptr_array([self.ll[w].data_ptr()]) for w in range(2)]
+        self.pull_count = torch.zeros(2, dtype=torch.int32, device=device)
 
 
 class SymmetricWorkspace:
@@ -179,7 +184,9 @@ class SymmetricWorkspace:
         self.off_pflags = self.off_push + 2 * push_bytes
         pf_rows = big_elems // hidden
         ml = PrefillPipe.max_local_for(pf_rows, world)
-        self.off_pf_slots = (self.off_pflags + 2 * 8 * 4 + 255) // 256 * 256
+        self.off_ll = (self.off_pflags + 2 * 8 * 4 + 255) // 256 * 256
+        ll_bytes = 8 * (hidden // 2) * 8
+        self.off_pf_slots = (self.off_ll + 2 * ll_bytes + 255) // 256 * 256
         pf_slot_bytes = world * ml * PrefillPipe.TILE * hidden * 2
         self.off_pf_x = self.off_pf_slots + pf_slot_bytes
         self.off_pf_flags = self.off_pf_x + pf_rows * hidden * 2
@@ -209,6 +216,9 @@ class SymmetricWorkspace:
         self.push_count = torch.zeros(2, dtype=torch.int32, device=device)
         self.push_seq = torch.zeros(2, dtype=torch.int32, device=device)
         self.push_counters = torch.zeros(2, MAX_ROWS, dtype=torch.int32, device=device)
+        self.push_ll = [_ptr_array([b + self.off_ll + w * ll_bytes for b in base]) for w in range(2)]
+        self.push_ll_local = [self.buf[self.off_ll + w * ll_bytes:self.off_ll + (w + 1) * ll_bytes] for w in range(2)]
+        self.pull_count = torch.zeros(2, dtype=torch.int32, device=device)
         fl = world * ml * 4
         self.prefill = PrefillPipe(
             rank, world, hidden, pf_rows, device=device,
@@ -240,26 +250,31 @@ class SymmetricWorkspace:
                            eps: float = 1e-6, pdl: bool = False, fma: bool = False) -> None:
         """Consumer of ``gemv_push`` / ``fma_push``: waits until every rank's flag reached the sequence number the LOCAL
         producer of this call site published last (one number series per call site, whichever producer or consumer kernel
-        a step uses), then residual + norm. ``fma``: the producer was ``fma_push`` (slots are [rank][k part])."""
+        a step uses), then residual + norm. ``fma``: the producer was ``fma_push`` (one row; the slots are the 8-byte words
+        [rank][k part] of that exchange, which carry their own number, and this kernel advances the call site's word)."""
         K.call("owl_push_residual_norm", K.ptr(self.push_slots[which]), K.ptr(self.push_flags_local[which]),
                K.ptr(self.push_counters[which]), K.ptr(h), K.ptr(norm_w), K.ptr(normed), K.ptr(xpack), K.ptr(xs), m,
                self.hidden, group, self.world, MAX_ROWS, eps, 1, SPIN_LIMIT,
-               K.ptr(self.push_seq[which:]), self.kparts if fma else 1, int(pdl), K.stream())
+               K.ptr(self.push_seq[which:]), self.kparts if fma else 1, K.ptr(self.push_ll_local[which]) if fma else None,
+               int(pdl), K.stream())
 
     # -- one-token projections on the FMA arm with the collective inside (csrc/gemv_fma.cu) ------------------------------
     def fma_push(self, which: int, w, x, *, pdl: bool = False, groups_per_cta: int = 0) -> None:
-        """Row-parallel projection of one token: the partial sums go straight into slot [rank] of every rank's buffer."""
-        K.call("owl_w4_fma_tp", K.ptr(w.records), K.ptr(x), None, None, w.n, w.k, 0, 0.0, 1, 1, self.push_dst[which],
-               self.push_flag[which], K.ptr(self.push_count[which:]), K.ptr(self.push_seq[which:]), None, None, None, None,
-               None, None, 0, self.rank, self.world, MAX_ROWS, self.kparts, SPIN_LIMIT, groups_per_cta, int(pdl), K.stream())
+        """Row-parallel projection of one token: the partial sums go straight into slot [rank] of every rank's word buffer,
+        each 8-byte word carrying two sums and the number of this exchange (no flag, no fence)."""
+        assert w.n == self.hidden
+        K.call("owl_w4_fma_tp", K.ptr(w.records), K.ptr(x), None, None, w.n, w.k, 0, 0.0, 1, 1, self.push_ll[which],
+               K.ptr(self.push_seq[which:]), None, None, None, None, None, 0, self.rank, self.world, self.kparts, SPIN_LIMIT,
+               groups_per_cta, int(pdl), K.stream())
 
     def fma_pull(self, which: int, w, h_in, h_out, norm_w, out, *, epi: int = 0, eps: float = 1e-6, ab_w=None, ab_out=None,
                  ab_rows: int = 0, pdl: bool = False, groups_per_cta: int = 0) -> None:
         """Column-parallel projection of one token that first completes the all-reduce of call site ``which``:
         ``h_out = h_in + sum of the ranks' slots`` (stored by one CTA), ``out = epilogue(W . rmsnorm(h_out))``."""
-        K.call("owl_w4_fma_tp", K.ptr(w.records), K.ptr(h_in), K.ptr(norm_w), K.ptr(out), w.n, w.k, epi, eps, 1, 0, None, None,
-               None, None, K.ptr(self.push_slots[which]), K.ptr(self.push_flags_local[which]), K.ptr(self.push_seq[which:]),
-               K.ptr(h_out), K.ptr(ab_w), K.ptr(ab_out), ab_rows, self.rank, self.world, MAX_ROWS, self.kparts, SPIN_LIMIT,
+        assert w.k == self.hidden
+        K.call("owl_w4_fma_tp", K.ptr(w.records), K.ptr(h_in), K.ptr(norm_w), K.ptr(out), w.n, w.k, epi, eps, 1, 0, None,
+               K.ptr(self.push_seq[which:]), K.ptr(self.push_ll_local[which]), K.ptr(self.pull_count[which:]),
+               K.ptr(h_out), K.ptr(ab_w), K.ptr(ab_out), ab_rows, self.rank, self.world, self.kparts, SPIN_LIMIT,
                groups_per_cta, int(pdl), K.stream())
 
     def partial(self, which: int) -> torch.Tensor:

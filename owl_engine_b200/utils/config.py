@@ -75,7 +75,7 @@ SCHEMA: dict = {
     "kvmem": {"select_decode": bool, "index": bool, "workspace_per_req": int, "select_sink": int, "select_recent": int,
               "select_query_tokens": int, "score_mode": Enum("cosine-max", "dot-max", "dot-mean"), "recall_every": int,
               "gqa_aggregation": Enum("max", "mean")},
-    "kernel": {"prefill_gemm": Enum("tc", "tcr", "tc8", "tc8r", "baseline"), "decode_arm": Enum("paged"), "gdn_chunked": bool,
+    "kernel": {"prefill_gemm": Enum("tc", "tcr", "tc8", "tc8r", "tc4", "baseline"), "decode_arm": Enum("paged"), "gdn_chunked": bool,
                "gdn_fused_decode": bool, "pdl": bool, "attn_splits": int, "selfcheck": bool},
     "probes": {"step_profile": bool, "perf_level": Enum("off", "counters", "host", "gpu"), "debug": bool,
                "step_gate": Enum("off", "sticky", "single"), "step_gate_ms": int, "raw_completion": bool,

@@ -110,18 +110,18 @@ def test_w4_fma_rejects_bad_shapes():
 @pytest.mark.parametrize("parts", [1, 4])
 def test_w4_fma_push_pull_protocol_world_of_one(parts):
     """``parts`` > 1 also cuts every row tile of the row-parallel launch into k parts that land in slots of their own.
-    The tensor-parallel pairing on one GPU: the row-parallel launch stores its partial sums into slot 0 of a local
-    buffer and publishes sequence numbers; the column-parallel launch waits for them, adds the slot to the residual stream
-    (stored into a second buffer) and normalises in its prologue. Two rounds, so the sequence numbers advance."""
+    The tensor-parallel pairing on one GPU: the row-parallel launch stores its partial sums, two per 8-byte word together
+    with the number of the exchange, into slot 0 of a local word buffer; the column-parallel launch polls the words it
+    needs for that number, adds the slot to the residual stream (stored into a second buffer), normalises in its prologue
+    and advances the call site's sequence word. Two rounds, so the numbers advance."""
     import ctypes
 
     from owl_engine_b200.parallel import symm  # noqa: F401  (registers the signature)
 
-    hdim, kdim, n2, rows = 5120, 2176, 1024, 32
+    hdim, kdim, n2 = 5120, 2176, 1024
     cr, wr = _weight(hdim, kdim, 21)          # row-parallel: kdim -> hidden
     cc, wc = _weight(n2, hdim, 22)            # column-parallel: hidden -> n2
-    slots = torch.zeros(parts, rows, hdim, dtype=torch.bfloat16, device=DEV)
-    flags = torch.zeros(8, dtype=torch.int32, device=DEV)
+    words = torch.zeros(parts, hdim // 2, 2, dtype=torch.int32, device=DEV)
     count = torch.zeros(1, dtype=torch.int32, device=DEV)
     seq = torch.zeros(1, dtype=torch.int32, device=DEV)
     arr = lambda t: (ctypes.c_void_p * 8)(t.data_ptr())
@@ -132,12 +132,14 @@ def test_w4_fma_push_pull_protocol_world_of_one(parts):
     for rnd in range(2):
         x = torch.randn(kdim, generator=gen(30 + rnd)).to(torch.bfloat16)
         out = torch.zeros(n2, dtype=torch.bfloat16, device=DEV)
-        K.call("owl_w4_fma_tp", K.ptr(wr.records), K.ptr(x.to(DEV)), None, None, hdim, kdim, 0, 0.0, 1, 1, arr(slots), arr(flags),
-               K.ptr(count), K.ptr(seq), None, None, None, None, None, None, 0, 0, 1, rows, parts, 1 << 20, 0, 0, K.stream())
-        K.call("owl_w4_fma_tp", K.ptr(wc.records), K.ptr(h_in), K.ptr(nw), K.ptr(out), n2, hdim, 0, 1e-6, 1, 0, None, None, None,
-               None, K.ptr(slots), K.ptr(flags), K.ptr(seq), K.ptr(h_out), None, None, 0, 0, 1, rows, parts, 1 << 20, 0, 0, K.stream())
+        K.call("owl_w4_fma_tp", K.ptr(wr.records), K.ptr(x.to(DEV)), None, None, hdim, kdim, 0, 0.0, 1, 1, arr(words),
+               K.ptr(seq), None, None, None, None, None, 0, 0, 1, parts, 1 << 20, 0, 0, K.stream())
         torch.cuda.synchronize()
-        assert int(seq.item()) == rnd + 1 and int(flags[0].item()) == rnd + 1 and int(count.item()) == 0
+        assert int(seq.item()) == rnd and bool((words[..., 1] == rnd + 1).all())      # the producer leaves the word alone
+        K.call("owl_w4_fma_tp", K.ptr(wc.records), K.ptr(h_in), K.ptr(nw), K.ptr(out), n2, hdim, 0, 1e-6, 1, 0, None,
+               K.ptr(seq), K.ptr(words), K.ptr(count), K.ptr(h_out), None, None, 0, 0, 1, parts, 1 << 20, 0, 0, K.stream())
+        torch.cuda.synchronize()
+        assert int(seq.item()) == rnd + 1 and int(count.item()) == 0
         part = cr.dequant() @ x.float()
         want_h = (want_h + part).to(torch.bfloat16).float()
         torch.testing.assert_close(h_out.float().cpu(), want_h, rtol=2e-2, atol=6e-2)
@@ -149,11 +151,12 @@ def test_w4_fma_push_pull_protocol_world_of_one(parts):
         h_in, h_out = h_out, h_in
         want_h = h_in.float().cpu()
     assert K.fma_status() == 0
-    # a flag nobody raises: the bounded wait runs out, the kernel finishes and reports it (nothing hangs)
+    # words nobody writes: the bounded wait runs out, the kernel finishes and reports it (nothing hangs)
     seq.fill_(99)
     out = torch.zeros(n2, dtype=torch.bfloat16, device=DEV)
-    K.call("owl_w4_fma_tp", K.ptr(wc.records), K.ptr(h_in), K.ptr(nw), K.ptr(out), n2, hdim, 0, 1e-6, 1, 0, None, None, None,
-           None, K.ptr(slots), K.ptr(flags), K.ptr(seq), K.ptr(h_out), None, None, 0, 0, 1, rows, parts, 2000, 0, 0, K.stream())
+    K.call("owl_w4_fma_tp", K.ptr(wc.records), K.ptr(h_in), K.ptr(nw), K.ptr(out), n2, hdim, 0, 1e-6, 1, 0, None,
+           K.ptr(seq), K.ptr(words), K.ptr(count), K.ptr(h_out), None, None, 0, 0, 1, parts, 2000, 0, 0, K.stream())
     torch.cuda.synchronize()
     assert K.fma_status() == 3        # OWL_ERR_WAIT_PEER
     assert K.fma_status() == 0        # read clears it
+    assert int(seq.item()) == 100 and int(count.item()) == 0       # the call site's word still advances

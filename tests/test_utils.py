@@ -93,7 +93,7 @@ def test_kernel_registry_matches_sources_and_bindings():
     assert R.cross_check() == []
     assert {k.entry for k in R.admit("gemm")} == {"owl_w4a16_gemm_tc", "owl_f16_gemm_tc", "owl_f16_gemm_persist",
                                                      "owl_f16_gemm_ag", "owl_f16_gemm_rs", "owl_e4m3_gemm",
-                                                     "owl_f16_gemm_persist_f16out"}
+                                                     "owl_f16_gemm_persist_f16out", "owl_nvfp4_gemm"}
     assert all("tcgen05" in k.gen for k in R.admit("gemm"))
 
 
