@@ -143,15 +143,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(0x989680u) : "memory");
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(0xF4240u) : "memory");      // suspend-time hint: 1 ms
   return ok != 0;
 }
+// Wall-clock bound of every wait loop: a poll may sleep in hardware for up to its suspend-time hint, so counting polls does
+// not bound the time. A loop notes global_ns() when it starts and gives up once wait_expired() says so.
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+constexpr uint64_t OWL_WAIT_LIMIT_NS = 2000000000ull;      // 2 s: far beyond any legitimate wait inside one kernel
+__device__ __forceinline__ bool wait_expired(uint64_t t0) { return global_ns() - t0 > OWL_WAIT_LIMIT_NS; }
 // try_wait carries a suspend-time hint, so a waiting warp sleeps in hardware instead of burning
 // issue slots on polls; the loop below only bounds the total wait.
 // Bounded wait. Returns false when the limit ran out (caller records the error and unwinds).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 24)) {
+  const uint64_t t0 = global_ns();
   for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 15u) == 15u && wait_expired(t0)) return false;
   }
   return false;
 }

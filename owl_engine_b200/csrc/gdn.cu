@@ -40,6 +40,7 @@ struct GdnDecodeParams {
   float* conv_state;            // [slots][conv_dim][3]  (x[t-3], x[t-2], x[t-1])
   float* state;                 // [slots][nv][128][128]
   const int* slots;             // [batch]; < 0 = padding row
+  const int* tlen;              // optional [batch]: rows of sequence b to consume (min with T); the rest are skipped
   __nv_bfloat16* out;           // [rows][V] (optional)
   uint4* xpack;                 // ActPack of out (optional)
   float2* xs;
@@ -106,7 +107,8 @@ __global__ void __launch_bounds__(256) gdn_decode_kernel(GdnDecodeParams p) {
   pdl_launch_dependents();
   pdl_wait();
 
-  for (int r = 0; r < p.T; ++r) {
+  const int Tn = p.tlen ? min(p.T, max(p.tlen[b], 0)) : p.T;     // uniform in the cluster (b is)
+  for (int r = 0; r < Tn; ++r) {
     const size_t row = (size_t)b * p.T + r;
     const __nv_bfloat16* xr = p.qkvz + row * p.ld;
     const int buf = r & 1;
@@ -535,13 +537,13 @@ using namespace owl;
 OWL_API int owl_gdn_decode(const void* qkvz, int ld, const void* ab, int ldab, const void* conv_w, const void* a_log,
                            const void* dt_bias, const void* gamma, void* conv_state, void* state, const void* slots,
                            void* out, void* xpack, void* xs, int batch, int T, int nk, int nv, int G, float eps,
-                           int pdl, cudaStream_t st) {
+                           const void* tlen, int pdl, cudaStream_t st) {
   if (batch < 1 || T < 1 || T > GDN_MAX_T || nk < 1 || nv % nk || nv / nk > 8 || !actpack_group_ok(G, xpack ? batch * T : 1))
     return OWL_ERR_BAD_ARG;
   GdnDecodeParams p;
   p.qkvz = (const __nv_bfloat16*)qkvz; p.ab = (const __nv_bfloat16*)ab; p.conv_w = (const float*)conv_w;
   p.a_log = (const float*)a_log; p.dt_bias = (const float*)dt_bias; p.gamma = (const float*)gamma;
-  p.conv_state = (float*)conv_state; p.state = (float*)state; p.slots = (const int*)slots;
+  p.conv_state = (float*)conv_state; p.state = (float*)state; p.slots = (const int*)slots; p.tlen = (const int*)tlen;
   p.out = (__nv_bfloat16*)out; p.xpack = (uint4*)xpack; p.xs = (float2*)xs;
   p.ld = ld; p.ldab = ldab; p.nk = nk; p.nv = nv; p.T = T; p.G = G; p.eps = eps;
   cudaLaunchConfig_t cfg = {};

@@ -54,8 +54,10 @@ struct NfCtl {
 };
 
 __device__ __forceinline__ bool nf_wait(uint64_t* bar, uint32_t parity, NfCtl* c, int code) {
+  const uint64_t t0 = global_ns();
   for (uint32_t i = 0; i < (1u << 22); ++i) {
     if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 15u) == 15u && wait_expired(t0)) break;
     if ((i & 255u) == 255u && c->abort_flag) return false;
   }
   c->abort_flag = 1;

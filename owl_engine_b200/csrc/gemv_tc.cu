@@ -107,8 +107,10 @@ __device__ __forceinline__ bool vt_try_wait(uint64_t* bar, uint32_t parity) {
 __device__ __noinline__ bool vt_wait_slow(uint64_t* bar, uint32_t parity, VtCtl* ctl, int code) {
   // the hinted try_wait parks the warp in hardware until the phase completes: a spinning warp
   // would take issue slots from the warps it is waiting for
+  const uint64_t t0 = global_ns();
   for (uint32_t i = 0; i < (1u << 22); ++i) {
     if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 15u) == 15u && wait_expired(t0)) break;
     if ((i & 255u) == 255u && ctl->abort_flag) return false;
   }
   ctl->abort_flag = 1;

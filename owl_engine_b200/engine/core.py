@@ -32,6 +32,7 @@ class EngineConfig:
     n_pages: int = 4096            # KV pool pages (16 tokens each) per rank
     n_slots: int = 8               # GDN state rows (= concurrency ceiling, like gdn_slots)
     n_snap_rows: int = 2           # extra state rows that hold prefix-boundary snapshots
+    spec_rows: int = 1             # scratch state rows of speculative verify steps (= sequences per batched verify)
     host_cache_mb: int = 0         # pinned-host KV tier (0 = off)
     disk_cache_mb: int = 0         # disk KV tier behind the host tier (0 = off)
     disk_dir: str = ""             # directory of the disk tier (block files + restart index)
@@ -104,12 +105,12 @@ class Engine:
                                                    vocab_split=cfg.vocab_split,
                                                    quant="nvfp4" if cfg.quant == "nvfp4" else "w4a16")
         self.ledger.track_tree("weights", "weights", self.weights)
-        n_rows = cfg.n_slots + cfg.n_snap_rows + 1
+        n_rows = cfg.n_slots + cfg.n_snap_rows + max(1, cfg.spec_rows)
         if cfg.n_pages <= 0:
             cfg.n_pages = self._plan_pages(cfg, n_rows)
         self.ledger.check("kv pool + gdn state", cfg.n_pages * H.StatePool.bytes_per_page(self.spec, cfg.kv_dtype)
                           + n_rows * H.StatePool.bytes_per_slot(self.spec))
-        # GDN rows: one per sequence slot, the prefix-snapshot rows, and one scratch row for speculative rollback
+        # GDN rows: one per sequence slot, the prefix-snapshot rows, and the scratch rows for speculative rollback
         self.pool = H.StatePool(self.spec, self.device, cfg.n_pages, n_rows, kv_dtype=cfg.kv_dtype)
         for nm in ("k_pool", "v_pool", "k_scale", "v_scale"):
             if getattr(self.pool, nm, None) is not None:

@@ -67,7 +67,7 @@ class RunningEngine:
         self.park_sessions, self.max_parked, self.evict_pad_id = park_sessions, max_parked, evict_pad_id
         self.parked: dict = {}       # session -> (engine sequence id, PaddedSeq of everything in the sequence, tick)
         self.resumed = self.gap_drops = 0
-        self.sched = Scheduler(max_batch, engine.cfg.prefill_chunk, on_full)
+        self.sched = Scheduler(max_batch, engine.cfg.prefill_chunk, on_full, spec_batch=max(1, getattr(engine.cfg, "spec_rows", 1)))
         self.turns: dict[int, Turn] = {}
         self.reservations = B.Reservations()
         self._next = 0
@@ -111,6 +111,12 @@ class RunningEngine:
                 continue
             fed = self.e.seqs[t.sid].n_cached if t.sid is not None else 0
             need = (len(t.tokens) + t.opts.max_new + PAGE - 1) // PAGE
+            if t.state == QUEUED and self.park_sessions and t.opts.session in self.parked:
+                # the session's parked sequence already holds most of these pages (resumed, it keeps them; released, they
+                # become evictable prefix blocks): only the growth counts against the pool
+                psid = self.parked[t.opts.session][0]
+                if psid in self.e.seqs:
+                    need = max(1, need - len(self.e.seqs[psid].pages))
             # the speculative round accepts by greedy agreement: sampled turns decode plainly so that temperature / top-p /
             # seed keep their meaning
             spec = self.spec_runner is not None and t.opts.sampling.mode == "greedy"
@@ -127,7 +133,10 @@ class RunningEngine:
         if self._tick % 16 == 0 and self.e.host is not None:
             self.e.relieve()                 # watermark relief: cold prefix blocks leave the pool before a turn needs the room
         kvs = self.e.kv.stats()
-        evictable = kvs["lru_len"]
+        # prefix blocks on the device that no live sequence holds can all make room (leaf by leaf: the LRU list only ever
+        # shows the current leaves, which would count a long published chain as one block)
+        pinned = sum(s.reused // PAGE for s in self.e.seqs.values())
+        evictable = max(kvs["lru_len"], kvs["device_nodes"] - pinned)
         step, rejected = self.sched.schedule(self._views(), self.e.kv.free_pages, evictable,
                                              self.reservations.outstanding, self.e.cfg.n_pages,
                                              min(len(self.e.states.free_rows), len(self.e.free_rows)))
@@ -264,11 +273,16 @@ class RunningEngine:
             self._emit(t, tok)
 
     def _do_spec(self, step) -> None:
-        t = self.turns[step.turns[0]]
-        for tok in self.spec_runner.round(self.e, t.sid):
-            if t.state == DONE:
-                break
-            self._emit(t, tok)
+        ts = [self.turns[i] for i in step.turns]
+        if len(ts) == 1:
+            outs = [self.spec_runner.round(self.e, ts[0].sid)]
+        else:
+            outs = self.spec_runner.round_batch(self.e, [t.sid for t in ts])
+        for t, toks in zip(ts, outs):
+            for tok in toks:
+                if t.state == DONE:
+                    break
+                self._emit(t, tok)
 
     def _resample(self, t: Turn, row: int) -> int:
         """Sampling modes: the device returns the row's top-32 logits with the repetition penalty

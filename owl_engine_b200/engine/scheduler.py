@@ -5,7 +5,8 @@ need, the pool state and free GDN rows) and **phase policy** (round-robin betwee
 prefill: a prefill chunk is granted after every ``PREFILL_EVERY`` decode beats, immediately when
 nothing is decoding). ``schedule`` returns ``Idle`` or one ``Step``: ``Begin`` (start a queued
 turn: borrow a row, plan prefix reuse), ``Prefill`` (one chunk of one turn), ``Decode`` (all
-decoding turns, up to ``max_batch`` rows) or ``SpecRound`` (one speculative round of one turn).
+decoding turns, up to ``max_batch`` rows) or ``SpecRound`` (one speculative round of up to ``spec_batch``
+turns, when every decoding turn can take one).
 
 Reference counterpart: ``crates/engine/src/sched/{scheduler,sched_policy}.rs``.
 """
@@ -58,8 +59,9 @@ class PhaseSched:
 
 
 class Scheduler:
-    def __init__(self, max_batch: int, prefill_chunk: int, on_full: str = "reject"):
+    def __init__(self, max_batch: int, prefill_chunk: int, on_full: str = "reject", spec_batch: int = 1):
         self.max_batch, self.prefill_chunk, self.on_full = max_batch, prefill_chunk, on_full
+        self.spec_batch = spec_batch       # decoding turns one speculative round may cover (the engine's scratch state rows)
         self.phase = PhaseSched()
 
     def admission(self, t: TurnView, free_pages: int, evictable: int, outstanding: int, pool_pages: int,
@@ -89,8 +91,9 @@ class Scheduler:
             return Step("prefill", [t.turn], (t.fed, end)), rejected
         if what == "decode":
             spec = [t for t in decoding if t.spec]
-            if spec and len(decoding) == 1:
-                return Step("spec", [spec[0].turn]), rejected
+            if spec and len(spec) == len(decoding) and len(spec) <= self.spec_batch:
+                # every decoding turn can take a speculative round: one batched verify for all of them
+                return Step("spec", [t.turn for t in spec]), rejected
             batch = decoding[:self.max_batch]
             return Step("decode", [t.turn for t in batch]), rejected
         return IDLE, rejected

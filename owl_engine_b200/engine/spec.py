@@ -89,7 +89,7 @@ class LookupDraft:
                         return follow
         return []
 
-    def observe(self, engine, sid, n_rows, emitted):
+    def observe(self, engine, sid, n_rows, emitted, row0=0):
         pass
 
 
@@ -109,7 +109,7 @@ class OracleDraft:
             out.append((self.cont[i + len(out)] + 1) % self.vocab)     # a deliberately wrong draft
         return out
 
-    def observe(self, engine, sid, n_rows, emitted):
+    def observe(self, engine, sid, n_rows, emitted, row0=0):
         pass
 
 
@@ -158,11 +158,12 @@ class MtpDraft:
             return []
         return self.head.chain(depth).tolist()
 
-    def observe(self, engine: Engine, sid: int, n_rows: int, emitted: list[int]) -> None:
-        """After a verify step: rows 0..n_rows-1 were accepted; feed them with the target's hiddens."""
+    def observe(self, engine: Engine, sid: int, n_rows: int, emitted: list[int], row0: int = 0) -> None:
+        """After a verify step: its rows row0..row0+n_rows-1 (this sequence's accepted rows) feed the head, with the
+        target's hiddens."""
         seq = engine.seqs[sid]
         q0 = seq.n_cached - n_rows
-        self.head.absorb(emitted, engine.runner.h[:n_rows], q0, seq.row, seq.pages)
+        self.head.absorb(emitted, engine.runner.h[row0:row0 + n_rows], q0, seq.row, seq.pages)
         self.ready[sid] = True
 
 
@@ -202,12 +203,54 @@ class DFlash2Draft:
         seq = engine.seqs[sid]
         return self.draft.propose(seq.tokens[-1], seq.n_cached, depth)
 
-    def observe(self, engine: Engine, sid: int, n_rows: int, emitted: list[int]) -> None:
+    def observe(self, engine: Engine, sid: int, n_rows: int, emitted: list[int], row0: int = 0) -> None:
         if sid != self.sid:
             return
         seq = engine.seqs[sid]
-        cat = torch.cat([self.runner.taps[i][:n_rows] for i in self.draft.spec.taps], dim=1)
+        cat = torch.cat([self.runner.taps[i][row0:row0 + n_rows] for i in self.draft.spec.taps], dim=1)
         self.draft.encode(cat, seq.n_cached - n_rows)
+
+
+class DFlash2Pool:
+    """DFlash2 for several live sequences: one draft instance (ring KV, block buffers, captured proposal) per sequence over
+    ONE shared set of draft weights. ``bind(sid)`` before the sequence's prefill routes the prompt's tap hiddens to its
+    instance; ``release(sid)`` returns the instance. The draft forward itself still runs once per sequence and round (an
+    8-row block each); the target's verify and fold are batched by ``SpecRunner.round_batch``."""
+
+    def __init__(self, make_draft, n: int, runner, lookup: LookupDraft | None = None):
+        self.members = [DFlash2Draft(make_draft(), runner, lookup) for _ in range(n)]
+        self.free = list(range(n))
+        self.of: dict = {}
+        self.runner = runner
+        runner.tap_sink = self._on_chunk
+        self._cur = None
+
+    def bind(self, sid: int) -> None:
+        if not self.free:
+            raise RuntimeError("no free draft instance")
+        self.of[sid] = self._cur = self.members[self.free.pop()]
+        self._cur.draft.reset()
+
+    def release(self, sid: int) -> None:
+        m = self.of.pop(sid, None)
+        if m is not None:
+            self.free.append(self.members.index(m))
+
+    def _on_chunk(self, pos0: int, t: int, taps: dict) -> None:
+        if self._cur is not None:
+            self._cur._on_chunk(pos0, t, taps)
+
+    def after_prefill(self, engine: Engine, sid: int) -> None:
+        self.of[sid].after_prefill(engine, sid)
+
+    def propose(self, engine: Engine, sid: int, depth: int) -> list[int]:
+        m = self.of.get(sid)
+        return m.propose(engine, sid, depth) if m is not None else []
+
+    def observe(self, engine: Engine, sid: int, n_rows: int, emitted: list[int], row0: int = 0) -> None:
+        m = self.of.get(sid)
+        if m is not None:
+            m.observe(engine, sid, n_rows, emitted, row0)
 
 
 # ---- the round machine ------------------------------------------------------------------------
@@ -239,22 +282,23 @@ class SpecRunner:
             # from here on every step of this engine (plain or verify) uses row-count-independent arithmetic
             engine.runner.uniform_rows = True
             engine.runner.graphs.clear()
-        if hasattr(self.draft, "after_prefill"):
-            self.draft.after_prefill(engine, sid)
+        draft = self.draft_of(sid)
+        if hasattr(draft, "after_prefill"):
+            draft.after_prefill(engine, sid)
 
     def round(self, engine: Engine, sid: int) -> list[int]:
         """Emit one or more tokens for the sequence (appended to ``seq.tokens``)."""
-        st = self.stats
+        st, draft = self.stats, self.draft_of(sid)
         if self._cool > 0:                       # degraded: plain decoding until the cooldown ends
             self._cool -= 1
             st.degraded_steps += 1
             out = engine.decode_step([sid])
-            self.draft.observe(engine, sid, 1, out)
+            draft.observe(engine, sid, 1, out)
             return out
-        drafts = self.draft.propose(engine, sid, self.depth)[:self.depth]
+        drafts = draft.propose(engine, sid, self.depth)[:self.depth]
         if not drafts:
             out = engine.decode_step([sid])
-            self.draft.observe(engine, sid, 1, out)
+            draft.observe(engine, sid, 1, out)
             return out
         seq = engine.seqs[sid]
         rows = [seq.tokens[-1]] + drafts
@@ -270,7 +314,7 @@ class SpecRunner:
         emitted = target[:n_rows]
         seq.tokens.extend(emitted)
         seq.n_cached += n_rows
-        self.draft.observe(engine, sid, n_rows, emitted)
+        draft.observe(engine, sid, n_rows, emitted)
         st.rounds += 1
         st.drafted += len(drafts)
         st.accepted += m
@@ -281,6 +325,73 @@ class SpecRunner:
                 self._cool = self.cooldown
             st.window.clear()
         return emitted
+
+
+    # -- several sequences per round ---------------------------------------------------------------------------------
+    def draft_of(self, sid: int):
+        """The draft source of a sequence: ``self.per_sid[sid]`` when one was registered (sources that keep per-sequence
+        state, like the oracle of the forced-acceptance runs), else the shared one."""
+        return getattr(self, "per_sid", {}).get(sid, self.draft)
+
+    def round_batch(self, engine: Engine, sids: list[int]) -> list[list[int]]:
+        """One speculative round for every listed sequence, the target run as ONE (B, T) verify step per group of
+        ``MAX_ROWS // T`` sequences and the recurrent states of all sequences with rejected rows replayed by ONE batched
+        fold. Returns the tokens emitted per sequence (appended to their ``seq.tokens``). Needs ``EngineConfig.spec_rows``
+        >= the group size (one scratch state row per sequence of a group)."""
+        if self._cool > 0 or len(sids) == 1:
+            return [self.round(engine, sid) for sid in sids]
+        st = self.stats
+        drafts = [self.draft_of(sid).propose(engine, sid, self.depth)[:self.depth] for sid in sids]
+        d = min(len(x) for x in drafts)
+        if d == 0:
+            out = engine.decode_step(sids)
+            for i, (sid, tok) in enumerate(zip(sids, out)):
+                self.draft_of(sid).observe(engine, sid, 1, [tok], row0=i)
+            return [[tok] for tok in out]
+        t = d + 1
+        per = max(1, min(engine.runner.MAX_ROWS // t, engine.cfg.spec_rows))
+        emitted_all = []
+        for g0 in range(0, len(sids), per):
+            grp, dr = sids[g0:g0 + per], [x[:d] for x in drafts[g0:g0 + per]]
+            rows = [[engine.seqs[sid].tokens[-1]] + x for sid, x in zip(grp, dr)]
+            targets = verify_batch(engine, grp, rows)
+            slots, tlen, need = [], [], False
+            acc = []
+            for i, sid in enumerate(grp):
+                m = accept_greedy(dr[i], targets[i])
+                acc.append(m)
+                if m + 1 < t:
+                    need = True
+                    engine.pool.copy_slot(engine.spec_row + i, engine.seqs[sid].slot)
+                    slots.append(engine.seqs[sid].slot)
+                    tlen.append(m + 1)
+                else:
+                    slots.append(-1)
+                    tlen.append(0)
+            if need:
+                r = engine.runner
+                graph = r.capture_fold_batch(len(grp), t)
+                r.fold_slots[:len(grp)].copy_(torch.tensor(slots, dtype=torch.int32))
+                r.fold_tlen[:len(grp)].copy_(torch.tensor(tlen, dtype=torch.int32))
+                graph.replay()
+                st.folds += 1
+            for i, sid in enumerate(grp):
+                seq, n_rows = engine.seqs[sid], acc[i] + 1
+                emitted = targets[i][:n_rows]
+                seq.tokens.extend(emitted)
+                seq.n_cached += n_rows
+                self.draft_of(sid).observe(engine, sid, n_rows, emitted, row0=i * t)
+                st.rounds += 1
+                st.drafted += d
+                st.accepted += acc[i]
+                st.emitted += n_rows
+                st.window.append(acc[i])
+                emitted_all.append(emitted)
+        if len(st.window) >= self.window:
+            if sum(st.window) / len(st.window) < self.degrade_below:
+                self._cool = self.cooldown
+            st.window.clear()
+        return emitted_all
 
 
 def generate_spec(engine: Engine, prompt: list[int], max_new_tokens: int, spec: SpecRunner, eos: int | None = None) -> list[int]:
@@ -296,6 +407,48 @@ def generate_spec(engine: Engine, prompt: list[int], max_new_tokens: int, spec: 
         return out[:max_new_tokens]
     finally:
         engine.free_sequence(sid, publish=False)
+
+
+def verify_batch(engine: Engine, sids: list[int], rows: list[list[int]]) -> list[list[int]]:
+    """Run the target over ``rows[i]`` (anchor + drafts, the same count T for every sequence) of every listed sequence as
+    one (B, T) step; returns the argmax after each row, per sequence. Each sequence's GDN state is first copied to its own
+    scratch row (``engine.spec_row + i``); every GDN layer's inputs are kept for the fold."""
+    r = engine.runner
+    b, t = len(sids), len(rows[0])
+    m = b * t
+    assert all(len(x) == t for x in rows) and m <= r.MAX_ROWS and b <= engine.cfg.spec_rows
+    if r.gdn_save is None:
+        r.enable_gdn_save()
+        r.uniform_rows = True
+        r.capture_fold(1)
+    engine._last_rows = {}
+    lay = H.StepLayout(b, t)
+    hi = engine.h_inp_np
+    ctx_max = 0
+    for i, sid in enumerate(sids):
+        seq = engine.seqs[sid]
+        pos = seq.n_cached
+        engine._ensure_pages(seq, pos + t + 1)
+        engine.pool.copy_slot(seq.slot, engine.spec_row + i)
+        for j, tok in enumerate(rows[i]):
+            p, q = pos + j, i * t + j
+            hi[lay.ids + q] = tok
+            hi[lay.pos3 + q] = hi[lay.pos3 + m + q] = hi[lay.pos3 + 2 * m + q] = p + seq.rope_delta
+            hi[lay.kv_slot + q] = seq.pages[p // PAGE] * PAGE + p % PAGE
+        hi[lay.ctx + i] = pos + t
+        hi[lay.gslot + i] = seq.slot
+        hi[lay.bt_row + i] = seq.row
+        ctx_max = max(ctx_max, pos + t)
+    graph = r.capture(b, t, ctx_hint=engine._ctx_bucket(ctx_max))
+    n = lay.size
+    r.inp[:n].copy_(engine.h_inp[:n], non_blocking=True)
+    graph.replay()
+    engine.h_tok[:m].copy_(r.out_tok[:m], non_blocking=True)
+    torch.cuda.current_stream().synchronize()
+    engine.h2d_bytes += n * 4
+    engine.d2h_bytes += m * 4
+    engine._check_status()
+    return [[int(engine.h_tok_np[i * t + j]) for j in range(t)] for i in range(b)]
 
 
 def verify_step(engine: Engine, sid: int, rows: list[int]) -> list[int]:

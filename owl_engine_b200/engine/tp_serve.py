@@ -8,7 +8,7 @@ function of its call sequence (page allocation, prefix matches, tier moves), so 
 exchanging anything else, and they meet on the device inside the kernels' collectives. NCCL carries no step traffic.
 
 Mirrored: ``add_sequence``, ``free_sequence``, ``drop_ranges``, ``append_tokens``, ``extend_sequence``,
-``prefill_range``, ``decode_step``, ``set_last_token``, ``relieve``, ``checkpoint``, ``close``, the speculative runner's ``after_prefill`` / ``round``, and
+``prefill_range``, ``decode_step``, ``set_last_token``, ``relieve``, ``checkpoint``, ``close``, the speculative runner's ``after_prefill`` / ``round`` / ``round_batch``, and
 ``shutdown``. Everything else (statistics, plans, sequence lookups) is read-only and stays local.
 
 Reference counterpart: ``TpEngine::assemble / run`` and the ``mirror2!`` call sites
@@ -123,6 +123,10 @@ class MirroredSpec:
         self._ring.push("spec_round", sid)
         return self._s.round(self._real(engine), sid)
 
+    def round_batch(self, engine, sids: list):
+        self._ring.push("spec_round_batch", list(sids))
+        return self._s.round_batch(self._real(engine), list(sids))
+
 
 def follower_loop(engine, ring: StepRing, spec_runner=None, idle_timeout_s: float | None = None) -> int:
     """Apply the leader's descriptors to this rank's engine until ``shutdown`` (or the ring closes). Returns the
@@ -142,6 +146,8 @@ def follower_loop(engine, ring: StepRing, spec_runner=None, idle_timeout_s: floa
                 spec_runner.after_prefill(engine, *args)
             elif op == "spec_round":
                 spec_runner.round(engine, *args)
+            elif op == "spec_round_batch":
+                spec_runner.round_batch(engine, *args)
             elif op in MIRRORED:
                 getattr(engine, op)(*args, **kw)
             else:

@@ -1,13 +1,15 @@
-"""Long-context agent session: one large prompt, then turns that each append new tokens to the parked sequence.
+"""Long-context agent session through the serving engine (``RunningEngine`` with parked sessions).
 
-    turn 0      a random prompt of ``--prompt`` tokens is prefilled in chunks (time to first token), ``--gen`` tokens follow
-    turn k      ``--append`` new tokens extend the live sequence (only the new tail is prefilled), ``--gen`` tokens follow
+    turn 0      the client sends a random prompt of ``--prompt`` tokens (chunked prefill: time to first token), ``--gen``
+                tokens follow; the finished turn parks its sequence (pages + recurrent state row) under the session name
+    turn k      the client sends its whole history plus ``--append`` new tokens; the engine recognises the parked sequence,
+                prefills only the new tail (the hit rate is cached / prompt tokens), ``--gen`` tokens follow
     --image-turn / --drop-turn   a ``--patches``-patch image runs through the vision tower and its merged embeddings enter
-                the turn's text, padded to page boundaries; a later turn unlinks exactly those pages (leave-gap deletion)
-    afterwards  the sequence is published, a second sequence with the same first ``--prompt`` tokens measures the prefix
-                hit (blocks adopted, tokens prefilled, time to first token); with a device pool smaller than the session
-                (``--kv-gb``) cold blocks have moved to the pinned-host tier and to disk in between and come back here,
-                which gives the recall latency.
+                the turn's text as a droppable segment (padded to page boundaries by the engine); at the drop turn the
+                client's history no longer contains it and the engine unlinks exactly those pages (leave-gap deletion)
+    afterwards  the session is released (its exact prefix is published), and a second session with the same first
+                ``--prompt`` tokens measures the cross-session prefix hit; with a device pool smaller than the session
+                (``--kv-gb``) cold blocks have moved to the pinned-host tier and to disk in between and come back here.
 
 Prints one JSON line (rank 0). Under ``torchrun`` every rank runs the same calls on its weight shard.
 
@@ -66,7 +68,7 @@ def main() -> None:
     total = a.prompt + a.turns * (a.append + a.gen) + a.gen + 4096
     disk_dir = tempfile.mkdtemp(prefix=f"owl_agent_r{rank}_")
     # bytes of one KV page on this rank: probe a throw-away config through the engine's own plan
-    cfg = EngineConfig(model="qwen3.8-27b", group=128, n_pages=64, n_slots=4, n_snap_rows=4, max_seqs=4, max_seq=total,
+    cfg = EngineConfig(model="qwen3.8-27b", group=128, n_pages=64, n_slots=4, n_snap_rows=a.turns + 3, max_seqs=4, max_seq=total,
                        lm_head_int8=True, prefill_gemm=a.prefill_gemm, n_layers=a.layers,
                        quant="nvfp4" if a.quant == "nvfp4" else "w4a16", act_bits=8 if a.quant == "w4a8" else 15,
                        host_cache_mb=int(a.host_gb * 1024), disk_cache_mb=int(a.disk_gb * 1024), disk_dir=disk_dir)
@@ -95,78 +97,81 @@ def main() -> None:
     tower_ms = (time.perf_counter() - t0) * 1e3
     n_img = emb.shape[0]
 
+    from ..engine.running import RunningEngine, TurnOpts
+
+    re_ = RunningEngine(eng, max_batch=4, park_sessions=True, max_parked=2, evict_pad_id=pad_id - 1)
+
+    def run_turn(tokens, session, images=None, spans=None):
+        """Submit the client's full history as one turn of ``session``; returns (generated tokens, facts)."""
+        opts = TurnOpts(max_new=a.gen, ignore_eos=True, session=session, images=list(images or []),
+                        image_pad_id=pad_id if images else None, evict_spans=list(spans or []))
+        sync()
+        t0 = time.perf_counter()
+        tid = re_.submit(tokens, opts)
+        turn = re_.turns[tid]
+        out, ttft, t_first, usage = [], None, None, {}
+        while not re_.idle():
+            if not re_.pump():
+                break
+            while not turn.sink.empty():
+                ev = turn.sink.get()
+                if ev[0] == "token":
+                    if ttft is None:
+                        torch.cuda.synchronize()
+                        t_first = time.perf_counter()
+                        ttft = t_first - t0
+                    out.append(ev[2])
+                elif ev[0] == "completed":
+                    usage = ev[3]
+                elif ev[0] == "failed":
+                    raise RuntimeError(ev[2])
+        sync()
+        dt = time.perf_counter() - (t_first or t0)
+        fresh = len(tokens) - usage.get("cached_tokens", 0)
+        return out, {"prompt_tokens": len(tokens), "cached_tokens": usage.get("cached_tokens", 0),
+                     "hit_rate": round(usage.get("cached_tokens", 0) / len(tokens), 4), "prefilled": fresh,
+                     "ttft_s": round(ttft, 3), "prefill_tok_s": round(fresh / ttft, 1),
+                     "decode_tok_s": round((len(out) - 1) / dt, 1) if len(out) > 1 and dt > 0 else None}
+
     turns = []
     prompt = rnd(a.prompt)
-    sid = eng.add_sequence(prompt)
-    sync()
-    t0 = time.perf_counter()
-    tok = eng.prefill(sid)
-    sync()
-    ttft = time.perf_counter() - t0
-
-    def decode(n):
-        sync()
-        t1 = time.perf_counter()
-        for _ in range(n):
-            eng.decode_step([sid])
-        sync()
-        return n / (time.perf_counter() - t1)
-
-    turns.append({"turn": 0, "new_tokens": a.prompt, "ttft_s": round(ttft, 3), "prefill_tok_s": round(a.prompt / ttft, 1),
-                  "decode_tok_s": round(decode(a.gen), 1), "ctx": eng.seqs[sid].n_cached})
-    img_range = None
+    history = list(prompt)
+    gen, facts = run_turn(history, "agent")
+    turns.append({"turn": 0, **facts})
+    history += gen
+    images, spans, img_at = [], [], None
     for k in range(1, a.turns + 1):
-        seq = eng.seqs[sid]
-        new = rnd(a.append)
-        images = None
         note = {}
+        new = rnd(a.append)
         if k == a.image_turn:
-            # pad so that the image's rows start and end on page boundaries of the live sequence
-            base = len(seq.tokens)
-            lead = (-base) % PAGE
-            tail = (-(base + lead + n_img)) % PAGE
-            new = rnd(lead) + [pad_id] * n_img + rnd(tail) + new
+            img_at = len(history) + len(new) // 2
+            new = new[:len(new) // 2] + [pad_id] * n_img + new[len(new) // 2:]
             images = [(emb, grid, V.fingerprint(b"agent-session-image"))]
-            img_range = (base + lead, base + lead + n_img + tail)
+            spans = [(img_at, img_at + n_img)]
             note["image_rows"] = n_img
-        if k == a.drop_turn and img_range is not None:
-            sync()
-            t1 = time.perf_counter()
-            removed = eng.drop_ranges(sid, [img_range])
-            sync()
-            note["dropped_tokens"] = removed
-            note["drop_ms"] = round((time.perf_counter() - t1) * 1e3, 3)
-        sync()
-        t1 = time.perf_counter()
-        eng.extend_sequence(sid, new, images=images, image_pad_id=pad_id if images else None)
-        sync()
-        dt = time.perf_counter() - t1
-        turns.append({"turn": k, "new_tokens": len(new), "ttft_s": round(dt, 3), "prefill_tok_s": round(len(new) / dt, 1),
-                      "decode_tok_s": round(decode(a.gen), 1), "ctx": eng.seqs[sid].n_cached, **note})
+        if k == a.drop_turn and img_at is not None:
+            # the client drops the screenshot from its history: the server unlinks exactly those pages
+            history = history[:img_at] + history[img_at + n_img:]
+            images, spans, img_at = [], [], None
+            note["client_dropped_rows"] = n_img
+        history += new
+        drops0 = re_.gap_drops
+        gen, facts = run_turn(history, "agent", images, spans)
+        history += gen
+        turns.append({"turn": k, **facts, **note, "resumed": re_.resumed, "gap_drops": re_.gap_drops - drops0})
     facts_live = eng.rel.facts()
-    eng.free_sequence(sid, publish=True)
-    # a second session on the same prefix: adopted blocks, recall from the lower tiers, time to first token
+    if "agent" in re_.parked:
+        re_._release_parked("agent", publish=True)           # the session ends: its exact prefix becomes content-addressable
+    # a second session on the same first prompt: adopted blocks, recall from the lower tiers, time to first token
     prompt2 = prompt + rnd(a.append)
-    lookups0, hits0, rec0 = eng.prefix_lookups, eng.prefix_hits, eng.rel.recalled
-    sync()
-    t1 = time.perf_counter()
-    sid2 = eng.add_sequence(prompt2)
-    sync()
-    adopt_s = time.perf_counter() - t1
-    reused = eng.seqs[sid2].reused
-    t1 = time.perf_counter()
-    eng.prefill(sid2)
-    sync()
-    ttft2 = time.perf_counter() - t1
+    rec0, hits0 = eng.rel.recalled, eng.prefix_hits
+    gen2, facts2 = run_turn(prompt2, "agent-2")
     recalled = eng.rel.recalled - rec0
-    res = {"what": "agent session", "tp": world, "quant": a.quant, "prefill_gemm": a.prefill_gemm, "kv_pool_gb": a.kv_gb,
+    res = {"what": "agent session through RunningEngine (parked session resume, leave-gap image drop, prefix tree, tiers)",
+           "tp": world, "quant": a.quant, "prefill_gemm": a.prefill_gemm, "kv_pool_gb": a.kv_gb,
            "kv_pages": cfg.n_pages, "page_bytes": page_bytes, "vision_tower_ms": round(tower_ms, 1), "turns": turns,
            "tiers_after_session": {k: v for k, v in facts_live.items() if k != "last_verdict"},
-           "second_session": {"prompt": len(prompt2), "reused_tokens": reused, "hit_rate": round(reused / len(prompt2), 4),
-                              "adopt_s": round(adopt_s, 3), "recalled_blocks": recalled,
-                              "recall_ms_per_block": round(adopt_s * 1e3 / recalled, 3) if recalled else None,
-                              "ttft_s": round(adopt_s + ttft2, 3), "prefix_hits": eng.prefix_hits - hits0,
-                              "lookups": eng.prefix_lookups - lookups0},
+           "second_session": {**facts2, "recalled_blocks": recalled, "prefix_hits": eng.prefix_hits - hits0},
            "tiers_final": {k: v for k, v in eng.rel.facts().items() if k != "last_verdict"}}
     status = K.all_status()
     if comm:
@@ -174,7 +179,8 @@ def main() -> None:
     res["kernel_status"] = status
     if rank == 0:
         print(json.dumps(res))
-    eng.free_sequence(sid2, publish=False)
+    for name in list(re_.parked):
+        re_._release_parked(name, publish=False)
     eng.close()
     if comm is not None:
         import torch.distributed as dist

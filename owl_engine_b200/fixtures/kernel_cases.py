@@ -2,7 +2,7 @@
 L2 but well under a few GB, then exits.
 
 ``python -m owl_engine_b200.fixtures.kernel_cases <case>`` with case in
-``gemm16 gemm8 gemm_nvfp4 quant_nvfp4 gemm_w4 gemv attn attn16 attn_prefill_gemm attn_prefill_fused gdn_decode gdn_scan dflash_attn`` (prints the CUDA-event time per launch).
+``gemm16 gemm8 gemm_nvfp4 quant_nvfp4 gemm_w4 gemv attn attn16 attn_prefill_tc attn_tc_only attn_prefill_gemm attn_prefill_fused gdn_decode gdn_scan dflash_attn`` (prints the CUDA-event time per launch).
 """
 import math
 import sys
@@ -160,8 +160,35 @@ def _prefill_attn_case(ctx: int, t: int):
     return hq, hkv, hd, kp, vp, bt, q, qraw
 
 
+def attn_prefill_tc(ctx: int = 8192, t: int = 2048):
+    """The last 2048-row chunk of an 8192-token prompt, attention only, on the fused tcgen05 kernel (gather + group + one
+    kernel with S and O in tensor memory + gate). ``attn_tc_only`` times the fused kernel alone."""
+    K.ATTN_FUSED = True
+    hq, hkv, hd, kp, vp, bt, q, qraw = _prefill_attn_case(ctx, t)
+    ws = K.attn_gemm_ws(dev, t, ctx, hq, hkv, hd)
+    out = torch.empty(t, hq * hd, dtype=torch.float16, device=dev)
+    ms = timed(lambda: K.attn_gemm_prefill(q, kp, vp, None, bt[0], ctx - t, t, hq, hkv, hd, 1 / math.sqrt(hd), ws, qraw,
+                                           hq * 2 * hd, out))
+    flops = 4 * hq * hd * (t * (ctx - t) + t * t / 2)
+    return ms, f"{flops / ms / 1e9:.0f} TFLOP/s of causal attention work (status {K.all_status()['attn_tc']})"
+
+
+def attn_tc_only(ctx: int = 8192, t: int = 2048):
+    hq, hkv, hd = 24, 4, 256
+    gq = hq // hkv
+    qg = torch.randn(hkv, t * gq, hd, device=dev).bfloat16()
+    kk = torch.randn(hkv, ctx, hd, device=dev).bfloat16()
+    vt = torch.randn(hkv, hd, ctx, device=dev).half()
+    og = torch.empty(hkv, t * gq, hd, dtype=torch.bfloat16, device=dev)
+    ms = timed(lambda: K.call("owl_attn_tc", K.ptr(qg), K.ptr(kk), K.ptr(vt), K.ptr(og), t * gq, gq, hkv, ctx, ctx - t,
+                              1 / math.sqrt(hd), K.stream()))
+    flops = 4 * hq * hd * (t * (ctx - t) + t * t / 2)
+    return ms, f"{flops / ms / 1e9:.0f} TFLOP/s of causal attention work (status {K.all_status()['attn_tc']})"
+
+
 def attn_prefill_gemm(ctx: int = 8192, t: int = 2048):
     """The last 2048-row chunk of an 8192-token prompt, attention only, GEMM form (gather + 4 x (GEMM, softmax, GEMM) + gate)."""
+    K.ATTN_FUSED = False
     hq, hkv, hd, kp, vp, bt, q, qraw = _prefill_attn_case(ctx, t)
     ws = K.attn_gemm_ws(dev, t, ctx, hq, hkv, hd)
     out = torch.empty(t, hq * hd, dtype=torch.float16, device=dev)

@@ -768,6 +768,44 @@ class HybridRunner:
                          group=self.G, eps=sp.eps, pdl=False)
             gi += 1
 
+    def fold_batch(self, b: int, t: int) -> None:
+        """``fold`` for the ``b`` sequences of the last (b, t) step at once: sequence i (GDN slot ``fold_slots[i]``) advances
+        over its first ``fold_tlen[i]`` rows; a slot < 0 or a length 0 leaves that sequence alone. Capturable."""
+        sp = self.spec
+        qs, as_ = self.gdn_save
+        gi = 0
+        for lw in self.w.layers:
+            if lw.kind != "gdn":
+                continue
+            K.gdn_decode(qs[gi], qs.shape[2], as_[gi], self.ldab, lw.conv_w, lw.a_log, lw.dt_bias, lw.gamma,
+                         self.pool.conv_state[gi], self.pool.rec_state[gi], self.fold_slots, batch=b, t=t, nk=sp.nk, nv=sp.nv,
+                         group=self.G, eps=sp.eps, pdl=False, tlen=self.fold_tlen)
+            gi += 1
+
+    def capture_fold_batch(self, b: int, t: int):
+        """CUDA graph of fold_batch(b, t) reading ``self.fold_slots`` / ``self.fold_tlen`` (int32 [MAX_ROWS])."""
+        key = ("foldb", b, t)
+        g = self.graphs.get(key)
+        if g is None:
+            if not hasattr(self, "fold_slots"):
+                self.fold_slots = torch.full((self.MAX_ROWS,), -1, dtype=torch.int32, device=self.device)
+                self.fold_tlen = torch.zeros(self.MAX_ROWS, dtype=torch.int32, device=self.device)
+            stream = torch.cuda.Stream(device=self.device)
+            stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(stream):
+                saved = (self.fold_slots.clone(), self.fold_tlen.clone())
+                self.fold_slots.fill_(-1)
+                self.fold_batch(b, t)                  # warm-up on inert slots
+                stream.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    self.fold_batch(b, t)
+                self.fold_slots.copy_(saved[0])
+                self.fold_tlen.copy_(saved[1])
+            torch.cuda.current_stream().wait_stream(stream)
+            self.graphs[key] = g
+        return g
+
     def capture_fold(self, t: int):
         """CUDA graph of fold(t) reading the GDN slot from ``self.fold_slot``."""
         key = ("fold", t)

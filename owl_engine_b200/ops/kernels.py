@@ -8,6 +8,7 @@ from __future__ import annotations
 
 import collections
 import ctypes
+import os
 from ctypes import c_longlong, c_float, c_int, c_void_p
 
 import torch
@@ -31,7 +32,7 @@ _SIGS = {
     "owl_sigmoid_gate": [_P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _P],
     "owl_embed": [_P, _P, _P, _I, _I, _I, _I, _P],
     "owl_argmax": [_P, _I, _I, _I, _P, _P, _I, _P, _I, _P, _I, _P],
-    "owl_gdn_decode": [_P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
+    "owl_gdn_decode": [_P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _I, _P],
     "owl_gdn_conv_fwd": [_P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _P],
     "owl_gdn_scan": [_P, _P, _I, _P, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _F, _I, _P],
     "owl_qknorm_rope_insert": [_P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F,
@@ -83,6 +84,10 @@ _launch_seq = 0
 
 def call(name: str, *args) -> None:
     global _launch_seq
+    if args and name not in _SIGS:
+        # without argument types ctypes would pass 64-bit pointers as 32-bit ints: the module that registers this entry's
+        # signature has not been imported
+        raise RuntimeError(f"{name}: no ctypes signature registered (import the module that binds it first)")
     rc = fn(name)(*args)
     _launch_seq += 1
     _LAUNCHES.append((_launch_seq, name, args))
@@ -211,7 +216,7 @@ def fma_status() -> int:
 
 
 _STATUS_WORDS = {"skinny": "owl_skinny_status", "fma": "owl_fma_status", "stream_tc": "owl_stream_tc_status",
-                 "gemm": "owl_gemm_status", "gemm_dense": "owl_gemm_dense_status", "gemm_nvfp4": "owl_gemm_nvfp4_status", "comm": "owl_comm_status"}
+                 "gemm": "owl_gemm_status", "gemm_dense": "owl_gemm_dense_status", "gemm_nvfp4": "owl_gemm_nvfp4_status", "attn_tc": "owl_attn_tc_status", "comm": "owl_comm_status"}
 
 
 def all_status() -> dict:
@@ -280,10 +285,11 @@ def argmax(logits, m: int, vocab: int, ld: int, scratch_val, scratch_idx, nparts
 
 def gdn_decode(qkvz, ld: int, ab, ldab: int, conv_w, a_log, dt_bias, gamma, conv_state, state, slots, *, out=None,
                xpack=None, xs=None, batch: int, t: int, nk: int, nv: int, group: int = 128, eps: float = 1e-6,
-               pdl: bool = False) -> None:
+               pdl: bool = False, tlen=None) -> None:
+    """``tlen`` (int32 [batch], optional): sequence b consumes only its first ``tlen[b]`` rows (batched fold after a verify)."""
     call("owl_gdn_decode", ptr(qkvz), ld, ptr(ab), ldab, ptr(conv_w), ptr(a_log), ptr(dt_bias), ptr(gamma),
          ptr(conv_state), ptr(state), ptr(slots), ptr(out), ptr(xpack), ptr(xs), batch, t, nk, nv, group, eps,
-         int(pdl), stream())
+         ptr(tlen), int(pdl), stream())
 
 
 def gdn_conv_fwd(x, ld: int, conv_w, conv_state, slot: int, out, t: int, nk: int, nv: int, use_state: bool) -> None:
@@ -394,6 +400,8 @@ def attn_gemm_prefill(q, k_pool, v_pool, scales, bt_row, pos0: int, t: int, hq: 
     dense k-major operands (K bf16, V transposed fp16), then per q head S = Q K^T (fp16 scores), a causal softmax in place,
     O = P V; the sigmoid gate of the q projection closes it. ``q``: bf16 [t, hq, hd] after norm and rotary; ``bt_row``: the
     sequence's block-table row; ``ws``: scratch tensors kept by the caller (``attn_gemm_ws``); ``out``: [t, hq * hd] bf16 / fp16."""
+    from . import gemm_tc  # noqa: F401  (binds the dense GEMM entries this path calls)
+
     ctx = pos0 + t
     ctx_pad = (ctx + 63) // 64 * 64
     fmt = 2 if k_pool.dtype == torch.float16 else (1 if scales is not None else 0)
@@ -402,6 +410,14 @@ def attn_gemm_prefill(q, k_pool, v_pool, scales, bt_row, pos0: int, t: int, hq: 
          ptr(bt_row), ctx, ctx_pad, hkv, hd, ptr(kb), ptr(vt), stream())
     gq, st = hq // hkv, stream()
     inv = ws["inv"][:hq * t]            # 1 / softmax denominator per (head, token), applied with the gate
+    if ATTN_FUSED and ws.get("grouped", True) and hd == 256:
+        # one fused kernel for all kv heads: S and O in tensor memory, online softmax between the two products, key tiles
+        # past a row tile's causal limit skipped (csrc/attn_tc.cu); the output is normalised already
+        qg, og = ws["qg"][:hq * t * hd], ws["og"][:hq * t * hd]
+        call("owl_q_group", ptr(q), ptr(qg), t, hq, hkv, hd, st)
+        call("owl_attn_tc", ptr(qg), ptr(kb), ptr(vt), ptr(og), t * gq, gq, hkv, ctx_pad, pos0, float(scale), st)
+        call("owl_attn_gate", ptr(og), ptr(qraw), ldq, hd, ptr(out), t, hq * hd, _is_f16(out), gq, None, st)
+        return
     if ws.get("grouped", True):
         # the gq q heads of a kv head as consecutive rows: one GEMM pair per kv head, K and V^T read once for all of them
         qg, og = ws["qg"][:hq * t * hd], ws["og"][:hq * t * hd]
@@ -423,6 +439,10 @@ def attn_gemm_prefill(q, k_pool, v_pool, scales, bt_row, pos0: int, t: int, hq: 
         call("owl_f16_gemm_persist", ptr(s), ctx_pad, vt.data_ptr() + kh * hd * ctx_pad * 2, ctx_pad, o.data_ptr() + h * hd * 2,
              t, hd, ctx_pad, hq * hd, 0, st)
     call("owl_attn_gate", ptr(o), ptr(qraw), ldq, hd, ptr(out), t, hq * hd, _is_f16(out), 0, ptr(inv), st)
+
+
+ATTN_FUSED = os.environ.get("OWL_ATTN_TC", "1") == "1"      # long-context prefill attention: the fused tcgen05 kernel (0: GEMM form)
+register("owl_attn_tc", [_P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P])
 
 
 def attn_gemm_ws(device, t: int, max_ctx: int, hq: int, hkv: int, hd: int) -> dict:

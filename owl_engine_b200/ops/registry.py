@@ -57,6 +57,8 @@ _T = [
     KernelSpec("owl_nvfp4_gemm", "gemm_nvfp4.cu", "gemm", gen="tcgen05.block_scale+tmem+tma"),
     KernelSpec("owl_nvfp4_quant_rows", "gemm_nvfp4.cu", "quant"),
     KernelSpec("owl_gemm_nvfp4_status", "gemm_nvfp4.cu", "status", capture=False),
+    KernelSpec("owl_attn_tc", "attn_tc.cu", "attn", gen="tcgen05+tmem+tma"),
+    KernelSpec("owl_attn_tc_status", "attn_tc.cu", "status", capture=False),
     KernelSpec("owl_w4_dequant", "dequant.cu", "load"),
     KernelSpec("owl_quant_e4m3_rows", "dequant.cu", "load"),
     KernelSpec("owl_kv_pages_gather", "kvmove.cu", "store"),

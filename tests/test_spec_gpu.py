@@ -61,3 +61,33 @@ def test_degrade_after_low_acceptance():
     spec = SpecRunner(OracleDraft(plain, len(p), 0, eng.spec.vocab), depth=2, window=4, degrade_below=0.5, cooldown=8)
     assert generate_spec(eng, p, 40, spec) == plain
     assert spec.stats.degraded_steps >= 8
+
+
+@pytest.mark.parametrize("depth,accepts", [(3, [3, 1, 0]), (7, [3, 3, 7])])
+def test_batched_rounds_equal_plain_decoding_per_sequence(depth, accepts):
+    """Several sequences share one (B, T) verify step and one batched fold per round; every sequence's output equals its
+    plain greedy continuation, whatever its acceptance length."""
+    eng = Engine(EngineConfig(model="test-hybrid", snap_cut=True, n_pages=192, n_slots=4, n_snap_rows=2, spec_rows=4, max_seqs=4,
+                              max_seq=512, prefill_chunk=64))
+    eng.runner.uniform_rows = True
+    n_new = 26
+    prompts = [prompt(33 + 5 * i, seed=10 + i) for i in range(len(accepts))]
+    plains = [eng.generate(p, n_new) for p in prompts]
+    spec = SpecRunner(None, depth=depth, degrade_below=-1.0)
+    spec.per_sid = {}
+    sids, outs = [], []
+    for p, plain, acc in zip(prompts, plains, accepts):
+        sid = eng.add_sequence(p, reuse=False)
+        outs.append([eng.prefill(sid)])
+        spec.per_sid[sid] = OracleDraft(plain, len(p), acc, eng.spec.vocab)
+        spec.after_prefill(eng, sid)
+        sids.append(sid)
+    while any(len(o) < n_new for o in outs):
+        live = [i for i, o in enumerate(outs) if len(o) < n_new]
+        for i, toks in zip(live, spec.round_batch(eng, [sids[i] for i in live])):
+            outs[i].extend(toks)
+    for o, plain in zip(outs, plains):
+        assert o[:n_new] == plain
+    assert spec.stats.folds > 0 and spec.stats.rounds > len(accepts)
+    # the verify steps were batched: fewer (B, T) graphs than rounds
+    assert any(isinstance(k, tuple) and len(k) > 2 and isinstance(k[0], int) and k[0] > 1 and k[1] > 1 for k in eng.runner.graphs)
