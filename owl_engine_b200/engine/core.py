@@ -80,7 +80,9 @@ class Sequence:
 
 class Engine:
     def __init__(self, cfg: EngineConfig, *, spec: ModelSpec | None = None, weights: H.HybridWeights | None = None,
-                 comm=None, device=None, ledger=None):
+                 comm=None, device=None, ledger=None, limits=None):
+        """``device="cpu"`` boots the engine on the CPU face (``engine/cpu_mock.py``): every host-side mechanism runs over a
+        stand-in model, ``limits`` (``utils.cpuface.MockLimits``) injects the capacity and capture limits."""
         from ..store.kv import KvStore
         from ..store.rel import Rel
         from ..store.state import StateStore
@@ -89,6 +91,11 @@ class Engine:
 
         self.cfg = cfg
         self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
+        self.mock = self.device.type == "cpu"
+        if self.mock and ledger is None and limits is not None and limits.vram_bytes:
+            from .cpu_mock import ledger_from
+
+            ledger = ledger_from(limits)
         full = spec or PRESETS[cfg.model]()
         if cfg.n_layers is not None:
             from dataclasses import replace
@@ -99,6 +106,10 @@ class Engine:
         world = comm.world if comm is not None else 1
         rank = comm.rank if comm is not None else 0
         self.spec = full.sharded(rank, world) if world > 1 and full.tp_world == 1 else full
+        if self.mock and weights is None:
+            from types import SimpleNamespace
+
+            weights = SimpleNamespace(embed=None, vocab_offset=0, layers=[])
         self.weights = weights or H.random_weights(self.spec, self.device, group=cfg.group, seed=cfg.seed + rank * 7919,
                                                    lm_head_int8=cfg.lm_head_int8,
                                                    layout="block" if cfg.decode_gemv == "tc" else "slice",
@@ -119,9 +130,15 @@ class Engine:
         self.ledger.track("pool.rec_state", "gdn state", self.pool.rec_state)
         self.spec_row = cfg.n_slots + cfg.n_snap_rows
         self.max_blocks = (cfg.max_seq + PAGE - 1) // PAGE
-        self.runner = H.HybridRunner(self.spec, self.weights, self.pool, max_seqs=cfg.max_seqs * (2 if cfg.kvmem_budget else 1),
-                                     max_blocks=self.max_blocks, prefill_chunk=cfg.prefill_chunk, comm=comm,
-                                     pdl=cfg.pdl, prefill_gemm=cfg.prefill_gemm)
+        if self.mock:
+            from .cpu_mock import NullRunner
+
+            self.runner = NullRunner(self.spec, self.pool, max_seqs=cfg.max_seqs * (2 if cfg.kvmem_budget else 1),
+                                     max_blocks=self.max_blocks, limits=limits)
+        else:
+            self.runner = H.HybridRunner(self.spec, self.weights, self.pool, max_seqs=cfg.max_seqs * (2 if cfg.kvmem_budget else 1),
+                                         max_blocks=self.max_blocks, prefill_chunk=cfg.prefill_chunk, comm=comm,
+                                         pdl=cfg.pdl, prefill_gemm=cfg.prefill_gemm)
         self.runner.decode_gemv = cfg.decode_gemv
         if cfg.act_bits != 15:
             assert cfg.act_bits == 8, "act_bits is 15 or 8"
@@ -146,8 +163,9 @@ class Engine:
         self.seqs: dict[int, Sequence] = {}
         self._next_sid = 0
         # pinned staging for the host-fed step
-        self.h_inp = torch.zeros(self.runner.inp.numel(), dtype=torch.int32).pin_memory()
-        self.h_tok = torch.zeros(H.HybridRunner.MAX_ROWS, dtype=torch.int32).pin_memory()
+        pin = (lambda t: t) if self.mock else (lambda t: t.pin_memory())
+        self.h_inp = pin(torch.zeros(self.runner.inp.numel(), dtype=torch.int32))
+        self.h_tok = pin(torch.zeros(H.HybridRunner.MAX_ROWS, dtype=torch.int32))
         self.h_inp_np = self.h_inp.numpy()
         self.h_tok_np = self.h_tok.numpy()
         self.h2d_bytes = 0
@@ -405,7 +423,9 @@ class Engine:
         seq = self.seqs[sid]
         assert start == seq.n_cached and end <= seq.n_prompt
         self._ensure_pages(seq, end + 1)
-        ids = torch.tensor(seq.tokens[start:end], dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
+        ids = torch.tensor(seq.tokens[start:end], dtype=torch.int32)
+        if not self.mock:
+            ids = ids.pin_memory().to(self.device, non_blocking=True)
         embeds = pos3 = None
         if seq.images:
             # text rows from the embedding table, image rows from the vision tower's merged embeddings
@@ -495,7 +515,8 @@ class Engine:
         self.runner.inp[:n].copy_(self.h_inp[:n], non_blocking=True)
         graph.replay()
         self.h_tok[:b].copy_(self.runner.out_tok[:b], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        if not self.mock:
+            torch.cuda.current_stream().synchronize()
         self.h2d_bytes += n * 4
         self.d2h_bytes += b * 4
         self._check_status()
@@ -517,6 +538,8 @@ class Engine:
         library arm (every rank runs the same check on the same step count, so they switch together). Single-GPU steps
         check every ``STATUS_EVERY`` x 8 steps (only copy / MMA waits exist there), tensor-parallel ones every
         ``STATUS_EVERY``."""
+        if self.mock:
+            return
         self._status_tick = getattr(self, "_status_tick", 0) + 1
         every = self.STATUS_EVERY * (1 if self.comm is not None else 8)
         if not force and self._status_tick % every:

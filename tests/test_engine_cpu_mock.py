@@ -1,0 +1,102 @@
+"""The engine on the CPU face: boot, budget refusal, prefix reuse, tier round trips and agent sessions without a GPU.
+
+The stand-in model (``engine/cpu_mock.py``) makes every next token depend on the sequence's recurrent state row and on a
+mark in every page of its context, so these tests fail if the host logic adopts, moves or drops the wrong bytes."""
+import pytest
+import torch
+
+from owl_engine_b200.engine.core import Engine, EngineConfig
+from owl_engine_b200.engine.running import RunningEngine, TurnOpts
+from owl_engine_b200.utils.cpuface import CaptureUnsupported, MockLimits
+from owl_engine_b200.utils.ledger import BudgetError
+
+
+def cfg(**kw):
+    base = dict(model="test-hybrid", n_pages=64, n_slots=4, n_snap_rows=3, max_seqs=4, max_seq=512, prefill_chunk=64)
+    base.update(kw)
+    return EngineConfig(**base)
+
+
+def toks(n, seed=0, vocab=500):
+    return torch.randint(0, vocab, (n,), generator=torch.Generator().manual_seed(seed)).tolist()
+
+
+def test_boot_generates_deterministically_and_counts_pages():
+    a, b = Engine(cfg(), device="cpu"), Engine(cfg(), device="cpu")
+    p = toks(70)
+    out = a.generate(p, 20)
+    assert out == b.generate(p, 20) and len(set(out)) > 5
+    assert a.kv.free_pages + a.kv.stats()["device_nodes"] == a.cfg.n_pages          # nothing leaked
+    assert a.runner.launches == 70 + 19
+
+
+def test_vram_limit_refuses_the_boot_loudly():
+    with pytest.raises(BudgetError) as ei:
+        Engine(cfg(n_pages=4096), device="cpu", limits=MockLimits(vram_bytes=8 << 20))
+    assert "kv pool" in str(ei.value) and "MiB" in str(ei.value)
+    Engine(cfg(), device="cpu", limits=MockLimits(vram_bytes=1 << 30))            # and a pool that fits is accepted
+
+
+def test_prefix_hit_restores_state_and_pages():
+    e = Engine(cfg(), device="cpu")
+    p = toks(100, 1)
+    want = e.generate(p + toks(9, 2), 12)
+    assert e.prefix_hits == 0
+    again = e.generate(p + toks(9, 2), 12)                # same prompt: adopted up to the snapshot boundary
+    assert again == want and e.prefix_hits == 1
+    sid = e.add_sequence(p + toks(30, 3))                 # shares only the first 100 tokens
+    assert e.seqs[sid].reused == 0 or e.seqs[sid].reused % 16 == 0
+    e.free_sequence(sid, publish=False)
+
+
+def test_pressure_demotes_to_the_host_tier_and_replays_promote_back(tmp_path):
+    e = Engine(cfg(n_pages=24, host_cache_mb=1, disk_cache_mb=4, disk_dir=str(tmp_path)), device="cpu")
+    prompts = [toks(150, 10 + i) for i in range(3)]      # 9 full blocks each: the third one pushes the oldest tails to the host
+    first = [e.generate(p, 6) for p in prompts]
+    assert e.rel.demoted > 0 and e.kv.stats()["device_nodes"] < e.kv.stats()["nodes"]
+    hits0 = e.prefix_hits
+    for p, w in zip(prompts, first):                      # every prompt again: demoted blocks are promoted, the state row restored
+        sid = e.add_sequence(p)
+        assert e.seqs[sid].reused == 144
+        out = [e.prefill(sid)]
+        while len(out) < 6:
+            out.append(e.decode_step([sid])[0])
+        e.free_sequence(sid)
+        assert out == w
+    assert e.prefix_hits == hits0 + 3
+    # a restart adopts what the disk tier and its index hold
+    e.checkpoint()
+    e.close()
+    e2 = Engine(cfg(n_pages=24, host_cache_mb=1, disk_cache_mb=4, disk_dir=str(tmp_path)), device="cpu")
+    assert e2.adopted["blocks"] > 0
+    assert e2.generate(prompts[2], 6) == first[2]
+
+
+def test_parked_session_resume_and_leave_gap_drop():
+    e = Engine(cfg(n_pages=96), device="cpu")
+    re_ = RunningEngine(e, max_batch=2, park_sessions=True, max_parked=2, evict_pad_id=499)
+    hist = toks(80, 20)
+    out = re_.generate(hist, TurnOpts(max_new=5, ignore_eos=True, session="s"))
+    hist += out
+    img = [498] * 32                                      # a droppable segment (client coordinates)
+    new = toks(10, 21) + img + toks(7, 22)
+    spans = [(len(hist) + 10, len(hist) + 42)]
+    hist2 = hist + new
+    out2 = re_.generate(hist2, TurnOpts(max_new=5, ignore_eos=True, session="s", evict_spans=spans))
+    assert re_.resumed == 1
+    hist2 += out2
+    # the client drops the segment: the engine unlinks its pages instead of recomputing the history
+    lo, hi = spans[0]
+    hist3 = hist2[:lo] + hist2[hi:] + toks(6, 23)
+    launches0 = e.runner.launches
+    out3 = re_.generate(hist3, TurnOpts(max_new=4, ignore_eos=True, session="s"))
+    assert re_.resumed == 2 and re_.gap_drops == 1 and len(out3) == 4
+    assert e.runner.launches - launches0 < 20             # only the new tail ran, not the history
+
+
+def test_capture_limit_surfaces():
+    e = Engine(cfg(), device="cpu", limits=MockLimits(graph_capture=False))
+    sid = e.add_sequence(toks(20))
+    e.prefill(sid)
+    with pytest.raises(CaptureUnsupported):
+        e.decode_step([sid])
