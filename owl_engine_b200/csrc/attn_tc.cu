@@ -9,12 +9,13 @@
 //   qg  bf16 [hkv][rows][256]       K  bf16 [hkv][ctx_pad][256]       Vt  fp16 [hkv][256][ctx_pad]       og  bf16 [hkv][rows][256]
 // All three are k-major for their MMA, read by plain (non-multicast) TMA with the 128-byte swizzle.
 //
-// One CTA = one (row tile, kv head), 192 threads, key tiles of 64:
+// One CTA = one (row tile, kv head), 320 threads, key tiles of 64:
 //   warp 0      producer: Q once (64 KB), then K_j (32 KB) and V_j (32 KB) through two-stage rings of their own
 //   warp 1      one thread issues S_j = Q K_j^T (16 x M128 N64 K16, bf16) into one of two 64-column S buffers, then
 //               O += P_{j-1} V_{j-1} (4 x M128 N256 K16, fp16) into the 256 O columns: S_{j} runs while the softmax of tile j-1
 //               is still busy
-//   warps 2-5   softmax, one query row per thread: tcgen05.ld S_j, scale, causal mask on the diagonal tiles, running maximum,
+//   warps 2-9   softmax, two threads per query row (each half of the tile's key columns; the halves' row maxima meet through
+//               shared memory at an mbarrier): tcgen05.ld S_j, causal mask on the diagonal tiles, running maximum,
 //               P_j = 2^(s - m) as fp16 into swizzled shared memory (the A operand of the second MMA), row sums. The maximum
 //               in use only moves when the new one exceeds it by more than 8 (a factor 256, far inside fp16 / fp32 range);
 //               then, after the PV product in flight has completed, the warp rescales its O rows in tensor memory
@@ -38,8 +39,8 @@ constexpr int AT_V_BYTES = AT_HD * AT_BN * 2;            // 32 KB: [256 rows x 1
 constexpr int AT_P_BYTES = AT_BM * AT_BN * 2;            // 16 KB: [128 rows x 128 B]
 constexpr int AT_OFF_K = AT_Q_BYTES, AT_OFF_V = AT_OFF_K + 2 * AT_K_BYTES, AT_OFF_P = AT_OFF_V + 2 * AT_V_BYTES;
 constexpr int AT_OFF_CTL = AT_OFF_P + 2 * AT_P_BYTES;    // 224 KB
-constexpr int AT_SMEM = AT_OFF_CTL + 256 + 1024;
-constexpr int AT_THREADS = 192;
+constexpr int AT_SMEM = AT_OFF_CTL + 2304;          // 231,680 bytes: the dynamic region is declared 1024-aligned
+constexpr int AT_THREADS = 320;        // producer warp, MMA warp, 8 softmax warps
 constexpr uint32_t AT_COL_S = 0, AT_COL_O = 128;         // TMEM columns: S0, S1 (64 each), O (256)
 constexpr float AT_LAZY = 8.f;
 
@@ -50,9 +51,13 @@ struct AtParams {
 };
 struct AtCtl {
   uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full[2], p_empty[2], o_done;
+  uint64_t pair[4];            // meeting point of the two softmax warps of a lane quarter (64 arrivals per phase)
   uint32_t tmem_base;
   volatile int abort_flag;
+  float mx[2][2][AT_BM];       // [tile parity][column half][row]: row maxima of the halves (and, at the end, the halves' sums)
 };
+
+static_assert(sizeof(AtCtl) <= 2304, "control block exceeds its reservation");
 
 __device__ __forceinline__ bool at_wait(uint64_t* bar, uint32_t parity, AtCtl* c, int code) {
   const uint64_t t0 = global_ns();
@@ -60,6 +65,27 @@ __device__ __forceinline__ bool at_wait(uint64_t* bar, uint32_t parity, AtCtl* c
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 15u) == 15u && wait_expired(t0)) break;
     if ((i & 255u) == 255u && c->abort_flag) return false;
+  }
+  c->abort_flag = 1;
+  atomicCAS(&g_attn_tc_status, 0, code);
+  return false;
+}
+// The same wait for the hand-offs on the critical path of a tile (scores ready, probabilities ready, the warps' meeting
+// point): test_wait polls instead of suspending the thread, whose wake-up costs more than the work it waits for.
+__device__ __forceinline__ bool at_spin(uint64_t* bar, uint32_t parity, AtCtl* c, int code) {
+  const uint64_t t0 = global_ns();
+  for (uint32_t i = 0;; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    if (ok) return true;
+    if ((i & 63u) == 63u) {
+      if (c->abort_flag) return false;
+      if (wait_expired(t0)) break;
+    }
   }
   c->abort_flag = 1;
   atomicCAS(&g_attn_tc_status, 0, code);
@@ -86,9 +112,13 @@ __device__ __forceinline__ float at_ex2(float x) {
 __global__ void __launch_bounds__(AT_THREADS, 1) attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
                                                                 const __grid_constant__ CUtensorMap tmK,
                                                                 const __grid_constant__ CUtensorMap tmV, AtParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* base = smem_raw;
   AtCtl* ctl = reinterpret_cast<AtCtl*>(base + AT_OFF_CTL);
+  if ((smem_u32(base) & 1023u) != 0u) {              // the swizzled tiles need a 1024-byte aligned base: refuse to run on anything else
+    if (threadIdx.x == 0) atomicCAS(&g_attn_tc_status, 0, OWL_ERR_BAD_ARG);
+    return;
+  }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // the row tiles with the most key tiles start first
   const int tile = p.row_tiles - 1 - (int)blockIdx.x, kh = blockIdx.y;
@@ -101,10 +131,11 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_tc_kernel(const __grid_con
     for (int s = 0; s < 2; ++s) {
       mbar_init(&ctl->k_full[s], 1); mbar_init(&ctl->k_empty[s], 1);
       mbar_init(&ctl->v_full[s], 1); mbar_init(&ctl->v_empty[s], 1);
-      mbar_init(&ctl->s_full[s], 1); mbar_init(&ctl->s_empty[s], 4);
-      mbar_init(&ctl->p_full[s], 4); mbar_init(&ctl->p_empty[s], 1);
+      mbar_init(&ctl->s_full[s], 1); mbar_init(&ctl->s_empty[s], 8);
+      mbar_init(&ctl->p_full[s], 8); mbar_init(&ctl->p_empty[s], 1);
     }
     mbar_init(&ctl->o_done, 1);
+    for (int q = 0; q < 4; ++q) mbar_init(&ctl->pair[q], 64);
     ctl->abort_flag = 0;
     mbar_fence_init();
     prefetch_tmap(&tmQ);
@@ -154,8 +185,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_tc_kernel(const __grid_con
       auto pv = [&](int j) -> bool {        // O (+)= P_j V_j
         const int s = j & 1;
         const uint32_t ph = ((uint32_t)(j >> 1)) & 1u;
-        if (!at_wait(&ctl->p_full[s], ph, ctl, OWL_ERR_WAIT_EPI)) return false;
-        if (!at_wait(&ctl->v_full[s], ph, ctl, OWL_ERR_WAIT_TMA)) return false;
+        if (!at_spin(&ctl->p_full[s], ph, ctl, OWL_ERR_WAIT_EPI)) return false;
+        if (!at_spin(&ctl->v_full[s], ph, ctl, OWL_ERR_WAIT_TMA)) return false;
         tc_fence_after();
         const uint64_t dp = umma_desc_k128(smem_u32(base + AT_OFF_P + s * AT_P_BYTES));
         const uint64_t dv = umma_desc_k128(smem_u32(base + AT_OFF_V + s * AT_V_BYTES));
@@ -170,8 +201,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_tc_kernel(const __grid_con
       for (int j = 0; ok && j < n_kv; ++j) {
         const int s = j & 1;
         const uint32_t ph = ((uint32_t)(j >> 1)) & 1u;
-        if (!at_wait(&ctl->k_full[s], ph, ctl, OWL_ERR_WAIT_TMA)) { ok = false; break; }
-        if (!at_wait(&ctl->s_empty[s], ph ^ 1u, ctl, OWL_ERR_WAIT_EPI)) { ok = false; break; }
+        if (!at_spin(&ctl->k_full[s], ph, ctl, OWL_ERR_WAIT_TMA)) { ok = false; break; }
+        if (!at_spin(&ctl->s_empty[s], ph ^ 1u, ctl, OWL_ERR_WAIT_EPI)) { ok = false; break; }
         tc_fence_after();
         const uint32_t sk = smem_u32(base + AT_OFF_K + s * AT_K_BYTES);
 #pragma unroll
@@ -188,42 +219,49 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_tc_kernel(const __grid_con
       if (ok && n_kv > 0) pv(n_kv - 1);
     }
   } else {
-    const int q4 = warp & 3;                                 // TMEM lane quarter of this warp
+    // Two warps per TMEM lane quarter: both own the same 32 query rows, each half of a tile's 64 key columns (and half of
+    // the O columns when rows are rescaled). They meet once per tile, at an mbarrier of 64 arrivals (a bounded wait like every other), to exchange the
+    // row maxima of their halves through shared memory.
+    const int q4 = warp & 3, hf = (warp - 2) >> 2;           // lane quarter, column half
     const int r_loc = q4 * 32 + lane, grow = row0 + r_loc;
     const int limit = grow < p.rows ? p.pos0 + grow / p.gq + 1 : 1;      // keys visible to this row (padding rows: one key)
     const uint32_t lane_addr = tmem + ((uint32_t)(q4 * 32) << 16);
     uint8_t* prow_base = base + AT_OFF_P + (r_loc >> 3) * 1024 + (r_loc & 7) * 128;
-    float m_used = -INFINITY, l = 0.f;
+    float m_used = -INFINITY, l = 0.f;                       // l: this thread's half of the row sum
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
       const int s = j & 1;
       const uint32_t ph = ((uint32_t)(j >> 1)) & 1u;
-      if (!__all_sync(0xffffffffu, at_wait(&ctl->s_full[s], ph, ctl, OWL_ERR_WAIT_MMA))) { ok = false; break; }
+      if (!__all_sync(0xffffffffu, at_spin(&ctl->s_full[s], ph, ctl, OWL_ERR_WAIT_MMA))) { ok = false; break; }
       tc_fence_after();
-      uint32_t sv[64];
-      tmem_ld_32x32b_x32(lane_addr + AT_COL_S + s * AT_BN, sv);
-      tmem_ld_32x32b_x32(lane_addr + AT_COL_S + s * AT_BN + 32, sv + 32);
+      uint32_t sv[32];
+      tmem_ld_32x32b_x32(lane_addr + AT_COL_S + s * AT_BN + hf * 32, sv);
       tc_wait_ld();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&ctl->s_empty[s]);
-      const int k0 = j * AT_BN;
+      const int k0 = j * AT_BN + hf * 32;
       // raw scores: the softmax scale (> 0) is folded into the exponent's multiply-add; four independent running maxima
-      if (k0 + AT_BN > limit) {
+      if (k0 + 32 > limit) {
 #pragma unroll
-        for (int c = 0; c < 64; ++c)
+        for (int c = 0; c < 32; ++c)
           if (k0 + c >= limit) sv[c] = 0xff800000u;           // -inf: outside this row's causal limit
       }
       float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < 64; c += 4) {
+      for (int c = 0; c < 32; c += 4) {
         m4[0] = fmaxf(m4[0], __uint_as_float(sv[c]));     m4[1] = fmaxf(m4[1], __uint_as_float(sv[c + 1]));
         m4[2] = fmaxf(m4[2], __uint_as_float(sv[c + 2])); m4[3] = fmaxf(m4[3], __uint_as_float(sv[c + 3]));
       }
-      const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.scale_log2;
+      float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.scale_log2;
+      ctl->mx[s][hf][r_loc] = mx;
+      mbar_arrive(&ctl->pair[q4]);                           // (arrive has release, the wait acquire semantics)
+      if (!__all_sync(0xffffffffu, at_spin(&ctl->pair[q4], (uint32_t)j & 1u, ctl, OWL_ERR_WAIT_EPI))) { ok = false; break; }
+      mx = fmaxf(mx, ctl->mx[s][hf ^ 1][r_loc]);             // both warps of the row now hold the same maximum
       // Rows whose every key of this tile is masked keep their maximum (a tile past the row's limit inside the row tile).
       const bool grow_m = mx > m_used + AT_LAZY;
-      if (__any_sync(0xffffffffu, grow_m)) {
+      const unsigned any_here = __any_sync(0xffffffffu, grow_m);
+      if (any_here) {
         const float m_new = grow_m ? mx : m_used;
         const float f = (m_used == -INFINITY) ? 0.f : at_ex2(m_used - m_new);
         if (j > 0) {
@@ -231,13 +269,13 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_tc_kernel(const __grid_con
           if (!__all_sync(0xffffffffu, at_wait(&ctl->o_done, ((uint32_t)(j - 1)) & 1u, ctl, OWL_ERR_WAIT_MMA))) { ok = false; break; }
           tc_fence_after();
 #pragma unroll 1
-          for (int c = 0; c < AT_HD / 32; ++c) {
+          for (int c = 0; c < AT_HD / 64; ++c) {             // this warp's half of the O columns
             uint32_t o[32];
-            tmem_ld_32x32b_x32(lane_addr + AT_COL_O + c * 32, o);
+            tmem_ld_32x32b_x32(lane_addr + AT_COL_O + hf * (AT_HD / 2) + c * 32, o);
             tc_wait_ld();
 #pragma unroll
             for (int v = 0; v < 32; ++v) o[v] = __float_as_uint(__uint_as_float(o[v]) * f);
-            at_tmem_st_x32(lane_addr + AT_COL_O + c * 32, o);
+            at_tmem_st_x32(lane_addr + AT_COL_O + hf * (AT_HD / 2) + c * 32, o);
           }
           tc_wait_st();
           tc_fence_before();
@@ -246,19 +284,19 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_tc_kernel(const __grid_con
         m_used = m_new;
       }
       // P_j (fp16) into the swizzled A-operand tile; the buffer is free once the product two tiles back has read it
-      if (!__all_sync(0xffffffffu, at_wait(&ctl->p_empty[s], ph ^ 1u, ctl, OWL_ERR_WAIT_MMA))) { ok = false; break; }
+      if (!__all_sync(0xffffffffu, at_spin(&ctl->p_empty[s], ph ^ 1u, ctl, OWL_ERR_WAIT_MMA))) { ok = false; break; }
       uint8_t* prow = prow_base + s * AT_P_BYTES;
       float s4[4] = {0.f, 0.f, 0.f, 0.f};
       const float nm = -m_used;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < 4; ++c) {
         float e[8];
 #pragma unroll
         for (int v = 0; v < 8; ++v) {
           e[v] = at_ex2(fmaf(__uint_as_float(sv[c * 8 + v]), p.scale_log2, nm));
           s4[v & 3] += e[v];
         }
-        *reinterpret_cast<uint4*>(prow + ((c ^ (r_loc & 7)) << 4)) =
+        *reinterpret_cast<uint4*>(prow + (((hf * 4 + c) ^ (r_loc & 7)) << 4)) =
             make_uint4(pack_f16(e[0], e[1]), pack_f16(e[2], e[3]), pack_f16(e[4], e[5]), pack_f16(e[6], e[7]));
       }
       l += (s4[0] + s4[1]) + (s4[2] + s4[3]);
@@ -266,14 +304,21 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_tc_kernel(const __grid_con
       __syncwarp();
       if (lane == 0) mbar_arrive(&ctl->p_full[s]);
     }
+    // the two halves of every row sum meet; then each warp writes its half of the output columns
+    ctl->mx[n_kv & 1][hf][r_loc] = l;                         // the parity buffer the last tile did not use
+    if (ok) {
+      mbar_arrive(&ctl->pair[q4]);
+      ok = __all_sync(0xffffffffu, at_wait(&ctl->pair[q4], (uint32_t)n_kv & 1u, ctl, OWL_ERR_WAIT_EPI));
+    }
+    l += ctl->mx[n_kv & 1][hf ^ 1][r_loc];
     if (ok && n_kv > 0 && __all_sync(0xffffffffu, at_wait(&ctl->o_done, ((uint32_t)(n_kv - 1)) & 1u, ctl, OWL_ERR_WAIT_MMA))) {
       tc_fence_after();
       const float inv = 1.f / l;
-      __nv_bfloat16* orow = p.out + ((size_t)kh * p.rows + grow) * AT_HD;
+      __nv_bfloat16* orow = p.out + ((size_t)kh * p.rows + grow) * AT_HD + hf * (AT_HD / 2);
 #pragma unroll 1
-      for (int c = 0; c < AT_HD / 32; ++c) {
+      for (int c = 0; c < AT_HD / 64; ++c) {
         uint32_t o[32];
-        tmem_ld_32x32b_x32(lane_addr + AT_COL_O + c * 32, o);
+        tmem_ld_32x32b_x32(lane_addr + AT_COL_O + hf * (AT_HD / 2) + c * 32, o);
         tc_wait_ld();
         if (grow < p.rows) {
 #pragma unroll

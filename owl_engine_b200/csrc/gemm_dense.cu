@@ -78,6 +78,28 @@ __device__ __forceinline__ bool gd_wait(uint64_t* bar, uint32_t parity, GdCtl* c
   return false;
 }
 
+// The producer's and the MMA issuer's waits: one thread each, polling with test_wait (a suspended thread's wake-up adds to
+// every stage's round trip).
+__device__ __forceinline__ bool gd_spin(uint64_t* bar, uint32_t parity, GdCtl* c, int code) {
+  const uint64_t t0 = global_ns();
+  for (uint32_t i = 0;; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    if (ok) return true;
+    if ((i & 63u) == 63u) {
+      if (c->abort_flag) return false;
+      if (wait_expired(t0)) break;
+    }
+  }
+  c->abort_flag = 1;
+  atomicCAS(&g_gemm_dense_status, 0, code);
+  return false;
+}
+
 __device__ __forceinline__ void gd_st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -142,7 +164,7 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gemm_dense_kernel(const __grid_
         }
         for (int k = kb; k < ke; ++k, ++it) {
           const int s = it % GD_STAGES;
-          if (!gd_wait(&ctl->empty[s], (((uint32_t)(it / GD_STAGES)) & 1u) ^ 1u, ctl, OWL_ERR_WAIT_MMA)) goto prod_done;
+          if (!gd_spin(&ctl->empty[s], (((uint32_t)(it / GD_STAGES)) & 1u) ^ 1u, ctl, OWL_ERR_WAIT_MMA)) goto prod_done;
           mbar_expect_tx(&ctl->full[s], GD_STAGE_BYTES);
           uint8_t* st = base + (size_t)s * GD_STAGE_BYTES;
           tma_load_2d(st, &tmA, &ctl->full[s], k * BKE, m0);
@@ -162,14 +184,14 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gemm_dense_kernel(const __grid_
       int it = 0, lt = 0;                                   // stage counter, local tile counter
       for (int tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x, ++lt) {
         const int ab = lt & 1;
-        if (!gd_wait(&ctl->acc_empty[ab], (((uint32_t)(lt >> 1)) & 1u) ^ 1u, ctl, OWL_ERR_WAIT_EPI)) break;
+        if (!gd_spin(&ctl->acc_empty[ab], (((uint32_t)(lt >> 1)) & 1u) ^ 1u, ctl, OWL_ERR_WAIT_EPI)) break;
         tc_fence_after();
         const uint32_t td = tmem + ab * GD_BN;
         bool ok = true;
         const int kb = (tile % KS) * KI / KS, ke = (tile % KS + 1) * KI / KS;
         for (int k = kb; k < ke; ++k, ++it) {
           const int s = it % GD_STAGES;
-          if (!gd_wait(&ctl->full[s], ((uint32_t)(it / GD_STAGES)) & 1u, ctl, OWL_ERR_WAIT_TMA)) { ok = false; break; }
+          if (!gd_spin(&ctl->full[s], ((uint32_t)(it / GD_STAGES)) & 1u, ctl, OWL_ERR_WAIT_TMA)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(base + (size_t)s * GD_STAGE_BYTES);
           const uint64_t da = umma_desc_k128(sa), db = umma_desc_k128(sa + GD_A_BYTES);

@@ -64,6 +64,27 @@ __device__ __forceinline__ bool nf_wait(uint64_t* bar, uint32_t parity, NfCtl* c
   atomicCAS(&g_gemm_nvfp4_status, 0, code);
   return false;
 }
+// The producer's and the MMA issuer's waits: one thread each, polling with test_wait (a suspended thread's wake-up would
+// add to every stage's round trip, which bounds this kernel).
+__device__ __forceinline__ bool nf_spin(uint64_t* bar, uint32_t parity, NfCtl* c, int code) {
+  const uint64_t t0 = global_ns();
+  for (uint32_t i = 0;; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    if (ok) return true;
+    if ((i & 63u) == 63u) {
+      if (c->abort_flag) return false;
+      if (wait_expired(t0)) break;
+    }
+  }
+  c->abort_flag = 1;
+  atomicCAS(&g_gemm_nvfp4_status, 0, code);
+  return false;
+}
 // plain (non-multicast) bulk copy global -> this CTA's shared memory; bytes and both addresses multiples of 16
 __device__ __forceinline__ void nf_bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -122,7 +143,7 @@ __global__ void __launch_bounds__(NF_THREADS, 1) gemm_nvfp4_kernel(const __grid_
         const uint8_t* sfb = p.sfb + (size_t)nt * KI * NF_SF_BYTES;
         for (int k = 0; k < KI; ++k, ++it) {
           const int s = it % NF_STAGES;
-          if (!nf_wait(&ctl->empty[s], (((uint32_t)(it / NF_STAGES)) & 1u) ^ 1u, ctl, OWL_ERR_WAIT_MMA)) goto prod_done;
+          if (!nf_spin(&ctl->empty[s], (((uint32_t)(it / NF_STAGES)) & 1u) ^ 1u, ctl, OWL_ERR_WAIT_MMA)) goto prod_done;
           mbar_expect_tx(&ctl->full[s], NF_STAGE_BYTES);
           uint8_t* st = base + (size_t)s * NF_STAGE_BYTES;
           tma_load_2d(st, &tmA, &ctl->full[s], k * NF_BKB, mt * NF_BM);
@@ -144,13 +165,13 @@ __global__ void __launch_bounds__(NF_THREADS, 1) gemm_nvfp4_kernel(const __grid_
       int it = 0, lt = 0;
       for (int tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x, ++lt) {
         const int ab = lt & 1;
-        if (!nf_wait(&ctl->acc_empty[ab], (((uint32_t)(lt >> 1)) & 1u) ^ 1u, ctl, OWL_ERR_WAIT_EPI)) break;
+        if (!nf_spin(&ctl->acc_empty[ab], (((uint32_t)(lt >> 1)) & 1u) ^ 1u, ctl, OWL_ERR_WAIT_EPI)) break;
         tc_fence_after();
         const uint32_t td = tmem + ab * NF_BN;
         bool ok = true;
         for (int k = 0; k < KI; ++k, ++it) {
           const int s = it % NF_STAGES;
-          if (!nf_wait(&ctl->full[s], ((uint32_t)(it / NF_STAGES)) & 1u, ctl, OWL_ERR_WAIT_TMA)) { ok = false; break; }
+          if (!nf_spin(&ctl->full[s], ((uint32_t)(it / NF_STAGES)) & 1u, ctl, OWL_ERR_WAIT_TMA)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(base + (size_t)s * NF_STAGE_BYTES);
           const uint32_t ssfa = sa + NF_A_BYTES + NF_B_BYTES, ssfb = ssfa + NF_SF_BYTES;

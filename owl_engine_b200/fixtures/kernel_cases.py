@@ -2,7 +2,7 @@
 L2 but well under a few GB, then exits.
 
 ``python -m owl_engine_b200.fixtures.kernel_cases <case>`` with case in
-``gemm16 gemm8 gemm_nvfp4 quant_nvfp4 gemm_w4 gemv attn attn16 attn_prefill_tc attn_tc_only attn_prefill_gemm attn_prefill_fused gdn_decode gdn_scan dflash_attn`` (prints the CUDA-event time per launch).
+``gemm16 gemm8 gemm_nvfp4 quant_nvfp4 gemm_w4 gemv attn attn16 attn_prefill_tc attn_tc_only attn_prefill_gemm attn_prefill_fused gdn_decode gdn_scan dflash_attn`` (prints the CUDA-event time per launch; integer arguments of a case may follow its name).
 """
 import math
 import sys
@@ -266,5 +266,5 @@ def dflash_attn():
 
 if __name__ == "__main__":
     case = sys.argv[1]
-    ms, note = globals()[case]()
+    ms, note = globals()[case](*[int(a) for a in sys.argv[2:]])      # optional integer arguments of the case, in order
     print(f"{case}: {ms * 1e3:.1f} us per launch, {note}")

@@ -98,10 +98,11 @@ def qwen_27b() -> ModelSpec:
                      rotary_dim=64, rope_theta=1e7, nk=16, kd=128, nv=48, vd=128)
 
 
-def test_hybrid(n_layers: int = 4, hidden: int = 256, vocab: int = 512) -> ModelSpec:
-    """A few-layer model with the 27B head geometry (hd 256, GVA 3:1) for kernel / engine tests."""
-    return ModelSpec(name="test-hybrid", vocab=vocab, hidden=hidden, inter=2 * hidden, n_layers=n_layers, hq=6, hkv=1,
-                     hd=256, rotary_dim=64, rope_theta=1e7, nk=2, kd=128, nv=6, vd=128)
+def test_hybrid(n_layers: int = 4, hidden: int = 256, vocab: int = 512, mult: int = 1) -> ModelSpec:
+    """A few-layer model with the 27B head geometry (hd 256, GVA 3:1) for kernel / engine tests. ``mult`` multiplies every
+    head count (2: divisible by a tensor-parallel world of 4, with 2 kv heads replicated over pairs of ranks)."""
+    return ModelSpec(name="test-hybrid", vocab=vocab, hidden=hidden, inter=2 * hidden, n_layers=n_layers, hq=6 * mult, hkv=mult,
+                     hd=256, rotary_dim=64, rope_theta=1e7, nk=2 * mult, kd=128, nv=6 * mult, vd=128)
 
 
 PRESETS = {

@@ -180,6 +180,108 @@ class VisionTower:
         return grid[0] * grid[1] * grid[2] // (self.spec.merge ** 2)
 
 
+class VisionTowerKernels:
+    """The tower on this package's own kernels: every matrix product on the dense tcgen05 GEMM (bf16 operands), everything
+    between them one fused pass each (``csrc/vision.cu``: LayerNorm, bias + GELU / residual epilogues, bilinear position
+    resampling, 2-D rotary, non-causal tensor-core attention per image). Weights are converted once: bf16 matrices with the k
+    dimension padded to a multiple of 64 (the GEMM's tile), fp32 vectors. Same interface and results (to bf16 rounding) as
+    ``VisionTower``; several images run as one batch of segments."""
+
+    def __init__(self, spec: VisionSpec, weights: dict | None = None, device="cuda"):
+        from ..ops import kernels as K
+
+        _bind_vision(K)
+        self.spec, self.device = spec, torch.device(device)
+        w = weights or init_vision_weights(spec)
+        self.inter_p = (spec.inter + 63) // 64 * 64
+        self.m, self.v = {}, {}
+        for k, t in w.items():
+            t = t.float()
+            if t.dim() == 2 and k != "pos_embed":
+                if k.endswith("fc1.weight") and "merger" not in k:
+                    t = torch.cat([t, torch.zeros(self.inter_p - spec.inter, t.shape[1])])          # extra rows: gelu(0) = 0
+                if k.endswith("fc2.weight") and "merger" not in k:
+                    t = torch.cat([t, torch.zeros(t.shape[0], self.inter_p - spec.inter)], dim=1)   # and they meet zero columns
+                self.m[k] = t.to(self.device, torch.bfloat16).contiguous()
+            else:
+                if k.endswith("fc1.bias") and "merger" not in k:
+                    t = torch.cat([t, torch.zeros(self.inter_p - spec.inter)])
+                self.v[k] = t.to(self.device).contiguous()
+
+    def _gemm(self, x, name, out=None):
+        from ..ops import gemm_tc
+
+        w = self.m[name]
+        out = torch.empty(x.shape[0], w.shape[0], dtype=torch.bfloat16, device=self.device) if out is None else out
+        return gemm_tc.f16_gemm(x, w, out)
+
+    @torch.no_grad()
+    def forward_many(self, images: list) -> list:
+        """``images``: [(patches [n_i, patch_dim], (t, gh, gw))]; returns the merged embeddings of each, bf16."""
+        from ..ops import kernels as K
+
+        sp, dev, st = self.spec, self.device, K.stream
+        C, hd = sp.hidden, sp.head_dim
+        x_in = torch.cat([p.to(dev, torch.bfloat16) for p, _ in images]).contiguous()
+        n = x_in.shape[0]
+        offs = [0]
+        for p, _ in images:
+            offs.append(offs[-1] + p.shape[0])
+        seg = torch.tensor(offs, dtype=torch.int32, device=dev)
+        bf = lambda *s: torch.empty(*s, dtype=torch.bfloat16, device=dev)
+        x, y, qkv, att, mid = bf(n, C), bf(n, C), bf(n, 3 * C), bf(n, C), bf(n, self.inter_p)
+        self._gemm(x_in, "patch_embed.weight", x)
+        K.call("owl_vis_bias_act", K.ptr(x), C, K.ptr(self.v["patch_embed.bias"]), None, 0, K.ptr(x), C, n, C, 0, st())
+        for i, (_, (_, gh, gw)) in enumerate(images):
+            K.call("owl_vis_pos_embed", x.data_ptr() + offs[i] * C * 2, C, K.ptr(self.v["pos_embed"]), sp.pos_grid, gh, gw, sp.merge, C, st())
+        for li in range(sp.depth):
+            b = f"blocks.{li}."
+            K.call("owl_vis_layernorm", K.ptr(x), C, K.ptr(self.v[b + "norm1.weight"]), K.ptr(self.v[b + "norm1.bias"]), K.ptr(y), C,
+                   n, C, sp.eps, st())
+            self._gemm(y, b + "qkv.weight", qkv)
+            K.call("owl_vis_bias_act", K.ptr(qkv), 3 * C, K.ptr(self.v[b + "qkv.bias"]), None, 0, K.ptr(qkv), 3 * C, n, 3 * C, 0, st())
+            for i, (_, (_, gh, gw)) in enumerate(images):
+                K.call("owl_vis_rope", K.ptr(qkv), sp.heads, hd, offs[i], gh, gw, sp.merge, st())
+            K.call("owl_vis_attn", K.ptr(qkv), K.ptr(att), n, sp.heads, hd, K.ptr(seg), len(images), st())
+            self._gemm(att, b + "proj.weight", y)
+            K.call("owl_vis_bias_act", K.ptr(y), C, K.ptr(self.v[b + "proj.bias"]), K.ptr(x), C, K.ptr(x), C, n, C, 0, st())
+            K.call("owl_vis_layernorm", K.ptr(x), C, K.ptr(self.v[b + "norm2.weight"]), K.ptr(self.v[b + "norm2.bias"]), K.ptr(y), C,
+                   n, C, sp.eps, st())
+            self._gemm(y, b + "fc1.weight", mid)
+            K.call("owl_vis_bias_act", K.ptr(mid), self.inter_p, K.ptr(self.v[b + "fc1.bias"]), None, 0, K.ptr(mid), self.inter_p, n,
+                   self.inter_p, 1, st())
+            self._gemm(mid, b + "fc2.weight", y)
+            K.call("owl_vis_bias_act", K.ptr(y), C, K.ptr(self.v[b + "fc2.bias"]), K.ptr(x), C, K.ptr(x), C, n, C, 0, st())
+        K.call("owl_vis_layernorm", K.ptr(x), C, K.ptr(self.v["merger.norm.weight"]), K.ptr(self.v["merger.norm.bias"]), K.ptr(y), C, n,
+               C, sp.eps, st())
+        mh = C * sp.merge * sp.merge
+        ym = y.view(n // (sp.merge * sp.merge), mh)
+        h1 = self._gemm(ym, "merger.fc1.weight")
+        K.call("owl_vis_bias_act", K.ptr(h1), mh, K.ptr(self.v["merger.fc1.bias"]), None, 0, K.ptr(h1), mh, h1.shape[0], mh, 2, st())
+        out = self._gemm(h1, "merger.fc2.weight")
+        K.call("owl_vis_bias_act", K.ptr(out), sp.out_hidden, K.ptr(self.v["merger.fc2.bias"]), None, 0, K.ptr(out), sp.out_hidden,
+               out.shape[0], sp.out_hidden, 0, st())
+        m2 = sp.merge * sp.merge
+        return [out[offs[i] // m2:offs[i + 1] // m2] for i in range(len(images))]
+
+    def forward(self, patches: torch.Tensor, grid: tuple[int, int, int]) -> torch.Tensor:
+        return self.forward_many([(patches, grid)])[0]
+
+    def n_tokens(self, grid: tuple[int, int, int]) -> int:
+        return grid[0] * grid[1] * grid[2] // (self.spec.merge ** 2)
+
+
+def _bind_vision(K) -> None:
+    import ctypes
+
+    P, I, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+    K.register("owl_vis_layernorm", [P, I, P, P, P, I, I, I, F, P])
+    K.register("owl_vis_bias_act", [P, I, P, P, I, P, I, I, I, I, P])
+    K.register("owl_vis_pos_embed", [P, I, P, I, I, I, I, I, P])
+    K.register("owl_vis_rope", [P, I, I, I, I, I, I, P])
+    K.register("owl_vis_attn", [P, P, I, I, I, P, I, P])
+
+
 # ---- text side --------------------------------------------------------------------------------
 def scatter_images(embeds: torch.Tensor, ids: torch.Tensor, image_pad_id: int, image_embeds: list[torch.Tensor]) -> torch.Tensor:
     """Overwrite the rows of ``embeds`` whose token is the image pad with the images' merged embeddings, in order."""

@@ -405,7 +405,7 @@ def attn_gemm_prefill(q, k_pool, v_pool, scales, bt_row, pos0: int, t: int, hq: 
     ctx = pos0 + t
     ctx_pad = (ctx + 63) // 64 * 64
     fmt = 2 if k_pool.dtype == torch.float16 else (1 if scales is not None else 0)
-    kb, vt, s, o = ws["k"][:hkv * ctx_pad * hd], ws["vt"][:hkv * hd * ctx_pad], ws["s"][:t * ctx_pad], ws["o"][:t * hq * hd]
+    kb, vt, o = ws["k"][:hkv * ctx_pad * hd], ws["vt"][:hkv * hd * ctx_pad], ws["o"][:t * hq * hd]
     call("owl_kv_gather", ptr(k_pool), ptr(v_pool), ptr(scales[0]) if scales else None, ptr(scales[1]) if scales else None, fmt,
          ptr(bt_row), ctx, ctx_pad, hkv, hd, ptr(kb), ptr(vt), stream())
     gq, st = hq // hkv, stream()
@@ -418,6 +418,9 @@ def attn_gemm_prefill(q, k_pool, v_pool, scales, bt_row, pos0: int, t: int, hq: 
         call("owl_attn_tc", ptr(qg), ptr(kb), ptr(vt), ptr(og), t * gq, gq, hkv, ctx_pad, pos0, float(scale), st)
         call("owl_attn_gate", ptr(og), ptr(qraw), ldq, hd, ptr(out), t, hq * hd, _is_f16(out), gq, None, st)
         return
+    if ws["s"] is None:
+        ws["s"] = torch.zeros(ws["t"] * gq * ws["ctx"], dtype=torch.float16, device=q.device)
+    s = ws["s"][:t * ctx_pad]
     if ws.get("grouped", True):
         # the gq q heads of a kv head as consecutive rows: one GEMM pair per kv head, K and V^T read once for all of them
         qg, og = ws["qg"][:hq * t * hd], ws["og"][:hq * t * hd]
@@ -450,7 +453,8 @@ def attn_gemm_ws(device, t: int, max_ctx: int, hq: int, hkv: int, hd: int) -> di
     cp = (max_ctx + 63) // 64 * 64
     return {"k": torch.zeros(hkv * cp * hd, dtype=torch.bfloat16, device=device),
             "vt": torch.zeros(hkv * hd * cp, dtype=torch.float16, device=device),
-            "s": torch.zeros(t * (hq // hkv) * cp, dtype=torch.float16, device=device),
+            # fp16 scores of the GEMM form (rows x keys): the fused kernel keeps them in tensor memory and needs no such buffer
+            "s": None if ATTN_FUSED and hd == 256 else torch.zeros(t * (hq // hkv) * cp, dtype=torch.float16, device=device),
             "o": torch.zeros(t * hq * hd, dtype=torch.bfloat16, device=device),
             "qg": torch.zeros(t * hq * hd, dtype=torch.bfloat16, device=device),
             "og": torch.zeros(t * hq * hd, dtype=torch.bfloat16, device=device),

@@ -59,6 +59,11 @@ _T = [
     KernelSpec("owl_gemm_nvfp4_status", "gemm_nvfp4.cu", "status", capture=False),
     KernelSpec("owl_attn_tc", "attn_tc.cu", "attn", gen="tcgen05+tmem+tma"),
     KernelSpec("owl_attn_tc_status", "attn_tc.cu", "status", capture=False),
+    KernelSpec("owl_vis_layernorm", "vision.cu", "vision"),
+    KernelSpec("owl_vis_bias_act", "vision.cu", "vision"),
+    KernelSpec("owl_vis_pos_embed", "vision.cu", "vision"),
+    KernelSpec("owl_vis_rope", "vision.cu", "vision"),
+    KernelSpec("owl_vis_attn", "vision.cu", "vision", gen="mma.sync"),
     KernelSpec("owl_w4_dequant", "dequant.cu", "load"),
     KernelSpec("owl_quant_e4m3_rows", "dequant.cu", "load"),
     KernelSpec("owl_kv_pages_gather", "kvmove.cu", "store"),
@@ -145,7 +150,9 @@ def cross_check() -> list[str]:
     """Mismatches between the sources, this table and the ctypes signatures (empty = consistent)."""
     from . import kernels as K
     from . import gemm_tc, nvfp4_tc  # noqa: F401  (register their signatures)
-    from ..models import dflash2  # noqa: F401
+    from ..models import dflash2, vision  # noqa: F401
+
+    vision._bind_vision(K)
     from ..parallel import symm  # noqa: F401
     from ..store import select
 

@@ -63,4 +63,4 @@ def test_all_gather_gated_gemm_unwinds_when_its_tiles_never_arrive():
 
 def test_status_words_are_all_readable_and_clean():
     st = K.all_status()
-    assert set(st) == {"skinny", "fma", "stream_tc", "gemm", "gemm_dense", "comm"} and not any(st.values()), st
+    assert set(st) == {"skinny", "fma", "stream_tc", "gemm", "gemm_dense", "gemm_nvfp4", "attn_tc", "comm"} and not any(st.values()), st

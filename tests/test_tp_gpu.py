@@ -57,6 +57,11 @@ def _leave(comm, runners=()):
     dist.destroy_process_group()
 
 
+def _mult() -> int:
+    """Head-count multiplier of the test model: a world of 4 needs head counts divisible by 4."""
+    return 2 if int(os.environ.get("WORLD_SIZE", "1")) >= 4 else 1
+
+
 def _run(target, world, args=(), timeout=240):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
@@ -64,12 +69,25 @@ def _run(target, world, args=(), timeout=240):
     procs = [ctx.Process(target=target, args=(r, world, port, q) + tuple(args)) for r in range(world)]
     for p in procs:
         p.start()
-    res = []
+    import queue as _q
+    import time
+
+    res, t_end = [], time.monotonic() + timeout
     try:
-        res = sorted([q.get(timeout=timeout) for _ in procs], key=lambda x: x[0])
+        while len(res) < world:
+            try:
+                res.append(q.get(timeout=2.0))
+            except _q.Empty:
+                # a rank that died will never report: fail now instead of waiting out the whole limit
+                dead = [p.exitcode for p in procs if p.exitcode not in (None, 0)]
+                assert not dead, f"rank processes exited with {dead}"
+                assert time.monotonic() < t_end, "timed out waiting for the ranks"
+        res.sort(key=lambda x: x[0])
     finally:
         for p in procs:
-            p.join(timeout=60)
+            p.join(timeout=30)
+            if p.is_alive():
+                p.kill()
     assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
     return res
 
@@ -79,7 +97,7 @@ def _model(rank, world, dev, comm, mode, n_layers=4):
     from owl_engine_b200.models.reference import init_weights
     from owl_engine_b200.models.spec import test_hybrid as make_spec
 
-    full = make_spec(n_layers=n_layers, vocab=512)
+    full = make_spec(n_layers=n_layers, vocab=512, mult=_mult())
     dense = init_weights(full, seed=3, std=0.05)
     spec = full.sharded(rank, world) if world > 1 else full
     hw, _ = H.weights_from_dense(spec, dense, dev, vocab_split=(world > 1 and mode in ("fused", "push")))
@@ -258,7 +276,7 @@ def _worker_sp(rank, world, port, q):
     comm = TpComm.from_env("fused", hidden=256, big_elems=256 * 256)
     dev = comm.device
     assert comm.proof["ok"] and "sp_gemm" in comm.proof and comm.symm is not None, comm.proof
-    full = make_spec(n_layers=4, vocab=512)
+    full = make_spec(n_layers=4, vocab=512, mult=_mult())
     dense = init_weights(full, seed=3, std=0.05)
     spec = full.sharded(rank, world)
     hw, _ = H.weights_from_dense(spec, dense, dev, vocab_split=True)
