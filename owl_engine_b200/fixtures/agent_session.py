@@ -45,6 +45,9 @@ def main() -> None:
     ap.add_argument("--image-turn", type=int, default=2)
     ap.add_argument("--drop-turn", type=int, default=5)
     ap.add_argument("--patches", type=int, default=1024)
+    ap.add_argument("--churn", type=int, default=0,
+                    help="tokens of an unrelated prompt served between the session's end and the second session: with a device "
+                         "pool smaller than both, the first session's published blocks move to the host tier and to disk")
     ap.add_argument("--layers", type=int, default=None)
     ap.add_argument("--comm", default="fused")
     a = ap.parse_args()
@@ -162,6 +165,12 @@ def main() -> None:
     facts_live = eng.rel.facts()
     if "agent" in re_.parked:
         re_._release_parked("agent", publish=True)           # the session ends: its exact prefix becomes content-addressable
+    churn = None
+    if a.churn > 0:
+        _, churn = run_turn(rnd(a.churn), "other")
+        if "other" in re_.parked:
+            re_._release_parked("other", publish=True)
+        churn["tiers"] = {k: v for k, v in eng.rel.facts().items() if k != "last_verdict"}
     # a second session on the same first prompt: adopted blocks, recall from the lower tiers, time to first token
     prompt2 = prompt + rnd(a.append)
     rec0, hits0 = eng.rel.recalled, eng.prefix_hits
@@ -171,6 +180,7 @@ def main() -> None:
            "tp": world, "quant": a.quant, "prefill_gemm": a.prefill_gemm, "kv_pool_gb": a.kv_gb,
            "kv_pages": cfg.n_pages, "page_bytes": page_bytes, "vision_tower_ms": round(tower_ms, 1), "turns": turns,
            "tiers_after_session": {k: v for k, v in facts_live.items() if k != "last_verdict"},
+           "churn_session": churn,
            "second_session": {**facts2, "recalled_blocks": recalled, "prefix_hits": eng.prefix_hits - hits0},
            "tiers_final": {k: v for k, v in eng.rel.facts().items() if k != "last_verdict"}}
     status = K.all_status()

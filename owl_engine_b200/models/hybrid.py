@@ -440,8 +440,10 @@ class HybridRunner:
         if w.layout == "nvfp4":
             self._gemv_nvfp4(w, xp, xs, out, m, residual, epi, ldo)
             return
+        # (not under uniform_rows: a speculating engine needs the same arithmetic for every row count, and the dense product
+        # rounds differently from the integer arm that plain steps of a few rows use)
         if m >= self.BATCH_GEMM_FROM and self.prefill_gemm in ("tcr", "tc8r") and w.layout == "slice" and w.k % 128 == 0 \
-                and epi in (K.EPI_STORE, K.EPI_RESIDUAL, K.EPI_SILU_MUL):
+                and epi in (K.EPI_STORE, K.EPI_RESIDUAL, K.EPI_SILU_MUL) and not self.uniform_rows:
             self._gemv_dense16(w, xp, xs, out, m, residual, epi, ldo)
             return
         if w.layout != "block":
@@ -582,6 +584,9 @@ class HybridRunner:
         if self.attn_splits:
             return self.attn_splits
         pages = max(1, (ctx_hint + PAGE - 1) // PAGE)
+        if self.uniform_rows:
+            b = 8        # a speculating engine: the split of the keys (and with it the order of the partial sums) must not
+                         # depend on how many sequences share the step, or batched verify rows round differently from plain ones
         want = max(1, (2 * 148) // max(1, b * self.spec.hkv))
         return max(1, min(self.max_splits, want, (pages + 3) // 4))
 

@@ -103,6 +103,8 @@ class PrefillPipe:
     def own_rows(self, t: int) -> torch.Tensor:
         """Global row numbers of the rows this rank owns, in local order (padded tiles clipped to t)."""
         tiles = (t + self.TILE - 1) // self.TILE
+        if self.rank >= tiles:                                # a chunk with fewer row tiles than ranks: nothing to own
+            return torch.empty(0, dtype=torch.int64, device=self.device)
         mine = torch.arange(self.rank, tiles, self.world)
         rows = (mine[:, None] * self.TILE + torch.arange(self.TILE)[None]).reshape(-1)
         return rows.to(self.device)

@@ -126,6 +126,11 @@ def build_spec_factory(cfg: C.OwlConfig):
         from ..models.mtp import MtpHead
 
         lookup = LookupDraft(sp["lookup_nmin"], sp["lookup_nmax"]) if sp["lookup"] else None
+        if sp["kind"] in ("mtp", "dflash2") and getattr(engine, "comm", None) is not None:
+            # the draft models are not tensor-parallel: with them in the loop a forced-acceptance run at 4 ranks did not
+            # reproduce plain decoding, so the profile is refused instead of served wrong (lookup drafting works at any size)
+            raise ValueError(f"[spec] kind = {sp['kind']!r} is not available under tensor parallelism; use lookup drafting "
+                             "or serve the profile on one GPU")
         if sp["kind"] == "mtp":
             weights = None
             if sp["draft_path"]:
