@@ -18,6 +18,7 @@ import json
 from dataclasses import dataclass
 from pathlib import Path
 
+import numpy as np
 import torch
 
 from ..models import hybrid as H
@@ -103,8 +104,51 @@ def gguf_name(hf: str) -> str:
 
 
 class GgufProvider:
+    """Tensors of a GGUF file under their HF names, in the model's (grouped) value-head order: converted checkpoints store the
+    gated-delta-net's value heads tiled (``formats/gguf_shard.py``), which is undone here when the tensor is read, on the raw
+    blocks for quantised types. ``general`` metadata key ``owl.vhead_order = "grouped"`` marks a file that is in model order
+    already. ``read_shard`` reads one rank's window of a tensor without materialising the rest."""
+
     def __init__(self, f: gguf.GgufFile):
         self.f = f
+        self.dims = None
+        self.tiled = str(f.meta.get("owl.vhead_order", "tiled")) != "grouped"
+
+    def set_dims(self, spec) -> None:
+        from .gguf_shard import GdnDims
+
+        self.dims = GdnDims(spec.nk, spec.nv, spec.kd, spec.vd)
+
+    def _plan(self, g: str, sel=None):
+        """Read plan of GGUF tensor ``g`` (None: take it whole, as stored)."""
+        from . import gguf_shard as S
+
+        if self.dims is None or (not self.tiled and sel is None):
+            return None
+        t = self.f.tensors[g]
+        shape = tuple(t.shape) if len(t.shape) == 2 else (int(np.prod(t.shape)), 1) if len(t.shape) == 1 else None
+        if shape is None or S.role(g, sel) == S.REPLICATE:
+            return None
+        dims = self.dims if self.tiled else S.GdnDims(self.dims.nk, self.dims.nk, self.dims.kd, self.dims.vd * self.dims.vpr)
+        return S.plan(g, shape, gguf.BLOCK.get(t.type, (1, 0))[0], dims, sel)
+
+    def read_shard(self, name: str, sel) -> torch.Tensor:
+        """Dequantised window of rank ``sel.rank`` (value heads in grouped order): equals the matching block of ``dense``."""
+        from . import gguf_shard as S
+
+        g = gguf_name(name)
+        t = self.f.tensors[g]
+        p = self._plan(g, sel)
+        if p is None:
+            return self.f.dequant(g)
+        be, bb = gguf.BLOCK.get(t.type, (1, 0))
+        if be == 1:
+            x = self.f.dequant(g)
+            x = x.reshape(x.shape[0], -1) if x.dim() > 1 else x
+            return torch.from_numpy(np.ascontiguousarray(S.apply_dense(x.numpy(), p)))
+        shape = tuple(t.shape)
+        raw = S.apply_raw(self.f.raw(g), shape, be, bb, p)
+        return torch.from_numpy(gguf.dequantize(raw.reshape(-1), t.type, p.shape[0] * p.shape[1])).view(*p.shape)
 
     def has(self, name: str) -> bool:
         try:
@@ -113,7 +157,15 @@ class GgufProvider:
             return False
 
     def dense(self, name: str) -> torch.Tensor:
-        t = self.f.dequant(gguf_name(name))
+        from . import gguf_shard as S
+
+        g = gguf_name(name)
+        t = self.f.dequant(g)
+        p = self._plan(g)
+        if p is not None:
+            shp = t.shape
+            x = S.apply_dense(t.reshape(shp[0], -1).numpy() if t.dim() > 1 else t.numpy(), p)
+            t = torch.from_numpy(np.ascontiguousarray(x)).view(*shp)
         if name.endswith(_PLUS_ONE_NORMS):
             t = t - 1.0                     # GGUF stores gamma with the +1 baked in; kernels apply (1 + w)
         if name.endswith("A_log"):
@@ -121,12 +173,30 @@ class GgufProvider:
         return t
 
     def w4(self, name: str) -> Q.W4Canonical:
+        from . import gguf_shard as S
+
         g = gguf_name(name)
         t = self.f.tensors[g]
         if t.type == "Q4_K":
-            return gguf.q4k_to_w4(self.f.raw(g), t.shape[0], t.shape[1])
+            raw = self.f.raw(g)
+            try:
+                p = self._plan(g)
+            except S.ShardError:
+                # a 256-element super-block spans two value heads that the tiled order separates (ssm_out with 128-wide
+                # heads): the columns are reordered after the conversion, on the 32-element groups of the int4 form, which is
+                # just as exact
+                p = None
+                c = gguf.q4k_to_w4(raw, t.shape[0], t.shape[1])
+                sub = S.plan(g, tuple(t.shape), c.group, self.dims, None)
+                atoms = torch.from_numpy(np.asarray(sub.col_atoms))
+                cols = torch.from_numpy(S.head_rows(np.asarray(sub.col_atoms), c.group))
+                return Q.W4Canonical(c.q[:, cols].contiguous(), c.scales[:, atoms].contiguous(), c.zeros[:, atoms].contiguous(),
+                                     c.group)
+            if p is not None:
+                raw = S.apply_raw(raw, tuple(t.shape), *gguf.BLOCK["Q4_K"], p).reshape(-1)
+            return gguf.q4k_to_w4(raw, t.shape[0], t.shape[1])
         log.warn("load.gguf", f"{g}: {t.type} is dequantised and re-quantised to int4 g32")
-        return Q.quantize_w4(self.f.dequant(g).float(), 32)
+        return Q.quantize_w4(self.dense(name).float(), 32)
 
 
 @dataclass
@@ -299,4 +369,6 @@ def load_model(path: str | Path, device, spec: ModelSpec | None = None, rank: in
             from ..models.config_json import spec_from_hf_config
 
             spec = spec_from_hf_config(json.loads((Path(path) / "config.json").read_text()))
+    if kind == "gguf":
+        provider.set_dims(spec)
     return spec, build_weights(spec, provider, device, rank, world, **kw)

@@ -259,3 +259,75 @@ def test_nvfp4_checkpoint_source_and_row_surgery():
     gu = L.interleave_rows(prov.w4("g.weight"), prov.w4("u.weight"))
     from owl_engine_b200.ops import quant as Q
     assert torch.allclose(deq(gu), Q.interleave_gate_up(dense["g.weight"], dense["u.weight"]), rtol=1e-6, atol=1e-8)
+
+
+def test_gguf_shard_plans_keep_the_contiguous_block_invariant():
+    """What rank r reads equals a contiguous block of the fully loaded tensor in grouped head order, for every role; what cannot
+    be cut exactly is refused."""
+    from owl_engine_b200.formats import gguf_shard as S
+
+    dims = S.GdnDims(nk=4, nv=12, kd=8, vd=32)
+    order = S.grouped_head_order(dims)
+    assert sorted(order.tolist()) == list(range(12))
+    assert order[:3].tolist() == [0, 4, 8]                  # the three value heads of key head 0 sit 4 apart in the file
+    rng = np.random.default_rng(0)
+    inv = np.argsort(order)
+
+    def tiled_rows(a, width):       # grouped -> file order
+        return a[S.head_rows(inv, width)]
+
+    cases = {
+        "blk.0.ffn_up.weight": (rng.standard_normal((64, 96)).astype(np.float32), None),
+        "blk.0.attn_gate.weight": (rng.standard_normal((12 * 32, 64)).astype(np.float32), "rows_head"),
+        "blk.0.ssm_a": (rng.standard_normal((12, 1)).astype(np.float32), "rows_head"),
+        "blk.0.attn_qkv.weight": (rng.standard_normal((2 * 32 + 12 * 32, 64)).astype(np.float32), "segs"),
+        "blk.0.ffn_down.weight": (rng.standard_normal((16, 128)).astype(np.float32), None),
+        "blk.0.ssm_out.weight": (rng.standard_normal((16, 12 * 32)).astype(np.float32), "cols_head"),
+        "blk.0.attn_norm.weight": (rng.standard_normal((64, 1)).astype(np.float32), None),
+    }
+    for key, (full, kind) in cases.items():
+        if kind == "rows_head":
+            filed = tiled_rows(full, full.shape[0] // 12)
+        elif kind == "segs":
+            filed = np.concatenate([full[:64], tiled_rows(full[64:], 32)])
+        elif kind == "cols_head":
+            filed = full[:, S.head_rows(inv, 32)]
+        else:
+            filed = full
+        whole = S.apply_dense(filed, S.plan(key, full.shape, 1, dims, None))
+        assert np.array_equal(whole, full), key
+        for world in (2, 4):
+            parts = [S.apply_dense(filed, S.plan(key, full.shape, 1, dims, S.ShardSel(r, world))) for r in range(world)]
+            r = S.role(key)
+            if r == S.REPLICATE:
+                assert all(np.array_equal(p, full) for p in parts)
+            elif r in (S.COLS, S.COLS_HEAD):
+                assert np.array_equal(np.concatenate(parts, axis=1), full), (key, world)
+            elif r == S.SEGS:
+                kq = 32
+                for seg, (lo, hi) in enumerate([(0, kq), (kq, 2 * kq), (2 * kq, full.shape[0])]):
+                    n = (hi - lo) // world
+                    got = []
+                    for p in parts:
+                        o = [0, kq // world, 2 * kq // world][seg]
+                        got.append(p[o:o + n])
+                    assert np.array_equal(np.concatenate(got), full[lo:hi]), (key, world, seg)
+            else:
+                assert np.array_equal(np.concatenate(parts), full), (key, world)
+    # raw blocks: a column window of a block-quantised tensor is a window of blocks
+    w = (rng.standard_normal((8, 512)) * 0.05).astype(np.float32)
+    raw = gguf.quantize_q8_0(w)
+    pl = S.plan("blk.0.ffn_down.weight", (8, 512), 32, dims, S.ShardSel(1, 2))
+    cut = S.apply_raw(raw, (8, 512), 32, 34, pl)
+    assert np.array_equal(gguf.dequantize(cut.reshape(-1), "Q8_0", 8 * 256).reshape(8, 256),
+                          gguf.dequantize(raw, "Q8_0", 8 * 512).reshape(8, 512)[:, 256:])
+    # refusals
+    with pytest.raises(S.ShardError):
+        S.plan("blk.0.ffn_up.weight", (66, 96), 1, dims, S.ShardSel(0, 4))            # rows not divisible
+    with pytest.raises(S.ShardError):
+        S.plan("blk.0.ffn_down.weight", (16, 96), 32, dims, S.ShardSel(0, 2))         # cut inside a block
+    with pytest.raises(S.ShardError):
+        S.plan("blk.0.ssm_out.weight", (16, 12 * 32), 256, dims, None)                # a block spans two heads
+    with pytest.raises(S.ShardError):
+        S.plan("blk.0.ssm_a", (12, 1), 1, S.GdnDims(4, 12, 8, 32), S.ShardSel(0, 5))  # heads not divisible
+    assert S.role("output.weight") == S.REPLICATE and S.role("output.weight", S.ShardSel(0, 2, head_split=True)) == S.ROWS

@@ -2,6 +2,7 @@
 import json
 
 import numpy as np
+import pytest
 import torch
 
 from owl_engine_b200.formats import awq, gguf, loader, safetensors as st
@@ -62,7 +63,28 @@ def test_tp_shards_tile_the_full_weight():
     assert torch.equal(torch.cat([p.q for p in ps], dim=0), f.q)
 
 
-def test_gguf_q4k_file_loads(tmp_path):
+def _to_file_order(g: str, a: np.ndarray, spec) -> np.ndarray:
+    """What the converter does to a tensor of the gated-delta-net: value heads from the model's grouped order to the tiled one."""
+    from owl_engine_b200.formats import gguf_shard as S
+
+    dims = S.GdnDims(spec.nk, spec.nv, spec.kd, spec.vd)
+    inv = np.argsort(S.grouped_head_order(dims))            # file position f holds grouped head inv[f]
+    name = g.split(".")[2]
+    r = S.role(g)
+    if r == S.ROWS_HEAD:
+        w = a.shape[0] // spec.nv
+        return a[S.head_rows(inv, w)]
+    if r == S.SEGS:
+        kq = spec.nk * spec.kd
+        return np.concatenate([a[:2 * kq], a[2 * kq:][S.head_rows(inv, spec.vd)]])
+    if r == S.COLS_HEAD:
+        return a[:, S.head_rows(inv, spec.vd)]
+    return a
+
+
+@pytest.mark.parametrize("order", ["grouped", "tiled"])
+def test_gguf_q4k_file_loads(tmp_path, order):
+    """``tiled``: the file stores the value heads the way the llama.cpp converter writes them; the loader undoes it."""
     spec = make_spec(n_layers=4, vocab=512)
     dense = init_weights(spec, seed=3, std=0.05)
     tensors = {}
@@ -70,6 +92,9 @@ def test_gguf_q4k_file_loads(tmp_path):
     for k, v in dense.items():
         g = loader.gguf_name(k)
         a = v.float().numpy()
+        a = np.ascontiguousarray(a.reshape(a.shape[0], -1) if a.ndim == 3 else a)
+        if order == "tiled" and g.startswith("blk."):
+            a = np.ascontiguousarray(_to_file_order(g, a, spec))
         if k.endswith(loader._PLUS_ONE_NORMS):
             a = a + 1.0
         if k in lin:
@@ -81,6 +106,8 @@ def test_gguf_q4k_file_loads(tmp_path):
             "qwen35.feed_forward_length": spec.inter, "qwen35.block_count": spec.n_layers,
             "qwen35.attention.head_count": spec.hq, "qwen35.attention.head_count_kv": spec.hkv,
             "qwen35.ssm.group_count": spec.nk, "qwen35.ssm.time_step_rank": spec.nv, "qwen35.vocab_size": spec.vocab}
+    if order == "grouped":
+        meta["owl.vhead_order"] = "grouped"
     gguf.write_gguf(tmp_path / "m.gguf", meta, tensors)
     got_spec, hw = loader.load_model(tmp_path / "m.gguf", "cpu")
     assert got_spec.hidden == spec.hidden and got_spec.nv == spec.nv and hw.group == 32
@@ -88,3 +115,15 @@ def test_gguf_q4k_file_loads(tmp_path):
     w = dense["model.layers.0.mlp.down_proj.weight"]
     assert ((c.dequant() - w).norm() / w.norm()) < 0.15
     torch.testing.assert_close(hw.layers[0].ln1.float(), dense["model.layers.0.input_layernorm.weight"], atol=1e-2, rtol=1e-2)
+    # a gated-delta-net layer's tensors come out in the model's head order whichever order the file uses
+    kind, prov, f = loader.open_source(tmp_path / "m.gguf")
+    prov.set_dims(spec)
+    for name in ("linear_attn.in_proj_z.weight", "linear_attn.out_proj.weight", "linear_attn.in_proj_qkv.weight"):
+        k = f"model.layers.0.{name}"
+        got = prov.w4(k).dequant()
+        assert ((got - dense[k]).norm() / dense[k].norm()) < 0.15, (order, name)
+    for name in ("linear_attn.A_log", "linear_attn.dt_bias", "linear_attn.in_proj_a.weight"):
+        k = f"model.layers.0.{name}"
+        if name.endswith("A_log"):
+            continue
+        torch.testing.assert_close(prov.dense(k).float().view(-1), dense[k].float().view(-1), atol=2e-2, rtol=2e-2)
