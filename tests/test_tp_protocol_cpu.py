@@ -73,6 +73,60 @@ def test_push_pull_pairing_with_two_alternating_sites(world):
 
 
 @pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_word_exchange_of_the_one_token_projections(world):
+    """The exchange inside the one-token projections: a producer stores, per pair of sums, ONE word (data, number of this
+    exchange) into slot [rank] of every rank's buffer of the call site -- words of one exchange land in any order and at any time
+    -- and reads the call site's sequence word without writing it; a consumer accepts a word only when its number matches,
+    adds the slots in rank order and advances the sequence word when its last "CTA" leaves. Two call sites alternate. Every
+    rank must compute the same sums from exactly this exchange's data, with stale words of the site's previous use in place."""
+    steps, n_words, n_ctas = 30, 6, 3
+    words = np.zeros((world, 2, world, n_words, 2), dtype=np.int64)      # [dst][site][src][word] = (data, number)
+    seq_word = np.zeros((world, 2), dtype=np.int64)                      # per rank, per call site
+    left = np.zeros((world, 2), dtype=np.int64)
+    sums = np.zeros((world, steps, n_words), dtype=np.int64)
+    lock = threading.Lock()
+
+    def rank(r):
+        rng = np.random.default_rng(100 + r)
+        for s in range(steps):
+            w = s & 1
+            number = seq_word[r][w] + 1                      # the producer only reads the word
+            order = rng.permutation(n_words * world)
+            for o in order:                                   # words reach the peers in any order
+                peer, i = divmod(int(o), n_words)
+                words[peer][w][r][i] = (1000 * (s + 1) + 10 * r + i, number)   # one atomic 8-byte store in the kernel
+            # the consumer kernel: several CTAs, each reads the word, polls, the last one to leave advances the word
+            want = seq_word[r][w] + 1
+            acc = np.zeros(n_words, dtype=np.int64)
+            for cta in range(n_ctas):
+                assert seq_word[r][w] + 1 == want             # nobody advanced it while CTAs of this grid still start
+                got = np.zeros(n_words, dtype=np.int64)
+                for src in range(world):
+                    for i in range(n_words):
+                        while True:
+                            d, n = words[r][w][src][i]
+                            if n == want:
+                                break
+                        got[i] += d
+                acc = got
+                with lock:
+                    left[r][w] += 1
+                    if left[r][w] == n_ctas:
+                        left[r][w] = 0
+                        seq_word[r][w] = want
+            sums[r][s] = acc
+    ts = [threading.Thread(target=rank, args=(r,)) for r in range(world)]
+    [t.start() for t in ts]
+    [t.join(120) for t in ts]
+    assert not any(t.is_alive() for t in ts)
+    for s in range(steps):
+        want = np.array([sum(1000 * (s + 1) + 10 * r + i for r in range(world)) for i in range(n_words)])
+        for r in range(world):
+            assert np.array_equal(sums[r][s], want), (r, s)
+    assert (seq_word == steps // 2).all()
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
 @pytest.mark.parametrize("t", [128, 300, 2048, 2049])
 def test_prefill_tile_ownership_is_a_partition(world, t):
     tiles = (t + 127) // 128
