@@ -100,3 +100,42 @@ def test_capture_limit_surfaces():
     e.prefill(sid)
     with pytest.raises(CaptureUnsupported):
         e.decode_step([sid])
+
+
+def test_http_server_end_to_end_on_the_cpu_face():
+    """The whole serving stack without a GPU: HTTP surface -> engine service thread -> RunningEngine -> engine on the CPU face.
+    Non-stream and SSE agree, the debug endpoints answer, an identical prompt is served from the prefix tree."""
+    import asyncio
+    import json
+
+    from owl_engine_b200.engine.service import EngineService
+    from owl_engine_b200.engine.tokenizer import ByteTokenizer
+    from owl_engine_b200.server.http import App, serve
+    from test_server_http import dechunk, request
+
+    svc = EngineService(lambda: Engine(cfg(n_pages=128), device="cpu"), max_batch=4)
+    client = svc.boot()
+    tok = ByteTokenizer()
+
+    async def main():
+        app = App(client, tok, "test-hybrid")
+        server = await serve(app, "127.0.0.1", 0)
+        port = server.sockets[0].getsockname()[1]
+        async with server:
+            body = {"messages": [{"role": "user", "content": "hello there, cpu face"}], "max_tokens": 12, "ignore_eos": True}
+            st, _, a = await request(port, "POST", "/v1/chat/completions", body)
+            assert st == 200
+            ra = json.loads(a)
+            assert ra["usage"]["completion_tokens"] == 12
+            st, _, b = await request(port, "POST", "/v1/chat/completions", {**body, "stream": True})
+            events = [l[6:] for l in dechunk(b).split("\n\n") if l.startswith("data: ")]
+            assert events[-1] == "[DONE]" and len(events) > 3
+            st, _, v = await request(port, "GET", "/debug/blocks")
+            assert st == 200 and "kv" in json.loads(v)
+            st, _, c = await request(port, "POST", "/v1/chat/completions", body)
+            rc = json.loads(c)
+            assert rc["choices"][0]["message"] == ra["choices"][0]["message"]
+    try:
+        asyncio.run(main())
+    finally:
+        assert svc.shutdown().code == 0
