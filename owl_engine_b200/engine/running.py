@@ -58,7 +58,7 @@ class Turn:
 
 class RunningEngine:
     def __init__(self, engine: Engine, max_batch: int = 8, on_full: str = "reject", spec_runner=None,
-                 park_sessions: bool = False, max_parked: int = 2, evict_pad_id: int = 0):
+                 park_sessions: bool = False, max_parked: int = 2, evict_pad_id: int = 0, prefill_every: int = 8):
         """``park_sessions``: a finished turn of a named session keeps its sequence alive (pages + GDN row) so that the next
         turn continues it: droppable segments the client removed are unlinked in place (leave-gap, ``engine/img_evict.py``) and
         only the new tokens are prefilled. At most ``max_parked`` sequences wait; the oldest is released (and published) when
@@ -67,7 +67,8 @@ class RunningEngine:
         self.park_sessions, self.max_parked, self.evict_pad_id = park_sessions, max_parked, evict_pad_id
         self.parked: dict = {}       # session -> (engine sequence id, PaddedSeq of everything in the sequence, tick)
         self.resumed = self.gap_drops = 0
-        self.sched = Scheduler(max_batch, engine.cfg.prefill_chunk, on_full, spec_batch=max(1, getattr(engine.cfg, "spec_rows", 1)))
+        self.sched = Scheduler(max_batch, engine.cfg.prefill_chunk, on_full, spec_batch=max(1, getattr(engine.cfg, "spec_rows", 1)),
+                               prefill_every=prefill_every)
         self.turns: dict[int, Turn] = {}
         self.reservations = B.Reservations()
         self._next = 0

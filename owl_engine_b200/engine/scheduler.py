@@ -44,12 +44,16 @@ IDLE = Step("idle")
 
 
 class PhaseSched:
-    def __init__(self):
+    def __init__(self, prefill_every: int = PREFILL_EVERY):
+        """``prefill_every``: decode beats between two prefill chunks while both phases have work (the reference's constant is
+        8, which protects the decoding turns' inter-token latency; 1 alternates, which gets queued prompts into the decode
+        batch soonest and is the throughput setting)."""
         self.decode_beats = 0
         self.rr = 0
+        self.prefill_every = max(1, int(prefill_every))
 
     def pick(self, prefilling: list, decoding: list) -> str:
-        if prefilling and (not decoding or self.decode_beats >= PREFILL_EVERY):
+        if prefilling and (not decoding or self.decode_beats >= self.prefill_every):
             self.decode_beats = 0
             return "prefill"
         if decoding:
@@ -59,10 +63,11 @@ class PhaseSched:
 
 
 class Scheduler:
-    def __init__(self, max_batch: int, prefill_chunk: int, on_full: str = "reject", spec_batch: int = 1):
+    def __init__(self, max_batch: int, prefill_chunk: int, on_full: str = "reject", spec_batch: int = 1,
+                 prefill_every: int = PREFILL_EVERY):
         self.max_batch, self.prefill_chunk, self.on_full = max_batch, prefill_chunk, on_full
         self.spec_batch = spec_batch       # decoding turns one speculative round may cover (the engine's scratch state rows)
-        self.phase = PhaseSched()
+        self.phase = PhaseSched(prefill_every)
 
     def admission(self, t: TurnView, free_pages: int, evictable: int, outstanding: int, pool_pages: int,
                   free_rows: int) -> str:

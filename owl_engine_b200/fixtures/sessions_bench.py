@@ -20,14 +20,14 @@ import torch
 
 
 def run_sessions(eng, n: int = 32, lo: int = 1024, hi: int = 8192, out: int = 256, max_batch: int = 32, seed: int = 7,
-                 breakdown: bool = False) -> dict:
+                 breakdown: bool = False, prefill_every: int = 8) -> dict:
     """``breakdown``: time every step kind (begin / prefill / decode) with a device synchronise after each step, which
     attributes the wall time but serialises host and device (the rates of such a run are not the headline)."""
     import queue
 
     from ..engine.running import RunningEngine, TurnOpts
 
-    re = RunningEngine(eng, max_batch=max_batch, on_full="queue")
+    re = RunningEngine(eng, max_batch=max_batch, on_full="queue", prefill_every=prefill_every)
     kinds: dict = {}
     if breakdown:
         for kind in ("begin", "prefill", "decode"):
@@ -72,7 +72,7 @@ def run_sessions(eng, n: int = 32, lo: int = 1024, hi: int = 8192, out: int = 25
     return {"sessions": n, "prompt_tokens": sum(lens), "output_tokens": n_tok, "seconds": round(dt, 3),
             "output_tok_s": round(n_tok / dt, 1), "total_tok_s": round((n_tok + sum(lens)) / dt, 1),
             "ttft_p50_s": round(ttft[len(ttft) // 2], 3) if ttft else None, "max_batch": max_batch,
-            "prefix_hits": eng.prefix_hits,
+            "prefix_hits": eng.prefix_hits, "prefill_every": prefill_every,
             **({"steps": {k: {"n": v[0], "ms_total": round(v[1] * 1e3, 1), "ms_avg": round(v[1] * 1e3 / v[0], 2),
                               "turns_avg": round(v[2] / v[0], 1)} for k, v in kinds.items()}} if breakdown else {})}
 
@@ -87,6 +87,7 @@ def main() -> None:
     ap.add_argument("--comm", default="fused")
     ap.add_argument("--prefill-gemm", default="tc")
     ap.add_argument("--layers", type=int, default=None)
+    ap.add_argument("--prefill-every", type=int, default=8, help="decode beats between prefill chunks (8: the latency policy; 1: throughput)")
     ap.add_argument("--breakdown", action="store_true", help="time each step kind (adds a device synchronise per step)")
     a = ap.parse_args()
     from ..engine.core import Engine, EngineConfig
@@ -102,7 +103,8 @@ def main() -> None:
                        max_seq=a.hi + a.out + 64, lm_head_int8=True, prefill_gemm=a.prefill_gemm, n_layers=a.layers,
                        quant="nvfp4" if a.quant == "nvfp4" else "w4a16", act_bits=8 if a.quant == "w4a8" else 15)
     eng = Engine(cfg, comm=comm)
-    res = run_sessions(eng, a.sessions, a.lo, a.hi, a.out, max_batch=min(32, a.sessions), breakdown=a.breakdown)
+    res = run_sessions(eng, a.sessions, a.lo, a.hi, a.out, max_batch=min(32, a.sessions), breakdown=a.breakdown,
+                       prefill_every=a.prefill_every)
     status = K.all_status()
     if comm is not None:
         res["seconds"] = round(comm.max_over_ranks(res["seconds"]), 3)
