@@ -169,6 +169,23 @@ def main() -> None:
     ttft_ms = (time.perf_counter() - t0) * 1e3
     if comm:
         ttft_ms = comm.max_over_ranks(ttft_ms)
+    # the same prompt length on the arm that keeps NO resident dense copy of the weights (dequantise once per call into a
+    # shared scratch, then the dense GEMM): what time to first token costs without the extra memory of "tcr" / "tc8r"
+    ttft_tc_ms = None
+    if args.prefill_gemm in ("tcr", "tc8r"):
+        eng.runner.prefill_gemm = "tc"
+        p3 = torch.randint(0, eng.spec.vocab, (args.prompt_len,), generator=g).tolist()
+        for timed in (False, True):
+            s3 = eng.add_sequence(p3 if timed else p3[::-1], reuse=False)
+            sync_all()
+            t0 = time.perf_counter()
+            eng.prefill(s3)
+            torch.cuda.synchronize()
+            ttft_tc_ms = (time.perf_counter() - t0) * 1e3
+            eng.free_sequence(s3, publish=False)
+        if comm:
+            ttft_tc_ms = comm.max_over_ranks(ttft_tc_ms)
+        eng.runner.prefill_gemm = args.prefill_gemm
 
     # ---- count our kernel launches per decode step ---------------------------------------
     launches = {"n": 0}
@@ -277,12 +294,14 @@ def main() -> None:
                        "comm": comm.mode if world > 1 else "none",
                        "comm_proof": (getattr(comm, "proof", {}).get("ok") if world > 1 else None),
                        "sp_prefill": bool(world > 1 and eng.runner._pipe() is not None), "cuda_graph": True, "decode_gemv": args.gemv,
-                       "prefill_gemm": args.prefill_gemm},
+                       "prefill_gemm": args.prefill_gemm,
+                       "resident_copies_gb": round(eng.ledger.by_class().get("resident copies", 0) / 1e9, 2)},
             "e2e": {"value": round(e2e_value, 2), "unit": "tokens/s",
                     "h2d_bytes_per_step": (eng.h2d_bytes - h2d0) // steps,
                     "d2h_bytes_per_step": (eng.d2h_bytes - d2h0) // steps,
                     "p50_itl_ms": round(itl[len(itl) // 2], 4), "ttft_ms": round(ttft_ms, 2),
-                    "ttft_first_call_ms": round(ttft_cold_ms, 2)},
+                    "ttft_first_call_ms": round(ttft_cold_ms, 2),
+                    "ttft_ms_without_resident_copies": None if ttft_tc_ms is None else round(ttft_tc_ms, 2)},
             "gpu_launches": launches_per_step * steps,
             "launches_per_step": launches_per_step,
             "clocks": clocks,
