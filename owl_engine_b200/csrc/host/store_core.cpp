@@ -11,6 +11,7 @@
 // Reference counterpart: crates/store/src/kv/{mod,tree,chain,slot}.rs, leg.rs (carriers), id.rs.
 #include <cstdint>
 #include <cstring>
+#include <cmath>
 #include <list>
 #include <unordered_map>
 #include <vector>
@@ -37,6 +38,8 @@ struct Node {
   int32_t dev_children;// children that are device resident
   std::list<uint64_t>::iterator lru_it;
   bool in_lru;
+  double crf;          // LRFU: combined recency / frequency value at crf_tick (every use adds 1, age halves it every 1/lambda ticks)
+  uint64_t crf_tick;
 };
 
 struct Store {
@@ -47,9 +50,16 @@ struct Store {
   std::list<uint64_t> lru;            // device-resident evictable candidates, front = oldest
   uint64_t tick = 0;
   uint64_t hits = 0, lookups = 0, evictions = 0, published = 0;
+  double lambda = -1.0;               // < 0: plain LRU order of the candidate list; >= 0: LRFU with this decay
+
+  // LRFU order without a clock: value(now) = crf * 2^(-lambda (now - crf_tick)), so log2(crf) + lambda * crf_tick orders
+  // the candidates the same way at every `now`.
+  double lrfu_key(const Node& n) const { return std::log2(n.crf > 0 ? n.crf : 1e-300) + lambda * (double)n.crf_tick; }
 
   void touch(Node& n) {
     n.last_use = ++tick;
+    n.crf = 1.0 + n.crf * std::exp2(-(lambda >= 0 ? lambda : 0.05) * (double)(tick - n.crf_tick));
+    n.crf_tick = tick;
     if (n.in_lru) { lru.erase(n.lru_it); n.in_lru = false; }
     maybe_enlist(n);
   }
@@ -67,6 +77,10 @@ struct Store {
 };
 
 }  // namespace
+
+// Victim order of owl_kv_evict: lambda < 0 = least recently used leaf first; lambda >= 0 = LRFU (0 = pure frequency,
+// large = recency only).
+API void owl_kv_set_policy(void* h, double lambda) { static_cast<Store*>(h)->lambda = lambda; }
 
 API void* owl_kv_new(int n_pages, int block_tokens) {
   Store* s = new Store();
@@ -182,6 +196,19 @@ API int owl_kv_evict(void* h, int need, int mode, int32_t* pages_out, uint64_t* 
   int got = 0;
   auto it = s->lru.begin();
   while (it != s->lru.end() && got < max && (int)s->free_pages.size() < need) {
+    if (s->lambda >= 0) {
+      // LRFU: the candidate of least combined value (a block hit often stays although it was not hit last)
+      auto best = s->lru.end();
+      double best_key = 0;
+      for (auto c = s->lru.begin(); c != s->lru.end(); ++c) {
+        const Node& cn = s->nodes.find(*c)->second;
+        if (s->refs[cn.page] > 1) continue;
+        const double k = s->lrfu_key(cn);
+        if (best == s->lru.end() || k < best_key) { best = c; best_key = k; }
+      }
+      if (best == s->lru.end()) break;
+      it = best;
+    }
     auto nit = s->nodes.find(*it);
     Node& nd = nit->second;
     if (s->refs[nd.page] > 1) { ++it; continue; }   // in use by a sequence

@@ -14,6 +14,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
+import numpy as np
 import torch
 
 from ..models import hybrid as H
@@ -34,6 +35,7 @@ class EngineConfig:
     n_snap_rows: int = 2           # extra state rows that hold prefix-boundary snapshots
     spec_rows: int = 1             # scratch state rows of speculative verify steps (= sequences per batched verify)
     host_cache_mb: int = 0         # pinned-host KV tier (0 = off)
+    pinned_segment_mb: int = 256   # the host tier's pinned memory is allocated in segments of this size
     disk_cache_mb: int = 0         # disk KV tier behind the host tier (0 = off)
     disk_dir: str = ""             # directory of the disk tier (block files + restart index)
     max_seqs: int = 8
@@ -53,9 +55,26 @@ class EngineConfig:
                                    # view of sink + recent + best-scoring blocks, re-selected at every block boundary
     kvmem_sink: int = 2
     kvmem_recent: int = 4
+    kvmem_query_tokens: int = 1    # the newest queries (one per decode step) a block is scored against; the score is their maximum
+    kvmem_recall_every: int = 1    # blocks written between two selections (the blocks written in between join the view as recent)
     recall_mode: str = "sync"      # recall of demoted prefix blocks: "sync" (host and disk), "host" (host only), "resident" (none)
     workspace_reserve_mb: int = 3072   # n_pages = 0: device memory the boot plan leaves for graphs, prefill workspace, scratch
     vocab_split: bool = True       # tensor parallel: each rank holds vocab / world lm_head rows and the winners are merged
+    attn_splits: int = 0           # split-KV factor of decode attention (0 = from the context length)
+    cuda_graph: bool = True        # False: steps launch their kernels eagerly (debugging; slower)
+    rope_yarn: tuple = None        # (factor, original_max, beta_fast, beta_slow, attention_factor): YaRN context extension
+    prefix_cache: bool = True      # False: nothing is looked up in or published to the prefix tree, no snapshots are taken
+    no_reclaim: bool = False       # diagnostic: cached blocks are never evicted under pressure (requests that do not fit fail)
+    evict_policy: str = "lru"      # victim order of the prefix tree's leaves: "lru", "lrfu" or "lrfu:<lambda>"
+    # recurrent-state snapshot policy (store/snap_policy.py)
+    msg_open_ids: tuple = ()       # token ids of the chat format's message-open marker; () = no message-boundary snapshots
+    snap_msg_min_gap: int = 2048   # tokens between kept message boundaries (the first and the newest `recent` are always kept)
+    snap_msg_recent: int = 4
+    snap_decode_stride: int = 0    # pages of generated text between rolling snapshots (0 = generation takes none)
+    snap_session_cap: int = 0      # snapshots one session may hold over all tiers (0 = unbounded)
+    snap_structural_reserve: int = 4
+    snap_host_mb: int = 0          # host memory for snapshots whose state row was recycled
+    snap_disk_mb: int = 0          # disk budget of snapshot files (needs the disk tier); 0 = only checkpoints write them
 
 
 @dataclass
@@ -72,10 +91,17 @@ class Sequence:
     meank: object = None           # KV selection: block means of de-rotated keys (last full-attention layer), float [blocks, hkv, hd]
     meank_n: int = 0               # blocks indexed so far
     view: list = None              # block indices of the current view (ascending, ends with the block being written)
+    view_at: int = 0               # block index at which the view was last selected
+    q_ring: object = None          # KV selection: the newest queries of this sequence, bf16 [window, hq, hd] (ring by step)
+    q_ring_pos: object = None      # their rope positions, int32 [window]
+    q_ring_n: int = 0              # queries recorded so far
     gap_from: int = None           # first token index after which the KV is carried memory (leave-gap deletions); None = exact
     images: list = field(default_factory=list)    # [(first token index, merged embeddings [n, H], fingerprint)]
     pos3: object = None            # multimodal (t, h, w) position ids of the prompt, int32 [3, n_prompt] (None = text only)
     rope_delta: int = 0            # rope position of a decode token = its cache index + rope_delta
+    snap_points: dict = field(default_factory=dict)   # page-aligned prompt position -> (class, rank) of the snapshot to take there
+    session: str = None            # whose snapshots these are (per-session cap)
+    tail_hash: int = None          # prefix hash of this sequence's rolling generation-phase snapshot
 
 
 class Engine:
@@ -100,6 +126,9 @@ class Engine:
         if cfg.n_layers is not None:
             from dataclasses import replace
             full = replace(full, n_layers=cfg.n_layers)
+        if cfg.rope_yarn and cfg.rope_yarn[0] > 1.0:
+            from dataclasses import replace
+            full = replace(full, rope_yarn=tuple(cfg.rope_yarn))
         self.full_spec = full
         self.ledger = ledger if ledger is not None else ledger_for(self.device)
         self.comm = comm
@@ -140,6 +169,9 @@ class Engine:
                                          max_blocks=self.max_blocks, prefill_chunk=cfg.prefill_chunk, comm=comm,
                                          pdl=cfg.pdl, prefill_gemm=cfg.prefill_gemm)
         self.runner.decode_gemv = cfg.decode_gemv
+        if cfg.attn_splits:
+            self.runner.attn_splits = cfg.attn_splits
+        self.runner.use_graphs = cfg.cuda_graph
         if cfg.act_bits != 15:
             assert cfg.act_bits == 8, "act_bits is 15 or 8"
             self.runner.act_bits = 8
@@ -147,16 +179,25 @@ class Engine:
         if comm is not None and getattr(comm, "symm", None) is not None:
             self.ledger.track("symmetric workspace", "symmetric", comm.symm.buf)
         self.kv = KvStore(cfg.n_pages, PAGE)
-        self.states = StateStore(cfg.n_slots, cfg.n_snap_rows)
-        self.host = HostTier(page_bytes(self.pool), cfg.host_cache_mb << 20) if cfg.host_cache_mb else None
+        from ..store.snap_policy import SessionCap
+
+        self.states = StateStore(cfg.n_slots, cfg.n_snap_rows, cap=SessionCap(cfg.snap_session_cap, cfg.snap_structural_reserve))
+        if cfg.evict_policy != "lru":
+            self.kv.set_policy(cfg.evict_policy)
+        self.host = HostTier(page_bytes(self.pool), cfg.host_cache_mb << 20, segment_bytes=cfg.pinned_segment_mb << 20) \
+            if cfg.host_cache_mb else None
         self.mover = Mover(self.pool, self.host) if self.host else None
         self.disk = None
         if cfg.disk_cache_mb and cfg.disk_dir and self.host is not None:
             from ..store.tiers import DiskTier
 
-            self.disk = DiskTier(cfg.disk_dir, page_bytes(self.pool), cfg.disk_cache_mb << 20)
+            self.disk = DiskTier(cfg.disk_dir, page_bytes(self.pool), cfg.disk_cache_mb << 20,
+                                 state_capacity=(cfg.snap_disk_mb << 20) if cfg.snap_disk_mb else None)
+        elif cfg.snap_disk_mb:
+            raise ValueError("snap_disk_mb needs the disk tier (host_cache_mb, disk_cache_mb and disk_dir)")
         # every move between the device pool, the host tier and the disk tier goes through the relocation facade
-        self.rel = Rel(self.kv, self.states, self.pool, self.host, self.mover, self.disk, PAGE)
+        self.rel = Rel(self.kv, self.states, self.pool, self.host, self.mover, self.disk, PAGE,
+                       snap_host_bytes=cfg.snap_host_mb << 20, no_reclaim=cfg.no_reclaim)
         self.adopted = self.rel.adopt() if self.disk is not None else {"blocks": 0, "states": 0}
         self._last_rows: dict = {}
         self.free_rows = list(range(cfg.max_seqs - 1, -1, -1))
@@ -257,13 +298,15 @@ class Engine:
         return toks
 
     def add_sequence(self, prompt: list[int], reuse: bool = True, images: list | None = None,
-                     image_pad_id: int | None = None) -> int:
+                     image_pad_id: int | None = None, session: str | None = None, snap_extra: list | None = None) -> int:
         """Start a sequence. With ``reuse`` the longest cached prefix for which a GDN snapshot exists
         is adopted: its KV pages are shared (pinned) and the snapshot is copied into the new row.
 
         ``images``: ``[(merged embeddings [n_i, hidden], (t, gh, gw), fingerprint)]`` in prompt order
         (``models.vision``); their rows replace the ``image_pad_id`` tokens and the prompt gets
-        (t, h, w) position ids."""
+        (t, h, w) position ids. ``session`` tags the sequence's snapshots (per-session cap); ``snap_extra``: further
+        page-aligned prompt positions worth a snapshot (the start of a segment the client may drop later)."""
+        reuse = reuse and self.cfg.prefix_cache
         if not self.free_rows:
             raise RuntimeError("no free sequence row")
         sid = self._next_sid
@@ -271,7 +314,7 @@ class Engine:
         if slot is None:
             raise RuntimeError("no free GDN state row (concurrency ceiling reached)")
         self._next_sid += 1
-        seq = Sequence(sid, self.free_rows.pop(), slot, list(prompt), n_prompt=len(prompt))
+        seq = Sequence(sid, self.free_rows.pop(), slot, list(prompt), n_prompt=len(prompt), session=session)
         self.pool.reset_slot(slot)
         if images:
             from ..models.vision import mrope_positions
@@ -287,6 +330,7 @@ class Engine:
                 i += emb.shape[0]
         usable = (len(prompt) - 1) // PAGE * PAGE             # at least one token is always prefilled
         seq.chain = self.kv.chain(self._hash_tokens(prompt, seq.images)[:usable]) if reuse and usable else None
+        self._plan_snapshots(seq, snap_extra)
         if seq.chain is not None and len(seq.chain):
             self.prefix_lookups += 1
             m, pages, carriers = self.kv.match(seq.chain)
@@ -315,11 +359,63 @@ class Engine:
         self.seqs[sid] = seq
         return sid
 
+    def _plan_snapshots(self, seq: Sequence, extra: list | None = None) -> None:
+        """Prompt positions at which the recurrent state is saved while this prompt is prefilled: the kept message
+        boundaries with their eviction classes, caller-named extra points, and the prompt's last page boundary."""
+        from ..store import snap_policy as P
+
+        seq.snap_points = {}
+        if seq.chain is None or not len(seq.chain):
+            return
+        usable = len(seq.chain) * PAGE
+        cfg = self.cfg
+        if cfg.msg_open_ids:
+            pts = [p for p in P.message_points(seq.tokens[:seq.n_prompt], cfg.msg_open_ids, PAGE, cfg.snap_msg_min_gap,
+                                               cfg.snap_msg_recent) if p <= usable]
+            seq.snap_points.update(zip(pts, P.classify(pts, seq.n_prompt, cfg.snap_msg_recent)))
+        for p in extra or ():
+            if 0 < p <= usable and p % PAGE == 0:
+                seq.snap_points.setdefault(int(p), ("extra", 0))
+        seq.snap_points[usable] = ("durable", 0)
+
+    def _hash_slice(self, seq: Sequence, lo: int, hi: int) -> list:
+        """``_hash_tokens`` of tokens [lo, hi) only (the generation phase extends a chain block by block)."""
+        toks = list(seq.tokens[lo:hi])
+        for first, emb, fp in seq.images or []:
+            for j in range(max(first, lo) - first, min(first + emb.shape[0], hi) - first):
+                toks[first + j - lo] = ((fp >> (8 * (j % 8))) ^ (j * 0x9E3779B1)) & 0x7FFFFFFF
+        return toks
+
+    def _tail_snapshot(self, seq: Sequence, pos_before: int) -> None:
+        """Generation advanced the sequence from ``pos_before`` to ``seq.n_cached`` cached tokens and its state row holds
+        the state after exactly ``n_cached`` tokens: when that is a page boundary on the configured stride, save it as the
+        sequence's rolling snapshot (the previous one is released), keyed like the blocks ``free_sequence`` will publish."""
+        from ..store.snap_policy import decode_boundary
+
+        if seq.chain is None or seq.gap_from is not None:
+            return
+        b = decode_boundary(pos_before, seq.n_cached, PAGE, self.cfg.snap_decode_stride)
+        if b is None or b != seq.n_cached:
+            return
+        have = len(seq.chain)
+        if have < b // PAGE:
+            more = self.kv.chain(self._hash_slice(seq, have * PAGE, b), root=int(seq.chain[-1]) if have else 0)
+            seq.chain = np.concatenate([seq.chain, more])
+        h = int(seq.chain[b // PAGE - 1])
+        old = seq.tail_hash
+        row = self.states.snapshot(h, b, "tail", session=seq.session)
+        if row is None:
+            return
+        self.pool.copy_slot(seq.slot, row)
+        if old is not None and old != h and old in self.states.snaps and self.states.snaps[old].klass == "tail":
+            self.states.forget(old)
+        seq.tail_hash = h
+
     def free_sequence(self, sid: int, publish: bool = True) -> None:
         """End a sequence: index its full blocks in the prefix tree (the tree takes its own
         references) and give pages, row and state row back."""
         seq = self.seqs.pop(sid)
-        if publish and seq.n_cached >= PAGE:
+        if publish and self.cfg.prefix_cache and seq.n_cached >= PAGE:
             exact = seq.n_cached if seq.gap_from is None else min(seq.n_cached, seq.gap_from)
             nb = min(exact // PAGE, len(seq.pages))
             hashed = self._hash_tokens(seq.tokens, seq.images)[:nb * PAGE]
@@ -414,7 +510,9 @@ class Engine:
         seq.n_prompt = len(seq.tokens)
         if seq.gap_from is None:
             usable = (seq.n_prompt - 1) // PAGE * PAGE        # the longer prompt has its own block identities
-            seq.chain = self.kv.chain(self._hash_tokens(seq.tokens, seq.images)[:usable]) if usable else None
+            seq.chain = self.kv.chain(self._hash_tokens(seq.tokens, seq.images)[:usable]) if usable and self.cfg.prefix_cache else None
+            self._plan_snapshots(seq)
+            seq.snap_points = {p: c for p, c in seq.snap_points.items() if p > seq.n_cached}
 
     # -- prefill ------------------------------------------------------------------------------
     def prefill_range(self, sid: int, start: int, end: int, want_token: bool):
@@ -440,19 +538,21 @@ class Engine:
         elif seq.rope_delta:
             # positions after a leave-gap deletion: cache index + the removed length
             pos3 = torch.arange(start + seq.rope_delta, end + seq.rope_delta, dtype=torch.int32, device=self.device).repeat(3, 1)
-        boundary = (seq.n_prompt - 1) // PAGE * PAGE
-        can_snap = boundary > seq.reused and seq.chain is not None and len(seq.chain)
+        pts = [p for p in seq.snap_points if start < p <= end and p > seq.reused] if seq.chain is not None else []
+        inside = [p for p in pts if p < end]
         snap = None
-        if can_snap and start < boundary < end:
-            # the last block boundary lies inside this chunk: the runner leaves the GDN state of that point in the snapshot row
-            row = self.states.snapshot(int(seq.chain[boundary // PAGE - 1]), boundary)
+        if inside:
+            # a snapshot point lies inside this chunk: the runner leaves the GDN state of that point in the snapshot row
+            # (one per chunk: `prefill_plan` cuts so that a chunk holds at most one inside and one at its end)
+            p = max(inside)
+            row = self.states.snapshot(int(seq.chain[p // PAGE - 1]), p, *seq.snap_points[p], session=seq.session)
             if row is not None:
-                snap = (boundary - start, row)
+                snap = (p - start, row)
         tok = self.runner.prefill_chunk_forward(ids, start, seq.row, seq.slot, want_logits=want_token, embeds=embeds,
                                                 pos3=pos3, snap=snap)
         seq.n_cached = end
-        if end == boundary and can_snap:
-            row = self.states.snapshot(int(seq.chain[boundary // PAGE - 1]), boundary)
+        if end in pts:
+            row = self.states.snapshot(int(seq.chain[end // PAGE - 1]), end, *seq.snap_points[end], session=seq.session)
             if row is not None:
                 self.pool.copy_slot(seq.slot, row)
         if want_token:
@@ -468,13 +568,17 @@ class Engine:
         seq = self.seqs[sid]
         n, c = seq.n_prompt, self.cfg.prefill_chunk
         boundary = (n - 1) // PAGE * PAGE
-        extra = {boundary} if (self.cfg.snap_cut and boundary > seq.n_cached) else set()
-        cuts = sorted({min(n, x) for x in range(seq.n_cached + c, n + c, c)} | extra | {n})
+        pts = sorted(p for p in seq.snap_points if p > max(seq.n_cached, seq.reused)) if seq.chain is not None else []
         out, lo = [], seq.n_cached
-        for hi in cuts:
-            if hi > lo:
-                out.append((lo, hi))
-                lo = hi
+        while lo < n:
+            hi = min(lo + c, n)
+            inside = [p for p in pts if lo < p < hi]
+            if len(inside) > 1:
+                hi = inside[1]             # one point inside the chunk (saved by the runner) and one at its end (saved after it)
+            if self.cfg.snap_cut and lo < boundary < hi:
+                hi = boundary
+            out.append((lo, hi))
+            lo = hi
         return out
 
     def prefill(self, sid: int) -> int:
@@ -515,6 +619,8 @@ class Engine:
         self.runner.inp[:n].copy_(self.h_inp[:n], non_blocking=True)
         graph.replay()
         self.h_tok[:b].copy_(self.runner.out_tok[:b], non_blocking=True)
+        if self.cfg.kvmem_budget and self.cfg.kvmem_query_tokens > 1 and not self.mock:
+            self._record_queries(sids)
         if not self.mock:
             torch.cuda.current_stream().synchronize()
         self.h2d_bytes += n * 4
@@ -527,6 +633,8 @@ class Engine:
             seq.n_cached += 1
             seq.tokens.append(t)
             out.append(t)
+            if self.cfg.snap_decode_stride and seq.n_cached % PAGE == 0:
+                self._tail_snapshot(seq, seq.n_cached - 1)
         return out
 
     STATUS_EVERY = 16      # steps between reads of the kernels' bounded-wait status words on a tensor-parallel rank
@@ -552,6 +660,21 @@ class Engine:
             self.runner.graphs.clear()
         raise RuntimeError(f"a bounded wait ran out inside a kernel ({bad}): the step's output is discarded")
 
+    def _record_queries(self, sids: list) -> None:
+        """Keep this step's rotated query of every long sequence in its ring (what the next block selection scores with)."""
+        W, sp = self.cfg.kvmem_query_tokens, self.spec
+        for i, sid in enumerate(sids):
+            seq = self.seqs[sid]
+            if seq.n_cached + 1 <= self.cfg.kvmem_budget:
+                continue
+            if seq.q_ring is None:
+                seq.q_ring = torch.zeros(W, sp.hq, sp.hd, dtype=torch.bfloat16, device=self.device)
+                seq.q_ring_pos = torch.zeros(W, dtype=torch.int32, device=self.device)
+            j = seq.q_ring_n % W
+            seq.q_ring[j].copy_(self.runner.q_rope[i].view(sp.hq, sp.hd))
+            seq.q_ring_pos[j] = seq.n_cached + seq.rope_delta
+            seq.q_ring_n += 1
+
     def set_last_token(self, sid: int, tok: int) -> None:
         """Replace the sequence's newest token (the host sampled something other than the device's argmax). The next
         step reads it as its input, so under tensor parallelism this call is mirrored to every rank."""
@@ -568,6 +691,12 @@ class Engine:
         if seq.view is not None and seq.view[-1] == cur:
             return len(seq.view)
         sp, run, dev = self.spec, self.runner, self.device
+        if seq.view is not None and cur - seq.view_at < self.cfg.kvmem_recall_every and seq.view[-1] == cur - 1:
+            # between two selections the block just entered joins the view as it is (one more recent block)
+            seq.view = seq.view + [cur]
+            row = seq.row + self.cfg.max_seqs
+            run.block_table[row, len(seq.view) - 1] = seq.pages[cur]
+            return len(seq.view)
         fi = sp.n_full - 1
         if seq.meank is None:
             seq.meank = torch.zeros(self.max_blocks, sp.hkv, sp.hd, dtype=torch.float32, device=dev)
@@ -580,13 +709,18 @@ class Engine:
             seq.meank_n = cur
         budget_blocks = max(self.cfg.kvmem_sink + self.cfg.kvmem_recent + 1, self.cfg.kvmem_budget // PAGE)
         q_row = self._last_rows.get(seq.sid, -1)
-        if q_row >= 0 and cur > 0:
+        if seq.q_ring is not None and seq.q_ring_n and cur > 0:
+            # the window of newest queries (one per decode step, kept by `decode_step`)
+            n = min(seq.q_ring_n, seq.q_ring.shape[0])
+            scores = S.score_blocks_gpu(seq.q_ring[:n], seq.q_ring_pos[:n], seq.meank[:cur], run.inv_freq, sp.rotary_dim).cpu()
+        elif q_row >= 0 and cur > 0:
             qpos = torch.tensor([pos - 1 + seq.rope_delta], dtype=torch.int32, device=dev)
             scores = S.score_blocks_gpu(run.q_rope[q_row:q_row + 1], qpos, seq.meank[:cur], run.inv_freq, sp.rotary_dim).cpu()
         else:
             scores = torch.zeros(max(cur, 1))
         scores = torch.cat([scores[:cur], torch.zeros(1)])          # the block being written is always "recent"
         seq.view = S.select(scores, cur + 1, budget_blocks, self.cfg.kvmem_sink, self.cfg.kvmem_recent)
+        seq.view_at = cur
         row = seq.row + self.cfg.max_seqs
         run.block_table[row, :len(seq.view)] = torch.tensor([seq.pages[b] for b in seq.view], dtype=torch.int32, device=dev)
         return len(seq.view)

@@ -15,6 +15,7 @@ Reference counterpart: ``crates/engine/src/running.rs`` (``submit_session_opts``
 from __future__ import annotations
 
 import queue
+import time
 from dataclasses import dataclass, field
 
 import torch
@@ -58,13 +59,15 @@ class Turn:
 
 class RunningEngine:
     def __init__(self, engine: Engine, max_batch: int = 8, on_full: str = "reject", spec_runner=None,
-                 park_sessions: bool = False, max_parked: int = 2, evict_pad_id: int = 0, prefill_every: int = 8):
+                 park_sessions: bool = False, max_parked: int = 2, evict_pad_id: int = 0, prefill_every: int = 8,
+                 step_profile: bool = False):
         """``park_sessions``: a finished turn of a named session keeps its sequence alive (pages + GDN row) so that the next
         turn continues it: droppable segments the client removed are unlinked in place (leave-gap, ``engine/img_evict.py``) and
         only the new tokens are prefilled. At most ``max_parked`` sequences wait; the oldest is released (and published) when
         a row is needed."""
         self.e = engine
         self.park_sessions, self.max_parked, self.evict_pad_id = park_sessions, max_parked, evict_pad_id
+        self.step_profile = step_profile      # one "engine.step" event per executed step (kind, turns, ms) in the metrics store
         self.parked: dict = {}       # session -> (engine sequence id, PaddedSeq of everything in the sequence, tick)
         self.resumed = self.gap_drops = 0
         self.sched = Scheduler(max_batch, engine.cfg.prefill_chunk, on_full, spec_batch=max(1, getattr(engine.cfg, "spec_rows", 1)),
@@ -148,8 +151,12 @@ class RunningEngine:
         if step.kind == "idle":
             return bool(rejected)
         try:
+            t0 = time.perf_counter() if self.step_profile else 0.0
             with METRICS.timer("pump." + step.kind):
                 getattr(self, "_do_" + step.kind)(step)
+            if self.step_profile:
+                METRICS.event("engine.step", kind=step.kind, turns=len(step.turns), ms=(time.perf_counter() - t0) * 1e3,
+                              free_pages=self.e.kv.free_pages)
         except Exception as ex:  # a failed step fails its turns, the engine keeps serving
             log.error("engine.pump", f"{step.kind} failed: {ex!r}")
             for tid in step.turns:
@@ -225,16 +232,20 @@ class RunningEngine:
         if not (self.park_sessions and t.opts.session and self._try_resume(t)):
             if t.opts.session in self.parked:
                 self._release_parked(t.opts.session)
-            prompt = t.tokens
+            prompt, anchors = t.tokens, None
             if self.park_sessions and t.opts.evict_spans:
                 spans = sorted(t.opts.evict_spans)
                 prompt = E.pad_rule(t.tokens, spans, PAGE, self.evict_pad_id).ids
                 t.padded = E.pad_rule(self._ident(t), spans, PAGE, self.evict_pad_id)     # what later histories are compared with
+                # a state snapshot in front of every droppable segment: when the segment goes and the session's sequence is no
+                # longer parked, the surviving prefix still has an anchor to resume from
+                anchors = [sp.start for sp in t.padded.spans]
             elif self.park_sessions and t.opts.session:
                 t.padded = E.PaddedSeq(self._ident(t))
             while True:
                 try:
-                    t.sid = self.e.add_sequence(prompt, images=t.opts.images or None, image_pad_id=t.opts.image_pad_id)
+                    t.sid = self.e.add_sequence(prompt, images=t.opts.images or None, image_pad_id=t.opts.image_pad_id,
+                                                session=t.opts.session, snap_extra=anchors)
                     break
                 except RuntimeError:
                     if not self.parked:

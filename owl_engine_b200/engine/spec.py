@@ -270,12 +270,48 @@ class SpecStats:
 
 
 class SpecRunner:
-    def __init__(self, draft, depth: int = 3, *, window: int = 16, degrade_below: float = 0.3, cooldown: int = 64):
+    def __init__(self, draft, depth: int = 3, *, window: int = 16, degrade_below: float = 0.3, cooldown: int = 64,
+                 depth_min: int | None = None, switch_ctx: int = 0, degrade_after: int = 0, probe_every: int = 8,
+                 force_accept: int = -1):
+        """``depth_min`` / ``switch_ctx`` (adaptive depth): sequences whose context reached ``switch_ctx`` tokens are drafted
+        ``depth_min`` deep (a long context makes every verify row dearer, so fewer speculative rows pay). ``degrade_after``:
+        that many rounds in a row without a single accepted draft switch to plain decoding for ``probe_every`` tokens, then
+        drafting is tried again (0 = off; the windowed acceptance rule ``degrade_below`` / ``cooldown`` works beside it).
+        ``force_accept >= 0``: every round accepts exactly that many drafts whatever the target says -- a throughput
+        harness: the emitted text is then the drafts', not the target's."""
         assert 1 <= depth <= 7
         self.draft, self.depth = draft, depth
         self.window, self.degrade_below, self.cooldown = window, degrade_below, cooldown
+        self.depth_min, self.switch_ctx = depth_min, switch_ctx
+        self.degrade_after, self.probe_every, self.force_accept = degrade_after, probe_every, force_accept
         self.stats = SpecStats()
         self._cool = 0
+        self._zero_streak = 0
+
+    def depth_for(self, n_cached: int) -> int:
+        if self.depth_min and self.switch_ctx and n_cached >= self.switch_ctx:
+            return min(self.depth, self.depth_min)
+        return self.depth
+
+    def _accept(self, drafts: list[int], target: list[int]) -> tuple[int, list[int]]:
+        """(accepted drafts m, the m + 1 tokens the round emits)."""
+        if self.force_accept >= 0:
+            m = min(self.force_accept, len(drafts))
+            return m, list(drafts[:m]) + [target[m]]
+        m = accept_greedy(drafts, target)
+        return m, list(target[:m + 1])
+
+    def _note(self, m: int) -> None:
+        """Acceptance bookkeeping of one round: the zero-streak rule and the windowed rule, either may start a cooldown."""
+        st = self.stats
+        self._zero_streak = self._zero_streak + 1 if m == 0 else 0
+        if self.degrade_after and self._zero_streak >= self.degrade_after:
+            self._cool, self._zero_streak = max(self._cool, self.probe_every), 0
+        st.window.append(m)
+        if len(st.window) >= self.window:
+            if sum(st.window) / len(st.window) < self.degrade_below:
+                self._cool = max(self._cool, self.cooldown)
+            st.window.clear()
 
     def after_prefill(self, engine: Engine, sid: int) -> None:
         if not engine.runner.uniform_rows:
@@ -295,15 +331,16 @@ class SpecRunner:
             out = engine.decode_step([sid])
             draft.observe(engine, sid, 1, out)
             return out
-        drafts = draft.propose(engine, sid, self.depth)[:self.depth]
+        seq = engine.seqs[sid]
+        depth = self.depth_for(seq.n_cached)
+        drafts = draft.propose(engine, sid, depth)[:depth]
         if not drafts:
             out = engine.decode_step([sid])
             draft.observe(engine, sid, 1, out)
             return out
-        seq = engine.seqs[sid]
         rows = [seq.tokens[-1]] + drafts
         target = verify_step(engine, sid, rows)
-        m = accept_greedy(drafts, target)
+        m, emitted = self._accept(drafts, target)
         n_rows = m + 1
         if n_rows < len(rows):
             # rejected rows advanced the recurrent state: restore and replay the accepted prefix
@@ -311,19 +348,18 @@ class SpecRunner:
             engine.runner.fold_slot.fill_(seq.slot)
             engine.runner.capture_fold(n_rows).replay()
             st.folds += 1
-        emitted = target[:n_rows]
         seq.tokens.extend(emitted)
         seq.n_cached += n_rows
+        if engine.cfg.snap_decode_stride and seq.n_cached % PAGE == 0:
+            # the round ended exactly on a page boundary: the row holds that boundary's state (a boundary crossed in the
+            # middle of a round is left to a later round; the rolling snapshot trails by a few pages at most)
+            engine._tail_snapshot(seq, seq.n_cached - n_rows)
         draft.observe(engine, sid, n_rows, emitted)
         st.rounds += 1
         st.drafted += len(drafts)
         st.accepted += m
         st.emitted += n_rows
-        st.window.append(m)
-        if len(st.window) >= self.window:
-            if sum(st.window) / len(st.window) < self.degrade_below:
-                self._cool = self.cooldown
-            st.window.clear()
+        self._note(m)
         return emitted
 
 
@@ -341,7 +377,8 @@ class SpecRunner:
         if self._cool > 0 or len(sids) == 1:
             return [self.round(engine, sid) for sid in sids]
         st = self.stats
-        drafts = [self.draft_of(sid).propose(engine, sid, self.depth)[:self.depth] for sid in sids]
+        depth = min(self.depth_for(engine.seqs[sid].n_cached) for sid in sids)
+        drafts = [self.draft_of(sid).propose(engine, sid, depth)[:depth] for sid in sids]
         d = min(len(x) for x in drafts)
         if d == 0:
             out = engine.decode_step(sids)
@@ -356,10 +393,11 @@ class SpecRunner:
             rows = [[engine.seqs[sid].tokens[-1]] + x for sid, x in zip(grp, dr)]
             targets = verify_batch(engine, grp, rows)
             slots, tlen, need = [], [], False
-            acc = []
+            acc, emit = [], []
             for i, sid in enumerate(grp):
-                m = accept_greedy(dr[i], targets[i])
+                m, em = self._accept(dr[i], targets[i])
                 acc.append(m)
+                emit.append(em)
                 if m + 1 < t:
                     need = True
                     engine.pool.copy_slot(engine.spec_row + i, engine.seqs[sid].slot)
@@ -377,20 +415,18 @@ class SpecRunner:
                 st.folds += 1
             for i, sid in enumerate(grp):
                 seq, n_rows = engine.seqs[sid], acc[i] + 1
-                emitted = targets[i][:n_rows]
+                emitted = emit[i]
                 seq.tokens.extend(emitted)
                 seq.n_cached += n_rows
+                if engine.cfg.snap_decode_stride and seq.n_cached % PAGE == 0:
+                    engine._tail_snapshot(seq, seq.n_cached - n_rows)
                 self.draft_of(sid).observe(engine, sid, n_rows, emitted, row0=i * t)
                 st.rounds += 1
                 st.drafted += d
                 st.accepted += acc[i]
                 st.emitted += n_rows
-                st.window.append(acc[i])
+                self._note(acc[i])
                 emitted_all.append(emitted)
-        if len(st.window) >= self.window:
-            if sum(st.window) / len(st.window) < self.degrade_below:
-                self._cool = self.cooldown
-            st.window.clear()
         return emitted_all
 
 

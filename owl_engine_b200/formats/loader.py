@@ -305,21 +305,120 @@ def interleave_rows(gate, up):
     return Q.W4Canonical(il(gate.q, up.q), il(gate.scales, up.scales), il(gate.zeros, up.zeros), gate.group)
 
 
+class LoadError(ValueError):
+    pass
+
+
+class Stager:
+    """Host-to-device upload through a bounded pinned staging buffer (``[load] staging_mb``): a tensor larger than the bound
+    crosses in slices of its first dimension, so loading never pins more host memory than the bound, whatever the
+    checkpoint's largest tensor is. 0 = unbounded (one copy per tensor straight from pageable memory)."""
+
+    def __init__(self, device, staging_mb: int = 0):
+        self.device = torch.device(device)
+        self.cap = int(staging_mb) << 20
+        self.buf = None
+        self.uploads = self.slices = 0
+
+    def __call__(self, t: torch.Tensor) -> torch.Tensor:
+        self.uploads += 1
+        nb = t.numel() * t.element_size()
+        if self.cap == 0 or self.device.type != "cuda" or nb == 0 or t.device.type != "cpu":
+            self.slices += 1
+            return t.to(self.device)
+        t = t.contiguous()
+        if self.buf is None:
+            self.buf = torch.empty(self.cap, dtype=torch.uint8).pin_memory()
+        out = torch.empty_like(t, device=self.device)
+        flat_src, flat_dst = t.view(-1).view(torch.uint8), out.view(-1).view(torch.uint8)
+        for lo in range(0, nb, self.cap):
+            n = min(self.cap, nb - lo)
+            self.buf[:n].copy_(flat_src[lo:lo + n])
+            flat_dst[lo:lo + n].copy_(self.buf[:n], non_blocking=True)
+            torch.cuda.current_stream().synchronize()          # the staging buffer is reused by the next slice
+            self.slices += 1
+        return out
+
+
+def tensor_table(hw, keep_tensors: bool = False) -> list[dict]:
+    """Every tensor of a weight set with its place in the tree, dtype, shape and bytes (``[load] dump``)."""
+    rows, seen = [], set()
+
+    def walk(prefix, obj, depth=0):
+        if id(obj) in seen or depth > 6:
+            return
+        seen.add(id(obj))
+        if isinstance(obj, torch.Tensor):
+            rows.append({"name": prefix, "dtype": str(obj.dtype).replace("torch.", ""), "shape": list(obj.shape),
+                         "bytes": obj.numel() * obj.element_size(), "device": str(obj.device),
+                         **({"tensor": obj} if keep_tensors else {})})
+        elif isinstance(obj, dict):
+            for k, v in obj.items():
+                walk(f"{prefix}.{k}", v, depth + 1)
+        elif isinstance(obj, (list, tuple)):
+            for i, v in enumerate(obj):
+                walk(f"{prefix}[{i}]", v, depth + 1)
+        elif hasattr(obj, "__dict__") and not isinstance(obj, type):
+            for k, v in vars(obj).items():
+                if not k.startswith("_") and not callable(v):
+                    walk(f"{prefix}.{k}" if prefix else k, v, depth + 1)
+    walk("", hw)
+    return rows
+
+
+def verify_weights(hw, spec: ModelSpec) -> dict:
+    """Post-load checks (``[load] verify``): the layer list matches the model description, every floating-point tensor
+    (norms, scales, dense matrices, biases) is finite, and the per-layer vectors have the widths the kernels index with.
+    Raises ``LoadError`` naming every offender; returns counts."""
+    bad = []
+    if len(hw.layers) != spec.n_layers:
+        bad.append(f"{len(hw.layers)} layers loaded, the model description has {spec.n_layers}")
+    for i, lw in enumerate(hw.layers):
+        want = "full" if spec.is_full(i) else "gdn"
+        if lw.kind != want:
+            bad.append(f"layer {i}: loaded as {lw.kind}, the model description says {want}")
+        for nm in ("ln1", "ln2"):
+            t = getattr(lw, nm)
+            if t.numel() != spec.hidden:
+                bad.append(f"layer {i}.{nm}: {t.numel()} elements, hidden is {spec.hidden}")
+        if lw.kind == "full" and (lw.q_norm.numel() != spec.hd or lw.k_norm.numel() != spec.hd):
+            bad.append(f"layer {i}: q / k norm widths {lw.q_norm.numel()} / {lw.k_norm.numel()}, head width is {spec.hd}")
+    checked = 0
+    table = tensor_table(hw, keep_tensors=True)
+    for r in table:
+        t = r["tensor"]
+        if t.is_floating_point() and t.numel():
+            checked += 1
+            if not bool(torch.isfinite(t.float() if t.element_size() == 1 else t).all()):
+                bad.append(f"{r['name']}: non-finite values")
+    n = len(table)
+    if bad:
+        raise LoadError("checkpoint verification failed:\n  " + "\n  ".join(bad[:32]))
+    return {"tensors": n, "float_tensors_checked": checked}
+
+
 def build_weights(full: ModelSpec, provider, device, rank: int = 0, world: int = 1, lm_head_int8: bool = False,
-                  vocab_split: bool = True) -> H.HybridWeights:
-    """Read every tensor through ``provider`` and produce the rank's device weights."""
+                  vocab_split: bool = True, staging_mb: int = 0, repack: str = "auto") -> H.HybridWeights:
+    """Read every tensor through ``provider`` and produce the rank's device weights. ``repack``: where the canonical int4
+    form is packed into the kernels' record layout: ``"cpu"`` (pack on the host, upload the records), ``"device"`` (upload
+    the canonical tensors, pack with device ops: the host does not become the bottleneck of a large checkpoint), ``"auto"``
+    = cpu. Uploads go through ``Stager`` (``staging_mb``)."""
     from ..parallel.plan import shard_tensor
 
     spec = full.sharded(rank, world) if world > 1 else full
     plan = TpPlan(rank, world)
-    bf = lambda t: t.to(torch.bfloat16).to(device)
-    f32 = lambda t: t.float().to(device)
+    put = Stager(device, staging_mb)
+    bf = lambda t: put(t.to(torch.bfloat16))
+    f32 = lambda t: put(t.float())
     dn = lambda name: shard_tensor(name, provider.dense(name), full, plan)
     w4 = lambda name: shard_w4(name, provider.w4(name), full, plan)
     def pack(c):
         if isinstance(c, NvCanonical):
             n, k = c.shape
-            return Q.NvFp4Linear(c.codes.to(device), c.scales.to(device), 1.0, n, k, c.group, "nvfp4", c.row_scale.float().to(device))
+            return Q.NvFp4Linear(put(c.codes), put(c.scales), 1.0, n, k, c.group, "nvfp4", put(c.row_scale.float()))
+        if repack == "device":
+            c = Q.W4Canonical(put(c.q), put(c.scales), put(c.zeros), c.group)
+            return Q.pack_skinny(c)
         return Q.pack_skinny(c).to(device)
     layers, group = [], None
     for i in range(full.n_layers):
@@ -333,7 +432,7 @@ def build_weights(full: ModelSpec, provider, device, rank: int = 0, world: int =
             a = p + "linear_attn."
             lw.qkvz = pack(cat_rows([w4(a + "in_proj_qkv.weight"), w4(a + "in_proj_z.weight")]))
             ab = torch.cat([dn(a + "in_proj_a.weight"), dn(a + "in_proj_b.weight")]).to(torch.bfloat16)
-            lw.ab_dense = H._pad16_rows(ab).to(device)
+            lw.ab_dense = put(H._pad16_rows(ab))
             lw.ab = Q.dense_skinny(lw.ab_dense, device)
             lw.conv_w = f32(dn(a + "conv1d.weight").reshape(spec.conv_dim, spec.conv_k))
             lw.a_log, lw.dt_bias = f32(dn(a + "A_log")), f32(dn(a + "dt_bias"))
@@ -347,13 +446,13 @@ def build_weights(full: ModelSpec, provider, device, rank: int = 0, world: int =
         layers.append(lw)
     emb = provider.dense("model.embed_tokens.weight").to(torch.bfloat16)
     head = emb if (full.tied or not provider.has("lm_head.weight")) else provider.dense("lm_head.weight").to(torch.bfloat16)
-    hw = H.HybridWeights(spec=spec, embed=emb.to(device), final_norm=bf(provider.dense("model.norm.weight")),
+    hw = H.HybridWeights(spec=spec, embed=put(emb), final_norm=bf(provider.dense("model.norm.weight")),
                          lm_head=None, layers=layers, group=group)
     vrows = full.vocab
     if vocab_split and world > 1 and full.vocab % (16 * world) == 0:
         vrows = full.vocab // world
         hw.vocab_offset = rank * vrows
-    hw.lm_head = Q.dense_skinny(head[hw.vocab_offset:hw.vocab_offset + vrows].contiguous().to(device), device,
+    hw.lm_head = Q.dense_skinny(put(head[hw.vocab_offset:hw.vocab_offset + vrows].contiguous()), device,
                                 int8=lm_head_int8)
     return hw
 
@@ -371,4 +470,12 @@ def load_model(path: str | Path, device, spec: ModelSpec | None = None, rank: in
             spec = spec_from_hf_config(json.loads((Path(path) / "config.json").read_text()))
     if kind == "gguf":
         provider.set_dims(spec)
-    return spec, build_weights(spec, provider, device, rank, world, **kw)
+    verify, dump = kw.pop("verify", False), kw.pop("dump", False)
+    hw = build_weights(spec, provider, device, rank, world, **kw)
+    if verify:
+        facts = verify_weights(hw, hw.spec)
+        log.info("load.verify", f"{facts['tensors']} tensors, {facts['float_tensors_checked']} floating-point ones finite")
+    if dump:
+        for r in tensor_table(hw):
+            log.info("load.dump", f"{r['name']:<48s} {r['dtype']:<10s} {str(r['shape']):<20s} {r['bytes']:>12d} B  {r['device']}")
+    return spec, hw

@@ -302,6 +302,16 @@ class StepLayout:
         self.size = 5 * m + 3 * b
 
 
+class _EagerStep:
+    """Stands in for a captured graph when steps run eagerly: ``replay()`` launches the kernel sequence directly."""
+
+    def __init__(self, fn):
+        self.fn = fn
+
+    def replay(self) -> None:
+        self.fn()
+
+
 class HybridRunner:
     MAX_ROWS = 32
 
@@ -354,6 +364,7 @@ class HybridRunner:
         self.qkv_out = bf(M, self.qkv_n)
         self.q_rope = bf(M, spec.hq, spec.hd)
         self.attn_splits = attn_splits
+        self.use_graphs = True          # False: every step, fold and verify launches its kernels eagerly (debugging)
         self.max_splits = 64
         self.part_o = f32(M * spec.hq * self.max_splits * spec.hd)
         self.part_ml = f32(M * spec.hq * self.max_splits * 2)
@@ -369,8 +380,13 @@ class HybridRunner:
         self.loc_val, self.loc_idx = f32(M), torch.zeros(M, dtype=torch.int32, device=dev)
         self.vocab_split = self.vocab_local != spec.vocab
         self.inv_freq = R.rope_inv_freq(spec.rotary_dim, spec.rope_theta).to(dev)
+        yarn_scale = 1.0
+        if getattr(spec, "rope_yarn", None):
+            factor, orig, bf, bs, af = spec.rope_yarn
+            inv, yarn_scale = R.rope_yarn(spec.rotary_dim, spec.rope_theta, factor, orig or spec.max_position, bf, bs, af)
+            self.inv_freq = inv.to(dev)
         self.section = torch.tensor(mrope_section_map(spec), dtype=torch.uint8, device=dev)
-        self.rope_scale = 1.0
+        self.rope_scale = yarn_scale
         self.scale = 1.0 / math.sqrt(spec.hd)
         self.graphs: dict = {}
         self._pf = None   # lazily allocated prefill workspace
@@ -795,6 +811,9 @@ class HybridRunner:
             if not hasattr(self, "fold_slots"):
                 self.fold_slots = torch.full((self.MAX_ROWS,), -1, dtype=torch.int32, device=self.device)
                 self.fold_tlen = torch.zeros(self.MAX_ROWS, dtype=torch.int32, device=self.device)
+            if not self.use_graphs:
+                g = self.graphs[key] = _EagerStep(lambda: self.fold_batch(b, t))
+                return g
             stream = torch.cuda.Stream(device=self.device)
             stream.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(stream):
@@ -818,6 +837,9 @@ class HybridRunner:
         if g is None:
             if not hasattr(self, "fold_slot"):
                 self.fold_slot = torch.full((1,), -1, dtype=torch.int32, device=self.device)
+            if not self.use_graphs:
+                g = self.graphs[key] = _EagerStep(lambda: self.fold(self.fold_slot, t))
+                return g
             stream = torch.cuda.Stream(device=self.device)
             stream.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(stream):
@@ -840,14 +862,10 @@ class HybridRunner:
         if g is not None:
             return g
         lay = StepLayout(b, t)
-        if self.comm is not None and not getattr(self.comm, "capturable", True):
-            # a transport that crosses the host (relay fallback) cannot be captured: the "graph" is the eager step
-            runner = self
-
-            class _Eager:
-                def replay(self_inner):
-                    runner.step_forward(lay, ctx_hint=ctx_hint, advance=advance, sample=sample)
-            self.graphs[key] = _Eager()
+        if not self.use_graphs or (self.comm is not None and not getattr(self.comm, "capturable", True)):
+            # graphs switched off (`[cuda] graph = false`), or a transport that crosses the host (relay fallback) and cannot
+            # be captured: the "graph" is the eager step
+            self.graphs[key] = _EagerStep(lambda: self.step_forward(lay, ctx_hint=ctx_hint, advance=advance, sample=sample))
             return self.graphs[key]
         stream = torch.cuda.Stream(device=self.device)
         stream.wait_stream(torch.cuda.current_stream())

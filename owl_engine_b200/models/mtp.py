@@ -27,8 +27,10 @@ from . import hybrid as H
 
 
 class MtpHead:
-    def __init__(self, target: H.HybridRunner, *, seed: int = 1, std: float = 0.02, weights: dict | None = None):
-        """``weights`` (optional): dense tensors ``fc`` [H, 2H], ``norm_e``, ``norm_h``, ``norm`` [H] and the
+    def __init__(self, target: H.HybridRunner, *, seed: int = 1, std: float = 0.02, weights: dict | None = None,
+                 kv_dtype: str | None = None):
+        """``kv_dtype``: format of the head's own KV pool (``"bf16"`` or ``"fp8"``, half the memory; None = the target
+        pool's format). ``weights`` (optional): dense tensors ``fc`` [H, 2H], ``norm_e``, ``norm_h``, ``norm`` [H] and the
         HF-named tensors of one full-attention layer under ``layers.0.*``; random-init otherwise."""
         self.target = target
         spec = replace(target.spec, n_layers=1, full_every=1)
@@ -53,7 +55,7 @@ class MtpHead:
         self.fc_h = Q.dense_skinny(fc[:, Hd:].contiguous().to(torch.bfloat16), dev)
         self.fc_dense = fc.to(torch.bfloat16)
         self.norm_e, self.norm_h = norm_e.to(torch.bfloat16), norm_h.to(torch.bfloat16)
-        self.pool = H.StatePool(spec, dev, target.pool.n_pages, 1)
+        self.pool = H.StatePool(spec, dev, target.pool.n_pages, 1, kv_dtype=kv_dtype or getattr(target.pool, "kv_dtype", "fp8"))
         self.runner = H.HybridRunner(spec, hw, self.pool, max_seqs=target.max_seqs, max_blocks=target.max_blocks,
                                      prefill_chunk=target.prefill_chunk, comm=target.comm, pdl=target.pdl,
                                      prefill_gemm=target.prefill_gemm)

@@ -32,6 +32,8 @@ class ModelSpec:
     eps: float = 1e-6
     tied: bool = False
     mrope_section: tuple = (11, 11, 10)
+    max_position: int = 262144     # context length the checkpoint was trained for (YaRN's original_max when the profile gives 0)
+    rope_yarn: tuple = None        # (factor, original_max, beta_fast, beta_slow, attention_factor) or None = plain rope
     # tensor parallel view (filled by ``sharded``)
     tp_rank: int = 0
     tp_world: int = 1

@@ -80,6 +80,13 @@ def stream() -> int:
 # what ran last is the first question after a wrong token or a status word, and a captured graph hides it from the host.
 _LAUNCHES: collections.deque = collections.deque(maxlen=2048)
 _launch_seq = 0
+LAUNCH_SYNC = False       # debugging: wait for every launch and read the bounded-wait status words after it (no graph capture then)
+
+
+def set_trace_ring(n: int) -> None:
+    """Capacity of the launch ring (``[cuda] trace_ring``; 0 keeps the default of 2048 entries)."""
+    global _LAUNCHES
+    _LAUNCHES = collections.deque(_LAUNCHES, maxlen=n if n > 0 else 2048)
 
 
 def call(name: str, *args) -> None:
@@ -93,6 +100,16 @@ def call(name: str, *args) -> None:
     _LAUNCHES.append((_launch_seq, name, args))
     if rc != 0:
         _native.check(rc, name)
+    if LAUNCH_SYNC:
+        # the failing launch is the one that just ran: a device fault surfaces here with the entry's name instead of at
+        # some later synchronisation point
+        try:
+            torch.cuda.synchronize()
+        except RuntimeError as ex:
+            raise RuntimeError(f"{name} (launch {_launch_seq}): {ex}") from None
+        bad = {k: v for k, v in all_status().items() if v}
+        if bad:
+            raise RuntimeError(f"{name} (launch {_launch_seq}): a bounded wait ran out {bad}")
 
 
 def recent_launches(n: int = 256) -> list[dict]:

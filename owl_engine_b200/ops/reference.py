@@ -22,6 +22,32 @@ def rope_inv_freq(rotary_dim: int, theta: float) -> torch.Tensor:
     return 1.0 / (theta ** (torch.arange(0, rotary_dim, 2, dtype=torch.int64).float() / rotary_dim))
 
 
+def rope_yarn(rotary_dim: int, theta: float, factor: float, original_max: int, beta_fast: float = 32.0, beta_slow: float = 1.0,
+              attention_factor: float = 1.0) -> tuple[torch.Tensor, float]:
+    """YaRN context extension: per-frequency blend of the original rotary frequencies (dimensions that turn more than
+    ``beta_fast`` times within the trained context keep theirs) and frequencies divided by ``factor`` (dimensions that turn
+    less than ``beta_slow`` times), linear in between; cos / sin are multiplied by ``(0.1 ln(factor) + 1) * attention_factor``.
+    Returns (inv_freq [rotary_dim / 2], scale). ``factor <= 1`` is plain rope.
+
+    Reference counterpart: ``[model.rope]`` of ``profiles/full.toml:147-155`` (YaRN keys; the same formula as the HF
+    ``yarn`` rope type)."""
+    base = rope_inv_freq(rotary_dim, theta)
+    if factor <= 1.0:
+        return base, float(attention_factor)
+
+    def turn_dim(n_rot: float) -> float:              # the (fractional) frequency index that makes n_rot turns in original_max
+        return rotary_dim * math.log(original_max / (n_rot * 2 * math.pi)) / (2 * math.log(theta))
+
+    lo = max(math.floor(turn_dim(beta_fast)), 0)
+    hi = min(math.ceil(turn_dim(beta_slow)), rotary_dim - 1)
+    if lo == hi:
+        hi += 0.001
+    ramp = ((torch.arange(rotary_dim // 2, dtype=torch.float32) - lo) / (hi - lo)).clamp(0, 1)
+    keep = 1.0 - ramp                                 # 1 = extrapolate (original frequency), 0 = interpolate (divided by factor)
+    inv = base / factor * (1 - keep) + base * keep
+    return inv, float((0.1 * math.log(factor) + 1.0) * attention_factor)
+
+
 def rope_cos_sin(pos3: torch.Tensor, inv_freq: torch.Tensor, section: list[int], scale: float = 1.0):
     """pos3: int [3, T]. Returns cos, sin of shape [T, rotary_dim/2] (fp32 angle as in HF)."""
     sec = torch.tensor(section, dtype=torch.long)

@@ -13,6 +13,7 @@ from __future__ import annotations
 import asyncio
 import collections
 import json
+import os
 import queue as pyqueue
 import threading
 import time
@@ -35,7 +36,8 @@ REASONS = {200: "OK", 400: "Bad Request", 404: "Not Found", 405: "Method Not All
 class App:
     def __init__(self, client, tokenizer, model_name: str, template: ChatTemplate | None = None,
                  default_sampling: SamplingParams | None = None, default_max_new: int = 4096, max_new_cap: int = 32768,
-                 queue_timeout_ms: int = 30000, keepalive_ms: int = 15000, max_concurrent: int = 8, vision=None):
+                 queue_timeout_ms: int = 30000, keepalive_ms: int = 15000, max_concurrent: int = 8, vision=None,
+                 request_dump_dir: str = "", prompt_dump: bool = False, raw_completion: bool = False):
         self.client, self.tok, self.model = client, tokenizer, model_name
         self.tpl = template or ChatTemplate()
         self.default_sampling = default_sampling or SamplingParams()
@@ -45,6 +47,11 @@ class App:
         self.session_locks: dict[str, asyncio.Lock] = {}
         self.guard = RepeatGuard()
         self.vision = vision      # Vision (tower + image cache + pad token id) or None: image parts are then refused
+        # debugging aids: every request body as a file; the rendered prompt and the undivided completion text in the log
+        self.request_dump_dir, self.prompt_dump, self.raw_completion = request_dump_dir, prompt_dump, raw_completion
+        self._dump_seq = 0
+        if request_dump_dir:
+            os.makedirs(request_dump_dir, exist_ok=True)
         self.started = time.time()
         self.stop = threading.Event()
         self.agent_trace: collections.deque = collections.deque(maxlen=64)   # per turn: the output splitter's structural trace
@@ -188,13 +195,28 @@ class App:
             self._vwrap = tuple(ids) if None not in ids else (None, None)
         return self._vwrap
 
+    def _dump_request(self, body: bytes) -> None:
+        """One file per request body, named by arrival time and a counter (bodies hold user data and image data URLs:
+        the directory is the operator's responsibility)."""
+        self._dump_seq += 1
+        path = os.path.join(self.request_dump_dir, f"{int(time.time() * 1e3):013d}-{self._dump_seq:06d}.json")
+        try:
+            with open(path, "wb") as f:
+                f.write(body)
+        except OSError as ex:
+            log.warn("server.dump", f"cannot write {path}: {ex}")
+
     async def chat(self, body, reader, w) -> None:
+        if self.request_dump_dir:
+            self._dump_request(body)
         req = ChatRequest.parse(body)
         kwargs = dict(req.chat_template_kwargs)
         if req.reasoning_effort in ("none", "minimal"):
             kwargs.setdefault("enable_thinking", False)
         prompt = self.tpl.render(req.messages, tools=req.tools, **kwargs)
         ids = self.tok.encode(prompt)
+        if self.prompt_dump:
+            log.LOG.emit("warn", "server.prompt", f"{len(ids)} tokens: {prompt!r}")
         images, evict_spans = [], []
         if req.images:
             if self.vision is None:
@@ -226,6 +248,7 @@ class App:
             if req.stream:
                 await self._sse_open(w)
             last_io, t_submit = time.time(), time.time()
+            raw_ids: list = []
             reason, usage = "stop", {"prompt_tokens": len(ids), "completion_tokens": 0}
             while True:
                 try:
@@ -238,6 +261,8 @@ class App:
                         last_io = time.time()
                     continue
                 if ev[0] == "token":
+                    if self.raw_completion:
+                        raw_ids.append(ev[2])
                     chunks = streamer.on_token(ev[2])
                     if req.stream:
                         for c in chunks:
@@ -268,6 +293,9 @@ class App:
             else:
                 streamer.drain()
                 await self._send(w, 200, streamer.full_response(reason, usage))
+            if self.raw_completion:
+                # what the model wrote before the thinking / tool-call splitter divided it, special tokens included
+                log.LOG.emit("warn", "server.raw", f"{streamer.id}: {self.tok.decode(raw_ids)!r}")
             sp = streamer.splitter
             self.agent_trace.append({"id": streamer.id, "session": req.session, "tool_calls": sp.n_calls, "malformed": sp.malformed,
                                      "strays": sp.strays, "reasoning_tokens": sp.reasoning_steps, "trace": sp.trace()})

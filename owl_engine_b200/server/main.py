@@ -58,7 +58,43 @@ def parallel_plan(cfg: C.OwlConfig, env=None) -> dict:
             "vocab_split": bool(p["tp_vocab_split"]), "fused_gemm": bool(p["tp_fused_gemm"])}
 
 
-def build_engine_factory(cfg: C.OwlConfig, plan: dict | None = None):
+def open_tokenizer(cfg: C.OwlConfig):
+    """The profile's tokenizer: the checkpoint's ``tokenizer.json`` when the model path has one, else the byte-level one."""
+    from ..engine.tokenizer import ByteTokenizer, HfTokenizer
+
+    v = cfg.values
+    path = v["model"]["path"]
+    try:
+        return HfTokenizer(path) if path and v["model"]["format"] != "gguf" else ByteTokenizer()
+    except Exception:   # noqa: BLE001  (no tokenizer files next to the weights)
+        return ByteTokenizer()
+
+
+def evict_pad_token(cfg: C.OwlConfig, tok) -> int:
+    """``[vision] image_evict_pad``: the filler that page-aligns a droppable segment must be exactly one token. An empty
+    setting tries an ideographic full stop, a space, then a newline."""
+    text = cfg.values["vision"]["image_evict_pad"]
+    for cand in ([text] if text else ["\u3002", " ", "\n"]):
+        ids = tok.encode(cand)
+        if len(ids) == 1:
+            return int(ids[0])
+    raise C.ConfigError(f"vision.image_evict_pad = {text!r} is {len(tok.encode(text))} tokens for this tokenizer; it must be exactly one")
+
+
+def apply_process_switches(cfg: C.OwlConfig) -> None:
+    """Profile keys that switch process-wide behaviour of the kernel launcher and the debugging aids."""
+    from ..ops import kernels as K
+    from ..utils.stepgate import GATE
+
+    v = cfg.values
+    K.LAUNCH_SYNC = bool(v["cuda"]["launch_sync"])
+    K.set_trace_ring(v["cuda"]["trace_ring"])
+    if not v["kernel"]["gdn_chunked"]:
+        K.GDN_CHUNKED_FROM = 0            # prefill runs the serial / column-split recurrence instead of the chunked form
+    GATE.configure(v["probes"]["step_gate"], v["probes"]["step_gate_ms"])
+
+
+def build_engine_factory(cfg: C.OwlConfig, plan: dict | None = None, msg_open_ids: tuple = ()):
     v = cfg.values
     plan = plan or {"world": 1, "rank": 0, "local": 0, "comm_mode": None}
 
@@ -79,7 +115,7 @@ def build_engine_factory(cfg: C.OwlConfig, plan: dict | None = None):
             torch.cuda.set_device(plan["local"])
         dev = torch.device(f"cuda:{torch.cuda.current_device()}")
         est = estimate(cfg)
-        km = v["kvmem"]
+        km, st, sg, rp = v["kvmem"], v["store"], v["store.gdn"], v["model.rope"]
         ecfg = EngineConfig(model=v["model"]["name"], group=v["model"]["group"],
                             quant="nvfp4" if v["model"]["quant"] == "nvfp4" else "w4a16",
                             act_bits=8 if v["model"]["quant"] == "w4a8" else 15,
@@ -92,7 +128,18 @@ def build_engine_factory(cfg: C.OwlConfig, plan: dict | None = None):
                             prefill_chunk=v["runtime"]["prefill_chunk"], pdl=v["kernel"]["pdl"],
                             prefill_gemm=v["kernel"]["prefill_gemm"], host_cache_mb=v["store"]["host_cache_mb"],
                             disk_cache_mb=v["store"]["disk_cache_mb"], disk_dir=v["store"]["disk_dir"],
-                            kv_dtype=v["store.kv"]["kv_dtype"], vocab_split=plan.get("vocab_split", True))
+                            kv_dtype=v["store.kv"]["kv_dtype"], vocab_split=plan.get("vocab_split", True),
+                            prefix_cache=st["prefix_cache"], no_reclaim=st["no_reclaim"], evict_policy=st["evict_policy"],
+                            snap_host_mb=st["snap_host_mb"], snap_disk_mb=st["snap_disk_mb"],
+                            msg_open_ids=tuple(msg_open_ids) if st["prefix_cache"] and sg["snap_max"] > 0 else (),
+                            snap_msg_min_gap=sg["snap_msg_min_gap"], snap_msg_recent=sg["snap_msg_recent"],
+                            snap_decode_stride=sg["snap_decode_stride"] if st["prefix_cache"] and sg["snap_max"] > 0 else 0,
+                            snap_session_cap=sg["snap_session_cap"], snap_structural_reserve=sg["snap_structural_reserve"],
+                            attn_splits=v["kernel"]["attn_splits"], cuda_graph=v["cuda"]["graph"],
+                            pinned_segment_mb=v["cuda"]["pinned_segment_mb"],
+                            rope_yarn=(rp["yarn_factor"], rp["original_max"], rp["beta_fast"], rp["beta_slow"],
+                                       rp["attention_factor"]) if rp["yarn_factor"] > 1.0 else None,
+                            kvmem_query_tokens=km["select_query_tokens"], kvmem_recall_every=km["recall_every"])
         if v["kernel"]["selfcheck"]:
             from ..ops import selfcheck
 
@@ -104,7 +151,9 @@ def build_engine_factory(cfg: C.OwlConfig, plan: dict | None = None):
 
             spec, weights = load_model(v["model"]["path"], dev, spec=PRESETS.get(v["model"]["name"], lambda: None)(),
                                        rank=plan["rank"], world=plan["world"], group=v["model"]["group"],
-                                       lm_head_int8=ecfg.lm_head_int8, vocab_split=plan.get("vocab_split", True))
+                                       lm_head_int8=ecfg.lm_head_int8, vocab_split=plan.get("vocab_split", True),
+                                       verify=v["load"]["verify"], dump=v["load"]["dump"], staging_mb=v["load"]["staging_mb"],
+                                       repack=v["load"]["repack"])
             eng = Engine(ecfg, spec=spec, weights=weights, comm=comm)
         if comm is not None:
             eng.runner.sp_prefill = plan["fused_gemm"]
@@ -138,7 +187,7 @@ def build_spec_factory(cfg: C.OwlConfig):
 
                 src = SafeDir(sp["draft_path"])
                 weights = {k: src.get(k) for k in src.keys()}
-            draft = MtpDraft(MtpHead(engine.runner, weights=weights), lookup)
+            draft = MtpDraft(MtpHead(engine.runner, weights=weights, kv_dtype=cfg.values["store.kv"]["draft_kv_dtype"]), lookup)
         elif sp["kind"] == "dflash2":
             from ..engine.spec import DFlash2Draft
             from ..models import dflash2 as D
@@ -159,7 +208,9 @@ def build_spec_factory(cfg: C.OwlConfig):
             draft = DFlash2Draft(head, engine.runner, lookup)
         else:
             draft = lookup
-        return SpecRunner(draft, depth=max(1, min(7, sp["depth"] or 3)))
+        return SpecRunner(draft, depth=max(1, min(7, sp["depth"] or 3)),
+                          depth_min=sp["depth_min"] if sp["adaptive_depth"] else None, switch_ctx=sp["depth_switch_ctx"],
+                          degrade_after=sp["degrade_after"], probe_every=sp["probe_every"], force_accept=sp["force_accept"])
     return make
 
 
@@ -215,21 +266,30 @@ def main(argv=None) -> int:
         print(f"config error: {e}", file=sys.stderr)
         return 2
     lv = cfg.values["log"]
-    log.LOG.configure(a.log_level or lv["level"], lv["tags_allow"], lv["tags_deny"], lv["timestamp"])
+    log.LOG.configure(a.log_level or lv["level"], lv["tags_allow"], lv["tags_deny"], lv["timestamp"], path=lv["file"] or None,
+                      max_mb=lv["max_mb"], keep=lv["keep"])
     from ..engine.sampler import SamplingParams
     from ..engine.service import EngineService
-    from ..engine.tokenizer import ByteTokenizer, HfTokenizer
     from ..utils.metrics import METRICS
     from .chat_tpl import ChatTemplate
     from .http import App, serve
 
     METRICS.set_level(cfg.values["probes"]["perf_level"])
     v = cfg.values
+    apply_process_switches(cfg)
+    tok = open_tokenizer(cfg)
+    try:
+        pad_id = evict_pad_token(cfg, tok) if v["vision"]["image_evict"] else 0
+    except C.ConfigError as e:
+        print(f"config error: {e}", file=sys.stderr)
+        return 2
+    # the chat format's message-open marker: where conversations fork, so where recurrent-state snapshots are worth taking
+    msg_open_ids = tuple(tok.encode("<|im_start|>"))
     if plan["rank"] > 0:
         # follower rank of a tensor-parallel job: no listener, no scheduler; apply the leader's step descriptors
         from ..engine.tp_serve import follower_loop, follower_ring
 
-        engine = build_engine_factory(cfg, plan)()
+        engine = build_engine_factory(cfg, plan, msg_open_ids)()
         make_spec = build_spec_factory(cfg)
         spec_runner = make_spec(engine) if make_spec else None
         ring = follower_ring(plan["rank"])
@@ -238,15 +298,11 @@ def main(argv=None) -> int:
         ring.free()
         _leave_group(engine)
         return 0
-    svc = EngineService(build_engine_factory(cfg, plan), max_batch=v["runtime"]["max_batch"], on_full=v["runtime"]["admission_on_full"],
-                        spec_runner=build_spec_factory(cfg),
-                        running_kw={"park_sessions": bool(v["vision"]["image_evict"]), "max_parked": max(1, v["store.gdn"]["gdn_slots"] // 2)})
+    svc = EngineService(build_engine_factory(cfg, plan, msg_open_ids), max_batch=v["runtime"]["max_batch"],
+                        on_full=v["runtime"]["admission_on_full"], spec_runner=build_spec_factory(cfg),
+                        running_kw={"park_sessions": bool(v["vision"]["image_evict"]), "max_parked": max(1, v["store.gdn"]["gdn_slots"] // 2),
+                                    "evict_pad_id": pad_id, "step_profile": bool(v["probes"]["step_profile"])})
     client = svc.boot()
-    path = v["model"]["path"]
-    try:
-        tok = HfTokenizer(path) if path and v["model"]["format"] != "gguf" else ByteTokenizer()
-    except Exception:
-        tok = ByteTokenizer()
     vision = None
     if v["vision"]["enabled"]:
         import torch
@@ -268,7 +324,8 @@ def main(argv=None) -> int:
     app = App(client, tok, v["model"]["name"], ChatTemplate(v["server"]["template_path"], v["server"]["template_vars"]),
               SamplingParams(s["mode"], s["temp"], s["topk"], s["topp"], s["rep_penalty"]), v["runtime"]["default_max_new"],
               v["runtime"]["max_new_cap"], v["server"]["queue_timeout_ms"], v["server"]["keepalive_ms"],
-              max_concurrent=v["store.gdn"]["gdn_slots"], vision=vision)
+              max_concurrent=v["store.gdn"]["gdn_slots"], vision=vision, request_dump_dir=v["server"]["request_dump_dir"],
+              prompt_dump=v["probes"]["prompt_dump"], raw_completion=v["probes"]["raw_completion"])
     host, _, port = v["server"]["bind"].rpartition(":")
 
     async def run():

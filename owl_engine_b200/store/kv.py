@@ -46,6 +46,8 @@ def lib():
         l.owl_kv_node.argtypes = [c_void_p, c_uint64, c_void_p, c_void_p, c_void_p, c_void_p]
         l.owl_kv_stats.argtypes = [c_void_p, c_void_p]
         l.owl_kv_list.argtypes = [c_void_p, c_int, c_void_p, c_int]
+        l.owl_kv_set_policy.argtypes = [c_void_p, ctypes.c_double]
+        l.owl_kv_set_policy.restype = None
         _lib = l
     return _lib
 
@@ -63,6 +65,22 @@ class KvStore:
         if getattr(self, "h", None) and _lib is not None:
             _lib.owl_kv_free(self.h)
             self.h = None
+
+    def set_policy(self, policy: str) -> None:
+        """Victim order of ``evict``: ``"lru"`` (least recently used leaf), ``"lrfu"`` or ``"lrfu:<lambda>"`` (combined
+        recency / frequency: every use adds 1 to a block's value, which halves every ``1 / lambda`` uses of the store;
+        default lambda 0.05)."""
+        name, _, arg = policy.partition(":")
+        if name == "lru" and not arg:
+            lam = -1.0
+        elif name == "lrfu":
+            lam = float(arg) if arg else 0.05
+            if lam < 0:
+                raise ValueError(f"evict_policy {policy!r}: lambda must be >= 0")
+        else:
+            raise ValueError(f"evict_policy {policy!r}: expected lru, lrfu or lrfu:<lambda>")
+        self.policy = policy
+        lib().owl_kv_set_policy(self.h, lam)
 
     # -- hashing -----------------------------------------------------------------------------
     def chain(self, tokens, root: int = 0, tags=None) -> np.ndarray:

@@ -30,16 +30,31 @@ DEVICE, HOST, DISK = 0, 1, 2
 
 
 class Rel:
-    def __init__(self, kv, states, pool, host=None, mover=None, disk=None, block_tokens: int = 16, policy: B.PressurePolicy | None = None):
+    def __init__(self, kv, states, pool, host=None, mover=None, disk=None, block_tokens: int = 16, policy: B.PressurePolicy | None = None,
+                 snap_host_bytes: int = 0, no_reclaim: bool = False):
+        """``snap_host_bytes``: host memory for recurrent-state snapshots whose row was recycled (0 = they are dropped, or go
+        straight to the disk tier when it has a snapshot budget). ``no_reclaim``: the pressure path never takes a cached
+        block out of the device pool (diagnostic: a request that does not fit is refused instead)."""
+        from collections import OrderedDict
+
         self.kv, self.states, self.pool = kv, states, pool
         self.host, self.mover, self.disk = host, mover, disk
         self.block_tokens = block_tokens
         self.policy = policy or B.PressurePolicy()
+        self.no_reclaim = no_reclaim
         self.host_slot_of: dict[int, int] = {}        # chain hash -> host slot, oldest first
         self.meta: dict[int, tuple] = {}              # chain hash -> (parent hash, tag, tokens as int32 array): what the index stores
-        self.disk_snaps: dict[int, int] = {}          # prefix hash -> n_tokens of a snapshot that exists only on disk
+        self.snap_host: "OrderedDict[int, torch.Tensor]" = OrderedDict()    # prefix hash -> state bytes on the host, oldest first
+        self.snap_host_cap, self.snap_host_used = int(snap_host_bytes), 0
+        self.snap_demoted = self.snap_spilled = self.snap_recalled = self.snap_dropped = 0
         self.spilled = self.recalled = self.demoted = self.dropped = self.adopted = 0
         self.last_verdict: B.Verdict | None = None
+        states.on_evict, states.on_forget = self._snap_demote, self._snap_forget
+
+    @property
+    def disk_snaps(self) -> dict:
+        """prefix hash -> n_tokens of the snapshots that exist only on disk."""
+        return {h: s.n_tokens for h, s in self.states.lower.items() if s.tier == "disk"}
 
     # -- bookkeeping at publish time ----------------------------------------------------------------------------------------
     def note_published(self, chain, tokens, tags=None) -> None:
@@ -71,6 +86,8 @@ class Rel:
 
     def make_room(self, need: int) -> None:
         """Free device pages until ``need`` are available, cheapest sink first."""
+        if self.no_reclaim:
+            return
         st = self.kv.stats()
         # leaves expose their parents as they go, so every device-resident tree block is a candidate in the end
         free, evictable = st["free_pages"], st["device_nodes"]
@@ -109,7 +126,7 @@ class Rel:
 
     def relieve(self) -> int:
         """Watermark relief between steps. Returns the number of pages demoted."""
-        if self.host is None:
+        if self.host is None or self.no_reclaim:
             return 0
         free = self.kv.free_pages
         target = self.policy.target(free, self.kv.n_pages)
@@ -213,25 +230,81 @@ class Rel:
         self.pool.conv_state[:, row].copy_(raw[:nc].view(torch.float32).view_as(self.pool.conv_state[:, row]))
         self.pool.rec_state[:, row].copy_(raw[nc:].view(torch.float32).view_as(self.pool.rec_state[:, row]))
 
+    # snapshots whose row was recycled: pinned-host bytes first, the disk tier's ``.gdn`` files behind them
+    def _snap_to_disk(self, s, data: torch.Tensor) -> bool:
+        d = self.disk
+        if d is None:
+            return False
+        if d.state_capacity is not None:
+            nb = data.numel() * data.element_size()
+            lower = self.states.lower
+            while d.state_used + nb > d.state_capacity and d.states:
+                old = next(iter(d.states))                       # the file written longest ago
+                d.drop_state(old)
+                if old in lower and lower[old].tier == "disk":
+                    del lower[old]
+                    self.snap_dropped += 1
+        return bool(d.put_state(s.chain_hash, s.n_tokens, data))
+
+    def _snap_demote(self, s) -> str | None:
+        """``StateStore.on_evict``: keep the bytes of a snapshot that loses its row. Returns the tier that took them."""
+        nb = (self.pool.conv_state[:, s.row].numel() + self.pool.rec_state[:, s.row].numel()) * 4
+        if self.snap_host_cap >= nb:
+            self.snap_host[s.chain_hash] = self._state_bytes(s.row).cpu()
+            self.snap_host_used += nb
+            self.snap_demoted += 1
+            while self.snap_host_used > self.snap_host_cap:
+                h, data = self.snap_host.popitem(last=False)   # the oldest host snapshot moves down (or is dropped)
+                self.snap_host_used -= data.numel()
+                old = self.states.lower.get(h)
+                if old is not None and self._snap_to_disk(old, data):
+                    old.tier = "disk"
+                    self.snap_spilled += 1
+                else:
+                    self.states.lower.pop(h, None)
+                    self.snap_dropped += 1
+            return "host"
+        if self.disk is not None and self.disk.state_capacity is not None and self._snap_to_disk(s, self._state_bytes(s.row).cpu()):
+            self.snap_spilled += 1
+            return "disk"
+        return None
+
+    def _snap_forget(self, s) -> None:
+        """``StateStore.on_forget``: a lower-tier snapshot is gone for good."""
+        if s.tier == "host":
+            data = self.snap_host.pop(s.chain_hash, None)
+            if data is not None:
+                self.snap_host_used -= data.numel()
+        elif s.tier == "disk" and self.disk is not None:
+            self.disk.drop_state(s.chain_hash)
+
     def find_snapshot(self, chain):
-        """Deepest snapshot along a chain: live ones first; a snapshot that only exists on disk is loaded into a snapshot
-        row (evicting the least recently used one) and becomes live."""
+        """Deepest snapshot along a chain: live ones first; a snapshot whose bytes live on the host or on disk is loaded
+        into a snapshot row (the lowest-ranked live one leaves) and becomes live."""
         snap = self.states.find(chain)
-        if not self.disk_snaps:
+        lower = self.states.lower
+        if not lower:
             return snap
         for i in range(len(chain) - 1, -1, -1):
             h = int(chain[i])
             if snap is not None and snap.chain_hash == h:
                 return snap
-            if h in self.disk_snaps:
-                n_tok = self.disk_snaps[h]
-                row = self.states.snapshot(h, n_tok)
-                if row is None:
-                    return snap
-                self._state_load(row, self.disk.get_state(h).to(self.pool.conv_state.device))
-                del self.disk_snaps[h]
-                self.recalled += 1
-                return self.states.snaps[h]
+            low = lower.get(h)
+            if low is None:
+                continue
+            if low.tier == "host":
+                raw = self.snap_host.pop(h)
+                self.snap_host_used -= raw.numel()
+            else:
+                raw = self.disk.get_state(h)            # the file stays: a restart can adopt it again
+            del lower[h]
+            row = self.states.snapshot(h, low.n_tokens, low.klass, low.rank, low.session)
+            if row is None:
+                return snap
+            self._state_load(row, raw.to(self.pool.conv_state.device))
+            self.recalled += 1
+            self.snap_recalled += 1
+            return self.states.snaps[h]
         return snap
 
     # -- checkpoint / adoption --------------------------------------------------------------------------------------------
@@ -259,9 +332,13 @@ class Rel:
                 parent, tag, toks = self._meta(h)
                 wrote += self.disk.spill(h, parent, toks, data, tag) and 1
         n_states = 0
+        own_budget = self.disk.state_capacity is not None          # with its own budget every lasting snapshot is worth a file
         for h, s in list(self.states.snaps.items()):
-            if s.klass == "durable" and h not in self.disk.states:
-                n_states += self.disk.put_state(h, s.n_tokens, self._state_bytes(s.row)) and 1
+            if (s.klass == "durable" or (own_budget and s.klass != "transient")) and h not in self.disk.states:
+                n_states += self._snap_to_disk(s, self._state_bytes(s.row).cpu()) and 1
+        for h, data in list(self.snap_host.items()):
+            if own_budget and h not in self.disk.states and h in self.states.lower:
+                n_states += self._snap_to_disk(self.states.lower[h], data) and 1
         n = self.disk.save_index(self.block_tokens)
         return {"blocks": wrote, "states": n_states, "indexed": n}
 
@@ -286,8 +363,10 @@ class Rel:
             if self.kv.adopt(h, rec["parent"], DISK, 0, rec.get("tag", 0)):
                 self.meta[h] = (rec["parent"], rec.get("tag", 0), toks)
                 self.adopted += 1
+        from .state import Snapshot
+
         for h, st in self.disk.states.items():
-            self.disk_snaps[h] = st["n_tokens"]
+            self.states.lower[h] = Snapshot(-1, h, st["n_tokens"], "durable", tier="disk")
         return {"blocks": self.adopted, "states": len(self.disk_snaps), "refused_blocks": bad}
 
     def facts(self) -> dict:
@@ -295,4 +374,7 @@ class Rel:
                 "disk_blocks": len(self.disk.index) if self.disk else 0, "disk_states": len(self.disk.states) if self.disk else 0,
                 "demoted": self.demoted, "spilled": self.spilled, "recalled": self.recalled, "dropped": self.dropped,
                 "adopted": self.adopted, "mover_copies": self.mover.copies if self.mover else 0,
+                "snapshots": {"live": len(self.states.snaps), "host": len(self.snap_host), "host_bytes": self.snap_host_used,
+                              "disk": len(self.disk_snaps), "demoted": self.snap_demoted, "spilled": self.snap_spilled,
+                              "recalled": self.snap_recalled, "dropped": self.snap_dropped, "cap_skips": self.states.skipped},
                 "last_verdict": None if self.last_verdict is None else vars(self.last_verdict)}

@@ -3,7 +3,8 @@
 ``StateStore`` lends recurrent-state rows (the concurrency ceiling) to running turns and keeps
 *snapshots*: copies of a row taken at block-aligned positions, keyed by the chain hash of the prefix
 they correspond to, so a prefix-cache hit can restore the linear-attention state that matches the
-reused KV blocks. Classes: transient (speculative rollback), durable (prefix boundaries), extra.
+reused KV blocks. Classes order the eviction (``store/snap_policy.py``); a snapshot whose row is recycled can move to a lower
+tier (pinned host memory, then disk) through the ``on_evict`` hook and stays findable in ``lower``.
 ``SessionTable`` maps a client ``session`` id to its last chain for multi-turn reuse.
 
 Reference counterpart: ``crates/store/src/{state,session}.rs``.
@@ -13,23 +14,37 @@ from __future__ import annotations
 import time
 from dataclasses import dataclass, field
 
+from . import snap_policy as P
+
 
 @dataclass
 class Snapshot:
-    row: int               # state row that holds the copy
+    row: int               # state row that holds the copy (-1 while the bytes live in a lower tier)
     chain_hash: int        # prefix identity (hash of the last block included)
     n_tokens: int
-    klass: str             # "transient" | "durable" | "extra"
+    klass: str             # "transient" | "extra" | "binary" | "tail" | "dense" | "durable" (eviction order, store/snap_policy.py)
+    rank: int = 0          # rung of the binary ladder
+    session: str | None = None
+    tier: str = "device"   # "device" | "host" | "disk"
     last_use: float = field(default_factory=time.monotonic)
 
 
 class StateStore:
-    def __init__(self, n_rows: int, n_snap_rows: int = 0):
-        """Rows 0..n_rows-1 are lendable; rows n_rows..n_rows+n_snap_rows-1 hold snapshots."""
+    def __init__(self, n_rows: int, n_snap_rows: int = 0, cap: P.SessionCap | None = None):
+        """Rows 0..n_rows-1 are lendable; rows n_rows..n_rows+n_snap_rows-1 hold snapshots.
+
+        ``on_evict(snapshot) -> "host" | "disk" | None`` is called before a snapshot's row is recycled: the owner of the
+        lower tiers copies the row's bytes away and answers where they went (None = dropped); the snapshot then stays
+        findable in ``lower``. ``on_forget(snapshot)`` tells that owner that a lower-tier snapshot is gone for good."""
         self.free_rows = list(range(n_rows - 1, -1, -1))
         self.snap_rows = list(range(n_rows + n_snap_rows - 1, n_rows - 1, -1))
-        self.snaps: dict[int, Snapshot] = {}     # chain_hash -> snapshot
+        self.snaps: dict[int, Snapshot] = {}     # chain_hash -> snapshot in a state row
+        self.lower: dict[int, Snapshot] = {}     # chain_hash -> snapshot whose bytes are on the host or on disk
         self.lent: dict[int, int] = {}           # turn -> row
+        self.cap = cap or P.SessionCap()
+        self.on_evict = None
+        self.on_forget = None
+        self.evicted = self.skipped = 0
 
     def borrow(self, turn: int) -> int | None:
         if not self.free_rows:
@@ -43,27 +58,61 @@ class StateStore:
         if r is not None:
             self.free_rows.append(r)
 
-    def snapshot(self, chain_hash: int, n_tokens: int, klass: str = "durable") -> int | None:
-        """Reserve a snapshot row for a prefix (evicting the least recently used one when full).
-        The caller copies the live row into the returned row."""
-        if chain_hash in self.snaps:
-            s = self.snaps[chain_hash]
+    # -- snapshots ------------------------------------------------------------------------------------------------------
+    def _recycle(self, s: Snapshot, demote: bool) -> None:
+        """Take a live snapshot out of its row; with ``demote`` the lower tiers get the chance to keep its bytes."""
+        del self.snaps[s.chain_hash]
+        tier = self.on_evict(s) if demote and self.on_evict is not None and s.klass != "transient" else None
+        self.snap_rows.append(s.row)
+        self.evicted += 1
+        if tier:
+            s.row, s.tier = -1, tier
+            self.lower[s.chain_hash] = s
+
+    def forget(self, chain_hash: int) -> None:
+        """Drop a snapshot wherever it lives (a rolling snapshot that was superseded, a session-cap replacement)."""
+        s = self.snaps.get(chain_hash)
+        if s is not None:
+            self._recycle(s, demote=False)
+            return
+        s = self.lower.pop(chain_hash, None)
+        if s is not None and self.on_forget is not None:
+            self.on_forget(s)
+
+    def of_session(self, session: str) -> list:
+        return [s for s in list(self.snaps.values()) + list(self.lower.values()) if s.session == session]
+
+    def snapshot(self, chain_hash: int, n_tokens: int, klass: str = "durable", rank: int = 0, session: str | None = None) -> int | None:
+        """Reserve a snapshot row for a prefix. The caller copies the live row into the returned row. When every row is
+        taken the snapshot that ``snap_policy.order_key`` ranks lowest leaves (to a lower tier when there is one); a session
+        at its cap replaces its own lowest-ranked snapshot or, if the newcomer ranks below everything held, gets None."""
+        s = self.snaps.get(chain_hash)
+        if s is not None:
             s.last_use = time.monotonic()
+            if P.PRIORITY[klass] > P.PRIORITY[s.klass]:
+                s.klass, s.rank = klass, rank
             return s.row
-        if not self.snap_rows:
-            victims = sorted((s for s in self.snaps.values() if s.klass != "durable"), key=lambda s: s.last_use) or \
-                sorted(self.snaps.values(), key=lambda s: s.last_use)
-            if not victims:
+        if session is not None and self.cap.cap > 0:
+            verdict, victim = self.cap.gate(self.of_session(session), klass, rank)
+            if verdict == "skip":
+                self.skipped += 1
                 return None
-            v = victims[0]
-            del self.snaps[v.chain_hash]
-            self.snap_rows.append(v.row)
+            if victim is not None:
+                self.forget(victim.chain_hash)
+        if not self.snap_rows:
+            if not self.snaps:
+                return None
+            v = min(self.snaps.values(), key=lambda x: P.order_key(x.klass, x.rank, x.last_use))
+            self._recycle(v, demote=True)
+        stale = self.lower.pop(chain_hash, None)          # being re-taken (or reloaded by the owner of the lower tiers)
+        if stale is not None and self.on_forget is not None:
+            self.on_forget(stale)
         row = self.snap_rows.pop()
-        self.snaps[chain_hash] = Snapshot(row, chain_hash, n_tokens, klass)
+        self.snaps[chain_hash] = Snapshot(row, chain_hash, n_tokens, klass, rank, session)
         return row
 
     def find(self, chain_hashes) -> Snapshot | None:
-        """Deepest snapshot along a chain (list of block hashes, shallow -> deep)."""
+        """Deepest live snapshot along a chain (list of block hashes, shallow -> deep)."""
         for h in reversed(list(chain_hashes)):
             s = self.snaps.get(int(h))
             if s:

@@ -225,9 +225,14 @@ class DiskTier:
     MAGIC = b"OWLB2IDX"
     VERSION = 2
 
-    def __init__(self, directory: str, page_bytes: int, capacity_bytes: int, background: bool = True):
+    def __init__(self, directory: str, page_bytes: int, capacity_bytes: int, background: bool = True,
+                 state_capacity: int | None = None):
+        """``state_capacity``: a budget of its own for the recurrent-state snapshot files (None: they share ``capacity_bytes``
+        with the blocks)."""
         import queue
         import threading
+
+        self.state_capacity, self.state_used = state_capacity, 0
 
         self.dir, self.page_bytes, self.capacity = directory, page_bytes, capacity_bytes
         os.makedirs(directory, exist_ok=True)
@@ -331,11 +336,16 @@ class DiskTier:
         nb = data.numel() * data.element_size()
         if h in self.states:
             return True
-        if self.used + nb > self.capacity:
-            return False
+        if self.state_capacity is not None:
+            if self.state_used + nb > self.state_capacity:
+                return False
+            self.state_used += nb
+        else:
+            if self.used + nb > self.capacity:
+                return False
+            self.used += nb
         self._put(self.state_path(h), data.cpu().contiguous().view(torch.uint8).numpy().tobytes())
         self.states[h] = {"n_tokens": int(n_tokens), "bytes": nb}
-        self.used += nb
         return True
 
     def get_state(self, h: int) -> torch.Tensor:
@@ -344,7 +354,10 @@ class DiskTier:
     def drop_state(self, h: int) -> None:
         st = self.states.pop(h, None)
         if st:
-            self.used -= st["bytes"]
+            if self.state_capacity is not None:
+                self.state_used -= st["bytes"]
+            else:
+                self.used -= st["bytes"]
             with self._lock:
                 self.pending.pop(self.state_path(h), None)
             try:
@@ -393,7 +406,11 @@ class DiskTier:
             off += 20
             if os.path.exists(self.state_path(h)) and os.path.getsize(self.state_path(h)) == nb:
                 self.states[h] = {"n_tokens": ntok, "bytes": nb}
-        self.used = len(self.index) * self.page_bytes + sum(s["bytes"] for s in self.states.values())
+        state_bytes = sum(s["bytes"] for s in self.states.values())
+        if self.state_capacity is not None:
+            self.used, self.state_used = len(self.index) * self.page_bytes, state_bytes
+        else:
+            self.used = len(self.index) * self.page_bytes + state_bytes
         return len(self.index)
 
     def chain_order(self) -> list[int]:

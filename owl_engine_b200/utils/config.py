@@ -61,17 +61,17 @@ SCHEMA: dict = {
                    "attention_factor": float},
     "store": {"prefix_cache": bool, "host_cache_mb": int, "snap_host_mb": int, "disk_cache_mb": int,
               "snap_disk_mb": int, "disk_dir": str, "vram_budget": float, "vram_reserve_mb": int, "no_reclaim": bool,
-              "block_tokens": Enum(16, 32), "evict_policy": Enum("lru", "lrfu")},
+              "block_tokens": Enum(16, 32), "evict_policy": str},
     "store.kv": {"kv_dtype": Enum("fp8", "int8", "bf16", "f16"), "draft_kv_dtype": Enum("bf16", "fp8")},
     "store.gdn": {"gdn_slots": int, "snap_decode_stride": int, "snap_max": int, "snap_msg_min_gap": int,
                   "snap_msg_recent": int, "snap_session_cap": int, "snap_structural_reserve": int},
     "spec": {"depth": int, "draft_path": str, "kind": Enum("none", "mtp", "dflash2"), "lookup": bool, "lookup_nmin": int,
              "lookup_nmax": int, "mtp_window": int, "mtp_sink": int, "mtp_ring": bool, "adaptive_depth": bool,
-             "depth_min": int, "tp_draft": bool, "degrade_after": int, "probe_every": int, "q_alpha": float,
+             "depth_min": int, "depth_switch_ctx": int, "tp_draft": bool, "degrade_after": int, "probe_every": int, "q_alpha": float,
              "q_floor": float, "force_accept": int},
     "vision": {"enabled": bool, "path": str, "max_pixels": int, "image_evict": bool, "image_evict_pad": str},
     "sampling": {"mode": Enum("greedy", "sampling"), "temp": float, "topk": int, "topp": float, "rep_penalty": float},
-    "load": {"verify": bool, "staging_mb": int, "repack": Enum("auto", "always", "never"), "dump": bool},
+    "load": {"verify": bool, "staging_mb": int, "repack": Enum("auto", "device", "cpu"), "dump": bool},
     "kvmem": {"select_decode": bool, "index": bool, "workspace_per_req": int, "select_sink": int, "select_recent": int,
               "select_query_tokens": int, "score_mode": Enum("cosine-max", "dot-max", "dot-mean"), "recall_every": int,
               "gqa_aggregation": Enum("max", "mean")},
@@ -82,7 +82,7 @@ SCHEMA: dict = {
                "prompt_dump": bool},
     "cuda": {"graph": bool, "launch_sync": bool, "trace_ring": int, "pinned_segment_mb": int},
     "log": {"level": Enum("error", "warn", "info", "debug", "trace"), "tags_allow": ListOf(str),
-            "tags_deny": ListOf(str), "max_mb": int, "keep": int, "timestamp": bool},
+            "tags_deny": ListOf(str), "file": str, "max_mb": int, "keep": int, "timestamp": bool},
 }
 OPTIONAL_SECTIONS = {"intent"}
 
@@ -292,6 +292,65 @@ def validate(cfg: OwlConfig) -> None:
         raise ConfigError("runtime.admission_on_full must be reject | queue | queue:<ms>")
     if v["spec"]["kind"] != "none" and v["spec"]["depth"] < 1:
         raise ConfigError("spec.depth must be >= 1 when a draft head is configured")
+    _validate_honoured(v)
+
+
+def _validate_honoured(v: dict) -> None:
+    """Keys whose value this build cannot honour are refused here, never ignored (the reference's loader rule): a profile
+    that asks for something that is not built must not start and then behave as if the key were not there."""
+    def refuse(cond: bool, msg: str) -> None:
+        if cond:
+            raise ConfigError(msg)
+
+    st, sp, km, kn = v["store"], v["spec"], v["kvmem"], v["kernel"]
+    pol, _, lam = st["evict_policy"].partition(":")
+    ok = (pol == "lru" and not lam) or pol == "lrfu"
+    if ok and lam:
+        try:
+            ok = float(lam) >= 0
+        except ValueError:
+            ok = False
+    refuse(not ok, f"store.evict_policy = {st['evict_policy']!r}: expected lru | lrfu | lrfu:<lambda >= 0>")
+    refuse(st["snap_disk_mb"] > 0 and not (st["host_cache_mb"] and st["disk_cache_mb"] and st["disk_dir"]),
+           "store.snap_disk_mb needs the disk tier: set store.host_cache_mb, store.disk_cache_mb and store.disk_dir")
+    refuse(min(st["host_cache_mb"], st["snap_host_mb"], st["disk_cache_mb"], st["snap_disk_mb"]) < 0, "store.*_mb must be >= 0")
+    g = v["store.gdn"]
+    refuse(g["snap_decode_stride"] < 0 or g["snap_msg_min_gap"] < 0 or g["snap_msg_recent"] < 0 or g["snap_session_cap"] < 0
+           or g["snap_structural_reserve"] < 0, "store.gdn.snap_* must be >= 0")
+    refuse(v["model"]["embed_quant"] != "bf16", "model.embed_quant = \"int8-row\": the int8 embedding table is not built; use bf16")
+    r = v["model.rope"]
+    refuse(r["yarn_factor"] < 1.0, "model.rope.yarn_factor must be >= 1.0 (1.0 = off)")
+    refuse(r["original_max"] < 0 or r["beta_fast"] <= 0 or r["beta_slow"] <= 0 or r["attention_factor"] <= 0,
+           "model.rope: original_max >= 0 and beta_fast, beta_slow, attention_factor > 0")
+    refuse(v["store.kv"]["draft_kv_dtype"] == "fp8" and sp["kind"] != "mtp",
+           "store.kv.draft_kv_dtype = \"fp8\" applies to the MTP head's KV pool: set spec.kind = \"mtp\" or leave it at bf16")
+    refuse(sp["mtp_window"] != 0 or sp["mtp_ring"], "spec.mtp_window / spec.mtp_ring: the windowed MTP attention and its ring "
+           "pool are not built; the MTP head attends to the whole context (mtp_window = 0, mtp_ring = false)")
+    refuse(sp["tp_draft"], "spec.tp_draft = true: the draft models are not tensor-parallel in this build")
+    refuse(sp["q_alpha"] != 1.0 or sp["q_floor"] != 0.0, "spec.q_alpha / spec.q_floor: served speculative rounds accept by greedy "
+           "agreement, so a calibration of the draft distribution has nothing to act on; leave them at 1.0 / 0.0")
+    refuse(sp["adaptive_depth"] and sp["kind"] != "mtp", "spec.adaptive_depth applies to the MTP head only")
+    refuse(sp["depth_min"] < 1 or sp["depth_min"] > 7 or sp["depth"] > 7, "spec.depth and spec.depth_min are at most 7 (and depth_min >= 1)")
+    refuse(sp["degrade_after"] < 0 or sp["probe_every"] < 1, "spec.degrade_after >= 0 and spec.probe_every >= 1")
+    refuse(sp["force_accept"] > 7, "spec.force_accept is at most 7 (-1 = off)")
+    if km["select_decode"]:
+        refuse(km["score_mode"] != "cosine-max", f"kvmem.score_mode = {km['score_mode']!r}: the GPU block scorer implements "
+               "cosine-max only")
+        refuse(km["gqa_aggregation"] != "max", "kvmem.gqa_aggregation = \"mean\": the GPU block scorer aggregates by max only")
+        refuse(km["recall_every"] < 1, "kvmem.recall_every must be >= 1")
+        refuse(not (1 <= km["select_query_tokens"] <= 64), "kvmem.select_query_tokens must be in 1..64")
+    refuse(not kn["gdn_fused_decode"], "kernel.gdn_fused_decode = false: the unfused one-token GDN path is not built")
+    refuse(kn["attn_splits"] < 0 or kn["attn_splits"] > 64, "kernel.attn_splits must be in 0..64 (0 = from the context length)")
+    cu = v["cuda"]
+    refuse(cu["launch_sync"] and cu["graph"], "cuda.launch_sync = true synchronises after every launch, which a graph capture "
+           "forbids: set cuda.graph = false with it")
+    refuse(not cu["graph"] and sp["kind"] in ("mtp", "dflash2"), "cuda.graph = false: the draft models' proposal chains exist "
+           "only as captured graphs; run them with cuda.graph = true or use lookup drafting")
+    refuse(cu["trace_ring"] < 0 or cu["pinned_segment_mb"] < 1, "cuda.trace_ring >= 0 and cuda.pinned_segment_mb >= 1")
+    refuse(v["load"]["staging_mb"] < 0, "load.staging_mb must be >= 0 (0 = no bound)")
+    lg = v["log"]
+    refuse((lg["max_mb"] or lg["keep"]) and not lg["file"], "log.max_mb / log.keep rotate log.file: set log.file")
+    refuse(v["probes"]["step_gate_ms"] < 0, "probes.step_gate_ms must be >= 0")
 
 
 def main_cli(argv: list[str] | None = None) -> int:
