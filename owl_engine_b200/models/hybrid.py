@@ -382,8 +382,8 @@ class HybridRunner:
         self.inv_freq = R.rope_inv_freq(spec.rotary_dim, spec.rope_theta).to(dev)
         yarn_scale = 1.0
         if getattr(spec, "rope_yarn", None):
-            factor, orig, bf, bs, af = spec.rope_yarn
-            inv, yarn_scale = R.rope_yarn(spec.rotary_dim, spec.rope_theta, factor, orig or spec.max_position, bf, bs, af)
+            y_factor, y_orig, y_fast, y_slow, y_att = spec.rope_yarn
+            inv, yarn_scale = R.rope_yarn(spec.rotary_dim, spec.rope_theta, y_factor, y_orig or spec.max_position, y_fast, y_slow, y_att)
             self.inv_freq = inv.to(dev)
         self.section = torch.tensor(mrope_section_map(spec), dtype=torch.uint8, device=dev)
         self.rope_scale = yarn_scale

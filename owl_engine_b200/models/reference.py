@@ -83,7 +83,10 @@ class RefModel:
         self.kv_fp8 = kv_fp8
         self.chunked_gdn = chunked_gdn
         self.linear_hook = linear_hook
-        self.inv_freq = R.rope_inv_freq(spec.rotary_dim, spec.rope_theta)
+        self.inv_freq, self.rope_scale = R.rope_inv_freq(spec.rotary_dim, spec.rope_theta), 1.0
+        if getattr(spec, "rope_yarn", None):
+            factor, orig, bf, bs, af = spec.rope_yarn
+            self.inv_freq, self.rope_scale = R.rope_yarn(spec.rotary_dim, spec.rope_theta, factor, orig or spec.max_position, bf, bs, af)
         self.section = mrope_section_map(spec)
 
     # -- helpers -------------------------------------------------------------------------
@@ -107,7 +110,7 @@ class RefModel:
         v = self.lin(a + "v_proj.weight", x).view(t, sp.hkv, sp.hd)
         q = R.rmsnorm(q, self.w[a + "q_norm.weight"], sp.eps)
         k = R.rmsnorm(k, self.w[a + "k_norm.weight"], sp.eps)
-        cos, sin = R.rope_cos_sin(pos3, self.inv_freq, self.section)
+        cos, sin = R.rope_cos_sin(pos3, self.inv_freq, self.section, self.rope_scale)
         q, k = R.apply_rope(q, cos, sin), R.apply_rope(k, cos, sin)
         if self.kv_fp8:
             k, v = R.fp8_e4m3_roundtrip(k), R.fp8_e4m3_roundtrip(v)
