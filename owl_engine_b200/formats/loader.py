@@ -172,6 +172,33 @@ class GgufProvider:
             t = torch.log(-t) if (t < 0).all() else t     # some converters store A = -exp(A_log)
         return t
 
+    def w4_shard(self, name: str, full: ModelSpec, plan: TpPlan):
+        """One rank's part of a Q4_K tensor, cut on the raw blocks of the memory-mapped file (row windows, block-aligned
+        column windows, value heads in grouped order) BEFORE the conversion to the int4 form, so a rank neither reads nor
+        converts the other ranks' parts. Returns None when the tensor has no raw plan that equals the canonical cut (another
+        block type, kv heads replicated over ranks, a column cut inside a super-block): the caller then reads it whole and
+        slices the int4 form. ``tests/test_loader.py`` checks that both routes give the same tensors."""
+        from . import gguf_shard as S
+
+        g = gguf_name(name)
+        t = self.f.tensors[g]
+        if plan.world == 1 or t.type != "Q4_K" or self.dims is None:
+            return None
+        r = rule_of(name)
+        if r is Rule.KV_COL and full.hkv % plan.world:
+            return None
+        if r is Rule.Q_COL and full.hq % plan.world:
+            return None
+        try:
+            p = self._plan(g, S.ShardSel(plan.rank, plan.world))
+        except S.ShardError:
+            return None
+        if p is None:
+            return None
+        raw = S.apply_raw(self.f.raw(g), tuple(t.shape), *gguf.BLOCK["Q4_K"], p)
+        self.shard_reads = getattr(self, "shard_reads", 0) + 1
+        return gguf.q4k_to_w4(raw.reshape(-1), p.shape[0], p.shape[1])
+
     def w4(self, name: str) -> Q.W4Canonical:
         from . import gguf_shard as S
 
@@ -411,7 +438,12 @@ def build_weights(full: ModelSpec, provider, device, rank: int = 0, world: int =
     bf = lambda t: put(t.to(torch.bfloat16))
     f32 = lambda t: put(t.float())
     dn = lambda name: shard_tensor(name, provider.dense(name), full, plan)
-    w4 = lambda name: shard_w4(name, provider.w4(name), full, plan)
+    def w4(name):
+        if world > 1 and hasattr(provider, "w4_shard"):
+            c = provider.w4_shard(name, full, plan)          # the rank's window straight from the file's blocks
+            if c is not None:
+                return c
+        return shard_w4(name, provider.w4(name), full, plan)
     def pack(c):
         if isinstance(c, NvCanonical):
             n, k = c.shape

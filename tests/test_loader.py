@@ -127,3 +127,56 @@ def test_gguf_q4k_file_loads(tmp_path, order):
         if name.endswith("A_log"):
             continue
         torch.testing.assert_close(prov.dense(k).float().view(-1), dense[k].float().view(-1), atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("order", ["grouped", "tiled"])
+def test_gguf_ranks_read_their_part_from_the_raw_blocks(tmp_path, order):
+    """Under tensor parallelism a rank cuts its window out of the file's Q4_K blocks before converting them; the result must
+    be the tensor that slicing the fully loaded int4 form gives, for every projection, and the built weights must be equal."""
+    from owl_engine_b200.parallel.plan import TpPlan
+
+    spec = make_spec(n_layers=4, vocab=512, mult=2)            # head counts a world of 2 divides (ssm_out heads: 128 wide)
+    dense = init_weights(spec, seed=5, std=0.05)
+    lin = set(_linear_names(spec))
+    tensors = {}
+    for k, v in dense.items():
+        g = loader.gguf_name(k)
+        a = v.float().numpy()
+        a = np.ascontiguousarray(a.reshape(a.shape[0], -1) if a.ndim == 3 else a)
+        if order == "tiled" and g.startswith("blk."):
+            a = np.ascontiguousarray(_to_file_order(g, a, spec))
+        if k.endswith(loader._PLUS_ONE_NORMS):
+            a = a + 1.0
+        tensors[g] = (tuple(a.shape), "Q4_K", gguf.quantize_q4_k(a)) if k in lin else (tuple(a.shape), "F32", a.view(np.uint8).reshape(-1))
+    meta = {"general.architecture": "qwen35", "qwen35.embedding_length": spec.hidden,
+            "qwen35.feed_forward_length": spec.inter, "qwen35.block_count": spec.n_layers,
+            "qwen35.attention.head_count": spec.hq, "qwen35.attention.head_count_kv": spec.hkv,
+            "qwen35.ssm.group_count": spec.nk, "qwen35.ssm.time_step_rank": spec.nv, "qwen35.vocab_size": spec.vocab}
+    if order == "grouped":
+        meta["owl.vhead_order"] = "grouped"
+    gguf.write_gguf(tmp_path / "m.gguf", meta, tensors)
+    _, prov, _ = loader.open_source(tmp_path / "m.gguf")
+    prov.set_dims(spec)
+    raw_route = 0
+    for rank in range(2):
+        plan = TpPlan(rank, 2)
+        for name in sorted(lin):
+            want = loader.shard_w4(name, prov.w4(name), spec, plan)
+            got = prov.w4_shard(name, spec, plan)
+            if got is None:
+                continue                                   # no raw plan (e.g. a super-block spanning two heads): whole read + slice
+            raw_route += 1
+            assert got.q.shape == want.q.shape, name
+            assert torch.equal(got.q, want.q) and torch.equal(got.scales, want.scales) and torch.equal(got.zeros, want.zeros), name
+    assert raw_route >= len(lin)                           # most projections take the raw route on both ranks
+    # the rank's built weights are the same whichever route read them
+    a = loader.build_weights(spec, prov, "cpu", rank=1, world=2)
+    reads = prov.shard_reads
+    prov.w4_shard = lambda *args, **kw: None
+    b = loader.build_weights(spec, prov, "cpu", rank=1, world=2)
+    assert reads > 0
+    for la, lb in zip(a.layers, b.layers):
+        for nm in ("gate_up", "down", "qkvz", "out_proj", "qkv", "o_proj"):
+            ta, tb = getattr(la, nm, None), getattr(lb, nm, None)
+            if ta is not None:
+                assert torch.equal(ta.records, tb.records), nm
