@@ -70,6 +70,37 @@ def open_tokenizer(cfg: C.OwlConfig):
         return ByteTokenizer()
 
 
+def load_vision_checkpoint(model_format: str, model_path: str, vision_path: str, default_spec, over: dict):
+    """(spec, weights) of the vision tower. A GGUF language model takes its tower from the projector file next to it
+    (``mmproj*.gguf``, or the file ``[vision] path`` names); otherwise ``[vision] path`` (or the model directory) is an HF
+    safetensors directory whose ``[model.]visual.*`` tensors and ``config.json`` ``vision_config`` describe it. Without any
+    checkpoint the tower is random-init with the default geometry (``weights = None``)."""
+    import json as _json
+    import os
+
+    from ..formats import vision_weights as VW
+
+    if model_format == "gguf" and model_path:
+        return VW.load_mmproj(model_path, vision_path or None, **over)
+    src_dir = vision_path or (model_path if model_path and os.path.isdir(model_path) else "")
+    if not src_dir:
+        return default_spec, None
+    from ..formats.safetensors import SafeDir
+
+    src = SafeDir(src_dir)
+    w = VW.from_hf({k: src.get(k) for k in src.keys() if "visual." in k})
+    if not w:
+        raise VW.VisionLoadError(f"{src_dir}: no visual.* tensors (vision is enabled but this checkpoint has no tower)")
+    spec = default_spec
+    cfg_json = os.path.join(src_dir, "config.json")
+    if os.path.exists(cfg_json):
+        vc = _json.load(open(cfg_json)).get("vision_config")
+        if vc:
+            spec = VW.spec_from_hf(vc, **over)
+    VW.check_complete(spec, w)
+    return spec, w
+
+
 def evict_pad_token(cfg: C.OwlConfig, tok) -> int:
     """``[vision] image_evict_pad``: the filler that page-aligns a droppable segment must be exactly one token. An empty
     setting tries an ideographic full stop, a space, then a newline."""
@@ -308,18 +339,23 @@ def main(argv=None) -> int:
         import torch
 
         from ..models.spec import PRESETS
-        from ..models.vision import VisionSpec, VisionTower
+        from ..models.vision import VisionSpec
         from .http import Vision
 
         hidden = PRESETS[v["model"]["name"]]().hidden if v["model"]["name"] in PRESETS else 5120
-        vspec = VisionSpec(out_hidden=hidden, max_pixels=v["vision"]["max_pixels"] or VisionSpec.max_pixels)
-        vweights = None
-        if v["vision"]["path"]:
-            from ..formats.safetensors import SafeDir
+        over = {"max_pixels": v["vision"]["max_pixels"]} if v["vision"]["max_pixels"] else {}
+        vspec, vweights = VisionSpec(out_hidden=hidden, **over), None
+        try:
+            vspec, vweights = load_vision_checkpoint(v["model"]["format"], v["model"]["path"], v["vision"]["path"], vspec, over)
+        except ValueError as e:
+            print(f"config error: {e}", file=sys.stderr)
+            return 2
+        # the tower runs on the package's own kernels (csrc/vision.cu + the dense tcgen05 GEMM); the eager PyTorch tower is its
+        # test oracle
+        from ..models.vision import VisionTowerKernels
 
-            src = SafeDir(v["vision"]["path"])
-            vweights = {k.removeprefix("visual.").removeprefix("model.visual."): src.get(k) for k in src.keys() if "visual" in k or "blocks." in k or "merger." in k or "patch_embed" in k or "pos_embed" in k}
-        vision = Vision(VisionTower(vspec, vweights, device="cuda:0", dtype=torch.bfloat16), getattr(tok, "image_pad_id", None) or 0)
+        vision = Vision(VisionTowerKernels(vspec, vweights, device=f"cuda:{torch.cuda.current_device()}"),
+                        getattr(tok, "image_pad_id", None) or 0)
     s = v["sampling"]
     app = App(client, tok, v["model"]["name"], ChatTemplate(v["server"]["template_path"], v["server"]["template_vars"]),
               SamplingParams(s["mode"], s["temp"], s["topk"], s["topp"], s["rep_penalty"]), v["runtime"]["default_max_new"],
