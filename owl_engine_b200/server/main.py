@@ -228,7 +228,11 @@ def build_spec_factory(cfg: C.OwlConfig):
             taps = D.DraftSpec.taps if n >= 62 else tuple(sorted({max(0, n * (2 * i + 1) // 10 - 1) for i in range(5)}))
             dspec = D.DraftSpec(hidden=ts.hidden, vocab=ts.vocab, inter=ts.inter, taps=taps, mask_token_id=ts.vocab - 1,
                                 rope_theta=ts.rope_theta)
-            if sp["draft_path"]:
+            if sp["draft_path"].endswith(".gguf"):
+                from ..formats import dflash_gguf
+
+                dspec, dw = dflash_gguf.load_draft(sp["draft_path"], ts, engine.device)     # facts from the file's dflash.* keys
+            elif sp["draft_path"]:
                 from ..formats.safetensors import SafeDir
 
                 src = SafeDir(sp["draft_path"])
