@@ -170,7 +170,9 @@ def build_engine_factory(cfg: C.OwlConfig, plan: dict | None = None, msg_open_id
                             pinned_segment_mb=v["cuda"]["pinned_segment_mb"],
                             rope_yarn=(rp["yarn_factor"], rp["original_max"], rp["beta_fast"], rp["beta_slow"],
                                        rp["attention_factor"]) if rp["yarn_factor"] > 1.0 else None,
-                            kvmem_query_tokens=km["select_query_tokens"], kvmem_recall_every=km["recall_every"])
+                            kvmem_query_tokens=km["select_query_tokens"], kvmem_recall_every=km["recall_every"],
+                            # speculative rounds of several decoding turns run as one batched verify: one scratch state row each
+                            spec_rows=min(v["runtime"]["max_batch"], 8) if (v["spec"]["kind"] != "none" or v["spec"]["lookup"]) else 1)
         if v["kernel"]["selfcheck"]:
             from ..ops import selfcheck
 
@@ -188,6 +190,19 @@ def build_engine_factory(cfg: C.OwlConfig, plan: dict | None = None, msg_open_id
             eng = Engine(ecfg, spec=spec, weights=weights, comm=comm)
         if comm is not None:
             eng.runner.sp_prefill = plan["fused_gemm"]
+        if v["cuda"]["graph"]:
+            # every rank captures the same fleet in the same order (a capture's warm-up step runs the collectives)
+            from ..engine.graph_fleet import GraphFleet
+
+            sp = v["spec"]
+            spec_on = sp["kind"] != "none" or sp["lookup"]
+            if spec_on:
+                eng.runner.uniform_rows = True        # what the speculative runner switches on at its first round anyway
+            fleet = GraphFleet(eng, max_batch=v["runtime"]["max_batch"], spec_depths=(max(1, min(7, sp["depth"] or 3)),) if spec_on else (),
+                               spec_rows=ecfg.spec_rows)
+            rep = fleet.assemble()
+            eng.graph_fleet = fleet
+            log.info("boot.graphs", f"{rep['states']} in {rep['capture_ms']:.0f} ms, {rep['bytes'] >> 20} MiB")
             if plan["rank"] == 0:
                 from ..engine.tp_serve import MirroredEngine, leader_ring
 

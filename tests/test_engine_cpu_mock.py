@@ -139,3 +139,21 @@ def test_http_server_end_to_end_on_the_cpu_face():
         asyncio.run(main())
     finally:
         assert svc.shutdown().code == 0
+
+
+def test_graph_fleet_plans_and_meters_on_the_cpu_face():
+    """The fleet lists every step shape the profile can reach and captures them at boot; on the CPU face a capture is a
+    replay object and costs no device memory, and a face that cannot capture leaves its entries eager with the reason."""
+    from owl_engine_b200.engine.graph_fleet import GraphFleet
+
+    e = Engine(cfg(), device="cpu")
+    fleet = GraphFleet(e, max_batch=4, spec_depths=(3,), spec_rows=2)
+    names = [en.name for en in fleet.entries]
+    assert names[:4] == ["graph.decode.b1.ctx2048", "graph.decode.b2.ctx2048", "graph.decode.b3.ctx2048", "graph.decode.b4.ctx2048"]
+    assert "graph.verify.b1.t4.ctx2048" in names and "graph.batch_spec.b2.t4.ctx2048" in names and "graph.fold.b1.t4" in names
+    rep = fleet.assemble()
+    assert rep["states"].get("captured", 0) == 6 and rep["states"].get("eager", 0) == 2          # the stand-in runner has no fold
+    assert {(4, 1), (1, 4), (2, 4)} <= set(e.runner.graphs) and rep["bytes"] == 0
+    off = Engine(cfg(), device="cpu", limits=MockLimits(graph_capture=False))
+    rep = GraphFleet(off, max_batch=2).assemble()
+    assert rep["states"] == {"eager": 2} and "CaptureUnsupported" in rep["entries"][0]["error"]

@@ -130,3 +130,17 @@ def test_kv_selection_scores_with_the_query_window():
     seq = e.seqs[sid]
     assert seq.q_ring is not None and seq.q_ring_n == 20 and seq.q_ring.abs().sum().item() > 0
     assert len(seq.view) <= 256 // 16 + 2 and seq.view[-1] == seq.n_cached // 16
+
+
+def test_graph_fleet_captures_at_boot_and_meters_into_the_ledger():
+    from owl_engine_b200.engine.graph_fleet import GraphFleet
+
+    e = Engine(cfg(spec_rows=2))
+    e.runner.uniform_rows = True
+    fleet = GraphFleet(e, max_batch=3, spec_depths=(3,), spec_rows=2)
+    rep = fleet.assemble()
+    assert rep["states"] == {"captured": len(fleet.entries)} and rep["bytes"] > 0
+    assert e.ledger.by_class().get("graphs", 0) == rep["bytes"]
+    n = len(e.runner.graphs)
+    out = e.generate(toks(70, 9), 10)                       # decode replays what the fleet captured: no new graph
+    assert len(out) == 10 and len(e.runner.graphs) == n
