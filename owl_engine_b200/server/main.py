@@ -198,8 +198,12 @@ def build_engine_factory(cfg: C.OwlConfig, plan: dict | None = None, msg_open_id
             spec_on = sp["kind"] != "none" or sp["lookup"]
             if spec_on:
                 eng.runner.uniform_rows = True        # what the speculative runner switches on at its first round anyway
+            buckets, bk = [], 512             # the context buckets a step can fall into (`Engine._ctx_bucket`)
+            while bk < 2 * v["runtime"]["max_seq"]:
+                buckets.append(bk)
+                bk *= 2
             fleet = GraphFleet(eng, max_batch=v["runtime"]["max_batch"], spec_depths=(max(1, min(7, sp["depth"] or 3)),) if spec_on else (),
-                               spec_rows=ecfg.spec_rows)
+                               spec_rows=ecfg.spec_rows, ctx_buckets=tuple(buckets))
             rep = fleet.assemble()
             eng.graph_fleet = fleet
             log.info("boot.graphs", f"{rep['states']} in {rep['capture_ms']:.0f} ms, {rep['bytes'] >> 20} MiB")
