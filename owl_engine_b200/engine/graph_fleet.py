@@ -84,6 +84,12 @@ class GraphFleet:
 
         led, r = self.e.ledger, self.e.runner
         eager = not getattr(r, "use_graphs", True)
+        if any(en.kind != "decode" for en in self.entries):
+            # speculative steps keep every GDN layer's inputs for the fold and use row-count-independent arithmetic; both
+            # switches re-point buffers (and would drop graphs captured before them), so they come first
+            if hasattr(r, "enable_gdn_save"):
+                r.enable_gdn_save()
+            r.uniform_rows = True
         for en in self.entries:
             if en.state != "planned":
                 continue

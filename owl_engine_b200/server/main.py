@@ -190,14 +190,13 @@ def build_engine_factory(cfg: C.OwlConfig, plan: dict | None = None, msg_open_id
             eng = Engine(ecfg, spec=spec, weights=weights, comm=comm)
         if comm is not None:
             eng.runner.sp_prefill = plan["fused_gemm"]
-        if v["cuda"]["graph"]:
-            # every rank captures the same fleet in the same order (a capture's warm-up step runs the collectives)
+        if v["cuda"]["graph"] and comm is None:
+            # single-GPU profiles capture their graphs at boot; tensor-parallel ranks keep capturing a shape at its first
+            # use, in lockstep through the mirrored step calls (a capture's warm-up step runs the collectives)
             from ..engine.graph_fleet import GraphFleet
 
             sp = v["spec"]
             spec_on = sp["kind"] != "none" or sp["lookup"]
-            if spec_on:
-                eng.runner.uniform_rows = True        # what the speculative runner switches on at its first round anyway
             buckets, bk = [], 512             # the context buckets a step can fall into (`Engine._ctx_bucket`)
             while bk < 2 * v["runtime"]["max_seq"]:
                 buckets.append(bk)
@@ -207,10 +206,10 @@ def build_engine_factory(cfg: C.OwlConfig, plan: dict | None = None, msg_open_id
             rep = fleet.assemble()
             eng.graph_fleet = fleet
             log.info("boot.graphs", f"{rep['states']} in {rep['capture_ms']:.0f} ms, {rep['bytes'] >> 20} MiB")
-            if plan["rank"] == 0:
-                from ..engine.tp_serve import MirroredEngine, leader_ring
+        if comm is not None and plan["rank"] == 0:
+            from ..engine.tp_serve import MirroredEngine, leader_ring
 
-                return MirroredEngine(eng, leader_ring(plan["world"]))
+            return MirroredEngine(eng, leader_ring(plan["world"]))
         return eng
     return build
 

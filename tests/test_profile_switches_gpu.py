@@ -136,7 +136,6 @@ def test_graph_fleet_captures_at_boot_and_meters_into_the_ledger():
     from owl_engine_b200.engine.graph_fleet import GraphFleet
 
     e = Engine(cfg(spec_rows=2))
-    e.runner.uniform_rows = True
     fleet = GraphFleet(e, max_batch=3, spec_depths=(3,), spec_rows=2, ctx_buckets=(512, 1024))
     rep = fleet.assemble()
     assert rep["states"] == {"captured": len(fleet.entries)} and rep["bytes"] >= 0
@@ -145,3 +144,109 @@ def test_graph_fleet_captures_at_boot_and_meters_into_the_ledger():
     n = len(e.runner.graphs)
     out = e.generate(toks(70, 9), 10)                       # decode replays what the fleet captured: no new graph
     assert len(out) == 10 and len(e.runner.graphs) == n
+
+
+def _server_proc(profile, q):
+    import os
+
+    for k in ("WORLD_SIZE", "RANK", "LOCAL_RANK"):
+        os.environ.pop(k, None)
+    from owl_engine_b200.server import main as M
+
+    q.put(M.main(["-p", profile, "--log-level", "info"]))
+
+
+def test_server_main_boots_a_profile_that_uses_the_switches(tmp_path):
+    """The product's entry point on one GPU with a profile that turns the optional machinery on: message / generation
+    snapshots, LRFU eviction, lookup drafting (so the boot captures verify and fold graphs too), checkpoint verification with a
+    1 MiB upload stager, request dumps, step profile. Two conversations share a system prompt: the second is served from the
+    snapshot at the message boundary."""
+    import http.client
+    import json
+    import multiprocessing as mp
+    import os
+    import sys
+    import time
+
+    sys.path.insert(0, os.path.dirname(__file__))
+    from test_tp_gpu import _free_port, _shutdown, _write_checkpoint
+
+    ckpt, port = str(tmp_path / "ckpt"), _free_port()
+    _write_checkpoint(ckpt)
+    root = os.path.abspath(os.path.join(os.path.dirname(__file__), "..", "configs", "full.toml"))
+    prof = tmp_path / "p.toml"
+    prof.write_text(f'''extends = ["{root}"]
+[server]
+bind = "127.0.0.1:{port}"
+request_dump_dir = "{tmp_path / 'dumps'}"
+[model]
+name = "test-hybrid"
+path = "{ckpt}"
+format = "safetensors"
+[runtime]
+max_seq = 1024
+prefill_chunk = 64
+max_batch = 3
+default_max_new = 16
+[store]
+evict_policy = "lrfu:0.1"
+snap_host_mb = 64
+[store.gdn]
+gdn_slots = 3
+snap_max = 4
+snap_msg_min_gap = 32
+[spec]
+lookup = true
+depth = 3
+[load]
+verify = true
+staging_mb = 1
+[probes]
+step_profile = true
+prompt_dump = true
+[cuda]
+trace_ring = 128
+[kernel]
+selfcheck = false
+''')
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    p = ctx.Process(target=_server_proc, args=(str(prof), q))
+    p.start()
+
+    def post(body, timeout=180.0):
+        t0 = time.time()
+        while True:
+            try:
+                c = http.client.HTTPConnection("127.0.0.1", port, timeout=120)
+                c.request("POST", "/v1/chat/completions", json.dumps(body), {"Content-Type": "application/json"})
+                r = c.getresponse()
+                raw = r.read().decode()
+                c.close()
+                assert r.status == 200, raw
+                return json.loads(raw)
+            except (ConnectionRefusedError, ConnectionResetError):
+                if time.time() - t0 > timeout or not p.is_alive():
+                    raise
+                time.sleep(0.5)
+    try:
+        system = "You are a careful assistant. " * 12
+        outs = [post({"messages": [{"role": "system", "content": system}, {"role": "user", "content": u}], "max_tokens": 20,
+                      "ignore_eos": True}) for u in ("first question", "another, longer second question")]
+        c = http.client.HTTPConnection("127.0.0.1", port, timeout=30)
+        c.request("GET", "/debug/launches/8")
+        dbg = json.loads(c.getresponse().read())
+        c.close()
+    finally:
+        try:
+            _shutdown(port)
+        except Exception:   # noqa: BLE001
+            pass
+        p.join(timeout=120)
+    assert p.exitcode == 0 and q.get(timeout=10) == 0
+    cached = [o["usage"].get("prompt_tokens_details", {}).get("cached_tokens", o["usage"].get("cached_tokens", 0)) for o in outs]
+    assert cached[0] == 0 and cached[1] >= 256 and cached[1] % 16 == 0
+    assert all(o["usage"]["completion_tokens"] == 20 for o in outs)
+    fleet = dbg["fleet"]
+    assert fleet and fleet["states"].get("captured", 0) >= 3 and any("verify" in e["name"] for e in fleet["entries"])
+    assert len(dbg["launches"]) == 8 and len(os.listdir(tmp_path / "dumps")) == 2
