@@ -725,6 +725,43 @@ class Engine:
         run.block_table[row, :len(seq.view)] = torch.tensor([seq.pages[b] for b in seq.view], dtype=torch.int32, device=dev)
         return len(seq.view)
 
+    def pool_keys(self, sid: int, layer: int | None = None) -> torch.Tensor:
+        """The cached keys of a sequence as float ``[n_cached, hkv, hd]`` (rotated, as the attention kernels read them), read
+        from the paged pool of one full-attention layer (default: the last, the one the KV-selection index is built on)."""
+        seq = self.seqs[sid]
+        fi = self.spec.n_full - 1 if layer is None else layer
+        n = seq.n_cached
+        pages = torch.tensor(seq.pages[:(n + PAGE - 1) // PAGE], dtype=torch.long, device=self.device)
+        raw = self.pool.k_pool[fi][pages]                                  # [pages, 16, hkv, hd]
+        if raw.dtype == torch.float16:
+            k = raw.float()
+        elif self.pool.k_scale is not None:
+            k = raw.view(torch.int8).float() * self.pool.k_scale[fi][pages][..., None]
+        else:
+            k = raw.view(torch.float8_e4m3fn).float()
+        return k.reshape(-1, k.shape[-2], k.shape[-1])[:n]
+
+    def coverage_probe(self, sid: int, ks=(1, 2, 4, 8, 16, 32)) -> dict:
+        """How much of the true attention mass of the sequence's newest queries lies in the blocks the Mean-K index scores
+        highest (``store/coverage.py``). Queries: the sequence's query window when KV selection keeps one, else the query of
+        its last decode step. Read-only; runs on the host."""
+        from ..store import coverage as C
+
+        seq = self.seqs[sid]
+        if seq.q_ring is not None and seq.q_ring_n:
+            n = min(seq.q_ring_n, seq.q_ring.shape[0])
+            q, qpos = seq.q_ring[:n].float().cpu(), seq.q_ring_pos[:n].cpu()
+        else:
+            row = self._last_rows.get(sid)
+            if row is None:
+                raise RuntimeError("coverage probe: the sequence has no decode step yet (no query to probe with)")
+            q = self.runner.q_rope[row:row + 1].float().cpu()
+            qpos = torch.tensor([seq.n_cached - 1 + seq.rope_delta])
+        k = self.pool_keys(sid).cpu()
+        if seq.rope_delta:
+            raise RuntimeError("coverage probe: sequences with shifted positions (images, leave-gap deletions) are not supported")
+        return C.probe(q, qpos, k, self.runner.inv_freq.cpu(), self.spec.rotary_dim, PAGE, ks)
+
     @staticmethod
     def _ctx_bucket(ctx: int) -> int:
         """Context-length bucket that picks the split-KV factor of the captured graph."""

@@ -250,3 +250,17 @@ selfcheck = false
     fleet = dbg["fleet"]
     assert fleet and fleet["states"].get("captured", 0) >= 3 and any("verify" in e["name"] for e in fleet["entries"])
     assert len(dbg["launches"]) == 8 and len(os.listdir(tmp_path / "dumps")) == 2
+
+
+def test_coverage_probe_reads_the_pool_and_the_last_query():
+    e = Engine(cfg(n_pages=256, max_seq=2048))
+    sid = e.add_sequence(toks(400, 11), reuse=False)
+    e.prefill(sid)
+    for _ in range(3):
+        e.decode_step([sid])
+    k = e.pool_keys(sid)
+    assert k.shape == (e.seqs[sid].n_cached, e.spec.hkv, e.spec.hd) and torch.isfinite(k).all() and k.abs().sum() > 0
+    rep = e.coverage_probe(sid, ks=(1, 4, 16))
+    assert rep["blocks"] == (e.seqs[sid].n_cached + 15) // 16
+    for k_, c in rep["curve"].items():
+        assert 0.0 <= c["index"] <= c["oracle"] + 1e-6 <= 1.0 + 1e-6 and c["chance"] == min(k_, rep["blocks"]) / rep["blocks"]

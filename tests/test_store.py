@@ -110,3 +110,35 @@ def test_state_store_and_sessions():
     t = SessionTable()
     t.commit("s", [1, 2, 3, 4])
     assert t.common_prefix(t.get_or_create("s").tokens, [1, 2, 9]) == 2
+
+
+def test_coverage_probe_finds_the_block_the_queries_attend_to():
+    """Keys of one block point along the query direction: the true attention mass concentrates there, and the Mean-K index
+    must rank that block first (index curve = oracle curve at k = 1, far above chance). A scrambled index falls to chance."""
+    import torch
+
+    from owl_engine_b200.ops import reference as R
+    from owl_engine_b200.store import coverage as C
+    from owl_engine_b200.store import select as S
+
+    g = torch.Generator().manual_seed(0)
+    T, block, hq, hkv, hd, rot = 256, 16, 4, 2, 64, 32
+    inv = R.rope_inv_freq(rot, 1e4)
+    direction = torch.randn(hkv, hd, generator=g)
+    k = torch.randn(T, hkv, hd, generator=g) * 0.3
+    k[5 * block:6 * block] += 2.0 * direction                        # the needle block (de-rotated space)
+    q = (direction.repeat_interleave(hq // hkv, 0) * 1.5 + torch.randn(3, hq, hd, generator=g) * 0.2)
+    ang = lambda pos: (pos.float()[:, None] * inv[None, :], )
+    kc, ks = ang(torch.arange(T))[0].cos(), ang(torch.arange(T))[0].sin()
+    qpos = torch.tensor([T, T + 1, T + 2])
+    qc, qs = ang(qpos)[0].cos(), ang(qpos)[0].sin()
+    rope = lambda x, c, s: S.derope(x, c, -s)                           # rotating = de-rotating by the negative angle
+    rep = C.probe(rope(q, qc, qs), qpos, rope(k, kc, ks), inv, rot, block, ks=(1, 4))
+    assert rep["blocks"] == 16
+    one = rep["curve"][1]
+    assert one["index"] == one["oracle"] and one["index"] > 0.5 and one["chance"] == 1 / 16
+    assert rep["spearman"] > 0.3
+    mass = C.block_mass(rope(q, qc, qs), rope(k, kc, ks), block)
+    assert abs(float(mass.sum()) - 1.0) < 1e-5 and int(mass.argmax()) == 5
+    scrambled = C.coverage_curve(mass, torch.arange(16).float(), ks=(1,))[1]      # scores unrelated to the mass
+    assert scrambled["index"] < 0.2
