@@ -302,6 +302,19 @@ class StepLayout:
         self.size = 5 * m + 3 * b
 
 
+class _CapturedStep:
+    """A captured CUDA graph with its manifest: the native launches the capture recorded, and how often it was replayed.
+    A replay is invisible to the host-side launch ring (the graph launches its kernels itself), so this is what attributes
+    device work to entries when steps run from graphs."""
+
+    def __init__(self, graph, launches: list):
+        self.graph, self.launches, self.replays = graph, launches, 0
+
+    def replay(self) -> None:
+        self.replays += 1
+        self.graph.replay()
+
+
 class _EagerStep:
     """Stands in for a captured graph when steps run eagerly: ``replay()`` launches the kernel sequence directly."""
 
@@ -884,6 +897,7 @@ class HybridRunner:
             sched, self._pf_rec = self._pf_rec, None
             stream.synchronize()
             graph = torch.cuda.CUDAGraph()
+            mark = K.launch_seq()
             with torch.cuda.graph(graph, stream=stream):
                 if prefetch and sched:
                     side = torch.cuda.Stream(device=self.device)
@@ -896,8 +910,21 @@ class HybridRunner:
                         self._pf_play = None
             self.inp.copy_(saved)
         torch.cuda.current_stream().wait_stream(stream)
-        self.graphs[key] = graph
-        return graph
+        self.graphs[key] = _CapturedStep(graph, K.launches_since(mark))
+        return self.graphs[key]
+
+    def graph_manifest(self) -> list[dict]:
+        """Per captured step graph: its key, how often it was replayed, and the native entries one replay launches (with
+        their multiplicity), so that device work is attributable to entries although replays bypass the launch ring."""
+        out = []
+        for key, g in self.graphs.items():
+            if isinstance(g, _CapturedStep):
+                counts: dict = {}
+                for name in g.launches:
+                    counts[name] = counts.get(name, 0) + 1
+                out.append({"key": [str(k) for k in key] if isinstance(key, tuple) else str(key), "replays": g.replays,
+                            "launches_per_replay": len(g.launches), "entries": counts})
+        return out
 
     # -- prefill ---------------------------------------------------------------------------------
     def _prefill_ws(self, t: int):

@@ -112,6 +112,16 @@ def call(name: str, *args) -> None:
             raise RuntimeError(f"{name} (launch {_launch_seq}): a bounded wait ran out {bad}")
 
 
+def launch_seq() -> int:
+    """Sequence number of the newest launch (a mark for ``launches_since``)."""
+    return _launch_seq
+
+
+def launches_since(mark: int) -> list[str]:
+    """Entry names of the launches made after ``mark`` that are still in the ring, oldest first."""
+    return [name for seq, name, _ in _LAUNCHES if seq > mark]
+
+
 def recent_launches(n: int = 256) -> list[dict]:
     """The last ``n`` launches: sequence number, entry, stream handle and the small integer arguments (shapes, modes)."""
     out = []

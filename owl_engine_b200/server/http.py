@@ -176,6 +176,7 @@ class App:
 
             return await self._send(w, 200, q(lambda re: {"graphs": [list(k) for k in re.e.runner.graphs.keys()],
                                                            "fleet": re.e.graph_fleet.facts() if getattr(re.e, "graph_fleet", None) else None,
+                                                           "graph_manifest": re.e.runner.graph_manifest() if hasattr(re.e.runner, "graph_manifest") else [],
                                                            "launches": K.recent_launches(n), "status": K.all_status()}))
         if parts[0] == "shutdown" and method == "POST":
             # orderly stop (tests, supervisors): the listener loop sees the flag, the engine thread checkpoints and exits

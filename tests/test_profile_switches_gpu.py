@@ -250,6 +250,8 @@ selfcheck = false
     fleet = dbg["fleet"]
     assert fleet and fleet["states"].get("captured", 0) >= 3 and any("verify" in e["name"] for e in fleet["entries"])
     assert len(dbg["launches"]) == 8 and len(os.listdir(tmp_path / "dumps")) == 2
+    used = [g for g in dbg["graph_manifest"] if g["replays"] > 0]
+    assert used and all(g["launches_per_replay"] > 0 and sum(g["entries"].values()) == g["launches_per_replay"] for g in used)
 
 
 def test_coverage_probe_reads_the_pool_and_the_last_query():
