@@ -392,8 +392,10 @@ class Engine:
         sequence's rolling snapshot (the previous one is released), keyed like the blocks ``free_sequence`` will publish."""
         from ..store.snap_policy import decode_boundary
 
-        if seq.chain is None or seq.gap_from is not None:
+        if seq.gap_from is not None or not self.cfg.prefix_cache:
             return
+        if seq.chain is None:
+            seq.chain = np.zeros(0, dtype=np.uint64)          # a prompt shorter than a page: the chain starts with the answer
         b = decode_boundary(pos_before, seq.n_cached, PAGE, self.cfg.snap_decode_stride)
         if b is None or b != seq.n_cached:
             return

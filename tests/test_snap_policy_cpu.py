@@ -239,3 +239,38 @@ def test_prefix_cache_off_and_no_reclaim():
     assert e.kv.stats()["evictions"] == evictions
     sid = e.add_sequence(toks(150, 1))
     assert e.seqs[sid].reused == 144                     # the first prompt's blocks are all still there
+
+
+def test_generation_snapshots_start_a_chain_for_a_prompt_shorter_than_a_page():
+    e = Engine(cfg(snap_decode_stride=1, msg_open_ids=()), device="cpu")
+    prompt = toks(9, 77)
+    answer = e.generate(prompt, 50)
+    follow = prompt + answer + toks(12, 78)
+    sid = e.add_sequence(follow)
+    assert e.seqs[sid].reused == (9 + 49) // 16 * 16
+    e.free_sequence(sid, publish=False)
+    assert e.generate(follow, 6) == Engine(cfg(msg_open_ids=()), device="cpu").generate(follow, 6)
+
+
+def test_running_engine_tags_snapshots_with_the_session_and_respects_its_cap():
+    from owl_engine_b200.engine.running import RunningEngine, TurnOpts
+
+    def run(cap):
+        e = Engine(cfg(snap_decode_stride=1, snap_session_cap=cap, snap_structural_reserve=1, snap_msg_min_gap=0, snap_msg_recent=8,
+                       n_snap_rows=8), device="cpu")
+        re_ = RunningEngine(e, max_batch=2)
+        history, outs = msg(60, 1), []
+        for turn in range(3):
+            out = re_.generate(history, TurnOpts(max_new=20, ignore_eos=True, session="s"))
+            outs.append(out)
+            history = history + out + msg(40, 10 + turn)
+        other = re_.generate(msg(50, 99), TurnOpts(max_new=8, ignore_eos=True, session="t"))
+        return e, outs, other
+    free, outs_free, _ = run(0)
+    capped, outs_cap, _ = run(3)
+    assert outs_cap == outs_free                                      # a cap changes what is kept, never what is computed
+    assert len(free.states.of_session("s")) > 3
+    held = capped.states.of_session("s")
+    assert 0 < len(held) <= 3 and capped.states.of_session("t")
+    assert sum(s.klass == "extra" for s in held) <= 2                  # cap - reserve
+    assert any(s.klass in ("durable", "tail", "dense") for s in held)  # what the next turn resumes from survived
