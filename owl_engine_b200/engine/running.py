@@ -60,13 +60,18 @@ class Turn:
 class RunningEngine:
     def __init__(self, engine: Engine, max_batch: int = 8, on_full: str = "reject", spec_runner=None,
                  park_sessions: bool = False, max_parked: int = 2, evict_pad_id: int = 0, prefill_every: int = 8,
-                 step_profile: bool = False):
+                 step_profile: bool = False, auto_sessions: bool = False):
         """``park_sessions``: a finished turn of a named session keeps its sequence alive (pages + GDN row) so that the next
         turn continues it: droppable segments the client removed are unlinked in place (leave-gap, ``engine/img_evict.py``) and
         only the new tokens are prefilled. At most ``max_parked`` sequences wait; the oldest is released (and published) when
         a row is needed."""
         self.e = engine
         self.park_sessions, self.max_parked, self.evict_pad_id = park_sessions, max_parked, evict_pad_id
+        # session identity = content identity: a turn without a session name continues the parked session whose previous
+        # prompt it repeats in full, and is parked under a generated name when it matches none
+        self.auto_sessions = auto_sessions and park_sessions
+        self.parked_prompt_len: dict = {}      # session -> client-coordinate length of the prompt of its last turn
+        self.auto_matched = 0
         self.step_profile = step_profile      # one "engine.step" event per executed step (kind, turns, ms) in the metrics store
         self.parked: dict = {}       # session -> (engine sequence id, PaddedSeq of everything in the sequence, tick)
         self.resumed = self.gap_drops = 0
@@ -105,6 +110,7 @@ class RunningEngine:
         st = [t.state for t in self.turns.values()]
         return {"queued": st.count(QUEUED), "prefill": st.count(PREFILL), "decode": st.count(DECODE),
                 "free_rows": len(self.e.states.free_rows), "free_pages": self.e.kv.free_pages,
+                "sessions": sorted(self.parked), "auto_matched": self.auto_matched,
                 "prefix_hits": self.e.prefix_hits, "prefix_lookups": self.e.prefix_lookups}
 
     # -- pump -----------------------------------------------------------------------------------
@@ -173,7 +179,25 @@ class RunningEngine:
             n += 1
 
     # -- step executors -------------------------------------------------------------------------
+    def _match_idle_session(self, t: Turn) -> str | None:
+        """The parked session this nameless turn continues: its prompt must repeat the WHOLE prompt of that session's last
+        turn (more than a page would not do: the chat template's preamble alone is longer than a page and is common to every
+        conversation; and asking for the whole history would never match: the client re-renders the model's answer as text,
+        whose tokens need not be the ones that were sampled). The longest such prompt wins."""
+        from . import img_evict as E
+
+        ident, best, best_n = None, None, 0
+        for name, (sid, hist, _) in self.parked.items():
+            n = self.parked_prompt_len.get(name, 0)
+            if n <= max(PAGE, best_n) or n > len(t.tokens) or sid not in self.e.seqs:
+                continue
+            ident = self._ident(t) if ident is None else ident
+            if ident[:n] == E.unpad(hist)[:n]:
+                best, best_n = name, n
+        return best
+
     def _release_parked(self, session: str, publish: bool = True) -> None:
+        self.parked_prompt_len.pop(session, None)
         sid, _, _ = self.parked.pop(session)
         if sid in self.e.seqs:
             self.e.free_sequence(sid, publish=publish)
@@ -209,6 +233,7 @@ class RunningEngine:
             hist = E.apply_deletions(hist, ranges)
             self.gap_drops += len(ranges)
         del self.parked[t.opts.session]
+        self.parked_prompt_len.pop(t.opts.session, None)
         # the appended part: its real tokens, the images whose pad runs lie in it, and its droppable segments padded from
         # the sequence's current length (the sequence's last sampled token is history too: in seq.tokens, not yet cached)
         cut = len(t.tokens) - len(suffix)
@@ -229,6 +254,12 @@ class RunningEngine:
         from . import img_evict as E
 
         t.padded = None
+        if self.auto_sessions and t.opts.session is None:
+            t.opts.session = self._match_idle_session(t)
+            if t.opts.session is not None:
+                self.auto_matched += 1
+            else:
+                t.opts.session = f"auto:{t.turn}"
         if not (self.park_sessions and t.opts.session and self._try_resume(t)):
             if t.opts.session in self.parked:
                 self._release_parked(t.opts.session)
@@ -349,6 +380,7 @@ class RunningEngine:
                 seq = self.e.seqs[t.sid]
                 gen = seq.tokens[len(padded.ids):]
                 self.parked[t.opts.session] = (t.sid, E.PaddedSeq(padded.ids + gen, padded.spans, padded.pads), self._tick)
+                self.parked_prompt_len[t.opts.session] = len(t.tokens)
                 while len(self.parked) > self.max_parked:
                     self._release_parked(min(self.parked, key=lambda k: self.parked[k][2]))
             else:

@@ -354,7 +354,9 @@ def main(argv=None) -> int:
     svc = EngineService(build_engine_factory(cfg, plan, msg_open_ids), max_batch=v["runtime"]["max_batch"],
                         on_full=v["runtime"]["admission_on_full"], spec_runner=build_spec_factory(cfg),
                         running_kw={"park_sessions": bool(v["vision"]["image_evict"]), "max_parked": max(1, v["store.gdn"]["gdn_slots"] // 2),
-                                    "evict_pad_id": pad_id, "step_profile": bool(v["probes"]["step_profile"])})
+                                    "evict_pad_id": pad_id, "step_profile": bool(v["probes"]["step_profile"]),
+                                    # requests that name no session continue the parked conversation whose prompt they repeat
+                                    "auto_sessions": bool(v["vision"]["image_evict"])})
     client = svc.boot()
     vision = None
     if v["vision"]["enabled"]:

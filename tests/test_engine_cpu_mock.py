@@ -157,3 +157,37 @@ def test_graph_fleet_plans_and_meters_on_the_cpu_face():
     off = Engine(cfg(), device="cpu", limits=MockLimits(graph_capture=False))
     rep = GraphFleet(off, max_batch=2).assemble()
     assert rep["states"] == {"eager": 2} and "CaptureUnsupported" in rep["entries"][0]["error"]
+
+
+def test_nameless_turns_find_their_session_by_content():
+    """Session identity = content identity: a turn without a session name continues the parked conversation whose last
+    prompt it repeats in full; a conversation that only shares the preamble gets a session of its own; named sessions
+    stay named."""
+    e = Engine(cfg(n_pages=256, max_seq=1024), device="cpu")
+    re_ = RunningEngine(e, max_batch=2, park_sessions=True, max_parked=4, auto_sessions=True)
+    opts = lambda **kw: TurnOpts(max_new=6, ignore_eos=True, **kw)
+    preamble = toks(24, 50)                                  # longer than a page and common to every conversation
+    a1 = preamble + toks(40, 51)
+    out_a1 = re_.generate(a1, opts())
+    assert sorted(re_.parked) == ["auto:0"] and re_.auto_matched == 0
+    b1 = preamble + toks(44, 52)
+    out_b1 = re_.generate(b1, opts())
+    assert len(re_.parked) == 2 and re_.auto_matched == 0     # the shared preamble does not make it A's session
+    a2 = a1 + out_a1 + toks(10, 53)
+    out_a2 = re_.generate(a2, opts())
+    assert re_.auto_matched == 1 and re_.resumed == 1 and len(re_.parked) == 2
+    a3 = a2 + out_a2 + toks(7, 54)
+    re_.generate(a3, opts())
+    b2 = b1 + out_b1 + toks(5, 55)
+    re_.generate(b2, opts())
+    assert re_.auto_matched == 3 and re_.resumed == 3 and len(re_.parked) == 2
+    # a client that re-renders the answer differently still lands in its session (prompt segment covered), resumes by prefix
+    a4 = a3 + toks(6, 56) + toks(9, 57)
+    re_.generate(a4, opts())
+    assert re_.auto_matched == 4 and re_.resumed == 3
+    c1 = preamble + toks(30, 60)
+    out_c1 = re_.generate(c1, opts(session="named"))
+    re_.generate(c1 + out_c1 + toks(4, 61), opts(session="named"))
+    assert "named" in re_.parked and re_.queue_facts()["sessions"].count("named") == 1
+    fresh = Engine(cfg(n_pages=256, max_seq=1024), device="cpu")
+    assert fresh.generate(a2, 6) == out_a2                    # resumed turns produce what a cold engine produces
