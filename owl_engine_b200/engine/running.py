@@ -130,7 +130,7 @@ class RunningEngine:
             # the speculative round accepts by greedy agreement: sampled turns decode plainly so that temperature / top-p /
             # seed keep their meaning
             spec = self.spec_runner is not None and t.opts.sampling.mode == "greedy"
-            out.append(TurnView(t.turn, t.state, len(t.tokens), fed, need, spec, t.arrival))
+            out.append(TurnView(t.turn, t.state, len(t.tokens), fed, need, spec, t.arrival, max(0, t.opts.max_new - t.n_out)))
         return out
 
     def pump(self) -> bool:
@@ -153,7 +153,11 @@ class RunningEngine:
         for r in rejected:
             t = self.turns.pop(r)          # terminal: the ledger forgets the turn once its last event is out
             t.state = DONE
-            t.sink.put(("failed", r, "rejected: the request does not fit the KV pool / no free slot"))
+            adm = self.sched.take_rejection(r)
+            why = {"never_fits": "the request is larger than the whole KV pool", "slots": "every sequence slot is in use",
+                   "memory": "the KV pool has no room for the request", "queue_timeout": "no room appeared while the request was queued"}
+            t.sink.put(("failed", r, f"rejected ({adm.reason}): {why.get(adm.reason, adm.reason)}; retry_after_ms={adm.retry_after_ms}"))
+            METRICS.count("engine.rejected." + (adm.reason or "other"))
         if step.kind == "idle":
             return bool(rejected)
         try:
@@ -307,7 +311,9 @@ class RunningEngine:
     def _do_decode(self, step) -> None:
         ts = [self.turns[i] for i in step.turns]
         sids = [t.sid for t in ts]
+        t0 = time.perf_counter()
         toks = self.e.decode_step(sids)
+        self.sched.note_decode_ms((time.perf_counter() - t0) * 1e3)
         for i, t in enumerate(ts):
             tok = toks[i]
             if t.opts.sampling.mode != "greedy":

@@ -31,6 +31,7 @@ class TurnView:
     need_pages: int = 0
     spec: bool = False
     arrival: int = 0
+    remaining: int = 0                 # decoding turns: tokens until max_new (the retry hint of a rejection is built from it)
 
 
 @dataclass
@@ -64,33 +65,54 @@ class PhaseSched:
 
 class Scheduler:
     def __init__(self, max_batch: int, prefill_chunk: int, on_full: str = "reject", spec_batch: int = 1,
-                 prefill_every: int = PREFILL_EVERY):
+                 prefill_every: int = PREFILL_EVERY, clock=None):
+        import time
+
         self.max_batch, self.prefill_chunk, self.on_full = max_batch, prefill_chunk, on_full
         self.spec_batch = spec_batch       # decoding turns one speculative round may cover (the engine's scratch state rows)
         self.phase = PhaseSched(prefill_every)
+        self.clock = clock or time.monotonic
+        self.held_since: dict = {}         # turn -> when it was first held (queue:<ms> counts from there)
+        self.itl_ms = 20.0                 # running estimate of a decode beat, fed by the pump (`note_decode_ms`)
+        self.rejections: dict = {}         # turn -> Admission of its rejection (reason + retry hint for the client)
+        self.decode_rr = 0
+
+    def note_decode_ms(self, ms: float) -> None:
+        self.itl_ms = 0.9 * self.itl_ms + 0.1 * ms
 
     def admission(self, t: TurnView, free_pages: int, evictable: int, outstanding: int, pool_pages: int,
-                  free_rows: int) -> str:
-        return B.check_admission(t.need_pages, free_pages, evictable, outstanding, pool_pages, free_rows, self.on_full)
+                  free_rows: int, eta_ms: float = 1000.0) -> B.Admission:
+        waited = (self.clock() - self.held_since[t.turn]) * 1e3 if t.turn in self.held_since else 0.0
+        return B.decide_admission(t.need_pages, free_pages, evictable, outstanding, pool_pages, free_rows, self.on_full,
+                                  waited_ms=waited, eta_ms=eta_ms)
 
     def schedule(self, turns: list[TurnView], free_pages: int, evictable: int, outstanding: int, pool_pages: int,
                  free_rows: int):
         """Returns (Step, rejected_turn_ids)."""
         rejected = []
         queued = sorted((t for t in turns if t.state == QUEUED), key=lambda t: t.arrival)
+        decoding = [t for t in turns if t.state == DECODE]
+        # when room can next appear: the decoding turn closest to its token limit, at the measured beat
+        eta_ms = min((t.remaining for t in decoding), default=50) * self.itl_ms
         for t in queued:
-            verdict = self.admission(t, free_pages, evictable, outstanding, pool_pages, free_rows)
-            if verdict == B.ADMIT:
+            adm = self.admission(t, free_pages, evictable, outstanding, pool_pages, free_rows, eta_ms)
+            if adm.verdict == B.ADMIT:
+                self.held_since.pop(t.turn, None)
                 return Step("begin", [t.turn]), rejected
-            if verdict == B.REJECT:
+            if adm.verdict == B.REJECT:
+                self.held_since.pop(t.turn, None)
+                self.rejections[t.turn] = adm
                 rejected.append(t.turn)
                 continue
+            self.held_since.setdefault(t.turn, self.clock())
             break                           # Hold: keep FIFO order, try again next pump
         prefilling = [t for t in turns if t.state == PREFILL]
-        decoding = [t for t in turns if t.state == DECODE]
         what = self.phase.pick(prefilling, decoding)
         if what == "prefill":
-            t = prefilling[self.phase.rr % len(prefilling)]
+            # the turn that is owed most (fewest tokens fed) gets the chunk; ties go round
+            least = min(t.fed for t in prefilling)
+            owed = [t for t in prefilling if t.fed == least]
+            t = owed[self.phase.rr % len(owed)]
             self.phase.rr += 1
             end = min(t.n_prompt, t.fed + self.prefill_chunk)
             return Step("prefill", [t.turn], (t.fed, end)), rejected
@@ -99,6 +121,15 @@ class Scheduler:
             if spec and len(spec) == len(decoding) and len(spec) <= self.spec_batch:
                 # every decoding turn can take a speculative round: one batched verify for all of them
                 return Step("spec", [t.turn for t in spec]), rejected
-            batch = decoding[:self.max_batch]
+            if len(decoding) > self.max_batch:
+                # more decoding turns than batch rows: the window moves on every beat, so nobody waits for somebody else's end
+                k = self.decode_rr % len(decoding)
+                self.decode_rr += self.max_batch
+                batch = (decoding[k:] + decoding[:k])[:self.max_batch]
+            else:
+                batch = decoding
             return Step("decode", [t.turn for t in batch]), rejected
         return IDLE, rejected
+
+    def take_rejection(self, turn: int) -> B.Admission:
+        return self.rejections.pop(turn, B.Admission(B.REJECT, "memory", 1000))

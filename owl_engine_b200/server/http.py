@@ -88,10 +88,11 @@ class App:
             except Exception:
                 pass
 
-    async def _send(self, w, status: int, obj, ctype="application/json") -> None:
+    async def _send(self, w, status: int, obj, ctype="application/json", headers: dict | None = None) -> None:
         data = obj if isinstance(obj, bytes) else (json.dumps(obj, ensure_ascii=False).encode() if not isinstance(obj, str) else obj.encode())
+        extra = "".join(f"{k}: {v}\r\n" for k, v in (headers or {}).items())
         w.write(f"HTTP/1.1 {status} {REASONS.get(status, '')}\r\nContent-Type: {ctype}\r\nContent-Length: {len(data)}\r\n"
-                f"Connection: keep-alive\r\n\r\n".encode() + data)
+                f"{extra}Connection: keep-alive\r\n\r\n".encode() + data)
         await w.drain()
 
     async def _sse_open(self, w) -> None:
@@ -281,8 +282,16 @@ class App:
                         await self._sse(w, "data: [DONE]\n\n")
                         w.write(b"0\r\n\r\n")
                         return await w.drain()
-                    code = 429 if "rejected" in ev[2] else 500
-                    return await self._send(w, code, {"error": {"message": ev[2], "type": "engine_error"}})
+                    if "rejected" in ev[2]:
+                        # an admission refusal the client can act on: why, and when to try again
+                        import re as _re
+
+                        m = _re.search(r"rejected \((\w+)\).*retry_after_ms=(\d+)", ev[2])
+                        reason, retry = (m.group(1), int(m.group(2))) if m else ("memory", 1000)
+                        hdr = {"Retry-After": str(max(1, -(-retry // 1000)))} if retry else {}
+                        return await self._send(w, 429, {"error": {"message": ev[2], "type": "overloaded", "code": reason,
+                                                                   "retry_after_ms": retry}}, headers=hdr)
+                    return await self._send(w, 500, {"error": {"message": ev[2], "type": "engine_error"}})
             for c in streamer.tool_calls:
                 if req.session and self.guard.observe(req.session, c):
                     log.warn("server.repeat", f"session {req.session}: identical tool call repeated")

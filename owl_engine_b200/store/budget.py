@@ -122,6 +122,33 @@ def check_admission(need_pages: int, free_pages: int, evictable_pages: int, outs
 
 
 @dataclass
+class Admission:
+    """An admission verdict a client can act on: why a turn was not admitted and when trying again makes sense."""
+    verdict: str                 # ADMIT | HOLD | REJECT
+    reason: str = ""             # "" | "never_fits" | "slots" | "memory" | "queue_timeout"
+    retry_after_ms: int = 0      # 0: retrying the same request cannot help
+
+
+def decide_admission(need_pages: int, free_pages: int, evictable_pages: int, outstanding: int, pool_pages: int, free_slots: int,
+                     on_full: str = "reject", waited_ms: float = 0.0, eta_ms: float = 1000.0) -> Admission:
+    """``check_admission`` with the reason and a retry hint. ``on_full``: ``"reject"`` refuses at once, ``"queue"`` holds the
+    turn until room appears, ``"queue:<ms>"`` holds it for at most that long (``waited_ms`` = how long it has been held) and
+    then rejects with ``queue_timeout``. ``eta_ms``: the caller's estimate of when a running turn will have finished."""
+    if need_pages > pool_pages:
+        return Admission(REJECT, "never_fits", 0)
+    reason = "slots" if free_slots <= 0 else ("" if need_pages <= free_pages + evictable_pages - outstanding else "memory")
+    if not reason:
+        return Admission(ADMIT)
+    retry = int(max(100.0, min(eta_ms, 30000.0)))
+    if on_full.startswith("queue"):
+        limit = float(on_full[6:]) if on_full.startswith("queue:") else None
+        if limit is None or waited_ms < limit:
+            return Admission(HOLD, reason, retry)
+        return Admission(REJECT, "queue_timeout", retry)
+    return Admission(REJECT, reason, retry)
+
+
+@dataclass
 class PressurePolicy:
     low: float = 0.12      # start relieving when free pages fall below 12 % of the pool
     high: float = 0.25     # and free up to 25 %

@@ -191,3 +191,45 @@ def test_nameless_turns_find_their_session_by_content():
     assert "named" in re_.parked and re_.queue_facts()["sessions"].count("named") == 1
     fresh = Engine(cfg(n_pages=256, max_seq=1024), device="cpu")
     assert fresh.generate(a2, 6) == out_a2                    # resumed turns produce what a cold engine produces
+
+
+def test_http_rejections_are_actionable():
+    """A request the pool can never hold answers 429 with the reason and no retry hint; one that only has to wait for a
+    running turn answers 429 with ``Retry-After``."""
+    import asyncio
+    import json
+
+    from owl_engine_b200.engine.service import EngineService
+    from owl_engine_b200.engine.tokenizer import ByteTokenizer
+    from owl_engine_b200.server.http import App, serve
+    from owl_engine_b200.utils.stepgate import GATE
+    from test_server_http import request
+
+    svc = EngineService(lambda: Engine(cfg(n_pages=24, max_seq=2048), device="cpu"), max_batch=2, on_full="reject")
+    client = svc.boot()
+    tok = ByteTokenizer()
+
+    async def main():
+        app = App(client, tok, "test-hybrid", max_new_cap=4096)
+        server = await serve(app, "127.0.0.1", 0)
+        port = server.sockets[0].getsockname()[1]
+        async with server:
+            big = {"messages": [{"role": "user", "content": "x" * 900}], "max_tokens": 8}
+            st, head, raw = await request(port, "POST", "/v1/chat/completions", big)
+            err = json.loads(raw)["error"]
+            assert st == 429 and err["code"] == "never_fits" and err["retry_after_ms"] == 0 and "Retry-After" not in head
+            # a slow turn occupies most of the pool; a second one of the same size has to wait for it
+            GATE.configure("sticky", 20)
+            slow = {"messages": [{"role": "user", "content": "y" * 150}], "max_tokens": 60, "ignore_eos": True}
+            first = asyncio.create_task(request(port, "POST", "/v1/chat/completions", slow))
+            await asyncio.sleep(0.4)
+            st, head, raw = await request(port, "POST", "/v1/chat/completions", slow)
+            GATE.configure("off")
+            err = json.loads(raw)["error"]
+            assert st == 429 and err["code"] == "memory" and err["retry_after_ms"] >= 100 and "Retry-After: " in head
+            assert (await first)[0] == 200
+    try:
+        asyncio.run(main())
+    finally:
+        GATE.configure("off")
+        assert svc.shutdown().code == 0
