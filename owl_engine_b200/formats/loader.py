@@ -429,9 +429,11 @@ def build_weights(full: ModelSpec, provider, device, rank: int = 0, world: int =
     """Read every tensor through ``provider`` and produce the rank's device weights. ``repack``: where the canonical int4
     form is packed into the kernels' record layout: ``"cpu"`` (pack on the host, upload the records), ``"device"`` (upload
     the canonical tensors, pack with device ops: the host does not become the bottleneck of a large checkpoint), ``"auto"``
-    = cpu. Uploads go through ``Stager`` (``staging_mb``)."""
+    = device on a GPU, cpu otherwise. Uploads go through ``Stager`` (``staging_mb``)."""
     from ..parallel.plan import shard_tensor
 
+    if repack == "auto":
+        repack = "device" if torch.device(device).type == "cuda" else "cpu"
     spec = full.sharded(rank, world) if world > 1 else full
     plan = TpPlan(rank, world)
     put = Stager(device, staging_mb)

@@ -266,3 +266,26 @@ def test_coverage_probe_reads_the_pool_and_the_last_query():
     assert rep["blocks"] == (e.seqs[sid].n_cached + 15) // 16
     for k_, c in rep["curve"].items():
         assert 0.0 <= c["index"] <= c["oracle"] + 1e-6 <= 1.0 + 1e-6 and c["chance"] == min(k_, rep["blocks"]) / rep["blocks"]
+
+
+def test_packing_on_the_device_gives_the_records_of_packing_on_the_host(tmp_path):
+    import os
+    import sys
+
+    sys.path.insert(0, os.path.dirname(__file__))
+    from owl_engine_b200.formats import loader
+    from test_tp_gpu import _write_checkpoint
+
+    ckpt = str(tmp_path / "ckpt")
+    _write_checkpoint(ckpt)
+    spec = make_spec(n_layers=4, vocab=512)
+    _, a = loader.load_model(ckpt, DEV, spec=spec, repack="cpu")
+    _, b = loader.load_model(ckpt, DEV, spec=spec, repack="device", staging_mb=1)
+    _, c = loader.load_model(ckpt, DEV, spec=spec)                      # auto = device on a GPU
+    for la, lb, lc in zip(a.layers, b.layers, c.layers):
+        for nm in ("gate_up", "down", "qkvz", "out_proj", "qkv", "o_proj"):
+            ta = getattr(la, nm, None)
+            if ta is not None:
+                assert torch.equal(ta.records, getattr(lb, nm).records) and torch.equal(ta.records, getattr(lc, nm).records), nm
+                assert getattr(lb, nm).records.device.type == "cuda"
+    assert torch.equal(a.embed, b.embed) and torch.equal(a.lm_head.records, b.lm_head.records)
