@@ -310,7 +310,14 @@ def main(argv=None) -> int:
     if a.print_config:
         print(cfg.to_json() if a.format == "json" else cfg.to_toml())
     if a.check:
+        from ..formats.preflight import check_profile
+
         print(json.dumps(estimate(cfg), indent=1))
+        items = check_profile(cfg)
+        for it in items:
+            print(it.line())
+        if not all(it.ok for it in items):
+            return 1
     if a.explain or a.print_config or a.check:
         return 0
     try:
