@@ -364,6 +364,18 @@ def _vram(re) -> dict:
     """The engine's allocation ledger as mutually exclusive buckets that close to the driver's total (``utils/ledger.py``)."""
     v = re.e.ledger.view()
     v["tiers"] = re.e.rel.facts()
+    # the session table: parked conversations (their sequence keeps its pages and its state row between turns) and what
+    # each holds, so that "which conversation owns the pool" has an answer
+    sessions = []
+    for name, (sid, hist, tick) in re.parked.items():
+        seq = re.e.seqs.get(sid)
+        sessions.append({"session": name, "tokens": len(hist.ids), "pages": len(seq.pages) if seq else 0,
+                         "droppable_segments": len(hist.spans), "idle_ticks": re._tick - tick,
+                         "snapshots": len(re.e.states.of_session(name))})
+    v["sessions"] = sessions
+    v["snapshots"] = {"rows": len(re.e.states.snaps), "lower_tiers": len(re.e.states.lower),
+                      "by_class": {k: sum(1 for s in re.e.states.snaps.values() if s.klass == k)
+                                   for k in sorted({s.klass for s in re.e.states.snaps.values()})}}
     return v
 
 

@@ -132,6 +132,9 @@ def test_http_server_end_to_end_on_the_cpu_face():
             assert events[-1] == "[DONE]" and len(events) > 3
             st, _, v = await request(port, "GET", "/debug/blocks")
             assert st == 200 and "kv" in json.loads(v)
+            st, _, v = await request(port, "GET", "/debug/vram")
+            vram = json.loads(v)
+            assert st == 200 and vram["sessions"] == [] and vram["snapshots"]["rows"] >= 1 and "durable" in vram["snapshots"]["by_class"]
             st, _, c = await request(port, "POST", "/v1/chat/completions", body)
             rc = json.loads(c)
             assert rc["choices"][0]["message"] == ra["choices"][0]["message"]
