@@ -243,10 +243,10 @@ class Engine:
             raise BudgetError("no room for a KV pool")
         return int(min(plan.kv_pages, cap))
 
-    def checkpoint(self, include_device: bool = True) -> dict:
+    def checkpoint(self, include_device: bool = True, budget_bytes: int | None = None) -> dict:
         """Write the cached prefix blocks and their state snapshots through to the disk tier and save the restart index
-        (called when the server goes idle and at shutdown)."""
-        return self.rel.checkpoint(include_device)
+        (called in beats of ``budget_bytes`` while the server is idle, and whole at shutdown)."""
+        return self.rel.checkpoint(include_device, budget_bytes)
 
     def relieve(self) -> int:
         """Watermark relief between steps (``store/rel.py``): demote cold prefix blocks before an admission needs the room."""

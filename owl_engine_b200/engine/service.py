@@ -49,6 +49,9 @@ class EngineService:
             raise RuntimeError(self.boot_error)
         return EngineClient(self)
 
+    CHECKPOINT_BEAT = 64 << 20      # bytes written to the disk tier per idle beat
+    checkpoint_beats = 0
+
     def _main(self) -> None:
         build, max_batch, on_full, spec_runner = self._args
         try:
@@ -80,8 +83,11 @@ class EngineService:
                     # idle: after a quiet spell write the cache through to the disk tier once (restart recall)
                     idle_since = idle_since or time.monotonic()
                     if not checkpointed and self.re.e.disk is not None and time.monotonic() - idle_since > self.idle_checkpoint_s:
-                        self.re.e.checkpoint()
-                        checkpointed = True
+                        # one beat of at most CHECKPOINT_BEAT bytes, then back to the inbox: a request that arrives while
+                        # the cache is being written waits for a beat, not for the whole cache
+                        rep = self.re.e.checkpoint(budget_bytes=self.CHECKPOINT_BEAT)
+                        self.checkpoint_beats += 1
+                        checkpointed = rep.get("pending", 0) == 0
                     time.sleep(0.0005)
                 else:
                     idle_since, checkpointed = None, False

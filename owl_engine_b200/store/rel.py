@@ -308,39 +308,65 @@ class Rel:
         return snap
 
     # -- checkpoint / adoption --------------------------------------------------------------------------------------------
-    def checkpoint(self, include_device: bool = True) -> dict:
+    def checkpoint(self, include_device: bool = True, budget_bytes: int | None = None) -> dict:
         """Write-through for a restart: host-tier blocks (and the device-resident tree blocks) are copied to the disk tier
-        without leaving their carrier, durable state snapshots too, then the index is saved."""
+        without leaving their carrier, lasting state snapshots too, then the index is saved.
+
+        ``budget_bytes``: write at most about that much in this call and report what is left in ``pending`` (the index is
+        saved only by the call that finishes the job): the serving loop checkpoints in beats of a few tens of MB while it
+        is idle, so a request that arrives in between waits for one beat, not for the whole cache."""
         if self.disk is None:
-            return {"blocks": 0, "states": 0}
-        wrote = 0
+            return {"blocks": 0, "states": 0, "pending": 0}
+        wrote = n_states = spent = pending = 0
+        room = lambda nb: budget_bytes is None or spent + nb <= budget_bytes or spent == 0      # a beat always makes progress
         if self.mover is not None:
             self.mover.sync()
+        pb = self.disk.page_bytes
         for h, slot in list(self.host_slot_of.items()):
+            if h in self.disk.index:
+                continue
+            if not room(pb):
+                pending += 1
+                continue
             parent, tag, toks = self._meta(h)
-            wrote += self.disk.spill(h, parent, toks, self.host.slot(slot), tag) and 1
+            if self.disk.spill(h, parent, toks, self.host.slot(slot), tag):
+                wrote, spent = wrote + 1, spent + pb
         if include_device and self.host is not None:
             from .tiers import page_views
 
             for h in self.kv.list(DEVICE):
                 if h in self.disk.index or h not in self.meta:
                     continue
-                if self.disk.used + self.disk.page_bytes > self.disk.capacity:
+                if self.disk.used + pb > self.disk.capacity:
                     break
+                if not room(pb):
+                    pending += 1
+                    continue
                 nd = self.kv.node(h)
                 data = torch.cat([v.reshape(-1) for v in page_views(self.pool, nd["page"])]).cpu()
                 parent, tag, toks = self._meta(h)
-                wrote += self.disk.spill(h, parent, toks, data, tag) and 1
-        n_states = 0
+                if self.disk.spill(h, parent, toks, data, tag):
+                    wrote, spent = wrote + 1, spent + pb
         own_budget = self.disk.state_capacity is not None          # with its own budget every lasting snapshot is worth a file
+        sb = (self.pool.conv_state[:, 0].numel() + self.pool.rec_state[:, 0].numel()) * 4
         for h, s in list(self.states.snaps.items()):
             if (s.klass == "durable" or (own_budget and s.klass != "transient")) and h not in self.disk.states:
-                n_states += self._snap_to_disk(s, self._state_bytes(s.row).cpu()) and 1
+                if not room(sb):
+                    pending += 1
+                    continue
+                if self._snap_to_disk(s, self._state_bytes(s.row).cpu()):
+                    n_states, spent = n_states + 1, spent + sb
         for h, data in list(self.snap_host.items()):
             if own_budget and h not in self.disk.states and h in self.states.lower:
-                n_states += self._snap_to_disk(self.states.lower[h], data) and 1
-        n = self.disk.save_index(self.block_tokens)
-        return {"blocks": wrote, "states": n_states, "indexed": n}
+                if not room(sb):
+                    pending += 1
+                    continue
+                if self._snap_to_disk(self.states.lower[h], data):
+                    n_states, spent = n_states + 1, spent + sb
+        out = {"blocks": wrote, "states": n_states, "pending": pending, "bytes": spent}
+        if pending == 0:
+            out["indexed"] = self.disk.save_index(self.block_tokens)
+        return out
 
     def adopt(self) -> dict:
         """Rebuild prefix-tree nodes (disk carrier) and lazily loadable snapshots from the disk tier's index."""

@@ -177,3 +177,39 @@ def test_ledger_budget_refusal_and_view():
     assert v["buckets"]["kv pool"] == 1 << 18 and v["buckets"]["weights"] == 700 and v["tracked"] == (1 << 18) + 700
     led.release("pool")
     assert led.by_class().get("kv pool", 0) == 0
+
+
+def test_checkpoint_in_beats_writes_a_bounded_amount_and_saves_the_index_last(tmp_path):
+    """The idle checkpoint of the serving loop: every call writes about ``budget_bytes`` and says how much is pending; only
+    the call that finishes the job saves the restart index; a restarted engine adopts everything."""
+    import os
+
+    from owl_engine_b200.engine.core import Engine, EngineConfig
+
+    kw = dict(model="test-hybrid", n_pages=64, n_slots=4, n_snap_rows=3, max_seqs=4, max_seq=512, prefill_chunk=64,
+              host_cache_mb=1, disk_cache_mb=8, disk_dir=str(tmp_path))
+    e = Engine(EngineConfig(**kw), device="cpu")
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, 500, (100,), generator=g).tolist() for _ in range(3)]
+    first = [e.generate(p, 4) for p in prompts]
+    pb = e.disk.page_bytes
+    beats, pend = 0, None
+    while True:
+        rep = e.checkpoint(budget_bytes=4 * pb)
+        beats += 1
+        assert rep["bytes"] <= 4 * pb or rep["blocks"] + rep["states"] == 1      # a beat stays within its budget
+        if pend is not None:
+            assert rep["pending"] < pend                                          # and always makes progress
+        pend = rep["pending"]
+        if pend:
+            assert "indexed" not in rep and not os.path.exists(tmp_path / "chain.idx")
+        else:
+            assert rep["indexed"] >= 18
+            break
+    assert beats >= 4
+    e.disk.close()
+    e2 = Engine(EngineConfig(**kw), device="cpu")
+    assert e2.adopted["blocks"] >= 18 and e2.adopted["states"] == 3
+    for p, w in zip(prompts, first):
+        assert e2.generate(p, 4) == w
+    e2.close()
