@@ -125,6 +125,26 @@ def apply_process_switches(cfg: C.OwlConfig) -> None:
     GATE.configure(v["probes"]["step_gate"], v["probes"]["step_gate_ms"])
 
 
+def boot_facts(eng, v: dict, plan: dict) -> list[str]:
+    """What an operator wants to see once at boot: the memory governor's arithmetic, the kernel arms in use, the pools."""
+    led, r, c = eng.ledger, eng.runner, eng.cfg
+    by = {k: f"{b / 2**30:.2f} GiB" for k, b in sorted(led.by_class().items(), key=lambda kv: -kv[1])}
+    lines = [f"[vram-gov] total {led._total() / 2**30:.1f} GiB x budget {led.budget_frac:.2f} - reserve {led.reserve >> 20} MiB = "
+             f"{led.avail / 2**30:.2f} GiB; in use {led.used() / 2**30:.2f} GiB {by}",
+             f"[kernel-env] sm_100a; decode projection arm {getattr(r, 'decode_gemv', '?')}, prefill GEMM {c.prefill_gemm}, "
+             f"graphs {'on' if c.cuda_graph else 'off'}, dependent launch {'on' if c.pdl else 'off'}, kv {c.kv_dtype}, "
+             f"weights {c.quant} g{c.group}",
+             f"[pools] {c.n_pages} KV pages of 16 tokens ({c.n_pages * 16} tokens), {c.n_slots} sequence slots, "
+             f"{c.n_snap_rows} snapshot rows, host tier {c.host_cache_mb} MiB, disk tier {c.disk_cache_mb} MiB, "
+             f"snapshot tiers {c.snap_host_mb} / {c.snap_disk_mb} MiB"]
+    if plan.get("world", 1) > 1:
+        comm = getattr(eng, "comm", None)
+        lines.append(f"[parallel] rank {plan['rank']} of {plan['world']}, collectives {getattr(comm, 'mode', '?')}, "
+                     f"vocabulary split {'on' if c.vocab_split else 'off'}, fused prefill GEMM + collective "
+                     f"{'on' if getattr(r, 'sp_prefill', False) else 'off'}")
+    return lines
+
+
 def build_engine_factory(cfg: C.OwlConfig, plan: dict | None = None, msg_open_ids: tuple = ()):
     v = cfg.values
     plan = plan or {"world": 1, "rank": 0, "local": 0, "comm_mode": None}
@@ -206,6 +226,8 @@ def build_engine_factory(cfg: C.OwlConfig, plan: dict | None = None, msg_open_id
             rep = fleet.assemble()
             eng.graph_fleet = fleet
             log.info("boot.graphs", f"{rep['states']} in {rep['capture_ms']:.0f} ms, {rep['bytes'] >> 20} MiB")
+        for line in boot_facts(eng, v, plan):
+            log.info("boot", line)
         if comm is not None and plan["rank"] == 0:
             from ..engine.tp_serve import MirroredEngine, leader_ring
 
