@@ -226,8 +226,11 @@ def build_engine_factory(cfg: C.OwlConfig, plan: dict | None = None, msg_open_id
             rep = fleet.assemble()
             eng.graph_fleet = fleet
             log.info("boot.graphs", f"{rep['states']} in {rep['capture_ms']:.0f} ms, {rep['bytes'] >> 20} MiB")
-        for line in boot_facts(eng, v, plan):
-            log.info("boot", line)
+        try:
+            for line in boot_facts(eng, v, plan):
+                log.info("boot", line)
+        except Exception as ex:   # noqa: BLE001  (a report line must never cost the boot)
+            log.warn("boot", f"boot facts unavailable: {ex!r}")
         if comm is not None and plan["rank"] == 0:
             from ..engine.tp_serve import MirroredEngine, leader_ring
 
