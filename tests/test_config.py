@@ -66,3 +66,27 @@ def test_cli_check(capsys):
     out = capsys.readouterr().out
     assert "kv_pages" in out and "vram_budget" in out
     assert C.main_cli(["-p", str(ROOT / "full.toml"), "--set", "runtime.nope=1"]) == 2
+
+
+def test_every_shipped_profile_and_part_loads(tmp_path):
+    import glob
+    import os
+
+    root = os.path.abspath(os.path.join(os.path.dirname(__file__), "..", "configs"))
+    leaves = sorted(glob.glob(os.path.join(root, "*.toml")))
+    assert len(leaves) >= 7
+    for leaf in leaves:
+        C.load(leaf)
+    parts = sorted(glob.glob(os.path.join(root, "parts", "*", "*.toml")))
+    assert len(parts) >= 20
+    for part in parts:
+        if os.path.basename(part) in ("disk-tier.toml",):
+            continue                                       # needs a directory and the host tier from the leaf (checked below)
+        p = tmp_path / "one.toml"
+        p.write_text(f'extends = ["{root}/full.toml", "{part}"]\n')
+        C.load(str(p))
+    p = tmp_path / "disk.toml"
+    p.write_text(f'extends = ["{root}/full.toml", "{root}/parts/feature/agent.toml", "{root}/parts/feature/disk-tier.toml"]\n'
+                 f'[store]\ndisk_dir = "{tmp_path}"\n')
+    cfg = C.load(str(p))
+    assert cfg.get("store.snap_disk_mb") == 16384 and cfg.get("store.evict_policy") == "lrfu"
