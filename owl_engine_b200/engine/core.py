@@ -557,6 +557,9 @@ class Engine:
             row = self.states.snapshot(int(seq.chain[end // PAGE - 1]), end, *seq.snap_points[end], session=seq.session)
             if row is not None:
                 self.pool.copy_slot(seq.slot, row)
+        for p in pts:
+            if seq.snap_points[p][0] == "durable":
+                self.states.supersede(seq.chain[:p // PAGE], p)       # this conversation's earlier anchors become fork points
         if want_token:
             t = int(tok.item())
             seq.tokens.append(t)

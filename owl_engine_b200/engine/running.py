@@ -147,9 +147,20 @@ class RunningEngine:
         # shows the current leaves, which would count a long published chain as one block)
         pinned = sum(s.reused // PAGE for s in self.e.seqs.values())
         evictable = max(kvs["lru_len"], kvs["device_nodes"] - pinned)
+        # parked sessions hold pages that no running turn uses: they count as room for admission, and when the turns already
+        # admitted need more than is free plus evictable, the session idle longest is released here, between steps (its
+        # blocks move to the prefix tree, where the pressure path can reach them)
+        def parked_pages():
+            return sum(len(self.e.seqs[sid].pages) for sid, _, _ in self.parked.values() if sid in self.e.seqs)
+        while self.parked and self.e.kv.free_pages + evictable < self.reservations.outstanding:
+            before = parked_pages()
+            self._release_parked(min(self.parked, key=lambda k: self.parked[k][2]))
+            evictable += before - parked_pages()
+        evictable += parked_pages()
         step, rejected = self.sched.schedule(self._views(), self.e.kv.free_pages, evictable,
                                              self.reservations.outstanding, self.e.cfg.n_pages,
-                                             min(len(self.e.states.free_rows), len(self.e.free_rows)))
+                                             # a parked session gives its rows back when a new turn needs them (`_do_begin`)
+                                             min(len(self.e.states.free_rows), len(self.e.free_rows)) + len(self.parked))
         for r in rejected:
             t = self.turns.pop(r)          # terminal: the ledger forgets the turn once its last event is out
             t.state = DONE

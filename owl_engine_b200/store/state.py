@@ -111,6 +111,22 @@ class StateStore:
         self.snaps[chain_hash] = Snapshot(row, chain_hash, n_tokens, klass, rank, session)
         return row
 
+    def supersede(self, chain, n_tokens: int) -> int:
+        """A ``durable`` snapshot (the end of a prompt) at ``n_tokens`` of ``chain`` was just taken: live ``durable`` and
+        ``tail`` snapshots that lie EARLIER ON THE SAME CHAIN are no longer where this conversation continues from, only
+        possible fork points, and are re-classed ``extra`` so that they leave before anybody's current anchor does. (A
+        ``tail`` snapshot does not supersede its own prompt's anchor: it lies inside the answer, and a client that renders
+        the answer back with other tokens can only resume from the prompt's end.) Returns how many."""
+        bt, n = 0, 0
+        for s in self.snaps.values():
+            if s.klass in ("durable", "tail") and 0 < s.n_tokens < n_tokens:
+                bt = bt or max(1, n_tokens // max(1, len(chain)))          # tokens per block of this chain
+                i = s.n_tokens // bt - 1
+                if 0 <= i < len(chain) and int(chain[i]) == s.chain_hash:
+                    s.klass, s.rank = "extra", 0
+                    n += 1
+        return n
+
     def find(self, chain_hashes) -> Snapshot | None:
         """Deepest live snapshot along a chain (list of block hashes, shallow -> deep)."""
         for h in reversed(list(chain_hashes)):

@@ -236,3 +236,18 @@ def test_http_rejections_are_actionable():
     finally:
         GATE.configure("off")
         assert svc.shutdown().code == 0
+
+
+def test_parked_sessions_give_way_to_new_turns():
+    """Parked conversations hold rows and pages; a new turn that needs them is admitted, and the session idle longest is
+    released (its blocks become evictable prefix blocks) instead of the newcomer being refused."""
+    e = Engine(cfg(n_pages=40, n_slots=3, max_seqs=3, max_seq=512), device="cpu")
+    re_ = RunningEngine(e, max_batch=2, park_sessions=True, max_parked=3, auto_sessions=True)
+    opts = lambda: TurnOpts(max_new=6, ignore_eos=True)
+    outs = [re_.generate(toks(150, 70 + i), opts()) for i in range(3)]       # three parked conversations: every row, 30 of 40 pages
+    assert len(re_.parked) == 3 and len(e.states.free_rows) == 0
+    out = re_.generate(toks(200, 80), opts())                                 # needs a row and 13 pages
+    assert len(out) == 6 and len(re_.parked) <= 3 and "auto:0" not in re_.parked
+    assert all(len(o) == 6 for o in outs)
+    fresh = Engine(cfg(n_pages=40, n_slots=3, max_seqs=3, max_seq=512), device="cpu")
+    assert fresh.generate(toks(200, 80), 6) == out
