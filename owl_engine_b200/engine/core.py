@@ -413,6 +413,25 @@ class Engine:
             self.states.forget(old)
         seq.tail_hash = h
 
+    def snapshot_now(self, sid: int, klass: str = "dense") -> bool:
+        """Save the sequence's recurrent state as it stands, when it stands on a page boundary inside the prompt's chain
+        (a turn cancelled between two prefill chunks: the blocks it wrote are published, and with this snapshot the retry
+        resumes behind them instead of recomputing the prompt). Returns whether a snapshot was taken."""
+        seq = self.seqs.get(sid)
+        if seq is None or seq.chain is None or seq.gap_from is not None or not self.cfg.prefix_cache:
+            return False
+        n = seq.n_cached
+        if n < PAGE or n % PAGE or n // PAGE > len(seq.chain) or n <= seq.reused:
+            return False
+        h = int(seq.chain[n // PAGE - 1])
+        if h in self.states.snaps:
+            return False
+        row = self.states.snapshot(h, n, klass, session=seq.session)
+        if row is None:
+            return False
+        self.pool.copy_slot(seq.slot, row)
+        return True
+
     def free_sequence(self, sid: int, publish: bool = True) -> None:
         """End a sequence: index its full blocks in the prefix tree (the tree takes its own
         references) and give pages, row and state row back."""

@@ -401,6 +401,13 @@ class RunningEngine:
                 while len(self.parked) > self.max_parked:
                     self._release_parked(min(self.parked, key=lambda k: self.parked[k][2]))
             else:
+                if reason in ("cancelled", "failed") and t.state == PREFILL:
+                    # stopped between two prefill chunks: keep the state of the point reached, so that the retry of this
+                    # prompt resumes behind the blocks published below
+                    try:
+                        self.e.snapshot_now(t.sid)
+                    except Exception as ex:   # noqa: BLE001  (best effort: the turn is ending anyway)
+                        log.warn("engine.turn", f"no snapshot at the abort point: {ex!r}")
                 self.e.free_sequence(t.sid, publish=True)     # cancelled turns publish their written prefix too
         self.reservations.release(t.turn)
         t.state = DONE

@@ -8,7 +8,7 @@ function of its call sequence (page allocation, prefix matches, tier moves), so 
 exchanging anything else, and they meet on the device inside the kernels' collectives. NCCL carries no step traffic.
 
 Mirrored: ``add_sequence``, ``free_sequence``, ``drop_ranges``, ``append_tokens``, ``extend_sequence``,
-``prefill_range``, ``decode_step``, ``set_last_token``, ``relieve``, ``checkpoint``, ``close``, the speculative runner's ``after_prefill`` / ``round`` / ``round_batch``, and
+``prefill_range``, ``decode_step``, ``set_last_token``, ``snapshot_now``, ``relieve``, ``checkpoint``, ``close``, the speculative runner's ``after_prefill`` / ``round`` / ``round_batch``, and
 ``shutdown``. Everything else (statistics, plans, sequence lookups) is read-only and stays local.
 
 Reference counterpart: ``TpEngine::assemble / run`` and the ``mirror2!`` call sites
@@ -23,7 +23,7 @@ from ..parallel.ring import RingClosed, StepRing, ring_name
 from ..utils import log
 
 MIRRORED = ("add_sequence", "free_sequence", "drop_ranges", "append_tokens", "extend_sequence", "prefill_range",
-            "decode_step", "set_last_token", "relieve", "checkpoint", "close")
+            "decode_step", "set_last_token", "relieve", "checkpoint", "close", "snapshot_now")
 
 
 class MirroredEngine:
@@ -48,6 +48,9 @@ class MirroredEngine:
 
     def free_sequence(self, *a, **kw):
         return self._mirror("free_sequence", *a, **kw)
+
+    def snapshot_now(self, *a, **kw):
+        return self._mirror("snapshot_now", *a, **kw)
 
     def drop_ranges(self, *a, **kw):
         return self._mirror("drop_ranges", *a, **kw)

@@ -251,3 +251,24 @@ def test_parked_sessions_give_way_to_new_turns():
     assert all(len(o) == 6 for o in outs)
     fresh = Engine(cfg(n_pages=40, n_slots=3, max_seqs=3, max_seq=512), device="cpu")
     assert fresh.generate(toks(200, 80), 6) == out
+
+
+def test_a_turn_cancelled_between_prefill_chunks_leaves_an_anchor_for_the_retry():
+    """Abort, then retry: the cancelled turn publishes the blocks it wrote AND saves the state of the point it reached, so
+    the same prompt resumes there instead of starting over."""
+    e = Engine(cfg(n_pages=128, max_seq=1024, prefill_chunk=64), device="cpu")
+    re_ = RunningEngine(e, max_batch=2)
+    prompt = toks(400, 90)
+    tid = re_.submit(prompt, TurnOpts(max_new=4, ignore_eos=True))
+    for _ in range(4):                     # begin + three chunks of 64
+        re_.pump()
+    assert e.seqs[re_.turns[tid].sid].n_cached == 192
+    re_.cancel_turn(tid)
+    re_.pump()
+    assert tid not in re_.turns and not e.seqs
+    sid = e.add_sequence(prompt)
+    assert e.seqs[sid].reused == 192
+    e.free_sequence(sid, publish=False)
+    want = Engine(cfg(n_pages=128, max_seq=1024, prefill_chunk=64), device="cpu").generate(prompt, 6)
+    assert re_.generate(prompt, TurnOpts(max_new=6, ignore_eos=True)) == want
+    assert re_.trace[-1]["cached_tokens"] == 192
