@@ -1,0 +1,77 @@
+"""Streaming invariants of the output splitter: what a turn's text is divided into must not depend on how the token
+stream happened to cut it, and no character may be lost or invented."""
+import json
+
+from hypothesis import given, settings, strategies as st
+
+from owl_engine_b200.server.toolcall import ChannelSplitter
+
+TOOLS = [{"type": "function", "function": {"name": "get_weather", "parameters": {"type": "object", "properties": {
+    "city": {"type": "string"}, "days": {"type": "integer"}}}}}]
+
+PIECES = [
+    "plain words ", "and more, with < and > and <b>tags</b> ", "\n", "<think>", "</think>", "reasoning about it ",
+    "<tool_call>", "</tool_call>", '{"name": "get_weather", "arguments": {"city": "Oslo", "days": 2}}',
+    "<function=get_weather>", "<parameter=city>", "Oslo", "</parameter>", "</function>", "<tool", "</thi", "<|im_end|>",
+    "<thinking>", "</thinking>", "{", "}", '"', "é", "日本",
+]
+
+
+def run(chunks, start_in_think=False):
+    sp = ChannelSplitter(start_in_think=start_in_think, tools=TOOLS)
+    ev = []
+    for c in chunks:
+        ev += sp.feed(c)
+    ev += sp.finish()
+    # merge adjacent text / reasoning events: their boundaries are an artefact of the chunking
+    merged = []
+    for e in ev:
+        if merged and e[0] in ("text", "reasoning") and merged[-1][0] == e[0]:
+            merged[-1] = (e[0], merged[-1][1] + e[1])
+        else:
+            merged.append(tuple(e))
+    return merged, sp
+
+
+def cuts(text, points):
+    pts = sorted({p % (len(text) + 1) for p in points})
+    out, last = [], 0
+    for p in pts:
+        out.append(text[last:p])
+        last = p
+    out.append(text[last:])
+    return [c for c in out if c]
+
+
+@settings(max_examples=300, deadline=None)
+@given(st.lists(st.sampled_from(PIECES), min_size=1, max_size=14), st.lists(st.integers(0, 10 ** 6), max_size=12), st.booleans())
+def test_events_do_not_depend_on_the_chunking(pieces, points, in_think):
+    text = "".join(pieces)
+    whole, _ = run([text], in_think)
+    chunked, _ = run(cuts(text, points), in_think)
+    by_char, _ = run(list(text), in_think)
+    assert chunked == whole and by_char == whole
+
+
+@settings(max_examples=200, deadline=None)
+@given(st.text(alphabet=st.characters(blacklist_characters="<", blacklist_categories=("Cs",)), max_size=200),
+       st.lists(st.integers(0, 10 ** 6), max_size=8))
+def test_text_without_markers_passes_through_unchanged(text, points):
+    ev, sp = run(cuts(text, points) or [""])
+    assert "".join(e[1] for e in ev if e[0] == "text") == text and all(e[0] == "text" for e in ev)
+    assert sp.n_calls == 0 and sp.malformed == 0
+
+
+@settings(max_examples=150, deadline=None)
+@given(st.text(alphabet="abc xyz.\n", max_size=40), st.text(alphabet="abc xyz.\n", max_size=40),
+       st.sampled_from(["Oslo", "New York", 'a "quoted" city', "日本"]), st.integers(0, 9), st.lists(st.integers(0, 10 ** 6), max_size=10))
+def test_a_well_formed_call_is_found_whatever_surrounds_it(before, after, city, days, points):
+    call = json.dumps({"name": "get_weather", "arguments": {"city": city, "days": days}}, ensure_ascii=False)
+    text = f"{before}<tool_call>\n{call}\n</tool_call>{after}"
+    ev, sp = run(cuts(text, points))
+    calls = [e for e in ev if e[0] == "tool_call"]
+    assert len(calls) == 1 and sp.malformed == 0
+    name, args = calls[0][1]["name"], calls[0][1]["arguments"]
+    assert name == "get_weather" and json.loads(args) == {"city": city, "days": days}
+    shown = "".join(e[1] for e in ev if e[0] == "text")
+    assert shown.replace("\n", "").replace(" ", "") == (before + after).replace("\n", "").replace(" ", "")
