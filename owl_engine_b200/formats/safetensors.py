@@ -82,8 +82,8 @@ def save_file(tensors: dict, path: str | Path, metadata: dict | None = None) -> 
     header, blobs, off = {}, [], 0
     for k, t in tensors.items():
         t = t.detach().cpu().contiguous()
-        raw = t.view(torch.uint8).numpy().tobytes() if t.dtype in (torch.bfloat16, torch.float8_e4m3fn) \
-            else t.numpy().tobytes()
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.dtype in (torch.bfloat16, torch.float8_e4m3fn) \
+            else t.numpy().tobytes()                  # reshape first: a 0-dimensional tensor cannot be viewed as bytes
         header[k] = {"dtype": _REV[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + len(raw)]}
         blobs.append(raw)
         off += len(raw)
