@@ -97,3 +97,53 @@ def test_pad_rule_aligns_segments_and_unpad_restores_the_client_view(ids, raw_sp
         assert all(lo % PAGE == 0 and hi % PAGE == 0 for lo, hi in ranges)
         after = E.apply_deletions(ps, ranges)
         assert E.unpad(after) == kept                                                 # what remains is the client's history
+
+
+@settings(max_examples=15, deadline=None)
+@given(st.lists(st.integers(0, 6000), min_size=1, max_size=80), st.integers(0, 2 ** 31 - 1))
+def test_step_ring_delivers_random_sized_messages_intact_and_in_order(sizes, seed):
+    import os
+    import threading
+
+    from owl_engine_b200.parallel.ring import StepRing
+
+    name = f"/owl_prop_ring_{os.getpid()}_{seed % 100000}"
+    ring = StepRing.create(name, 2, capacity=16384)                 # small: the producer keeps running into the readers
+    readers = [StepRing.open(name, r, 5.0) for r in range(2)]
+    rng = np.random.default_rng(seed)
+    msgs = [rng.integers(0, 256, n, dtype=np.uint8).tobytes() for n in sizes]
+    got = [[], []]
+
+    def read(i):
+        for _ in msgs:
+            got[i].append(readers[i].pop_bytes(10.0))
+    ts = [threading.Thread(target=read, args=(i,)) for i in range(2)]
+    for t in ts:
+        t.start()
+    for m in msgs:
+        ring.push_bytes(m, timeout_s=10.0)
+    for t in ts:
+        t.join(20)
+    for r in readers:
+        r.free()
+    ring.free()
+    assert got[0] == msgs and got[1] == msgs
+
+
+@settings(max_examples=200, deadline=None)
+@given(st.lists(st.integers(0, 5), min_size=0, max_size=400), st.integers(1, 64), st.integers(0, 500), st.integers(0, 6))
+def test_message_points_are_page_aligned_ascending_and_keep_the_ends(stream, page, min_gap, recent):
+    from owl_engine_b200.store import snap_policy as P
+
+    toks = [9 if x else 1 for x in stream]                          # 1 = the marker
+    pts = P.message_points(toks, [1], page, min_gap, recent)
+    cand = sorted({i // page * page for i, t in enumerate(toks) if t == 1 and i // page > 0})
+    assert pts == sorted(set(pts)) and all(p % page == 0 and p > 0 for p in pts) and set(pts) <= set(cand)
+    if cand:
+        assert pts[0] == cand[0]                                    # the first boundary is always kept
+        assert set(cand[len(cand) - recent:] if recent else []) <= set(pts)      # and the newest `recent`
+        middle = [p for p in pts if p not in cand[len(cand) - recent:]] if recent else pts
+        assert all(b - a >= min_gap for a, b in zip(middle, middle[1:]))          # the rest keep their distance
+    cls = P.classify(pts, len(toks), recent)
+    assert len(cls) == len(pts) and all(c in ("dense", "binary", "extra") for c, _ in cls)
+    assert [c for c, _ in cls[len(cls) - recent:]] == ["dense"] * min(recent, len(cls)) if recent else True
