@@ -1,3 +1,4 @@
+"""Profiles: extends chains, strict keys, --set / --explain / --check, the intent layer, every shipped profile and part."""
 import json
 from pathlib import Path
 

@@ -1,3 +1,4 @@
+"""Checkpoint containers and codecs against host references: safetensors, AWQ / compressed-tensors, NVFP4, GGUF blocks and grids, the AWQ converter, shard plans."""
 import numpy as np
 import pytest
 import torch

@@ -1,5 +1,4 @@
-
-
+"""Tensor-parallel planning on the host: shard rules, peer classification against a fake NVML, the host relay over gloo."""
 def test_peer_classification_limits_and_plan():
     """Reference rules (crates/backends/cuda/src/comm/peer.rs): P2P + both BAR1 wide -> static, both narrow -> window with
     the smaller aperture minus the reserve, mixed or no P2P -> refused; NVLink pairs bypass the aperture."""

@@ -1,3 +1,4 @@
+"""Server parts without a server: the output splitter on recorded shapes, the repeat guard, the chat template, exact rejection sampling."""
 import json
 
 from owl_engine_b200.server.chat_tpl import ChatTemplate

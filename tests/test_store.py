@@ -1,3 +1,4 @@
+"""The store on the host: chain hashes and the prefix tree, budgets and admission, state rows, selection, the coverage probe."""
 import numpy as np
 import pytest
 import torch

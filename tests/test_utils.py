@@ -1,3 +1,4 @@
+"""Shared utilities: logger, metrics, step gate, device lock, ledger, the CPU face."""
 import os
 
 import pytest
