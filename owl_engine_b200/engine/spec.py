@@ -29,6 +29,7 @@ from __future__ import annotations
 import random
 from dataclasses import dataclass, field
 
+import numpy as np
 import torch
 
 from ..models import hybrid as H
@@ -71,23 +72,91 @@ def _draw(dist: dict, rng: random.Random) -> int:
 
 
 # ---- draft sources ----------------------------------------------------------------------------
-class LookupDraft:
-    """Suffix lookup: if the last ``n`` tokens occurred earlier in the sequence, propose what followed."""
+def suffix_lookup(hist, k: int, nmin: int, nmax: int):
+    """Where did the current suffix occur before, and what followed it? ``hist`` (array of token ids) ends with the token
+    fed last. A candidate is any earlier end position ``e`` whose last ``nmin`` tokens equal the last ``nmin`` tokens of
+    ``hist``; the match is extended towards older tokens up to ``nmax``; the longest match wins, the more recent one on a
+    tie; candidate and suffix may overlap (periodic text). Returns ``(follow, match_len)`` with up to ``k`` tokens that
+    followed the match, or None."""
+    h = np.asarray(hist)
+    n = len(h)
+    if nmin < 1 or n < nmin + 1 or k < 1:
+        return None
+    ends = np.arange(nmin - 1, n - 1)                          # e < n - 1: something must follow the match
+    ok = np.ones(len(ends), dtype=bool)
+    for j in range(nmin):
+        ok &= h[ends - j] == h[n - 1 - j]
+    cand = ends[ok]
+    if len(cand) == 0:
+        return None
+    best_e, best_len = -1, 0
+    for e in cand[::-1]:                                       # most recent first: on equal length the earlier pick stays
+        m = nmin
+        while m < nmax and e - m >= 0 and h[e - m] == h[n - 1 - m]:
+            m += 1
+        if m > best_len:
+            best_e, best_len = int(e), m
+            if m >= nmax:
+                break
+    follow = h[best_e + 1:best_e + 1 + k].tolist()
+    return follow, best_len
 
-    def __init__(self, min_match: int = 2, max_match: int = 8):
+
+def fuse_lookup(draft: list, follow: list, match_len: int, nmin: int, nstrong: int, agree_min: int) -> list:
+    """Lookup-augmented drafting: the looked-up continuation replaces the head of the model's draft when the match is
+    strong (``match_len >= nstrong``) or when it is at least ``nmin`` long and agrees with the draft on its first
+    ``agree_min`` tokens; positions the lookup does not reach keep the model's tokens."""
+    if not follow or match_len < nmin:
+        return list(draft)
+    agree = 0
+    while agree < min(len(draft), len(follow)) and draft[agree] == follow[agree]:
+        agree += 1
+    if match_len >= nstrong or agree >= agree_min:
+        return list(follow) + list(draft[len(follow):])
+    return list(draft)
+
+
+class LookupDraft:
+    """Suffix lookup in the sequence's own history (host side): if the last tokens occurred earlier, propose what followed
+    (``suffix_lookup``). Alone it is a draft source; next to a draft model it overrides the head of the model's draft
+    (``fuse``). The history is kept as a growing array per sequence, so a round costs a few vector compares, not a copy
+    of the history."""
+
+    def __init__(self, min_match: int = 2, max_match: int = 8, nstrong: int | None = None, agree: int = 0):
         self.min_match, self.max_match = min_match, max_match
+        self.nstrong = min_match if nstrong is None else nstrong
+        self.agree = agree
+        self._hist: dict = {}          # sid -> (array with spare room, valid length)
+        self.hits = self.lookups = 0
+
+    def _array(self, sid: int, toks: list):
+        buf, n = self._hist.get(sid, (None, 0))
+        m = len(toks)
+        if buf is None or m < n or m > len(buf) or (n and buf[n - 1] != toks[n - 1]):
+            buf = np.empty(max(1024, 2 * m), dtype=np.int64)
+            buf[:m] = toks
+        elif m > n:
+            buf[n:m] = toks[n:m]
+        self._hist[sid] = (buf, m)
+        if len(self._hist) > 64:
+            self._hist.pop(next(iter(self._hist)))
+        return buf[:m]
+
+    def find(self, engine: Engine, sid: int, depth: int):
+        self.lookups += 1
+        r = suffix_lookup(self._array(sid, engine.seqs[sid].tokens), depth, self.min_match, self.max_match)
+        if r is not None:
+            self.hits += 1
+        return r
 
     def propose(self, engine: Engine, sid: int, depth: int) -> list[int]:
-        toks = engine.seqs[sid].tokens
-        n = len(toks)
-        for k in range(min(self.max_match, n - 1), self.min_match - 1, -1):
-            suffix = toks[n - k:]
-            for start in range(n - k - 1, -1, -1):
-                if toks[start:start + k] == suffix:
-                    follow = toks[start + k:start + k + depth]
-                    if follow:
-                        return follow
-        return []
+        r = self.find(engine, sid, depth)
+        return r[0] if r is not None else []
+
+    def fuse(self, draft: list, found) -> list:
+        if found is None:
+            return list(draft)
+        return fuse_lookup(draft, found[0], found[1], self.min_match, self.nstrong, self.agree)
 
     def observe(self, engine, sid, n_rows, emitted, row0=0):
         pass
@@ -150,13 +219,13 @@ class MtpDraft:
         self.ready[sid] = True
 
     def propose(self, engine: Engine, sid: int, depth: int) -> list[int]:
-        if self.lookup is not None:
-            hit = self.lookup.propose(engine, sid, depth)
-            if len(hit) >= depth:
-                return hit
+        found = self.lookup.find(engine, sid, depth) if self.lookup is not None else None
+        if found is not None and len(found[0]) >= depth and found[1] >= self.lookup.nstrong:
+            return found[0]                        # a strong match covers the whole draft: the head need not run
         if not self.ready.get(sid):
-            return []
-        return self.head.chain(depth).tolist()
+            return found[0] if found is not None else []
+        draft = self.head.chain(depth).tolist()
+        return self.lookup.fuse(draft, found) if self.lookup is not None else draft
 
     def observe(self, engine: Engine, sid: int, n_rows: int, emitted: list[int], row0: int = 0) -> None:
         """After a verify step: its rows row0..row0+n_rows-1 (this sequence's accepted rows) feed the head, with the
@@ -194,14 +263,14 @@ class DFlash2Draft:
             self.draft.capture()
 
     def propose(self, engine: Engine, sid: int, depth: int) -> list[int]:
-        if self.lookup is not None:
-            hit = self.lookup.propose(engine, sid, depth)
-            if len(hit) >= depth:
-                return hit
+        found = self.lookup.find(engine, sid, depth) if self.lookup is not None else None
+        if found is not None and len(found[0]) >= depth and found[1] >= self.lookup.nstrong:
+            return found[0]                        # a strong match covers the whole draft: the draft model need not run
         if sid != self.sid:
-            return []
+            return found[0] if found is not None else []
         seq = engine.seqs[sid]
-        return self.draft.propose(seq.tokens[-1], seq.n_cached, depth)
+        draft = self.draft.propose(seq.tokens[-1], seq.n_cached, depth)
+        return self.lookup.fuse(list(draft), found) if self.lookup is not None else draft
 
     def observe(self, engine: Engine, sid: int, n_rows: int, emitted: list[int], row0: int = 0) -> None:
         if sid != self.sid:

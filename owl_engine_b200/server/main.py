@@ -248,7 +248,7 @@ def build_spec_factory(cfg: C.OwlConfig):
         from ..engine.spec import LookupDraft, MtpDraft, SpecRunner
         from ..models.mtp import MtpHead
 
-        lookup = LookupDraft(sp["lookup_nmin"], sp["lookup_nmax"]) if sp["lookup"] else None
+        lookup = LookupDraft(sp["lookup_nmin"], sp["lookup_nmax"], sp["lookup_nstrong"], sp["lookup_agree"]) if sp["lookup"] else None
         if sp["kind"] in ("mtp", "dflash2") and getattr(engine, "comm", None) is not None:
             # the draft models are not tensor-parallel: with them in the loop a forced-acceptance run at 4 ranks did not
             # reproduce plain decoding, so the profile is refused instead of served wrong (lookup drafting works at any size)

@@ -66,7 +66,7 @@ SCHEMA: dict = {
     "store.gdn": {"gdn_slots": int, "snap_decode_stride": int, "snap_max": int, "snap_msg_min_gap": int,
                   "snap_msg_recent": int, "snap_session_cap": int, "snap_structural_reserve": int},
     "spec": {"depth": int, "draft_path": str, "kind": Enum("none", "mtp", "dflash2"), "lookup": bool, "lookup_nmin": int,
-             "lookup_nmax": int, "mtp_window": int, "mtp_sink": int, "mtp_ring": bool, "adaptive_depth": bool,
+             "lookup_nmax": int, "lookup_nstrong": int, "lookup_agree": int, "mtp_window": int, "mtp_sink": int, "mtp_ring": bool, "adaptive_depth": bool,
              "depth_min": int, "depth_switch_ctx": int, "tp_draft": bool, "degrade_after": int, "probe_every": int, "q_alpha": float,
              "q_floor": float, "force_accept": int},
     "vision": {"enabled": bool, "path": str, "max_pixels": int, "image_evict": bool, "image_evict_pad": str},
@@ -333,6 +333,8 @@ def _validate_honoured(v: dict) -> None:
     refuse(sp["depth_min"] < 1 or sp["depth_min"] > 7 or sp["depth"] > 7, "spec.depth and spec.depth_min are at most 7 (and depth_min >= 1)")
     refuse(sp["degrade_after"] < 0 or sp["probe_every"] < 1, "spec.degrade_after >= 0 and spec.probe_every >= 1")
     refuse(sp["force_accept"] > 7, "spec.force_accept is at most 7 (-1 = off)")
+    refuse(not (1 <= sp["lookup_nmin"] <= sp["lookup_nmax"]) or sp["lookup_nstrong"] < sp["lookup_nmin"] or sp["lookup_agree"] < 0,
+           "spec.lookup_*: 1 <= lookup_nmin <= lookup_nmax, lookup_nstrong >= lookup_nmin, lookup_agree >= 0")
     if km["select_decode"]:
         refuse(km["score_mode"] != "cosine-max", f"kvmem.score_mode = {km['score_mode']!r}: the GPU block scorer implements "
                "cosine-max only")

@@ -223,3 +223,35 @@ def test_request_dump_prompt_dump_and_raw_completion(tmp_path):
     files = sorted(os.listdir(tmp_path / "dumps"))
     assert len(files) == 2 and json.loads(open(tmp_path / "dumps" / files[1]).read()) == {"messages": [1]}
     assert app.prompt_dump and not app.raw_completion
+
+
+def test_suffix_lookup_and_head_fusion():
+    from owl_engine_b200.engine.spec import fuse_lookup, suffix_lookup
+
+    assert suffix_lookup([1, 2, 3, 4, 9, 1, 2, 3, 4], 3, 2, 8) == ([9, 1, 2], 4)          # extended to the whole earlier run
+    assert suffix_lookup([5, 6, 5, 6, 5, 6], 3, 2, 8) == ([5, 6], 4)                      # overlap allowed; what follows is short
+    assert suffix_lookup([7, 1, 2, 8, 1, 2, 9, 1, 2], 2, 2, 8) == ([9, 1], 2)             # equal length: the more recent match
+    assert suffix_lookup([1, 2, 3, 4, 9, 1, 2, 3, 4], 3, 2, 3)[1] == 3                    # the extension stops at nmax
+    assert suffix_lookup([1, 2, 3], 3, 2, 8) is None and suffix_lookup([1, 2], 3, 2, 8) is None
+    assert suffix_lookup([4, 4, 4, 4], 2, 1, 8) == ([4], 3)
+    draft = [10, 11, 12, 13]
+    assert fuse_lookup(draft, [20, 21], 6, 3, 6, 0) == [20, 21, 12, 13]                   # strong: the head is replaced, the tail kept
+    assert fuse_lookup(draft, [20, 21], 4, 3, 6, 1) == draft                              # weak and disagreeing: the model's draft stays
+    assert fuse_lookup(draft, [10, 21], 4, 3, 6, 1) == [10, 21, 12, 13]                   # weak but agreeing on the first token
+    assert fuse_lookup(draft, [20, 21], 2, 3, 6, 0) == draft                              # shorter than nmin never counts
+    assert fuse_lookup(draft, [], 9, 3, 6, 0) == draft
+
+
+def test_lookup_history_buffer_tracks_the_sequence():
+    from types import SimpleNamespace
+
+    from owl_engine_b200.engine.spec import LookupDraft
+
+    seq = SimpleNamespace(tokens=[1, 2, 3, 4, 9, 1, 2, 3, 4])
+    eng = SimpleNamespace(seqs={0: seq})
+    lk = LookupDraft(2, 8)
+    assert lk.propose(eng, 0, 3) == [9, 1, 2]
+    seq.tokens += [9, 1]
+    assert lk.propose(eng, 0, 2) == [2, 3]                  # the buffer grew in place
+    seq.tokens[:] = [3, 3, 7, 3, 3]                         # another history under the same id (a rewritten sequence)
+    assert lk.propose(eng, 0, 1) == [7] and lk.hits == 3
