@@ -33,6 +33,33 @@ def weight_bytes(spec: ModelSpec, quant: str, group: int, head_int8: bool) -> in
     return int(body + small + embed + head)
 
 
+def linear_params(spec: ModelSpec) -> int:
+    """Parameters of the quantised projections (what a resident dense copy of the weights duplicates)."""
+    h = spec.hidden
+    lin_mlp = 3 * spec.inter * h
+    lin_gdn = (spec.conv_dim + spec.value_dim) * h + spec.value_dim * h
+    lin_full = (2 * spec.hq * spec.hd + 2 * spec.hkv * spec.hd) * h + spec.hq * spec.hd * h
+    return spec.n_layers * lin_mlp + spec.n_gdn * lin_gdn + spec.n_full * lin_full
+
+
+def draft_bytes(kind: str, spec: ModelSpec) -> int:
+    """Device memory of the draft model: the MTP head is one full-attention layer plus a [H, 2H] mix in int4 / bf16; the
+    DFlash2 draft is five bf16 layers, the tap projection and two selector code books (about 3.8 GB at 27B scale)."""
+    h = spec.hidden
+    if kind == "mtp":
+        layer = (2 * spec.hq * spec.hd + 2 * spec.hkv * spec.hd + spec.hq * spec.hd) * h + 3 * spec.inter * h
+        return int(layer * 0.53 + 2 * h * h * 2)
+    if kind == "dflash2":
+        from ..models.dflash2 import DraftSpec
+
+        d = DraftSpec(hidden=h, vocab=spec.vocab, inter=spec.inter)
+        return int(d.params() * 2)
+    return 0
+
+
+VISION_TOWER_BYTES = 900 << 20             # the 27-block tower in bf16 with its padded matrices
+
+
 def estimate(cfg) -> dict:
     v = cfg.values
     spec = PRESETS[v["model"]["name"]]()
@@ -42,15 +69,27 @@ def estimate(cfg) -> dict:
     avail = int(total * v["store"]["vram_budget"]) - (v["store"]["vram_reserve_mb"] << 20)
     kv_elem = {"fp8": 1, "int8": 1, "bf16": 2, "f16": 2}[v["store.kv"]["kv_dtype"]]
     w = weight_bytes(rspec, v["model"]["quant"], v["model"]["group"], v["model"]["head_quant"] != "bf16")
-    slots = v["store.gdn"]["gdn_slots"] + v["store.gdn"]["snap_max"]
+    # the prefill arms with resident dense weights keep a second copy of every projection: fp16 (tcr) or e4m3 (tc8r)
+    arm = v["kernel"]["prefill_gemm"]
+    resident = linear_params(rspec) * {"tcr": 2, "tc8r": 1}.get(arm, 0)
+    sp = v["spec"]
+    spec_on = sp["kind"] != "none" or sp["lookup"]
+    spec_rows = min(v["runtime"]["max_batch"], 8) if spec_on else 1
+    # state rows: one per sequence slot, the snapshot rows (at least two), the scratch rows of speculative verify steps
+    slots = v["store.gdn"]["gdn_slots"] + max(2, v["store.gdn"]["snap_max"]) + spec_rows
     gdn = slots * rspec.gdn_state_bytes()
+    draft = draft_bytes(sp["kind"], spec)                     # the draft models are not sharded
+    vision = VISION_TOWER_BYTES if v["vision"]["enabled"] else 0
     kv_per_tok = rspec.kv_bytes_per_token(kv_elem)
-    pool = avail - w - gdn - WORKSPACE_RESERVE
+    pool = avail - w - resident - gdn - draft - vision - WORKSPACE_RESERVE
     block = v["store"]["block_tokens"]
     pages = max(0, pool // (kv_per_tok * block))
+    host = (v["store"]["host_cache_mb"] + v["store"]["snap_host_mb"]) << 20
     return {"model": spec.name, "tp": world, "total_bytes": total, "avail_bytes": avail, "weights_bytes": w,
-            "gdn_state_bytes": gdn, "workspace_reserve_bytes": WORKSPACE_RESERVE, "kv_pool_bytes": max(0, pool),
+            "resident_copies_bytes": int(resident), "gdn_state_bytes": gdn, "state_rows": slots, "draft_bytes": draft,
+            "vision_bytes": vision, "workspace_reserve_bytes": WORKSPACE_RESERVE, "kv_pool_bytes": max(0, pool),
             "kv_bytes_per_token": kv_per_tok, "kv_pages": int(pages), "kv_tokens": int(pages * block),
+            "pinned_host_bytes": host, "disk_bytes": (v["store"]["disk_cache_mb"] + v["store"]["snap_disk_mb"]) << 20,
             "fits": pool > 0 and pages * block >= v["runtime"]["max_seq"],
             "max_seq": v["runtime"]["max_seq"]}
 

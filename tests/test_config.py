@@ -91,3 +91,18 @@ def test_every_shipped_profile_and_part_loads(tmp_path):
                  f'[store]\ndisk_dir = "{tmp_path}"\n')
     cfg = C.load(str(p))
     assert cfg.get("store.snap_disk_mb") == 16384 and cfg.get("store.evict_policy") == "lrfu"
+
+
+def test_memory_model_counts_resident_copies_draft_vision_and_state_rows():
+    base = estimate(C.load(str(ROOT / "full.toml")))
+    tcr = estimate(C.load(str(ROOT / "full.toml"), ['kernel.prefill_gemm="tcr"']))
+    tc8r = estimate(C.load(str(ROOT / "full.toml"), ['kernel.prefill_gemm="tc8r"']))
+    assert base["resident_copies_bytes"] == 0 and tcr["resident_copies_bytes"] == 2 * tc8r["resident_copies_bytes"]
+    assert 40e9 < tcr["resident_copies_bytes"] < 60e9                                   # an fp16 copy of a 27B model's projections
+    assert base["kv_pool_bytes"] - tcr["kv_pool_bytes"] == tcr["resident_copies_bytes"]
+    dfl = estimate(C.load(str(ROOT / "full.toml"), ['spec.kind="dflash2"', "spec.depth=7"]))
+    assert 3e9 < dfl["draft_bytes"] < 5e9 and dfl["state_rows"] == base["state_rows"] + 7   # batched verify scratch rows
+    vis = estimate(C.load(str(ROOT / "full.toml"), ["vision.enabled=true"]))
+    assert vis["vision_bytes"] > 0 and vis["kv_pool_bytes"] < base["kv_pool_bytes"]
+    snap = estimate(C.load(str(ROOT / "full.toml"), ["store.gdn.snap_max=8", "store.snap_host_mb=4096", "store.host_cache_mb=1024"]))
+    assert snap["state_rows"] == base["state_rows"] + 6 and snap["pinned_host_bytes"] == 5120 << 20
