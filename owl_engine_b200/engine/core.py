@@ -212,6 +212,8 @@ class Engine:
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self.prefix_hits = self.prefix_lookups = 0
+        self.last_recall: dict = {}
+        self.recall_modes: dict = {}
 
     # counters that used to live on the engine (kept for callers and tests)
     @property
@@ -356,6 +358,13 @@ class Engine:
                 self.pool.copy_slot(snap.row, slot)
                 seq.n_cached = seq.reused = keep * PAGE
                 self.prefix_hits += 1
+            # the recall report: "exact" = KV blocks and a recurrent state of the same point were both found; "context_only"
+            # = blocks matched but no state snapshot lies inside them (a hybrid model cannot resume from KV alone); "miss"
+            self.last_recall = {"mode": "exact" if keep else ("context_only" if m else "miss"), "prompt_blocks": len(seq.chain),
+                                "matched_blocks": m, "used_blocks": keep, "promoted_blocks": len(promoted),
+                                "from_lower_tiers": sum(1 for c in carriers[:keep0] if c != 0),
+                                "snapshot_tokens": snap.n_tokens if (snap is not None and keep) else 0}
+            self.recall_modes[self.last_recall["mode"]] = self.recall_modes.get(self.last_recall["mode"], 0) + 1
         self.seqs[sid] = seq
         return sid
 

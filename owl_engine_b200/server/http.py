@@ -161,7 +161,9 @@ class App:
         if parts[0] == "blocks":
             return await self._send(w, 200, q(lambda re: {"kv": re.e.kv.stats(), "free_rows": len(re.e.states.free_rows),
                                                            "snapshots": len(re.e.states.snaps),
-                                                           "host_used": re.e.host.used if re.e.host else 0}))
+                                                           "host_used": re.e.host.used if re.e.host else 0,
+                                                           "recall": {"last": getattr(re.e, "last_recall", {}),
+                                                                      "modes": getattr(re.e, "recall_modes", {})}}))
         if parts[0] == "agent":
             if parts[1:] == ["clear"] and method == "POST":
                 q(lambda re: re.trace.clear())

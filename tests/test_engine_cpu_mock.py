@@ -272,3 +272,17 @@ def test_a_turn_cancelled_between_prefill_chunks_leaves_an_anchor_for_the_retry(
     want = Engine(cfg(n_pages=128, max_seq=1024, prefill_chunk=64), device="cpu").generate(prompt, 6)
     assert re_.generate(prompt, TurnOpts(max_new=6, ignore_eos=True)) == want
     assert re_.trace[-1]["cached_tokens"] == 192
+
+
+def test_recall_report_tells_exact_from_context_only_from_miss():
+    e = Engine(cfg(n_snap_rows=1), device="cpu")
+    p, other = toks(100, 1), toks(100, 2)
+    e.generate(p, 4)
+    assert e.last_recall["mode"] == "miss"
+    e.generate(p, 4)
+    assert e.last_recall["mode"] == "exact" and e.last_recall["used_blocks"] == 6 and e.last_recall["snapshot_tokens"] == 96
+    e.generate(other, 4)                                   # takes the only snapshot row: p's blocks stay, its state is gone
+    sid = e.add_sequence(p)
+    assert e.last_recall["mode"] == "context_only" and e.last_recall["matched_blocks"] == 6 and e.seqs[sid].reused == 0
+    e.free_sequence(sid, publish=False)
+    assert e.recall_modes == {"miss": 2, "exact": 1, "context_only": 1}
