@@ -650,7 +650,10 @@ class ChannelSplitter:
                 if hit is not None:
                     p, m = hit
                     if self.buf[:p].strip():
-                        self._go(TEXT)                    # real text before the marker: hand it to the text channel
+                        # real text before the marker: hand it to the text channel, without the template's white space in
+                        # front of it (the same text arriving in smaller pieces is stripped below: one rule for both)
+                        self.buf = self.buf.lstrip()
+                        self._go(TEXT)
                         continue
                     self.buf = self.buf[p if m == FUNC_OPEN else p + len(m):]
                     self._go({TOOL_CLOSE: TEXT, CALLS_CLOSE: TEXT, TOOL_OPEN: TOOL, FUNC_OPEN: BARE, CALLS_OPEN: INVOKE}[m])
