@@ -14,6 +14,8 @@ PIECES = [
     "<tool_call>", "</tool_call>", '{"name": "get_weather", "arguments": {"city": "Oslo", "days": 2}}',
     "<function=get_weather>", "<parameter=city>", "Oslo", "</parameter>", "</function>", "<tool", "</thi", "<|im_end|>",
     "<thinking>", "</thinking>", "{", "}", '"', "é", "日本",
+    "<thought>", "</thought>", "<function_calls>", "</function_calls>", '<invoke name="get_weather">', "</invoke>",
+    '<parameter name="city">', "  ", "\n\n", "<function=", "<function=unknown_tool>", '{"name": "get_weather"', "</",
 ]
 
 
