@@ -77,3 +77,32 @@ def test_a_well_formed_call_is_found_whatever_surrounds_it(before, after, city, 
     assert name == "get_weather" and json.loads(args) == {"city": city, "days": days}
     shown = "".join(e[1] for e in ev if e[0] == "text")
     assert shown.replace("\n", "").replace(" ", "") == (before + after).replace("\n", "").replace(" ", "")
+
+
+@settings(max_examples=300, deadline=None)
+@given(st.text(alphabet="ab <>\nSTOPé日", max_size=60), st.lists(st.sampled_from(["STOP", "\n\n", "ab", "é日", "<b>"]), min_size=1, max_size=3,
+                                                                   unique=True))
+def test_streamed_content_ends_before_the_first_stop_string_whatever_the_token_boundaries(text, stops):
+    """Through the whole response path (byte tokens -> incremental detokeniser -> splitter -> stop holding): the streamed
+    content is the text up to the first stop string, the chunks never contain a piece of a stop string that then completes,
+    and multi-byte characters are never cut."""
+    from owl_engine_b200.engine.tokenizer import ByteTokenizer, StreamDecoder
+    from owl_engine_b200.server.openai import Streamer
+
+    tok = ByteTokenizer()
+    s = Streamer("m", StreamDecoder(tok), stops)
+    chunks = []
+    for t in tok.encode(text):
+        chunks += s.on_token(t)
+        if s.stopped:
+            break
+    chunks += s.finish("length", {"prompt_tokens": 1, "completion_tokens": 1}, False)
+    got = "".join(c["choices"][0]["delta"].get("content", "") for c in chunks)
+    cut = min((text.find(x) for x in stops if x in text), default=len(text))
+    want = text[:cut]
+    # the splitter drops nothing here except marker look-alikes it must hold until they are decided; "<b>" is plain text
+    assert got == want, (got, want)
+    assert chunks[-1]["choices"][0]["finish_reason"] == ("stop" if cut < len(text) else "length")
+    for c in chunks:
+        piece = c["choices"][0]["delta"].get("content", "")
+        assert "\\ufffd" not in piece.encode("unicode_escape").decode()
