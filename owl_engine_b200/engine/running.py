@@ -396,6 +396,10 @@ class RunningEngine:
 
                 seq = self.e.seqs[t.sid]
                 gen = seq.tokens[len(padded.ids):]
+                if t.opts.session in self.parked and self.parked[t.opts.session][0] != t.sid:
+                    # two turns of one session ran side by side (the HTTP layer serialises a session, this interface does
+                    # not): the sequence parked by the one that ended first gives way, it must not be orphaned
+                    self._release_parked(t.opts.session)
                 self.parked[t.opts.session] = (t.sid, E.PaddedSeq(padded.ids + gen, padded.spans, padded.pads), self._tick)
                 self.parked_prompt_len[t.opts.session] = len(t.tokens)
                 while len(self.parked) > self.max_parked:

@@ -286,3 +286,15 @@ def test_recall_report_tells_exact_from_context_only_from_miss():
     assert e.last_recall["mode"] == "context_only" and e.last_recall["matched_blocks"] == 6 and e.seqs[sid].reused == 0
     e.free_sequence(sid, publish=False)
     assert e.recall_modes == {"miss": 2, "exact": 1, "context_only": 1}
+
+
+def test_two_turns_of_one_session_side_by_side_do_not_orphan_a_parked_sequence():
+    e = Engine(cfg(n_pages=64), device="cpu")
+    re_ = RunningEngine(e, max_batch=2, park_sessions=True, max_parked=2)
+    a = re_.submit(toks(40, 1), TurnOpts(max_new=3, ignore_eos=True, session="s"))
+    b = re_.submit(toks(40, 1), TurnOpts(max_new=5, ignore_eos=True, session="s"))
+    assert a != b
+    re_.run_until_idle()
+    assert list(re_.parked) == ["s"] and len(e.seqs) == 1               # one parked sequence, the other was released
+    re_._release_parked("s")
+    assert not e.seqs and e.kv.free_pages + e.kv.stats()["device_nodes"] == e.cfg.n_pages

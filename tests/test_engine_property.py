@@ -48,3 +48,70 @@ def test_cached_generation_equals_cold_generation(requests, stride, tiers, polic
         warm.close()
     finally:
         shutil.rmtree(tmp, ignore_errors=True)
+
+
+@settings(max_examples=20, deadline=None)
+@given(st.lists(st.one_of(
+    st.tuples(st.just("submit"), st.integers(0, 2), st.integers(0, 3), st.integers(1, 60), st.integers(1, 16), st.sampled_from([None, None, "a", "b"])),
+    st.tuples(st.just("pump"), st.integers(1, 12)),
+    st.tuples(st.just("cancel"), st.integers(0, 7)),
+    st.tuples(st.just("follow"), st.integers(1, 30), st.integers(1, 12))), min_size=4, max_size=24),
+    st.booleans(), st.sampled_from(["queue", "reject"]))
+def test_running_engine_under_random_traffic_serves_what_a_cold_engine_serves(ops, park, on_full):
+    """Concurrent turns, parked and nameless sessions, cancellations, a pool that overflows: every turn that completes
+    carries the tokens of a cold engine, rejected turns say why, and nothing is left allocated afterwards."""
+    from owl_engine_b200.engine.running import RunningEngine, TurnOpts
+
+    kw = dict(model="test-hybrid", n_slots=3, max_seqs=3, max_seq=1024, prefill_chunk=64, msg_open_ids=MARK, snap_msg_min_gap=32,
+              snap_msg_recent=2, snap_decode_stride=1)
+    cold = Engine(EngineConfig(n_pages=256, n_snap_rows=2, prefix_cache=False, **kw), device="cpu")
+    e = Engine(EngineConfig(n_pages=48, n_snap_rows=3, **kw), device="cpu")
+    re_ = RunningEngine(e, max_batch=2, on_full=on_full, park_sessions=park, max_parked=2, auto_sessions=park, prefill_every=2)
+    live, done, last = {}, [], None
+
+    def drain():
+        for tid, (t, prompt, n_new) in list(live.items()):
+            out, end = t.setdefault("out", []), None
+            while not t["sink"].empty():
+                ev = t["sink"].get()
+                if ev[0] == "token":
+                    out.append(ev[2])
+                elif ev[0] in ("completed", "failed"):
+                    end = ev
+            if end is not None:
+                del live[tid]
+                done.append((prompt, n_new, out, end))
+
+    def submit(prompt, n_new, session):
+        tid = re_.submit(prompt, TurnOpts(max_new=n_new, ignore_eos=True, session=session))
+        live[tid] = ({"sink": re_.turns[tid].sink}, prompt, n_new)
+
+    for op in ops:
+        if op[0] == "submit":
+            _, stem, variant, tail, n_new, session = op
+            submit(STEMS[stem] + list(MARK) + _tokens(tail, 1000 * stem + variant), n_new, session)
+        elif op[0] == "follow" and done:
+            prompt, _, out, end = done[-1]
+            if end[0] == "completed":
+                submit(prompt + out + list(MARK) + _tokens(op[1], 5), op[2], None)
+        elif op[0] == "pump":
+            for _ in range(op[1]):
+                re_.pump()
+        elif op[0] == "cancel" and live:
+            re_.cancel_turn(sorted(live)[op[1] % len(live)])
+        drain()
+    re_.run_until_idle(max_steps=5000)
+    drain()
+    assert not live and re_.idle()
+    for prompt, n_new, out, end in done:
+        if end[0] == "completed" and end[2] in ("length", "stop"):
+            assert out == cold.generate(prompt, n_new), (len(prompt), n_new, end)
+        elif end[0] == "completed":
+            assert end[2] == "cancelled" and out == cold.generate(prompt, n_new)[:len(out)]      # what was emitted was right
+        else:
+            assert "rejected (" in end[2] and "retry_after_ms=" in end[2]
+    for name in list(re_.parked):
+        re_._release_parked(name)
+    st_ = e.kv.stats()
+    assert not e.seqs and e.kv.free_pages + st_["device_nodes"] == e.cfg.n_pages and len(e.states.free_rows) == 3
+    assert re_.reservations.outstanding == 0
