@@ -26,7 +26,8 @@ class Snapshot:
     rank: int = 0          # rung of the binary ladder
     session: str | None = None
     tier: str = "device"   # "device" | "host" | "disk"
-    last_use: float = field(default_factory=time.monotonic)
+    last_use: int = 0      # the store's use counter at the last touch (a counter, not a clock: the ranks of a tensor-parallel
+                           # job must pick the same victims, and their clocks differ)
 
 
 class StateStore:
@@ -45,6 +46,11 @@ class StateStore:
         self.on_evict = None
         self.on_forget = None
         self.evicted = self.skipped = 0
+        self._uses = 0
+
+    def _touch(self, s: Snapshot) -> None:
+        self._uses += 1
+        s.last_use = self._uses
 
     def borrow(self, turn: int) -> int | None:
         if not self.free_rows:
@@ -88,7 +94,7 @@ class StateStore:
         at its cap replaces its own lowest-ranked snapshot or, if the newcomer ranks below everything held, gets None."""
         s = self.snaps.get(chain_hash)
         if s is not None:
-            s.last_use = time.monotonic()
+            self._touch(s)
             if P.PRIORITY[klass] > P.PRIORITY[s.klass]:
                 s.klass, s.rank = klass, rank
             return s.row
@@ -109,6 +115,7 @@ class StateStore:
             self.on_forget(stale)
         row = self.snap_rows.pop()
         self.snaps[chain_hash] = Snapshot(row, chain_hash, n_tokens, klass, rank, session)
+        self._touch(self.snaps[chain_hash])
         return row
 
     def supersede(self, chain, n_tokens: int) -> int:
@@ -132,7 +139,7 @@ class StateStore:
         for h in reversed(list(chain_hashes)):
             s = self.snaps.get(int(h))
             if s:
-                s.last_use = time.monotonic()
+                self._touch(s)
                 return s
         return None
 

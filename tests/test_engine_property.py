@@ -115,3 +115,62 @@ def test_running_engine_under_random_traffic_serves_what_a_cold_engine_serves(op
     st_ = e.kv.stats()
     assert not e.seqs and e.kv.free_pages + st_["device_nodes"] == e.cfg.n_pages and len(e.states.free_rows) == 3
     assert re_.reservations.outstanding == 0
+
+
+@settings(max_examples=12, deadline=None)
+@given(st.lists(st.one_of(
+    st.tuples(st.just("submit"), st.integers(0, 2), st.integers(0, 3), st.integers(1, 60), st.integers(1, 12), st.sampled_from([None, "a"])),
+    st.tuples(st.just("pump"), st.integers(1, 10)),
+    st.tuples(st.just("cancel"), st.integers(0, 7))), min_size=4, max_size=18), st.booleans())
+def test_follower_rank_ends_in_the_leaders_state(ops, park):
+    """Tensor-parallel serving keeps its ranks in lockstep by mirroring the leader's engine calls over the step ring and
+    relying on the engine's host logic being a function of its call sequence. Random traffic through a leader (scheduler,
+    parked sessions, cancellations, an overflowing pool with a host tier) and a follower that only replays the ring: both
+    engines must end with the same pages, tree, snapshots and token streams."""
+    import os
+    import threading
+
+    from owl_engine_b200.engine import tp_serve as T
+    from owl_engine_b200.engine.running import RunningEngine, TurnOpts
+    from owl_engine_b200.parallel.ring import StepRing
+
+    kw = dict(model="test-hybrid", n_pages=40, n_slots=3, n_snap_rows=2, max_seqs=3, max_seq=1024, prefill_chunk=64, msg_open_ids=MARK,
+              snap_msg_min_gap=32, snap_msg_recent=2, snap_decode_stride=1, host_cache_mb=1, snap_host_mb=1)
+    lead, foll = Engine(EngineConfig(**kw), device="cpu"), Engine(EngineConfig(**kw), device="cpu")
+    name = f"/owl_prop_tp_{os.getpid()}_{abs(hash(str(ops))) % 10 ** 8}"
+    ring = StepRing.create(name, 1, capacity=8 << 20)
+    rd = StepRing.open(name, 0, 20.0)
+    applied = {}
+    th = threading.Thread(target=lambda: applied.setdefault("n", T.follower_loop(foll, rd, None, idle_timeout_s=20.0)))
+    th.start()
+    me = T.MirroredEngine(lead, ring)
+    re_ = RunningEngine(me, max_batch=2, on_full="queue", park_sessions=park, max_parked=2, auto_sessions=park, prefill_every=2)
+    live = []
+    try:
+        for op in ops:
+            if op[0] == "submit":
+                _, stem, variant, tail, n_new, session = op
+                live.append(re_.submit(STEMS[stem] + list(MARK) + _tokens(tail, 1000 * stem + variant),
+                                       TurnOpts(max_new=n_new, ignore_eos=True, session=session)))
+            elif op[0] == "pump":
+                for _ in range(op[1]):
+                    re_.pump()
+            elif op[0] == "cancel" and live:
+                re_.cancel_turn(live[op[1] % len(live)])
+        re_.run_until_idle(max_steps=5000)
+        for nm in list(re_.parked):
+            re_._release_parked(nm)
+    finally:
+        me.shutdown()
+        th.join(30)
+        rd.free()
+        ring.free()
+    assert "n" in applied and not th.is_alive()
+    a, b = lead.kv.stats(), foll.kv.stats()
+    assert a == b and lead.kv.free_pages == foll.kv.free_pages
+    assert sorted(lead.kv.list()) == sorted(foll.kv.list())
+    snaps = lambda e: {h: (s.row, s.n_tokens, s.klass) for h, s in e.states.snaps.items()}
+    assert snaps(lead) == snaps(foll)
+    assert sorted(lead.states.lower) == sorted(foll.states.lower) and lead.rel.facts()["demoted"] == foll.rel.facts()["demoted"]
+    assert lead.runner.launches == foll.runner.launches and not foll.seqs and not lead.seqs
+    assert torch.equal(lead.pool.conv_state, foll.pool.conv_state) and torch.equal(lead.pool.k_pool, foll.pool.k_pool)
