@@ -42,6 +42,24 @@ class _Replay:
         self.r.step_forward(H.StepLayout(self.b, self.t))
 
 
+class _Fold:
+    """Stand-in for the captured fold graphs: replays the recurrent-state update of the first rows of the last step."""
+
+    def __init__(self, runner, b: int, t: int, batched: bool):
+        self.r, self.b, self.t, self.batched = runner, b, t, batched
+
+    def replay(self) -> None:
+        r = self.r
+        for i in range(self.b):
+            slot = int(r.fold_slots[i]) if self.batched else int(r.fold_slot[0])
+            n = int(r.fold_tlen[i]) if self.batched else self.t
+            if slot < 0:
+                continue
+            for tok, pos in r._saved.get(i, [])[:n]:
+                r._set_state(slot, (r._state(slot) * 31 + tok + pos) % (1 << 23))
+                r.launches += 1
+
+
 class NullRunner:
     """Stand-in for ``HybridRunner`` on host tensors (see the module docstring for its arithmetic)."""
     MAX_ROWS = H.HybridRunner.MAX_ROWS
@@ -58,6 +76,10 @@ class NullRunner:
         self.graphs: dict = {}
         self.uniform_rows = True
         self.gdn_save = self.taps = self.tap_sink = None
+        self._saved: dict = {}        # batch index -> [(token, position)] of the last step (what a fold replays)
+        self.fold_slot = torch.full((1,), -1, dtype=torch.int32)
+        self.fold_slots = torch.full((m,), -1, dtype=torch.int32)
+        self.fold_tlen = torch.zeros(m, dtype=torch.int32)
         self.decode_gemv, self.act_bits, self.vocab_split = "null", 15, False
         self.launches = 0
 
@@ -103,8 +125,10 @@ class NullRunner:
             slot, row, ctx = int(v["gslot"][i]), int(v["bt_row"][i]), int(v["ctx"][i])
             if slot < 0:
                 continue
+            self._saved[i] = []
             for j in range(lay.t):
                 pos = ctx - lay.t + j
+                self._saved[i].append((int(v["ids"][i * lay.t + j]), pos))
                 self.out_tok[i * lay.t + j] = self._consume(row, slot, pos, int(v["ids"][i * lay.t + j]))
 
     def capture(self, b: int, t: int = 1, *, ctx_hint: int = 2048, advance: bool = False, sample: bool = True):
@@ -117,6 +141,18 @@ class NullRunner:
         if g is None:
             g = self.graphs[key] = _Replay(self, b, t)
         return g
+
+    # speculative decoding: the verify step keeps its rows (above), a fold replays the accepted ones on the restored state
+    def enable_gdn_save(self) -> None:
+        if self.gdn_save is None:
+            self.gdn_save = True
+            self.graphs.clear()
+
+    def capture_fold(self, t: int):
+        return self.graphs.setdefault(("fold", t), _Fold(self, 1, t, False))
+
+    def capture_fold_batch(self, b: int, t: int):
+        return self.graphs.setdefault(("foldb", b, t), _Fold(self, b, t, True))
 
     def prefill_chunk_forward(self, ids, pos0: int, seq_row: int, slot: int, want_logits: bool = True, embeds=None, pos3=None,
                               snap=None):

@@ -549,7 +549,8 @@ def verify_batch(engine: Engine, sids: list[int], rows: list[list[int]]) -> list
     r.inp[:n].copy_(engine.h_inp[:n], non_blocking=True)
     graph.replay()
     engine.h_tok[:m].copy_(r.out_tok[:m], non_blocking=True)
-    torch.cuda.current_stream().synchronize()
+    if not engine.mock:
+        torch.cuda.current_stream().synchronize()
     engine.h2d_bytes += n * 4
     engine.d2h_bytes += m * 4
     engine._check_status()
@@ -585,7 +586,8 @@ def verify_step(engine: Engine, sid: int, rows: list[int]) -> list[int]:
     r.inp[:n].copy_(engine.h_inp[:n], non_blocking=True)
     graph.replay()
     engine.h_tok[:t].copy_(r.out_tok[:t], non_blocking=True)
-    torch.cuda.current_stream().synchronize()
+    if not engine.mock:
+        torch.cuda.current_stream().synchronize()
     engine.h2d_bytes += n * 4
     engine.d2h_bytes += t * 4
     return [int(x) for x in engine.h_tok_np[:t]]

@@ -56,8 +56,8 @@ def test_cached_generation_equals_cold_generation(requests, stride, tiers, polic
     st.tuples(st.just("pump"), st.integers(1, 12)),
     st.tuples(st.just("cancel"), st.integers(0, 7)),
     st.tuples(st.just("follow"), st.integers(1, 30), st.integers(1, 12))), min_size=4, max_size=24),
-    st.booleans(), st.sampled_from(["queue", "reject"]))
-def test_running_engine_under_random_traffic_serves_what_a_cold_engine_serves(ops, park, on_full):
+    st.booleans(), st.sampled_from(["queue", "reject"]), st.booleans())
+def test_running_engine_under_random_traffic_serves_what_a_cold_engine_serves(ops, park, on_full, spec):
     """Concurrent turns, parked and nameless sessions, cancellations, a pool that overflows: every turn that completes
     carries the tokens of a cold engine, rejected turns say why, and nothing is left allocated afterwards."""
     from owl_engine_b200.engine.running import RunningEngine, TurnOpts
@@ -65,8 +65,12 @@ def test_running_engine_under_random_traffic_serves_what_a_cold_engine_serves(op
     kw = dict(model="test-hybrid", n_slots=3, max_seqs=3, max_seq=1024, prefill_chunk=64, msg_open_ids=MARK, snap_msg_min_gap=32,
               snap_msg_recent=2, snap_decode_stride=1)
     cold = Engine(EngineConfig(n_pages=256, n_snap_rows=2, prefix_cache=False, **kw), device="cpu")
-    e = Engine(EngineConfig(n_pages=48, n_snap_rows=3, **kw), device="cpu")
-    re_ = RunningEngine(e, max_batch=2, on_full=on_full, park_sessions=park, max_parked=2, auto_sessions=park, prefill_every=2)
+    from owl_engine_b200.engine.spec import LookupDraft, SpecRunner
+
+    e = Engine(EngineConfig(n_pages=48, n_snap_rows=3, spec_rows=2, **kw), device="cpu")
+    runner = SpecRunner(LookupDraft(1, 6), depth=3, degrade_after=3, probe_every=4) if spec else None      # speculative rounds too
+    re_ = RunningEngine(e, max_batch=2, on_full=on_full, park_sessions=park, max_parked=2, auto_sessions=park, prefill_every=2,
+                        spec_runner=runner)
     live, done, last = {}, [], None
 
     def drain():
