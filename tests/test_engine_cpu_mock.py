@@ -155,8 +155,8 @@ def test_graph_fleet_plans_and_meters_on_the_cpu_face():
     assert names[:4] == ["graph.decode.b1.ctx2048", "graph.decode.b2.ctx2048", "graph.decode.b3.ctx2048", "graph.decode.b4.ctx2048"]
     assert "graph.verify.b1.t4.ctx2048" in names and "graph.batch_spec.b2.t4.ctx2048" in names and "graph.fold.b1.t4" in names
     rep = fleet.assemble()
-    assert rep["states"].get("captured", 0) == 6 and rep["states"].get("eager", 0) == 2          # the stand-in runner has no fold
-    assert {(4, 1), (1, 4), (2, 4)} <= set(e.runner.graphs) and rep["bytes"] == 0
+    assert rep["states"] == {"captured": 8}                      # decode x 4, verify, batched verify, fold, batched fold
+    assert {(4, 1), (1, 4), (2, 4), ("fold", 4), ("foldb", 2, 4)} <= set(e.runner.graphs) and rep["bytes"] == 0
     off = Engine(cfg(), device="cpu", limits=MockLimits(graph_capture=False))
     rep = GraphFleet(off, max_batch=2).assemble()
     assert rep["states"] == {"eager": 2} and "CaptureUnsupported" in rep["entries"][0]["error"]
