@@ -125,8 +125,8 @@ def test_running_engine_under_random_traffic_serves_what_a_cold_engine_serves(op
 @given(st.lists(st.one_of(
     st.tuples(st.just("submit"), st.integers(0, 2), st.integers(0, 3), st.integers(1, 60), st.integers(1, 12), st.sampled_from([None, "a"])),
     st.tuples(st.just("pump"), st.integers(1, 10)),
-    st.tuples(st.just("cancel"), st.integers(0, 7))), min_size=4, max_size=18), st.booleans())
-def test_follower_rank_ends_in_the_leaders_state(ops, park):
+    st.tuples(st.just("cancel"), st.integers(0, 7))), min_size=4, max_size=18), st.booleans(), st.booleans())
+def test_follower_rank_ends_in_the_leaders_state(ops, park, spec):
     """Tensor-parallel serving keeps its ranks in lockstep by mirroring the leader's engine calls over the step ring and
     relying on the engine's host logic being a function of its call sequence. Random traffic through a leader (scheduler,
     parked sessions, cancellations, an overflowing pool with a host tier) and a follower that only replays the ring: both
@@ -138,17 +138,23 @@ def test_follower_rank_ends_in_the_leaders_state(ops, park):
     from owl_engine_b200.engine.running import RunningEngine, TurnOpts
     from owl_engine_b200.parallel.ring import StepRing
 
-    kw = dict(model="test-hybrid", n_pages=40, n_slots=3, n_snap_rows=2, max_seqs=3, max_seq=1024, prefill_chunk=64, msg_open_ids=MARK,
-              snap_msg_min_gap=32, snap_msg_recent=2, snap_decode_stride=1, host_cache_mb=1, snap_host_mb=1)
+    from owl_engine_b200.engine.spec import LookupDraft, SpecRunner
+
+    kw = dict(model="test-hybrid", n_pages=40, n_slots=3, n_snap_rows=2, spec_rows=2, max_seqs=3, max_seq=1024, prefill_chunk=64,
+              msg_open_ids=MARK, snap_msg_min_gap=32, snap_msg_recent=2, snap_decode_stride=1, host_cache_mb=1, snap_host_mb=1)
     lead, foll = Engine(EngineConfig(**kw), device="cpu"), Engine(EngineConfig(**kw), device="cpu")
     name = f"/owl_prop_tp_{os.getpid()}_{abs(hash(str(ops))) % 10 ** 8}"
     ring = StepRing.create(name, 1, capacity=8 << 20)
     rd = StepRing.open(name, 0, 20.0)
     applied = {}
-    th = threading.Thread(target=lambda: applied.setdefault("n", T.follower_loop(foll, rd, None, idle_timeout_s=20.0)))
+    make_spec = lambda: SpecRunner(LookupDraft(1, 6), depth=3, degrade_after=3, probe_every=4) if spec else None
+    foll_spec = make_spec()
+    th = threading.Thread(target=lambda: applied.setdefault("n", T.follower_loop(foll, rd, foll_spec, idle_timeout_s=20.0)))
     th.start()
     me = T.MirroredEngine(lead, ring)
-    re_ = RunningEngine(me, max_batch=2, on_full="queue", park_sessions=park, max_parked=2, auto_sessions=park, prefill_every=2)
+    lead_spec = T.MirroredSpec(make_spec(), ring) if spec else None      # speculative rounds are mirrored as whole calls
+    re_ = RunningEngine(me, max_batch=2, on_full="queue", park_sessions=park, max_parked=2, auto_sessions=park, prefill_every=2,
+                        spec_runner=lead_spec)
     live = []
     try:
         for op in ops:
@@ -177,4 +183,6 @@ def test_follower_rank_ends_in_the_leaders_state(ops, park):
     assert snaps(lead) == snaps(foll)
     assert sorted(lead.states.lower) == sorted(foll.states.lower) and lead.rel.facts()["demoted"] == foll.rel.facts()["demoted"]
     assert lead.runner.launches == foll.runner.launches and not foll.seqs and not lead.seqs
+    if spec:
+        assert vars(lead_spec.stats) == vars(foll_spec.stats)                 # the same rounds, drafts, folds on both ranks
     assert torch.equal(lead.pool.conv_state, foll.pool.conv_state) and torch.equal(lead.pool.k_pool, foll.pool.k_pool)
