@@ -116,8 +116,17 @@ class App:
             if path == "/v1/models":
                 return await self._send(writer, 200, {"object": "list", "data": [{"id": self.model, "object": "model"}]})
             if path == "/tokenize" and method == "POST":
-                d = json.loads(body or b"{}")
-                text = d.get("text") if "text" in d else self.tpl.render(d.get("messages", []), tools=d.get("tools"))
+                try:
+                    d = json.loads(body or b"{}")
+                    if not isinstance(d, dict):
+                        raise ValueError("the body must be an object")
+                    text = d.get("text") if "text" in d else self.tpl.render(d.get("messages", []), tools=d.get("tools"))
+                    if not isinstance(text, str):
+                        raise ValueError("text must be a string")
+                except BadRequest:
+                    raise
+                except Exception as e:   # noqa: BLE001
+                    raise BadRequest(f"cannot tokenize this body: {e!r}") from None
                 ids = self.tok.encode(text)
                 return await self._send(writer, 200, {"tokens": ids, "count": len(ids)})
             if path.startswith("/debug/"):
@@ -144,17 +153,27 @@ class App:
             return await self._send(w, 200, METRICS.tree())
         if parts[0] == "log":
             if len(parts) >= 3 and parts[1] == "level" and method == "POST":
-                LOG.set_level(parts[2])
+                try:
+                    LOG.set_level(parts[2])
+                except ValueError as e:
+                    raise BadRequest(str(e)) from None
             elif len(parts) >= 3 and parts[1] == "tags" and method == "POST":
                 LOG.set_tags([t for t in parts[2].split(",") if t])
             return await self._send(w, 200, {"level": LOG.level, "tags_allow": LOG.allow, "tail": LOG.tail(100)})
         if parts[0] == "step":
             if method == "POST":
-                d = json.loads(body or b"{}")
-                if "mode" in d:
-                    GATE.configure(d["mode"], d.get("ms", GATE.ms), d.get("every", 1))
-                else:
-                    GATE.step(int(d.get("n", 1)))
+                try:
+                    d = json.loads(body or b"{}")
+                    if not isinstance(d, dict):
+                        raise ValueError("the body must be an object")
+                    if "mode" in d:
+                        if d["mode"] not in ("off", "sticky", "single"):
+                            raise ValueError("mode must be off | sticky | single")
+                        GATE.configure(d["mode"], int(d.get("ms", GATE.ms)), int(d.get("every", 1)))
+                    else:
+                        GATE.step(int(d.get("n", 1)))
+                except (ValueError, TypeError, UnicodeDecodeError) as e:
+                    raise BadRequest(f"/debug/step: {e}") from None
             return await self._send(w, 200, GATE.status())
         if parts[0] == "vram":
             return await self._send(w, 200, q(lambda re: _vram(re)))
@@ -218,7 +237,12 @@ class App:
         kwargs = dict(req.chat_template_kwargs)
         if req.reasoning_effort in ("none", "minimal"):
             kwargs.setdefault("enable_thinking", False)
-        prompt = self.tpl.render(req.messages, tools=req.tools, **kwargs)
+        try:
+            prompt = self.tpl.render(req.messages, tools=req.tools, **kwargs)
+        except BadRequest:
+            raise
+        except Exception as e:   # noqa: BLE001  (a template cannot be told apart from its input here: the request gets the blame)
+            raise BadRequest(f"the chat template could not render these messages: {e!r}") from None
         ids = self.tok.encode(prompt)
         if self.prompt_dump:
             log.LOG.emit("warn", "server.prompt", f"{len(ids)} tokens: {prompt!r}")

@@ -48,13 +48,48 @@ class ChatRequest:
     def parse(cls, body: bytes) -> "ChatRequest":
         try:
             d = json.loads(body)
-        except json.JSONDecodeError as e:
+        except (ValueError, UnicodeDecodeError) as e:      # JSONDecodeError is a ValueError; bytes that are not UTF-8
             raise BadRequest(f"invalid JSON: {e}") from None
         if not isinstance(d, dict) or not isinstance(d.get("messages"), list) or not d["messages"]:
             raise BadRequest("messages must be a non-empty array")
         for m in d["messages"]:
-            if not isinstance(m, dict) or m.get("role") not in ("system", "user", "assistant", "tool", "developer"):
+            if not isinstance(m, dict) or not isinstance(m.get("role"), str) or \
+                    m["role"] not in ("system", "user", "assistant", "tool", "developer"):
                 raise BadRequest("every message needs a role of system|user|assistant|tool")
+            c = m.get("content")
+            if c is not None and not isinstance(c, (str, list)):
+                raise BadRequest("message content must be a string, an array of parts or null")
+            if isinstance(c, list):
+                for part in c:
+                    if not isinstance(part, dict) or not isinstance(part.get("type"), str):
+                        raise BadRequest("every content part must be an object with a type")
+                    if part["type"] == "text" and not isinstance(part.get("text"), str):
+                        raise BadRequest("a text part needs a text string")
+                    if part["type"] == "image_url" and not isinstance(part.get("image_url"), (dict, str)):
+                        raise BadRequest("an image_url part needs an image_url object")
+                    if part["type"] not in ("text", "image_url"):
+                        raise BadRequest(f"content part type {part['type']!r} is not supported (text, image_url)")
+            tc = m.get("tool_calls")
+            if tc is not None and (not isinstance(tc, list) or not all(isinstance(x, dict) for x in tc)):
+                raise BadRequest("tool_calls must be an array of objects")
+            if m.get("name") is not None and not isinstance(m["name"], str):
+                raise BadRequest("message name must be a string")
+
+        def typed(k, types, what):
+            v = d.get(k)
+            if v is not None and not isinstance(v, types):
+                raise BadRequest(f"{k} must be {what}")
+            return v
+
+        typed("session", str, "a string")
+        typed("stream_options", dict, "an object")
+        typed("chat_template_kwargs", dict, "an object")
+        typed("reasoning_effort", str, "a string")
+        tools = typed("tools", list, "an array")
+        if tools is not None and not all(isinstance(t, dict) and isinstance(t.get("function", {}), dict) for t in tools):
+            raise BadRequest("every tool must be an object with a function object")
+        for k in ("stream", "ignore_eos"):
+            typed(k, bool, "a boolean")
 
         def num(k, typ, lo=None, hi=None):
             v = d.get(k)
@@ -76,8 +111,9 @@ class ChatRequest:
             if isinstance(m.get("content"), list):
                 for part in m["content"]:
                     if part.get("type") == "image_url":
-                        url = (part.get("image_url") or {}).get("url", "")
-                        if not url.startswith("data:"):
+                        iu = part.get("image_url")
+                        url = iu if isinstance(iu, str) else (iu or {}).get("url", "")
+                        if not isinstance(url, str) or not url.startswith("data:") or "," not in url:
                             raise BadRequest("only data: URLs are accepted for images")
                         try:
                             raw = base64.b64decode(url.split(",", 1)[1])
