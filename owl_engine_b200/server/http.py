@@ -29,11 +29,13 @@ from .chat_tpl import ChatTemplate
 from .openai import BadRequest, ChatRequest, Streamer
 from .toolcall import RepeatGuard
 
-REASONS = {200: "OK", 400: "Bad Request", 404: "Not Found", 405: "Method Not Allowed", 429: "Too Many Requests",
+REASONS = {200: "OK", 400: "Bad Request", 404: "Not Found", 405: "Method Not Allowed", 413: "Content Too Large", 429: "Too Many Requests",
            503: "Service Unavailable", 500: "Internal Server Error"}
 
 
 class App:
+    MAX_BODY = 512 << 20        # a request body (images travel as data URLs) may not be larger than this
+
     def __init__(self, client, tokenizer, model_name: str, template: ChatTemplate | None = None,
                  default_sampling: SamplingParams | None = None, default_max_new: int = 4096, max_new_cap: int = 32768,
                  queue_timeout_ms: int = 30000, keepalive_ms: int = 15000, max_concurrent: int = 8, vision=None,
@@ -75,7 +77,16 @@ class App:
                         break
                     k, _, v = h.decode("latin1").partition(":")
                     headers[k.strip().lower()] = v.strip()
-                body = await reader.readexactly(int(headers.get("content-length", 0))) if headers.get("content-length") else b""
+                try:
+                    n_body = int(headers.get("content-length") or 0)
+                except ValueError:
+                    n_body = -1
+                if n_body < 0 or n_body > self.MAX_BODY:
+                    await self._send(writer, 400 if n_body < 0 else 413,
+                                     {"error": {"message": "bad Content-Length" if n_body < 0 else f"body larger than {self.MAX_BODY} bytes",
+                                                "type": "invalid_request_error"}})
+                    break
+                body = await reader.readexactly(n_body) if n_body else b""
                 keep = headers.get("connection", "keep-alive").lower() != "close"
                 await self.route(method, target.split("?")[0], body, reader, writer)
                 if not keep:

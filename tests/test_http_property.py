@@ -86,3 +86,25 @@ def test_bytes_that_are_not_json_never_take_the_server_down(raw, path):
     status, _ = post(s["port"], raw, path)
     assert status in (200, 400, 404, 405), (status, raw, path)
     assert post(s["port"], json.dumps({"messages": [{"role": "user", "content": "ok"}], "max_tokens": 1}).encode())[0] == 200
+
+
+@settings(max_examples=80, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+@given(st.one_of(st.binary(max_size=120),
+                 st.builds(lambda m, p, h, b: f"{m} {p} HTTP/1.1\r\n{h}\r\n\r\n".encode("latin1", "replace") + b,
+                           st.sampled_from(["GET", "POST", "PUT", "", "G E T"]), st.text("/abc?%", max_size=12),
+                           st.sampled_from(["Content-Length: 5", "Content-Length: -1", "Content-Length: x", "Content-Length: 99999999999",
+                                            "Host: x", ": novalue", "A" * 300]), st.binary(max_size=40))))
+def test_raw_bytes_on_the_socket_never_take_the_listener_down(raw):
+    import socket
+
+    s = server()
+    with socket.create_connection(("127.0.0.1", s["port"]), timeout=5) as c:
+        c.sendall(raw)
+        c.shutdown(socket.SHUT_WR)
+        c.settimeout(5)
+        try:
+            while c.recv(4096):
+                pass
+        except (TimeoutError, ConnectionError, OSError):
+            pass
+    assert post(s["port"], json.dumps({"messages": [{"role": "user", "content": "ok"}], "max_tokens": 1}).encode())[0] == 200
