@@ -293,6 +293,9 @@ def validate(cfg: OwlConfig) -> None:
     if v["spec"]["kind"] != "none" and v["spec"]["depth"] < 1:
         raise ConfigError("spec.depth must be >= 1 when a draft head is configured")
     _validate_honoured(v)
+    from .memory import model_spec
+
+    model_spec(cfg)            # an unknown model name without a checkpoint that declares the geometry is refused here
 
 
 def _validate_honoured(v: dict) -> None:

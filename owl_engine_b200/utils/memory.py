@@ -60,9 +60,36 @@ def draft_bytes(kind: str, spec: ModelSpec) -> int:
 VISION_TOWER_BYTES = 900 << 20             # the 27-block tower in bf16 with its padded matrices
 
 
+def model_spec(cfg) -> ModelSpec:
+    """The geometry a profile talks about: the named model when the name is known, else what the checkpoint declares
+    (``config.json`` of an HF directory, the metadata of a GGUF file)."""
+    import json
+    from pathlib import Path
+
+    from .config import ConfigError
+
+    m = cfg.values["model"]
+    if m["name"] in PRESETS:
+        return PRESETS[m["name"]]()
+    p = Path(m["path"]) if m["path"] else None
+    try:
+        if p is not None and p.is_file() and p.suffix == ".gguf":
+            from ..formats import gguf
+
+            return gguf.spec_from_meta(gguf.GgufFile(p).meta)
+        if p is not None and (p / "config.json").exists():
+            from ..models.config_json import spec_from_hf_config
+
+            return spec_from_hf_config(json.loads((p / "config.json").read_text()))
+    except (KeyError, TypeError, ValueError, OSError) as e:
+        raise ConfigError(f"model.path = {m['path']!r}: the checkpoint's model description cannot be read ({e!r})") from None
+    raise ConfigError(f"model.name = {m['name']!r} is not a known model ({', '.join(sorted(PRESETS))}) and model.path names no "
+                      "checkpoint that declares its geometry")
+
+
 def estimate(cfg) -> dict:
     v = cfg.values
-    spec = PRESETS[v["model"]["name"]]()
+    spec = model_spec(cfg)
     world = max(1, len(v["parallel"]["device"])) if v["parallel"]["mode"] == "tp" else 1
     rspec = spec.sharded(0, world) if world > 1 else spec
     total = B200_HBM_BYTES

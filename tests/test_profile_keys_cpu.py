@@ -255,3 +255,39 @@ def test_lookup_history_buffer_tracks_the_sequence():
     assert lk.propose(eng, 0, 2) == [2, 3]                  # the buffer grew in place
     seq.tokens[:] = [3, 3, 7, 3, 3]                         # another history under the same id (a rewritten sequence)
     assert lk.propose(eng, 0, 1) == [7] and lk.hits == 3
+
+
+def test_any_override_of_any_key_loads_or_is_refused_with_a_config_error():
+    """Random values for random keys: the loader answers with a validated profile or a ConfigError that names the key,
+    never with another exception; what loads also survives the memory model and the preflight."""
+    from hypothesis import given, settings, strategies as st
+
+    from owl_engine_b200.formats.preflight import check_profile
+    from owl_engine_b200.utils.memory import estimate
+
+    keys = sorted(f"{sec}.{k}" for sec, ks in C.SCHEMA.items() if sec != "intent" for k in ks)
+    value = st.one_of(st.booleans(), st.integers(-3, 10 ** 7), st.floats(-2, 8, allow_nan=False), st.text("abclrfutq0123:._-/ ", max_size=10),
+                      st.lists(st.text("0123", max_size=2), max_size=9), st.sampled_from(["tp", "fp8", "tcr", "mtp", "queue:50", "lrfu:0.5"]))
+
+    def lit(v):
+        if isinstance(v, bool):
+            return "true" if v else "false"
+        if isinstance(v, str):
+            return '"' + v.replace("\\\\", "").replace('"', "") + '"'
+        if isinstance(v, list):
+            return "[" + ", ".join(lit(x) for x in v) + "]"
+        return repr(v)
+
+    @settings(max_examples=400, deadline=None)
+    @given(st.lists(st.tuples(st.sampled_from(keys), value), min_size=1, max_size=4))
+    def run(overrides):
+        sets = [f"{k}={lit(v)}" for k, v in overrides]
+        try:
+            cfg = C.load(FULL, sets)
+        except C.ConfigError as e:
+            assert str(e)
+            return
+        est = estimate(cfg)
+        assert est["kv_pool_bytes"] >= 0 and isinstance(est["fits"], bool)
+        assert all(isinstance(i.line(), str) for i in check_profile(cfg))
+    run()
