@@ -13,6 +13,7 @@ host dequant tables) and ``crates/kernels/cu/gguf/gguf.cuh`` (block layouts).
 """
 from __future__ import annotations
 
+import math
 import struct
 from dataclasses import dataclass
 from pathlib import Path
@@ -49,6 +50,20 @@ class GgufTensor:
 
 class GgufFile:
     def __init__(self, path: str | Path):
+        """Memory-map the file and read its header. A truncated or corrupted header is reported as one ``ValueError`` naming
+        the file, whatever the reader stumbled over; tensors whose data would lie outside the file are refused here too."""
+        try:
+            self._parse(path)
+        except UnsupportedGgufType:
+            raise
+        except (struct.error, OverflowError, TypeError, IndexError, KeyError, UnicodeDecodeError, RuntimeError, MemoryError) as e:
+            raise ValueError(f"{path}: truncated or corrupted GGUF header ({type(e).__name__}: {e})") from None
+        size = len(self.mm)
+        for t in self.tensors.values():
+            if t.offset < 0 or t.nbytes < 0 or t.offset + t.nbytes > size:
+                raise ValueError(f"{path}: tensor {t.name} ({t.nbytes} bytes at {t.offset}) lies outside the file ({size} bytes)")
+
+    def _parse(self, path: str | Path) -> None:
         self.path = Path(path)
         self.mm = np.memmap(self.path, dtype=np.uint8, mode="r")
         self.pos = 0
@@ -74,8 +89,10 @@ class GgufFile:
         self.data_start = (self.pos + align - 1) // align * align
         for name, shape, t, off in infos:
             tn = GGML_TYPES.get(t, f"type{t}")
-            n = int(np.prod(shape)) if shape else 1
+            n = math.prod(int(d) for d in shape) if shape else 1          # Python integers: a corrupted dimension cannot wrap
             be, bb = BLOCK.get(tn, (1, 0))
+            if len(shape) > 4 or any(d <= 0 for d in shape) or n >= 1 << 48 or n % be:
+                raise ValueError(f"{path}: tensor {name} has the impossible shape {tuple(shape)} for type {tn}")
             self.tensors[name] = GgufTensor(name, shape, tn, self.data_start + off, n // be * bb)
 
     # -- primitive readers ---------------------------------------------------------------------

@@ -24,13 +24,39 @@ _REV = {v[1]: k for k, v in _DT.items()}
 
 class SafeFile:
     def __init__(self, path: str | Path):
+        """Read the header and memory-map the data. A truncated or damaged file is refused with a ``ValueError`` naming it:
+        a header length beyond the file, a header that is not a JSON object, an entry with an unknown dtype, a shape that does
+        not match its byte range, a byte range outside the file."""
         self.path = Path(path)
-        with open(self.path, "rb") as f:
-            (n,) = struct.unpack("<Q", f.read(8))
-            self.header = json.loads(f.read(n))
-        self.base = 8 + n
-        self.meta = self.header.pop("__metadata__", {})
-        self.mm = np.memmap(self.path, dtype=np.uint8, mode="r")
+        size = self.path.stat().st_size
+        try:
+            with open(self.path, "rb") as f:
+                (n,) = struct.unpack("<Q", f.read(8))
+                if n > size - 8:
+                    raise ValueError(f"header length {n} exceeds the file ({size} bytes)")
+                self.header = json.loads(f.read(n))
+            if not isinstance(self.header, dict):
+                raise ValueError("the header is not a JSON object")
+            self.base = 8 + n
+            self.meta = self.header.pop("__metadata__", {})
+            for k, info in self.header.items():
+                if not isinstance(info, dict) or info.get("dtype") not in _DT:
+                    raise ValueError(f"tensor {k!r}: unknown dtype {info.get('dtype') if isinstance(info, dict) else info!r}")
+                shape, off = info.get("shape"), info.get("data_offsets")
+                if not isinstance(shape, list) or not all(isinstance(d, int) and d >= 0 for d in shape) or \
+                        not isinstance(off, list) or len(off) != 2 or not all(isinstance(o, int) for o in off):
+                    raise ValueError(f"tensor {k!r}: malformed shape / data_offsets")
+                numel = 1
+                for d in shape:
+                    numel *= d
+                lo, hi = off
+                if not (0 <= lo <= hi <= size - self.base) or hi - lo != numel * np.dtype(_DT[info["dtype"]][0]).itemsize:
+                    raise ValueError(f"tensor {k!r}: byte range {off} does not fit its shape {shape} or the file")
+        except (struct.error, UnicodeDecodeError, json.JSONDecodeError, AttributeError, TypeError) as e:
+            raise ValueError(f"{self.path}: truncated or corrupted safetensors header ({type(e).__name__}: {e})") from None
+        except ValueError as e:
+            raise ValueError(f"{self.path}: {e}") from None
+        self.mm = np.memmap(self.path, dtype=np.uint8, mode="r") if size > self.base else np.zeros(0, dtype=np.uint8)
 
     def keys(self):
         return self.header.keys()

@@ -85,3 +85,46 @@ def test_safetensors_round_trips_every_dtype_and_rank(tmp_path_factory, spec):
     for name, t in tensors.items():
         got = back.get(name)
         assert got.dtype == t.dtype and got.shape == t.shape and torch.equal(got, t)
+
+
+@settings(max_examples=300, deadline=None)
+@given(st.integers(0, 2), st.lists(st.tuples(st.integers(0, 400), st.integers(0, 255)), min_size=1, max_size=6), st.integers(10, 62),
+       st.integers(0, 10 ** 6))
+def test_damaged_container_files_are_refused_with_a_value_error(mode, flips, big, cut):
+    """Truncated files, flipped header bytes and absurd 64-bit counts: the GGUF and safetensors readers either read the file
+    or raise ``ValueError`` (``UnsupportedGgufType`` for a type id they do not decode) -- nothing else, and quickly."""
+    import os
+    import tempfile
+    import time
+
+    d = tempfile.mkdtemp(prefix="owl_fuzz_")
+    a = np.random.default_rng(0).standard_normal((4, 64)).astype(np.float32)
+    gguf.write_gguf(os.path.join(d, "ok.gguf"), {"general.architecture": "qwen35", "x.list": [1, 2, 3], "x.s": "hello", "x.f": 1.5},
+                    {"t.weight": (a.shape, "F32", a.view(np.uint8).reshape(-1)), "q.weight": (a.shape, "Q8_0", gguf.quantize_q8_0(a))})
+    sf.save_file({"a": torch.from_numpy(a), "b": torch.arange(6).view(2, 3).to(torch.bfloat16)}, os.path.join(d, "ok.safetensors"))
+    for name in ("ok.gguf", "ok.safetensors"):
+        good = open(os.path.join(d, name), "rb").read()
+        b = bytearray(good)
+        if mode == 0:
+            b = b[:cut % len(b)]
+        elif mode == 1:
+            for pos, val in flips:
+                b[pos % min(len(b), 300)] = val
+        else:
+            p = flips[0][0] % (min(len(b), 300) - 8)
+            b[p:p + 8] = (1 << big).to_bytes(8, "little")
+        path = os.path.join(d, "bad" + os.path.splitext(name)[1])
+        open(path, "wb").write(bytes(b))
+        t0 = time.time()
+        try:
+            if name.endswith(".gguf"):
+                f = gguf.GgufFile(path)
+                for n in f.tensors:
+                    f.dequant(n)
+            else:
+                f = sf.SafeFile(path)
+                for n in f.keys():
+                    f.get(n)
+        except (ValueError, gguf.UnsupportedGgufType):
+            pass
+        assert time.time() - t0 < 2.0
