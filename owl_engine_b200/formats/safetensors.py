@@ -40,8 +40,8 @@ class SafeFile:
             self.base = 8 + n
             self.meta = self.header.pop("__metadata__", {})
             for k, info in self.header.items():
-                if not isinstance(info, dict) or info.get("dtype") not in _DT:
-                    raise ValueError(f"tensor {k!r}: unknown dtype {info.get('dtype') if isinstance(info, dict) else info!r}")
+                if not isinstance(info, dict) or not isinstance(info.get("dtype"), str):
+                    raise ValueError(f"tensor {k!r}: malformed entry")
                 shape, off = info.get("shape"), info.get("data_offsets")
                 if not isinstance(shape, list) or not all(isinstance(d, int) and d >= 0 for d in shape) or \
                         not isinstance(off, list) or len(off) != 2 or not all(isinstance(o, int) for o in off):
@@ -50,8 +50,11 @@ class SafeFile:
                 for d in shape:
                     numel *= d
                 lo, hi = off
-                if not (0 <= lo <= hi <= size - self.base) or hi - lo != numel * np.dtype(_DT[info["dtype"]][0]).itemsize:
-                    raise ValueError(f"tensor {k!r}: byte range {off} does not fit its shape {shape} or the file")
+                if not (0 <= lo <= hi <= size - self.base):
+                    raise ValueError(f"tensor {k!r}: byte range {off} lies outside the file")
+                # a dtype this reader does not decode (a newer format) is only an error when that tensor is asked for
+                if info["dtype"] in _DT and hi - lo != numel * np.dtype(_DT[info["dtype"]][0]).itemsize:
+                    raise ValueError(f"tensor {k!r}: byte range {off} does not fit its shape {shape}")
         except (struct.error, UnicodeDecodeError, json.JSONDecodeError, AttributeError, TypeError) as e:
             raise ValueError(f"{self.path}: truncated or corrupted safetensors header ({type(e).__name__}: {e})") from None
         except ValueError as e:
@@ -63,6 +66,8 @@ class SafeFile:
 
     def get(self, name: str) -> torch.Tensor:
         info = self.header[name]
+        if info["dtype"] not in _DT:
+            raise ValueError(f"{self.path}: tensor {name!r} has dtype {info['dtype']}, which this reader does not decode")
         npdt, tdt = _DT[info["dtype"]]
         lo, hi = info["data_offsets"]
         raw = self.mm[self.base + lo:self.base + hi]
