@@ -262,9 +262,12 @@ class App:
             if self.vision is None:
                 raise BadRequest("this server was started without a vision tower; image parts are not accepted")
             loop0 = asyncio.get_running_loop()
-            ids, images, evict_spans = await loop0.run_in_executor(
-                None, self.vision.expand, ids, [im["data"] for im in req.images], [im["evict"] for im in req.images],
-                self.vision_wrap())
+            try:
+                ids, images, evict_spans = await loop0.run_in_executor(
+                    None, self.vision.expand, ids, [im["data"] for im in req.images], [im["evict"] for im in req.images],
+                    self.vision_wrap())
+            except ValueError as e:          # bytes that are not an image this server decodes: the client's fault, not ours
+                raise BadRequest(f"image cannot be decoded: {e}") from None
         max_new = min(req.max_tokens or self.default_max_new, self.max_new_cap)
         opts = TurnOpts(max_new=max_new, ignore_eos=req.ignore_eos, sampling=req.sampling(self.default_sampling),
                         eos_ids=tuple(self.tok.eos_ids), session=req.session, images=images,

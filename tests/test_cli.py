@@ -77,3 +77,61 @@ def test_needle_and_ladder_fixtures_against_scripted_server():
         assert rows[0]["hit_rate"] == 0.0 and rows[0]["words"] == 50        # the scripted reply never contains the value
         lad = needle.run_ladder(c, [30], new_tokens=8)
         assert lad[0]["error"] is None and lad[0]["prompt_tokens"] > 30
+
+
+def test_png_decoder_reads_every_filter_and_refuses_damaged_files():
+    """Images come from clients: all five row filters decode (checked against rows filtered here, independently of the
+    writer), and truncated, flipped or lying files raise ValueError before anything large is allocated."""
+    import random
+    import struct
+    import zlib
+
+    import numpy as np
+    import pytest
+
+    from owl_engine_b200.cli import png
+
+    rng = np.random.default_rng(0)
+    h, w, bpp = 20, 30, 3
+    img = rng.integers(0, 256, (h, w, bpp), dtype=np.uint8)
+
+    def paeth(a, b, c):
+        p = a + b - c
+        pa, pb, pc = abs(p - a), abs(p - b), abs(p - c)
+        return a if pa <= pb and pa <= pc else (b if pb <= pc else c)
+    raw, prev = bytearray(), np.zeros(w * bpp, dtype=np.int32)
+    for y in range(h):
+        f, line = y % 5, img[y].reshape(-1).astype(np.int32)
+        enc = np.zeros_like(line)
+        for i in range(w * bpp):
+            a, b, c = (line[i - bpp] if i >= bpp else 0), prev[i], (prev[i - bpp] if i >= bpp else 0)
+            enc[i] = (line[i] - {0: 0, 1: a, 2: b, 3: (a + b) // 2, 4: paeth(a, b, c)}[f]) & 255
+        raw.append(f)
+        raw += enc.astype(np.uint8).tobytes()
+        prev = line
+    chunk = lambda t, b: struct.pack(">I", len(b)) + t + b + struct.pack(">I", zlib.crc32(t + b) & 0xFFFFFFFF)
+    sig = bytes([0x89]) + b"PNG" + bytes([13, 10, 26, 10])
+    good = sig + chunk(b"IHDR", struct.pack(">IIBBBBB", w, h, 8, 2, 0, 0, 0)) + chunk(b"IDAT", zlib.compress(bytes(raw))) + chunk(b"IEND", b"")
+    assert np.array_equal(png.decode_png(good), img)
+    huge = sig + chunk(b"IHDR", struct.pack(">IIBBBBB", 2 ** 31 - 1, 2 ** 31 - 1, 8, 2, 0, 0, 0)) + chunk(b"IDAT", zlib.compress(b"x"))
+    with pytest.raises(ValueError, match="sides must be"):
+        png.decode_png(huge)
+    bomb = sig + chunk(b"IHDR", struct.pack(">IIBBBBB", 4, 4, 8, 2, 0, 0, 0)) + chunk(b"IDAT", zlib.compress(bytes(50_000_000)))
+    with pytest.raises(ValueError, match="inflates to"):
+        png.decode_png(bomb)                                # a small header with a large stream behind it is cut off, not inflated
+    rnd = random.Random(3)
+    for _ in range(600):
+        b = bytearray(good)
+        mode = rnd.randrange(3)
+        if mode == 0:
+            b = b[:rnd.randrange(len(b))]
+        elif mode == 1:
+            for _ in range(rnd.randrange(1, 5)):
+                b[rnd.randrange(len(b))] = rnd.randrange(256)
+        else:
+            b = bytearray(rnd.randbytes(rnd.randrange(0, 120)))
+        try:
+            out = png.decode_png(bytes(b))
+            assert out.shape[2] == 3
+        except ValueError:
+            pass

@@ -141,9 +141,10 @@ def test_message_points_are_page_aligned_ascending_and_keep_the_ends(stream, pag
     assert pts == sorted(set(pts)) and all(p % page == 0 and p > 0 for p in pts) and set(pts) <= set(cand)
     if cand:
         assert pts[0] == cand[0]                                    # the first boundary is always kept
-        assert set(cand[len(cand) - recent:] if recent else []) <= set(pts)      # and the newest `recent`
-        middle = [p for p in pts if p not in cand[len(cand) - recent:]] if recent else pts
+        tail = cand[max(0, len(cand) - recent):] if recent else []
+        assert set(tail) <= set(pts)                                # and the newest `recent`
+        middle = [p for p in pts if p not in tail]
         assert all(b - a >= min_gap for a, b in zip(middle, middle[1:]))          # the rest keep their distance
     cls = P.classify(pts, len(toks), recent)
     assert len(cls) == len(pts) and all(c in ("dense", "binary", "extra") for c, _ in cls)
-    assert [c for c, _ in cls[len(cls) - recent:]] == ["dense"] * min(recent, len(cls)) if recent else True
+    assert [c for c, _ in cls[max(0, len(cls) - recent):]] == ["dense"] * min(recent, len(cls)) if recent else True
