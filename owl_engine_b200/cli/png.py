@@ -36,6 +36,7 @@ def encode_png(w: int, h: int, rgb: tuple, box: tuple | None = None, box_rgb: tu
 
 
 MAX_PNG_SIDE = 16384          # images come from clients: the header's claims are checked before anything is allocated
+MAX_PNG_PIXELS = 64 << 20     # 64 Mpixel (an 8k x 8k screenshot): about 200 MB decoded
 
 
 def decode_png(data: bytes):
@@ -66,8 +67,8 @@ def decode_png(data: bytes):
     w, h, depth, ctype, comp, filt, interlace = hdr
     if depth != 8 or ctype not in (2, 6) or interlace != 0 or comp != 0 or filt != 0:
         raise ValueError("only 8-bit RGB / RGBA non-interlaced PNGs are accepted")
-    if not (0 < w <= MAX_PNG_SIDE and 0 < h <= MAX_PNG_SIDE):
-        raise ValueError(f"PNG of {w} x {h} pixels (sides must be 1..{MAX_PNG_SIDE})")
+    if not (0 < w <= MAX_PNG_SIDE and 0 < h <= MAX_PNG_SIDE) or w * h > MAX_PNG_PIXELS:
+        raise ValueError(f"PNG of {w} x {h} pixels (sides must be 1..{MAX_PNG_SIDE}, at most {MAX_PNG_PIXELS >> 20} Mpixel)")
     bpp = 3 if ctype == 2 else 4
     stride = w * bpp
     want = h * (stride + 1)
