@@ -106,3 +106,26 @@ def test_streamed_content_ends_before_the_first_stop_string_whatever_the_token_b
     for c in chunks:
         piece = c["choices"][0]["delta"].get("content", "")
         assert "\\ufffd" not in piece.encode("unicode_escape").decode()
+
+
+@settings(max_examples=300, deadline=None)
+@given(st.text(alphabet=st.characters(blacklist_categories=("Cs",)), max_size=80),
+       st.lists(st.sampled_from(["<|im_start|>", "<|im_end|>", "<think>", "</think>", "<tool_call>", "<|image_pad|>"]), max_size=4),
+       st.randoms(use_true_random=False))
+def test_byte_tokenizer_round_trips_and_the_stream_decoder_never_cuts_a_character(text, specials, rnd):
+    from owl_engine_b200.engine.tokenizer import ByteTokenizer, StreamDecoder
+
+    tok = ByteTokenizer()
+    parts = [text[i:i + 7] for i in range(0, len(text), 7)] or [""]
+    for sp in specials:
+        parts.insert(rnd.randrange(len(parts) + 1), sp)
+    full = "".join(parts)
+    ids = tok.encode(full)
+    assert tok.decode(ids) == full
+    assert all(0 <= t < tok.vocab_size for t in ids)
+    dec, out = StreamDecoder(tok), []
+    for t in ids:
+        piece = dec.push(t)
+        assert "\\ufffd" not in piece.encode("unicode_escape").decode() or "\\ufffd" in full.encode("unicode_escape").decode()
+        out.append(piece)
+    assert "".join(out) == full
