@@ -207,6 +207,8 @@ def lenient_json(s: str):
         return json.loads(t), False
     except json.JSONDecodeError:
         pass
+    except RecursionError:                    # nesting deeper than the interpreter's stack: the model ran away, not JSON
+        raise ValueError("nesting") from None
     return _Lenient(t).value(), True
 
 
@@ -251,12 +253,12 @@ class ToolSchemas:
         """Bare JSON, or JSON wrapped in JSON quotes (``"512"`` -> 512); ``...`` (Ellipsis) when it is neither."""
         try:
             v = json.loads(raw.strip())
-        except json.JSONDecodeError:
+        except (json.JSONDecodeError, RecursionError):
             return ...
         if isinstance(v, str):
             try:
                 return json.loads(v.strip())
-            except json.JSONDecodeError:
+            except (json.JSONDecodeError, RecursionError):
                 return v
         return v
 
@@ -304,7 +306,7 @@ def _args_string(args) -> str:
         try:
             json.loads(args)
             return args
-        except json.JSONDecodeError:
+        except (json.JSONDecodeError, RecursionError):
             try:
                 return json.dumps(lenient_json(args)[0], ensure_ascii=False)
             except ValueError:

@@ -1,6 +1,8 @@
 """Server parts without a server: the output splitter on recorded shapes, the repeat guard, the chat template, exact rejection sampling."""
 import json
 
+import pytest
+
 from owl_engine_b200.server.chat_tpl import ChatTemplate
 from owl_engine_b200.server.toolcall import ChannelSplitter, RepeatGuard, parse_tool_body
 
@@ -157,3 +159,19 @@ def test_rejection_sampling_is_exact():
         first[d if m == 1 else nxt] += 1
     for t, pv in p0.items():
         assert abs(first[t] / n - pv) < 0.015
+
+
+def test_runaway_nesting_in_a_tool_block_is_a_malformed_item_not_a_crash():
+    from owl_engine_b200.server.toolcall import ChannelSplitter, lenient_json
+
+    for s in ("[" * 100000, '{"a":' * 50000):
+        with pytest.raises(ValueError):
+            lenient_json(s)
+    tools = [{"type": "function", "function": {"name": "f", "parameters": {"type": "object", "properties": {"a": {"type": "array"}}}}}]
+    deep = "[" * 50000 + "]" * 50000
+    sp = ChannelSplitter(tools=tools)
+    ev = sp.feed('<tool_call>{"name": "f", "arguments": ' + deep + "}</tool_call>") + sp.finish()
+    assert [e[0] for e in ev] == ["malformed"] and sp.malformed == 1
+    sp = ChannelSplitter(tools=tools)
+    ev = sp.feed("<tool_call><function=f><parameter=a>" + deep + "</parameter></function></tool_call>after") + sp.finish()
+    assert [e[0] for e in ev] == ["tool_call", "text"]              # the argument stays a string; the stream goes on
