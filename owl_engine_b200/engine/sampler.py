@@ -55,7 +55,7 @@ def apply_rep_penalty(cands: list[tuple[int, float]], history: set, penalty: flo
 
 def distribution(cands: list[tuple[int, float]], p: SamplingParams) -> list[tuple[int, float]]:
     """(token, probability) after temperature, top-k and top-p, sorted by probability (descending)."""
-    c = sorted(cands, key=lambda x: -x[1])[:max(1, p.topk)]
+    c = sorted(cands, key=lambda x: (-x[1], x[0]))[:max(1, p.topk)]        # equal logits: the smaller id first, whatever order they came in
     t = max(p.temp, 1e-5)
     m = c[0][1]
     w = [math.exp((l - m) / t) for _, l in c]
@@ -73,7 +73,7 @@ def distribution(cands: list[tuple[int, float]], p: SamplingParams) -> list[tupl
 
 def sample(cands: list[tuple[int, float]], p: SamplingParams, turn: int, step: int, history: set | None = None) -> int:
     if p.mode == "greedy" or p.temp <= 0:
-        return max(apply_rep_penalty(cands, history or set(), p.rep_penalty), key=lambda x: x[1])[0]
+        return max(apply_rep_penalty(cands, history or set(), p.rep_penalty), key=lambda x: (x[1], -x[0]))[0]
     dist = distribution(apply_rep_penalty(cands, history or set(), p.rep_penalty), p)
     u = XorShift64Star(step_seed(p.seed, turn, step)).uniform()
     acc = 0.0

@@ -1,0 +1,50 @@
+"""Properties of the host sampler: the draw is a function of (seed, turn, step), stays inside the candidates and their top-k /
+top-p cut, and the extreme settings reduce to the arg max."""
+import math
+
+from hypothesis import given, settings, strategies as st
+
+from owl_engine_b200.engine import sampler as S
+
+cands = st.lists(st.tuples(st.integers(0, 10 ** 5), st.floats(-30, 30, allow_nan=False)), min_size=1, max_size=32,
+                 unique_by=lambda c: c[0])
+params = st.builds(S.SamplingParams, st.just("sampling"), st.floats(0.0, 3.0), st.integers(1, 40), st.floats(0.01, 1.0),
+                   st.floats(0.8, 1.5), st.integers(0, 2 ** 40))
+
+
+@settings(max_examples=400)
+@given(cands, params, st.integers(0, 1000), st.integers(0, 5000), st.sets(st.integers(0, 10 ** 5), max_size=6))
+def test_draws_are_reproducible_and_stay_inside_the_cut(c, p, turn, step, history):
+    tok = S.sample(c, p, turn, step, history)
+    assert tok == S.sample(list(reversed(c)), p, turn, step, history)        # a function of the values, not of their order
+    assert tok in {t for t, _ in c}
+    pen = S.apply_rep_penalty(c, history, p.rep_penalty)
+    dist = S.distribution(pen, p)
+    assert abs(sum(q for _, q in dist) - 1.0) < 1e-9 and len(dist) <= min(p.topk, len(c))
+    assert all(a[1] >= b[1] - 1e-12 for a, b in zip(dist, dist[1:]))          # sorted by probability
+    if p.temp > 0:
+        assert tok in {t for t, _ in dist}
+    top = sorted(pen, key=lambda x: (-x[1], x[0]))[:p.topk]
+    assert {t for t, _ in dist} <= {t for t, _ in top}
+
+
+@settings(max_examples=200)
+@given(cands, st.integers(0, 2 ** 40), st.integers(0, 100), st.integers(0, 100))
+def test_extreme_settings_reduce_to_the_arg_max(c, seed, turn, step):
+    best = max(c, key=lambda x: x[1])[1]
+    winners = {t for t, l in c if l == best}
+    assert S.sample(c, S.SamplingParams("greedy"), turn, step) in winners
+    assert S.sample(c, S.SamplingParams("sampling", 0.0, 20, 0.95, 1.0, seed), turn, step) in winners
+    assert S.sample(c, S.SamplingParams("sampling", 1.0, 1, 1.0, 1.0, seed), turn, step) in winners          # top-k = 1
+    if len(winners) == 1 and all(l <= best - 1e-3 for t, l in c if t not in winners):
+        assert S.sample(c, S.SamplingParams("sampling", 1e-4, 20, 1.0, 1.0, seed), turn, step) in winners    # temperature -> 0
+
+
+@settings(max_examples=60)
+@given(st.integers(0, 2 ** 60))
+def test_the_generator_is_uniform_enough_and_never_stalls(seed):
+    r = S.XorShift64Star(seed)
+    xs = [r.uniform() for _ in range(2000)]
+    assert all(0.0 <= x < 1.0 for x in xs) and 0.45 < sum(xs) / len(xs) < 0.55 and len(set(xs)) > 1990
+    assert S.step_seed(seed, 1, 2) != S.step_seed(seed, 2, 1) and S.step_seed(seed, 0, 0) != 0
+    assert not math.isnan(xs[0])
