@@ -418,11 +418,25 @@ class SpecRunner:
             engine.runner.capture_fold(n_rows).replay()
             st.folds += 1
         seq.tokens.extend(emitted)
-        seq.n_cached += n_rows
+        pos = seq.n_cached
+        if engine.cfg.snap_decode_stride:
+            from ..store.snap_policy import decode_boundary
+
+            b = decode_boundary(pos, pos + n_rows, PAGE, engine.cfg.snap_decode_stride)
+            if b is not None and b < pos + n_rows:
+                # the round stepped over a page boundary: roll the state back to the round's start, replay the rows up to the
+                # boundary, save that state as the sequence's rolling snapshot, then replay the accepted rows again
+                engine.pool.copy_slot(engine.spec_row, seq.slot)
+                engine.runner.fold_slot.fill_(seq.slot)
+                engine.runner.capture_fold(b - pos).replay()
+                seq.n_cached = b
+                engine._tail_snapshot(seq, pos)
+                engine.pool.copy_slot(engine.spec_row, seq.slot)
+                engine.runner.capture_fold(n_rows).replay()
+                st.folds += 2
+        seq.n_cached = pos + n_rows
         if engine.cfg.snap_decode_stride and seq.n_cached % PAGE == 0:
-            # the round ended exactly on a page boundary: the row holds that boundary's state (a boundary crossed in the
-            # middle of a round is left to a later round; the rolling snapshot trails by a few pages at most)
-            engine._tail_snapshot(seq, seq.n_cached - n_rows)
+            engine._tail_snapshot(seq, pos)         # the round ended exactly on a boundary: the row holds that boundary's state
         draft.observe(engine, sid, n_rows, emitted)
         st.rounds += 1
         st.drafted += len(drafts)
