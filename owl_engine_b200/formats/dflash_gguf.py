@@ -18,7 +18,6 @@ Reference counterpart: ``crates/models/src/formats/gguf/draft.rs:1-275`` (name t
 """
 from __future__ import annotations
 
-import torch
 
 from ..models import dflash2 as D
 from . import gguf

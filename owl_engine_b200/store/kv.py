@@ -12,7 +12,7 @@ block is the KV page, 16 tokens by default).
 from __future__ import annotations
 
 import ctypes
-from ctypes import POINTER, c_int, c_int8, c_int32, c_uint64, c_void_p
+from ctypes import c_int, c_int8, c_int32, c_uint64, c_void_p
 
 import numpy as np
 

@@ -1,6 +1,5 @@
 """The relocation facade on the CPU: a small pool of plain tensors goes through pressure (device -> host -> disk -> drop),
 recall in its three modes, a checkpoint and the adoption of the disk tier's index by a fresh store, as after a restart."""
-import numpy as np
 import pytest
 import torch
 

@@ -2,7 +2,6 @@
 mirroring wrapper against a follower loop on a recording engine, and the ``[parallel]`` refusals of the server."""
 import multiprocessing as mp
 import os
-import time
 
 import pytest
 import torch
