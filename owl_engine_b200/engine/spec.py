@@ -496,13 +496,44 @@ class SpecRunner:
                 r.fold_tlen[:len(grp)].copy_(torch.tensor(tlen, dtype=torch.int32))
                 graph.replay()
                 st.folds += 1
+            pos0 = [engine.seqs[sid].n_cached for sid in grp]
+            for i, sid in enumerate(grp):
+                engine.seqs[sid].tokens.extend(emit[i])
+            if engine.cfg.snap_decode_stride:
+                from ..store.snap_policy import decode_boundary
+
+                # sequences whose round stepped over a page boundary: roll them back together, replay each up to its
+                # boundary (one batched fold), save the states, then replay their accepted rows (a second batched fold)
+                cross = []
+                for i, sid in enumerate(grp):
+                    b = decode_boundary(pos0[i], pos0[i] + acc[i] + 1, PAGE, engine.cfg.snap_decode_stride)
+                    if b is not None and b < pos0[i] + acc[i] + 1:
+                        cross.append((i, sid, b))
+                if cross:
+                    r = engine.runner
+                    graph = r.capture_fold_batch(len(grp), t)
+                    for phase in (0, 1):
+                        sl, tl = [-1] * len(grp), [0] * len(grp)
+                        for i, sid, b in cross:
+                            seq = engine.seqs[sid]
+                            engine.pool.copy_slot(engine.spec_row + i, seq.slot)
+                            sl[i], tl[i] = seq.slot, (b - pos0[i]) if phase == 0 else acc[i] + 1
+                        r.fold_slots[:len(grp)].copy_(torch.tensor(sl, dtype=torch.int32))
+                        r.fold_tlen[:len(grp)].copy_(torch.tensor(tl, dtype=torch.int32))
+                        graph.replay()
+                        st.folds += 1
+                        if phase == 0:
+                            for i, sid, b in cross:
+                                seq = engine.seqs[sid]
+                                seq.n_cached = b
+                                engine._tail_snapshot(seq, pos0[i])
+                                seq.n_cached = pos0[i]
             for i, sid in enumerate(grp):
                 seq, n_rows = engine.seqs[sid], acc[i] + 1
                 emitted = emit[i]
-                seq.tokens.extend(emitted)
-                seq.n_cached += n_rows
+                seq.n_cached = pos0[i] + n_rows
                 if engine.cfg.snap_decode_stride and seq.n_cached % PAGE == 0:
-                    engine._tail_snapshot(seq, seq.n_cached - n_rows)
+                    engine._tail_snapshot(seq, pos0[i])
                 self.draft_of(sid).observe(engine, sid, n_rows, emitted, row0=i * t)
                 st.rounds += 1
                 st.drafted += d

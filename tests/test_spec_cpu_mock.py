@@ -59,6 +59,36 @@ def test_batched_rounds_through_the_running_engine():
     assert ("foldb", 3, 4) in e.runner.graphs                     # the batched fold ran for the three of them
 
 
+def test_batched_rounds_save_the_boundaries_they_step_over():
+    prompts = [toks(40 + 7 * i, 20 + i) for i in range(3)]
+    plain = Engine(cfg(), device="cpu")
+    want = [plain.generate(p, 70) for p in prompts]
+    e = Engine(cfg(snap_decode_stride=1, n_snap_rows=16), device="cpu")        # rows enough that nothing is evicted in this test
+    spec = SpecRunner(LookupDraft(2, 8), depth=3, degrade_below=-1.0)
+    spec.per_sid = {i: OracleDraft(want[i], len(prompts[i]), 2, 512) for i in range(3)}
+    sids = [e.add_sequence(p) for p in prompts]
+    outs = [[e.prefill(s)] for s in sids]
+    for s in sids:
+        spec.after_prefill(e, s)
+    while min(len(o) for o in outs) < 60:
+        for o, em in zip(outs, spec.round_batch(e, sids)):
+            o.extend(em)
+    for i, s in enumerate(sids):
+        seq = e.seqs[s]
+        assert outs[i] == want[i][:len(outs[i])]
+        tail = e.states.snaps[seq.tail_hash]
+        assert tail.klass == "tail" and tail.n_tokens == seq.n_cached // 16 * 16        # never a whole page behind
+    n_cached = [e.seqs[s].n_cached for s in sids]
+    for s in sids:
+        e.free_sequence(s)
+    for i, p in enumerate(prompts):                                # the next turn of each resumes at its rolling snapshot
+        follow = p + outs[i][:n_cached[i] - len(p) + 1] + toks(9, 30 + i)
+        sid = e.add_sequence(follow)
+        assert e.seqs[sid].reused == n_cached[i] // 16 * 16
+        e.free_sequence(sid, publish=False)
+        assert e.generate(follow, 5) == Engine(cfg(), device="cpu").generate(follow, 5)
+
+
 def test_lookup_finds_a_repeat_and_its_rejected_drafts_are_rolled_back():
     base = toks(23, 2)
     prompt = base * 3 + base[:9]
