@@ -71,6 +71,7 @@ class EngineConfig:
     snap_msg_min_gap: int = 2048   # tokens between kept message boundaries (the first and the newest `recent` are always kept)
     snap_msg_recent: int = 4
     snap_decode_stride: int = 0    # pages of generated text between rolling snapshots (0 = generation takes none)
+    snap_spec_rollback: bool = False   # speculative rounds that step over a page boundary roll back and save it (two extra folds)
     snap_session_cap: int = 0      # snapshots one session may hold over all tiers (0 = unbounded)
     snap_structural_reserve: int = 4
     snap_host_mb: int = 0          # host memory for snapshots whose state row was recycled

@@ -419,7 +419,7 @@ class SpecRunner:
             st.folds += 1
         seq.tokens.extend(emitted)
         pos = seq.n_cached
-        if engine.cfg.snap_decode_stride:
+        if engine.cfg.snap_decode_stride and engine.cfg.snap_spec_rollback:
             from ..store.snap_policy import decode_boundary
 
             b = decode_boundary(pos, pos + n_rows, PAGE, engine.cfg.snap_decode_stride)
@@ -499,7 +499,7 @@ class SpecRunner:
             pos0 = [engine.seqs[sid].n_cached for sid in grp]
             for i, sid in enumerate(grp):
                 engine.seqs[sid].tokens.extend(emit[i])
-            if engine.cfg.snap_decode_stride:
+            if engine.cfg.snap_decode_stride and engine.cfg.snap_spec_rollback:
                 from ..store.snap_policy import decode_boundary
 
                 # sequences whose round stepped over a page boundary: roll them back together, replay each up to its

@@ -185,7 +185,7 @@ def build_engine_factory(cfg: C.OwlConfig, plan: dict | None = None, msg_open_id
                             msg_open_ids=tuple(msg_open_ids) if st["prefix_cache"] and sg["snap_max"] > 0 else (),
                             snap_msg_min_gap=sg["snap_msg_min_gap"], snap_msg_recent=sg["snap_msg_recent"],
                             snap_decode_stride=sg["snap_decode_stride"] if st["prefix_cache"] and sg["snap_max"] > 0 else 0,
-                            snap_session_cap=sg["snap_session_cap"], snap_structural_reserve=sg["snap_structural_reserve"],
+                            snap_spec_rollback=sg["snap_spec_rollback"], snap_session_cap=sg["snap_session_cap"], snap_structural_reserve=sg["snap_structural_reserve"],
                             attn_splits=v["kernel"]["attn_splits"], cuda_graph=v["cuda"]["graph"],
                             pinned_segment_mb=v["cuda"]["pinned_segment_mb"],
                             rope_yarn=(rp["yarn_factor"], rp["original_max"], rp["beta_fast"], rp["beta_slow"],

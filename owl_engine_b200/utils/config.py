@@ -63,7 +63,7 @@ SCHEMA: dict = {
               "snap_disk_mb": int, "disk_dir": str, "vram_budget": float, "vram_reserve_mb": int, "no_reclaim": bool,
               "block_tokens": Enum(16, 32), "evict_policy": str},
     "store.kv": {"kv_dtype": Enum("fp8", "int8", "bf16", "f16"), "draft_kv_dtype": Enum("bf16", "fp8")},
-    "store.gdn": {"gdn_slots": int, "snap_decode_stride": int, "snap_max": int, "snap_msg_min_gap": int,
+    "store.gdn": {"gdn_slots": int, "snap_decode_stride": int, "snap_spec_rollback": bool, "snap_max": int, "snap_msg_min_gap": int,
                   "snap_msg_recent": int, "snap_session_cap": int, "snap_structural_reserve": int},
     "spec": {"depth": int, "draft_path": str, "kind": Enum("none", "mtp", "dflash2"), "lookup": bool, "lookup_nmin": int,
              "lookup_nmax": int, "lookup_nstrong": int, "lookup_agree": int, "mtp_window": int, "mtp_sink": int, "mtp_ring": bool, "adaptive_depth": bool,

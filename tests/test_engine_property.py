@@ -63,7 +63,7 @@ def test_running_engine_under_random_traffic_serves_what_a_cold_engine_serves(op
     from owl_engine_b200.engine.running import RunningEngine, TurnOpts
 
     kw = dict(model="test-hybrid", n_slots=3, max_seqs=3, max_seq=1024, prefill_chunk=64, msg_open_ids=MARK, snap_msg_min_gap=32,
-              snap_msg_recent=2, snap_decode_stride=1)
+              snap_msg_recent=2, snap_decode_stride=1, snap_spec_rollback=True)
     cold = Engine(EngineConfig(n_pages=256, n_snap_rows=2, prefix_cache=False, **kw), device="cpu")
     from owl_engine_b200.engine.spec import LookupDraft, SpecRunner
 
@@ -141,7 +141,8 @@ def test_follower_rank_ends_in_the_leaders_state(ops, park, spec):
     from owl_engine_b200.engine.spec import LookupDraft, SpecRunner
 
     kw = dict(model="test-hybrid", n_pages=40, n_slots=3, n_snap_rows=2, spec_rows=2, max_seqs=3, max_seq=1024, prefill_chunk=64,
-              msg_open_ids=MARK, snap_msg_min_gap=32, snap_msg_recent=2, snap_decode_stride=1, host_cache_mb=1, snap_host_mb=1)
+              msg_open_ids=MARK, snap_msg_min_gap=32, snap_msg_recent=2, snap_decode_stride=1, snap_spec_rollback=True, host_cache_mb=1,
+              snap_host_mb=1)
     lead, foll = Engine(EngineConfig(**kw), device="cpu"), Engine(EngineConfig(**kw), device="cpu")
     name = f"/owl_prop_tp_{os.getpid()}_{abs(hash(str(ops))) % 10 ** 8}"
     ring = StepRing.create(name, 1, capacity=8 << 20)

@@ -63,7 +63,7 @@ def test_batched_rounds_save_the_boundaries_they_step_over():
     prompts = [toks(40 + 7 * i, 20 + i) for i in range(3)]
     plain = Engine(cfg(), device="cpu")
     want = [plain.generate(p, 70) for p in prompts]
-    e = Engine(cfg(snap_decode_stride=1, n_snap_rows=16), device="cpu")        # rows enough that nothing is evicted in this test
+    e = Engine(cfg(snap_decode_stride=1, snap_spec_rollback=True, n_snap_rows=16), device="cpu")        # rows enough that nothing is evicted in this test
     spec = SpecRunner(LookupDraft(2, 8), depth=3, degrade_below=-1.0)
     spec.per_sid = {i: OracleDraft(want[i], len(prompts[i]), 2, 512) for i in range(3)}
     sids = [e.add_sequence(p) for p in prompts]
@@ -128,7 +128,7 @@ def test_forced_acceptance_harness_emits_the_drafts():
 def test_generation_snapshots_are_taken_when_a_round_lands_on_a_page_boundary():
     prompt = toks(60, 5)
     want = Engine(cfg(), device="cpu").generate(prompt, 80)
-    e = Engine(cfg(snap_decode_stride=1), device="cpu")
+    e = Engine(cfg(snap_decode_stride=1, snap_spec_rollback=True), device="cpu")
     spec = SpecRunner(OracleDraft(want, len(prompt), 2, 512), depth=3, degrade_below=-1.0)
     sid = e.add_sequence(prompt)
     out = [e.prefill(sid)]
