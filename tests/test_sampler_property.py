@@ -48,3 +48,37 @@ def test_the_generator_is_uniform_enough_and_never_stalls(seed):
     assert all(0.0 <= x < 1.0 for x in xs) and 0.45 < sum(xs) / len(xs) < 0.55 and len(set(xs)) > 1990
     assert S.step_seed(seed, 1, 2) != S.step_seed(seed, 2, 1) and S.step_seed(seed, 0, 0) != 0
     assert not math.isnan(xs[0])
+
+
+@settings(max_examples=300)
+@given(st.lists(st.one_of(st.tuples(st.just("append"), st.lists(st.integers(0, 6), min_size=1, max_size=9)),
+                          st.tuples(st.just("truncate"), st.integers(0, 30)),
+                          st.tuples(st.just("rewrite"), st.lists(st.integers(0, 6), min_size=0, max_size=30))), min_size=1, max_size=25),
+       st.integers(1, 3), st.integers(3, 8), st.integers(1, 5))
+def test_lookup_history_buffer_always_answers_like_a_fresh_search(ops, nmin, nmax, k):
+    """The lookup keeps a growing array per sequence instead of converting the token list every round: whatever happens to
+    the list (appends, rollbacks, another history under the same id), its answer equals a search over the list itself;
+    and the answer is a real continuation of a real earlier occurrence."""
+    from types import SimpleNamespace
+
+    from owl_engine_b200.engine.spec import LookupDraft, suffix_lookup
+
+    seq = SimpleNamespace(tokens=[])
+    eng = SimpleNamespace(seqs={7: seq})
+    lk = LookupDraft(nmin, nmax)
+    for op, arg in ops:
+        if op == "append":
+            seq.tokens += arg
+        elif op == "truncate":
+            del seq.tokens[max(0, len(seq.tokens) - arg):]
+        else:
+            seq.tokens[:] = arg
+        got = lk.find(eng, 7, k)
+        want = suffix_lookup(list(seq.tokens), k, nmin, nmax)
+        assert got == want
+        if got is not None:
+            follow, m = got
+            t = seq.tokens
+            assert nmin <= m <= nmax and 1 <= len(follow) <= k
+            ends = [e for e in range(m - 1, len(t) - 1) if t[e - m + 1:e + 1] == t[len(t) - m:] and t[e + 1:e + 1 + len(follow)] == follow]
+            assert ends                                                    # it followed an earlier occurrence of the last m tokens
