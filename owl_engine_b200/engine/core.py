@@ -96,6 +96,7 @@ class Sequence:
     q_ring: object = None          # KV selection: the newest queries of this sequence, bf16 [window, hq, hd] (ring by step)
     q_ring_pos: object = None      # their rope positions, int32 [window]
     q_ring_n: int = 0              # queries recorded so far
+    tokens_epoch: int = 0          # bumped by every edit of ``tokens`` other than an append (host-side caches of the history key on it)
     gap_from: int = None           # first token index after which the KV is carried memory (leave-gap deletions); None = exact
     images: list = field(default_factory=list)    # [(first token index, merged embeddings [n, H], fingerprint)]
     pos3: object = None            # multimodal (t, h, w) position ids of the prompt, int32 [3, n_prompt] (None = text only)
@@ -481,6 +482,7 @@ class Engine:
         for lo, hi in reversed(ranges):
             del seq.tokens[lo:hi]
             removed += hi - lo
+        seq.tokens_epoch += 1
         if seq.pos3 is not None:
             keep_tok = torch.ones(seq.pos3.shape[1], dtype=torch.bool)
             for lo, hi in ranges:
@@ -713,6 +715,7 @@ class Engine:
         """Replace the sequence's newest token (the host sampled something other than the device's argmax). The next
         step reads it as its input, so under tensor parallelism this call is mirrored to every rank."""
         self.seqs[sid].tokens[-1] = int(tok)
+        self.seqs[sid].tokens_epoch += 1
 
     def _kvmem_view(self, seq: Sequence, pos: int) -> int:
         """Bounded attention view of a long sequence: sink blocks + recent blocks + the best-scoring blocks of the rest,

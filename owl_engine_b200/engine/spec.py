@@ -126,25 +126,30 @@ class LookupDraft:
         self.min_match, self.max_match = min_match, max_match
         self.nstrong = min_match if nstrong is None else nstrong
         self.agree = agree
-        self._hist: dict = {}          # sid -> (array with spare room, valid length)
+        self._hist: dict = {}          # sid -> (array with spare room, valid length, epoch)
         self.hits = self.lookups = 0
 
-    def _array(self, sid: int, toks: list):
-        buf, n = self._hist.get(sid, (None, 0))
+    def _array(self, sid: int, toks: list, epoch: int = 0):
+        """The history as an array. Between two calls the list may have grown or been cut at its end; every other edit
+        (tokens removed from the middle, the newest token replaced) is announced by a new ``epoch`` and rebuilds the array.
+        The last few tokens of the part already held are compared as well, so an unannounced edit near the end is caught."""
+        buf, n, ep = self._hist.get(sid, (None, 0, 0))
         m = len(toks)
-        if buf is None or m < n or m > len(buf) or (n and buf[n - 1] != toks[n - 1]):
+        g = min(n, 8)
+        if buf is None or ep != epoch or m < n or m > len(buf) or (g and buf[n - g:n].tolist() != list(toks[n - g:n])):
             buf = np.empty(max(1024, 2 * m), dtype=np.int64)
             buf[:m] = toks
         elif m > n:
             buf[n:m] = toks[n:m]
-        self._hist[sid] = (buf, m)
+        self._hist[sid] = (buf, m, epoch)
         if len(self._hist) > 64:
             self._hist.pop(next(iter(self._hist)))
         return buf[:m]
 
     def find(self, engine: Engine, sid: int, depth: int):
         self.lookups += 1
-        r = suffix_lookup(self._array(sid, engine.seqs[sid].tokens), depth, self.min_match, self.max_match)
+        seq = engine.seqs[sid]
+        r = suffix_lookup(self._array(sid, seq.tokens, getattr(seq, "tokens_epoch", 0)), depth, self.min_match, self.max_match)
         if r is not None:
             self.hits += 1
         return r

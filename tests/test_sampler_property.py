@@ -57,13 +57,13 @@ def test_the_generator_is_uniform_enough_and_never_stalls(seed):
        st.integers(1, 3), st.integers(3, 8), st.integers(1, 5))
 def test_lookup_history_buffer_always_answers_like_a_fresh_search(ops, nmin, nmax, k):
     """The lookup keeps a growing array per sequence instead of converting the token list every round: whatever happens to
-    the list (appends, rollbacks, another history under the same id), its answer equals a search over the list itself;
+    the list (appends, rollbacks, announced rewrites), its answer equals a search over the list itself;
     and the answer is a real continuation of a real earlier occurrence."""
     from types import SimpleNamespace
 
     from owl_engine_b200.engine.spec import LookupDraft, suffix_lookup
 
-    seq = SimpleNamespace(tokens=[])
+    seq = SimpleNamespace(tokens=[], tokens_epoch=0)
     eng = SimpleNamespace(seqs={7: seq})
     lk = LookupDraft(nmin, nmax)
     for op, arg in ops:
@@ -73,6 +73,7 @@ def test_lookup_history_buffer_always_answers_like_a_fresh_search(ops, nmin, nma
             del seq.tokens[max(0, len(seq.tokens) - arg):]
         else:
             seq.tokens[:] = arg
+            seq.tokens_epoch += 1                                          # in-place edits are announced
         got = lk.find(eng, 7, k)
         want = suffix_lookup(list(seq.tokens), k, nmin, nmax)
         assert got == want

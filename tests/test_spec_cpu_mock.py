@@ -147,3 +147,25 @@ def test_generation_snapshots_are_taken_when_a_round_lands_on_a_page_boundary():
     assert e.seqs[sid].reused == tails[0].n_tokens                 # the next turn resumes at the rolling snapshot
     e.free_sequence(sid, publish=False)
     assert e.generate(follow, 6) == Engine(cfg(), device="cpu").generate(follow, 6)
+
+
+def test_the_engines_own_token_edits_reach_the_lookups_history():
+    """Replacing the newest token and excising a page range both edit the history in place; the lookup's array follows."""
+    from owl_engine_b200.engine.core import PAGE
+    from owl_engine_b200.engine.spec import suffix_lookup
+
+    e = Engine(cfg(), device="cpu")
+    lk = LookupDraft(1, 4)
+    base = toks(PAGE, 5)
+    sid = e.add_sequence(base * 3 + base[:5], reuse=False)
+    e.prefill(sid)
+    seq = e.seqs[sid]
+    assert lk.find(e, sid, 3) == suffix_lookup(seq.tokens, 3, 1, 4)
+    ep = seq.tokens_epoch
+    e.set_last_token(sid, (seq.tokens[-1] + 1) % 50)
+    assert seq.tokens_epoch == ep + 1 and lk.find(e, sid, 3) == suffix_lookup(seq.tokens, 3, 1, 4)
+    n = len(seq.tokens)
+    e.drop_ranges(sid, [(PAGE, 2 * PAGE)])
+    seq.tokens.extend(base[:PAGE])                                 # back to the old length before the next lookup
+    assert len(seq.tokens) == n and seq.tokens_epoch == ep + 2
+    assert lk.find(e, sid, 3) == suffix_lookup(seq.tokens, 3, 1, 4)
