@@ -62,16 +62,23 @@ class HfTokenizer:
 
 
 class StreamDecoder:
-    """Incremental detokenisation that never emits half of a multi-byte character."""
+    """Incremental detokenisation that never emits half of a multi-byte character.
+
+    Each token decodes a short window of ids, not the whole answer: ``ids[prefix:read]`` is the part of the window whose text
+    is already out, and the new text is what decoding ``ids[prefix:]`` adds to it (a tokenizer may render a token differently
+    after its neighbours -- a leading space, a merged byte pair -- so the window keeps the previous emission as context).
+    The window moves up only when text was emitted, so it always starts where a character ended; a long answer costs the
+    same per token as a short one."""
 
     def __init__(self, tok):
-        self.tok, self.ids, self.emitted = tok, [], 0
+        self.tok, self.ids = tok, []
+        self.prefix = self.read = 0
 
     def push(self, token: int) -> str:
         self.ids.append(token)
-        text = self.tok.decode(self.ids)
-        if text.endswith("�"):
-            return ""
-        delta = text[self.emitted:]
-        self.emitted = len(text)
-        return delta
+        done = self.tok.decode(self.ids[self.prefix:self.read])
+        full = self.tok.decode(self.ids[self.prefix:])
+        if len(full) <= len(done) or full.endswith("\ufffd"):
+            return ""                                   # nothing new yet, or the last character is still incomplete
+        self.prefix, self.read = self.read, len(self.ids)
+        return full[len(done):]

@@ -83,3 +83,32 @@ def test_lookup_history_buffer_always_answers_like_a_fresh_search(ops, nmin, nma
             assert nmin <= m <= nmax and 1 <= len(follow) <= k
             ends = [e for e in range(m - 1, len(t) - 1) if t[e - m + 1:e + 1] == t[len(t) - m:] and t[e + 1:e + 1 + len(follow)] == follow]
             assert ends                                                    # it followed an earlier occurrence of the last m tokens
+
+
+@settings(max_examples=300)
+@given(st.lists(st.one_of(st.integers(0, 265), st.sampled_from(list("aé€😀 \n".encode()))), min_size=0, max_size=60))
+def test_streamed_text_is_the_decoded_text_and_each_token_decodes_a_short_window(ids):
+    """Whatever the ids (valid UTF-8, stray continuation bytes, specials), the pieces a stream emits join to the decoded
+    whole, except for a tail that still ends in an incomplete character; and no push decodes more than the two latest
+    emissions' worth of ids."""
+    from owl_engine_b200.engine.tokenizer import ByteTokenizer, StreamDecoder
+
+    class Counting(ByteTokenizer):
+        longest = 0
+
+        def decode(self, ids):
+            ids = list(ids)
+            self.longest = max(self.longest, len(ids))
+            return super().decode(ids)
+
+    tok = Counting()
+    d = StreamDecoder(tok)
+    out = "".join(d.push(t) for t in ids)
+    whole = ByteTokenizer().decode(ids)
+    assert whole.startswith(out)
+    rest = whole[len(out):]
+    assert rest == "" or rest.endswith("�")
+    text = [ord("x")] * 500
+    tok2 = Counting()
+    d2 = StreamDecoder(tok2)
+    assert "".join(d2.push(t) for t in text) == "x" * 500 and tok2.longest <= 2
