@@ -6,6 +6,8 @@ random-init weights. Reference counterpart: ``crates/models/src/tokenizer.rs``.
 """
 from __future__ import annotations
 
+import re
+
 
 class ByteTokenizer:
     SPECIALS = ["<|im_start|>", "<|im_end|>", "<|endoftext|>", "<think>", "</think>", "<tool_call>", "</tool_call>",
@@ -17,18 +19,16 @@ class ByteTokenizer:
         self.id_special = {v: k for k, v in self.special_ids.items()}
         self.eos_ids = [self.special_ids["<|im_end|>"], self.special_ids["<|endoftext|>"]]
         self.image_pad_id = self.special_ids["<|image_pad|>"]
+        self._split = re.compile("(" + "|".join(re.escape(x) for x in self.SPECIALS) + ")")
 
     def encode(self, text: str) -> list[int]:
-        out, i = [], 0
-        while i < len(text):
-            for s, sid in self.special_ids.items():
-                if text.startswith(s, i):
-                    out.append(sid)
-                    i += len(s)
-                    break
-            else:
-                out.extend(text[i].encode("utf-8"))
-                i += 1
+        out = []
+        for part in self._split.split(text):              # specials (leftmost first, list order on a tie) and the text between
+            sid = self.special_ids.get(part)
+            if sid is not None:
+                out.append(sid)
+            elif part:
+                out.extend(part.encode("utf-8"))
         return out
 
     def decode(self, ids) -> str:

@@ -112,3 +112,23 @@ def test_streamed_text_is_the_decoded_text_and_each_token_decodes_a_short_window
     tok2 = Counting()
     d2 = StreamDecoder(tok2)
     assert "".join(d2.push(t) for t in text) == "x" * 500 and tok2.longest <= 2
+
+
+@settings(max_examples=300)
+@given(st.lists(st.one_of(st.sampled_from(["<|im_start|>", "<|im_end|>", "<think>", "</think>", "<tool_call>", "<|image_pad|>", "<", "|", ">", "im_"]),
+                          st.text(max_size=6)), max_size=12))
+def test_byte_tokenizer_round_trips_text_with_specials_and_their_fragments(parts):
+    """encode then decode gives the text back (lone surrogates aside, which UTF-8 cannot carry), specials take one id each,
+    and fragments of specials stay bytes."""
+    from owl_engine_b200.engine.tokenizer import ByteTokenizer
+
+    tok = ByteTokenizer()
+    text = "".join(parts)
+    try:
+        text.encode("utf-8")
+    except UnicodeEncodeError:
+        return
+    ids = tok.encode(text)
+    assert tok.decode(ids) == text
+    assert sum(1 for t in ids if t >= 256) == sum(text.count(s) for s in tok.SPECIALS)
+    assert all(0 <= t < 256 + len(tok.SPECIALS) for t in ids)
